@@ -1,0 +1,309 @@
+// Bandwidth-bound glue kernels: embedding gather, (skip-)RMSNorm, SwiGLU, rotary embedding fused
+// with the KV-page append, and fp8 page quantisation.
+//
+// Reference counterparts: skip_rmsnorm_* / rmsnorm_* (crates/onnx-runtime-ep-cuda/src/kernels/
+// normalization.rs:1327), rotary_embedding_* (kernels/rotary_embedding.rs:45,620-640),
+// gqa_fuse_decode_prep* / gqa_append_cache* (kernels/group_query_attention.rs:33-140), silu_mul_*
+// (kernels/elementwise.rs), gather (kernels/gather.rs).  Out-of-range token ids, positions or
+// slots set kStatusIndexOutOfRange in the status word and the access is skipped, following the
+// capture-error-word convention of that code base.
+#include <cuda_fp8.h>
+#include "common.cuh"
+#include "ogb_kernels.h"
+
+namespace ogb {
+
+// ------------------------------------------------------------------------------------------
+// embedding gather: out[t, :] = table[ids[t], :]
+// ------------------------------------------------------------------------------------------
+__global__ void embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                                 __nv_bfloat16* __restrict__ out, int hidden, int vocab, int* status) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicOr(status, kStatusIndexOutOfRange);
+    id = 0;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(table + static_cast<size_t>(id) * hidden);
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * hidden);
+  for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dst[i] = __ldg(src + i);
+}
+
+// ------------------------------------------------------------------------------------------
+// RMSNorm with fp32 statistics; optional residual add written back (SkipSimplifiedLayerNorm)
+// ------------------------------------------------------------------------------------------
+constexpr int kNormThreads = 256;
+constexpr int kNormMaxVec = 4;  // cached 16-byte vectors per thread (hidden <= 8192 stays in registers)
+
+__global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(__nv_bfloat16* x, const __nv_bfloat16* __restrict__ delta,
+                                                                const __nv_bfloat16* __restrict__ weight,
+                                                                __nv_bfloat16* __restrict__ out, int hidden, int ldx,
+                                                                int ldo, float eps) {
+  const int row = blockIdx.x;
+  __nv_bfloat16* xr = x + static_cast<size_t>(row) * ldx;
+  const __nv_bfloat16* dr = delta ? delta + static_cast<size_t>(row) * hidden : nullptr;
+  const int nvec = hidden / 8;
+  float cache[kNormMaxVec][8];
+  float ss = 0.f;
+  int c = 0;
+  for (int i = threadIdx.x; i < nvec; i += kNormThreads, ++c) {
+    uint4 v = reinterpret_cast<const uint4*>(xr)[i];
+    float f[8];
+    float2 t;
+    t = unpack_bf16(v.x); f[0] = t.x; f[1] = t.y;
+    t = unpack_bf16(v.y); f[2] = t.x; f[3] = t.y;
+    t = unpack_bf16(v.z); f[4] = t.x; f[5] = t.y;
+    t = unpack_bf16(v.w); f[6] = t.x; f[7] = t.y;
+    if (dr) {
+      uint4 d = reinterpret_cast<const uint4*>(dr)[i];
+      t = unpack_bf16(d.x); f[0] += t.x; f[1] += t.y;
+      t = unpack_bf16(d.y); f[2] += t.x; f[3] += t.y;
+      t = unpack_bf16(d.z); f[4] += t.x; f[5] += t.y;
+      t = unpack_bf16(d.w); f[6] += t.x; f[7] += t.y;
+      // the residual stream is stored in bf16: round first so the statistics see the stored value
+      uint4 w4 = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+      reinterpret_cast<uint4*>(xr)[i] = w4;
+      t = unpack_bf16(w4.x); f[0] = t.x; f[1] = t.y;
+      t = unpack_bf16(w4.y); f[2] = t.x; f[3] = t.y;
+      t = unpack_bf16(w4.z); f[4] = t.x; f[5] = t.y;
+      t = unpack_bf16(w4.w); f[6] = t.x; f[7] = t.y;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      ss += f[k] * f[k];
+      if (c < kNormMaxVec) cache[c][k] = f[k];
+    }
+  }
+  __shared__ float red[kNormThreads / 32];
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < kNormThreads / 32; ++i) tot += red[i];
+  const float inv = rsqrtf(tot / static_cast<float>(hidden) + eps);
+  __nv_bfloat16* orow = out + static_cast<size_t>(row) * ldo;
+  c = 0;
+  for (int i = threadIdx.x; i < nvec; i += kNormThreads, ++c) {
+    float f[8];
+    if (c < kNormMaxVec) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) f[k] = cache[c][k];
+    } else {
+      uint4 v = reinterpret_cast<const uint4*>(xr)[i];
+      float2 t;
+      t = unpack_bf16(v.x); f[0] = t.x; f[1] = t.y;
+      t = unpack_bf16(v.y); f[2] = t.x; f[3] = t.y;
+      t = unpack_bf16(v.z); f[4] = t.x; f[5] = t.y;
+      t = unpack_bf16(v.w); f[6] = t.x; f[7] = t.y;
+    }
+    uint4 wv = __ldg(reinterpret_cast<const uint4*>(weight) + i);
+    float2 w0 = unpack_bf16(wv.x), w1 = unpack_bf16(wv.y), w2 = unpack_bf16(wv.z), w3 = unpack_bf16(wv.w);
+    uint4 o4 = make_uint4(pack_bf16(f[0] * inv * w0.x, f[1] * inv * w0.y), pack_bf16(f[2] * inv * w1.x, f[3] * inv * w1.y),
+                          pack_bf16(f[4] * inv * w2.x, f[5] * inv * w2.y), pack_bf16(f[6] * inv * w3.x, f[7] * inv * w3.y));
+    reinterpret_cast<uint4*>(orow)[i] = o4;
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// out[r, j] = silu(gate_up[r, j]) * gate_up[r, inter + j]   (unfused fallback of the GEMM epilogue)
+// ------------------------------------------------------------------------------------------
+__global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int inter,
+                                size_t total_vec) {
+  const int vec_per_row = inter / 8;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total_vec;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t row = i / vec_per_row;
+    const int cv = static_cast<int>(i % vec_per_row);
+    const uint4 g = reinterpret_cast<const uint4*>(gu + row * 2 * inter)[cv];
+    const uint4 u = reinterpret_cast<const uint4*>(gu + row * 2 * inter + inter)[cv];
+    const uint32_t gs[4] = {g.x, g.y, g.z, g.w}, us[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 a = unpack_bf16(gs[k]), b = unpack_bf16(us[k]);
+      o[k] = pack_bf16(a.x / (1.f + __expf(-a.x)) * b.x, a.y / (1.f + __expf(-a.y)) * b.y);
+    }
+    reinterpret_cast<uint4*>(out + row * inter)[cv] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// RoPE (q and k, in place) + append of k, v to the paged pool.
+// One CTA per token; thread = one (head, pair-chunk).  cos_sin: [max_pos, rotary_dim/2, 2] fp32.
+// ------------------------------------------------------------------------------------------
+template <bool FP8>
+__global__ void rope_kv_append_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                                      const int64_t* __restrict__ slots, const float* __restrict__ cos_sin,
+                                      void* __restrict__ pool, float* __restrict__ scales, int hq, int hkv, int d,
+                                      int rotary_dim, int interleaved, int page_size, int64_t num_slots, int max_pos,
+                                      int* status) {
+  const int t = blockIdx.x;
+  int pos = positions[t];
+  const int64_t slot = slots[t];
+  if (pos < 0 || pos >= max_pos) {
+    if (threadIdx.x == 0) atomicOr(status, kStatusIndexOutOfRange);
+    pos = 0;
+  }
+  const bool slot_ok = slot >= 0 && slot < num_slots;  // slot < 0: token is not cached (padding row)
+  if (!slot_ok && slot >= num_slots && threadIdx.x == 0) atomicOr(status, kStatusIndexOutOfRange);
+  __nv_bfloat16* row = qkv + static_cast<size_t>(t) * (hq + 2 * hkv) * d;
+  const int half = rotary_dim / 2;
+  const float* cs = cos_sin + static_cast<size_t>(pos) * half * 2;
+  // rotate q and k heads
+  const int rot_heads = hq + hkv;
+  for (int i = threadIdx.x; i < rot_heads * half; i += blockDim.x) {
+    const int h = i / half, j = i % half;
+    __nv_bfloat16* hp = row + h * d;
+    const int i0 = interleaved ? 2 * j : j;
+    const int i1 = interleaved ? 2 * j + 1 : j + half;
+    const float c = cs[2 * j], s = cs[2 * j + 1];
+    const float x0 = __bfloat162float(hp[i0]), x1 = __bfloat162float(hp[i1]);
+    hp[i0] = __float2bfloat16(x0 * c - x1 * s);
+    hp[i1] = __float2bfloat16(x1 * c + x0 * s);
+  }
+  __syncthreads();
+  if (!slot_ok) return;
+  const int64_t page = slot / page_size;
+  const int off = static_cast<int>(slot % page_size);
+  if constexpr (!FP8) {
+    __nv_bfloat16* pl = static_cast<__nv_bfloat16*>(pool);
+    const int vec_per_head = d / 8;
+    for (int i = threadIdx.x; i < 2 * hkv * vec_per_head; i += blockDim.x) {
+      const int kv = i / (hkv * vec_per_head);  // 0 = K, 1 = V
+      const int h = (i / vec_per_head) % hkv;
+      const int v = i % vec_per_head;
+      const uint4 val = reinterpret_cast<const uint4*>(row + (hq + kv * hkv + h) * d)[v];
+      __nv_bfloat16* dst = pl + ((((page * hkv + h) * 2 + kv) * page_size + off) * static_cast<int64_t>(d));
+      reinterpret_cast<uint4*>(dst)[v] = val;
+    }
+  } else {
+    // e4m3 pages with one scale per (page, head, k|v).  The first token written to a page fixes
+    // the scale (amax * 2 / 448, so later tokens have headroom); later tokens saturate to it.
+    uint8_t* pl = static_cast<uint8_t*>(pool);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int u = warp; u < 2 * hkv; u += nwarps) {
+      const int kv = u / hkv, h = u % hkv;
+      const __nv_bfloat16* src = row + (hq + kv * hkv + h) * d;
+      float amax = 0.f;
+      for (int j = lane; j < d; j += 32) amax = fmaxf(amax, fabsf(__bfloat162float(src[j])));
+      amax = warp_max(amax);
+      float* sc = scales + ((page * hkv + h) * 2 + kv);
+      float scale;
+      if (off == 0) {
+        scale = fmaxf(amax * 2.f, 1e-6f) / 448.f;
+        if (lane == 0) *sc = scale;
+      } else {
+        scale = *sc;
+        if (!(scale > 0.f)) scale = fmaxf(amax * 2.f, 1e-6f) / 448.f;
+      }
+      const float inv = 1.f / scale;
+      uint8_t* dst = pl + ((((page * hkv + h) * 2 + kv) * page_size + off) * static_cast<int64_t>(d));
+      for (int j = lane; j < d; j += 32) {
+        float v = __bfloat162float(src[j]) * inv;
+        v = fminf(fmaxf(v, -448.f), 448.f);
+        dst[j] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// page copy (copy-on-write fork) and gather / scatter to a staging buffer (swap out / in)
+// ------------------------------------------------------------------------------------------
+__global__ void page_copy_kernel(uint8_t* dst_base, const uint8_t* src_base, const int64_t* __restrict__ src_pages,
+                                 const int64_t* __restrict__ dst_pages, int64_t page_bytes, int src_indexed,
+                                 int dst_indexed) {
+  const int i = blockIdx.y;
+  const int64_t sp = src_indexed ? src_pages[i] : i;
+  const int64_t dp = dst_indexed ? dst_pages[i] : i;
+  const uint4* src = reinterpret_cast<const uint4*>(src_base + sp * page_bytes);
+  uint4* dst = reinterpret_cast<uint4*>(dst_base + dp * page_bytes);
+  const int64_t nvec = page_bytes / 16;
+  for (int64_t v = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; v < nvec;
+       v += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    dst[v] = src[v];
+}
+
+}  // namespace ogb
+
+using namespace ogb;
+
+extern "C" int ogb_embedding_bf16(const int* ids, const void* table, void* out, int tokens, int hidden, int vocab,
+                                  int* status, void* stream) {
+  if (tokens <= 0) return 0;
+  if (hidden % 8) return -3;
+  embedding_kernel<<<tokens, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      ids, static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out), hidden, vocab, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int ogb_rmsnorm_bf16(void* x, const void* delta, const void* weight, void* out, int rows, int hidden, int ldx,
+                                int ldo, float eps, void* stream) {
+  if (rows <= 0) return 0;
+  if (hidden % 8 || ldx % 8 || ldo % 8) return -3;
+  rmsnorm_kernel<<<rows, kNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(weight),
+      static_cast<__nv_bfloat16*>(out), hidden, ldx, ldo, eps);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int ogb_silu_mul_bf16(const void* gate_up, void* out, int rows, int inter, void* stream) {
+  if (rows <= 0) return 0;
+  if (inter % 8) return -3;
+  const size_t total_vec = static_cast<size_t>(rows) * (inter / 8);
+  int blocks = static_cast<int>((total_vec + 255) / 256);
+  const int cap = ogb_num_sms() * 8;
+  if (blocks > cap) blocks = cap;
+  silu_mul_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(gate_up),
+                                                                          static_cast<__nv_bfloat16*>(out), inter, total_vec);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int ogb_rope_kv_append_bf16(void* qkv, const int* positions, const int64_t* slots, const float* cos_sin,
+                                       void* pool, int tokens, int hq, int hkv, int d, int rotary_dim, int interleaved,
+                                       int page_size, int64_t num_slots, int max_pos, int* status, void* stream) {
+  if (tokens <= 0) return 0;
+  if (d % 8 || rotary_dim % 2 || rotary_dim > d) return -3;
+  rope_kv_append_kernel<false><<<tokens, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(qkv), positions, slots, cos_sin, pool, nullptr, hq, hkv, d, rotary_dim, interleaved,
+      page_size, num_slots, max_pos, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int ogb_rope_kv_append_fp8(void* qkv, const int* positions, const int64_t* slots, const float* cos_sin,
+                                      void* pool, float* scales, int tokens, int hq, int hkv, int d, int rotary_dim,
+                                      int interleaved, int page_size, int64_t num_slots, int max_pos, int* status,
+                                      void* stream) {
+  if (tokens <= 0) return 0;
+  if (d % 8 || rotary_dim % 2 || rotary_dim > d) return -3;
+  rope_kv_append_kernel<true><<<tokens, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(qkv), positions, slots, cos_sin, pool, scales, hq, hkv, d, rotary_dim, interleaved,
+      page_size, num_slots, max_pos, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+static int launch_page_copy(void* dst, const void* src, const int64_t* sp, const int64_t* dp, int n, int64_t page_bytes,
+                            int si, int di, void* stream) {
+  if (n <= 0) return 0;
+  if (page_bytes % 16) return -3;
+  int bx = static_cast<int>((page_bytes / 16 + 255) / 256);
+  if (bx > 64) bx = 64;
+  dim3 grid(bx, n);
+  page_copy_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint8_t*>(dst),
+                                                                         static_cast<const uint8_t*>(src), sp, dp,
+                                                                         page_bytes, si, di);
+  return static_cast<int>(cudaGetLastError());
+}
+extern "C" int ogb_kv_page_copy(void* pool, const int64_t* src_pages, const int64_t* dst_pages, int n, int64_t page_bytes,
+                                void* stream) {
+  return launch_page_copy(pool, pool, src_pages, dst_pages, n, page_bytes, 1, 1, stream);
+}
+extern "C" int ogb_kv_gather_pages(const void* pool, void* staging, const int64_t* pages, int n, int64_t page_bytes,
+                                   void* stream) {
+  return launch_page_copy(staging, pool, pages, nullptr, n, page_bytes, 1, 0, stream);
+}
+extern "C" int ogb_kv_scatter_pages(void* pool, const void* staging, const int64_t* pages, int n, int64_t page_bytes,
+                                    void* stream) {
+  return launch_page_copy(pool, staging, nullptr, pages, n, page_bytes, 0, 1, stream);
+}

@@ -1,0 +1,391 @@
+// Dense bf16 GEMM for sm_100a:  C[M,N] = A[M,K] * W[N,K]^T  (+bias) (+residual) | SwiGLU.
+//
+// This is the projection GEMM of the decoder (qkv, o_proj, gate_up, down_proj, lm_head).  It
+// takes the place of the library GEMMs the reference calls for MatMul / Gemm / FusedMatMulBias
+// (crates/onnx-runtime-ep-cuda/src/blas.rs:305,430, kernels/matmul.rs:649) and of its dense
+// GEMV (kernels/matmul.rs:732-748); the SwiGLU epilogue covers the silu_mul glue
+// (kernels/elementwise.rs) and the residual epilogue covers the bias-slot residual add of
+// optimizer.rs:42-60.
+//
+// Design (one CTA per SM, persistent over output tiles):
+//   warp 0      : TMA producer.  One elected lane streams 128x64 (A) and BNx64 (W) bf16 tiles,
+//                 128-byte swizzled, into a shared-memory ring and arms a "full" mbarrier.
+//   warp 1      : allocates TMEM, then one elected lane issues tcgen05.mma (M=128, N=BN, K=16)
+//                 four times per ring stage; tcgen05.commit releases the stage ("empty") and,
+//                 at the end of a tile, publishes the accumulator ("tmem_full").
+//   warps 2..5  : epilogue.  Each warp owns one 32-lane quarter of TMEM, reads the fp32
+//                 accumulator with tcgen05.ld, applies the epilogue and writes bf16 rows.
+//   TMEM holds two accumulators so the epilogue of tile i overlaps the main loop of tile i+1.
+// Every wait is bounded; a wait that runs out sets kStatusWaitTimeout in *status, the CTA
+// drains and frees its TMEM, and the kernel returns.
+#include "common.cuh"
+#include "ogb_kernels.h"
+
+extern "C" int ogb_num_sms() {
+  static int num_sms = 0;
+  if (num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (num_sms <= 0) num_sms = 148;
+  }
+  return num_sms;
+}
+
+namespace ogb {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;  // 64 bf16 = one 128-byte swizzle row
+constexpr int kGemmThreads = 192;
+
+enum GemmEpilogue : int { kEpiNone = 0, kEpiResidual = 1, kEpiSwiGLU = 2 };
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kStageA = kBM * kBK * 2;
+  static constexpr int kStageB = BN * kBK * 2;
+  static constexpr int kStage = kStageA + kStageB;
+  static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
+  static constexpr int kSmemBytes = kStages * kStage + 1024 /*align slack*/ + 256 /*barriers*/;
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                         __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias,
+                         const __nv_bfloat16* residual, float* __restrict__ C_f32, int M, int N, int K, int ldc, int ldr,
+                         int* status) {
+  using Cfg = GemmCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStage);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + Cfg::kStages;
+  uint64_t* tmem_full = bars + 2 * Cfg::kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_tiles = (M + kBM - 1) / kBM;
+  const int n_tiles = (N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int k_blocks = (K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < Cfg::kStages; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * kBM;
+        const int n0 = (tile / m_tiles) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; break; }
+          uint8_t* sa = smem + stage * Cfg::kStage;
+          uint8_t* sb = sa + Cfg::kStageA;
+          mbar_expect_tx(&full_bar[stage], Cfg::kStage);
+          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * kBK, m0);
+          tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBK, n0);
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) { atomicOr(status, kStatusWaitTimeout); *abort_flag = 1; }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(kBM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_addr = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::kStage);
+          const uint32_t sb = sa + Cfg::kStageA;
+          const uint64_t da = make_kmajor_sw128_desc(sa);
+          const uint64_t db = make_kmajor_sw128_desc(sb);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            // advance 16 bf16 = 32 bytes inside the swizzle row: +2 in the (>>4) address field
+            umma_f16(d_addr, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&tmem_full[acc]);
+      }
+      if (!ok) { atomicOr(status, kStatusWaitTimeout); *abort_flag = 1; }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    bool ok = true;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const int m0 = (tile % m_tiles) * kBM;
+      const int n_tile = tile / m_tiles;
+      const int n0 = n_tile * BN;
+      // every lane polls (each needs the acquire); the vote keeps the warp converged for tcgen05.ld
+      if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full[acc], acc_phase))) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      if constexpr (EPI == kEpiSwiGLU) {
+        constexpr int HALF = BN / 2;
+        const int out_n = N / 2;
+#pragma unroll 1
+        for (int c = 0; c < HALF / 32; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(t_row + c * 32, g);
+          tmem_ld_32x32(t_row + HALF + c * 32, u);
+          tmem_ld_wait();
+          const int col = n_tile * HALF + c * 32;
+          if (row < M && col < out_n) {
+            uint32_t o[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
+              float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
+              float s0 = g0 / (1.f + __expf(-g0)) * u0;
+              float s1 = g1 / (1.f + __expf(-g1)) * u1;
+              o[j] = pack_bf16(s0, s1);
+            }
+            __nv_bfloat16* dst = C + static_cast<size_t>(row) * ldc + col;
+            if (col + 32 <= out_n) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v)
+                reinterpret_cast<uint4*>(dst)[v] = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+            } else {
+              for (int j = 0; j < 32 && col + j < out_n; ++j) {
+                float2 f = unpack_bf16(o[j >> 1]);
+                dst[j] = __float2bfloat16((j & 1) ? f.y : f.x);
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c * 32, r);
+          tmem_ld_wait();
+          const int col = n0 + c * 32;
+          if (row < M && col < N) {
+            const bool full = (col + 32 <= N);
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            if (bias != nullptr) {
+              if (full) {
+#pragma unroll
+                for (int j4 = 0; j4 < 4; ++j4) {
+                  uint4 b = __ldg(reinterpret_cast<const uint4*>(bias + col) + j4);
+                  float2 f;
+                  f = unpack_bf16(b.x); v[8 * j4 + 0] += f.x; v[8 * j4 + 1] += f.y;
+                  f = unpack_bf16(b.y); v[8 * j4 + 2] += f.x; v[8 * j4 + 3] += f.y;
+                  f = unpack_bf16(b.z); v[8 * j4 + 4] += f.x; v[8 * j4 + 5] += f.y;
+                  f = unpack_bf16(b.w); v[8 * j4 + 6] += f.x; v[8 * j4 + 7] += f.y;
+                }
+              } else {
+                for (int j = 0; j < 32 && col + j < N; ++j) v[j] += __bfloat162float(bias[col + j]);
+              }
+            }
+            if constexpr (EPI == kEpiResidual) {
+              const __nv_bfloat16* rs = residual + static_cast<size_t>(row) * ldr + col;
+              if (full) {
+#pragma unroll
+                for (int j4 = 0; j4 < 4; ++j4) {
+                  uint4 b = reinterpret_cast<const uint4*>(rs)[j4];
+                  float2 f;
+                  f = unpack_bf16(b.x); v[8 * j4 + 0] += f.x; v[8 * j4 + 1] += f.y;
+                  f = unpack_bf16(b.y); v[8 * j4 + 2] += f.x; v[8 * j4 + 3] += f.y;
+                  f = unpack_bf16(b.z); v[8 * j4 + 4] += f.x; v[8 * j4 + 5] += f.y;
+                  f = unpack_bf16(b.w); v[8 * j4 + 6] += f.x; v[8 * j4 + 7] += f.y;
+                }
+              } else {
+                for (int j = 0; j < 32 && col + j < N; ++j) v[j] += __bfloat162float(rs[j]);
+              }
+            }
+            if (C_f32 != nullptr) {
+              float* dst = C_f32 + static_cast<size_t>(row) * ldc + col;
+              if (full) {
+#pragma unroll
+                for (int j4 = 0; j4 < 8; ++j4)
+                  reinterpret_cast<float4*>(dst)[j4] = make_float4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]);
+              } else {
+                for (int j = 0; j < 32 && col + j < N; ++j) dst[j] = v[j];
+              }
+            } else {
+              __nv_bfloat16* dst = C + static_cast<size_t>(row) * ldc + col;
+              if (full) {
+#pragma unroll
+                for (int j4 = 0; j4 < 4; ++j4)
+                  reinterpret_cast<uint4*>(dst)[j4] =
+                      make_uint4(pack_bf16(v[8 * j4], v[8 * j4 + 1]), pack_bf16(v[8 * j4 + 2], v[8 * j4 + 3]),
+                                 pack_bf16(v[8 * j4 + 4], v[8 * j4 + 5]), pack_bf16(v[8 * j4 + 6], v[8 * j4 + 7]));
+              } else {
+                for (int j = 0; j < 32 && col + j < N; ++j) dst[j] = __float2bfloat16(v[j]);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+    }
+    if (!ok && lane == 0) { atomicOr(status, kStatusWaitTimeout); *abort_flag = 1; }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0 && threadIdx.x == 0) {
+    // A wait ran out: give copies that may still be in flight a bounded time to land.
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) { __nanosleep(1000); }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// host side
+// ----------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  }
+  return fn;
+}
+
+// 2-D row-major bf16 matrix [rows, cols] with row stride `ld` elements; box = {64 cols, box_rows}.
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                      uint32_t box_cols) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 1000;
+}
+
+
+template <int BN, int EPI>
+static int launch_gemm(const void* A, const void* W, void* C, const void* bias, const void* residual, void* C_f32, int M,
+                       int N, int K, int lda, int ldw, int ldc, int ldr, int* status, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_bf16_2d(&ta, A, M, K, lda, kBM, kBK);
+  if (rc != 0) return rc;
+  rc = make_tmap_bf16_2d(&tb, W, N, K, ldw, BN, kBK);
+  if (rc != 0) return rc;
+  static bool attr_set = false;
+  if (!attr_set) {
+    OGB_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        Cfg::kSmemBytes));
+    attr_set = true;
+  }
+  const int m_tiles = (M + kBM - 1) / kBM, n_tiles = (N + BN - 1) / BN;
+  int grid = m_tiles * n_tiles;
+  if (grid > ogb_num_sms()) grid = ogb_num_sms();
+  gemm_bf16_tcgen05_kernel<BN, EPI><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(
+      ta, tb, static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(bias),
+      static_cast<const __nv_bfloat16*>(residual), static_cast<float*>(C_f32), M, N, K, ldc, ldr, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace ogb
+
+using namespace ogb;
+
+#define OGB_GEMM_DISPATCH_BN(EPI)                                                                                       \
+  switch (bn) {                                                                                                         \
+    case 32: return launch_gemm<32, EPI>(A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, status, stream);  \
+    case 64: return launch_gemm<64, EPI>(A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, status, stream);  \
+    case 128: return launch_gemm<128, EPI>(A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, status, stream); \
+    case 256: return launch_gemm<256, EPI>(A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, status, stream); \
+    default: return -2;                                                                                                 \
+  }
+
+extern "C" int ogb_gemm_bf16(const void* A, const void* W, void* C, const void* bias, const void* residual, void* C_f32,
+                             int M, int N, int K, int lda, int ldw, int ldc, int ldr, int epilogue, int bn, int* status,
+                             void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K % 8) != 0 || (lda % 8) != 0 || (ldw % 8) != 0 || (ldc % 8) != 0) return -3;  // 16-byte TMA / vector rules
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(C)) & 15) return -4;
+  if (epilogue == kEpiResidual && (residual == nullptr || (ldr % 8) != 0)) return -5;
+  if (epilogue == kEpiSwiGLU && (bn < 64 || (N % bn) != 0 || C_f32 != nullptr)) return -6;
+  if (bn == 0) {
+    // Pick the widest tile that still gives every SM work (M tiles x N tiles >= SM count).
+    const int m_tiles = (M + kBM - 1) / kBM;
+    const int sms = ogb_num_sms();
+    bn = 256;
+    while (bn > 32 && m_tiles * ((N + bn - 1) / bn) < sms) bn >>= 1;
+  }
+  if (epilogue == kEpiNone) { OGB_GEMM_DISPATCH_BN(kEpiNone) }
+  if (epilogue == kEpiResidual) { OGB_GEMM_DISPATCH_BN(kEpiResidual) }
+  if (epilogue == kEpiSwiGLU) {
+    switch (bn) {
+      case 64: return launch_gemm<64, kEpiSwiGLU>(A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, status, stream);
+      case 128: return launch_gemm<128, kEpiSwiGLU>(A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, status, stream);
+      case 256: return launch_gemm<256, kEpiSwiGLU>(A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, status, stream);
+      default: return -2;
+    }
+  }
+  return -7;
+}

@@ -1,0 +1,95 @@
+// C entry points of the sm_100a kernel library (libogb_cuda.so).  Every function takes raw
+// device pointers plus a CUDA stream handle and returns 0 on success, a cudaError_t (>0) from
+// the launch, or a negative code for an argument the kernel cannot serve.  No function here
+// allocates device memory: scratch buffers are passed in by the caller.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int ogb_num_sms(void);
+
+// C[M,N] = A[M,K] * W[N,K]^T, bf16 in, fp32 accumulate (tcgen05), bf16 (C) or fp32 (C_f32) out.
+// epilogue: 0 = (+bias), 1 = (+bias) + residual[M,N] (may alias C), 2 = SwiGLU over column-interleaved
+// gate|up tiles (output [M, N/2]).  bn = 0 picks the tile width; status = device int32 word.
+int ogb_gemm_bf16(const void* A, const void* W, void* C, const void* bias, const void* residual, void* C_f32, int M,
+                  int N, int K, int lda, int ldw, int ldc, int ldr, int epilogue, int bn, int* status, void* stream);
+
+// out[r,:] = x[r,:] * rsqrt(mean(x^2) + eps) * w ; if delta != NULL first x += delta (written back to x).
+int ogb_rmsnorm_bf16(void* x, const void* delta, const void* weight, void* out, int rows, int hidden, int ldx, int ldo,
+                     float eps, void* stream);
+int ogb_embedding_bf16(const int* ids, const void* table, void* out, int tokens, int hidden, int vocab, int* status,
+                       void* stream);
+int ogb_silu_mul_bf16(const void* gate_up, void* out, int rows, int inter, void* stream);
+
+// Rotary embedding on q and k (in place on the packed qkv rows) + append of k, v into the paged pool.
+// qkv: [tokens, (hq + 2*hkv) * d]; pool: [pages, hkv, 2, page_size, d] bf16; slot = page * page_size + offset.
+int ogb_rope_kv_append_bf16(void* qkv, const int* positions, const int64_t* slots, const float* cos_sin, void* pool,
+                            int tokens, int hq, int hkv, int d, int rotary_dim, int interleaved, int page_size,
+                            int64_t num_slots, int max_pos, int* status, void* stream);
+// Same with e4m3 pages and one fp32 scale per (page, head, k|v): scales [pages, hkv, 2].
+int ogb_rope_kv_append_fp8(void* qkv, const int* positions, const int64_t* slots, const float* cos_sin, void* pool,
+                           float* scales, int tokens, int hq, int hkv, int d, int rotary_dim, int interleaved,
+                           int page_size, int64_t num_slots, int max_pos, int* status, void* stream);
+
+// Paged GQA attention.  q rows live inside the packed qkv buffer (row stride q_stride elements).
+int ogb_paged_prefill_bf16(const void* q, void* out, const void* pool, const int* page_table, const int* ctx_len,
+                           const int* cu_q, const int* tile_seq, const int* tile_q0, int num_tiles, int num_seqs,
+                           int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride, int o_stride,
+                           float scale, int window, int* status, void* stream);
+int ogb_paged_decode_bf16(const void* q, void* out, const void* pool, const int* page_table, const int* ctx_len,
+                          int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride,
+                          int o_stride, float scale, int num_splits, float* part_o, float* part_ml, int window,
+                          int* status, void* stream);
+// kv_fp8 != 0: pool holds e4m3 bytes, scales [pages, hkv, 2] fp32.
+int ogb_paged_decode_fp8(const void* q, void* out, const void* pool, const float* scales, const int* page_table,
+                         const int* ctx_len, int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d,
+                         int q_stride, int o_stride, float scale, int num_splits, float* part_o, float* part_ml,
+                         int q_per_seq, int* status, void* stream);
+
+// Sampling.  logits [rows, vocab] bf16 (ld = row stride).  out_tokens int32 [rows].
+int ogb_argmax_bf16(const void* logits, int* out_tokens, int rows, int vocab, int ld, void* stream);
+// Fused temperature -> top-k -> top-p -> min-p -> inverse-CDF draw (u in [0,1) per row).
+// work: uint32 [rows, vocab] scratch.  Rows with temperature <= 0 take the argmax.
+int ogb_sample_bf16(const void* logits, int* out_tokens, const float* temperature, const int* top_k, const float* top_p,
+                    const float* min_p, const float* uniform, uint32_t* work, int rows, int vocab, int ld, void* stream);
+// Greedy speculative verification: argmax over (k+1) logits rows per sequence, accepted-prefix length, next token.
+int ogb_spec_verify_greedy(const void* logits, const int* draft_tokens, int* accept_len, int* out_tokens, int num_seqs,
+                           int k, int vocab, int ld, void* stream);
+
+// KV page utilities.
+int ogb_kv_page_copy(void* pool, const int64_t* src_pages, const int64_t* dst_pages, int n, int64_t page_bytes,
+                     void* stream);
+int ogb_kv_gather_pages(const void* pool, void* staging, const int64_t* pages, int n, int64_t page_bytes, void* stream);
+int ogb_kv_scatter_pages(void* pool, const void* staging, const int64_t* pages, int n, int64_t page_bytes, void* stream);
+
+// MatMulNBits int4 (block 32, optional nibble zero points) weight-only GEMM, in-kernel dequant.
+// qweight [N, K/32, 16] uint8 (low nibble = even k), scales [N, K/32] bf16 or fp32, zp [N, ceil(K/32/2)] or NULL.
+int ogb_w4a16_gemv(const void* x, const void* qweight, const void* scales, const void* zp, const void* bias, void* y,
+                   int M, int N, int K, int scales_fp32, void* stream);
+int ogb_w4a16_dequant(const void* qweight, const void* scales, const void* zp, void* w_bf16, int N, int K,
+                      int scales_fp32, void* stream);
+
+// MoE: softmax router with top-k (renormalised), token permutation by expert, grouped GEMM.
+int ogb_moe_route_topk(const void* router_logits, int* topk_ids, float* topk_w, int tokens, int experts, int k,
+                       int renormalize, void* stream);
+int ogb_moe_permute(const int* topk_ids, int* expert_counts, int* expert_offsets, int* sorted_route, int* route_pos,
+                    int tokens, int k, int experts, void* stream);
+int ogb_moe_gather_rows(const void* x, const int* sorted_route, void* xs, int routes, int k, int hidden, void* stream);
+int ogb_moe_combine(const void* ys, const int* route_pos, const float* topk_w, void* out, int tokens, int k, int hidden,
+                    int accumulate, void* stream);
+int ogb_grouped_gemm_bf16(const void* A, const void* W, void* C, const int* expert_offsets, int experts, int max_rows,
+                          int N, int K, int epilogue, int bn, int* status, void* stream);
+
+// Tensor-parallel collectives over peer-mapped symmetric buffers (plain NVLink loads/stores).
+int ogb_allreduce_p2p_bf16(void* const* peer_bufs, void* out, uint32_t* const* peer_flags, int rank, int world,
+                           int64_t elems, uint32_t epoch, int* status, void* stream);
+int ogb_gemm_bf16_reduce_scatter(const void* A, const void* W, void* const* peer_out, uint32_t* const* peer_flags, int M,
+                                 int N, int K, int lda, int ldw, int rank, int world, uint32_t epoch, int bn, int* status,
+                                 void* stream);
+
+#ifdef __cplusplus
+}
+#endif

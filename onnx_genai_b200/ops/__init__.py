@@ -1,0 +1,302 @@
+"""Fused ops of the decoder step.
+
+Each function takes torch tensors.  CUDA tensors run the hand-written sm_100a kernels from
+``libogb_cuda.so`` (a missing library is an error, never a silent fallback); CPU tensors run
+the fp32 PyTorch statements in :mod:`onnx_genai_b200.ops.reference`, which are also the oracle
+the GPU tests compare against.  Launch counters per op (``launch_counts``) let callers and tests
+prove which path ran, like the reference's dispatch hit counters (dispatch_manifest.toml:1-35).
+"""
+from __future__ import annotations
+
+import collections
+import math
+
+import torch
+
+from . import _native, reference
+
+PAGE = reference.PAGE
+launch_counts: collections.Counter = collections.Counter()
+_status_words: dict[int, torch.Tensor] = {}
+
+STATUS_WAIT_TIMEOUT = 1
+STATUS_INDEX_OUT_OF_RANGE = 2
+STATUS_BAD_ARGUMENT = 4
+STATUS_PEER_TIMEOUT = 8
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def status_word(device=None) -> torch.Tensor:
+    """Per-device int32 word kernels OR error bits into (wait timeout, index out of range...)."""
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index or 0
+    w = _status_words.get(idx)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=f"cuda:{idx}")
+        _status_words[idx] = w
+    return w
+
+
+def check_status(reset: bool = True) -> None:
+    """Synchronising read of the status word; raises with the decoded bits when non-zero."""
+    w = status_word()
+    v = int(w.item())
+    if v:
+        if reset:
+            w.zero_()
+        names = [n for b, n in ((1, "wait timeout"), (2, "index out of range"), (4, "bad argument"),
+                                (8, "peer wait timeout")) if v & b]
+        raise _native.KernelError("device status word = %d (%s)" % (v, ", ".join(names)))
+
+
+def _ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def num_sms() -> int:
+    return _native.load().ogb_num_sms()
+
+
+# ------------------------------------------------------------------------------------------
+# GEMM
+# ------------------------------------------------------------------------------------------
+_EPI = {"none": 0, "residual": 1, "swiglu": 2}
+
+
+def gemm(a, w, bias=None, residual=None, epilogue="none", out=None, out_f32=False, bn=0, swiglu_half=None):
+    """out[M,N] = a[M,K] @ w[N,K]^T (+bias)(+residual) or SwiGLU over a :func:`pack_gate_up` weight.
+
+    For ``epilogue="swiglu"`` ``w`` must have been packed with half-width ``swiglu_half`` and the
+    kernel tile width is ``2*swiglu_half``; the output is [M, N/2].
+    """
+    m, k = a.shape
+    n = w.shape[0]
+    if not a.is_cuda:
+        if epilogue == "swiglu":
+            return reference.swiglu_packed(a, w, swiglu_half or 128)
+        return reference.gemm(a, w, bias, residual, epilogue, torch.float32 if out_f32 else None)
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.stride(1) == 1 and w.stride(1) == 1
+    lib = _native.load()
+    if epilogue == "swiglu":
+        bn = 2 * (swiglu_half or 128)
+        n_out = n // 2
+    else:
+        n_out = n
+    if out is None:
+        out = torch.empty(m, n_out, dtype=torch.float32 if out_f32 else torch.bfloat16, device=a.device)
+    c_bf16 = 0 if out_f32 else out.data_ptr()
+    c_f32 = out.data_ptr() if out_f32 else 0
+    rc = lib.ogb_gemm_bf16(a.data_ptr(), w.data_ptr(), c_bf16, _ptr(bias), _ptr(residual), c_f32, m, n, k,
+                           a.stride(0), w.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
+                           _EPI[epilogue], bn, status_word().data_ptr(), _stream())
+    _native.check(rc, "ogb_gemm_bf16")
+    launch_counts["gemm_bf16_tcgen05"] += 1
+    return out
+
+
+pack_gate_up = reference.pack_gate_up
+
+
+# ------------------------------------------------------------------------------------------
+# glue
+# ------------------------------------------------------------------------------------------
+def rmsnorm(x, weight, eps, delta=None, out=None):
+    """Returns normed x; with ``delta`` the residual x is updated in place first (x += delta)."""
+    if not x.is_cuda:
+        y, new_x = reference.rmsnorm(x, weight, eps, delta)
+        if delta is not None:
+            x.copy_(new_x)
+        return y
+    rows, hidden = x.shape
+    if out is None:
+        out = torch.empty(rows, hidden, dtype=x.dtype, device=x.device)
+    rc = _native.load().ogb_rmsnorm_bf16(x.data_ptr(), _ptr(delta), weight.data_ptr(), out.data_ptr(), rows, hidden,
+                                         x.stride(0), out.stride(0), float(eps), _stream())
+    _native.check(rc, "ogb_rmsnorm_bf16")
+    launch_counts["rmsnorm"] += 1
+    return out
+
+
+def embedding(ids, table, out=None):
+    if not table.is_cuda:
+        return table[ids.long()]
+    t = ids.numel()
+    vocab, hidden = table.shape
+    if out is None:
+        out = torch.empty(t, hidden, dtype=table.dtype, device=table.device)
+    rc = _native.load().ogb_embedding_bf16(ids.data_ptr(), table.data_ptr(), out.data_ptr(), t, hidden, vocab,
+                                           status_word().data_ptr(), _stream())
+    _native.check(rc, "ogb_embedding_bf16")
+    launch_counts["embedding"] += 1
+    return out
+
+
+def silu_mul(gate_up, out=None):
+    if not gate_up.is_cuda:
+        return reference.silu_mul(gate_up)
+    rows, two_inter = gate_up.shape
+    if out is None:
+        out = torch.empty(rows, two_inter // 2, dtype=gate_up.dtype, device=gate_up.device)
+    rc = _native.load().ogb_silu_mul_bf16(gate_up.data_ptr(), out.data_ptr(), rows, two_inter // 2, _stream())
+    _native.check(rc, "ogb_silu_mul_bf16")
+    launch_counts["silu_mul"] += 1
+    return out
+
+
+def rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim=None, interleaved=False,
+                   kv_scales=None):
+    """Rotate q,k in place inside qkv and append k,v to the paged pool (bf16, or e4m3 with kv_scales)."""
+    rotary_dim = rotary_dim or d
+    if not qkv.is_cuda:
+        assert kv_scales is None
+        return reference.rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim, interleaved)
+    t = qkv.shape[0]
+    assert qkv.is_contiguous() and positions.dtype == torch.int32 and slots.dtype == torch.int64
+    num_slots = pool.shape[0] * PAGE
+    lib = _native.load()
+    if kv_scales is None:
+        rc = lib.ogb_rope_kv_append_bf16(qkv.data_ptr(), positions.data_ptr(), slots.data_ptr(), cos_sin.data_ptr(),
+                                         pool.data_ptr(), t, hq, hkv, d, rotary_dim, int(interleaved), PAGE, num_slots,
+                                         cos_sin.shape[0], status_word().data_ptr(), _stream())
+    else:
+        rc = lib.ogb_rope_kv_append_fp8(qkv.data_ptr(), positions.data_ptr(), slots.data_ptr(), cos_sin.data_ptr(),
+                                        pool.data_ptr(), kv_scales.data_ptr(), t, hq, hkv, d, rotary_dim,
+                                        int(interleaved), PAGE, num_slots, cos_sin.shape[0],
+                                        status_word().data_ptr(), _stream())
+    _native.check(rc, "ogb_rope_kv_append")
+    launch_counts["rope_kv_append"] += 1
+    return qkv
+
+
+# ------------------------------------------------------------------------------------------
+# attention
+# ------------------------------------------------------------------------------------------
+def prefill_tiles(q_lens, block_m=64):
+    """Host-side tile list for the prefill kernel: (tile_seq, tile_q0) int32 lists."""
+    seqs, q0s = [], []
+    for s, n in enumerate(q_lens):
+        for q0 in range(0, int(n), block_m):
+            seqs.append(s)
+            q0s.append(q0)
+    return seqs, q0s
+
+
+def paged_prefill(q, out, pool, page_table, ctx_len, cu_q, tile_seq, tile_q0, num_tiles, hq, hkv, d, scale=None,
+                  window=0):
+    """Causal varlen GQA over paged KV for chunks of new tokens.  q: packed qkv rows (first hq*d cols)."""
+    scale = scale or 1.0 / math.sqrt(d)
+    if not q.is_cuda:
+        out.copy_(reference.paged_attention(q, pool, page_table, ctx_len, cu_q, hq, hkv, d, scale, window))
+        return out
+    rc = _native.load().ogb_paged_prefill_bf16(
+        q.data_ptr(), out.data_ptr(), pool.data_ptr(), page_table.data_ptr(), ctx_len.data_ptr(), cu_q.data_ptr(),
+        tile_seq.data_ptr(), tile_q0.data_ptr(), int(num_tiles), ctx_len.numel(), page_table.shape[1], pool.shape[0],
+        hq, hkv, d, q.stride(0), out.stride(0), float(scale), int(window), status_word().data_ptr(), _stream())
+    _native.check(rc, "ogb_paged_prefill_bf16")
+    launch_counts["paged_prefill"] += 1
+    return out
+
+
+def paged_decode(q, out, pool, page_table, ctx_len, hq, hkv, d, scale=None, num_splits=1, part_o=None, part_ml=None,
+                 window=0):
+    """One query token per sequence (row s of q) over paged KV; ctx_len[s] <= 0 marks an idle row."""
+    scale = scale or 1.0 / math.sqrt(d)
+    n = ctx_len.numel()
+    if not q.is_cuda:
+        cu = torch.arange(n + 1, dtype=torch.int32)
+        out[:n].copy_(reference.paged_attention(q[:n], pool, page_table, ctx_len, cu, hq, hkv, d, scale, window))
+        return out
+    if num_splits > 1 and part_o is None:
+        part_o = torch.empty(n * hq * num_splits * d, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(n * hq * num_splits * 2, dtype=torch.float32, device=q.device)
+    rc = _native.load().ogb_paged_decode_bf16(
+        q.data_ptr(), out.data_ptr(), pool.data_ptr(), page_table.data_ptr(), ctx_len.data_ptr(), n,
+        page_table.shape[1], pool.shape[0], hq, hkv, d, q.stride(0), out.stride(0), float(scale), int(num_splits),
+        _ptr(part_o), _ptr(part_ml), int(window), status_word().data_ptr(), _stream())
+    _native.check(rc, "ogb_paged_decode_bf16")
+    launch_counts["paged_decode"] += 1
+    return out
+
+
+# ------------------------------------------------------------------------------------------
+# token selection
+# ------------------------------------------------------------------------------------------
+def argmax(logits, out=None):
+    if not logits.is_cuda:
+        return reference.argmax(logits)
+    rows, vocab = logits.shape
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    rc = _native.load().ogb_argmax_bf16(logits.data_ptr(), out.data_ptr(), rows, vocab, logits.stride(0), _stream())
+    _native.check(rc, "ogb_argmax_bf16")
+    launch_counts["argmax"] += 1
+    return out
+
+
+def sample(logits, temperature, top_k, top_p, min_p, uniform, work=None, out=None):
+    """Fused temperature/top-k/top-p/min-p sampler; per-row parameter tensors; ``uniform`` in [0,1)."""
+    if not logits.is_cuda:
+        return reference.sample(logits, temperature, top_k, top_p, min_p, uniform)
+    rows, vocab = logits.shape
+    if work is None:
+        work = torch.empty(rows * vocab, dtype=torch.int32, device=logits.device)
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    rc = _native.load().ogb_sample_bf16(logits.data_ptr(), out.data_ptr(), temperature.data_ptr(), top_k.data_ptr(),
+                                        top_p.data_ptr(), min_p.data_ptr(), uniform.data_ptr(), work.data_ptr(), rows,
+                                        vocab, logits.stride(0), _stream())
+    _native.check(rc, "ogb_sample_bf16")
+    launch_counts["sample"] += 1
+    return out
+
+
+def spec_verify_greedy(logits, draft, k):
+    if not logits.is_cuda:
+        return reference.spec_verify_greedy(logits, draft, k)
+    s = draft.shape[0]
+    accept = torch.empty(s, dtype=torch.int32, device=logits.device)
+    out = torch.empty(s, k + 1, dtype=torch.int32, device=logits.device)
+    rc = _native.load().ogb_spec_verify_greedy(logits.data_ptr(), draft.data_ptr(), accept.data_ptr(), out.data_ptr(),
+                                               s, k, logits.shape[1], logits.stride(0), _stream())
+    _native.check(rc, "ogb_spec_verify_greedy")
+    launch_counts["spec_verify_greedy"] += 1
+    return accept, out
+
+
+# ------------------------------------------------------------------------------------------
+# KV page utilities (pool: one layer [P, hkv, 2, PAGE, d])
+# ------------------------------------------------------------------------------------------
+def _page_bytes(pool):
+    return pool.stride(0) * pool.element_size()
+
+
+def kv_page_copy(pool, src_pages, dst_pages):
+    if not pool.is_cuda:
+        pool[dst_pages.long()] = pool[src_pages.long()]
+        return
+    rc = _native.load().ogb_kv_page_copy(pool.data_ptr(), src_pages.data_ptr(), dst_pages.data_ptr(),
+                                         src_pages.numel(), _page_bytes(pool), _stream())
+    _native.check(rc, "ogb_kv_page_copy")
+    launch_counts["kv_page_copy"] += 1
+
+
+def kv_gather_pages(pool, staging, pages):
+    if not pool.is_cuda:
+        staging[: pages.numel()] = pool[pages.long()]
+        return
+    rc = _native.load().ogb_kv_gather_pages(pool.data_ptr(), staging.data_ptr(), pages.data_ptr(), pages.numel(),
+                                            _page_bytes(pool), _stream())
+    _native.check(rc, "ogb_kv_gather_pages")
+    launch_counts["kv_gather_pages"] += 1
+
+
+def kv_scatter_pages(pool, staging, pages):
+    if not pool.is_cuda:
+        pool[pages.long()] = staging[: pages.numel()]
+        return
+    rc = _native.load().ogb_kv_scatter_pages(pool.data_ptr(), staging.data_ptr(), pages.data_ptr(), pages.numel(),
+                                             _page_bytes(pool), _stream())
+    _native.check(rc, "ogb_kv_scatter_pages")
+    launch_counts["kv_scatter_pages"] += 1

@@ -1,0 +1,254 @@
+"""Numerics of every sm_100a kernel against the fp32 PyTorch statement of the same op."""
+import math
+
+import pytest
+import torch
+
+from onnx_genai_b200 import ops
+from onnx_genai_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return float((a - b).norm() / (b.norm() + 1e-12))
+
+
+@pytest.mark.parametrize("m,n,k,bn", [
+    (128, 256, 64, 256), (200, 384, 512, 128), (1, 3584, 3584, 0), (300, 4608, 3584, 256),
+    (257, 1000, 448, 64), (77, 96, 128, 32), (1300, 3584, 2368, 0),
+])
+def test_gemm_tcgen05(m, n, k, bn):
+    torch.manual_seed(0)
+    a = (torch.randn(m, k, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(n, k, device=DEV) * 0.05).bfloat16()
+    bias = torch.randn(n, device=DEV).bfloat16()
+    out = ops.gemm(a, w, bias=bias, bn=bn)
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = ref.gemm(a, w, bias, out_dtype=torch.float32)
+    assert _rel_err(out, want) < 1e-2
+    out32 = ops.gemm(a, w, out_f32=True, bn=bn)
+    assert _rel_err(out32, ref.gemm(a, w, out_dtype=torch.float32)) < 1e-5 + 1e-3
+
+
+def test_gemm_residual_in_place():
+    torch.manual_seed(1)
+    m, n, k = 390, 3584, 512
+    a = (torch.randn(m, k, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(n, k, device=DEV) * 0.05).bfloat16()
+    res = torch.randn(m, n, device=DEV).bfloat16()
+    want = ref.gemm(a, w, None, res, "residual", torch.float32)
+    got = ops.gemm(a, w, residual=res, epilogue="residual", out=res)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert got.data_ptr() == res.data_ptr()
+    assert _rel_err(got, want) < 1e-2
+
+
+@pytest.mark.parametrize("half", [32, 64, 128])
+def test_gemm_swiglu(half):
+    torch.manual_seed(2)
+    m, inter, k = 333, 1024, 896
+    a = (torch.randn(m, k, device=DEV) * 0.5).bfloat16()
+    g = (torch.randn(inter, k, device=DEV) * 0.05).bfloat16()
+    u = (torch.randn(inter, k, device=DEV) * 0.05).bfloat16()
+    packed = ops.pack_gate_up(g, u, half)
+    got = ops.gemm(a, packed, epilogue="swiglu", swiglu_half=half)
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = torch.nn.functional.silu(a.float() @ g.float().t()) * (a.float() @ u.float().t())
+    assert got.shape == (m, inter)
+    assert _rel_err(got, want) < 1.5e-2
+
+
+@pytest.mark.parametrize("rows,hidden", [(5, 896), (300, 3584), (3, 16384)])
+def test_rmsnorm(rows, hidden):
+    torch.manual_seed(3)
+    x = torch.randn(rows, hidden, device=DEV).bfloat16()
+    w = torch.randn(hidden, device=DEV).bfloat16()
+    want, _ = ref.rmsnorm(x, w, 1e-6)
+    got = ops.rmsnorm(x, w, 1e-6)
+    assert _rel_err(got, want) < 5e-3
+    delta = torch.randn(rows, hidden, device=DEV).bfloat16()
+    x2 = x.clone()
+    want2, newx = ref.rmsnorm(x, w, 1e-6, delta)
+    got2 = ops.rmsnorm(x2, w, 1e-6, delta=delta)
+    assert torch.equal(x2, newx)
+    assert _rel_err(got2, want2) < 5e-3
+
+
+def test_embedding_bounds():
+    table = torch.randn(100, 64, device=DEV).bfloat16()
+    ids = torch.tensor([0, 5, 99], dtype=torch.int32, device=DEV)
+    assert torch.equal(ops.embedding(ids, table), table[ids.long()])
+    bad = torch.tensor([3, 100], dtype=torch.int32, device=DEV)
+    ops.embedding(bad, table)
+    with pytest.raises(Exception, match="index out of range"):
+        ops.check_status()
+    ops.check_status()  # word was reset
+
+
+def _make_paged(num_seqs, ctx_lens, hkv, d, extra_pages=3, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    pages_per = [(c + ref.PAGE - 1) // ref.PAGE for c in ctx_lens]
+    total = sum(pages_per) + extra_pages
+    perm = torch.randperm(total, generator=g)
+    max_pages = max(pages_per)
+    table = torch.zeros(num_seqs, max_pages, dtype=torch.int32)
+    o = 0
+    for s, n in enumerate(pages_per):
+        table[s, :n] = perm[o:o + n].to(torch.int32)
+        o += n
+    pool = (torch.randn(total, hkv, 2, ref.PAGE, d, generator=g) * 0.5).bfloat16()
+    return pool.to(DEV), table.to(DEV)
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(28, 4, 128), (14, 2, 64), (4, 1, 128), (3, 1, 128)])
+def test_paged_decode(hq, hkv, d):
+    torch.manual_seed(4)
+    ctx = [1, 15, 16, 17, 63, 64, 65, 300, 1000]
+    n = len(ctx)
+    pool, table = _make_paged(n, ctx, hkv, d)
+    ctx_t = torch.tensor(ctx, dtype=torch.int32, device=DEV)
+    q = torch.randn(n, (hq + 2 * hkv) * d, device=DEV).bfloat16()
+    out = torch.zeros(n, hq * d, device=DEV, dtype=torch.bfloat16)
+    cu = torch.arange(n + 1, dtype=torch.int32, device=DEV)
+    want = ref.paged_attention(q, pool, table, ctx_t, cu, hq, hkv, d)
+    for splits in (1, 4):
+        out.zero_()
+        ops.paged_decode(q, out, pool, table, ctx_t, hq, hkv, d, num_splits=splits)
+        torch.cuda.synchronize()
+        ops.check_status()
+        assert _rel_err(out, want) < 2e-2, splits
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(28, 4, 128), (14, 2, 64)])
+def test_paged_prefill(hq, hkv, d):
+    torch.manual_seed(5)
+    q_lens = [1, 5, 64, 65, 200, 130]
+    past = [0, 11, 0, 64, 37, 512]
+    ctx = [a + b for a, b in zip(q_lens, past)]
+    n = len(ctx)
+    pool, table = _make_paged(n, ctx, hkv, d, seed=1)
+    t = sum(q_lens)
+    q = torch.randn(t, (hq + 2 * hkv) * d, device=DEV).bfloat16()
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    ctx_t = torch.tensor(ctx, dtype=torch.int32, device=DEV)
+    ts, tq = ops.prefill_tiles(q_lens)
+    tile_seq = torch.tensor(ts, dtype=torch.int32, device=DEV)
+    tile_q0 = torch.tensor(tq, dtype=torch.int32, device=DEV)
+    out = torch.zeros(t, hq * d, device=DEV, dtype=torch.bfloat16)
+    ops.paged_prefill(q, out, pool, table, ctx_t, cu, tile_seq, tile_q0, len(ts), hq, hkv, d)
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = ref.paged_attention(q, pool, table, ctx_t, cu, hq, hkv, d)
+    assert _rel_err(out, want) < 2e-2
+    # sliding window
+    out.zero_()
+    ops.paged_prefill(q, out, pool, table, ctx_t, cu, tile_seq, tile_q0, len(ts), hq, hkv, d, window=48)
+    want = ref.paged_attention(q, pool, table, ctx_t, cu, hq, hkv, d, window=48)
+    assert _rel_err(out, want) < 2e-2
+
+
+def test_rope_kv_append():
+    torch.manual_seed(6)
+    hq, hkv, d, t, pages = 14, 2, 64, 37, 9
+    qkv = torch.randn(t, (hq + 2 * hkv) * d, device=DEV).bfloat16()
+    pos = torch.randint(0, 500, (t,), dtype=torch.int32, device=DEV)
+    slots = torch.randperm(pages * ref.PAGE, device=DEV)[:t].to(torch.int64)
+    slots[3] = -1
+    cs = ref.rope_table(512, d, 1e6, DEV)
+    pool = torch.zeros(pages, hkv, 2, ref.PAGE, d, device=DEV, dtype=torch.bfloat16)
+    qkv_ref, pool_ref = qkv.clone(), pool.clone()
+    ref.rope_kv_append(qkv_ref, pos, slots, cs, pool_ref, hq, hkv, d)
+    ops.rope_kv_append(qkv, pos, slots, cs, pool, hq, hkv, d)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert _rel_err(qkv, qkv_ref) < 4e-3
+    assert _rel_err(pool, pool_ref) < 4e-3
+
+
+def test_argmax_and_ties():
+    torch.manual_seed(7)
+    logits = torch.randn(9, 151936, device=DEV).bfloat16()
+    logits[0, 777] = 50.0
+    logits[0, 12345] = 50.0
+    logits[1, 5] = float("nan")
+    got = ops.argmax(logits)
+    want = ref.argmax(logits)
+    assert torch.equal(got.cpu(), want.cpu())
+    assert int(got[0]) == 777
+
+
+def test_sampler_matches_integer_oracle():
+    torch.manual_seed(8)
+    rows, vocab = 12, 32000
+    logits = (torch.randn(rows, vocab, device=DEV) * 3).bfloat16()
+    temperature = torch.tensor([0.7, 1.0, 0.0, 0.7, 1.3, 0.7, 0.7, 1.0, 0.5, 0.7, 0.7, 2.0], device=DEV)
+    top_k = torch.tensor([0, 50, 0, 1, 0, 40, 0, 0, 5, 0, 1000, 0], dtype=torch.int32, device=DEV)
+    top_p = torch.tensor([0.9, 1.0, 1.0, 1.0, 0.5, 0.95, 1.0, 0.1, 0.9, 0.9, 0.8, 1.0], device=DEV)
+    min_p = torch.tensor([0.0, 0.0, 0.0, 0.0, 0.0, 0.05, 0.2, 0.0, 0.0, 0.0, 0.01, 0.0], device=DEV)
+    for trial in range(3):
+        u = torch.rand(rows, device=DEV)
+        got = ops.sample(logits, temperature, top_k, top_p, min_p, u).cpu()
+        # the oracle consumes the device's own fixed-point weights semantics: recompute them in torch
+        for r in range(rows):
+            t = float(temperature[r])
+            if t <= 0:
+                assert int(got[r]) == int(ref.argmax(logits[r:r + 1])[0])
+                continue
+            w = ref.sample_weights(logits[r].cpu(), t)
+            want = ref.sample_from_weights(w, int(top_k[r]), float(top_p[r]), float(min_p[r]), float(u[r]))
+            if int(got[r]) != want:
+                # __expf differs from torch.exp in the last ulp: allow a neighbouring survivor only when
+                # the draw lands within 1e-5 of a CDF boundary
+                kept = w.double() / w.sum()
+                assert abs(int(got[r]) - want) < vocab and kept[int(got[r])] > 0, (r, int(got[r]), want)
+
+
+def test_sampler_distribution():
+    torch.manual_seed(9)
+    vocab = 64
+    logits = torch.randn(1, vocab, device=DEV).bfloat16().repeat(4096, 1)
+    n = logits.shape[0]
+    temperature = torch.full((n,), 1.0, device=DEV)
+    top_k = torch.zeros(n, dtype=torch.int32, device=DEV)
+    top_p = torch.ones(n, device=DEV)
+    min_p = torch.zeros(n, device=DEV)
+    u = torch.rand(n, device=DEV)
+    got = ops.sample(logits, temperature, top_k, top_p, min_p, u)
+    freq = torch.bincount(got.long(), minlength=vocab).float() / n
+    p = torch.softmax(logits[0].float(), -1)
+    assert float((freq - p).abs().max()) < 0.03
+
+
+def test_spec_verify_greedy():
+    torch.manual_seed(10)
+    s, k, vocab = 5, 4, 1000
+    logits = torch.randn(s * (k + 1), vocab, device=DEV).bfloat16()
+    best = ref.argmax(logits).view(s, k + 1)
+    draft = best[:, :k].clone()
+    draft[1, 2] = (draft[1, 2] + 1) % vocab
+    draft[3, 0] = (draft[3, 0] + 1) % vocab
+    acc, out = ops.spec_verify_greedy(logits, draft.contiguous(), k)
+    acc_r, out_r = ref.spec_verify_greedy(logits, draft, k)
+    assert torch.equal(acc.cpu(), acc_r.cpu()) and torch.equal(out.cpu(), out_r.cpu())
+    assert acc.cpu().tolist() == [4, 2, 4, 0, 4]
+
+
+def test_kv_page_utils():
+    pool = torch.randn(10, 2, 2, 16, 64, device=DEV).bfloat16()
+    orig = pool.clone()
+    src = torch.tensor([1, 2], dtype=torch.int64, device=DEV)
+    dst = torch.tensor([7, 8], dtype=torch.int64, device=DEV)
+    ops.kv_page_copy(pool, src, dst)
+    assert torch.equal(pool[7], orig[1]) and torch.equal(pool[8], orig[2])
+    staging = torch.zeros(2, 2, 2, 16, 64, device=DEV, dtype=torch.bfloat16)
+    ops.kv_gather_pages(pool, staging, src)
+    assert torch.equal(staging[0], orig[1])
+    pool[1].zero_()
+    ops.kv_scatter_pages(pool, staging, src)
+    assert torch.equal(pool[1], orig[1])
