@@ -134,13 +134,13 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloa
 // ------------------------------------------------------------------------------------------
 template <bool FP8>
 __global__ void rope_kv_append_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
-                                      const int64_t* __restrict__ slots, const float* __restrict__ cos_sin,
+                                      const int* __restrict__ slots, const float* __restrict__ cos_sin,
                                       void* __restrict__ pool, float* __restrict__ scales, int hq, int hkv, int d,
                                       int rotary_dim, int interleaved, int page_size, int64_t num_slots, int max_pos,
                                       int* status) {
   const int t = blockIdx.x;
   int pos = positions[t];
-  const int64_t slot = slots[t];
+  const int64_t slot = slots[t];  // slot = page * page_size + offset; negative = do not cache
   if (pos < 0 || pos >= max_pos) {
     if (threadIdx.x == 0) atomicOr(status, kStatusIndexOutOfRange);
     pos = 0;
@@ -260,7 +260,7 @@ extern "C" int ogb_silu_mul_bf16(const void* gate_up, void* out, int rows, int i
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int ogb_rope_kv_append_bf16(void* qkv, const int* positions, const int64_t* slots, const float* cos_sin,
+extern "C" int ogb_rope_kv_append_bf16(void* qkv, const int* positions, const int* slots, const float* cos_sin,
                                        void* pool, int tokens, int hq, int hkv, int d, int rotary_dim, int interleaved,
                                        int page_size, int64_t num_slots, int max_pos, int* status, void* stream) {
   if (tokens <= 0) return 0;
@@ -271,7 +271,7 @@ extern "C" int ogb_rope_kv_append_bf16(void* qkv, const int* positions, const in
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int ogb_rope_kv_append_fp8(void* qkv, const int* positions, const int64_t* slots, const float* cos_sin,
+extern "C" int ogb_rope_kv_append_fp8(void* qkv, const int* positions, const int* slots, const float* cos_sin,
                                       void* pool, float* scales, int tokens, int hq, int hkv, int d, int rotary_dim,
                                       int interleaved, int page_size, int64_t num_slots, int max_pos, int* status,
                                       void* stream) {

@@ -26,11 +26,11 @@ int ogb_silu_mul_bf16(const void* gate_up, void* out, int rows, int inter, void*
 
 // Rotary embedding on q and k (in place on the packed qkv rows) + append of k, v into the paged pool.
 // qkv: [tokens, (hq + 2*hkv) * d]; pool: [pages, hkv, 2, page_size, d] bf16; slot = page * page_size + offset.
-int ogb_rope_kv_append_bf16(void* qkv, const int* positions, const int64_t* slots, const float* cos_sin, void* pool,
+int ogb_rope_kv_append_bf16(void* qkv, const int* positions, const int* slots, const float* cos_sin, void* pool,
                             int tokens, int hq, int hkv, int d, int rotary_dim, int interleaved, int page_size,
                             int64_t num_slots, int max_pos, int* status, void* stream);
 // Same with e4m3 pages and one fp32 scale per (page, head, k|v): scales [pages, hkv, 2].
-int ogb_rope_kv_append_fp8(void* qkv, const int* positions, const int64_t* slots, const float* cos_sin, void* pool,
+int ogb_rope_kv_append_fp8(void* qkv, const int* positions, const int* slots, const float* cos_sin, void* pool,
                            float* scales, int tokens, int hq, int hkv, int d, int rotary_dim, int interleaved,
                            int page_size, int64_t num_slots, int max_pos, int* status, void* stream);
 

@@ -79,31 +79,79 @@ OGB_DEVICE unsigned long long block_sum_u64(unsigned long long v, unsigned long 
 // Radix select over the weights of one row.  Finds the largest threshold T such that
 //   measure({ i : w[i] >= T }) >= target
 // where measure is the element count (BY_MASS = false, used for top-k) or the summed weight
-// (BY_MASS = true, used for top-p).  Only weights >= floor participate.  Four 8-bit passes.
+// (BY_MASS = true, used for top-p).  Only weights >= floor participate.  Weights are < 2^30, so
+// five 6-bit digit passes cover them.  Each warp owns a private histogram (64-bit sums kept as
+// lo/hi 32-bit words with carry detection, so only native 32-bit shared atomics are used); when
+// all 32 lanes of an iteration fall into the same bucket -- the common case, most weights share
+// the leading digits -- the warp reduces in registers and lane 0 does one plain add.
+constexpr int kDigitBits = 6;
+constexpr int kBuckets = 1 << kDigitBits;
+
+struct RadixScratch {
+  uint32_t lo[kSampleThreads / 32][kBuckets];
+  uint32_t hi[kSampleThreads / 32][kBuckets];
+  unsigned long long total[kBuckets];
+};
+
+OGB_DEVICE unsigned long long warp_sum_u64(unsigned long long v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
 template <bool BY_MASS>
 OGB_DEVICE uint32_t radix_threshold(const uint32_t* __restrict__ w, int vocab, uint32_t floor_w,
-                                    unsigned long long target, unsigned long long* hist /*[256]*/) {
+                                    unsigned long long target, RadixScratch& sc) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint32_t prefix = 0;
   unsigned long long above = 0;  // measure of weights strictly above the current prefix bucket
-  for (int shift = 24; shift >= 0; shift -= 8) {
-    for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0ull;
-    __syncthreads();
-    const uint32_t hi_mask = (shift == 24) ? 0u : (0xffffffffu << (shift + 8));
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-      const uint32_t v = w[i];
-      if (v >= floor_w && (v & hi_mask) == prefix) {
-        atomicAdd(&hist[(v >> shift) & 0xff], BY_MASS ? static_cast<unsigned long long>(v) : 1ull);
-      }
+  for (int shift = 30 - kDigitBits; shift >= 0; shift -= kDigitBits) {
+    for (int i = threadIdx.x; i < (kSampleThreads / 32) * kBuckets; i += blockDim.x) {
+      (&sc.lo[0][0])[i] = 0u;
+      (&sc.hi[0][0])[i] = 0u;
     }
     __syncthreads();
-    // walk buckets from the top; every thread does the same 256-step walk (cheap, deterministic)
+    const uint32_t hi_mask = ~((1u << (shift + kDigitBits)) - 1u);
+    const int iters = (vocab + kSampleThreads - 1) / kSampleThreads;
+    for (int it = 0; it < iters; ++it) {
+      const int i = it * kSampleThreads + threadIdx.x;
+      const uint32_t v = (i < vocab) ? w[i] : 0u;
+      const bool part = (i < vocab) && v >= floor_w && (v & hi_mask) == prefix;
+      const int bucket = part ? static_cast<int>((v >> shift) & (kBuckets - 1)) : kBuckets;
+      const unsigned long long val = part ? (BY_MASS ? static_cast<unsigned long long>(v) : 1ull) : 0ull;
+      const int b0 = __shfl_sync(0xffffffffu, bucket, 0);
+      if (__all_sync(0xffffffffu, bucket == b0)) {
+        if (b0 != kBuckets) {
+          const unsigned long long tot = warp_sum_u64(val);
+          if (lane == 0) {
+            const uint32_t add = static_cast<uint32_t>(tot);
+            const uint32_t old = sc.lo[warp][b0];
+            sc.lo[warp][b0] = old + add;
+            sc.hi[warp][b0] += static_cast<uint32_t>(tot >> 32) + ((old + add < old) ? 1u : 0u);
+          }
+        }
+      } else if (part) {
+        const uint32_t add = static_cast<uint32_t>(val);
+        const uint32_t old = atomicAdd(&sc.lo[warp][bucket], add);
+        if (old + add < old) atomicAdd(&sc.hi[warp][bucket], 1u);
+      }
+      __syncwarp();
+    }
+    __syncthreads();
+    if (threadIdx.x < kBuckets) {
+      unsigned long long t = 0;
+      for (int wi = 0; wi < kSampleThreads / 32; ++wi)
+        t += (static_cast<unsigned long long>(sc.hi[wi][threadIdx.x]) << 32) + sc.lo[wi][threadIdx.x];
+      sc.total[threadIdx.x] = t;
+    }
+    __syncthreads();
+    // walk buckets from the top; every thread does the same short walk
     int chosen = 0;
     unsigned long long run = above;
-    for (int b = 255; b >= 0; --b) {
-      const unsigned long long h = hist[b];
+    for (int b = kBuckets - 1; b >= 0; --b) {
+      const unsigned long long h = sc.total[b];
       if (run + h >= target) { chosen = b; break; }
       run += h;
-      if (b == 0) chosen = 0;
     }
     above = run;
     prefix |= static_cast<uint32_t>(chosen) << shift;
@@ -118,7 +166,7 @@ sample_kernel(const __nv_bfloat16* __restrict__ logits, int* __restrict__ out, c
               const float* __restrict__ uniform, uint32_t* __restrict__ work, int vocab, int ld) {
   __shared__ ArgMax sh_arg[32];
   __shared__ unsigned long long sh_sum[32];
-  __shared__ unsigned long long hist[256];
+  __shared__ RadixScratch sc;
   __shared__ unsigned long long sh_scan[kSampleThreads / 32];
   __shared__ int sh_pick;
   const int rowi = blockIdx.x;
@@ -136,7 +184,8 @@ sample_kernel(const __nv_bfloat16* __restrict__ logits, int* __restrict__ out, c
     const float l = __bfloat162float(row[i]);
     float e = __expf((l - best.v) * inv_t);   // in (0, 1]; NaN logits get weight 0
     if (!(e >= 0.f)) e = 0.f;
-    const uint32_t q = static_cast<uint32_t>(e * 1073741824.f + 0.5f);
+    uint32_t q = static_cast<uint32_t>(e * 1073741824.f + 0.5f);
+    if (q > 1073741823u) q = 1073741823u;
     w[i] = q;
     local += q;
   }
@@ -146,9 +195,9 @@ sample_kernel(const __nv_bfloat16* __restrict__ logits, int* __restrict__ out, c
 
   const int k = top_k[rowi];
   if (k > 0 && k < vocab) {
-    thr = radix_threshold<false>(w, vocab, thr, static_cast<unsigned long long>(k), hist);
+    thr = radix_threshold<false>(w, vocab, thr, static_cast<unsigned long long>(k), sc);
     unsigned long long s = 0;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) s += (w[i] >= thr) ? w[i] : 0u;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) { const uint32_t v = w[i]; s += (v >= thr) ? v : 0u; }
     total = block_sum_u64(s, sh_sum);
   }
   const float p = top_p[rowi];
@@ -156,58 +205,62 @@ sample_kernel(const __nv_bfloat16* __restrict__ logits, int* __restrict__ out, c
     // smallest set of largest weights whose mass reaches p * total (mass renormalised over survivors)
     unsigned long long target = static_cast<unsigned long long>(static_cast<double>(total) * static_cast<double>(p));
     if (target < 1ull) target = 1ull;
-    thr = radix_threshold<true>(w, vocab, thr, target, hist);
+    thr = radix_threshold<true>(w, vocab, thr, target, sc);
   }
   const float mp = min_p[rowi];
   if (mp > 0.f) {
-    // the maximum weight is always 2^30 (the argmax token)
     const uint32_t floor_mp = static_cast<uint32_t>(fminf(mp, 1.f) * 1073741824.f);
     if (floor_mp > thr) thr = floor_mp;
   }
-  // final mass and inverse-CDF draw in token-index order
-  const int per = (vocab + blockDim.x - 1) / blockDim.x;
-  const int begin = threadIdx.x * per;
-  const int end = min(vocab, begin + per);
-  unsigned long long mine = 0;
-  for (int i = begin; i < end; ++i) mine += (w[i] >= thr) ? w[i] : 0u;
-  // inclusive scan across threads
-  unsigned long long incl = mine;
+  // final mass per warp-contiguous range, then the inverse-CDF draw in token-index order
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    unsigned long long n = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += n;
-  }
-  if (lane == 31) sh_scan[warp] = incl;
+  const int per_warp = ((vocab + 31) / 32 + 31) / 32 * 32;  // range length per warp, multiple of 32
+  const int wbegin = warp * per_warp;
+  const int wend = min(vocab, wbegin + per_warp);
+  unsigned long long mine = 0;
+  for (int i = wbegin + lane; i < wend; i += 32) { const uint32_t v = w[i]; mine += (v >= thr) ? v : 0u; }
+  mine = warp_sum_u64(mine);
+  if (lane == 0) sh_scan[warp] = mine;
   if (threadIdx.x == 0) sh_pick = -1;
   __syncthreads();
   if (warp == 0) {
-    unsigned long long v = (lane < kSampleThreads / 32) ? sh_scan[lane] : 0ull;
+    unsigned long long v = sh_scan[lane];
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       unsigned long long n = __shfl_up_sync(0xffffffffu, v, o);
       if (lane >= o) v += n;
     }
-    if (lane < kSampleThreads / 32) sh_scan[lane] = v;  // inclusive prefix of warp totals
+    sh_scan[lane] = v;  // inclusive prefix of warp totals
   }
   __syncthreads();
-  const unsigned long long warp_excl = (warp == 0) ? 0ull : sh_scan[warp - 1];
   const unsigned long long final_total = sh_scan[kSampleThreads / 32 - 1];
-  const unsigned long long my_incl = warp_excl + incl;
-  const unsigned long long my_excl = my_incl - mine;
   float u = uniform[rowi];
   u = fminf(fmaxf(u, 0.f), 0.99999994f);
   unsigned long long target = static_cast<unsigned long long>(static_cast<double>(u) * static_cast<double>(final_total));
   if (final_total > 0 && target >= final_total) target = final_total - 1;
-  if (final_total > 0 && mine > 0 && target >= my_excl && target < my_incl) {
-    unsigned long long run = my_excl;
-    int pick = begin;
-    for (int i = begin; i < end; ++i) {
-      const uint32_t v = (w[i] >= thr) ? w[i] : 0u;
-      if (v > 0 && target < run + v) { pick = i; break; }
-      run += v;
+  const unsigned long long w_incl = sh_scan[warp];
+  const unsigned long long w_excl = w_incl - mine;
+  if (final_total > 0 && mine > 0 && target >= w_excl && target < w_incl) {
+    // this warp owns the draw: walk its range 32 tokens at a time with a warp scan
+    unsigned long long run = w_excl;
+    for (int base = wbegin; base < wend; base += 32) {
+      const int i = base + lane;
+      const uint32_t v0 = (i < wend) ? w[i] : 0u;
+      const unsigned long long v = (v0 >= thr) ? v0 : 0u;
+      unsigned long long incl = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        unsigned long long n = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += n;
+      }
+      const bool hit = v > 0 && target >= run + incl - v && target < run + incl;
+      const unsigned ball = __ballot_sync(0xffffffffu, hit);
+      if (ball) {
+        if (lane == __ffs(ball) - 1) sh_pick = i;
+        break;
+      }
+      run += __shfl_sync(0xffffffffu, incl, 31);
     }
-    sh_pick = pick;
   }
   __syncthreads();
   if (threadIdx.x == 0) out[rowi] = (sh_pick >= 0) ? sh_pick : best.i;

@@ -1,0 +1,665 @@
+// Implementation of the host runtime core declared in core.h.
+#include "core.h"
+
+#include <algorithm>
+#include <cstring>
+
+namespace ogb {
+
+// ------------------------------------------------------------------------------------------
+// BlockPool
+// ------------------------------------------------------------------------------------------
+BlockPool::BlockPool(int num_pages) : ref_(num_pages, 0), hash_of_(num_pages, 0), in_evictable_(num_pages, 0) {
+  free_.reserve(num_pages);
+  for (int i = num_pages - 1; i >= 0; --i) free_.push_back(i);  // pop_back hands out page 0 first
+}
+
+int BlockPool::allocate() {
+  int page = -1;
+  if (!free_.empty()) {
+    page = free_.back();
+    free_.pop_back();
+  } else {
+    while (!evictable_.empty()) {
+      int cand = evictable_.front();
+      evictable_.pop_front();
+      if (!in_evictable_[cand] || ref_[cand] != 0) continue;  // stale entry
+      in_evictable_[cand] = 0;
+      page = cand;
+      break;
+    }
+    if (page < 0) return -1;
+    if (hash_of_[page] != 0) {
+      auto it = by_hash_.find(hash_of_[page]);
+      if (it != by_hash_.end() && it->second == page) by_hash_.erase(it);
+      hash_of_[page] = 0;
+    }
+  }
+  ref_[page] = 1;
+  return page;
+}
+
+void BlockPool::release(int page) {
+  if (page < 0 || page >= num_pages() || ref_[page] <= 0) return;
+  if (--ref_[page] > 0) return;
+  if (hash_of_[page] != 0) {
+    evictable_.push_back(page);
+    in_evictable_[page] = 1;
+  } else {
+    free_.push_back(page);
+  }
+}
+
+uint64_t BlockPool::chain_hash(uint64_t parent, const int32_t* tokens, int n) {
+  uint64_t h = parent ^ 0x9E3779B97F4A7C15ull;
+  for (int i = 0; i < n; ++i) {
+    h ^= static_cast<uint32_t>(tokens[i]) + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+    h *= 0xff51afd7ed558ccdull;
+    h ^= h >> 33;
+  }
+  return h == 0 ? 1 : h;
+}
+
+int BlockPool::lookup(uint64_t hash) {
+  ++lookups_;
+  auto it = by_hash_.find(hash);
+  if (it == by_hash_.end()) return -1;
+  const int page = it->second;
+  if (ref_[page] == 0) in_evictable_[page] = 0;  // leaves the LRU lazily (stale deque entry is skipped)
+  ++ref_[page];
+  ++hits_;
+  return page;
+}
+
+void BlockPool::publish(int page, uint64_t hash) {
+  if (hash_of_[page] != 0) return;
+  if (by_hash_.count(hash)) return;  // another page already serves this prefix
+  hash_of_[page] = hash;
+  by_hash_[hash] = page;
+}
+
+void BlockPool::reset_prefix_cache() {
+  for (int p : evictable_) {
+    if (in_evictable_[p] && ref_[p] == 0) {
+      in_evictable_[p] = 0;
+      free_.push_back(p);
+    }
+  }
+  evictable_.clear();
+  by_hash_.clear();
+  std::fill(hash_of_.begin(), hash_of_.end(), 0);
+}
+
+// ------------------------------------------------------------------------------------------
+// Core
+// ------------------------------------------------------------------------------------------
+static PlanLayout make_layout(const CoreConfig& c) {
+  PlanLayout l{};
+  int o = 32;
+  auto take = [&](int n) { int at = o; o += n; return at; };
+  l.header = 0;
+  l.token_ids = take(c.max_tokens_per_step);
+  l.positions = take(c.max_tokens_per_step);
+  l.slots = take(c.max_tokens_per_step);
+  l.seq_slot = take(c.max_seqs);
+  l.ctx_len = take(c.max_seqs);
+  l.cu_q = take(c.max_seqs + 1);
+  l.page_table = take(c.max_seqs * c.max_pages_per_seq);
+  l.max_tiles = c.max_tokens_per_step / 64 + c.max_seqs + 1;
+  l.tile_seq = take(l.max_tiles);
+  l.tile_q0 = take(l.max_tiles);
+  l.logit_rows = take(c.max_seqs);
+  l.temperature = take(c.max_seqs);
+  l.top_k = take(c.max_seqs);
+  l.top_p = take(c.max_seqs);
+  l.min_p = take(c.max_seqs);
+  l.uniform = take(c.max_seqs);
+  l.copy_src = take(c.max_seqs);
+  l.copy_dst = take(c.max_seqs);
+  l.max_swap = c.max_seqs * c.max_pages_per_seq;
+  if (c.num_host_pages == 0) l.max_swap = 1;
+  l.swap_out_dev = take(l.max_swap);
+  l.swap_out_host = take(l.max_swap);
+  l.swap_in_dev = take(l.max_swap);
+  l.swap_in_host = take(l.max_swap);
+  l.total_words = o;
+  return l;
+}
+
+Core::Core(const CoreConfig& cfg) : cfg_(cfg), layout_(make_layout(cfg)), pool_(cfg.num_pages) {
+  for (int i = cfg.num_host_pages - 1; i >= 0; --i) host_free_.push_back(i);
+}
+
+Sequence* Core::find(int64_t id) {
+  auto it = seqs_.find(id);
+  return it == seqs_.end() ? nullptr : &it->second;
+}
+const Sequence* Core::find(int64_t id) const {
+  auto it = seqs_.find(id);
+  return it == seqs_.end() ? nullptr : &it->second;
+}
+
+static uint64_t splitmix64(uint64_t& x) {
+  uint64_t z = (x += 0x9E3779B97F4A7C15ull);
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+float Core::next_uniform(Sequence& s) {
+  const uint64_t r = splitmix64(s.rng_state);
+  return static_cast<float>(r >> 40) * (1.0f / 16777216.0f);  // 24 random bits -> [0, 1)
+}
+
+int64_t Core::add_request(const int32_t* prompt, int n, int max_new_tokens, const SamplingParams& sp, int priority,
+                          int tenant, bool ignore_eos, const int32_t* stop_ids, int n_stop) {
+  if (n <= 0 || max_new_tokens < 0) return -1;
+  const int max_len = cfg_.max_pages_per_seq * kPageTokens;
+  if (n + max_new_tokens > max_len) {
+    if (n >= max_len) return -2;  // prompt alone does not fit a page table row
+    max_new_tokens = max_len - n; // admission capping, like the reference's GenerationBudgetCap
+  }
+  Sequence s;
+  s.id = next_id_++;
+  s.tokens.assign(prompt, prompt + n);
+  s.prompt_len = n;
+  s.max_new_tokens = max_new_tokens;
+  s.sampling = sp;
+  s.rng_state = sp.seed ? sp.seed : (0x1234567ull + static_cast<uint64_t>(s.id) * 0x9E3779B97F4A7C15ull);
+  s.priority = priority;
+  s.tenant = tenant;
+  s.arrival = clock_++;
+  s.ignore_eos = ignore_eos;
+  if (stop_ids && n_stop > 0) s.stop_ids.assign(stop_ids, stop_ids + n_stop);
+  const int64_t id = s.id;
+  seqs_.emplace(id, std::move(s));
+  waiting_.push_back(id);
+  return id;
+}
+
+void Core::free_pages(Sequence& s, bool publish_prefix) {
+  if (publish_prefix) publish_full_pages(s);
+  for (int p : s.pages) pool_.release(p);
+  s.pages.clear();
+}
+
+void Core::publish_full_pages(Sequence& s) {
+  if (!cfg_.enable_prefix_cache) return;
+  const int full = std::min(s.num_computed, static_cast<int>(s.tokens.size())) / kPageTokens;
+  uint64_t h = 0;
+  for (int i = 0; i < full && i < static_cast<int>(s.pages.size()); ++i) {
+    h = BlockPool::chain_hash(h, s.tokens.data() + i * kPageTokens, kPageTokens);
+    pool_.publish(s.pages[i], h);
+  }
+}
+
+void Core::try_prefix_attach(Sequence& s) {
+  if (!cfg_.enable_prefix_cache || !s.pages.empty()) return;
+  // never serve the whole prompt from cache: the last token must run to produce logits
+  const int max_full = (static_cast<int>(s.tokens.size()) - 1) / kPageTokens;
+  uint64_t h = 0;
+  int matched = 0;
+  for (int i = 0; i < max_full; ++i) {
+    h = BlockPool::chain_hash(h, s.tokens.data() + i * kPageTokens, kPageTokens);
+    const int page = pool_.lookup(h);
+    if (page < 0) break;
+    s.pages.push_back(page);
+    ++matched;
+  }
+  s.num_computed = matched * kPageTokens;
+  s.num_cached_prefix = s.num_computed;
+}
+
+bool Core::ensure_pages(Sequence& s, int new_len, std::vector<std::pair<int, int>>& copies) {
+  const int need = (new_len + kPageTokens - 1) / kPageTokens;
+  if (need > cfg_.max_pages_per_seq) return false;
+  // copy-on-write: the page that receives the next token must be exclusively owned
+  const int write_page = s.num_computed / kPageTokens;
+  if (write_page < static_cast<int>(s.pages.size()) && pool_.refcount(s.pages[write_page]) > 1 &&
+      (s.num_computed % kPageTokens) != 0) {
+    const int fresh = pool_.allocate();
+    if (fresh < 0) return false;
+    copies.emplace_back(s.pages[write_page], fresh);
+    pool_.release(s.pages[write_page]);
+    s.pages[write_page] = fresh;
+  }
+  const int have = static_cast<int>(s.pages.size());
+  if (need - have > pool_.num_free()) return false;
+  for (int i = have; i < need; ++i) {
+    const int p = pool_.allocate();
+    if (p < 0) return false;  // cannot happen after the check above
+    s.pages.push_back(p);
+  }
+  return true;
+}
+
+bool Core::preempt_one(Sequence* keep, std::vector<std::pair<int, int>>& swap_out) {
+  // victim: lowest priority, then latest arrival, among running sequences other than `keep`
+  int victim_idx = -1;
+  for (int i = 0; i < static_cast<int>(running_.size()); ++i) {
+    Sequence* c = find(running_[i]);
+    if (!c || c == keep) continue;
+    if (victim_idx < 0) { victim_idx = i; continue; }
+    Sequence* v = find(running_[victim_idx]);
+    if (c->priority < v->priority || (c->priority == v->priority && c->arrival > v->arrival)) victim_idx = i;
+  }
+  if (victim_idx < 0) return false;
+  Sequence& v = *find(running_[victim_idx]);
+  running_.erase(running_.begin() + victim_idx);
+  ++preemptions_;
+  v.scheduled = 0;
+  v.samples_this_step = false;
+  const int used_pages = (v.num_computed + kPageTokens - 1) / kPageTokens;
+  if (cfg_.preempt == PreemptMode::Swap && static_cast<int>(host_free_.size()) >= used_pages && used_pages > 0) {
+    v.host_pages.clear();
+    for (int i = 0; i < used_pages; ++i) {
+      const int hp = host_free_.back();
+      host_free_.pop_back();
+      v.host_pages.push_back(hp);
+      swap_out.emplace_back(v.pages[i], hp);
+    }
+    for (int p : v.pages) pool_.release(p);
+    v.pages.clear();
+    v.status = SeqStatus::Swapped;
+    swapped_.push_back(v.id);
+  } else {
+    free_pages(v, true);
+    v.num_computed = 0;
+    v.status = SeqStatus::Waiting;
+    waiting_.push_front(v.id);
+  }
+  return true;
+}
+
+std::vector<int64_t> Core::waiting_order() {
+  std::vector<int64_t> order(waiting_.begin(), waiting_.end());
+  if (cfg_.policy == Policy::Priority) {
+    std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) {
+      const Sequence *sa = find(a), *sb = find(b);
+      if (sa->priority != sb->priority) return sa->priority > sb->priority;
+      return sa->arrival < sb->arrival;
+    });
+  } else if (cfg_.policy == Policy::FairShare) {
+    std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) {
+      const Sequence *sa = find(a), *sb = find(b);
+      const int64_t ta = tenant_served_[sa->tenant], tb = tenant_served_[sb->tenant];
+      if (ta != tb) return ta < tb;  // least-served tenant first
+      return sa->arrival < sb->arrival;
+    });
+  }
+  return order;
+}
+
+int Core::build_step(int32_t* plan) {
+  const PlanLayout& L = layout_;
+  std::memset(plan, 0, sizeof(int32_t) * 32);
+  ++step_id_;
+  std::vector<std::pair<int, int>> copies, swap_out, swap_in;
+  int budget = cfg_.max_tokens_per_step;
+
+  struct Item { Sequence* s; int n; };
+  std::vector<Item> decode_items, prefill_items;
+
+  // 1. sequences already running: decode rows take one token, unfinished prompts take a chunk
+  for (size_t i = 0; i < running_.size();) {
+    Sequence* s = find(running_[i]);
+    const int remaining = static_cast<int>(s->tokens.size()) - s->num_computed;
+    int n = std::min({remaining, budget, remaining > 1 ? cfg_.prefill_chunk : 1});
+    if (n <= 0) { s->scheduled = 0; ++i; continue; }
+    bool ok = ensure_pages(*s, s->num_computed + n, copies);
+    while (!ok) {
+      if (!preempt_one(s, swap_out)) break;
+      ok = ensure_pages(*s, s->num_computed + n, copies);
+    }
+    // preempt_one may have removed an element before position i
+    size_t pos = std::find(running_.begin(), running_.end(), s->id) - running_.begin();
+    i = pos;
+    if (!ok) {
+      // alone and still out of pages: this sequence can never advance; fail it
+      finish(*s, FinishReason::Error);
+      continue;
+    }
+    s->scheduled = n;
+    budget -= n;
+    (remaining == 1 ? decode_items : prefill_items).push_back({s, n});
+    ++i;
+  }
+  // drop items whose sequence was preempted after being scheduled
+  auto still_running = [&](const Item& it) { return it.s->status == SeqStatus::Running && it.s->scheduled > 0; };
+  decode_items.erase(std::remove_if(decode_items.begin(), decode_items.end(), [&](const Item& it) { return !still_running(it); }),
+                     decode_items.end());
+  prefill_items.erase(std::remove_if(prefill_items.begin(), prefill_items.end(), [&](const Item& it) { return !still_running(it); }),
+                      prefill_items.end());
+
+  // 2. swapped sequences come back first (they hold progress), then new admissions
+  while (!swapped_.empty() && budget > 0 && static_cast<int>(running_.size()) < cfg_.max_seqs && swap_out.empty()) {
+    Sequence* s = find(swapped_.front());
+    const int used_pages = static_cast<int>(s->host_pages.size());
+    if (used_pages + 1 > pool_.num_free()) break;
+    for (int i = 0; i < used_pages; ++i) {
+      const int p = pool_.allocate();
+      s->pages.push_back(p);
+      swap_in.emplace_back(p, s->host_pages[i]);
+      host_free_.push_back(s->host_pages[i]);
+    }
+    s->host_pages.clear();
+    swapped_.pop_front();
+    s->status = SeqStatus::Running;
+    running_.push_back(s->id);
+    const int remaining = static_cast<int>(s->tokens.size()) - s->num_computed;
+    const int n = std::min({remaining, budget, remaining > 1 ? cfg_.prefill_chunk : 1});
+    if (n > 0 && ensure_pages(*s, s->num_computed + n, copies)) {
+      s->scheduled = n;
+      budget -= n;
+      (remaining == 1 ? decode_items : prefill_items).push_back({s, n});
+    }
+  }
+  if (swapped_.empty() && swap_out.empty()) {
+    for (int64_t id : waiting_order()) {
+      if (budget <= 0 || static_cast<int>(running_.size()) >= cfg_.max_seqs) break;
+      Sequence* s = find(id);
+      if (s->pages.empty() && s->num_computed == 0) try_prefix_attach(*s);
+      const int remaining = static_cast<int>(s->tokens.size()) - s->num_computed;
+      int n = std::min({remaining, budget, cfg_.prefill_chunk});
+      if (n <= 0) break;
+      // keep one page of headroom per running sequence so decode rows are not starved next step
+      const int need = (s->num_computed + n + kPageTokens - 1) / kPageTokens - static_cast<int>(s->pages.size());
+      if (need + static_cast<int>(running_.size()) > pool_.num_free()) {
+        if (s->num_cached_prefix > 0 && s->num_computed == s->num_cached_prefix) {  // give the cached pages back
+          free_pages(*s, false);
+          s->num_computed = 0;
+          s->num_cached_prefix = 0;
+        }
+        break;
+      }
+      if (!ensure_pages(*s, s->num_computed + n, copies)) break;
+      waiting_.erase(std::find(waiting_.begin(), waiting_.end(), id));
+      s->status = SeqStatus::Running;
+      running_.push_back(id);
+      s->scheduled = n;
+      budget -= n;
+      tenant_served_[s->tenant] += n;
+      (remaining == 1 ? decode_items : prefill_items).push_back({s, n});
+    }
+  }
+
+  // 3. optional rounding of the step size: shrink the last prefill chunk so T % token_multiple == 0
+  int total = 0;
+  for (auto& it : decode_items) total += it.n;
+  for (auto& it : prefill_items) total += it.n;
+  if (cfg_.token_multiple > 1 && !prefill_items.empty()) {
+    int excess = total % cfg_.token_multiple;
+    for (int i = static_cast<int>(prefill_items.size()) - 1; i >= 0 && excess > 0; --i) {
+      Item& it = prefill_items[i];
+      const int remaining = static_cast<int>(it.s->tokens.size()) - it.s->num_computed;
+      const bool completes = (it.n == remaining);
+      int cut = std::min(excess, it.n - 1);
+      if (completes && cut > 0 && it.n - cut < 1) cut = 0;
+      if (cut > 0) { it.n -= cut; it.s->scheduled = it.n; excess -= cut; total -= cut; }
+    }
+  }
+
+  // 4. emit the plan: decode rows first, then prefill chunks
+  int t = 0, row = 0, nlog = 0, ntiles = 0, max_ctx = 0;
+  step_rows_.clear();
+  step_seqs_.clear();
+  auto emit = [&](Sequence* s, int n, bool is_prefill, int prefill_token_base) {
+    const int start = s->num_computed;
+    for (int j = 0; j < n; ++j) {
+      const int pos = start + j;
+      plan[L.token_ids + t + j] = s->tokens[pos];
+      plan[L.positions + t + j] = pos;
+      plan[L.slots + t + j] = s->pages[pos / kPageTokens] * kPageTokens + pos % kPageTokens;
+    }
+    const int ctx = start + n;
+    max_ctx = std::max(max_ctx, ctx);
+    plan[L.ctx_len + row] = ctx;
+    plan[L.seq_slot + row] = static_cast<int32_t>(s->id & 0x7fffffff);
+    int32_t* pt = plan + L.page_table + static_cast<size_t>(row) * cfg_.max_pages_per_seq;
+    const int np = static_cast<int>(s->pages.size());
+    for (int j = 0; j < np; ++j) pt[j] = s->pages[j];
+    if (is_prefill) {
+      const int prow = row - static_cast<int>(decode_items.size());
+      plan[L.cu_q + prow] = t - prefill_token_base;
+      plan[L.cu_q + prow + 1] = t - prefill_token_base + n;
+      for (int q0 = 0; q0 < n; q0 += 64) {
+        plan[L.tile_seq + ntiles] = prow;
+        plan[L.tile_q0 + ntiles] = q0;
+        ++ntiles;
+      }
+    }
+    const bool completes = (ctx == static_cast<int>(s->tokens.size()));
+    s->samples_this_step = completes;
+    if (completes) {
+      plan[L.logit_rows + nlog] = t + n - 1;
+      float tmp = s->sampling.temperature;
+      std::memcpy(&plan[L.temperature + nlog], &tmp, 4);
+      plan[L.top_k + nlog] = s->sampling.top_k;
+      tmp = s->sampling.top_p;
+      std::memcpy(&plan[L.top_p + nlog], &tmp, 4);
+      tmp = s->sampling.min_p;
+      std::memcpy(&plan[L.min_p + nlog], &tmp, 4);
+      tmp = (s->sampling.temperature > 0.f) ? next_uniform(*s) : 0.f;
+      std::memcpy(&plan[L.uniform + nlog], &tmp, 4);
+      step_rows_.push_back(s->id);
+      ++nlog;
+    }
+    step_seqs_.push_back(s->id);
+    t += n;
+    ++row;
+  };
+  for (auto& it : decode_items) emit(it.s, it.n, false, 0);
+  const int prefill_base = t;
+  for (auto& it : prefill_items) emit(it.s, it.n, true, prefill_base);
+
+  int ncopy = 0;
+  for (auto& c : copies) {
+    if (ncopy >= cfg_.max_seqs) break;
+    plan[L.copy_src + ncopy] = c.first;
+    plan[L.copy_dst + ncopy] = c.second;
+    ++ncopy;
+  }
+  int nso = 0, nsi = 0;
+  for (auto& c : swap_out) { if (nso < L.max_swap) { plan[L.swap_out_dev + nso] = c.first; plan[L.swap_out_host + nso] = c.second; ++nso; } }
+  for (auto& c : swap_in) { if (nsi < L.max_swap) { plan[L.swap_in_dev + nsi] = c.first; plan[L.swap_in_host + nsi] = c.second; ++nsi; } }
+
+  plan[kHdrNumTokens] = t;
+  plan[kHdrNumDecode] = static_cast<int>(decode_items.size());
+  plan[kHdrNumPrefillSeqs] = static_cast<int>(prefill_items.size());
+  plan[kHdrNumTiles] = ntiles;
+  plan[kHdrNumLogitRows] = nlog;
+  plan[kHdrNumCopies] = ncopy;
+  plan[kHdrNumSwapOut] = nso;
+  plan[kHdrNumSwapIn] = nsi;
+  plan[kHdrNumPrefillTokens] = t - prefill_base;
+  plan[kHdrMaxCtx] = max_ctx;
+  plan[kHdrNumPreempted] = static_cast<int>(preemptions_ & 0x7fffffff);
+  plan[kHdrStepId] = static_cast<int>(step_id_ & 0x7fffffff);
+  return t;
+}
+
+void Core::finish(Sequence& s, FinishReason why) {
+  s.finish = why;
+  s.status = SeqStatus::Finished;
+  s.scheduled = 0;
+  free_pages(s, why != FinishReason::Error);
+  for (int hp : s.host_pages) host_free_.push_back(hp);
+  s.host_pages.clear();
+  running_.erase(std::remove(running_.begin(), running_.end(), s.id), running_.end());
+  waiting_.erase(std::remove(waiting_.begin(), waiting_.end(), s.id), waiting_.end());
+  swapped_.erase(std::remove(swapped_.begin(), swapped_.end(), s.id), swapped_.end());
+}
+
+int Core::commit_step(const int32_t* sampled, int n, StepEvent* events, int max_events) {
+  int ne = 0;
+  // advance every scheduled sequence
+  for (int64_t id : step_seqs_) {
+    Sequence* s = find(id);
+    if (!s || s->status != SeqStatus::Running) continue;
+    s->num_computed += s->scheduled;
+    s->scheduled = 0;
+  }
+  const int rows = std::min(n, static_cast<int>(step_rows_.size()));
+  for (int r = 0; r < rows; ++r) {
+    Sequence* s = find(step_rows_[r]);
+    if (!s || s->status != SeqStatus::Running || !s->samples_this_step) continue;
+    s->samples_this_step = false;
+    const int32_t tok = sampled[r];
+    s->tokens.push_back(tok);
+    const int generated = static_cast<int>(s->tokens.size()) - s->prompt_len;
+    FinishReason why = FinishReason::None;
+    if (!s->ignore_eos && cfg_.eos_token >= 0 && tok == cfg_.eos_token) why = FinishReason::Stop;
+    for (int32_t st : s->stop_ids) if (tok == st) why = FinishReason::Stop;
+    if (why == FinishReason::None && generated >= s->max_new_tokens) why = FinishReason::Length;
+    if (why != FinishReason::None) finish(*s, why);
+    if (ne < max_events) events[ne++] = StepEvent{s->id, tok, static_cast<int32_t>(why)};
+  }
+  step_rows_.clear();
+  step_seqs_.clear();
+  return ne;
+}
+
+bool Core::cancel(int64_t seq_id) {
+  Sequence* s = find(seq_id);
+  if (!s || s->status == SeqStatus::Finished) return false;
+  finish(*s, FinishReason::Cancelled);
+  return true;
+}
+
+int64_t Core::fork(int64_t seq_id) {
+  Sequence* s = find(seq_id);
+  if (!s) return -1;
+  Sequence c = *s;
+  c.id = next_id_++;
+  c.arrival = clock_++;
+  c.host_pages.clear();
+  c.scheduled = 0;
+  c.samples_this_step = false;
+  c.rng_state ^= 0xD1B54A32D192ED03ull * static_cast<uint64_t>(c.id);
+  for (int p : c.pages) pool_.retain(p);
+  if (s->status == SeqStatus::Swapped) {  // a swapped parent has no device pages to share
+    c.pages.clear();
+    c.num_computed = 0;
+    c.status = SeqStatus::Waiting;
+  }
+  if (c.status == SeqStatus::Finished) { c.status = SeqStatus::Waiting; c.finish = FinishReason::None; }
+  const int64_t id = c.id;
+  const SeqStatus st = c.status;
+  seqs_.emplace(id, std::move(c));
+  if (st == SeqStatus::Running) running_.push_back(id); else waiting_.push_back(id);
+  return id;
+}
+
+bool Core::rewind(int64_t seq_id, int new_len) {
+  Sequence* s = find(seq_id);
+  if (!s || new_len < 1 || new_len > static_cast<int>(s->tokens.size())) return false;
+  s->tokens.resize(new_len);
+  if (s->prompt_len > new_len) s->prompt_len = new_len;
+  // the last kept token must be re-run to produce logits unless its successor is about to be fed
+  if (s->num_computed > new_len) s->num_computed = new_len;
+  const int keep_pages = (s->num_computed + kPageTokens - 1) / kPageTokens;
+  while (static_cast<int>(s->pages.size()) > keep_pages) {
+    pool_.release(s->pages.back());
+    s->pages.pop_back();
+  }
+  return true;
+}
+
+int Core::seq_len(int64_t seq_id) const {
+  const Sequence* s = find(seq_id);
+  return s ? static_cast<int>(s->tokens.size()) : -1;
+}
+
+int Core::seq_tokens(int64_t seq_id, int32_t* out, int cap) const {
+  const Sequence* s = find(seq_id);
+  if (!s) return -1;
+  const int n = std::min(cap, static_cast<int>(s->tokens.size()));
+  std::memcpy(out, s->tokens.data(), sizeof(int32_t) * n);
+  return static_cast<int>(s->tokens.size());
+}
+
+void Core::release(int64_t seq_id) {
+  Sequence* s = find(seq_id);
+  if (!s) return;
+  if (s->status != SeqStatus::Finished) finish(*s, FinishReason::Cancelled);
+  seqs_.erase(seq_id);
+}
+
+}  // namespace ogb
+
+// ------------------------------------------------------------------------------------------
+// C ABI for ctypes
+// ------------------------------------------------------------------------------------------
+using namespace ogb;
+
+extern "C" {
+
+void* ogb_core_create(int num_pages, int num_host_pages, int max_seqs, int max_tokens_per_step, int max_pages_per_seq,
+                      int prefill_chunk, int token_multiple, int policy, int preempt_mode, int enable_prefix_cache,
+                      int eos_token) {
+  CoreConfig c;
+  c.num_pages = num_pages;
+  c.num_host_pages = num_host_pages;
+  c.max_seqs = max_seqs;
+  c.max_tokens_per_step = max_tokens_per_step;
+  c.max_pages_per_seq = max_pages_per_seq;
+  c.prefill_chunk = prefill_chunk;
+  c.token_multiple = token_multiple;
+  c.policy = static_cast<Policy>(policy);
+  c.preempt = static_cast<PreemptMode>(preempt_mode);
+  c.enable_prefix_cache = enable_prefix_cache != 0;
+  c.eos_token = eos_token;
+  return new Core(c);
+}
+void ogb_core_destroy(void* h) { delete static_cast<Core*>(h); }
+int ogb_core_layout(void* h, int32_t* out, int cap) {
+  const PlanLayout& l = static_cast<Core*>(h)->layout();
+  const int32_t v[] = {l.header, l.token_ids, l.positions, l.slots, l.seq_slot, l.ctx_len, l.cu_q, l.page_table,
+                       l.tile_seq, l.tile_q0, l.logit_rows, l.temperature, l.top_k, l.top_p, l.min_p, l.uniform,
+                       l.copy_src, l.copy_dst, l.swap_out_dev, l.swap_out_host, l.swap_in_dev, l.swap_in_host,
+                       l.total_words, l.max_tiles, l.max_swap};
+  const int n = static_cast<int>(sizeof(v) / sizeof(v[0]));
+  for (int i = 0; i < n && i < cap; ++i) out[i] = v[i];
+  return n;
+}
+int64_t ogb_core_add_request(void* h, const int32_t* prompt, int n, int max_new_tokens, float temperature, int top_k,
+                             float top_p, float min_p, uint64_t seed, int priority, int tenant, int ignore_eos,
+                             const int32_t* stop_ids, int n_stop) {
+  SamplingParams sp;
+  sp.temperature = temperature;
+  sp.top_k = top_k;
+  sp.top_p = top_p;
+  sp.min_p = min_p;
+  sp.seed = seed;
+  return static_cast<Core*>(h)->add_request(prompt, n, max_new_tokens, sp, priority, tenant, ignore_eos != 0, stop_ids, n_stop);
+}
+int ogb_core_build_step(void* h, int32_t* plan) { return static_cast<Core*>(h)->build_step(plan); }
+int ogb_core_commit_step(void* h, const int32_t* sampled, int n, int64_t* ev_seq, int32_t* ev_token, int32_t* ev_finish,
+                         int max_events) {
+  std::vector<StepEvent> ev(max_events > 0 ? max_events : 1);
+  const int ne = static_cast<Core*>(h)->commit_step(sampled, n, ev.data(), max_events);
+  for (int i = 0; i < ne; ++i) { ev_seq[i] = ev[i].seq_id; ev_token[i] = ev[i].token; ev_finish[i] = ev[i].finish; }
+  return ne;
+}
+int ogb_core_cancel(void* h, int64_t id) { return static_cast<Core*>(h)->cancel(id) ? 1 : 0; }
+int64_t ogb_core_fork(void* h, int64_t id) { return static_cast<Core*>(h)->fork(id); }
+int ogb_core_rewind(void* h, int64_t id, int new_len) { return static_cast<Core*>(h)->rewind(id, new_len) ? 1 : 0; }
+int ogb_core_seq_len(void* h, int64_t id) { return static_cast<Core*>(h)->seq_len(id); }
+int ogb_core_seq_tokens(void* h, int64_t id, int32_t* out, int cap) { return static_cast<Core*>(h)->seq_tokens(id, out, cap); }
+void ogb_core_release(void* h, int64_t id) { static_cast<Core*>(h)->release(id); }
+int64_t ogb_core_stat(void* h, int which) {
+  Core* c = static_cast<Core*>(h);
+  switch (which) {
+    case 0: return c->num_waiting();
+    case 1: return c->num_running();
+    case 2: return c->num_swapped();
+    case 3: return c->num_free_pages();
+    case 4: return c->prefix_hits();
+    case 5: return c->prefix_lookups();
+    case 6: return c->num_preemptions();
+    case 7: return c->has_work() ? 1 : 0;
+    default: return -1;
+  }
+}
+
+}  // extern "C"

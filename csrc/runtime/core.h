@@ -1,0 +1,191 @@
+// Host runtime core: paged-KV block pool, prefix cache, continuous-batching scheduler and the
+// step builder that fills one packed int32 plan per engine step.
+//
+// What it covers of the reference:
+//   * page table / pages / CoW fork / rewind / checkpoint (crates/onnx-genai-kv/src/page_table.rs:943-1905,
+//     paged_cache.rs:913-1085) -- here page *ids* only; the bytes live in the device pool that the
+//     attention kernels read directly;
+//   * prefix radix trie with ref-counted pages (crates/onnx-genai-kv/src/prefix_cache.rs:24-370) -- here
+//     a chained block hash -> page map with LRU reuse of unreferenced cached pages;
+//   * scheduler: FCFS / priority / fair-share admission, token and page budgets, swap or recompute
+//     preemption (crates/onnx-genai-scheduler/src/lib.rs:133-145,245-601, policy.rs:7-80);
+//   * continuous batching (crates/onnx-genai-engine/src/batched.rs:340-368,663-749) -- but with chunked
+//     multi-token prefill mixed into decode steps and preemption of batched rows, which the
+//     reference's one-token-per-row manager does not do;
+//   * per-request RNG: one uniform per sampled token, independent of the batch row
+//     (crates/onnx-genai-engine/src/sampling.rs:9-32).
+#pragma once
+#include <cstdint>
+#include <deque>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+namespace ogb {
+
+constexpr int kPageTokens = 16;
+
+enum class SeqStatus : int { Waiting = 0, Running = 1, Swapped = 2, Finished = 3 };
+enum class FinishReason : int { None = 0, Length = 1, Stop = 2, Cancelled = 3, Error = 4 };
+enum class Policy : int { Fcfs = 0, Priority = 1, FairShare = 2 };
+enum class PreemptMode : int { Recompute = 0, Swap = 1 };
+
+struct SamplingParams {
+  float temperature = 0.f;  // <= 0: greedy
+  int top_k = 0;
+  float top_p = 1.f;
+  float min_p = 0.f;
+  uint64_t seed = 0;
+};
+
+struct Sequence {
+  int64_t id = 0;
+  std::vector<int32_t> tokens;   // prompt + generated
+  int prompt_len = 0;
+  int num_computed = 0;          // tokens whose K/V are in the cache
+  int max_new_tokens = 0;
+  int priority = 0;              // higher runs first under Policy::Priority
+  int tenant = 0;                // fair-share bucket
+  int64_t arrival = 0;
+  bool ignore_eos = false;
+  std::vector<int32_t> stop_ids;
+  SamplingParams sampling;
+  uint64_t rng_state = 0;
+  SeqStatus status = SeqStatus::Waiting;
+  FinishReason finish = FinishReason::None;
+  std::vector<int32_t> pages;        // device page ids, one per 16 tokens
+  std::vector<int32_t> host_pages;   // swap space page ids while Swapped
+  int num_cached_prefix = 0;         // tokens served from the prefix cache at admission
+  int scheduled = 0;                 // tokens scheduled in the step being built
+  bool samples_this_step = false;
+};
+
+// Reference-counted device pages with a prefix cache over full pages.
+class BlockPool {
+ public:
+  explicit BlockPool(int num_pages);
+  int num_pages() const { return static_cast<int>(ref_.size()); }
+  int num_free() const { return static_cast<int>(free_.size() + evictable_.size()); }
+  int allocate();                    // -1 when exhausted
+  void retain(int page) { ++ref_[page]; }
+  void release(int page);            // refcount--; cached pages become evictable, others free
+  int refcount(int page) const { return ref_[page]; }
+  // prefix cache
+  static uint64_t chain_hash(uint64_t parent, const int32_t* tokens, int n);
+  int lookup(uint64_t hash);         // page id (retained) or -1
+  void publish(int page, uint64_t hash);
+  int64_t hits() const { return hits_; }
+  int64_t lookups() const { return lookups_; }
+  void reset_prefix_cache();
+
+ private:
+  std::vector<int> ref_;
+  std::vector<uint64_t> hash_of_;    // 0 = not cached
+  std::vector<int> free_;
+  std::deque<int> evictable_;        // cached, refcount 0, LRU order (front = oldest)
+  std::vector<uint8_t> in_evictable_;
+  std::unordered_map<uint64_t, int> by_hash_;
+  int64_t hits_ = 0, lookups_ = 0;
+};
+
+struct CoreConfig {
+  int num_pages = 0;
+  int num_host_pages = 0;        // swap space
+  int max_seqs = 256;            // concurrent running sequences
+  int max_tokens_per_step = 2048;
+  int max_pages_per_seq = 256;
+  int prefill_chunk = 2048;      // per-sequence cap of prompt tokens per step
+  int token_multiple = 1;        // pad-free rounding of the step size (prefill chunks shrink to fit)
+  Policy policy = Policy::Fcfs;
+  PreemptMode preempt = PreemptMode::Recompute;
+  bool enable_prefix_cache = true;
+  int eos_token = -1;
+};
+
+// Offsets (in int32 words) of the sections of a packed step plan.
+struct PlanLayout {
+  int header = 0;        // 32 words
+  int token_ids, positions, slots;           // [max_tokens]
+  int seq_slot, ctx_len;                     // [max_seqs]
+  int cu_q;                                  // [max_seqs + 1]  (prefill rows only, relative to first prefill token)
+  int page_table;                            // [max_seqs * max_pages_per_seq]
+  int tile_seq, tile_q0;                     // [max_tiles]
+  int logit_rows;                            // [max_seqs]
+  int temperature, top_k, top_p, min_p, uniform;  // [max_seqs] (floats stored by bit pattern)
+  int copy_src, copy_dst;                    // [max_seqs] CoW page copies to run before the step
+  int swap_out_dev, swap_out_host, swap_in_dev, swap_in_host;  // [max_swap]
+  int total_words;
+  int max_tiles, max_swap;
+};
+
+enum PlanHeader : int {
+  kHdrNumTokens = 0, kHdrNumDecode, kHdrNumPrefillSeqs, kHdrNumTiles, kHdrNumLogitRows, kHdrNumCopies,
+  kHdrNumSwapOut, kHdrNumSwapIn, kHdrNumPrefillTokens, kHdrMaxCtx, kHdrNumPreempted, kHdrStepId,
+};
+
+struct StepEvent {
+  int64_t seq_id;
+  int32_t token;      // -1 when the event only reports a state change
+  int32_t finish;     // FinishReason
+};
+
+class Core {
+ public:
+  explicit Core(const CoreConfig& cfg);
+  const CoreConfig& config() const { return cfg_; }
+  const PlanLayout& layout() const { return layout_; }
+
+  int64_t add_request(const int32_t* prompt, int n, int max_new_tokens, const SamplingParams& sp, int priority, int tenant,
+                      bool ignore_eos, const int32_t* stop_ids, int n_stop);
+  bool cancel(int64_t seq_id);
+  // Builds the next step into `plan` (layout().total_words int32 words).  Returns the number of tokens scheduled.
+  int build_step(int32_t* plan);
+  // Consumes the sampled tokens of the last built step (one per logit row, in row order).
+  int commit_step(const int32_t* sampled, int n, StepEvent* events, int max_events);
+
+  // session-style operations on a live sequence
+  int64_t fork(int64_t seq_id);                    // copy-on-write clone (shares pages)
+  bool rewind(int64_t seq_id, int new_len);        // drop trailing tokens and their pages
+  int seq_len(int64_t seq_id) const;
+  int seq_tokens(int64_t seq_id, int32_t* out, int cap) const;
+  void release(int64_t seq_id);                    // forget a finished sequence
+
+  int num_waiting() const { return static_cast<int>(waiting_.size()); }
+  int num_running() const { return static_cast<int>(running_.size()); }
+  int num_swapped() const { return static_cast<int>(swapped_.size()); }
+  int num_free_pages() const { return pool_.num_free(); }
+  int64_t prefix_hits() const { return pool_.hits(); }
+  int64_t prefix_lookups() const { return pool_.lookups(); }
+  int64_t num_preemptions() const { return preemptions_; }
+  bool has_work() const { return !waiting_.empty() || !running_.empty() || !swapped_.empty(); }
+
+ private:
+  Sequence* find(int64_t id);
+  const Sequence* find(int64_t id) const;
+  bool ensure_pages(Sequence& s, int new_len, std::vector<std::pair<int, int>>& copies);
+  void free_pages(Sequence& s, bool publish_prefix);
+  void try_prefix_attach(Sequence& s);
+  void publish_full_pages(Sequence& s);
+  bool preempt_one(Sequence* keep, std::vector<std::pair<int, int>>& swap_out);
+  std::vector<int64_t> waiting_order();
+  float next_uniform(Sequence& s);
+  void finish(Sequence& s, FinishReason why);
+
+  CoreConfig cfg_;
+  PlanLayout layout_;
+  BlockPool pool_;
+  std::vector<int> host_free_;
+  std::unordered_map<int64_t, Sequence> seqs_;
+  std::deque<int64_t> waiting_;
+  std::vector<int64_t> running_;
+  std::deque<int64_t> swapped_;
+  std::vector<int64_t> step_rows_;       // sequence of each logit row of the last built step
+  std::vector<int64_t> step_seqs_;       // every sequence scheduled in the last built step
+  std::unordered_map<int, int64_t> tenant_served_;
+  int64_t next_id_ = 1;
+  int64_t clock_ = 0;
+  int64_t step_id_ = 0;
+  int64_t preemptions_ = 0;
+};
+
+}  // namespace ogb

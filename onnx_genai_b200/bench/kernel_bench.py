@@ -1,0 +1,187 @@
+"""CUDA-event microbenchmarks of the hot kernels against their rooflines.
+
+Counterpart of the reference's roofline probes and kernel benches
+(crates/onnx-genai-bench/src/bin/roofline_gemv.rs, marlin_bench.rs).  Every timing follows the
+same hygiene: >= 3 warm-up launches, an L2 flush (a write larger than the 126 MB L2) before each
+timed launch, CUDA events on the launching stream.  Peaks come from MEASURED_PEAKS.json when it
+is present next to the repository root, otherwise from the documented fallback figures.
+
+    python -m onnx_genai_b200.bench.kernel_bench --what gemm,attn --json out.json
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+from pathlib import Path
+
+import torch
+
+from .. import ops
+from ..ops import reference as ref
+
+
+def peaks():
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class Timer:
+    def __init__(self, flush_mb=256):
+        self.flush = torch.empty(flush_mb * 1024 * 1024, dtype=torch.uint8, device="cuda")
+
+    def time(self, fn, iters=10, warmup=3):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            self.flush.zero_()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e))
+        ts.sort()
+        return ts[len(ts) // 2], ts[0]
+
+
+def bench_gemm(timer, pk, shapes=None):
+    rows = []
+    shapes = shapes or [
+        # (M, N, K, epilogue) -- Qwen2.5-7B projections at decode / mixed / prefill step sizes
+        (256, 4608, 3584, "none"), (256, 3584, 3584, "residual"), (256, 37888, 3584, "swiglu"), (256, 3584, 18944, "residual"),
+        (1280, 4608, 3584, "none"), (1280, 3584, 3584, "residual"), (1280, 37888, 3584, "swiglu"), (1280, 3584, 18944, "residual"),
+        (2048, 4608, 3584, "none"), (2048, 37888, 3584, "swiglu"), (2048, 3584, 18944, "residual"),
+        (256, 152064, 3584, "none"), (8192, 8192, 8192, "none"),
+    ]
+    for m, n, k, epi in shapes:
+        a = (torch.randn(m, k, device="cuda") * 0.1).bfloat16()
+        w = (torch.randn(n, k, device="cuda") * 0.02).bfloat16()
+        res = torch.randn(m, n, device="cuda").bfloat16() if epi == "residual" else None
+        n_out = n // 2 if epi == "swiglu" else n
+        out = torch.empty(m, n_out, device="cuda", dtype=torch.bfloat16)
+        best = None
+        for bn in ((256, 128) if epi == "swiglu" else (256, 128, 64)):
+            if epi == "swiglu":
+                fn = lambda: ops.gemm(a, w, epilogue="swiglu", swiglu_half=bn // 2, out=out)
+            elif epi == "residual":
+                fn = lambda: ops.gemm(a, w, residual=res, epilogue="residual", out=out, bn=bn)
+            else:
+                fn = lambda: ops.gemm(a, w, out=out, bn=bn)
+            med, mn = timer.time(fn)
+            if best is None or med < best[0]:
+                best = (med, mn, bn)
+        full = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        lib_med, _ = timer.time(lambda: torch.matmul(a, w.t(), out=full))
+        flops = 2.0 * m * n * k
+        byts = 2.0 * (m * k + n * k + m * n_out)
+        tf = flops / best[0] / 1e9
+        rows.append({
+            "kernel": "gemm_bf16_tcgen05", "M": m, "N": n, "K": k, "epilogue": epi, "bn": best[2],
+            "ms": round(best[0], 4), "tflops": round(tf, 1), "frac_of_%s_bf16_peak" % pk["source"]: round(tf / pk["bf16_tflops"], 3),
+            "gbs": round(byts / best[0] / 1e6, 1), "frac_of_%s_hbm" % pk["source"]: round(byts / best[0] / 1e6 / pk["hbm_gbs"], 3),
+            "cublas_ms": round(lib_med, 4), "vs_cublas": round(lib_med / best[0], 3),
+        })
+        print(json.dumps(rows[-1]), flush=True)
+    ops.check_status()
+    return rows
+
+
+def bench_attention(timer, pk):
+    rows = []
+    hq, hkv, d = 28, 4, 128
+    for n, ctx in [(256, 1200), (256, 2304), (64, 8192), (8, 32768)]:
+        pages_per = (ctx + 15) // 16
+        total = n * pages_per
+        pool = (torch.randn(total, hkv, 2, 16, d, device="cuda") * 0.5).bfloat16()
+        table = torch.randperm(total, device="cuda").to(torch.int32).view(n, pages_per)
+        ctx_t = torch.full((n,), ctx, dtype=torch.int32, device="cuda")
+        q = torch.randn(n, (hq + 2 * hkv) * d, device="cuda").bfloat16()
+        out = torch.empty(n, hq * d, device="cuda", dtype=torch.bfloat16)
+        for splits in (1, 2, 4, 8, 16):
+            if n * hkv * splits > 148 * 16 and splits > 1:
+                continue
+            po = torch.empty(n * hq * splits * d, dtype=torch.float32, device="cuda")
+            pm = torch.empty(n * hq * splits * 2, dtype=torch.float32, device="cuda")
+            med, _ = timer.time(lambda: ops.paged_decode(q, out, pool, table, ctx_t, hq, hkv, d, num_splits=splits,
+                                                         part_o=po, part_ml=pm))
+            byts = float(n) * ctx * hkv * 2 * d * 2
+            rows.append({"kernel": "paged_decode", "seqs": n, "ctx": ctx, "splits": splits, "ms": round(med, 4),
+                         "gbs": round(byts / med / 1e6, 1),
+                         "frac_of_%s_hbm" % pk["source"]: round(byts / med / 1e6 / pk["hbm_gbs"], 3)})
+            print(json.dumps(rows[-1]), flush=True)
+        del pool
+    for q_len, past in [(1024, 0), (2048, 0), (512, 1536)]:
+        nseq = 4
+        ctx = q_len + past
+        pages_per = (ctx + 15) // 16
+        total = nseq * pages_per
+        pool = (torch.randn(total, hkv, 2, 16, d, device="cuda") * 0.5).bfloat16()
+        table = torch.randperm(total, device="cuda").to(torch.int32).view(nseq, pages_per)
+        ctx_t = torch.full((nseq,), ctx, dtype=torch.int32, device="cuda")
+        t = nseq * q_len
+        q = torch.randn(t, (hq + 2 * hkv) * d, device="cuda").bfloat16()
+        out = torch.empty(t, hq * d, device="cuda", dtype=torch.bfloat16)
+        cu = torch.arange(0, t + 1, q_len, dtype=torch.int32, device="cuda")
+        ts, tq = ops.prefill_tiles([q_len] * nseq)
+        tsd = torch.tensor(ts, dtype=torch.int32, device="cuda")
+        tqd = torch.tensor(tq, dtype=torch.int32, device="cuda")
+        med, _ = timer.time(lambda: ops.paged_prefill(q, out, pool, table, ctx_t, cu, tsd, tqd, len(ts), hq, hkv, d))
+        flops = 4.0 * nseq * hq * d * (q_len * past + q_len * (q_len + 1) / 2)
+        rows.append({"kernel": "paged_prefill", "seqs": nseq, "q_len": q_len, "past": past, "ms": round(med, 4),
+                     "tflops": round(flops / med / 1e9, 1)})
+        print(json.dumps(rows[-1]), flush=True)
+    ops.check_status()
+    return rows
+
+
+def bench_misc(timer, pk):
+    rows = []
+    x = torch.randn(1280, 3584, device="cuda").bfloat16()
+    w = torch.randn(3584, device="cuda").bfloat16()
+    out = torch.empty_like(x)
+    med, _ = timer.time(lambda: ops.rmsnorm(x, w, 1e-6, out=out))
+    rows.append({"kernel": "rmsnorm", "rows": 1280, "hidden": 3584, "ms": round(med, 4),
+                 "gbs": round(2 * x.numel() * 2 / med / 1e6, 1)})
+    logits = torch.randn(256, 152064, device="cuda").bfloat16()
+    temp = torch.full((256,), 0.7, device="cuda")
+    tk = torch.zeros(256, dtype=torch.int32, device="cuda")
+    tp = torch.full((256,), 0.9, device="cuda")
+    mp = torch.zeros(256, device="cuda")
+    u = torch.rand(256, device="cuda")
+    work = torch.empty(256 * 152064, dtype=torch.int32, device="cuda")
+    med, _ = timer.time(lambda: ops.sample(logits, temp, tk, tp, mp, u, work=work))
+    rows.append({"kernel": "sample_topp", "rows": 256, "vocab": 152064, "ms": round(med, 4)})
+    med, _ = timer.time(lambda: ops.argmax(logits))
+    rows.append({"kernel": "argmax", "rows": 256, "vocab": 152064, "ms": round(med, 4)})
+    for r in rows:
+        print(json.dumps(r), flush=True)
+    return rows
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--what", default="gemm,attn,misc")
+    ap.add_argument("--json", default="")
+    args = ap.parse_args()
+    pk = peaks()
+    timer = Timer()
+    res = {"peaks": pk}
+    what = args.what.split(",")
+    if "gemm" in what:
+        res["gemm"] = bench_gemm(timer, pk)
+    if "attn" in what:
+        res["attn"] = bench_attention(timer, pk)
+    if "misc" in what:
+        res["misc"] = bench_misc(timer, pk)
+    if args.json:
+        Path(args.json).write_text(json.dumps(res, indent=1))
+
+
+if __name__ == "__main__":
+    main()

@@ -116,7 +116,7 @@ def build_runtime(force: bool = False, verbose: bool = False) -> Path:
         return RUNTIME_LIB
     LIB_DIR.mkdir(parents=True, exist_ok=True)
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
-    cxx = os.environ.get("CXX", "g++")
+    cxx = os.environ.get("OGB_CXX") or shutil.which("g++") or "g++"
     inc = ["-I", str(ROOT / "csrc"), "-I", str(ROOT / "csrc" / "capi")]
 
     def one(src: Path) -> Path:

@@ -1,0 +1,179 @@
+"""ctypes binding of the C++ runtime core (scheduler + paged-KV block pool + step builder).
+
+The reference splits this across `onnx-genai-scheduler` and `onnx-genai-kv`
+(crates/onnx-genai-scheduler/src/lib.rs:199-760, crates/onnx-genai-kv/src/paged_cache.rs:57-1085);
+the C++ restatement lives in csrc/runtime/core.{h,cpp}.  A step is exchanged as one packed int32
+plan written straight into pinned host memory, so the per-step host work is one C call plus one
+host-to-device copy.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, c_float, c_int, c_int32, c_int64, c_uint64, c_void_p
+from dataclasses import dataclass
+from pathlib import Path
+
+import numpy as np
+
+_LIB = None
+
+POLICIES = {"fcfs": 0, "priority": 1, "fair_share": 2}
+PREEMPT = {"recompute": 0, "swap": 1}
+FINISH = {0: None, 1: "length", 2: "stop", 3: "cancelled", 4: "error"}
+
+HDR = dict(num_tokens=0, num_decode=1, num_prefill_seqs=2, num_tiles=3, num_logit_rows=4, num_copies=5,
+           num_swap_out=6, num_swap_in=7, num_prefill_tokens=8, max_ctx=9, num_preempted=10, step_id=11)
+
+_LAYOUT_FIELDS = ["header", "token_ids", "positions", "slots", "seq_slot", "ctx_len", "cu_q", "page_table", "tile_seq",
+                  "tile_q0", "logit_rows", "temperature", "top_k", "top_p", "min_p", "uniform", "copy_src", "copy_dst",
+                  "swap_out_dev", "swap_out_host", "swap_in_dev", "swap_in_host", "total_words", "max_tiles", "max_swap"]
+
+
+def load_runtime():
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = Path(__file__).resolve().parent.parent / "_lib" / "libogb_runtime.so"
+    try:
+        from .. import build as _build
+
+        path = _build.build_runtime()
+    except Exception as exc:
+        if not path.exists():
+            raise RuntimeError(f"runtime library {path} is missing and could not be built: {exc}") from exc
+    lib = ctypes.CDLL(str(path))
+    P = c_void_p
+    I32P = POINTER(c_int32)
+    lib.ogb_core_create.argtypes = [c_int] * 11
+    lib.ogb_core_create.restype = P
+    lib.ogb_core_destroy.argtypes = [P]
+    lib.ogb_core_layout.argtypes = [P, I32P, c_int]
+    lib.ogb_core_layout.restype = c_int
+    lib.ogb_core_add_request.argtypes = [P, I32P, c_int, c_int, c_float, c_int, c_float, c_float, c_uint64, c_int, c_int,
+                                         c_int, I32P, c_int]
+    lib.ogb_core_add_request.restype = c_int64
+    lib.ogb_core_build_step.argtypes = [P, c_void_p]
+    lib.ogb_core_build_step.restype = c_int
+    lib.ogb_core_commit_step.argtypes = [P, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int]
+    lib.ogb_core_commit_step.restype = c_int
+    for name in ("ogb_core_cancel",):
+        getattr(lib, name).argtypes = [P, c_int64]
+        getattr(lib, name).restype = c_int
+    lib.ogb_core_fork.argtypes = [P, c_int64]
+    lib.ogb_core_fork.restype = c_int64
+    lib.ogb_core_rewind.argtypes = [P, c_int64, c_int]
+    lib.ogb_core_rewind.restype = c_int
+    lib.ogb_core_seq_len.argtypes = [P, c_int64]
+    lib.ogb_core_seq_len.restype = c_int
+    lib.ogb_core_seq_tokens.argtypes = [P, c_int64, I32P, c_int]
+    lib.ogb_core_seq_tokens.restype = c_int
+    lib.ogb_core_release.argtypes = [P, c_int64]
+    lib.ogb_core_stat.argtypes = [P, c_int]
+    lib.ogb_core_stat.restype = c_int64
+    _LIB = lib
+    return lib
+
+
+@dataclass
+class CoreConfig:
+    num_pages: int
+    num_host_pages: int = 0
+    max_seqs: int = 256
+    max_tokens_per_step: int = 2048
+    max_pages_per_seq: int = 256
+    prefill_chunk: int = 2048
+    token_multiple: int = 1
+    policy: str = "fcfs"
+    preempt: str = "recompute"
+    enable_prefix_cache: bool = True
+    eos_token: int = -1
+
+
+class Layout:
+    def __init__(self, values):
+        for k, v in zip(_LAYOUT_FIELDS, values):
+            setattr(self, k, int(v))
+
+
+class Core:
+    """Owner of all sequence / page bookkeeping.  Not thread-safe: one driver thread owns it."""
+
+    def __init__(self, cfg: CoreConfig):
+        self.cfg = cfg
+        self.lib = load_runtime()
+        self.h = self.lib.ogb_core_create(cfg.num_pages, cfg.num_host_pages, cfg.max_seqs, cfg.max_tokens_per_step,
+                                          cfg.max_pages_per_seq, cfg.prefill_chunk, cfg.token_multiple,
+                                          POLICIES[cfg.policy], PREEMPT[cfg.preempt], int(cfg.enable_prefix_cache),
+                                          cfg.eos_token)
+        buf = (c_int32 * 32)()
+        n = self.lib.ogb_core_layout(self.h, buf, 32)
+        self.layout = Layout(list(buf)[:n])
+        self._ev_seq = np.zeros(cfg.max_seqs, dtype=np.int64)
+        self._ev_tok = np.zeros(cfg.max_seqs, dtype=np.int32)
+        self._ev_fin = np.zeros(cfg.max_seqs, dtype=np.int32)
+
+    def __del__(self):
+        try:
+            if self.h:
+                self.lib.ogb_core_destroy(self.h)
+                self.h = None
+        except Exception:
+            pass
+
+    def add_request(self, prompt, max_new_tokens, temperature=0.0, top_k=0, top_p=1.0, min_p=0.0, seed=0, priority=0,
+                    tenant=0, ignore_eos=False, stop_ids=()):
+        arr = np.ascontiguousarray(prompt, dtype=np.int32)
+        stop = np.ascontiguousarray(stop_ids, dtype=np.int32)
+        sid = self.lib.ogb_core_add_request(
+            self.h, arr.ctypes.data_as(POINTER(c_int32)), len(arr), int(max_new_tokens), float(temperature), int(top_k),
+            float(top_p), float(min_p), int(seed) & 0xFFFFFFFFFFFFFFFF, int(priority), int(tenant), int(ignore_eos),
+            stop.ctypes.data_as(POINTER(c_int32)), len(stop))
+        if sid == -1:
+            raise ValueError("empty prompt or negative max_new_tokens")
+        if sid == -2:
+            raise ValueError(f"prompt of {len(arr)} tokens does not fit max_pages_per_seq={self.cfg.max_pages_per_seq} "
+                             f"({self.cfg.max_pages_per_seq * 16} tokens); raise it or shorten the prompt")
+        return int(sid)
+
+    def build_step(self, plan_ptr: int) -> int:
+        return self.lib.ogb_core_build_step(self.h, plan_ptr)
+
+    def commit_step(self, sampled_ptr: int, n: int):
+        ne = self.lib.ogb_core_commit_step(self.h, sampled_ptr, n, self._ev_seq.ctypes.data, self._ev_tok.ctypes.data,
+                                           self._ev_fin.ctypes.data, len(self._ev_seq))
+        return [(int(self._ev_seq[i]), int(self._ev_tok[i]), FINISH[int(self._ev_fin[i])]) for i in range(ne)]
+
+    def cancel(self, sid):
+        return bool(self.lib.ogb_core_cancel(self.h, sid))
+
+    def fork(self, sid):
+        return int(self.lib.ogb_core_fork(self.h, sid))
+
+    def rewind(self, sid, new_len):
+        return bool(self.lib.ogb_core_rewind(self.h, sid, new_len))
+
+    def seq_len(self, sid):
+        return int(self.lib.ogb_core_seq_len(self.h, sid))
+
+    def seq_tokens(self, sid):
+        n = self.seq_len(sid)
+        if n < 0:
+            raise KeyError(sid)
+        out = np.zeros(n, dtype=np.int32)
+        self.lib.ogb_core_seq_tokens(self.h, sid, out.ctypes.data_as(POINTER(c_int32)), n)
+        return out
+
+    def release(self, sid):
+        self.lib.ogb_core_release(self.h, sid)
+
+    def _stat(self, i):
+        return int(self.lib.ogb_core_stat(self.h, i))
+
+    num_waiting = property(lambda self: self._stat(0))
+    num_running = property(lambda self: self._stat(1))
+    num_swapped = property(lambda self: self._stat(2))
+    num_free_pages = property(lambda self: self._stat(3))
+    prefix_hits = property(lambda self: self._stat(4))
+    prefix_lookups = property(lambda self: self._stat(5))
+    num_preemptions = property(lambda self: self._stat(6))
+    has_work = property(lambda self: bool(self._stat(7)))

@@ -1,0 +1,271 @@
+"""Continuous-batching engine: C++ scheduler core + fused decoder executor + device sampler.
+
+Role of `Engine` + `ContinuousBatchManager` in the reference
+(crates/onnx-genai-engine/src/engine/runtime.rs:340-1524, src/batched.rs:189-749).  One
+``step()`` is:
+
+    core.build_step  -> packed plan in pinned host memory          (C++)
+    one H2D copy of the plan, CoW / swap page moves if the plan asks for them
+    DecoderModel.forward over the mixed batch (decode rows + prefill chunks)
+    fused sampler (or argmax when every row is greedy) -> int32 tokens
+    one D2H copy of the tokens, core.commit_step -> token / finish events
+
+Differences from the reference by design: prompts are prefilled in multi-token chunks inside the
+same step as decode rows (the reference feeds one prompt token per row per step,
+batched.rs:663-749), batched rows can be preempted (swap or recompute), and attention reads KV
+pages in place.  Under tensor parallelism every rank runs an identical scheduler replica on the
+same request stream, so no per-step control message crosses ranks.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..models.config import DecoderConfig
+from ..models.decoder import DecoderModel, DecoderWeights, KVCache, StepInputs, random_weights
+from ..parallel.sharding import shard_heads
+from .core import HDR, Core, CoreConfig
+
+
+@dataclass
+class EngineConfig:
+    model: DecoderConfig
+    num_pages: int = 0                 # 0: size from free device memory
+    gpu_memory_utilization: float = 0.85
+    num_host_pages: int = 0
+    max_seqs: int = 256
+    max_tokens_per_step: int = 2048
+    max_seq_len: int = 4096
+    prefill_chunk: int = 2048
+    token_multiple: int = 1
+    policy: str = "fcfs"
+    preempt: str = "recompute"
+    enable_prefix_cache: bool = True
+    kv_dtype: str = "bf16"
+    decode_splits: int = 0             # 0: pick from batch shape
+    sync_sampled_tokens: bool = True   # TP: broadcast rank 0's tokens so replicas cannot diverge
+    seed: int = 0
+
+
+@dataclass
+class RequestStats:
+    arrival: float = 0.0
+    first_token: float = 0.0
+    finished: float = 0.0
+    prompt_tokens: int = 0
+    output_tokens: int = 0
+    finish_reason: str | None = None
+
+
+@dataclass
+class StepOutput:
+    events: list = field(default_factory=list)    # (seq_id, token, finish_reason | None)
+    num_tokens: int = 0
+    num_decode: int = 0
+    num_prefill_tokens: int = 0
+
+
+class LLMEngine:
+    def __init__(self, cfg: EngineConfig, weights: DecoderWeights | None = None, device="cuda", tp: int = 1,
+                 rank: int = 0, comm=None):
+        self.cfg, self.device = cfg, torch.device(device)
+        self.tp, self.rank, self.comm = tp, rank, comm
+        m = cfg.model
+        is_cuda = self.device.type == "cuda"
+        if weights is None:
+            dtype = torch.bfloat16 if is_cuda else torch.float32
+            weights = random_weights(m, self.device, tp, rank, seed=cfg.seed, dtype=dtype)
+        self.weights = weights
+        max_pages_per_seq = (cfg.max_seq_len + ops.PAGE - 1) // ops.PAGE
+        hs = shard_heads(m.num_heads, m.num_kv_heads, tp, rank)
+        self.model = DecoderModel(m, weights, self.device, cfg.max_tokens_per_step, cfg.max_seqs, tp, rank, comm)
+        num_pages = cfg.num_pages
+        if num_pages <= 0:
+            kv_bytes = 1 if cfg.kv_dtype == "fp8" else 2
+            page_bytes = m.num_layers * len(hs.kv_heads) * 2 * ops.PAGE * m.head_dim * kv_bytes
+            if is_cuda:
+                free, total = torch.cuda.mem_get_info(self.device)
+                budget = int(free - (1.0 - cfg.gpu_memory_utilization) * total)
+                if self.comm is not None:   # every replica must agree on the pool size
+                    budget = self.comm.min_int(budget)
+                num_pages = max(64, budget // page_bytes)
+                # no more pages than max_seqs full-length sequences can ever use
+                num_pages = min(num_pages, cfg.max_seqs * max_pages_per_seq + 64)
+            else:
+                num_pages = min(4096, cfg.max_seqs * max_pages_per_seq + 16)
+        self.num_pages = int(num_pages)
+        self.kv = KVCache(m, self.num_pages, self.device, len(hs.kv_heads), cfg.kv_dtype)
+        self.core = Core(CoreConfig(num_pages=self.num_pages, num_host_pages=cfg.num_host_pages, max_seqs=cfg.max_seqs,
+                                    max_tokens_per_step=cfg.max_tokens_per_step, max_pages_per_seq=max_pages_per_seq,
+                                    prefill_chunk=cfg.prefill_chunk, token_multiple=cfg.token_multiple,
+                                    policy=cfg.policy, preempt=cfg.preempt,
+                                    enable_prefix_cache=cfg.enable_prefix_cache, eos_token=m.eos_token))
+        L = self.core.layout
+        self.L = L
+        self.plan_host = torch.zeros(L.total_words, dtype=torch.int32, pin_memory=is_cuda)
+        self.plan_np = self.plan_host.numpy()
+        self.dev_words = L.swap_out_dev      # sections after this offset are host-only
+        self.plan_dev = torch.zeros(self.dev_words, dtype=torch.int32, device=self.device) if is_cuda else self.plan_host
+        self.sampled_host = torch.zeros(cfg.max_seqs, dtype=torch.int32, pin_memory=is_cuda)
+        self.sampled_dev = torch.zeros(cfg.max_seqs, dtype=torch.int32, device=self.device)
+        self.sample_work = (torch.empty(cfg.max_seqs * m.vocab, dtype=torch.int32, device=self.device)
+                            if is_cuda else None)
+        self.host_kv = None
+        if cfg.num_host_pages > 0:
+            shape = (cfg.num_host_pages,) + tuple(self.kv.pools[0].shape[1:])
+            self.host_kv = [torch.zeros(shape, dtype=self.kv.pools[0].dtype, pin_memory=is_cuda)
+                            for _ in range(m.num_layers)]
+            self.swap_stage = torch.zeros((max_pages_per_seq,) + tuple(self.kv.pools[0].shape[1:]),
+                                          dtype=self.kv.pools[0].dtype, device=self.device)
+        p = self.plan_dev
+        S, T, MP = cfg.max_seqs, cfg.max_tokens_per_step, max_pages_per_seq
+        self.si = StepInputs(
+            0, 0, 0, 0, 0,
+            token_ids=p[L.token_ids:L.token_ids + T], positions=p[L.positions:L.positions + T],
+            slots=p[L.slots:L.slots + T], ctx_len=p[L.ctx_len:L.ctx_len + S],
+            page_table=p[L.page_table:L.page_table + S * MP].view(S, MP), cu_q=p[L.cu_q:L.cu_q + S + 1],
+            tile_seq=p[L.tile_seq:L.tile_seq + L.max_tiles], tile_q0=p[L.tile_q0:L.tile_q0 + L.max_tiles],
+            logit_rows=p[L.logit_rows:L.logit_rows + S])
+        f32 = lambda off: p[off:off + S].view(torch.float32)
+        self.temperature, self.top_p, self.min_p, self.uniform = (f32(L.temperature), f32(L.top_p), f32(L.min_p),
+                                                                  f32(L.uniform))
+        self.top_k = p[L.top_k:L.top_k + S]
+        self.stats: dict[int, RequestStats] = {}
+        self.steps = 0
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    # --------------------------------------------------------------------------------------
+    def add_request(self, prompt_ids, max_new_tokens=256, temperature=0.0, top_k=0, top_p=1.0, min_p=0.0, seed=0,
+                    priority=0, tenant=0, ignore_eos=False, stop_ids=()) -> int:
+        sid = self.core.add_request(prompt_ids, max_new_tokens, temperature, top_k, top_p, min_p, seed, priority, tenant,
+                                    ignore_eos, stop_ids)
+        self.stats[sid] = RequestStats(arrival=time.perf_counter(), prompt_tokens=len(prompt_ids))
+        return sid
+
+    @property
+    def has_work(self) -> bool:
+        return self.core.has_work
+
+    def _page_moves(self, hdr):
+        L, pn = self.L, self.plan_np
+        nso, nsi, ncp = int(hdr[HDR["num_swap_out"]]), int(hdr[HDR["num_swap_in"]]), int(hdr[HDR["num_copies"]])
+        if nso:
+            dev_pages = torch.from_numpy(pn[L.swap_out_dev:L.swap_out_dev + nso].astype(np.int64))
+            host_pages = torch.from_numpy(pn[L.swap_out_host:L.swap_out_host + nso].astype(np.int64))
+            dp = dev_pages.to(self.device)
+            for li, pool in enumerate(self.kv.pools):
+                for s in range(0, nso, self.swap_stage.shape[0]):
+                    e = min(nso, s + self.swap_stage.shape[0])
+                    ops.kv_gather_pages(pool, self.swap_stage, dp[s:e])
+                    self.host_kv[li][host_pages[s:e]] = self.swap_stage[: e - s].cpu()
+        if nsi:
+            dev_pages = torch.from_numpy(pn[L.swap_in_dev:L.swap_in_dev + nsi].astype(np.int64))
+            host_pages = torch.from_numpy(pn[L.swap_in_host:L.swap_in_host + nsi].astype(np.int64))
+            dp = dev_pages.to(self.device)
+            for li, pool in enumerate(self.kv.pools):
+                for s in range(0, nsi, self.swap_stage.shape[0]):
+                    e = min(nsi, s + self.swap_stage.shape[0])
+                    self.swap_stage[: e - s].copy_(self.host_kv[li][host_pages[s:e]])
+                    ops.kv_scatter_pages(pool, self.swap_stage, dp[s:e])
+        if ncp:
+            src = torch.from_numpy(pn[L.copy_src:L.copy_src + ncp].astype(np.int64)).to(self.device)
+            dst = torch.from_numpy(pn[L.copy_dst:L.copy_dst + ncp].astype(np.int64)).to(self.device)
+            for pool in self.kv.pools:
+                ops.kv_page_copy(pool, src, dst)
+
+    def _pick_splits(self, nd: int, max_ctx: int) -> int:
+        if self.cfg.decode_splits > 0:
+            return self.cfg.decode_splits
+        ctas = nd * self.model.hkv
+        target = 2 * 148
+        if ctas >= target or max_ctx < 1024:
+            return 1
+        s = 1
+        while ctas * s < target and s < 32 and max_ctx // (s * 2) >= 256:
+            s *= 2
+        return s
+
+    def step(self) -> StepOutput:
+        """Schedule, run and commit one engine step."""
+        out = StepOutput()
+        t = self.core.build_step(self.plan_host.data_ptr())
+        if t <= 0:
+            return out
+        hdr = self.plan_np[:32]
+        si = self.si
+        si.num_tokens, si.num_decode = t, int(hdr[HDR["num_decode"]])
+        si.num_prefill_seqs, si.num_tiles = int(hdr[HDR["num_prefill_seqs"]]), int(hdr[HDR["num_tiles"]])
+        si.num_logit_rows, si.max_ctx = int(hdr[HDR["num_logit_rows"]]), int(hdr[HDR["max_ctx"]])
+        r = si.num_logit_rows
+        if self.device.type == "cuda":
+            self.plan_dev.copy_(self.plan_host[: self.dev_words], non_blocking=True)
+            self.h2d_bytes += self.dev_words * 4
+        if hdr[HDR["num_swap_out"]] or hdr[HDR["num_swap_in"]] or hdr[HDR["num_copies"]]:
+            self._page_moves(hdr)
+        if si.num_decode:
+            splits = self._pick_splits(si.num_decode, si.max_ctx)
+            if splits != self.model.decode_splits:
+                self.model.set_decode_splits(splits)
+        logits = self.model.forward(si, self.kv)
+        if r > 0:
+            temps = self.plan_np[self.L.temperature:self.L.temperature + r].view(np.float32)
+            if self.device.type == "cuda":
+                if (temps <= 0).all():
+                    ops.argmax(logits, out=self.sampled_dev[:r])
+                else:
+                    ops.sample(logits, self.temperature[:r], self.top_k[:r], self.top_p[:r], self.min_p[:r],
+                               self.uniform[:r], work=self.sample_work, out=self.sampled_dev[:r])
+                if self.tp > 1 and self.cfg.sync_sampled_tokens:
+                    self.comm.broadcast(self.sampled_dev[:r], src=0)
+                self.sampled_host[:r].copy_(self.sampled_dev[:r], non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                self.d2h_bytes += r * 4
+            else:
+                if (temps <= 0).all():
+                    toks = ops.argmax(logits)
+                else:
+                    toks = ops.sample(logits, self.temperature[:r], self.top_k[:r], self.top_p[:r], self.min_p[:r],
+                                      self.uniform[:r])
+                self.sampled_host[:r] = toks
+        elif self.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
+        events = self.core.commit_step(self.sampled_host.data_ptr(), r)
+        now = time.perf_counter()
+        for sid, tok, fin in events:
+            st = self.stats.get(sid)
+            if st is None:
+                continue
+            st.output_tokens += 1
+            if st.output_tokens == 1:
+                st.first_token = now
+            if fin is not None:
+                st.finished, st.finish_reason = now, fin
+        self.steps += 1
+        out.events, out.num_tokens, out.num_decode = events, t, si.num_decode
+        out.num_prefill_tokens = int(hdr[HDR["num_prefill_tokens"]])
+        return out
+
+    # --------------------------------------------------------------------------------------
+    def generate(self, prompts, max_new_tokens=64, **sampling):
+        """Run a batch of token-id prompts to completion; returns the generated ids per prompt."""
+        ids = [self.add_request(p, max_new_tokens, **sampling) for p in prompts]
+        outs = {i: [] for i in ids}
+        done = set()
+        while len(done) < len(ids) and self.core.has_work:
+            for sid, tok, fin in self.step().events:
+                if sid in outs:
+                    outs[sid].append(tok)
+                    if fin is not None:
+                        done.add(sid)
+        for sid in ids:
+            self.core.release(sid)
+        return [outs[i] for i in ids]
+
+    def check_device_status(self):
+        if self.device.type == "cuda":
+            ops.check_status()

@@ -1,0 +1,274 @@
+"""Fused decoder executor: one static plan of ~8 kernels per layer over a paged KV pool.
+
+The reference executes the decoder ONNX graph node by node (≈300-2600 kernel nodes per token,
+docs/execution/NATIVE_CUDA_DECODE.md:133-150) after graph-level fusions
+(crates/onnx-runtime-ep-cuda/src/optimizer.rs:106-158).  Here the recognised pattern
+(RMSNorm -> qkv MatMul -> rotary + GQA with KV append -> o_proj + residual -> RMSNorm ->
+gate/up MatMul + SwiGLU -> down MatMul + residual) is lowered once to this plan:
+
+    rmsnorm | gemm(qkv,+bias) | rope_kv_append | paged_decode + paged_prefill |
+    gemm(o_proj,+residual) | rmsnorm | gemm(gate_up, SwiGLU epilogue) | gemm(down,+residual)
+
+Every buffer is preallocated for the largest step, so a step launches kernels and nothing else.
+Under tensor parallelism the two row-parallel GEMMs produce partial sums that the communicator
+reduces; the residual add then rides in the next RMSNorm (``delta``).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+
+from .. import ops
+from ..ops import reference as ref
+from ..parallel.sharding import shard_heads, shard_range
+from .config import DecoderConfig
+
+
+@dataclass
+class LayerWeights:
+    ln1: torch.Tensor
+    qkv_w: torch.Tensor
+    qkv_b: torch.Tensor | None
+    o_w: torch.Tensor
+    ln2: torch.Tensor
+    gate_up_w: torch.Tensor | None = None     # packed by ops.pack_gate_up
+    down_w: torch.Tensor | None = None
+    # MoE
+    router_w: torch.Tensor | None = None
+    expert_gate_up: torch.Tensor | None = None  # [E_local, 2*I, H] packed per expert
+    expert_down: torch.Tensor | None = None     # [E_local, H, I]
+    quant: dict = field(default_factory=dict)   # int4 tensors keyed by projection name
+
+
+@dataclass
+class DecoderWeights:
+    embed: torch.Tensor
+    layers: list[LayerWeights]
+    final_norm: torch.Tensor
+    lm_head: torch.Tensor
+    swiglu_half: int = 128
+
+
+def pick_swiglu_half(inter_local: int) -> int:
+    for half in (128, 64, 32):
+        if inter_local % half == 0:
+            return half
+    raise ValueError(f"intermediate size {inter_local} is not a multiple of 32")
+
+
+def random_weights(cfg: DecoderConfig, device, tp: int = 1, rank: int = 0, seed: int = 0, std: float = 0.02,
+                   dtype=torch.bfloat16) -> DecoderWeights:
+    """Seeded N(0, std) weights of the architecture, sharded for (tp, rank).
+
+    Each full matrix is drawn from its own generator seed, then sliced, so every rank of any
+    TP degree sees slices of the same global matrices.
+    """
+    dev = torch.device(device)
+    counter = [seed * 1000003]
+
+    def draw(*shape):
+        counter[0] += 1
+        g = torch.Generator(device=dev).manual_seed(counter[0])
+        return (torch.randn(*shape, generator=g, device=dev, dtype=torch.float32) * std).to(dtype)
+
+    hs = shard_heads(cfg.num_heads, cfg.num_kv_heads, tp, rank)
+    d, hid = cfg.head_dim, cfg.hidden
+    q_rows = torch.tensor([h * d + i for h in hs.q_heads for i in range(d)], device=dev)
+    kv_rows = torch.tensor([h * d + i for h in hs.kv_heads for i in range(d)], device=dev)
+    moe = cfg.moe.num_experts > 0
+    if not moe:
+        i0, i1 = shard_range(cfg.intermediate, tp, rank, 32 if tp > 1 else 1)
+        half = pick_swiglu_half(i1 - i0)
+    else:
+        half = pick_swiglu_half(cfg.moe.expert_intermediate)
+    embed = draw(cfg.vocab, hid)
+    layers = []
+    for _ in range(cfg.num_layers):
+        wq, wk, wv = draw(cfg.q_size, hid), draw(cfg.kv_size, hid), draw(cfg.kv_size, hid)
+        qkv_w = torch.cat([wq[q_rows], wk[kv_rows], wv[kv_rows]], 0).contiguous()
+        qkv_b = None
+        if cfg.qkv_bias:
+            bq, bk, bv = draw(cfg.q_size), draw(cfg.kv_size), draw(cfg.kv_size)
+            qkv_b = torch.cat([bq[q_rows], bk[kv_rows], bv[kv_rows]], 0).contiguous()
+        del wq, wk, wv
+        o_w = draw(hid, cfg.q_size)[:, q_rows].contiguous()
+        lw = LayerWeights(ln1=torch.ones(hid, device=dev, dtype=dtype), qkv_w=qkv_w, qkv_b=qkv_b, o_w=o_w,
+                          ln2=torch.ones(hid, device=dev, dtype=dtype))
+        if not moe:
+            g = draw(cfg.intermediate, hid)[i0:i1]
+            u = draw(cfg.intermediate, hid)[i0:i1]
+            lw.gate_up_w = ops.pack_gate_up(g.contiguous(), u.contiguous(), half)
+            del g, u
+            lw.down_w = draw(hid, cfg.intermediate)[:, i0:i1].contiguous()
+        else:
+            e0, e1 = shard_range(cfg.moe.num_experts, tp, rank)
+            lw.router_w = draw(cfg.moe.num_experts, hid)
+            inter = cfg.moe.expert_intermediate
+            gus, dws = [], []
+            for e in range(cfg.moe.num_experts):
+                g, u, dw = draw(inter, hid), draw(inter, hid), draw(hid, inter)
+                if e0 <= e < e1:
+                    gus.append(ops.pack_gate_up(g, u, half))
+                    dws.append(dw)
+            lw.expert_gate_up = torch.stack(gus).contiguous()
+            lw.expert_down = torch.stack(dws).contiguous()
+        layers.append(lw)
+    final_norm = torch.ones(hid, device=dev, dtype=dtype)
+    lm_head = embed if cfg.tie_embeddings else draw(cfg.vocab, hid)
+    return DecoderWeights(embed=embed, layers=layers, final_norm=final_norm, lm_head=lm_head, swiglu_half=half)
+
+
+@dataclass
+class StepInputs:
+    """Device views of one packed step plan (see csrc/runtime/core.h PlanLayout)."""
+    num_tokens: int
+    num_decode: int
+    num_prefill_seqs: int
+    num_tiles: int
+    num_logit_rows: int
+    token_ids: torch.Tensor
+    positions: torch.Tensor
+    slots: torch.Tensor
+    ctx_len: torch.Tensor          # [S] decode rows first
+    page_table: torch.Tensor       # [S, max_pages]
+    cu_q: torch.Tensor             # [Np + 1]
+    tile_seq: torch.Tensor
+    tile_q0: torch.Tensor
+    logit_rows: torch.Tensor       # [R]
+    max_ctx: int = 0
+
+
+class KVCache:
+    """Per-layer paged pools [pages, kv_heads_local, 2, 16, head_dim] (bf16, or e4m3 + scales)."""
+
+    def __init__(self, cfg: DecoderConfig, num_pages: int, device, kv_heads_local: int | None = None, dtype="bf16"):
+        hkv = kv_heads_local or cfg.num_kv_heads
+        self.num_pages = num_pages
+        self.dtype = dtype
+        tdtype = torch.bfloat16 if dtype == "bf16" else torch.uint8
+        if torch.device(device).type == "cpu":
+            tdtype = torch.float32
+        self.pools = [torch.zeros(num_pages, hkv, 2, ops.PAGE, cfg.head_dim, dtype=tdtype, device=device)
+                      for _ in range(cfg.num_layers)]
+        self.scales = None
+        if dtype == "fp8":
+            self.scales = [torch.zeros(num_pages, hkv, 2, dtype=torch.float32, device=device)
+                           for _ in range(cfg.num_layers)]
+
+    def page_bytes(self) -> int:
+        p = self.pools[0]
+        return p.stride(0) * p.element_size() * len(self.pools)
+
+
+class DecoderModel:
+    def __init__(self, cfg: DecoderConfig, weights: DecoderWeights, device, max_tokens: int, max_seqs: int,
+                 tp: int = 1, rank: int = 0, comm=None):
+        self.cfg, self.w, self.device = cfg, weights, torch.device(device)
+        self.tp, self.rank, self.comm = tp, rank, comm
+        hs = shard_heads(cfg.num_heads, cfg.num_kv_heads, tp, rank)
+        self.hq, self.hkv, self.d = len(hs.q_heads), len(hs.kv_heads), cfg.head_dim
+        self.rotary_dim = cfg.rotary_dim or cfg.head_dim
+        self.max_tokens, self.max_seqs = max_tokens, max_seqs
+        dt = weights.embed.dtype
+        dev = self.device
+        hid = cfg.hidden
+        self.cos_sin = ref.rope_table(cfg.max_position, self.rotary_dim, cfg.rope_theta, dev)
+        z = lambda *s: torch.zeros(*s, dtype=dt, device=dev)
+        self.x = z(max_tokens, hid)                 # residual stream
+        self.h = z(max_tokens, hid)                 # normed activations
+        self.qkv = z(max_tokens, (self.hq + 2 * self.hkv) * self.d)
+        self.attn = z(max_tokens, self.hq * self.d)
+        inter_local = (weights.layers[0].gate_up_w.shape[0] // 2) if weights.layers[0].gate_up_w is not None else 0
+        self.act = z(max_tokens, max(inter_local, 8))
+        self.partial = z(max_tokens, hid) if tp > 1 else None
+        self.h_last = z(max_seqs, hid)
+        self.x_last = z(max_seqs, hid)
+        self.logits = z(max_seqs, cfg.vocab)
+        self.scale = 1.0 / math.sqrt(self.d)
+        self.decode_splits = 1
+        self.part_o = self.part_ml = None
+
+    def set_decode_splits(self, splits: int):
+        self.decode_splits = splits
+        if splits > 1 and self.device.type == "cuda":
+            self.part_o = torch.empty(self.max_seqs * self.hq * splits * self.d, dtype=torch.float32, device=self.device)
+            self.part_ml = torch.empty(self.max_seqs * self.hq * splits * 2, dtype=torch.float32, device=self.device)
+
+    # --------------------------------------------------------------------------------------
+    def forward(self, si: StepInputs, kv: KVCache) -> torch.Tensor:
+        """Runs one step; returns logits [num_logit_rows, vocab] (a view of a static buffer)."""
+        cfg, w = self.cfg, self.w
+        t, nd = si.num_tokens, si.num_decode
+        x, h, qkv, attn = self.x[:t], self.h[:t], self.qkv[:t], self.attn[:t]
+        ops.embedding(si.token_ids[:t], w.embed, out=x) if x.is_cuda else x.copy_(w.embed[si.token_ids[:t].long()])
+        pending = None  # partial sums still to be added to the residual (TP only)
+        for li, lw in enumerate(w.layers):
+            pool = kv.pools[li]
+            self._norm(x, lw.ln1, pending, h)
+            self._gemm(h, lw.qkv_w, out=qkv, bias=lw.qkv_b)
+            ops.rope_kv_append(qkv, si.positions[:t], si.slots[:t], self.cos_sin, pool, self.hq, self.hkv, self.d,
+                               self.rotary_dim, cfg.rotary_interleaved,
+                               kv_scales=kv.scales[li] if kv.scales is not None else None)
+            if nd > 0:
+                ops.paged_decode(qkv[:nd], attn[:nd], pool, si.page_table[:nd], si.ctx_len[:nd], self.hq, self.hkv,
+                                 self.d, self.scale, self.decode_splits, self.part_o, self.part_ml, cfg.sliding_window)
+            if si.num_prefill_seqs > 0:
+                np_ = si.num_prefill_seqs
+                ops.paged_prefill(qkv[nd:], attn[nd:], pool, si.page_table[nd:nd + np_], si.ctx_len[nd:nd + np_],
+                                  si.cu_q, si.tile_seq, si.tile_q0, si.num_tiles, self.hq, self.hkv, self.d, self.scale,
+                                  cfg.sliding_window)
+            pending = self._row_parallel(attn, lw.o_w, x)
+            self._norm(x, lw.ln2, pending, h)
+            if lw.gate_up_w is not None:
+                act = self.act[:t]
+                if x.is_cuda:
+                    ops.gemm(h, lw.gate_up_w, epilogue="swiglu", swiglu_half=w.swiglu_half, out=act)
+                else:
+                    act = ops.gemm(h, lw.gate_up_w, epilogue="swiglu", swiglu_half=w.swiglu_half)
+                pending = self._row_parallel(act, lw.down_w, x)
+            else:
+                pending = self._moe(h, lw, x)
+        r = si.num_logit_rows
+        if pending is not None:   # fold the last partial sum into the residual before selecting rows
+            x.add_(pending)
+        xl = self.x_last[:r]
+        torch.index_select(x, 0, si.logit_rows[:r].long(), out=xl)
+        hl = self.h_last[:r]
+        self._norm(xl, w.final_norm, None, hl)
+        logits = self.logits[:r]
+        self._gemm(hl, w.lm_head, out=logits)
+        return logits
+
+    # --------------------------------------------------------------------------------------
+    def _norm(self, x, weight, delta, out):
+        if x.is_cuda:
+            ops.rmsnorm(x, weight, self.cfg.rms_eps, delta=delta, out=out)
+        else:
+            out.copy_(ops.rmsnorm(x, weight, self.cfg.rms_eps, delta=delta))
+
+    def _gemm(self, a, wt, out, bias=None):
+        if a.is_cuda:
+            ops.gemm(a, wt, bias=bias, out=out)
+        else:
+            out.copy_(ops.gemm(a, wt, bias=bias))
+
+    def _row_parallel(self, a, wt, x):
+        """x += a @ wt^T.  TP=1: fused residual epilogue.  TP>1: partial sum -> all-reduce -> returned as
+        a pending delta that the next RMSNorm adds."""
+        if self.tp == 1:
+            if a.is_cuda:
+                ops.gemm(a, wt, residual=x, epilogue="residual", out=x)
+            else:
+                x.copy_(ops.gemm(a, wt, residual=x, epilogue="residual"))
+            return None
+        part = self.partial[: a.shape[0]]
+        self._gemm(a, wt, out=part)
+        self.comm.all_reduce(part)
+        return part
+
+    def _moe(self, h, lw, x):
+        from . import moe
+
+        return moe.moe_forward(self, h, lw, x)

@@ -153,7 +153,7 @@ def rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim=
         assert kv_scales is None
         return reference.rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim, interleaved)
     t = qkv.shape[0]
-    assert qkv.is_contiguous() and positions.dtype == torch.int32 and slots.dtype == torch.int64
+    assert qkv.is_contiguous() and positions.dtype == torch.int32 and slots.dtype == torch.int32
     num_slots = pool.shape[0] * PAGE
     lib = _native.load()
     if kv_scales is None:

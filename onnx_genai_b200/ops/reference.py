@@ -160,11 +160,11 @@ def argmax(logits):
 
 
 def sample_weights(logits_row, temperature):
-    """Fixed-point weights w = round(exp((l - max)/T) * 2^30) as int64 (the device sampler's mass unit)."""
+    """Fixed-point weights w = min(round(exp((l - max)/T) * 2^30), 2^30 - 1) as int64 (the device sampler's mass unit)."""
     l = logits_row.float()
     e = torch.exp((l - l.max()) / temperature)
     e = torch.where(torch.isnan(e), torch.zeros_like(e), e)
-    return torch.floor(e.double() * 1073741824.0 + 0.5).to(torch.int64)
+    return torch.floor(e.double() * 1073741824.0 + 0.5).clamp_max(1073741823.0).to(torch.int64)
 
 
 def sample_from_weights(w, top_k, top_p, min_p, u):

@@ -158,7 +158,7 @@ def test_rope_kv_append():
     hq, hkv, d, t, pages = 14, 2, 64, 37, 9
     qkv = torch.randn(t, (hq + 2 * hkv) * d, device=DEV).bfloat16()
     pos = torch.randint(0, 500, (t,), dtype=torch.int32, device=DEV)
-    slots = torch.randperm(pages * ref.PAGE, device=DEV)[:t].to(torch.int64)
+    slots = torch.randperm(pages * ref.PAGE, device=DEV)[:t].to(torch.int32)
     slots[3] = -1
     cs = ref.rope_table(512, d, 1e6, DEV)
     pool = torch.zeros(pages, hkv, 2, ref.PAGE, d, device=DEV, dtype=torch.bfloat16)
