@@ -1,0 +1,309 @@
+"""Headline benchmark: continuous-batching output tokens/s on the Qwen2.5-7B shape, TP = --gpus.
+
+    python bench.py --gpus 1 --steps 64 --warmup 8
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Workload: a closed loop of 256 concurrent requests; prompts of uniform-random token ids with
+lengths uniform in 128..2048; 256 output tokens each (EOS ignored); temperature 0.7, top-p 0.9;
+paged KV with 16-token bf16 pages; bf16 weights drawn N(0, 0.02).  Requests enter at the
+steady-state rate (one per engine step) until 256 are in flight; from then on a finished request
+is replaced at once, so every step mixes ~250 decode rows with the prefill chunk of a new
+prompt.  A "step" is one engine step (schedule + forward + sample + commit).
+
+Two timed regions, both after the ramp and W warm-up steps:
+  e2e     K steps through the public API (LLMEngine.step): each step builds the plan in pinned
+          host memory, copies it to the device, runs the kernels, and reads the sampled tokens
+          back.  Wall clock bracketed by barrier + synchronize.
+  device  the same K steps replayed from their recorded device-resident plans (forward +
+          sampler only; no host scheduling, no copies), timed with CUDA events.  `value` and
+          `ms_per_step` come from here.  Inputs per step (15 GB of weights / TP + KV pages) are far
+          larger than the 126 MB L2, so no explicit L2 flush is issued between steps.
+Multi-GPU numbers take the max over ranks of the elapsed time.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+BASELINE_CONTEXT = {"qwen2.5-7b int4 batch-1 decode tok/s on 1xH200 (reference native CUDA EP)": 308.34}
+
+
+def reference_arm(args):
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "reference is a Rust workspace (cargo/rustc/maturin absent offline; `pip install /root/reference` "
+                       "reports 'neither setup.py nor pyproject.toml', its Python crate needs maturin) and it has no "
+                       "multi-GPU or NCCL path at all",
+    }))
+    return 0
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.perf_counter(), [x.strip() for x in line.split(",")]))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self, t0, t1):
+        rows = [r for ts, r in self.rows if t0 <= ts <= t1 and len(r) >= 9] or [r for _, r in self.rows if len(r) >= 9]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = [float(r[1]) for r in rows if r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in rows if r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in rows:
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(rows)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "baseline"])
+    ap.add_argument("--model", default="qwen2.5-7b")
+    ap.add_argument("--concurrency", type=int, default=256)
+    ap.add_argument("--min-prompt", type=int, default=128)
+    ap.add_argument("--max-prompt", type=int, default=2048)
+    ap.add_argument("--output-tokens", type=int, default=256)
+    ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
+    ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "fused"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    args.warmup = max(args.warmup, 3)
+
+    import numpy as np
+    import torch
+
+    from onnx_genai_b200 import ops
+    from onnx_genai_b200.engine.llm_engine import EngineConfig, LLMEngine
+    from onnx_genai_b200.models.config import preset
+    from onnx_genai_b200.parallel import comm as comm_mod
+
+    rank, world, local_rank = comm_mod.init_distributed()
+    if world != args.gpus:
+        if rank == 0:
+            print(f"bench.py: --gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run", file=sys.stderr)
+        if world == 1 and args.gpus > 1:
+            return 2
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if args.impl == "baseline":
+        os.environ["OGB_BASELINE"] = "1"
+        ops.set_baseline(True)
+    comm = None
+    if world > 1:
+        comm = comm_mod.NcclComm()
+        if args.comm in ("auto", "fused") and args.impl == "ours":
+            try:
+                from onnx_genai_b200.parallel.fused import FusedComm
+
+                comm = FusedComm(comm, dev)
+            except Exception as exc:  # stays on the NCCL path and says so
+                if rank == 0:
+                    print(f"bench.py: fused communicator unavailable ({exc}); using NCCL", file=sys.stderr)
+
+    model = preset(args.model)
+    invalid = None
+    if args.layers:
+        model = model.replace(num_layers=args.layers)
+        invalid = "reduced layer count (debug)"
+    max_len = args.max_prompt + args.output_tokens
+    cfg = EngineConfig(model=model, max_seqs=args.concurrency, max_tokens_per_step=args.concurrency + args.max_prompt,
+                       max_seq_len=max_len, prefill_chunk=args.max_prompt, enable_prefix_cache=False, seed=0,
+                       sync_sampled_tokens=True)
+    eng = LLMEngine(cfg, device=dev, tp=world, rank=rank, comm=comm)
+    rng = np.random.default_rng(1234)  # same stream on every rank: replicas schedule identically
+
+    def new_request():
+        n = int(rng.integers(args.min_prompt, args.max_prompt + 1))
+        ids = rng.integers(0, model.vocab, size=n, dtype=np.int64).astype(np.int32)
+        return eng.add_request(ids, args.output_tokens, temperature=0.7, top_p=0.9, seed=int(rng.integers(1, 2**31)),
+                               ignore_eos=True)
+
+    active = 0
+    finished_ids = []
+
+    def one_step():
+        nonlocal active
+        out = eng.step()
+        for sid, tok, fin in out.events:
+            if fin is not None:
+                active -= 1
+                finished_ids.append(sid)
+        return out
+
+    # ---- ramp: one admission per step until the batch is full and requests have started to turn over ----
+    t_ramp = time.perf_counter()
+    ramp_steps = 0
+    while active < args.concurrency or not finished_ids:
+        if active < args.concurrency:
+            new_request()
+            active += 1
+        one_step()
+        ramp_steps += 1
+        if ramp_steps > 4 * (args.concurrency + args.output_tokens):
+            break
+
+    def closed_loop_step():
+        nonlocal active
+        while active < args.concurrency:
+            new_request()
+            active += 1
+        return one_step()
+
+    for _ in range(args.warmup):
+        closed_loop_step()
+    eng.check_device_status()
+    ramp_s = time.perf_counter() - t_ramp
+
+    # ---- region 1: end to end through the public API ----
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    plans = torch.empty(args.steps, eng.dev_words, dtype=torch.int32, device=dev)
+    shapes = []
+    launches0 = sum(ops.launch_counts.values())
+    h2d0, d2h0 = eng.h2d_bytes, eng.d2h_bytes
+    if comm is not None:
+        comm.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    e2e_tokens = 0
+    for i in range(args.steps):
+        out = closed_loop_step()
+        e2e_tokens += len(out.events)
+        plans[i].copy_(eng.plan_dev)   # device-to-device record for region 2 (tiny; part of neither claim)
+        si = eng.si
+        shapes.append((si.num_tokens, si.num_decode, si.num_prefill_seqs, si.num_tiles, si.num_logit_rows, si.max_ctx,
+                       eng.model.decode_splits))
+    if comm is not None:
+        comm.barrier()
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    e2e_s = t1 - t0
+    launches_e2e = sum(ops.launch_counts.values()) - launches0
+    h2d = (eng.h2d_bytes - h2d0) / args.steps
+    d2h = (eng.d2h_bytes - d2h0) / args.steps
+
+    # ---- region 2: the same K steps, kernels only, from device-resident plans ----
+    def replay(i):
+        eng.plan_dev.copy_(plans[i])
+        si = eng.si
+        (si.num_tokens, si.num_decode, si.num_prefill_seqs, si.num_tiles, si.num_logit_rows, si.max_ctx, splits) = shapes[i]
+        if splits != eng.model.decode_splits:
+            eng.model.set_decode_splits(splits)
+        logits = eng.model.forward(si, eng.kv)
+        r = si.num_logit_rows
+        if r:
+            ops.sample(logits, eng.temperature[:r], eng.top_k[:r], eng.top_p[:r], eng.min_p[:r], eng.uniform[:r],
+                       work=eng.sample_work, out=eng.sampled_dev[:r])
+
+    for i in range(min(3, args.steps)):
+        replay(i)
+    if comm is not None:
+        comm.barrier()
+    torch.cuda.synchronize()
+    launches1 = sum(ops.launch_counts.values())
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    td0 = time.perf_counter()
+    ev0.record()
+    for i in range(args.steps):
+        replay(i)
+    ev1.record()
+    if comm is not None:
+        comm.barrier()
+    torch.cuda.synchronize()
+    td1 = time.perf_counter()
+    dev_ms = ev0.elapsed_time(ev1)
+    launches_dev = sum(ops.launch_counts.values()) - launches1
+    sampler.stop()
+    eng.check_device_status()
+
+    if comm is not None:
+        dev_ms = comm.max_float(dev_ms)
+        e2e_s = comm.max_float(e2e_s)
+    dev_tokens = sum(s[4] for s in shapes)
+    value = dev_tokens / (dev_ms / 1e3)
+    e2e_value = e2e_tokens / e2e_s
+
+    ttft, tpot = [], []
+    for sid in finished_ids:
+        st = eng.stats.get(sid)
+        if st and st.finished and st.output_tokens > 1:
+            ttft.append((st.first_token - st.arrival) * 1e3)
+            tpot.append((st.finished - st.first_token) * 1e3 / (st.output_tokens - 1))
+    clocks = sampler.summary(t0, td1)
+    if rank == 0:
+        result = {
+            "metric": "output tok/s (Qwen2.5-7B-shape, continuous batching, 256 concurrent, TP=%d)" % world,
+            "value": round(value, 1), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(dev_ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform-random token ids, N(0,0.02) weights)",
+            "impl": args.impl,
+            "config": {"model": model.name + "-shape", "global_batch": args.concurrency, "seq_len": f"prompt U[{args.min_prompt},{args.max_prompt}] + {args.output_tokens} out",
+                       "parallelism": f"tp{world}", "kv": "paged, 16-token bf16 pages", "sampling": "temperature 0.7, top-p 0.9",
+                       "l2": "per-step inputs (weights + KV) exceed L2; no explicit flush",
+                       "comm": getattr(comm, "backend_name", "none"),
+                       "tokens_per_step_mean": round(sum(s[0] for s in shapes) / len(shapes), 1),
+                       "decode_rows_mean": round(sum(s[1] for s in shapes) / len(shapes), 1),
+                       "kv_pages": eng.num_pages, "ramp_steps": ramp_steps, "ramp_s": round(ramp_s, 2)},
+            "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                    "ms_per_step": round(e2e_s * 1e3 / args.steps, 4)},
+            "gpu_launches": int(launches_dev),
+            "gpu_launches_e2e": int(launches_e2e),
+            "clocks": clocks,
+            "latency": {"ttft_ms_p50": round(statistics.median(ttft), 2) if ttft else None,
+                        "tpot_ms_p50": round(statistics.median(tpot), 3) if tpot else None, "finished_requests": len(ttft)},
+            "baseline_context": BASELINE_CONTEXT,
+        }
+        if invalid:
+            result["invalid"] = invalid
+        print(json.dumps(result))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

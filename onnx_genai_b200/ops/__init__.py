@@ -63,6 +63,37 @@ def num_sms() -> int:
 # GEMM
 # ------------------------------------------------------------------------------------------
 _EPI = {"none": 0, "residual": 1, "swiglu": 2}
+_BASELINE = False
+
+
+def set_baseline(on: bool) -> None:
+    """Route GEMMs to the library path (torch.matmul -> cuBLAS) with unfused epilogues.
+
+    This is the labelled same-machine *baseline* the hand-written kernels are compared with;
+    it is never selected implicitly.
+    """
+    global _BASELINE
+    _BASELINE = bool(on)
+
+
+def _baseline_gemm(a, w, bias, residual, epilogue, out, out_f32, swiglu_half):
+    y = torch.matmul(a, w.t())
+    launch_counts["baseline_cublas_gemm"] += 1
+    if bias is not None:
+        y = y + bias
+    if epilogue == "residual":
+        y = y + residual
+    elif epilogue == "swiglu":
+        half = swiglu_half or 128
+        m, n = y.shape
+        y4 = y.view(m, n // (2 * half), 2, half)
+        y = (torch.nn.functional.silu(y4[:, :, 0, :]) * y4[:, :, 1, :]).reshape(m, n // 2)
+    if out_f32:
+        y = y.float()
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
 
 
 def gemm(a, w, bias=None, residual=None, epilogue="none", out=None, out_f32=False, bn=0, swiglu_half=None):
@@ -73,6 +104,8 @@ def gemm(a, w, bias=None, residual=None, epilogue="none", out=None, out_f32=Fals
     """
     m, k = a.shape
     n = w.shape[0]
+    if _BASELINE and a.is_cuda:
+        return _baseline_gemm(a, w, bias, residual, epilogue, out, out_f32, swiglu_half)
     if not a.is_cuda:
         if epilogue == "swiglu":
             return reference.swiglu_packed(a, w, swiglu_half or 128)
