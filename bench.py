@@ -105,6 +105,10 @@ def main():
     ap.add_argument("--output-tokens", type=int, default=256)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
     ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "fused"])
+    ap.add_argument("--token-multiple", type=int, default=128,
+                    help="the scheduler trims the last prefill chunk so a step's token count is a multiple of this (GEMM M tile)")
+    ap.add_argument("--no-native-executor", action="store_true", help="drive the layer stack from Python (for op profiling)")
+    ap.add_argument("--profile-ops", action="store_true", help="after the timed regions, replay 4 steps with per-op CUDA-event timing (stderr)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -149,6 +153,8 @@ def main():
     max_len = args.max_prompt + args.output_tokens
     cfg = EngineConfig(model=model, max_seqs=args.concurrency, max_tokens_per_step=args.concurrency + args.max_prompt,
                        max_seq_len=max_len, prefill_chunk=args.max_prompt, enable_prefix_cache=False, seed=0,
+                       token_multiple=args.token_multiple,
+                       native_executor=not (args.no_native_executor or args.profile_ops),
                        sync_sampled_tokens=True)
     eng = LLMEngine(cfg, device=dev, tp=world, rank=rank, comm=comm)
     rng = np.random.default_rng(1234)  # same stream on every rank: replicas schedule identically
@@ -174,9 +180,11 @@ def main():
     # ---- ramp: one admission per step until the batch is full and requests have started to turn over ----
     t_ramp = time.perf_counter()
     ramp_steps = 0
-    while active < args.concurrency or not finished_ids:
-        if active < args.concurrency:
+    admitted = 0
+    while not finished_ids:
+        if admitted < args.concurrency:
             new_request()
+            admitted += 1
             active += 1
         one_step()
         ramp_steps += 1
@@ -256,6 +264,17 @@ def main():
     launches_dev = sum(ops.launch_counts.values()) - launches1
     sampler.stop()
     eng.check_device_status()
+    if args.profile_ops and rank == 0:
+        n_prof = min(4, args.steps)
+        ops.profile_start()
+        for i in range(n_prof):
+            replay(i)
+        agg = ops.profile_stop()
+        tot = sum(t for t, _ in agg.values())
+        print("per-op device time over %d replayed steps (ms per step, calls per step, share):" % n_prof, file=sys.stderr)
+        for name, (t, c) in sorted(agg.items(), key=lambda kv: -kv[1][0]):
+            print("  %-44s %8.3f ms %6.1f calls %5.1f%%" % (name, t / n_prof, c / n_prof, 100 * t / tot), file=sys.stderr)
+        print("  %-44s %8.3f ms" % ("sum", tot / n_prof), file=sys.stderr)
 
     if comm is not None:
         dev_ms = comm.max_float(dev_ms)

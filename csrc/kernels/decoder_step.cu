@@ -1,0 +1,136 @@
+// Native step executor: launches the whole decoder stack of one engine step from a single call.
+//
+// The reference's counterpart is the nxrt session executor with its pre-bound device buffers and
+// static plan (crates/onnx-runtime-session/src/executor/{build,run,bindings}.rs) driven by
+// DecodeCudaState (crates/onnx-genai-engine/src/native_decode/cuda.rs:2958-3031).  Here the plan is
+// the fused layer recipe itself, not an op list: per layer
+//   rmsnorm -> qkv GEMM(+bias) -> RoPE + KV-page append -> paged decode / prefill attention ->
+//   o_proj GEMM(+residual) -> rmsnorm -> gate_up GEMM(SwiGLU) -> down GEMM(+residual)
+// then a gather of the rows that sample, the final norm and the lm_head GEMM.  All buffers are
+// bound once at plan creation; a step passes only the shape of the batch and the device
+// addresses of the plan sections.  Host cost per step is ~10 kernel launches per layer from C++
+// (no interpreter in the loop), which keeps the GPU queue full.
+#include <vector>
+
+#include "common.cuh"
+#include "ogb_kernels.h"
+
+namespace ogb {
+
+struct LayerPtrs {
+  const void *ln1, *qkv_w, *qkv_b, *o_w, *ln2, *gate_up_w, *down_w;
+  void* kv_pool;
+};
+
+struct DecoderPlan {
+  int num_layers, hidden, hq, hkv, d, rotary_dim, interleaved, inter_local, vocab, swiglu_bn, window, max_pages, max_pos;
+  int tp;
+  int64_t num_pages;
+  float eps, scale;
+  const void *embed, *final_norm, *lm_head;
+  const float* cos_sin;
+  void *x, *h, *qkv, *attn, *act, *x_last, *h_last, *logits, *partial;
+  float *part_o, *part_ml;
+  int* status;
+  std::vector<LayerPtrs> layers;
+  long long launches = 0;
+};
+
+}  // namespace ogb
+
+using namespace ogb;
+
+#define STEP_CHECK(expr)          \
+  do {                            \
+    int _rc = (expr);             \
+    ++p->launches;                \
+    if (_rc != 0) return _rc;     \
+  } while (0)
+
+// iparams: num_layers, hidden, hq, hkv, d, rotary_dim, interleaved, inter_local, vocab, swiglu_bn, window, max_pages,
+//          max_pos, tp
+// fparams: eps, scale
+// gptrs  : embed, final_norm, lm_head, cos_sin, x, h, qkv, attn, act, x_last, h_last, logits, partial, part_o, part_ml, status
+// lptrs  : per layer 8 pointers (ln1, qkv_w, qkv_b, o_w, ln2, gate_up_w, down_w, kv_pool)
+extern "C" void* ogb_decoder_create(const int* iparams, int64_t num_pages, const float* fparams, const uint64_t* gptrs,
+                                    const uint64_t* lptrs) {
+  DecoderPlan* p = new DecoderPlan();
+  p->num_layers = iparams[0]; p->hidden = iparams[1]; p->hq = iparams[2]; p->hkv = iparams[3]; p->d = iparams[4];
+  p->rotary_dim = iparams[5]; p->interleaved = iparams[6]; p->inter_local = iparams[7]; p->vocab = iparams[8];
+  p->swiglu_bn = iparams[9]; p->window = iparams[10]; p->max_pages = iparams[11]; p->max_pos = iparams[12];
+  p->tp = iparams[13];
+  p->num_pages = num_pages;
+  p->eps = fparams[0]; p->scale = fparams[1];
+  auto P = [&](int i) { return reinterpret_cast<void*>(gptrs[i]); };
+  p->embed = P(0); p->final_norm = P(1); p->lm_head = P(2); p->cos_sin = static_cast<const float*>(P(3));
+  p->x = P(4); p->h = P(5); p->qkv = P(6); p->attn = P(7); p->act = P(8); p->x_last = P(9); p->h_last = P(10);
+  p->logits = P(11); p->partial = P(12); p->part_o = static_cast<float*>(P(13)); p->part_ml = static_cast<float*>(P(14));
+  p->status = static_cast<int*>(P(15));
+  p->layers.resize(p->num_layers);
+  for (int l = 0; l < p->num_layers; ++l) {
+    const uint64_t* q = lptrs + 8 * l;
+    LayerPtrs& L = p->layers[l];
+    L.ln1 = reinterpret_cast<void*>(q[0]); L.qkv_w = reinterpret_cast<void*>(q[1]); L.qkv_b = reinterpret_cast<void*>(q[2]);
+    L.o_w = reinterpret_cast<void*>(q[3]); L.ln2 = reinterpret_cast<void*>(q[4]); L.gate_up_w = reinterpret_cast<void*>(q[5]);
+    L.down_w = reinterpret_cast<void*>(q[6]); L.kv_pool = reinterpret_cast<void*>(q[7]);
+  }
+  return p;
+}
+
+extern "C" void ogb_decoder_destroy(void* plan) { delete static_cast<DecoderPlan*>(plan); }
+extern "C" long long ogb_decoder_launches(void* plan) { return static_cast<DecoderPlan*>(plan)->launches; }
+extern "C" void ogb_decoder_set_split_scratch(void* plan, float* part_o, float* part_ml) {
+  DecoderPlan* p = static_cast<DecoderPlan*>(plan);
+  p->part_o = part_o;
+  p->part_ml = part_ml;
+}
+
+// One forward pass for a single-GPU (tp == 1) dense decoder.  Section pointers address the
+// device copy of the packed step plan.
+extern "C" int ogb_decoder_step(void* plan, const int* token_ids, const int* positions, const int* slots,
+                                const int* ctx_len, const int* page_table, const int* cu_q, const int* tile_seq,
+                                const int* tile_q0, const int* logit_rows, int T, int Nd, int Np, int num_tiles, int R,
+                                int decode_splits, void* stream) {
+  DecoderPlan* p = static_cast<DecoderPlan*>(plan);
+  if (T <= 0) return 0;
+  if (p->tp != 1) return -10;
+  const int hid = p->hidden, d = p->d, hq = p->hq, hkv = p->hkv;
+  const int qkv_n = (hq + 2 * hkv) * d;
+  const int attn_n = hq * d;
+  char* qkv_prefill = static_cast<char*>(p->qkv) + static_cast<size_t>(Nd) * qkv_n * 2;
+  char* attn_prefill = static_cast<char*>(p->attn) + static_cast<size_t>(Nd) * attn_n * 2;
+  STEP_CHECK(ogb_embedding_bf16(token_ids, p->embed, p->x, T, hid, p->vocab, p->status, stream));
+  for (int l = 0; l < p->num_layers; ++l) {
+    const LayerPtrs& L = p->layers[l];
+    STEP_CHECK(ogb_rmsnorm_bf16(p->x, nullptr, L.ln1, p->h, T, hid, hid, hid, p->eps, stream));
+    STEP_CHECK(ogb_gemm_bf16(p->h, L.qkv_w, p->qkv, L.qkv_b, nullptr, nullptr, T, qkv_n, hid, hid, hid, qkv_n, 0, 0, 0,
+                             p->status, stream));
+    STEP_CHECK(ogb_rope_kv_append_bf16(p->qkv, positions, slots, p->cos_sin, L.kv_pool, T, hq, hkv, d, p->rotary_dim,
+                                       p->interleaved, 16, p->num_pages * 16, p->max_pos, p->status, stream));
+    if (Nd > 0) {
+      STEP_CHECK(ogb_paged_decode_bf16(p->qkv, p->attn, L.kv_pool, page_table, ctx_len, Nd, p->max_pages, p->num_pages, hq,
+                                       hkv, d, qkv_n, attn_n, p->scale, decode_splits, p->part_o, p->part_ml, p->window,
+                                       p->status, stream));
+    }
+    if (Np > 0) {
+      STEP_CHECK(ogb_paged_prefill_bf16(qkv_prefill, attn_prefill, L.kv_pool, page_table + static_cast<size_t>(Nd) * p->max_pages,
+                                        ctx_len + Nd, cu_q, tile_seq, tile_q0, num_tiles, Np, p->max_pages, p->num_pages, hq,
+                                        hkv, d, qkv_n, attn_n, p->scale, p->window, p->status, stream));
+    }
+    STEP_CHECK(ogb_gemm_bf16(p->attn, L.o_w, p->x, nullptr, p->x, nullptr, T, hid, attn_n, attn_n, attn_n, hid, hid, 1, 0,
+                             p->status, stream));
+    STEP_CHECK(ogb_rmsnorm_bf16(p->x, nullptr, L.ln2, p->h, T, hid, hid, hid, p->eps, stream));
+    STEP_CHECK(ogb_gemm_bf16(p->h, L.gate_up_w, p->act, nullptr, nullptr, nullptr, T, 2 * p->inter_local, hid, hid, hid,
+                             p->inter_local, 0, 2, p->swiglu_bn, p->status, stream));
+    STEP_CHECK(ogb_gemm_bf16(p->act, L.down_w, p->x, nullptr, p->x, nullptr, T, hid, p->inter_local, p->inter_local,
+                             p->inter_local, hid, hid, 1, 0, p->status, stream));
+  }
+  if (R > 0) {
+    // rows that sample: x_last[r] = x[logit_rows[r]] (the embedding gather doubles as a row gather)
+    STEP_CHECK(ogb_embedding_bf16(logit_rows, p->x, p->x_last, R, hid, T, p->status, stream));
+    STEP_CHECK(ogb_rmsnorm_bf16(p->x_last, nullptr, p->final_norm, p->h_last, R, hid, hid, hid, p->eps, stream));
+    STEP_CHECK(ogb_gemm_bf16(p->h_last, p->lm_head, p->logits, nullptr, nullptr, nullptr, R, p->vocab, hid, hid, hid,
+                             p->vocab, 0, 0, 0, p->status, stream));
+  }
+  return 0;
+}

@@ -371,11 +371,22 @@ extern "C" int ogb_gemm_bf16(const void* A, const void* W, void* C, const void* 
   if (epilogue == kEpiResidual && (residual == nullptr || (ldr % 8) != 0)) return -5;
   if (epilogue == kEpiSwiGLU && (bn < 64 || (N % bn) != 0 || C_f32 != nullptr)) return -6;
   if (bn == 0) {
-    // Pick the widest tile that still gives every SM work (M tiles x N tiles >= SM count).
+    // Tiles are handed out round-robin to one persistent CTA per SM, so the kernel takes
+    // ceil(tiles / SMs) "waves" of one tile time each.  Pick the tile width with the lowest
+    // waves x relative-tile-cost (narrower tiles re-read A more often and amortise the epilogue
+    // worse, hence the > bn/256 costs); ties go to the wider tile.
     const int m_tiles = (M + kBM - 1) / kBM;
     const int sms = ogb_num_sms();
+    const int cand[4] = {256, 128, 64, 32};
+    const float cost[4] = {1.0f, 0.55f, 0.33f, 0.22f};
+    float best = 1e30f;
     bn = 256;
-    while (bn > 32 && m_tiles * ((N + bn - 1) / bn) < sms) bn >>= 1;
+    for (int i = 0; i < 4; ++i) {
+      if (cand[i] < 128 && m_tiles > 3) break;  // narrow tiles only pay off for decode-sized M
+      const int tiles = m_tiles * ((N + cand[i] - 1) / cand[i]);
+      const float t = static_cast<float>((tiles + sms - 1) / sms) * cost[i];
+      if (t < best - 1e-6f) { best = t; bn = cand[i]; }
+    }
   }
   if (epilogue == kEpiNone) { OGB_GEMM_DISPATCH_BN(kEpiNone) }
   if (epilogue == kEpiResidual) { OGB_GEMM_DISPATCH_BN(kEpiResidual) }

@@ -48,6 +48,7 @@ class EngineConfig:
     kv_dtype: str = "bf16"
     decode_splits: int = 0             # 0: pick from batch shape
     sync_sampled_tokens: bool = True   # TP: broadcast rank 0's tokens so replicas cannot diverge
+    native_executor: bool = True       # launch the layer stack from the C++ step executor when possible
     seed: int = 0
 
 
@@ -134,6 +135,7 @@ class LLMEngine:
         self.temperature, self.top_p, self.min_p, self.uniform = (f32(L.temperature), f32(L.top_p), f32(L.min_p),
                                                                   f32(L.uniform))
         self.top_k = p[L.top_k:L.top_k + S]
+        self.native_executor = cfg.native_executor and self.model.bind_native(self.kv, max_pages_per_seq)
         self.stats: dict[int, RequestStats] = {}
         self.steps = 0
         self.h2d_bytes = 0

@@ -189,18 +189,71 @@ class DecoderModel:
         self.scale = 1.0 / math.sqrt(self.d)
         self.decode_splits = 1
         self.part_o = self.part_ml = None
+        self.native = None          # C++ step executor (single GPU, dense bf16 layers, bf16 pages)
+        self.native_launches = 0
+
+    def bind_native(self, kv: "KVCache", max_pages_per_seq: int) -> bool:
+        """Create the C++ step executor over this model's buffers; returns False when the
+        configuration needs the Python-driven path (TP > 1, MoE, int4 weights, fp8 pages, CPU)."""
+        import ctypes
+
+        from ..ops import _native
+
+        cfg, w = self.cfg, self.w
+        if (self.device.type != "cuda" or self.tp != 1 or kv.scales is not None or ops._BASELINE
+                or any(l.gate_up_w is None or l.quant for l in w.layers)):
+            return False
+        lib = _native.load()
+        lib.ogb_decoder_create.restype = ctypes.c_void_p
+        lib.ogb_decoder_create.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+        lib.ogb_decoder_step.restype = ctypes.c_int
+        lib.ogb_decoder_step.argtypes = [ctypes.c_void_p] * 10 + [ctypes.c_int] * 6 + [ctypes.c_void_p]
+        lib.ogb_decoder_launches.restype = ctypes.c_longlong
+        lib.ogb_decoder_launches.argtypes = [ctypes.c_void_p]
+        lib.ogb_decoder_set_split_scratch.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+        lib.ogb_decoder_set_split_scratch.restype = None
+        inter_local = w.layers[0].gate_up_w.shape[0] // 2
+        ip = (ctypes.c_int * 14)(cfg.num_layers, cfg.hidden, self.hq, self.hkv, self.d, self.rotary_dim,
+                                 int(cfg.rotary_interleaved), inter_local, cfg.vocab, 2 * w.swiglu_half,
+                                 cfg.sliding_window, max_pages_per_seq, self.cos_sin.shape[0], self.tp)
+        fp = (ctypes.c_float * 2)(cfg.rms_eps, self.scale)
+        ptr = lambda t: 0 if t is None else t.data_ptr()
+        g = [w.embed, w.final_norm, w.lm_head, self.cos_sin, self.x, self.h, self.qkv, self.attn, self.act, self.x_last,
+             self.h_last, self.logits, self.partial, self.part_o, self.part_ml, ops.status_word(self.device)]
+        gp = (ctypes.c_uint64 * len(g))(*[ptr(t) for t in g])
+        lp = (ctypes.c_uint64 * (8 * cfg.num_layers))()
+        for i, lw in enumerate(w.layers):
+            for j, t in enumerate((lw.ln1, lw.qkv_w, lw.qkv_b, lw.o_w, lw.ln2, lw.gate_up_w, lw.down_w, kv.pools[i])):
+                lp[8 * i + j] = ptr(t)
+        self._native_lib = lib
+        self.native = lib.ogb_decoder_create(ip, kv.num_pages, fp, gp, lp)
+        return bool(self.native)
 
     def set_decode_splits(self, splits: int):
         self.decode_splits = splits
         if splits > 1 and self.device.type == "cuda":
             self.part_o = torch.empty(self.max_seqs * self.hq * splits * self.d, dtype=torch.float32, device=self.device)
             self.part_ml = torch.empty(self.max_seqs * self.hq * splits * 2, dtype=torch.float32, device=self.device)
+            if self.native:
+                self._native_lib.ogb_decoder_set_split_scratch(self.native, self.part_o.data_ptr(), self.part_ml.data_ptr())
 
     # --------------------------------------------------------------------------------------
     def forward(self, si: StepInputs, kv: KVCache) -> torch.Tensor:
         """Runs one step; returns logits [num_logit_rows, vocab] (a view of a static buffer)."""
         cfg, w = self.cfg, self.w
         t, nd = si.num_tokens, si.num_decode
+        if self.native:
+            before = self._native_lib.ogb_decoder_launches(self.native)
+            rc = self._native_lib.ogb_decoder_step(
+                self.native, si.token_ids.data_ptr(), si.positions.data_ptr(), si.slots.data_ptr(), si.ctx_len.data_ptr(),
+                si.page_table.data_ptr(), si.cu_q.data_ptr(), si.tile_seq.data_ptr(), si.tile_q0.data_ptr(),
+                si.logit_rows.data_ptr(), t, nd, si.num_prefill_seqs, si.num_tiles, si.num_logit_rows,
+                self.decode_splits, torch.cuda.current_stream().cuda_stream)
+            if rc != 0:
+                raise RuntimeError(f"ogb_decoder_step failed with code {rc}")
+            n = self._native_lib.ogb_decoder_launches(self.native) - before
+            ops.launch_counts["native_step_kernels"] += n
+            return self.logits[: si.num_logit_rows]
         x, h, qkv, attn = self.x[:t], self.h[:t], self.qkv[:t], self.attn[:t]
         ops.embedding(si.token_ids[:t], w.embed, out=x) if x.is_cuda else x.copy_(w.embed[si.token_ids[:t].long()])
         pending = None  # partial sums still to be added to the residual (TP only)

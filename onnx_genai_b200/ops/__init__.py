@@ -55,6 +55,53 @@ def _ptr(t):
     return 0 if t is None else t.data_ptr()
 
 
+# ------------------------------------------------------------------------------------------
+# per-op device timing (stage profiler: role of ONNX_GENAI_PROFILE / prof_span! in the reference,
+# crates/onnx-genai-ort/src/profile.rs:1-52).  Disabled path = one global load.
+# ------------------------------------------------------------------------------------------
+_PROFILE: list | None = None
+
+
+def profile_start() -> None:
+    global _PROFILE
+    _PROFILE = []
+
+
+def profile_stop() -> dict:
+    """Stops profiling; returns {op: (total_ms, calls)} measured with CUDA events."""
+    global _PROFILE
+    rec, _PROFILE = _PROFILE or [], None
+    torch.cuda.synchronize()
+    agg: dict = {}
+    for name, e0, e1 in rec:
+        t, c = agg.get(name, (0.0, 0))
+        agg[name] = (t + e0.elapsed_time(e1), c + 1)
+    return agg
+
+
+def _timed(name):
+    def deco(fn):
+        import functools
+
+        @functools.wraps(fn)
+        def wrapper(*a, **kw):
+            if _PROFILE is None:
+                return fn(*a, **kw)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = fn(*a, **kw)
+            e1.record()
+            tag = name
+            if name == "gemm":
+                tag = "gemm[%s N=%d K=%d]" % (kw.get("epilogue", "none"), a[1].shape[0], a[1].shape[1])
+            _PROFILE.append((tag, e0, e1))
+            return out
+
+        return wrapper
+
+    return deco
+
+
 def num_sms() -> int:
     return _native.load().ogb_num_sms()
 
@@ -96,6 +143,7 @@ def _baseline_gemm(a, w, bias, residual, epilogue, out, out_f32, swiglu_half):
     return y
 
 
+@_timed("gemm")
 def gemm(a, w, bias=None, residual=None, epilogue="none", out=None, out_f32=False, bn=0, swiglu_half=None):
     """out[M,N] = a[M,K] @ w[N,K]^T (+bias)(+residual) or SwiGLU over a :func:`pack_gate_up` weight.
 
@@ -135,6 +183,7 @@ pack_gate_up = reference.pack_gate_up
 # ------------------------------------------------------------------------------------------
 # glue
 # ------------------------------------------------------------------------------------------
+@_timed("rmsnorm")
 def rmsnorm(x, weight, eps, delta=None, out=None):
     """Returns normed x; with ``delta`` the residual x is updated in place first (x += delta)."""
     if not x.is_cuda:
@@ -152,6 +201,7 @@ def rmsnorm(x, weight, eps, delta=None, out=None):
     return out
 
 
+@_timed("embedding")
 def embedding(ids, table, out=None):
     if not table.is_cuda:
         return table[ids.long()]
@@ -166,6 +216,7 @@ def embedding(ids, table, out=None):
     return out
 
 
+@_timed("silu_mul")
 def silu_mul(gate_up, out=None):
     if not gate_up.is_cuda:
         return reference.silu_mul(gate_up)
@@ -178,6 +229,7 @@ def silu_mul(gate_up, out=None):
     return out
 
 
+@_timed("rope_kv_append")
 def rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim=None, interleaved=False,
                    kv_scales=None):
     """Rotate q,k in place inside qkv and append k,v to the paged pool (bf16, or e4m3 with kv_scales)."""
@@ -216,6 +268,7 @@ def prefill_tiles(q_lens, block_m=64):
     return seqs, q0s
 
 
+@_timed("paged_prefill")
 def paged_prefill(q, out, pool, page_table, ctx_len, cu_q, tile_seq, tile_q0, num_tiles, hq, hkv, d, scale=None,
                   window=0):
     """Causal varlen GQA over paged KV for chunks of new tokens.  q: packed qkv rows (first hq*d cols)."""
@@ -232,6 +285,7 @@ def paged_prefill(q, out, pool, page_table, ctx_len, cu_q, tile_seq, tile_q0, nu
     return out
 
 
+@_timed("paged_decode")
 def paged_decode(q, out, pool, page_table, ctx_len, hq, hkv, d, scale=None, num_splits=1, part_o=None, part_ml=None,
                  window=0):
     """One query token per sequence (row s of q) over paged KV; ctx_len[s] <= 0 marks an idle row."""
@@ -256,6 +310,7 @@ def paged_decode(q, out, pool, page_table, ctx_len, hq, hkv, d, scale=None, num_
 # ------------------------------------------------------------------------------------------
 # token selection
 # ------------------------------------------------------------------------------------------
+@_timed("argmax")
 def argmax(logits, out=None):
     if not logits.is_cuda:
         return reference.argmax(logits)
@@ -268,6 +323,7 @@ def argmax(logits, out=None):
     return out
 
 
+@_timed("sample")
 def sample(logits, temperature, top_k, top_p, min_p, uniform, work=None, out=None):
     """Fused temperature/top-k/top-p/min-p sampler; per-row parameter tensors; ``uniform`` in [0,1)."""
     if not logits.is_cuda:
@@ -285,6 +341,7 @@ def sample(logits, temperature, top_k, top_p, min_p, uniform, work=None, out=Non
     return out
 
 
+@_timed("spec_verify_greedy")
 def spec_verify_greedy(logits, draft, k):
     if not logits.is_cuda:
         return reference.spec_verify_greedy(logits, draft, k)

@@ -51,8 +51,16 @@ def test_generate_mixed_batch_runs_and_counts_kernels():
     ops.check_status()
     assert all(len(o) == 24 for o in outs)
     assert all(0 <= t < cfg.vocab for o in outs for t in o)
-    for k in ("gemm_bf16_tcgen05", "paged_decode", "paged_prefill", "rope_kv_append", "rmsnorm", "sample"):
+    assert eng.native_executor
+    for k in ("native_step_kernels", "sample"):
         assert ops.launch_counts[k] > before.get(k, 0), k
+    # the Python-driven path launches the same kernels one by one and must agree token for token
+    eng_py = LLMEngine(EngineConfig(model=cfg, num_pages=256, max_seqs=16, max_tokens_per_step=256, max_seq_len=512,
+                                    prefill_chunk=128, native_executor=False), weights=eng.weights, device="cuda")
+    outs_py = eng_py.generate(prompts, max_new_tokens=24, temperature=0.8, top_p=0.9, top_k=50, seed=3)
+    for k in ("gemm_bf16_tcgen05", "paged_decode", "paged_prefill", "rope_kv_append", "rmsnorm"):
+        assert ops.launch_counts[k] > before.get(k, 0), k
+    assert outs_py == outs
     # same seeds -> same tokens on a second engine (device sampler is deterministic)
     eng2 = LLMEngine(EngineConfig(model=cfg, num_pages=256, max_seqs=16, max_tokens_per_step=256, max_seq_len=512,
                                   prefill_chunk=128), weights=eng.weights, device="cuda")
