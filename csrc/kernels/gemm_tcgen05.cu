@@ -45,8 +45,8 @@ struct GemmCfg {
   static constexpr int kStageA = kBM * kBK * 2;
   static constexpr int kStageB = BN * kBK * 2;
   static constexpr int kStage = kStageA + kStageB;
-  static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
-  static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
+  static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 192 ? 5 : (BN >= 128 ? 6 : 8));
+  static constexpr int kTmemCols = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));  // power of two
   static constexpr int kSmemBytes = kStages * kStage + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
@@ -357,6 +357,7 @@ using namespace ogb;
     case 32: return launch_gemm<32, EPI>(A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, status, stream);  \
     case 64: return launch_gemm<64, EPI>(A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, status, stream);  \
     case 128: return launch_gemm<128, EPI>(A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, status, stream); \
+    case 192: return launch_gemm<192, EPI>(A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, status, stream); \
     case 256: return launch_gemm<256, EPI>(A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, status, stream); \
     default: return -2;                                                                                                 \
   }
@@ -377,11 +378,13 @@ extern "C" int ogb_gemm_bf16(const void* A, const void* W, void* C, const void* 
     // worse, hence the > bn/256 costs); ties go to the wider tile.
     const int m_tiles = (M + kBM - 1) / kBM;
     const int sms = ogb_num_sms();
-    const int cand[4] = {256, 128, 64, 32};
-    const float cost[4] = {1.0f, 0.55f, 0.33f, 0.22f};
+    // Measured on B200: with one CTA per tile, a 128-wide tile is shared-memory-bandwidth bound
+    // (A and B are re-read per MMA) and costs ~0.62 of a 256-wide one, not 0.5.
+    const int cand[5] = {256, 192, 128, 64, 32};
+    const float cost[5] = {1.0f, 0.78f, 0.62f, 0.40f, 0.28f};
     float best = 1e30f;
     bn = 256;
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 5; ++i) {
       if (cand[i] < 128 && m_tiles > 3) break;  // narrow tiles only pay off for decode-sized M
       const int tiles = m_tiles * ((N + cand[i] - 1) / cand[i]);
       const float t = static_cast<float>((tiles + sms - 1) / sms) * cost[i];

@@ -422,7 +422,8 @@ int Core::build_step(int32_t* plan) {
       const int prow = row - static_cast<int>(decode_items.size());
       plan[L.cu_q + prow] = t - prefill_token_base;
       plan[L.cu_q + prow + 1] = t - prefill_token_base + n;
-      for (int q0 = 0; q0 < n; q0 += 64) {
+      // longest tiles first: the last query block of a chunk attends to the most keys
+      for (int q0 = ((n - 1) / 64) * 64; q0 >= 0; q0 -= 64) {
         plan[L.tile_seq + ntiles] = prow;
         plan[L.tile_q0 + ntiles] = q0;
         ++ntiles;
