@@ -20,6 +20,7 @@
 // drains and frees its TMEM, and the kernel returns.
 #include "common.cuh"
 #include "ogb_kernels.h"
+#include "tp_comm.cuh"
 
 extern "C" int ogb_num_sms() {
   static int num_sms = 0;
@@ -38,7 +39,7 @@ constexpr int kBM = 128;
 constexpr int kBK = 64;  // 64 bf16 = one 128-byte swizzle row
 constexpr int kGemmThreads = 192;
 
-enum GemmEpilogue : int { kEpiNone = 0, kEpiResidual = 1, kEpiSwiGLU = 2 };
+enum GemmEpilogue : int { kEpiNone = 0, kEpiResidual = 1, kEpiSwiGLU = 2, kEpiScatter = 3 };
 
 template <int BN>
 struct GemmCfg {
@@ -55,7 +56,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias,
                          const __nv_bfloat16* residual, float* __restrict__ C_f32, int M, int N, int K, int ldc, int ldr,
-                         int* status) {
+                         int* status, const TpScatter* __restrict__ sc) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -253,7 +254,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 for (int j = 0; j < 32 && col + j < N; ++j) dst[j] = v[j];
               }
             } else {
-              __nv_bfloat16* dst = C + static_cast<size_t>(row) * ldc + col;
+              __nv_bfloat16* dst;
+              if constexpr (EPI == kEpiScatter) {
+                // partial sums go straight to the rank that owns this row (peer-mapped staging, NVLink stores)
+                const int owner = row / sc->chunk;
+                dst = sc->staging[owner] +
+                      (static_cast<size_t>(sc->rank) * sc->chunk + (row - owner * sc->chunk)) * N + col;
+              } else {
+                dst = C + static_cast<size_t>(row) * ldc + col;
+              }
               if (full) {
 #pragma unroll
                 for (int j4 = 0; j4 < 4; ++j4)
@@ -265,6 +274,21 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
               }
             }
           }
+        }
+      }
+      if constexpr (EPI == kEpiScatter) {
+        // publish this warp's 32 rows x BN columns to their owner: every lane orders its stores at
+        // system scope, then one lane bumps the owner's per-row-group arrival counter
+        const int row0 = m0 + q * 32;
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0 && row0 < M) {
+          const int owner = row0 / sc->chunk;
+          uint32_t* cnt = sc->tile_cnt[owner] + (row0 - owner * sc->chunk) / 32;
+          // counted in 32-column units so the owner's expectation (N/32 per source rank) does not
+          // depend on the tile width this launch picked
+          const uint32_t units = static_cast<uint32_t>(min(BN, N - n0) / 32);
+          asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(cnt), "r"(units) : "memory");
         }
       }
       tc_fence_before();
@@ -326,7 +350,8 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_
 
 template <int BN, int EPI>
 static int launch_gemm(const void* A, const void* W, void* C, const void* bias, const void* residual, void* C_f32, int M,
-                       int N, int K, int lda, int ldw, int ldc, int ldr, int* status, cudaStream_t stream) {
+                       int N, int K, int lda, int ldw, int ldc, int ldr, int* status, cudaStream_t stream,
+                       const TpScatter* sc = nullptr) {
   using Cfg = GemmCfg<BN>;
   CUtensorMap ta, tb;
   int rc = make_tmap_bf16_2d(&ta, A, M, K, lda, kBM, kBK);
@@ -344,7 +369,7 @@ static int launch_gemm(const void* A, const void* W, void* C, const void* bias, 
   if (grid > ogb_num_sms()) grid = ogb_num_sms();
   gemm_bf16_tcgen05_kernel<BN, EPI><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(
       ta, tb, static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(bias),
-      static_cast<const __nv_bfloat16*>(residual), static_cast<float*>(C_f32), M, N, K, ldc, ldr, status);
+      static_cast<const __nv_bfloat16*>(residual), static_cast<float*>(C_f32), M, N, K, ldc, ldr, status, sc);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -402,4 +427,35 @@ extern "C" int ogb_gemm_bf16(const void* A, const void* W, void* C, const void* 
     }
   }
   return -7;
+}
+
+// Row-parallel GEMM of a tensor-parallel group: the partial product A[M,K_local] * W[N,K_local]^T of
+// this rank is written tile by tile into the staging buffer of the rank that owns each row, and
+// the owner's arrival counter for that 32-row group is bumped.  `sc` is a device-resident TpScatter.
+extern "C" int ogb_gemm_bf16_scatter(const void* A, const void* W, int M, int N, int K, int lda, int ldw, const void* sc,
+                                     int bn, int* status, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M <= 0) return 0;
+  if ((K % 8) != 0 || (lda % 8) != 0 || (ldw % 8) != 0 || (N % 32) != 0 || sc == nullptr) return -3;
+  if (bn == 0) {
+    const int m_tiles = (M + kBM - 1) / kBM;
+    const int sms = ogb_num_sms();
+    const int cand[3] = {256, 192, 128};
+    const float cost[3] = {1.0f, 0.78f, 0.62f};
+    float best = 1e30f;
+    bn = 256;
+    for (int i = 0; i < 3; ++i) {
+      const int tiles = m_tiles * ((N + cand[i] - 1) / cand[i]);
+      const float t = static_cast<float>((tiles + sms - 1) / sms) * cost[i];
+      if (t < best - 1e-6f) { best = t; bn = cand[i]; }
+    }
+  }
+  const TpScatter* s = static_cast<const TpScatter*>(sc);
+  void* dummy = const_cast<void*>(A);  // C is unused by the scatter epilogue but must be 16-byte aligned
+  switch (bn) {
+    case 128: return launch_gemm<128, kEpiScatter>(A, W, dummy, nullptr, nullptr, nullptr, M, N, K, lda, ldw, N, 0, status, stream, s);
+    case 192: return launch_gemm<192, kEpiScatter>(A, W, dummy, nullptr, nullptr, nullptr, M, N, K, lda, ldw, N, 0, status, stream, s);
+    case 256: return launch_gemm<256, kEpiScatter>(A, W, dummy, nullptr, nullptr, nullptr, M, N, K, lda, ldw, N, 0, status, stream, s);
+    default: return -2;
+  }
 }

@@ -1,0 +1,164 @@
+// Tensor-parallel communication over peer-mapped memory (NVLink 5 / NVSwitch), no NCCL inside.
+//
+// The reference has no multi-GPU execution at all: its comm crate is a trait plus an in-process
+// host oracle (crates/onnx-runtime-comm/src/lib.rs:19-29, communicator.rs:32-160) and its TP
+// notes are an analytic plan (docs/research/tensor-parallelism-feasibility.md:60-110).  This file
+// is the product-side backend of that contract for row-parallel projections:
+//
+//   1. gemm_bf16_tcgen05<kEpiScatter> (gemm_tcgen05.cu) writes each partial output tile into the
+//      staging buffer of the rank that owns the rows and bumps that rank's arrival counter, so the
+//      reduce-scatter traffic leaves the SM while later tiles are still in the tensor cores;
+//   2. tp_reduce_bcast_kernel (here) waits per 32-row group for all sources, sums them in a fixed
+//      rank order in fp32, adds the residual, and stores the new residual rows into every rank's
+//      copy of the residual stream (the all-gather half), then waits until every other owner's
+//      rows have landed locally.
+// Every result row is produced by exactly one rank and copied bit-for-bit to the others, so all
+// replicas stay identical.  Waits are bounded: on expiry the kernel ORs kStatusPeerTimeout into
+// the status word and returns.  Counters are reset by the kernel that consumed them.
+#include "common.cuh"
+#include "ogb_kernels.h"
+#include "tp_comm.cuh"
+
+namespace ogb {
+
+constexpr int kRbThreads = 256;
+constexpr int kRbCols = 512;   // columns per CTA
+
+OGB_DEVICE uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Bounded spin until *p >= want.  Returns false on timeout.
+OGB_DEVICE bool wait_counter(const uint32_t* p, uint32_t want, uint64_t limit_ns = kWaitLimitNs) {
+  if (ld_acquire_sys(p) >= want) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (ld_acquire_sys(p) < want) {
+    if (((++spins) & 0xff) == 0 && global_timer_ns() - t0 > limit_ns) return false;
+  }
+  return true;
+}
+
+// grid = (min(owned row groups, SMs / column blocks), column blocks); CTAs stride over row groups.
+// rows = total rows of the step (M).
+__global__ void __launch_bounds__(kRbThreads) tp_reduce_bcast_kernel(const TpReduce* __restrict__ rp, int rows,
+                                                                      uint32_t expect_x, int* status) {
+  const TpReduce& r = *rp;
+  const int groups = r.chunk / 32;
+  const int col0 = blockIdx.y * kRbCols;
+  const int ncols = min(kRbCols, r.n - col0);
+  const int vec_per_row = ncols / 8;
+  __shared__ int ok_sh;
+  for (int g = blockIdx.x; g < groups; g += gridDim.x) {   // g = owned 32-row group
+    const int row_base = r.rank * r.chunk + g * 32;        // global row of the group
+    if (row_base >= rows) break;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const bool ok = wait_counter(r.tile_cnt + g, static_cast<uint32_t>(r.n / 32) * r.tp);
+      if (!ok) atomicOr(status, kStatusPeerTimeout);
+      ok_sh = ok ? 1 : 0;
+    }
+    __syncthreads();
+    if (ok_sh) {
+      for (int i = threadIdx.x; i < 32 * vec_per_row; i += kRbThreads) {
+        const int lr = i / vec_per_row, cv = i % vec_per_row;
+        const int row = row_base + lr;
+        if (row >= rows) continue;
+        const int col = col0 + cv * 8;
+        float acc[8];
+        {
+          const uint4 v = *reinterpret_cast<const uint4*>(r.x[r.rank] + static_cast<size_t>(row) * r.n + col);
+          float2 f;
+          f = unpack_bf16(v.x); acc[0] = f.x; acc[1] = f.y;
+          f = unpack_bf16(v.y); acc[2] = f.x; acc[3] = f.y;
+          f = unpack_bf16(v.z); acc[4] = f.x; acc[5] = f.y;
+          f = unpack_bf16(v.w); acc[6] = f.x; acc[7] = f.y;
+        }
+        for (int src = 0; src < r.tp; ++src) {    // fixed order: the sum does not depend on arrival order
+          const uint4 v = *reinterpret_cast<const uint4*>(
+              r.staging + (static_cast<size_t>(src) * r.chunk + g * 32 + lr) * r.n + col);
+          float2 f;
+          f = unpack_bf16(v.x); acc[0] += f.x; acc[1] += f.y;
+          f = unpack_bf16(v.y); acc[2] += f.x; acc[3] += f.y;
+          f = unpack_bf16(v.z); acc[4] += f.x; acc[5] += f.y;
+          f = unpack_bf16(v.w); acc[6] += f.x; acc[7] += f.y;
+        }
+        const uint4 o = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]),
+                                   pack_bf16(acc[6], acc[7]));
+        for (int p = 0; p < r.tp; ++p)            // all-gather half: every replica receives the new row
+          *reinterpret_cast<uint4*>(r.x[p] + static_cast<size_t>(row) * r.n + col) = o;
+      }
+    }
+    // publish: this block of rows is in place everywhere
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int p = 0; p < r.tp; ++p) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(r.x_cnt[p]) : "memory");
+    }
+  }
+  if (threadIdx.x == 0) {
+    // wait until every owner's blocks have landed in this rank's residual stream
+    if (!wait_counter(r.x_cnt[r.rank], expect_x)) atomicOr(status, kStatusPeerTimeout);
+    // the last CTA of this launch resets the counters it consumed (safe: no rank can produce for the
+    // next use of this slot before it has received this rank's rows, which were sent above)
+    __threadfence();
+    const uint32_t total = gridDim.x * gridDim.y;
+    if (atomicAdd(r.done_cnt, 1u) == total - 1) {
+      for (int i = 0; i < groups; ++i) r.tile_cnt[i] = 0;
+      *r.x_cnt[r.rank] = 0;
+      *r.done_cnt = 0;
+      __threadfence_system();
+    }
+  }
+}
+
+}  // namespace ogb
+
+using namespace ogb;
+
+// x (every rank's residual stream) += sum over ranks of the staged partial tiles; `rp` is a
+// device-resident TpReduce for the slot.  Must follow ogb_gemm_bf16_scatter on the same stream.
+extern "C" int ogb_tp_reduce_bcast(const void* rp, int rows, int n, int chunk, int tp, int* status, void* stream) {
+  if (rows <= 0) return 0;
+  if (n % 8 || chunk % 32 || chunk / 32 > kTpMaxGroups) return -3;
+  const int groups = chunk / 32;
+  const int col_blocks = (n + kRbCols - 1) / kRbCols;
+  // blocks that will signal = row groups (over all ranks) that hold at least one valid row
+  const int total_groups = (rows + 31) / 32;
+  const uint32_t expect_x = static_cast<uint32_t>(total_groups) * col_blocks;
+  int gx = ogb_num_sms() / col_blocks;   // every CTA spins at the end: all must be co-resident
+  if (gx < 1) return -4;
+  if (gx > groups) gx = groups;
+  dim3 grid(gx, col_blocks);
+  tp_reduce_bcast_kernel<<<grid, kRbThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const TpReduce*>(rp), rows, expect_x, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// ---- peer mapping helpers (CUDA IPC) ----
+extern "C" int ogb_ipc_alloc(void** ptr, uint64_t bytes) {
+  cudaError_t e = cudaMalloc(ptr, bytes);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return static_cast<int>(cudaMemset(*ptr, 0, bytes));
+}
+extern "C" int ogb_ipc_free(void* ptr) { return static_cast<int>(cudaFree(ptr)); }
+extern "C" int ogb_ipc_get_handle(void* ptr, void* handle64) {
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, ptr);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  memcpy(handle64, &h, sizeof(h));
+  return 0;
+}
+extern "C" int ogb_ipc_open_handle(const void* handle64, void** ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  return static_cast<int>(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+}
+extern "C" int ogb_ipc_close_handle(void* ptr) { return static_cast<int>(cudaIpcCloseMemHandle(ptr)); }
+extern "C" int ogb_tp_struct_sizes(int* scatter_bytes, int* reduce_bytes) {
+  *scatter_bytes = static_cast<int>(sizeof(TpScatter));
+  *reduce_bytes = static_cast<int>(sizeof(TpReduce));
+  return 0;
+}

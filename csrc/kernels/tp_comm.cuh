@@ -1,0 +1,30 @@
+// Device-visible description of a tensor-parallel group whose ranks have mapped each other's
+// buffers (CUDA IPC over NVLink).  Shared by the GEMM scatter epilogue and the reduce+broadcast
+// kernel.  All cross-GPU traffic is plain loads/stores and release/acquire counters on these
+// mappings; nothing here issues TMA against peer memory.
+#pragma once
+#include <stdint.h>
+#include <cuda_bf16.h>
+
+namespace ogb {
+
+constexpr int kMaxTp = 8;
+constexpr int kTpSlots = 2;          // slot 0: o_proj, slot 1: down_proj (separate staging + counters)
+constexpr int kTpMaxGroups = 256;    // 32-row groups one rank can own (8192 rows)
+
+struct TpScatter {
+  __nv_bfloat16* staging[kMaxTp];    // rank p's staging for this slot: [tp sources][chunk rows][N]
+  uint32_t* tile_cnt[kMaxTp];        // rank p's arrival counters for this slot, one per owned 32-row group
+  int rank, tp, chunk, n;            // chunk = rows owned per rank (multiple of 32)
+};
+
+struct TpReduce {
+  __nv_bfloat16* staging;            // this rank's staging for the slot
+  uint32_t* tile_cnt;                // this rank's arrival counters for the slot
+  __nv_bfloat16* x[kMaxTp];          // every rank's residual stream [rows, n]
+  uint32_t* x_cnt[kMaxTp];           // every rank's "row blocks delivered" counter
+  uint32_t* done_cnt;                // local: CTAs of this launch that have finished
+  int rank, tp, chunk, n;
+};
+
+}  // namespace ogb

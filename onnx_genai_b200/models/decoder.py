@@ -176,7 +176,13 @@ class DecoderModel:
         hid = cfg.hidden
         self.cos_sin = ref.rope_table(cfg.max_position, self.rotary_dim, cfg.rope_theta, dev)
         z = lambda *s: torch.zeros(*s, dtype=dt, device=dev)
-        self.x = z(max_tokens, hid)                 # residual stream
+        self.fused_comm = comm if (comm is not None and hasattr(comm, "row_parallel") and dev.type == "cuda") else None
+        if self.fused_comm is not None:
+            if not self.fused_comm.ready:
+                self.fused_comm.setup(hid, max_tokens)
+            self.x = self.fused_comm.x              # residual stream lives in the peer-mapped region
+        else:
+            self.x = z(max_tokens, hid)             # residual stream
         self.h = z(max_tokens, hid)                 # normed activations
         self.qkv = z(max_tokens, (self.hq + 2 * self.hkv) * self.d)
         self.attn = z(max_tokens, self.hq * self.d)
@@ -272,7 +278,7 @@ class DecoderModel:
                 ops.paged_prefill(qkv[nd:], attn[nd:], pool, si.page_table[nd:nd + np_], si.ctx_len[nd:nd + np_],
                                   si.cu_q, si.tile_seq, si.tile_q0, si.num_tiles, self.hq, self.hkv, self.d, self.scale,
                                   cfg.sliding_window)
-            pending = self._row_parallel(attn, lw.o_w, x)
+            pending = self._row_parallel(attn, lw.o_w, x, 0)
             self._norm(x, lw.ln2, pending, h)
             if lw.gate_up_w is not None:
                 act = self.act[:t]
@@ -280,7 +286,7 @@ class DecoderModel:
                     ops.gemm(h, lw.gate_up_w, epilogue="swiglu", swiglu_half=w.swiglu_half, out=act)
                 else:
                     act = ops.gemm(h, lw.gate_up_w, epilogue="swiglu", swiglu_half=w.swiglu_half)
-                pending = self._row_parallel(act, lw.down_w, x)
+                pending = self._row_parallel(act, lw.down_w, x, 1)
             else:
                 pending = self._moe(h, lw, x)
         r = si.num_logit_rows
@@ -307,7 +313,7 @@ class DecoderModel:
         else:
             out.copy_(ops.gemm(a, wt, bias=bias))
 
-    def _row_parallel(self, a, wt, x):
+    def _row_parallel(self, a, wt, x, slot=0):
         """x += a @ wt^T.  TP=1: fused residual epilogue.  TP>1: partial sum -> all-reduce -> returned as
         a pending delta that the next RMSNorm adds."""
         if self.tp == 1:
@@ -315,6 +321,11 @@ class DecoderModel:
                 ops.gemm(a, wt, residual=x, epilogue="residual", out=x)
             else:
                 x.copy_(ops.gemm(a, wt, residual=x, epilogue="residual"))
+            return None
+        if self.fused_comm is not None:
+            # GEMM epilogue scatters partial tiles to the owner ranks; the owners reduce, add the
+            # residual and write the new rows into every rank's x.  Nothing is left pending.
+            self.fused_comm.row_parallel(a, wt, a.shape[0], slot)
             return None
         part = self.partial[: a.shape[0]]
         self._gemm(a, wt, out=part)

@@ -1,0 +1,191 @@
+"""Fused tensor-parallel communicator: GEMM + reduce-scatter + all-gather over peer-mapped memory.
+
+Every rank allocates one symmetric region (staging tiles for two projection slots, arrival
+counters, the residual stream) with ``cudaMalloc``, exports it through CUDA IPC and maps every
+peer's region.  A row-parallel projection is then two launches on each rank and no library
+collective:
+
+    ogb_gemm_bf16_scatter   tcgen05 GEMM whose epilogue stores each partial tile into the owner
+                            rank's staging over NVLink and bumps the owner's arrival counter
+    ogb_tp_reduce_bcast     owner sums the sources in fixed rank order + residual, stores the new
+                            rows into every rank's residual stream, waits for the other owners
+
+Collectives this class does not cover (broadcast of sampled tokens, barriers, scalar reductions)
+go to the wrapped NCCL communicator.  The reference's counterpart is only a contract
+(crates/onnx-runtime-comm/src/communicator.rs:32-160); its ordering rule -- every rank issues the
+same collective in the same slot (ordering.rs:349-384) -- holds here by construction because every
+rank runs the same step plan.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..ops import _native
+
+MAX_TP = 8
+SLOTS = 2
+MAX_GROUPS = 256
+
+
+class _Scatter(ctypes.Structure):
+    _fields_ = [("staging", ctypes.c_uint64 * MAX_TP), ("tile_cnt", ctypes.c_uint64 * MAX_TP),
+                ("rank", ctypes.c_int), ("tp", ctypes.c_int), ("chunk", ctypes.c_int), ("n", ctypes.c_int)]
+
+
+class _Reduce(ctypes.Structure):
+    _fields_ = [("staging", ctypes.c_uint64), ("tile_cnt", ctypes.c_uint64), ("x", ctypes.c_uint64 * MAX_TP),
+                ("x_cnt", ctypes.c_uint64 * MAX_TP), ("done_cnt", ctypes.c_uint64),
+                ("rank", ctypes.c_int), ("tp", ctypes.c_int), ("chunk", ctypes.c_int), ("n", ctypes.c_int)]
+
+
+class _CudaArray:
+    """Minimal __cuda_array_interface__ holder so torch can view IPC memory it did not allocate."""
+
+    def __init__(self, ptr, shape, typestr):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False),
+                                         "version": 2}
+
+
+def _lib():
+    lib = _native.load()
+    P, I = ctypes.c_void_p, ctypes.c_int
+    lib.ogb_ipc_alloc.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_uint64]
+    lib.ogb_ipc_get_handle.argtypes = [P, P]
+    lib.ogb_ipc_open_handle.argtypes = [P, ctypes.POINTER(ctypes.c_void_p)]
+    lib.ogb_ipc_close_handle.argtypes = [P]
+    lib.ogb_ipc_free.argtypes = [P]
+    lib.ogb_tp_struct_sizes.argtypes = [ctypes.POINTER(I), ctypes.POINTER(I)]
+    lib.ogb_gemm_bf16_scatter.argtypes = [P, P, I, I, I, I, I, P, I, P, P]
+    lib.ogb_tp_reduce_bcast.argtypes = [P, I, I, I, I, P, P]
+    for f in ("ogb_ipc_alloc", "ogb_ipc_get_handle", "ogb_ipc_open_handle", "ogb_ipc_close_handle", "ogb_ipc_free",
+              "ogb_tp_struct_sizes", "ogb_gemm_bf16_scatter", "ogb_tp_reduce_bcast"):
+        getattr(lib, f).restype = I
+    return lib
+
+
+class FusedComm:
+    backend_name = "fused-p2p"
+
+    def __init__(self, base, device, hidden: int = 0, max_tokens: int = 0):
+        self.base = base
+        self.rank, self.world = base.rank, base.world
+        self.device = torch.device(device)
+        self.lib = _lib()
+        self.ready = False
+        self.calls = 0
+        if hidden and max_tokens:
+            self.setup(hidden, max_tokens)
+
+    # -- collectives delegated to the library backend ------------------------------------------
+    def all_reduce(self, t):
+        return self.base.all_reduce(t)
+
+    def broadcast(self, t, src=0):
+        return self.base.broadcast(t, src)
+
+    def barrier(self):
+        return self.base.barrier()
+
+    def min_int(self, v):
+        return self.base.min_int(v)
+
+    def max_float(self, v):
+        return self.base.max_float(v)
+
+    # -- symmetric region ----------------------------------------------------------------------
+    def setup(self, hidden: int, max_tokens: int):
+        """Allocate, export and map the symmetric region for a residual stream [max_tokens, hidden]."""
+        sb, rb = ctypes.c_int(), ctypes.c_int()
+        self.lib.ogb_tp_struct_sizes(ctypes.byref(sb), ctypes.byref(rb))
+        assert sb.value == ctypes.sizeof(_Scatter) and rb.value == ctypes.sizeof(_Reduce), "struct layout mismatch"
+        tp = self.world
+        self.hidden, self.max_tokens = hidden, max_tokens
+        self.chunk_max = ((max_tokens + tp - 1) // tp + 31) // 32 * 32
+        stage_bytes = tp * self.chunk_max * hidden * 2
+        align = lambda v: (v + 255) // 256 * 256
+        self.off_stage = [0, align(stage_bytes)]
+        self.off_x = self.off_stage[1] + align(stage_bytes)
+        self.off_cnt = self.off_x + align(max_tokens * hidden * 2)
+        # counters: tile_cnt[SLOTS][MAX_GROUPS], x_cnt, done_cnt
+        cnt_words = SLOTS * MAX_GROUPS + 64
+        total = self.off_cnt + align(cnt_words * 4)
+        ptr = ctypes.c_void_p()
+        rc = self.lib.ogb_ipc_alloc(ctypes.byref(ptr), total)
+        if rc != 0:
+            raise RuntimeError(f"symmetric allocation of {total} bytes failed (cuda error {rc})")
+        self.local_ptr = ptr.value
+        handle = ctypes.create_string_buffer(64)
+        rc = self.lib.ogb_ipc_get_handle(ptr, handle)
+        if rc != 0:
+            raise RuntimeError(f"cudaIpcGetMemHandle failed ({rc})")
+        handles = [None] * tp
+        dist.all_gather_object(handles, bytes(handle.raw))
+        self.peer_ptrs = []
+        for p in range(tp):
+            if p == self.rank:
+                self.peer_ptrs.append(self.local_ptr)
+                continue
+            out = ctypes.c_void_p()
+            buf = ctypes.create_string_buffer(handles[p], 64)
+            rc = self.lib.ogb_ipc_open_handle(buf, ctypes.byref(out))
+            if rc != 0:
+                raise RuntimeError(f"cudaIpcOpenMemHandle for rank {p} failed ({rc})")
+            self.peer_ptrs.append(out.value)
+        self.x = torch.as_tensor(_CudaArray(self.local_ptr + self.off_x, (max_tokens, hidden), "<u2"),
+                                 device=self.device).view(torch.bfloat16)
+        self._structs: dict = {}
+        torch.cuda.synchronize()
+        self.base.barrier()
+        self.ready = True
+
+    def _tile_cnt(self, p, slot):
+        return self.peer_ptrs[p] + self.off_cnt + slot * MAX_GROUPS * 4
+
+    def _x_cnt(self, p):
+        return self.peer_ptrs[p] + self.off_cnt + SLOTS * MAX_GROUPS * 4
+
+    def _get_structs(self, slot: int, chunk: int):
+        key = (slot, chunk)
+        hit = self._structs.get(key)
+        if hit is not None:
+            return hit
+        tp = self.world
+        sc, rd = _Scatter(), _Reduce()
+        for p in range(tp):
+            sc.staging[p] = self.peer_ptrs[p] + self.off_stage[slot]
+            sc.tile_cnt[p] = self._tile_cnt(p, slot)
+            rd.x[p] = self.peer_ptrs[p] + self.off_x
+            rd.x_cnt[p] = self._x_cnt(p)
+        sc.rank, sc.tp, sc.chunk, sc.n = self.rank, tp, chunk, self.hidden
+        rd.staging = self.local_ptr + self.off_stage[slot]
+        rd.tile_cnt = self._tile_cnt(self.rank, slot)
+        rd.done_cnt = self.local_ptr + self.off_cnt + (SLOTS * MAX_GROUPS + 8) * 4
+        rd.rank, rd.tp, rd.chunk, rd.n = self.rank, tp, chunk, self.hidden
+        mk = lambda st: torch.frombuffer(bytearray(bytes(st)), dtype=torch.uint8).to(self.device)
+        hit = (mk(sc), mk(rd))
+        self._structs[key] = hit
+        return hit
+
+    def chunk_for(self, rows: int) -> int:
+        tp = self.world
+        return max(32, ((rows + tp - 1) // tp + 31) // 32 * 32)
+
+    # -- the fused row-parallel projection -----------------------------------------------------
+    def row_parallel(self, a, w, rows: int, slot: int):
+        """x[:rows] += sum over ranks of a @ w^T, on every rank (x = the symmetric residual stream)."""
+        chunk = self.chunk_for(rows)
+        sc, rd = self._get_structs(slot, chunk)
+        st = ops.status_word(self.device).data_ptr()
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = self.lib.ogb_gemm_bf16_scatter(a.data_ptr(), w.data_ptr(), rows, self.hidden, a.shape[1], a.stride(0),
+                                            w.stride(0), sc.data_ptr(), 0, st, stream)
+        _native.check(rc, "ogb_gemm_bf16_scatter")
+        rc = self.lib.ogb_tp_reduce_bcast(rd.data_ptr(), rows, self.hidden, chunk, self.world, st, stream)
+        _native.check(rc, "ogb_tp_reduce_bcast")
+        ops.launch_counts["gemm_bf16_scatter"] += 1
+        ops.launch_counts["tp_reduce_bcast"] += 1
+        self.calls += 1

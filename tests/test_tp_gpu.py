@@ -1,0 +1,36 @@
+"""Tensor parallelism on 2 GPUs: the fused peer-memory path and the NCCL baseline against TP=1."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(nproc, mode, out, port):
+    env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
+    if nproc == 1:
+        cmd = [sys.executable, os.path.join(ROOT, "tests", "tp_worker.py"), mode, out]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+               "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "tp_worker.py"),
+               mode, out]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-4000:]
+    return torch.load(out)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp2_fused_and_nccl_match_single_gpu(tmp_path):
+    single = _run(1, "nccl", str(tmp_path / "s.pt"), 0)
+    nccl = _run(2, "nccl", str(tmp_path / "n.pt"), 29631)
+    fused = _run(2, "fused", str(tmp_path / "f.pt"), 29632)
+    ref = single["logits"]
+    for name, got in (("nccl", nccl), ("fused", fused)):
+        err = float((got["logits"] - ref).norm() / ref.norm())
+        assert err < 3e-2, (name, err)
+    assert fused["launches"].get("gemm_bf16_scatter", 0) > 0 and fused["launches"].get("tp_reduce_bcast", 0) > 0
+    assert len(fused["tokens"]) == len(single["tokens"])

@@ -1,0 +1,55 @@
+"""Worker for the tensor-parallel GPU tests (launched by torch.distributed.run, one rank per GPU)."""
+import json
+import sys
+
+import numpy as np
+import torch
+
+from onnx_genai_b200 import ops
+from onnx_genai_b200.engine.llm_engine import EngineConfig, LLMEngine
+from onnx_genai_b200.models.config import DecoderConfig
+from onnx_genai_b200.parallel import comm as comm_mod
+
+
+def main():
+    mode, out_path = sys.argv[1], sys.argv[2]
+    rank, world, local_rank = comm_mod.init_distributed()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    cfg = DecoderConfig(name="tp", num_layers=3, hidden=512, num_heads=8, num_kv_heads=2, head_dim=64, intermediate=1024,
+                        vocab=2048, rope_theta=1e6, tie_embeddings=False, qkv_bias=True, max_position=1024)
+    comm = comm_mod.NcclComm() if world > 1 else None
+    if mode == "fused" and world > 1:
+        from onnx_genai_b200.parallel.fused import FusedComm
+
+        comm = FusedComm(comm, dev)
+    eng = LLMEngine(EngineConfig(model=cfg, num_pages=256, max_seqs=16, max_tokens_per_step=512, max_seq_len=512,
+                                 seed=21), device=dev, tp=world, rank=rank, comm=comm)
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(0, cfg.vocab, size=n).astype(np.int32) for n in (3, 64, 97, 200)]
+    for p in prompts:
+        eng.add_request(p, 12)
+    eng.step()
+    logits = eng.model.logits[: len(prompts)].float().cpu()
+    toks = []
+    while eng.has_work:
+        toks += [(sid, tok) for sid, tok, _ in eng.step().events]
+    torch.cuda.synchronize()
+    ops.check_status()
+    gathered = [None] * world
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.all_gather_object(gathered, toks)
+        assert all(g == gathered[0] for g in gathered), "ranks diverged"
+    if rank == 0:
+        torch.save({"logits": logits, "tokens": toks, "launches": dict(ops.launch_counts)}, out_path)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
