@@ -85,15 +85,28 @@ extern "C" void ogb_decoder_set_split_scratch(void* plan, float* part_o, float* 
   p->part_ml = part_ml;
 }
 
-// One forward pass for a single-GPU (tp == 1) dense decoder.  Section pointers address the
-// device copy of the packed step plan.
+// One forward pass of a dense decoder.  Section pointers address the device copy of the packed
+// step plan.
+extern "C" int ogb_gemm_bf16_scatter(const void* A, const void* W, int M, int N, int K, int lda, int ldw, const void* sc,
+                                     int bn, int* status, void* stream_);
+extern "C" int ogb_tp_reduce_bcast(const void* rp, int rows, int n, int chunk, int tp, int* status, void* stream);
+
+// tp > 1: `tp_structs` = {scatter slot 0, reduce slot 0, scatter slot 1, reduce slot 1} device structs
+// for this step's row chunk; the residual stream p->x then lives in the peer-mapped region and the
+// row-parallel projections run as GEMM-scatter + reduce/broadcast instead of a residual epilogue.
 extern "C" int ogb_decoder_step(void* plan, const int* token_ids, const int* positions, const int* slots,
                                 const int* ctx_len, const int* page_table, const int* cu_q, const int* tile_seq,
                                 const int* tile_q0, const int* logit_rows, int T, int Nd, int Np, int num_tiles, int R,
-                                int decode_splits, void* stream) {
+                                int decode_splits, void* stream, const uint64_t* tp_structs, int tp_chunk) {
   DecoderPlan* p = static_cast<DecoderPlan*>(plan);
   if (T <= 0) return 0;
-  if (p->tp != 1) return -10;
+  if (p->tp != 1 && tp_structs == nullptr) return -10;
+  const void* sc[2] = {nullptr, nullptr};
+  const void* rd[2] = {nullptr, nullptr};
+  if (p->tp != 1) {
+    sc[0] = reinterpret_cast<const void*>(tp_structs[0]); rd[0] = reinterpret_cast<const void*>(tp_structs[1]);
+    sc[1] = reinterpret_cast<const void*>(tp_structs[2]); rd[1] = reinterpret_cast<const void*>(tp_structs[3]);
+  }
   const int hid = p->hidden, d = p->d, hq = p->hq, hkv = p->hkv;
   const int qkv_n = (hq + 2 * hkv) * d;
   const int attn_n = hq * d;
@@ -117,13 +130,24 @@ extern "C" int ogb_decoder_step(void* plan, const int* token_ids, const int* pos
                                         ctx_len + Nd, cu_q, tile_seq, tile_q0, num_tiles, Np, p->max_pages, p->num_pages, hq,
                                         hkv, d, qkv_n, attn_n, p->scale, p->window, p->status, stream));
     }
-    STEP_CHECK(ogb_gemm_bf16(p->attn, L.o_w, p->x, nullptr, p->x, nullptr, T, hid, attn_n, attn_n, attn_n, hid, hid, 1, 0,
-                             p->status, stream));
+    if (p->tp == 1) {
+      STEP_CHECK(ogb_gemm_bf16(p->attn, L.o_w, p->x, nullptr, p->x, nullptr, T, hid, attn_n, attn_n, attn_n, hid, hid, 1, 0,
+                               p->status, stream));
+    } else {
+      STEP_CHECK(ogb_gemm_bf16_scatter(p->attn, L.o_w, T, hid, attn_n, attn_n, attn_n, sc[0], 0, p->status, stream));
+      STEP_CHECK(ogb_tp_reduce_bcast(rd[0], T, hid, tp_chunk, p->tp, p->status, stream));
+    }
     STEP_CHECK(ogb_rmsnorm_bf16(p->x, nullptr, L.ln2, p->h, T, hid, hid, hid, p->eps, stream));
     STEP_CHECK(ogb_gemm_bf16(p->h, L.gate_up_w, p->act, nullptr, nullptr, nullptr, T, 2 * p->inter_local, hid, hid, hid,
                              p->inter_local, 0, 2, p->swiglu_bn, p->status, stream));
-    STEP_CHECK(ogb_gemm_bf16(p->act, L.down_w, p->x, nullptr, p->x, nullptr, T, hid, p->inter_local, p->inter_local,
-                             p->inter_local, hid, hid, 1, 0, p->status, stream));
+    if (p->tp == 1) {
+      STEP_CHECK(ogb_gemm_bf16(p->act, L.down_w, p->x, nullptr, p->x, nullptr, T, hid, p->inter_local, p->inter_local,
+                               p->inter_local, hid, hid, 1, 0, p->status, stream));
+    } else {
+      STEP_CHECK(ogb_gemm_bf16_scatter(p->act, L.down_w, T, hid, p->inter_local, p->inter_local, p->inter_local, sc[1], 0,
+                                       p->status, stream));
+      STEP_CHECK(ogb_tp_reduce_bcast(rd[1], T, hid, tp_chunk, p->tp, p->status, stream));
+    }
   }
   if (R > 0) {
     // rows that sample: x_last[r] = x[logit_rows[r]] (the embedding gather doubles as a row gather)

@@ -195,7 +195,8 @@ class DecoderModel:
         self.scale = 1.0 / math.sqrt(self.d)
         self.decode_splits = 1
         self.part_o = self.part_ml = None
-        self.native = None          # C++ step executor (single GPU, dense bf16 layers, bf16 pages)
+        self._tp_args_cache: dict = {}
+        self.native = None          # C++ step executor (dense bf16 layers, bf16 pages; TP needs the fused communicator)
         self.native_launches = 0
 
     def bind_native(self, kv: "KVCache", max_pages_per_seq: int) -> bool:
@@ -206,14 +207,16 @@ class DecoderModel:
         from ..ops import _native
 
         cfg, w = self.cfg, self.w
-        if (self.device.type != "cuda" or self.tp != 1 or kv.scales is not None or ops._BASELINE
+        if (self.device.type != "cuda" or (self.tp != 1 and self.fused_comm is None) or kv.scales is not None
+                or ops._BASELINE
                 or any(l.gate_up_w is None or l.quant for l in w.layers)):
             return False
         lib = _native.load()
         lib.ogb_decoder_create.restype = ctypes.c_void_p
         lib.ogb_decoder_create.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
         lib.ogb_decoder_step.restype = ctypes.c_int
-        lib.ogb_decoder_step.argtypes = [ctypes.c_void_p] * 10 + [ctypes.c_int] * 6 + [ctypes.c_void_p]
+        lib.ogb_decoder_step.argtypes = ([ctypes.c_void_p] * 10 + [ctypes.c_int] * 6 + [ctypes.c_void_p, ctypes.c_void_p,
+                                                                                         ctypes.c_int])
         lib.ogb_decoder_launches.restype = ctypes.c_longlong
         lib.ogb_decoder_launches.argtypes = [ctypes.c_void_p]
         lib.ogb_decoder_set_split_scratch.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
@@ -235,6 +238,22 @@ class DecoderModel:
         self.native = lib.ogb_decoder_create(ip, kv.num_pages, fp, gp, lp)
         return bool(self.native)
 
+    def _tp_step_args(self, rows: int):
+        """(pointer to the 4 device-struct addresses for this step's row chunk, chunk) or (None, 0)."""
+        fc = self.fused_comm
+        if fc is None:
+            return None, 0
+        import ctypes
+
+        chunk = fc.chunk_for(rows)
+        hit = self._tp_args_cache.get(chunk)
+        if hit is None:
+            sc0, rd0 = fc._get_structs(0, chunk)
+            sc1, rd1 = fc._get_structs(1, chunk)
+            hit = (ctypes.c_uint64 * 4)(sc0.data_ptr(), rd0.data_ptr(), sc1.data_ptr(), rd1.data_ptr())
+            self._tp_args_cache[chunk] = hit
+        return hit, chunk
+
     def set_decode_splits(self, splits: int):
         self.decode_splits = splits
         if splits > 1 and self.device.type == "cuda":
@@ -254,7 +273,7 @@ class DecoderModel:
                 self.native, si.token_ids.data_ptr(), si.positions.data_ptr(), si.slots.data_ptr(), si.ctx_len.data_ptr(),
                 si.page_table.data_ptr(), si.cu_q.data_ptr(), si.tile_seq.data_ptr(), si.tile_q0.data_ptr(),
                 si.logit_rows.data_ptr(), t, nd, si.num_prefill_seqs, si.num_tiles, si.num_logit_rows,
-                self.decode_splits, torch.cuda.current_stream().cuda_stream)
+                self.decode_splits, torch.cuda.current_stream().cuda_stream, *self._tp_step_args(t))
             if rc != 0:
                 raise RuntimeError(f"ogb_decoder_step failed with code {rc}")
             n = self._native_lib.ogb_decoder_launches(self.native) - before

