@@ -113,6 +113,10 @@ def main():
     if args.impl == "reference":
         return reference_arm(args)
     args.warmup = max(args.warmup, 3)
+    # stdout carries exactly one JSON line: anything libraries print (NCCL's version banner, torchrun
+    # notices) is sent to stderr by pointing fd 1 at fd 2 and keeping a private handle on the real stdout
+    real_stdout = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
 
     import numpy as np
     import torch
@@ -315,7 +319,8 @@ def main():
         }
         if invalid:
             result["invalid"] = invalid
-        print(json.dumps(result))
+        real_stdout.write(json.dumps(result) + "\n")
+        real_stdout.flush()
     if world > 1:
         import torch.distributed as dist
 

@@ -102,6 +102,26 @@ def _timed(name):
     return deco
 
 
+class timed_region:
+    """``with ops.timed_region("name"):`` records a CUDA-event pair when the op profiler is on."""
+
+    def __init__(self, name):
+        self.name = name
+
+    def __enter__(self):
+        if _PROFILE is not None:
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e0.record()
+        return self
+
+    def __exit__(self, *exc):
+        if _PROFILE is not None and hasattr(self, "e0"):
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record()
+            _PROFILE.append((self.name, self.e0, e1))
+        return False
+
+
 def num_sms() -> int:
     return _native.load().ogb_num_sms()
 

@@ -181,10 +181,12 @@ class FusedComm:
         sc, rd = self._get_structs(slot, chunk)
         st = ops.status_word(self.device).data_ptr()
         stream = torch.cuda.current_stream().cuda_stream
-        rc = self.lib.ogb_gemm_bf16_scatter(a.data_ptr(), w.data_ptr(), rows, self.hidden, a.shape[1], a.stride(0),
-                                            w.stride(0), sc.data_ptr(), 0, st, stream)
+        with ops.timed_region("gemm_scatter[K=%d]" % a.shape[1]):
+            rc = self.lib.ogb_gemm_bf16_scatter(a.data_ptr(), w.data_ptr(), rows, self.hidden, a.shape[1], a.stride(0),
+                                                w.stride(0), sc.data_ptr(), 0, st, stream)
         _native.check(rc, "ogb_gemm_bf16_scatter")
-        rc = self.lib.ogb_tp_reduce_bcast(rd.data_ptr(), rows, self.hidden, chunk, self.world, st, stream)
+        with ops.timed_region("tp_reduce_bcast"):
+            rc = self.lib.ogb_tp_reduce_bcast(rd.data_ptr(), rows, self.hidden, chunk, self.world, st, stream)
         _native.check(rc, "ogb_tp_reduce_bcast")
         ops.launch_counts["gemm_bf16_scatter"] += 1
         ops.launch_counts["tp_reduce_bcast"] += 1
