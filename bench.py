@@ -107,6 +107,7 @@ def main():
     ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "fused"])
     ap.add_argument("--token-multiple", type=int, default=128,
                     help="the scheduler trims the last prefill chunk so a step's token count is a multiple of this (GEMM M tile)")
+    ap.add_argument("--deadline", type=int, default=900, help="seconds after which a stuck run dumps stacks and exits")
     ap.add_argument("--no-native-executor", action="store_true", help="drive the layer stack from Python (for op profiling)")
     ap.add_argument("--profile-ops", action="store_true", help="after the timed regions, replay 4 steps with per-op CUDA-event timing (stderr)")
     args = ap.parse_args()
@@ -117,6 +118,11 @@ def main():
     # notices) is sent to stderr by pointing fd 1 at fd 2 and keeping a private handle on the real stdout
     real_stdout = os.fdopen(os.dup(1), "w")
     os.dup2(2, 1)
+    # a rank that stops making progress (a peer died, a collective never completes) must not hold the
+    # GPUs forever: dump the stacks and exit after the deadline
+    import faulthandler
+
+    faulthandler.dump_traceback_later(args.deadline, exit=True)
 
     import numpy as np
     import torch
@@ -268,13 +274,15 @@ def main():
     launches_dev = sum(ops.launch_counts.values()) - launches1
     sampler.stop()
     eng.check_device_status()
-    if args.profile_ops and rank == 0:
+    if args.profile_ops:
+        # every rank replays (the steps contain collectives); rank 0 reports
         n_prof = min(4, args.steps)
         ops.profile_start()
         for i in range(n_prof):
             replay(i)
         agg = ops.profile_stop()
         tot = sum(t for t, _ in agg.values())
+    if args.profile_ops and rank == 0:
         print("per-op device time over %d replayed steps (ms per step, calls per step, share):" % n_prof, file=sys.stderr)
         for name, (t, c) in sorted(agg.items(), key=lambda kv: -kv[1][0]):
             print("  %-44s %8.3f ms %6.1f calls %5.1f%%" % (name, t / n_prof, c / n_prof, 100 * t / tot), file=sys.stderr)
