@@ -256,10 +256,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             } else {
               __nv_bfloat16* dst;
               if constexpr (EPI == kEpiScatter) {
-                // partial sums go straight to the rank that owns this row (peer-mapped staging, NVLink stores)
-                const int owner = row / sc->chunk;
-                dst = sc->staging[owner] +
-                      (static_cast<size_t>(sc->rank) * sc->chunk + (row - owner * sc->chunk)) * N + col;
+                // the partial product stays in this rank's own buffer; the owner of the row pulls it
+                dst = sc->staging[sc->rank] + static_cast<size_t>(row) * N + col;
               } else {
                 dst = C + static_cast<size_t>(row) * ldc + col;
               }
@@ -277,10 +275,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         }
       }
       if constexpr (EPI == kEpiScatter) {
-        // publish this warp's 32 rows x BN columns to their owner: every lane orders its stores at
-        // system scope, then one lane bumps the owner's per-row-group arrival counter
+        // publish this warp's 32 rows x BN columns to their owner: the warp barrier orders every
+        // lane's stores before lane 0, whose release at system scope is cumulative over them, then
+        // bumps the owner's per-row-group arrival counter (the only remote write of this kernel)
         const int row0 = m0 + q * 32;
-        __threadfence_system();
         __syncwarp();
         if (lane == 0 && row0 < M) {
           const int owner = row0 / sc->chunk;
@@ -430,8 +428,8 @@ extern "C" int ogb_gemm_bf16(const void* A, const void* W, void* C, const void* 
 }
 
 // Row-parallel GEMM of a tensor-parallel group: the partial product A[M,K_local] * W[N,K_local]^T of
-// this rank is written tile by tile into the staging buffer of the rank that owns each row, and
-// the owner's arrival counter for that 32-row group is bumped.  `sc` is a device-resident TpScatter.
+// this rank is written tile by tile into this rank's peer-mapped partial buffer, and the arrival
+// counter of the rank that owns each 32-row group is bumped as soon as the tile is stored.  `sc` is a device-resident TpScatter.
 extern "C" int ogb_gemm_bf16_scatter(const void* A, const void* W, int M, int N, int K, int lda, int ldw, const void* sc,
                                      int bn, int* status, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);

@@ -5,13 +5,15 @@
 // notes are an analytic plan (docs/research/tensor-parallelism-feasibility.md:60-110).  This file
 // is the product-side backend of that contract for row-parallel projections:
 //
-//   1. gemm_bf16_tcgen05<kEpiScatter> (gemm_tcgen05.cu) writes each partial output tile into the
-//      staging buffer of the rank that owns the rows and bumps that rank's arrival counter, so the
-//      reduce-scatter traffic leaves the SM while later tiles are still in the tensor cores;
-//   2. tp_reduce_bcast_kernel (here) waits per 32-row group for all sources, sums them in a fixed
+//   1. gemm_bf16_tcgen05<kEpiScatter> (gemm_tcgen05.cu) keeps its partial output in a peer-mapped
+//      buffer of its own GPU and, tile by tile, bumps the arrival counter of the rank that owns
+//      the rows (one remote reduction per warp tile; the tensor-core loop never waits on NVLink);
+//   2. tp_reduce_bcast_kernel (here) waits per 32-row group for all sources, pulls their partial
+//      rows with coalesced 512-byte peer loads (the reduce-scatter half), sums them in a fixed
 //      rank order in fp32, adds the residual, and stores the new residual rows into every rank's
 //      copy of the residual stream (the all-gather half), then waits until every other owner's
-//      rows have landed locally.
+//      rows have landed locally.  Row groups are consumed as their counters fill, so the pull
+//      overlaps the tail of slower peers' GEMMs.
 // Every result row is produced by exactly one rank and copied bit-for-bit to the others, so all
 // replicas stay identical.  Waits are bounded: on expiry the kernel ORs kStatusPeerTimeout into
 // the status word and returns.  Counters are reset by the kernel that consumed them.
@@ -77,8 +79,7 @@ __global__ void __launch_bounds__(kRbThreads) tp_reduce_bcast_kernel(const TpRed
           f = unpack_bf16(v.w); acc[6] = f.x; acc[7] = f.y;
         }
         for (int src = 0; src < r.tp; ++src) {    // fixed order: the sum does not depend on arrival order
-          const uint4 v = *reinterpret_cast<const uint4*>(
-              r.staging + (static_cast<size_t>(src) * r.chunk + g * 32 + lr) * r.n + col);
+          const uint4 v = *reinterpret_cast<const uint4*>(r.part[src] + static_cast<size_t>(row) * r.n + col);
           float2 f;
           f = unpack_bf16(v.x); acc[0] += f.x; acc[1] += f.y;
           f = unpack_bf16(v.y); acc[2] += f.x; acc[3] += f.y;

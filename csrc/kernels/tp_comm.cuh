@@ -13,13 +13,13 @@ constexpr int kTpSlots = 2;          // slot 0: o_proj, slot 1: down_proj (separ
 constexpr int kTpMaxGroups = 256;    // 32-row groups one rank can own (8192 rows)
 
 struct TpScatter {
-  __nv_bfloat16* staging[kMaxTp];    // rank p's staging for this slot: [tp sources][chunk rows][N]
+  __nv_bfloat16* staging[kMaxTp];    // rank p's partial-product buffer for this slot: [rows][N] (only [rank] is written)
   uint32_t* tile_cnt[kMaxTp];        // rank p's arrival counters for this slot, one per owned 32-row group
   int rank, tp, chunk, n;            // chunk = rows owned per rank (multiple of 32)
 };
 
 struct TpReduce {
-  __nv_bfloat16* staging;            // this rank's staging for the slot
+  const __nv_bfloat16* part[kMaxTp]; // every rank's partial-product buffer for the slot (peer-mapped, read here)
   uint32_t* tile_cnt;                // this rank's arrival counters for the slot
   __nv_bfloat16* x[kMaxTp];          // every rank's residual stream [rows, n]
   uint32_t* x_cnt[kMaxTp];           // every rank's "row blocks delivered" counter

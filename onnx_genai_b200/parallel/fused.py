@@ -5,10 +5,11 @@ counters, the residual stream) with ``cudaMalloc``, exports it through CUDA IPC 
 peer's region.  A row-parallel projection is then two launches on each rank and no library
 collective:
 
-    ogb_gemm_bf16_scatter   tcgen05 GEMM whose epilogue stores each partial tile into the owner
-                            rank's staging over NVLink and bumps the owner's arrival counter
-    ogb_tp_reduce_bcast     owner sums the sources in fixed rank order + residual, stores the new
-                            rows into every rank's residual stream, waits for the other owners
+    ogb_gemm_bf16_scatter   tcgen05 GEMM whose epilogue keeps the partial tile in this rank's peer-mapped
+                            buffer and bumps the owner rank's arrival counter over NVLink
+    ogb_tp_reduce_bcast     owner pulls the sources' rows (peer loads), sums them in fixed rank order
+                            + residual, stores the new rows into every rank's residual stream, waits
+                            for the other owners
 
 Collectives this class does not cover (broadcast of sampled tokens, barriers, scalar reductions)
 go to the wrapped NCCL communicator.  The reference's counterpart is only a contract
@@ -37,7 +38,7 @@ class _Scatter(ctypes.Structure):
 
 
 class _Reduce(ctypes.Structure):
-    _fields_ = [("staging", ctypes.c_uint64), ("tile_cnt", ctypes.c_uint64), ("x", ctypes.c_uint64 * MAX_TP),
+    _fields_ = [("part", ctypes.c_uint64 * MAX_TP), ("tile_cnt", ctypes.c_uint64), ("x", ctypes.c_uint64 * MAX_TP),
                 ("x_cnt", ctypes.c_uint64 * MAX_TP), ("done_cnt", ctypes.c_uint64),
                 ("rank", ctypes.c_int), ("tp", ctypes.c_int), ("chunk", ctypes.c_int), ("n", ctypes.c_int)]
 
@@ -105,7 +106,7 @@ class FusedComm:
         tp = self.world
         self.hidden, self.max_tokens = hidden, max_tokens
         self.chunk_max = ((max_tokens + tp - 1) // tp + 31) // 32 * 32
-        stage_bytes = tp * self.chunk_max * hidden * 2
+        stage_bytes = max_tokens * hidden * 2          # one partial-product buffer [max_tokens, hidden] per slot
         align = lambda v: (v + 255) // 256 * 256
         self.off_stage = [0, align(stage_bytes)]
         self.off_x = self.off_stage[1] + align(stage_bytes)
@@ -158,10 +159,10 @@ class FusedComm:
         for p in range(tp):
             sc.staging[p] = self.peer_ptrs[p] + self.off_stage[slot]
             sc.tile_cnt[p] = self._tile_cnt(p, slot)
+            rd.part[p] = self.peer_ptrs[p] + self.off_stage[slot]
             rd.x[p] = self.peer_ptrs[p] + self.off_x
             rd.x_cnt[p] = self._x_cnt(p)
         sc.rank, sc.tp, sc.chunk, sc.n = self.rank, tp, chunk, self.hidden
-        rd.staging = self.local_ptr + self.off_stage[slot]
         rd.tile_cnt = self._tile_cnt(self.rank, slot)
         rd.done_cnt = self.local_ptr + self.off_cnt + (SLOTS * MAX_GROUPS + 8) * 4
         rd.rank, rd.tp, rd.chunk, rd.n = self.rank, tp, chunk, self.hidden
