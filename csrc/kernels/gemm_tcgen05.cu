@@ -38,6 +38,7 @@ namespace ogb {
 constexpr int kBM = 128;
 constexpr int kBK = 64;  // 64 bf16 = one 128-byte swizzle row
 constexpr int kGemmThreads = 192;
+constexpr int kGemmThreadsScatter = 224;  // + one warp that publishes finished tiles to peer GPUs
 
 enum GemmEpilogue : int { kEpiNone = 0, kEpiResidual = 1, kEpiSwiGLU = 2, kEpiScatter = 3 };
 
@@ -52,7 +53,7 @@ struct GemmCfg {
 };
 
 template <int BN, int EPI>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreadsScatter, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias,
                          const __nv_bfloat16* residual, float* __restrict__ C_f32, int M, int N, int K, int ldc, int ldr,
@@ -67,6 +68,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   uint64_t* tmem_empty = tmem_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint32_t* stored_cnt = tmem_slot + 2;  // [4] tiles stored so far by each epilogue warp (scatter epilogue only)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -85,6 +87,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       mbar_init(&tmem_empty[i], 4);
     }
     *abort_flag = 0;
+    stored_cnt[0] = stored_cnt[1] = stored_cnt[2] = stored_cnt[3] = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
@@ -152,7 +155,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       }
       if (!ok) { atomicOr(status, kStatusWaitTimeout); *abort_flag = 1; }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------ epilogue ------------------------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     bool ok = true;
@@ -275,25 +278,50 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         }
       }
       if constexpr (EPI == kEpiScatter) {
-        // publish this warp's 32 rows x BN columns to their owner: the warp barrier orders every
-        // lane's stores before lane 0, whose release at system scope is cumulative over them, then
-        // bumps the owner's per-row-group arrival counter (the only remote write of this kernel)
-        const int row0 = m0 + q * 32;
+        // hand the finished warp tile to the signal warp: the warp barrier orders every lane's stores
+        // before lane 0, whose CTA-scope release on the shared counter the signal lane acquires
         __syncwarp();
-        if (lane == 0 && row0 < M) {
-          const int owner = row0 / sc->chunk;
-          uint32_t* cnt = sc->tile_cnt[owner] + (row0 - owner * sc->chunk) / 32;
-          // counted in 32-column units so the owner's expectation (N/32 per source rank) does not
-          // depend on the tile width this launch picked
-          const uint32_t units = static_cast<uint32_t>(min(BN, N - n0) / 32);
-          asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(cnt), "r"(units) : "memory");
-        }
+        if (lane == 0) asm volatile("red.release.cta.shared::cta.add.u32 [%0], 1;" ::"r"(smem_u32(&stored_cnt[q])) : "memory");
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
     }
     if (!ok && lane == 0) { atomicOr(status, kStatusWaitTimeout); *abort_flag = 1; }
+  } else {
+    // ------------------------------ signal warp (scatter epilogue) ------------------------------
+    // Lane q publishes the tiles of epilogue warp q: once that warp's stores are ordered (acquire on
+    // its counter) a system-scope release bumps the arrival counter of the rank that owns the 32-row
+    // group.  The tensor-core and epilogue warps never execute a system-scope fence.
+    if constexpr (EPI == kEpiScatter) {
+      if (lane < 4) {
+        const int q = lane;  // row quarter of the tile = TMEM quarter of the epilogue warp that stores it
+        uint32_t done = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++done) {
+          const uint64_t t0 = global_timer_ns();
+          uint32_t spins = 0;
+          while (true) {
+            uint32_t v;
+            asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(&stored_cnt[q])) : "memory");
+            if (v > done) break;
+            if (*abort_flag != 0 || (((++spins) & 0x3ff) == 0 && global_timer_ns() - t0 > kWaitLimitNs)) { ok = false; break; }
+          }
+          if (!ok) break;
+          const int m0 = (tile % m_tiles) * kBM;
+          const int n0 = (tile / m_tiles) * BN;
+          const int row0 = m0 + q * 32;
+          if (row0 < M) {
+            const int owner = row0 / sc->chunk;
+            uint32_t* cnt = sc->tile_cnt[owner] + (row0 - owner * sc->chunk) / 32;
+            // counted in 32-column units so the owner's expectation (N/32 per source rank) does not
+            // depend on the tile width this launch picked
+            const uint32_t units = static_cast<uint32_t>(min(BN, N - n0) / 32);
+            asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(cnt), "r"(units) : "memory");
+          }
+        }
+      }
+    }
   }
 
   tc_fence_before();
@@ -365,7 +393,7 @@ static int launch_gemm(const void* A, const void* W, void* C, const void* bias, 
   const int m_tiles = (M + kBM - 1) / kBM, n_tiles = (N + BN - 1) / BN;
   int grid = m_tiles * n_tiles;
   if (grid > ogb_num_sms()) grid = ogb_num_sms();
-  gemm_bf16_tcgen05_kernel<BN, EPI><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(
+  gemm_bf16_tcgen05_kernel<BN, EPI><<<grid, EPI == kEpiScatter ? kGemmThreadsScatter : kGemmThreads, Cfg::kSmemBytes, stream>>>(
       ta, tb, static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(bias),
       static_cast<const __nv_bfloat16*>(residual), static_cast<float*>(C_f32), M, N, K, ldc, ldr, status, sc);
   return static_cast<int>(cudaGetLastError());

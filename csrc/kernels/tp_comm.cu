@@ -24,7 +24,6 @@
 namespace ogb {
 
 constexpr int kRbThreads = 256;
-constexpr int kRbCols = 512;   // columns per CTA
 
 OGB_DEVICE uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
@@ -43,60 +42,77 @@ OGB_DEVICE bool wait_counter(const uint32_t* p, uint32_t want, uint64_t limit_ns
   return true;
 }
 
+OGB_DEVICE void add_bf16x8(float (&acc)[8], const uint4& v) {
+  float2 f;
+  f = unpack_bf16(v.x); acc[0] += f.x; acc[1] += f.y;
+  f = unpack_bf16(v.y); acc[2] += f.x; acc[3] += f.y;
+  f = unpack_bf16(v.z); acc[4] += f.x; acc[5] += f.y;
+  f = unpack_bf16(v.w); acc[6] += f.x; acc[7] += f.y;
+}
+
 // grid = (min(owned row groups, SMs / column blocks), column blocks); CTAs stride over row groups.
-// rows = total rows of the step (M).
-__global__ void __launch_bounds__(kRbThreads) tp_reduce_bcast_kernel(const TpReduce* __restrict__ rp, int rows,
+// rows = total rows of the step (M); cols = columns per CTA.  TP is a template parameter so the
+// loads of all sources for U vectors are issued back to back before the first add: with peer-load
+// latencies of a few microseconds the kernel lives on memory-level parallelism.
+template <int TP, int U>
+__global__ void __launch_bounds__(kRbThreads) tp_reduce_bcast_kernel(const TpReduce* __restrict__ rp, int rows, int cols,
                                                                       uint32_t expect_x, int* status) {
   const TpReduce& r = *rp;
   const int groups = r.chunk / 32;
-  const int col0 = blockIdx.y * kRbCols;
-  const int ncols = min(kRbCols, r.n - col0);
+  const int col0 = blockIdx.y * cols;
+  const int ncols = min(cols, r.n - col0);
   const int vec_per_row = ncols / 8;
+  const int total = 32 * vec_per_row;
   __shared__ int ok_sh;
   for (int g = blockIdx.x; g < groups; g += gridDim.x) {   // g = owned 32-row group
     const int row_base = r.rank * r.chunk + g * 32;        // global row of the group
     if (row_base >= rows) break;
     __syncthreads();
     if (threadIdx.x == 0) {
-      const bool ok = wait_counter(r.tile_cnt + g, static_cast<uint32_t>(r.n / 32) * r.tp);
+      const bool ok = wait_counter(r.tile_cnt + g, static_cast<uint32_t>(r.n / 32) * TP);
       if (!ok) atomicOr(status, kStatusPeerTimeout);
       ok_sh = ok ? 1 : 0;
     }
     __syncthreads();
     if (ok_sh) {
-      for (int i = threadIdx.x; i < 32 * vec_per_row; i += kRbThreads) {
-        const int lr = i / vec_per_row, cv = i % vec_per_row;
-        const int row = row_base + lr;
-        if (row >= rows) continue;
-        const int col = col0 + cv * 8;
-        float acc[8];
-        {
-          const uint4 v = *reinterpret_cast<const uint4*>(r.x[r.rank] + static_cast<size_t>(row) * r.n + col);
-          float2 f;
-          f = unpack_bf16(v.x); acc[0] = f.x; acc[1] = f.y;
-          f = unpack_bf16(v.y); acc[2] = f.x; acc[3] = f.y;
-          f = unpack_bf16(v.z); acc[4] = f.x; acc[5] = f.y;
-          f = unpack_bf16(v.w); acc[6] = f.x; acc[7] = f.y;
+      for (int i0 = threadIdx.x; i0 < total; i0 += kRbThreads * U) {
+        uint4 xv[U];
+        uint4 pv[U][TP];
+        size_t off[U];
+        bool live[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int i = i0 + u * kRbThreads;
+          const int lr = i / vec_per_row, cv = i % vec_per_row;
+          const int row = row_base + lr;
+          live[u] = (i < total) && (row < rows);
+          off[u] = static_cast<size_t>(row) * r.n + col0 + cv * 8;
+          if (live[u]) {
+            xv[u] = *reinterpret_cast<const uint4*>(r.x[r.rank] + off[u]);
+#pragma unroll
+            for (int src = 0; src < TP; ++src) pv[u][src] = *reinterpret_cast<const uint4*>(r.part[src] + off[u]);
+          }
         }
-        for (int src = 0; src < r.tp; ++src) {    // fixed order: the sum does not depend on arrival order
-          const uint4 v = *reinterpret_cast<const uint4*>(r.part[src] + static_cast<size_t>(row) * r.n + col);
-          float2 f;
-          f = unpack_bf16(v.x); acc[0] += f.x; acc[1] += f.y;
-          f = unpack_bf16(v.y); acc[2] += f.x; acc[3] += f.y;
-          f = unpack_bf16(v.z); acc[4] += f.x; acc[5] += f.y;
-          f = unpack_bf16(v.w); acc[6] += f.x; acc[7] += f.y;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (!live[u]) continue;
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          add_bf16x8(acc, xv[u]);
+#pragma unroll
+          for (int src = 0; src < TP; ++src) add_bf16x8(acc, pv[u][src]);  // fixed order: independent of arrival order
+          const uint4 o = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]),
+                                     pack_bf16(acc[6], acc[7]));
+#pragma unroll
+          for (int p = 0; p < TP; ++p)            // all-gather half: every replica receives the new row
+            *reinterpret_cast<uint4*>(r.x[p] + off[u]) = o;
         }
-        const uint4 o = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]),
-                                   pack_bf16(acc[6], acc[7]));
-        for (int p = 0; p < r.tp; ++p)            // all-gather half: every replica receives the new row
-          *reinterpret_cast<uint4*>(r.x[p] + static_cast<size_t>(row) * r.n + col) = o;
       }
     }
     // publish: this block of rows is in place everywhere
-    __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
-      for (int p = 0; p < r.tp; ++p) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(r.x_cnt[p]) : "memory");
+      __threadfence_system();
+      for (int p = 0; p < TP; ++p) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(r.x_cnt[p]) : "memory");
     }
   }
   if (threadIdx.x == 0) {
@@ -105,8 +121,8 @@ __global__ void __launch_bounds__(kRbThreads) tp_reduce_bcast_kernel(const TpRed
     // the last CTA of this launch resets the counters it consumed (safe: no rank can produce for the
     // next use of this slot before it has received this rank's rows, which were sent above)
     __threadfence();
-    const uint32_t total = gridDim.x * gridDim.y;
-    if (atomicAdd(r.done_cnt, 1u) == total - 1) {
+    const uint32_t total_ctas = gridDim.x * gridDim.y;
+    if (atomicAdd(r.done_cnt, 1u) == total_ctas - 1) {
       for (int i = 0; i < groups; ++i) r.tile_cnt[i] = 0;
       *r.x_cnt[r.rank] = 0;
       *r.done_cnt = 0;
@@ -125,7 +141,10 @@ extern "C" int ogb_tp_reduce_bcast(const void* rp, int rows, int n, int chunk, i
   if (rows <= 0) return 0;
   if (n % 8 || chunk % 32 || chunk / 32 > kTpMaxGroups) return -3;
   const int groups = chunk / 32;
-  const int col_blocks = (n + kRbCols - 1) / kRbCols;
+  // narrower column blocks at higher TP keep enough CTAs (and peer loads) in flight when each rank
+  // owns only a few row groups
+  const int cols = tp <= 2 ? 512 : (tp <= 4 ? 256 : 128);
+  const int col_blocks = (n + cols - 1) / cols;
   // blocks that will signal = row groups (over all ranks) that hold at least one valid row
   const int total_groups = (rows + 31) / 32;
   const uint32_t expect_x = static_cast<uint32_t>(total_groups) * col_blocks;
@@ -133,8 +152,14 @@ extern "C" int ogb_tp_reduce_bcast(const void* rp, int rows, int n, int chunk, i
   if (gx < 1) return -4;
   if (gx > groups) gx = groups;
   dim3 grid(gx, col_blocks);
-  tp_reduce_bcast_kernel<<<grid, kRbThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const TpReduce*>(rp), rows, expect_x, status);
+  const TpReduce* r = static_cast<const TpReduce*>(rp);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (tp) {
+    case 2: tp_reduce_bcast_kernel<2, 4><<<grid, kRbThreads, 0, st>>>(r, rows, cols, expect_x, status); break;
+    case 4: tp_reduce_bcast_kernel<4, 2><<<grid, kRbThreads, 0, st>>>(r, rows, cols, expect_x, status); break;
+    case 8: tp_reduce_bcast_kernel<8, 1><<<grid, kRbThreads, 0, st>>>(r, rows, cols, expect_x, status); break;
+    default: return -5;
+  }
   return static_cast<int>(cudaGetLastError());
 }
 
