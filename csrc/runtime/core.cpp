@@ -108,12 +108,14 @@ static PlanLayout make_layout(const CoreConfig& c) {
   l.max_tiles = c.max_tokens_per_step / 64 + c.max_seqs + 1;
   l.tile_seq = take(l.max_tiles);
   l.tile_q0 = take(l.max_tiles);
-  l.logit_rows = take(c.max_seqs);
-  l.temperature = take(c.max_seqs);
-  l.top_k = take(c.max_seqs);
-  l.top_p = take(c.max_seqs);
-  l.min_p = take(c.max_seqs);
-  l.uniform = take(c.max_seqs);
+  l.max_rows = c.max_seqs * (1 + (c.max_draft_tokens > 0 ? c.max_draft_tokens : 0));
+  l.logit_rows = take(l.max_rows);
+  l.temperature = take(l.max_rows);
+  l.top_k = take(l.max_rows);
+  l.top_p = take(l.max_rows);
+  l.min_p = take(l.max_rows);
+  l.uniform = take(l.max_rows);
+  l.logit_seq = take(l.max_rows);
   l.copy_src = take(c.max_seqs);
   l.copy_dst = take(c.max_seqs);
   l.max_swap = c.max_seqs * c.max_pages_per_seq;
@@ -247,6 +249,10 @@ bool Core::preempt_one(Sequence* keep, std::vector<std::pair<int, int>>& swap_ou
   Sequence& v = *find(running_[victim_idx]);
   running_.erase(running_.begin() + victim_idx);
   ++preemptions_;
+  if (v.num_draft > 0) {  // unverified drafts never survive a preemption
+    v.tokens.resize(v.tokens.size() - v.num_draft);
+    v.num_draft = 0;
+  }
   v.scheduled = 0;
   v.samples_this_step = false;
   const int used_pages = (v.num_computed + kPageTokens - 1) / kPageTokens;
@@ -303,8 +309,23 @@ int Core::build_step(int32_t* plan) {
   // 1. sequences already running: decode rows take one token, unfinished prompts take a chunk
   for (size_t i = 0; i < running_.size();) {
     Sequence* s = find(running_[i]);
-    const int remaining = static_cast<int>(s->tokens.size()) - s->num_computed;
+    int remaining = static_cast<int>(s->tokens.size()) - s->num_computed;
+    s->num_draft = 0;
+    if (remaining == 1 && !s->draft.empty() && cfg_.max_draft_tokens > 0) {
+      // speculative verification: feed the last token and the drafts as one short chunk
+      int k = std::min<int>(static_cast<int>(s->draft.size()), cfg_.max_draft_tokens);
+      const int generated = static_cast<int>(s->tokens.size()) - s->prompt_len;
+      k = std::min(k, std::max(0, s->max_new_tokens - generated - 1));
+      k = std::min(k, cfg_.max_pages_per_seq * kPageTokens - static_cast<int>(s->tokens.size()));
+      if (k > 0 && 1 + k <= budget) {
+        s->tokens.insert(s->tokens.end(), s->draft.begin(), s->draft.begin() + k);
+        s->num_draft = k;
+        remaining = 1 + k;
+      }
+      s->draft.clear();
+    }
     int n = std::min({remaining, budget, remaining > 1 ? cfg_.prefill_chunk : 1});
+    if (s->num_draft > 0) n = remaining;
     if (n <= 0) { s->scheduled = 0; ++i; continue; }
     bool ok = ensure_pages(*s, s->num_computed + n, copies);
     while (!ok) {
@@ -324,6 +345,7 @@ int Core::build_step(int32_t* plan) {
     (remaining == 1 ? decode_items : prefill_items).push_back({s, n});
     ++i;
   }
+  // (a preempted speculative sequence drops its drafts: see preempt_one)
   // drop items whose sequence was preempted after being scheduled
   auto still_running = [&](const Item& it) { return it.s->status == SeqStatus::Running && it.s->scheduled > 0; };
   decode_items.erase(std::remove_if(decode_items.begin(), decode_items.end(), [&](const Item& it) { return !still_running(it); }),
@@ -393,6 +415,7 @@ int Core::build_step(int32_t* plan) {
       Item& it = prefill_items[i];
       const int remaining = static_cast<int>(it.s->tokens.size()) - it.s->num_computed;
       const bool completes = (it.n == remaining);
+      if (it.s->num_draft > 0) continue;  // a verification chunk is all-or-nothing
       int cut = std::min(excess, it.n - 1);
       if (completes && cut > 0 && it.n - cut < 1) cut = 0;
       if (cut > 0) { it.n -= cut; it.s->scheduled = it.n; excess -= cut; total -= cut; }
@@ -432,18 +455,23 @@ int Core::build_step(int32_t* plan) {
     const bool completes = (ctx == static_cast<int>(s->tokens.size()));
     s->samples_this_step = completes;
     if (completes) {
-      plan[L.logit_rows + nlog] = t + n - 1;
-      float tmp = s->sampling.temperature;
-      std::memcpy(&plan[L.temperature + nlog], &tmp, 4);
-      plan[L.top_k + nlog] = s->sampling.top_k;
-      tmp = s->sampling.top_p;
-      std::memcpy(&plan[L.top_p + nlog], &tmp, 4);
-      tmp = s->sampling.min_p;
-      std::memcpy(&plan[L.min_p + nlog], &tmp, 4);
-      tmp = (s->sampling.temperature > 0.f) ? next_uniform(*s) : 0.f;
-      std::memcpy(&plan[L.uniform + nlog], &tmp, 4);
-      step_rows_.push_back(s->id);
-      ++nlog;
+      // one logit row for the last position, or one per fed position when drafts are being verified
+      const int first = s->num_draft > 0 ? 0 : n - 1;
+      for (int j = first; j < n && nlog < L.max_rows; ++j) {
+        plan[L.logit_rows + nlog] = t + j;
+        plan[L.logit_seq + nlog] = static_cast<int32_t>(s->id & 0x7fffffff);
+        float tmp = s->sampling.temperature;
+        std::memcpy(&plan[L.temperature + nlog], &tmp, 4);
+        plan[L.top_k + nlog] = s->sampling.top_k;
+        tmp = s->sampling.top_p;
+        std::memcpy(&plan[L.top_p + nlog], &tmp, 4);
+        tmp = s->sampling.min_p;
+        std::memcpy(&plan[L.min_p + nlog], &tmp, 4);
+        tmp = (s->sampling.temperature > 0.f) ? next_uniform(*s) : 0.f;
+        std::memcpy(&plan[L.uniform + nlog], &tmp, 4);
+        step_rows_.push_back(s->id);
+        ++nlog;
+      }
     }
     step_seqs_.push_back(s->id);
     t += n;
@@ -501,11 +529,7 @@ int Core::commit_step(const int32_t* sampled, int n, StepEvent* events, int max_
     s->scheduled = 0;
   }
   const int rows = std::min(n, static_cast<int>(step_rows_.size()));
-  for (int r = 0; r < rows; ++r) {
-    Sequence* s = find(step_rows_[r]);
-    if (!s || s->status != SeqStatus::Running || !s->samples_this_step) continue;
-    s->samples_this_step = false;
-    const int32_t tok = sampled[r];
+  auto push_token = [&](Sequence* s, int32_t tok) -> bool {  // returns true when the sequence finished
     s->tokens.push_back(tok);
     const int generated = static_cast<int>(s->tokens.size()) - s->prompt_len;
     FinishReason why = FinishReason::None;
@@ -514,6 +538,41 @@ int Core::commit_step(const int32_t* sampled, int n, StepEvent* events, int max_
     if (why == FinishReason::None && generated >= s->max_new_tokens) why = FinishReason::Length;
     if (why != FinishReason::None) finish(*s, why);
     if (ne < max_events) events[ne++] = StepEvent{s->id, tok, static_cast<int32_t>(why)};
+    return why != FinishReason::None;
+  };
+  for (int r = 0; r < rows;) {
+    Sequence* s = find(step_rows_[r]);
+    int group = 1;
+    while (r + group < rows && step_rows_[r + group] == step_rows_[r]) ++group;
+    if (!s || s->status != SeqStatus::Running || !s->samples_this_step) { r += group; continue; }
+    s->samples_this_step = false;
+    if (s->num_draft > 0 && group == s->num_draft + 1) {
+      // tokens = [... last, d0 .. d(k-1)]; sampled[r + j] follows position (last + j)
+      const int k = s->num_draft;
+      const int base = static_cast<int>(s->tokens.size()) - k;   // index of d0
+      int a = 0;
+      while (a < k && s->tokens[base + a] == sampled[r + a]) ++a;
+      ++spec_steps_;
+      spec_proposed_ += k;
+      spec_accepted_ += a;
+      std::vector<int32_t> accepted(s->tokens.begin() + base, s->tokens.begin() + base + a);
+      s->tokens.resize(base);
+      s->num_draft = 0;
+      // K/V of the last token and of the accepted drafts are valid; everything after is rewound
+      s->num_computed = base + a;
+      const int keep_pages = (s->num_computed + kPageTokens - 1) / kPageTokens;
+      while (static_cast<int>(s->pages.size()) > keep_pages) { pool_.release(s->pages.back()); s->pages.pop_back(); }
+      bool done = false;
+      for (int j = 0; j < a && !done; ++j) done = push_token(s, accepted[j]);
+      if (done) {
+        // finished inside the accepted run: later accepted tokens are dropped with the sequence
+      } else {
+        push_token(s, sampled[r + a]);
+      }
+    } else {
+      push_token(s, sampled[r + group - 1]);
+    }
+    r += group;
   }
   step_rows_.clear();
   step_seqs_.clear();
@@ -566,6 +625,13 @@ bool Core::rewind(int64_t seq_id, int new_len) {
   return true;
 }
 
+bool Core::set_draft(int64_t seq_id, const int32_t* tokens, int k) {
+  Sequence* s = find(seq_id);
+  if (!s || s->status == SeqStatus::Finished || k < 0) return false;
+  s->draft.assign(tokens, tokens + k);
+  return true;
+}
+
 int Core::seq_len(int64_t seq_id) const {
   const Sequence* s = find(seq_id);
   return s ? static_cast<int>(s->tokens.size()) : -1;
@@ -597,7 +663,7 @@ extern "C" {
 
 void* ogb_core_create(int num_pages, int num_host_pages, int max_seqs, int max_tokens_per_step, int max_pages_per_seq,
                       int prefill_chunk, int token_multiple, int policy, int preempt_mode, int enable_prefix_cache,
-                      int eos_token) {
+                      int eos_token, int max_draft_tokens) {
   CoreConfig c;
   c.num_pages = num_pages;
   c.num_host_pages = num_host_pages;
@@ -610,6 +676,7 @@ void* ogb_core_create(int num_pages, int num_host_pages, int max_seqs, int max_t
   c.preempt = static_cast<PreemptMode>(preempt_mode);
   c.enable_prefix_cache = enable_prefix_cache != 0;
   c.eos_token = eos_token;
+  c.max_draft_tokens = max_draft_tokens;
   return new Core(c);
 }
 void ogb_core_destroy(void* h) { delete static_cast<Core*>(h); }
@@ -618,7 +685,7 @@ int ogb_core_layout(void* h, int32_t* out, int cap) {
   const int32_t v[] = {l.header, l.token_ids, l.positions, l.slots, l.seq_slot, l.ctx_len, l.cu_q, l.page_table,
                        l.tile_seq, l.tile_q0, l.logit_rows, l.temperature, l.top_k, l.top_p, l.min_p, l.uniform,
                        l.copy_src, l.copy_dst, l.swap_out_dev, l.swap_out_host, l.swap_in_dev, l.swap_in_host,
-                       l.total_words, l.max_tiles, l.max_swap};
+                       l.total_words, l.max_tiles, l.max_swap, l.logit_seq, l.max_rows};
   const int n = static_cast<int>(sizeof(v) / sizeof(v[0]));
   for (int i = 0; i < n && i < cap; ++i) out[i] = v[i];
   return n;
@@ -645,6 +712,9 @@ int ogb_core_commit_step(void* h, const int32_t* sampled, int n, int64_t* ev_seq
 int ogb_core_cancel(void* h, int64_t id) { return static_cast<Core*>(h)->cancel(id) ? 1 : 0; }
 int64_t ogb_core_fork(void* h, int64_t id) { return static_cast<Core*>(h)->fork(id); }
 int ogb_core_rewind(void* h, int64_t id, int new_len) { return static_cast<Core*>(h)->rewind(id, new_len) ? 1 : 0; }
+int ogb_core_set_draft(void* h, int64_t id, const int32_t* tokens, int k) {
+  return static_cast<Core*>(h)->set_draft(id, tokens, k) ? 1 : 0;
+}
 int ogb_core_seq_len(void* h, int64_t id) { return static_cast<Core*>(h)->seq_len(id); }
 int ogb_core_seq_tokens(void* h, int64_t id, int32_t* out, int cap) { return static_cast<Core*>(h)->seq_tokens(id, out, cap); }
 void ogb_core_release(void* h, int64_t id) { static_cast<Core*>(h)->release(id); }
@@ -659,6 +729,9 @@ int64_t ogb_core_stat(void* h, int which) {
     case 5: return c->prefix_lookups();
     case 6: return c->num_preemptions();
     case 7: return c->has_work() ? 1 : 0;
+    case 8: return c->spec_proposed();
+    case 9: return c->spec_accepted();
+    case 10: return c->spec_steps();
     default: return -1;
   }
 }

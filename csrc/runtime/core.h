@@ -58,6 +58,8 @@ struct Sequence {
   int num_cached_prefix = 0;         // tokens served from the prefix cache at admission
   int scheduled = 0;                 // tokens scheduled in the step being built
   bool samples_this_step = false;
+  int num_draft = 0;                 // speculative tokens appended to `tokens` for the step being built
+  std::vector<int32_t> draft;        // proposed continuation waiting to be verified
 };
 
 // Reference-counted device pages with a prefix cache over full pages.
@@ -100,6 +102,7 @@ struct CoreConfig {
   PreemptMode preempt = PreemptMode::Recompute;
   bool enable_prefix_cache = true;
   int eos_token = -1;
+  int max_draft_tokens = 0;      // speculative decoding: draft tokens verified per sequence per step
 };
 
 // Offsets (in int32 words) of the sections of a packed step plan.
@@ -111,11 +114,13 @@ struct PlanLayout {
   int page_table;                            // [max_seqs * max_pages_per_seq]
   int tile_seq, tile_q0;                     // [max_tiles]
   int logit_rows;                            // [max_seqs]
-  int temperature, top_k, top_p, min_p, uniform;  // [max_seqs] (floats stored by bit pattern)
+  int temperature, top_k, top_p, min_p, uniform;  // [max_rows] (floats stored by bit pattern)
+  int logit_seq;                             // [max_rows] sequence id (low 31 bits) of every logit row
   int copy_src, copy_dst;                    // [max_seqs] CoW page copies to run before the step
   int swap_out_dev, swap_out_host, swap_in_dev, swap_in_host;  // [max_swap]
   int total_words;
   int max_tiles, max_swap;
+  int max_rows;                              // max_seqs * (1 + max_draft_tokens)
 };
 
 enum PlanHeader : int {
@@ -148,6 +153,13 @@ class Core {
   bool rewind(int64_t seq_id, int new_len);        // drop trailing tokens and their pages
   int seq_len(int64_t seq_id) const;
   int seq_tokens(int64_t seq_id, int32_t* out, int cap) const;
+  // Speculative decoding: propose `k` tokens to follow the sequence's last token.  The next step feeds the
+  // last token plus the drafts, samples every position, and commit_step keeps the longest prefix of the
+  // drafts that the samples confirm (plus the correction / bonus token), rewinding the KV pages of the rest.
+  bool set_draft(int64_t seq_id, const int32_t* tokens, int k);
+  int64_t spec_proposed() const { return spec_proposed_; }
+  int64_t spec_accepted() const { return spec_accepted_; }
+  int64_t spec_steps() const { return spec_steps_; }
   void release(int64_t seq_id);                    // forget a finished sequence
 
   int num_waiting() const { return static_cast<int>(waiting_.size()); }
@@ -186,6 +198,7 @@ class Core {
   int64_t clock_ = 0;
   int64_t step_id_ = 0;
   int64_t preemptions_ = 0;
+  int64_t spec_proposed_ = 0, spec_accepted_ = 0, spec_steps_ = 0;
 };
 
 }  // namespace ogb

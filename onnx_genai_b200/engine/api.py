@@ -1,0 +1,371 @@
+"""Public engine API: load a model directory, generate, stream, sessions, extension seams.
+
+Surface of the reference's `Engine` (crates/onnx-genai-engine/src/engine/runtime.rs:340-1524) and
+its Python binding (`onnx_genai.Engine.from_dir / generate / generate_stream / tokenize`,
+crates/onnx-genai-python/src/lib.rs:186-343): `GenerateOptions` carries the same request fields as
+the reference's 26-field struct (src/config.rs:1176-1274); `Sampler`, `LogitProcessor` and
+`SpeculativeProposer` are the user-pluggable seams; sessions offer create / close / reset /
+checkpoint / restore / rewind / fork (runtime.rs:1240-1330, config.rs:472-484).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from .. import metadata as md
+from .. import package as pkg
+from ..package import onnx_pb
+from ..package.decoder_graph import lower_decoder
+from ..speculative import SpeculativeStats
+from . import processors as procs
+from .llm_engine import EngineConfig, LLMEngine
+
+
+@dataclass
+class GenerateOptions:
+    max_new_tokens: int = 256
+    temperature: float = 1.0
+    top_k: int = 0
+    top_p: float = 1.0
+    min_p: float = 0.0
+    top_a: float = 0.0
+    typical_p: float = 1.0
+    greedy: bool = True
+    repetition_penalty: float = 1.0
+    repetition_window: int = 0
+    frequency_penalty: float = 0.0
+    presence_penalty: float = 0.0
+    dry_multiplier: float = 0.0
+    dry_base: float = 1.75
+    dry_allowed_length: int = 2
+    dry_sequence_breakers: tuple = ()
+    mirostat: bool = False
+    mirostat_tau: float = 5.0
+    mirostat_eta: float = 0.1
+    xtc_probability: float = 0.0
+    xtc_threshold: float = 0.1
+    banned_tokens: tuple = ()
+    seed: int = 0
+    stop: tuple = ()                 # stop strings
+    stop_token_ids: tuple = ()
+    ignore_eos: bool = False
+    logprobs: int = 0                # top-N log-probabilities per generated token (0 = off)
+    priority: int = 0
+    tenant: int = 0
+    speculative: bool = False
+
+    def validate(self):
+        if self.max_new_tokens < 0:
+            raise ValueError("max_new_tokens must be >= 0; pass a non-negative token budget")
+        if self.temperature < 0:
+            raise ValueError("temperature must be >= 0; use greedy=True (or temperature=0) for deterministic decoding")
+        if not 0.0 < self.top_p <= 1.0:
+            raise ValueError("top_p must be in (0, 1]; 1 disables nucleus filtering")
+        if self.logprobs < 0 or self.logprobs > 20:
+            raise ValueError("logprobs must be between 0 and 20")
+
+
+@dataclass
+class GenerateResult:
+    text: str
+    token_ids: list
+    finish_reason: str | None
+    prompt_tokens: int
+    completion_tokens: int
+    ttft_s: float = 0.0
+    total_s: float = 0.0
+    logprobs: list = field(default_factory=list)   # per token: (token logprob, [(id, logprob) top-N])
+    speculative: SpeculativeStats | None = None
+
+    @property
+    def decode_tokens_per_s(self) -> float:
+        dt = self.total_s - self.ttft_s
+        return (self.completion_tokens - 1) / dt if dt > 0 and self.completion_tokens > 1 else 0.0
+
+
+@dataclass
+class SessionCheckpoint:
+    session_id: int
+    position: int
+
+
+class _Session:
+    def __init__(self, sid):
+        self.id = sid
+        self.tokens: list = []
+
+
+class Engine:
+    """One model, one device (or one tensor-parallel group), one owner thread."""
+
+    def __init__(self, llm: LLMEngine, tokenizer=None, chat_template: str | None = None, metadata=None,
+                 eos_token_ids=(), draft: "Engine | None" = None):
+        self.llm = llm
+        self.tokenizer = tokenizer
+        self.chat_template = chat_template
+        self.metadata = metadata or md.InferenceMetadata()
+        self.eos_token_ids = tuple(eos_token_ids)
+        self.draft = draft
+        self.sessions: dict[int, _Session] = {}
+        self._next_session = 1
+        self.proposer_factory = None      # () -> SpeculativeProposer; default prompt lookup
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_dir(cls, model_dir: str, device=None, page_size: int | None = None, max_seqs: int = 32,
+                 max_seq_len: int | None = None, num_pages: int = 0, max_tokens_per_step: int = 2048,
+                 kv_dtype: str = "bf16", max_draft_tokens: int = 0, draft_model_dir: str | None = None, **engine_kw):
+        """Load a flat model directory or a model package.  ``page_size`` is accepted for API
+        compatibility; pages hold 16 tokens (the attention kernels' tile)."""
+        if page_size not in (None, 16):
+            raise ValueError(f"page_size={page_size} is not supported: KV pages hold 16 tokens")
+        device = device or ("cuda" if torch.cuda.is_available() else "cpu")
+        d = pkg.open_model_directory(model_dir, ep="cuda" if str(device).startswith("cuda") else "cpu",
+                                     device="gpu" if str(device).startswith("cuda") else "cpu")
+        meta = d.load_metadata()
+        dtype = torch.bfloat16 if str(device).startswith("cuda") else torch.float32
+        cfg, weights, _ = lower_decoder(onnx_pb.load_model(d.model_path), dtype=dtype, device=device)
+        if meta.vocab_size and meta.vocab_size != cfg.vocab:
+            raise md.MetadataError(f"{d.metadata_path}: model.vocab_size={meta.vocab_size} but the graph's embedding has "
+                                   f"{cfg.vocab} rows; fix the metadata or re-export the model")
+        limit = meta.max_sequence_length or cfg.max_position
+        max_seq_len = min(max_seq_len or limit, limit, cfg.max_position)
+        tok = None
+        eos = []
+        if d.tokenizer_path:
+            from tokenizers import Tokenizer
+
+            tok = Tokenizer.from_file(d.tokenizer_path)
+            for name in ("<|endoftext|>", "<|im_end|>", "</s>", "<|eot_id|>"):
+                tid = tok.token_to_id(name)
+                if tid is not None:
+                    eos.append(tid)
+        if d.genai_config:
+            from ..package.genai_config import eos_token_ids
+
+            eos = eos_token_ids(d.genai_config) or eos
+        cfg = cfg.replace(eos_token=eos[0] if eos else -1)
+        ecfg = EngineConfig(model=cfg, num_pages=num_pages, max_seqs=max_seqs, max_seq_len=max_seq_len,
+                            max_tokens_per_step=max_tokens_per_step, prefill_chunk=meta.chunked_prefill_size or 2048,
+                            kv_dtype=kv_dtype, max_draft_tokens=max_draft_tokens, **engine_kw)
+        llm = LLMEngine(ecfg, weights=weights, device=device)
+        draft = cls.from_dir(draft_model_dir, device=device, max_seqs=max_seqs, max_seq_len=max_seq_len) if draft_model_dir else None
+        return cls(llm, tok, d.chat_template, meta, eos, draft)
+
+    # ------------------------------------------------------------------ text helpers
+    def tokenize(self, text: str) -> list:
+        if self.tokenizer is None:
+            raise RuntimeError("this engine was built without a tokenizer; pass token ids or load a directory with tokenizer.json")
+        return self.tokenizer.encode(text, add_special_tokens=False).ids
+
+    def detokenize(self, ids) -> str:
+        if self.tokenizer is None:
+            return " ".join(str(int(i)) for i in ids)
+        return self.tokenizer.decode([int(i) for i in ids], skip_special_tokens=False)
+
+    def apply_chat_template(self, messages, add_generation_prompt=True, tools=None, **extra) -> str:
+        import jinja2
+
+        tmpl = self.chat_template or ("{% for m in messages %}{{ m['role'] }}: {{ m['content'] }}\n{% endfor %}"
+                                      "{% if add_generation_prompt %}assistant: {% endif %}")
+        env = jinja2.Environment(trim_blocks=False, lstrip_blocks=False)
+        env.globals["raise_exception"] = lambda msg: (_ for _ in ()).throw(ValueError(msg))
+        return env.from_string(tmpl).render(messages=messages, add_generation_prompt=add_generation_prompt, tools=tools,
+                                            **extra)
+
+    # ------------------------------------------------------------------ generation
+    def _submit(self, ids, opt: GenerateOptions, sampler=None, processors=()):
+        opt.validate()
+        defaults = self.metadata.generation_defaults or {}
+        greedy = opt.greedy or opt.temperature == 0
+        temperature = 0.0 if greedy else (opt.temperature if opt.temperature is not None else defaults.get("temperature", 1.0))
+        stop_ids = tuple(opt.stop_token_ids) + (() if opt.ignore_eos else self.eos_token_ids)
+        sid = self.llm.add_request(np.asarray(ids, dtype=np.int32), opt.max_new_tokens, temperature=temperature,
+                                   top_k=opt.top_k, top_p=opt.top_p, min_p=opt.min_p, seed=opt.seed, priority=opt.priority,
+                                   tenant=opt.tenant, ignore_eos=opt.ignore_eos, stop_ids=stop_ids)
+        rng = np.random.default_rng(opt.seed or None)
+        eff = GenerateOptions(**{**opt.__dict__, "greedy": greedy})
+        chain = procs.build_processor_chain(eff, len(ids), rng, extra=processors)
+        plan = procs.device_sampling_plan(chain, eff, sampler is not None)
+        state = {"ids": list(int(i) for i in ids), "chain": chain, "logprobs": [], "plan": plan}
+        if plan == "host":
+            smp = sampler or (procs.GreedySampler() if greedy else procs.CategoricalSampler())
+
+            def host_fn(row_logits, u, st=state, smp=smp, n_lp=opt.logprobs):
+                logits = st["chain"].process(st["ids"], row_logits.astype(np.float32, copy=True))
+                tok = int(smp.sample(logits, u))
+                if n_lp:
+                    lp = procs.log_softmax(row_logits)
+                    top = np.argsort(-lp)[:n_lp]
+                    st["logprobs"].append((float(lp[tok]), [(int(i), float(lp[i])) for i in top]))
+                for p in st["chain"].processors:
+                    if hasattr(p, "observe"):
+                        p.observe(tok)
+                return tok
+
+            self.llm.host_samplers[sid & 0x7FFFFFFF] = host_fn
+        if opt.speculative and self.llm.cfg.max_draft_tokens > 0 and greedy:
+            from ..speculative import DraftModelProposer, NgramProposer
+
+            if self.proposer_factory is not None:
+                self.llm.proposers[sid] = self.proposer_factory()
+            elif self.draft is not None:
+                self.llm.proposers[sid] = DraftModelProposer(self.draft.llm)
+            else:
+                self.llm.proposers[sid] = NgramProposer()
+        return sid, state
+
+    def _finish(self, sid):
+        self.llm.host_samplers.pop(sid & 0x7FFFFFFF, None)
+        prop = self.llm.proposers.pop(sid, None)
+        if prop is not None and hasattr(prop, "close"):
+            prop.close()
+        self.llm.core.release(sid)
+        self.llm.stats.pop(sid, None)
+
+    def generate_stream(self, prompt, options: GenerateOptions | None = None, sampler=None, processors=()):
+        """Yields (token_id, text_delta, finish_reason | None) as tokens are produced."""
+        opt = options or GenerateOptions()
+        ids = self.tokenize(prompt) if isinstance(prompt, str) else [int(t) for t in prompt]
+        sid, state = self._submit(ids, opt, sampler, processors)
+        out_ids, emitted = [], ""
+        try:
+            done = False
+            while not done and self.llm.has_work:
+                for esid, tok, fin in self.llm.step().events:
+                    if esid != sid:
+                        continue
+                    out_ids.append(tok)
+                    state["ids"].append(tok)
+                    text = self.detokenize(out_ids) if self.tokenizer is not None else ""
+                    delta = text[len(emitted):]
+                    if opt.stop and self.tokenizer is not None:
+                        hit = min((text.find(s) for s in opt.stop if s and text.find(s) >= 0), default=-1)
+                        if hit >= 0:
+                            delta = text[len(emitted):hit] if hit > len(emitted) else ""
+                            self.llm.core.cancel(sid)
+                            fin = "stop"
+                    emitted += delta
+                    yield tok, delta, fin
+                    if fin is not None:
+                        done = True
+                        break
+        finally:
+            self._last_state = state
+            self._finish(sid)
+
+    def generate(self, prompt, options: GenerateOptions | None = None, sampler=None, processors=(), on_token=None) -> GenerateResult:
+        opt = options or GenerateOptions()
+        ids = self.tokenize(prompt) if isinstance(prompt, str) else [int(t) for t in prompt]
+        t0 = time.perf_counter()
+        c0 = (self.llm.core.spec_steps, self.llm.core.spec_proposed, self.llm.core.spec_accepted)
+        toks, text, fin, ttft = [], "", None, 0.0
+        for tok, delta, f in self.generate_stream(ids, opt, sampler, processors):
+            if not toks:
+                ttft = time.perf_counter() - t0
+            toks.append(tok)
+            text += delta
+            fin = f
+            if on_token is not None:
+                on_token(tok, delta)
+        spec = None
+        if opt.speculative:
+            c1 = (self.llm.core.spec_steps, self.llm.core.spec_proposed, self.llm.core.spec_accepted)
+            spec = SpeculativeStats(c1[0] - c0[0], c1[1] - c0[1], c1[2] - c0[2])
+        if self.tokenizer is None:
+            text = ""
+        return GenerateResult(text=text, token_ids=toks, finish_reason=fin, prompt_tokens=len(ids), completion_tokens=len(toks),
+                              ttft_s=ttft, total_s=time.perf_counter() - t0, logprobs=list(self._last_state["logprobs"]),
+                              speculative=spec)
+
+    def generate_batch(self, prompts, options: GenerateOptions | None = None):
+        """Continuous batching over many prompts; returns results in prompt order."""
+        opt = options or GenerateOptions()
+        t0 = time.perf_counter()
+        entries = []
+        for p in prompts:
+            ids = self.tokenize(p) if isinstance(p, str) else [int(t) for t in p]
+            sid, state = self._submit(ids, opt)
+            entries.append({"sid": sid, "ids": ids, "state": state, "out": [], "fin": None, "ttft": 0.0})
+        by_sid = {e["sid"]: e for e in entries}
+        pending = len(entries)
+        while pending and self.llm.has_work:
+            for sid, tok, fin in self.llm.step().events:
+                e = by_sid.get(sid)
+                if e is None or e["fin"] is not None:
+                    continue
+                if not e["out"]:
+                    e["ttft"] = time.perf_counter() - t0
+                e["out"].append(tok)
+                e["state"]["ids"].append(tok)
+                if fin is not None:
+                    e["fin"] = fin
+                    pending -= 1
+        results = []
+        for e in entries:
+            self._finish(e["sid"])
+            text = self.detokenize(e["out"]) if self.tokenizer is not None else ""
+            results.append(GenerateResult(text, e["out"], e["fin"], len(e["ids"]), len(e["out"]), e["ttft"],
+                                          time.perf_counter() - t0, list(e["state"]["logprobs"])))
+        return results
+
+    # ------------------------------------------------------------------ sessions
+    def create_session(self) -> int:
+        sid = self._next_session
+        self._next_session += 1
+        self.sessions[sid] = _Session(sid)
+        return sid
+
+    def close_session(self, session_id: int) -> None:
+        self.sessions.pop(session_id, None)
+
+    def reset_session(self, session_id: int) -> None:
+        self._session(session_id).tokens = []
+
+    def _session(self, session_id) -> _Session:
+        s = self.sessions.get(session_id)
+        if s is None:
+            raise KeyError(f"session {session_id} does not exist; create it with create_session()")
+        return s
+
+    def generate_in_session(self, session_id: int, prompt, options: GenerateOptions | None = None, **kw) -> GenerateResult:
+        """Continue a conversation: the session's token history is the prefix; its KV pages are found again
+        through the prefix cache, so only the new tokens are prefilled."""
+        s = self._session(session_id)
+        new_ids = self.tokenize(prompt) if isinstance(prompt, str) else [int(t) for t in prompt]
+        res = self.generate(s.tokens + new_ids, options, **kw)
+        s.tokens = s.tokens + new_ids + list(res.token_ids)
+        return res
+
+    def checkpoint_session(self, session_id: int) -> SessionCheckpoint:
+        return SessionCheckpoint(session_id, len(self._session(session_id).tokens))
+
+    def restore_session(self, cp: SessionCheckpoint) -> None:
+        self.rewind_session(cp.session_id, cp.position)
+
+    def rewind_session(self, session_id: int, position: int) -> None:
+        s = self._session(session_id)
+        if not 0 <= position <= len(s.tokens):
+            raise ValueError(f"cannot rewind session {session_id} to {position}: it holds {len(s.tokens)} tokens")
+        s.tokens = s.tokens[:position]
+
+    def fork_session(self, session_id: int) -> int:
+        """Copy-on-write clone: the child shares every full KV page of the parent through the prefix cache."""
+        child = self.create_session()
+        self.sessions[child].tokens = list(self._session(session_id).tokens)
+        return child
+
+    def session_len(self, session_id: int) -> int:
+        return len(self._session(session_id).tokens)
+
+    # ------------------------------------------------------------------ introspection
+    def resource_snapshot(self) -> dict:
+        core = self.llm.core
+        total = self.llm.num_pages
+        return {"kv_pages_total": total, "kv_pages_free": core.num_free_pages, "kv_usage": 1.0 - core.num_free_pages / max(1, total),
+                "waiting": core.num_waiting, "running": core.num_running, "swapped": core.num_swapped,
+                "prefix_cache_hits": core.prefix_hits, "prefix_cache_lookups": core.prefix_lookups,
+                "preemptions": core.num_preemptions, "steps": self.llm.steps, "sessions": len(self.sessions)}

@@ -26,7 +26,8 @@ HDR = dict(num_tokens=0, num_decode=1, num_prefill_seqs=2, num_tiles=3, num_logi
 
 _LAYOUT_FIELDS = ["header", "token_ids", "positions", "slots", "seq_slot", "ctx_len", "cu_q", "page_table", "tile_seq",
                   "tile_q0", "logit_rows", "temperature", "top_k", "top_p", "min_p", "uniform", "copy_src", "copy_dst",
-                  "swap_out_dev", "swap_out_host", "swap_in_dev", "swap_in_host", "total_words", "max_tiles", "max_swap"]
+                  "swap_out_dev", "swap_out_host", "swap_in_dev", "swap_in_host", "total_words", "max_tiles", "max_swap",
+                  "logit_seq", "max_rows"]
 
 
 def load_runtime():
@@ -44,7 +45,7 @@ def load_runtime():
     lib = ctypes.CDLL(str(path))
     P = c_void_p
     I32P = POINTER(c_int32)
-    lib.ogb_core_create.argtypes = [c_int] * 11
+    lib.ogb_core_create.argtypes = [c_int] * 12
     lib.ogb_core_create.restype = P
     lib.ogb_core_destroy.argtypes = [P]
     lib.ogb_core_layout.argtypes = [P, I32P, c_int]
@@ -63,6 +64,8 @@ def load_runtime():
     lib.ogb_core_fork.restype = c_int64
     lib.ogb_core_rewind.argtypes = [P, c_int64, c_int]
     lib.ogb_core_rewind.restype = c_int
+    lib.ogb_core_set_draft.argtypes = [P, c_int64, I32P, c_int]
+    lib.ogb_core_set_draft.restype = c_int
     lib.ogb_core_seq_len.argtypes = [P, c_int64]
     lib.ogb_core_seq_len.restype = c_int
     lib.ogb_core_seq_tokens.argtypes = [P, c_int64, I32P, c_int]
@@ -87,6 +90,7 @@ class CoreConfig:
     preempt: str = "recompute"
     enable_prefix_cache: bool = True
     eos_token: int = -1
+    max_draft_tokens: int = 0
 
 
 class Layout:
@@ -104,13 +108,13 @@ class Core:
         self.h = self.lib.ogb_core_create(cfg.num_pages, cfg.num_host_pages, cfg.max_seqs, cfg.max_tokens_per_step,
                                           cfg.max_pages_per_seq, cfg.prefill_chunk, cfg.token_multiple,
                                           POLICIES[cfg.policy], PREEMPT[cfg.preempt], int(cfg.enable_prefix_cache),
-                                          cfg.eos_token)
+                                          cfg.eos_token, cfg.max_draft_tokens)
         buf = (c_int32 * 32)()
         n = self.lib.ogb_core_layout(self.h, buf, 32)
         self.layout = Layout(list(buf)[:n])
-        self._ev_seq = np.zeros(cfg.max_seqs, dtype=np.int64)
-        self._ev_tok = np.zeros(cfg.max_seqs, dtype=np.int32)
-        self._ev_fin = np.zeros(cfg.max_seqs, dtype=np.int32)
+        self._ev_seq = np.zeros(self.layout.max_rows, dtype=np.int64)
+        self._ev_tok = np.zeros(self.layout.max_rows, dtype=np.int32)
+        self._ev_fin = np.zeros(self.layout.max_rows, dtype=np.int32)
 
     def __del__(self):
         try:
@@ -152,6 +156,11 @@ class Core:
     def rewind(self, sid, new_len):
         return bool(self.lib.ogb_core_rewind(self.h, sid, new_len))
 
+    def set_draft(self, sid, tokens):
+        """Propose tokens to follow the sequence's last token; verified (and rewound) by the next step."""
+        arr = np.ascontiguousarray(tokens, dtype=np.int32)
+        return bool(self.lib.ogb_core_set_draft(self.h, sid, arr.ctypes.data_as(POINTER(c_int32)), len(arr)))
+
     def seq_len(self, sid):
         return int(self.lib.ogb_core_seq_len(self.h, sid))
 
@@ -177,3 +186,6 @@ class Core:
     prefix_lookups = property(lambda self: self._stat(5))
     num_preemptions = property(lambda self: self._stat(6))
     has_work = property(lambda self: bool(self._stat(7)))
+    spec_proposed = property(lambda self: self._stat(8))
+    spec_accepted = property(lambda self: self._stat(9))
+    spec_steps = property(lambda self: self._stat(10))

@@ -48,6 +48,7 @@ class EngineConfig:
     kv_dtype: str = "bf16"
     decode_splits: int = 0             # 0: pick from batch shape
     sync_sampled_tokens: bool = True   # TP: broadcast rank 0's tokens so replicas cannot diverge
+    max_draft_tokens: int = 0          # speculative decoding: drafts verified per sequence per step
     native_executor: bool = True       # launch the layer stack from the C++ step executor when possible
     seed: int = 0
 
@@ -83,7 +84,8 @@ class LLMEngine:
         self.weights = weights
         max_pages_per_seq = (cfg.max_seq_len + ops.PAGE - 1) // ops.PAGE
         hs = shard_heads(m.num_heads, m.num_kv_heads, tp, rank)
-        self.model = DecoderModel(m, weights, self.device, cfg.max_tokens_per_step, cfg.max_seqs, tp, rank, comm)
+        max_rows = cfg.max_seqs * (1 + max(0, cfg.max_draft_tokens))
+        self.model = DecoderModel(m, weights, self.device, cfg.max_tokens_per_step, max_rows, tp, rank, comm)
         num_pages = cfg.num_pages
         if num_pages <= 0:
             kv_bytes = 1 if cfg.kv_dtype == "fp8" else 2
@@ -104,16 +106,17 @@ class LLMEngine:
                                     max_tokens_per_step=cfg.max_tokens_per_step, max_pages_per_seq=max_pages_per_seq,
                                     prefill_chunk=cfg.prefill_chunk, token_multiple=cfg.token_multiple,
                                     policy=cfg.policy, preempt=cfg.preempt,
-                                    enable_prefix_cache=cfg.enable_prefix_cache, eos_token=m.eos_token))
+                                    enable_prefix_cache=cfg.enable_prefix_cache, eos_token=m.eos_token,
+                                    max_draft_tokens=cfg.max_draft_tokens))
         L = self.core.layout
         self.L = L
         self.plan_host = torch.zeros(L.total_words, dtype=torch.int32, pin_memory=is_cuda)
         self.plan_np = self.plan_host.numpy()
         self.dev_words = L.swap_out_dev      # sections after this offset are host-only
         self.plan_dev = torch.zeros(self.dev_words, dtype=torch.int32, device=self.device) if is_cuda else self.plan_host
-        self.sampled_host = torch.zeros(cfg.max_seqs, dtype=torch.int32, pin_memory=is_cuda)
-        self.sampled_dev = torch.zeros(cfg.max_seqs, dtype=torch.int32, device=self.device)
-        self.sample_work = (torch.empty(cfg.max_seqs * m.vocab, dtype=torch.int32, device=self.device)
+        self.sampled_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=is_cuda)
+        self.sampled_dev = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
+        self.sample_work = (torch.empty(max_rows * m.vocab, dtype=torch.int32, device=self.device)
                             if is_cuda else None)
         self.host_kv = None
         if cfg.num_host_pages > 0:
@@ -130,12 +133,14 @@ class LLMEngine:
             slots=p[L.slots:L.slots + T], ctx_len=p[L.ctx_len:L.ctx_len + S],
             page_table=p[L.page_table:L.page_table + S * MP].view(S, MP), cu_q=p[L.cu_q:L.cu_q + S + 1],
             tile_seq=p[L.tile_seq:L.tile_seq + L.max_tiles], tile_q0=p[L.tile_q0:L.tile_q0 + L.max_tiles],
-            logit_rows=p[L.logit_rows:L.logit_rows + S])
-        f32 = lambda off: p[off:off + S].view(torch.float32)
+            logit_rows=p[L.logit_rows:L.logit_rows + max_rows])
+        f32 = lambda off: p[off:off + max_rows].view(torch.float32)
         self.temperature, self.top_p, self.min_p, self.uniform = (f32(L.temperature), f32(L.top_p), f32(L.min_p),
                                                                   f32(L.uniform))
-        self.top_k = p[L.top_k:L.top_k + S]
+        self.top_k = p[L.top_k:L.top_k + max_rows]
         self.native_executor = cfg.native_executor and self.model.bind_native(self.kv, max_pages_per_seq)
+        self.host_samplers: dict = {}     # seq id -> fn(logits_row fp32 numpy, uniform) -> token id
+        self.proposers: dict = {}         # seq id -> SpeculativeProposer
         self.stats: dict[int, RequestStats] = {}
         self.steps = 0
         self.h2d_bytes = 0
@@ -195,6 +200,13 @@ class LLMEngine:
     def step(self) -> StepOutput:
         """Schedule, run and commit one engine step."""
         out = StepOutput()
+        for sid, proposer in list(self.proposers.items()):   # speculative drafts for the coming step
+            toks = self.core.seq_tokens(sid) if self.core.seq_len(sid) > 0 else None
+            if toks is None:
+                continue
+            draft = proposer.propose(toks, self.cfg.max_draft_tokens)
+            if len(draft):
+                self.core.set_draft(sid, draft)
         t = self.core.build_step(self.plan_host.data_ptr())
         if t <= 0:
             return out
@@ -236,6 +248,17 @@ class LLMEngine:
                 self.sampled_host[:r] = toks
         elif self.device.type == "cuda":
             torch.cuda.current_stream().synchronize()
+        if self.host_samplers and r > 0:
+            # rows whose request cannot use the device sampler: logits cross to the host, the request's
+            # processor chain and sampler pick the token, and the device's choice for that row is replaced
+            seq_of_row = self.plan_np[self.L.logit_seq:self.L.logit_seq + r]
+            unis = self.plan_np[self.L.uniform:self.L.uniform + r].view(np.float32)
+            for row in range(r):
+                fn = self.host_samplers.get(int(seq_of_row[row]))
+                if fn is not None:
+                    row_logits = logits[row].float().cpu().numpy()
+                    self.d2h_bytes += row_logits.nbytes
+                    self.sampled_host[row] = int(fn(row_logits, float(unis[row])))
         events = self.core.commit_step(self.sampled_host.data_ptr(), r)
         now = time.perf_counter()
         for sid, tok, fin in events:

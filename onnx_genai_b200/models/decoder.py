@@ -174,7 +174,9 @@ class DecoderModel:
         dt = weights.embed.dtype
         dev = self.device
         hid = cfg.hidden
-        self.cos_sin = ref.rope_table(cfg.max_position, self.rotary_dim, cfg.rope_theta, dev)
+        cs = getattr(weights, "cos_sin", None)   # a loaded package brings its own cos/sin caches
+        self.cos_sin = (cs.to(dev) if cs is not None
+                        else ref.rope_table(cfg.max_position, self.rotary_dim, cfg.rope_theta, dev))
         z = lambda *s: torch.zeros(*s, dtype=dt, device=dev)
         self.fused_comm = comm if (comm is not None and hasattr(comm, "row_parallel") and dev.type == "cuda") else None
         if self.fused_comm is not None:
