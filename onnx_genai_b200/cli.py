@@ -1,0 +1,283 @@
+"""Command line: ``python -m onnx_genai_b200 {serve,generate,run,show,list,version,export,bench}``.
+
+Mirrors the reference CLI (crates/onnx-genai-cli/src/lib.rs:92-330): sampling flags
+(``--max-new-tokens --temperature --top-p --top-k --greedy/--no-greedy --stop --raw``), engine flags
+(``--device auto|cpu|cuda[:N]``), global ``--profile / --profile-json / --profile-trace``, the
+``run`` REPL with slash commands (``/help /system /raw /stats /profile /reset /quit``) and the
+compact per-turn stats line (TTFT, decode tok/s, finish reason).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+from . import __version__
+
+
+def _add_sampling(p):
+    p.add_argument("--max-new-tokens", type=int, default=256)
+    p.add_argument("--max-context", type=int, default=0)
+    p.add_argument("--temperature", type=float, default=0.7)
+    p.add_argument("--top-p", type=float, default=1.0)
+    p.add_argument("--top-k", type=int, default=0)
+    p.add_argument("--min-p", type=float, default=0.0)
+    p.add_argument("--repetition-penalty", type=float, default=1.0)
+    p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--greedy", dest="greedy", action="store_true", default=False)
+    p.add_argument("--no-greedy", dest="greedy", action="store_false")
+    p.add_argument("--stop", action="append", default=[])
+    p.add_argument("--raw", action="store_true", help="do not apply the chat template")
+    p.add_argument("--speculative", action="store_true", help="prompt-lookup speculative decoding (greedy only)")
+
+
+def _add_engine(p):
+    p.add_argument("--device", default="auto", help="auto | cpu | cuda[:N]")
+    p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3fn"])
+    p.add_argument("--max-batch", type=int, default=32)
+    p.add_argument("--vram-limit", default="0.85", help="fraction of device memory the KV pool may take")
+
+
+def _options(args):
+    from .engine.api import GenerateOptions
+
+    return GenerateOptions(max_new_tokens=args.max_new_tokens, temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
+                           min_p=args.min_p, repetition_penalty=args.repetition_penalty, seed=args.seed,
+                           greedy=args.greedy or args.temperature == 0, stop=tuple(args.stop), speculative=args.speculative)
+
+
+def _load(args):
+    import torch
+
+    from .engine.api import Engine
+
+    dev = args.device
+    if dev == "auto":
+        dev = "cuda" if torch.cuda.is_available() else "cpu"
+    try:
+        util = float(args.vram_limit)
+    except ValueError:
+        util = 0.85
+    return Engine.from_dir(args.model, device=dev, max_seqs=args.max_batch, kv_dtype="fp8" if args.kv_cache_dtype.startswith("fp8") else "bf16",
+                           gpu_memory_utilization=util if 0 < util <= 1 else 0.85,
+                           max_draft_tokens=4 if getattr(args, "speculative", False) else 0,
+                           max_seq_len=args.max_context or None)
+
+
+def _prompt_text(engine, text, raw, system=None):
+    if raw or engine.tokenizer is None:
+        return text
+    msgs = ([{"role": "system", "content": system}] if system else []) + [{"role": "user", "content": text}]
+    return engine.apply_chat_template(msgs, add_generation_prompt=True)
+
+
+def _stats_line(res):
+    return (f"[{res.completion_tokens} tok | TTFT {res.ttft_s * 1e3:.1f} ms | decode {res.decode_tokens_per_s:.1f} tok/s | "
+            f"finish {res.finish_reason}]")
+
+
+def cmd_generate(args, profiler):
+    eng = _load(args)
+    prompt = args.prompt if args.prompt is not None else sys.stdin.read()
+    t_lat = []
+    last = [time.perf_counter()]
+
+    def on_token(tok, delta):
+        now = time.perf_counter()
+        t_lat.append(now - last[0])
+        last[0] = now
+        sys.stdout.write(delta)
+        sys.stdout.flush()
+
+    with profiler.span("generate"):
+        res = eng.generate(_prompt_text(eng, prompt, args.raw), _options(args), on_token=on_token)
+    sys.stdout.write("\n")
+    print(_stats_line(res), file=sys.stderr)
+    profiler.report(res, t_lat[1:], eng)
+    return 0
+
+
+def cmd_run(args, profiler):
+    eng = _load(args)
+    session = eng.create_session()
+    system, raw, stats = None, args.raw, True
+    print("interactive session; /help lists commands", file=sys.stderr)
+    while True:
+        try:
+            line = input(">>> ")
+        except (EOFError, KeyboardInterrupt):
+            print()
+            return 0
+        if not line.strip():
+            continue
+        if line.startswith("/"):
+            cmd, _, rest = line.partition(" ")
+            if cmd in ("/quit", "/exit"):
+                return 0
+            if cmd == "/help":
+                print("/system TEXT  /raw  /stats  /profile  /reset  /model  /quit")
+            elif cmd == "/system":
+                system = rest.strip() or None
+            elif cmd == "/raw":
+                raw = not raw
+                print(f"raw = {raw}")
+            elif cmd == "/stats":
+                stats = not stats
+            elif cmd == "/reset":
+                eng.reset_session(session)
+            elif cmd == "/model":
+                print(json.dumps(eng.resource_snapshot(), indent=1))
+            elif cmd == "/profile":
+                profiler.enabled = not profiler.enabled
+                print(f"profile = {profiler.enabled}")
+            else:
+                print(f"unknown command {cmd}; /help lists commands")
+            continue
+        text = _prompt_text(eng, line, raw, system if eng.session_len(session) == 0 else None)
+        res = eng.generate_in_session(session, text, _options(args), on_token=lambda t, d: (sys.stdout.write(d), sys.stdout.flush()))
+        print()
+        if stats:
+            print(_stats_line(res), file=sys.stderr)
+
+
+def cmd_serve(args, profiler):
+    import uvicorn
+
+    from .server import create_app
+
+    eng = _load(args)
+    host, _, port = args.addr.rpartition(":")
+    app = create_app(eng, model_name=os.path.basename(os.path.abspath(args.model)), max_output_tokens=args.max_output_tokens,
+                     max_queue_depth=args.max_queue_depth, enable_debug_endpoints=args.enable_debug_endpoints, node_id=args.node_id)
+    uvicorn.run(app, host=host or "127.0.0.1", port=int(port), log_level="info")
+    return 0
+
+
+def cmd_show(args, profiler):
+    from . import package as pkg
+    from .package import onnx_pb
+    from .package.decoder_graph import lower_decoder
+
+    d = pkg.open_model_directory(args.model)
+    meta = d.load_metadata()
+    model = onnx_pb.load_model(d.model_path)
+    ops_count: dict = {}
+    for n in model.graph.nodes:
+        key = (n.domain + "::" if n.domain else "") + n.op_type
+        ops_count[key] = ops_count.get(key, 0) + 1
+    cfg, _, _ = lower_decoder(model)
+    out = {"model_path": d.model_path, "variant": d.variant, "tokenizer": d.tokenizer_path, "metadata": d.metadata_path,
+           "architecture": {k: getattr(cfg, k) for k in ("num_layers", "hidden", "num_heads", "num_kv_heads", "head_dim",
+                                                         "intermediate", "vocab", "weight_format", "tie_embeddings", "qkv_bias")},
+           "max_sequence_length": meta.max_sequence_length, "required_capabilities": meta.required_capabilities,
+           "operators": dict(sorted(ops_count.items())), "weight_bytes": cfg.weight_bytes()}
+    print(json.dumps(out, indent=1))
+    return 0
+
+
+def cmd_list(args, profiler):
+    root = args.models_dir
+    for name in sorted(os.listdir(root)):
+        p = os.path.join(root, name)
+        if os.path.isdir(p) and (os.path.exists(os.path.join(p, "manifest.json")) or any(f.endswith(".onnx") for f in os.listdir(p))):
+            print(name)
+    return 0
+
+
+def cmd_export(args, profiler):
+    from .package import export
+
+    sys.argv = ["export", "--preset", args.preset, "--out", args.out] + (["--int4"] if args.int4 else []) + \
+        (["--layers", str(args.layers)] if args.layers else [])
+    export.main()
+    return 0
+
+
+class Profiler:
+    """--profile: per-stage wall clock table + latency percentiles; --profile-json / --profile-trace write files."""
+
+    def __init__(self, enabled, json_path=None, trace_path=None):
+        self.enabled, self.json_path, self.trace_path = enabled or bool(json_path) or bool(trace_path), json_path, trace_path
+        self.spans = []
+
+    def span(self, name):
+        prof = self
+
+        class _S:
+            def __enter__(self):
+                self.t0 = time.perf_counter()
+
+            def __exit__(self, *a):
+                prof.spans.append((name, self.t0, time.perf_counter()))
+
+        return _S()
+
+    def report(self, res, itl, eng):
+        if not self.enabled:
+            return
+        itl_ms = sorted(x * 1e3 for x in itl)
+        pct = lambda p: itl_ms[min(len(itl_ms) - 1, int(p * len(itl_ms)))] if itl_ms else 0.0
+        rep = {"ttft_ms": res.ttft_s * 1e3, "decode_tok_per_s": res.decode_tokens_per_s,
+               "e2e_tok_per_s": res.completion_tokens / res.total_s if res.total_s else 0.0,
+               "itl_ms": {"mean": sum(itl_ms) / len(itl_ms) if itl_ms else 0.0, "p50": pct(0.5), "p90": pct(0.9), "p99": pct(0.99),
+                          "max": itl_ms[-1] if itl_ms else 0.0},
+               "finish_reason": res.finish_reason, "prompt_tokens": res.prompt_tokens, "completion_tokens": res.completion_tokens,
+               "kv": eng.resource_snapshot(), "stages": [{"name": n, "ms": (b - a) * 1e3} for n, a, b in self.spans]}
+        print("profile: TTFT %.1f ms | decode %.2f tok/s | ITL p50 %.1f / p99 %.1f ms | %s" %
+              (rep["ttft_ms"], rep["decode_tok_per_s"], rep["itl_ms"]["p50"], rep["itl_ms"]["p99"], rep["finish_reason"]), file=sys.stderr)
+        if self.json_path:
+            json.dump(rep, open(self.json_path, "w"), indent=1)
+        if self.trace_path:
+            from .utils.trace import write_chrome_trace
+
+            write_chrome_trace(self.trace_path, [(n, a, b, "cli") for n, a, b in self.spans])
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="onnx-genai-b200")
+    ap.add_argument("--profile", action="store_true")
+    ap.add_argument("--profile-json", default=None)
+    ap.add_argument("--profile-trace", default=None)
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("generate")
+    g.add_argument("model")
+    g.add_argument("--prompt", default=None)
+    _add_sampling(g)
+    _add_engine(g)
+    r = sub.add_parser("run")
+    r.add_argument("model")
+    _add_sampling(r)
+    _add_engine(r)
+    s = sub.add_parser("serve")
+    s.add_argument("model")
+    s.add_argument("--addr", default="127.0.0.1:8080")
+    s.add_argument("--max-output-tokens", type=int, default=4096)
+    s.add_argument("--max-sessions", type=int, default=256)
+    s.add_argument("--max-queue-depth", type=int, default=256)
+    s.add_argument("--enable-debug-endpoints", action="store_true")
+    s.add_argument("--node-id", default="node-0")
+    s.add_argument("--max-context", type=int, default=0)
+    _add_engine(s)
+    sh = sub.add_parser("show")
+    sh.add_argument("model")
+    ls = sub.add_parser("list")
+    ls.add_argument("--models-dir", default=".")
+    sub.add_parser("version")
+    ex = sub.add_parser("export")
+    ex.add_argument("--preset", default="tiny-llama")
+    ex.add_argument("--out", required=True)
+    ex.add_argument("--int4", action="store_true")
+    ex.add_argument("--layers", type=int, default=0)
+    args = ap.parse_args(argv)
+    if args.cmd == "version":
+        print(f"onnx-genai-b200 {__version__}")
+        return 0
+    profiler = Profiler(args.profile, args.profile_json, args.profile_trace)
+    return {"generate": cmd_generate, "run": cmd_run, "serve": cmd_serve, "show": cmd_show, "list": cmd_list,
+            "export": cmd_export}[args.cmd](args, profiler)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

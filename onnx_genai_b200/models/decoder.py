@@ -58,6 +58,18 @@ def pick_swiglu_half(inter_local: int) -> int:
     raise ValueError(f"intermediate size {inter_local} is not a multiple of 32")
 
 
+def pad_mlp(gate, up, down, multiple: int = 64):
+    """Zero-pad the MLP's intermediate dimension to a multiple of the GEMM tile half-width.  Exact:
+    padded gate/up rows produce silu(0) * 0 = 0 and meet zero columns of the down projection."""
+    inter = gate.shape[0]
+    pad = (-inter) % multiple
+    if pad == 0:
+        return gate, up, down
+    z = torch.zeros(pad, gate.shape[1], dtype=gate.dtype, device=gate.device)
+    zd = torch.zeros(down.shape[0], pad, dtype=down.dtype, device=down.device)
+    return torch.cat([gate, z], 0), torch.cat([up, z], 0), torch.cat([down, zd], 1)
+
+
 def random_weights(cfg: DecoderConfig, device, tp: int = 1, rank: int = 0, seed: int = 0, std: float = 0.02,
                    dtype=torch.bfloat16) -> DecoderWeights:
     """Seeded N(0, std) weights of the architecture, sharded for (tp, rank).
@@ -80,7 +92,7 @@ def random_weights(cfg: DecoderConfig, device, tp: int = 1, rank: int = 0, seed:
     moe = cfg.moe.num_experts > 0
     if not moe:
         i0, i1 = shard_range(cfg.intermediate, tp, rank, 32 if tp > 1 else 1)
-        half = pick_swiglu_half(i1 - i0)
+        half = pick_swiglu_half((i1 - i0) + (-(i1 - i0)) % 64 if (i1 - i0) % 32 else (i1 - i0))
     else:
         half = pick_swiglu_half(cfg.moe.expert_intermediate)
     embed = draw(cfg.vocab, hid)
@@ -99,9 +111,12 @@ def random_weights(cfg: DecoderConfig, device, tp: int = 1, rank: int = 0, seed:
         if not moe:
             g = draw(cfg.intermediate, hid)[i0:i1]
             u = draw(cfg.intermediate, hid)[i0:i1]
+            dn = draw(hid, cfg.intermediate)[:, i0:i1]
+            if (i1 - i0) % 32:
+                g, u, dn = pad_mlp(g, u, dn)
             lw.gate_up_w = ops.pack_gate_up(g.contiguous(), u.contiguous(), half)
             del g, u
-            lw.down_w = draw(hid, cfg.intermediate)[:, i0:i1].contiguous()
+            lw.down_w = dn.contiguous()
         else:
             e0, e1 = shard_range(cfg.moe.num_experts, tp, rank)
             lw.router_w = draw(cfg.moe.num_experts, hid)

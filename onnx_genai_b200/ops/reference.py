@@ -224,8 +224,8 @@ def spec_verify_greedy(logits, draft, k):
     return accept.to(logits.device), out.to(logits.device)
 
 
-def dequant_w4(qweight, scales, zero_points=None, block=32):
-    """MatMulNBits int4: qweight [N, K/block, block/2] uint8, scales [N, K/block] -> W [N, K] fp32."""
+def dequant_w4(qweight, scales, zero_points=None, block=32, k=None):
+    """MatMulNBits int4: qweight [N, ceil(K/block), block/2] uint8, scales [N, ceil(K/block)] -> W [N, K] fp32."""
     n, kb, _ = qweight.shape
     lo = (qweight & 0xF).to(torch.int16)
     hi = (qweight >> 4).to(torch.int16)
@@ -236,12 +236,16 @@ def dequant_w4(qweight, scales, zero_points=None, block=32):
         zlo = (zero_points & 0xF).to(torch.int16)
         zhi = (zero_points >> 4).to(torch.int16)
         zp = torch.stack([zlo, zhi], dim=-1).reshape(n, -1)[:, :kb].float()
-    return ((codes - zp[:, :, None]) * scales.float()[:, :, None]).reshape(n, kb * block)
+    w = ((codes - zp[:, :, None]) * scales.float()[:, :, None]).reshape(n, kb * block)
+    return w[:, :k].contiguous() if k is not None and k < kb * block else w
 
 
 def quantize_w4(w, block=32, symmetric=True):
     """Block-wise int4 quantisation producing the MatMulNBits layout (used by exporters and tests)."""
     n, k = w.shape
+    if k % block:  # MatMulNBits pads the last K block with zeros
+        w = torch.cat([w.float(), torch.zeros(n, block - k % block)], 1)
+        k = w.shape[1]
     wb = w.float().view(n, k // block, block)
     if symmetric:
         amax = wb.abs().amax(-1).clamp_min(1e-8)

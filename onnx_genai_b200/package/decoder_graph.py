@@ -16,7 +16,7 @@ import numpy as np
 import torch
 
 from ..models.config import DecoderConfig
-from ..models.decoder import DecoderWeights, LayerWeights, pick_swiglu_half
+from ..models.decoder import DecoderWeights, LayerWeights, pad_mlp, pick_swiglu_half
 from ..ops import reference as ref
 from . import onnx_pb as pb
 
@@ -162,11 +162,12 @@ class _Lin:
         self.q = self.scales = self.zp = None
         self.bias = None
         self.block = 32
+        self.k = None
 
     def dense(self, dtype) -> torch.Tensor:
         if self.w is not None:
             return self.w.to(dtype)
-        return ref.dequant_w4(self.q, self.scales.float(), self.zp, self.block).to(dtype)
+        return ref.dequant_w4(self.q, self.scales.float(), self.zp, self.block, self.k).to(dtype)
 
 
 def lower_decoder(model: pb.Model, dtype=torch.float32, device="cpu", keep_int4: bool = False):
@@ -188,6 +189,7 @@ def lower_decoder(model: pb.Model, dtype=torch.float32, device="cpu", keep_int4:
             if int(node.attrs.get("bits", 4)) != 4:
                 raise GraphPatternError(f"node {node.name!r}: MatMulNBits with bits={node.attrs.get('bits')} is not supported (int4 only)")
             lin.block = int(node.attrs.get("block_size", 32))
+            lin.k = int(node.attrs["K"]) if "K" in node.attrs else None
             lin.q = _torch_of(const(node.inputs[1]))
             lin.scales = _torch_of(const(node.inputs[2]))
             if len(node.inputs) > 3 and node.inputs[3]:
@@ -295,7 +297,7 @@ def lower_decoder(model: pb.Model, dtype=torch.float32, device="cpu", keep_int4:
                         rotary_dim=int(cos.shape[1] * 2) if cos is not None else 0,
                         sliding_window=max(0, int(gqa_attrs.get("local_window_size", -1))),
                         weight_format="int4" if int4 else "bf16", int4_block=first["o"].block if int4 else 32)
-    half = pick_swiglu_half(inter)
+    half = pick_swiglu_half(inter + (-inter) % 64 if inter % 32 else inter)
     dev = torch.device(device)
     layers, unpacked = [], []
     for lr in layers_raw:
@@ -308,6 +310,8 @@ def lower_decoder(model: pb.Model, dtype=torch.float32, device="cpu", keep_int4:
             qkv_b = torch.cat([p.bias if p.bias is not None else torch.zeros(p.dense(torch.float32).shape[0]) for p in projs], 0)
         gate, up, down = (lr["mlp"][i].dense(torch.float32) for i in range(3))
         unpacked.append((gate, up))
+        if inter % 32:
+            gate, up, down = pad_mlp(gate, up, down)
         lw = LayerWeights(ln1=lr["ln1"].to(dtype).to(dev), qkv_w=qkv_w.to(dtype).to(dev),
                           qkv_b=qkv_b.to(dtype).to(dev) if qkv_b is not None else None,
                           o_w=lr["o"].dense(dtype).to(dev), ln2=lr["ln2"].to(dtype).to(dev),

@@ -50,7 +50,18 @@ def export_package(cfg: DecoderConfig, weights, out_dir: str, dtype: str = "fp32
                    scale_dtype: str = "fp32", generation_defaults=None, tokenizer: bool = True) -> str:
     os.makedirs(out_dir, exist_ok=True)
     half = weights.swiglu_half
-    export_decoder(cfg, lambda li: unpack_gate_up(weights.layers[li].gate_up_w.float().cpu(), half), weights,
+    import copy
+
+    def natural(li):  # strip the zero padding the executor may have added to the intermediate dimension
+        g, u = unpack_gate_up(weights.layers[li].gate_up_w.float().cpu(), half)
+        return g[: cfg.intermediate], u[: cfg.intermediate]
+
+    if weights.layers[0].down_w.shape[1] != cfg.intermediate:
+        weights = copy.copy(weights)
+        weights.layers = [copy.copy(l) for l in weights.layers]
+        for l in weights.layers:
+            l.down_w = l.down_w[:, : cfg.intermediate].contiguous()
+    export_decoder(cfg, natural, weights,
                    os.path.join(out_dir, "decoder.onnx"), dtype=dtype, int4=int4, scale_dtype=scale_dtype)
     doc = md.emit(cfg, generation_defaults=generation_defaults)
     if int4:

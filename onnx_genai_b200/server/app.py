@@ -1,0 +1,390 @@
+"""OpenAI-compatible HTTP server with SSE streaming.
+
+Route surface of the reference's axum server (crates/onnx-genai-server/src/lib.rs:65-133):
+``/health``, ``/v1/models``, ``/v1/status``, ``/v1/resources``, ``/v1/sessions`` (POST, DELETE),
+``/v1/completions``, ``/v1/chat/completions`` (SSE when ``stream: true``), ``/v1/embeddings``
+(declined with a precise error: decoder packages expose no pooled output), ``/metrics``
+(Prometheus text) and opt-in ``/v1/debug/*``.  Like the reference (src/driver.rs:266-326) the
+engine is owned by ONE driver thread; request handlers talk to it through queues, and the driver
+runs the continuous-batching step loop so concurrent requests share every forward pass.
+"""
+from __future__ import annotations
+
+import asyncio
+import json
+import queue
+import threading
+import time
+import uuid
+
+from fastapi import FastAPI, Header, HTTPException, Request
+from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
+
+from ..engine.api import Engine, GenerateOptions
+from . import tools as tool_calls
+from .metrics import Metrics
+
+
+class EngineDriver:
+    """Owns the engine on a dedicated thread; multiplexes requests into shared engine steps."""
+
+    def __init__(self, engine: Engine, max_queue_depth: int = 256):
+        self.engine = engine
+        self.inbox: queue.Queue = queue.Queue()
+        self.max_queue_depth = max_queue_depth
+        self.active: dict = {}
+        self.tokens_generated = 0
+        self.started = time.time()
+        self._stop = False
+        self.thread = threading.Thread(target=self._run, name="onnx-genai-batch-driver", daemon=True)
+        self.thread.start()
+
+    def submit(self, ids, opt: GenerateOptions, loop, out_q: asyncio.Queue):
+        if self.inbox.qsize() + len(self.active) >= self.max_queue_depth:
+            raise OverflowError("queue full")
+        self.inbox.put(("gen", ids, opt, loop, out_q))
+
+    def cancel(self, out_q):
+        self.inbox.put(("cancel", out_q))
+
+    def shutdown(self):
+        self._stop = True
+        self.inbox.put(("noop",))
+
+    def _admit(self, item):
+        kind = item[0]
+        if kind == "gen":
+            _, ids, opt, loop, out_q = item
+            try:
+                sid, state = self.engine._submit(ids, opt)
+            except Exception as exc:
+                loop.call_soon_threadsafe(out_q.put_nowait, ("error", str(exc)))
+                return
+            self.active[sid] = {"loop": loop, "q": out_q, "state": state, "out": [], "emitted": "", "opt": opt}
+        elif kind == "cancel":
+            for sid, a in list(self.active.items()):
+                if a["q"] is item[1]:
+                    self.engine.llm.core.cancel(sid)
+                    self.engine._finish(sid)
+                    del self.active[sid]
+
+    def _run(self):
+        eng = self.engine
+        while not self._stop:
+            try:
+                item = self.inbox.get(timeout=0.25 if not self.active else 0.0)
+                self._admit(item)
+                while True:
+                    self._admit(self.inbox.get_nowait())
+            except queue.Empty:
+                pass
+            if not self.active or not eng.llm.has_work:
+                continue
+            try:
+                events = eng.llm.step().events
+            except Exception as exc:  # fail every in-flight request with the cause, keep serving
+                for sid, a in list(self.active.items()):
+                    a["loop"].call_soon_threadsafe(a["q"].put_nowait, ("error", f"engine step failed: {exc}"))
+                    eng._finish(sid)
+                self.active.clear()
+                continue
+            for sid, tok, fin in events:
+                a = self.active.get(sid)
+                if a is None:
+                    continue
+                self.tokens_generated += 1
+                a["out"].append(tok)
+                a["state"]["ids"].append(tok)
+                text = eng.detokenize(a["out"]) if eng.tokenizer is not None else ""
+                delta = text[len(a["emitted"]):]
+                for s in a["opt"].stop or ():
+                    hit = text.find(s) if s else -1
+                    if hit >= 0:
+                        delta = text[len(a["emitted"]):hit] if hit > len(a["emitted"]) else ""
+                        eng.llm.core.cancel(sid)
+                        fin = "stop"
+                        break
+                if delta.endswith("�") and fin is None:
+                    delta = ""  # incomplete UTF-8 sequence: wait for the next token
+                a["emitted"] += delta
+                a["loop"].call_soon_threadsafe(a["q"].put_nowait, ("token", tok, delta, fin))
+                if fin is not None:
+                    lp = list(a["state"]["logprobs"])
+                    a["loop"].call_soon_threadsafe(a["q"].put_nowait, ("done", fin, len(a["out"]), lp))
+                    eng._finish(sid)
+                    del self.active[sid]
+
+
+def _options_from_request(body: dict, default_max: int, max_cap: int) -> GenerateOptions:
+    mt = body.get("max_completion_tokens", body.get("max_tokens", default_max))
+    mt = max(0, min(int(mt if mt is not None else default_max), max_cap))
+    temperature = body.get("temperature", 1.0)
+    temperature = 1.0 if temperature is None else float(temperature)
+    stop = body.get("stop") or ()
+    if isinstance(stop, str):
+        stop = (stop,)
+    lp = body.get("top_logprobs") if body.get("logprobs") is True else (body.get("logprobs") if isinstance(body.get("logprobs"), int) else 0)
+    if body.get("logprobs") is True and not lp:
+        lp = 1
+    if lp and int(lp) > 20:
+        raise HTTPException(400, "top_logprobs must be <= 20")
+    return GenerateOptions(
+        max_new_tokens=mt, temperature=temperature, greedy=(temperature == 0.0), top_p=float(body.get("top_p") or 1.0),
+        top_k=int(body.get("top_k") or 0), min_p=float(body.get("min_p") or 0.0), top_a=float(body.get("top_a") or 0.0),
+        typical_p=float(body.get("typical_p") or 1.0), repetition_penalty=float(body.get("repetition_penalty") or 1.0),
+        frequency_penalty=float(body.get("frequency_penalty") or 0.0), presence_penalty=float(body.get("presence_penalty") or 0.0),
+        dry_multiplier=float(body.get("dry_multiplier") or 0.0), dry_base=float(body.get("dry_base") or 1.75),
+        dry_allowed_length=int(body.get("dry_allowed_length") or 2), mirostat=bool(body.get("mirostat")),
+        mirostat_tau=float(body.get("mirostat_tau") or 5.0), mirostat_eta=float(body.get("mirostat_eta") or 0.1),
+        xtc_probability=float(body.get("xtc_probability") or 0.0), xtc_threshold=float(body.get("xtc_threshold") or 0.1),
+        seed=int(body.get("seed") or 0), stop=tuple(stop), logprobs=int(lp or 0))
+
+
+def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int = 4096, max_queue_depth: int = 256,
+               enable_debug_endpoints: bool = False, node_id: str = "node-0") -> FastAPI:
+    app = FastAPI(title="onnx-genai-b200")
+    driver = EngineDriver(engine, max_queue_depth)
+    metrics = Metrics()
+    app.state.driver, app.state.metrics, app.state.engine = driver, metrics, engine
+    sessions: dict = {}
+
+    @app.middleware("http")
+    async def trace_request(request: Request, call_next):
+        t0 = time.perf_counter()
+        response = await call_next(request)
+        metrics.request(request.url.path, response.status_code, time.perf_counter() - t0)
+        return response
+
+    @app.get("/health")
+    async def health():
+        return {"status": "ok"}
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": model_name, "object": "model", "owned_by": "onnx-genai-b200"}]}
+
+    @app.get("/v1/status")
+    async def status():
+        snap = engine.resource_snapshot()
+        up = max(1e-6, time.time() - driver.started)
+        return {"node_id": node_id, "model": model_name, "kv_usage": snap["kv_usage"], "pages_total": snap["kv_pages_total"],
+                "pages_free": snap["kv_pages_free"], "queue_depth": driver.inbox.qsize() + snap["waiting"],
+                "active_requests": len(driver.active), "tokens_per_second": driver.tokens_generated / up,
+                "batch_utilization": snap["running"] / max(1, engine.llm.cfg.max_seqs), "prefix_hashes": [],
+                "sessions": len(sessions)}
+
+    @app.get("/v1/resources")
+    async def resources():
+        snap = engine.resource_snapshot()
+        cfg = engine.llm.cfg
+        return {"limits": {"max_sessions": 256, "max_queue_depth": max_queue_depth, "max_output_tokens": max_output_tokens},
+                "kv": {"pages_total": snap["kv_pages_total"], "page_tokens": 16, "dtype": cfg.kv_dtype},
+                "batching": {"continuous": True, "max_batch": cfg.max_seqs, "max_tokens_per_step": cfg.max_tokens_per_step,
+                             "chunked_prefill": cfg.prefill_chunk, "preemption": cfg.preempt}}
+
+    @app.post("/v1/sessions")
+    async def create_session():
+        sid = "sess-" + uuid.uuid4().hex[:12]
+        sessions[sid] = engine.create_session()
+        return {"id": sid}
+
+    @app.delete("/v1/sessions/{sid}")
+    async def delete_session(sid: str):
+        if sid not in sessions:
+            raise HTTPException(404, f"session {sid!r} does not exist")
+        engine.close_session(sessions.pop(sid))
+        return {"id": sid, "deleted": True}
+
+    @app.get("/metrics")
+    async def prometheus():
+        snap = engine.resource_snapshot()
+        return PlainTextResponse(metrics.render(extra={
+            "onnx_genai_active_sessions": len(sessions), "onnx_genai_pending_requests": driver.inbox.qsize(),
+            "onnx_genai_batch_size": snap["running"], "onnx_genai_kv_pages_free": snap["kv_pages_free"],
+            "onnx_genai_kv_pages_total": snap["kv_pages_total"], "onnx_genai_prefix_cache_hits_total": snap["prefix_cache_hits"],
+            "onnx_genai_prefix_cache_lookups_total": snap["prefix_cache_lookups"], "onnx_genai_preemptions_total": snap["preemptions"],
+            "onnx_genai_engine_steps_total": snap["steps"]}), media_type="text/plain; version=0.0.4")
+
+    @app.post("/v1/embeddings")
+    async def embeddings():
+        raise HTTPException(501, "this model package exposes logits only: no pooled hidden-state output is declared in its "
+                                 "inference metadata, so /v1/embeddings cannot be served")
+
+    if enable_debug_endpoints:
+        @app.get("/v1/debug/config")
+        async def debug_config():
+            return {k: (v if isinstance(v, (int, float, str, bool, type(None))) else str(v)) for k, v in engine.llm.cfg.__dict__.items()}
+
+        @app.get("/v1/debug/kv")
+        async def debug_kv():
+            return engine.resource_snapshot()
+
+    async def _run_generation(ids, opt, request: Request):
+        loop = asyncio.get_running_loop()
+        q: asyncio.Queue = asyncio.Queue()
+        try:
+            driver.submit(ids, opt, loop, q)
+        except OverflowError:
+            metrics.rejected()
+            raise HTTPException(429, f"request queue is full ({max_queue_depth} in flight); retry later")
+        return q
+
+    def _prompt_ids(body, chat: bool, session_header):
+        if chat:
+            msgs = body.get("messages")
+            if not isinstance(msgs, list) or not msgs:
+                raise HTTPException(400, "messages must be a non-empty list of {role, content} objects")
+            norm = []
+            for m in msgs:
+                content = m.get("content")
+                if isinstance(content, list):
+                    parts = []
+                    for part in content:
+                        if part.get("type") == "text":
+                            parts.append(part.get("text", ""))
+                        else:
+                            raise HTTPException(400, f"content part of type {part.get('type')!r} is not supported by this text-only model")
+                    content = "".join(parts)
+                norm.append({**m, "content": content or ""})
+            tools = body.get("tools")
+            if body.get("tool_choice") == "none":
+                tools = None
+            if tools:
+                norm = tool_calls.inject_tool_prompt(norm, tools, body.get("tool_choice"))
+            if body.get("response_format", {}).get("type") in ("json_object", "json_schema"):
+                norm = norm + [{"role": "system", "content": "Respond with a single valid JSON object and nothing else."}]
+            text = engine.apply_chat_template(norm, add_generation_prompt=True, tools=tools)
+        else:
+            text = body.get("prompt")
+            if isinstance(text, list):
+                text = text[0] if text and isinstance(text[0], str) else text
+            if body.get("suffix") and isinstance(text, str):  # fill-in-the-middle
+                text = f"<|fim_prefix|>{text}<|fim_suffix|>{body['suffix']}<|fim_middle|>"
+        ids = engine.tokenize(text) if isinstance(text, str) else [int(t) for t in (text or [])]
+        if not ids:
+            raise HTTPException(400, "the prompt is empty after tokenisation")
+        if session_header and session_header in sessions:
+            hist = engine._session(sessions[session_header]).tokens
+            ids = hist + ids
+        limit = engine.llm.cfg.max_seq_len
+        if len(ids) >= limit:
+            raise HTTPException(400, f"prompt has {len(ids)} tokens but the model's context is {limit}; shorten the prompt")
+        return ids
+
+    async def _complete(body: dict, request: Request, chat: bool, session_header):
+        opt = _options_from_request(body, 256, max_output_tokens)
+        ids = _prompt_ids(body, chat, session_header)
+        rid = ("chatcmpl-" if chat else "cmpl-") + uuid.uuid4().hex[:24]
+        created = int(time.time())
+        q = await _run_generation(ids, opt, request)
+        t0 = time.perf_counter()
+        metrics.prompt_tokens(len(ids))
+        obj = "chat.completion" if chat else "text_completion"
+
+        def finish_session(out_ids):
+            if session_header and session_header in sessions:
+                engine._session(sessions[session_header]).tokens = ids + list(out_ids)
+
+        if body.get("stream"):
+            async def gen():
+                first = True
+                out_ids = []
+                try:
+                    if chat:
+                        yield _sse({"id": rid, "object": obj + ".chunk", "created": created, "model": model_name,
+                                    "choices": [{"index": 0, "delta": {"role": "assistant"}, "finish_reason": None}]})
+                    while True:
+                        ev = await q.get()
+                        if ev[0] == "error":
+                            yield _sse({"error": {"message": ev[1], "type": "engine_error"}})
+                            break
+                        if ev[0] == "token":
+                            _, tok, delta, fin = ev
+                            out_ids.append(tok)
+                            if first:
+                                metrics.ttft(time.perf_counter() - t0)
+                                first = False
+                            if delta:
+                                choice = ({"index": 0, "delta": {"content": delta}, "finish_reason": None} if chat
+                                          else {"index": 0, "text": delta, "finish_reason": None})
+                                yield _sse({"id": rid, "object": obj + ".chunk", "created": created, "model": model_name,
+                                            "choices": [choice]})
+                        elif ev[0] == "done":
+                            _, fin, n, _lp = ev
+                            metrics.completion_tokens(n)
+                            metrics.e2e(time.perf_counter() - t0)
+                            choice = ({"index": 0, "delta": {}, "finish_reason": fin} if chat
+                                      else {"index": 0, "text": "", "finish_reason": fin})
+                            yield _sse({"id": rid, "object": obj + ".chunk", "created": created, "model": model_name,
+                                        "choices": [choice],
+                                        "usage": {"prompt_tokens": len(ids), "completion_tokens": n, "total_tokens": len(ids) + n}})
+                            finish_session(out_ids)
+                            break
+                    yield "data: [DONE]\n\n"
+                except asyncio.CancelledError:
+                    driver.cancel(q)
+                    raise
+
+            return StreamingResponse(gen(), media_type="text/event-stream")
+
+        text, out_ids, fin, lps = "", [], None, []
+        while True:
+            ev = await q.get()
+            if ev[0] == "error":
+                raise HTTPException(500, ev[1])
+            if ev[0] == "token":
+                if not out_ids:
+                    metrics.ttft(time.perf_counter() - t0)
+                out_ids.append(ev[1])
+                text += ev[2]
+            elif ev[0] == "done":
+                fin, lps = ev[1], ev[3]
+                break
+        metrics.completion_tokens(len(out_ids))
+        metrics.e2e(time.perf_counter() - t0)
+        finish_session(out_ids)
+        usage = {"prompt_tokens": len(ids), "completion_tokens": len(out_ids), "total_tokens": len(ids) + len(out_ids)}
+        if chat:
+            msg = {"role": "assistant", "content": text}
+            calls = tool_calls.parse_tool_calls(text) if body.get("tools") else []
+            if calls:
+                msg = {"role": "assistant", "content": None, "tool_calls": calls}
+                fin = "tool_calls"
+            choice = {"index": 0, "message": msg, "finish_reason": fin}
+            if lps:
+                choice["logprobs"] = {"content": [
+                    {"token": engine.detokenize([t]), "logprob": lp, "top_logprobs": [{"token": engine.detokenize([i]), "logprob": l} for i, l in top]}
+                    for t, (lp, top) in zip(out_ids, lps)]}
+        else:
+            choice = {"index": 0, "text": text, "finish_reason": fin}
+            if lps:
+                choice["logprobs"] = {"tokens": [engine.detokenize([t]) for t in out_ids], "token_logprobs": [lp for lp, _ in lps]}
+        return JSONResponse({"id": rid, "object": obj, "created": created, "model": model_name, "choices": [choice], "usage": usage})
+
+    @app.post("/v1/completions")
+    async def completions(request: Request, x_session_id: str | None = Header(default=None)):
+        return await _complete(await _json(request), request, False, x_session_id)
+
+    @app.post("/v1/chat/completions")
+    async def chat_completions(request: Request, x_session_id: str | None = Header(default=None)):
+        return await _complete(await _json(request), request, True, x_session_id)
+
+    @app.on_event("shutdown")
+    async def _shutdown():
+        driver.shutdown()
+
+    return app
+
+
+async def _json(request: Request) -> dict:
+    try:
+        body = await request.json()
+    except Exception:
+        raise HTTPException(400, "request body is not valid JSON")
+    if not isinstance(body, dict):
+        raise HTTPException(400, "request body must be a JSON object")
+    return body
+
+
+def _sse(obj) -> str:
+    return "data: " + json.dumps(obj, ensure_ascii=False) + "\n\n"

@@ -1,0 +1,61 @@
+"""Chrome Trace Event (Perfetto) timeline export and a small span collector.
+
+Role of the reference's runtime trace (crates/onnx-genai-engine/src/runtime_trace.rs:1-107,
+`ONNX_GENAI_TRACE=path`): engine spans and per-op device spans on one clock, written as JSON that
+https://ui.perfetto.dev opens directly.
+"""
+from __future__ import annotations
+
+import json
+import os
+import threading
+import time
+
+
+def write_chrome_trace(path: str, spans, pid: int = 1) -> None:
+    """spans: iterable of (name, t_start_s, t_end_s, category)."""
+    events = []
+    tids = {}
+    for name, a, b, cat in spans:
+        tid = tids.setdefault(cat, len(tids) + 1)
+        events.append({"name": name, "cat": cat, "ph": "X", "ts": a * 1e6, "dur": max(0.0, (b - a) * 1e6), "pid": pid, "tid": tid})
+    for cat, tid in tids.items():
+        events.append({"name": "thread_name", "ph": "M", "pid": pid, "tid": tid, "args": {"name": cat}})
+    with open(path, "w", encoding="utf-8") as f:
+        json.dump({"traceEvents": events, "displayTimeUnit": "ms"}, f)
+
+
+class Tracer:
+    """Process-wide span collector; enabled by ONNX_GENAI_TRACE=<path> or start()."""
+
+    def __init__(self):
+        self.lock = threading.Lock()
+        self.spans = []
+        self.path = os.environ.get("ONNX_GENAI_TRACE") or None
+        self.enabled = self.path is not None
+
+    def start(self, path):
+        self.path, self.enabled = path, True
+
+    def span(self, name, cat="engine"):
+        tracer = self
+
+        class _Span:
+            def __enter__(self):
+                self.t0 = time.perf_counter()
+                return self
+
+            def __exit__(self, *exc):
+                if tracer.enabled:
+                    with tracer.lock:
+                        tracer.spans.append((name, self.t0, time.perf_counter(), cat))
+                return False
+
+        return _Span()
+
+    def flush(self):
+        if self.enabled and self.path:
+            write_chrome_trace(self.path, self.spans)
+
+
+TRACER = Tracer()

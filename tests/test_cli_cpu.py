@@ -1,0 +1,34 @@
+import json
+import subprocess
+import sys
+
+import pytest
+
+
+@pytest.fixture(scope="module")
+def pkg_dir(tmp_path_factory):
+    out = str(tmp_path_factory.mktemp("cli") / "tiny")
+    r = subprocess.run([sys.executable, "-m", "onnx_genai_b200", "export", "--preset", "tiny-llama", "--layers", "1", "--out", out, "--int4"],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    return out
+
+
+def test_version_and_show(pkg_dir):
+    r = subprocess.run([sys.executable, "-m", "onnx_genai_b200", "version"], capture_output=True, text=True)
+    assert r.stdout.startswith("onnx-genai-b200 ")
+    r = subprocess.run([sys.executable, "-m", "onnx_genai_b200", "show", pkg_dir], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    info = json.loads(r.stdout)
+    assert info["architecture"]["weight_format"] == "int4" and info["operators"]["com.microsoft::MatMulNBits"] >= 7
+
+
+def test_generate_with_profile_json(pkg_dir, tmp_path):
+    prof, trace = str(tmp_path / "p.json"), str(tmp_path / "t.json")
+    r = subprocess.run([sys.executable, "-m", "onnx_genai_b200", "--profile-json", prof, "--profile-trace", trace, "generate", pkg_dir,
+                        "--prompt", "hello", "--max-new-tokens", "5", "--greedy", "--device", "cpu"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    assert "tok |" in r.stderr
+    rep = json.load(open(prof))
+    assert rep["completion_tokens"] <= 5 and "itl_ms" in rep and "kv" in rep
+    assert json.load(open(trace))["traceEvents"]
