@@ -43,11 +43,6 @@ int ogb_paged_decode_bf16(const void* q, void* out, const void* pool, const int*
                           int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride,
                           int o_stride, float scale, int num_splits, float* part_o, float* part_ml, int window,
                           int* status, void* stream);
-// kv_fp8 != 0: pool holds e4m3 bytes, scales [pages, hkv, 2] fp32.
-int ogb_paged_decode_fp8(const void* q, void* out, const void* pool, const float* scales, const int* page_table,
-                         const int* ctx_len, int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d,
-                         int q_stride, int o_stride, float scale, int num_splits, float* part_o, float* part_ml,
-                         int q_per_seq, int* status, void* stream);
 
 // Sampling.  logits [rows, vocab] bf16 (ld = row stride).  out_tokens int32 [rows].
 int ogb_argmax_bf16(const void* logits, int* out_tokens, int rows, int vocab, int ld, void* stream);
@@ -68,7 +63,7 @@ int ogb_kv_scatter_pages(void* pool, const void* staging, const int64_t* pages, 
 // MatMulNBits int4 (block 32, optional nibble zero points) weight-only GEMM, in-kernel dequant.
 // qweight [N, K/32, 16] uint8 (low nibble = even k), scales [N, K/32] bf16 or fp32, zp [N, ceil(K/32/2)] or NULL.
 int ogb_w4a16_gemv(const void* x, const void* qweight, const void* scales, const void* zp, const void* bias, void* y,
-                   int M, int N, int K, int scales_fp32, void* stream);
+                   int M, int N, int K, int ldx, int ldy, int scales_fp32, void* stream);
 int ogb_w4a16_dequant(const void* qweight, const void* scales, const void* zp, void* w_bf16, int N, int K,
                       int scales_fp32, void* stream);
 
@@ -83,12 +78,13 @@ int ogb_moe_combine(const void* ys, const int* route_pos, const float* topk_w, v
 int ogb_grouped_gemm_bf16(const void* A, const void* W, void* C, const int* expert_offsets, int experts, int max_rows,
                           int N, int K, int epilogue, int bn, int* status, void* stream);
 
-// Tensor-parallel collectives over peer-mapped symmetric buffers (plain NVLink loads/stores).
-int ogb_allreduce_p2p_bf16(void* const* peer_bufs, void* out, uint32_t* const* peer_flags, int rank, int world,
-                           int64_t elems, uint32_t epoch, int* status, void* stream);
-int ogb_gemm_bf16_reduce_scatter(const void* A, const void* W, void* const* peer_out, uint32_t* const* peer_flags, int M,
-                                 int N, int K, int lda, int ldw, int rank, int world, uint32_t epoch, int bn, int* status,
-                                 void* stream);
+
+// Tensor parallelism over peer-mapped memory (CUDA IPC): row-parallel GEMM whose epilogue publishes tiles to
+// the owner rank, and the owner-side reduce + residual add + broadcast.  `sc` / `rp` are device-resident
+// TpScatter / TpReduce structs (tp_comm.cuh).
+int ogb_gemm_bf16_scatter(const void* A, const void* W, int M, int N, int K, int lda, int ldw, const void* sc, int bn,
+                          int* status, void* stream);
+int ogb_tp_reduce_bcast(const void* rp, int rows, int n, int chunk, int tp, int* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -127,7 +127,8 @@ class Engine:
                                      device="gpu" if str(device).startswith("cuda") else "cpu")
         meta = d.load_metadata()
         dtype = torch.bfloat16 if str(device).startswith("cuda") else torch.float32
-        cfg, weights, _ = lower_decoder(onnx_pb.load_model(d.model_path), dtype=dtype, device=device)
+        cfg, weights, _ = lower_decoder(onnx_pb.load_model(d.model_path), dtype=dtype, device=device,
+                                        keep_int4=str(device).startswith("cuda"))
         if meta.vocab_size and meta.vocab_size != cfg.vocab:
             raise md.MetadataError(f"{d.metadata_path}: model.vocab_size={meta.vocab_size} but the graph's embedding has "
                                    f"{cfg.vocab} rows; fix the metadata or re-export the model")

@@ -206,6 +206,18 @@ class DecoderModel:
         inter_local = (weights.layers[0].gate_up_w.shape[0] // 2) if weights.layers[0].gate_up_w is not None else 0
         self.act = z(max_tokens, max(inter_local, 8))
         self.partial = z(max_tokens, hid) if tp > 1 else None
+        if any(l.quant for l in weights.layers):     # MatMulNBits layers: build the int4 projections
+            from ..ops.quant import QuantLinear
+
+            for l in weights.layers:
+                if l.quant and not isinstance(l.quant.get("o"), QuantLinear):
+                    mk = lambda lin: QuantLinear(lin.q, lin.scales, lin.zp, lin.bias, lin.k, lin.block, dev)
+                    l.quant = {"qkv": [mk(p) for p in l.quant["qkv"]], "o": mk(l.quant["o"]), "gate": mk(l.quant["gate"]),
+                               "up": mk(l.quant["up"]), "down": mk(l.quant["down"])}
+            inter_q = weights.layers[0].quant["gate"].n
+            self.partial = z(max_tokens, hid)
+            self.gate_up = z(max_tokens, 2 * inter_q)
+            self.act_q = z(max_tokens, inter_q)
         self.h_last = z(max_seqs, hid)
         self.x_last = z(max_seqs, hid)
         self.logits = z(max_seqs, cfg.vocab)
@@ -302,7 +314,13 @@ class DecoderModel:
         for li, lw in enumerate(w.layers):
             pool = kv.pools[li]
             self._norm(x, lw.ln1, pending, h)
-            self._gemm(h, lw.qkv_w, out=qkv, bias=lw.qkv_b)
+            if lw.quant:
+                c0 = 0
+                for proj in lw.quant["qkv"]:          # q, k, v MatMulNBits write adjacent column slices
+                    proj(h, out=qkv[:, c0:c0 + proj.n])
+                    c0 += proj.n
+            else:
+                self._gemm(h, lw.qkv_w, out=qkv, bias=lw.qkv_b)
             ops.rope_kv_append(qkv, si.positions[:t], si.slots[:t], self.cos_sin, pool, self.hq, self.hkv, self.d,
                                self.rotary_dim, cfg.rotary_interleaved,
                                kv_scales=kv.scales[li] if kv.scales is not None else None)
@@ -314,6 +332,16 @@ class DecoderModel:
                 ops.paged_prefill(qkv[nd:], attn[nd:], pool, si.page_table[nd:nd + np_], si.ctx_len[nd:nd + np_],
                                   si.cu_q, si.tile_seq, si.tile_q0, si.num_tiles, self.hq, self.hkv, self.d, self.scale,
                                   cfg.sliding_window)
+            if lw.quant:
+                pending = lw.quant["o"](attn, out=self.partial[:t])
+                self._norm(x, lw.ln2, pending, h)
+                inter = lw.quant["gate"].n
+                gu = self.gate_up[:t, : 2 * inter]
+                lw.quant["gate"](h, out=gu[:, :inter])
+                lw.quant["up"](h, out=gu[:, inter:])
+                act = ops.silu_mul(gu, out=self.act_q[:t]) if x.is_cuda else ops.silu_mul(gu)
+                pending = lw.quant["down"](act, out=self.partial[:t])
+                continue
             pending = self._row_parallel(attn, lw.o_w, x, 0)
             self._norm(x, lw.ln2, pending, h)
             if lw.gate_up_w is not None:

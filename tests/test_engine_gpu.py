@@ -87,3 +87,28 @@ def test_greedy_gpu_matches_baseline_library_path():
             ops.set_baseline(False)
     err = float((outs[False] - outs[True]).norm() / outs[True].norm())
     assert err < 2e-2, err
+
+
+def test_int4_package_runs_in_kernel_dequant_on_gpu(tmp_path):
+    """A MatMulNBits package loaded on the GPU keeps its weights int4 (GEMV / dequant kernels) and agrees with the CPU path."""
+    from onnx_genai_b200.engine.api import Engine, GenerateOptions
+    from onnx_genai_b200.package.export import export_package
+
+    cfg = DecoderConfig(name="q", num_layers=2, hidden=256, num_heads=4, num_kv_heads=2, head_dim=64, intermediate=688,
+                        vocab=512, rope_theta=1e4, tie_embeddings=False, qkv_bias=True, max_position=256)
+    w = random_weights(cfg, "cpu", seed=2, std=0.08, dtype=torch.float32)
+    d = export_package(cfg, w, str(tmp_path / "q4"), int4=True)
+    outs = {}
+    for dev in ("cuda", "cpu"):
+        eng = Engine.from_dir(d, device=dev, num_pages=64, max_seqs=4, max_tokens_per_step=64)
+        before = ops.launch_counts["w4a16_gemv"]
+        eng.llm.add_request(np.arange(3, 40, dtype=np.int32), 3)
+        eng.llm.step()
+        first = eng.llm.model.logits[:1].float().cpu().clone()
+        eng.llm.step()
+        outs[dev] = (first, eng.llm.model.logits[:1].float().cpu().clone())
+        if dev == "cuda":
+            assert not eng.llm.native_executor and ops.launch_counts["w4a16_gemv"] > before
+    ops.check_status()
+    for a, b in zip(outs["cuda"], outs["cpu"]):
+        assert float((a - b).norm() / b.norm()) < 4e-2

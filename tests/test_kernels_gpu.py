@@ -252,3 +252,24 @@ def test_kv_page_utils():
     pool[1].zero_()
     ops.kv_scatter_pages(pool, staging, src)
     assert torch.equal(pool[1], orig[1])
+
+
+@pytest.mark.parametrize("m,n,k,sym,fp32_scales", [(1, 896, 896, True, False), (3, 1152, 896, False, True), (8, 896, 4864, True, False),
+                                                   (5, 100, 688, False, False), (40, 1152, 896, True, False)])
+def test_w4a16_linear(m, n, k, sym, fp32_scales):
+    from onnx_genai_b200.ops.quant import QuantLinear
+
+    torch.manual_seed(11)
+    w = torch.randn(n, k) * 0.05
+    q, s, zp = ref.quantize_w4(w, 32, symmetric=sym)
+    if not fp32_scales:
+        s = s.bfloat16()
+    bias = torch.randn(n) * 0.1
+    lin = QuantLinear(q, s, zp, bias, k=k, device=DEV)
+    x = (torch.randn(m, k, device=DEV) * 0.5).bfloat16()
+    got = lin(x)
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = x.float().cpu() @ ref.dequant_w4(q, s.float(), zp, 32, k).t() + bias.bfloat16().float()
+    assert _rel_err(got.cpu(), want) < 1.2e-2
+    assert ops.launch_counts["w4a16_gemv" if m <= 8 else "w4a16_dequant"] > 0
