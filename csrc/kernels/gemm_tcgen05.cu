@@ -57,7 +57,8 @@ __global__ void __launch_bounds__(kGemmThreadsScatter, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias,
                          const __nv_bfloat16* residual, float* __restrict__ C_f32, int M, int N, int K, int ldc, int ldr,
-                         int* status, const TpScatter* __restrict__ sc) {
+                         int* status, const TpScatter* __restrict__ sc, const int* __restrict__ group_tab,
+                         const int* __restrict__ group_mtiles) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -72,7 +73,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int m_tiles = (M + kBM - 1) / kBM;
+  // grouped (MoE) mode: the m-tile list {expert, first row, end row} and its length live in device memory
+  const int m_tiles = group_tab != nullptr ? *group_mtiles : (M + kBM - 1) / kBM;
   const int n_tiles = (N + BN - 1) / BN;
   const int num_tiles = m_tiles * n_tiles;
   const int k_blocks = (K + kBK - 1) / kBK;
@@ -108,15 +110,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % m_tiles) * kBM;
+        const int mt = tile % m_tiles;
         const int n0 = (tile / m_tiles) * BN;
+        const int m0 = group_tab != nullptr ? group_tab[4 * mt + 1] : mt * kBM;
+        const int b_row = group_tab != nullptr ? group_tab[4 * mt] * N + n0 : n0;   // expert e's weights start at row e*N
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::kStage;
           uint8_t* sb = sa + Cfg::kStageA;
           mbar_expect_tx(&full_bar[stage], Cfg::kStage);
           tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * kBK, m0);
-          tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBK, n0);
+          tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBK, b_row);
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -163,7 +167,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      const int m0 = (tile % m_tiles) * kBM;
+      const int mt = tile % m_tiles;
+      const int m0 = group_tab != nullptr ? group_tab[4 * mt + 1] : mt * kBM;
+      const int m_end = group_tab != nullptr ? group_tab[4 * mt + 2] : M;   // rows past m_end belong to the next expert
       const int n_tile = tile / m_tiles;
       const int n0 = n_tile * BN;
       // every lane polls (each needs the acquire); the vote keeps the warp converged for tcgen05.ld
@@ -181,7 +187,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           tmem_ld_32x32(t_row + HALF + c * 32, u);
           tmem_ld_wait();
           const int col = n_tile * HALF + c * 32;
-          if (row < M && col < out_n) {
+          if (row < m_end && col < out_n) {
             uint32_t o[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -211,7 +217,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           tmem_ld_32x32(t_row + c * 32, r);
           tmem_ld_wait();
           const int col = n0 + c * 32;
-          if (row < M && col < N) {
+          if (row < m_end && col < N) {
             const bool full = (col + 32 <= N);
             float v[32];
 #pragma unroll
@@ -377,12 +383,13 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_
 template <int BN, int EPI>
 static int launch_gemm(const void* A, const void* W, void* C, const void* bias, const void* residual, void* C_f32, int M,
                        int N, int K, int lda, int ldw, int ldc, int ldr, int* status, cudaStream_t stream,
-                       const TpScatter* sc = nullptr) {
+                       const TpScatter* sc = nullptr, const int* group_tab = nullptr, const int* group_mtiles = nullptr,
+                       int experts = 1, int max_mtiles = 0) {
   using Cfg = GemmCfg<BN>;
   CUtensorMap ta, tb;
   int rc = make_tmap_bf16_2d(&ta, A, M, K, lda, kBM, kBK);
   if (rc != 0) return rc;
-  rc = make_tmap_bf16_2d(&tb, W, N, K, ldw, BN, kBK);
+  rc = make_tmap_bf16_2d(&tb, W, static_cast<uint64_t>(N) * experts, K, ldw, BN, kBK);
   if (rc != 0) return rc;
   static bool attr_set = false;
   if (!attr_set) {
@@ -390,12 +397,12 @@ static int launch_gemm(const void* A, const void* W, void* C, const void* bias, 
                                         Cfg::kSmemBytes));
     attr_set = true;
   }
-  const int m_tiles = (M + kBM - 1) / kBM, n_tiles = (N + BN - 1) / BN;
+  const int m_tiles = group_tab != nullptr ? max_mtiles : (M + kBM - 1) / kBM, n_tiles = (N + BN - 1) / BN;
   int grid = m_tiles * n_tiles;
   if (grid > ogb_num_sms()) grid = ogb_num_sms();
   gemm_bf16_tcgen05_kernel<BN, EPI><<<grid, EPI == kEpiScatter ? kGemmThreadsScatter : kGemmThreads, Cfg::kSmemBytes, stream>>>(
       ta, tb, static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(bias),
-      static_cast<const __nv_bfloat16*>(residual), static_cast<float*>(C_f32), M, N, K, ldc, ldr, status, sc);
+      static_cast<const __nv_bfloat16*>(residual), static_cast<float*>(C_f32), M, N, K, ldc, ldr, status, sc, group_tab, group_mtiles);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -484,4 +491,25 @@ extern "C" int ogb_gemm_bf16_scatter(const void* A, const void* W, int M, int N,
     case 256: return launch_gemm<256, kEpiScatter>(A, W, dummy, nullptr, nullptr, nullptr, M, N, K, lda, ldw, N, 0, status, stream, s);
     default: return -2;
   }
+}
+
+// Grouped GEMM over experts (MoE): rows of A are sorted by expert; `group_tab` holds one int4 per
+// 128-row tile {expert, first row, end row, 0} and `group_mtiles` their count, both produced on the
+// device by ogb_moe_permute, so no routing information crosses to the host.  W is [experts, N, K].
+// epilogue 0 = plain, 2 = SwiGLU over per-expert packed gate|up weights (output width N/2).
+extern "C" int ogb_grouped_gemm_bf16(const void* A, const void* W, void* C, const int* group_tab, const int* group_mtiles,
+                                     int experts, int max_rows, int max_mtiles, int N, int K, int epilogue, int bn, int* status,
+                                     void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (max_rows <= 0 || experts <= 0) return 0;
+  if ((K % 8) != 0 || (N % bn) != 0) return -3;
+  const int ldc = epilogue == kEpiSwiGLU ? N / 2 : N;
+  if (epilogue == kEpiNone) {
+    if (bn == 256) return launch_gemm<256, kEpiNone>(A, W, C, nullptr, nullptr, nullptr, max_rows, N, K, K, K, ldc, 0, status, stream, nullptr, group_tab, group_mtiles, experts, max_mtiles);
+    if (bn == 128) return launch_gemm<128, kEpiNone>(A, W, C, nullptr, nullptr, nullptr, max_rows, N, K, K, K, ldc, 0, status, stream, nullptr, group_tab, group_mtiles, experts, max_mtiles);
+  } else if (epilogue == kEpiSwiGLU) {
+    if (bn == 256) return launch_gemm<256, kEpiSwiGLU>(A, W, C, nullptr, nullptr, nullptr, max_rows, N, K, K, K, ldc, 0, status, stream, nullptr, group_tab, group_mtiles, experts, max_mtiles);
+    if (bn == 128) return launch_gemm<128, kEpiSwiGLU>(A, W, C, nullptr, nullptr, nullptr, max_rows, N, K, K, K, ldc, 0, status, stream, nullptr, group_tab, group_mtiles, experts, max_mtiles);
+  }
+  return -2;
 }

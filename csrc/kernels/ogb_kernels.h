@@ -67,17 +67,17 @@ int ogb_w4a16_gemv(const void* x, const void* qweight, const void* scales, const
 int ogb_w4a16_dequant(const void* qweight, const void* scales, const void* zp, void* w_bf16, int N, int K,
                       int scales_fp32, void* stream);
 
-// MoE: softmax router with top-k (renormalised), token permutation by expert, grouped GEMM.
+// MoE: softmax router with top-k (renormalised), device-side permutation by expert, grouped GEMM, combine.
 int ogb_moe_route_topk(const void* router_logits, int* topk_ids, float* topk_w, int tokens, int experts, int k,
-                       int renormalize, void* stream);
-int ogb_moe_permute(const int* topk_ids, int* expert_counts, int* expert_offsets, int* sorted_route, int* route_pos,
-                    int tokens, int k, int experts, void* stream);
-int ogb_moe_gather_rows(const void* x, const int* sorted_route, void* xs, int routes, int k, int hidden, void* stream);
+                       int renormalize, int ld, void* stream);
+int ogb_moe_permute(const int* topk_ids, int* counts, int* offsets, int* cursor, int* sorted_route, int* route_pos,
+                    int* tile_tab, int* meta, int tokens, int k, int e0, int experts, int max_mtiles, void* stream);
+int ogb_moe_gather_rows(const void* x, const int* sorted_route, const int* meta, void* xs, int max_routes, int k, int hidden,
+                        void* stream);
 int ogb_moe_combine(const void* ys, const int* route_pos, const float* topk_w, void* out, int tokens, int k, int hidden,
                     int accumulate, void* stream);
-int ogb_grouped_gemm_bf16(const void* A, const void* W, void* C, const int* expert_offsets, int experts, int max_rows,
-                          int N, int K, int epilogue, int bn, int* status, void* stream);
-
+int ogb_grouped_gemm_bf16(const void* A, const void* W, void* C, const int* group_tab, const int* group_mtiles, int experts,
+                          int max_rows, int max_mtiles, int N, int K, int epilogue, int bn, int* status, void* stream);
 
 // Tensor parallelism over peer-mapped memory (CUDA IPC): row-parallel GEMM whose epilogue publishes tiles to
 // the owner rank, and the owner-side reduce + residual add + broadcast.  `sc` / `rp` are device-resident

@@ -144,3 +144,26 @@ def test_admission_rejects_oversized_prompt():
     core = Core(CoreConfig(num_pages=32, max_seqs=4, max_tokens_per_step=64, max_pages_per_seq=2))
     with pytest.raises(ValueError, match="does not fit"):
         core.add_request(list(range(40)), 4)
+
+
+def test_moe_decoder_cpu_matches_dense_expert_loop():
+    """MoE decoder (router top-k + experts) through the engine on CPU: expert split across two ranks sums to the same output."""
+    from onnx_genai_b200.models.config import MoEConfig
+    from onnx_genai_b200.ops import moe as moe_ops
+
+    torch.manual_seed(0)
+    t, e, k, hidden, inter, half = 9, 8, 2, 32, 64, 32
+    h = torch.randn(t, hidden)
+    router = torch.randn(t, e)
+    gu = torch.randn(e, 2 * inter, hidden) * 0.1
+    dn = torch.randn(e, hidden, inter) * 0.1
+    full = moe_ops.moe_experts(h, router, gu, dn, None, torch.zeros(t, hidden), k, True, half, 0, False)
+    a = moe_ops.moe_experts(h, router, gu[:4], dn[:4], None, torch.zeros(t, hidden), k, True, half, 0, False)
+    b = moe_ops.moe_experts(h, router, gu[4:], dn[4:], None, torch.zeros(t, hidden), k, True, half, 4, False)
+    assert torch.allclose(a + b, full, atol=1e-5)
+    cfg = DecoderConfig(name="moe", num_layers=2, hidden=64, num_heads=4, num_kv_heads=2, head_dim=16, intermediate=0, vocab=97,
+                        max_position=256, moe=MoEConfig(num_experts=8, top_k=2, expert_intermediate=64))
+    w = random_weights(cfg, "cpu", seed=1, std=0.2, dtype=torch.float32)
+    eng = LLMEngine(EngineConfig(model=cfg, num_pages=32, max_seqs=4, max_tokens_per_step=64, max_seq_len=128), weights=w, device="cpu")
+    out = eng.generate([[1, 2, 3, 4, 5], [7, 8, 9]], max_new_tokens=6)
+    assert all(len(o) == 6 for o in out)

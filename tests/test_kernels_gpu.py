@@ -273,3 +273,37 @@ def test_w4a16_linear(m, n, k, sym, fp32_scales):
     want = x.float().cpu() @ ref.dequant_w4(q, s.float(), zp, 32, k).t() + bias.bfloat16().float()
     assert _rel_err(got.cpu(), want) < 1.2e-2
     assert ops.launch_counts["w4a16_gemv" if m <= 8 else "w4a16_dequant"] > 0
+
+
+@pytest.mark.parametrize("t,e,k,hidden,inter", [(37, 16, 4, 256, 128), (300, 128, 8, 512, 256), (5, 8, 2, 256, 768)])
+def test_moe_experts_grouped_gemm(t, e, k, hidden, inter):
+    from onnx_genai_b200.ops import moe as moe_ops
+
+    torch.manual_seed(12)
+    half = 128
+    h = (torch.randn(t, hidden, device=DEV) * 0.5).bfloat16()
+    router = torch.randn(t, e, device=DEV).bfloat16()
+    gate = (torch.randn(e, inter, hidden, device=DEV) * 0.05).bfloat16()
+    up = (torch.randn(e, inter, hidden, device=DEV) * 0.05).bfloat16()
+    down = (torch.randn(e, hidden, inter, device=DEV) * 0.05).bfloat16()
+    packed = torch.stack([ops.pack_gate_up(gate[i], up[i], half) for i in range(e)]).contiguous()
+    x0 = torch.randn(t, hidden, device=DEV).bfloat16()
+    ws = moe_ops.MoEWorkspace(t, k, e, hidden, inter, DEV)
+    got = moe_ops.moe_experts(h, router, packed, down, ws, x0.clone(), k, True, half)
+    torch.cuda.synchronize()
+    ops.check_status()
+    ids, w = ref.moe_route(router, k, True)
+    want = x0.float().clone()
+    for tok in range(t):
+        for j in range(k):
+            ex = int(ids[tok, j])
+            a = torch.nn.functional.silu(h[tok].float() @ gate[ex].float().t()) * (h[tok].float() @ up[ex].float().t())
+            want[tok] += float(w[tok, j]) * (a.bfloat16().float() @ down[ex].float().t())
+    assert _rel_err(got, want) < 2.5e-2
+    assert int(ws.meta[1]) == t * k
+    # expert-parallel slice: only experts [e/2, e) -> partial sums of the two halves add up to the full result
+    lo = moe_ops.moe_experts(h, router, packed[: e // 2].contiguous(), down[: e // 2].contiguous(),
+                             moe_ops.MoEWorkspace(t, k, e // 2, hidden, inter, DEV), torch.zeros_like(x0), k, True, half, 0, False)
+    hi = moe_ops.moe_experts(h, router, packed[e // 2:].contiguous(), down[e // 2:].contiguous(),
+                             moe_ops.MoEWorkspace(t, k, e // 2, hidden, inter, DEV), torch.zeros_like(x0), k, True, half, e // 2, False)
+    assert _rel_err(lo.float() + hi.float() + x0.float(), want) < 3e-2
