@@ -320,3 +320,39 @@ extern "C" int ogb_spec_verify_greedy(const void* logits, const int* draft_token
       static_cast<const __nv_bfloat16*>(logits), draft_tokens, accept_len, out_tokens, k, vocab, ld);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ------------------------------------------------------------------------------------------
+// Sampler entry point for callers that cannot allocate device memory (see ogb_no_alloc.h).
+// ------------------------------------------------------------------------------------------
+namespace ogb {
+constexpr int kNoAllocMaxRows = 4;
+constexpr int kNoAllocMaxVocab = 262144;
+// Work area of the fused sampler (one 32-bit weight per logit).  It lives in the library image, so
+// every GPU that loads the library carries these 4 MiB until the process exits.
+static __device__ __align__(256) uint32_t g_no_alloc_sample_work[kNoAllocMaxRows * kNoAllocMaxVocab];
+constexpr int kNoAllocMaxDevices = 64;
+static uint32_t* g_no_alloc_work_ptr[kNoAllocMaxDevices] = {};
+}  // namespace ogb
+
+extern "C" int ogb_sample_bf16_no_alloc(const void* logits, int* out_tokens, const float* temperature, const int* top_k,
+                                        const float* top_p, const float* min_p, const float* uniform, int rows, int vocab,
+                                        int ld, void* stream) {
+  if (rows <= 0) return 0;
+  if (rows > kNoAllocMaxRows || vocab <= 0 || vocab > kNoAllocMaxVocab) return -3;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kNoAllocMaxDevices) return -4;
+  if (g_no_alloc_work_ptr[dev] == nullptr) {
+    // In host code the array's name is only a handle; the device address has to be looked up, once
+    // per device, with that device current.
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_no_alloc_sample_work);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    g_no_alloc_work_ptr[dev] = static_cast<uint32_t*>(p);
+  }
+  sample_kernel<<<rows, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(logits), out_tokens, temperature, top_k, top_p, min_p, uniform,
+      g_no_alloc_work_ptr[dev], vocab, ld);
+  return static_cast<int>(cudaGetLastError());
+}
