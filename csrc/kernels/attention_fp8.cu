@@ -1,0 +1,552 @@
+// Paged GQA attention over e4m3 KV pages with one fp32 scale per (page, kv head, K|V).
+//
+// The reference quantises KV only in host page storage with a software codec (one scale per
+// (head, token slot), crates/onnx-genai-kv/src/page_table.rs:250-297,776-832, src/fp8.rs:5-198) and
+// its attention kernels never read quantised KV (group_query_attention.rs:1140-1200 rejects
+// k/v_quant_type != NONE).  Here the pages stay e4m3 in HBM (half the bytes of bf16 on the decode
+// critical path) and are expanded on chip:
+//   pool   [pages, kv_heads, 2, 16 tokens, 128] uint8 e4m3, scales [pages, kv_heads, 2] fp32
+//   TMA    one 2 KB box per (page, K|V), 128-byte swizzled, 3-stage (decode) / 2-stage (prefill) ring
+//   expand each consumer warp turns fp8 pairs into bf16 (exact: every e4m3 value is a bf16 value) and
+//          writes them in the bf16 tile layout the shared ldmatrix / mma.sync code reads
+//   scale  K scale multiplies the scores of the page's 16 keys, V scale multiplies their
+//          probabilities before P.V; the running row sum uses the unscaled probabilities
+// Head dimension 128 only.  Same bounded waits and status word as the bf16 kernels.
+#include <cuda_fp8.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "attention_common.cuh"
+#include "ogb_kernels.h"
+
+namespace ogb {
+
+constexpr int kD = 128;
+constexpr int kRawPage = kPageTokens * kD;           // 2 KB of e4m3 per page side
+constexpr int kRawStage = 4 * 2 * kRawPage;          // 4 pages x (K, V) = 16 KB
+constexpr int kWorkPage = kPageTokens * kD * 2;      // 4 KB of bf16 per page side
+
+// 16 e4m3 bytes -> 16 bf16, as two 16-byte vectors
+OGB_DEVICE void cvt16_e4m3_bf16(const uint4& raw, uint4& lo, uint4& hi) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  uint32_t o[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const __nv_fp8x2_storage_t pair = static_cast<__nv_fp8x2_storage_t>((w[i] >> (16 * h)) & 0xffffu);
+      const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(pair, __NV_E4M3);
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+      o[2 * i + h] = pack_bf16(f.x, f.y);
+    }
+  }
+  lo = make_uint4(o[0], o[1], o[2], o[3]);
+  hi = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+// Expand one raw page side (16 tokens x 128 e4m3, 128-byte swizzled rows) into a bf16 page tile
+// ([2 halves][16 rows][128 B], same swizzle), using `nthreads` threads starting at `tid`.
+OGB_DEVICE void expand_page(const uint8_t* raw, uint8_t* work, int tid, int nthreads) {
+  for (int i = tid; i < kPageTokens * 8; i += nthreads) {   // 16 rows x 8 chunks of 16 bytes
+    const int r = i >> 3, c = i & 7;
+    const uint4 v = *reinterpret_cast<const uint4*>(raw + r * 128 + ((c ^ (r & 7)) << 4));
+    uint4 lo, hi;
+    cvt16_e4m3_bf16(v, lo, hi);
+    const int d0 = c * 16;
+    *reinterpret_cast<uint4*>(work + kv_tile_off<kD>(r, d0)) = lo;
+    *reinterpret_cast<uint4*>(work + kv_tile_off<kD>(r, d0 + 8)) = hi;
+  }
+}
+
+OGB_DEVICE bool fp8_produce(const CUtensorMap* kv_map, const AttnParams& p, uint8_t* stages, uint64_t* full_bar,
+                            uint64_t* empty_bar, int nstages, int seq, int kvh, int ctx, int b_begin, int b_end) {
+  const int n_pages = (ctx + kPageTokens - 1) / kPageTokens;
+  const int* table = p.page_table + static_cast<size_t>(seq) * p.max_pages;
+  int stage = 0;
+  uint32_t phase = 0;
+  for (int b = b_begin; b < b_end; ++b) {
+    if (!mbar_wait(&empty_bar[stage], phase ^ 1)) return false;
+    uint8_t* s = stages + stage * kRawStage;
+    mbar_expect_tx(&full_bar[stage], kRawStage);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int pi = min(min(b * 4 + i, n_pages - 1), p.max_pages - 1);
+      int64_t page = table[pi];
+      if (page < 0 || page >= p.num_pages) { atomicOr(p.status, kStatusIndexOutOfRange); page = 0; }
+      const int row_k = static_cast<int>(((page * p.hkv + kvh) * 2) * kPageTokens);
+      tma_load_2d(s + i * kRawPage, kv_map, &full_bar[stage], 0, row_k);
+      tma_load_2d(s + (4 + i) * kRawPage, kv_map, &full_bar[stage], 0, row_k + kPageTokens);
+    }
+    if (++stage == nstages) { stage = 0; phase ^= 1; }
+  }
+  return true;
+}
+
+OGB_DEVICE int64_t page_of(const AttnParams& p, int seq, int ctx, int pi) {
+  const int n_pages = (ctx + kPageTokens - 1) / kPageTokens;
+  pi = min(min(pi, n_pages - 1), p.max_pages - 1);
+  int64_t page = p.page_table[static_cast<size_t>(seq) * p.max_pages + pi];
+  return (page < 0 || page >= p.num_pages) ? 0 : page;
+}
+
+// ------------------------------------------------------------------------------------------
+// decode
+// ------------------------------------------------------------------------------------------
+constexpr int kDecStages = 3;
+constexpr int kDecSmem = kDecStages * kRawStage + 4 * 2 * kWorkPage + 16 * kD * 2 + 1024 + 1024;
+
+__global__ void __launch_bounds__(kAttnThreads) paged_decode_fp8_kernel(const __grid_constant__ CUtensorMap kv_map,
+                                                                         const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stages = smem;
+  uint8_t* work = smem + kDecStages * kRawStage;          // [4 warps][K 4 KB | V 4 KB]
+  uint8_t* sq = work + 4 * 2 * kWorkPage;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sq + 16 * kD * 2);
+  uint64_t* empty_bar = full_bar + kDecStages;
+  float* sm_ml = reinterpret_cast<float*>(empty_bar + kDecStages);
+
+  const int seq = blockIdx.x / p.num_splits, split = blockIdx.x % p.num_splits, kvh = blockIdx.y;
+  const int G = p.group;
+  const int ctx = p.ctx_len[seq];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int b_begin = 0, b_end = 0;
+  if (ctx > 0) {
+    const int last = (ctx + kKvBlock - 1) / kKvBlock;
+    const int per = (last + p.num_splits - 1) / p.num_splits;
+    b_begin = split * per;
+    b_end = min(b_begin + per, last);
+  }
+  if (b_begin >= b_end) {
+    if (p.num_splits > 1 && ctx > 0) {
+      for (int idx = threadIdx.x; idx < G * kD; idx += blockDim.x) {
+        const int r = idx / kD, d = idx % kD;
+        const size_t slot = (static_cast<size_t>(seq) * p.hq + kvh * G + r) * p.num_splits + split;
+        p.part_o[slot * kD + d] = 0.f;
+        if (d == 0) { p.part_ml[slot * 2] = -INFINITY; p.part_ml[slot * 2 + 1] = 0.f; }
+      }
+    }
+    return;
+  }
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kDecStages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 4); }
+    mbar_fence_init();
+    tma_prefetch_desc(&kv_map);
+  }
+  __syncthreads();
+  if (warp == 4) {
+    if (lane == 0 && !fp8_produce(&kv_map, p, stages, full_bar, empty_bar, kDecStages, seq, kvh, ctx, b_begin, b_end))
+      atomicOr(p.status, kStatusWaitTimeout);
+    return;
+  }
+  {
+    const __nv_bfloat16* qsrc = p.q + static_cast<size_t>(seq) * p.q_stride + kvh * G * kD;
+    for (int idx = threadIdx.x; idx < 16 * (kD / 8); idx += 128) {
+      const int row = idx / (kD / 8), ch = idx % (kD / 8);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (row < G) v = *reinterpret_cast<const uint4*>(qsrc + row * kD + ch * 8);
+      *reinterpret_cast<uint4*>(sq + q_tile_off<16>(row, ch * 8)) = v;
+    }
+  }
+  compute_bar_sync();
+  uint32_t qf[kD / 16][4];
+  {
+    const uint32_t sq_u = smem_u32(sq);
+#pragma unroll
+    for (int kk = 0; kk < kD / 16; ++kk)
+      ldsm_x4(sq_u + q_tile_off<16>(lane & 15, 16 * kk + 8 * (lane >> 4)), qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+  }
+  float o[kD / 8][4];
+#pragma unroll
+  for (int j = 0; j < kD / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  uint8_t* wk = work + warp * 2 * kWorkPage;
+  uint8_t* wv = wk + kWorkPage;
+  const uint32_t sk = smem_u32(wk), sv = smem_u32(wv);
+
+  int stage = 0;
+  uint32_t phase = 0;
+  bool ok = true;
+  for (int b = b_begin; b < b_end; ++b) {
+    if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], phase))) { ok = false; break; }
+    const int tok0 = b * kKvBlock + 16 * warp;
+    if (tok0 < ctx) {
+      const uint8_t* raw = stages + stage * kRawStage;
+      expand_page(raw + warp * kRawPage, wk, lane, 32);
+      expand_page(raw + (4 + warp) * kRawPage, wv, lane, 32);
+      const int64_t page = page_of(p, seq, ctx, b * 4 + warp);
+      const float ks = p.kv_scales[(page * p.hkv + kvh) * 2] * p.scale_log2e;
+      const float vs = p.kv_scales[(page * p.hkv + kvh) * 2 + 1];
+      __syncwarp();
+      float s[2][4];
+      s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < kD / 16; ++kk) {
+        const int mi = lane >> 3;
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(sk + kv_tile_off<kD>(8 * (mi >> 1) + (lane & 7), 16 * kk + 8 * (mi & 1)), b0, b1, b2, b3);
+        mma_bf16_16816(s[0], qf[kk], b0, b1);
+        mma_bf16_16816(s[1], qf[kk], b2, b3);
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int col = tok0 + 8 * j + 2 * (lane & 3) + (e & 1);
+          s[j][e] = (col < ctx) ? s[j][e] * ks : -INFINITY;
+        }
+      float pv[2][4];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        float mx = fmaxf(fmaxf(s[0][2 * r], s[0][2 * r + 1]), fmaxf(s[1][2 * r], s[1][2 * r + 1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run[r], mx);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = exp2f(m_run[r] - m_use);
+        m_run[r] = m_new;
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const float p0 = exp2f(s[j][2 * r] - m_use), p1 = exp2f(s[j][2 * r + 1] - m_use);
+          sum += p0 + p1;
+          pv[j][2 * r] = p0 * vs;        // V scale folded into the probabilities that meet V
+          pv[j][2 * r + 1] = p1 * vs;
+        }
+        l_run[r] = l_run[r] * alpha + sum;
+#pragma unroll
+        for (int j = 0; j < kD / 8; ++j) { o[j][2 * r] *= alpha; o[j][2 * r + 1] *= alpha; }
+      }
+      uint32_t a[4];
+      a[0] = pack_bf16(pv[0][0], pv[0][1]);
+      a[1] = pack_bf16(pv[0][2], pv[0][3]);
+      a[2] = pack_bf16(pv[1][0], pv[1][1]);
+      a[3] = pack_bf16(pv[1][2], pv[1][3]);
+#pragma unroll
+      for (int jd = 0; jd < kD / 16; ++jd) {
+        const int mi = lane >> 3;
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(sv + kv_tile_off<kD>(8 * (mi & 1) + (lane & 7), 16 * jd + 8 * (mi >> 1)), b0, b1, b2, b3);
+        mma_bf16_16816(o[2 * jd], a, b0, b1);
+        mma_bf16_16816(o[2 * jd + 1], a, b2, b3);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[stage]);
+    if (++stage == kDecStages) { stage = 0; phase ^= 1; }
+  }
+  if (!ok && lane == 0) atomicOr(p.status, kStatusWaitTimeout);
+
+  compute_bar_sync();
+  float* sm_o = reinterpret_cast<float*>(stages);   // [4][16][128] fp32 = 32 KB <= 48 KB of ring
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float l = l_run[r];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const int row = (lane >> 2) + 8 * r;
+    if ((lane & 3) == 0) { sm_ml[(warp * 16 + row) * 2] = m_run[r]; sm_ml[(warp * 16 + row) * 2 + 1] = l; }
+#pragma unroll
+    for (int j = 0; j < kD / 8; ++j) {
+      float* dst = sm_o + static_cast<size_t>(warp * 16 + row) * kD + 8 * j + 2 * (lane & 3);
+      dst[0] = o[j][2 * r];
+      dst[1] = o[j][2 * r + 1];
+    }
+  }
+  compute_bar_sync();
+  for (int idx = threadIdx.x; idx < G * kD; idx += 128) {
+    const int row = idx / kD, d = idx % kD;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mx = fmaxf(mx, sm_ml[(w * 16 + row) * 2]);
+    const float m_use = (mx == -INFINITY) ? 0.f : mx;
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float wgt = exp2f(sm_ml[(w * 16 + row) * 2] - m_use);
+      acc += wgt * sm_o[static_cast<size_t>(w * 16 + row) * kD + d];
+      l += wgt * sm_ml[(w * 16 + row) * 2 + 1];
+    }
+    const int head = kvh * G + row;
+    if (p.num_splits == 1) {
+      p.out[static_cast<size_t>(seq) * p.o_stride + head * kD + d] = __float2bfloat16(l > 0.f ? acc / l : 0.f);
+    } else {
+      const size_t slot = (static_cast<size_t>(seq) * p.hq + head) * p.num_splits + split;
+      p.part_o[slot * kD + d] = acc;
+      if (d == 0) { p.part_ml[slot * 2] = mx; p.part_ml[slot * 2 + 1] = l; }
+    }
+  }
+}
+
+__global__ void paged_decode_fp8_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                              const int* __restrict__ ctx_len, __nv_bfloat16* __restrict__ out, int hq,
+                                              int num_splits, int o_stride) {
+  const int seq = blockIdx.x, head = blockIdx.y;
+  if (ctx_len[seq] <= 0) return;
+  const size_t base = (static_cast<size_t>(seq) * hq + head) * num_splits;
+  float mx = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) mx = fmaxf(mx, part_ml[(base + s) * 2]);
+  const float m_use = (mx == -INFINITY) ? 0.f : mx;
+  for (int d = threadIdx.x; d < kD; d += blockDim.x) {
+    float acc = 0.f, l = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+      const float w = exp2f(part_ml[(base + s) * 2] - m_use);
+      acc += w * part_o[(base + s) * kD + d];
+      l += w * part_ml[(base + s) * 2 + 1];
+    }
+    out[static_cast<size_t>(seq) * o_stride + head * kD + d] = __float2bfloat16(l > 0.f ? acc / l : 0.f);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// prefill (chunked, causal): 64 query rows x one head per CTA; the four consumer warps expand each
+// 64-key block together into one shared bf16 tile
+// ------------------------------------------------------------------------------------------
+constexpr int kPreStages = 2;
+constexpr int kPreTile = kKvBlock * kD * 2;   // 16 KB bf16 K tile (and as much for V)
+constexpr int kPreSmem = kPreStages * kRawStage + 2 * kPreTile + 64 * kD * 2 + 1024 + 1024;
+
+__global__ void __launch_bounds__(kAttnThreads) paged_prefill_fp8_kernel(const __grid_constant__ CUtensorMap kv_map,
+                                                                          const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stages = smem;
+  uint8_t* tile_k = smem + kPreStages * kRawStage;
+  uint8_t* tile_v = tile_k + kPreTile;
+  uint8_t* sq = tile_v + kPreTile;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sq + 64 * kD * 2);
+  uint64_t* empty_bar = full_bar + kPreStages;
+  float* sc_sh = reinterpret_cast<float*>(empty_bar + kPreStages);   // [4 pages][2]
+
+  const int tile = blockIdx.x;
+  if (tile >= p.num_tiles) return;
+  const int head = blockIdx.y, kvh = head / p.group;
+  const int seq = p.tile_seq[tile], q0 = p.tile_q0[tile];
+  const int q_begin = p.cu_q[seq];
+  const int q_len = p.cu_q[seq + 1] - q_begin;
+  const int ctx = p.ctx_len[seq];
+  const int rows = min(64, q_len - q0);
+  const int pos0 = ctx - q_len + q0;
+  if (rows <= 0 || ctx <= 0) return;
+  const int kv_end = min(ctx, pos0 + rows);
+  const int b_end = (kv_end + kKvBlock - 1) / kKvBlock;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kPreStages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 4); }
+    mbar_fence_init();
+    tma_prefetch_desc(&kv_map);
+  }
+  __syncthreads();
+  if (warp == 4) {
+    if (lane == 0 && !fp8_produce(&kv_map, p, stages, full_bar, empty_bar, kPreStages, seq, kvh, ctx, 0, b_end))
+      atomicOr(p.status, kStatusWaitTimeout);
+    return;
+  }
+  {
+    const __nv_bfloat16* qsrc = p.q + static_cast<size_t>(q_begin + q0) * p.q_stride + head * kD;
+    for (int idx = threadIdx.x; idx < 64 * (kD / 8); idx += 128) {
+      const int row = idx / (kD / 8), ch = idx % (kD / 8);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (row < rows) v = *reinterpret_cast<const uint4*>(qsrc + static_cast<size_t>(row) * p.q_stride + ch * 8);
+      *reinterpret_cast<uint4*>(sq + q_tile_off<64>(row, ch * 8)) = v;
+    }
+  }
+  compute_bar_sync();
+  uint32_t qf[kD / 16][4];
+  {
+    const uint32_t sq_u = smem_u32(sq);
+#pragma unroll
+    for (int kk = 0; kk < kD / 16; ++kk)
+      ldsm_x4(sq_u + q_tile_off<64>(16 * warp + (lane & 15), 16 * kk + 8 * (lane >> 4)), qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+  }
+  float o[kD / 8][4];
+#pragma unroll
+  for (int j = 0; j < kD / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const int row_a = 16 * warp + (lane >> 2);
+  const int qpos_a = pos0 + row_a, qpos_b = pos0 + row_a + 8;
+  const uint32_t sk = smem_u32(tile_k), sv = smem_u32(tile_v);
+
+  int stage = 0;
+  uint32_t phase = 0;
+  bool ok = true;
+  for (int b = 0; b < b_end; ++b) {
+    if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], phase))) { ok = false; break; }
+    const uint8_t* raw = stages + stage * kRawStage;
+    // warp w expands page w of the block (K and V) into the shared bf16 tiles
+    expand_page(raw + warp * kRawPage, tile_k + warp * kWorkPage, lane, 32);
+    expand_page(raw + (4 + warp) * kRawPage, tile_v + warp * kWorkPage, lane, 32);
+    if (lane < 2) {
+      const int64_t page = page_of(p, seq, ctx, b * 4 + warp);
+      sc_sh[warp * 2 + lane] = p.kv_scales[(page * p.hkv + kvh) * 2 + lane];
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[stage]);   // the raw bytes are no longer needed
+    compute_bar_sync();
+    float s[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+#pragma unroll
+    for (int kk = 0; kk < kD / 16; ++kk) {
+#pragma unroll
+      for (int jp = 0; jp < 4; ++jp) {
+        const int mi = lane >> 3;
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(sk + kv_tile_off<kD>(16 * jp + 8 * (mi >> 1) + (lane & 7), 16 * kk + 8 * (mi & 1)), b0, b1, b2, b3);
+        mma_bf16_16816(s[2 * jp], qf[kk], b0, b1);
+        mma_bf16_16816(s[2 * jp + 1], qf[kk], b2, b3);
+      }
+    }
+    const int kv_base = b * kKvBlock;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float ks = sc_sh[(j >> 1) * 2] * p.scale_log2e;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int col = kv_base + 8 * j + 2 * (lane & 3) + (e & 1);
+        const int qpos = (e < 2) ? qpos_a : qpos_b;
+        s[j][e] = (col <= qpos && col < ctx) ? s[j][e] * ks : -INFINITY;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fmaxf(s[j][2 * r], s[j][2 * r + 1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run[r], mx);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = exp2f(m_run[r] - m_use);
+      m_run[r] = m_new;
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float p0 = exp2f(s[j][2 * r] - m_use), p1 = exp2f(s[j][2 * r + 1] - m_use);
+        sum += p0 + p1;
+        const float vs = sc_sh[(j >> 1) * 2 + 1];
+        s[j][2 * r] = p0 * vs;
+        s[j][2 * r + 1] = p1 * vs;
+      }
+      l_run[r] = l_run[r] * alpha + sum;
+#pragma unroll
+      for (int j = 0; j < kD / 8; ++j) { o[j][2 * r] *= alpha; o[j][2 * r + 1] *= alpha; }
+    }
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      uint32_t a[4];
+      a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+      a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+      a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int jd = 0; jd < kD / 16; ++jd) {
+        const int mi = lane >> 3;
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(sv + kv_tile_off<kD>(16 * kk + 8 * (mi & 1) + (lane & 7), 16 * jd + 8 * (mi >> 1)), b0, b1, b2, b3);
+        mma_bf16_16816(o[2 * jd], a, b0, b1);
+        mma_bf16_16816(o[2 * jd + 1], a, b2, b3);
+      }
+    }
+    compute_bar_sync();   // everyone is done with the bf16 tiles before the next block is expanded
+    if (++stage == kPreStages) { stage = 0; phase ^= 1; }
+  }
+  if (!ok) {
+    if (lane == 0) atomicOr(p.status, kStatusWaitTimeout);
+    return;
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float l = l_run[r];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const float inv = (l > 0.f) ? 1.f / l : 0.f;
+    const int row = row_a + 8 * r;
+    if (row < rows) {
+      __nv_bfloat16* dst = p.out + static_cast<size_t>(q_begin + q0 + row) * p.o_stride + head * kD + 2 * (lane & 3);
+#pragma unroll
+      for (int j = 0; j < kD / 8; ++j)
+        *reinterpret_cast<uint32_t*>(dst + 8 * j) = pack_bf16(o[j][2 * r] * inv, o[j][2 * r + 1] * inv);
+    }
+  }
+}
+
+static int get_fp8_tmap(const void* pool, int64_t num_pages, int hkv, CUtensorMap* out) {
+  static std::mutex mu;
+  static std::unordered_map<const void*, std::pair<uint64_t, CUtensorMap>> cache;
+  const uint64_t rows = static_cast<uint64_t>(num_pages) * hkv * 2 * kPageTokens;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(pool);
+  if (it != cache.end() && it->second.first == rows) { *out = it->second.second; return 0; }
+  CUtensorMap m;
+  int rc = make_tmap_u8_2d(&m, pool, rows, kD, kD, kPageTokens, kD);
+  if (rc != 0) return rc;
+  cache[pool] = {rows, m};
+  *out = m;
+  return 0;
+}
+
+}  // namespace ogb
+
+using namespace ogb;
+
+static void fill_params(AttnParams& p, const void* q, void* out, const float* scales, const int* page_table, const int* ctx_len,
+                        int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int q_stride, int o_stride, float scale,
+                        int* status) {
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.page_table = page_table; p.ctx_len = ctx_len; p.num_seqs = num_seqs; p.max_pages = max_pages; p.num_pages = num_pages;
+  p.hq = hq; p.hkv = hkv; p.group = hq / hkv; p.q_stride = q_stride; p.o_stride = o_stride;
+  p.scale_log2e = scale * 1.4426950408889634f; p.status = status; p.kv_scales = scales; p.num_splits = 1;
+}
+
+extern "C" int ogb_paged_decode_fp8(const void* q, void* out, const void* pool, const float* scales, const int* page_table,
+                                    const int* ctx_len, int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d,
+                                    int q_stride, int o_stride, float scale, int num_splits, float* part_o, float* part_ml,
+                                    int* status, void* stream) {
+  if (num_seqs <= 0) return 0;
+  if (d != kD || hkv <= 0 || hq % hkv != 0 || hq / hkv > 16 || (q_stride % 8) != 0 || scales == nullptr) return -3;
+  if (num_splits < 1) num_splits = 1;
+  if (num_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return -4;
+  CUtensorMap map;
+  int rc = get_fp8_tmap(pool, num_pages, hkv, &map);
+  if (rc != 0) return rc;
+  AttnParams p{};
+  fill_params(p, q, out, scales, page_table, ctx_len, num_seqs, max_pages, num_pages, hq, hkv, q_stride, o_stride, scale, status);
+  p.num_splits = num_splits; p.part_o = part_o; p.part_ml = part_ml;
+  static bool attr_set = false;
+  if (!attr_set) {
+    OGB_CUDA_CHECK(cudaFuncSetAttribute(paged_decode_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem));
+    attr_set = true;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  paged_decode_fp8_kernel<<<dim3(num_seqs * num_splits, hkv), kAttnThreads, kDecSmem, st>>>(map, p);
+  rc = static_cast<int>(cudaGetLastError());
+  if (rc == 0 && num_splits > 1) {
+    paged_decode_fp8_merge_kernel<<<dim3(num_seqs, hq), kD, 0, st>>>(part_o, part_ml, ctx_len, p.out, hq, num_splits, o_stride);
+    rc = static_cast<int>(cudaGetLastError());
+  }
+  return rc;
+}
+
+extern "C" int ogb_paged_prefill_fp8(const void* q, void* out, const void* pool, const float* scales, const int* page_table,
+                                     const int* ctx_len, const int* cu_q, const int* tile_seq, const int* tile_q0, int num_tiles,
+                                     int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride,
+                                     int o_stride, float scale, int* status, void* stream) {
+  if (num_tiles <= 0) return 0;
+  if (d != kD || hkv <= 0 || hq % hkv != 0 || (q_stride % 8) != 0 || (o_stride % 2) != 0 || scales == nullptr) return -3;
+  CUtensorMap map;
+  int rc = get_fp8_tmap(pool, num_pages, hkv, &map);
+  if (rc != 0) return rc;
+  AttnParams p{};
+  fill_params(p, q, out, scales, page_table, ctx_len, num_seqs, max_pages, num_pages, hq, hkv, q_stride, o_stride, scale, status);
+  p.cu_q = cu_q; p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.num_tiles = num_tiles;
+  static bool attr_set = false;
+  if (!attr_set) {
+    OGB_CUDA_CHECK(cudaFuncSetAttribute(paged_prefill_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPreSmem));
+    attr_set = true;
+  }
+  paged_prefill_fp8_kernel<<<dim3(num_tiles, hq), kAttnThreads, kPreSmem, static_cast<cudaStream_t>(stream)>>>(map, p);
+  return static_cast<int>(cudaGetLastError());
+}

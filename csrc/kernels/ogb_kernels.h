@@ -44,6 +44,16 @@ int ogb_paged_decode_bf16(const void* q, void* out, const void* pool, const int*
                           int o_stride, float scale, int num_splits, float* part_o, float* part_ml, int window,
                           int* status, void* stream);
 
+// Same over e4m3 pages [pages, hkv, 2, 16, 128] uint8 with scales [pages, hkv, 2] fp32 (head_dim 128 only).
+int ogb_paged_decode_fp8(const void* q, void* out, const void* pool, const float* scales, const int* page_table,
+                         const int* ctx_len, int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d,
+                         int q_stride, int o_stride, float scale, int num_splits, float* part_o, float* part_ml, int* status,
+                         void* stream);
+int ogb_paged_prefill_fp8(const void* q, void* out, const void* pool, const float* scales, const int* page_table,
+                          const int* ctx_len, const int* cu_q, const int* tile_seq, const int* tile_q0, int num_tiles,
+                          int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride, int o_stride,
+                          float scale, int* status, void* stream);
+
 // Sampling.  logits [rows, vocab] bf16 (ld = row stride).  out_tokens int32 [rows].
 int ogb_argmax_bf16(const void* logits, int* out_tokens, int rows, int vocab, int ld, void* stream);
 // Fused temperature -> top-k -> top-p -> min-p -> inverse-CDF draw (u in [0,1) per row).

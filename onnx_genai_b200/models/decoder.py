@@ -326,12 +326,13 @@ class DecoderModel:
                                kv_scales=kv.scales[li] if kv.scales is not None else None)
             if nd > 0:
                 ops.paged_decode(qkv[:nd], attn[:nd], pool, si.page_table[:nd], si.ctx_len[:nd], self.hq, self.hkv,
-                                 self.d, self.scale, self.decode_splits, self.part_o, self.part_ml, cfg.sliding_window)
+                                 self.d, self.scale, self.decode_splits, self.part_o, self.part_ml, cfg.sliding_window,
+                                 kv_scales=kv.scales[li] if kv.scales is not None else None)
             if si.num_prefill_seqs > 0:
                 np_ = si.num_prefill_seqs
                 ops.paged_prefill(qkv[nd:], attn[nd:], pool, si.page_table[nd:nd + np_], si.ctx_len[nd:nd + np_],
                                   si.cu_q, si.tile_seq, si.tile_q0, si.num_tiles, self.hq, self.hkv, self.d, self.scale,
-                                  cfg.sliding_window)
+                                  cfg.sliding_window, kv_scales=kv.scales[li] if kv.scales is not None else None)
             if lw.quant:
                 pending = lw.quant["o"](attn, out=self.partial[:t])
                 self._norm(x, lw.ln2, pending, h)

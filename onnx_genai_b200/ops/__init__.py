@@ -290,11 +290,20 @@ def prefill_tiles(q_lens, block_m=64):
 
 @_timed("paged_prefill")
 def paged_prefill(q, out, pool, page_table, ctx_len, cu_q, tile_seq, tile_q0, num_tiles, hq, hkv, d, scale=None,
-                  window=0):
-    """Causal varlen GQA over paged KV for chunks of new tokens.  q: packed qkv rows (first hq*d cols)."""
+                  window=0, kv_scales=None):
+    """Causal varlen GQA over paged KV for chunks of new tokens.  q: packed qkv rows (first hq*d cols).
+    ``kv_scales`` selects the e4m3 page kernels."""
     scale = scale or 1.0 / math.sqrt(d)
     if not q.is_cuda:
-        out.copy_(reference.paged_attention(q, pool, page_table, ctx_len, cu_q, hq, hkv, d, scale, window))
+        out.copy_(reference.paged_attention(q, pool, page_table, ctx_len, cu_q, hq, hkv, d, scale, window, kv_scales))
+        return out
+    if kv_scales is not None:
+        rc = _native.load().ogb_paged_prefill_fp8(
+            q.data_ptr(), out.data_ptr(), pool.data_ptr(), kv_scales.data_ptr(), page_table.data_ptr(), ctx_len.data_ptr(),
+            cu_q.data_ptr(), tile_seq.data_ptr(), tile_q0.data_ptr(), int(num_tiles), ctx_len.numel(), page_table.shape[1],
+            pool.shape[0], hq, hkv, d, q.stride(0), out.stride(0), float(scale), status_word().data_ptr(), _stream())
+        _native.check(rc, "ogb_paged_prefill_fp8")
+        launch_counts["paged_prefill_fp8"] += 1
         return out
     rc = _native.load().ogb_paged_prefill_bf16(
         q.data_ptr(), out.data_ptr(), pool.data_ptr(), page_table.data_ptr(), ctx_len.data_ptr(), cu_q.data_ptr(),
@@ -307,17 +316,26 @@ def paged_prefill(q, out, pool, page_table, ctx_len, cu_q, tile_seq, tile_q0, nu
 
 @_timed("paged_decode")
 def paged_decode(q, out, pool, page_table, ctx_len, hq, hkv, d, scale=None, num_splits=1, part_o=None, part_ml=None,
-                 window=0):
-    """One query token per sequence (row s of q) over paged KV; ctx_len[s] <= 0 marks an idle row."""
+                 window=0, kv_scales=None):
+    """One query token per sequence (row s of q) over paged KV; ctx_len[s] <= 0 marks an idle row.
+    ``kv_scales`` selects the e4m3 page kernels."""
     scale = scale or 1.0 / math.sqrt(d)
     n = ctx_len.numel()
     if not q.is_cuda:
         cu = torch.arange(n + 1, dtype=torch.int32)
-        out[:n].copy_(reference.paged_attention(q[:n], pool, page_table, ctx_len, cu, hq, hkv, d, scale, window))
+        out[:n].copy_(reference.paged_attention(q[:n], pool, page_table, ctx_len, cu, hq, hkv, d, scale, window, kv_scales))
         return out
     if num_splits > 1 and part_o is None:
         part_o = torch.empty(n * hq * num_splits * d, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(n * hq * num_splits * 2, dtype=torch.float32, device=q.device)
+    if kv_scales is not None:
+        rc = _native.load().ogb_paged_decode_fp8(
+            q.data_ptr(), out.data_ptr(), pool.data_ptr(), kv_scales.data_ptr(), page_table.data_ptr(), ctx_len.data_ptr(), n,
+            page_table.shape[1], pool.shape[0], hq, hkv, d, q.stride(0), out.stride(0), float(scale), int(num_splits),
+            _ptr(part_o), _ptr(part_ml), status_word().data_ptr(), _stream())
+        _native.check(rc, "ogb_paged_decode_fp8")
+        launch_counts["paged_decode_fp8"] += 1
+        return out
     rc = _native.load().ogb_paged_decode_bf16(
         q.data_ptr(), out.data_ptr(), pool.data_ptr(), page_table.data_ptr(), ctx_len.data_ptr(), n,
         page_table.shape[1], pool.shape[0], hq, hkv, d, q.stride(0), out.stride(0), float(scale), int(num_splits),

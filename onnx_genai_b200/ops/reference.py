@@ -130,7 +130,10 @@ def paged_attention(q, pool, page_table, ctx_len, cu_q, hq, hkv, d, scale=None, 
         if kv_scales is not None:
             n_pages = (ctx + PAGE - 1) // PAGE
             idx = page_table[s][:n_pages].long()
-            pages = pool[idx].float() * kv_scales[idx][:, :, :, None, None]
+            raw = pool[idx]
+            if raw.dtype == torch.uint8:   # e4m3 bytes
+                raw = raw.view(torch.float8_e4m3fn)
+            pages = raw.float() * kv_scales[idx][:, :, :, None, None]
             k = pages[:, :, 0].permute(1, 0, 2, 3).reshape(hkv, -1, d)[:, :ctx]
             v = pages[:, :, 1].permute(1, 0, 2, 3).reshape(hkv, -1, d)[:, :ctx]
         else:

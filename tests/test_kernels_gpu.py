@@ -307,3 +307,79 @@ def test_moe_experts_grouped_gemm(t, e, k, hidden, inter):
     hi = moe_ops.moe_experts(h, router, packed[e // 2:].contiguous(), down[e // 2:].contiguous(),
                              moe_ops.MoEWorkspace(t, k, e // 2, hidden, inter, DEV), torch.zeros_like(x0), k, True, half, e // 2, False)
     assert _rel_err(lo.float() + hi.float() + x0.float(), want) < 3e-2
+
+
+def _make_paged_fp8(ctx_lens, hkv, d, seed=0):
+    """Random KV quantised to e4m3 per (page, head, K|V) with amax scaling; returns pool bytes, scales, table and the
+    dequantised fp32 values the oracle should see."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    pages_per = [(c + ref.PAGE - 1) // ref.PAGE for c in ctx_lens]
+    total = sum(pages_per) + 2
+    perm = torch.randperm(total, generator=g)
+    table = torch.zeros(len(ctx_lens), max(pages_per), dtype=torch.int32)
+    o = 0
+    for s, n in enumerate(pages_per):
+        table[s, :n] = perm[o:o + n].to(torch.int32)
+        o += n
+    vals = torch.randn(total, hkv, 2, ref.PAGE, d, generator=g) * torch.rand(total, hkv, 2, 1, 1, generator=g) * 2
+    scales = vals.abs().amax(dim=(-1, -2)).clamp_min(1e-6) / 448.0
+    q8 = (vals / scales[..., None, None]).to(torch.float8_e4m3fn)
+    return q8.view(torch.uint8).to(DEV), scales.float().to(DEV), table.to(DEV)
+
+
+def test_paged_attention_fp8_pages():
+    torch.manual_seed(13)
+    hq, hkv, d = 28, 4, 128
+    ctx = [1, 16, 17, 63, 64, 65, 300, 1000]
+    n = len(ctx)
+    pool, scales, table = _make_paged_fp8(ctx, hkv, d)
+    ctx_t = torch.tensor(ctx, dtype=torch.int32, device=DEV)
+    q = torch.randn(n, (hq + 2 * hkv) * d, device=DEV).bfloat16()
+    cu = torch.arange(n + 1, dtype=torch.int32, device=DEV)
+    want = ref.paged_attention(q, pool, table, ctx_t, cu, hq, hkv, d, kv_scales=scales)
+    out = torch.zeros(n, hq * d, device=DEV, dtype=torch.bfloat16)
+    for splits in (1, 4):
+        out.zero_()
+        ops.paged_decode(q, out, pool, table, ctx_t, hq, hkv, d, num_splits=splits, kv_scales=scales)
+        torch.cuda.synchronize()
+        ops.check_status()
+        assert _rel_err(out, want) < 2e-2, splits
+    # chunked prefill over the same pages
+    q_lens = [1, 7, 17, 40, 64, 65, 130, 200]
+    t = sum(q_lens)
+    qp = torch.randn(t, (hq + 2 * hkv) * d, device=DEV).bfloat16()
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    ts, tq = ops.prefill_tiles(q_lens)
+    outp = torch.zeros(t, hq * d, device=DEV, dtype=torch.bfloat16)
+    ops.paged_prefill(qp, outp, pool, table, ctx_t, cu, torch.tensor(ts, dtype=torch.int32, device=DEV),
+                      torch.tensor(tq, dtype=torch.int32, device=DEV), len(ts), hq, hkv, d, kv_scales=scales)
+    torch.cuda.synchronize()
+    ops.check_status()
+    wantp = ref.paged_attention(qp, pool, table, ctx_t, cu, hq, hkv, d, kv_scales=scales)
+    assert _rel_err(outp, wantp) < 2e-2
+
+
+def test_rope_kv_append_fp8_roundtrip():
+    torch.manual_seed(14)
+    hq, hkv, d, pages = 4, 2, 128, 4
+    t = pages * ref.PAGE
+    qkv = torch.randn(t, (hq + 2 * hkv) * d, device=DEV).bfloat16()
+    pos = torch.arange(t, dtype=torch.int32, device=DEV)
+    slots = torch.arange(t, dtype=torch.int32, device=DEV)       # tokens land in order: offset 0 of each page first
+    cs = ref.rope_table(256, d, 1e4, DEV)
+    pool = torch.zeros(pages, hkv, 2, ref.PAGE, d, device=DEV, dtype=torch.uint8)
+    scales = torch.zeros(pages, hkv, 2, device=DEV)
+    want_qkv = qkv.clone()
+    bf_pool = torch.zeros(pages, hkv, 2, ref.PAGE, d, device=DEV, dtype=torch.bfloat16)
+    ref.rope_kv_append(want_qkv, pos, slots, cs, bf_pool, hq, hkv, d)
+    for s0 in range(0, t, ref.PAGE):          # one launch per position inside a page keeps the "first token sets the scale" order
+        for off in range(ref.PAGE):
+            i = s0 + off
+            ops.rope_kv_append(qkv[i:i + 1], pos[i:i + 1], slots[i:i + 1], cs, pool, hq, hkv, d, kv_scales=scales)
+    torch.cuda.synchronize()
+    ops.check_status()
+    deq = pool.view(torch.float8_e4m3fn).float() * scales[..., None, None]
+    clipped = (bf_pool.float().abs() > 448 * scales[..., None, None]).float().mean()
+    assert float(clipped) < 0.02                                   # 2x headroom over the first token's amax
+    err = (deq - bf_pool.float()).abs() / (bf_pool.float().abs() + 0.05 * bf_pool.float().abs().amax())
+    assert float(err[(bf_pool.float().abs() <= 448 * scales[..., None, None])].mean()) < 0.05
