@@ -29,7 +29,7 @@ namespace ogb {
 // prefill: 64 query rows x one head per CTA
 // ------------------------------------------------------------------------------------------
 template <int D>
-__global__ void __launch_bounds__(kAttnThreads) paged_prefill_kernel(const __grid_constant__ CUtensorMap kv_map,
+__global__ void __launch_bounds__(kAttnThreads, 2) paged_prefill_kernel(const __grid_constant__ CUtensorMap kv_map,
                                                                       const AttnParams p) {
   using Cfg = AttnCfg<D, 2, 64>;
   extern __shared__ uint8_t smem_raw[];
@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_prefill_kernel(const __gri
 // decode: one query token per sequence; MMA rows = the G query heads sharing a kv head
 // ------------------------------------------------------------------------------------------
 template <int D>
-__global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const __grid_constant__ CUtensorMap kv_map,
+__global__ void __launch_bounds__(kAttnThreads, 2) paged_decode_kernel(const __grid_constant__ CUtensorMap kv_map,
                                                                      const AttnParams p) {
   using Cfg = AttnCfg<D, 3, 16>;
   extern __shared__ uint8_t smem_raw[];
@@ -463,6 +463,7 @@ static int launch_prefill(const CUtensorMap& map, const AttnParams& p, cudaStrea
   static bool attr_set = false;
   if (!attr_set) {
     OGB_CUDA_CHECK(cudaFuncSetAttribute(paged_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    OGB_CUDA_CHECK(cudaFuncSetAttribute(paged_prefill_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     attr_set = true;
   }
   dim3 grid(p.num_tiles, p.hq);
@@ -475,6 +476,7 @@ static int launch_decode(const CUtensorMap& map, const AttnParams& p, cudaStream
   static bool attr_set = false;
   if (!attr_set) {
     OGB_CUDA_CHECK(cudaFuncSetAttribute(paged_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    OGB_CUDA_CHECK(cudaFuncSetAttribute(paged_decode_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     attr_set = true;
   }
   dim3 grid(p.num_seqs * p.num_splits, p.hkv);

@@ -518,6 +518,7 @@ extern "C" int ogb_paged_decode_fp8(const void* q, void* out, const void* pool, 
   static bool attr_set = false;
   if (!attr_set) {
     OGB_CUDA_CHECK(cudaFuncSetAttribute(paged_decode_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem));
+    OGB_CUDA_CHECK(cudaFuncSetAttribute(paged_decode_fp8_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     attr_set = true;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -545,6 +546,7 @@ extern "C" int ogb_paged_prefill_fp8(const void* q, void* out, const void* pool,
   static bool attr_set = false;
   if (!attr_set) {
     OGB_CUDA_CHECK(cudaFuncSetAttribute(paged_prefill_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPreSmem));
+    OGB_CUDA_CHECK(cudaFuncSetAttribute(paged_prefill_fp8_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     attr_set = true;
   }
   paged_prefill_fp8_kernel<<<dim3(num_tiles, hq), kAttnThreads, kPreSmem, static_cast<cudaStream_t>(stream)>>>(map, p);

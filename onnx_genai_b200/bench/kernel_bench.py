@@ -164,11 +164,68 @@ def bench_misc(timer, pk):
     return rows
 
 
+def ncu_case(name: str, iters: int = 3):
+    """Small single-kernel workloads for `ncu` captures: inputs larger than L2 where DRAM figures matter,
+    a few hundred MB on the device at most, `iters` launches of the one kernel of interest."""
+    hq, hkv, d = 28, 4, 128
+    if name in ("gemm_swiglu", "gemm_down", "gemm_qkv"):
+        m = 1280
+        n, k, epi = {"gemm_swiglu": (37888, 3584, "swiglu"), "gemm_down": (3584, 18944, "residual"), "gemm_qkv": (4608, 3584, "none")}[name]
+        a = (torch.randn(m, k, device="cuda") * 0.1).bfloat16()
+        w = (torch.randn(n, k, device="cuda") * 0.02).bfloat16()
+        out = torch.empty(m, n // 2 if epi == "swiglu" else n, device="cuda", dtype=torch.bfloat16)
+        res = torch.randn(m, n, device="cuda").bfloat16() if epi == "residual" else None
+        for _ in range(iters):
+            if epi == "swiglu":
+                ops.gemm(a, w, epilogue="swiglu", swiglu_half=128, out=out)
+            elif epi == "residual":
+                ops.gemm(a, w, residual=res, epilogue="residual", out=out)
+            else:
+                ops.gemm(a, w, out=out)
+    elif name == "decode":
+        n, ctx = 256, 1200
+        pages_per = (ctx + 15) // 16
+        pool = (torch.randn(n * pages_per, hkv, 2, 16, d, device="cuda") * 0.5).bfloat16()
+        table = torch.randperm(n * pages_per, device="cuda").to(torch.int32).view(n, pages_per)
+        ctx_t = torch.full((n,), ctx, dtype=torch.int32, device="cuda")
+        q = torch.randn(n, (hq + 2 * hkv) * d, device="cuda").bfloat16()
+        out = torch.empty(n, hq * d, device="cuda", dtype=torch.bfloat16)
+        for _ in range(iters):
+            ops.paged_decode(q, out, pool, table, ctx_t, hq, hkv, d)
+    elif name == "prefill":
+        nseq, q_len = 4, 1024
+        pages_per = q_len // 16
+        pool = (torch.randn(nseq * pages_per, hkv, 2, 16, d, device="cuda") * 0.5).bfloat16()
+        table = torch.randperm(nseq * pages_per, device="cuda").to(torch.int32).view(nseq, pages_per)
+        ctx_t = torch.full((nseq,), q_len, dtype=torch.int32, device="cuda")
+        q = torch.randn(nseq * q_len, (hq + 2 * hkv) * d, device="cuda").bfloat16()
+        out = torch.empty(nseq * q_len, hq * d, device="cuda", dtype=torch.bfloat16)
+        cu = torch.arange(0, nseq * q_len + 1, q_len, dtype=torch.int32, device="cuda")
+        ts, tq = ops.prefill_tiles([q_len] * nseq)
+        tsd, tqd = torch.tensor(ts, dtype=torch.int32, device="cuda"), torch.tensor(tq, dtype=torch.int32, device="cuda")
+        for _ in range(iters):
+            ops.paged_prefill(q, out, pool, table, ctx_t, cu, tsd, tqd, len(ts), hq, hkv, d)
+    elif name == "sample":
+        logits = torch.randn(256, 152064, device="cuda").bfloat16()
+        f = lambda v: torch.full((256,), v, device="cuda")
+        work = torch.empty(256 * 152064, dtype=torch.int32, device="cuda")
+        for _ in range(iters):
+            ops.sample(logits, f(0.7), torch.zeros(256, dtype=torch.int32, device="cuda"), f(0.9), f(0.0), torch.rand(256, device="cuda"), work=work)
+    else:
+        raise SystemExit(f"unknown ncu case {name!r}")
+    torch.cuda.synchronize()
+    ops.check_status()
+    print("ncu case", name, "ok")
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--ncu-case", default="", help="run one small single-kernel workload (for ncu) and exit")
     ap.add_argument("--what", default="gemm,attn,misc")
     ap.add_argument("--json", default="")
     args = ap.parse_args()
+    if args.ncu_case:
+        return ncu_case(args.ncu_case)
     pk = peaks()
     timer = Timer()
     res = {"peaks": pk}
