@@ -105,6 +105,75 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(__nv_bfloat16* x,
   }
 }
 
+// One warp per row, every 16-byte vector of the row held in registers (hidden <= 4096): all loads of
+// a row are issued back to back, the statistics never touch shared memory, and a step's ~1300 rows
+// fit in a single wave of CTAs.
+constexpr int kNormWarpMaxVec = 16;
+
+__global__ void __launch_bounds__(128) rmsnorm_warp_kernel(__nv_bfloat16* x, const __nv_bfloat16* __restrict__ delta,
+                                                            const __nv_bfloat16* __restrict__ weight,
+                                                            __nv_bfloat16* __restrict__ out, int rows, int hidden, int ldx,
+                                                            int ldo, float eps) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  __nv_bfloat16* xr = x + static_cast<size_t>(row) * ldx;
+  const int nvec = hidden / 8;
+  uint4 v[kNormWarpMaxVec], wq[kNormWarpMaxVec];
+#pragma unroll
+  for (int c = 0; c < kNormWarpMaxVec; ++c) {
+    const int i = lane + 32 * c;
+    if (i < nvec) {
+      v[c] = reinterpret_cast<const uint4*>(xr)[i];
+      wq[c] = __ldg(reinterpret_cast<const uint4*>(weight) + i);   // in flight together with the row itself
+    }
+  }
+  if (delta != nullptr) {
+    const __nv_bfloat16* dr = delta + static_cast<size_t>(row) * hidden;
+#pragma unroll
+    for (int c = 0; c < kNormWarpMaxVec; ++c) {
+      const int i = lane + 32 * c;
+      if (i < nvec) {
+        const uint4 d = reinterpret_cast<const uint4*>(dr)[i];
+        float2 a, b;
+        a = unpack_bf16(v[c].x); b = unpack_bf16(d.x); v[c].x = pack_bf16(a.x + b.x, a.y + b.y);
+        a = unpack_bf16(v[c].y); b = unpack_bf16(d.y); v[c].y = pack_bf16(a.x + b.x, a.y + b.y);
+        a = unpack_bf16(v[c].z); b = unpack_bf16(d.z); v[c].z = pack_bf16(a.x + b.x, a.y + b.y);
+        a = unpack_bf16(v[c].w); b = unpack_bf16(d.w); v[c].w = pack_bf16(a.x + b.x, a.y + b.y);
+        reinterpret_cast<uint4*>(xr)[i] = v[c];   // the residual stream keeps the bf16-rounded sum
+      }
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < kNormWarpMaxVec; ++c) {
+    if (lane + 32 * c < nvec) {
+      float2 f;
+      f = unpack_bf16(v[c].x); ss += f.x * f.x + f.y * f.y;
+      f = unpack_bf16(v[c].y); ss += f.x * f.x + f.y * f.y;
+      f = unpack_bf16(v[c].z); ss += f.x * f.x + f.y * f.y;
+      f = unpack_bf16(v[c].w); ss += f.x * f.x + f.y * f.y;
+    }
+  }
+  ss = warp_sum(ss);
+  const float inv = rsqrtf(ss / static_cast<float>(hidden) + eps);
+  __nv_bfloat16* orow = out + static_cast<size_t>(row) * ldo;
+#pragma unroll
+  for (int c = 0; c < kNormWarpMaxVec; ++c) {
+    const int i = lane + 32 * c;
+    if (i < nvec) {
+      const uint4 wv = wq[c];
+      float2 a, w;
+      uint4 o4;
+      a = unpack_bf16(v[c].x); w = unpack_bf16(wv.x); o4.x = pack_bf16(a.x * inv * w.x, a.y * inv * w.y);
+      a = unpack_bf16(v[c].y); w = unpack_bf16(wv.y); o4.y = pack_bf16(a.x * inv * w.x, a.y * inv * w.y);
+      a = unpack_bf16(v[c].z); w = unpack_bf16(wv.z); o4.z = pack_bf16(a.x * inv * w.x, a.y * inv * w.y);
+      a = unpack_bf16(v[c].w); w = unpack_bf16(wv.w); o4.w = pack_bf16(a.x * inv * w.x, a.y * inv * w.y);
+      reinterpret_cast<uint4*>(orow)[i] = o4;
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // out[r, j] = silu(gate_up[r, j]) * gate_up[r, inter + j]   (unfused fallback of the GEMM epilogue)
 // ------------------------------------------------------------------------------------------
@@ -242,6 +311,12 @@ extern "C" int ogb_rmsnorm_bf16(void* x, const void* delta, const void* weight, 
                                 int ldo, float eps, void* stream) {
   if (rows <= 0) return 0;
   if (hidden % 8 || ldx % 8 || ldo % 8) return -3;
+  if (hidden / 8 <= 32 * kNormWarpMaxVec) {
+    rmsnorm_warp_kernel<<<(rows + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<__nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(weight),
+        static_cast<__nv_bfloat16*>(out), rows, hidden, ldx, ldo, eps);
+    return static_cast<int>(cudaGetLastError());
+  }
   rmsnorm_kernel<<<rows, kNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(weight),
       static_cast<__nv_bfloat16*>(out), hidden, ldx, ldo, eps);

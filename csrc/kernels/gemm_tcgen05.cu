@@ -42,14 +42,17 @@ constexpr int kGemmThreadsScatter = 224;  // + one warp that publishes finished 
 
 enum GemmEpilogue : int { kEpiNone = 0, kEpiResidual = 1, kEpiSwiGLU = 2, kEpiScatter = 3 };
 
+constexpr int kStagingPitch = 272;                       // bytes per staged row: 128 bf16 + 16 bytes of padding
+constexpr int kStagingWarpBytes = 32 * kStagingPitch;    // one epilogue warp: 32 rows
+
 template <int BN>
 struct GemmCfg {
   static constexpr int kStageA = kBM * kBK * 2;
   static constexpr int kStageB = BN * kBK * 2;
   static constexpr int kStage = kStageA + kStageB;
-  static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 192 ? 5 : (BN >= 128 ? 6 : 8));
+  static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 192 ? 4 : (BN >= 128 ? 6 : 8));
   static constexpr int kTmemCols = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));  // power of two
-  static constexpr int kSmemBytes = kStages * kStage + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kStages * kStage + 256 /*barriers*/ + 4 * kStagingWarpBytes /*epilogue staging*/;
 };
 
 template <int BN, int EPI>
@@ -60,9 +63,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                          int* status, const TpScatter* __restrict__ sc, const int* __restrict__ group_tab,
                          const int* __restrict__ group_mtiles) {
   using Cfg = GemmCfg<BN>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // the kernel declares no static shared memory, so the dynamic window starts at the 1024-byte aligned
+  // base the 128-byte swizzle needs
+  extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStage);
+  uint8_t* staging = smem + Cfg::kStages * Cfg::kStage + 256;
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + Cfg::kStages;
   uint64_t* tmem_full = bars + 2 * Cfg::kStages;
@@ -177,40 +182,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      if constexpr (EPI == kEpiSwiGLU) {
-        constexpr int HALF = BN / 2;
-        const int out_n = N / 2;
-#pragma unroll 1
-        for (int c = 0; c < HALF / 32; ++c) {
-          uint32_t g[32], u[32];
-          tmem_ld_32x32(t_row + c * 32, g);
-          tmem_ld_32x32(t_row + HALF + c * 32, u);
-          tmem_ld_wait();
-          const int col = n_tile * HALF + c * 32;
-          if (row < m_end && col < out_n) {
-            uint32_t o[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
-              float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
-              float s0 = g0 / (1.f + __expf(-g0)) * u0;
-              float s1 = g1 / (1.f + __expf(-g1)) * u1;
-              o[j] = pack_bf16(s0, s1);
-            }
-            __nv_bfloat16* dst = C + static_cast<size_t>(row) * ldc + col;
-            if (col + 32 <= out_n) {
-#pragma unroll
-              for (int v = 0; v < 4; ++v)
-                reinterpret_cast<uint4*>(dst)[v] = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
-            } else {
-              for (int j = 0; j < 32 && col + j < out_n; ++j) {
-                float2 f = unpack_bf16(o[j >> 1]);
-                dst[j] = __float2bfloat16((j & 1) ? f.y : f.x);
-              }
-            }
-          }
-        }
-      } else {
+      if (C_f32 != nullptr) {
+        // fp32 output (diagnostics / fp32 logits): direct row-per-thread stores
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
@@ -218,69 +191,135 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           tmem_ld_wait();
           const int col = n0 + c * 32;
           if (row < m_end && col < N) {
-            const bool full = (col + 32 <= N);
-            float v[32];
+            float* dst = C_f32 + static_cast<size_t>(row) * ldc + col;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-            if (bias != nullptr) {
-              if (full) {
-#pragma unroll
-                for (int j4 = 0; j4 < 4; ++j4) {
-                  uint4 b = __ldg(reinterpret_cast<const uint4*>(bias + col) + j4);
-                  float2 f;
-                  f = unpack_bf16(b.x); v[8 * j4 + 0] += f.x; v[8 * j4 + 1] += f.y;
-                  f = unpack_bf16(b.y); v[8 * j4 + 2] += f.x; v[8 * j4 + 3] += f.y;
-                  f = unpack_bf16(b.z); v[8 * j4 + 4] += f.x; v[8 * j4 + 5] += f.y;
-                  f = unpack_bf16(b.w); v[8 * j4 + 6] += f.x; v[8 * j4 + 7] += f.y;
-                }
-              } else {
-                for (int j = 0; j < 32 && col + j < N; ++j) v[j] += __bfloat162float(bias[col + j]);
-              }
-            }
-            if constexpr (EPI == kEpiResidual) {
-              const __nv_bfloat16* rs = residual + static_cast<size_t>(row) * ldr + col;
-              if (full) {
-#pragma unroll
-                for (int j4 = 0; j4 < 4; ++j4) {
-                  uint4 b = reinterpret_cast<const uint4*>(rs)[j4];
-                  float2 f;
-                  f = unpack_bf16(b.x); v[8 * j4 + 0] += f.x; v[8 * j4 + 1] += f.y;
-                  f = unpack_bf16(b.y); v[8 * j4 + 2] += f.x; v[8 * j4 + 3] += f.y;
-                  f = unpack_bf16(b.z); v[8 * j4 + 4] += f.x; v[8 * j4 + 5] += f.y;
-                  f = unpack_bf16(b.w); v[8 * j4 + 6] += f.x; v[8 * j4 + 7] += f.y;
-                }
-              } else {
-                for (int j = 0; j < 32 && col + j < N; ++j) v[j] += __bfloat162float(rs[j]);
-              }
-            }
-            if (C_f32 != nullptr) {
-              float* dst = C_f32 + static_cast<size_t>(row) * ldc + col;
-              if (full) {
-#pragma unroll
-                for (int j4 = 0; j4 < 8; ++j4)
-                  reinterpret_cast<float4*>(dst)[j4] = make_float4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]);
-              } else {
-                for (int j = 0; j < 32 && col + j < N; ++j) dst[j] = v[j];
-              }
-            } else {
-              __nv_bfloat16* dst;
-              if constexpr (EPI == kEpiScatter) {
-                // the partial product stays in this rank's own buffer; the owner of the row pulls it
-                dst = sc->staging[sc->rank] + static_cast<size_t>(row) * N + col;
-              } else {
-                dst = C + static_cast<size_t>(row) * ldc + col;
-              }
-              if (full) {
-#pragma unroll
-                for (int j4 = 0; j4 < 4; ++j4)
-                  reinterpret_cast<uint4*>(dst)[j4] =
-                      make_uint4(pack_bf16(v[8 * j4], v[8 * j4 + 1]), pack_bf16(v[8 * j4 + 2], v[8 * j4 + 3]),
-                                 pack_bf16(v[8 * j4 + 4], v[8 * j4 + 5]), pack_bf16(v[8 * j4 + 6], v[8 * j4 + 7]));
-              } else {
-                for (int j = 0; j < 32 && col + j < N; ++j) dst[j] = __float2bfloat16(v[j]);
+            for (int j = 0; j < 32; ++j) {
+              if (col + j < N) {
+                float v = __uint_as_float(r[j]);
+                if (bias != nullptr) v += __bfloat162float(bias[col + j]);
+                if constexpr (EPI == kEpiResidual) v += __bfloat162float(residual[static_cast<size_t>(row) * ldr + col + j]);
+                dst[j] = v;
               }
             }
           }
+        }
+      } else {
+        // bf16 output.  Phase 1 (thread = row): TMEM -> registers -> epilogue math -> bf16 into this warp's
+        // staging slab (32 rows x up to 128 columns, 272-byte pitch: conflict-free for 16-byte accesses).
+        // Phase 2 (lanes along the row): 16-byte vectors are read back so that a warp instruction covers
+        // whole 256-byte row segments; residual reads and output stores are therefore coalesced.
+        constexpr int OUTW = (EPI == kEpiSwiGLU) ? BN / 2 : BN;      // output columns this tile produces
+        const int out_cols = (EPI == kEpiSwiGLU) ? N / 2 : N;        // output matrix width
+        const int out_col0 = (EPI == kEpiSwiGLU) ? n_tile * (BN / 2) : n0;
+        uint8_t* stg = staging + (warp - 2) * kStagingWarpBytes;
+#pragma unroll 1
+        for (int cb = 0; cb < OUTW; cb += 128) {
+          const int cw = (OUTW - cb < 128) ? OUTW - cb : 128;         // 128, 64 or 32
+#pragma unroll 1
+          for (int c = 0; c < cw / 32; ++c) {
+            uint32_t o[16];
+            if constexpr (EPI == kEpiSwiGLU) {
+              uint32_t g[32], u[32];
+              tmem_ld_32x32(t_row + cb + c * 32, g);
+              tmem_ld_32x32(t_row + BN / 2 + cb + c * 32, u);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
+                const float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
+                o[j] = pack_bf16(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+              }
+            } else {
+              uint32_t r[32];
+              tmem_ld_32x32(t_row + cb + c * 32, r);
+              tmem_ld_wait();
+              const int col = n0 + cb + c * 32;
+              if (bias != nullptr && col < N) {
+                if (col + 32 <= N) {
+#pragma unroll
+                  for (int j4 = 0; j4 < 4; ++j4) {
+                    const uint4 bv = __ldg(reinterpret_cast<const uint4*>(bias + col) + j4);
+                    float2 f;
+                    f = unpack_bf16(bv.x); r[8 * j4 + 0] = __float_as_uint(__uint_as_float(r[8 * j4 + 0]) + f.x); r[8 * j4 + 1] = __float_as_uint(__uint_as_float(r[8 * j4 + 1]) + f.y);
+                    f = unpack_bf16(bv.y); r[8 * j4 + 2] = __float_as_uint(__uint_as_float(r[8 * j4 + 2]) + f.x); r[8 * j4 + 3] = __float_as_uint(__uint_as_float(r[8 * j4 + 3]) + f.y);
+                    f = unpack_bf16(bv.z); r[8 * j4 + 4] = __float_as_uint(__uint_as_float(r[8 * j4 + 4]) + f.x); r[8 * j4 + 5] = __float_as_uint(__uint_as_float(r[8 * j4 + 5]) + f.y);
+                    f = unpack_bf16(bv.w); r[8 * j4 + 6] = __float_as_uint(__uint_as_float(r[8 * j4 + 6]) + f.x); r[8 * j4 + 7] = __float_as_uint(__uint_as_float(r[8 * j4 + 7]) + f.y);
+                  }
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j)
+                    if (col + j < N) r[j] = __float_as_uint(__uint_as_float(r[j]) + __bfloat162float(bias[col + j]));
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 16; ++j) o[j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+            }
+            uint4* srow = reinterpret_cast<uint4*>(stg + lane * kStagingPitch + c * 64);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) srow[v] = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+          }
+          __syncwarp();
+          const int lanes_per_row = cw / 8;                 // 16, 8 or 4 sixteen-byte vectors per row segment
+          const int rows_per_pass = 32 / lanes_per_row;
+          const int ch = lane % lanes_per_row;
+          const int gcol = out_col0 + cb + ch * 8;
+          // the residual vectors of a batch of passes are requested together (memory-level parallelism:
+          // one L2 round trip per batch instead of one per row) before any of them is consumed
+          constexpr int kBatch = 8;
+#pragma unroll 1
+          for (int rb = 0; rb < 32; rb += rows_per_pass * kBatch) {
+            uint4 resv[kBatch];
+            if constexpr (EPI == kEpiResidual) {
+#pragma unroll
+              for (int t = 0; t < kBatch; ++t) {
+                const int r_loc = rb + t * rows_per_pass + lane / lanes_per_row;
+                const int grow = m0 + q * 32 + r_loc;
+                resv[t] = make_uint4(0, 0, 0, 0);
+                if (r_loc < 32 && grow < m_end && gcol + 8 <= out_cols)
+                  resv[t] = *reinterpret_cast<const uint4*>(residual + static_cast<size_t>(grow) * ldr + gcol);
+              }
+            }
+#pragma unroll
+            for (int t = 0; t < kBatch; ++t) {
+              const int r_loc = rb + t * rows_per_pass + lane / lanes_per_row;
+              const int grow = m0 + q * 32 + r_loc;
+              if (r_loc < 32 && grow < m_end && gcol < out_cols) {
+                uint4 v = *reinterpret_cast<const uint4*>(stg + r_loc * kStagingPitch + ch * 16);
+                __nv_bfloat16* dst;
+                if constexpr (EPI == kEpiScatter) {
+                  // the partial product stays in this rank's own buffer; the owner of the row pulls it
+                  dst = sc->staging[sc->rank] + static_cast<size_t>(grow) * N + gcol;
+                } else {
+                  dst = C + static_cast<size_t>(grow) * ldc + gcol;
+                }
+                const bool full = (gcol + 8 <= out_cols);
+                if constexpr (EPI == kEpiResidual) {
+                  if (full) {
+                    const uint4 rv = resv[t];
+                    float2 a, b2;
+                    a = unpack_bf16(v.x); b2 = unpack_bf16(rv.x); v.x = pack_bf16(a.x + b2.x, a.y + b2.y);
+                    a = unpack_bf16(v.y); b2 = unpack_bf16(rv.y); v.y = pack_bf16(a.x + b2.x, a.y + b2.y);
+                    a = unpack_bf16(v.z); b2 = unpack_bf16(rv.z); v.z = pack_bf16(a.x + b2.x, a.y + b2.y);
+                    a = unpack_bf16(v.w); b2 = unpack_bf16(rv.w); v.w = pack_bf16(a.x + b2.x, a.y + b2.y);
+                    *reinterpret_cast<uint4*>(dst) = v;
+                  } else {
+                    const __nv_bfloat16* rs = residual + static_cast<size_t>(grow) * ldr + gcol;
+                    const __nv_bfloat16* pv = reinterpret_cast<const __nv_bfloat16*>(&v);
+                    for (int j = 0; j < 8 && gcol + j < out_cols; ++j)
+                      dst[j] = __float2bfloat16(__bfloat162float(pv[j]) + __bfloat162float(rs[j]));
+                  }
+                } else {
+                  if (full) {
+                    *reinterpret_cast<uint4*>(dst) = v;
+                  } else {
+                    const __nv_bfloat16* pv = reinterpret_cast<const __nv_bfloat16*>(&v);
+                    for (int j = 0; j < 8 && gcol + j < out_cols; ++j) dst[j] = pv[j];
+                  }
+                }
+              }
+            }
+          }
+          __syncwarp();
         }
       }
       if constexpr (EPI == kEpiScatter) {
