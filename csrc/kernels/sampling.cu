@@ -266,6 +266,227 @@ sample_kernel(const __nv_bfloat16* __restrict__ logits, int* __restrict__ out, c
   if (threadIdx.x == 0) out[rowi] = (sh_pick >= 0) ? sh_pick : best.i;
 }
 
+// ------------------------------------------------------------------------------------------
+// Vectorised variant of sample_kernel: identical arithmetic and results, but every pass over the
+// row uses 16-byte loads (8 logits or 4 weights per thread per iteration), so a pass costs ~4x fewer
+// dependent memory round trips.  Requires vocab % 8 == 0, ld % 8 == 0 and 16-byte aligned rows.
+// ------------------------------------------------------------------------------------------
+template <bool BY_MASS>
+OGB_DEVICE uint32_t radix_threshold_vec(const uint32_t* __restrict__ w, int vocab, uint32_t floor_w,
+                                        unsigned long long target, RadixScratch& sc) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint32_t prefix = 0;
+  unsigned long long above = 0;
+  const int nvec = vocab / 4;
+  const int iters = (nvec + kSampleThreads - 1) / kSampleThreads;
+  for (int shift = 30 - kDigitBits; shift >= 0; shift -= kDigitBits) {
+    for (int i = threadIdx.x; i < (kSampleThreads / 32) * kBuckets; i += blockDim.x) {
+      (&sc.lo[0][0])[i] = 0u;
+      (&sc.hi[0][0])[i] = 0u;
+    }
+    __syncthreads();
+    const uint32_t hi_mask = ~((1u << (shift + kDigitBits)) - 1u);
+    for (int it = 0; it < iters; ++it) {
+      const int vi = it * kSampleThreads + threadIdx.x;
+      uint4 q = make_uint4(0, 0, 0, 0);
+      if (vi < nvec) q = reinterpret_cast<const uint4*>(w)[vi];
+      const uint32_t vals[4] = {q.x, q.y, q.z, q.w};
+      bool parts[4];
+      bool any = false;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        parts[e] = (vi < nvec) && vals[e] >= floor_w && (vals[e] & hi_mask) == prefix;
+        any |= parts[e];
+      }
+      if (!__any_sync(0xffffffffu, any)) continue;   // nothing in this stripe belongs to the current prefix
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const uint32_t v = vals[e];
+        const bool part = parts[e];
+        const int bucket = part ? static_cast<int>((v >> shift) & (kBuckets - 1)) : kBuckets;
+        const unsigned long long val = part ? (BY_MASS ? static_cast<unsigned long long>(v) : 1ull) : 0ull;
+        const int b0 = __shfl_sync(0xffffffffu, bucket, 0);
+        if (__all_sync(0xffffffffu, bucket == b0)) {
+          if (b0 != kBuckets) {
+            const unsigned long long tot = warp_sum_u64(val);
+            if (lane == 0) {
+              const uint32_t add = static_cast<uint32_t>(tot);
+              const uint32_t old = sc.lo[warp][b0];
+              sc.lo[warp][b0] = old + add;
+              sc.hi[warp][b0] += static_cast<uint32_t>(tot >> 32) + ((old + add < old) ? 1u : 0u);
+            }
+          }
+        } else if (part) {
+          const uint32_t add = static_cast<uint32_t>(val);
+          const uint32_t old = atomicAdd(&sc.lo[warp][bucket], add);
+          if (old + add < old) atomicAdd(&sc.hi[warp][bucket], 1u);
+        }
+        __syncwarp();
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < kBuckets) {
+      unsigned long long t = 0;
+      for (int wi = 0; wi < kSampleThreads / 32; ++wi)
+        t += (static_cast<unsigned long long>(sc.hi[wi][threadIdx.x]) << 32) + sc.lo[wi][threadIdx.x];
+      sc.total[threadIdx.x] = t;
+    }
+    __syncthreads();
+    int chosen = 0;
+    unsigned long long run = above;
+    for (int b = kBuckets - 1; b >= 0; --b) {
+      const unsigned long long h = sc.total[b];
+      if (run + h >= target) { chosen = b; break; }
+      run += h;
+    }
+    above = run;
+    prefix |= static_cast<uint32_t>(chosen) << shift;
+    __syncthreads();
+  }
+  return prefix < floor_w ? floor_w : prefix;
+}
+
+__global__ void __launch_bounds__(kSampleThreads)
+sample_kernel_vec(const __nv_bfloat16* __restrict__ logits, int* __restrict__ out, const float* __restrict__ temperature,
+                  const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
+                  const float* __restrict__ uniform, uint32_t* __restrict__ work, int vocab, int ld) {
+  __shared__ ArgMax sh_arg[32];
+  __shared__ unsigned long long sh_sum[32];
+  __shared__ RadixScratch sc;
+  __shared__ unsigned long long sh_scan[kSampleThreads / 32];
+  __shared__ int sh_pick;
+  const int rowi = blockIdx.x;
+  const __nv_bfloat16* row = logits + static_cast<size_t>(rowi) * ld;
+  // argmax with 8 logits per load; within a thread indices ascend, so ">" keeps the lowest index on ties
+  ArgMax best{-INFINITY, 0x7fffffff};
+  const int nvec8 = vocab / 8;
+  for (int vi = threadIdx.x; vi < nvec8; vi += blockDim.x) {
+    const uint4 q = reinterpret_cast<const uint4*>(row)[vi];
+    const uint32_t ws[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = unpack_bf16(ws[e]);
+      if (f.x > best.v) { best.v = f.x; best.i = vi * 8 + 2 * e; }
+      if (f.y > best.v) { best.v = f.y; best.i = vi * 8 + 2 * e + 1; }
+    }
+  }
+  best = block_argmax(best, sh_arg);
+  const float temp = temperature[rowi];
+  if (!(temp > 0.f) || best.i == 0x7fffffff) {
+    if (threadIdx.x == 0) out[rowi] = (best.i == 0x7fffffff) ? 0 : best.i;
+    return;
+  }
+  uint32_t* w = work + static_cast<size_t>(rowi) * vocab;
+  const float inv_t = 1.f / temp;
+  unsigned long long local = 0;
+  for (int vi = threadIdx.x; vi < nvec8; vi += blockDim.x) {
+    const uint4 q = reinterpret_cast<const uint4*>(row)[vi];
+    const uint32_t ws[4] = {q.x, q.y, q.z, q.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = unpack_bf16(ws[e]);
+      float e0 = __expf((f.x - best.v) * inv_t), e1 = __expf((f.y - best.v) * inv_t);
+      if (!(e0 >= 0.f)) e0 = 0.f;
+      if (!(e1 >= 0.f)) e1 = 0.f;
+      uint32_t q0 = static_cast<uint32_t>(e0 * 1073741824.f + 0.5f), q1 = static_cast<uint32_t>(e1 * 1073741824.f + 0.5f);
+      if (q0 > 1073741823u) q0 = 1073741823u;
+      if (q1 > 1073741823u) q1 = 1073741823u;
+      o[2 * e] = q0;
+      o[2 * e + 1] = q1;
+      local += q0;
+      local += q1;
+    }
+    reinterpret_cast<uint4*>(w)[2 * vi] = make_uint4(o[0], o[1], o[2], o[3]);
+    reinterpret_cast<uint4*>(w)[2 * vi + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+  }
+  __syncthreads();
+  unsigned long long total = block_sum_u64(local, sh_sum);
+  uint32_t thr = 1;
+  const int nvec4 = vocab / 4;
+  const int k = top_k[rowi];
+  if (k > 0 && k < vocab) {
+    thr = radix_threshold_vec<false>(w, vocab, thr, static_cast<unsigned long long>(k), sc);
+    unsigned long long s = 0;
+    for (int vi = threadIdx.x; vi < nvec4; vi += blockDim.x) {
+      const uint4 q = reinterpret_cast<const uint4*>(w)[vi];
+      s += (q.x >= thr ? q.x : 0u);
+      s += (q.y >= thr ? q.y : 0u);
+      s += (q.z >= thr ? q.z : 0u);
+      s += (q.w >= thr ? q.w : 0u);
+    }
+    total = block_sum_u64(s, sh_sum);
+  }
+  const float p = top_p[rowi];
+  if (p > 0.f && p < 1.f) {
+    unsigned long long target = static_cast<unsigned long long>(static_cast<double>(total) * static_cast<double>(p));
+    if (target < 1ull) target = 1ull;
+    thr = radix_threshold_vec<true>(w, vocab, thr, target, sc);
+  }
+  const float mp = min_p[rowi];
+  if (mp > 0.f) {
+    const uint32_t floor_mp = static_cast<uint32_t>(fminf(mp, 1.f) * 1073741824.f);
+    if (floor_mp > thr) thr = floor_mp;
+  }
+  // identical partition of the row into 32 warp-contiguous ranges as the scalar kernel
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int per_warp = ((vocab + 31) / 32 + 31) / 32 * 32;
+  const int wbegin = warp * per_warp;
+  const int wend = min(vocab, wbegin + per_warp);
+  unsigned long long mine = 0;
+  for (int i = wbegin + 4 * lane; i < wend; i += 128) {   // per_warp and vocab are multiples of 4
+    const uint4 q = *reinterpret_cast<const uint4*>(w + i);
+    mine += (q.x >= thr ? q.x : 0u);
+    mine += (q.y >= thr ? q.y : 0u);
+    mine += (q.z >= thr ? q.z : 0u);
+    mine += (q.w >= thr ? q.w : 0u);
+  }
+  mine = warp_sum_u64(mine);
+  if (lane == 0) sh_scan[warp] = mine;
+  if (threadIdx.x == 0) sh_pick = -1;
+  __syncthreads();
+  if (warp == 0) {
+    unsigned long long v = sh_scan[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      unsigned long long n = __shfl_up_sync(0xffffffffu, v, o);
+      if (lane >= o) v += n;
+    }
+    sh_scan[lane] = v;
+  }
+  __syncthreads();
+  const unsigned long long final_total = sh_scan[kSampleThreads / 32 - 1];
+  float u = uniform[rowi];
+  u = fminf(fmaxf(u, 0.f), 0.99999994f);
+  unsigned long long target = static_cast<unsigned long long>(static_cast<double>(u) * static_cast<double>(final_total));
+  if (final_total > 0 && target >= final_total) target = final_total - 1;
+  const unsigned long long w_incl = sh_scan[warp];
+  const unsigned long long w_excl = w_incl - mine;
+  if (final_total > 0 && mine > 0 && target >= w_excl && target < w_incl) {
+    unsigned long long run = w_excl;
+    for (int base = wbegin; base < wend; base += 32) {
+      const int i = base + lane;
+      const uint32_t v0 = (i < wend) ? w[i] : 0u;
+      const unsigned long long v = (v0 >= thr) ? v0 : 0u;
+      unsigned long long incl = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        unsigned long long n = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += n;
+      }
+      const bool hit = v > 0 && target >= run + incl - v && target < run + incl;
+      const unsigned ball = __ballot_sync(0xffffffffu, hit);
+      if (ball) {
+        if (lane == __ffs(ball) - 1) sh_pick = i;
+        break;
+      }
+      run += __shfl_sync(0xffffffffu, incl, 31);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) out[rowi] = (sh_pick >= 0) ? sh_pick : best.i;
+}
+
 // One CTA per sequence: rows [seq*(k+1), seq*(k+1)+k] of the target logits.  Row j predicts the
 // token after draft position j-1 (row 0 follows the last committed token).  accept_len = length of
 // the longest prefix with draft[j] == argmax(row j); out_tokens[seq, 0..accept_len] = the accepted
@@ -307,6 +528,13 @@ extern "C" int ogb_sample_bf16(const void* logits, int* out_tokens, const float*
                                int vocab, int ld, void* stream) {
   if (rows <= 0) return 0;
   if (work == nullptr) return -4;
+  const bool vec_ok = (vocab % 8 == 0) && (ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(logits) & 15) == 0) &&
+                      ((reinterpret_cast<uintptr_t>(work) & 15) == 0);
+  if (vec_ok) {
+    sample_kernel_vec<<<rows, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(logits), out_tokens, temperature, top_k, top_p, min_p, uniform, work, vocab, ld);
+    return static_cast<int>(cudaGetLastError());
+  }
   sample_kernel<<<rows, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(logits), out_tokens, temperature, top_k, top_p, min_p, uniform, work, vocab, ld);
   return static_cast<int>(cudaGetLastError());
