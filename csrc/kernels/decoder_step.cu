@@ -89,9 +89,10 @@ extern "C" void ogb_decoder_set_split_scratch(void* plan, float* part_o, float* 
 // step plan.
 extern "C" int ogb_gemm_bf16_scatter(const void* A, const void* W, int M, int N, int K, int lda, int ldw, const void* sc,
                                      int bn, int* status, void* stream_);
-extern "C" int ogb_tp_reduce_bcast(const void* rp, int rows, int n, int chunk, int tp, int* status, void* stream);
+extern "C" int ogb_tp_reduce_bcast(const void* rp, int rows, int n, int chunk, int tp, int nvls, int* status, void* stream);
 
-// tp > 1: `tp_structs` = {scatter slot 0, reduce slot 0, scatter slot 1, reduce slot 1} device structs
+// tp > 1: `tp_structs` = {scatter slot 0, reduce slot 0, scatter slot 1, reduce slot 1} device structs, then one
+// word that is non-zero when the reduce structs carry NVSwitch multicast pointers
 // for this step's row chunk; the residual stream p->x then lives in the peer-mapped region and the
 // row-parallel projections run as GEMM-scatter + reduce/broadcast instead of a residual epilogue.
 extern "C" int ogb_decoder_step(void* plan, const int* token_ids, const int* positions, const int* slots,
@@ -103,9 +104,11 @@ extern "C" int ogb_decoder_step(void* plan, const int* token_ids, const int* pos
   if (p->tp != 1 && tp_structs == nullptr) return -10;
   const void* sc[2] = {nullptr, nullptr};
   const void* rd[2] = {nullptr, nullptr};
+  int nvls = 0;
   if (p->tp != 1) {
     sc[0] = reinterpret_cast<const void*>(tp_structs[0]); rd[0] = reinterpret_cast<const void*>(tp_structs[1]);
     sc[1] = reinterpret_cast<const void*>(tp_structs[2]); rd[1] = reinterpret_cast<const void*>(tp_structs[3]);
+    nvls = tp_structs[4] != 0 ? 1 : 0;
   }
   const int hid = p->hidden, d = p->d, hq = p->hq, hkv = p->hkv;
   const int qkv_n = (hq + 2 * hkv) * d;
@@ -135,7 +138,7 @@ extern "C" int ogb_decoder_step(void* plan, const int* token_ids, const int* pos
                                p->status, stream));
     } else {
       STEP_CHECK(ogb_gemm_bf16_scatter(p->attn, L.o_w, T, hid, attn_n, attn_n, attn_n, sc[0], 0, p->status, stream));
-      STEP_CHECK(ogb_tp_reduce_bcast(rd[0], T, hid, tp_chunk, p->tp, p->status, stream));
+      STEP_CHECK(ogb_tp_reduce_bcast(rd[0], T, hid, tp_chunk, p->tp, nvls, p->status, stream));
     }
     STEP_CHECK(ogb_rmsnorm_bf16(p->x, nullptr, L.ln2, p->h, T, hid, hid, hid, p->eps, stream));
     STEP_CHECK(ogb_gemm_bf16(p->h, L.gate_up_w, p->act, nullptr, nullptr, nullptr, T, 2 * p->inter_local, hid, hid, hid,
@@ -146,7 +149,7 @@ extern "C" int ogb_decoder_step(void* plan, const int* token_ids, const int* pos
     } else {
       STEP_CHECK(ogb_gemm_bf16_scatter(p->act, L.down_w, T, hid, p->inter_local, p->inter_local, p->inter_local, sc[1], 0,
                                        p->status, stream));
-      STEP_CHECK(ogb_tp_reduce_bcast(rd[1], T, hid, tp_chunk, p->tp, p->status, stream));
+      STEP_CHECK(ogb_tp_reduce_bcast(rd[1], T, hid, tp_chunk, p->tp, nvls, p->status, stream));
     }
   }
   if (R > 0) {

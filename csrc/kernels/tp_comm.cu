@@ -50,6 +50,22 @@ OGB_DEVICE void add_bf16x8(float (&acc)[8], const uint4& v) {
   f = unpack_bf16(v.w); acc[6] += f.x; acc[7] += f.y;
 }
 
+// Tail shared by both exchange kernels: wait (bounded) until every owner's row blocks have landed in this
+// rank's residual stream, then let the last CTA of the launch reset the counters it consumed.  That is
+// safe: no rank can produce for the next use of this slot before it has received this rank's rows.
+OGB_DEVICE void finish_reduce(const TpReduce& r, int groups, uint32_t expect_x, int* status) {
+  if (threadIdx.x != 0) return;
+  if (!wait_counter(r.x_cnt[r.rank], expect_x)) atomicOr(status, kStatusPeerTimeout);
+  __threadfence();
+  const uint32_t total_ctas = gridDim.x * gridDim.y;
+  if (atomicAdd(r.done_cnt, 1u) == total_ctas - 1) {
+    for (int i = 0; i < groups; ++i) r.tile_cnt[i] = 0;
+    *r.x_cnt[r.rank] = 0;
+    *r.done_cnt = 0;
+    __threadfence_system();
+  }
+}
+
 // grid = (min(owned row groups, SMs / column blocks), column blocks); CTAs stride over row groups.
 // rows = total rows of the step (M); cols = columns per CTA.  TP is a template parameter so the
 // loads of all sources for U vectors are issued back to back before the first add: with peer-load
@@ -64,6 +80,8 @@ __global__ void __launch_bounds__(kRbThreads) tp_reduce_bcast_kernel(const TpRed
   const int vec_per_row = ncols / 8;
   const int total = 32 * vec_per_row;
   __shared__ int ok_sh;
+  const bool stamp = r.dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0;
+  if (stamp) r.dbg[0] = global_timer_ns();
   for (int g = blockIdx.x; g < groups; g += gridDim.x) {   // g = owned 32-row group
     const int row_base = r.rank * r.chunk + g * 32;        // global row of the group
     if (row_base >= rows) break;
@@ -72,6 +90,7 @@ __global__ void __launch_bounds__(kRbThreads) tp_reduce_bcast_kernel(const TpRed
       const bool ok = wait_counter(r.tile_cnt + g, static_cast<uint32_t>(r.n / 32) * TP);
       if (!ok) atomicOr(status, kStatusPeerTimeout);
       ok_sh = ok ? 1 : 0;
+      if (stamp && g == 0) r.dbg[1] = global_timer_ns();
     }
     __syncthreads();
     if (ok_sh) {
@@ -109,58 +128,155 @@ __global__ void __launch_bounds__(kRbThreads) tp_reduce_bcast_kernel(const TpRed
       }
     }
     // publish: this block of rows is in place everywhere
+    if (stamp && g == 0) r.dbg[4] = global_timer_ns();
     __syncthreads();
     if (threadIdx.x == 0) {
+      if (stamp && g == 0) r.dbg[5] = global_timer_ns();
       __threadfence_system();
-      for (int p = 0; p < TP; ++p) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(r.x_cnt[p]) : "memory");
+      if (stamp && g == 0) r.dbg[6] = global_timer_ns();
+      // one fence orders the CTA's row stores before all the signals; a releasing reduction per peer would
+      // each wait again for the SM's outstanding NVLink writes (measured: ~12 us apiece under load)
+      for (int p = 0; p < TP; ++p) asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(r.x_cnt[p]) : "memory");
     }
   }
-  if (threadIdx.x == 0) {
-    // wait until every owner's blocks have landed in this rank's residual stream
-    if (!wait_counter(r.x_cnt[r.rank], expect_x)) atomicOr(status, kStatusPeerTimeout);
-    // the last CTA of this launch resets the counters it consumed (safe: no rank can produce for the
-    // next use of this slot before it has received this rank's rows, which were sent above)
-    __threadfence();
-    const uint32_t total_ctas = gridDim.x * gridDim.y;
-    if (atomicAdd(r.done_cnt, 1u) == total_ctas - 1) {
-      for (int i = 0; i < groups; ++i) r.tile_cnt[i] = 0;
-      *r.x_cnt[r.rank] = 0;
-      *r.done_cnt = 0;
+  if (stamp) r.dbg[2] = global_timer_ns();
+  finish_reduce(r, groups, expect_x, status);
+  if (stamp) r.dbg[3] = global_timer_ns();
+}
+
+// The same exchange through NVSwitch multicast (NVLS).  One multimem.ld_reduce returns the fp32-accumulated
+// sum of all ranks' partial rows (the switch pulls each rank's copy: 1/TP of the bytes of TP peer loads
+// arrive here), one multimem.st delivers the finished row to every rank's residual stream, and one
+// multimem.red bumps every rank's delivery counter.  The owner still adds the residual and rounds once,
+// so all replicas receive identical bits.
+template <int U>
+__global__ void __launch_bounds__(kRbThreads) tp_reduce_bcast_nvls_kernel(const TpReduce* __restrict__ rp, int rows, int cols,
+                                                                           uint32_t expect_x, int* status) {
+  const TpReduce& r = *rp;
+  const int groups = r.chunk / 32;
+  const int col0 = blockIdx.y * cols;
+  const int ncols = min(cols, r.n - col0);
+  const int vec_per_row = ncols / 8;
+  const int total = 32 * vec_per_row;
+  __shared__ int ok_sh;
+  const bool stamp = r.dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0;
+  if (stamp) r.dbg[0] = global_timer_ns();
+  for (int g = blockIdx.x; g < groups; g += gridDim.x) {
+    const int row_base = r.rank * r.chunk + g * 32;
+    if (row_base >= rows) break;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const bool ok = wait_counter(r.tile_cnt + g, static_cast<uint32_t>(r.n / 32) * r.tp);
+      if (!ok) atomicOr(status, kStatusPeerTimeout);
+      ok_sh = ok ? 1 : 0;
+      if (stamp && g == 0) r.dbg[1] = global_timer_ns();
+    }
+    __syncthreads();
+    if (ok_sh) {
+      for (int i0 = threadIdx.x; i0 < total; i0 += kRbThreads * U) {
+        uint4 xv[U], sv[U];
+        size_t off[U];
+        bool live[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int i = i0 + u * kRbThreads;
+          const int lr = i / vec_per_row, cv = i % vec_per_row;
+          const int row = row_base + lr;
+          live[u] = (i < total) && (row < rows);
+          off[u] = static_cast<size_t>(row) * r.n + col0 + cv * 8;
+          if (live[u]) {
+            xv[u] = *reinterpret_cast<const uint4*>(r.x[r.rank] + off[u]);
+            asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(sv[u].x), "=r"(sv[u].y), "=r"(sv[u].z), "=r"(sv[u].w)
+                         : "l"(r.part_mc + off[u])
+                         : "memory");
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (!live[u]) continue;
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          add_bf16x8(acc, xv[u]);
+          add_bf16x8(acc, sv[u]);
+          const uint32_t o0 = pack_bf16(acc[0], acc[1]), o1 = pack_bf16(acc[2], acc[3]), o2 = pack_bf16(acc[4], acc[5]),
+                         o3 = pack_bf16(acc[6], acc[7]);
+          asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(r.x_mc + off[u]),
+                       "f"(__uint_as_float(o0)), "f"(__uint_as_float(o1)), "f"(__uint_as_float(o2)), "f"(__uint_as_float(o3))
+                       : "memory");
+        }
+      }
+    }
+    if (stamp && g == 0) r.dbg[4] = global_timer_ns();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      if (stamp && g == 0) r.dbg[5] = global_timer_ns();
       __threadfence_system();
+      if (stamp && g == 0) r.dbg[6] = global_timer_ns();
+      asm volatile("multimem.red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(r.x_cnt_mc), "r"(1u) : "memory");
     }
   }
+  if (stamp) r.dbg[2] = global_timer_ns();
+  finish_reduce(r, groups, expect_x, status);
+  if (stamp) r.dbg[3] = global_timer_ns();
 }
 
 }  // namespace ogb
 
 using namespace ogb;
 
-// x (every rank's residual stream) += sum over ranks of the staged partial tiles; `rp` is a
-// device-resident TpReduce for the slot.  Must follow ogb_gemm_bf16_scatter on the same stream.
-extern "C" int ogb_tp_reduce_bcast(const void* rp, int rows, int n, int chunk, int tp, int* status, void* stream) {
-  if (rows <= 0) return 0;
-  if (n % 8 || chunk % 32 || chunk / 32 > kTpMaxGroups) return -3;
+namespace {
+// CTAs of `kernel` that fit on the device at once (every CTA of an exchange launch spins at the end, so
+// the grid must be co-resident).  Queried once per kernel.
+template <typename K>
+int resident_ctas(K kernel, int* cache) {
+  if (*cache == 0) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kRbThreads, 0) != cudaSuccess || per_sm < 1) per_sm = 1;
+    if (per_sm > 4) per_sm = 4;
+    *cache = per_sm * ogb_num_sms();
+  }
+  return *cache;
+}
+
+template <typename K>
+int launch_exchange(K kernel, int* occ_cache, const TpReduce* r, int rows, int n, int chunk, int cols, int* status,
+                    cudaStream_t st) {
   const int groups = chunk / 32;
-  // narrower column blocks at higher TP keep enough CTAs (and peer loads) in flight when each rank
-  // owns only a few row groups
-  const int cols = tp <= 2 ? 512 : (tp <= 4 ? 256 : 128);
   const int col_blocks = (n + cols - 1) / cols;
   // blocks that will signal = row groups (over all ranks) that hold at least one valid row
   const int total_groups = (rows + 31) / 32;
   const uint32_t expect_x = static_cast<uint32_t>(total_groups) * col_blocks;
-  int gx = ogb_num_sms() / col_blocks;   // every CTA spins at the end: all must be co-resident
+  int gx = resident_ctas(kernel, occ_cache) / col_blocks;
   if (gx < 1) return -4;
   if (gx > groups) gx = groups;
-  dim3 grid(gx, col_blocks);
+  kernel<<<dim3(gx, col_blocks), kRbThreads, 0, st>>>(r, rows, cols, expect_x, status);
+  return static_cast<int>(cudaGetLastError());
+}
+}  // namespace
+
+// x (every rank's residual stream) += sum over ranks of the staged partial tiles; `rp` is a
+// device-resident TpReduce for the slot.  Must follow ogb_gemm_bf16_scatter on the same stream.
+// nvls != 0 selects the NVSwitch-multicast kernel and requires the *_mc members of `rp` to be set.
+extern "C" int ogb_tp_reduce_bcast(const void* rp, int rows, int n, int chunk, int tp, int nvls, int* status, void* stream) {
+  if (rows <= 0) return 0;
+  if (n % 8 || chunk % 32 || chunk / 32 > kTpMaxGroups) return -3;
   const TpReduce* r = static_cast<const TpReduce*>(rp);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // Peer round trips cost microseconds, so the exchange is latency-bound: column blocks are sized so that
+  // every thread issues all of its loads in one batch (256 threads x U vectors = 32 rows x cols) and the
+  // grid covers all owned row groups at once whenever they fit on the device.
+  static int occ[5] = {0, 0, 0, 0, 0};
+  if (nvls) {
+    if (tp == 8) return launch_exchange(tp_reduce_bcast_nvls_kernel<2>, &occ[0], r, rows, n, chunk, 128, status, st);
+    if (tp == 2 || tp == 4) return launch_exchange(tp_reduce_bcast_nvls_kernel<4>, &occ[1], r, rows, n, chunk, 256, status, st);
+    return -5;
+  }
   switch (tp) {
-    case 2: tp_reduce_bcast_kernel<2, 4><<<grid, kRbThreads, 0, st>>>(r, rows, cols, expect_x, status); break;
-    case 4: tp_reduce_bcast_kernel<4, 2><<<grid, kRbThreads, 0, st>>>(r, rows, cols, expect_x, status); break;
-    case 8: tp_reduce_bcast_kernel<8, 1><<<grid, kRbThreads, 0, st>>>(r, rows, cols, expect_x, status); break;
+    case 2: return launch_exchange(tp_reduce_bcast_kernel<2, 4>, &occ[2], r, rows, n, chunk, 256, status, st);
+    case 4: return launch_exchange(tp_reduce_bcast_kernel<4, 4>, &occ[3], r, rows, n, chunk, 256, status, st);
+    case 8: return launch_exchange(tp_reduce_bcast_kernel<8, 2>, &occ[4], r, rows, n, chunk, 128, status, st);
     default: return -5;
   }
-  return static_cast<int>(cudaGetLastError());
 }
 
 // ---- peer mapping helpers (CUDA IPC) ----

@@ -24,6 +24,14 @@ struct TpReduce {
   __nv_bfloat16* x[kMaxTp];          // every rank's residual stream [rows, n]
   uint32_t* x_cnt[kMaxTp];           // every rank's "row blocks delivered" counter
   uint32_t* done_cnt;                // local: CTAs of this launch that have finished
+  // NVSwitch multicast views of the same symmetric region (null when the region has no multicast
+  // binding): a load through part_mc returns the sum over all ranks' buffers, a store through x_mc or
+  // a reduction through x_cnt_mc lands in every rank's copy.
+  const __nv_bfloat16* part_mc;
+  __nv_bfloat16* x_mc;
+  uint32_t* x_cnt_mc;
+  unsigned long long* dbg;           // optional: 8 globaltimer stamps of CTA (0,0): start, group 0 ready, all rows signalled, end,
+                                     // then for group 0: own stores issued, CTA stores issued, fence done
   int rank, tp, chunk, n;
 };
 

@@ -279,7 +279,7 @@ class DecoderModel:
         if hit is None:
             sc0, rd0 = fc._get_structs(0, chunk)
             sc1, rd1 = fc._get_structs(1, chunk)
-            hit = (ctypes.c_uint64 * 4)(sc0.data_ptr(), rd0.data_ptr(), sc1.data_ptr(), rd1.data_ptr())
+            hit = (ctypes.c_uint64 * 5)(sc0.data_ptr(), rd0.data_ptr(), sc1.data_ptr(), rd1.data_ptr(), 1 if fc.nvls else 0)
             self._tp_args_cache[chunk] = hit
         return hit, chunk
 

@@ -11,6 +11,13 @@ collective:
                             + residual, stores the new rows into every rank's residual stream, waits
                             for the other owners
 
+When the region can be bound to an NVSwitch multicast object (the region is then allocated through
+``torch.distributed._symmetric_memory``, which does the handle exchange and the binding), the second
+launch uses ``multimem.ld_reduce`` / ``multimem.st`` / ``multimem.red`` instead of per-peer loads and
+stores: the switch adds the partial rows and replicates the result (used from TP=4 up, where it moves
+fewer bytes per GPU).  ``OGB_TP_NVLS=0`` keeps plain peer loads, ``OGB_TP_NVLS=1`` forces multicast at
+TP=2; ``OGB_TP_SYMM=0`` keeps the CUDA-IPC region.
+
 Collectives this class does not cover (broadcast of sampled tokens, barriers, scalar reductions)
 go to the wrapped NCCL communicator.  The reference's counterpart is only a contract
 (crates/onnx-runtime-comm/src/communicator.rs:32-160); its ordering rule -- every rank issues the
@@ -20,6 +27,7 @@ rank runs the same step plan.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
@@ -40,6 +48,7 @@ class _Scatter(ctypes.Structure):
 class _Reduce(ctypes.Structure):
     _fields_ = [("part", ctypes.c_uint64 * MAX_TP), ("tile_cnt", ctypes.c_uint64), ("x", ctypes.c_uint64 * MAX_TP),
                 ("x_cnt", ctypes.c_uint64 * MAX_TP), ("done_cnt", ctypes.c_uint64),
+                ("part_mc", ctypes.c_uint64), ("x_mc", ctypes.c_uint64), ("x_cnt_mc", ctypes.c_uint64), ("dbg", ctypes.c_uint64),
                 ("rank", ctypes.c_int), ("tp", ctypes.c_int), ("chunk", ctypes.c_int), ("n", ctypes.c_int)]
 
 
@@ -61,7 +70,7 @@ def _lib():
     lib.ogb_ipc_free.argtypes = [P]
     lib.ogb_tp_struct_sizes.argtypes = [ctypes.POINTER(I), ctypes.POINTER(I)]
     lib.ogb_gemm_bf16_scatter.argtypes = [P, P, I, I, I, I, I, P, I, P, P]
-    lib.ogb_tp_reduce_bcast.argtypes = [P, I, I, I, I, P, P]
+    lib.ogb_tp_reduce_bcast.argtypes = [P, I, I, I, I, I, P, P]
     for f in ("ogb_ipc_alloc", "ogb_ipc_get_handle", "ogb_ipc_open_handle", "ogb_ipc_close_handle", "ogb_ipc_free",
               "ogb_tp_struct_sizes", "ogb_gemm_bf16_scatter", "ogb_tp_reduce_bcast"):
         getattr(lib, f).restype = I
@@ -114,6 +123,51 @@ class FusedComm:
         # counters: tile_cnt[SLOTS][MAX_GROUPS], x_cnt, done_cnt
         cnt_words = SLOTS * MAX_GROUPS + 64
         total = self.off_cnt + align(cnt_words * 4)
+        self.total_bytes = total
+        self.mc_ptr = 0
+        self.nvls = False
+        self._symm = None
+        if os.environ.get("OGB_TP_SYMM", "1") != "0":
+            try:
+                self._setup_symmetric(total)
+            except Exception as exc:       # no VMM handle exchange on this host: CUDA IPC still gives peer pointers
+                self._symm = None
+                self.symm_error = repr(exc)
+        if not self.base.min_int(1 if self._symm is not None else 0):   # all ranks or none
+            self._symm = None
+            self.mc_ptr = 0
+        if self._symm is None:
+            self._setup_ipc(total)
+        # Bytes per GPU and direction for a [rows, n] exchange: peer loads + stores move 2(tp-1)/tp of it, the
+        # multicast path (tp+1)/tp (the switch also reads and writes the caller's own copy), so multicast pays
+        # from tp = 4 up.  OGB_TP_NVLS=1 forces it at tp = 2, OGB_TP_NVLS=0 disables it.
+        knob = os.environ.get("OGB_TP_NVLS", "auto")
+        want_nvls = bool(self.mc_ptr) and knob != "0" and (self.world >= 4 or knob == "1")
+        self.nvls = bool(self.base.min_int(1 if want_nvls else 0))
+        if self.nvls:
+            self.backend_name = "fused-nvls"
+        self.dbg = torch.zeros(8, dtype=torch.int64, device=self.device) if os.environ.get("OGB_TP_STAMPS") else None
+        self.x = torch.as_tensor(_CudaArray(self.local_ptr + self.off_x, (max_tokens, hidden), "<u2"),
+                                 device=self.device).view(torch.bfloat16)
+        self._structs: dict = {}
+        torch.cuda.synchronize()
+        self.base.barrier()
+        self.ready = True
+
+    def _setup_symmetric(self, total: int):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        buf = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
+        hdl = symm_mem.rendezvous(buf, dist.group.WORLD)
+        buf.zero_()
+        self._symm = (buf, hdl)
+        self.peer_ptrs = [int(p) for p in hdl.buffer_ptrs]
+        self.local_ptr = self.peer_ptrs[self.rank]
+        assert self.local_ptr == buf.data_ptr()
+        self.mc_ptr = int(hdl.multicast_ptr or 0)
+
+    def _setup_ipc(self, total: int):
+        tp = self.world
         ptr = ctypes.c_void_p()
         rc = self.lib.ogb_ipc_alloc(ctypes.byref(ptr), total)
         if rc != 0:
@@ -136,12 +190,6 @@ class FusedComm:
             if rc != 0:
                 raise RuntimeError(f"cudaIpcOpenMemHandle for rank {p} failed ({rc})")
             self.peer_ptrs.append(out.value)
-        self.x = torch.as_tensor(_CudaArray(self.local_ptr + self.off_x, (max_tokens, hidden), "<u2"),
-                                 device=self.device).view(torch.bfloat16)
-        self._structs: dict = {}
-        torch.cuda.synchronize()
-        self.base.barrier()
-        self.ready = True
 
     def _tile_cnt(self, p, slot):
         return self.peer_ptrs[p] + self.off_cnt + slot * MAX_GROUPS * 4
@@ -165,6 +213,11 @@ class FusedComm:
         sc.rank, sc.tp, sc.chunk, sc.n = self.rank, tp, chunk, self.hidden
         rd.tile_cnt = self._tile_cnt(self.rank, slot)
         rd.done_cnt = self.local_ptr + self.off_cnt + (SLOTS * MAX_GROUPS + 8) * 4
+        if self.nvls:
+            rd.part_mc = self.mc_ptr + self.off_stage[slot]
+            rd.x_mc = self.mc_ptr + self.off_x
+            rd.x_cnt_mc = self.mc_ptr + self.off_cnt + SLOTS * MAX_GROUPS * 4
+        rd.dbg = self.dbg.data_ptr() if self.dbg is not None else 0
         rd.rank, rd.tp, rd.chunk, rd.n = self.rank, tp, chunk, self.hidden
         mk = lambda st: torch.frombuffer(bytearray(bytes(st)), dtype=torch.uint8).to(self.device)
         hit = (mk(sc), mk(rd))
@@ -187,7 +240,7 @@ class FusedComm:
                                                 w.stride(0), sc.data_ptr(), 0, st, stream)
         _native.check(rc, "ogb_gemm_bf16_scatter")
         with ops.timed_region("tp_reduce_bcast"):
-            rc = self.lib.ogb_tp_reduce_bcast(rd.data_ptr(), rows, self.hidden, chunk, self.world, st, stream)
+            rc = self.lib.ogb_tp_reduce_bcast(rd.data_ptr(), rows, self.hidden, chunk, self.world, 1 if self.nvls else 0, st, stream)
         _native.check(rc, "ogb_tp_reduce_bcast")
         ops.launch_counts["gemm_bf16_scatter"] += 1
         ops.launch_counts["tp_reduce_bcast"] += 1

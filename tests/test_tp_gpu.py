@@ -10,8 +10,8 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(nproc, mode, out, port):
-    env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
+def _run(nproc, mode, out, port, **extra_env):
+    env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0", **extra_env)
     if nproc == 1:
         cmd = [sys.executable, os.path.join(ROOT, "tests", "tp_worker.py"), mode, out]
     else:
@@ -27,9 +27,14 @@ def _run(nproc, mode, out, port):
 def test_tp2_fused_and_nccl_match_single_gpu(tmp_path):
     single = _run(1, "nccl", str(tmp_path / "s.pt"), 0)
     nccl = _run(2, "nccl", str(tmp_path / "n.pt"), 29631)
-    fused = _run(2, "fused", str(tmp_path / "f.pt"), 29632)
-    fused_py = _run(2, "fused-py", str(tmp_path / "fp.pt"), 29633)
+    fused = _run(2, "fused", str(tmp_path / "f.pt"), 29632, OGB_TP_NVLS="1")       # NVSwitch multicast kernels
+    fused_py = _run(2, "fused-py", str(tmp_path / "fp.pt"), 29633, OGB_TP_NVLS="1")
+    assert fused["backend"] == "fused-nvls"
+    p2p = _run(2, "fused", str(tmp_path / "p.pt"), 29634, OGB_TP_NVLS="0", OGB_TP_SYMM="0")   # plain peer loads, CUDA IPC
     ref = single["logits"]
+    err = float((p2p["logits"] - ref).norm() / ref.norm())
+    assert err < 3e-2, ("fused-p2p", err)
+    assert p2p["backend"] == "fused-p2p"
     assert fused["launches"].get("native_step_kernels", 0) > 0
     assert fused_py["tokens"] == fused["tokens"]          # C++ executor and Python-driven path run the same kernels
     fused = fused_py

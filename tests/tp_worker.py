@@ -44,7 +44,8 @@ def main():
         dist.all_gather_object(gathered, toks)
         assert all(g == gathered[0] for g in gathered), "ranks diverged"
     if rank == 0:
-        torch.save({"logits": logits, "tokens": toks, "launches": dict(ops.launch_counts)}, out_path)
+        torch.save({"logits": logits, "tokens": toks, "launches": dict(ops.launch_counts),
+                    "backend": getattr(comm, "backend_name", "none")}, out_path)
     if world > 1:
         import torch.distributed as dist
 
