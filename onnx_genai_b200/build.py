@@ -68,7 +68,7 @@ def cuda_sources() -> list[Path]:
 
 def runtime_sources() -> list[Path]:
     out: list[Path] = []
-    for sub in ("runtime", "cpu_ref", "capi"):
+    for sub in ("runtime", "cpu_ref"):
         out += sorted((ROOT / "csrc" / sub).glob("*.cpp"))
     return out
 

@@ -117,7 +117,8 @@ class Engine:
     @classmethod
     def from_dir(cls, model_dir: str, device=None, page_size: int | None = None, max_seqs: int = 32,
                  max_seq_len: int | None = None, num_pages: int = 0, max_tokens_per_step: int = 2048,
-                 kv_dtype: str = "bf16", max_draft_tokens: int = 0, draft_model_dir: str | None = None, **engine_kw):
+                 kv_dtype: str = "bf16", max_draft_tokens: int = 0, draft_model_dir: str | None = None,
+                 keep_int4: bool | None = None, **engine_kw):
         """Load a flat model directory or a model package.  ``page_size`` is accepted for API
         compatibility; pages hold 16 tokens (the attention kernels' tile)."""
         if page_size not in (None, 16):
@@ -127,8 +128,11 @@ class Engine:
                                      device="gpu" if str(device).startswith("cuda") else "cpu")
         meta = d.load_metadata()
         dtype = torch.bfloat16 if str(device).startswith("cuda") else torch.float32
-        cfg, weights, _ = lower_decoder(onnx_pb.load_model(d.model_path), dtype=dtype, device=device,
-                                        keep_int4=str(device).startswith("cuda"))
+        if keep_int4 is None:   # MatMulNBits weights stay packed wherever a kernel reads them directly
+            from ..ops import cpu as _cpu_ops
+
+            keep_int4 = str(device).startswith("cuda") or _cpu_ops.available()
+        cfg, weights, _ = lower_decoder(onnx_pb.load_model(d.model_path), dtype=dtype, device=device, keep_int4=keep_int4)
         if meta.vocab_size and meta.vocab_size != cfg.vocab:
             raise md.MetadataError(f"{d.metadata_path}: model.vocab_size={meta.vocab_size} but the graph's embedding has "
                                    f"{cfg.vocab} rows; fix the metadata or re-export the model")

@@ -1,9 +1,9 @@
 """Fused ops of the decoder step.
 
 Each function takes torch tensors.  CUDA tensors run the hand-written sm_100a kernels from
-``libogb_cuda.so`` (a missing library is an error, never a silent fallback); CPU tensors run
-the fp32 PyTorch statements in :mod:`onnx_genai_b200.ops.reference`, which are also the oracle
-the GPU tests compare against.  Launch counters per op (``launch_counts``) let callers and tests
+``libogb_cuda.so`` (a missing library is an error, never a silent fallback); fp32 CPU tensors run
+the C++ kernels of :mod:`onnx_genai_b200.ops.cpu` and other CPU tensors the PyTorch statements in
+:mod:`onnx_genai_b200.ops.reference`, which are also the oracle the GPU tests compare against.  Launch counters per op (``launch_counts``) let callers and tests
 prove which path ran, like the reference's dispatch hit counters (dispatch_manifest.toml:1-35).
 """
 from __future__ import annotations
@@ -13,9 +13,15 @@ import math
 
 import torch
 
-from . import _native, reference
+from . import _native, cpu, reference
 
 PAGE = reference.PAGE
+
+
+def _cpu_native(t) -> bool:
+    """True when a CPU tensor should go to the C++ kernels (fp32 and the library is built)."""
+    return t.dtype == torch.float32 and cpu.available()
+
 launch_counts: collections.Counter = collections.Counter()
 _status_words: dict[int, torch.Tensor] = {}
 
@@ -207,7 +213,10 @@ pack_gate_up = reference.pack_gate_up
 def rmsnorm(x, weight, eps, delta=None, out=None):
     """Returns normed x; with ``delta`` the residual x is updated in place first (x += delta)."""
     if not x.is_cuda:
-        y, new_x = reference.rmsnorm(x, weight, eps, delta)
+        if _cpu_native(x):
+            y, new_x = cpu.rmsnorm(x, weight, eps, delta)
+        else:
+            y, new_x = reference.rmsnorm(x, weight, eps, delta)
         if delta is not None:
             x.copy_(new_x)
         return y
@@ -239,7 +248,7 @@ def embedding(ids, table, out=None):
 @_timed("silu_mul")
 def silu_mul(gate_up, out=None):
     if not gate_up.is_cuda:
-        return reference.silu_mul(gate_up)
+        return cpu.silu_mul(gate_up) if _cpu_native(gate_up) else reference.silu_mul(gate_up)
     rows, two_inter = gate_up.shape
     if out is None:
         out = torch.empty(rows, two_inter // 2, dtype=gate_up.dtype, device=gate_up.device)
@@ -256,6 +265,8 @@ def rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim=
     rotary_dim = rotary_dim or d
     if not qkv.is_cuda:
         assert kv_scales is None
+        if _cpu_native(qkv) and qkv.is_contiguous() and pool.dtype == torch.float32 and pool.is_contiguous():
+            return cpu.rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim, interleaved)
         return reference.rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim, interleaved)
     t = qkv.shape[0]
     assert qkv.is_contiguous() and positions.dtype == torch.int32 and slots.dtype == torch.int32
@@ -295,6 +306,9 @@ def paged_prefill(q, out, pool, page_table, ctx_len, cu_q, tile_seq, tile_q0, nu
     ``kv_scales`` selects the e4m3 page kernels."""
     scale = scale or 1.0 / math.sqrt(d)
     if not q.is_cuda:
+        if kv_scales is None and _cpu_native(q) and pool.dtype == torch.float32 and pool.is_contiguous():
+            out.copy_(cpu.paged_attention(q, pool, page_table, ctx_len, cu_q, hq, hkv, d, scale, window))
+            return out
         out.copy_(reference.paged_attention(q, pool, page_table, ctx_len, cu_q, hq, hkv, d, scale, window, kv_scales))
         return out
     if kv_scales is not None:
@@ -323,6 +337,9 @@ def paged_decode(q, out, pool, page_table, ctx_len, hq, hkv, d, scale=None, num_
     n = ctx_len.numel()
     if not q.is_cuda:
         cu = torch.arange(n + 1, dtype=torch.int32)
+        if kv_scales is None and _cpu_native(q) and pool.dtype == torch.float32 and pool.is_contiguous():
+            out[:n].copy_(cpu.paged_attention(q[:n], pool, page_table, ctx_len, cu, hq, hkv, d, scale, window))
+            return out
         out[:n].copy_(reference.paged_attention(q[:n], pool, page_table, ctx_len, cu, hq, hkv, d, scale, window, kv_scales))
         return out
     if num_splits > 1 and part_o is None:
@@ -351,7 +368,7 @@ def paged_decode(q, out, pool, page_table, ctx_len, hq, hkv, d, scale=None, num_
 @_timed("argmax")
 def argmax(logits, out=None):
     if not logits.is_cuda:
-        return reference.argmax(logits)
+        return cpu.argmax(logits) if _cpu_native(logits) else reference.argmax(logits)
     rows, vocab = logits.shape
     if out is None:
         out = torch.empty(rows, dtype=torch.int32, device=logits.device)
@@ -365,6 +382,8 @@ def argmax(logits, out=None):
 def sample(logits, temperature, top_k, top_p, min_p, uniform, work=None, out=None):
     """Fused temperature/top-k/top-p/min-p sampler; per-row parameter tensors; ``uniform`` in [0,1)."""
     if not logits.is_cuda:
+        if _cpu_native(logits):
+            return cpu.sample(logits, temperature, top_k, top_p, min_p, uniform)
         return reference.sample(logits, temperature, top_k, top_p, min_p, uniform)
     rows, vocab = logits.shape
     if work is None:

@@ -1,5 +1,6 @@
 """MatMulNBits int4 projections on the GPU: GEMV with in-kernel dequant for decode-sized M, dequant +
-tcgen05 GEMM above that.  CPU tensors use the fp32 statement in ops.reference."""
+tcgen05 GEMM above that.  CPU tensors use the C++ block-wise kernel (ops.cpu), or the fp32 statement in
+ops.reference when the runtime library is not built."""
 from __future__ import annotations
 
 import torch
@@ -34,6 +35,10 @@ class QuantLinear:
     def __call__(self, x, out=None):
         m = x.shape[0]
         if not x.is_cuda:
+            from . import cpu
+
+            if cpu.available():
+                return cpu.matmul_nbits(x, self.qweight, self.scales, self.zp, self.bias, self.k, out=out)
             y = x.float() @ self.dense().t()
             if self.bias is not None:
                 y = y + self.bias.float()
