@@ -133,9 +133,36 @@ def build_runtime(force: bool = False, verbose: bool = False) -> Path:
     return RUNTIME_LIB
 
 
+CAPI_LIB = LIB_DIR / "libonnx_genai_b200.so"
+
+
+def build_capi(force: bool = False, verbose: bool = False) -> Path:
+    """The C interface (csrc/capi): a CPython embedding, so it links the interpreter's shared library."""
+    import sysconfig
+
+    src = ROOT / "csrc" / "capi" / "capi.cpp"
+    hdr = ROOT / "csrc" / "capi" / "onnx_genai_b200.h"
+    libdir = sysconfig.get_config_var("LIBDIR") or ""
+    ldver = sysconfig.get_config_var("LDVERSION") or sysconfig.get_python_version()
+    flags = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-I", sysconfig.get_paths()["include"],
+             f'-DOGB_DEFAULT_PYTHON="{sys.executable}"', f'-DOGB_DEFAULT_ROOT="{ROOT}"']
+    digest = _digest([src, hdr], " ".join(flags) + libdir + ldver)
+    if not force and _stamp_ok(CAPI_LIB, digest):
+        return CAPI_LIB
+    LIB_DIR.mkdir(parents=True, exist_ok=True)
+    cxx = os.environ.get("OGB_CXX") or shutil.which("g++") or "g++"
+    _run([cxx, *flags, "-shared", str(src), "-o", str(CAPI_LIB), f"-L{libdir}", f"-lpython{ldver}", f"-Wl,-rpath,{libdir}",
+          "-ldl", "-lpthread"])
+    CAPI_LIB.with_suffix(".stamp").write_text(digest)
+    if verbose:
+        print(f"built {CAPI_LIB}")
+    return CAPI_LIB
+
+
 def build_all(force: bool = False, verbose: bool = False) -> None:
     build_cuda(force, verbose)
     build_runtime(force, verbose)
+    build_capi(force, verbose)
 
 
 if __name__ == "__main__":
