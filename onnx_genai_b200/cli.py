@@ -31,6 +31,9 @@ def _add_sampling(p):
     p.add_argument("--stop", action="append", default=[])
     p.add_argument("--raw", action="store_true", help="do not apply the chat template")
     p.add_argument("--speculative", action="store_true", help="prompt-lookup speculative decoding (greedy only)")
+    p.add_argument("--json", dest="json_output", action="store_true", help="constrain the output to one JSON object")
+    p.add_argument("--json-schema", default="", help="file with a JSON Schema the output must satisfy")
+    p.add_argument("--regex", default="", help="regular expression the whole output must match")
 
 
 def _add_engine(p):
@@ -43,9 +46,20 @@ def _add_engine(p):
 def _options(args):
     from .engine.api import GenerateOptions
 
+    constraint = None
+    if getattr(args, "json_schema", ""):
+        import json
+
+        with open(args.json_schema, encoding="utf-8") as f:
+            constraint = ("json_schema", json.load(f))
+    elif getattr(args, "regex", ""):
+        constraint = ("regex", args.regex)
+    elif getattr(args, "json_output", False):
+        constraint = ("json_object",)
     return GenerateOptions(max_new_tokens=args.max_new_tokens, temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
                            min_p=args.min_p, repetition_penalty=args.repetition_penalty, seed=args.seed,
-                           greedy=args.greedy or args.temperature == 0, stop=tuple(args.stop), speculative=args.speculative)
+                           greedy=args.greedy or args.temperature == 0, stop=tuple(args.stop), speculative=args.speculative,
+                           constraint=constraint)
 
 
 def _load(args):

@@ -56,6 +56,8 @@ class GenerateOptions:
     priority: int = 0
     tenant: int = 0
     speculative: bool = False
+    # None, a constraints.Constraint, or (kind, argument) with kind json | json_object | json_schema | regex | choice
+    constraint: object = None
 
     def validate(self):
         if self.max_new_tokens < 0:
@@ -193,9 +195,14 @@ class Engine:
                                    tenant=opt.tenant, ignore_eos=opt.ignore_eos, stop_ids=stop_ids)
         rng = np.random.default_rng(opt.seed or None)
         eff = GenerateOptions(**{**opt.__dict__, "greedy": greedy})
-        chain = procs.build_processor_chain(eff, len(ids), rng, extra=processors)
+        cproc = None
+        if opt.constraint is not None:
+            from . import constraints as cons
+
+            cproc = cons.ConstraintProcessor(cons.make_constraint(opt.constraint), self.token_texts(), stop_ids)
+        chain = procs.build_processor_chain(eff, len(ids), rng, extra=processors, constraint=cproc)
         plan = procs.device_sampling_plan(chain, eff, sampler is not None)
-        state = {"ids": list(int(i) for i in ids), "chain": chain, "logprobs": [], "plan": plan}
+        state = {"ids": list(int(i) for i in ids), "chain": chain, "logprobs": [], "plan": plan, "constraint": cproc}
         if plan == "host":
             smp = sampler or (procs.GreedySampler() if greedy else procs.CategoricalSampler())
 
@@ -222,6 +229,26 @@ class Engine:
             else:
                 self.llm.proposers[sid] = NgramProposer()
         return sid, state
+
+    def token_texts(self) -> list:
+        """Decoded text of every vocabulary entry ('' for special tokens and incomplete byte sequences);
+        computed once, used by constrained decoding."""
+        if getattr(self, "_token_texts", None) is None:
+            if self.tokenizer is None:
+                raise ValueError("constrained decoding needs the model's tokenizer (tokenizer.json is missing)")
+            vocab = self.llm.cfg.model.vocab
+            n_tok = self.tokenizer.get_vocab_size()
+            texts = []
+            for i in range(vocab):
+                t = self.tokenizer.decode([i], skip_special_tokens=True) if i < n_tok else ""
+                texts.append("" if "\ufffd" in t else t)
+            self._token_texts = texts
+        return self._token_texts
+
+    @staticmethod
+    def constraint_finished(state) -> bool:
+        c = state.get("constraint")
+        return c is not None and c.constraint.terminal(c.token_texts)
 
     def _finish(self, sid):
         self.llm.host_samplers.pop(sid & 0x7FFFFFFF, None)
@@ -253,6 +280,9 @@ class Engine:
                             delta = text[len(emitted):hit] if hit > len(emitted) else ""
                             self.llm.core.cancel(sid)
                             fin = "stop"
+                    if fin is None and self.constraint_finished(state):
+                        self.llm.core.cancel(sid)
+                        fin = "stop"
                     emitted += delta
                     yield tok, delta, fin
                     if fin is not None:
@@ -306,6 +336,9 @@ class Engine:
                     e["ttft"] = time.perf_counter() - t0
                 e["out"].append(tok)
                 e["state"]["ids"].append(tok)
+                if fin is None and self.constraint_finished(e["state"]):
+                    self.llm.core.cancel(sid)
+                    fin = "stop"
                 if fin is not None:
                     e["fin"] = fin
                     pending -= 1

@@ -104,6 +104,9 @@ class EngineDriver:
                         eng.llm.core.cancel(sid)
                         fin = "stop"
                         break
+                if fin is None and eng.constraint_finished(a["state"]):
+                    eng.llm.core.cancel(sid)
+                    fin = "stop"
                 if delta.endswith("�") and fin is None:
                     delta = ""  # incomplete UTF-8 sequence: wait for the next token
                 a["emitted"] += delta
@@ -128,7 +131,32 @@ def _options_from_request(body: dict, default_max: int, max_cap: int) -> Generat
         lp = 1
     if lp and int(lp) > 20:
         raise HTTPException(400, "top_logprobs must be <= 20")
+    constraint = None
+    rf = body.get("response_format") or {}
+    if rf.get("type") == "json_object":
+        constraint = ("json_object",)
+    elif rf.get("type") == "json_schema":
+        schema = (rf.get("json_schema") or {}).get("schema")
+        if schema is None:
+            raise HTTPException(400, "response_format.json_schema.schema is required when type is 'json_schema'")
+        constraint = ("json_schema", schema)
+    elif rf.get("type") not in (None, "text"):
+        raise HTTPException(400, f"response_format.type {rf.get('type')!r} is not supported; use text, json_object or json_schema")
+    if body.get("guided_regex"):
+        constraint = ("regex", str(body["guided_regex"]))
+    elif body.get("guided_choice"):
+        constraint = ("choice", list(body["guided_choice"]))
+    elif body.get("guided_json") is not None:
+        constraint = ("json_schema", body["guided_json"])
+    if constraint is not None:
+        from ..engine import constraints as _cons
+
+        try:
+            _cons.make_constraint(constraint)      # reject unsupported schemas / patterns before queueing
+        except ValueError as exc:
+            raise HTTPException(400, str(exc)) from exc
     return GenerateOptions(
+        constraint=constraint,
         max_new_tokens=mt, temperature=temperature, greedy=(temperature == 0.0), top_p=float(body.get("top_p") or 1.0),
         top_k=int(body.get("top_k") or 0), min_p=float(body.get("min_p") or 0.0), top_a=float(body.get("top_a") or 0.0),
         typical_p=float(body.get("typical_p") or 1.0), repetition_penalty=float(body.get("repetition_penalty") or 1.0),
