@@ -155,6 +155,7 @@ class Engine:
 
             eos = eos_token_ids(d.genai_config) or eos
         cfg = cfg.replace(eos_token=eos[0] if eos else -1)
+        engine_kw.setdefault("cuda_graphs", str(device).startswith("cuda"))
         ecfg = EngineConfig(model=cfg, num_pages=num_pages, max_seqs=max_seqs, max_seq_len=max_seq_len,
                             max_tokens_per_step=max_tokens_per_step, prefill_chunk=meta.chunked_prefill_size or 2048,
                             kv_dtype=kv_dtype, max_draft_tokens=max_draft_tokens, **engine_kw)

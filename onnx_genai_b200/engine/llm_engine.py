@@ -50,6 +50,7 @@ class EngineConfig:
     sync_sampled_tokens: bool = True   # TP: broadcast rank 0's tokens so replicas cannot diverge
     max_draft_tokens: int = 0          # speculative decoding: drafts verified per sequence per step
     native_executor: bool = True       # launch the layer stack from the C++ step executor when possible
+    cuda_graphs: bool = False          # replay decode-only steps (forward + sampler) from captured CUDA graphs
     seed: int = 0
 
 
@@ -145,6 +146,11 @@ class LLMEngine:
         self.steps = 0
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        # CUDA graphs of decode-only steps, keyed by (row bucket, KV splits, sampler kind).  A capture that
+        # fails is a decline, not an error: the bucket is marked and the step runs eagerly from then on.
+        self.graphs: dict = {}
+        self.graph_replays = 0
+        self.graph_declines: list = []
 
     # --------------------------------------------------------------------------------------
     def add_request(self, prompt_ids, max_new_tokens=256, temperature=0.0, top_k=0, top_p=1.0, min_p=0.0, seed=0,
@@ -197,6 +203,69 @@ class LLMEngine:
             s *= 2
         return s
 
+    # ---- CUDA graphs for decode-only steps -------------------------------------------------
+    GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512)
+
+    def _graph_eligible(self, si, r, hdr) -> bool:
+        return (self.cfg.cuda_graphs and self.device.type == "cuda" and self.native_executor and self.tp == 1
+                and si.num_prefill_seqs == 0 and si.num_tiles == 0 and si.num_decode == si.num_tokens == r and r > 0
+                and r <= min(self.cfg.max_seqs, self.GRAPH_BUCKETS[-1]))
+
+    def _graph_step(self, si, r) -> bool:
+        """Run a decode-only step of r rows as a graph replay over the next row bucket.  Rows r..bucket are
+        padding: token 0 at position 0, no KV slot, context length 0 (idle in attention), greedy."""
+        bucket = next(b for b in self.GRAPH_BUCKETS if b >= r)
+        if bucket > self.cfg.max_seqs or bucket > self.cfg.max_tokens_per_step:
+            return False
+        L, pn = self.L, self.plan_np
+        temps = pn[L.temperature:L.temperature + r].view(np.float32)
+        greedy = bool((temps <= 0).all())
+        key = (bucket, self.model.decode_splits, greedy)
+        entry = self.graphs.get(key)
+        if entry is False:
+            return False
+        if bucket > r:
+            pn[L.token_ids + r:L.token_ids + bucket] = 0
+            pn[L.positions + r:L.positions + bucket] = 0
+            pn[L.slots + r:L.slots + bucket] = -1
+            pn[L.ctx_len + r:L.ctx_len + bucket] = 0
+            pn[L.logit_rows + r:L.logit_rows + bucket] = np.arange(r, bucket, dtype=np.int32)
+            pn[L.temperature + r:L.temperature + bucket] = 0          # 0.0f: padded rows take the argmax path
+            self.plan_dev.copy_(self.plan_host[: self.dev_words], non_blocking=True)
+            self.h2d_bytes += self.dev_words * 4
+        saved = (si.num_tokens, si.num_decode, si.num_logit_rows)
+        si.num_tokens = si.num_decode = si.num_logit_rows = bucket
+
+        def body():
+            logits = self.model.forward(si, self.kv)
+            if greedy:
+                ops.argmax(logits, out=self.sampled_dev[:bucket])
+            else:
+                ops.sample(logits, self.temperature[:bucket], self.top_k[:bucket], self.top_p[:bucket], self.min_p[:bucket],
+                           self.uniform[:bucket], work=self.sample_work, out=self.sampled_dev[:bucket])
+
+        try:
+            if entry is None:
+                body()                                   # eager warm-up: one-time setup must not land in the capture
+                torch.cuda.current_stream().synchronize()
+                g = torch.cuda.CUDAGraph()
+                try:
+                    with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                        body()
+                except Exception as exc:                 # decline: remember why, fall back to eager for this bucket
+                    self.graphs[key] = False
+                    self.graph_declines.append((key, repr(exc)))
+                    return False
+                self.graphs[key] = g
+                # the warm-up already produced this step's tokens
+                return True
+            entry.replay()
+            self.graph_replays += 1
+            ops.launch_counts["graph_replay"] += 1
+            return True
+        finally:
+            si.num_tokens, si.num_decode, si.num_logit_rows = saved
+
     def step(self) -> StepOutput:
         """Schedule, run and commit one engine step."""
         out = StepOutput()
@@ -225,10 +294,16 @@ class LLMEngine:
             splits = self._pick_splits(si.num_decode, si.max_ctx)
             if splits != self.model.decode_splits:
                 self.model.set_decode_splits(splits)
-        logits = self.model.forward(si, self.kv)
+                self.graphs.clear()          # split scratch was reallocated: captured pointers are stale
+        graphed = self._graph_step(si, r) if self._graph_eligible(si, r, hdr) else False
+        logits = self.model.logits[:r] if graphed else self.model.forward(si, self.kv)
         if r > 0:
             temps = self.plan_np[self.L.temperature:self.L.temperature + r].view(np.float32)
-            if self.device.type == "cuda":
+            if graphed:
+                self.sampled_host[:r].copy_(self.sampled_dev[:r], non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                self.d2h_bytes += r * 4
+            elif self.device.type == "cuda":
                 if (temps <= 0).all():
                     ops.argmax(logits, out=self.sampled_dev[:r])
                 else:

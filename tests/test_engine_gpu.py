@@ -112,3 +112,21 @@ def test_int4_package_runs_in_kernel_dequant_on_gpu(tmp_path):
     ops.check_status()
     for a, b in zip(outs["cuda"], outs["cpu"]):
         assert float((a - b).norm() / b.norm()) < 4e-2
+
+
+def test_cuda_graph_replay_of_decode_steps_matches_eager():
+    """Decode-only steps replayed from captured graphs (padded to a row bucket) give the eager tokens."""
+    rng = np.random.default_rng(4)
+    prompts = [rng.integers(0, CFG.vocab, size=n).astype(np.int32) for n in (9, 40, 3, 120, 17)]   # 5 rows -> bucket 8
+    outs = {}
+    for graphs in (False, True):
+        eng = LLMEngine(EngineConfig(model=CFG, num_pages=256, max_seqs=16, max_tokens_per_step=256, max_seq_len=512,
+                                     cuda_graphs=graphs), device="cuda")
+        for sampling in (dict(temperature=0.0), dict(temperature=0.9, top_p=0.8, seed=5)):
+            outs[(graphs, sampling["temperature"])] = eng.generate(prompts, max_new_tokens=20, **sampling)
+        ops.check_status()
+        if graphs:
+            assert not eng.graph_declines, eng.graph_declines
+            assert eng.graph_replays >= 30 and len(eng.graphs) == 2      # one graph per sampler kind, many replays
+    assert outs[(True, 0.0)] == outs[(False, 0.0)]
+    assert outs[(True, 0.9)] == outs[(False, 0.9)]
