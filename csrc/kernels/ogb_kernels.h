@@ -74,6 +74,9 @@ int ogb_kv_scatter_pages(void* pool, const void* staging, const int64_t* pages, 
 // qweight [N, K/32, 16] uint8 (low nibble = even k), scales [N, K/32] bf16 or fp32, zp [N, ceil(K/32/2)] or NULL.
 int ogb_w4a16_gemv(const void* x, const void* qweight, const void* scales, const void* zp, const void* bias, void* y,
                    int M, int N, int K, int ldx, int ldy, int scales_fp32, void* stream);
+int ogb_w4a16_gemv_fused(const void* x, const void* qweight, const void* scales, const void* zp, const void* bias,
+                         const void* norm_w, const void* residual, void* y, int M, int N, int K, int ldx, int ldy, int ldr,
+                         float eps, int prologue, int scales_fp32, void* stream);
 int ogb_w4a16_dequant(const void* qweight, const void* scales, const void* zp, void* w_bf16, int N, int K,
                       int scales_fp32, void* stream);
 

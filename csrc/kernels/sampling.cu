@@ -516,10 +516,71 @@ spec_verify_greedy_kernel(const __nv_bfloat16* __restrict__ logits, const int* _
 
 using namespace ogb;
 
+// ------------------------------------------------------------------------------------------
+// Split argmax for few rows: with one CTA per row a batch-1 decode step spends 70 us scanning 152 k logits
+// with 2-byte loads.  Here `parts` CTAs share a row, each scans its slice with 16-byte loads and folds its
+// best (value, index) into a per-row 64-bit key with atomicMax: the high word is the float in an order-
+// preserving integer form, the low word ~index, so the largest value wins and ties go to the lowest index.
+// The last CTA of a row to finish decodes the key into the token id and resets the row's words.  The words
+// live in the library image, so launches on one device must not overlap (the engine has one stream).
+// ------------------------------------------------------------------------------------------
+constexpr int kArgmaxMaxRows = 1024;
+static __device__ unsigned long long g_argmax_key[kArgmaxMaxRows];
+static __device__ unsigned int g_argmax_done[kArgmaxMaxRows];
+
+__global__ void __launch_bounds__(kSampleThreads) argmax_split_kernel(const __nv_bfloat16* __restrict__ logits,
+                                                                       int* __restrict__ out, int vocab, int ld, int per_part) {
+  __shared__ ArgMax sh[32];
+  const int row = blockIdx.y, part = blockIdx.x;
+  const __nv_bfloat16* r = logits + static_cast<size_t>(row) * ld;
+  const int begin = part * per_part;                       // per_part is a multiple of 8
+  const int end = min(vocab, begin + per_part);
+  ArgMax best{-INFINITY, 0x7fffffff};
+  const int nvec = (end - begin) / 8;
+  for (int vi = threadIdx.x; vi < nvec; vi += blockDim.x) {
+    const uint4 q = *reinterpret_cast<const uint4*>(r + begin + vi * 8);
+    const uint32_t ws[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = unpack_bf16(ws[e]);
+      if (f.x > best.v) { best.v = f.x; best.i = begin + vi * 8 + 2 * e; }
+      if (f.y > best.v) { best.v = f.y; best.i = begin + vi * 8 + 2 * e + 1; }
+    }
+  }
+  for (int i = begin + nvec * 8 + threadIdx.x; i < end; i += blockDim.x) {
+    const float v = __bfloat162float(r[i]);
+    if (v > best.v) { best.v = v; best.i = i; }
+  }
+  best = block_argmax(best, sh);
+  if (threadIdx.x == 0) {
+    if (best.i != 0x7fffffff) {
+      const uint32_t bits = __float_as_uint(best.v);
+      const uint32_t ord = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+      atomicMax(&g_argmax_key[row], (static_cast<unsigned long long>(ord) << 32) | (0xffffffffu - static_cast<uint32_t>(best.i)));
+    }
+    __threadfence();
+    if (atomicAdd(&g_argmax_done[row], 1u) == gridDim.x - 1) {
+      const unsigned long long key = atomicExch(&g_argmax_key[row], 0ull);
+      out[row] = (key == 0ull) ? 0 : static_cast<int>(0xffffffffu - static_cast<uint32_t>(key & 0xffffffffull));
+      g_argmax_done[row] = 0;
+    }
+  }
+}
+
 extern "C" int ogb_argmax_bf16(const void* logits, int* out_tokens, int rows, int vocab, int ld, void* stream) {
   if (rows <= 0) return 0;
-  argmax_kernel<<<rows, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(logits), out_tokens, vocab, ld);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool vec_ok = (ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(logits) & 15) == 0);
+  int parts = (2 * ogb_num_sms() + rows - 1) / rows;
+  if (parts > 16) parts = 16;
+  if (parts > vocab / 8192) parts = vocab / 8192;
+  if (vec_ok && parts >= 2 && rows <= kArgmaxMaxRows) {
+    const int per_part = ((vocab + parts - 1) / parts + 7) / 8 * 8;
+    argmax_split_kernel<<<dim3(parts, rows), kSampleThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(logits), out_tokens,
+                                                                     vocab, ld, per_part);
+    return static_cast<int>(cudaGetLastError());
+  }
+  argmax_kernel<<<rows, kSampleThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(logits), out_tokens, vocab, ld);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -165,6 +165,204 @@ __global__ void w4a16_dequant_kernel(const uint8_t* __restrict__ qw, const void*
   }
 }
 
+
+// ------------------------------------------------------------------------------------------
+// Fused decode-size projection: optional prologue on the activations (RMSNorm, or SiLU(gate)*up), int4
+// GEMV, optional residual add in the epilogue.  One launch replaces norm + GEMV, or silu_mul + GEMV +
+// residual add (the reference fuses the same neighbours: gate_up+SwiGLU and RMSNorm-prologue GEMVs,
+// crates/onnx-runtime-ep-cuda/src/optimizer.rs:27-60).
+//
+// The kernel is specialised on the row count MT in {1,2,4,8} so the M=1 code stays small: with one
+// generic 8-row body the unrolled kernel was dominated by instruction fetch (22-35 us per launch for
+// matrices that stream in 1-2 us).  Activations are staged once per CTA in shared memory as bf16 -- after
+// the prologue, rounded exactly as the unfused path rounds them -- in chunks of kGemvChunk values of K.
+// Each warp owns kFusedCols output columns; lanes stride over the 32-weight blocks of a chunk.
+// ------------------------------------------------------------------------------------------
+constexpr int kFusedCols = 2;
+constexpr int kFusedWarps = 8;
+constexpr int kGemvChunk = 4096;   // K values staged per pass (8 rows x 4096 x 2 B = 64 KB of shared memory)
+
+enum : int { kProNone = 0, kProRmsNorm = 1, kProSiluMul = 2 };
+
+struct GemvFusedParams {
+  const __nv_bfloat16* x;        // [M, ldx]; kProSiluMul: gate at [0, K), up at [K, 2K)
+  const uint8_t* qw;
+  const void* scales;
+  const uint8_t* zp;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* norm_w;   // kProRmsNorm: [K]
+  const __nv_bfloat16* resid;    // optional [M, ldr], added in the epilogue (may alias y)
+  __nv_bfloat16* y;              // [M, ldy]
+  int M, N, K, ldx, ldy, ldr;
+  float eps;
+};
+
+template <int MT, int PRO, bool SCALES_F32>
+__global__ void __launch_bounds__(kFusedWarps * 32) w4a16_gemv_fused_kernel(const GemvFusedParams p) {
+  extern __shared__ __align__(16) uint8_t gemv_smem[];
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(gemv_smem);   // [MT][kGemvChunk]
+  __shared__ float rstd_sh[MT];
+  __shared__ float red_sh[kFusedWarps][MT];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int K = p.K, N = p.N, M = p.M;
+  const int kb = (K + 31) / 32;
+  const int zp_stride = (kb + 1) / 2;
+
+  if constexpr (PRO == kProRmsNorm) {
+    float ss[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) ss[m] = 0.f;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        if (m < M) {
+          const float v = __bfloat162float(p.x[static_cast<size_t>(m) * p.ldx + k]);
+          ss[m] += v * v;
+        }
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      const float v = warp_sum(ss[m]);
+      if (lane == 0) red_sh[warp][m] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < MT) {
+      float t = 0.f;
+      for (int w = 0; w < kFusedWarps; ++w) t += red_sh[w][threadIdx.x];
+      rstd_sh[threadIdx.x] = rsqrtf(t / static_cast<float>(K) + p.eps);
+    }
+    __syncthreads();
+  }
+
+  const int n0 = (blockIdx.x * kFusedWarps + warp) * kFusedCols;
+  float acc[kFusedCols][MT];
+#pragma unroll
+  for (int c = 0; c < kFusedCols; ++c)
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[c][m] = 0.f;
+
+  for (int k0 = 0; k0 < K; k0 += kGemvChunk) {
+    const int klen = min(kGemvChunk, K - k0);
+    const int klen_pad = (klen + 31) / 32 * 32;
+    if (k0 > 0) __syncthreads();                 // every warp is done with the previous chunk
+    for (int i = threadIdx.x; i < klen_pad; i += blockDim.x) {
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        float v = 0.f;
+        if (m < M && i < klen) {
+          const size_t row = static_cast<size_t>(m) * p.ldx;
+          if constexpr (PRO == kProSiluMul) {
+            const float g = __bfloat162float(p.x[row + k0 + i]);
+            const float u = __bfloat162float(p.x[row + K + k0 + i]);
+            v = g / (1.f + __expf(-g)) * u;
+          } else if constexpr (PRO == kProRmsNorm) {
+            v = __bfloat162float(p.x[row + k0 + i]) * rstd_sh[m] * __bfloat162float(p.norm_w[k0 + i]);
+          } else {
+            v = __bfloat162float(p.x[row + k0 + i]);
+          }
+        }
+        xs[m * kGemvChunk + i] = __float2bfloat16(v);
+      }
+    }
+    __syncthreads();
+    if (n0 < N) {
+      const int b0 = k0 / 32, b1 = b0 + klen_pad / 32;
+      for (int b = b0 + lane; b < b1; b += 32) {
+        uint4 wq[kFusedCols];
+        float sc[kFusedCols], zz[kFusedCols];
+#pragma unroll
+        for (int c = 0; c < kFusedCols; ++c) {
+          const int n = min(n0 + c, N - 1);
+          wq[c] = __ldg(reinterpret_cast<const uint4*>(p.qw + (static_cast<size_t>(n) * kb + b) * 16));
+          sc[c] = load_scale<SCALES_F32>(p.scales, static_cast<size_t>(n) * kb + b);
+          zz[c] = 8.f;
+          if (p.zp != nullptr) {
+            const uint8_t zb = p.zp[static_cast<size_t>(n) * zp_stride + (b >> 1)];
+            zz[c] = static_cast<float>((b & 1) ? (zb >> 4) : (zb & 0xF));
+          }
+        }
+        float dot[kFusedCols][MT], xsum[MT];
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          xsum[m] = 0.f;
+#pragma unroll
+          for (int c = 0; c < kFusedCols; ++c) dot[c][m] = 0.f;
+        }
+        const __nv_bfloat16* xb = xs + (b - b0) * 32;
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+          float f[kFusedCols][8];
+#pragma unroll
+          for (int c = 0; c < kFusedCols; ++c) {
+            const uint32_t word = (wi == 0) ? wq[c].x : (wi == 1) ? wq[c].y : (wi == 2) ? wq[c].z : wq[c].w;
+            nibbles_to_float(word, f[c]);
+          }
+#pragma unroll
+          for (int m = 0; m < MT; ++m) {
+            const uint4 q = *reinterpret_cast<const uint4*>(xb + m * kGemvChunk + 8 * wi);
+            float xv[8];
+            float2 t;
+            t = unpack_bf16(q.x); xv[0] = t.x; xv[1] = t.y;
+            t = unpack_bf16(q.y); xv[2] = t.x; xv[3] = t.y;
+            t = unpack_bf16(q.z); xv[4] = t.x; xv[5] = t.y;
+            t = unpack_bf16(q.w); xv[6] = t.x; xv[7] = t.y;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              xsum[m] += xv[i];
+#pragma unroll
+              for (int c = 0; c < kFusedCols; ++c) dot[c][m] += f[c][i] * xv[i];
+            }
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < kFusedCols; ++c)
+#pragma unroll
+          for (int m = 0; m < MT; ++m) acc[c][m] += sc[c] * (dot[c][m] - zz[c] * xsum[m]);
+      }
+    }
+  }
+  if (n0 >= N) return;
+#pragma unroll
+  for (int c = 0; c < kFusedCols; ++c) {
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      float v = warp_sum(acc[c][m]);
+      const int n = n0 + c;
+      if (lane == 0 && m < M && n < N) {
+        if (p.bias != nullptr) v += __bfloat162float(p.bias[n]);
+        if (p.resid != nullptr) v += __bfloat162float(p.resid[static_cast<size_t>(m) * p.ldr + n]);
+        p.y[static_cast<size_t>(m) * p.ldy + n] = __float2bfloat16(v);
+      }
+    }
+  }
+}
+
+template <int MT, int PRO>
+static int launch_gemv_fused(const GemvFusedParams& p, bool scales_fp32, cudaStream_t st) {
+  const int warps_needed = (p.N + kFusedCols - 1) / kFusedCols;
+  const int blocks = (warps_needed + kFusedWarps - 1) / kFusedWarps;
+  const size_t smem = static_cast<size_t>(MT) * kGemvChunk * sizeof(__nv_bfloat16);
+  if (scales_fp32) {
+    auto kern = w4a16_gemv_fused_kernel<MT, PRO, true>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    kern<<<blocks, kFusedWarps * 32, smem, st>>>(p);
+  } else {
+    auto kern = w4a16_gemv_fused_kernel<MT, PRO, false>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    kern<<<blocks, kFusedWarps * 32, smem, st>>>(p);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <int PRO>
+static int dispatch_gemv_fused(const GemvFusedParams& p, bool scales_fp32, cudaStream_t st) {
+  if (p.M <= 1) return launch_gemv_fused<1, PRO>(p, scales_fp32, st);
+  if (p.M <= 2) return launch_gemv_fused<2, PRO>(p, scales_fp32, st);
+  if (p.M <= 4) return launch_gemv_fused<4, PRO>(p, scales_fp32, st);
+  return launch_gemv_fused<8, PRO>(p, scales_fp32, st);
+}
+
 }  // namespace ogb
 
 using namespace ogb;
@@ -201,4 +399,31 @@ extern "C" int ogb_w4a16_dequant(const void* qweight, const void* scales, const 
     w4a16_dequant_kernel<false><<<blocks, 256, 0, st>>>(static_cast<const uint8_t*>(qweight), scales,
                                                        static_cast<const uint8_t*>(zp), static_cast<__nv_bfloat16*>(w_bf16), N, K);
   return static_cast<int>(cudaGetLastError());
+}
+
+// y[M,N] = prologue(x)[M,K] . dequant(W)^T (+ bias) (+ residual).  prologue: 0 none, 1 RMSNorm with norm_w/eps,
+// 2 SiLU(x[:, :K]) * x[:, K:2K].  M <= 8; K, ldx multiples of 8.  `residual` may alias `y`.
+extern "C" int ogb_w4a16_gemv_fused(const void* x, const void* qweight, const void* scales, const void* zp, const void* bias,
+                                    const void* norm_w, const void* residual, void* y, int M, int N, int K, int ldx, int ldy,
+                                    int ldr, float eps, int prologue, int scales_fp32, void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > kGemvMaxM || K <= 0) return -3;
+  if (prologue == kProRmsNorm && norm_w == nullptr) return -3;
+  GemvFusedParams p;
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.qw = static_cast<const uint8_t*>(qweight);
+  p.scales = scales;
+  p.zp = static_cast<const uint8_t*>(zp);
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.norm_w = static_cast<const __nv_bfloat16*>(norm_w);
+  p.resid = static_cast<const __nv_bfloat16*>(residual);
+  p.y = static_cast<__nv_bfloat16*>(y);
+  p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.ldy = ldy; p.ldr = ldr; p.eps = eps;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (prologue) {
+    case kProNone: return dispatch_gemv_fused<kProNone>(p, scales_fp32 != 0, st);
+    case kProRmsNorm: return dispatch_gemv_fused<kProRmsNorm>(p, scales_fp32 != 0, st);
+    case kProSiluMul: return dispatch_gemv_fused<kProSiluMul>(p, scales_fp32 != 0, st);
+    default: return -3;
+  }
 }

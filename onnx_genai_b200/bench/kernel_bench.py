@@ -182,6 +182,21 @@ def ncu_case(name: str, iters: int = 3):
                 ops.gemm(a, w, residual=res, epilogue="residual", out=out)
             else:
                 ops.gemm(a, w, out=out)
+    elif name == "decode_step_0p5b_int4":
+        # whole decode steps of the Qwen2.5-0.5B-shape int4 model at batch 1 (512-token prompt), launched one kernel
+        # at a time so a launch list shows the device time of every kernel of a step
+        import tempfile
+
+        import numpy as np
+
+        from onnx_genai_b200.bench.config_bench import _export
+        from onnx_genai_b200.engine.api import Engine, GenerateOptions
+
+        with tempfile.TemporaryDirectory() as tmp:
+            cfg = _export("qwen2.5-0.5b", tmp, "bf16")
+            eng = Engine.from_dir(tmp, device="cuda", max_seqs=1, max_seq_len=640, cuda_graphs=False)
+            prompt = np.random.default_rng(0).integers(0, cfg.vocab, size=512).tolist()
+            eng.generate_batch([prompt], GenerateOptions(max_new_tokens=1 + iters, greedy=True, ignore_eos=True))
     elif name == "decode":
         n, ctx = 256, 1200
         pages_per = (ctx + 15) // 16

@@ -196,10 +196,10 @@ class LLMEngine:
             return self.cfg.decode_splits
         ctas = nd * self.model.hkv
         target = 2 * 148
-        if ctas >= target or max_ctx < 1024:
+        if ctas >= target or max_ctx < 256:
             return 1
         s = 1
-        while ctas * s < target and s < 32 and max_ctx // (s * 2) >= 256:
+        while ctas * s < target and s < 32 and max_ctx // (s * 2) >= 128:
             s *= 2
         return s
 
@@ -207,7 +207,7 @@ class LLMEngine:
     GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512)
 
     def _graph_eligible(self, si, r, hdr) -> bool:
-        return (self.cfg.cuda_graphs and self.device.type == "cuda" and self.native_executor and self.tp == 1
+        return (self.cfg.cuda_graphs and self.device.type == "cuda" and self.tp == 1
                 and si.num_prefill_seqs == 0 and si.num_tiles == 0 and si.num_decode == si.num_tokens == r and r > 0
                 and r <= min(self.cfg.max_seqs, self.GRAPH_BUCKETS[-1]))
 

@@ -214,6 +214,12 @@ class DecoderModel:
                     mk = lambda lin: QuantLinear(lin.q, lin.scales, lin.zp, lin.bias, lin.k, lin.block, dev)
                     l.quant = {"qkv": [mk(p) for p in l.quant["qkv"]], "o": mk(l.quant["o"]), "gate": mk(l.quant["gate"]),
                                "up": mk(l.quant["up"]), "down": mk(l.quant["down"])}
+                    # sibling projections of one input become one launch (the reference does this in its
+                    # CudaQkvProjectionFusion / gate_up fusion passes, ep-cuda/src/optimizer.rs:64-83,3175)
+                    merged_qkv = QuantLinear.merge(l.quant["qkv"])
+                    if merged_qkv is not None:
+                        l.quant["qkv"] = [merged_qkv]
+                    l.quant["gate_up"] = QuantLinear.merge([l.quant["gate"], l.quant["up"]])
             inter_q = weights.layers[0].quant["gate"].n
             self.partial = z(max_tokens, hid)
             self.gate_up = z(max_tokens, 2 * inter_q)
@@ -311,8 +317,30 @@ class DecoderModel:
         x, h, qkv, attn = self.x[:t], self.h[:t], self.qkv[:t], self.attn[:t]
         ops.embedding(si.token_ids[:t], w.embed, out=x) if x.is_cuda else x.copy_(w.embed[si.token_ids[:t].long()])
         pending = None  # partial sums still to be added to the residual (TP only)
+        # int4 layers at decode size: norm, SwiGLU glue and residual adds live inside the GEMV launches
+        fused_q = (x.is_cuda and t <= 8 and self.tp == 1 and all(l.quant and len(l.quant["qkv"]) == 1 and
+                                                                 l.quant.get("gate_up") is not None for l in w.layers))
         for li, lw in enumerate(w.layers):
             pool = kv.pools[li]
+            if fused_q:
+                lw.quant["qkv"][0].fused(x, qkv, norm_weight=lw.ln1, eps=cfg.rms_eps)
+                ops.rope_kv_append(qkv, si.positions[:t], si.slots[:t], self.cos_sin, pool, self.hq, self.hkv, self.d,
+                                   self.rotary_dim, cfg.rotary_interleaved,
+                                   kv_scales=kv.scales[li] if kv.scales is not None else None)
+                if nd > 0:
+                    ops.paged_decode(qkv[:nd], attn[:nd], pool, si.page_table[:nd], si.ctx_len[:nd], self.hq, self.hkv,
+                                     self.d, self.scale, self.decode_splits, self.part_o, self.part_ml, cfg.sliding_window,
+                                     kv_scales=kv.scales[li] if kv.scales is not None else None)
+                if si.num_prefill_seqs > 0:
+                    np_ = si.num_prefill_seqs
+                    ops.paged_prefill(qkv[nd:], attn[nd:], pool, si.page_table[nd:nd + np_], si.ctx_len[nd:nd + np_],
+                                      si.cu_q, si.tile_seq, si.tile_q0, si.num_tiles, self.hq, self.hkv, self.d, self.scale,
+                                      cfg.sliding_window, kv_scales=kv.scales[li] if kv.scales is not None else None)
+                lw.quant["o"].fused(attn, x, residual=x)
+                gu = self.gate_up[:t, : 2 * lw.quant["gate"].n]
+                lw.quant["gate_up"].fused(x, gu, norm_weight=lw.ln2, eps=cfg.rms_eps)
+                lw.quant["down"].fused(gu, x, silu_mul=True, residual=x)
+                continue
             self._norm(x, lw.ln1, pending, h)
             if lw.quant:
                 c0 = 0
@@ -338,8 +366,11 @@ class DecoderModel:
                 self._norm(x, lw.ln2, pending, h)
                 inter = lw.quant["gate"].n
                 gu = self.gate_up[:t, : 2 * inter]
-                lw.quant["gate"](h, out=gu[:, :inter])
-                lw.quant["up"](h, out=gu[:, inter:])
+                if lw.quant.get("gate_up") is not None:
+                    lw.quant["gate_up"](h, out=gu)
+                else:
+                    lw.quant["gate"](h, out=gu[:, :inter])
+                    lw.quant["up"](h, out=gu[:, inter:])
                 act = ops.silu_mul(gu, out=self.act_q[:t]) if x.is_cuda else ops.silu_mul(gu)
                 pending = lw.quant["down"](act, out=self.partial[:t])
                 continue

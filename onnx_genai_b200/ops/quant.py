@@ -11,6 +11,9 @@ from . import gemm as _gemm
 GEMV_MAX_M = 8
 _native.register("ogb_w4a16_gemv", [_native.P] * 6 + [_native.I] * 6 + [_native.P])
 _native.register("ogb_w4a16_dequant", [_native.P] * 4 + [_native.I] * 3 + [_native.P])
+_native.register("ogb_w4a16_gemv_fused", [_native.P] * 8 + [_native.I] * 6 + [_native.F] + [_native.I] * 2 + [_native.P])
+PRO_NONE, PRO_RMSNORM, PRO_SILU_MUL = 0, 1, 2
+_LEGACY_GEMV = __import__("os").environ.get("OGB_W4A16_LEGACY", "0") == "1"   # A/B switch: the unspecialised 8-row GEMV
 
 
 class QuantLinear:
@@ -28,9 +31,52 @@ class QuantLinear:
         self.bias = bias.to(torch.bfloat16).contiguous().to(dev) if bias is not None else None
         self._scratch = None
 
+    # Above the GEMV range the tcgen05 GEMM needs bf16 weights.  With cache_dense the dequantised copy is
+    # built once per projection and kept (a one-time repack, as the reference keeps its interleaved-weight
+    # cache, crates/onnx-runtime-ep-cuda/src/interleave_cache.rs); without it the copy is rebuilt into a
+    # scratch buffer on every call, which costs a full weight write + read per step.
+    cache_dense = True
+
+    @classmethod
+    def merge(cls, parts):
+        """One projection that computes the concatenation of ``parts`` along N (same K, same quantisation form)."""
+        parts = list(parts)
+        first = parts[0]
+        if len(parts) == 1:
+            return first
+        if any(p.k != first.k or (p.zp is None) != (first.zp is None) or p.scales.dtype != first.scales.dtype for p in parts):
+            return None
+        bias = None
+        if any(p.bias is not None for p in parts):
+            bias = torch.cat([p.bias if p.bias is not None else torch.zeros(p.n, dtype=torch.bfloat16, device=p.qweight.device)
+                              for p in parts])
+        zp = torch.cat([p.zp for p in parts]) if first.zp is not None else None
+        return cls(torch.cat([p.qweight for p in parts]), torch.cat([p.scales for p in parts]), zp, bias, first.k, 32,
+                   first.qweight.device)
+
     def dense(self, dtype=torch.float32):
         return reference.dequant_w4(self.qweight.cpu(), self.scales.float().cpu(), self.zp.cpu() if self.zp is not None else None,
                                     32, self.k).to(dtype)
+
+    def fused(self, x, out, norm_weight=None, eps=0.0, silu_mul=False, residual=None):
+        """Decode-size rows (M <= 8) on the GPU in one launch: ``out = prologue(x) @ W^T (+ bias) (+ residual)``
+        with prologue = RMSNorm(x, norm_weight, eps), or SiLU(x[:, :K]) * x[:, K:], or nothing."""
+        m = x.shape[0]
+        assert x.is_cuda and m <= GEMV_MAX_M and x.stride(1) == 1 and out.stride(1) == 1
+        pro = PRO_RMSNORM if norm_weight is not None else (PRO_SILU_MUL if silu_mul else PRO_NONE)
+        if silu_mul:
+            assert x.shape[1] == 2 * self.k
+        lib = _native.load()
+        with timed_region("w4a16_gemv_fused"):
+            rc = lib.ogb_w4a16_gemv_fused(
+                x.data_ptr(), self.qweight.data_ptr(), self.scales.data_ptr(), self.zp.data_ptr() if self.zp is not None else 0,
+                self.bias.data_ptr() if self.bias is not None else 0, norm_weight.data_ptr() if norm_weight is not None else 0,
+                residual.data_ptr() if residual is not None else 0, out.data_ptr(), m, self.n, self.k, x.stride(0), out.stride(0),
+                residual.stride(0) if residual is not None else 0, float(eps), pro, int(self.scales_fp32),
+                torch.cuda.current_stream().cuda_stream)
+        _native.check(rc, "ogb_w4a16_gemv_fused")
+        launch_counts["w4a16_gemv_fused"] += 1
+        return out
 
     def __call__(self, x, out=None):
         m = x.shape[0]
@@ -51,6 +97,8 @@ class QuantLinear:
             out = torch.empty(m, self.n, dtype=torch.bfloat16, device=x.device)
         lib = _native.load()
         stream = torch.cuda.current_stream().cuda_stream
+        if m <= GEMV_MAX_M and not _LEGACY_GEMV and x.stride(1) == 1:
+            return self.fused(x, out)
         if m <= GEMV_MAX_M:
             with timed_region("w4a16_gemv"):
                 rc = lib.ogb_w4a16_gemv(x.data_ptr(), self.qweight.data_ptr(), self.scales.data_ptr(),
@@ -60,6 +108,8 @@ class QuantLinear:
             _native.check(rc, "ogb_w4a16_gemv")
             launch_counts["w4a16_gemv"] += 1
             return out
+        if self._scratch is not None and self.cache_dense:
+            return _gemm(x, self._scratch, bias=self.bias, out=out)
         if self._scratch is None:
             self._scratch = torch.empty(self.n, self.k, dtype=torch.bfloat16, device=x.device)
         with timed_region("w4a16_dequant"):

@@ -101,14 +101,14 @@ def test_int4_package_runs_in_kernel_dequant_on_gpu(tmp_path):
     outs = {}
     for dev in ("cuda", "cpu"):
         eng = Engine.from_dir(d, device=dev, num_pages=64, max_seqs=4, max_tokens_per_step=64)
-        before = ops.launch_counts["w4a16_gemv"]
+        before = ops.launch_counts["w4a16_gemv_fused"]
         eng.llm.add_request(np.arange(3, 40, dtype=np.int32), 3)
         eng.llm.step()
         first = eng.llm.model.logits[:1].float().cpu().clone()
         eng.llm.step()
         outs[dev] = (first, eng.llm.model.logits[:1].float().cpu().clone())
         if dev == "cuda":
-            assert not eng.llm.native_executor and ops.launch_counts["w4a16_gemv"] > before
+            assert not eng.llm.native_executor and ops.launch_counts["w4a16_gemv_fused"] > before
     ops.check_status()
     for a, b in zip(outs["cuda"], outs["cpu"]):
         assert float((a - b).norm() / b.norm()) < 4e-2

@@ -272,7 +272,42 @@ def test_w4a16_linear(m, n, k, sym, fp32_scales):
     ops.check_status()
     want = x.float().cpu() @ ref.dequant_w4(q, s.float(), zp, 32, k).t() + bias.bfloat16().float()
     assert _rel_err(got.cpu(), want) < 1.2e-2
-    assert ops.launch_counts["w4a16_gemv" if m <= 8 else "w4a16_dequant"] > 0
+    assert ops.launch_counts["w4a16_gemv_fused" if m <= 8 else "w4a16_dequant"] > 0
+
+
+@pytest.mark.parametrize("m,n,k,sym", [(1, 896, 896, True), (2, 1152, 896, False), (4, 128, 4864, True), (7, 100, 688, False), (8, 64, 9000, True)])
+def test_w4a16_fused_prologues_and_residual(m, n, k, sym):
+    """RMSNorm prologue, SiLU*up prologue and residual epilogue of the decode-size int4 projection, each against
+    the unfused fp32 statement with the same bf16 rounding points (K = 9000 spans three shared-memory chunks)."""
+    from onnx_genai_b200.ops.quant import QuantLinear
+
+    torch.manual_seed(13)
+    w = torch.randn(n, k) * 0.05
+    q, s, zp = ref.quantize_w4(w, 32, symmetric=sym)
+    lin = QuantLinear(q, s.bfloat16(), zp, torch.randn(n) * 0.1, k=k, device=DEV)
+    wd = ref.dequant_w4(q, s.bfloat16().float(), zp, 32, k)
+    bias = lin.bias.float().cpu()
+    # RMSNorm prologue
+    x = (torch.randn(m, k, device=DEV) * 0.7).bfloat16()
+    g = (torch.rand(k, device=DEV) + 0.5).bfloat16()
+    out = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    lin.fused(x, out, norm_weight=g, eps=1e-6)
+    h, _ = ref.rmsnorm(x.cpu(), g.cpu(), 1e-6)
+    assert _rel_err(out.cpu(), h.float() @ wd.t() + bias) < 1.2e-2
+    # SiLU(gate) * up prologue + residual epilogue written in place
+    gu = (torch.randn(m, 2 * k, device=DEV) * 0.8).bfloat16()
+    res = torch.randn(m, n, device=DEV).bfloat16()
+    want = ref.silu_mul(gu.cpu()).float() @ wd.t() + bias + res.float().cpu()
+    lin.fused(gu, res, silu_mul=True, residual=res)
+    assert _rel_err(res.cpu(), want) < 1.2e-2
+    # plain + residual into a strided output
+    wide = torch.zeros(m, n + 64, device=DEV, dtype=torch.bfloat16)
+    r2 = torch.randn(m, n, device=DEV).bfloat16()
+    lin.fused(x, wide[:, 32:32 + n], residual=r2)
+    assert _rel_err(wide[:, 32:32 + n].cpu(), x.float().cpu() @ wd.t() + bias + r2.float().cpu()) < 1.2e-2
+    assert float(wide[:, :32].abs().max()) == 0 and float(wide[:, 32 + n:].abs().max()) == 0
+    torch.cuda.synchronize()
+    ops.check_status()
 
 
 @pytest.mark.parametrize("t,e,k,hidden,inter", [(37, 16, 4, 256, 128), (300, 128, 8, 512, 256), (5, 8, 2, 256, 768)])
