@@ -197,27 +197,69 @@ struct GemvFusedParams {
   float eps;
 };
 
-template <int MT, int PRO, bool SCALES_F32>
+// Weights, scale and zero point of one 32-weight block for the C columns starting at n0.
+template <int C, bool SCALES_F32>
+struct BlockW {
+  uint4 wq[C];
+  float sc[C], zz[C];
+  OGB_DEVICE void load(const GemvFusedParams& p, int n0, int b, int kb, int zp_stride) {
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+      const int n = min(n0 + c, p.N - 1);
+      wq[c] = __ldg(reinterpret_cast<const uint4*>(p.qw + (static_cast<size_t>(n) * kb + b) * 16));
+      sc[c] = load_scale<SCALES_F32>(p.scales, static_cast<size_t>(n) * kb + b);
+      zz[c] = 8.f;
+      if (p.zp != nullptr) {
+        const uint8_t zb = p.zp[static_cast<size_t>(n) * zp_stride + (b >> 1)];
+        zz[c] = static_cast<float>((b & 1) ? (zb >> 4) : (zb & 0xF));
+      }
+    }
+  }
+};
+
+// SPLITK = false: each warp owns kFusedCols columns and walks all of K (wide N, short K).
+// SPLITK = true : the CTA owns kSplitCols columns and its 8 warps share the blocks of K, then reduce through
+//                 shared memory (narrow N, long K: the down projection), which turns a chain of dependent
+//                 loads per lane into one.
+constexpr int kSplitCols = 4;
+
+template <int MT, int PRO, bool SCALES_F32, bool SPLITK>
 __global__ void __launch_bounds__(kFusedWarps * 32) w4a16_gemv_fused_kernel(const GemvFusedParams p) {
+  constexpr int C = SPLITK ? kSplitCols : kFusedCols;
   extern __shared__ __align__(16) uint8_t gemv_smem[];
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(gemv_smem);   // [MT][kGemvChunk]
   __shared__ float rstd_sh[MT];
   __shared__ float red_sh[kFusedWarps][MT];
+  __shared__ float part_sh[SPLITK ? kFusedWarps : 1][C][MT];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int K = p.K, N = p.N, M = p.M;
   const int kb = (K + 31) / 32;
   const int zp_stride = (kb + 1) / 2;
+  const int n0 = SPLITK ? blockIdx.x * C : (blockIdx.x * kFusedWarps + warp) * C;
+  // block index of this lane inside a chunk of kGemvChunk/32 = 128 blocks, and the stride to its next one
+  const int j0 = SPLITK ? warp * 32 + lane : lane;
+  constexpr int jstep = SPLITK ? kFusedWarps * 32 : 32;
+
+  // The first block's weights do not depend on the activations: request them before the prologue so the
+  // DRAM round trip overlaps the norm / staging chain.
+  BlockW<C, SCALES_F32> w0;
+  const bool have_w0 = (n0 < N) && (j0 < min(kb, kGemvChunk / 32));
+  if (have_w0) w0.load(p, n0, j0, kb, zp_stride);
 
   if constexpr (PRO == kProRmsNorm) {
     float ss[MT];
 #pragma unroll
     for (int m = 0; m < MT; ++m) ss[m] = 0.f;
-    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+    for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {       // K is a multiple of 8
 #pragma unroll
       for (int m = 0; m < MT; ++m) {
         if (m < M) {
-          const float v = __bfloat162float(p.x[static_cast<size_t>(m) * p.ldx + k]);
-          ss[m] += v * v;
+          const uint4 q = *reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(m) * p.ldx + k);
+          float2 t;
+          t = unpack_bf16(q.x); ss[m] += t.x * t.x + t.y * t.y;
+          t = unpack_bf16(q.y); ss[m] += t.x * t.x + t.y * t.y;
+          t = unpack_bf16(q.z); ss[m] += t.x * t.x + t.y * t.y;
+          t = unpack_bf16(q.w); ss[m] += t.x * t.x + t.y * t.y;
         }
       }
     }
@@ -235,10 +277,9 @@ __global__ void __launch_bounds__(kFusedWarps * 32) w4a16_gemv_fused_kernel(cons
     __syncthreads();
   }
 
-  const int n0 = (blockIdx.x * kFusedWarps + warp) * kFusedCols;
-  float acc[kFusedCols][MT];
+  float acc[C][MT];
 #pragma unroll
-  for (int c = 0; c < kFusedCols; ++c)
+  for (int c = 0; c < C; ++c)
 #pragma unroll
     for (int m = 0; m < MT; ++m) acc[c][m] = 0.f;
 
@@ -246,56 +287,60 @@ __global__ void __launch_bounds__(kFusedWarps * 32) w4a16_gemv_fused_kernel(cons
     const int klen = min(kGemvChunk, K - k0);
     const int klen_pad = (klen + 31) / 32 * 32;
     if (k0 > 0) __syncthreads();                 // every warp is done with the previous chunk
-    for (int i = threadIdx.x; i < klen_pad; i += blockDim.x) {
+    // stage prologue(x) for this chunk, 8 values per thread per step (K, ldx multiples of 8)
+    for (int i = threadIdx.x * 8; i < klen_pad; i += blockDim.x * 8) {
 #pragma unroll
       for (int m = 0; m < MT; ++m) {
-        float v = 0.f;
+        uint4 o = make_uint4(0u, 0u, 0u, 0u);
         if (m < M && i < klen) {
-          const size_t row = static_cast<size_t>(m) * p.ldx;
-          if constexpr (PRO == kProSiluMul) {
-            const float g = __bfloat162float(p.x[row + k0 + i]);
-            const float u = __bfloat162float(p.x[row + K + k0 + i]);
-            v = g / (1.f + __expf(-g)) * u;
-          } else if constexpr (PRO == kProRmsNorm) {
-            v = __bfloat162float(p.x[row + k0 + i]) * rstd_sh[m] * __bfloat162float(p.norm_w[k0 + i]);
+          const __nv_bfloat16* src = p.x + static_cast<size_t>(m) * p.ldx + k0 + i;
+          const uint4 q = *reinterpret_cast<const uint4*>(src);
+          if constexpr (PRO == kProNone) {
+            o = q;
           } else {
-            v = __bfloat162float(p.x[row + k0 + i]);
+            const uint32_t qa[4] = {q.x, q.y, q.z, q.w};
+            uint32_t oa[4];
+            uint4 aux;
+            if constexpr (PRO == kProSiluMul) aux = *reinterpret_cast<const uint4*>(src + K);
+            else aux = *reinterpret_cast<const uint4*>(p.norm_w + k0 + i);
+            const uint32_t xa[4] = {aux.x, aux.y, aux.z, aux.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 a = unpack_bf16(qa[e]);
+              const float2 bq = unpack_bf16(xa[e]);
+              if constexpr (PRO == kProSiluMul) {
+                oa[e] = pack_bf16(a.x / (1.f + __expf(-a.x)) * bq.x, a.y / (1.f + __expf(-a.y)) * bq.y);
+              } else {
+                oa[e] = pack_bf16(a.x * rstd_sh[m] * bq.x, a.y * rstd_sh[m] * bq.y);
+              }
+            }
+            o = make_uint4(oa[0], oa[1], oa[2], oa[3]);
           }
         }
-        xs[m * kGemvChunk + i] = __float2bfloat16(v);
+        *reinterpret_cast<uint4*>(xs + m * kGemvChunk + i) = o;
       }
     }
     __syncthreads();
     if (n0 < N) {
-      const int b0 = k0 / 32, b1 = b0 + klen_pad / 32;
-      for (int b = b0 + lane; b < b1; b += 32) {
-        uint4 wq[kFusedCols];
-        float sc[kFusedCols], zz[kFusedCols];
-#pragma unroll
-        for (int c = 0; c < kFusedCols; ++c) {
-          const int n = min(n0 + c, N - 1);
-          wq[c] = __ldg(reinterpret_cast<const uint4*>(p.qw + (static_cast<size_t>(n) * kb + b) * 16));
-          sc[c] = load_scale<SCALES_F32>(p.scales, static_cast<size_t>(n) * kb + b);
-          zz[c] = 8.f;
-          if (p.zp != nullptr) {
-            const uint8_t zb = p.zp[static_cast<size_t>(n) * zp_stride + (b >> 1)];
-            zz[c] = static_cast<float>((b & 1) ? (zb >> 4) : (zb & 0xF));
-          }
-        }
-        float dot[kFusedCols][MT], xsum[MT];
+      const int b0 = k0 / 32, nb = klen_pad / 32;
+      for (int j = j0; j < nb; j += jstep) {
+        BlockW<C, SCALES_F32> w;
+        if (k0 == 0 && j == j0 && have_w0) w = w0;
+        else w.load(p, n0, b0 + j, kb, zp_stride);
+        float dot[C][MT], xsum[MT];
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
           xsum[m] = 0.f;
 #pragma unroll
-          for (int c = 0; c < kFusedCols; ++c) dot[c][m] = 0.f;
+          for (int c = 0; c < C; ++c) dot[c][m] = 0.f;
         }
-        const __nv_bfloat16* xb = xs + (b - b0) * 32;
+        const __nv_bfloat16* xb = xs + j * 32;
 #pragma unroll
         for (int wi = 0; wi < 4; ++wi) {
-          float f[kFusedCols][8];
+          float f[C][8];
 #pragma unroll
-          for (int c = 0; c < kFusedCols; ++c) {
-            const uint32_t word = (wi == 0) ? wq[c].x : (wi == 1) ? wq[c].y : (wi == 2) ? wq[c].z : wq[c].w;
+          for (int c = 0; c < C; ++c) {
+            const uint32_t word = (wi == 0) ? w.wq[c].x : (wi == 1) ? w.wq[c].y : (wi == 2) ? w.wq[c].z : w.wq[c].w;
             nibbles_to_float(word, f[c]);
           }
 #pragma unroll
@@ -311,48 +356,74 @@ __global__ void __launch_bounds__(kFusedWarps * 32) w4a16_gemv_fused_kernel(cons
             for (int i = 0; i < 8; ++i) {
               xsum[m] += xv[i];
 #pragma unroll
-              for (int c = 0; c < kFusedCols; ++c) dot[c][m] += f[c][i] * xv[i];
+              for (int c = 0; c < C; ++c) dot[c][m] += f[c][i] * xv[i];
             }
           }
         }
 #pragma unroll
-        for (int c = 0; c < kFusedCols; ++c)
+        for (int c = 0; c < C; ++c)
 #pragma unroll
-          for (int m = 0; m < MT; ++m) acc[c][m] += sc[c] * (dot[c][m] - zz[c] * xsum[m]);
+          for (int m = 0; m < MT; ++m) acc[c][m] += w.sc[c] * (dot[c][m] - w.zz[c] * xsum[m]);
       }
     }
   }
-  if (n0 >= N) return;
+  if constexpr (SPLITK) {
 #pragma unroll
-  for (int c = 0; c < kFusedCols; ++c) {
+    for (int c = 0; c < C; ++c)
 #pragma unroll
-    for (int m = 0; m < MT; ++m) {
-      float v = warp_sum(acc[c][m]);
+      for (int m = 0; m < MT; ++m) {
+        const float v = warp_sum(acc[c][m]);
+        if (lane == 0) part_sh[warp][c][m] = v;
+      }
+    __syncthreads();
+    if (threadIdx.x < C * MT) {
+      const int c = threadIdx.x / MT, m = threadIdx.x % MT;
       const int n = n0 + c;
-      if (lane == 0 && m < M && n < N) {
+      if (m < M && n < N) {
+        float v = 0.f;
+        for (int w = 0; w < kFusedWarps; ++w) v += part_sh[w][c][m];
         if (p.bias != nullptr) v += __bfloat162float(p.bias[n]);
         if (p.resid != nullptr) v += __bfloat162float(p.resid[static_cast<size_t>(m) * p.ldr + n]);
         p.y[static_cast<size_t>(m) * p.ldy + n] = __float2bfloat16(v);
       }
     }
+  } else {
+    if (n0 >= N) return;
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        float v = warp_sum(acc[c][m]);
+        const int n = n0 + c;
+        if (lane == 0 && m < M && n < N) {
+          if (p.bias != nullptr) v += __bfloat162float(p.bias[n]);
+          if (p.resid != nullptr) v += __bfloat162float(p.resid[static_cast<size_t>(m) * p.ldr + n]);
+          p.y[static_cast<size_t>(m) * p.ldy + n] = __float2bfloat16(v);
+        }
+      }
+    }
   }
+}
+
+template <int MT, int PRO, bool SF32, bool SPLITK>
+static int launch_gemv_fused_one(const GemvFusedParams& p, cudaStream_t st) {
+  const int per_cta = SPLITK ? kSplitCols : kFusedWarps * kFusedCols;
+  const int blocks = (p.N + per_cta - 1) / per_cta;
+  const size_t smem = static_cast<size_t>(MT) * kGemvChunk * sizeof(__nv_bfloat16);
+  auto kern = w4a16_gemv_fused_kernel<MT, PRO, SF32, SPLITK>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  kern<<<blocks, kFusedWarps * 32, smem, st>>>(p);
+  return static_cast<int>(cudaGetLastError());
 }
 
 template <int MT, int PRO>
 static int launch_gemv_fused(const GemvFusedParams& p, bool scales_fp32, cudaStream_t st) {
-  const int warps_needed = (p.N + kFusedCols - 1) / kFusedCols;
-  const int blocks = (warps_needed + kFusedWarps - 1) / kFusedWarps;
-  const size_t smem = static_cast<size_t>(MT) * kGemvChunk * sizeof(__nv_bfloat16);
+  // long K over few columns: share K between the warps of a CTA (see the kernel comment)
+  const bool splitk = p.K >= 2048 && p.N <= 4096;
   if (scales_fp32) {
-    auto kern = w4a16_gemv_fused_kernel<MT, PRO, true>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    kern<<<blocks, kFusedWarps * 32, smem, st>>>(p);
-  } else {
-    auto kern = w4a16_gemv_fused_kernel<MT, PRO, false>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    kern<<<blocks, kFusedWarps * 32, smem, st>>>(p);
+    return splitk ? launch_gemv_fused_one<MT, PRO, true, true>(p, st) : launch_gemv_fused_one<MT, PRO, true, false>(p, st);
   }
-  return static_cast<int>(cudaGetLastError());
+  return splitk ? launch_gemv_fused_one<MT, PRO, false, true>(p, st) : launch_gemv_fused_one<MT, PRO, false, false>(p, st);
 }
 
 template <int PRO>
@@ -402,12 +473,12 @@ extern "C" int ogb_w4a16_dequant(const void* qweight, const void* scales, const 
 }
 
 // y[M,N] = prologue(x)[M,K] . dequant(W)^T (+ bias) (+ residual).  prologue: 0 none, 1 RMSNorm with norm_w/eps,
-// 2 SiLU(x[:, :K]) * x[:, K:2K].  M <= 8; K, ldx multiples of 8.  `residual` may alias `y`.
+// 2 SiLU(x[:, :K]) * x[:, K:2K].  M <= 8; K and ldx multiples of 8, x 16-byte aligned.  `residual` may alias `y`.
 extern "C" int ogb_w4a16_gemv_fused(const void* x, const void* qweight, const void* scales, const void* zp, const void* bias,
                                     const void* norm_w, const void* residual, void* y, int M, int N, int K, int ldx, int ldy,
                                     int ldr, float eps, int prologue, int scales_fp32, void* stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (M > kGemvMaxM || K <= 0) return -3;
+  if (M > kGemvMaxM || K <= 0 || (K % 8) != 0 || (ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0) return -3;
   if (prologue == kProRmsNorm && norm_w == nullptr) return -3;
   GemvFusedParams p;
   p.x = static_cast<const __nv_bfloat16*>(x);

@@ -318,7 +318,7 @@ class DecoderModel:
         ops.embedding(si.token_ids[:t], w.embed, out=x) if x.is_cuda else x.copy_(w.embed[si.token_ids[:t].long()])
         pending = None  # partial sums still to be added to the residual (TP only)
         # int4 layers at decode size: norm, SwiGLU glue and residual adds live inside the GEMV launches
-        fused_q = (x.is_cuda and t <= 8 and self.tp == 1 and all(l.quant and len(l.quant["qkv"]) == 1 and
+        fused_q = (x.is_cuda and t <= 4 and self.tp == 1 and all(l.quant and len(l.quant["qkv"]) == 1 and
                                                                  l.quant.get("gate_up") is not None for l in w.layers))
         for li, lw in enumerate(w.layers):
             pool = kv.pools[li]

@@ -8,7 +8,8 @@ import torch
 from . import _native, launch_counts, reference, status_word, timed_region
 from . import gemm as _gemm
 
-GEMV_MAX_M = 8
+GEMV_MAX_M = 8          # rows the GEMV kernels accept
+FUSED_MAX_M = 4         # above this the cached-bf16 tcgen05 GEMM is faster than the row-specialised GEMV (measured: 8 rows 2.2 ms/step vs 16 rows 2.1 ms/step on the 0.5B shape)
 _native.register("ogb_w4a16_gemv", [_native.P] * 6 + [_native.I] * 6 + [_native.P])
 _native.register("ogb_w4a16_dequant", [_native.P] * 4 + [_native.I] * 3 + [_native.P])
 _native.register("ogb_w4a16_gemv_fused", [_native.P] * 8 + [_native.I] * 6 + [_native.F] + [_native.I] * 2 + [_native.P])
@@ -97,9 +98,9 @@ class QuantLinear:
             out = torch.empty(m, self.n, dtype=torch.bfloat16, device=x.device)
         lib = _native.load()
         stream = torch.cuda.current_stream().cuda_stream
-        if m <= GEMV_MAX_M and not _LEGACY_GEMV and x.stride(1) == 1:
+        if m <= FUSED_MAX_M and not _LEGACY_GEMV and x.stride(1) == 1:
             return self.fused(x, out)
-        if m <= GEMV_MAX_M:
+        if m <= GEMV_MAX_M and _LEGACY_GEMV:
             with timed_region("w4a16_gemv"):
                 rc = lib.ogb_w4a16_gemv(x.data_ptr(), self.qweight.data_ptr(), self.scales.data_ptr(),
                                         self.zp.data_ptr() if self.zp is not None else 0,
