@@ -103,6 +103,7 @@ def main():
     ap.add_argument("--min-prompt", type=int, default=128)
     ap.add_argument("--max-prompt", type=int, default=2048)
     ap.add_argument("--output-tokens", type=int, default=256)
+    ap.add_argument("--greedy", action="store_true", help="greedy decoding instead of temperature 0.7 / top-p 0.9 (the MoE config)")
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
     ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "fused"])
     ap.add_argument("--token-multiple", type=int, default=128,
@@ -172,7 +173,8 @@ def main():
     def new_request():
         n = int(rng.integers(args.min_prompt, args.max_prompt + 1))
         ids = rng.integers(0, model.vocab, size=n, dtype=np.int64).astype(np.int32)
-        return eng.add_request(ids, args.output_tokens, temperature=0.7, top_p=0.9, seed=int(rng.integers(1, 2**31)),
+        return eng.add_request(ids, args.output_tokens, temperature=0.0 if args.greedy else 0.7, top_p=1.0 if args.greedy else 0.9,
+                               seed=int(rng.integers(1, 2**31)),
                                ignore_eos=True)
 
     active = 0
@@ -304,13 +306,15 @@ def main():
     clocks = sampler.summary(t0, td1)
     if rank == 0:
         result = {
-            "metric": "output tok/s (Qwen2.5-7B-shape, continuous batching, 256 concurrent, TP=%d)" % world,
+            "metric": "output tok/s (%s-shape, continuous batching, %d concurrent, %s=%d)" % (
+                {"qwen2.5-7b": "Qwen2.5-7B", "qwen3-30b-a3b": "Qwen3-30B-A3B"}.get(model.name, model.name), args.concurrency,
+                "TP=EP" if model.moe.num_experts > 0 else "TP", world),
             "value": round(value, 1), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(dev_ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform-random token ids, N(0,0.02) weights)",
             "impl": args.impl,
             "config": {"model": model.name + "-shape", "global_batch": args.concurrency, "seq_len": f"prompt U[{args.min_prompt},{args.max_prompt}] + {args.output_tokens} out",
-                       "parallelism": f"tp{world}", "kv": "paged, 16-token bf16 pages", "sampling": "temperature 0.7, top-p 0.9",
+                       "parallelism": f"tp{world}", "kv": "paged, 16-token bf16 pages", "sampling": "greedy" if args.greedy else "temperature 0.7, top-p 0.9",
                        "l2": "per-step inputs (weights + KV) exceed L2; no explicit flush",
                        "comm": getattr(comm, "backend_name", "none"),
                        "tokens_per_step_mean": round(sum(s[0] for s in shapes) / len(shapes), 1),

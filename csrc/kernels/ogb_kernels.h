@@ -97,6 +97,7 @@ int ogb_grouped_gemm_bf16(const void* A, const void* W, void* C, const int* grou
 // TpScatter / TpReduce structs (tp_comm.cuh).
 int ogb_gemm_bf16_scatter(const void* A, const void* W, int M, int N, int K, int lda, int ldw, const void* sc, int bn,
                           int* status, void* stream);
+int ogb_tp_signal_rows(const void* sc, int rows, void* stream);
 int ogb_tp_reduce_bcast(const void* rp, int rows, int n, int chunk, int tp, int nvls, int* status, void* stream);
 
 #ifdef __cplusplus

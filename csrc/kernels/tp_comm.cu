@@ -220,9 +220,33 @@ __global__ void __launch_bounds__(kRbThreads) tp_reduce_bcast_nvls_kernel(const 
   if (stamp) r.dbg[3] = global_timer_ns();
 }
 
+// Marks every 32-row group of this rank's staged partial product as complete on the rank that owns it.  Used
+// when the partial was produced by kernels that do not signal themselves (the MoE combine): the kernel
+// boundary has made the rows visible, one releasing reduction per group publishes them.
+__global__ void tp_signal_rows_kernel(const TpScatter* __restrict__ scp, int rows) {
+  const TpScatter& sc = *scp;
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;
+  const int row0 = g * 32;
+  if (row0 >= rows) return;
+  const int owner = row0 / sc.chunk;
+  uint32_t* cnt = sc.tile_cnt[owner] + (row0 - owner * sc.chunk) / 32;
+  const uint32_t units = static_cast<uint32_t>(sc.n / 32);
+  __threadfence_system();
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(cnt), "r"(units) : "memory");
+}
+
 }  // namespace ogb
 
 using namespace ogb;
+
+// Publishes rows [0, rows) of the local staging buffer described by `sc` (a device TpScatter) to their owners;
+// ogb_tp_reduce_bcast on the same stream then folds all ranks' partials into the residual stream.
+extern "C" int ogb_tp_signal_rows(const void* sc, int rows, void* stream) {
+  if (rows <= 0) return 0;
+  const int groups = (rows + 31) / 32;
+  tp_signal_rows_kernel<<<(groups + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const TpScatter*>(sc), rows);
+  return static_cast<int>(cudaGetLastError());
+}
 
 namespace {
 // CTAs of `kernel` that fit on the device at once (every CTA of an exchange launch spins at the end, so

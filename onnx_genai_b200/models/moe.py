@@ -3,7 +3,8 @@
 Expert parallelism here rides on the tensor-parallel group: attention output is reduced to every
 rank, so each rank already holds every token's hidden state; it runs the routes whose experts it
 owns (experts are split contiguously over ranks) and the per-rank partial outputs are summed by
-the communicator.  Dispatch therefore needs no all-to-all; combine is the one reduction.  The
+the communicator -- by the peer-memory exchange kernel when the fused communicator is active, by
+ncclAllReduce otherwise.  Dispatch therefore needs no all-to-all; combine is the one reduction.  The
 reference only sketches EP (docs/quantization/MOE_EXPERT_PARALLELISM.md:60-100) and runs float
 MoE on the CPU (crates/onnx-runtime-ep-cpu/src/kernels/moe.rs:1-8).
 """
@@ -28,6 +29,15 @@ def moe_forward(model, h, lw, x):
     if model.tp == 1:
         moe_ops.moe_experts(h, router_logits, lw.expert_gate_up, lw.expert_down, ws, x, cfg.moe.top_k, cfg.moe.renormalize,
                             model.w.swiglu_half, e0, accumulate=True)
+        return None
+    fc = getattr(model, "fused_comm", None)
+    if fc is not None and fc.ready:
+        # combine over the peer-memory exchange: this rank's experts write their partial sum into the symmetric
+        # staging buffer, the owners reduce all ranks' rows (NVSwitch multicast from TP=4) into the residual stream
+        part = fc.staging_view(1, t)
+        moe_ops.moe_experts(h, router_logits, lw.expert_gate_up, lw.expert_down, ws, part, cfg.moe.top_k, cfg.moe.renormalize,
+                            model.w.swiglu_half, e0, accumulate=False)
+        fc.reduce_partial(t, 1)
         return None
     part = model.partial[:t]
     moe_ops.moe_experts(h, router_logits, lw.expert_gate_up, lw.expert_down, ws, part, cfg.moe.top_k, cfg.moe.renormalize,

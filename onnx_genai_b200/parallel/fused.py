@@ -71,6 +71,8 @@ def _lib():
     lib.ogb_tp_struct_sizes.argtypes = [ctypes.POINTER(I), ctypes.POINTER(I)]
     lib.ogb_gemm_bf16_scatter.argtypes = [P, P, I, I, I, I, I, P, I, P, P]
     lib.ogb_tp_reduce_bcast.argtypes = [P, I, I, I, I, I, P, P]
+    lib.ogb_tp_signal_rows.argtypes = [P, I, P]
+    lib.ogb_tp_signal_rows.restype = I
     for f in ("ogb_ipc_alloc", "ogb_ipc_get_handle", "ogb_ipc_open_handle", "ogb_ipc_close_handle", "ogb_ipc_free",
               "ogb_tp_struct_sizes", "ogb_gemm_bf16_scatter", "ogb_tp_reduce_bcast"):
         getattr(lib, f).restype = I
@@ -243,5 +245,28 @@ class FusedComm:
             rc = self.lib.ogb_tp_reduce_bcast(rd.data_ptr(), rows, self.hidden, chunk, self.world, 1 if self.nvls else 0, st, stream)
         _native.check(rc, "ogb_tp_reduce_bcast")
         ops.launch_counts["gemm_bf16_scatter"] += 1
+        ops.launch_counts["tp_reduce_bcast"] += 1
+        self.calls += 1
+
+    # -- partial sums produced by other kernels (MoE combine) -------------------------------------
+    def staging_view(self, slot: int, rows: int):
+        """This rank's staging buffer of ``slot`` as a [rows, hidden] bf16 tensor: kernels that produce a partial
+        sum of the residual stream write it here, then call :meth:`reduce_partial`."""
+        t = torch.as_tensor(_CudaArray(self.local_ptr + self.off_stage[slot], (self.max_tokens, self.hidden), "<u2"),
+                            device=self.device).view(torch.bfloat16)
+        return t[:rows]
+
+    def reduce_partial(self, rows: int, slot: int):
+        """x[:rows] += sum over ranks of the staged partials (same exchange kernel as :meth:`row_parallel`)."""
+        chunk = self.chunk_for(rows)
+        sc, rd = self._get_structs(slot, chunk)
+        st = ops.status_word(self.device).data_ptr()
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = self.lib.ogb_tp_signal_rows(sc.data_ptr(), rows, stream)
+        _native.check(rc, "ogb_tp_signal_rows")
+        with ops.timed_region("tp_reduce_bcast"):
+            rc = self.lib.ogb_tp_reduce_bcast(rd.data_ptr(), rows, self.hidden, chunk, self.world, 1 if self.nvls else 0, st, stream)
+        _native.check(rc, "ogb_tp_reduce_bcast")
+        ops.launch_counts["tp_signal_rows"] += 1
         ops.launch_counts["tp_reduce_bcast"] += 1
         self.calls += 1

@@ -43,3 +43,18 @@ def test_tp2_fused_and_nccl_match_single_gpu(tmp_path):
         assert err < 3e-2, (name, err)
     assert fused["launches"].get("gemm_bf16_scatter", 0) > 0 and fused["launches"].get("tp_reduce_bcast", 0) > 0
     assert len(fused["tokens"]) == len(single["tokens"])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp2_moe_combine_over_the_exchange_kernel_matches_single_gpu(tmp_path):
+    """Experts split over 2 ranks: the combine goes through the peer-memory exchange (multicast forced on) and
+    through NCCL; both must agree with one GPU holding every expert."""
+    single = _run(1, "nccl-moe", str(tmp_path / "s.pt"), 0)
+    nccl = _run(2, "nccl-moe", str(tmp_path / "n.pt"), 29641)
+    fused = _run(2, "fused-py-moe", str(tmp_path / "f.pt"), 29642, OGB_TP_NVLS="1")
+    ref = single["logits"]
+    for name, got in (("nccl", nccl), ("fused", fused)):
+        err = float((got["logits"] - ref).norm() / ref.norm())
+        assert err < 3e-2, (name, err)
+    assert fused["launches"].get("tp_signal_rows", 0) > 0 and fused["launches"].get("moe_grouped_gemm", 0) > 0
+    assert len(fused["tokens"]) == len(single["tokens"])

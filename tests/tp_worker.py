@@ -18,6 +18,11 @@ def main():
     torch.cuda.set_device(dev)
     cfg = DecoderConfig(name="tp", num_layers=3, hidden=512, num_heads=8, num_kv_heads=2, head_dim=64, intermediate=1024,
                         vocab=2048, rope_theta=1e6, tie_embeddings=False, qkv_bias=True, max_position=1024)
+    if mode.endswith("-moe"):
+        from onnx_genai_b200.models.config import MoEConfig
+
+        mode = mode[: -len("-moe")]
+        cfg = cfg.replace(name="tp-moe", intermediate=0, moe=MoEConfig(num_experts=8, top_k=2, expert_intermediate=256, renormalize=True))
     comm = comm_mod.NcclComm() if world > 1 else None
     if mode.startswith("fused") and world > 1:
         from onnx_genai_b200.parallel.fused import FusedComm
