@@ -161,10 +161,30 @@ def cmd_serve(args, profiler):
 
     from .server import create_app
 
-    eng = _load(args)
     host, _, port = args.addr.rpartition(":")
-    app = create_app(eng, model_name=os.path.basename(os.path.abspath(args.model)), max_output_tokens=args.max_output_tokens,
-                     max_queue_depth=args.max_queue_depth, enable_debug_endpoints=args.enable_debug_endpoints, node_id=args.node_id)
+    app_kw = dict(max_output_tokens=args.max_output_tokens, max_queue_depth=args.max_queue_depth,
+                  enable_debug_endpoints=args.enable_debug_endpoints, node_id=args.node_id,
+                  admission_window_ms=args.admission_window_ms)
+    if args.models_dir:
+        import copy
+
+        from .server.registry import ModelRegistry, RegistryApp
+
+        def loader(path):
+            a = copy.copy(args)
+            a.model = path
+            return _load(a)
+
+        reg = ModelRegistry.from_dir(args.models_dir, max_loaded=args.max_loaded_models, loader=loader, **app_kw)
+        if args.model:
+            reg.warmup([os.path.basename(os.path.abspath(args.model))])
+        app = RegistryApp(reg)
+    else:
+        if not args.model:
+            print("serve: give a model directory or --models-dir", file=sys.stderr)
+            return 2
+        eng = _load(args)
+        app = create_app(eng, model_name=os.path.basename(os.path.abspath(args.model)), **app_kw)
     uvicorn.run(app, host=host or "127.0.0.1", port=int(port), log_level="info")
     return 0
 
@@ -265,7 +285,10 @@ def main(argv=None):
     _add_sampling(r)
     _add_engine(r)
     s = sub.add_parser("serve")
-    s.add_argument("model")
+    s.add_argument("model", nargs="?", default="", help="model directory (or use --models-dir)")
+    s.add_argument("--models-dir", default="", help="serve every model directory below this one; requests pick one by name")
+    s.add_argument("--max-loaded-models", type=int, default=1, help="models kept resident; the least recently used idle one is evicted")
+    s.add_argument("--admission-window-ms", type=float, default=2.0, help="an idle server waits this long for companion requests before its first step")
     s.add_argument("--addr", default="127.0.0.1:8080")
     s.add_argument("--max-output-tokens", type=int, default=4096)
     s.add_argument("--max-sessions", type=int, default=256)

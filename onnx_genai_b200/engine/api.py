@@ -351,6 +351,38 @@ class Engine:
                                           time.perf_counter() - t0, list(e["state"]["logprobs"])))
         return results
 
+    # ------------------------------------------------------------------ embeddings
+    def embed(self, inputs, normalize: bool = True) -> np.ndarray:
+        """[n, hidden] fp32: the final-normed hidden state of each input's last token (last-token pooling, the
+        usual choice for decoder-only models), L2-normalised unless ``normalize`` is False.  Inputs are strings
+        or token-id lists; they run as one continuous batch of prefill-only requests."""
+        if isinstance(inputs, str) or (inputs and isinstance(inputs[0], int)):
+            inputs = [inputs]
+        sids = []
+        for item in inputs:
+            ids = self.tokenize(item) if isinstance(item, str) else [int(t) for t in item]
+            if not ids:
+                raise ValueError("cannot embed an empty input")
+            sid = self.llm.add_request(np.asarray(ids, dtype=np.int32), 1, temperature=0.0, ignore_eos=True)
+            self.llm.hidden_taps[sid & 0x7FFFFFFF] = None
+            sids.append(sid)
+        pending = set(sids)
+        while pending and self.llm.has_work:
+            for sid, _tok, fin in self.llm.step().events:
+                if fin is not None:
+                    pending.discard(sid)
+        out = []
+        for sid in sids:
+            vec = self.llm.hidden_taps.pop(sid & 0x7FFFFFFF, None)
+            self.llm.core.release(sid)
+            self.llm.stats.pop(sid, None)
+            if vec is None:
+                raise RuntimeError("the engine finished an embedding request without producing its hidden state")
+            if normalize:
+                vec = vec / max(float(np.linalg.norm(vec)), 1e-12)
+            out.append(vec.astype(np.float32))
+        return np.stack(out)
+
     # ------------------------------------------------------------------ sessions
     def create_session(self) -> int:
         sid = self._next_session

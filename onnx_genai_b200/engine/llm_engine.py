@@ -148,6 +148,7 @@ class LLMEngine:
         self.d2h_bytes = 0
         # CUDA graphs of decode-only steps, keyed by (row bucket, KV splits, sampler kind).  A capture that
         # fails is a decline, not an error: the bucket is marked and the step runs eagerly from then on.
+        self.hidden_taps: dict = {}       # seq id -> None until the request's first logits row exists, then its final hidden state
         self.graphs: dict = {}
         self.graph_replays = 0
         self.graph_declines: list = []
@@ -323,6 +324,13 @@ class LLMEngine:
                 self.sampled_host[:r] = toks
         elif self.device.type == "cuda":
             torch.cuda.current_stream().synchronize()
+        if self.hidden_taps and r > 0:
+            # embeddings: the final-normed hidden state of a tapped request's last prompt token
+            seq_of_row = self.plan_np[self.L.logit_seq:self.L.logit_seq + r]
+            for row in range(r):
+                key = int(seq_of_row[row])
+                if key in self.hidden_taps and self.hidden_taps[key] is None:
+                    self.hidden_taps[key] = self.model.h_last[row].float().cpu().numpy().copy()
         if self.host_samplers and r > 0:
             # rows whose request cannot use the device sampler: logits cross to the host, the request's
             # processor chain and sampler pick the token, and the device's choice for that row is replaced

@@ -21,6 +21,7 @@ from fastapi import FastAPI, Header, HTTPException, Request
 from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 
 from ..engine.api import Engine, GenerateOptions
+from .. import reasoning as reasoning_mod
 from . import tools as tool_calls
 from .metrics import Metrics
 
@@ -28,8 +29,12 @@ from .metrics import Metrics
 class EngineDriver:
     """Owns the engine on a dedicated thread; multiplexes requests into shared engine steps."""
 
-    def __init__(self, engine: Engine, max_queue_depth: int = 256):
+    def __init__(self, engine: Engine, max_queue_depth: int = 256, admission_window_ms: float = 2.0):
         self.engine = engine
+        # an idle driver that receives a request waits this long for companions before its first step, so
+        # requests that arrive together prefill together (the reference's micro-batch window is 2-12 ms,
+        # crates/onnx-genai-server/src/driver.rs:935-1050)
+        self.admission_window_s = max(0.0, admission_window_ms) / 1e3
         self.inbox: queue.Queue = queue.Queue()
         self.max_queue_depth = max_queue_depth
         self.active: dict = {}
@@ -43,6 +48,11 @@ class EngineDriver:
         if self.inbox.qsize() + len(self.active) >= self.max_queue_depth:
             raise OverflowError("queue full")
         self.inbox.put(("gen", ids, opt, loop, out_q))
+
+    def submit_embed(self, ids, loop, out_q: asyncio.Queue):
+        if self.inbox.qsize() + len(self.active) >= self.max_queue_depth:
+            raise OverflowError("queue full")
+        self.inbox.put(("embed", ids, loop, out_q))
 
     def cancel(self, out_q):
         self.inbox.put(("cancel", out_q))
@@ -61,6 +71,17 @@ class EngineDriver:
                 loop.call_soon_threadsafe(out_q.put_nowait, ("error", str(exc)))
                 return
             self.active[sid] = {"loop": loop, "q": out_q, "state": state, "out": [], "emitted": "", "opt": opt}
+        elif kind == "embed":
+            _, ids, loop, out_q = item
+            try:
+                import numpy as np
+
+                sid = self.engine.llm.add_request(np.asarray(ids, dtype=np.int32), 1, temperature=0.0, ignore_eos=True)
+            except Exception as exc:
+                loop.call_soon_threadsafe(out_q.put_nowait, ("error", str(exc)))
+                return
+            self.engine.llm.hidden_taps[sid & 0x7FFFFFFF] = None
+            self.active[sid] = {"loop": loop, "q": out_q, "embed": True}
         elif kind == "cancel":
             for sid, a in list(self.active.items()):
                 if a["q"] is item[1]:
@@ -72,8 +93,16 @@ class EngineDriver:
         eng = self.engine
         while not self._stop:
             try:
+                was_idle = not self.active
                 item = self.inbox.get(timeout=0.25 if not self.active else 0.0)
                 self._admit(item)
+                if was_idle and self.admission_window_s > 0:
+                    deadline = time.perf_counter() + self.admission_window_s
+                    while True:
+                        left = deadline - time.perf_counter()
+                        if left <= 0:
+                            break
+                        self._admit(self.inbox.get(timeout=left))
                 while True:
                     self._admit(self.inbox.get_nowait())
             except queue.Empty:
@@ -91,6 +120,14 @@ class EngineDriver:
             for sid, tok, fin in events:
                 a = self.active.get(sid)
                 if a is None:
+                    continue
+                if a.get("embed"):
+                    if fin is not None:
+                        vec = eng.llm.hidden_taps.pop(sid & 0x7FFFFFFF, None)
+                        eng.llm.core.release(sid)
+                        eng.llm.stats.pop(sid, None)
+                        a["loop"].call_soon_threadsafe(a["q"].put_nowait, ("embedding", vec))
+                        del self.active[sid]
                     continue
                 self.tokens_generated += 1
                 a["out"].append(tok)
@@ -169,12 +206,14 @@ def _options_from_request(body: dict, default_max: int, max_cap: int) -> Generat
 
 
 def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int = 4096, max_queue_depth: int = 256,
-               enable_debug_endpoints: bool = False, node_id: str = "node-0") -> FastAPI:
+               enable_debug_endpoints: bool = False, node_id: str = "node-0", admission_window_ms: float = 2.0) -> FastAPI:
     app = FastAPI(title="onnx-genai-b200")
-    driver = EngineDriver(engine, max_queue_depth)
+    driver = EngineDriver(engine, max_queue_depth, admission_window_ms)
     metrics = Metrics()
     app.state.driver, app.state.metrics, app.state.engine = driver, metrics, engine
     sessions: dict = {}
+    # models whose chat template declares a thinking block get it returned as `reasoning_content`
+    think = reasoning_mod.detect(getattr(engine, "chat_template", None))
 
     @app.middleware("http")
     async def trace_request(request: Request, call_next):
@@ -234,9 +273,44 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
             "onnx_genai_engine_steps_total": snap["steps"]}), media_type="text/plain; version=0.0.4")
 
     @app.post("/v1/embeddings")
-    async def embeddings():
-        raise HTTPException(501, "this model package exposes logits only: no pooled hidden-state output is declared in its "
-                                 "inference metadata, so /v1/embeddings cannot be served")
+    async def embeddings(request: Request):
+        """Last-token pooling of the final-normed hidden state, L2-normalised (``encoding_format`` float only)."""
+        import numpy as np
+
+        body = await _json(request)
+        inputs = body.get("input")
+        if isinstance(inputs, str) or (isinstance(inputs, list) and inputs and isinstance(inputs[0], int)):
+            inputs = [inputs]
+        if not isinstance(inputs, list) or not inputs:
+            raise HTTPException(400, "input must be a string, a list of strings, or token-id lists")
+        if body.get("encoding_format", "float") != "float":
+            raise HTTPException(400, "only encoding_format 'float' is supported")
+        loop = asyncio.get_running_loop()
+        queues, total = [], 0
+        for item in inputs:
+            ids = engine.tokenize(item) if isinstance(item, str) else [int(t) for t in item]
+            if not ids:
+                raise HTTPException(400, "an input is empty after tokenisation")
+            if len(ids) >= engine.llm.cfg.max_seq_len:
+                raise HTTPException(400, f"an input has {len(ids)} tokens but the model's context is {engine.llm.cfg.max_seq_len}")
+            total += len(ids)
+            q: asyncio.Queue = asyncio.Queue()
+            try:
+                driver.submit_embed(ids, loop, q)
+            except OverflowError:
+                metrics.rejected()
+                raise HTTPException(429, f"request queue is full ({max_queue_depth} in flight); retry later")
+            queues.append(q)
+        data = []
+        for i, q in enumerate(queues):
+            ev = await q.get()
+            if ev[0] == "error" or ev[1] is None:
+                raise HTTPException(500, f"embedding failed: {ev[1]}")
+            vec = np.asarray(ev[1], dtype=np.float32)
+            vec = vec / max(float(np.linalg.norm(vec)), 1e-12)
+            data.append({"object": "embedding", "index": i, "embedding": [float(v) for v in vec]})
+        metrics.prompt_tokens(total)
+        return {"object": "list", "model": model_name, "data": data, "usage": {"prompt_tokens": total, "total_tokens": total}}
 
     if enable_debug_endpoints:
         @app.get("/v1/debug/config")
@@ -246,6 +320,25 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
         @app.get("/v1/debug/kv")
         async def debug_kv():
             return engine.resource_snapshot()
+
+        @app.get("/v1/debug/sessions")
+        async def debug_sessions():
+            return {"sessions": [{"id": k, "tokens": engine.session_len(v)} for k, v in sessions.items()],
+                    "active_requests": len(driver.active), "queued": driver.inbox.qsize()}
+
+        @app.get("/v1/debug/profile")
+        async def debug_profile():
+            from .. import ops
+
+            return {"launch_counts": dict(ops.launch_counts), "engine_steps": engine.llm.steps,
+                    "graph_replays": engine.llm.graph_replays, "graph_declines": [str(d) for d in engine.llm.graph_declines],
+                    "h2d_bytes": engine.llm.h2d_bytes, "d2h_bytes": engine.llm.d2h_bytes}
+
+        @app.get("/v1/debug/trace/perfetto")
+        async def debug_trace():
+            from ..utils import trace
+
+            return JSONResponse(trace.chrome_trace_events())
 
     async def _run_generation(ids, opt, request: Request):
         loop = asyncio.get_running_loop()
@@ -317,6 +410,7 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
             async def gen():
                 first = True
                 out_ids = []
+                splitter = reasoning_mod.StreamSplitter(think if chat else None)
                 try:
                     if chat:
                         yield _sse({"id": rid, "object": obj + ".chunk", "created": created, "model": model_name,
@@ -333,8 +427,18 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
                                 metrics.ttft(time.perf_counter() - t0)
                                 first = False
                             if delta:
-                                choice = ({"index": 0, "delta": {"content": delta}, "finish_reason": None} if chat
-                                          else {"index": 0, "text": delta, "finish_reason": None})
+                                if chat:
+                                    r_d, a_d = splitter.feed(delta)
+                                    payload = {}
+                                    if r_d:
+                                        payload["reasoning_content"] = r_d
+                                    if a_d:
+                                        payload["content"] = a_d
+                                    if not payload:
+                                        continue
+                                    choice = {"index": 0, "delta": payload, "finish_reason": None}
+                                else:
+                                    choice = {"index": 0, "text": delta, "finish_reason": None}
                                 yield _sse({"id": rid, "object": obj + ".chunk", "created": created, "model": model_name,
                                             "choices": [choice]})
                         elif ev[0] == "done":
@@ -373,7 +477,10 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
         finish_session(out_ids)
         usage = {"prompt_tokens": len(ids), "completion_tokens": len(out_ids), "total_tokens": len(ids) + len(out_ids)}
         if chat:
+            thought, text = reasoning_mod.split(text, think)
             msg = {"role": "assistant", "content": text}
+            if thought is not None:
+                msg["reasoning_content"] = thought
             calls = tool_calls.parse_tool_calls(text) if body.get("tools") else []
             if calls:
                 msg = {"role": "assistant", "content": None, "tool_calls": calls}

@@ -12,6 +12,21 @@ import threading
 import time
 
 
+def chrome_trace_events(spans=None, pid: int = 1) -> dict:
+    """The collected spans (default: the process-wide tracer's) as a Chrome Trace Event document."""
+    if spans is None:
+        with TRACER.lock:
+            spans = list(TRACER.spans)
+    events = []
+    tids = {}
+    for name, a, b, cat in spans:
+        tid = tids.setdefault(cat, len(tids) + 1)
+        events.append({"name": name, "cat": cat, "ph": "X", "ts": a * 1e6, "dur": max(0.0, (b - a) * 1e6), "pid": pid, "tid": tid})
+    for cat, tid in tids.items():
+        events.append({"name": "thread_name", "ph": "M", "pid": pid, "tid": tid, "args": {"name": cat}})
+    return {"traceEvents": events, "displayTimeUnit": "ms"}
+
+
 def write_chrome_trace(path: str, spans, pid: int = 1) -> None:
     """spans: iterable of (name, t_start_s, t_end_s, category)."""
     events = []

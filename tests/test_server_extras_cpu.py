@@ -1,0 +1,77 @@
+"""Embeddings, reasoning blocks, the multi-model registry and the debug endpoints."""
+import numpy as np
+import pytest
+from fastapi.testclient import TestClient
+
+from onnx_genai_b200 import reasoning
+from onnx_genai_b200.bench.config_bench import _export
+from onnx_genai_b200.engine.api import Engine
+from onnx_genai_b200.server.app import create_app
+from onnx_genai_b200.server.registry import ModelRegistry, RegistryApp
+
+
+def test_reasoning_detection_split_and_streaming():
+    tmpl = "{% for m in messages %}{{ m.content }}{% endfor %}{% if add_generation_prompt %}<|im_start|>assistant\n<think>\n{% endif %} ... </think>"
+    d = reasoning.detect(tmpl)
+    assert d == reasoning.ReasoningDelimiters("<think>", "</think>", prefilled=True)
+    assert reasoning.detect("{{ messages }}") is None
+    assert reasoning.split("step 1\nstep 2</think>\n\nThe answer is 4.", d) == ("step 1\nstep 2", "The answer is 4.")
+    assert reasoning.split("still thinking", d) == ("still thinking", "")
+    plain = reasoning.ReasoningDelimiters("<think>", "</think>")
+    assert reasoning.split("<think>a</think>b", plain) == ("a", "b")
+    assert reasoning.split("no block here", plain) == (None, "no block here")
+    sp = reasoning.StreamSplitter(plain)
+    r_all, a_all = "", ""
+    for piece in ["<th", "ink>rea", "son</th", "ink>ans", "wer"]:          # tags arrive split across deltas
+        r, a = sp.feed(piece)
+        r_all, a_all = r_all + r, a_all + a
+    r, a = sp.flush()
+    assert (r_all + r, a_all + a) == ("reason", "answer")
+
+
+@pytest.fixture(scope="module")
+def dirs(tmp_path_factory):
+    out = []
+    for name in ("alpha", "beta"):
+        d = tmp_path_factory.mktemp(name)
+        _export("tiny-llama", str(d), "fp32", layers=1)
+        out.append(str(d))
+    return out
+
+
+def test_embeddings_endpoint_matches_engine_embed(dirs):
+    eng = Engine.from_dir(dirs[0], device="cpu", max_seqs=4, max_seq_len=128)
+    direct = eng.embed(["hello world", "goodbye"])
+    assert direct.shape == (2, 256) and np.allclose(np.linalg.norm(direct, axis=1), 1.0, atol=1e-5)
+    assert not np.allclose(direct[0], direct[1])
+    with TestClient(create_app(eng, model_name="tiny", enable_debug_endpoints=True)) as client:
+        r = client.post("/v1/embeddings", json={"model": "tiny", "input": ["hello world", "goodbye"]})
+        assert r.status_code == 200, r.text
+        data = r.json()["data"]
+        got = np.array([d["embedding"] for d in data], dtype=np.float32)
+        assert np.allclose(got, direct, atol=1e-5) and r.json()["usage"]["prompt_tokens"] > 0
+        assert client.post("/v1/embeddings", json={"input": []}).status_code == 400
+        # generation still works beside embedding traffic, and the debug endpoints answer
+        g = client.post("/v1/completions", json={"model": "tiny", "prompt": "hi", "max_tokens": 4})
+        assert g.status_code == 200 and g.json()["usage"]["completion_tokens"] == 4
+        prof = client.get("/v1/debug/profile").json()
+        assert prof["engine_steps"] > 0 and "launch_counts" in prof
+        assert "sessions" in client.get("/v1/debug/sessions").json()
+        assert "traceEvents" in client.get("/v1/debug/trace/perfetto").json()
+
+
+def test_registry_loads_on_demand_and_evicts_least_recently_used(dirs):
+    reg = ModelRegistry({"alpha": dirs[0], "beta": dirs[1]}, max_loaded=1,
+                        loader=lambda path: Engine.from_dir(path, device="cpu", max_seqs=2, max_seq_len=64))
+    with TestClient(RegistryApp(reg)) as client:
+        listing = client.get("/v1/models").json()["data"]
+        assert [m["id"] for m in listing] == ["alpha", "beta"] and not any(m["loaded"] for m in listing)
+        for name in ("alpha", "beta", "alpha"):
+            r = client.post("/v1/completions", json={"model": name, "prompt": "x", "max_tokens": 2})
+            assert r.status_code == 200 and r.json()["model"] == name, r.text
+        assert reg.loads == 3 and reg.evictions == 2 and list(reg.loaded) == ["alpha"]
+        r = client.post("/v1/completions", json={"prompt": "x", "max_tokens": 1})          # no model named: the default
+        assert r.status_code == 200 and r.json()["model"] == "alpha" and reg.loads == 3
+        missing = client.post("/v1/completions", json={"model": "gamma", "prompt": "x"})
+        assert missing.status_code == 404 and "available: alpha, beta" in missing.text
+    assert not reg.loaded                                                                   # shutdown released everything
