@@ -250,11 +250,17 @@ def main():
         (si.num_tokens, si.num_decode, si.num_prefill_seqs, si.num_tiles, si.num_logit_rows, si.max_ctx, splits) = shapes[i]
         if splits != eng.model.decode_splits:
             eng.model.set_decode_splits(splits)
-        logits = eng.model.forward(si, eng.kv)
         r = si.num_logit_rows
+        if r and eng._shard_rows(r):       # TP: the engine's own split of the lm_head + sampler rows, tokens all-gathered
+            eng.forward_and_sample_sharded(si, r, args.greedy)
+            return
+        logits = eng.model.forward(si, eng.kv)
         if r:
-            ops.sample(logits, eng.temperature[:r], eng.top_k[:r], eng.top_p[:r], eng.min_p[:r], eng.uniform[:r],
-                       work=eng.sample_work, out=eng.sampled_dev[:r])
+            if args.greedy:
+                ops.argmax(logits, out=eng.sampled_dev[:r])
+            else:
+                ops.sample(logits, eng.temperature[:r], eng.top_k[:r], eng.top_p[:r], eng.min_p[:r], eng.uniform[:r],
+                           work=eng.sample_work, out=eng.sampled_dev[:r])
 
     for i in range(min(3, args.steps)):
         replay(i)

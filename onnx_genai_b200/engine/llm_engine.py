@@ -51,6 +51,7 @@ class EngineConfig:
     max_draft_tokens: int = 0          # speculative decoding: drafts verified per sequence per step
     native_executor: bool = True       # launch the layer stack from the C++ step executor when possible
     cuda_graphs: bool = False          # replay decode-only steps (forward + sampler) from captured CUDA graphs
+    shard_sampling: bool = True        # TP: each rank runs lm_head + sampler for 1/tp of the rows, tokens are all-gathered
     seed: int = 0
 
 
@@ -267,6 +268,43 @@ class LLMEngine:
         finally:
             si.num_tokens, si.num_decode, si.num_logit_rows = saved
 
+    # ---- TP: rows of the logits/sampling stage split over the ranks -------------------------------
+    def _shard_rows(self, r: int) -> bool:
+        """With a replicated lm_head every rank would compute and sample all r rows.  Instead rank k takes rows
+        [k*chunk, (k+1)*chunk): its lm_head GEMM and sampler see 1/tp of the rows and one all-gather of the token
+        ids (4 bytes per row) replaces the broadcast that kept replicas in step.  Steps whose logits are needed on
+        the host (custom samplers, log-probabilities, embeddings, speculative verification) keep all rows."""
+        return (self.tp > 1 and self.cfg.shard_sampling and self.device.type == "cuda" and r >= self.tp
+                and not self.host_samplers and not self.hidden_taps and self.cfg.max_draft_tokens == 0)
+
+    def forward_and_sample_sharded(self, si, r: int, greedy: bool) -> None:
+        """Run the step with this rank's share of the sampling rows; leaves all r token ids in sampled_dev[:r]."""
+        tp, rank = self.tp, self.rank
+        chunk = (r + tp - 1) // tp
+        r0 = min(r, rank * chunk)
+        n_loc = max(0, min(r, r0 + chunk) - r0)
+        if getattr(self, "_shard_buf", None) is None or self._shard_buf.numel() < chunk:
+            cap = (self.sampled_dev.numel() + tp - 1) // tp + 1
+            self._shard_buf = torch.zeros(cap, dtype=torch.int32, device=self.device)
+            self._gather_buf = torch.zeros(cap * tp, dtype=torch.int32, device=self.device)
+        saved_rows, saved_n = si.logit_rows, si.num_logit_rows
+        # a rank whose share is empty (r not a multiple of tp) still runs the layers; it samples one throw-away row
+        lo = r0 if n_loc > 0 else 0
+        n_run = max(n_loc, 1)
+        si.logit_rows, si.num_logit_rows = saved_rows[lo:], n_run
+        try:
+            logits = self.model.forward(si, self.kv)
+        finally:
+            si.logit_rows, si.num_logit_rows = saved_rows, saved_n
+        out = self._shard_buf[:n_run]
+        if greedy:
+            ops.argmax(logits, out=out)
+        else:
+            ops.sample(logits, self.temperature[lo:lo + n_run], self.top_k[lo:lo + n_run], self.top_p[lo:lo + n_run],
+                       self.min_p[lo:lo + n_run], self.uniform[lo:lo + n_run], work=self.sample_work, out=out)
+        self.comm.all_gather(self._gather_buf[: tp * chunk], self._shard_buf[:chunk])
+        self.sampled_dev[:r].copy_(self._gather_buf[:r])
+
     def step(self) -> StepOutput:
         """Schedule, run and commit one engine step."""
         out = StepOutput()
@@ -297,10 +335,21 @@ class LLMEngine:
                 self.model.set_decode_splits(splits)
                 self.graphs.clear()          # split scratch was reallocated: captured pointers are stale
         graphed = self._graph_step(si, r) if self._graph_eligible(si, r, hdr) else False
-        logits = self.model.logits[:r] if graphed else self.model.forward(si, self.kv)
+        sharded = (not graphed) and self._shard_rows(r)
+        if graphed:
+            logits = self.model.logits[:r]
+        elif sharded:
+            logits = None
+        else:
+            logits = self.model.forward(si, self.kv)
         if r > 0:
             temps = self.plan_np[self.L.temperature:self.L.temperature + r].view(np.float32)
             if graphed:
+                self.sampled_host[:r].copy_(self.sampled_dev[:r], non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                self.d2h_bytes += r * 4
+            elif sharded:
+                self.forward_and_sample_sharded(si, r, bool((temps <= 0).all()))
                 self.sampled_host[:r].copy_(self.sampled_dev[:r], non_blocking=True)
                 torch.cuda.current_stream().synchronize()
                 self.d2h_bytes += r * 4

@@ -99,6 +99,9 @@ class FusedComm:
     def broadcast(self, t, src=0):
         return self.base.broadcast(t, src)
 
+    def all_gather(self, out, t):
+        return self.base.all_gather(out, t)
+
     def barrier(self):
         return self.base.barrier()
 
