@@ -36,7 +36,18 @@ def main():
     for p in prompts:
         eng.add_request(p, 12)
     eng.step()
-    logits = eng.model.logits[: len(prompts)].float().cpu()
+    n = len(prompts)
+    if world > 1 and eng._shard_rows(n):
+        # each rank ran lm_head for its share of the rows only: collect the shares in rank order
+        import torch.distributed as dist
+
+        chunk = (n + world - 1) // world
+        n_loc = max(0, min(n, (rank + 1) * chunk) - rank * chunk)
+        shares = [None] * world
+        dist.all_gather_object(shares, eng.model.logits[:n_loc].float().cpu())
+        logits = torch.cat(shares)[:n]
+    else:
+        logits = eng.model.logits[:n].float().cpu()
     toks = []
     while eng.has_work:
         toks += [(sid, tok) for sid, tok, _ in eng.step().events]
