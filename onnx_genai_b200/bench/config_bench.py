@@ -124,7 +124,8 @@ def config5(args) -> dict:
         except Exception as exc:
             print(f"fused communicator unavailable ({exc}); using NCCL", file=sys.stderr)
     target_cfg = preset("qwen2.5-7b")
-    draft_cfg = preset("qwen2.5-0.5b").replace(weight_format="bf16")
+    # the draft takes the target's vocabulary (the target's tokens are its inputs)
+    draft_cfg = preset("qwen2.5-0.5b").replace(weight_format="bf16", vocab=target_cfg.vocab)
     if args.layers:
         target_cfg, draft_cfg = target_cfg.replace(num_layers=args.layers), draft_cfg.replace(num_layers=max(1, args.layers // 2))
     k = args.draft_tokens
