@@ -632,6 +632,16 @@ bool Core::set_draft(int64_t seq_id, const int32_t* tokens, int k) {
   return true;
 }
 
+bool Core::append_tokens(int64_t seq_id, const int32_t* tokens, int n) {
+  Sequence* s = find(seq_id);
+  if (!s || n < 0 || s->status == SeqStatus::Finished) return false;
+  if (static_cast<int>(s->tokens.size()) + n > cfg_.max_pages_per_seq * kPageTokens) return false;
+  s->tokens.insert(s->tokens.end(), tokens, tokens + n);
+  s->prompt_len = static_cast<int>(s->tokens.size());   // the generation budget counts from here
+  s->draft.clear();
+  return true;
+}
+
 int Core::seq_len(int64_t seq_id) const {
   const Sequence* s = find(seq_id);
   return s ? static_cast<int>(s->tokens.size()) : -1;
@@ -714,6 +724,9 @@ int64_t ogb_core_fork(void* h, int64_t id) { return static_cast<Core*>(h)->fork(
 int ogb_core_rewind(void* h, int64_t id, int new_len) { return static_cast<Core*>(h)->rewind(id, new_len) ? 1 : 0; }
 int ogb_core_set_draft(void* h, int64_t id, const int32_t* tokens, int k) {
   return static_cast<Core*>(h)->set_draft(id, tokens, k) ? 1 : 0;
+}
+int ogb_core_append_tokens(void* h, int64_t id, const int32_t* tokens, int n) {
+  return static_cast<Core*>(h)->append_tokens(id, tokens, n) ? 1 : 0;
 }
 int ogb_core_seq_len(void* h, int64_t id) { return static_cast<Core*>(h)->seq_len(id); }
 int ogb_core_seq_tokens(void* h, int64_t id, int32_t* out, int cap) { return static_cast<Core*>(h)->seq_tokens(id, out, cap); }

@@ -157,6 +157,10 @@ class Core {
   // last token plus the drafts, samples every position, and commit_step keeps the longest prefix of the
   // drafts that the samples confirm (plus the correction / bonus token), rewinding the KV pages of the rest.
   bool set_draft(int64_t seq_id, const int32_t* tokens, int k);
+  // Extends a live sequence with tokens chosen by the caller (they count as prompt: the next steps compute
+  // their K/V as a prefill chunk and sample after the last one).  With rewind this lets a caller re-align a
+  // sequence to a corrected continuation without re-submitting the prefix.
+  bool append_tokens(int64_t seq_id, const int32_t* tokens, int n);
   int64_t spec_proposed() const { return spec_proposed_; }
   int64_t spec_accepted() const { return spec_accepted_; }
   int64_t spec_steps() const { return spec_steps_; }

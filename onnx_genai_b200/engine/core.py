@@ -66,6 +66,8 @@ def load_runtime():
     lib.ogb_core_rewind.restype = c_int
     lib.ogb_core_set_draft.argtypes = [P, c_int64, I32P, c_int]
     lib.ogb_core_set_draft.restype = c_int
+    lib.ogb_core_append_tokens.argtypes = [P, c_int64, I32P, c_int]
+    lib.ogb_core_append_tokens.restype = c_int
     lib.ogb_core_seq_len.argtypes = [P, c_int64]
     lib.ogb_core_seq_len.restype = c_int
     lib.ogb_core_seq_tokens.argtypes = [P, c_int64, I32P, c_int]
@@ -160,6 +162,11 @@ class Core:
         """Propose tokens to follow the sequence's last token; verified (and rewound) by the next step."""
         arr = np.ascontiguousarray(tokens, dtype=np.int32)
         return bool(self.lib.ogb_core_set_draft(self.h, sid, arr.ctypes.data_as(POINTER(c_int32)), len(arr)))
+
+    def append_tokens(self, sid, tokens):
+        """Extend a live sequence with caller-chosen tokens (computed as a prefill chunk by the next steps)."""
+        arr = np.ascontiguousarray(tokens, dtype=np.int32)
+        return bool(self.lib.ogb_core_append_tokens(self.h, sid, arr.ctypes.data_as(POINTER(c_int32)), len(arr)))
 
     def seq_len(self, sid):
         return int(self.lib.ogb_core_seq_len(self.h, sid))

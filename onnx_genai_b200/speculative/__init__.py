@@ -94,8 +94,12 @@ class DraftModelProposer(SpeculativeProposer):
                 eng.core.release(self.sid)
                 self.sid = eng.add_request(ids, max_new_tokens=1 << 20, temperature=0.0, ignore_eos=True)
             elif common < len(have) or common < len(ids):
-                eng.core.rewind(self.sid, common)
-                if common < len(ids):
+                # drop what the target rejected, then feed what the target chose instead (usually one token):
+                # the draft keeps its KV pages for the common prefix, however long the prompt is
+                ok = eng.core.rewind(self.sid, common) if common < len(have) else True
+                if ok and common < len(ids):
+                    ok = eng.core.append_tokens(self.sid, ids[common:])
+                if not ok:
                     eng.core.release(self.sid)
                     self.sid = eng.add_request(ids, max_new_tokens=1 << 20, temperature=0.0, ignore_eos=True)
         out = []

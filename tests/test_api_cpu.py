@@ -148,3 +148,38 @@ def test_ngram_proposer():
     p = NgramProposer(max_ngram=3)
     assert p.propose([1, 2, 3, 9, 9, 1, 2, 3], 2).tolist() == [9, 9]
     assert p.propose([1, 2, 3], 4).tolist() == []
+
+
+def test_draft_model_proposer_keeps_its_sequence_aligned_without_resubmitting(model_dir):
+    """A draft engine with the target's own weights proposes the true continuation, so every draft is accepted; the
+    proposer re-aligns its sequence after each verification by rewind + append (never by re-submitting the prompt)."""
+    from onnx_genai_b200.speculative import DraftModelProposer
+
+    plain = _engine(model_dir)
+    spec = _engine(model_dir, max_draft_tokens=3)
+    draft = _engine(model_dir)
+    prompt = list(range(40, 75))
+    want = plain.generate(prompt, GenerateOptions(max_new_tokens=20, ignore_eos=True))
+    admitted = []
+    real_add = draft.llm.add_request
+    draft.llm.add_request = lambda *a, **k: (admitted.append(1), real_add(*a, **k))[1]
+    spec.proposer_factory = lambda: DraftModelProposer(draft.llm)
+    got = spec.generate(prompt, GenerateOptions(max_new_tokens=20, ignore_eos=True, speculative=True))
+    assert got.token_ids == want.token_ids
+    # everything is accepted except drafts that fall beyond the 20-token budget in the last step
+    assert got.speculative.proposed_tokens - 3 <= got.speculative.accepted_tokens <= got.speculative.proposed_tokens
+    assert got.speculative.accepted_per_step > 2
+    assert len(admitted) == 1                     # one submission for the whole generation
+
+    class HalfWrong(DraftModelProposer):          # corrupt the second draft token: rewind + append of the correction
+        def propose(self, token_ids, k):
+            out = super().propose(token_ids, k).copy()
+            if len(out) > 1:
+                out[1] = (int(out[1]) + 1) % 1000
+            return out
+
+    admitted.clear()
+    spec.proposer_factory = lambda: HalfWrong(draft.llm)
+    mixed = spec.generate(prompt, GenerateOptions(max_new_tokens=20, ignore_eos=True, speculative=True))
+    assert mixed.token_ids == want.token_ids and 0 < mixed.speculative.accepted_tokens < mixed.speculative.proposed_tokens
+    assert len(admitted) == 1
