@@ -308,13 +308,23 @@ class LLMEngine:
     def step(self) -> StepOutput:
         """Schedule, run and commit one engine step."""
         out = StepOutput()
+        batches: dict = {}
         for sid, proposer in list(self.proposers.items()):   # speculative drafts for the coming step
             toks = self.core.seq_tokens(sid) if self.core.seq_len(sid) > 0 else None
             if toks is None:
                 continue
+            key = getattr(proposer, "batch_key", None)
+            if key is not None:                              # proposers that can answer together (one draft engine)
+                batches.setdefault(key, []).append((sid, proposer, toks))
+                continue
             draft = proposer.propose(toks, self.cfg.max_draft_tokens)
             if len(draft):
                 self.core.set_draft(sid, draft)
+        for items in batches.values():
+            drafts = type(items[0][1]).propose_many([p for _, p, _ in items], [t for _, _, t in items], self.cfg.max_draft_tokens)
+            for (sid, _, _), draft in zip(items, drafts):
+                if len(draft):
+                    self.core.set_draft(sid, draft)
         t = self.core.build_step(self.plan_host.data_ptr())
         if t <= 0:
             return out

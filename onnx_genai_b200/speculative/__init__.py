@@ -77,39 +77,52 @@ class DraftModelProposer(SpeculativeProposer):
         self.sid = None
         self.synced = []
 
-    def propose(self, token_ids, k):
-        ids = [int(t) for t in token_ids]
+    @property
+    def batch_key(self):
+        """Proposers that share a draft engine are asked together (see :meth:`propose_many`)."""
+        return ("draft_model", id(self.eng))
+
+    def _align(self, ids):
+        """Make the draft's sequence equal to ``ids``: keep the common prefix (and its KV pages), drop what the
+        target rejected, feed what the target chose instead."""
         eng = self.eng
         if self.sid is None:
             self.sid = eng.add_request(ids, max_new_tokens=1 << 20, temperature=0.0, ignore_eos=True)
-        else:
-            # keep the longest common prefix with what the draft already holds, then re-feed the rest
-            have = eng.core.seq_tokens(self.sid).tolist()
-            common = 0
-            for a, b in zip(have, ids):
-                if a != b:
-                    break
-                common += 1
-            if common < 1:
-                eng.core.release(self.sid)
-                self.sid = eng.add_request(ids, max_new_tokens=1 << 20, temperature=0.0, ignore_eos=True)
-            elif common < len(have) or common < len(ids):
-                # drop what the target rejected, then feed what the target chose instead (usually one token):
-                # the draft keeps its KV pages for the common prefix, however long the prompt is
-                ok = eng.core.rewind(self.sid, common) if common < len(have) else True
-                if ok and common < len(ids):
-                    ok = eng.core.append_tokens(self.sid, ids[common:])
-                if not ok:
-                    eng.core.release(self.sid)
-                    self.sid = eng.add_request(ids, max_new_tokens=1 << 20, temperature=0.0, ignore_eos=True)
-        out = []
+            return
+        have = eng.core.seq_tokens(self.sid).tolist()
+        common = 0
+        for a, b in zip(have, ids):
+            if a != b:
+                break
+            common += 1
+        ok = common >= 1
+        if ok and common < len(have):
+            ok = eng.core.rewind(self.sid, common)
+        if ok and common < len(ids):
+            ok = eng.core.append_tokens(self.sid, ids[common:])
+        if not ok:
+            eng.core.release(self.sid)
+            self.sid = eng.add_request(ids, max_new_tokens=1 << 20, temperature=0.0, ignore_eos=True)
+
+    def propose(self, token_ids, k):
+        return self.propose_many([self], [token_ids], k)[0]
+
+    @staticmethod
+    def propose_many(proposers, token_lists, k):
+        """Drafts for several target sequences from one draft engine: every draft sequence is re-aligned first,
+        then the engine is stepped until each has k new tokens, so the draft model runs batched steps instead of
+        k steps per target sequence."""
+        eng = proposers[0].eng
+        for p, toks in zip(proposers, token_lists):
+            p._align([int(t) for t in toks])
+        out = {p.sid: [] for p in proposers}
         guard = 0
-        while len(out) < k and guard < k + 64:
+        while any(len(v) < k for v in out.values()) and guard < k + 64 and eng.has_work:
             guard += 1
             for sid, tok, fin in eng.step().events:
-                if sid == self.sid:
-                    out.append(tok)
-        return np.asarray(out[:k], dtype=np.int32)
+                if sid in out:
+                    out[sid].append(tok)
+        return [np.asarray(out[p.sid][:k], dtype=np.int32) for p in proposers]
 
     def close(self):
         if self.sid is not None:

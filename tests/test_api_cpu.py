@@ -183,3 +183,22 @@ def test_draft_model_proposer_keeps_its_sequence_aligned_without_resubmitting(mo
     mixed = spec.generate(prompt, GenerateOptions(max_new_tokens=20, ignore_eos=True, speculative=True))
     assert mixed.token_ids == want.token_ids and 0 < mixed.speculative.accepted_tokens < mixed.speculative.proposed_tokens
     assert len(admitted) == 1
+
+
+def test_draft_model_proposals_are_batched_across_sequences(model_dir):
+    """Two requests decoded together share one draft engine: their drafts come from batched draft steps."""
+    from onnx_genai_b200.speculative import DraftModelProposer
+
+    plain = _engine(model_dir)
+    spec = _engine(model_dir, max_draft_tokens=3)
+    draft = _engine(model_dir)
+    prompts = [list(range(40, 75)), list(range(100, 118))]
+    opt = GenerateOptions(max_new_tokens=16, ignore_eos=True)
+    want = plain.generate_batch(prompts, opt)
+    spec.proposer_factory = lambda: DraftModelProposer(draft.llm)
+    steps0 = draft.llm.steps
+    got = spec.generate_batch(prompts, GenerateOptions(max_new_tokens=16, ignore_eos=True, speculative=True))
+    assert [g.token_ids for g in got] == [w.token_ids for w in want]
+    verify_steps = spec.llm.core.spec_steps
+    # with per-sequence proposals the draft would need about 3 steps per sequence per verification step
+    assert draft.llm.steps - steps0 < 3 * verify_steps
