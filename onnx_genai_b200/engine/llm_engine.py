@@ -274,7 +274,7 @@ class LLMEngine:
         [k*chunk, (k+1)*chunk): its lm_head GEMM and sampler see 1/tp of the rows and one all-gather of the token
         ids (4 bytes per row) replaces the broadcast that kept replicas in step.  Steps whose logits are needed on
         the host (custom samplers, log-probabilities, embeddings, speculative verification) keep all rows."""
-        return (self.tp > 1 and self.cfg.shard_sampling and self.device.type == "cuda" and r >= self.tp
+        return (self.tp > 1 and self.cfg.shard_sampling and r >= self.tp
                 and not self.host_samplers and not self.hidden_taps and self.cfg.max_draft_tokens == 0)
 
     def forward_and_sample_sharded(self, si, r: int, greedy: bool) -> None:
@@ -297,7 +297,12 @@ class LLMEngine:
         finally:
             si.logit_rows, si.num_logit_rows = saved_rows, saved_n
         out = self._shard_buf[:n_run]
-        if greedy:
+        if self.device.type != "cuda":
+            toks = (ops.argmax(logits) if greedy else
+                    ops.sample(logits, self.temperature[lo:lo + n_run], self.top_k[lo:lo + n_run], self.top_p[lo:lo + n_run],
+                               self.min_p[lo:lo + n_run], self.uniform[lo:lo + n_run]))
+            out.copy_(toks)
+        elif greedy:
             ops.argmax(logits, out=out)
         else:
             ops.sample(logits, self.temperature[lo:lo + n_run], self.top_k[lo:lo + n_run], self.top_p[lo:lo + n_run],
@@ -361,7 +366,8 @@ class LLMEngine:
             elif sharded:
                 self.forward_and_sample_sharded(si, r, bool((temps <= 0).all()))
                 self.sampled_host[:r].copy_(self.sampled_dev[:r], non_blocking=True)
-                torch.cuda.current_stream().synchronize()
+                if self.device.type == "cuda":
+                    torch.cuda.current_stream().synchronize()
                 self.d2h_bytes += r * 4
             elif self.device.type == "cuda":
                 if (temps <= 0).all():

@@ -56,6 +56,10 @@ class NcclComm:
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         self.calls = 0
+        # the same class drives gloo ranks on CPU, which is how the multi-rank host logic (sharding, replica
+        # scheduling, row-split sampling) is tested without GPUs
+        self.backend_name = dist.get_backend(group)
+        self._scalar_device = "cuda" if self.backend_name == "nccl" else "cpu"
 
     def all_reduce(self, t):
         from .. import ops
@@ -85,12 +89,12 @@ class NcclComm:
         dist.barrier(group=self.group)
 
     def min_int(self, v: int) -> int:
-        t = torch.tensor([v], dtype=torch.int64, device="cuda")
+        t = torch.tensor([v], dtype=torch.int64, device=self._scalar_device)
         dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.group)
         return int(t.item())
 
     def max_float(self, v: float) -> float:
-        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+        t = torch.tensor([v], dtype=torch.float64, device=self._scalar_device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
         return float(t.item())
 

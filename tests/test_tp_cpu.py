@@ -1,0 +1,41 @@
+"""Tensor parallelism with CPU ranks (gloo): the host-side logic -- head / column / expert sharding, replicas that
+schedule identically, the row-split lm_head + sampler with its token all-gather -- against a single rank."""
+import os
+import subprocess
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(nproc, mode, out, port):
+    env = dict(os.environ, PYTHONPATH=ROOT, OGB_TEST_DEVICE="cpu", CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2")
+    worker = os.path.join(ROOT, "tests", "tp_worker.py")
+    if nproc == 1:
+        cmd = [sys.executable, worker, mode, out]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+               "--master-port", str(port), worker, mode, out]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-4000:]
+    return torch.load(out)
+
+
+def test_two_cpu_ranks_match_one_rank_dense_and_moe(tmp_path):
+    for suffix, port in (("", 29651), ("-moe", 29652)):
+        single = _run(1, "nccl" + suffix, str(tmp_path / f"s{suffix}.pt"), 0)
+        pair = _run(2, "nccl" + suffix, str(tmp_path / f"p{suffix}.pt"), port)
+        assert pair["backend"] == "gloo"
+        err = float((pair["logits"] - single["logits"]).norm() / single["logits"].norm())
+        assert err < 1e-4, (suffix, err)                       # fp32: only the summation order differs
+        assert pair["tokens"] == single["tokens"], suffix      # greedy tokens of every request, step by step
+
+
+def test_four_cpu_ranks_replicate_kv_heads(tmp_path):
+    """8 query heads / 2 KV heads over 4 ranks: each KV head is held by two ranks."""
+    single = _run(1, "nccl", str(tmp_path / "s.pt"), 0)
+    four = _run(4, "nccl", str(tmp_path / "t.pt"), 29653)
+    err = float((four["logits"] - single["logits"]).norm() / single["logits"].norm())
+    assert err < 1e-4, err
+    assert four["tokens"] == single["tokens"]
