@@ -152,6 +152,7 @@ class LLMEngine:
         self.hidden_taps: dict = {}       # seq id -> None until the request's first logits row exists, then its final hidden state
         self.graphs: dict = {}
         self.graph_replays = 0
+        self.verify_on_decode_kernel = 0   # steps whose draft rows ran on the split-KV decode kernel
         self.graph_declines: list = []
 
     # --------------------------------------------------------------------------------------
@@ -268,6 +269,41 @@ class LLMEngine:
         finally:
             si.num_tokens, si.num_decode, si.num_logit_rows = saved
 
+    # ---- speculative verification rows on the split-KV decode kernel ------------------------------
+    VERIFY_MIN_CTX = 2048
+
+    def _plan_verify_rows(self, si) -> None:
+        """When every non-decode sequence of the step is a short run of draft rows over a long context, describe
+        each query row as a decode row (own context length, the sequence's page-table row).  The prefill kernel
+        gives one CTA per (64-row tile, head) the whole context to walk; the decode kernel splits the context
+        across CTAs, which is what a 32k-token verification needs.  Only the Python-driven executor uses this
+        (fp8 KV always runs there); otherwise the fields stay None."""
+        si.verify_table = si.verify_ctx = None
+        np_ = si.num_prefill_seqs
+        if (np_ == 0 or self.cfg.max_draft_tokens <= 0 or self.device.type != "cuda" or self.native_executor
+                or si.max_ctx < self.VERIFY_MIN_CTX):
+            return
+        nd, L, pn = si.num_decode, self.L, self.plan_np
+        cu = pn[L.cu_q:L.cu_q + np_ + 1].astype(np.int64)
+        qlen = cu[1:] - cu[:-1]
+        if qlen.max() > self.cfg.max_draft_tokens + 1:
+            return                                        # a real prefill chunk is in the step
+        ctx_end = pn[L.ctx_len + nd:L.ctx_len + nd + np_].astype(np.int64)
+        seq_of_row = np.repeat(np.arange(np_), qlen)
+        within = np.arange(int(cu[-1])) - np.repeat(cu[:-1], qlen)
+        ctx_rows = (ctx_end[seq_of_row] - qlen[seq_of_row] + within + 1).astype(np.int32)
+        rows = int(cu[-1])
+        if rows > self.sampled_dev.numel():
+            return
+        idx = torch.from_numpy(seq_of_row.astype(np.int64)).to(self.device, non_blocking=True)
+        si.verify_table = si.page_table[nd:nd + np_].index_select(0, idx).contiguous()
+        si.verify_ctx = torch.from_numpy(ctx_rows).to(self.device, non_blocking=True)
+        splits = self._pick_splits(rows, int(si.max_ctx))
+        if self.model.ensure_split_scratch(splits):
+            self.graphs.clear()
+        si.verify_splits = splits
+        self.verify_on_decode_kernel += 1
+
     # ---- TP: rows of the logits/sampling stage split over the ranks -------------------------------
     def _shard_rows(self, r: int) -> bool:
         """With a replicated lm_head every rank would compute and sample all r rows.  Instead rank k takes rows
@@ -344,10 +380,10 @@ class LLMEngine:
             self.h2d_bytes += self.dev_words * 4
         if hdr[HDR["num_swap_out"]] or hdr[HDR["num_swap_in"]] or hdr[HDR["num_copies"]]:
             self._page_moves(hdr)
+        self._plan_verify_rows(si)
         if si.num_decode:
             splits = self._pick_splits(si.num_decode, si.max_ctx)
-            if splits != self.model.decode_splits:
-                self.model.set_decode_splits(splits)
+            if splits != self.model.decode_splits and self.model.set_decode_splits(splits):
                 self.graphs.clear()          # split scratch was reallocated: captured pointers are stale
         graphed = self._graph_step(si, r) if self._graph_eligible(si, r, hdr) else False
         sharded = (not graphed) and self._shard_rows(r)

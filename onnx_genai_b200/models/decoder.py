@@ -153,6 +153,12 @@ class StepInputs:
     tile_q0: torch.Tensor
     logit_rows: torch.Tensor       # [R]
     max_ctx: int = 0
+    # Speculative verification over long contexts: when every "prefill" sequence of the step is just a handful
+    # of draft rows, the engine describes those rows as decode rows (one page-table row and context length per
+    # query row) so attention runs on the split-KV decode kernel instead of walking the whole context in one CTA.
+    verify_table: torch.Tensor | None = None   # [rows, max_pages]
+    verify_ctx: torch.Tensor | None = None     # [rows]
+    verify_splits: int = 1
 
 
 class KVCache:
@@ -289,13 +295,21 @@ class DecoderModel:
             self._tp_args_cache[chunk] = hit
         return hit, chunk
 
-    def set_decode_splits(self, splits: int):
+    def ensure_split_scratch(self, splits: int) -> bool:
+        """Scratch for `splits` partial results per (row, head); grows only.  True when it was reallocated (pointers
+        captured in CUDA graphs are then stale)."""
+        if splits <= 1 or self.device.type != "cuda" or splits <= getattr(self, "_split_capacity", 1):
+            return False
+        self._split_capacity = splits
+        self.part_o = torch.empty(self.max_seqs * self.hq * splits * self.d, dtype=torch.float32, device=self.device)
+        self.part_ml = torch.empty(self.max_seqs * self.hq * splits * 2, dtype=torch.float32, device=self.device)
+        if self.native:
+            self._native_lib.ogb_decoder_set_split_scratch(self.native, self.part_o.data_ptr(), self.part_ml.data_ptr())
+        return True
+
+    def set_decode_splits(self, splits: int) -> bool:
         self.decode_splits = splits
-        if splits > 1 and self.device.type == "cuda":
-            self.part_o = torch.empty(self.max_seqs * self.hq * splits * self.d, dtype=torch.float32, device=self.device)
-            self.part_ml = torch.empty(self.max_seqs * self.hq * splits * 2, dtype=torch.float32, device=self.device)
-            if self.native:
-                self._native_lib.ogb_decoder_set_split_scratch(self.native, self.part_o.data_ptr(), self.part_ml.data_ptr())
+        return self.ensure_split_scratch(splits)
 
     # --------------------------------------------------------------------------------------
     def forward(self, si: StepInputs, kv: KVCache) -> torch.Tensor:
@@ -356,7 +370,12 @@ class DecoderModel:
                 ops.paged_decode(qkv[:nd], attn[:nd], pool, si.page_table[:nd], si.ctx_len[:nd], self.hq, self.hkv,
                                  self.d, self.scale, self.decode_splits, self.part_o, self.part_ml, cfg.sliding_window,
                                  kv_scales=kv.scales[li] if kv.scales is not None else None)
-            if si.num_prefill_seqs > 0:
+            if si.num_prefill_seqs > 0 and si.verify_table is not None:
+                nv = si.verify_ctx.numel()
+                ops.paged_decode(qkv[nd:nd + nv], attn[nd:nd + nv], pool, si.verify_table, si.verify_ctx, self.hq, self.hkv,
+                                 self.d, self.scale, si.verify_splits, self.part_o, self.part_ml, cfg.sliding_window,
+                                 kv_scales=kv.scales[li] if kv.scales is not None else None)
+            elif si.num_prefill_seqs > 0:
                 np_ = si.num_prefill_seqs
                 ops.paged_prefill(qkv[nd:], attn[nd:], pool, si.page_table[nd:nd + np_], si.ctx_len[nd:nd + np_],
                                   si.cu_q, si.tile_seq, si.tile_q0, si.num_tiles, self.hq, self.hkv, self.d, self.scale,

@@ -130,3 +130,58 @@ def test_cuda_graph_replay_of_decode_steps_matches_eager():
             assert eng.graph_replays >= 30 and len(eng.graphs) == 2      # one graph per sampler kind, many replays
     assert outs[(True, 0.0)] == outs[(False, 0.0)]
     assert outs[(True, 0.9)] == outs[(False, 0.9)]
+
+
+CFG128 = DecoderConfig(name="g128", num_layers=2, hidden=256, num_heads=4, num_kv_heads=2, head_dim=128, intermediate=512,
+                       vocab=1024, rope_theta=1e6, tie_embeddings=False, qkv_bias=True, max_position=4096)
+
+
+def test_fp8_kv_engine_stays_close_to_bf16_kv():
+    w = random_weights(CFG128, "cuda", seed=5, std=0.05)
+    prompt = np.random.default_rng(2).integers(0, CFG128.vocab, size=300).astype(np.int32)
+    logits = {}
+    for kv in ("bf16", "fp8"):
+        eng = LLMEngine(EngineConfig(model=CFG128, num_pages=64, max_seqs=2, max_tokens_per_step=512, max_seq_len=512,
+                                     kv_dtype=kv), weights=w, device="cuda")
+        eng.add_request(prompt, 2)
+        eng.step()
+        eng.step()                                            # second step: a decode row that reads the stored pages
+        logits[kv] = eng.model.logits[:1].float().cpu().clone()
+    ops.check_status()
+    err = float((logits["fp8"] - logits["bf16"]).norm() / logits["bf16"].norm())
+    assert err < 6e-2, err
+    assert ops.launch_counts["paged_decode_fp8"] > 0 and ops.launch_counts["paged_prefill_fp8"] > 0
+
+
+def test_long_context_draft_rows_run_on_the_split_kv_decode_kernel():
+    """Speculative verification over a 2.2k-token context with fp8 pages: the draft rows go to the decode kernel
+    (one page-table row and context length per query row); tokens equal the non-speculative run."""
+    from onnx_genai_b200.speculative import SpeculativeProposer
+
+    w = random_weights(CFG128, "cuda", seed=6, std=0.08)
+    prompt = np.random.default_rng(3).integers(0, CFG128.vocab, size=2200).astype(np.int32)
+    mk = lambda k: LLMEngine(EngineConfig(model=CFG128, num_pages=400, max_seqs=2, max_tokens_per_step=2304, max_seq_len=2400,
+                                          kv_dtype="fp8", max_draft_tokens=k, enable_prefix_cache=False), weights=w, device="cuda")
+    want = mk(0).generate([prompt], max_new_tokens=16)[0]
+
+    class Mixed(SpeculativeProposer):                     # true continuation, every third proposal corrupted
+        calls = 0
+
+        def propose(self, token_ids, k):
+            done = len(token_ids) - len(prompt)
+            out = np.asarray(want[done:done + k], dtype=np.int32).copy()
+            Mixed.calls += 1
+            if Mixed.calls % 3 == 0 and len(out):
+                out[-1] = (int(out[-1]) + 7) % CFG128.vocab
+            return out
+
+    eng = mk(3)
+    sid = eng.add_request(prompt, 16)
+    eng.proposers[sid] = Mixed()
+    got = []
+    while eng.has_work:
+        got += [tok for s, tok, fin in eng.step().events if s == sid]
+    ops.check_status()
+    assert eng.verify_on_decode_kernel > 0 and eng.core.spec_accepted > 0
+    agree = next((i for i, (a, b) in enumerate(zip(got, want)) if a != b), len(want))
+    assert agree >= 12, (agree, got, want)                # identical unless an fp8 near-tie flips late in the run
