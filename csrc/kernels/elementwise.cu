@@ -232,7 +232,7 @@ __global__ void rope_kv_append_kernel(__nv_bfloat16* __restrict__ qkv, const int
     hp[i1] = __float2bfloat16(x1 * c + x0 * s);
   }
   __syncthreads();
-  if (!slot_ok) return;
+  if (!slot_ok || pool == nullptr) return;     // pool == nullptr: rotation only (the e4m3 append is its own launch)
   const int64_t page = slot / page_size;
   const int off = static_cast<int>(slot % page_size);
   if constexpr (!FP8) {
@@ -246,33 +246,65 @@ __global__ void rope_kv_append_kernel(__nv_bfloat16* __restrict__ qkv, const int
       __nv_bfloat16* dst = pl + ((((page * hkv + h) * 2 + kv) * page_size + off) * static_cast<int64_t>(d));
       reinterpret_cast<uint4*>(dst)[v] = val;
     }
-  } else {
-    // e4m3 pages with one scale per (page, head, k|v).  The first token written to a page fixes
-    // the scale (amax * 2 / 448, so later tokens have headroom); later tokens saturate to it.
-    uint8_t* pl = static_cast<uint8_t*>(pool);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-    for (int u = warp; u < 2 * hkv; u += nwarps) {
-      const int kv = u / hkv, h = u % hkv;
-      const __nv_bfloat16* src = row + (hq + kv * hkv + h) * d;
+  }
+}
+
+// e4m3 append as its own launch, after the rotation kernel.  One scale per (page, head, K|V), fixed by the
+// page's first token (amax * 2 / 448: headroom for the 15 tokens that follow; they saturate to it).  A prefill
+// chunk writes many tokens of one page in the same launch, so a token must not read the scale from memory while
+// the first token's CTA may still be writing it: when the page's first token is a row of this launch (row
+// t - offset carries slot - offset), every token of the page derives the scale from that row's values, which the
+// preceding rotation launch has finalised; otherwise the page was started by an earlier launch and the stored
+// scale is read.
+__global__ void kv_append_fp8_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ slots,
+                                     uint8_t* __restrict__ pool, float* __restrict__ scales, int hq, int hkv, int d,
+                                     int page_size, int64_t num_slots, int* status) {
+  const int t = blockIdx.x;
+  const int64_t slot = slots[t];
+  if (slot < 0) return;
+  if (slot >= num_slots) {
+    if (threadIdx.x == 0) atomicOr(status, kStatusIndexOutOfRange);
+    return;
+  }
+  const int64_t page = slot / page_size;
+  const int off = static_cast<int>(slot % page_size);
+  const size_t row_elems = static_cast<size_t>(hq + 2 * hkv) * d;
+  const __nv_bfloat16* row = qkv + static_cast<size_t>(t) * row_elems;
+  bool first_in_launch = true;
+  const __nv_bfloat16* first_row = row;
+  if (off != 0) {
+    const int t0 = t - off;
+    if (t0 >= 0 && slots[t0] == slot - off) first_row = qkv + static_cast<size_t>(t0) * row_elems;
+    else first_in_launch = false;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int u = warp; u < 2 * hkv; u += nwarps) {
+    const int kv = u / hkv, h = u % hkv;
+    const size_t col = static_cast<size_t>(hq + kv * hkv + h) * d;
+    float* sc = scales + ((page * hkv + h) * 2 + kv);
+    float scale = 0.f;
+    if (first_in_launch) {
       float amax = 0.f;
-      for (int j = lane; j < d; j += 32) amax = fmaxf(amax, fabsf(__bfloat162float(src[j])));
+      for (int j = lane; j < d; j += 32) amax = fmaxf(amax, fabsf(__bfloat162float(first_row[col + j])));
       amax = warp_max(amax);
-      float* sc = scales + ((page * hkv + h) * 2 + kv);
-      float scale;
-      if (off == 0) {
+      scale = fmaxf(amax * 2.f, 1e-6f) / 448.f;
+      if (off == 0 && lane == 0) *sc = scale;
+    } else {
+      scale = *sc;
+      if (!(scale > 0.f)) {                        // a page that was never started: treat this token as its first
+        float amax = 0.f;
+        for (int j = lane; j < d; j += 32) amax = fmaxf(amax, fabsf(__bfloat162float(row[col + j])));
+        amax = warp_max(amax);
         scale = fmaxf(amax * 2.f, 1e-6f) / 448.f;
         if (lane == 0) *sc = scale;
-      } else {
-        scale = *sc;
-        if (!(scale > 0.f)) scale = fmaxf(amax * 2.f, 1e-6f) / 448.f;
       }
-      const float inv = 1.f / scale;
-      uint8_t* dst = pl + ((((page * hkv + h) * 2 + kv) * page_size + off) * static_cast<int64_t>(d));
-      for (int j = lane; j < d; j += 32) {
-        float v = __bfloat162float(src[j]) * inv;
-        v = fminf(fmaxf(v, -448.f), 448.f);
-        dst[j] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
-      }
+    }
+    const float inv = 1.f / scale;
+    uint8_t* dst = pool + ((((page * hkv + h) * 2 + kv) * page_size + off) * static_cast<int64_t>(d));
+    for (int j = lane; j < d; j += 32) {
+      float v = __bfloat162float(row[col + j]) * inv;
+      v = fminf(fmaxf(v, -448.f), 448.f);
+      dst[j] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
     }
   }
 }
@@ -352,9 +384,12 @@ extern "C" int ogb_rope_kv_append_fp8(void* qkv, const int* positions, const int
                                       void* stream) {
   if (tokens <= 0) return 0;
   if (d % 8 || rotary_dim % 2 || rotary_dim > d) return -3;
-  rope_kv_append_kernel<true><<<tokens, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<__nv_bfloat16*>(qkv), positions, slots, cos_sin, pool, scales, hq, hkv, d, rotary_dim, interleaved,
-      page_size, num_slots, max_pos, status);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  rope_kv_append_kernel<false><<<tokens, 256, 0, st>>>(static_cast<__nv_bfloat16*>(qkv), positions, slots, cos_sin, nullptr,
+                                                      nullptr, hq, hkv, d, rotary_dim, interleaved, page_size, num_slots,
+                                                      max_pos, status);
+  kv_append_fp8_kernel<<<tokens, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(qkv), slots, static_cast<uint8_t*>(pool), scales,
+                                               hq, hkv, d, page_size, num_slots, status);
   return static_cast<int>(cudaGetLastError());
 }
 

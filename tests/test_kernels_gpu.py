@@ -418,3 +418,36 @@ def test_rope_kv_append_fp8_roundtrip():
     assert float(clipped) < 0.02                                   # 2x headroom over the first token's amax
     err = (deq - bf_pool.float()).abs() / (bf_pool.float().abs() + 0.05 * bf_pool.float().abs().amax())
     assert float(err[(bf_pool.float().abs() <= 448 * scales[..., None, None])].mean()) < 0.05
+
+
+def test_rope_kv_append_fp8_one_launch_equals_token_by_token():
+    """A prefill chunk appends many tokens of a page in one launch; the stored bytes and scales must be exactly those
+    of appending the tokens one launch at a time (every token of a page uses the scale of the page's first token),
+    also when the pages held another sequence's scales before, and when a later chunk continues a page."""
+    torch.manual_seed(15)
+    hq, hkv, d, pages = 4, 2, 128, 5
+    t = pages * ref.PAGE - 5                                        # the last page stays partly empty
+    qkv = (torch.randn(t, (hq + 2 * hkv) * d, device=DEV) * torch.linspace(0.2, 3.0, t, device=DEV)[:, None]).bfloat16()
+    pos = torch.arange(t, dtype=torch.int32, device=DEV)
+    slots = torch.arange(t, dtype=torch.int32, device=DEV)
+    cs = ref.rope_table(256, d, 1e4, DEV)
+
+    def fresh():
+        pool = torch.zeros(pages, hkv, 2, ref.PAGE, d, device=DEV, dtype=torch.uint8)
+        scales = torch.full((pages, hkv, 2), 123.0, device=DEV)      # stale scales of a previous owner
+        return pool, scales
+
+    pool_a, scales_a = fresh()
+    for i in range(t):
+        ops.rope_kv_append(qkv[i:i + 1].clone(), pos[i:i + 1], slots[i:i + 1], cs, pool_a, hq, hkv, d, kv_scales=scales_a)
+    pool_b, scales_b = fresh()
+    ops.rope_kv_append(qkv.clone(), pos, slots, cs, pool_b, hq, hkv, d, kv_scales=scales_b)
+    pool_c, scales_c = fresh()                                      # two chunks; the second starts in the middle of a page
+    cut = 2 * ref.PAGE + 7
+    ops.rope_kv_append(qkv[:cut].clone(), pos[:cut], slots[:cut], cs, pool_c, hq, hkv, d, kv_scales=scales_c)
+    ops.rope_kv_append(qkv[cut:].clone(), pos[cut:], slots[cut:], cs, pool_c, hq, hkv, d, kv_scales=scales_c)
+    torch.cuda.synchronize()
+    ops.check_status()
+    for pool, scales in ((pool_b, scales_b), (pool_c, scales_c)):
+        assert torch.equal(scales, scales_a)
+        assert torch.equal(pool, pool_a)
