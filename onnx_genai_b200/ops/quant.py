@@ -100,7 +100,8 @@ class QuantLinear:
         stream = torch.cuda.current_stream().cuda_stream
         if m <= FUSED_MAX_M and not _LEGACY_GEMV and x.stride(1) == 1:
             return self.fused(x, out)
-        if m <= GEMV_MAX_M and _LEGACY_GEMV:
+        # shapes the tensor-core GEMM does not take (N or K not a multiple of 32) stay on the generic GEMV up to 8 rows
+        if m <= GEMV_MAX_M and (_LEGACY_GEMV or self.n % 32 or self.k % 32):
             with timed_region("w4a16_gemv"):
                 rc = lib.ogb_w4a16_gemv(x.data_ptr(), self.qweight.data_ptr(), self.scales.data_ptr(),
                                         self.zp.data_ptr() if self.zp is not None else 0,
