@@ -250,6 +250,8 @@ def main():
         (si.num_tokens, si.num_decode, si.num_prefill_seqs, si.num_tiles, si.num_logit_rows, si.max_ctx, splits) = shapes[i]
         if splits != eng.model.decode_splits:
             eng.model.set_decode_splits(splits)
+        si.verify_table = si.verify_ctx = None      # per-step state of the live engine does not apply to a replayed plan
+        si.force_python = False
         r = si.num_logit_rows
         if r and eng._shard_rows(r):       # TP: the engine's own split of the lm_head + sampler rows, tokens all-gathered
             eng.forward_and_sample_sharded(si, r, args.greedy)

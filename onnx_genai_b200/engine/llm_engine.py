@@ -276,18 +276,20 @@ class LLMEngine:
         """When every non-decode sequence of the step is a short run of draft rows over a long context, describe
         each query row as a decode row (own context length, the sequence's page-table row).  The prefill kernel
         gives one CTA per (64-row tile, head) the whole context to walk; the decode kernel splits the context
-        across CTAs, which is what a 32k-token verification needs.  Only the Python-driven executor uses this
-        (fp8 KV always runs there); otherwise the fields stay None."""
+        across CTAs, which is what a 32k-token verification needs.  Such a step is driven from Python even when the
+        C++ step executor is bound (it has no per-row page tables)."""
         si.verify_table = si.verify_ctx = None
+        si.force_python = False
         np_ = si.num_prefill_seqs
-        if (np_ == 0 or self.cfg.max_draft_tokens <= 0 or self.device.type != "cuda" or self.native_executor
-                or si.max_ctx < self.VERIFY_MIN_CTX):
+        if np_ == 0 or self.device.type != "cuda" or si.max_ctx < self.VERIFY_MIN_CTX:
             return
         nd, L, pn = si.num_decode, self.L, self.plan_np
         cu = pn[L.cu_q:L.cu_q + np_ + 1].astype(np.int64)
         qlen = cu[1:] - cu[:-1]
-        if qlen.max() > self.cfg.max_draft_tokens + 1:
+        if qlen.max() > max(8, self.cfg.max_draft_tokens + 1):
             return                                        # a real prefill chunk is in the step
+        # (also taken by a draft engine: after a rejection it is fed one or two corrected tokens over the whole context)
+        si.force_python = bool(self.native_executor)      # the C++ step executor has no per-row page tables
         ctx_end = pn[L.ctx_len + nd:L.ctx_len + nd + np_].astype(np.int64)
         seq_of_row = np.repeat(np.arange(np_), qlen)
         within = np.arange(int(cu[-1])) - np.repeat(cu[:-1], qlen)

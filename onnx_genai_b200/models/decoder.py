@@ -159,6 +159,7 @@ class StepInputs:
     verify_table: torch.Tensor | None = None   # [rows, max_pages]
     verify_ctx: torch.Tensor | None = None     # [rows]
     verify_splits: int = 1
+    force_python: bool = False                 # run this step op by op from Python even if the C++ executor is bound
 
 
 class KVCache:
@@ -316,7 +317,7 @@ class DecoderModel:
         """Runs one step; returns logits [num_logit_rows, vocab] (a view of a static buffer)."""
         cfg, w = self.cfg, self.w
         t, nd = si.num_tokens, si.num_decode
-        if self.native:
+        if self.native and not si.force_python:
             before = self._native_lib.ogb_decoder_launches(self.native)
             rc = self._native_lib.ogb_decoder_step(
                 self.native, si.token_ids.data_ptr(), si.positions.data_ptr(), si.slots.data_ptr(), si.ctx_len.data_ptr(),

@@ -153,7 +153,8 @@ def test_fp8_kv_engine_stays_close_to_bf16_kv():
     assert ops.launch_counts["paged_decode_fp8"] > 0 and ops.launch_counts["paged_prefill_fp8"] > 0
 
 
-def test_long_context_draft_rows_run_on_the_split_kv_decode_kernel():
+@pytest.mark.parametrize("kv", ["fp8", "bf16"])
+def test_long_context_draft_rows_run_on_the_split_kv_decode_kernel(kv):
     """Speculative verification over a 2.2k-token context with fp8 pages: the draft rows go to the decode kernel
     (one page-table row and context length per query row); tokens equal the non-speculative run."""
     from onnx_genai_b200.speculative import SpeculativeProposer
@@ -161,7 +162,7 @@ def test_long_context_draft_rows_run_on_the_split_kv_decode_kernel():
     w = random_weights(CFG128, "cuda", seed=6, std=0.08)
     prompt = np.random.default_rng(3).integers(0, CFG128.vocab, size=2200).astype(np.int32)
     mk = lambda k: LLMEngine(EngineConfig(model=CFG128, num_pages=400, max_seqs=2, max_tokens_per_step=2304, max_seq_len=2400,
-                                          kv_dtype="fp8", max_draft_tokens=k, enable_prefix_cache=False), weights=w, device="cuda")
+                                          kv_dtype=kv, max_draft_tokens=k, enable_prefix_cache=False), weights=w, device="cuda")
     want = mk(0).generate([prompt], max_new_tokens=16)[0]
 
     class Mixed(SpeculativeProposer):                     # true continuation, every third proposal corrupted
