@@ -211,6 +211,63 @@ def cmd_show(args, profiler):
     return 0
 
 
+def cmd_validate(args, profiler):
+    """Checks a model directory the way the loader will read it and prints every problem found (exit 1 if any):
+    the graph is a recognised decoder, metadata parses and agrees with the graph, tokenizer and template are present,
+    int4 tensors have consistent shapes.  The counterpart of the reference's `validate_metadata` tool and checker."""
+    from . import metadata as md
+    from . import package as pkg
+    from .package import onnx_pb
+    from .package.decoder_graph import lower_decoder
+
+    problems, notes = [], []
+    try:
+        d = pkg.open_model_directory(args.model)
+    except Exception as exc:
+        print(json.dumps({"ok": False, "problems": [f"{exc}"]}, indent=1))
+        return 1
+    meta = None
+    try:
+        meta = d.load_metadata()
+    except Exception as exc:
+        problems.append(f"metadata: {exc}")
+    cfg = None
+    try:
+        cfg, weights, _ = lower_decoder(onnx_pb.load_model(d.model_path), keep_int4=True)
+        notes.append(f"decoder graph recognised: {cfg.num_layers} layers, hidden {cfg.hidden}, {cfg.num_heads}/{cfg.num_kv_heads} heads "
+                     f"of {cfg.head_dim}, vocab {cfg.vocab}, weights {cfg.weight_format}")
+        for li, lw in enumerate(weights.layers):
+            for name, lin in (lw.quant or {}).items():
+                for one in (lin if isinstance(lin, list) else [lin]):
+                    kb = (one.k + one.block - 1) // one.block
+                    if tuple(one.q.shape) != (one.q.shape[0], kb, one.block // 2):
+                        problems.append(f"layer {li} {name}: MatMulNBits weight has shape {tuple(one.q.shape)}, expected [N, {kb}, {one.block // 2}]")
+                    if tuple(one.scales.shape)[:2] != (one.q.shape[0], kb) and one.scales.numel() != one.q.shape[0] * kb:
+                        problems.append(f"layer {li} {name}: scales have {one.scales.numel()} entries, expected {one.q.shape[0] * kb}")
+    except Exception as exc:
+        problems.append(f"graph: {exc}")
+    if meta is not None and cfg is not None:
+        if meta.vocab_size and meta.vocab_size != cfg.vocab:
+            problems.append(f"metadata model.vocab_size={meta.vocab_size} but the embedding has {cfg.vocab} rows")
+        if meta.max_sequence_length and meta.max_sequence_length > cfg.max_position:
+            notes.append(f"metadata max_sequence_length {meta.max_sequence_length} exceeds the rotary table ({cfg.max_position}); the smaller wins")
+    if d.tokenizer_path is None:
+        notes.append("no tokenizer.json: text prompts are unavailable, token-id prompts still work")
+    else:
+        try:
+            from tokenizers import Tokenizer
+
+            tok = Tokenizer.from_file(d.tokenizer_path)
+            if cfg is not None and tok.get_vocab_size() > cfg.vocab:
+                problems.append(f"tokenizer has {tok.get_vocab_size()} entries but the model's vocabulary is {cfg.vocab}")
+        except Exception as exc:
+            problems.append(f"tokenizer: {exc}")
+    if d.chat_template is None:
+        notes.append("no chat template: `run` and /v1/chat/completions fall back to a plain role-prefixed format")
+    print(json.dumps({"ok": not problems, "model": d.model_path, "problems": problems, "notes": notes}, indent=1))
+    return 0 if not problems else 1
+
+
 def cmd_list(args, profiler):
     root = args.models_dir
     for name in sorted(os.listdir(root)):
@@ -299,6 +356,8 @@ def main(argv=None):
     _add_engine(s)
     sh = sub.add_parser("show")
     sh.add_argument("model")
+    va = sub.add_parser("validate", help="check a model directory and report every problem")
+    va.add_argument("model")
     ls = sub.add_parser("list")
     ls.add_argument("--models-dir", default=".")
     sub.add_parser("version")
@@ -312,7 +371,7 @@ def main(argv=None):
         print(f"onnx-genai-b200 {__version__}")
         return 0
     profiler = Profiler(args.profile, args.profile_json, args.profile_trace)
-    return {"generate": cmd_generate, "run": cmd_run, "serve": cmd_serve, "show": cmd_show, "list": cmd_list,
+    return {"generate": cmd_generate, "run": cmd_run, "serve": cmd_serve, "show": cmd_show, "validate": cmd_validate, "list": cmd_list,
             "export": cmd_export}[args.cmd](args, profiler)
 
 

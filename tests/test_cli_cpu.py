@@ -32,3 +32,24 @@ def test_generate_with_profile_json(pkg_dir, tmp_path):
     rep = json.load(open(prof))
     assert rep["completion_tokens"] <= 5 and "itl_ms" in rep and "kv" in rep
     assert json.load(open(trace))["traceEvents"]
+
+
+def test_validate_reports_problems_and_exit_code(tmp_path):
+    import json as _json
+    import subprocess
+    import sys as _sys
+
+    from onnx_genai_b200.bench.config_bench import _export
+
+    d = tmp_path / "m"
+    _export("tiny-llama", str(d), "fp32", layers=1)
+    run = lambda: subprocess.run([_sys.executable, "-m", "onnx_genai_b200", "validate", str(d)], capture_output=True, text=True, timeout=300)
+    ok = run()
+    assert ok.returncode == 0 and _json.loads(ok.stdout)["ok"] is True
+    meta = d / "inference_metadata.yaml"
+    meta.write_text(meta.read_text().replace("vocab_size: 32000", "vocab_size: 31999"))
+    bad = run()
+    report = _json.loads(bad.stdout)
+    assert bad.returncode == 1 and not report["ok"] and "31999" in report["problems"][0]
+    missing = subprocess.run([_sys.executable, "-m", "onnx_genai_b200", "validate", str(tmp_path / "nope")], capture_output=True, text=True)
+    assert missing.returncode == 1 and "not a directory" in missing.stdout
