@@ -170,7 +170,7 @@ class KVCache:
         self.num_pages = num_pages
         self.dtype = dtype
         tdtype = torch.bfloat16 if dtype == "bf16" else torch.uint8
-        if torch.device(device).type == "cpu":
+        if torch.device(device).type == "cpu" and dtype == "bf16":
             tdtype = torch.float32
         self.pools = [torch.zeros(num_pages, hkv, 2, ops.PAGE, cfg.head_dim, dtype=tdtype, device=device)
                       for _ in range(cfg.num_layers)]

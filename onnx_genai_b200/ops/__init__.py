@@ -264,7 +264,8 @@ def rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim=
     """Rotate q,k in place inside qkv and append k,v to the paged pool (bf16, or e4m3 with kv_scales)."""
     rotary_dim = rotary_dim or d
     if not qkv.is_cuda:
-        assert kv_scales is None
+        if kv_scales is not None:
+            return reference.rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim, interleaved, kv_scales)
         if _cpu_native(qkv) and qkv.is_contiguous() and pool.dtype == torch.float32 and pool.is_contiguous():
             return cpu.rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim, interleaved)
         return reference.rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim, interleaved)

@@ -90,12 +90,42 @@ def apply_rope(x, positions, cos_sin, rotary_dim, interleaved=False):
     return xf.to(x.dtype)
 
 
-def rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim=None, interleaved=False):
-    """In place: rotate q,k inside qkv [T,(hq+2hkv)*d]; write k,v to pool [P,hkv,2,PAGE,d] at slots."""
+def e4m3_bytes(x):
+    """fp32 -> e4m3 bytes with saturation at +-448 (round to nearest even), as the device conversion does."""
+    return x.float().clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+
+
+def kv_append_fp8(qkv, slots, pool, scales, hq, hkv, d):
+    """e4m3 page codec: one scale per (page, head, K|V), fixed by the page's first token at amax * 2 / 448 (headroom
+    for the 15 tokens that follow, which saturate to it).  Tokens are taken in row order, so a chunk that starts a
+    page and continues it in the same call behaves like one append per token.  pool [P,hkv,2,PAGE,d] uint8,
+    scales [P,hkv,2] fp32; qkv already rotated."""
+    t = qkv.shape[0]
+    v = qkv.view(t, hq + 2 * hkv, d).float()
+    for i in range(t):
+        slot = int(slots[i])
+        if slot < 0:
+            continue
+        page, off = slot // PAGE, slot % PAGE
+        for kv in range(2):
+            for h in range(hkv):
+                vec = v[i, hq + kv * hkv + h]
+                if off == 0 or not float(scales[page, h, kv]) > 0.0:
+                    scales[page, h, kv] = max(float(vec.abs().max()) * 2.0, 1e-6) / 448.0
+                inv = torch.tensor(1.0, dtype=torch.float32) / scales[page, h, kv].float()
+                pool[page, h, kv, off] = e4m3_bytes(vec * inv)
+
+
+def rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim=None, interleaved=False, kv_scales=None):
+    """In place: rotate q,k inside qkv [T,(hq+2hkv)*d]; write k,v to pool [P,hkv,2,PAGE,d] at slots
+    (e4m3 bytes with per-(page, head) scales when ``kv_scales`` is given)."""
     rotary_dim = rotary_dim or d
     t = qkv.shape[0]
     v = qkv.view(t, hq + 2 * hkv, d)
     v[:, : hq + hkv] = apply_rope(v[:, : hq + hkv], positions, cos_sin, rotary_dim, interleaved)
+    if kv_scales is not None:
+        kv_append_fp8(qkv, slots, pool, kv_scales, hq, hkv, d)
+        return qkv
     ok = slots >= 0
     page, off = (slots // PAGE).long(), (slots % PAGE).long()
     k, vv = v[:, hq : hq + hkv], v[:, hq + hkv :]
