@@ -476,7 +476,5 @@ def test_fp8_append_kernel_matches_the_cpu_codec_byte_for_byte():
     same_rot = (q_g.cpu() == q_c).float().mean()
     assert float(same_rot) > 0.999
     assert torch.allclose(sc_g.cpu(), sc_c, rtol=1e-2)
-    mismatch = (pool_g.cpu()[:, :, :, : ref.PAGE] != pool_c).float()
-    written = torch.zeros_like(mismatch)
-    written.view(pages * hkv * 2 * ref.PAGE, d)   # layout check only
-    assert float(mismatch.mean()) < 0.01
+    mismatch = (pool_g.cpu() != pool_c).float()
+    assert float(mismatch.mean()) < 0.01                            # bytes differ only where the rotated input differed by an ulp
