@@ -86,15 +86,14 @@ class DraftModelProposer(SpeculativeProposer):
         """Make the draft's sequence equal to ``ids``: keep the common prefix (and its KV pages), drop what the
         target rejected, feed what the target chose instead."""
         eng = self.eng
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
         if self.sid is None:
             self.sid = eng.add_request(ids, max_new_tokens=1 << 20, temperature=0.0, ignore_eos=True)
             return
-        have = eng.core.seq_tokens(self.sid).tolist()
-        common = 0
-        for a, b in zip(have, ids):
-            if a != b:
-                break
-            common += 1
+        have = np.asarray(eng.core.seq_tokens(self.sid), dtype=np.int32)
+        n = min(len(have), len(ids))
+        diff = np.flatnonzero(have[:n] != ids[:n])          # contexts run to tens of thousands of tokens: no Python loop
+        common = int(diff[0]) if len(diff) else n
         ok = common >= 1
         if ok and common < len(have):
             ok = eng.core.rewind(self.sid, common)
@@ -114,7 +113,7 @@ class DraftModelProposer(SpeculativeProposer):
         k steps per target sequence."""
         eng = proposers[0].eng
         for p, toks in zip(proposers, token_lists):
-            p._align([int(t) for t in toks])
+            p._align(toks)
         out = {p.sid: [] for p in proposers}
         guard = 0
         while any(len(v) < k for v in out.values()) and guard < k + 64 and eng.has_work:
