@@ -197,6 +197,20 @@ def ncu_case(name: str, iters: int = 3):
             eng = Engine.from_dir(tmp, device="cuda", max_seqs=1, max_seq_len=640, cuda_graphs=False)
             prompt = np.random.default_rng(0).integers(0, cfg.vocab, size=512).tolist()
             eng.generate_batch([prompt], GenerateOptions(max_new_tokens=1 + iters, greedy=True, ignore_eos=True))
+    elif name == "w4a16_gemv":
+        # decode-size int4 projection of the 7B shape: gate_up (N = 37888, K = 3584) with the RMSNorm prologue, one row
+        from onnx_genai_b200.ops import reference as ref
+        from onnx_genai_b200.ops.quant import QuantLinear
+
+        n_, k_ = 37888, 3584
+        q = torch.randint(0, 256, (n_, k_ // 32, 16), dtype=torch.uint8)
+        sc = (torch.rand(n_, k_ // 32) * 0.02 + 0.005).bfloat16()
+        lin = QuantLinear(q, sc, None, None, k=k_, device="cuda")
+        x = torch.randn(1, k_, device="cuda").bfloat16()
+        g = torch.ones(k_, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(1, n_, device="cuda", dtype=torch.bfloat16)
+        for _ in range(iters):
+            lin.fused(x, out, norm_weight=g, eps=1e-6)
     elif name == "decode":
         n, ctx = 256, 1200
         pages_per = (ctx + 15) // 16
