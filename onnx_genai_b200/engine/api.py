@@ -351,6 +351,30 @@ class Engine:
                                           time.perf_counter() - t0, list(e["state"]["logprobs"])))
         return results
 
+    # ------------------------------------------------------------------ fill in the middle
+    FIM_FORMATS = (("<|fim_prefix|>", "<|fim_suffix|>", "<|fim_middle|>"),          # Qwen2.5-Coder, StarCoder2
+                   ("<fim_prefix>", "<fim_suffix>", "<fim_middle>"),                # StarCoder
+                   ("<PRE>", "<SUF>", "<MID>"),                                     # Code Llama (with spaces, handled below)
+                   ("<｜fim▁begin｜>", "<｜fim▁hole｜>", "<｜fim▁end｜>"))           # DeepSeek-Coder (prefix, hole, end)
+
+    def fim_prompt(self, prefix: str, suffix: str) -> str:
+        """The model's fill-in-the-middle prompt for (prefix, suffix): the first known sentinel triple whose tokens
+        all exist in the tokenizer (the reference resolves the same sentinels, crates/onnx-genai-engine/src/fim.rs)."""
+        if self.tokenizer is None:
+            raise ValueError("fill-in-the-middle needs the model's tokenizer")
+        for a, b, c in self.FIM_FORMATS:
+            if all(self.tokenizer.token_to_id(t) is not None for t in (a, b, c)):
+                if a == "<｜fim▁begin｜>":
+                    return f"{a}{prefix}{b}{suffix}{c}"
+                if a == "<PRE>":
+                    return f"{a} {prefix} {b}{suffix} {c}"
+                return f"{a}{prefix}{b}{suffix}{c}"
+        raise ValueError("this model's tokenizer has no fill-in-the-middle sentinel tokens (looked for "
+                         + ", ".join(f[0] for f in self.FIM_FORMATS) + ")")
+
+    def generate_fim(self, prefix: str, suffix: str, options: GenerateOptions | None = None, **kw) -> GenerateResult:
+        return self.generate(self.fim_prompt(prefix, suffix), options, **kw)
+
     # ------------------------------------------------------------------ embeddings
     def embed(self, inputs, normalize: bool = True) -> np.ndarray:
         """[n, hidden] fp32: the final-normed hidden state of each input's last token (last-token pooling, the

@@ -27,17 +27,21 @@ def unpack_gate_up(packed: torch.Tensor, half: int):
 
 def byte_tokenizer_json(vocab_size: int) -> dict:
     """A self-contained byte-level tokenizer (tokenizers JSON): ids 0..255 are bytes, the rest are filler
-    tokens so any id below ``vocab_size`` decodes; <|endoftext|> takes the last id."""
+    tokens so any id below ``vocab_size`` decodes; <|endoftext|> takes the last id and, for vocabularies of 272
+    entries or more, the three Qwen-style fill-in-the-middle sentinels the ids before it."""
     from tokenizers import Tokenizer, decoders, models, pre_tokenizers
 
     alphabet = pre_tokenizers.ByteLevel.alphabet()
     vocab = {ch: i for i, ch in enumerate(sorted(alphabet))}
-    for i in range(len(vocab), vocab_size - 1):
+    fim = ["<|fim_prefix|>", "<|fim_middle|>", "<|fim_suffix|>"] if vocab_size >= 272 else []
+    for i in range(len(vocab), vocab_size - 1 - len(fim)):
         vocab[f"<|extra_{i}|>"] = i
+    for name in fim:                                   # fill-in-the-middle sentinels just below <|endoftext|>
+        vocab[name] = len(vocab)
     tok = Tokenizer(models.BPE(vocab=vocab, merges=[]))
     tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)
     tok.decoder = decoders.ByteLevel()
-    tok.add_special_tokens(["<|endoftext|>"])
+    tok.add_special_tokens(fim + ["<|endoftext|>"])
     return json.loads(tok.to_str())
 
 

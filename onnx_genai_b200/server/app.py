@@ -380,7 +380,10 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
             if isinstance(text, list):
                 text = text[0] if text and isinstance(text[0], str) else text
             if body.get("suffix") and isinstance(text, str):  # fill-in-the-middle
-                text = f"<|fim_prefix|>{text}<|fim_suffix|>{body['suffix']}<|fim_middle|>"
+                try:
+                    text = engine.fim_prompt(text, body["suffix"])
+                except ValueError as exc:
+                    raise HTTPException(400, str(exc)) from exc
         ids = engine.tokenize(text) if isinstance(text, str) else [int(t) for t in (text or [])]
         if not ids:
             raise HTTPException(400, "the prompt is empty after tokenisation")

@@ -202,3 +202,14 @@ def test_draft_model_proposals_are_batched_across_sequences(model_dir):
     verify_steps = spec.llm.core.spec_steps
     # with per-sequence proposals the draft would need about 3 steps per sequence per verification step
     assert draft.llm.steps - steps0 < 3 * verify_steps
+
+
+def test_fill_in_the_middle_prompt_uses_the_models_sentinels(model_dir):
+    eng = _engine(model_dir)
+    prompt = eng.fim_prompt("def add(a, b):\n    return ", "\n\nprint(add(1, 2))")
+    assert prompt.startswith("<|fim_prefix|>def add") and "<|fim_suffix|>\n\nprint" in prompt and prompt.endswith("<|fim_middle|>")
+    ids = eng.tokenize(prompt)
+    tok = eng.tokenizer
+    assert ids[0] == tok.token_to_id("<|fim_prefix|>") and ids[-1] == tok.token_to_id("<|fim_middle|>")   # sentinels are single tokens
+    res = eng.generate_fim("x = ", " + 1", GenerateOptions(max_new_tokens=5, ignore_eos=True))
+    assert res.completion_tokens == 5
