@@ -116,6 +116,7 @@ class InferenceMetadata:
     generation_defaults: dict = field(default_factory=dict)
     speculative: dict = field(default_factory=dict)
     quantization: dict = field(default_factory=dict)
+    workflow: object = None            # metadata.workflow.Workflow when the document carries pipeline.workflow
     raw: dict = field(default_factory=dict)
 
 
@@ -201,6 +202,30 @@ def parse(doc: dict) -> InferenceMetadata:
     md.generation_defaults = dict(gen.get("defaults") or {})
     md.speculative = dict(doc.get("speculative") or {})
     md.quantization = dict(doc.get("quantization") or {})
+    # A package that carries the workflow form needs no model.io block: the decoder ABI is derived from it.
+    wf_doc = (doc.get("pipeline") or {}).get("workflow") if isinstance(doc.get("pipeline"), dict) else None
+    if wf_doc is not None:
+        from . import workflow as _wf
+
+        try:
+            md.workflow = _wf.parse(wf_doc)
+        except _wf.WorkflowError as exc:
+            raise MetadataError(f"pipeline.workflow: {exc}") from exc
+        problems = _wf.validate(md.workflow)
+        if problems:
+            raise MetadataError("pipeline.workflow is not valid: " + "; ".join(problems[:5]) +
+                                (f" (and {len(problems) - 5} more)" if len(problems) > 5 else ""))
+        if md.io is None:
+            try:
+                abi = _wf.decoder_abi(md.workflow)
+            except _wf.WorkflowError:
+                abi = None               # not a single-decoder workflow: nothing to derive for the decoder executor
+            if abi is not None:
+                layout = {"bnsh": "head_major_bnsh", "bsnh": "sequence_major_bsnh", "bsh": "sequence_major_bsh"}.get(abi.kv_layout or "", abi.kv_layout or "head_major_bnsh")
+                md.io = ModelIo(token_input=abi.token_input, attention_mask_input=abi.attention_mask_input,
+                                position_ids_input=abi.position_ids_input, logits_output=abi.logits_output,
+                                kv_inputs=[a for a, _ in abi.kv_pairs], kv_outputs=[b for _, b in abi.kv_pairs], kv_layout=layout,
+                                aliasing=abi.kv_aliasing or "forbidden")
     return md
 
 
