@@ -178,7 +178,7 @@ def cmd_serve(args, profiler):
         reg = ModelRegistry.from_dir(args.models_dir, max_loaded=args.max_loaded_models, loader=loader, **app_kw)
         if args.model:
             reg.warmup([os.path.basename(os.path.abspath(args.model))])
-        app = RegistryApp(reg)
+        app = RegistryApp(reg, enable_admin_endpoints=args.enable_admin_endpoints)
     else:
         if not args.model:
             print("serve: give a model directory or --models-dir", file=sys.stderr)
@@ -351,6 +351,7 @@ def main(argv=None):
     s.add_argument("--max-sessions", type=int, default=256)
     s.add_argument("--max-queue-depth", type=int, default=256)
     s.add_argument("--enable-debug-endpoints", action="store_true")
+    s.add_argument("--enable-admin-endpoints", action="store_true", help="with --models-dir: /v1/admin/models load / warmup / unload")
     s.add_argument("--node-id", default="node-0")
     s.add_argument("--max-context", type=int, default=0)
     _add_engine(s)

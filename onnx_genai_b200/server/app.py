@@ -312,7 +312,34 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
         metrics.prompt_tokens(total)
         return {"object": "list", "model": model_name, "data": data, "usage": {"prompt_tokens": total, "total_tokens": total}}
 
+    # Media routes of the reference server (image generation, speech, transcription): this build serves decoder-only
+    # text models, so they answer 501 with the reason instead of 404.
+    def _not_served(kind: str):
+        async def handler():
+            raise HTTPException(501, f"{kind} needs a {kind.split()[0]} model pipeline; this server hosts decoder-only text models "
+                                     "(chat, completions, embeddings)")
+        return handler
+
+    for _path, _kind in (("/v1/images/generations", "image generation"), ("/sdapi/v1/txt2img", "image generation"),
+                         ("/sdapi/v1/img2img", "image generation"), ("/v1/audio/transcriptions", "audio transcription"),
+                         ("/v1/audio/speech", "speech synthesis")):
+        app.post(_path)(_not_served(_kind))
+
     if enable_debug_endpoints:
+        @app.get("/v1/debug/trace")
+        async def debug_trace_summary():
+            from ..utils import trace
+
+            with trace.TRACER.lock:
+                spans = list(trace.TRACER.spans)
+            totals: dict = {}
+            for name, a, b, _cat in spans:
+                t = totals.setdefault(name, [0, 0.0])
+                t[0] += 1
+                t[1] += b - a
+            return {"enabled": trace.TRACER.enabled, "spans": len(spans),
+                    "stages": {k: {"calls": v[0], "total_ms": round(v[1] * 1e3, 3)} for k, v in sorted(totals.items())}}
+
         @app.get("/v1/debug/config")
         async def debug_config():
             return {k: (v if isinstance(v, (int, float, str, bool, type(None))) else str(v)) for k, v in engine.llm.cfg.__dict__.items()}

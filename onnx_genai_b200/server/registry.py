@@ -106,8 +106,49 @@ class ModelRegistry:
 class RegistryApp:
     """ASGI application that routes each request to the sub-application of the model it names."""
 
-    def __init__(self, registry: ModelRegistry):
+    def __init__(self, registry: ModelRegistry, enable_admin_endpoints: bool = False):
         self.registry = registry
+        self.admin = enable_admin_endpoints
+
+    async def _admin(self, scope, send):
+        """GET /v1/admin/models, POST /v1/admin/models/{id}/load | warmup, DELETE /v1/admin/models/{id}."""
+        reg, path, method = self.registry, scope["path"], scope["method"]
+        parts = [p for p in path.split("/") if p][3:]            # after v1/admin/models
+        loop = asyncio.get_running_loop()
+        if not parts and method == "GET":
+            with reg.lock:
+                data = [{"id": n, "path": reg.models[n], "loaded": n in reg.loaded,
+                         "inflight": reg.loaded[n]["inflight"] if n in reg.loaded else 0} for n in reg.names()]
+            return await self._json(send, 200, {"models": data, "max_loaded": reg.max_loaded, "loads": reg.loads, "evictions": reg.evictions})
+        if not parts:
+            return await self._json(send, 405, {"error": {"message": "use GET on /v1/admin/models"}})
+        name = parts[0]
+        if name not in reg.models:
+            return await self._json(send, 404, {"error": {"message": f"model {name!r} is not served here; available: {', '.join(reg.models)}"}})
+        action = parts[1] if len(parts) > 1 else None
+        try:
+            if method == "POST" and action in ("load", "warmup"):
+                entry = await loop.run_in_executor(None, reg.acquire, name)
+                try:
+                    if action == "warmup":           # one short generation so kernels, graphs and caches are primed
+                        from ..engine.api import GenerateOptions
+
+                        await loop.run_in_executor(None, lambda: entry["engine"].llm.generate([[1, 2, 3]], max_new_tokens=2))
+                finally:
+                    reg.release(entry)
+                return await self._json(send, 200, {"id": name, "loaded": True, "action": action})
+            if method == "DELETE" and action is None:
+                with reg.lock:
+                    entry = reg.loaded.get(name)
+                    if entry is None:
+                        return await self._json(send, 200, {"id": name, "loaded": False})
+                    if entry["inflight"]:
+                        return await self._json(send, 409, {"error": {"message": f"model {name!r} has {entry['inflight']} request(s) in flight; retry when idle"}})
+                    reg._evict(name)
+                return await self._json(send, 200, {"id": name, "loaded": False})
+        except RuntimeError as exc:
+            return await self._json(send, 503, {"error": {"message": str(exc), "type": "overloaded"}})
+        return await self._json(send, 405, {"error": {"message": "use POST .../load, POST .../warmup or DELETE /v1/admin/models/{id}"}})
 
     async def __call__(self, scope, receive, send):
         if scope["type"] == "lifespan":
@@ -124,6 +165,12 @@ class RegistryApp:
         path = scope["path"]
         if path == "/health":
             return await self._json(send, 200, {"status": "ok", "loaded": list(self.registry.loaded)})
+        if path.startswith("/v1/admin/"):
+            if not self.admin:
+                return await self._json(send, 404, {"error": {"message": "admin endpoints are disabled; start the server with --enable-admin-endpoints"}})
+            if path.startswith("/v1/admin/models"):
+                return await self._admin(scope, send)
+            return await self._json(send, 404, {"error": {"message": f"no admin route {path}"}})
         if path == "/v1/models" and scope["method"] == "GET":
             return await self._json(send, 200, {"object": "list", "data": [
                 {"id": n, "object": "model", "owned_by": "onnx-genai-b200", "loaded": n in self.registry.loaded} for n in self.registry.names()]})

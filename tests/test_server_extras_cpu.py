@@ -75,3 +75,24 @@ def test_registry_loads_on_demand_and_evicts_least_recently_used(dirs):
         missing = client.post("/v1/completions", json={"model": "gamma", "prompt": "x"})
         assert missing.status_code == 404 and "available: alpha, beta" in missing.text
     assert not reg.loaded                                                                   # shutdown released everything
+
+
+def test_admin_endpoints_and_media_routes(dirs):
+    reg = ModelRegistry({"alpha": dirs[0], "beta": dirs[1]}, max_loaded=2, enable_debug_endpoints=True,
+                        loader=lambda path: Engine.from_dir(path, device="cpu", max_seqs=2, max_seq_len=64))
+    with TestClient(RegistryApp(reg)) as client:
+        assert client.get("/v1/admin/models").status_code == 404                       # disabled unless asked for
+    with TestClient(RegistryApp(reg, enable_admin_endpoints=True)) as client:
+        assert [m["loaded"] for m in client.get("/v1/admin/models").json()["models"]] == [False, False]
+        assert client.post("/v1/admin/models/alpha/load").json() == {"id": "alpha", "loaded": True, "action": "load"}
+        assert client.post("/v1/admin/models/beta/warmup").json()["loaded"] is True
+        listing = client.get("/v1/admin/models").json()
+        assert [m["loaded"] for m in listing["models"]] == [True, True] and listing["loads"] == 2
+        assert client.delete("/v1/admin/models/alpha").json() == {"id": "alpha", "loaded": False}
+        assert list(reg.loaded) == ["beta"]
+        assert client.post("/v1/admin/models/gamma/load").status_code == 404
+        # media routes answer with the reason; the stage summary endpoint exists beside the Perfetto export
+        r = client.post("/v1/audio/speech", json={"model": "beta", "input": "hi"})
+        assert r.status_code == 501 and "decoder-only text models" in r.text
+        assert client.post("/v1/images/generations", json={"model": "beta", "prompt": "x"}).status_code == 501
+        assert "stages" in client.get("/v1/debug/trace?model=beta").json()
