@@ -642,6 +642,50 @@ bool Core::append_tokens(int64_t seq_id, const int32_t* tokens, int n) {
   return true;
 }
 
+int Core::seq_pages(int64_t seq_id, int32_t* out, int cap) const {
+  const Sequence* s = find(seq_id);
+  if (!s) return -1;
+  const int used = std::min(static_cast<int>(s->pages.size()), (s->num_computed + kPageTokens - 1) / kPageTokens);
+  const int n = std::min(cap, used);
+  for (int i = 0; i < n; ++i) out[i] = s->pages[i];
+  return n;
+}
+
+int Core::prefix_adopt(const int32_t* tokens, int n_tokens, int32_t* out_pages, int cap) {
+  if (!cfg_.enable_prefix_cache) return 0;
+  const int full = std::min(cap, n_tokens / kPageTokens);
+  uint64_t h = 0;
+  int served = 0;
+  for (int i = 0; i < full; ++i) {
+    h = BlockPool::chain_hash(h, tokens + i * kPageTokens, kPageTokens);
+    if (pool_.contains(h)) {
+      out_pages[i] = -1;
+    } else {
+      const int page = pool_.allocate();
+      if (page < 0) break;
+      pool_.publish(page, h);
+      pool_.release(page);          // cached and unreferenced: the next admission with this prefix retains it
+      out_pages[i] = page;
+    }
+    ++served;
+  }
+  return served;
+}
+
+int Core::prefix_peek(const int32_t* tokens, int n_tokens, int32_t* out_pages, int cap) const {
+  if (!cfg_.enable_prefix_cache) return 0;
+  const int full = std::min(cap, n_tokens / kPageTokens);
+  uint64_t h = 0;
+  int n = 0;
+  for (; n < full; ++n) {
+    h = BlockPool::chain_hash(h, tokens + n * kPageTokens, kPageTokens);
+    const int page = pool_.peek(h);
+    if (page < 0) break;
+    out_pages[n] = page;
+  }
+  return n;
+}
+
 int Core::seq_len(int64_t seq_id) const {
   const Sequence* s = find(seq_id);
   return s ? static_cast<int>(s->tokens.size()) : -1;
@@ -727,6 +771,13 @@ int ogb_core_set_draft(void* h, int64_t id, const int32_t* tokens, int k) {
 }
 int ogb_core_append_tokens(void* h, int64_t id, const int32_t* tokens, int n) {
   return static_cast<Core*>(h)->append_tokens(id, tokens, n) ? 1 : 0;
+}
+int ogb_core_seq_pages(void* h, int64_t id, int32_t* out, int cap) { return static_cast<Core*>(h)->seq_pages(id, out, cap); }
+int ogb_core_prefix_adopt(void* h, const int32_t* tokens, int n, int32_t* out_pages, int cap) {
+  return static_cast<Core*>(h)->prefix_adopt(tokens, n, out_pages, cap);
+}
+int ogb_core_prefix_peek(void* h, const int32_t* tokens, int n, int32_t* out_pages, int cap) {
+  return static_cast<Core*>(h)->prefix_peek(tokens, n, out_pages, cap);
 }
 int ogb_core_seq_len(void* h, int64_t id) { return static_cast<Core*>(h)->seq_len(id); }
 int ogb_core_seq_tokens(void* h, int64_t id, int32_t* out, int cap) { return static_cast<Core*>(h)->seq_tokens(id, out, cap); }

@@ -75,6 +75,8 @@ class BlockPool {
   // prefix cache
   static uint64_t chain_hash(uint64_t parent, const int32_t* tokens, int n);
   int lookup(uint64_t hash);         // page id (retained) or -1
+  bool contains(uint64_t hash) const { return by_hash_.count(hash) != 0; }
+  int peek(uint64_t hash) const { auto it = by_hash_.find(hash); return it == by_hash_.end() ? -1 : it->second; }
   void publish(int page, uint64_t hash);
   int64_t hits() const { return hits_; }
   int64_t lookups() const { return lookups_; }
@@ -161,6 +163,16 @@ class Core {
   // their K/V as a prefill chunk and sample after the last one).  With rewind this lets a caller re-align a
   // sequence to a corrected continuation without re-submitting the prefix.
   bool append_tokens(int64_t seq_id, const int32_t* tokens, int n);
+  // KV offload connector support.  seq_pages: the device pages of a live sequence that hold computed tokens.
+  // prefix_adopt: for every full page of `tokens` that the prefix cache does not serve yet, allocate a page and
+  // register it under the page's chained hash as a cached, unreferenced page; the caller then fills those pages
+  // with K/V fetched from outside the device.  out_pages[i] = adopted page id, or -1 where a page already
+  // existed; returns the number of leading pages that are now served (stops when the pool is exhausted).
+  int seq_pages(int64_t seq_id, int32_t* out, int cap) const;
+  int prefix_adopt(const int32_t* tokens, int n_tokens, int32_t* out_pages, int cap);
+  // prefix_peek: the pages that currently serve the leading full pages of `tokens` (no reference is taken; valid
+  // until the next call that allocates).  Returns how many leading pages are cached.
+  int prefix_peek(const int32_t* tokens, int n_tokens, int32_t* out_pages, int cap) const;
   int64_t spec_proposed() const { return spec_proposed_; }
   int64_t spec_accepted() const { return spec_accepted_; }
   int64_t spec_steps() const { return spec_steps_; }

@@ -191,6 +191,8 @@ class Engine:
         greedy = opt.greedy or opt.temperature == 0
         temperature = 0.0 if greedy else (opt.temperature if opt.temperature is not None else defaults.get("temperature", 1.0))
         stop_ids = tuple(opt.stop_token_ids) + (() if opt.ignore_eos else self.eos_token_ids)
+        if getattr(self, "kv_offload", None) is not None:
+            self.kv_offload.restore(ids)
         sid = self.llm.add_request(np.asarray(ids, dtype=np.int32), opt.max_new_tokens, temperature=temperature,
                                    top_k=opt.top_k, top_p=opt.top_p, min_p=opt.min_p, seed=opt.seed, priority=opt.priority,
                                    tenant=opt.tenant, ignore_eos=opt.ignore_eos, stop_ids=stop_ids)
@@ -251,7 +253,21 @@ class Engine:
         c = state.get("constraint")
         return c is not None and c.constraint.terminal(c.token_texts)
 
-    def _finish(self, sid):
+    def attach_kv_connector(self, connector) -> None:
+        """Offload the K/V of finished requests to ``connector`` and restore it on later prefix hits
+        (see :mod:`onnx_genai_b200.engine.kv_connector`).  Needs the device prefix cache."""
+        from .kv_connector import KvOffload
+
+        if not self.llm.cfg.enable_prefix_cache:
+            raise ValueError("a KV connector extends the device prefix cache; build the engine with enable_prefix_cache=True")
+        self.kv_offload = KvOffload(self.llm, connector)
+
+    def _finish(self, sid, tokens=None):
+        if tokens is not None and getattr(self, "kv_offload", None) is not None:
+            try:
+                self.kv_offload.save(tokens)
+            except Exception:          # offload is an optimisation: a full disk must not fail the request
+                pass
         self.llm.host_samplers.pop(sid & 0x7FFFFFFF, None)
         prop = self.llm.proposers.pop(sid, None)
         if prop is not None and hasattr(prop, "close"):
@@ -291,7 +307,7 @@ class Engine:
                         break
         finally:
             self._last_state = state
-            self._finish(sid)
+            self._finish(sid, state["ids"])
 
     def generate(self, prompt, options: GenerateOptions | None = None, sampler=None, processors=(), on_token=None) -> GenerateResult:
         opt = options or GenerateOptions()
@@ -345,7 +361,7 @@ class Engine:
                     pending -= 1
         results = []
         for e in entries:
-            self._finish(e["sid"])
+            self._finish(e["sid"], e["state"]["ids"])
             text = self.detokenize(e["out"]) if self.tokenizer is not None else ""
             results.append(GenerateResult(text, e["out"], e["fin"], len(e["ids"]), len(e["out"]), e["ttft"],
                                           time.perf_counter() - t0, list(e["state"]["logprobs"])))

@@ -68,6 +68,12 @@ def load_runtime():
     lib.ogb_core_set_draft.restype = c_int
     lib.ogb_core_append_tokens.argtypes = [P, c_int64, I32P, c_int]
     lib.ogb_core_append_tokens.restype = c_int
+    lib.ogb_core_seq_pages.argtypes = [P, c_int64, I32P, c_int]
+    lib.ogb_core_seq_pages.restype = c_int
+    lib.ogb_core_prefix_adopt.argtypes = [P, I32P, c_int, I32P, c_int]
+    lib.ogb_core_prefix_adopt.restype = c_int
+    lib.ogb_core_prefix_peek.argtypes = [P, I32P, c_int, I32P, c_int]
+    lib.ogb_core_prefix_peek.restype = c_int
     lib.ogb_core_seq_len.argtypes = [P, c_int64]
     lib.ogb_core_seq_len.restype = c_int
     lib.ogb_core_seq_tokens.argtypes = [P, c_int64, I32P, c_int]
@@ -167,6 +173,29 @@ class Core:
         """Extend a live sequence with caller-chosen tokens (computed as a prefill chunk by the next steps)."""
         arr = np.ascontiguousarray(tokens, dtype=np.int32)
         return bool(self.lib.ogb_core_append_tokens(self.h, sid, arr.ctypes.data_as(POINTER(c_int32)), len(arr)))
+
+    def seq_pages(self, sid):
+        """Device pages of a live sequence that hold computed tokens (in order)."""
+        out = np.zeros(self.cfg.max_pages_per_seq, dtype=np.int32)
+        n = int(self.lib.ogb_core_seq_pages(self.h, sid, out.ctypes.data_as(POINTER(c_int32)), len(out)))
+        return out[:max(n, 0)].copy()
+
+    def prefix_adopt(self, tokens):
+        """Register cached pages for every full page of ``tokens`` the prefix cache does not serve yet.  Returns an
+        int32 array with one entry per served page: the adopted page id to fill, or -1 where a page existed."""
+        arr = np.ascontiguousarray(tokens, dtype=np.int32)
+        out = np.full(len(arr) // 16 + 1, -1, dtype=np.int32)
+        n = int(self.lib.ogb_core_prefix_adopt(self.h, arr.ctypes.data_as(POINTER(c_int32)), len(arr),
+                                               out.ctypes.data_as(POINTER(c_int32)), len(out)))
+        return out[:max(n, 0)].copy()
+
+    def prefix_peek(self, tokens):
+        """Pages that currently serve the leading full pages of ``tokens`` in the prefix cache (no reference taken)."""
+        arr = np.ascontiguousarray(tokens, dtype=np.int32)
+        out = np.full(len(arr) // 16 + 1, -1, dtype=np.int32)
+        n = int(self.lib.ogb_core_prefix_peek(self.h, arr.ctypes.data_as(POINTER(c_int32)), len(arr),
+                                              out.ctypes.data_as(POINTER(c_int32)), len(out)))
+        return out[:max(n, 0)].copy()
 
     def seq_len(self, sid):
         return int(self.lib.ogb_core_seq_len(self.h, sid))

@@ -151,7 +151,7 @@ class EngineDriver:
                 if fin is not None:
                     lp = list(a["state"]["logprobs"])
                     a["loop"].call_soon_threadsafe(a["q"].put_nowait, ("done", fin, len(a["out"]), lp))
-                    eng._finish(sid)
+                    eng._finish(sid, a["state"]["ids"])
                     del self.active[sid]
 
 

@@ -1,0 +1,66 @@
+"""KV offload connector: chunks leave the device when a request finishes and come back on a later prefix hit."""
+import numpy as np
+import pytest
+import torch
+
+from onnx_genai_b200.engine.api import Engine, GenerateOptions
+from onnx_genai_b200.engine.kv_connector import LocalTieredConnector, chunk_keys
+from onnx_genai_b200.engine.llm_engine import EngineConfig, LLMEngine
+from onnx_genai_b200.models.config import DecoderConfig
+from onnx_genai_b200.models.decoder import random_weights
+
+CFG = DecoderConfig(name="kvc", num_layers=2, hidden=64, num_heads=4, num_kv_heads=2, head_dim=16, intermediate=96,
+                    vocab=211, rope_theta=1e4, tie_embeddings=True, qkv_bias=True, weight_format="bf16", max_position=1024)
+
+
+def _engine(weights, kv_dtype="bf16", num_pages=48):
+    llm = LLMEngine(EngineConfig(model=CFG, num_pages=num_pages, max_seqs=4, max_tokens_per_step=256, max_seq_len=768,
+                                 enable_prefix_cache=True, kv_dtype=kv_dtype), weights=weights, device="cpu")
+    return Engine(llm)
+
+
+@pytest.mark.parametrize("kv_dtype", ["bf16", "fp8"])
+def test_chunks_are_offloaded_and_restored_after_the_device_cache_forgot_them(tmp_path, kv_dtype):
+    weights = random_weights(CFG, "cpu", seed=11, std=0.3, dtype=torch.float32)
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, CFG.vocab, size=600).tolist()                      # two full 256-token chunks + a tail
+    opt = GenerateOptions(max_new_tokens=6, ignore_eos=True)
+    eng = _engine(weights, kv_dtype)
+    conn = LocalTieredConnector(str(tmp_path / "kv"), max_host_bytes=1)         # everything but one chunk spills to disk
+    eng.attach_kv_connector(conn)
+    first = eng.generate(prompt, opt)
+    assert eng.kv_offload.chunks_stored == 2 and conn.stats["spilled"] >= 1
+    for _ in range(3):                                                          # other traffic evicts the cached pages (48-page pool)
+        eng.generate(rng.integers(0, CFG.vocab, size=500).tolist(), opt)
+    assert len(eng.llm.core.prefix_peek(prompt)) < 32                           # the device no longer serves both chunks
+    hits0 = eng.llm.core.prefix_hits
+    again = eng.generate(prompt, opt)
+    assert eng.kv_offload.tokens_restored >= 256 and eng.llm.core.prefix_hits > hits0
+    assert again.token_ids == first.token_ids                                   # restored K/V is the K/V that was computed
+    # a second engine process (same weights) picks the chunks up from the directory
+    conn.flush()
+    other = _engine(weights, kv_dtype)
+    other.attach_kv_connector(LocalTieredConnector(str(tmp_path / "kv")))
+    fresh = other.generate(prompt, opt)
+    assert other.kv_offload.tokens_restored == 512 and other.kv_offload.connector.stats["disk_hits"] == 2
+    assert fresh.token_ids == first.token_ids
+
+
+def test_connector_tiers_keys_and_limits(tmp_path):
+    keys = chunk_keys(list(range(600)), "m")
+    assert len(keys) == 2 and keys != chunk_keys(list(range(600)), "other-model")
+    assert chunk_keys([9] + list(range(1, 600)), "m")[1] != keys[1]             # a key covers the whole prefix
+    c = LocalTieredConnector(str(tmp_path / "d"), max_host_bytes=250, max_disk_bytes=250)
+    for i in range(5):
+        c.store(f"k{i}", bytes([i]) * 100)
+    assert c.host_bytes <= 250 and c.disk_bytes <= 250 and c.stats["deleted"] >= 1
+    assert c.fetch("k4") == bytes([4]) * 100 and c.stats["host_hits"] == 1
+    assert c.fetch("k0") is None                                                # oldest chunk fell off the disk tier
+    survivors = [k for k in ("k1", "k2") if c.contains(k)]
+    assert survivors and c.fetch(survivors[-1]) is not None and c.stats["disk_hits"] == 1
+    c.evict("k4")
+    assert not c.contains("k4")
+    with pytest.raises(ValueError, match="prefix cache"):
+        llm = LLMEngine(EngineConfig(model=CFG, num_pages=16, max_seqs=2, max_tokens_per_step=64, max_seq_len=128,
+                                     enable_prefix_cache=False), weights=random_weights(CFG, "cpu", seed=1, dtype=torch.float32), device="cpu")
+        Engine(llm).attach_kv_connector(c)
