@@ -41,6 +41,9 @@ def _add_engine(p):
     p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3fn"])
     p.add_argument("--max-batch", type=int, default=32)
     p.add_argument("--vram-limit", default="0.85", help="fraction of device memory the KV pool may take")
+    p.add_argument("--kv-offload-dir", default="", help="keep the K/V of finished prompts in host memory and this directory; restored on prefix hits")
+    p.add_argument("--kv-offload-host-gib", type=float, default=4.0)
+    p.add_argument("--kv-offload-disk-gib", type=float, default=64.0)
 
 
 def _options(args):
@@ -74,10 +77,16 @@ def _load(args):
         util = float(args.vram_limit)
     except ValueError:
         util = 0.85
-    return Engine.from_dir(args.model, device=dev, max_seqs=args.max_batch, kv_dtype="fp8" if args.kv_cache_dtype.startswith("fp8") else "bf16",
-                           gpu_memory_utilization=util if 0 < util <= 1 else 0.85,
-                           max_draft_tokens=4 if getattr(args, "speculative", False) else 0,
-                           max_seq_len=args.max_context or None)
+    eng = Engine.from_dir(args.model, device=dev, max_seqs=args.max_batch, kv_dtype="fp8" if args.kv_cache_dtype.startswith("fp8") else "bf16",
+                          gpu_memory_utilization=util if 0 < util <= 1 else 0.85,
+                          max_draft_tokens=4 if getattr(args, "speculative", False) else 0,
+                          max_seq_len=args.max_context or None)
+    if getattr(args, "kv_offload_dir", ""):
+        from .engine.kv_connector import LocalTieredConnector
+
+        eng.attach_kv_connector(LocalTieredConnector(args.kv_offload_dir, max_host_bytes=int(args.kv_offload_host_gib * (1 << 30)),
+                                                     max_disk_bytes=int(args.kv_offload_disk_gib * (1 << 30))))
+    return eng
 
 
 def _prompt_text(engine, text, raw, system=None):
