@@ -38,7 +38,7 @@ BASELINE_CONTEXT = {"qwen2.5-7b int4 batch-1 decode tok/s on 1xH200 (reference n
 def reference_arm(args):
     print(json.dumps({
         "impl": "reference",
-        "unavailable": "reference is a Rust workspace (cargo/rustc/maturin absent offline; `pip install /root/reference` "
+        "unavailable": "reference is a Rust workspace (cargo/rustc/maturin absent offline; `pip install` of the reference tree "
                        "reports 'neither setup.py nor pyproject.toml', its Python crate needs maturin) and it has no "
                        "multi-GPU or NCCL path at all",
     }))

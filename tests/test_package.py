@@ -88,7 +88,8 @@ def test_metadata_closed_schema_and_capabilities():
 
 def test_reads_reference_fixture_metadata():
     for name in ("tiny-llm", "tiny-llm-scatter"):
-        p = f"/root/reference/tests/fixtures/{name}/inference_metadata.yaml"
+        p = os.path.join(os.environ.get("OGB_REFERENCE_DIR", os.path.join(os.path.expanduser("~"), "reference")), "tests", "fixtures", name,
+                         "inference_metadata.yaml")
         if os.path.exists(p):
             m = md.load(p)
             assert m.max_sequence_length == 16 and m.io is not None

@@ -134,7 +134,8 @@ def test_malformed_steps_are_parse_errors():
         wfm.decoder_abi(wfm.parse(doc))
 
 
-FIXTURES = "/root/reference/tests/fixtures/onnx_genai_workflows"
+FIXTURES = os.path.join(os.environ.get("OGB_REFERENCE_DIR", os.path.join(os.path.expanduser("~"), "reference")),
+                        "tests", "fixtures", "onnx_genai_workflows")
 
 
 @pytest.mark.skipif(not os.path.isdir(FIXTURES), reason="reference fixtures are not on this machine")
