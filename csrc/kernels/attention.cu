@@ -26,12 +26,18 @@
 namespace ogb {
 
 // ------------------------------------------------------------------------------------------
-// prefill: 64 query rows x one head per CTA
+// prefill: ROWS query rows x one head per CTA.  The scheduler emits 64-row tiles; ROWS = 64 gives one CTA per
+// tile, ROWS = 32 / 16 give two / four CTAs per tile with two / one compute warps each.  A warp's work is
+// the same in every variant (16 query rows against each 64-key block), so when tiles x heads cannot fill the
+// machine -- few heads per rank under tensor parallelism, or one short prompt -- the narrower variants cut
+// the kernel's duration by spreading the same warps over more SMs.
 // ------------------------------------------------------------------------------------------
-template <int D>
-__global__ void __launch_bounds__(kAttnThreads, 2) paged_prefill_kernel(const __grid_constant__ CUtensorMap kv_map,
-                                                                      const AttnParams p) {
+template <int D, int ROWS>
+__global__ void __launch_bounds__((ROWS / 16 + 1) * 32, 2) paged_prefill_kernel(const __grid_constant__ CUtensorMap kv_map,
+                                                                              const AttnParams p) {
   using Cfg = AttnCfg<D, 2, 64>;
+  constexpr int kWarps = ROWS / 16;          // compute warps; warp kWarps is the TMA producer
+  constexpr int kSub = 64 / ROWS;            // CTAs per 64-row tile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stages = smem;
@@ -39,16 +45,16 @@ __global__ void __launch_bounds__(kAttnThreads, 2) paged_prefill_kernel(const __
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(sq + Cfg::kQBytes);
   uint64_t* empty_bar = full_bar + Cfg::kStages;
 
-  const int tile = blockIdx.x;
+  const int tile = blockIdx.x / kSub;
   if (tile >= p.num_tiles) return;
   const int head = blockIdx.y;
   const int kvh = head / p.group;
   const int seq = p.tile_seq[tile];
-  const int q0 = p.tile_q0[tile];
+  const int q0 = p.tile_q0[tile] + (blockIdx.x % kSub) * ROWS;
   const int q_begin = p.cu_q[seq];
   const int q_len = p.cu_q[seq + 1] - q_begin;
   const int ctx = p.ctx_len[seq];
-  const int rows = min(64, q_len - q0);
+  const int rows = min(ROWS, q_len - q0);
   const int pos0 = ctx - q_len + q0;
   if (rows <= 0 || ctx <= 0) return;
   const int kv_end = min(ctx, pos0 + rows);
@@ -58,13 +64,13 @@ __global__ void __launch_bounds__(kAttnThreads, 2) paged_prefill_kernel(const __
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int i = 0; i < Cfg::kStages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 4); }
+    for (int i = 0; i < Cfg::kStages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], kWarps); }
     mbar_fence_init();
     tma_prefetch_desc(&kv_map);
   }
   __syncthreads();
 
-  if (warp == 4) {
+  if (warp == kWarps) {
     if (lane == 0) {
       if (!attn_produce<Cfg>(&kv_map, p, stages, full_bar, empty_bar, seq, kvh, ctx, b_begin, b_end))
         atomicOr(p.status, kStatusWaitTimeout);
@@ -75,14 +81,14 @@ __global__ void __launch_bounds__(kAttnThreads, 2) paged_prefill_kernel(const __
   // ---- stage Q (swizzled) and pull the A fragments into registers ----
   {
     const __nv_bfloat16* qsrc = p.q + static_cast<size_t>(q_begin + q0) * p.q_stride + head * D;
-    for (int idx = threadIdx.x; idx < 64 * (D / 8); idx += 128) {
+    for (int idx = threadIdx.x; idx < ROWS * (D / 8); idx += kWarps * 32) {
       const int row = idx / (D / 8), ch = idx % (D / 8);
       uint4 v = make_uint4(0, 0, 0, 0);
       if (row < rows) v = *reinterpret_cast<const uint4*>(qsrc + static_cast<size_t>(row) * p.q_stride + ch * 8);
       *reinterpret_cast<uint4*>(sq + q_tile_off<64>(row, ch * 8)) = v;
     }
   }
-  compute_bar_sync();
+  compute_bar_sync_n<kWarps * 32>();
   uint32_t qf[D / 16][4];
   {
     const uint32_t sq_u = smem_u32(sq);
@@ -457,18 +463,28 @@ static int get_pool_tmap(const void* pool, int64_t num_pages, int hkv, int d, CU
   return 0;
 }
 
-template <int D>
-static int launch_prefill(const CUtensorMap& map, const AttnParams& p, cudaStream_t stream) {
+template <int D, int ROWS>
+static int launch_prefill_rows(const CUtensorMap& map, const AttnParams& p, cudaStream_t stream) {
   using Cfg = AttnCfg<D, 2, 64>;
   static bool attr_set = false;
   if (!attr_set) {
-    OGB_CUDA_CHECK(cudaFuncSetAttribute(paged_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    OGB_CUDA_CHECK(cudaFuncSetAttribute(paged_prefill_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    OGB_CUDA_CHECK(cudaFuncSetAttribute(paged_prefill_kernel<D, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    OGB_CUDA_CHECK(cudaFuncSetAttribute(paged_prefill_kernel<D, ROWS>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     attr_set = true;
   }
-  dim3 grid(p.num_tiles, p.hq);
-  paged_prefill_kernel<D><<<grid, kAttnThreads, Cfg::kSmemBytes, stream>>>(map, p);
+  dim3 grid(p.num_tiles * (64 / ROWS), p.hq);
+  paged_prefill_kernel<D, ROWS><<<grid, (ROWS / 16 + 1) * 32, Cfg::kSmemBytes, stream>>>(map, p);
   return static_cast<int>(cudaGetLastError());
+}
+
+template <int D>
+static int launch_prefill(const CUtensorMap& map, const AttnParams& p, cudaStream_t stream) {
+  // two CTAs fit per SM: below ~3/4 of that many 64-row CTAs, narrower CTAs finish sooner (see the kernel comment)
+  const long ctas64 = static_cast<long>(p.num_tiles) * p.hq;
+  const long slots = 2L * ogb_num_sms();
+  if (4 * ctas64 >= 3 * slots) return launch_prefill_rows<D, 64>(map, p, stream);
+  if (8 * ctas64 >= 3 * slots) return launch_prefill_rows<D, 32>(map, p, stream);
+  return launch_prefill_rows<D, 16>(map, p, stream);
 }
 template <int D>
 static int launch_decode(const CUtensorMap& map, const AttnParams& p, cudaStream_t stream) {

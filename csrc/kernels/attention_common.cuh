@@ -42,6 +42,8 @@ OGB_DEVICE void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 OGB_DEVICE void compute_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+template <int THREADS>
+OGB_DEVICE void compute_bar_sync_n() { asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory"); }
 
 // byte offset of (token t, dim d) inside a 64-token K or V tile made of swizzled 2 KB boxes
 template <int D>

@@ -116,8 +116,10 @@ def bench_attention(timer, pk):
                          "frac_of_%s_hbm" % pk["source"]: round(byts / med / 1e6 / pk["hbm_gbs"], 3)})
             print(json.dumps(rows[-1]), flush=True)
         del pool
-    for q_len, past in [(1024, 0), (2048, 0), (512, 1536)]:
-        nseq = 4
+    # (q_len, past, sequences, query heads, kv heads): the last rows are one rank's share at TP=4 / TP=8, where tiles x heads
+    # no longer fill the machine and the kernel switches to 32- / 16-row CTAs
+    for q_len, past, nseq, hq, hkv in [(1024, 0, 4, 28, 4), (2048, 0, 4, 28, 4), (512, 1536, 4, 28, 4), (1024, 0, 1, 7, 1),
+                                       (1024, 0, 1, 4, 1), (256, 0, 4, 4, 1)]:
         ctx = q_len + past
         pages_per = (ctx + 15) // 16
         total = nseq * pages_per
@@ -133,7 +135,7 @@ def bench_attention(timer, pk):
         tqd = torch.tensor(tq, dtype=torch.int32, device="cuda")
         med, _ = timer.time(lambda: ops.paged_prefill(q, out, pool, table, ctx_t, cu, tsd, tqd, len(ts), hq, hkv, d))
         flops = 4.0 * nseq * hq * d * (q_len * past + q_len * (q_len + 1) / 2)
-        rows.append({"kernel": "paged_prefill", "seqs": nseq, "q_len": q_len, "past": past, "ms": round(med, 4),
+        rows.append({"kernel": "paged_prefill", "seqs": nseq, "q_len": q_len, "past": past, "hq": hq, "hkv": hkv, "ms": round(med, 4),
                      "tflops": round(flops / med / 1e9, 1)})
         print(json.dumps(rows[-1]), flush=True)
     ops.check_status()

@@ -125,7 +125,7 @@ def test_paged_decode(hq, hkv, d):
         assert _rel_err(out, want) < 2e-2, splits
 
 
-@pytest.mark.parametrize("hq,hkv,d", [(28, 4, 128), (14, 2, 64)])
+@pytest.mark.parametrize("hq,hkv,d", [(28, 4, 128), (14, 2, 64), (4, 2, 128), (4, 1, 64)])   # 64-, 32- and 16-row CTAs
 def test_paged_prefill(hq, hkv, d):
     torch.manual_seed(5)
     q_lens = [1, 5, 64, 65, 200, 130]
