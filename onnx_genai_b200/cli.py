@@ -40,7 +40,7 @@ def _add_engine(p):
     p.add_argument("--device", default="auto", help="auto | cpu | cuda[:N]")
     p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3fn"])
     p.add_argument("--max-batch", type=int, default=32)
-    p.add_argument("--vram-limit", default="0.85", help="fraction of device memory the KV pool may take")
+    p.add_argument("--vram-limit", default="0.85", help="0.85 (fraction of the device the engine may fill), auto, or a size such as 8GiB for weights + activations + KV")
     p.add_argument("--kv-offload-dir", default="", help="keep the K/V of finished prompts in host memory and this directory; restored on prefix hits")
     p.add_argument("--kv-offload-host-gib", type=float, default=4.0)
     p.add_argument("--kv-offload-disk-gib", type=float, default=64.0)
@@ -73,12 +73,15 @@ def _load(args):
     dev = args.device
     if dev == "auto":
         dev = "cuda" if torch.cuda.is_available() else "cpu"
+    # --vram-limit: a fraction keeps its old meaning (share of the device the engine may fill); a size such as 8GiB
+    # caps weights + activations + KV pool through the memory ledger
     try:
         util = float(args.vram_limit)
+        limit = None
     except ValueError:
-        util = 0.85
+        util, limit = 0.85, (None if args.vram_limit == "auto" else args.vram_limit)
     eng = Engine.from_dir(args.model, device=dev, max_seqs=args.max_batch, kv_dtype="fp8" if args.kv_cache_dtype.startswith("fp8") else "bf16",
-                          gpu_memory_utilization=util if 0 < util <= 1 else 0.85,
+                          gpu_memory_utilization=util if 0 < util <= 1 else 0.85, vram_limit=limit,
                           max_draft_tokens=4 if getattr(args, "speculative", False) else 0,
                           max_seq_len=args.max_context or None)
     if getattr(args, "kv_offload_dir", ""):

@@ -479,4 +479,5 @@ class Engine:
         return {"kv_pages_total": total, "kv_pages_free": core.num_free_pages, "kv_usage": 1.0 - core.num_free_pages / max(1, total),
                 "waiting": core.num_waiting, "running": core.num_running, "swapped": core.num_swapped,
                 "prefix_cache_hits": core.prefix_hits, "prefix_cache_lookups": core.prefix_lookups,
-                "preemptions": core.num_preemptions, "steps": self.llm.steps, "sessions": len(self.sessions)}
+                "preemptions": core.num_preemptions, "steps": self.llm.steps, "sessions": len(self.sessions),
+                "memory": self.llm.memory.snapshot()}

@@ -52,6 +52,7 @@ class EngineConfig:
     native_executor: bool = True       # launch the layer stack from the C++ step executor when possible
     cuda_graphs: bool = False          # replay decode-only steps (forward + sampler) from captured CUDA graphs
     shard_sampling: bool = True        # TP: each rank runs lm_head + sampler for 1/tp of the rows, tokens are all-gathered
+    vram_limit: str | None = None      # "8GiB" | "0.9" | "auto": cap on device bytes (weights + activations + KV pool)
     seed: int = 0
 
 
@@ -88,6 +89,16 @@ class LLMEngine:
         hs = shard_heads(m.num_heads, m.num_kv_heads, tp, rank)
         max_rows = cfg.max_seqs * (1 + max(0, cfg.max_draft_tokens))
         self.model = DecoderModel(m, weights, self.device, cfg.max_tokens_per_step, max_rows, tp, rank, comm)
+        # memory ledger: bytes come from the tensors that exist, the KV pool gets what the limit leaves
+        from .memory import MemoryLedger, parse_limit, tensor_bytes
+
+        tier = "vram" if is_cuda else "host"
+        self.memory = MemoryLedger()
+        if is_cuda and cfg.vram_limit:
+            self.memory.limits["vram"] = parse_limit(cfg.vram_limit, torch.cuda.mem_get_info(self.device)[1])
+        w_bytes = tensor_bytes(weights)
+        self.memory.lease("weights", tier, w_bytes, m.name)
+        self.memory.lease("activations", tier, max(0, tensor_bytes(self.model) - w_bytes), "step buffers")
         num_pages = cfg.num_pages
         if num_pages <= 0:
             kv_bytes = 1 if cfg.kv_dtype == "fp8" else 2
@@ -95,6 +106,9 @@ class LLMEngine:
             if is_cuda:
                 free, total = torch.cuda.mem_get_info(self.device)
                 budget = int(free - (1.0 - cfg.gpu_memory_utilization) * total)
+                ledger_budget = self.memory.kv_budget("vram", reserve=256 << 20)   # headroom for sampler scratch and graphs
+                if ledger_budget is not None:
+                    budget = min(budget, ledger_budget)
                 if self.comm is not None:   # every replica must agree on the pool size
                     budget = self.comm.min_int(budget)
                 num_pages = max(64, budget // page_bytes)
@@ -104,6 +118,7 @@ class LLMEngine:
                 num_pages = min(4096, cfg.max_seqs * max_pages_per_seq + 16)
         self.num_pages = int(num_pages)
         self.kv = KVCache(m, self.num_pages, self.device, len(hs.kv_heads), cfg.kv_dtype)
+        self.memory.lease("kv", tier, tensor_bytes(self.kv), f"{self.num_pages} pages of 16 tokens, {cfg.kv_dtype}")
         self.core = Core(CoreConfig(num_pages=self.num_pages, num_host_pages=cfg.num_host_pages, max_seqs=cfg.max_seqs,
                                     max_tokens_per_step=cfg.max_tokens_per_step, max_pages_per_seq=max_pages_per_seq,
                                     prefill_chunk=cfg.prefill_chunk, token_multiple=cfg.token_multiple,
