@@ -98,7 +98,11 @@ class LLMEngine:
             self.memory.limits["vram"] = parse_limit(cfg.vram_limit, torch.cuda.mem_get_info(self.device)[1])
         w_bytes = tensor_bytes(weights)
         self.memory.lease("weights", tier, w_bytes, m.name)
-        self.memory.lease("activations", tier, max(0, tensor_bytes(self.model) - w_bytes), "step buffers")
+        try:
+            act_bytes = max(0, tensor_bytes(self.model) - w_bytes)
+        except Exception:            # accounting must never stop an engine from starting
+            act_bytes = 0
+        self.memory.lease("activations", tier, act_bytes, "step buffers")
         num_pages = cfg.num_pages
         if num_pages <= 0:
             kv_bytes = 1 if cfg.kv_dtype == "fp8" else 2
