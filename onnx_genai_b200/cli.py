@@ -379,7 +379,13 @@ def main(argv=None):
     ex.add_argument("--out", required=True)
     ex.add_argument("--int4", action="store_true")
     ex.add_argument("--layers", type=int, default=0)
+    ic = sub.add_parser("import-comfyui", help="convert a ComfyUI API-format graph into a workflow metadata document")
+    ic.add_argument("graph")
+    ic.add_argument("-o", "--out", default="-")
     args = ap.parse_args(argv)
+    if args.cmd == "import-comfyui":
+        from .package.comfyui import main as comfy_main
+        return comfy_main([args.graph, "-o", args.out])
     if args.cmd == "version":
         print(f"onnx-genai-b200 {__version__}")
         return 0
