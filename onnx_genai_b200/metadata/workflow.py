@@ -92,7 +92,7 @@ class StateGroup:
 @dataclass
 class Workflow:
     capabilities: list
-    inputs: dict           # value name -> {"contract": Contract, "source": str, "role": str | None, "required": bool}
+    inputs: dict           # value name -> {"contract": Contract, "source": str, "role": str | None, "required": bool, "default"}
     outputs: dict          # output name -> Contract
     components: dict       # name -> Component
     state: dict            # cell -> {"contract": Contract, "initializer": str | None, "scope": str, "recurrence": str}
@@ -192,7 +192,7 @@ def parse(doc: dict) -> Workflow:
         role = d.get("role") if isinstance(d, dict) else None
         role_name = role.get("role") if isinstance(role, dict) else (role if isinstance(role, str) else None)
         inputs[str(name)] = {"contract": _contract(d.get("contract"), f"inputs.{name}"), "source": src, "role": role_name,
-                             "required": bool(d.get("required", False))}
+                             "required": bool(d.get("required", False)), "default": d.get("default") if isinstance(d, dict) else None}
     outputs = {str(n): _contract((d or {}).get("contract"), f"outputs.{n}") for n, d in (doc.get("outputs") or {}).items()}
     components = {}
     for name, d in (doc.get("components") or {}).items():

@@ -114,6 +114,8 @@ def import_comfyui(graph: dict) -> dict:
                                    "default": steps, "role": {"kind": "runtime", "version": "1.0", "role": "max_output_tokens"}},
         "package.false": {"contract": {"dtype": "bool", "rank": 1, "shape": [1]}, "source": {"kind": "literal"}, "default": False,
                           "role": {"kind": "opaque"}},
+        "package.loop_active": {"contract": {"dtype": "bool", "rank": 1, "shape": [1]}, "source": {"kind": "literal"}, "default": True,
+                                "role": {"kind": "opaque"}},
     }
     components = {"text_encoder": onnx("text_encoder"), "denoiser": onnx("unet"), "vae_decoder": onnx("vae_decoder"),
                   "schedule": {"implementation": {"kind": "onnx", "artifact": f"policies/schedule_{scheduler}.onnx"}},
@@ -153,7 +155,7 @@ def import_comfyui(graph: dict) -> dict:
         "components": components,
         "state": {"latent_state": {"contract": latent_contract, "scope": "invocation", "initializer": "request.noise",
                                    "recurrence": {"kind": "invariant"}},
-                  "loop_active": {"contract": {"dtype": "bool", "rank": 1, "shape": [1]}, "scope": "invocation", "initializer": "package.false",
+                  "loop_active": {"contract": {"dtype": "bool", "rank": 1, "shape": [1]}, "scope": "invocation", "initializer": "package.loop_active",
                                   "recurrence": {"kind": "invariant"}}},
         "steps": [
             {"kind": "loop", "setup": setup, "steps": body, "continue_when": "loop_active", "max_iterations": "request.max_iterations",

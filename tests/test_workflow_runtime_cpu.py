@@ -1,0 +1,120 @@
+"""Workflow executor: loops with carried state, branches, emits, session state, errors."""
+import copy
+
+import numpy as np
+import pytest
+
+from onnx_genai_b200.engine.workflow_runtime import WorkflowRuntimeError, WorkflowSession, run_workflow
+from onnx_genai_b200.package.comfyui import import_comfyui
+from test_comfyui_cpu import GRAPH
+from test_workflow_cpu import DOC
+
+
+def _diffusion_components(calls):
+    sig = np.linspace(1.0, 0.0, 21)
+
+    def denoiser(p):
+        calls.append(("denoiser", int(p["step"][0])))
+        return {"noise_pred": p["sample"] * 0.5 + p["encoder_hidden_states"].mean()}
+
+    return {
+        "schedule": lambda p: {"schedule": sig},
+        "text_encoder": lambda p: {"encoder_hidden_states": p["input_ids"].astype(np.float32) / 10.0},
+        "denoiser": denoiser,
+        "guidance": lambda p: {"guided": p["unconditional"] + float(p["scale"][0]) * (p["conditional"] - p["unconditional"])},
+        "solver_step": lambda p: {"next_state": p["sample"] + (p["schedule"][int(p["step"][0]) + 1] - p["schedule"][int(p["step"][0])]) * p["derivative"]},
+        "continue_predicate": lambda p: {"continue": ~np.asarray(p["done"])},
+        "vae_decoder": lambda p: {"image": np.repeat(np.repeat(p["latent"][:, :3], 8, axis=2), 8, axis=3)},
+    }
+
+
+def test_imported_diffusion_graph_runs_and_matches_a_plain_loop():
+    doc = import_comfyui(GRAPH)
+    calls = []
+    comps = _diffusion_components(calls)
+    rng = np.random.default_rng(0)
+    noise = rng.standard_normal((2, 4, 64, 96)).astype(np.float32)
+    pos, neg = np.array([[1, 2, 3]]), np.array([[4, 5, 6]])
+    out = run_workflow(doc, comps, {"request.positive_ids": pos, "request.negative_ids": neg, "request.noise": noise})
+    sig, x = np.linspace(1.0, 0.0, 21), noise.copy()
+    cp, cn = (pos / 10.0).mean(), (neg / 10.0).mean()
+    for i in range(20):
+        d = (x * 0.5 + cn) + 8.0 * ((x * 0.5 + cp) - (x * 0.5 + cn))
+        x = x + (sig[i + 1] - sig[i]) * d
+    assert out["image"].shape == (2, 3, 512, 768)
+    np.testing.assert_allclose(out["image"][:, :, ::8, ::8], x[:, :3], rtol=1e-5, atol=1e-5)
+    assert len(calls) == 40 and calls[0] == ("denoiser", 0) and calls[-1] == ("denoiser", 19)
+    # max_iterations from the request overrides the graph's step count
+    calls.clear()
+    run_workflow(doc, comps, {"request.positive_ids": pos, "request.negative_ids": neg, "request.noise": noise,
+                              "request.max_iterations": np.array([3])})
+    assert len(calls) == 6
+
+
+def _decoder_components(vocab=8, eos=None):
+    def lm(p):
+        ids = np.asarray(p["input_ids"])
+        logits = np.zeros((ids.shape[0], ids.shape[1], vocab), np.float32)
+        logits[:, -1, (int(ids[0, -1]) + 1) % vocab] = 5.0
+        return {"logits": logits}
+
+    pick = lambda p: {"token": p["logits"][:, -1].argmax(-1)[:, None]}
+    return {"lm": lm, "pick": pick, "pick_sampled": lambda p: {"token": p["logits"][:, -1].argmin(-1)[:, None]}}
+
+
+def test_decoder_loop_greedy_branch_eos_and_stop():
+    sess = WorkflowSession(copy.deepcopy(DOC), _decoder_components())
+    out = sess.run({"request.input_ids": np.array([[1, 2]]), "request.max_new": np.array([5])})
+    assert [int(t[0, 0]) for t in out["tokens"]] == [4, 5, 6, 7, 0]
+    assert sess.stats["invocations"]["lm"] == 6 and sess.stats["invocations"]["pick"] == 6
+    out = sess.run({"request.input_ids": np.array([[1, 2]]), "request.max_new": np.array([50])}, eos_token_ids=[6])
+    assert [int(t[0, 0]) for t in out["tokens"]] == [4, 5, 6]
+    seen = []
+    out = sess.run({"request.input_ids": np.array([[1, 2]]), "request.max_new": np.array([50])},
+                   on_emit=lambda name, v, mode: (seen.append((name, mode)), len(seen) < 2)[1])
+    assert len(out["tokens"]) == 2 and seen == [("tokens", "append")] * 2
+    # the default arm (sampling off the greedy flag) takes the other picker
+    out = sess.run({"request.input_ids": np.array([[1, 2]]), "request.max_new": np.array([1]), "package.greedy": np.array([False])})
+    assert int(out["tokens"][0][0, 0]) != 4
+
+
+def test_session_cells_persist_and_checkpoint():
+    doc = {"inputs": {"request.n": {"contract": {"dtype": "int64"}, "source": {"kind": "request"}, "required": True},
+                      "package.zero": {"source": {"kind": "literal"}, "default": 0},
+                      "package.on": {"source": {"kind": "literal"}, "default": True}},
+           "outputs": {"total": {"contract": {"dtype": "int64"}}},
+           "components": {"add": {"implementation": {"kind": "onnx", "artifact": "add.onnx"}}},
+           "state": {"acc": {"scope": "session", "initializer": "package.zero"},
+                     "go": {"scope": "invocation", "initializer": "package.on"}},
+           "steps": [{"kind": "loop", "steps": [{"kind": "invoke", "component": "add", "inputs": {"a": "acc", "i": "it"},
+                                                  "outputs": {"sum": "body.sum", "more": "body.more"}}],
+                      "continue_when": "go", "max_iterations": "request.n", "iteration": {"value": "it"},
+                      "carried": [{"cell": "acc", "next": "body.sum"}, {"cell": "go", "next": "body.more"}]},
+                     {"kind": "emit", "value": "acc", "output": "total", "mode": "replace"}]}
+    sess = WorkflowSession(doc, {"add": lambda p: {"sum": np.asarray(p["a"]) + 1, "more": np.array([True])}})
+    assert int(sess.run({"request.n": np.array([3])})["total"][0]) == 3
+    snap = sess.checkpoint()
+    assert int(sess.run({"request.n": np.array([2])})["total"][0]) == 5
+    sess.restore(snap)
+    assert int(sess.run({"request.n": np.array([1])})["total"][0]) == 4
+    sess.reset()
+    assert int(sess.run({"request.n": np.array([1])})["total"][0]) == 1
+    # the body's predicate ends the loop before the limit
+    sess2 = WorkflowSession(doc, {"add": lambda p: {"sum": np.asarray(p["a"]) + 1, "more": np.array([int(p["i"][0]) < 1])}})
+    assert int(sess2.run({"request.n": np.array([10])})["total"][0]) == 2
+
+
+def test_errors_name_the_step_and_the_fix():
+    with pytest.raises(WorkflowRuntimeError, match="no implementation bound for component\\(s\\) pick_sampled"):
+        WorkflowSession(copy.deepcopy(DOC), {k: v for k, v in _decoder_components().items() if k != "pick_sampled"})
+    sess = WorkflowSession(copy.deepcopy(DOC), _decoder_components() | {"pick": lambda p: {"tok": 1}})
+    with pytest.raises(WorkflowRuntimeError, match="did not produce output port 'token'"):
+        sess.run({"request.input_ids": np.array([[1]]), "request.max_new": np.array([1])})
+    with pytest.raises(WorkflowRuntimeError, match="required input 'request.input_ids'"):
+        WorkflowSession(copy.deepcopy(DOC), _decoder_components()).run({"request.max_new": np.array([1])})
+    with pytest.raises(WorkflowRuntimeError, match="unknown input"):
+        WorkflowSession(copy.deepcopy(DOC), _decoder_components()).run({"request.inputs": 1})
+    bad = copy.deepcopy(DOC)
+    bad["steps"][0]["steps"][0]["inputs"]["input_ids"] = "tokne"
+    with pytest.raises(WorkflowRuntimeError, match="does not validate"):
+        WorkflowSession(bad, _decoder_components())
