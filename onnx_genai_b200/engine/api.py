@@ -9,6 +9,8 @@ checkpoint / restore / rewind / fork (runtime.rs:1240-1330, config.rs:472-484).
 """
 from __future__ import annotations
 
+import os
+
 import time
 from dataclasses import dataclass, field
 
@@ -161,7 +163,14 @@ class Engine:
                             kv_dtype=kv_dtype, max_draft_tokens=max_draft_tokens, **engine_kw)
         llm = LLMEngine(ecfg, weights=weights, device=device)
         draft = cls.from_dir(draft_model_dir, device=device, max_seqs=max_seqs, max_seq_len=max_seq_len) if draft_model_dir else None
-        return cls(llm, tok, d.chat_template, meta, eos, draft)
+        eng = cls(llm, tok, d.chat_template, meta, eos, draft)
+        mtp_path = os.path.join(os.path.dirname(d.model_path), "mtp_head.safetensors")
+        if max_draft_tokens > 0 and draft is None and os.path.exists(mtp_path):
+            # a package that ships an MTP head drafts with it (speculative requests only)
+            from ..speculative.mtp import MtpHead, attach_mtp
+
+            attach_mtp(eng, MtpHead.load(mtp_path, weights.embed, weights.lm_head))
+        return eng
 
     # ------------------------------------------------------------------ text helpers
     def tokenize(self, text: str) -> list:

@@ -465,6 +465,19 @@ class LLMEngine:
                     self.d2h_bytes += row_logits.nbytes
                     self.sampled_host[row] = int(fn(row_logits, float(unis[row])))
         events = self.core.commit_step(self.sampled_host.data_ptr(), r)
+        if r > 0 and any(getattr(p, "wants_hidden", False) for p in self.proposers.values()):
+            # proposers that draft from the target's hidden state get the row that produced the last committed token:
+            # a sequence's rows are consecutive, and it committed (accepted drafts + 1) tokens
+            seq_of_row = self.plan_np[self.L.logit_seq:self.L.logit_seq + r]
+            first, committed = {}, {}
+            for row in range(r):
+                first.setdefault(int(seq_of_row[row]), row)
+            for sid, _tok, _fin in events:
+                committed[sid] = committed.get(sid, 0) + 1
+            for sid, proposer in self.proposers.items():
+                key = sid & 0x7FFFFFFF                       # the plan carries sequence ids as int32
+                if getattr(proposer, "wants_hidden", False) and key in first and committed.get(sid):
+                    proposer.observe(self.model.h_last[first[key] + committed[sid] - 1].clone())
         now = time.perf_counter()
         for sid, tok, fin in events:
             st = self.stats.get(sid)

@@ -1,0 +1,128 @@
+"""Multi-token-prediction proposer: a small head drafts from the target's own hidden state.
+
+The target's last hidden state already encodes most of what the next few tokens will be.  An MTP head takes that state
+and the embedding of the token the target just chose, produces the state one position ahead, and reads a draft token
+from it through the target's *shared* output projection; feeding its own output back gives the following draft
+tokens ("hidden-threaded": the recurrent state is the hidden vector, no KV cache of its own, nothing to rewind when
+drafts are rejected).  Same seam as the reference's ``MtpProposer`` -- last hidden state + greedy next token in, a chain
+of draft tokens out, the target's embedding table and LM head shared rather than duplicated
+(crates/onnx-genai-engine/src/speculative/mod.rs:48-63, 999-1170).
+
+One head step, for hidden ``h`` and token embedding ``e`` (all RMS-normalised with learned gains)::
+
+    z = W_fuse [norm(h) ; norm(e)]
+    z = z + W_down ( silu(W_gate norm(z)) * (W_up norm(z)) )
+    draft = argmax( LM_head norm_out(z) )          h <- z, e <- embed(draft)
+
+The engine hands every proposer that sets ``wants_hidden`` the final hidden state of the row that produced the last
+committed token (after verification: the row of the last accepted draft), so the head always continues from the
+verified prefix.  Sequences that share a head are drafted together: one [B, H] pass per draft position.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import SpeculativeProposer
+
+
+def _rms(x, g, eps=1e-6):
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * g
+
+
+class MtpHead:
+    """Weights of one hidden-threaded MTP block.  ``embed`` [V, H] and ``lm_head`` [V, H] belong to the target."""
+
+    NAMES = ("fuse", "gate", "up", "down", "norm_h", "norm_e", "norm_m", "norm_out")
+
+    def __init__(self, weights: dict, embed: torch.Tensor, lm_head: torch.Tensor, eps: float = 1e-6):
+        missing = [n for n in self.NAMES if n not in weights]
+        if missing:
+            raise ValueError(f"MTP head is missing tensors {missing}; it needs {list(self.NAMES)}")
+        hid = embed.shape[1]
+        if tuple(weights["fuse"].shape) != (hid, 2 * hid):
+            raise ValueError(f"MTP head hidden size {weights['fuse'].shape[0]} (fuse {tuple(weights['fuse'].shape)}) does not match the "
+                             f"target's embedding width {hid}")
+        self.w = {n: weights[n].to(device=embed.device, dtype=embed.dtype) for n in self.NAMES}
+        self.embed, self.lm_head, self.eps = embed, lm_head, eps
+        self.hidden, self.inter = hid, int(weights["gate"].shape[0])
+
+    @classmethod
+    def random(cls, embed, lm_head, inter: int | None = None, seed: int = 0, std: float = 0.02) -> "MtpHead":
+        hid = embed.shape[1]
+        inter = inter or 2 * hid
+        g = torch.Generator().manual_seed(seed)
+        w = {"fuse": torch.randn(hid, 2 * hid, generator=g) * std, "gate": torch.randn(inter, hid, generator=g) * std,
+             "up": torch.randn(inter, hid, generator=g) * std, "down": torch.randn(hid, inter, generator=g) * std,
+             "norm_h": torch.ones(hid), "norm_e": torch.ones(hid), "norm_m": torch.ones(hid), "norm_out": torch.ones(hid)}
+        return cls(w, embed, lm_head)
+
+    def save(self, path: str) -> None:
+        from safetensors.torch import save_file
+
+        save_file({n: t.detach().float().cpu().contiguous() for n, t in self.w.items()}, path)
+
+    @classmethod
+    def load(cls, path: str, embed, lm_head) -> "MtpHead":
+        from safetensors.torch import load_file
+
+        return cls(load_file(path), embed, lm_head)
+
+    @torch.no_grad()
+    def draft(self, hidden: torch.Tensor, tokens: torch.Tensor, k: int) -> torch.Tensor:
+        """``hidden`` [B, H] (the target's final-normed states), ``tokens`` [B] (the tokens chosen from them) -> [B, k] drafts."""
+        w, out = self.w, []
+        h, tok = hidden.to(self.embed.dtype), tokens.long()
+        for _ in range(k):
+            e = self.embed.index_select(0, tok)
+            z = torch.cat([_rms(h, w["norm_h"], self.eps), _rms(e, w["norm_e"], self.eps)], dim=-1) @ w["fuse"].T
+            m = _rms(z, w["norm_m"], self.eps)
+            z = z + (torch.nn.functional.silu(m @ w["gate"].T) * (m @ w["up"].T)) @ w["down"].T
+            tok = (_rms(z, w["norm_out"], self.eps) @ self.lm_head.T).float().argmax(-1)
+            out.append(tok)
+            h = z
+        return torch.stack(out, dim=1)
+
+
+class MtpProposer(SpeculativeProposer):
+    name = "mtp"
+    wants_hidden = True
+
+    def __init__(self, head: MtpHead):
+        self.head = head
+        self.hidden = None           # [H] on the head's device, set by the engine after every committed step
+
+    @property
+    def batch_key(self):
+        return ("mtp", id(self.head))
+
+    def observe(self, hidden: torch.Tensor) -> None:
+        self.hidden = hidden
+
+    def propose(self, token_ids, k):
+        return self.propose_many([self], [token_ids], k)[0]
+
+    @staticmethod
+    def propose_many(proposers, token_lists, k):
+        empty = np.zeros(0, dtype=np.int32)
+        live = [i for i, p in enumerate(proposers) if p.hidden is not None and len(token_lists[i])]
+        out = [empty] * len(proposers)
+        if not live or k <= 0:
+            return out
+        head = proposers[live[0]].head
+        hidden = torch.stack([proposers[i].hidden for i in live])
+        last = torch.tensor([int(token_lists[i][-1]) for i in live], device=hidden.device)
+        drafts = head.draft(hidden, last, k).to("cpu", torch.int32).numpy()
+        for row, i in enumerate(live):
+            out[i] = drafts[row]
+        return out
+
+
+def attach_mtp(engine, head: MtpHead | None = None, seed: int = 0) -> MtpHead:
+    """Make ``engine`` (an :class:`onnx_genai_b200.engine.api.Engine`) draft with an MTP head on speculative requests.
+    With no head given, a randomly initialised one is made (useful for measuring the mechanism, not acceptance)."""
+    w = engine.llm.model.w
+    head = head or MtpHead.random(w.embed, w.lm_head, seed=seed)
+    engine.proposer_factory = lambda: MtpProposer(head)
+    return head
