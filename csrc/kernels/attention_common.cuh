@@ -77,7 +77,8 @@ struct AttnParams {
   float* part_o;
   float* part_ml;
   int* status;
-  const float* kv_scales;   // e4m3 pages only: [pages, kv_heads, 2] fp32 (K scale, V scale)
+  const float* kv_scales;   // one-byte pages only: [pages, kv_heads, 2] fp32 (K scale, V scale)
+  int kv_fmt;               // one-byte pages only: 0 = e4m3, 1 = int8
 };
 
 // Producer: stream blocks [b_begin, b_end) of one sequence / kv head into the ring.

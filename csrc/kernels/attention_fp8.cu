@@ -45,14 +45,33 @@ OGB_DEVICE void cvt16_e4m3_bf16(const uint4& raw, uint4& lo, uint4& hi) {
   hi = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
-// Expand one raw page side (16 tokens x 128 e4m3, 128-byte swizzled rows) into a bf16 page tile
-// ([2 halves][16 rows][128 B], same swizzle), using `nthreads` threads starting at `tid`.
-OGB_DEVICE void expand_page(const uint8_t* raw, uint8_t* work, int tid, int nthreads) {
+// 16 int8 bytes -> 16 bf16 (exact: |v| <= 127 fits bf16's 8 significant bits)
+OGB_DEVICE void cvt16_i8_bf16(const uint4& raw, uint4& lo, uint4& hi) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  uint32_t o[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t pair = (w[i] >> (16 * h)) & 0xffffu;
+      const float a = static_cast<float>(static_cast<int8_t>(pair & 0xffu));
+      const float b = static_cast<float>(static_cast<int8_t>(pair >> 8));
+      o[2 * i + h] = pack_bf16(a, b);
+    }
+  }
+  lo = make_uint4(o[0], o[1], o[2], o[3]);
+  hi = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+// Expand one raw page side (16 tokens x 128 one-byte values, 128-byte swizzled rows) into a bf16 page tile
+// ([2 halves][16 rows][128 B], same swizzle), using `nthreads` threads starting at `tid`.  fmt 0: e4m3, 1: int8.
+OGB_DEVICE void expand_page(const uint8_t* raw, uint8_t* work, int tid, int nthreads, int fmt) {
   for (int i = tid; i < kPageTokens * 8; i += nthreads) {   // 16 rows x 8 chunks of 16 bytes
     const int r = i >> 3, c = i & 7;
     const uint4 v = *reinterpret_cast<const uint4*>(raw + r * 128 + ((c ^ (r & 7)) << 4));
     uint4 lo, hi;
-    cvt16_e4m3_bf16(v, lo, hi);
+    if (fmt == 0) cvt16_e4m3_bf16(v, lo, hi);
+    else cvt16_i8_bf16(v, lo, hi);
     const int d0 = c * 16;
     *reinterpret_cast<uint4*>(work + kv_tile_off<kD>(r, d0)) = lo;
     *reinterpret_cast<uint4*>(work + kv_tile_off<kD>(r, d0 + 8)) = hi;
@@ -173,8 +192,8 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_fp8_kernel(const __
     const int tok0 = b * kKvBlock + 16 * warp;
     if (tok0 < ctx) {
       const uint8_t* raw = stages + stage * kRawStage;
-      expand_page(raw + warp * kRawPage, wk, lane, 32);
-      expand_page(raw + (4 + warp) * kRawPage, wv, lane, 32);
+      expand_page(raw + warp * kRawPage, wk, lane, 32, p.kv_fmt);
+      expand_page(raw + (4 + warp) * kRawPage, wv, lane, 32, p.kv_fmt);
       const int64_t page = page_of(p, seq, ctx, b * 4 + warp);
       const float ks = p.kv_scales[(page * p.hkv + kvh) * 2] * p.scale_log2e;
       const float vs = p.kv_scales[(page * p.hkv + kvh) * 2 + 1];
@@ -375,8 +394,8 @@ __global__ void __launch_bounds__(kAttnThreads) paged_prefill_fp8_kernel(const _
     if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], phase))) { ok = false; break; }
     const uint8_t* raw = stages + stage * kRawStage;
     // warp w expands page w of the block (K and V) into the shared bf16 tiles
-    expand_page(raw + warp * kRawPage, tile_k + warp * kWorkPage, lane, 32);
-    expand_page(raw + (4 + warp) * kRawPage, tile_v + warp * kWorkPage, lane, 32);
+    expand_page(raw + warp * kRawPage, tile_k + warp * kWorkPage, lane, 32, p.kv_fmt);
+    expand_page(raw + (4 + warp) * kRawPage, tile_v + warp * kWorkPage, lane, 32, p.kv_fmt);
     if (lane < 2) {
       const int64_t page = page_of(p, seq, ctx, b * 4 + warp);
       sc_sh[warp * 2 + lane] = p.kv_scales[(page * p.hkv + kvh) * 2 + lane];
@@ -501,11 +520,12 @@ static void fill_params(AttnParams& p, const void* q, void* out, const float* sc
   p.scale_log2e = scale * 1.4426950408889634f; p.status = status; p.kv_scales = scales; p.num_splits = 1;
 }
 
-extern "C" int ogb_paged_decode_fp8(const void* q, void* out, const void* pool, const float* scales, const int* page_table,
-                                    const int* ctx_len, int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d,
-                                    int q_stride, int o_stride, float scale, int num_splits, float* part_o, float* part_ml,
-                                    int* status, void* stream) {
+static int launch_decode_q(const void* q, void* out, const void* pool, const float* scales, int kv_fmt, const int* page_table,
+                           const int* ctx_len, int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d,
+                           int q_stride, int o_stride, float scale, int num_splits, float* part_o, float* part_ml,
+                           int* status, void* stream) {
   if (num_seqs <= 0) return 0;
+  if (kv_fmt != 0 && kv_fmt != 1) return -3;
   if (d != kD || hkv <= 0 || hq % hkv != 0 || hq / hkv > 16 || (q_stride % 8) != 0 || scales == nullptr) return -3;
   if (num_splits < 1) num_splits = 1;
   if (num_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return -4;
@@ -514,7 +534,7 @@ extern "C" int ogb_paged_decode_fp8(const void* q, void* out, const void* pool, 
   if (rc != 0) return rc;
   AttnParams p{};
   fill_params(p, q, out, scales, page_table, ctx_len, num_seqs, max_pages, num_pages, hq, hkv, q_stride, o_stride, scale, status);
-  p.num_splits = num_splits; p.part_o = part_o; p.part_ml = part_ml;
+  p.num_splits = num_splits; p.part_o = part_o; p.part_ml = part_ml; p.kv_fmt = kv_fmt;
   static bool attr_set = false;
   if (!attr_set) {
     OGB_CUDA_CHECK(cudaFuncSetAttribute(paged_decode_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem));
@@ -531,18 +551,19 @@ extern "C" int ogb_paged_decode_fp8(const void* q, void* out, const void* pool, 
   return rc;
 }
 
-extern "C" int ogb_paged_prefill_fp8(const void* q, void* out, const void* pool, const float* scales, const int* page_table,
-                                     const int* ctx_len, const int* cu_q, const int* tile_seq, const int* tile_q0, int num_tiles,
-                                     int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride,
-                                     int o_stride, float scale, int* status, void* stream) {
+static int launch_prefill_q(const void* q, void* out, const void* pool, const float* scales, int kv_fmt, const int* page_table,
+                            const int* ctx_len, const int* cu_q, const int* tile_seq, const int* tile_q0, int num_tiles,
+                            int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride,
+                            int o_stride, float scale, int* status, void* stream) {
   if (num_tiles <= 0) return 0;
+  if (kv_fmt != 0 && kv_fmt != 1) return -3;
   if (d != kD || hkv <= 0 || hq % hkv != 0 || (q_stride % 8) != 0 || (o_stride % 2) != 0 || scales == nullptr) return -3;
   CUtensorMap map;
   int rc = get_fp8_tmap(pool, num_pages, hkv, &map);
   if (rc != 0) return rc;
   AttnParams p{};
   fill_params(p, q, out, scales, page_table, ctx_len, num_seqs, max_pages, num_pages, hq, hkv, q_stride, o_stride, scale, status);
-  p.cu_q = cu_q; p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.num_tiles = num_tiles;
+  p.cu_q = cu_q; p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.num_tiles = num_tiles; p.kv_fmt = kv_fmt;
   static bool attr_set = false;
   if (!attr_set) {
     OGB_CUDA_CHECK(cudaFuncSetAttribute(paged_prefill_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPreSmem));
@@ -551,4 +572,34 @@ extern "C" int ogb_paged_prefill_fp8(const void* q, void* out, const void* pool,
   }
   paged_prefill_fp8_kernel<<<dim3(num_tiles, hq), kAttnThreads, kPreSmem, static_cast<cudaStream_t>(stream)>>>(map, p);
   return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int ogb_paged_decode_fp8(const void* q, void* out, const void* pool, const float* scales, const int* page_table,
+                                    const int* ctx_len, int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d,
+                                    int q_stride, int o_stride, float scale, int num_splits, float* part_o, float* part_ml,
+                                    int* status, void* stream) {
+  return launch_decode_q(q, out, pool, scales, 0, page_table, ctx_len, num_seqs, max_pages, num_pages, hq, hkv, d, q_stride, o_stride,
+                         scale, num_splits, part_o, part_ml, status, stream);
+}
+extern "C" int ogb_paged_prefill_fp8(const void* q, void* out, const void* pool, const float* scales, const int* page_table,
+                                     const int* ctx_len, const int* cu_q, const int* tile_seq, const int* tile_q0, int num_tiles,
+                                     int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride,
+                                     int o_stride, float scale, int* status, void* stream) {
+  return launch_prefill_q(q, out, pool, scales, 0, page_table, ctx_len, cu_q, tile_seq, tile_q0, num_tiles, num_seqs, max_pages,
+                          num_pages, hq, hkv, d, q_stride, o_stride, scale, status, stream);
+}
+// One-byte pages in either format: kv_format 0 = e4m3, 1 = int8 (symmetric, same per-(page, head, K|V) scale layout).
+extern "C" int ogb_paged_decode_q8(const void* q, void* out, const void* pool, const float* scales, int kv_format,
+                                   const int* page_table, const int* ctx_len, int num_seqs, int max_pages, int64_t num_pages,
+                                   int hq, int hkv, int d, int q_stride, int o_stride, float scale, int num_splits,
+                                   float* part_o, float* part_ml, int* status, void* stream) {
+  return launch_decode_q(q, out, pool, scales, kv_format, page_table, ctx_len, num_seqs, max_pages, num_pages, hq, hkv, d, q_stride,
+                         o_stride, scale, num_splits, part_o, part_ml, status, stream);
+}
+extern "C" int ogb_paged_prefill_q8(const void* q, void* out, const void* pool, const float* scales, int kv_format,
+                                    const int* page_table, const int* ctx_len, const int* cu_q, const int* tile_seq,
+                                    const int* tile_q0, int num_tiles, int num_seqs, int max_pages, int64_t num_pages, int hq,
+                                    int hkv, int d, int q_stride, int o_stride, float scale, int* status, void* stream) {
+  return launch_prefill_q(q, out, pool, scales, kv_format, page_table, ctx_len, cu_q, tile_seq, tile_q0, num_tiles, num_seqs,
+                          max_pages, num_pages, hq, hkv, d, q_stride, o_stride, scale, status, stream);
 }

@@ -258,7 +258,8 @@ __global__ void rope_kv_append_kernel(__nv_bfloat16* __restrict__ qkv, const int
 // scale is read.
 __global__ void kv_append_fp8_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ slots,
                                      uint8_t* __restrict__ pool, float* __restrict__ scales, int hq, int hkv, int d,
-                                     int page_size, int64_t num_slots, int* status) {
+                                     int page_size, int64_t num_slots, int fmt, int* status) {
+  const float qmax = fmt == 0 ? 448.f : 127.f;     // fmt 0: e4m3, 1: int8 (symmetric)
   const int t = blockIdx.x;
   const int64_t slot = slots[t];
   if (slot < 0) return;
@@ -287,7 +288,7 @@ __global__ void kv_append_fp8_kernel(const __nv_bfloat16* __restrict__ qkv, cons
       float amax = 0.f;
       for (int j = lane; j < d; j += 32) amax = fmaxf(amax, fabsf(__bfloat162float(first_row[col + j])));
       amax = warp_max(amax);
-      scale = fmaxf(amax * 2.f, 1e-6f) / 448.f;
+      scale = fmaxf(amax * 2.f, 1e-6f) / qmax;
       if (off == 0 && lane == 0) *sc = scale;
     } else {
       scale = *sc;
@@ -295,7 +296,7 @@ __global__ void kv_append_fp8_kernel(const __nv_bfloat16* __restrict__ qkv, cons
         float amax = 0.f;
         for (int j = lane; j < d; j += 32) amax = fmaxf(amax, fabsf(__bfloat162float(row[col + j])));
         amax = warp_max(amax);
-        scale = fmaxf(amax * 2.f, 1e-6f) / 448.f;
+        scale = fmaxf(amax * 2.f, 1e-6f) / qmax;
         if (lane == 0) *sc = scale;
       }
     }
@@ -303,8 +304,9 @@ __global__ void kv_append_fp8_kernel(const __nv_bfloat16* __restrict__ qkv, cons
     uint8_t* dst = pool + ((((page * hkv + h) * 2 + kv) * page_size + off) * static_cast<int64_t>(d));
     for (int j = lane; j < d; j += 32) {
       float v = __bfloat162float(row[col + j]) * inv;
-      v = fminf(fmaxf(v, -448.f), 448.f);
-      dst[j] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+      v = fminf(fmaxf(v, -qmax), qmax);
+      dst[j] = fmt == 0 ? static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3))
+                        : static_cast<uint8_t>(static_cast<int8_t>(__float2int_rn(v)));
     }
   }
 }
@@ -378,19 +380,33 @@ extern "C" int ogb_rope_kv_append_bf16(void* qkv, const int* positions, const in
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int ogb_rope_kv_append_fp8(void* qkv, const int* positions, const int* slots, const float* cos_sin,
-                                      void* pool, float* scales, int tokens, int hq, int hkv, int d, int rotary_dim,
-                                      int interleaved, int page_size, int64_t num_slots, int max_pos, int* status,
-                                      void* stream) {
+static int launch_rope_kv_append_q8(void* qkv, const int* positions, const int* slots, const float* cos_sin, void* pool,
+                                    float* scales, int kv_format, int tokens, int hq, int hkv, int d, int rotary_dim,
+                                    int interleaved, int page_size, int64_t num_slots, int max_pos, int* status, void* stream) {
   if (tokens <= 0) return 0;
-  if (d % 8 || rotary_dim % 2 || rotary_dim > d) return -3;
+  if (d % 8 || rotary_dim % 2 || rotary_dim > d || (kv_format != 0 && kv_format != 1)) return -3;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   rope_kv_append_kernel<false><<<tokens, 256, 0, st>>>(static_cast<__nv_bfloat16*>(qkv), positions, slots, cos_sin, nullptr,
                                                       nullptr, hq, hkv, d, rotary_dim, interleaved, page_size, num_slots,
                                                       max_pos, status);
   kv_append_fp8_kernel<<<tokens, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(qkv), slots, static_cast<uint8_t*>(pool), scales,
-                                               hq, hkv, d, page_size, num_slots, status);
+                                               hq, hkv, d, page_size, num_slots, kv_format, status);
   return static_cast<int>(cudaGetLastError());
+}
+extern "C" int ogb_rope_kv_append_fp8(void* qkv, const int* positions, const int* slots, const float* cos_sin,
+                                      void* pool, float* scales, int tokens, int hq, int hkv, int d, int rotary_dim,
+                                      int interleaved, int page_size, int64_t num_slots, int max_pos, int* status,
+                                      void* stream) {
+  return launch_rope_kv_append_q8(qkv, positions, slots, cos_sin, pool, scales, 0, tokens, hq, hkv, d, rotary_dim, interleaved,
+                                  page_size, num_slots, max_pos, status, stream);
+}
+// kv_format 0 = e4m3, 1 = int8; same pool and scale layout
+extern "C" int ogb_rope_kv_append_q8(void* qkv, const int* positions, const int* slots, const float* cos_sin, void* pool,
+                                     float* scales, int kv_format, int tokens, int hq, int hkv, int d, int rotary_dim,
+                                     int interleaved, int page_size, int64_t num_slots, int max_pos, int* status,
+                                     void* stream) {
+  return launch_rope_kv_append_q8(qkv, positions, slots, cos_sin, pool, scales, kv_format, tokens, hq, hkv, d, rotary_dim,
+                                  interleaved, page_size, num_slots, max_pos, status, stream);
 }
 
 static int launch_page_copy(void* dst, const void* src, const int64_t* sp, const int64_t* dp, int n, int64_t page_bytes,

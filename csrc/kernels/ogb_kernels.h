@@ -54,6 +54,19 @@ int ogb_paged_prefill_fp8(const void* q, void* out, const void* pool, const floa
                           int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride, int o_stride,
                           float scale, int* status, void* stream);
 
+// One-byte pages in either format (kv_format 0 = e4m3, 1 = symmetric int8), same pool and scale layout.
+int ogb_rope_kv_append_q8(void* qkv, const int* positions, const int* slots, const float* cos_sin, void* pool, float* scales,
+                          int kv_format, int tokens, int hq, int hkv, int d, int rotary_dim, int interleaved, int page_size,
+                          int64_t num_slots, int max_pos, int* status, void* stream);
+int ogb_paged_decode_q8(const void* q, void* out, const void* pool, const float* scales, int kv_format, const int* page_table,
+                        const int* ctx_len, int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d,
+                        int q_stride, int o_stride, float scale, int num_splits, float* part_o, float* part_ml, int* status,
+                        void* stream);
+int ogb_paged_prefill_q8(const void* q, void* out, const void* pool, const float* scales, int kv_format, const int* page_table,
+                         const int* ctx_len, const int* cu_q, const int* tile_seq, const int* tile_q0, int num_tiles,
+                         int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride, int o_stride,
+                         float scale, int* status, void* stream);
+
 // Sampling.  logits [rows, vocab] bf16 (ld = row stride).  out_tokens int32 [rows].
 int ogb_argmax_bf16(const void* logits, int* out_tokens, int rows, int vocab, int ld, void* stream);
 // Fused temperature -> top-k -> top-p -> min-p -> inverse-CDF draw (u in [0,1) per row).

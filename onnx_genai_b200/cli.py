@@ -38,7 +38,7 @@ def _add_sampling(p):
 
 def _add_engine(p):
     p.add_argument("--device", default="auto", help="auto | cpu | cuda[:N]")
-    p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3fn"])
+    p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3fn", "int8"])
     p.add_argument("--max-batch", type=int, default=32)
     p.add_argument("--vram-limit", default="0.85", help="0.85 (fraction of the device the engine may fill), auto, or a size such as 8GiB for weights + activations + KV")
     p.add_argument("--kv-offload-dir", default="", help="keep the K/V of finished prompts in host memory and this directory; restored on prefix hits")
@@ -80,7 +80,7 @@ def _load(args):
         limit = None
     except ValueError:
         util, limit = 0.85, (None if args.vram_limit == "auto" else args.vram_limit)
-    eng = Engine.from_dir(args.model, device=dev, max_seqs=args.max_batch, kv_dtype="fp8" if args.kv_cache_dtype.startswith("fp8") else "bf16",
+    eng = Engine.from_dir(args.model, device=dev, max_seqs=args.max_batch, kv_dtype={"fp8_e4m3fn": "fp8", "int8": "int8"}.get(args.kv_cache_dtype, "bf16"),
                           gpu_memory_utilization=util if 0 < util <= 1 else 0.85, vram_limit=limit,
                           max_draft_tokens=4 if getattr(args, "speculative", False) else 0,
                           max_seq_len=args.max_context or None)

@@ -169,13 +169,15 @@ class KVCache:
         hkv = kv_heads_local or cfg.num_kv_heads
         self.num_pages = num_pages
         self.dtype = dtype
-        tdtype = torch.bfloat16 if dtype == "bf16" else torch.uint8
+        if dtype not in ("bf16", "fp8", "int8"):
+            raise ValueError(f"kv dtype {dtype!r} is not supported; use bf16, fp8 (e4m3 pages) or int8")
+        tdtype = {"bf16": torch.bfloat16, "fp8": torch.uint8, "int8": torch.int8}[dtype]   # one-byte pools say their format by dtype
         if torch.device(device).type == "cpu" and dtype == "bf16":
             tdtype = torch.float32
         self.pools = [torch.zeros(num_pages, hkv, 2, ops.PAGE, cfg.head_dim, dtype=tdtype, device=device)
                       for _ in range(cfg.num_layers)]
         self.scales = None
-        if dtype == "fp8":
+        if dtype in ("fp8", "int8"):
             self.scales = [torch.zeros(num_pages, hkv, 2, dtype=torch.float32, device=device)
                            for _ in range(cfg.num_layers)]
 

@@ -259,9 +259,14 @@ def silu_mul(gate_up, out=None):
 
 
 @_timed("rope_kv_append")
+def kv_format(pool) -> int:
+    """One-byte page pools say their format by dtype: uint8 holds e4m3 bit patterns (0), int8 holds symmetric int8 (1)."""
+    return 1 if pool.dtype == torch.int8 else 0
+
+
 def rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim=None, interleaved=False,
                    kv_scales=None):
-    """Rotate q,k in place inside qkv and append k,v to the paged pool (bf16, or e4m3 with kv_scales)."""
+    """Rotate q,k in place inside qkv and append k,v to the paged pool (bf16; with kv_scales e4m3 or int8 by the pool's dtype)."""
     rotary_dim = rotary_dim or d
     if not qkv.is_cuda:
         if kv_scales is not None:
@@ -278,10 +283,10 @@ def rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim=
                                          pool.data_ptr(), t, hq, hkv, d, rotary_dim, int(interleaved), PAGE, num_slots,
                                          cos_sin.shape[0], status_word().data_ptr(), _stream())
     else:
-        rc = lib.ogb_rope_kv_append_fp8(qkv.data_ptr(), positions.data_ptr(), slots.data_ptr(), cos_sin.data_ptr(),
-                                        pool.data_ptr(), kv_scales.data_ptr(), t, hq, hkv, d, rotary_dim,
-                                        int(interleaved), PAGE, num_slots, cos_sin.shape[0],
-                                        status_word().data_ptr(), _stream())
+        rc = lib.ogb_rope_kv_append_q8(qkv.data_ptr(), positions.data_ptr(), slots.data_ptr(), cos_sin.data_ptr(),
+                                       pool.data_ptr(), kv_scales.data_ptr(), kv_format(pool), t, hq, hkv, d, rotary_dim,
+                                       int(interleaved), PAGE, num_slots, cos_sin.shape[0],
+                                       status_word().data_ptr(), _stream())
     _native.check(rc, "ogb_rope_kv_append")
     launch_counts["rope_kv_append"] += 1
     return qkv
@@ -313,11 +318,11 @@ def paged_prefill(q, out, pool, page_table, ctx_len, cu_q, tile_seq, tile_q0, nu
         out.copy_(reference.paged_attention(q, pool, page_table, ctx_len, cu_q, hq, hkv, d, scale, window, kv_scales))
         return out
     if kv_scales is not None:
-        rc = _native.load().ogb_paged_prefill_fp8(
-            q.data_ptr(), out.data_ptr(), pool.data_ptr(), kv_scales.data_ptr(), page_table.data_ptr(), ctx_len.data_ptr(),
+        rc = _native.load().ogb_paged_prefill_q8(
+            q.data_ptr(), out.data_ptr(), pool.data_ptr(), kv_scales.data_ptr(), kv_format(pool), page_table.data_ptr(), ctx_len.data_ptr(),
             cu_q.data_ptr(), tile_seq.data_ptr(), tile_q0.data_ptr(), int(num_tiles), ctx_len.numel(), page_table.shape[1],
             pool.shape[0], hq, hkv, d, q.stride(0), out.stride(0), float(scale), status_word().data_ptr(), _stream())
-        _native.check(rc, "ogb_paged_prefill_fp8")
+        _native.check(rc, "ogb_paged_prefill_q8")
         launch_counts["paged_prefill_fp8"] += 1
         return out
     rc = _native.load().ogb_paged_prefill_bf16(
@@ -347,11 +352,11 @@ def paged_decode(q, out, pool, page_table, ctx_len, hq, hkv, d, scale=None, num_
         part_o = torch.empty(n * hq * num_splits * d, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(n * hq * num_splits * 2, dtype=torch.float32, device=q.device)
     if kv_scales is not None:
-        rc = _native.load().ogb_paged_decode_fp8(
-            q.data_ptr(), out.data_ptr(), pool.data_ptr(), kv_scales.data_ptr(), page_table.data_ptr(), ctx_len.data_ptr(), n,
+        rc = _native.load().ogb_paged_decode_q8(
+            q.data_ptr(), out.data_ptr(), pool.data_ptr(), kv_scales.data_ptr(), kv_format(pool), page_table.data_ptr(), ctx_len.data_ptr(), n,
             page_table.shape[1], pool.shape[0], hq, hkv, d, q.stride(0), out.stride(0), float(scale), int(num_splits),
             _ptr(part_o), _ptr(part_ml), status_word().data_ptr(), _stream())
-        _native.check(rc, "ogb_paged_decode_fp8")
+        _native.check(rc, "ogb_paged_decode_q8")
         launch_counts["paged_decode_fp8"] += 1
         return out
     rc = _native.load().ogb_paged_decode_bf16(

@@ -95,13 +95,20 @@ def e4m3_bytes(x):
     return x.float().clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
 
 
+def int8_bytes(x):
+    """fp32 -> symmetric int8 with saturation at +-127 (round to nearest even)."""
+    return torch.round(x.float().clamp(-127.0, 127.0)).to(torch.int8)
+
+
 def kv_append_fp8(qkv, slots, pool, scales, hq, hkv, d):
-    """e4m3 page codec: one scale per (page, head, K|V), fixed by the page's first token at amax * 2 / 448 (headroom
+    """One-byte page codec (e4m3 in a uint8 pool, symmetric int8 in an int8 pool): one scale per (page, head, K|V),
+    fixed by the page's first token at amax * 2 / qmax, qmax = 448 or 127 (headroom
     for the 15 tokens that follow, which saturate to it).  Tokens are taken in row order, so a chunk that starts a
     page and continues it in the same call behaves like one append per token.  pool [P,hkv,2,PAGE,d] uint8,
     scales [P,hkv,2] fp32; qkv already rotated."""
     t = qkv.shape[0]
     v = qkv.view(t, hq + 2 * hkv, d).float()
+    qmax, encode = (127.0, int8_bytes) if pool.dtype == torch.int8 else (448.0, e4m3_bytes)
     for i in range(t):
         slot = int(slots[i])
         if slot < 0:
@@ -111,9 +118,9 @@ def kv_append_fp8(qkv, slots, pool, scales, hq, hkv, d):
             for h in range(hkv):
                 vec = v[i, hq + kv * hkv + h]
                 if off == 0 or not float(scales[page, h, kv]) > 0.0:
-                    scales[page, h, kv] = max(float(vec.abs().max()) * 2.0, 1e-6) / 448.0
+                    scales[page, h, kv] = max(float(vec.abs().max()) * 2.0, 1e-6) / qmax
                 inv = torch.tensor(1.0, dtype=torch.float32) / scales[page, h, kv].float()
-                pool[page, h, kv, off] = e4m3_bytes(vec * inv)
+                pool[page, h, kv, off] = encode(vec * inv)
 
 
 def rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim=None, interleaved=False, kv_scales=None):

@@ -174,25 +174,29 @@ def test_fp8_kv_pages_on_cpu_stay_close_to_full_precision(weights):
     rng = np.random.default_rng(9)
     prompt = rng.integers(0, CFG.vocab, size=70).tolist()
     logits = {}
-    for kv in ("bf16", "fp8"):
+    for kv in ("bf16", "fp8", "int8"):
         eng = _engine(weights, kv_dtype=kv)
         eng.add_request(np.asarray(prompt, dtype=np.int32), 3)
         eng.step()
         eng.step()
         logits[kv] = eng.model.logits[:1].float().clone()
-        if kv == "fp8":
-            assert eng.kv.pools[0].dtype == torch.uint8 and float(eng.kv.scales[0].max()) > 0
-    err = float((logits["fp8"] - logits["bf16"]).norm() / logits["bf16"].norm())
-    assert err < 0.25, err          # 3 mantissa bits and sharp attention (weights of std 0.3): noise, not garbage
+        if kv != "bf16":
+            assert eng.kv.pools[0].dtype == (torch.uint8 if kv == "fp8" else torch.int8) and float(eng.kv.scales[0].max()) > 0
+    for kv in ("fp8", "int8"):
+        err = float((logits[kv] - logits["bf16"]).norm() / logits["bf16"].norm())
+        assert err < 0.25, (kv, err)          # 3 mantissa bits and sharp attention (weights of std 0.3): noise, not garbage
+    with pytest.raises(ValueError, match="kv dtype 'int4' is not supported"):
+        _engine(weights, kv_dtype="int4")
 
 
-def test_fp8_codec_chunked_append_equals_token_by_token():
+@pytest.mark.parametrize("dtype", [torch.uint8, torch.int8])
+def test_fp8_codec_chunked_append_equals_token_by_token(dtype):
     torch.manual_seed(4)
     hq, hkv, d = 2, 2, 16
     t = 3 * ref.PAGE - 4
     qkv = torch.randn(t, (hq + 2 * hkv) * d) * torch.linspace(0.3, 2.0, t)[:, None]
     slots = torch.arange(t, dtype=torch.int32)
-    mk = lambda: (torch.zeros(3, hkv, 2, ref.PAGE, d, dtype=torch.uint8), torch.full((3, hkv, 2), 9.0))
+    mk = lambda: (torch.zeros(3, hkv, 2, ref.PAGE, d, dtype=dtype), torch.full((3, hkv, 2), 9.0))
     pool_a, sc_a = mk()
     for i in range(t):
         ref.kv_append_fp8(qkv[i:i + 1], slots[i:i + 1], pool_a, sc_a, hq, hkv, d)
@@ -200,7 +204,7 @@ def test_fp8_codec_chunked_append_equals_token_by_token():
     ref.kv_append_fp8(qkv[:20], slots[:20], pool_b, sc_b, hq, hkv, d)
     ref.kv_append_fp8(qkv[20:], slots[20:], pool_b, sc_b, hq, hkv, d)
     assert torch.equal(pool_a, pool_b) and torch.equal(sc_a, sc_b)
-    deq = pool_a.view(torch.float8_e4m3fn).float() * sc_a[..., None, None]
+    deq = (pool_a.view(torch.float8_e4m3fn) if dtype == torch.uint8 else pool_a).float() * sc_a[..., None, None]
     want = qkv.view(t, hq + 2 * hkv, d)[:, hq:].reshape(t, 2, hkv, d)
     got = deq.permute(0, 3, 2, 1, 4).reshape(3 * ref.PAGE, 2, hkv, d)[:t]
     rel = (got - want).abs() / (want.abs() + 0.05 * want.abs().max())

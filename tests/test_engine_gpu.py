@@ -140,7 +140,7 @@ def test_fp8_kv_engine_stays_close_to_bf16_kv():
     w = random_weights(CFG128, "cuda", seed=5, std=0.05)
     prompt = np.random.default_rng(2).integers(0, CFG128.vocab, size=300).astype(np.int32)
     logits = {}
-    for kv in ("bf16", "fp8"):
+    for kv in ("bf16", "fp8", "int8"):
         eng = LLMEngine(EngineConfig(model=CFG128, num_pages=64, max_seqs=2, max_tokens_per_step=512, max_seq_len=512,
                                      kv_dtype=kv), weights=w, device="cuda")
         eng.add_request(prompt, 2)
@@ -148,8 +148,9 @@ def test_fp8_kv_engine_stays_close_to_bf16_kv():
         eng.step()                                            # second step: a decode row that reads the stored pages
         logits[kv] = eng.model.logits[:1].float().cpu().clone()
     ops.check_status()
-    err = float((logits["fp8"] - logits["bf16"]).norm() / logits["bf16"].norm())
-    assert err < 6e-2, err
+    for kv in ("fp8", "int8"):
+        err = float((logits[kv] - logits["bf16"]).norm() / logits["bf16"].norm())
+        assert err < 6e-2, (kv, err)
     assert ops.launch_counts["paged_decode_fp8"] > 0 and ops.launch_counts["paged_prefill_fp8"] > 0
 
 
@@ -186,3 +187,41 @@ def test_long_context_draft_rows_run_on_the_split_kv_decode_kernel(kv):
     assert eng.verify_on_decode_kernel > 0 and eng.core.spec_accepted > 0
     agree = next((i for i, (a, b) in enumerate(zip(got, want)) if a != b), len(want))
     assert agree >= 12, (agree, got, want)                # identical unless an fp8 near-tie flips late in the run
+
+
+def test_mtp_proposer_drafts_from_device_hidden_states():
+    """The MTP head runs on the device from the hidden rows the engine hands over.  A random head is almost never right,
+    so its run must equal that of a proposer that is always wrong (same verification shapes, every draft rewound), and
+    stay with plain greedy decoding up to bf16 near-ties between the 4-row verification pass and the 1-row decode pass."""
+    from onnx_genai_b200.speculative import SpeculativeProposer
+    from onnx_genai_b200.speculative.mtp import MtpHead, MtpProposer
+
+    w = random_weights(CFG128, "cuda", seed=7, std=0.08)
+    prompt = np.random.default_rng(4).integers(0, CFG128.vocab, size=90).astype(np.int32)
+    mk = lambda k: LLMEngine(EngineConfig(model=CFG128, num_pages=64, max_seqs=2, max_tokens_per_step=512, max_seq_len=512,
+                                          max_draft_tokens=k, enable_prefix_cache=False), weights=w, device="cuda")
+    plain = mk(0).generate([prompt], max_new_tokens=12)[0]
+
+    class Wrong(SpeculativeProposer):
+        def propose(self, token_ids, k):
+            return np.full(k, (int(token_ids[-1]) + 1) % 7, dtype=np.int32)
+
+    def run(proposer):
+        eng = mk(3)
+        sid = eng.add_request(prompt, 12)
+        eng.proposers[sid] = proposer
+        got = []
+        while eng.has_work:
+            got += [tok for s, tok, fin in eng.step().events if s == sid]
+        ops.check_status()
+        return got, eng
+
+    want, _ = run(Wrong())
+    prop = MtpProposer(MtpHead.random(w.embed, w.lm_head, inter=256, seed=1))
+    got, eng = run(prop)
+    assert prop.hidden is not None and prop.hidden.is_cuda and prop.hidden.shape == (CFG128.hidden,)
+    assert eng.core.spec_proposed >= 3
+    if eng.core.spec_accepted == 0:
+        assert got == want                                # same shapes, same rewinds: bit-identical runs
+    agree = next((i for i, (a, b) in enumerate(zip(got, plain)) if a != b), len(plain))
+    assert agree >= 6, (agree, got, plain)

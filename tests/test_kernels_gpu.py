@@ -344,9 +344,17 @@ def test_moe_experts_grouped_gemm(t, e, k, hidden, inter):
     assert _rel_err(lo.float() + hi.float() + x0.float(), want) < 3e-2
 
 
-def _make_paged_fp8(ctx_lens, hkv, d, seed=0):
-    """Random KV quantised to e4m3 per (page, head, K|V) with amax scaling; returns pool bytes, scales, table and the
-    dequantised fp32 values the oracle should see."""
+QMAX = {"fp8": 448.0, "int8": 127.0}
+POOL_DTYPE = {"fp8": torch.uint8, "int8": torch.int8}
+
+
+def _dequant(pool, scales):
+    raw = pool.view(torch.float8_e4m3fn) if pool.dtype == torch.uint8 else pool
+    return raw.float() * scales[..., None, None]
+
+
+def _make_paged_fp8(ctx_lens, hkv, d, seed=0, fmt="fp8"):
+    """Random KV quantised to e4m3 (or int8) per (page, head, K|V) with amax scaling; returns pool bytes, scales, table."""
     g = torch.Generator(device="cpu").manual_seed(seed)
     pages_per = [(c + ref.PAGE - 1) // ref.PAGE for c in ctx_lens]
     total = sum(pages_per) + 2
@@ -357,17 +365,21 @@ def _make_paged_fp8(ctx_lens, hkv, d, seed=0):
         table[s, :n] = perm[o:o + n].to(torch.int32)
         o += n
     vals = torch.randn(total, hkv, 2, ref.PAGE, d, generator=g) * torch.rand(total, hkv, 2, 1, 1, generator=g) * 2
-    scales = vals.abs().amax(dim=(-1, -2)).clamp_min(1e-6) / 448.0
-    q8 = (vals / scales[..., None, None]).to(torch.float8_e4m3fn)
-    return q8.view(torch.uint8).to(DEV), scales.float().to(DEV), table.to(DEV)
+    scales = vals.abs().amax(dim=(-1, -2)).clamp_min(1e-6) / QMAX[fmt]
+    if fmt == "int8":
+        q8 = torch.round(vals / scales[..., None, None]).clamp(-127, 127).to(torch.int8)
+    else:
+        q8 = (vals / scales[..., None, None]).to(torch.float8_e4m3fn).view(torch.uint8)
+    return q8.to(DEV), scales.float().to(DEV), table.to(DEV)
 
 
-def test_paged_attention_fp8_pages():
+@pytest.mark.parametrize("fmt", ["fp8", "int8"])
+def test_paged_attention_fp8_pages(fmt):
     torch.manual_seed(13)
     hq, hkv, d = 28, 4, 128
     ctx = [1, 16, 17, 63, 64, 65, 300, 1000]
     n = len(ctx)
-    pool, scales, table = _make_paged_fp8(ctx, hkv, d)
+    pool, scales, table = _make_paged_fp8(ctx, hkv, d, fmt=fmt)
     ctx_t = torch.tensor(ctx, dtype=torch.int32, device=DEV)
     q = torch.randn(n, (hq + 2 * hkv) * d, device=DEV).bfloat16()
     cu = torch.arange(n + 1, dtype=torch.int32, device=DEV)
@@ -394,15 +406,17 @@ def test_paged_attention_fp8_pages():
     assert _rel_err(outp, wantp) < 2e-2
 
 
-def test_rope_kv_append_fp8_roundtrip():
+@pytest.mark.parametrize("fmt", ["fp8", "int8"])
+def test_rope_kv_append_fp8_roundtrip(fmt):
     torch.manual_seed(14)
+    qmax = QMAX[fmt]
     hq, hkv, d, pages = 4, 2, 128, 4
     t = pages * ref.PAGE
     qkv = torch.randn(t, (hq + 2 * hkv) * d, device=DEV).bfloat16()
     pos = torch.arange(t, dtype=torch.int32, device=DEV)
     slots = torch.arange(t, dtype=torch.int32, device=DEV)       # tokens land in order: offset 0 of each page first
     cs = ref.rope_table(256, d, 1e4, DEV)
-    pool = torch.zeros(pages, hkv, 2, ref.PAGE, d, device=DEV, dtype=torch.uint8)
+    pool = torch.zeros(pages, hkv, 2, ref.PAGE, d, device=DEV, dtype=POOL_DTYPE[fmt])
     scales = torch.zeros(pages, hkv, 2, device=DEV)
     want_qkv = qkv.clone()
     bf_pool = torch.zeros(pages, hkv, 2, ref.PAGE, d, device=DEV, dtype=torch.bfloat16)
@@ -413,14 +427,15 @@ def test_rope_kv_append_fp8_roundtrip():
             ops.rope_kv_append(qkv[i:i + 1], pos[i:i + 1], slots[i:i + 1], cs, pool, hq, hkv, d, kv_scales=scales)
     torch.cuda.synchronize()
     ops.check_status()
-    deq = pool.view(torch.float8_e4m3fn).float() * scales[..., None, None]
-    clipped = (bf_pool.float().abs() > 448 * scales[..., None, None]).float().mean()
+    deq = _dequant(pool, scales)
+    clipped = (bf_pool.float().abs() > qmax * scales[..., None, None]).float().mean()
     assert float(clipped) < 0.02                                   # 2x headroom over the first token's amax
     err = (deq - bf_pool.float()).abs() / (bf_pool.float().abs() + 0.05 * bf_pool.float().abs().amax())
-    assert float(err[(bf_pool.float().abs() <= 448 * scales[..., None, None])].mean()) < 0.05
+    assert float(err[(bf_pool.float().abs() <= qmax * scales[..., None, None])].mean()) < 0.05
 
 
-def test_rope_kv_append_fp8_one_launch_equals_token_by_token():
+@pytest.mark.parametrize("fmt", ["fp8", "int8"])
+def test_rope_kv_append_fp8_one_launch_equals_token_by_token(fmt):
     """A prefill chunk appends many tokens of a page in one launch; the stored bytes and scales must be exactly those
     of appending the tokens one launch at a time (every token of a page uses the scale of the page's first token),
     also when the pages held another sequence's scales before, and when a later chunk continues a page."""
@@ -433,7 +448,7 @@ def test_rope_kv_append_fp8_one_launch_equals_token_by_token():
     cs = ref.rope_table(256, d, 1e4, DEV)
 
     def fresh():
-        pool = torch.zeros(pages, hkv, 2, ref.PAGE, d, device=DEV, dtype=torch.uint8)
+        pool = torch.zeros(pages, hkv, 2, ref.PAGE, d, device=DEV, dtype=POOL_DTYPE[fmt])
         scales = torch.full((pages, hkv, 2), 123.0, device=DEV)      # stale scales of a previous owner
         return pool, scales
 
@@ -453,8 +468,9 @@ def test_rope_kv_append_fp8_one_launch_equals_token_by_token():
         assert torch.equal(pool, pool_a)
 
 
-def test_fp8_append_kernel_matches_the_cpu_codec_byte_for_byte():
-    """The device e4m3 append (rotation launch + codec launch) against the CPU statement of the same codec."""
+@pytest.mark.parametrize("fmt", ["fp8", "int8"])
+def test_fp8_append_kernel_matches_the_cpu_codec_byte_for_byte(fmt):
+    """The device one-byte append (rotation launch + codec launch) against the CPU statement of the same codec."""
     torch.manual_seed(16)
     hq, hkv, d, pages = 4, 2, 128, 3
     t = pages * ref.PAGE - 3
@@ -462,11 +478,11 @@ def test_fp8_append_kernel_matches_the_cpu_codec_byte_for_byte():
     pos = torch.arange(t, dtype=torch.int32)
     slots = torch.arange(t, dtype=torch.int32)
     cs = ref.rope_table(128, d, 1e4)
-    pool_c = torch.zeros(pages, hkv, 2, ref.PAGE, d, dtype=torch.uint8)
+    pool_c = torch.zeros(pages, hkv, 2, ref.PAGE, d, dtype=POOL_DTYPE[fmt])
     sc_c = torch.zeros(pages, hkv, 2)
     q_c = qkv.clone()
     ref.rope_kv_append(q_c, pos, slots, cs, pool_c, hq, hkv, d, kv_scales=sc_c)
-    pool_g = torch.zeros(pages, hkv, 2, ref.PAGE, d, dtype=torch.uint8, device=DEV)
+    pool_g = torch.zeros(pages, hkv, 2, ref.PAGE, d, dtype=POOL_DTYPE[fmt], device=DEV)
     sc_g = torch.zeros(pages, hkv, 2, device=DEV)
     q_g = qkv.to(DEV)
     ops.rope_kv_append(q_g, pos.to(DEV), slots.to(DEV), cs.to(DEV), pool_g, hq, hkv, d, kv_scales=sc_g)

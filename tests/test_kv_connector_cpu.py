@@ -19,7 +19,7 @@ def _engine(weights, kv_dtype="bf16", num_pages=48):
     return Engine(llm)
 
 
-@pytest.mark.parametrize("kv_dtype", ["bf16", "fp8"])
+@pytest.mark.parametrize("kv_dtype", ["bf16", "fp8", "int8"])
 def test_chunks_are_offloaded_and_restored_after_the_device_cache_forgot_them(tmp_path, kv_dtype):
     weights = random_weights(CFG, "cpu", seed=11, std=0.3, dtype=torch.float32)
     rng = np.random.default_rng(0)
