@@ -14,6 +14,20 @@ BlockPool::BlockPool(int num_pages) : ref_(num_pages, 0), hash_of_(num_pages, 0)
   for (int i = num_pages - 1; i >= 0; --i) free_.push_back(i);  // pop_back hands out page 0 first
 }
 
+void BlockPool::add_pages(int n) {
+  if (n <= 0) return;
+  const int old = num_pages();
+  ref_.resize(old + n, 0);
+  hash_of_.resize(old + n, 0);
+  in_evictable_.resize(old + n, 0);
+  // the free list hands out from its back: put the new ids at the front so existing free pages are reused first
+  std::vector<int> fresh;
+  fresh.reserve(free_.size() + n);
+  for (int i = old + n - 1; i >= old; --i) fresh.push_back(i);
+  fresh.insert(fresh.end(), free_.begin(), free_.end());
+  free_.swap(fresh);
+}
+
 int BlockPool::allocate() {
   int page = -1;
   if (!free_.empty()) {
@@ -782,6 +796,7 @@ int ogb_core_prefix_peek(void* h, const int32_t* tokens, int n, int32_t* out_pag
 int ogb_core_seq_len(void* h, int64_t id) { return static_cast<Core*>(h)->seq_len(id); }
 int ogb_core_seq_tokens(void* h, int64_t id, int32_t* out, int cap) { return static_cast<Core*>(h)->seq_tokens(id, out, cap); }
 void ogb_core_release(void* h, int64_t id) { static_cast<Core*>(h)->release(id); }
+void ogb_core_add_pages(void* h, int n) { static_cast<Core*>(h)->add_pages(n); }
 int64_t ogb_core_stat(void* h, int which) {
   Core* c = static_cast<Core*>(h);
   switch (which) {
@@ -796,6 +811,7 @@ int64_t ogb_core_stat(void* h, int which) {
     case 8: return c->spec_proposed();
     case 9: return c->spec_accepted();
     case 10: return c->spec_steps();
+    case 11: return c->num_pages();
     default: return -1;
   }
 }

@@ -69,6 +69,7 @@ class BlockPool {
   int num_pages() const { return static_cast<int>(ref_.size()); }
   int num_free() const { return static_cast<int>(free_.size() + evictable_.size()); }
   int allocate();                    // -1 when exhausted
+  void add_pages(int n);             // the backing buffer grew: ids [old size, old size + n) become free pages
   void retain(int page) { ++ref_[page]; }
   void release(int page);            // refcount--; cached pages become evictable, others free
   int refcount(int page) const { return ref_[page]; }
@@ -182,6 +183,8 @@ class Core {
   int num_running() const { return static_cast<int>(running_.size()); }
   int num_swapped() const { return static_cast<int>(swapped_.size()); }
   int num_free_pages() const { return pool_.num_free(); }
+  int num_pages() const { return pool_.num_pages(); }
+  void add_pages(int n) { pool_.add_pages(n); cfg_.num_pages = pool_.num_pages(); }   // KV buffers grow in place
   int64_t prefix_hits() const { return pool_.hits(); }
   int64_t prefix_lookups() const { return pool_.lookups(); }
   int64_t num_preemptions() const { return preemptions_; }

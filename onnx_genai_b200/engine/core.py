@@ -60,6 +60,8 @@ def load_runtime():
     for name in ("ogb_core_cancel",):
         getattr(lib, name).argtypes = [P, c_int64]
         getattr(lib, name).restype = c_int
+    lib.ogb_core_add_pages.argtypes = [P, c_int]
+    lib.ogb_core_add_pages.restype = None
     lib.ogb_core_fork.argtypes = [P, c_int64]
     lib.ogb_core_fork.restype = c_int64
     lib.ogb_core_rewind.argtypes = [P, c_int64, c_int]
@@ -158,6 +160,10 @@ class Core:
     def cancel(self, sid):
         return bool(self.lib.ogb_core_cancel(self.h, sid))
 
+    def add_pages(self, n: int) -> None:
+        """The KV buffers grew in place: ``n`` more page ids become allocatable."""
+        self.lib.ogb_core_add_pages(self.h, int(n))
+
     def fork(self, sid):
         return int(self.lib.ogb_core_fork(self.h, sid))
 
@@ -225,3 +231,4 @@ class Core:
     spec_proposed = property(lambda self: self._stat(8))
     spec_accepted = property(lambda self: self._stat(9))
     spec_steps = property(lambda self: self._stat(10))
+    num_pages = property(lambda self: self._stat(11))

@@ -35,6 +35,8 @@ from .core import HDR, Core, CoreConfig
 class EngineConfig:
     model: DecoderConfig
     num_pages: int = 0                 # 0: size from free device memory
+    kv_max_pages: int = 0              # > num_pages (CUDA, TP=1): reserve address space for this many pages, back num_pages now
+                                       # and more on demand when the scheduler runs low (the pool grows in place)
     gpu_memory_utilization: float = 0.85
     num_host_pages: int = 0
     max_seqs: int = 256
@@ -121,8 +123,10 @@ class LLMEngine:
             else:
                 num_pages = min(4096, cfg.max_seqs * max_pages_per_seq + 16)
         self.num_pages = int(num_pages)
-        self.kv = KVCache(m, self.num_pages, self.device, len(hs.kv_heads), cfg.kv_dtype)
-        self.memory.lease("kv", tier, tensor_bytes(self.kv), f"{self.num_pages} pages of 16 tokens, {cfg.kv_dtype}")
+        kv_max = cfg.kv_max_pages if (is_cuda and self.tp == 1 and cfg.kv_max_pages > self.num_pages) else 0
+        self.kv = KVCache(m, self.num_pages, self.device, len(hs.kv_heads), cfg.kv_dtype, max_pages=kv_max)
+        self.kv_lease = self.memory.lease("kv", tier, self.kv.mapped_bytes(), f"pages of 16 tokens, {cfg.kv_dtype}")
+        self.kv_grows, self.kv_grow_error = 0, None
         self.core = Core(CoreConfig(num_pages=self.num_pages, num_host_pages=cfg.num_host_pages, max_seqs=cfg.max_seqs,
                                     max_tokens_per_step=cfg.max_tokens_per_step, max_pages_per_seq=max_pages_per_seq,
                                     prefill_chunk=cfg.prefill_chunk, token_multiple=cfg.token_multiple,
@@ -212,6 +216,32 @@ class LLMEngine:
             dst = torch.from_numpy(pn[L.copy_dst:L.copy_dst + ncp].astype(np.int64)).to(self.device)
             for pool in self.kv.pools:
                 ops.kv_page_copy(pool, src, dst)
+
+    def _maybe_grow_kv(self) -> None:
+        """Back more KV pages when the allocator runs low and the pool has address space left.  Addresses do not move,
+        so page tables, captured graphs and cached descriptors stay valid; a failure (device memory or the VRAM limit)
+        ends growth for good and the scheduler falls back to preemption as with a fixed pool."""
+        kv = self.kv
+        if not kv.growable:
+            return
+        low_water = self.cfg.max_tokens_per_step // ops.PAGE + self.cfg.max_seqs
+        if self.core.num_free_pages >= low_water:
+            return
+        before = kv.num_pages
+        target = min(kv.max_pages, max(before + 2 * low_water, before + before // 2))
+        old_bytes = self.kv_lease.nbytes
+        try:
+            self.kv_lease.resize(old_bytes // before * target)
+            kv.grow(target)
+        except Exception as exc:
+            self.kv_lease.resize(kv.mapped_bytes())
+            kv.max_pages = kv.num_pages                    # not growable any more
+            self.kv_grow_error = str(exc)
+        if kv.num_pages > before:
+            self.core.add_pages(kv.num_pages - before)
+            self.num_pages = kv.num_pages
+            self.kv_lease.resize(kv.mapped_bytes())
+            self.kv_grows += 1
 
     def _pick_splits(self, nd: int, max_ctx: int) -> int:
         if self.cfg.decode_splits > 0:
@@ -387,6 +417,7 @@ class LLMEngine:
             for (sid, _, _), draft in zip(items, drafts):
                 if len(draft):
                     self.core.set_draft(sid, draft)
+        self._maybe_grow_kv()
         t = self.core.build_step(self.plan_host.data_ptr())
         if t <= 0:
             return out

@@ -163,9 +163,15 @@ class StepInputs:
 
 
 class KVCache:
-    """Per-layer paged pools [pages, kv_heads_local, 2, 16, head_dim] (bf16, or e4m3 + scales)."""
+    """Per-layer paged pools [pages, kv_heads_local, 2, 16, head_dim] (bf16, or e4m3 + scales).
 
-    def __init__(self, cfg: DecoderConfig, num_pages: int, device, kv_heads_local: int | None = None, dtype="bf16"):
+    With ``max_pages`` > ``num_pages`` on a CUDA device each pool (and scale table) is a view over a reserved address
+    range of ``max_pages`` pages of which only the first ``num_pages`` are backed; :meth:`grow` backs more in place, so
+    page ids, tensor addresses, cached TMA descriptors and captured graphs stay valid.  Nothing may touch pages
+    beyond ``num_pages``; the page allocator never hands them out before :meth:`grow` has returned."""
+
+    def __init__(self, cfg: DecoderConfig, num_pages: int, device, kv_heads_local: int | None = None, dtype="bf16",
+                 max_pages: int = 0):
         hkv = kv_heads_local or cfg.num_kv_heads
         self.num_pages = num_pages
         self.dtype = dtype
@@ -174,12 +180,65 @@ class KVCache:
         tdtype = {"bf16": torch.bfloat16, "fp8": torch.uint8, "int8": torch.int8}[dtype]   # one-byte pools say their format by dtype
         if torch.device(device).type == "cpu" and dtype == "bf16":
             tdtype = torch.float32
+        quant = dtype in ("fp8", "int8")
+        self.max_pages = max(int(max_pages), num_pages)
+        self.buffers = None
+        if self.max_pages > num_pages and torch.device(device).type == "cuda":
+            from ..utils.vmm import GrowableBuffer
+
+            dev = torch.device(device).index or 0
+            self.page_nbytes = hkv * 2 * ops.PAGE * cfg.head_dim * torch.empty(0, dtype=tdtype).element_size()
+            self.scale_nbytes = hkv * 2 * 4
+            self.buffers, self.scale_buffers, self.pools, self.scales = [], [], [], [] if quant else None
+            for _ in range(cfg.num_layers):
+                buf = GrowableBuffer(self.max_pages * self.page_nbytes, dev, num_pages * self.page_nbytes)
+                self.buffers.append(buf)
+                buf.view(torch.uint8).zero_()
+                self.pools.append(buf.span(tdtype, (self.max_pages, hkv, 2, ops.PAGE, cfg.head_dim)))
+                if quant:
+                    sb = GrowableBuffer(self.max_pages * self.scale_nbytes, dev, num_pages * self.scale_nbytes)
+                    self.scale_buffers.append(sb)
+                    sb.view(torch.uint8).zero_()
+                    self.scales.append(sb.span(torch.float32, (self.max_pages, hkv, 2)))
+            return
+        self.max_pages = num_pages
         self.pools = [torch.zeros(num_pages, hkv, 2, ops.PAGE, cfg.head_dim, dtype=tdtype, device=device)
                       for _ in range(cfg.num_layers)]
         self.scales = None
-        if dtype in ("fp8", "int8"):
+        if quant:
             self.scales = [torch.zeros(num_pages, hkv, 2, dtype=torch.float32, device=device)
                            for _ in range(cfg.num_layers)]
+
+    @property
+    def growable(self) -> bool:
+        return self.buffers is not None and self.num_pages < self.max_pages
+
+    def grow(self, new_pages: int) -> int:
+        """Back pages up to ``new_pages`` (clamped to ``max_pages``) in every layer; returns the new page count.  If the
+        device runs out of memory part-way, layers that already grew keep their extra backing (harmless) and the page
+        count stays where it was."""
+        if self.buffers is None:
+            return self.num_pages
+        new_pages = min(int(new_pages), self.max_pages)
+        if new_pages <= self.num_pages:
+            return self.num_pages
+        for buf in self.buffers:
+            old = buf.mapped
+            buf.grow(new_pages * self.page_nbytes)
+            if buf.mapped > old:     # scale tables rely on zero meaning "page not started"; pools are zeroed for tidiness
+                buf.view(torch.uint8, (buf.mapped - old,), old).zero_()
+        for sb in self.scale_buffers:
+            old = sb.mapped
+            sb.grow(new_pages * self.scale_nbytes)
+            if sb.mapped > old:
+                sb.view(torch.uint8, (sb.mapped - old,), old).zero_()
+        self.num_pages = new_pages
+        return new_pages
+
+    def mapped_bytes(self) -> int:
+        if self.buffers is None:
+            return sum(p.numel() * p.element_size() for p in self.pools) + sum(s.numel() * 4 for s in (self.scales or []))
+        return sum(b.mapped for b in self.buffers) + sum(b.mapped for b in self.scale_buffers)
 
     def page_bytes(self) -> int:
         p = self.pools[0]
@@ -279,7 +338,7 @@ class DecoderModel:
             for j, t in enumerate((lw.ln1, lw.qkv_w, lw.qkv_b, lw.o_w, lw.ln2, lw.gate_up_w, lw.down_w, kv.pools[i])):
                 lp[8 * i + j] = ptr(t)
         self._native_lib = lib
-        self.native = lib.ogb_decoder_create(ip, kv.num_pages, fp, gp, lp)
+        self.native = lib.ogb_decoder_create(ip, kv.pools[0].shape[0], fp, gp, lp)   # the pool's address range, backed or not yet
         return bool(self.native)
 
     def _tp_step_args(self, rows: int):

@@ -225,3 +225,23 @@ def test_mtp_proposer_drafts_from_device_hidden_states():
         assert got == want                                # same shapes, same rewinds: bit-identical runs
     agree = next((i for i, (a, b) in enumerate(zip(got, plain)) if a != b), len(plain))
     assert agree >= 6, (agree, got, plain)
+
+
+def test_kv_pool_grows_in_place_and_results_do_not_change():
+    """A pool that starts with 8 backed pages inside a 256-page address range: the engine backs more as the scheduler
+    runs low; page ids, tensor addresses and results are those of a pool that was large from the start."""
+    w = random_weights(CFG128, "cuda", seed=8, std=0.05)
+    prompts = [np.random.default_rng(s).integers(0, CFG128.vocab, size=n).astype(np.int32) for s, n in ((5, 300), (6, 170))]
+    mk = lambda pages, mx: LLMEngine(EngineConfig(model=CFG128, num_pages=pages, kv_max_pages=mx, max_seqs=2, max_tokens_per_step=64,
+                                                  max_seq_len=512, enable_prefix_cache=False), weights=w, device="cuda")
+    want = mk(256, 0).generate(prompts, max_new_tokens=8)
+    eng = mk(8, 256)
+    base = [p.data_ptr() for p in eng.kv.pools]
+    assert eng.kv.growable and eng.kv.num_pages == 8 and eng.kv.pools[0].shape[0] == 256
+    got = eng.generate(prompts, max_new_tokens=8)
+    ops.check_status()
+    assert got == want
+    assert eng.kv_grows >= 2 and eng.kv_grow_error is None and 8 < eng.kv.num_pages <= 256 and eng.core.num_pages == eng.kv.num_pages
+    assert [p.data_ptr() for p in eng.kv.pools] == base
+    snap = eng.memory.snapshot()["vram"]["by_role"]["kv"]
+    assert snap == eng.kv.mapped_bytes() >= eng.kv.num_pages * eng.kv.page_nbytes * CFG128.num_layers

@@ -494,3 +494,42 @@ def test_fp8_append_kernel_matches_the_cpu_codec_byte_for_byte(fmt):
     assert torch.allclose(sc_g.cpu(), sc_c, rtol=1e-2)
     mismatch = (pool_g.cpu() != pool_c).float()
     assert float(mismatch.mean()) < 0.01                            # bytes differ only where the rotated input differed by an ulp
+
+
+def test_vmm_growable_buffer_keeps_its_address_and_contents():
+    from onnx_genai_b200.utils import vmm
+
+    assert vmm.available(0)
+    buf = vmm.GrowableBuffer(64 << 20, 0)
+    assert buf.mapped == 0 and buf.reserved >= 64 << 20 and buf.granularity >= 1 << 16
+    base = buf.ptr
+    buf.grow(3 << 20)
+    first = buf.mapped
+    assert first >= 3 << 20 and first % buf.granularity == 0 and buf.chunks == 1
+    a = buf.view(torch.int32)
+    a.copy_(torch.arange(a.numel(), dtype=torch.int32, device=DEV))
+    buf.grow(2 << 20)                                       # already covered: nothing happens
+    assert buf.mapped == first and buf.chunks == 1
+    buf.grow(first + (5 << 20))
+    assert buf.ptr == base and buf.mapped > first and buf.chunks == 2
+    whole = buf.view(torch.int32)
+    assert whole.data_ptr() == a.data_ptr() == base
+    whole[a.numel():].fill_(-7)
+    torch.cuda.synchronize()
+    assert torch.equal(whole[: a.numel()].cpu(), torch.arange(a.numel(), dtype=torch.int32))
+    assert int(whole[-1]) == -7
+    tail = buf.view(torch.float32, (4, 8), offset_bytes=first)
+    assert tail.data_ptr() == base + first
+    with pytest.raises(vmm.VmmError, match="exceeds"):
+        buf.view(torch.uint8, (buf.mapped + 1,))
+    with pytest.raises(vmm.VmmError, match="address space was reserved"):
+        buf.grow(buf.reserved + 1)
+    del whole, tail
+    assert buf.shrink(first) == first and buf.chunks == 1   # the second chunk goes back to the device
+    assert torch.equal(buf.view(torch.int32).cpu(), torch.arange(a.numel(), dtype=torch.int32))
+    free_before = torch.cuda.mem_get_info()[0]
+    buf.grow(48 << 20)
+    assert torch.cuda.mem_get_info()[0] <= free_before - (buf.mapped - first) + (1 << 20)
+    del a
+    buf.close()
+    assert torch.cuda.mem_get_info()[0] >= free_before - (1 << 20)

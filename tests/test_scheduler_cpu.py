@@ -126,3 +126,14 @@ def test_sampler_draws_follow_the_filtered_distribution():
     same = cpu.sample(logits[:100], torch.full((100,), temp), torch.full((100,), k, dtype=torch.int32), torch.full((100,), p),
                       torch.zeros(100), u[:100])
     assert torch.equal(same, toks[:100])                        # same uniforms -> same tokens
+
+
+def test_pool_growth_adds_allocatable_pages():
+    from onnx_genai_b200.engine.core import Core, CoreConfig
+
+    core = Core(CoreConfig(num_pages=4, max_seqs=2, max_tokens_per_step=64, max_pages_per_seq=16, enable_prefix_cache=False))
+    assert core.num_pages == 4 and core.num_free_pages == 4
+    core.add_pages(6)
+    assert core.num_pages == 10 and core.num_free_pages == 10
+    core.add_pages(0)
+    assert core.num_pages == 10
