@@ -36,6 +36,25 @@ class LocalComm:
         out.copy_(t.view_as(out))
         return out
 
+    def all_to_all(self, out, t, out_splits=None, in_splits=None):
+        out.copy_(t.view_as(out))
+        return out
+
+    def exchange_counts(self, counts):
+        return [int(c) for c in counts]
+
+    def all_to_all_v(self, t, send_counts, recv_counts=None):
+        return t.clone()
+
+    def send(self, t, dst: int):
+        raise RuntimeError("a world of one has no peer to send to")
+
+    def recv(self, t, src: int):
+        raise RuntimeError("a world of one has no peer to receive from")
+
+    def abort(self, cause: str):
+        pass
+
     def barrier(self):
         pass
 
@@ -84,6 +103,42 @@ class NcclComm:
     def all_to_all(self, out, t, out_splits=None, in_splits=None):
         dist.all_to_all_single(out, t, out_splits, in_splits, group=self.group)
         return out
+
+    def exchange_counts(self, counts):
+        """counts[dst] = rows this rank sends to dst; returns the rows each source sends here."""
+        t = torch.tensor([int(c) for c in counts], dtype=torch.int64, device=self._scalar_device)
+        out = torch.empty_like(t)
+        dist.all_to_all_single(out, t, group=self.group)
+        return out.tolist()
+
+    def all_to_all_v(self, t, send_counts, recv_counts=None):
+        """Variable-size row exchange (expert-parallel dispatch and combine): rows of ``t`` are grouped by destination
+        rank in rank order; returns the rows received, grouped by source rank."""
+        send_counts = [int(c) for c in send_counts]
+        if recv_counts is None:
+            recv_counts = self.exchange_counts(send_counts)
+        recv_counts = [int(c) for c in recv_counts]
+        out = t.new_empty((sum(recv_counts),) + tuple(t.shape[1:]))
+        dist.all_to_all_single(out, t.contiguous(), recv_counts, send_counts, group=self.group)
+        return out
+
+    def send(self, t, dst: int):
+        dist.send(t, dst=dist.get_global_rank(self.group, dst) if self.group is not None else dst, group=self.group)
+
+    def recv(self, t, src: int):
+        dist.recv(t, src=dist.get_global_rank(self.group, src) if self.group is not None else src, group=self.group)
+        return t
+
+    def abort(self, cause: str):
+        """End the group's outstanding and future collectives with an error on this rank (peers reach their timeout)."""
+        self.aborted = cause
+        try:
+            backend = self.group._get_backend(torch.device(self._scalar_device)) if self.group is not None else \
+                dist.distributed_c10d._get_default_group()._get_backend(torch.device(self._scalar_device))
+            if hasattr(backend, "abort"):
+                backend.abort()
+        except Exception:
+            pass
 
     def barrier(self):
         dist.barrier(group=self.group)

@@ -90,6 +90,8 @@ class _Group:
         self.registry = OwnershipRegistry()
         self.members = tuple(range(world))
         self.hash = membership_hash(self.members)
+        self.mail: dict = {}        # (src, dst) -> list of tensors in send order (point-to-point)
+        self.split_lists: dict = {} # sequence number -> {rank: send counts} of a variable-size exchange in flight
 
 
 class InProcessCommunicator:
@@ -127,7 +129,8 @@ class InProcessCommunicator:
     def _rendezvous(self, op, tensor, extra, compute):
         inst = self._next_instance()
         g = self.g
-        desc = (op, str(tensor.dtype), tensor.numel(), g.hash, extra)
+        # variable-size exchanges agree on everything but the element count, which each rank states in its split list
+        desc = (op, str(tensor.dtype), -1 if op == "all_to_all_v" else tensor.numel(), g.hash, None if op == "all_to_all_v" else extra)
         key = tensor.untyped_storage().data_ptr() + tensor.storage_offset() * tensor.element_size()
         with g.cv:
             if g.aborted is not None:
@@ -209,6 +212,66 @@ class InProcessCommunicator:
         res = self._rendezvous("all_to_all", t, None, compute)
         out.copy_(res[self.rank].view_as(out))
         return out
+
+    def all_to_all_v(self, t, send_counts, recv_counts=None):
+        """Variable-size exchange of rows: the first ``send_counts[0]`` rows of ``t`` go to rank 0, the next
+        ``send_counts[1]`` to rank 1, ...  Returns the rows received, ordered by source rank.  ``recv_counts`` (from
+        :meth:`exchange_counts`) is checked when given."""
+        send_counts = [int(c) for c in send_counts]
+        if len(send_counts) != self.world or sum(send_counts) != t.shape[0]:
+            raise ValueError(f"send_counts {send_counts} must have one entry per rank and sum to the {t.shape[0]} rows sent")
+        width = tuple(t.shape[1:])
+
+        def compute(bufs):
+            counts = bufs["counts"]
+            out = {}
+            for dst in range(self.world):
+                parts = []
+                for src in sorted(r for r in bufs if r != "counts"):
+                    lo = sum(counts[src][:dst])
+                    parts.append(bufs[src][lo:lo + counts[src][dst]])
+                out[dst] = torch.cat(parts) if parts else t.new_zeros((0,) + width)
+            return out
+
+        g, seq = self.g, self._seq + 1
+        with g.cv:                                   # every rank files its split list before it joins the rendezvous
+            g.split_lists.setdefault(seq, {})[self.rank] = send_counts
+
+        def wrapped(bufs):
+            merged = dict(bufs)
+            merged["counts"] = g.split_lists.pop(seq)
+            return compute(merged)
+
+        res = self._rendezvous("all_to_all_v", t, width, wrapped)[self.rank].clone()
+        if recv_counts is not None and sum(int(c) for c in recv_counts) != res.shape[0]:
+            raise ValueError(f"received {res.shape[0]} rows but recv_counts {list(recv_counts)} announce {sum(recv_counts)}")
+        return res
+
+    def send(self, t, dst: int):
+        """Point-to-point: hand a copy of ``t`` to rank ``dst`` (matched with its ``recv`` in order)."""
+        g = self.g
+        with g.cv:
+            if g.aborted is not None:
+                raise CommAborted(f"communicator aborted: {g.aborted}")
+            g.mail.setdefault((self.rank, int(dst)), []).append(t.detach().clone())
+            g.cv.notify_all()
+
+    def recv(self, t, src: int):
+        g = self.g
+        key = (int(src), self.rank)
+        with g.cv:
+            ok = g.cv.wait_for(lambda: g.mail.get(key) or g.aborted is not None, timeout=g.timeout)
+            if g.aborted is not None:
+                raise CommAborted(f"communicator aborted: {g.aborted}")
+            if not ok:
+                g.aborted = f"recv on rank {self.rank} from rank {src} timed out after {g.timeout}s: nothing was sent"
+                g.cv.notify_all()
+                raise CommAborted(g.aborted)
+            msg = g.mail[key].pop(0)
+        if msg.shape != t.shape or msg.dtype != t.dtype:
+            raise CollectiveMismatch(f"rank {src} sent {tuple(msg.shape)} {msg.dtype} but rank {self.rank} expected {tuple(t.shape)} {t.dtype}")
+        t.copy_(msg)
+        return t
 
     def exchange_counts(self, counts):
         """counts[dst] = rows this rank sends to dst; returns rows received from each source."""

@@ -39,3 +39,11 @@ def test_four_cpu_ranks_replicate_kv_heads(tmp_path):
     err = float((four["logits"] - single["logits"]).norm() / single["logits"].norm())
     assert err < 1e-4, err
     assert four["tokens"] == single["tokens"]
+
+
+def test_communicator_exchanges_and_expert_dispatch_over_gloo(tmp_path):
+    res = _run(3, "comm-api", str(tmp_path / "c.pt"), 29654)
+    assert res["backend"] == "gloo" and res["world"] == 3
+    assert res["recv"] == [s + 0 + 1 for s in range(3)]                    # what each source sends to rank 0
+    assert res["rows"] == [[s, 0] for s in range(3) for _ in range(s + 1)]
+    assert res["ring"] == 2.0 and res["ep_ok"] == 3

@@ -12,6 +12,43 @@ from onnx_genai_b200.models.config import DecoderConfig
 from onnx_genai_b200.parallel import comm as comm_mod
 
 
+def comm_api(comm, rank, world, dev, out_path):
+    """Variable-size exchange, point-to-point ring and token-sharded expert dispatch over the process group."""
+    from onnx_genai_b200.parallel.ep_dispatch import EpDispatcher
+
+    counts = [rank + d + 1 for d in range(world)]
+    rows = torch.tensor([[rank, d] for d in range(world) for _ in range(counts[d])], dtype=torch.int64, device=dev)
+    recv = comm.exchange_counts(counts)
+    got = comm.all_to_all_v(rows, counts, recv)
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+    token = torch.tensor([float(rank)], device=dev)
+    inbox = torch.zeros(1, device=dev)
+    if rank % 2 == 0:
+        comm.send(token, nxt)
+        comm.recv(inbox, prv)
+    else:
+        comm.recv(inbox, prv)
+        comm.send(token, nxt)
+    torch.manual_seed(0)
+    experts, hid, k, t_per = 3 * world, 16, 2, 9
+    w_exp = (torch.randn(experts, hid, hid) * 0.2).to(dev)
+    hidden = torch.randn(world, t_per, hid).to(dev)
+    ids = torch.stack([torch.stack([torch.randperm(experts)[:k] for _ in range(t_per)]) for _ in range(world)]).to(dev)
+    wts = torch.rand(world, t_per, k).to(dev)
+    d = EpDispatcher(comm, experts)
+    base = rank * d.per_rank
+    mine = d.run(hidden[rank], ids[rank], wts[rank], lambda x, e: torch.tanh(x @ w_exp[base + e]))
+    dense = torch.zeros(t_per, hid, device=dev)
+    for i in range(t_per):
+        for j in range(k):
+            dense[i] += wts[rank, i, j] * torch.tanh(hidden[rank, i] @ w_exp[ids[rank, i, j]])
+    ok = torch.tensor([float(torch.allclose(mine, dense, atol=1e-5))], device=dev)
+    comm.all_reduce(ok)
+    if rank == 0:
+        torch.save({"backend": comm.backend_name, "recv": recv, "rows": got.cpu().tolist(), "ring": float(inbox.item()),
+                    "ep_ok": int(ok.item()), "world": world}, out_path)
+
+
 def main():
     mode, out_path = sys.argv[1], sys.argv[2]
     on_cpu = os.environ.get("OGB_TEST_DEVICE") == "cpu" or not torch.cuda.is_available()
@@ -27,6 +64,8 @@ def main():
         mode = mode[: -len("-moe")]
         cfg = cfg.replace(name="tp-moe", intermediate=0, moe=MoEConfig(num_experts=8, top_k=2, expert_intermediate=256, renormalize=True))
     comm = comm_mod.NcclComm() if world > 1 else None
+    if mode == "comm-api":
+        return comm_api(comm, rank, world, dev, out_path)
     if mode.startswith("fused") and world > 1:
         from onnx_genai_b200.parallel.fused import FusedComm
 
