@@ -259,7 +259,7 @@ class LLMEngine:
     GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512)
 
     def _graph_eligible(self, si, r, hdr) -> bool:
-        return (self.cfg.cuda_graphs and self.device.type == "cuda" and self.tp == 1
+        return (self.cfg.cuda_graphs and self.device.type == "cuda" and self.tp == 1 and not getattr(self.model, "tap_layers", None)
                 and si.num_prefill_seqs == 0 and si.num_tiles == 0 and si.num_decode == si.num_tokens == r and r > 0
                 and r <= min(self.cfg.max_seqs, self.GRAPH_BUCKETS[-1]))
 
@@ -508,7 +508,11 @@ class LLMEngine:
             for sid, proposer in self.proposers.items():
                 key = sid & 0x7FFFFFFF                       # the plan carries sequence ids as int32
                 if getattr(proposer, "wants_hidden", False) and key in first and committed.get(sid):
-                    proposer.observe(self.model.h_last[first[key] + committed[sid] - 1].clone())
+                    row = first[key] + committed[sid] - 1
+                    if getattr(proposer, "tap_layers", None):
+                        proposer.observe(self.model.h_last[row].clone(), {l: self.model.taps[l][row].clone() for l in proposer.tap_layers})
+                    else:
+                        proposer.observe(self.model.h_last[row].clone())
         now = time.perf_counter()
         for sid, tok, fin in events:
             st = self.stats.get(sid)

@@ -374,11 +374,24 @@ class DecoderModel:
         return self.ensure_split_scratch(splits)
 
     # --------------------------------------------------------------------------------------
+    def set_hidden_taps(self, layers) -> None:
+        """Keep, for every logit row of a step, the residual stream entering each of ``layers`` (0 = the embeddings,
+        ``num_layers`` is not allowed: that state is ``h_last`` before its norm).  Draft heads that read intermediate
+        features (EAGLE-3 style) use them.  Taps make the step run layer by layer from Python."""
+        layers = sorted(set(int(l) for l in layers))
+        if any(l < 0 or l >= self.cfg.num_layers for l in layers):
+            raise ValueError(f"tap layers {layers} must lie in [0, {self.cfg.num_layers})")
+        if layers and self.tp != 1:
+            raise ValueError("hidden taps are supported on one GPU only: with tensor parallelism the residual is completed lazily")
+        self.tap_layers = layers
+        self.taps = {l: torch.zeros_like(self.h_last) for l in layers}
+
     def forward(self, si: StepInputs, kv: KVCache) -> torch.Tensor:
         """Runs one step; returns logits [num_logit_rows, vocab] (a view of a static buffer)."""
         cfg, w = self.cfg, self.w
         t, nd = si.num_tokens, si.num_decode
-        if self.native and not si.force_python:
+        tapping = bool(getattr(self, "tap_layers", None))
+        if self.native and not si.force_python and not tapping:
             before = self._native_lib.ogb_decoder_launches(self.native)
             rc = self._native_lib.ogb_decoder_step(
                 self.native, si.token_ids.data_ptr(), si.positions.data_ptr(), si.slots.data_ptr(), si.ctx_len.data_ptr(),
@@ -399,6 +412,8 @@ class DecoderModel:
         for li, lw in enumerate(w.layers):
             pool = kv.pools[li]
             if fused_q:
+                if tapping and li in self.taps:
+                    torch.index_select(x, 0, si.logit_rows[:si.num_logit_rows].long(), out=self.taps[li][:si.num_logit_rows])
                 lw.quant["qkv"][0].fused(x, qkv, norm_weight=lw.ln1, eps=cfg.rms_eps)
                 ops.rope_kv_append(qkv, si.positions[:t], si.slots[:t], self.cos_sin, pool, self.hq, self.hkv, self.d,
                                    self.rotary_dim, cfg.rotary_interleaved,
@@ -418,6 +433,8 @@ class DecoderModel:
                 lw.quant["down"].fused(gu, x, silu_mul=True, residual=x)
                 continue
             self._norm(x, lw.ln1, pending, h)
+            if tapping and li in self.taps:       # the norm has just folded the previous layer's output into x
+                torch.index_select(x, 0, si.logit_rows[:si.num_logit_rows].long(), out=self.taps[li][:si.num_logit_rows])
             if lw.quant:
                 c0 = 0
                 for proj in lw.quant["qkv"]:          # q, k, v MatMulNBits write adjacent column slices

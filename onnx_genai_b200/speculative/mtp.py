@@ -119,6 +119,75 @@ class MtpProposer(SpeculativeProposer):
         return out
 
 
+class Eagle3Head(MtpHead):
+    """EAGLE-3 style head: the draft state starts from a fusion of the target's low-, mid- and high-level features (the
+    residual stream entering three chosen layers) instead of the final hidden state alone, then threads through the
+    same recurrent block as :class:`MtpHead`.  The reference's ``Eagle3Proposer`` concatenates the three taps into its
+    ``fused_hidden`` input in the same order (crates/onnx-genai-engine/src/speculative/mod.rs:886, 1174-1200)."""
+
+    NAMES = MtpHead.NAMES + ("fuse3", "norm_low", "norm_mid", "norm_high")
+
+    def __init__(self, weights: dict, embed, lm_head, tap_layers, eps: float = 1e-6):
+        super().__init__(weights, embed, lm_head, eps)
+        if len(tap_layers) != 3:
+            raise ValueError(f"an EAGLE-3 head reads three layers (low, mid, high), got {list(tap_layers)}")
+        if tuple(weights["fuse3"].shape) != (self.hidden, 3 * self.hidden):
+            raise ValueError(f"fuse3 is {tuple(weights['fuse3'].shape)}; a head for hidden size {self.hidden} needs ({self.hidden}, {3 * self.hidden})")
+        self.tap_layers = [int(l) for l in tap_layers]
+
+    @classmethod
+    def random(cls, embed, lm_head, tap_layers, inter: int | None = None, seed: int = 0, std: float = 0.02) -> "Eagle3Head":
+        hid = embed.shape[1]
+        base = MtpHead.random(embed, lm_head, inter, seed, std)
+        g = torch.Generator().manual_seed(seed + 1)
+        w = {n: t.float().cpu() for n, t in base.w.items()}
+        w.update({"fuse3": torch.randn(hid, 3 * hid, generator=g) * std, "norm_low": torch.ones(hid), "norm_mid": torch.ones(hid),
+                  "norm_high": torch.ones(hid)})
+        return cls(w, embed, lm_head, tap_layers)
+
+    @staticmethod
+    def default_tap_layers(num_layers: int) -> list:
+        """Low, middle and high: after roughly 1/8, 1/2 and 7/8 of the stack."""
+        return sorted({max(1, num_layers // 8), max(1, num_layers // 2), max(1, num_layers - max(1, num_layers // 8))})[:3] \
+            if num_layers >= 4 else [0, max(0, num_layers // 2), num_layers - 1][:3]
+
+    def fuse(self, taps: dict) -> torch.Tensor:
+        """``taps``: layer -> [B, H] residual states; returns the fused draft state [B, H]."""
+        w = self.w
+        lo, mid, hi = (taps[l].to(self.embed.dtype) for l in self.tap_layers)
+        cat = torch.cat([_rms(lo, w["norm_low"], self.eps), _rms(mid, w["norm_mid"], self.eps), _rms(hi, w["norm_high"], self.eps)], dim=-1)
+        return cat @ w["fuse3"].T
+
+
+class Eagle3Proposer(MtpProposer):
+    name = "eagle3"
+
+    def __init__(self, head: Eagle3Head):
+        super().__init__(head)
+        self.tap_layers = head.tap_layers
+        self.taps = None
+
+    @property
+    def batch_key(self):
+        return ("eagle3", id(self.head))
+
+    def observe(self, hidden, taps=None) -> None:
+        if taps is None:
+            raise RuntimeError("the EAGLE-3 proposer needs the target's intermediate states; call model.set_hidden_taps(head.tap_layers)")
+        self.taps = taps
+        self.hidden = self.head.fuse({l: t[None] for l, t in taps.items()})[0]
+
+
+def attach_eagle3(engine, head: Eagle3Head | None = None, tap_layers=None, seed: int = 0) -> Eagle3Head:
+    """Make ``engine`` draft with an EAGLE-3 style head on speculative requests; switches the target's layer taps on."""
+    model = engine.llm.model
+    if head is None:
+        head = Eagle3Head.random(model.w.embed, model.w.lm_head, tap_layers or Eagle3Head.default_tap_layers(model.cfg.num_layers), seed=seed)
+    model.set_hidden_taps(head.tap_layers)
+    engine.proposer_factory = lambda: Eagle3Proposer(head)
+    return head
+
+
 def attach_mtp(engine, head: MtpHead | None = None, seed: int = 0) -> MtpHead:
     """Make ``engine`` (an :class:`onnx_genai_b200.engine.api.Engine`) draft with an MTP head on speculative requests.
     With no head given, a randomly initialised one is made (useful for measuring the mechanism, not acceptance)."""

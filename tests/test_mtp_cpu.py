@@ -106,3 +106,46 @@ def test_a_package_with_an_mtp_head_uses_it(model_dir, tmp_path):  # noqa: F811
     prompt = [3, 1, 4, 1, 5, 9, 2, 6]
     assert eng.generate(prompt, GenerateOptions(max_new_tokens=10, ignore_eos=True, speculative=True)).token_ids == \
         probe.generate(prompt, GenerateOptions(max_new_tokens=10, ignore_eos=True)).token_ids
+
+
+def test_eagle3_head_reads_three_layer_taps_and_keeps_greedy_output(model_dir):  # noqa: F811
+    from onnx_genai_b200.speculative.mtp import Eagle3Head, Eagle3Proposer, attach_eagle3
+
+    big = CFG.replace(num_layers=6)
+    from onnx_genai_b200.models.decoder import random_weights
+    from onnx_genai_b200.package.export import export_package
+    import tempfile
+
+    w = random_weights(big, "cpu", seed=9, std=0.3, dtype=torch.float32)
+    with tempfile.TemporaryDirectory() as tmp:
+        d = export_package(big, w, tmp)
+        plain = _engine(d)
+        spec = _engine(d, max_draft_tokens=3)
+        head = attach_eagle3(spec, seed=4)
+        assert head.tap_layers == [1, 3, 5] and spec.llm.model.tap_layers == [1, 3, 5]
+        assert isinstance(spec.proposer_factory(), Eagle3Proposer)
+        prompt = [9, 8, 7, 6, 5, 4, 3, 2, 1]
+        want = plain.generate(prompt, GenerateOptions(max_new_tokens=14, ignore_eos=True))
+        got = spec.generate(prompt, GenerateOptions(max_new_tokens=14, ignore_eos=True, speculative=True))
+        assert got.token_ids == want.token_ids and got.speculative.proposed_tokens > 0
+        # the taps are the residual stream entering those layers: a model cut after l layers ends with exactly that state
+        import dataclasses
+
+        from onnx_genai_b200.engine.llm_engine import EngineConfig, LLMEngine
+
+        def last_prompt_state(cfg, weights, taps=()):
+            eng = LLMEngine(EngineConfig(model=cfg, num_pages=32, max_seqs=2, max_tokens_per_step=64, max_seq_len=128), weights=weights,
+                            device="cpu")
+            eng.model.set_hidden_taps(taps)
+            eng.add_request(np.asarray(prompt, dtype=np.int32), 1)
+            eng.step()
+            return eng.model
+
+        full = last_prompt_state(big, w, head.tap_layers)
+        for l in head.tap_layers:
+            cut = last_prompt_state(big.replace(num_layers=l), dataclasses.replace(w, layers=w.layers[:l]))
+            assert torch.allclose(full.taps[l][0], cut.x_last[0], atol=1e-5), l
+    with pytest.raises(ValueError, match="three layers"):
+        Eagle3Head.random(torch.randn(10, 8), torch.randn(10, 8), [1, 2])
+    with pytest.raises(ValueError, match="must lie in"):
+        spec.llm.model.set_hidden_taps([6])
