@@ -129,3 +129,84 @@ def test_head_sharding_rules():
     assert shard_heads(32, 8, 4, 1).kv_heads == [2, 3]
     spans = [shard_range(18944, 8, r, 32) for r in range(8)]
     assert spans[0][0] == 0 and spans[-1][1] == 18944 and all(b == spans[i + 1][0] for i, (a, b) in enumerate(spans[:-1]))
+
+
+def _replay_check(log, world, programs):
+    """Independent checker: re-derive what the slot log must be from the ranks' programs alone.  Every rank issues the
+    same ops in the same order, so the log has one entry per program step, sequence numbers 1..n in order, and the
+    op recorded at each slot is the op every rank's program holds there."""
+    assert len({tuple(op for op, _ in p) for p in programs}) == 1, "ranks disagree on the program"
+    ops = [op for op, _ in programs[0]]
+    assert [inst.sequence for inst, _ in log] == list(range(1, len(ops) + 1))
+    assert [op for _, op in log] == ops
+    assert len({inst.execution for inst, _ in log}) == 1
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_seeded_schedule_campaign_is_bitwise_stable_and_replays(seed):
+    """Random programs of collectives run under random per-rank delays: results never depend on thread timing, equal a
+    single-thread evaluation in fixed rank order bit for bit, and the canonical slot log replays."""
+    import random
+    import time
+
+    rng = random.Random(seed)
+    world = rng.choice([2, 3, 4])
+    steps = []
+    for _ in range(12):
+        op = rng.choice(["all_reduce", "all_gather", "reduce_scatter", "broadcast", "all_to_all"])
+        n = world * rng.choice([1, 3, 8])
+        dtype = rng.choice([torch.float32, torch.bfloat16, torch.float16])
+        steps.append((op, (n, dtype, rng.randrange(world))))
+    gen = torch.Generator().manual_seed(seed)
+    data = [[(torch.randn(n, generator=gen) * 3).to(dt) for _op, (n, dt, _s) in steps] for _ in range(world)]
+    delays = [[rng.random() * 0.004 for _ in steps] for _ in range(world)]
+
+    def expect(i, r):
+        op, (n, dt, src) = steps[i]
+        bufs = {q: data[q][i] for q in range(world)}
+        if op == "all_reduce":
+            return InProcessCommunicator._reduce(bufs)
+        if op == "reduce_scatter":
+            return InProcessCommunicator._reduce(bufs).reshape(world, -1)[r]
+        if op == "all_gather":
+            return torch.cat([bufs[q] for q in range(world)])
+        if op == "broadcast":
+            return bufs[src]
+        return torch.cat([bufs[q].reshape(world, -1)[r] for q in range(world)])
+
+    def run_once(delay_table):
+        comms = InProcessCommunicator.create_group(world, timeout=10.0)
+        results, errs = [[None] * len(steps) for _ in range(world)], [None] * world
+
+        def body(r):
+            try:
+                c = comms[r]
+                for i, (op, (n, dt, src)) in enumerate(steps):
+                    time.sleep(delay_table[r][i])
+                    t = data[r][i].clone()
+                    if op == "all_reduce":
+                        results[r][i] = c.all_reduce(t).clone()
+                    elif op == "reduce_scatter":
+                        results[r][i] = c.reduce_scatter(torch.empty(n // world, dtype=dt), t).clone()
+                    elif op == "all_gather":
+                        results[r][i] = c.all_gather(torch.empty(n * world, dtype=dt), t).clone()
+                    elif op == "broadcast":
+                        results[r][i] = c.broadcast(t, src).clone()
+                    else:
+                        results[r][i] = c.all_to_all(torch.empty(n, dtype=dt), t).clone()
+            except Exception as e:
+                errs[r] = e
+
+        threads = [threading.Thread(target=body, args=(r,)) for r in range(world)]
+        [t.start() for t in threads]
+        [t.join() for t in threads]
+        assert errs == [None] * world, errs
+        return results, comms[0].g.log
+
+    first, log = run_once(delays)
+    second, _ = run_once([list(reversed(d)) for d in reversed(delays)])          # a different interleaving
+    for r in range(world):
+        for i in range(len(steps)):
+            assert torch.equal(first[r][i], second[r][i]), (r, i, steps[i][0])
+            assert torch.equal(first[r][i], expect(i, r)), (r, i, steps[i][0])
+    _replay_check(log, world, [steps] * world)
