@@ -405,6 +405,8 @@ class LLMEngine:
             toks = self.core.seq_tokens(sid) if self.core.seq_len(sid) > 0 else None
             if toks is None:
                 continue
+            if getattr(proposer, "wants_sequence", False):   # proposers that read this sequence's KV pages
+                proposer.bind(self, sid)
             key = getattr(proposer, "batch_key", None)
             if key is not None:                              # proposers that can answer together (one draft engine)
                 batches.setdefault(key, []).append((sid, proposer, toks))

@@ -188,6 +188,118 @@ def attach_eagle3(engine, head: Eagle3Head | None = None, tap_layers=None, seed:
     return head
 
 
+class SharedKvHead(MtpHead):
+    """A draft block that attends over the *target's* KV cache instead of keeping one of its own: its query is projected
+    from the draft state, rotated to the draft position, and run through the same paged-attention kernels against the
+    pages of one target layer (by default the last).  No extra cache memory, nothing to rewind.  The reference's
+    shared-KV proposer binds target KV slices to its ``shared_kv.*`` inputs for the same purpose
+    (crates/onnx-genai-engine/src/speculative/mod.rs:890-891)."""
+
+    NAMES = MtpHead.NAMES + ("q_proj", "o_proj", "norm_q")
+
+    def __init__(self, weights: dict, embed, lm_head, num_heads: int, head_dim: int, layer: int = -1, eps: float = 1e-6):
+        super().__init__(weights, embed, lm_head, eps)
+        if tuple(weights["q_proj"].shape) != (num_heads * head_dim, self.hidden):
+            raise ValueError(f"q_proj is {tuple(weights['q_proj'].shape)}; the target's attention needs ({num_heads * head_dim}, {self.hidden})")
+        self.num_heads, self.head_dim, self.layer = num_heads, head_dim, layer
+
+    @classmethod
+    def random(cls, embed, lm_head, num_heads: int, head_dim: int, layer: int = -1, inter: int | None = None, seed: int = 0,
+               std: float = 0.02) -> "SharedKvHead":
+        hid = embed.shape[1]
+        base = MtpHead.random(embed, lm_head, inter, seed, std)
+        g = torch.Generator().manual_seed(seed + 2)
+        w = {n: t.float().cpu() for n, t in base.w.items()}
+        w.update({"q_proj": torch.randn(num_heads * head_dim, hid, generator=g) * std,
+                  "o_proj": torch.randn(hid, num_heads * head_dim, generator=g) * std, "norm_q": torch.ones(hid)})
+        return cls(w, embed, lm_head, num_heads, head_dim, layer)
+
+    @torch.no_grad()
+    def draft_shared(self, hidden, tokens, k: int, llm, page_table, ctx_len) -> torch.Tensor:
+        """As :meth:`MtpHead.draft`, with one attention read of the target's pages per draft position.
+        ``page_table`` [B, P] int32 and ``ctx_len`` [B] int32 describe the computed context of each sequence."""
+        from .. import ops
+        from ..ops import reference
+
+        w, model, kv = self.w, llm.model, llm.kv
+        layer = self.layer % len(kv.pools)
+        pool = kv.pools[layer]
+        scales = kv.scales[layer] if kv.scales is not None else None
+        b, hq, d = hidden.shape[0], self.num_heads, self.head_dim
+        stride = (hq + 2 * model.hkv) * d                          # the attention entry points read q from packed qkv rows
+        qkv = torch.zeros(b, stride, dtype=self.embed.dtype, device=hidden.device)
+        attn = torch.zeros(b, hq * d, dtype=self.embed.dtype, device=hidden.device)
+        h, tok, out = hidden.to(self.embed.dtype), tokens.long(), []
+        for j in range(k):
+            e = self.embed.index_select(0, tok)
+            z = torch.cat([_rms(h, w["norm_h"], self.eps), _rms(e, w["norm_e"], self.eps)], dim=-1) @ w["fuse"].T
+            q = (_rms(z, w["norm_q"], self.eps) @ w["q_proj"].T).view(b, hq, d)
+            pos = (ctx_len.long() + j).clamp(max=model.cos_sin.shape[0] - 1)
+            qkv[:, : hq * d] = reference.apply_rope(q, pos, model.cos_sin, model.rotary_dim, model.cfg.rotary_interleaved).reshape(b, hq * d)
+            ops.paged_decode(qkv, attn, pool, page_table, ctx_len, hq, model.hkv, d, model.scale, kv_scales=scales)
+            z = z + attn[:b] @ w["o_proj"].T
+            m = _rms(z, w["norm_m"], self.eps)
+            z = z + (torch.nn.functional.silu(m @ w["gate"].T) * (m @ w["up"].T)) @ w["down"].T
+            tok = (_rms(z, w["norm_out"], self.eps) @ self.lm_head.T).float().argmax(-1)
+            out.append(tok)
+            h = z
+        return torch.stack(out, dim=1)
+
+
+class SharedKvProposer(MtpProposer):
+    name = "shared_kv"
+    wants_sequence = True
+
+    def __init__(self, head: SharedKvHead):
+        super().__init__(head)
+        self.llm, self.sid = None, None
+
+    @property
+    def batch_key(self):
+        return ("shared_kv", id(self.head))
+
+    def bind(self, llm, sid: int) -> None:
+        self.llm, self.sid = llm, sid
+
+    @staticmethod
+    def propose_many(proposers, token_lists, k):
+        empty = np.zeros(0, dtype=np.int32)
+        live = [i for i, p in enumerate(proposers) if p.hidden is not None and p.llm is not None and len(token_lists[i]) > 1]
+        out = [empty] * len(proposers)
+        if not live or k <= 0:
+            return out
+        llm, head = proposers[live[0]].llm, proposers[live[0]].head
+        # the last token was sampled but not fed yet: the cache holds every token before it
+        ctx = [len(token_lists[i]) - 1 for i in live]
+        pages = [llm.core.seq_pages(proposers[i].sid) for i in live]
+        need = [-(-c // 16) for c in ctx]
+        keep = [j for j in range(len(live)) if len(pages[j]) >= need[j] > 0]
+        if not keep:
+            return out
+        table = np.zeros((len(keep), max(need[j] for j in keep)), dtype=np.int32)
+        for row, j in enumerate(keep):
+            table[row, : need[j]] = pages[j][: need[j]]
+        dev = llm.device
+        hidden = torch.stack([proposers[live[j]].hidden for j in keep])
+        last = torch.tensor([int(token_lists[live[j]][-1]) for j in keep], device=dev)
+        drafts = head.draft_shared(hidden, last, k, llm, torch.from_numpy(table).to(dev),
+                                   torch.tensor([ctx[j] for j in keep], dtype=torch.int32, device=dev)).to("cpu", torch.int32).numpy()
+        for row, j in enumerate(keep):
+            out[live[j]] = drafts[row]
+        return out
+
+
+def attach_shared_kv(engine, head: SharedKvHead | None = None, layer: int = -1, seed: int = 0) -> SharedKvHead:
+    """Make ``engine`` draft with a head that reads the target's own KV pages (one GPU or CPU; not tensor parallel)."""
+    llm = engine.llm
+    if llm.tp != 1:
+        raise ValueError("the shared-KV proposer reads whole KV heads; with tensor parallelism each rank holds a slice")
+    model = llm.model
+    head = head or SharedKvHead.random(model.w.embed, model.w.lm_head, model.hq, model.d, layer, seed=seed)
+    engine.proposer_factory = lambda: SharedKvProposer(head)
+    return head
+
+
 def attach_mtp(engine, head: MtpHead | None = None, seed: int = 0) -> MtpHead:
     """Make ``engine`` (an :class:`onnx_genai_b200.engine.api.Engine`) draft with an MTP head on speculative requests.
     With no head given, a randomly initialised one is made (useful for measuring the mechanism, not acceptance)."""

@@ -245,3 +245,39 @@ def test_kv_pool_grows_in_place_and_results_do_not_change():
     assert [p.data_ptr() for p in eng.kv.pools] == base
     snap = eng.memory.snapshot()["vram"]["by_role"]["kv"]
     assert snap == eng.kv.mapped_bytes() >= eng.kv.num_pages * eng.kv.page_nbytes * CFG128.num_layers
+
+
+def test_shared_kv_proposer_reads_target_pages_on_the_device():
+    """The shared-KV head's attention runs on the paged decode kernel over the target's own pages; a dense restatement
+    over the gathered pages gives the same attention output."""
+    from onnx_genai_b200.ops import reference as ref
+    from onnx_genai_b200.speculative.mtp import SharedKvHead, SharedKvProposer
+
+    w = random_weights(CFG128, "cuda", seed=9, std=0.08)
+    prompt = np.random.default_rng(7).integers(0, CFG128.vocab, size=150).astype(np.int32)
+    eng = LLMEngine(EngineConfig(model=CFG128, num_pages=64, max_seqs=2, max_tokens_per_step=512, max_seq_len=512,
+                                 max_draft_tokens=2, enable_prefix_cache=False), weights=w, device="cuda")
+    head = SharedKvHead.random(w.embed, w.lm_head, eng.model.hq, eng.model.d, seed=3, std=0.05)
+    sid = eng.add_request(prompt, 6)
+    prop = eng.proposers[sid] = SharedKvProposer(head)
+    got = []
+    while eng.has_work:
+        got += [tok for s, tok, fin in eng.step().events if s == sid]
+    ops.check_status()
+    assert len(got) == 6 and eng.core.spec_proposed >= 2 and prop.llm is eng
+    # one attention read against a dense computation
+    sid = eng.add_request(prompt, 2)
+    eng.step()
+    ctx = len(prompt)
+    pages = eng.core.seq_pages(sid)[: -(-ctx // 16)]
+    m = eng.model
+    q = torch.randn(1, (m.hq + 2 * m.hkv) * m.d, device="cuda").bfloat16()
+    out = torch.zeros(1, m.hq * m.d, device="cuda", dtype=torch.bfloat16)
+    ops.paged_decode(q, out, eng.kv.pools[-1], torch.from_numpy(pages[None].copy()).cuda(), torch.tensor([ctx], dtype=torch.int32, device="cuda"),
+                     m.hq, m.hkv, m.d, m.scale)
+    torch.cuda.synchronize()
+    k_all, v_all = ref._gather_kv(eng.kv.pools[-1], torch.from_numpy(pages).cuda(), ctx)
+    g = m.hq // m.hkv
+    qh = q[0, : m.hq * m.d].float().view(m.hq, m.d)
+    want = torch.cat([torch.softmax((qh[h] @ k_all[h // g].T) * m.scale, -1) @ v_all[h // g] for h in range(m.hq)])
+    assert float((out[0].float() - want).norm() / want.norm()) < 2e-2

@@ -149,3 +149,49 @@ def test_eagle3_head_reads_three_layer_taps_and_keeps_greedy_output(model_dir): 
         Eagle3Head.random(torch.randn(10, 8), torch.randn(10, 8), [1, 2])
     with pytest.raises(ValueError, match="must lie in"):
         spec.llm.model.set_hidden_taps([6])
+
+
+def test_shared_kv_head_attends_over_the_targets_pages(model_dir):  # noqa: F811
+    from onnx_genai_b200.ops import reference
+    from onnx_genai_b200.speculative.mtp import SharedKvHead, SharedKvProposer, attach_shared_kv
+
+    plain = _engine(model_dir)
+    spec = _engine(model_dir, max_draft_tokens=2)
+    head = attach_shared_kv(spec, seed=6)
+    assert isinstance(spec.proposer_factory(), SharedKvProposer) and head.layer == -1
+    prompt = list(range(40, 75))                                   # 35 tokens: more than two pages of context
+    want = plain.generate(prompt, GenerateOptions(max_new_tokens=10, ignore_eos=True))
+    got = spec.generate(prompt, GenerateOptions(max_new_tokens=10, ignore_eos=True, speculative=True))
+    assert got.token_ids == want.token_ids and got.speculative.proposed_tokens > 0
+    # the attention read is the target's own: drafting from a dense restatement over the gathered pages gives the same tokens
+    llm = spec.llm
+    sid = llm.add_request(np.asarray(prompt, dtype=np.int32), 4, temperature=0.0, ignore_eos=True)
+    prop = llm.proposers[sid] = SharedKvProposer(head)
+    llm.step()                                                     # prefill: one token sampled, 35 tokens cached
+    toks = llm.core.seq_tokens(sid)
+    prop.bind(llm, sid)
+    drafts = SharedKvProposer.propose_many([prop], [toks], 2)[0]
+    ctx = len(toks) - 1
+    pages = llm.core.seq_pages(sid)[: -(-ctx // 16)]
+    k_all, v_all = reference._gather_kv(llm.kv.pools[-1], torch.from_numpy(pages), ctx)
+    w, m = head.w, llm.model
+    rms = lambda x: x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6)
+    h, tok, mine = prop.hidden[None].float(), int(toks[-1]), []
+    for j in range(2):
+        z = torch.cat([rms(h), rms(m.w.embed[tok][None].float())], -1) @ w["fuse"].T
+        q = reference.apply_rope((rms(z) @ w["q_proj"].T).view(1, m.hq, m.d), torch.tensor([ctx + j]), m.cos_sin, m.rotary_dim)[0]
+        g = m.hq // m.hkv
+        o = torch.cat([torch.softmax((q[hh] @ k_all[hh // g].T) * m.scale, -1) @ v_all[hh // g] for hh in range(m.hq)])
+        z = z + o[None] @ w["o_proj"].T
+        mm = rms(z)
+        z = z + (torch.nn.functional.silu(mm @ w["gate"].T) * (mm @ w["up"].T)) @ w["down"].T
+        tok = int((rms(z) @ m.w.lm_head.T.float()).argmax())
+        mine.append(tok)
+        h = z
+    assert drafts.tolist() == mine
+    llm.core.release(sid)
+    llm.proposers.pop(sid, None)
+    with pytest.raises(ValueError, match="q_proj is"):
+        SharedKvHead.random(torch.randn(10, 8), torch.randn(10, 8), 2, 4).__class__(
+            {**{n: torch.zeros(1) for n in SharedKvHead.NAMES}, "fuse": torch.zeros(8, 16), "gate": torch.zeros(4, 8),
+             "q_proj": torch.zeros(3, 8)}, torch.randn(10, 8), torch.randn(10, 8), 2, 4)
