@@ -41,6 +41,13 @@ def _add_engine(p):
     p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3fn", "int8"])
     p.add_argument("--max-batch", type=int, default=32)
     p.add_argument("--vram-limit", default="0.85", help="0.85 (fraction of the device the engine may fill), auto, or a size such as 8GiB for weights + activations + KV")
+    p.add_argument("--kv-max-pages", type=int, default=0, help="reserve address space for this many KV pages and back them on demand (CUDA, one GPU)")
+    p.add_argument("--host-ram-limit", default="auto", help="cap on pinned host memory for KV swap and the KV offload host tier: auto, a size such as 32GiB, or a fraction of RAM")
+    p.add_argument("--cpu-cores", type=int, default=0, help="threads for CPU kernels and host-side work (0: leave as is)")
+    p.add_argument("--draft-model", default="", help="directory of a smaller model that drafts for speculative requests")
+    p.add_argument("--draft-tokens", type=int, default=4, help="draft tokens per verification step when speculation is on")
+    p.add_argument("--proposer", default="auto", choices=["auto", "ngram", "draft", "mtp", "eagle3", "shared-kv"],
+                   help="who drafts for speculative requests (auto: the draft model if given, a packaged MTP head, else prompt lookup)")
     p.add_argument("--kv-offload-dir", default="", help="keep the K/V of finished prompts in host memory and this directory; restored on prefix hits")
     p.add_argument("--kv-offload-host-gib", type=float, default=4.0)
     p.add_argument("--kv-offload-disk-gib", type=float, default=64.0)
@@ -61,7 +68,8 @@ def _options(args):
         constraint = ("json_object",)
     return GenerateOptions(max_new_tokens=args.max_new_tokens, temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
                            min_p=args.min_p, repetition_penalty=args.repetition_penalty, seed=args.seed,
-                           greedy=args.greedy or args.temperature == 0, stop=tuple(args.stop), speculative=args.speculative,
+                           greedy=args.greedy or args.temperature == 0, stop=tuple(args.stop),
+                           speculative=args.speculative or getattr(args, "proposer", "auto") != "auto" or bool(getattr(args, "draft_model", "")),
                            constraint=constraint)
 
 
@@ -80,14 +88,41 @@ def _load(args):
         limit = None
     except ValueError:
         util, limit = 0.85, (None if args.vram_limit == "auto" else args.vram_limit)
+    if getattr(args, "cpu_cores", 0) > 0:
+        torch.set_num_threads(args.cpu_cores)
+        os.environ["OMP_NUM_THREADS"] = str(args.cpu_cores)
+    proposer = getattr(args, "proposer", "auto")
+    speculative = getattr(args, "speculative", False) or proposer != "auto" or bool(getattr(args, "draft_model", ""))
+    if proposer == "draft" and not getattr(args, "draft_model", ""):
+        raise SystemExit("--proposer draft needs --draft-model DIR")
+    extra = {"kv_max_pages": args.kv_max_pages} if getattr(args, "kv_max_pages", 0) > 0 else {}
     eng = Engine.from_dir(args.model, device=dev, max_seqs=args.max_batch, kv_dtype={"fp8_e4m3fn": "fp8", "int8": "int8"}.get(args.kv_cache_dtype, "bf16"),
                           gpu_memory_utilization=util if 0 < util <= 1 else 0.85, vram_limit=limit,
-                          max_draft_tokens=4 if getattr(args, "speculative", False) else 0,
-                          max_seq_len=args.max_context or None)
+                          max_draft_tokens=getattr(args, "draft_tokens", 4) if speculative else 0,
+                          draft_model_dir=(getattr(args, "draft_model", "") or None) if proposer in ("auto", "draft") else None,
+                          max_seq_len=args.max_context or None, **extra)
+    if proposer == "ngram":
+        from .speculative import NgramProposer
+
+        eng.proposer_factory = NgramProposer
+    elif proposer in ("mtp", "eagle3", "shared-kv"):
+        from .speculative import mtp as heads
+
+        {"mtp": heads.attach_mtp, "eagle3": heads.attach_eagle3, "shared-kv": heads.attach_shared_kv}[proposer](eng)
+    host_limit = None
+    if getattr(args, "host_ram_limit", "auto") not in ("", "auto"):
+        from .engine.memory import parse_limit
+
+        total = os.sysconf("SC_PAGE_SIZE") * os.sysconf("SC_PHYS_PAGES")
+        host_limit = parse_limit(args.host_ram_limit, total)
+        eng.llm.memory.limits["host"] = host_limit
     if getattr(args, "kv_offload_dir", ""):
         from .engine.kv_connector import LocalTieredConnector
 
-        eng.attach_kv_connector(LocalTieredConnector(args.kv_offload_dir, max_host_bytes=int(args.kv_offload_host_gib * (1 << 30)),
+        host_bytes = int(args.kv_offload_host_gib * (1 << 30))
+        if host_limit is not None:       # the offload tier lives inside what the host limit leaves
+            host_bytes = min(host_bytes, max(0, host_limit - eng.llm.memory.used("host")))
+        eng.attach_kv_connector(LocalTieredConnector(args.kv_offload_dir, max_host_bytes=host_bytes,
                                                      max_disk_bytes=int(args.kv_offload_disk_gib * (1 << 30))))
     return eng
 
@@ -176,24 +211,49 @@ def cmd_serve(args, profiler):
     host, _, port = args.addr.rpartition(":")
     app_kw = dict(max_output_tokens=args.max_output_tokens, max_queue_depth=args.max_queue_depth,
                   enable_debug_endpoints=args.enable_debug_endpoints, node_id=args.node_id,
-                  admission_window_ms=args.admission_window_ms)
-    if args.models_dir:
+                  admission_window_ms=args.admission_window_ms, default_reasoning_effort=args.default_reasoning_effort or None)
+    if args.models_dir or args.models_config:
         import copy
 
         from .server.registry import ModelRegistry, RegistryApp
 
+        per_model: dict = {}
+
         def loader(path):
             a = copy.copy(args)
             a.model = path
+            for key, value in per_model.get(path, {}).items():       # per-model overrides of the engine flags
+                setattr(a, key.replace("-", "_"), value)
             return _load(a)
 
-        reg = ModelRegistry.from_dir(args.models_dir, max_loaded=args.max_loaded_models, loader=loader, **app_kw)
+        if args.models_config:
+            import yaml
+
+            with open(args.models_config, encoding="utf-8") as f:
+                doc = yaml.safe_load(f) or {}
+            entries = doc.get("models") or {}
+            if not entries:
+                print(f"serve: {args.models_config} lists no models (expected `models: {{name: {{path: DIR}}}}`)", file=sys.stderr)
+                return 2
+            base = os.path.dirname(os.path.abspath(args.models_config))
+            found = {}
+            for name, spec in entries.items():
+                spec = {"path": spec} if isinstance(spec, str) else dict(spec or {})
+                if "path" not in spec:
+                    print(f"serve: model {name!r} in {args.models_config} has no path", file=sys.stderr)
+                    return 2
+                path = os.path.normpath(os.path.join(base, spec.pop("path")))
+                found[name] = path
+                per_model[path] = spec
+            reg = ModelRegistry(found, max_loaded=args.max_loaded_models, loader=loader, **app_kw)
+        else:
+            reg = ModelRegistry.from_dir(args.models_dir, max_loaded=args.max_loaded_models, loader=loader, **app_kw)
         if args.model:
             reg.warmup([os.path.basename(os.path.abspath(args.model))])
         app = RegistryApp(reg, enable_admin_endpoints=args.enable_admin_endpoints)
     else:
         if not args.model:
-            print("serve: give a model directory or --models-dir", file=sys.stderr)
+            print("serve: give a model directory, --models-dir or --models-config", file=sys.stderr)
             return 2
         eng = _load(args)
         app = create_app(eng, model_name=os.path.basename(os.path.abspath(args.model)), **app_kw)
@@ -365,6 +425,9 @@ def main(argv=None):
     s.add_argument("--enable-debug-endpoints", action="store_true")
     s.add_argument("--enable-admin-endpoints", action="store_true", help="with --models-dir: /v1/admin/models load / warmup / unload")
     s.add_argument("--node-id", default="node-0")
+    s.add_argument("--default-reasoning-effort", default="", choices=["", "low", "medium", "high"],
+                   help="reasoning effort handed to chat templates that take one, when a request names none")
+    s.add_argument("--models-config", default="", help="YAML or JSON file: models: {name: {path: DIR, ...engine flags}}")
     s.add_argument("--max-context", type=int, default=0)
     _add_engine(s)
     sh = sub.add_parser("show")

@@ -206,7 +206,8 @@ def _options_from_request(body: dict, default_max: int, max_cap: int) -> Generat
 
 
 def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int = 4096, max_queue_depth: int = 256,
-               enable_debug_endpoints: bool = False, node_id: str = "node-0", admission_window_ms: float = 2.0) -> FastAPI:
+               enable_debug_endpoints: bool = False, node_id: str = "node-0", admission_window_ms: float = 2.0,
+               default_reasoning_effort: str | None = None) -> FastAPI:
     app = FastAPI(title="onnx-genai-b200")
     driver = EngineDriver(engine, max_queue_depth, admission_window_ms)
     metrics = Metrics()
@@ -401,7 +402,12 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
                 norm = tool_calls.inject_tool_prompt(norm, tools, body.get("tool_choice"))
             if body.get("response_format", {}).get("type") in ("json_object", "json_schema"):
                 norm = norm + [{"role": "system", "content": "Respond with a single valid JSON object and nothing else."}]
-            text = engine.apply_chat_template(norm, add_generation_prompt=True, tools=tools)
+            # templates that take a reasoning effort (low / medium / high) read it as a variable; others ignore it
+            effort = body.get("reasoning_effort") or default_reasoning_effort
+            if effort is not None and effort not in ("low", "medium", "high"):
+                raise HTTPException(400, f"reasoning_effort must be low, medium or high, not {effort!r}")
+            text = engine.apply_chat_template(norm, add_generation_prompt=True, tools=tools,
+                                              **({"reasoning_effort": effort} if effort else {}))
         else:
             text = body.get("prompt")
             if isinstance(text, list):

@@ -53,3 +53,23 @@ def test_validate_reports_problems_and_exit_code(tmp_path):
     assert bad.returncode == 1 and not report["ok"] and "31999" in report["problems"][0]
     missing = subprocess.run([_sys.executable, "-m", "onnx_genai_b200", "validate", str(tmp_path / "nope")], capture_output=True, text=True)
     assert missing.returncode == 1 and "not a directory" in missing.stdout
+
+
+@pytest.mark.parametrize("proposer", ["ngram", "mtp", "eagle3", "shared-kv"])
+def test_generate_with_each_proposer_keeps_the_greedy_text(pkg_dir, proposer):
+    base = [sys.executable, "-m", "onnx_genai_b200", "generate", pkg_dir, "--prompt", "hello hello hello", "--max-new-tokens", "8",
+            "--greedy", "--device", "cpu", "--raw"]
+    plain = subprocess.run(base, capture_output=True, text=True)
+    spec = subprocess.run(base + ["--proposer", proposer, "--draft-tokens", "3", "--cpu-cores", "2", "--host-ram-limit", "2GiB"],
+                          capture_output=True, text=True)
+    assert plain.returncode == 0 and spec.returncode == 0, spec.stderr
+    assert spec.stdout == plain.stdout
+
+
+def test_proposer_draft_needs_a_draft_model(pkg_dir):
+    r = subprocess.run([sys.executable, "-m", "onnx_genai_b200", "generate", pkg_dir, "--prompt", "x", "--proposer", "draft", "--device", "cpu"],
+                       capture_output=True, text=True)
+    assert r.returncode != 0 and "--draft-model" in r.stderr
+    ok = subprocess.run([sys.executable, "-m", "onnx_genai_b200", "generate", pkg_dir, "--prompt", "hello", "--max-new-tokens", "4", "--greedy",
+                         "--device", "cpu", "--draft-model", pkg_dir], capture_output=True, text=True)
+    assert ok.returncode == 0, ok.stderr

@@ -96,3 +96,65 @@ def test_admin_endpoints_and_media_routes(dirs):
         assert r.status_code == 501 and "decoder-only text models" in r.text
         assert client.post("/v1/images/generations", json={"model": "beta", "prompt": "x"}).status_code == 501
         assert "stages" in client.get("/v1/debug/trace?model=beta").json()
+
+
+def test_reasoning_effort_reaches_the_chat_template_and_is_validated(tmp_path):
+    import torch
+    from fastapi.testclient import TestClient
+
+    from onnx_genai_b200.engine.api import Engine
+    from onnx_genai_b200.models.config import DecoderConfig
+    from onnx_genai_b200.models.decoder import random_weights
+    from onnx_genai_b200.package.export import export_package
+    from onnx_genai_b200.server.app import create_app
+
+    cfg = DecoderConfig(name="t", num_layers=1, hidden=64, num_heads=4, num_kv_heads=2, head_dim=16, intermediate=96, vocab=300,
+                        rope_theta=1e4, tie_embeddings=True, max_position=512)
+    d = export_package(cfg, random_weights(cfg, "cpu", seed=5, std=0.3, dtype=torch.float32), str(tmp_path / "pkg"))
+    eng = Engine.from_dir(d, device="cpu", num_pages=64, max_seqs=4, max_tokens_per_step=128)
+    eng.chat_template = ("{% if reasoning_effort is defined %}effort={{ reasoning_effort }}\n{% endif %}"
+                         "{% for m in messages %}{{ m['content'] }}\n{% endfor %}")
+    seen = []
+    real = eng.apply_chat_template
+    eng.apply_chat_template = lambda *a, **k: seen.append(real(*a, **k)) or seen[-1]
+    with TestClient(create_app(eng, model_name="tiny", default_reasoning_effort="low")) as c:
+        body = {"model": "tiny", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 2, "temperature": 0}
+        assert c.post("/v1/chat/completions", json=body).status_code == 200
+        assert c.post("/v1/chat/completions", json={**body, "reasoning_effort": "high"}).status_code == 200
+        r = c.post("/v1/chat/completions", json={**body, "reasoning_effort": "extreme"})
+        assert r.status_code == 400 and "low, medium or high" in r.text
+    assert seen[0].startswith("effort=low") and seen[1].startswith("effort=high")
+
+
+def test_serve_reads_a_models_config_with_per_model_flags(tmp_path, monkeypatch):
+    import subprocess
+    import sys
+
+    import uvicorn
+    import yaml
+
+    from onnx_genai_b200 import cli
+
+    a, b = str(tmp_path / "a"), str(tmp_path / "b")
+    for out in (a, b):
+        r = subprocess.run([sys.executable, "-m", "onnx_genai_b200", "export", "--preset", "tiny-llama", "--layers", "1", "--out", out],
+                           capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+    cfg = tmp_path / "models.yaml"
+    cfg.write_text(yaml.safe_dump({"models": {"small": "a", "quantised-kv": {"path": "b", "kv-cache-dtype": "int8", "max-batch": 3}}}, sort_keys=False))
+    captured = {}
+    monkeypatch.setattr(uvicorn, "run", lambda app, **kw: captured.update(app=app, **kw))
+    assert cli.main(["serve", "--models-config", str(cfg), "--device", "cpu", "--addr", "127.0.0.1:0", "--max-loaded-models", "2"]) == 0
+    reg = captured["app"].registry
+    assert reg.names() == ["small", "quantised-kv"]
+    entry = reg.acquire("quantised-kv")
+    try:
+        assert entry["engine"].llm.cfg.kv_dtype == "int8" and entry["engine"].llm.cfg.max_seqs == 3
+    finally:
+        reg.release(entry)
+    small = reg.acquire("small")
+    assert small["engine"].llm.cfg.kv_dtype == "bf16"
+    reg.release(small)
+    empty = tmp_path / "empty.yaml"
+    empty.write_text("models: {}\n")
+    assert cli.main(["serve", "--models-config", str(empty), "--device", "cpu"]) == 2
