@@ -38,6 +38,9 @@ def _add_sampling(p):
 
 def _add_engine(p):
     p.add_argument("--device", default="auto", help="auto | cpu | cuda[:N]")
+    p.add_argument("--backend", default="native", choices=["native", "graph"],
+                   help="native: this package's kernels and scheduler; graph: interpret the ONNX graph node by node "
+                        "(any decoder architecture, `generate` only, one sequence)")
     p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3fn", "int8"])
     p.add_argument("--max-batch", type=int, default=32)
     p.add_argument("--vram-limit", default="0.85", help="0.85 (fraction of the device the engine may fill), auto, or a size such as 8GiB for weights + activations + KV")
@@ -139,7 +142,52 @@ def _stats_line(res):
             f"finish {res.finish_reason}]")
 
 
+def _generate_on_graph_backend(args) -> int:
+    """``--backend graph``: run the model's ONNX graph node by node (any decoder architecture, one sequence, library
+    tensor operations) with the host processor chain and samplers."""
+    import numpy as np
+
+    from . import package as pkg
+    from .engine import processors as procs
+    from .engine.graph_decode import GraphDecodeSession
+
+    sess = GraphDecodeSession.from_dir(args.model, "cuda" if args.device.startswith("cuda") else "cpu")
+    tok_path = os.path.join(args.model, "tokenizer.json")
+    if not os.path.exists(tok_path):
+        tok_path = pkg.open_model_directory(args.model).tokenizer_path
+    if not tok_path:
+        print("generate --backend graph: the model directory has no tokenizer.json", file=sys.stderr)
+        return 2
+    from tokenizers import Tokenizer
+
+    tok = Tokenizer.from_file(tok_path)
+    prompt = args.prompt if args.prompt is not None else sys.stdin.read()
+    ids = tok.encode(prompt, add_special_tokens=False).ids
+    opt = _options(args)
+    chain = procs.build_processor_chain(opt, len(ids))
+    sampler = procs.GreedySampler() if opt.greedy else procs.CategoricalSampler()
+    rng = np.random.default_rng(opt.seed or None)
+    t0 = time.perf_counter()
+    logits = sess.feed(ids)[-1]
+    ttft, out = time.perf_counter() - t0, []
+    for _ in range(opt.max_new_tokens):
+        row = chain.process(np.asarray(sess.tokens), logits.cpu().numpy().astype(np.float32))
+        out.append(sampler.sample(row, float(rng.random())))
+        sys.stdout.write(tok.decode(out)[len(tok.decode(out[:-1])):])
+        sys.stdout.flush()
+        if len(out) == opt.max_new_tokens:
+            break
+        logits = sess.feed([out[-1]])[-1]
+    sys.stdout.write("\n")
+    total = time.perf_counter() - t0
+    print(f"[{len(out)} tok | TTFT {ttft * 1e3:.1f} ms | decode {max(len(out) - 1, 0) / max(total - ttft, 1e-9):.1f} tok/s | backend graph]",
+          file=sys.stderr)
+    return 0
+
+
 def cmd_generate(args, profiler):
+    if getattr(args, "backend", "native") == "graph":
+        return _generate_on_graph_backend(args)
     eng = _load(args)
     prompt = args.prompt if args.prompt is not None else sys.stdin.read()
     t_lat = []

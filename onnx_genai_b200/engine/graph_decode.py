@@ -1,0 +1,124 @@
+"""Decode loop over the generic graph executor: any decoder ONNX graph with past / present KV tensors, no lowering.
+
+The engine's fast path recognises Llama-style decoder graphs and runs them on its own kernels.  A graph it does not
+recognise -- another architecture, or an exporter's idiom the pattern matcher has not met -- can still be served
+through this session: the graph runs node by node (:class:`GraphExecutor`), and the session threads the KV tensors
+from each call's ``present.*`` outputs into the next call's ``past_key_values.*`` inputs, as the reference's dynamic
+past / present decode session does on its ONNX Runtime backend
+(crates/onnx-genai-ort/src/decode/mod.rs; the `model.io` block of the inference metadata names the ports).
+It is also the independent oracle for the fast path: same package, different executor, same greedy tokens.
+
+Throughput is whatever library tensor operations give; nothing here is tuned, and batch size is one sequence.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..package.graph_executor import _TORCH_DTYPE, GraphExecutor
+
+
+class GraphDecodeSession:
+    def __init__(self, model, device="cpu", io: dict | None = None, dtype=None):
+        """``model``: path or parsed model.  ``io`` (optional) names the ports: token_input, attention_mask_input,
+        position_ids_input, logits_output, kv_inputs, kv_outputs -- the ``model.io`` block; by default they are found by
+        the usual names (``input_ids``, ``attention_mask``, ``position_ids``, ``logits``, ``past*`` / ``present*``)."""
+        self.ex = model if isinstance(model, GraphExecutor) else GraphExecutor(model, device, dtype)
+        g = self.ex.model.graph
+        io = dict(io or {})
+        names = self.ex.input_names
+        self.token_in = io.get("token_input") or next((n for n in names if n in ("input_ids", "tokens")), None)
+        if self.token_in is None:
+            raise ValueError(f"cannot tell which of the inputs {names} takes token ids; pass io={{'token_input': ...}}")
+        self.mask_in = io.get("attention_mask_input") or ("attention_mask" if "attention_mask" in names else None)
+        self.pos_in = io.get("position_ids_input") or ("position_ids" if "position_ids" in names else None)
+        self.logits_out = io.get("logits_output") or ("logits" if "logits" in self.ex.output_names else self.ex.output_names[0])
+        self.kv_in = list(io.get("kv_inputs") or [n for n in names if n.startswith(("past", "key_cache", "value_cache"))])
+        self.kv_out = list(io.get("kv_outputs") or [n for n in self.ex.output_names if n.startswith("present")])
+        if len(self.kv_in) != len(self.kv_out):
+            raise ValueError(f"{len(self.kv_in)} KV inputs but {len(self.kv_out)} KV outputs; name them in io")
+        extra = [n for n in names if n not in {self.token_in, self.mask_in, self.pos_in, *self.kv_in}]
+        if extra:
+            raise ValueError(f"the graph has inputs this session does not know how to feed: {extra}")
+        self.info = {vi.name: vi for vi in g.inputs}
+        self.reset()
+
+    def reset(self) -> None:
+        self.tokens: list = []
+        self.past = {}
+        for name in self.kv_in:
+            vi = self.info[name]
+            shape, seq_axis = [], None
+            for axis, dim in enumerate(vi.shape):
+                if isinstance(dim, int):
+                    shape.append(dim)
+                elif axis == 0:
+                    shape.append(1)                                  # batch
+                else:
+                    shape.append(0)                                  # the past length
+                    seq_axis = axis
+            self.past[name] = torch.zeros(shape, dtype=_TORCH_DTYPE.get(vi.elem_type, torch.float32), device=self.ex.device)
+            self.seq_axis = seq_axis if seq_axis is not None else 2
+
+    @property
+    def length(self) -> int:
+        return len(self.tokens)
+
+    def feed(self, token_ids) -> torch.Tensor:
+        """Append tokens; returns the logits of every fed position [n, vocab]."""
+        ids = [int(t) for t in token_ids]
+        if not ids:
+            raise ValueError("feed needs at least one token")
+        past_len = self.length
+        feeds = {self.token_in: torch.tensor([ids], dtype=torch.int64)}
+        if self.mask_in:
+            feeds[self.mask_in] = torch.ones(1, past_len + len(ids), dtype=torch.int64)
+        if self.pos_in:
+            feeds[self.pos_in] = torch.arange(past_len, past_len + len(ids), dtype=torch.int64)[None]
+        feeds.update(self.past)
+        out = self.ex.run(feeds, [self.logits_out, *self.kv_out])
+        for src, dst in zip(self.kv_out, self.kv_in):
+            self.past[dst] = out[src]
+        self.tokens += ids
+        return out[self.logits_out][0].float()
+
+    def rewind(self, new_len: int) -> None:
+        if not 0 <= new_len <= self.length:
+            raise ValueError(f"cannot rewind to {new_len}: the session holds {self.length} tokens")
+        self.tokens = self.tokens[:new_len]
+        for name, t in self.past.items():
+            self.past[name] = t.narrow(self.seq_axis, 0, new_len).contiguous()
+
+    def generate(self, prompt, max_new_tokens: int, eos_token_ids=(), sampler=None) -> list:
+        """Greedy by default; ``sampler(logits [vocab] numpy) -> token`` replaces the argmax."""
+        logits = self.feed(prompt)[-1]
+        out = []
+        for _ in range(max_new_tokens):
+            tok = int(sampler(logits.cpu().numpy())) if sampler is not None else int(torch.argmax(logits))
+            out.append(tok)
+            if tok in eos_token_ids:
+                break
+            logits = self.feed([tok])[-1]
+        return out
+
+    @classmethod
+    def from_dir(cls, model_dir: str, device="cpu") -> "GraphDecodeSession":
+        """A model directory or package (binary or text-format ONNX); ports come from its ``model.io`` block when it has one."""
+        import os
+
+        from .. import package as pkg
+        from ..package.onnx_text import load_any
+
+        text = os.path.join(model_dir, "model.onnx.textproto")
+        if os.path.exists(text):
+            path, meta_path = text, os.path.join(model_dir, "inference_metadata.yaml")
+        else:
+            d = pkg.open_model_directory(model_dir)
+            path, meta_path = d.model_path, d.metadata_path
+        io = None
+        if meta_path and os.path.exists(meta_path):
+            import yaml
+
+            with open(meta_path, encoding="utf-8") as f:
+                io = ((yaml.safe_load(f) or {}).get("model") or {}).get("io")
+        return cls(load_any(path), device, io)

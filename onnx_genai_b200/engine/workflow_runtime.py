@@ -93,6 +93,37 @@ class WorkflowSession:
         self.session_cells: dict = {}
         self.stats = {"runs": 0, "invocations": {}, "iterations": 0}
 
+    @classmethod
+    def from_package(cls, package_dir: str, device="cpu", dtype=None, components: dict | None = None, metadata_name: str = "inference_metadata.yaml"):
+        """Bind every ONNX component of a package directory to the generic graph executor (binary ``.onnx`` or text
+        ``.onnx.textproto`` artifacts, resolved against the directory); ``components`` supplies or overrides bindings --
+        needed for components that are not ONNX graphs (adapters named by an ABI) and for a decoder that should run on
+        the engine instead."""
+        import os
+
+        import yaml
+
+        from ..package.graph_executor import as_component
+        from ..package.onnx_text import load_any
+
+        with open(os.path.join(package_dir, metadata_name), encoding="utf-8") as f:
+            doc = yaml.safe_load(f)
+        wf = wfm.load_document(doc)
+        if wf is None:
+            raise WorkflowRuntimeError(f"{package_dir}/{metadata_name} has no pipeline.workflow")
+        bound = dict(components or {})
+        for name, comp in wf.components.items():
+            if name in bound:
+                continue
+            if comp.kind != "onnx" or not comp.artifact:
+                raise WorkflowRuntimeError(f"component '{name}' is a '{comp.kind}' implementation, not an ONNX graph: pass a callable for it "
+                                           "in `components`")
+            path = os.path.join(package_dir, comp.artifact)
+            if not os.path.exists(path):
+                raise WorkflowRuntimeError(f"component '{name}': artifact {path} does not exist")
+            bound[name] = as_component(load_any(path), device, dtype)
+        return cls(wf, bound)
+
     def _invoked(self, steps):
         for s in steps:
             if s.kind == "invoke":
@@ -122,11 +153,23 @@ class WorkflowSession:
         unknown = sorted(set(inputs) - set(self.wf.inputs))
         if unknown:
             raise WorkflowRuntimeError(f"unknown input(s) {', '.join(unknown)}; the workflow declares {', '.join(sorted(self.wf.inputs))}")
+        # rows of the request: the leading extent of the first supplied input whose contract starts with a symbolic dimension
+        self._batch = 1
+        for name, spec in self.wf.inputs.items():
+            shape = spec["contract"].shape
+            if name in inputs and shape and isinstance(shape[0], str) and hasattr(inputs[name], "shape") and len(inputs[name].shape):
+                self._batch = int(inputs[name].shape[0])
+                break
         for name, spec in self.wf.inputs.items():
             if name in inputs:
                 root.set(name, inputs[name])
             elif spec.get("default") is not None:
-                root.set(name, np.asarray([spec["default"]]) if np.isscalar(spec["default"]) or isinstance(spec["default"], bool) else spec["default"])
+                default, shape = spec["default"], spec["contract"].shape
+                if np.isscalar(default) or isinstance(default, bool):
+                    # a scalar default of a per-row input stands for every row of the request
+                    rows = self._batch if shape and isinstance(shape[0], str) else 1
+                    default = np.full((rows,), default)
+                root.set(name, default)
             elif spec["required"]:
                 raise WorkflowRuntimeError(f"required input '{name}' was not supplied")
         for key, name in self.wf.serving.items():
@@ -182,7 +225,8 @@ class WorkflowSession:
             while it < limit and not self._stop and _all_true(self._read(scope, step.continue_when, step)):
                 body = _Scope(scope)
                 if step.iteration_value:
-                    body.set(step.iteration_value, np.asarray([it], dtype=np.int64))
+                    rows = self._batch if any(isinstance(d, str) for d in step.iteration_shape) else 1
+                    body.set(step.iteration_value, np.full((rows,), it, dtype=np.int64))
                 for s in step.steps:
                     self._exec(s, body)
                 nxt = [(cell, self._read(body, n, step)) for cell, _i, n in step.carried]

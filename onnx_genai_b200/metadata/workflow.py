@@ -64,6 +64,7 @@ class Step:
     max_iterations: str | None = None
     termination: str = "predicate"
     iteration_value: str | None = None
+    iteration_shape: list = field(default_factory=lambda: [1])   # [1], or ["batch"] for one counter per request row
     carried: list = field(default_factory=list)      # [(cell, initial | None, next)]
     predicate: str | None = None                     # branch
     cases: dict = field(default_factory=dict)        # label -> Step
@@ -157,6 +158,8 @@ def _step(d, where) -> Step:
             raise WorkflowError(f"{where}: loop termination {s.termination!r} is not predicate or generation_eos")
         it = d.get("iteration")
         s.iteration_value = str(it["value"]) if isinstance(it, dict) and "value" in it else None
+        if isinstance(it, dict) and isinstance(it.get("contract"), dict) and it["contract"].get("shape"):
+            s.iteration_shape = list(it["contract"]["shape"])
         for i, c in enumerate(d.get("carried") or []):
             if not isinstance(c, dict) or "cell" not in c or "next" not in c:
                 raise WorkflowError(f"{where}.carried[{i}]: a carried entry needs 'cell' and 'next'")

@@ -1,0 +1,620 @@
+"""Generic ONNX graph execution for the models around the decoder: encoders, projectors, VAEs, policies.
+
+The decoder itself runs on this package's own kernels and step executor.  A multi-model package also carries graphs
+that are not decoders -- a vision tower, an audio encoder, a text encoder, a denoiser, a VAE, small policy graphs
+(schedules, solvers, predicates) -- and the workflow runtime needs to call them.  :class:`GraphExecutor` interprets
+such a graph node by node in topological order over torch tensors on any device: the role of the reference's
+sequential executor over its CPU / CUDA operator registries for graphs outside the decode fast path
+(crates/onnx-runtime-session/src/executor/mod.rs; operator coverage crates/onnx-runtime-ep-cpu/src/lib.rs).  These
+graphs are off the token loop (they run once per request or per denoising step), so library tensor operations are the
+right tool; nothing here is used by the decoder.
+
+Coverage: the dense, convolutional, normalisation, activation, shape and indexing operators of the default domain
+that such graphs use (see ``OPS``), plus the ``com.microsoft`` contrib forms ``Gelu``, ``FastGelu``, ``BiasGelu``,
+``SkipLayerNormalization``, ``SimplifiedLayerNormalization``, ``SkipSimplifiedLayerNormalization``, ``GroupQueryAttention``
+(separate past / present buffers) and ``MatMulNBits``.
+Control flow (``If`` / ``Loop`` / ``Scan``) is not interpreted: loops belong to the workflow document.  An operator
+outside the table is an error that names the node and lists what is covered.
+
+``as_component(path)`` wraps a graph as a workflow component: a callable from a dict of input ports to a dict of
+output ports (ports are the graph's input and output names).
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+from . import onnx_pb
+
+_TORCH_DTYPE = {onnx_pb.FLOAT: torch.float32, onnx_pb.UINT8: torch.uint8, onnx_pb.INT8: torch.int8, onnx_pb.INT16: torch.int16,
+                onnx_pb.INT32: torch.int32, onnx_pb.INT64: torch.int64, onnx_pb.BOOL: torch.bool, onnx_pb.FLOAT16: torch.float16,
+                onnx_pb.DOUBLE: torch.float64, onnx_pb.BFLOAT16: torch.bfloat16}
+
+
+class GraphExecutionError(RuntimeError):
+    pass
+
+
+def tensor_to_torch(t: onnx_pb.Tensor, device="cpu") -> torch.Tensor:
+    arr = np.ascontiguousarray(t.numpy())
+    if t.data_type == onnx_pb.BFLOAT16:
+        return torch.from_numpy(arr.view(np.int16).copy()).view(torch.bfloat16).reshape(tuple(t.dims)).to(device)
+    if t.data_type == onnx_pb.FLOAT8E4M3FN:
+        return torch.from_numpy(arr.copy()).view(torch.float8_e4m3fn).reshape(tuple(t.dims)).to(device)
+    if arr.dtype == np.uint16:
+        arr = arr.astype(np.int32)
+    elif arr.dtype in (np.uint32, np.uint64):
+        arr = arr.astype(np.int64)
+    return torch.from_numpy(arr.copy()).reshape(tuple(t.dims)).to(device)
+
+
+def _ints(x):
+    if isinstance(x, torch.Tensor):
+        return [int(v) for v in x.reshape(-1).tolist()]
+    return [int(v) for v in x]
+
+
+def _axis_list(attrs, ins, idx=1, name="axes"):
+    if len(ins) > idx and ins[idx] is not None:
+        return _ints(ins[idx])
+    v = attrs.get(name)
+    return None if v in (None, 0, []) and name not in attrs else _ints(v if isinstance(v, (list, tuple)) else [v])
+
+
+def _pads(attrs, nd, x_shape=None, kernel=None, strides=None, dilations=None):
+    auto = attrs.get("auto_pad", "NOTSET")
+    if auto in ("SAME_UPPER", "SAME_LOWER"):
+        pads_b, pads_e = [], []
+        for i in range(nd):
+            out = math.ceil(x_shape[i] / strides[i])
+            total = max(0, (out - 1) * strides[i] + (kernel[i] - 1) * dilations[i] + 1 - x_shape[i])
+            lo = total // 2 if auto == "SAME_UPPER" else total - total // 2
+            pads_b.append(lo)
+            pads_e.append(total - lo)
+        return pads_b, pads_e
+    p = _ints(attrs.get("pads") or [0] * (2 * nd))
+    return p[:nd], p[nd:]
+
+
+def _conv(ins, attrs, transpose=False):
+    x, w = ins[0], ins[1]
+    b = ins[2] if len(ins) > 2 else None
+    nd = x.dim() - 2
+    strides = _ints(attrs.get("strides") or [1] * nd)
+    dil = _ints(attrs.get("dilations") or [1] * nd)
+    group = int(attrs.get("group", 1) or 1)
+    kernel = list(w.shape[2:])
+    pb, pe = _pads(attrs, nd, list(x.shape[2:]), kernel, strides, dil)
+    fn = {1: (F.conv1d, F.conv_transpose1d), 2: (F.conv2d, F.conv_transpose2d), 3: (F.conv3d, F.conv_transpose3d)}[nd][int(transpose)]
+    if transpose:
+        if pb != pe:
+            raise GraphExecutionError("ConvTranspose with asymmetric pads is not covered")
+        out_pad = _ints(attrs.get("output_padding") or [0] * nd)
+        return fn(x, w, b, stride=strides, padding=pb, output_padding=out_pad, groups=group, dilation=dil)
+    if pb != pe:
+        flat = []
+        for i in reversed(range(nd)):
+            flat += [pb[i], pe[i]]
+        x, pb = F.pad(x, flat), [0] * nd
+    return fn(x, w, b, stride=strides, padding=pb, dilation=dil, groups=group)
+
+
+def _pool(ins, attrs, kind):
+    x = ins[0]
+    nd = x.dim() - 2
+    k = _ints(attrs["kernel_shape"])
+    strides = _ints(attrs.get("strides") or [1] * nd)
+    dil = _ints(attrs.get("dilations") or [1] * nd)
+    pb, pe = _pads(attrs, nd, list(x.shape[2:]), k, strides, dil)
+    ceil = bool(attrs.get("ceil_mode", 0))
+    if pb != pe:
+        flat = []
+        for i in reversed(range(nd)):
+            flat += [pb[i], pe[i]]
+        x, pb = F.pad(x, flat, value=float("-inf") if kind == "max" else 0.0), [0] * nd
+    if kind == "max":
+        return {1: F.max_pool1d, 2: F.max_pool2d, 3: F.max_pool3d}[nd](x, k, strides, pb, dil, ceil)
+    include = bool(attrs.get("count_include_pad", 0))
+    return {1: F.avg_pool1d, 2: F.avg_pool2d, 3: F.avg_pool3d}[nd](x, k, strides, pb, ceil, include)
+
+
+def _layer_norm(x, scale, bias, axis, eps):
+    dims = tuple(range(axis % x.dim(), x.dim()))
+    xf = x.float()
+    mean = xf.mean(dims, keepdim=True)
+    var = (xf - mean).pow(2).mean(dims, keepdim=True)
+    y = ((xf - mean) * torch.rsqrt(var + eps)).to(x.dtype) * scale
+    return y + bias if bias is not None else y
+
+
+def _rms_norm(x, scale, axis, eps):
+    dims = tuple(range(axis % x.dim(), x.dim()))
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(dims, keepdim=True) + eps)).to(x.dtype) * scale
+
+
+def _slice(ins, attrs):
+    x = ins[0]
+    if len(ins) > 1:
+        starts, ends = _ints(ins[1]), _ints(ins[2])
+        axes = _ints(ins[3]) if len(ins) > 3 and ins[3] is not None else list(range(len(starts)))
+        steps = _ints(ins[4]) if len(ins) > 4 and ins[4] is not None else [1] * len(starts)
+    else:
+        starts, ends = _ints(attrs["starts"]), _ints(attrs["ends"])
+        axes = _ints(attrs.get("axes") or list(range(len(starts))))
+        steps = [1] * len(starts)
+    for s, e, a, st in zip(starts, ends, axes, steps):
+        a %= x.dim()
+        sel = range(*slice(s, e, st).indices(x.shape[a]))          # the operator clamps exactly as Python slicing does
+        if st > 0:
+            x = x.narrow(a, sel.start, len(sel)) if st == 1 else x.index_select(a, torch.tensor(list(sel), dtype=torch.long, device=x.device))
+        else:
+            x = x.index_select(a, torch.tensor(list(sel), dtype=torch.long, device=x.device))
+    return x
+
+
+def _squeeze(ins, attrs):
+    x, axes = ins[0], _axis_list(attrs, ins)
+    if axes is None:
+        return x.squeeze()
+    drop = {a % x.dim() for a in axes}
+    return x.reshape([s for d, s in enumerate(x.shape) if d not in drop])
+
+
+def _unsqueeze(ins, attrs):
+    x, axes = ins[0], _axis_list(attrs, ins)
+    nd = x.dim() + len(axes)
+    for d in sorted(a % nd for a in axes):
+        x = x.unsqueeze(d)
+    return x
+
+
+def _resize(ins, attrs):
+    x = ins[0]
+    scales = ins[2] if len(ins) > 2 and ins[2] is not None and ins[2].numel() else None
+    sizes = ins[3] if len(ins) > 3 and ins[3] is not None and ins[3].numel() else None
+    mode = attrs.get("mode", "nearest")
+    nd = x.dim() - 2
+    tmode = {"nearest": "nearest", "linear": {1: "linear", 2: "bilinear", 3: "trilinear"}[nd], "cubic": "bicubic"}[mode]
+    ctm = attrs.get("coordinate_transformation_mode", "half_pixel")
+    kw = {}
+    if tmode != "nearest":
+        kw["align_corners"] = ctm == "align_corners"
+    if sizes is not None:
+        return F.interpolate(x, size=_ints(sizes)[2:], mode=tmode, **kw)
+    return F.interpolate(x, scale_factor=[float(s) for s in scales.reshape(-1).tolist()][2:], mode=tmode, **kw)
+
+
+def _matmul_nbits(ins, attrs):
+    """com.microsoft::MatMulNBits (4-bit, block-wise): y = x @ dequant(B)^T."""
+    x, packed, scales = ins[0], ins[1], ins[2]
+    zp = ins[3] if len(ins) > 3 and ins[3] is not None else None
+    k, n, block = int(attrs["K"]), int(attrs["N"]), int(attrs["block_size"])
+    if int(attrs.get("bits", 4)) != 4:
+        raise GraphExecutionError("MatMulNBits is covered for bits=4 only")
+    p = packed.reshape(n, -1).to(torch.int32)
+    lo, hi = p & 0xF, (p >> 4) & 0xF
+    blocks = (k + block - 1) // block
+    q = torch.stack([lo, hi], dim=-1).reshape(n, blocks, block).float()       # K is padded to whole blocks in storage
+    s = scales.reshape(n, blocks).float()
+    if zp is not None:
+        z = zp.reshape(n, -1).to(torch.int32)
+        z = torch.stack([z & 0xF, (z >> 4) & 0xF], dim=-1).reshape(n, -1)[:, :blocks].float()
+    else:
+        z = torch.full((n, blocks), 8.0, device=x.device)
+    w = (q - z[..., None]) * s[..., None]
+    y = x.float() @ w.reshape(n, -1)[:, :k].T
+    if len(ins) > 5 and ins[5] is not None:
+        y = y + ins[5].float()
+    return y.to(x.dtype)
+
+
+def _gather_nd(data, idx):
+    idx = idx.long()
+    k = idx.shape[-1]
+    flat = idx.reshape(-1, k)
+    out = data[tuple(flat[:, i] for i in range(k))]
+    return out.reshape(tuple(idx.shape[:-1]) + tuple(data.shape[k:]))
+
+
+def _reduce(fn):
+    def run(ins, attrs):
+        x = ins[0]
+        axes = _axis_list(attrs, ins)
+        keep = bool(attrs.get("keepdims", 1))
+        if axes is None or len(axes) == 0:
+            if attrs.get("noop_with_empty_axes", 0):
+                return x
+            axes = list(range(x.dim()))
+        return fn(x, tuple(a % x.dim() for a in axes), keep)
+    return run
+
+
+def _constant(ins, attrs, device):
+    if "value" in attrs:
+        return tensor_to_torch(attrs["value"], device)
+    for key, dt in (("value_float", torch.float32), ("value_int", torch.int64)):
+        if key in attrs:
+            return torch.tensor(attrs[key], dtype=dt, device=device)
+    for key, dt in (("value_floats", torch.float32), ("value_ints", torch.int64)):
+        if key in attrs:
+            return torch.tensor(list(attrs[key]), dtype=dt, device=device)
+    raise GraphExecutionError("Constant without a value attribute")
+
+
+def _pad(ins, attrs):
+    x = ins[0]
+    pads = _ints(ins[1]) if len(ins) > 1 else _ints(attrs["pads"])
+    value = float(ins[2].reshape(-1)[0]) if len(ins) > 2 and ins[2] is not None and ins[2].numel() else float(attrs.get("value", 0.0))
+    axes = _ints(ins[3]) if len(ins) > 3 and ins[3] is not None else list(range(x.dim()))
+    lo, hi = [0] * x.dim(), [0] * x.dim()
+    for i, a in enumerate(axes):
+        lo[a % x.dim()], hi[a % x.dim()] = pads[i], pads[i + len(axes)]
+    flat = []
+    for d in reversed(range(x.dim())):
+        flat += [lo[d], hi[d]]
+    mode = attrs.get("mode", "constant")
+    while len(flat) > 2 and flat[-1] == 0 and flat[-2] == 0:       # leading dimensions without padding need not be listed
+        flat = flat[:-2]
+    if mode == "constant":
+        return F.pad(x, flat, value=value)
+    return F.pad(x, flat, mode={"reflect": "reflect", "edge": "replicate", "wrap": "circular"}[mode])
+
+
+def _split(ins, attrs, n_out):
+    x = ins[0]
+    axis = int(attrs.get("axis", 0))
+    if len(ins) > 1 and ins[1] is not None:
+        sizes = _ints(ins[1])
+    elif "split" in attrs:
+        sizes = _ints(attrs["split"])
+    else:
+        per = -(-x.shape[axis] // n_out)
+        sizes = [min(per, x.shape[axis] - i * per) for i in range(n_out)]
+    return list(torch.split(x, sizes, dim=axis))
+
+
+def _expand(x, shape):
+    shape = _ints(shape)
+    nd = max(len(shape), x.dim())
+    xs = [1] * (nd - x.dim()) + list(x.shape)
+    ss = [1] * (nd - len(shape)) + shape
+    return x.reshape(xs).expand([max(a, b) for a, b in zip(xs, ss)])
+
+
+def _reshape(x, shape, allowzero=0):
+    shape = _ints(shape)
+    if not allowzero:
+        shape = [x.shape[i] if s == 0 else s for i, s in enumerate(shape)]
+    return x.reshape(shape)
+
+
+def _rotary(ins, attrs):
+    """RotaryEmbedding (opset 23): X is [B, S, H*D] (with ``num_heads``) or [B, H, S, D]; caches are [positions, rot/2]
+    when position ids are given, else already gathered [B, S, rot/2]."""
+    x, cos, sin = ins[0], ins[1], ins[2]
+    pos = ins[3] if len(ins) > 3 and ins[3] is not None else None
+    three = x.dim() == 3
+    if three:
+        heads = int(attrs.get("num_heads", 0))
+        if heads <= 0:
+            raise GraphExecutionError("RotaryEmbedding on a 3-D input needs the num_heads attribute")
+        v = x.reshape(x.shape[0], x.shape[1], heads, -1)
+    else:
+        v = x.transpose(1, 2)
+    d = v.shape[-1]
+    rot = int(attrs.get("rotary_embedding_dim", 0)) or d
+    if pos is not None:
+        cos, sin = cos[pos.long()], sin[pos.long()]
+    cos, sin = cos.unsqueeze(2).to(v.dtype), sin.unsqueeze(2).to(v.dtype)
+    xr, rest = v[..., :rot], v[..., rot:]
+    if attrs.get("interleaved", 0):
+        x1, x2 = xr[..., 0::2], xr[..., 1::2]
+        out = torch.stack([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).flatten(-2)
+    else:
+        x1, x2 = xr[..., : rot // 2], xr[..., rot // 2:]
+        out = torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1)
+    out = torch.cat([out, rest], dim=-1)
+    return out.reshape(x.shape) if three else out.transpose(1, 2)
+
+
+def _attention(ins, attrs):
+    """Attention (opset 23): scaled dot-product attention with optional mask, past K/V, grouped query heads, softcap."""
+    q, k, v = ins[0], ins[1], ins[2]
+    mask = ins[3] if len(ins) > 3 else None
+    past_k = ins[4] if len(ins) > 4 else None
+    past_v = ins[5] if len(ins) > 5 else None
+    three = q.dim() == 3
+    if three:
+        hq, hkv = int(attrs["q_num_heads"]), int(attrs["kv_num_heads"])
+        b, s = q.shape[0], q.shape[1]
+        q = q.reshape(b, s, hq, -1).transpose(1, 2)
+        k = k.reshape(b, k.shape[1], hkv, -1).transpose(1, 2)
+        v = v.reshape(b, v.shape[1], hkv, -1).transpose(1, 2)
+    if past_k is not None:
+        k = torch.cat([past_k, k], dim=2)
+    if past_v is not None:
+        v = torch.cat([past_v, v], dim=2)
+    present_k, present_v = k, v
+    if q.shape[1] != k.shape[1]:
+        rep = q.shape[1] // k.shape[1]
+        k, v = k.repeat_interleave(rep, dim=1), v.repeat_interleave(rep, dim=1)
+    scale = float(attrs.get("scale", 0.0)) or 1.0 / math.sqrt(q.shape[-1])
+    scores = (q.float() @ k.float().transpose(-1, -2)) * scale
+    cap = float(attrs.get("softcap", 0.0))
+    if cap > 0:
+        scores = cap * torch.tanh(scores / cap)
+    if attrs.get("is_causal", 0):
+        # with past keys the triangle is aligned to the last key (query i sees keys up to past + i), which is what makes a
+        # cached step equal the same position of a full pass; without past this is the plain lower triangle
+        tri = torch.ones(scores.shape[-2], scores.shape[-1], dtype=torch.bool, device=scores.device).tril(scores.shape[-1] - scores.shape[-2])
+        scores = scores.masked_fill(~tri, float("-inf"))
+    if mask is not None:
+        scores = scores.masked_fill(~mask, float("-inf")) if mask.dtype == torch.bool else scores + mask.float()
+    y = (torch.softmax(scores, dim=-1) @ v.float()).to(ins[0].dtype)
+    if three:
+        y = y.transpose(1, 2).reshape(y.shape[0], y.shape[2], -1)
+    return [y, present_k, present_v, scores.to(ins[0].dtype)]
+
+
+def _group_query_attention(ins, attrs):
+    """com.microsoft::GroupQueryAttention with separate past / present buffers: packed [B, S, H*D] projections, optional
+    in-op rotary embedding at positions ``seqlens_k + 1 - S + i``, causal attention over past + new keys (bottom-right
+    aligned), optional local window."""
+    q, k, v = ins[0], ins[1], ins[2]
+    past_k = ins[3] if len(ins) > 3 else None
+    past_v = ins[4] if len(ins) > 4 else None
+    seqlens = ins[5].long().reshape(-1)
+    cos = ins[7] if len(ins) > 7 else None
+    sin = ins[8] if len(ins) > 8 else None
+    hq, hkv = int(attrs["num_heads"]), int(attrs["kv_num_heads"])
+    b, s = q.shape[0], q.shape[1]
+    d = q.shape[2] // hq
+    q = q.reshape(b, s, hq, d)
+    k = k.reshape(b, s, hkv, d)
+    v = v.reshape(b, s, hkv, d).transpose(1, 2)
+    pos = (seqlens + 1 - s)[:, None] + torch.arange(s, device=q.device)[None]          # [B, S]
+    if attrs.get("do_rotary", 0):
+        ra = {"interleaved": int(attrs.get("rotary_interleaved", 0)), "rotary_embedding_dim": 2 * cos.shape[-1]}
+        q = _rotary([q.transpose(1, 2), cos, sin, pos], ra).transpose(1, 2)
+        k = _rotary([k.transpose(1, 2), cos, sin, pos], ra).transpose(1, 2)
+    q, k = q.transpose(1, 2), k.transpose(1, 2)                                          # [B, H, S, D]
+    if past_k is not None and past_k.shape[2] > 0:
+        k, v = torch.cat([past_k.to(k.dtype), k], dim=2), torch.cat([past_v.to(v.dtype), v], dim=2)
+    present_k, present_v = k, v
+    t = k.shape[2]
+    rep = hq // hkv
+    kf, vf = k.repeat_interleave(rep, dim=1).float(), v.repeat_interleave(rep, dim=1).float()
+    scale = float(attrs.get("scale", 0.0)) or 1.0 / math.sqrt(d)
+    scores = (q.float() @ kf.transpose(-1, -2)) * scale
+    cap = float(attrs.get("softcap", 0.0))
+    if cap > 0:
+        scores = cap * torch.tanh(scores / cap)
+    key_pos = torch.arange(t, device=q.device)[None, None, :]
+    q_pos = (t - s + torch.arange(s, device=q.device))[None, :, None]
+    allowed = key_pos <= q_pos
+    window = int(attrs.get("local_window_size", -1))
+    if window > 0:
+        allowed = allowed & (key_pos > q_pos - window)
+    scores = scores.masked_fill(~allowed[:, None], float("-inf"))
+    y = (torch.softmax(scores, dim=-1) @ vf).to(ins[0].dtype)
+    return [y.transpose(1, 2).reshape(b, s, hq * d), present_k, present_v]
+
+
+def _bitshift(ins, attrs):
+    x, n = ins[0], ins[1]
+    if attrs.get("direction", "LEFT") == "LEFT":
+        return torch.bitwise_left_shift(x, n)
+    if x.dtype == torch.uint8:
+        return torch.bitwise_right_shift(x, n)
+    # the operator is defined on unsigned integers, which live in int64 here: shift logically, not arithmetically
+    n64 = n.to(torch.int64)
+    keep = torch.where(n64 > 0, (torch.ones_like(n64) << (64 - n64).clamp(max=63)) - 1, torch.full_like(n64, -1))
+    return torch.bitwise_right_shift(x.to(torch.int64), n64) & keep
+
+
+def _mod(ins, attrs):
+    a, b = ins[0], ins[1]
+    if attrs.get("fmod", 0) or a.is_floating_point():
+        return torch.fmod(a, b)
+    return torch.remainder(a, b)                 # integer Mod takes the sign of the divisor
+
+
+def _erf_gelu(x):
+    return 0.5 * x * (1.0 + torch.erf(x / math.sqrt(2.0)))
+
+
+def _cast(x, to):
+    to = int(to)
+    if to in (onnx_pb.UINT32, onnx_pb.UINT64, onnx_pb.UINT16):
+        # torch has no arithmetic on wide unsigned types: they live in int64 (two's complement wraps like uint64; narrower
+        # ones are masked at the cast, so a value that overflows between casts keeps its high bits until the next cast)
+        y = x.to(torch.int64)
+        return y & 0xFFFFFFFF if to == onnx_pb.UINT32 else (y & 0xFFFF if to == onnx_pb.UINT16 else y)
+    dt = _TORCH_DTYPE.get(to)
+    if dt is None:
+        raise GraphExecutionError(f"Cast to ONNX data type {to} is not covered")
+    return x.to(dt)
+
+
+# op name -> callable(inputs, attrs) -> tensor | list of tensors
+OPS = {
+    "Add": lambda i, a: i[0] + i[1], "Sub": lambda i, a: i[0] - i[1], "Mul": lambda i, a: i[0] * i[1],
+    "Div": lambda i, a: torch.div(i[0], i[1], rounding_mode="trunc") if not i[0].is_floating_point() else i[0] / i[1],
+    "Pow": lambda i, a: torch.pow(i[0], i[1].to(i[0].dtype) if i[0].is_floating_point() else i[1]),
+    "Neg": lambda i, a: -i[0], "Abs": lambda i, a: i[0].abs(), "Sqrt": lambda i, a: i[0].sqrt(), "Exp": lambda i, a: i[0].exp(),
+    "Log": lambda i, a: i[0].log(), "Reciprocal": lambda i, a: 1.0 / i[0], "Floor": lambda i, a: i[0].floor(), "Ceil": lambda i, a: i[0].ceil(),
+    "Round": lambda i, a: i[0].round(), "Sin": lambda i, a: i[0].sin(), "Cos": lambda i, a: i[0].cos(), "Tanh": lambda i, a: i[0].tanh(),
+    "Erf": lambda i, a: torch.erf(i[0]), "Sign": lambda i, a: i[0].sign(), "Sigmoid": lambda i, a: torch.sigmoid(i[0]),
+    "Relu": lambda i, a: F.relu(i[0]), "LeakyRelu": lambda i, a: F.leaky_relu(i[0], float(a.get("alpha", 0.01))),
+    "Elu": lambda i, a: F.elu(i[0], float(a.get("alpha", 1.0))), "Softplus": lambda i, a: F.softplus(i[0]),
+    "HardSigmoid": lambda i, a: torch.clamp(float(a.get("alpha", 0.2)) * i[0] + float(a.get("beta", 0.5)), 0, 1),
+    "HardSwish": lambda i, a: F.hardswish(i[0]), "Mish": lambda i, a: F.mish(i[0]),
+    "Gelu": lambda i, a: F.gelu(i[0], approximate="tanh") if a.get("approximate", "none") == "tanh" else _erf_gelu(i[0]),
+    "FastGelu": lambda i, a: F.gelu(i[0] + (i[1] if len(i) > 1 and i[1] is not None else 0), approximate="tanh"),
+    "BiasGelu": lambda i, a: _erf_gelu(i[0] + i[1]),
+    "QuickGelu": lambda i, a: i[0] * torch.sigmoid(float(a.get("alpha", 1.702)) * i[0]),
+    "Min": lambda i, a: torch.stack(torch.broadcast_tensors(*i)).amin(0) if len(i) > 1 else i[0],
+    "Max": lambda i, a: torch.stack(torch.broadcast_tensors(*i)).amax(0) if len(i) > 1 else i[0],
+    "Sum": lambda i, a: sum(i[1:], i[0]), "Mean": lambda i, a: sum(i[1:], i[0]) / len(i),
+    "Clip": lambda i, a: (lambda lo, hi: i[0] if lo is None and hi is None else torch.clamp(i[0], min=lo, max=hi))(
+        i[1].item() if len(i) > 1 and i[1] is not None else a.get("min"), i[2].item() if len(i) > 2 and i[2] is not None else a.get("max")),
+    "Equal": lambda i, a: i[0] == i[1], "Less": lambda i, a: i[0] < i[1], "LessOrEqual": lambda i, a: i[0] <= i[1],
+    "Greater": lambda i, a: i[0] > i[1], "GreaterOrEqual": lambda i, a: i[0] >= i[1],
+    "Not": lambda i, a: ~i[0], "And": lambda i, a: i[0] & i[1], "Or": lambda i, a: i[0] | i[1], "Xor": lambda i, a: i[0] ^ i[1],
+    "Where": lambda i, a: torch.where(i[0], i[1], i[2]), "IsNaN": lambda i, a: torch.isnan(i[0]),
+    "BitShift": _bitshift, "BitwiseAnd": lambda i, a: i[0] & i[1], "BitwiseOr": lambda i, a: i[0] | i[1],
+    "BitwiseXor": lambda i, a: i[0] ^ i[1], "BitwiseNot": lambda i, a: ~i[0], "Mod": _mod,
+    "IsInf": lambda i, a: torch.isinf(i[0]) & ((i[0] > 0) if not a.get("detect_negative", 1) else True) & ((i[0] < 0) if not a.get("detect_positive", 1) else True),
+    "Swish": lambda i, a: i[0] * torch.sigmoid(float(a.get("alpha", 1.0)) * i[0]),
+    "RotaryEmbedding": _rotary, "Attention": _attention, "GroupQueryAttention": _group_query_attention,
+    "MatMul": lambda i, a: i[0] @ i[1],
+    "Gemm": lambda i, a: float(a.get("alpha", 1.0)) * ((i[0].T if a.get("transA", 0) else i[0]) @ (i[1].T if a.get("transB", 0) else i[1]))
+                         + (float(a.get("beta", 1.0)) * i[2] if len(i) > 2 and i[2] is not None else 0),
+    "MatMulNBits": _matmul_nbits,
+    "Conv": lambda i, a: _conv(i, a), "ConvTranspose": lambda i, a: _conv(i, a, transpose=True),
+    "MaxPool": lambda i, a: _pool(i, a, "max"), "AveragePool": lambda i, a: _pool(i, a, "avg"),
+    "GlobalAveragePool": lambda i, a: i[0].mean(tuple(range(2, i[0].dim())), keepdim=True),
+    "GlobalMaxPool": lambda i, a: i[0].amax(tuple(range(2, i[0].dim())), keepdim=True),
+    "Resize": _resize, "Upsample": lambda i, a: _resize([i[0], None, i[1]], a),
+    "BatchNormalization": lambda i, a: F.batch_norm(i[0], i[3], i[4], i[1], i[2], False, 0.0, float(a.get("epsilon", 1e-5))),
+    "InstanceNormalization": lambda i, a: F.instance_norm(i[0], weight=i[1], bias=i[2], eps=float(a.get("epsilon", 1e-5))),
+    "GroupNormalization": lambda i, a: F.group_norm(i[0], int(a["num_groups"]), i[1], i[2], float(a.get("epsilon", 1e-5))),
+    "LayerNormalization": lambda i, a: _layer_norm(i[0], i[1], i[2] if len(i) > 2 else None, int(a.get("axis", -1)), float(a.get("epsilon", 1e-5))),
+    "SimplifiedLayerNormalization": lambda i, a: _rms_norm(i[0], i[1], int(a.get("axis", -1)), float(a.get("epsilon", 1e-5))),
+    "RMSNormalization": lambda i, a: _rms_norm(i[0], i[1], int(a.get("axis", -1)), float(a.get("epsilon", 1e-5))),
+    "Softmax": lambda i, a: torch.softmax(i[0].float(), int(a.get("axis", -1))).to(i[0].dtype),
+    "LogSoftmax": lambda i, a: torch.log_softmax(i[0].float(), int(a.get("axis", -1))).to(i[0].dtype),
+    "ReduceMean": _reduce(lambda x, ax, k: x.mean(ax, keepdim=k)), "ReduceSum": _reduce(lambda x, ax, k: x.sum(ax, keepdim=k)),
+    "ReduceMax": _reduce(lambda x, ax, k: x.amax(ax, keepdim=k)), "ReduceMin": _reduce(lambda x, ax, k: x.amin(ax, keepdim=k)),
+    "ReduceProd": _reduce(lambda x, ax, k: torch.prod(x, ax[0], keepdim=k) if len(ax) == 1 else x.flatten().prod()),
+    "ReduceL2": _reduce(lambda x, ax, k: x.pow(2).sum(ax, keepdim=k).sqrt()),
+    "ReduceSumSquare": _reduce(lambda x, ax, k: x.pow(2).sum(ax, keepdim=k)),
+    "ArgMax": lambda i, a: i[0].argmax(int(a.get("axis", 0)), keepdim=bool(a.get("keepdims", 1))),
+    "ArgMin": lambda i, a: i[0].argmin(int(a.get("axis", 0)), keepdim=bool(a.get("keepdims", 1))),
+    "TopK": lambda i, a: list(torch.topk(i[0], int(i[1].reshape(-1)[0]), dim=int(a.get("axis", -1)), largest=bool(a.get("largest", 1)))),
+    "CumSum": lambda i, a: torch.cumsum(i[0], int(i[1].reshape(-1)[0])),
+    "Reshape": lambda i, a: _reshape(i[0], i[1], a.get("allowzero", 0)),
+    "Flatten": lambda i, a: i[0].reshape(int(np.prod(i[0].shape[: int(a.get("axis", 1))])) if int(a.get("axis", 1)) else 1, -1),
+    "Transpose": lambda i, a: i[0].permute(_ints(a["perm"])) if a.get("perm") else i[0].permute(*reversed(range(i[0].dim()))),
+    "Squeeze": _squeeze, "Unsqueeze": _unsqueeze,
+    "Concat": lambda i, a: torch.cat([t for t in i if t is not None], dim=int(a.get("axis", 0))),
+    "Slice": _slice, "Pad": _pad, "Tile": lambda i, a: i[0].repeat(_ints(i[1])), "Expand": lambda i, a: _expand(i[0], i[1]),
+    "Gather": lambda i, a: (lambda x, idx, ax: x.index_select(ax, torch.where(idx < 0, idx + x.shape[ax], idx).reshape(-1).long())
+                            .reshape(tuple(x.shape[:ax]) + tuple(idx.shape) + tuple(x.shape[ax + 1:])))(i[0], i[1], int(a.get("axis", 0)) % i[0].dim()),
+    "GatherElements": lambda i, a: torch.gather(i[0], int(a.get("axis", 0)), i[1].long()),
+    "GatherND": lambda i, a: _gather_nd(i[0], i[1]),
+    "ScatterElements": lambda i, a: i[0].scatter(int(a.get("axis", 0)), i[1].long(), i[2]),
+    "ScatterND": lambda i, a: (lambda out, idx, upd: out.index_put_(tuple(idx.reshape(-1, idx.shape[-1]).long().T),
+                                                                    upd.reshape((-1,) + tuple(out.shape[idx.shape[-1]:]))))(i[0].clone(), i[1], i[2]),
+    "Shape": lambda i, a: torch.tensor(list(i[0].shape)[int(a.get("start", 0)): a.get("end")], dtype=torch.int64, device=i[0].device),
+    "Size": lambda i, a: torch.tensor(i[0].numel(), dtype=torch.int64, device=i[0].device),
+    "ConstantOfShape": lambda i, a: torch.zeros(_ints(i[0]), device=i[0].device) if "value" not in a else
+        tensor_to_torch(a["value"], i[0].device).reshape(-1)[0].expand(_ints(i[0])).clone(),
+    "Range": lambda i, a: torch.arange(i[0].item(), i[1].item(), i[2].item(), dtype=i[0].dtype, device=i[0].device),
+    "Cast": lambda i, a: _cast(i[0], a["to"]), "CastLike": lambda i, a: i[0].to(i[1].dtype),
+    "Identity": lambda i, a: i[0], "Dropout": lambda i, a: i[0],
+    "Einsum": lambda i, a: torch.einsum(a["equation"], *i),
+    "Trilu": lambda i, a: (torch.triu if a.get("upper", 1) else torch.tril)(i[0], int(i[1].item()) if len(i) > 1 and i[1] is not None else 0),
+    "OneHot": lambda i, a: (lambda oh, vals: oh * (vals[1] - vals[0]) + vals[0])(F.one_hot(i[0].long() % int(i[1].item()), int(i[1].item())).to(i[2].dtype), i[2]),
+    "DepthToSpace": lambda i, a: F.pixel_shuffle(i[0], int(a["blocksize"])) if a.get("mode", "DCR") == "CRD" else
+        (lambda x, b: x.reshape(x.shape[0], b, b, x.shape[1] // (b * b), x.shape[2], x.shape[3]).permute(0, 3, 4, 1, 5, 2)
+         .reshape(x.shape[0], x.shape[1] // (b * b), x.shape[2] * b, x.shape[3] * b))(i[0], int(a["blocksize"])),
+    "SpaceToDepth": lambda i, a: F.pixel_unshuffle(i[0], int(a["blocksize"])),
+    "SkipLayerNormalization": lambda i, a: (lambda s: [_layer_norm(s, i[2], i[3] if len(i) > 3 and i[3] is not None else None, -1,
+                                                                   float(a.get("epsilon", 1e-5))), None, None, s])(i[0] + i[1] + (i[4] if len(i) > 4 and i[4] is not None else 0)),
+    "SkipSimplifiedLayerNormalization": lambda i, a: (lambda s: [_rms_norm(s, i[2], -1, float(a.get("epsilon", 1e-5))), None, None, s])(
+        i[0] + i[1] + (i[3] if len(i) > 3 and i[3] is not None else 0)),
+}
+
+
+class GraphExecutor:
+    def __init__(self, model, device="cpu", dtype=None):
+        """``model``: a path to an ``.onnx`` file or a parsed :class:`onnx_pb.Model`.  Initializers move to ``device``
+        (floating-point ones are cast to ``dtype`` when given)."""
+        self.model = onnx_pb.load_model(model) if isinstance(model, str) else model
+        self.device = torch.device(device)
+        g = self.model.graph
+        self.constants = {}
+        for name, t in g.initializers.items():
+            v = tensor_to_torch(t, self.device)
+            if dtype is not None and v.is_floating_point():
+                v = v.to(dtype)
+            self.constants[name] = v
+        self.input_names = [vi.name for vi in g.inputs if vi.name not in self.constants]
+        self.output_names = [vi.name for vi in g.outputs]
+        self.input_types = {vi.name: vi.elem_type for vi in g.inputs}
+        unknown = sorted({(n.domain + "::" if n.domain else "") + n.op_type for n in g.nodes if n.op_type not in OPS and n.op_type != "Constant"
+                          and n.op_type != "Split"})
+        if unknown:
+            raise GraphExecutionError(f"graph '{g.name}' uses operators outside the covered set: {', '.join(unknown)} "
+                                      f"({len(OPS) + 2} operators are covered; control flow belongs to the workflow document)")
+        self.order = self._toposort(g)
+        self.runs = 0
+
+    def _toposort(self, g):
+        produced = set(self.constants) | set(self.input_names)
+        pending, order = list(g.nodes), []
+        while pending:
+            rest = []
+            for n in pending:
+                if all((not x) or x in produced for x in n.inputs):
+                    order.append(n)
+                    produced.update(o for o in n.outputs if o)
+                else:
+                    rest.append(n)
+            if len(rest) == len(pending):
+                missing = sorted({x for n in rest for x in n.inputs if x and x not in produced})
+                raise GraphExecutionError(f"graph '{g.name}' cannot be ordered: values {missing[:6]} are never produced")
+            pending = rest
+        return order
+
+    @torch.no_grad()
+    def run(self, feeds: dict, outputs=None) -> dict:
+        """``feeds``: input name -> tensor / array / scalar.  Returns output name -> tensor for ``outputs`` (default: all)."""
+        missing = [n for n in self.input_names if n not in feeds]
+        if missing:
+            raise GraphExecutionError(f"missing graph input(s) {missing}; the graph takes {self.input_names}")
+        env = dict(self.constants)
+        for name, v in feeds.items():
+            t = v if isinstance(v, torch.Tensor) else torch.as_tensor(np.asarray(v))
+            want = _TORCH_DTYPE.get(self.input_types.get(name))
+            if want is not None and t.dtype != want and (t.is_floating_point() == want.is_floating_point):
+                t = t.to(want)
+            env[name] = t.to(self.device)
+        for n in self.order:
+            ins = [env[x] if x else None for x in n.inputs]
+            try:
+                if n.op_type == "Constant":
+                    res = _constant(ins, n.attrs, self.device)
+                elif n.op_type == "Split":
+                    res = _split(ins, n.attrs, len(n.outputs))
+                else:
+                    res = OPS[n.op_type](ins, n.attrs)
+            except GraphExecutionError:
+                raise
+            except Exception as e:
+                shapes = [tuple(t.shape) if isinstance(t, torch.Tensor) else None for t in ins]
+                raise GraphExecutionError(f"node '{n.name or n.outputs[0]}' ({n.op_type}) failed on inputs {shapes}: {e}") from e
+            if isinstance(res, (list, tuple)):
+                for name, r in zip(n.outputs, res):
+                    if name and r is not None:
+                        env[name] = r
+            else:
+                env[n.outputs[0]] = res
+        self.runs += 1
+        return {name: env[name] for name in (outputs or self.output_names)}
+
+
+def as_component(model, device="cpu", dtype=None):
+    """A workflow component (dict of input ports -> dict of output ports) backed by an ONNX graph."""
+    ex = GraphExecutor(model, device, dtype)
+
+    def component(ports: dict) -> dict:
+        return ex.run({k: v for k, v in ports.items() if k in ex.input_names})
+
+    component.executor = ex
+    return component

@@ -73,3 +73,12 @@ def test_proposer_draft_needs_a_draft_model(pkg_dir):
     ok = subprocess.run([sys.executable, "-m", "onnx_genai_b200", "generate", pkg_dir, "--prompt", "hello", "--max-new-tokens", "4", "--greedy",
                          "--device", "cpu", "--draft-model", pkg_dir], capture_output=True, text=True)
     assert ok.returncode == 0, ok.stderr
+
+
+def test_graph_backend_prints_the_same_greedy_text(pkg_dir):
+    base = [sys.executable, "-m", "onnx_genai_b200", "generate", pkg_dir, "--prompt", "hello world", "--max-new-tokens", "8", "--greedy",
+            "--device", "cpu", "--raw"]
+    native = subprocess.run(base, capture_output=True, text=True)
+    graph = subprocess.run(base + ["--backend", "graph"], capture_output=True, text=True)
+    assert native.returncode == 0 and graph.returncode == 0, graph.stderr
+    assert graph.stdout == native.stdout and "backend graph" in graph.stderr

@@ -1,0 +1,53 @@
+"""Decode through the generic graph executor: the oracle for the fast path, and the route for unrecognised graphs."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from onnx_genai_b200.engine.api import Engine, GenerateOptions
+from onnx_genai_b200.engine.graph_decode import GraphDecodeSession
+from onnx_genai_b200.models.config import DecoderConfig
+from onnx_genai_b200.models.decoder import random_weights
+from onnx_genai_b200.package.export import export_package
+
+REF = os.environ.get("OGB_REFERENCE_DIR", os.path.join(os.path.expanduser("~"), "reference"))
+
+
+@pytest.mark.parametrize("int4, bias", [(False, True), (True, False)])
+def test_same_package_two_executors_same_greedy_tokens(tmp_path, int4, bias):
+    cfg = DecoderConfig(name="t", num_layers=2, hidden=64, num_heads=4, num_kv_heads=2, head_dim=16, intermediate=96, vocab=300,
+                        rope_theta=1e4, tie_embeddings=not int4, qkv_bias=bias, max_position=128,
+                        weight_format="int4" if int4 else "bf16")
+    w = random_weights(cfg, "cpu", seed=11, std=0.3, dtype=torch.float32)
+    d = export_package(cfg, w, str(tmp_path / "pkg"))
+    eng = Engine.from_dir(d, device="cpu", num_pages=32, max_seqs=2, max_tokens_per_step=64)
+    prompt = [5, 17, 200, 42, 42, 7, 99, 1, 250, 13, 8, 77, 3, 150, 21, 64, 33, 2]            # crosses a 16-token page
+    want = eng.generate(prompt, GenerateOptions(max_new_tokens=12, ignore_eos=True)).token_ids
+    sess = GraphDecodeSession.from_dir(d)
+    assert sess.generate(prompt, 12) == want
+    # KV threading: feeding token by token, all at once, or after a rewind gives the same logits
+    a = GraphDecodeSession.from_dir(d)
+    whole = a.feed(prompt)
+    b = GraphDecodeSession.from_dir(d)
+    step = torch.stack([b.feed([t])[0] for t in prompt])
+    assert torch.allclose(whole, step, atol=2e-4)
+    b.rewind(10)
+    assert b.length == 10 and torch.allclose(b.feed(prompt[10:]), whole[10:], atol=2e-4)
+    with pytest.raises(ValueError, match="cannot rewind to 99"):
+        b.rewind(99)
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(REF, "tests", "fixtures", "tiny-llm", "model.onnx.textproto")),
+                    reason="the upstream tiny-llm fixture is not available on this machine")
+def test_upstream_gpt2_style_fixture_decodes_with_consistent_kv():
+    """A decoder the pattern matcher does not lower (LayerNorm, learned positions, fused Attention op, text-format ONNX)."""
+    d = os.path.join(REF, "tests", "fixtures", "tiny-llm")
+    sess = GraphDecodeSession.from_dir(d)
+    assert sess.pos_in == "position_ids" and sess.kv_in == ["past_key_values.0.key", "past_key_values.0.value"]
+    prompt = [3, 9, 27, 1, 14]
+    toks = sess.generate(prompt, 6)
+    assert len(toks) == 6 and all(0 <= t < 32 for t in toks)
+    full = GraphDecodeSession.from_dir(d)
+    logits = full.feed(prompt + toks[:-1])                      # one pass over everything
+    assert [int(torch.argmax(logits[len(prompt) - 1 + i])) for i in range(6)] == toks

@@ -1,0 +1,164 @@
+"""Generic ONNX graph execution over torch: small graphs built with the package's own protobuf writer."""
+import math
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from onnx_genai_b200.package import onnx_pb as pb
+from onnx_genai_b200.package.graph_executor import GraphExecutionError, GraphExecutor, as_component
+
+
+def T(name, arr):
+    arr = np.asarray(arr)
+    dt = {np.dtype("float32"): pb.FLOAT, np.dtype("int64"): pb.INT64, np.dtype("bool"): pb.BOOL, np.dtype("uint8"): pb.UINT8}[arr.dtype]
+    return pb.Tensor(name=name, dims=tuple(arr.shape), data_type=dt, array=arr)
+
+
+def model(nodes, inits, inputs, outputs, tmp_path=None):
+    g = pb.Graph(name="g", nodes=nodes, initializers={t.name: t for t in inits},
+                 inputs=[pb.ValueInfo(n, dt, shape) for n, dt, shape in inputs], outputs=[pb.ValueInfo(n, pb.FLOAT, ()) for n in outputs])
+    m = pb.Model(graph=g)
+    if tmp_path is not None:                     # through the wire format and back
+        path = str(tmp_path / "m.onnx")
+        pb.save_model(m, path, external_data=False)
+        return path
+    return m
+
+
+def N(op, ins, outs, domain="", **attrs):
+    return pb.Node(op_type=op, inputs=list(ins), outputs=list(outs), name=outs[0], domain=domain, attrs=attrs)
+
+
+def test_mlp_block_round_trips_through_the_wire_format(tmp_path):
+    rng = np.random.default_rng(0)
+    w1, b1 = rng.standard_normal((16, 8)).astype(np.float32), rng.standard_normal(16).astype(np.float32)
+    w2 = rng.standard_normal((16, 4)).astype(np.float32)
+    gam, bet = rng.standard_normal(16).astype(np.float32), rng.standard_normal(16).astype(np.float32)
+    path = model([N("Gemm", ["x", "w1", "b1"], ["h"], transB=1, alpha=1.0, beta=1.0), N("Gelu", ["h"], ["a"], domain="com.microsoft"),
+                  N("LayerNormalization", ["a", "gam", "bet"], ["n"], axis=-1, epsilon=1e-5), N("MatMul", ["n", "w2"], ["l"]),
+                  N("Softmax", ["l"], ["p"], axis=-1)],
+                 [T("w1", w1), T("b1", b1), T("w2", w2), T("gam", gam), T("bet", bet)], [("x", pb.FLOAT, ("b", 8))], ["p"], tmp_path)
+    ex = GraphExecutor(path)
+    x = torch.randn(5, 8)
+    got = ex.run({"x": x})["p"]
+    h = F.gelu(x @ torch.from_numpy(w1).T + torch.from_numpy(b1))
+    want = torch.softmax(F.layer_norm(h, (16,), torch.from_numpy(gam), torch.from_numpy(bet), 1e-5) @ torch.from_numpy(w2), -1)
+    assert torch.allclose(got, want, atol=1e-5) and ex.input_names == ["x"] and ex.output_names == ["p"]
+    with pytest.raises(GraphExecutionError, match="missing graph input"):
+        ex.run({})
+
+
+def test_convolutional_stack():
+    rng = np.random.default_rng(1)
+    w = rng.standard_normal((6, 3, 3, 3)).astype(np.float32) * 0.3
+    b = rng.standard_normal(6).astype(np.float32)
+    bn = [np.abs(rng.standard_normal(6)).astype(np.float32) + 0.5 for _ in range(4)]
+    wt = rng.standard_normal((6, 2, 2, 2)).astype(np.float32) * 0.3
+    m = model([N("Conv", ["x", "w", "b"], ["c"], kernel_shape=[3, 3], pads=[1, 1, 1, 1], strides=[2, 2]),
+               N("BatchNormalization", ["c", "s", "bb", "mean", "var"], ["n"], epsilon=1e-5), N("Relu", ["n"], ["r"]),
+               N("MaxPool", ["r"], ["p"], kernel_shape=[2, 2], strides=[2, 2]),
+               N("ConvTranspose", ["p", "wt"], ["u"], kernel_shape=[2, 2], strides=[2, 2]),
+               N("Resize", ["u", "", "scales"], ["z"], mode="nearest"),
+               N("GroupNormalization", ["z", "gs", "gb"], ["gn"], num_groups=1, epsilon=1e-5),
+               N("GlobalAveragePool", ["gn"], ["g"]), N("Flatten", ["g"], ["f"], axis=1)],
+              [T("w", w), T("b", b), T("s", bn[0]), T("bb", bn[1]), T("mean", bn[2]), T("var", bn[3]), T("wt", wt),
+               T("scales", np.asarray([1, 1, 2, 2], np.float32)), T("gs", np.ones(2, np.float32)), T("gb", np.zeros(2, np.float32))],
+              [("x", pb.FLOAT, (1, 3, 16, 16))], ["f", "z"])
+    x = torch.randn(2, 3, 16, 16)
+    out = GraphExecutor(m).run({"x": x})
+    tt = torch.from_numpy
+    c = F.conv2d(x, tt(w), tt(b), stride=2, padding=1)
+    r = F.relu(F.batch_norm(c, tt(bn[2]), tt(bn[3]), tt(bn[0]), tt(bn[1]), False, 0.0, 1e-5))
+    u = F.conv_transpose2d(F.max_pool2d(r, 2, 2), tt(wt), stride=2)
+    z = F.interpolate(u, scale_factor=2.0, mode="nearest")
+    assert torch.allclose(out["z"], z, atol=1e-5) and out["z"].shape == (2, 2, 16, 16)
+    assert torch.allclose(out["f"], F.group_norm(z, 1).mean((2, 3)), atol=1e-5)
+
+
+def test_attention_shaped_graph_with_shape_ops():
+    """Single-head attention written with the shape plumbing exporters emit: Shape / Gather / Unsqueeze / Concat / Reshape,
+    Transpose, a causal mask from Trilu + Where, Slice with a negative step and Split."""
+    d = 8
+    rng = np.random.default_rng(2)
+    wqkv = rng.standard_normal((d, 3 * d)).astype(np.float32) * 0.3
+    nodes = [N("MatMul", ["x", "wqkv"], ["qkv"]), N("Split", ["qkv"], ["q", "k", "v"], axis=-1),
+             N("Transpose", ["k"], ["kt"], perm=[0, 2, 1]), N("MatMul", ["q", "kt"], ["s0"]),
+             N("Constant", [], ["scale"], value=T("", np.asarray(1.0 / math.sqrt(d), np.float32))), N("Mul", ["s0", "scale"], ["s"]),
+             N("Shape", ["x"], ["shp"]), N("Gather", ["shp", "one"], ["t"], axis=0), N("Unsqueeze", ["t", "zero_ax"], ["t1"]),
+             N("Concat", ["t1", "t1"], ["tt"], axis=0), N("ConstantOfShape", ["tt"], ["ones"], value=T("", np.asarray([1.0], np.float32))),
+             N("Trilu", ["ones"], ["low"], upper=0), N("Cast", ["low"], ["mask"], to=pb.BOOL),
+             N("Constant", [], ["neg"], value=T("", np.asarray(-1e9, np.float32))), N("Where", ["mask", "s", "neg"], ["sm"]),
+             N("Softmax", ["sm"], ["p"], axis=-1), N("MatMul", ["p", "v"], ["o"]),
+             N("Slice", ["o", "st", "en", "ax", "step"], ["rev"]), N("ReduceMean", ["rev"], ["m"], axes=[-1], keepdims=0)]
+    m = model(nodes, [T("wqkv", wqkv), T("one", np.asarray(1, np.int64)), T("zero_ax", np.asarray([0], np.int64)),
+                      T("st", np.asarray([-1], np.int64)), T("en", np.asarray([-(2 ** 62)], np.int64)), T("ax", np.asarray([1], np.int64)),
+                      T("step", np.asarray([-1], np.int64))], [("x", pb.FLOAT, ("b", "t", d))], ["o", "rev", "m"])
+    x = torch.randn(2, 5, d)
+    out = GraphExecutor(m).run({"x": x})
+    q, k, v = (x @ torch.from_numpy(wqkv)).split(d, -1)
+    want = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+    assert torch.allclose(out["o"], want, atol=1e-5)
+    assert torch.allclose(out["rev"], want.flip(1), atol=1e-5) and torch.allclose(out["m"], want.flip(1).mean(-1), atol=1e-5)
+
+
+def test_matmul_nbits_against_explicit_dequantisation():
+    rng = np.random.default_rng(3)
+    n, k, block = 6, 64, 32
+    q = rng.integers(0, 16, size=(n, k)).astype(np.uint8)
+    packed = (q[:, 0::2] | (q[:, 1::2] << 4)).reshape(n, k // block, block // 2)
+    scales = (rng.random((n, k // block)).astype(np.float32) + 0.1) * 0.1
+    zp_q = rng.integers(0, 16, size=(n, k // block)).astype(np.uint8)
+    zp = (zp_q[:, 0::2] | (zp_q[:, 1::2] << 4))
+    m = model([N("MatMulNBits", ["x", "B", "s", "zp"], ["y"], domain="com.microsoft", K=k, N=n, bits=4, block_size=block)],
+              [T("B", packed), T("s", scales.reshape(-1)), T("zp", zp.reshape(-1))], [("x", pb.FLOAT, ("m", k))], ["y"])
+    x = torch.randn(3, k)
+    got = GraphExecutor(m).run({"x": x})["y"]
+    w = (q.reshape(n, k // block, block).astype(np.float32) - zp_q[..., None]) * scales[..., None]
+    assert torch.allclose(got, x @ torch.from_numpy(w.reshape(n, k)).T, atol=1e-4)
+
+
+def test_errors_name_the_operator_or_the_node():
+    with pytest.raises(GraphExecutionError, match="outside the covered set: NonMaxSuppression"):
+        GraphExecutor(model([N("NonMaxSuppression", ["x"], ["y"])], [], [("x", pb.FLOAT, (1,))], ["y"]))
+    ex = GraphExecutor(model([N("MatMul", ["x", "w"], ["y"])], [T("w", np.zeros((3, 2), np.float32))], [("x", pb.FLOAT, ("b", 4))], ["y"]))
+    with pytest.raises(GraphExecutionError, match=r"node 'y' \(MatMul\) failed on inputs \[\(2, 4\), \(3, 2\)\]"):
+        ex.run({"x": torch.zeros(2, 4)})
+    with pytest.raises(GraphExecutionError, match="never produced"):
+        GraphExecutor(model([N("Relu", ["nowhere"], ["y"])], [], [("x", pb.FLOAT, (1,))], ["y"]))
+
+
+def test_onnx_policy_graphs_as_workflow_components(tmp_path):
+    """The imported ComfyUI document run with its policy components as ONNX graphs (Euler step, guidance, predicate)."""
+    from onnx_genai_b200.engine.workflow_runtime import run_workflow
+    from onnx_genai_b200.package.comfyui import import_comfyui
+    from test_comfyui_cpu import GRAPH
+
+    sig = np.linspace(1.0, 0.0, 21).astype(np.float32)
+    one = T("one", np.asarray([1], np.int64))
+    solver = model([N("Gather", ["schedule", "step"], ["s0"], axis=0), N("Add", ["step", "one"], ["nx"]), N("Gather", ["schedule", "nx"], ["s1"], axis=0),
+                    N("Sub", ["s1", "s0"], ["dt"]), N("Reshape", ["dt", "shape"], ["dt4"]), N("Mul", ["dt4", "derivative"], ["upd"]),
+                    N("Add", ["sample", "upd"], ["next_state"])], [one, T("shape", np.asarray([1, 1, 1, 1], np.int64))],
+                   [("sample", pb.FLOAT, ()), ("step", pb.INT64, (1,)), ("schedule", pb.FLOAT, (21,)), ("derivative", pb.FLOAT, ())], ["next_state"])
+    guidance = model([N("Sub", ["conditional", "unconditional"], ["d"]), N("Mul", ["d", "scale"], ["sd"]), N("Add", ["unconditional", "sd"], ["guided"])],
+                     [], [("conditional", pb.FLOAT, ()), ("unconditional", pb.FLOAT, ()), ("scale", pb.FLOAT, (1,))], ["guided"])
+    predicate = model([N("Not", ["done"], ["continue"])], [], [("done", pb.BOOL, (1,))], ["continue"])
+    schedule = model([N("Identity", ["sig"], ["schedule"])], [T("sig", sig)], [], ["schedule"])
+    comps = {"solver_step": as_component(solver), "guidance": as_component(guidance), "continue_predicate": as_component(predicate),
+             "schedule": as_component(schedule),
+             "text_encoder": lambda p: {"encoder_hidden_states": torch.as_tensor(p["input_ids"]).float() / 10.0},
+             "denoiser": lambda p: {"noise_pred": torch.as_tensor(p["sample"]) * 0.5 + torch.as_tensor(p["encoder_hidden_states"]).mean()},
+             "vae_decoder": lambda p: {"image": p["latent"][:, :3]}}
+    noise = torch.randn(1, 4, 8, 8)
+    pos, neg = np.array([[1, 2, 3]]), np.array([[4, 5, 6]])
+    g = {k: ({**v, "inputs": {**v["inputs"], "width": 64, "height": 64, "batch_size": 1}} if v["class_type"] == "EmptyLatentImage" else v)
+         for k, v in GRAPH.items()}
+    out = run_workflow(import_comfyui(g), comps, {"request.positive_ids": pos, "request.negative_ids": neg, "request.noise": noise})
+    x = noise.clone()
+    cp, cn = float((pos / 10.0).mean()), float((neg / 10.0).mean())
+    for i in range(20):
+        d = (x * 0.5 + cn) + 8.0 * ((x * 0.5 + cp) - (x * 0.5 + cn))
+        x = x + float(sig[i + 1] - sig[i]) * d
+    assert torch.allclose(out["image"], x[:, :3], atol=1e-4)
+    assert comps["solver_step"].executor.runs == 20
