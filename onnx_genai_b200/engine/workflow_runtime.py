@@ -30,6 +30,10 @@ import numpy as np
 from ..metadata import workflow as wfm
 
 
+_NP_DTYPE = {"float32": np.float32, "float16": np.float16, "float64": np.float64, "int64": np.int64, "int32": np.int32, "bool": np.bool_,
+             "uint8": np.uint8, "int8": np.int8}
+
+
 class WorkflowRuntimeError(RuntimeError):
     pass
 
@@ -153,22 +157,26 @@ class WorkflowSession:
         unknown = sorted(set(inputs) - set(self.wf.inputs))
         if unknown:
             raise WorkflowRuntimeError(f"unknown input(s) {', '.join(unknown)}; the workflow declares {', '.join(sorted(self.wf.inputs))}")
-        # rows of the request: the leading extent of the first supplied input whose contract starts with a symbolic dimension
+        # rows of the request: the extent of the request-aligned axis of the first supplied input that declares one
+        # (documents without batch layouts: the leading extent of an input whose contract starts with a symbolic dimension)
         self._batch = 1
         for name, spec in self.wf.inputs.items():
-            shape = spec["contract"].shape
-            if name in inputs and shape and isinstance(shape[0], str) and hasattr(inputs[name], "shape") and len(inputs[name].shape):
-                self._batch = int(inputs[name].shape[0])
+            c = spec["contract"]
+            axis = c.batch_axis if c.batch_axis is not None else (0 if c.shape and isinstance(c.shape[0], str) else None)
+            if name in inputs and axis is not None and hasattr(inputs[name], "shape") and len(inputs[name].shape) > axis:
+                self._batch = int(inputs[name].shape[axis])
                 break
         for name, spec in self.wf.inputs.items():
             if name in inputs:
                 root.set(name, inputs[name])
             elif spec.get("default") is not None:
-                default, shape = spec["default"], spec["contract"].shape
+                default, c = spec["default"], spec["contract"]
                 if np.isscalar(default) or isinstance(default, bool):
-                    # a scalar default of a per-row input stands for every row of the request
-                    rows = self._batch if shape and isinstance(shape[0], str) else 1
-                    default = np.full((rows,), default)
+                    # a scalar default fills the contract's shape: the request-aligned axis takes one entry per row of the
+                    # request, other symbolic extents take one entry
+                    axis = c.batch_axis if c.batch_axis is not None else (0 if c.shape and c.shape[0] == "batch" else None)
+                    dims = [self._batch if i == axis else (d if isinstance(d, int) else 1) for i, d in enumerate(c.shape)] or [1]
+                    default = np.full(tuple(dims), default, dtype=_NP_DTYPE.get(c.dtype))
                 root.set(name, default)
             elif spec["required"]:
                 raise WorkflowRuntimeError(f"required input '{name}' was not supplied")

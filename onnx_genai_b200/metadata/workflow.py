@@ -38,6 +38,7 @@ class Contract:
     rank: int | None = None
     shape: list = field(default_factory=list)
     optional: bool = False
+    batch_axis: int | None = None     # axis aligned with the rows of the request (batch_layout: request_aligned), if any
 
 
 @dataclass
@@ -128,7 +129,10 @@ def _contract(d, where) -> Contract:
         return Contract()
     if not isinstance(d, dict):
         raise WorkflowError(f"{where}: a tensor contract must be a mapping with dtype / rank / shape")
-    return Contract(dtype=str(d.get("dtype", "")), rank=d.get("rank"), shape=list(d.get("shape") or []), optional=bool(d.get("optional", False)))
+    layout = d.get("batch_layout")
+    axis = int(layout.get("axis", 0)) if isinstance(layout, dict) and layout.get("kind") == "request_aligned" else None
+    return Contract(dtype=str(d.get("dtype", "")), rank=d.get("rank"), shape=list(d.get("shape") or []), optional=bool(d.get("optional", False)),
+                    batch_axis=axis)
 
 
 def _step(d, where) -> Step:

@@ -167,6 +167,9 @@ def _dtype(v) -> int:
     return _DTYPES[_str(v)]
 
 
+_BASE_DIR: list = [None]      # directory of the file being read, for tensors stored as external data
+
+
 def _tensor(msg) -> pb.Tensor:
     t = pb.Tensor(name=_str(_one(msg, "name", b"")), dims=tuple(int(d) for d in msg.get("dims", [])), data_type=_dtype(_one(msg, "data_type")))
     npdt = pb._NP.get(t.data_type)
@@ -174,7 +177,19 @@ def _tensor(msg) -> pb.Tensor:
         raise TextFormatError(f"tensor {t.name!r}: unsupported ONNX data type {t.data_type}")
     count = int(np.prod(t.dims)) if t.dims else 1
     raw = _one(msg, "raw_data")
-    if raw is not None:
+    if "external_data" in msg:
+        import os
+
+        ext = {_str(_one(e, "key", b"")): _str(_one(e, "value", b"")) for e in msg["external_data"]}
+        if _BASE_DIR[0] is None:
+            raise TextFormatError(f"tensor {t.name!r} is stored as external data ({ext.get('location')}), but the text was parsed "
+                                  "without a directory to resolve it against; use load_model_text(path)")
+        path = os.path.join(_BASE_DIR[0], ext["location"])
+        if not os.path.exists(path):
+            raise TextFormatError(f"tensor {t.name!r}: external data file {path} does not exist")
+        t.external = ext
+        t.array = np.fromfile(path, dtype=npdt, count=count, offset=int(ext.get("offset", 0) or 0)).reshape(t.dims)
+    elif raw is not None:
         t.array = np.frombuffer(bytes(raw), dtype=npdt, count=count).reshape(t.dims)
     elif "float_data" in msg:
         t.array = np.asarray(msg["float_data"], dtype=np.float32).reshape(t.dims)
@@ -249,8 +264,15 @@ def parse_model_text(text: str) -> pb.Model:
 
 
 def load_model_text(path: str) -> pb.Model:
+    import os
+
     with open(path, encoding="utf-8") as f:
-        return parse_model_text(f.read())
+        text = f.read()
+    _BASE_DIR[0] = os.path.dirname(os.path.abspath(path))
+    try:
+        return parse_model_text(text)
+    finally:
+        _BASE_DIR[0] = None
 
 
 def load_any(path: str) -> pb.Model:

@@ -64,3 +64,16 @@ def test_text_syntax_corners_and_errors():
         parse_model_text("ir_version: 3")
     with pytest.raises(TextFormatError, match="unknown tensor data type"):
         parse_model_text('graph { initializer { data_type: QUATERNION name: "q" } }')
+
+
+def test_external_tensor_data_is_resolved_against_the_file(tmp_path):
+    np.arange(6, dtype=np.float32).tofile(tmp_path / "w.bin")
+    text = """graph { node { input: "x" input: "w" output: "y" op_type: "Add" }
+      initializer { dims: 2 data_type: 1 name: "w" data_location: EXTERNAL
+        external_data { key: "location" value: "w.bin" } external_data { key: "offset" value: "8" } }
+      input { name: "x" type { tensor_type { elem_type: 1 } } } output { name: "y" type { tensor_type { elem_type: 1 } } } }"""
+    (tmp_path / "m.onnx.textproto").write_text(text)
+    m = load_any(str(tmp_path / "m.onnx.textproto"))
+    assert m.graph.initializers["w"].array.tolist() == [2.0, 3.0]
+    with pytest.raises(TextFormatError, match="without a directory"):
+        parse_model_text(text)

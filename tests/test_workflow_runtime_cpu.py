@@ -142,7 +142,7 @@ def _synthetic_inputs(wf, rows=2):
 @pytest.mark.parametrize("name, outputs", [("diffusion", {"latent": (2, 4, 2, 2), "image": (2, 3, 2, 2)}),
                                            ("diffusion_guided", {"latent": (2, 4, 4, 4), "image": (2, 3, 4, 4)}),
                                            ("codec", {"waveform": (2, 1, 2)}), ("masked", {"tokens": (2, 2)}),
-                                           ("static_cache", {"logits": (2, 1, 8), "key_cache": (2, 8, 4)}), ("video", {})])
+                                           ("static_cache", {"logits": (2, 1, 8), "key_cache": (2, 8, 4)}), ("video", {}), ("decoder", {})])
 def test_upstream_workflow_packages_execute_end_to_end(name, outputs):
     """Whole packages of the upstream project -- text-format ONNX graphs for every model part and policy, wired by their
     workflow documents -- run unchanged: parsed, validated, every component on the generic graph executor."""
@@ -155,6 +155,8 @@ def test_upstream_workflow_packages_execute_end_to_end(name, outputs):
     flat = [v for val in out.values() for v in (val if isinstance(val, list) else [val])]
     assert flat and all(bool(torch.isfinite(torch.as_tensor(v).float()).all()) for v in flat)
     assert sess.stats["invocations"] and (name not in ("diffusion", "diffusion_guided") or sess.stats["iterations"] >= 3)
+    if name == "decoder":      # the whole token loop -- model, sampler, termination, cache bookkeeping -- is ONNX policy graphs
+        assert len(out["tokens"]) == 3 and sess.stats["invocations"]["token_sampler"] >= 3
     # a second run of the same session gives the same result (invocation-scoped state starts over)
     again = sess.run(_synthetic_inputs(sess.wf)) if name in ("codec", "static_cache") else None
     if again is not None:
