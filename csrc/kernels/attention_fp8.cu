@@ -27,37 +27,49 @@ constexpr int kRawPage = kPageTokens * kD;           // 2 KB of e4m3 per page si
 constexpr int kRawStage = 4 * 2 * kRawPage;          // 4 pages x (K, V) = 16 KB
 constexpr int kWorkPage = kPageTokens * kD * 2;      // 4 KB of bf16 per page side
 
+// One-byte values -> bf16 with integer and half-rate-free arithmetic only (no cvt instructions, which issue at a quarter
+// of the ALU rate and made the expansion, not HBM, the limit of these kernels).
+//
+// e4m3 (s eeee mmm, bias 7): the seven magnitude bits dropped at bit 4 of a bf16 (s eeeeeeee mmmmmmm, bias 127) read as the
+// same number times 2^-120 -- for subnormals too, which land on bf16 subnormals -- so one exact multiply by 2^120 finishes
+// the conversion.  Input word t holds the two bytes at bits 15:8 and 31:24.
+OGB_DEVICE uint32_t e4m3x2_to_bf16x2(uint32_t t) {
+  uint32_t bits = (t & 0x80008000u) | ((t >> 4) & 0x07f007f0u);
+  const uint32_t two120 = 0x7B807B80u;
+  __nv_bfloat162 v = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&bits), *reinterpret_cast<const __nv_bfloat162*>(&two120));
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// int8 (two's complement): with u = low seven bits, bf16(128 + u) is 0x4300 | u exactly, and the value is that minus
+// 128 (byte >= 0) or 256 (byte < 0), i.e. minus bf16 bits 0x4300 | (byte & 0x80).  Input word t holds the two bytes at
+// bits 7:0 and 23:16.
+OGB_DEVICE uint32_t i8x2_to_bf16x2(uint32_t t) {
+  uint32_t x = 0x43004300u | (t & 0x007f007fu);
+  uint32_t c = 0x43004300u | (t & 0x00800080u);
+  __nv_bfloat162 v = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&x), *reinterpret_cast<__nv_bfloat162*>(&c));
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
 // 16 e4m3 bytes -> 16 bf16, as two 16-byte vectors
 OGB_DEVICE void cvt16_e4m3_bf16(const uint4& raw, uint4& lo, uint4& hi) {
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
   uint32_t o[8];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const __nv_fp8x2_storage_t pair = static_cast<__nv_fp8x2_storage_t>((w[i] >> (16 * h)) & 0xffffu);
-      const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(pair, __NV_E4M3);
-      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
-      o[2 * i + h] = pack_bf16(f.x, f.y);
-    }
+    o[2 * i] = e4m3x2_to_bf16x2(__byte_perm(w[i], 0, 0x1404));       // bytes 0, 1 -> bits 15:8, 31:24
+    o[2 * i + 1] = e4m3x2_to_bf16x2(__byte_perm(w[i], 0, 0x3424));   // bytes 2, 3
   }
   lo = make_uint4(o[0], o[1], o[2], o[3]);
   hi = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
-// 16 int8 bytes -> 16 bf16 (exact: |v| <= 127 fits bf16's 8 significant bits)
+// 16 int8 bytes -> 16 bf16 (exact: |v| <= 128 fits bf16's 8 significant bits)
 OGB_DEVICE void cvt16_i8_bf16(const uint4& raw, uint4& lo, uint4& hi) {
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
   uint32_t o[8];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const uint32_t pair = (w[i] >> (16 * h)) & 0xffffu;
-      const float a = static_cast<float>(static_cast<int8_t>(pair & 0xffu));
-      const float b = static_cast<float>(static_cast<int8_t>(pair >> 8));
-      o[2 * i + h] = pack_bf16(a, b);
-    }
+    o[2 * i] = i8x2_to_bf16x2(__byte_perm(w[i], 0, 0x4140));         // bytes 0, 1 -> bits 7:0, 23:16
+    o[2 * i + 1] = i8x2_to_bf16x2(__byte_perm(w[i], 0, 0x4342));     // bytes 2, 3
   }
   lo = make_uint4(o[0], o[1], o[2], o[3]);
   hi = make_uint4(o[4], o[5], o[6], o[7]);

@@ -142,6 +142,36 @@ def bench_attention(timer, pk):
     return rows
 
 
+def bench_attention_one_byte(timer, pk):
+    """Decode attention over one-byte KV pages (e4m3 and int8): same contexts as the bf16 rows, half the bytes."""
+    rows = []
+    hq, hkv, d = 28, 4, 128
+    for fmt, dtype in (("fp8", torch.uint8), ("int8", torch.int8)):
+        for n, ctx, splits in [(256, 1200, 1), (256, 2304, 2), (64, 8192, 8), (8, 32768, 16)]:
+            pages_per = (ctx + 15) // 16
+            total = n * pages_per
+            if fmt == "fp8":
+                pool = (torch.randn(total, hkv, 2, 16, d, device="cuda") * 0.5).to(torch.float8_e4m3fn).view(torch.uint8)
+            else:
+                pool = torch.randint(-127, 128, (total, hkv, 2, 16, d), device="cuda", dtype=torch.int8)
+            scales = torch.rand(total, hkv, 2, device="cuda") * 0.02 + 0.005
+            table = torch.randperm(total, device="cuda").to(torch.int32).view(n, pages_per)
+            ctx_t = torch.full((n,), ctx, dtype=torch.int32, device="cuda")
+            q = torch.randn(n, (hq + 2 * hkv) * d, device="cuda").bfloat16()
+            out = torch.empty(n, hq * d, device="cuda", dtype=torch.bfloat16)
+            po = torch.empty(n * hq * splits * d, dtype=torch.float32, device="cuda")
+            pm = torch.empty(n * hq * splits * 2, dtype=torch.float32, device="cuda")
+            med, _ = timer.time(lambda: ops.paged_decode(q, out, pool, table, ctx_t, hq, hkv, d, num_splits=splits, part_o=po, part_ml=pm,
+                                                         kv_scales=scales))
+            byts = float(n) * ctx * hkv * 2 * d
+            rows.append({"kernel": "paged_decode_" + fmt, "seqs": n, "ctx": ctx, "splits": splits, "ms": round(med, 4),
+                         "gbs": round(byts / med / 1e6, 1), "frac_of_%s_hbm" % pk["source"]: round(byts / med / 1e6 / pk["hbm_gbs"], 3)})
+            print(json.dumps(rows[-1]), flush=True)
+            del pool
+    ops.check_status()
+    return rows
+
+
 def bench_misc(timer, pk):
     rows = []
     x = torch.randn(1280, 3584, device="cuda").bfloat16()
@@ -252,7 +282,7 @@ def ncu_case(name: str, iters: int = 3):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ncu-case", default="", help="run one small single-kernel workload (for ncu) and exit")
-    ap.add_argument("--what", default="gemm,attn,misc")
+    ap.add_argument("--what", default="gemm,attn,misc", help="comma list of gemm, attn, attn8 (one-byte KV pages), misc")
     ap.add_argument("--json", default="")
     args = ap.parse_args()
     if args.ncu_case:
@@ -265,6 +295,8 @@ def main():
         res["gemm"] = bench_gemm(timer, pk)
     if "attn" in what:
         res["attn"] = bench_attention(timer, pk)
+    if "attn8" in what:
+        res["attn8"] = bench_attention_one_byte(timer, pk)
     if "misc" in what:
         res["misc"] = bench_misc(timer, pk)
     if args.json:
