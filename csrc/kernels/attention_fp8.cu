@@ -199,16 +199,27 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_fp8_kernel(const __
   int stage = 0;
   uint32_t phase = 0;
   bool ok = true;
+  // The scales of a page sit behind two dependent global loads (page table, then scale table).  They are fetched one
+  // block ahead so that their latency overlaps the expansion and the MMAs of the current block instead of stalling it.
+  float ks_next, vs_next;
+  {
+    const int64_t page = page_of(p, seq, ctx, b_begin * 4 + warp);
+    ks_next = p.kv_scales[(page * p.hkv + kvh) * 2];
+    vs_next = p.kv_scales[(page * p.hkv + kvh) * 2 + 1];
+  }
   for (int b = b_begin; b < b_end; ++b) {
+    const float ks = ks_next * p.scale_log2e, vs = vs_next;
+    if (b + 1 < b_end) {
+      const int64_t page = page_of(p, seq, ctx, (b + 1) * 4 + warp);
+      ks_next = p.kv_scales[(page * p.hkv + kvh) * 2];
+      vs_next = p.kv_scales[(page * p.hkv + kvh) * 2 + 1];
+    }
     if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], phase))) { ok = false; break; }
     const int tok0 = b * kKvBlock + 16 * warp;
     if (tok0 < ctx) {
       const uint8_t* raw = stages + stage * kRawStage;
       expand_page(raw + warp * kRawPage, wk, lane, 32, p.kv_fmt);
       expand_page(raw + (4 + warp) * kRawPage, wv, lane, 32, p.kv_fmt);
-      const int64_t page = page_of(p, seq, ctx, b * 4 + warp);
-      const float ks = p.kv_scales[(page * p.hkv + kvh) * 2] * p.scale_log2e;
-      const float vs = p.kv_scales[(page * p.hkv + kvh) * 2 + 1];
       __syncwarp();
       float s[2][4];
       s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
