@@ -309,6 +309,76 @@ def cmd_serve(args, profiler):
     return 0
 
 
+def cmd_run_workflow(args) -> int:
+    """Run a multi-model package outside the token engine: diffusion, codec, video and policy-only workflows whose
+    components are ONNX graphs.  Prints one JSON line with the shape of every output."""
+    import numpy as np
+
+    from .engine.workflow_runtime import WorkflowRuntimeError, WorkflowSession
+
+    feeds = {}
+    for item in args.input:
+        name, sep, value = item.partition("=")
+        if not sep:
+            print(f"run-workflow: --input wants NAME=VALUE, got {item!r}", file=sys.stderr)
+            return 2
+        if value.endswith(".npy"):
+            feeds[name] = np.load(value)
+        elif value.startswith("ids:"):
+            feeds[name] = np.asarray([[int(t) for t in value[4:].split(",") if t]], dtype=np.int64)
+        else:
+            try:
+                feeds[name] = np.asarray(json.loads(value))
+            except ValueError:
+                print(f"run-workflow: cannot read the value of {name!r}: {value!r} is neither a .npy file, ids:..., nor JSON", file=sys.stderr)
+                return 2
+            if feeds[name].ndim == 0:
+                feeds[name] = feeds[name].reshape(1)
+    try:
+        sess = WorkflowSession.from_package(args.package, device=args.device)
+        out = sess.run(feeds)
+    except WorkflowRuntimeError as e:
+        print(f"run-workflow: {e}", file=sys.stderr)
+        return 1
+    summary = {}
+    if args.out:
+        os.makedirs(args.out, exist_ok=True)
+    for name, value in out.items():
+        vals = value if isinstance(value, list) else [value]
+        arrs = [np.asarray(v.detach().cpu() if hasattr(v, "detach") else v) for v in vals]
+        summary[name] = [list(a.shape) for a in arrs] if isinstance(value, list) else list(arrs[0].shape)
+        if args.out:
+            arr = np.stack(arrs) if isinstance(value, list) and len({a.shape for a in arrs}) == 1 else arrs[-1]
+            np.save(os.path.join(args.out, name + ".npy"), arr)
+            last = arrs[-1]
+            if last.ndim == 4 and last.shape[1] in (1, 3) and name in ("image", "images"):      # NCHW in [-1, 1] or [0, 1]
+                _save_png(os.path.join(args.out, name + ".png"), last[0])
+    print(json.dumps({"outputs": summary, "invocations": sess.stats["invocations"], "iterations": sess.stats["iterations"]}))
+    return 0
+
+
+def _save_png(path: str, chw) -> None:
+    """Minimal PNG writer (8-bit RGB or grey), so image workflows need no imaging library."""
+    import struct
+    import zlib
+
+    import numpy as np
+
+    x = np.asarray(chw, dtype=np.float32)
+    lo = -1.0 if x.min() < 0 else 0.0
+    x = np.clip((x - lo) / (1.0 - lo), 0.0, 1.0)
+    img = (x * 255.0 + 0.5).astype(np.uint8).transpose(1, 2, 0)
+    h, w, c = img.shape
+    raw = b"".join(b"\x00" + img[r].tobytes() for r in range(h))
+
+    def chunk(tag, data):
+        return struct.pack(">I", len(data)) + tag + data + struct.pack(">I", zlib.crc32(tag + data) & 0xFFFFFFFF)
+
+    with open(path, "wb") as f:
+        f.write(b"\x89PNG\r\n\x1a\n" + chunk(b"IHDR", struct.pack(">IIBBBBB", w, h, 8, 2 if c == 3 else 0, 0, 0, 0)) +
+                chunk(b"IDAT", zlib.compress(raw, 6)) + chunk(b"IEND", b""))
+
+
 def cmd_show(args, profiler):
     from . import package as pkg
     from .package import onnx_pb
@@ -493,7 +563,15 @@ def main(argv=None):
     ic = sub.add_parser("import-comfyui", help="convert a ComfyUI API-format graph into a workflow metadata document")
     ic.add_argument("graph")
     ic.add_argument("-o", "--out", default="-")
+    rw = sub.add_parser("run-workflow", help="run a workflow package (every ONNX component on the generic graph executor)")
+    rw.add_argument("package", help="directory with inference_metadata.yaml and the component graphs")
+    rw.add_argument("--input", action="append", default=[], metavar="NAME=VALUE",
+                    help="a workflow input: a .npy file, a JSON literal (3, [1,2], 0.5) or ids:1,2,3 for a row of token ids")
+    rw.add_argument("--out", default="", help="directory for the outputs (one .npy per output, .png for image outputs)")
+    rw.add_argument("--device", default="cpu")
     args = ap.parse_args(argv)
+    if args.cmd == "run-workflow":
+        return cmd_run_workflow(args)
     if args.cmd == "import-comfyui":
         from .package.comfyui import main as comfy_main
         return comfy_main([args.graph, "-o", args.out])

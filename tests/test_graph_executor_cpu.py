@@ -162,3 +162,79 @@ def test_onnx_policy_graphs_as_workflow_components(tmp_path):
         x = x + float(sig[i + 1] - sig[i]) * d
     assert torch.allclose(out["image"], x[:, :3], atol=1e-4)
     assert comps["solver_step"].executor.runs == 20
+
+
+def test_run_workflow_cli_on_a_package_written_to_disk(tmp_path):
+    """ComfyUI graph -> metadata document; every component an ONNX file written by this package's writer; run from the CLI."""
+    import json as _json
+    import struct
+    import zlib
+
+    import yaml
+
+    from onnx_genai_b200 import cli
+    from onnx_genai_b200.package.comfyui import import_comfyui
+    from test_comfyui_cpu import GRAPH
+
+    g = {k: ({**v, "inputs": {**v["inputs"], "width": 64, "height": 64, "batch_size": 1, }} if v["class_type"] == "EmptyLatentImage" else v)
+         for k, v in GRAPH.items()}
+    g["3"] = {**g["3"], "inputs": {**g["3"]["inputs"], "steps": 4}}
+    doc = import_comfyui(g)
+    pkg = tmp_path / "pkg"
+    sig = np.linspace(1.0, 0.0, 5).astype(np.float32)
+    one = T("one", np.asarray([1], np.int64))
+    graphs = {
+        "policies/solver_euler.onnx": model(
+            [N("Gather", ["schedule", "step"], ["s0"], axis=0), N("Add", ["step", "one"], ["nx"]), N("Gather", ["schedule", "nx"], ["s1"], axis=0),
+             N("Sub", ["s1", "s0"], ["dt"]), N("Reshape", ["dt", "shape"], ["dt4"]), N("Mul", ["dt4", "derivative"], ["upd"]),
+             N("Add", ["sample", "upd"], ["next_state"])], [one, T("shape", np.asarray([1, 1, 1, 1], np.int64))],
+            [("sample", pb.FLOAT, ()), ("step", pb.INT64, (1,)), ("schedule", pb.FLOAT, (5,)), ("derivative", pb.FLOAT, ())], ["next_state"]),
+        "policies/classifier_free_guidance.onnx": model(
+            [N("Sub", ["conditional", "unconditional"], ["d"]), N("Mul", ["d", "scale"], ["sd"]), N("Add", ["unconditional", "sd"], ["guided"])],
+            [], [("conditional", pb.FLOAT, ()), ("unconditional", pb.FLOAT, ()), ("scale", pb.FLOAT, (1,))], ["guided"]),
+        "policies/continue.onnx": model([N("Not", ["done"], ["continue"])], [], [("done", pb.BOOL, (1,))], ["continue"]),
+        "policies/schedule_karras.onnx": model([N("Identity", ["sig"], ["schedule"])], [T("sig", sig)], [], ["schedule"]),
+        "sd15/text_encoder.onnx": model([N("Cast", ["input_ids"], ["f"], to=pb.FLOAT), N("ReduceMean", ["f"], ["m"], axes=[1], keepdims=1),
+                                         N("Mul", ["m", "tenth"], ["encoder_hidden_states"])], [T("tenth", np.asarray(0.1, np.float32))],
+                                        [("input_ids", pb.INT64, ("b", "s"))], ["encoder_hidden_states"]),
+        "sd15/unet.onnx": model([N("Mul", ["sample", "half"], ["h"]), N("ReduceMean", ["encoder_hidden_states"], ["c"], keepdims=0),
+                                 N("Add", ["h", "c"], ["noise_pred"])], [T("half", np.asarray(0.5, np.float32))],
+                                [("sample", pb.FLOAT, ()), ("step", pb.INT64, (1,)), ("schedule", pb.FLOAT, (5,)),
+                                 ("encoder_hidden_states", pb.FLOAT, ())], ["noise_pred"]),
+        "sd15/vae_decoder.onnx": model([N("Slice", ["latent", "s", "e", "ax"], ["rgb"]), N("Resize", ["rgb", "", "scales"], ["big"], mode="nearest"),
+                                        N("Tanh", ["big"], ["image"])],
+                                       [T("s", np.asarray([0], np.int64)), T("e", np.asarray([3], np.int64)), T("ax", np.asarray([1], np.int64)),
+                                        T("scales", np.asarray([1, 1, 8, 8], np.float32))], [("latent", pb.FLOAT, ())], ["image"]),
+    }
+    for rel, m in graphs.items():
+        path = pkg / rel
+        path.parent.mkdir(parents=True, exist_ok=True)
+        pb.save_model(m, str(path), external_data=False)
+    (pkg / "inference_metadata.yaml").write_text(yaml.safe_dump(doc, sort_keys=False))
+    noise = np.random.default_rng(0).standard_normal((1, 4, 8, 8)).astype(np.float32)
+    np.save(tmp_path / "noise.npy", noise)
+    out_dir = tmp_path / "out"
+    import io
+    import contextlib
+
+    buf = io.StringIO()
+    with contextlib.redirect_stdout(buf):
+        rc = cli.main(["run-workflow", str(pkg), "--input", "request.positive_ids=ids:1,2,3", "--input", "request.negative_ids=ids:4,5,6",
+                       "--input", f"request.noise={tmp_path / 'noise.npy'}", "--out", str(out_dir)])
+    assert rc == 0
+    rep = _json.loads(buf.getvalue().strip().splitlines()[-1])
+    assert rep["outputs"] == {"image": [1, 3, 64, 64]} and rep["iterations"] == 4 and rep["invocations"]["denoiser"] == 8
+    x = noise.copy()
+    for i in range(4):
+        d = (x * 0.5 + 0.5) + 8.0 * ((x * 0.5 + 0.2) - (x * 0.5 + 0.5))
+        x = x + (sig[i + 1] - sig[i]) * d
+    want = np.tanh(np.repeat(np.repeat(x[:, :3], 8, 2), 8, 3))
+    assert np.allclose(np.load(out_dir / "image.npy"), want, atol=1e-4)
+    png = (out_dir / "image.png").read_bytes()
+    assert png[:8] == b"\x89PNG\r\n\x1a\n" and struct.unpack(">II", png[16:24]) == (64, 64)
+    idat = png[png.index(b"IDAT") + 4: png.index(b"IEND") - 8]
+    assert len(zlib.decompress(idat)) == 64 * (64 * 3 + 1)
+    # a missing input and a missing artifact are reported, not raised
+    assert cli.main(["run-workflow", str(pkg), "--input", "request.positive_ids=ids:1"]) == 1
+    (pkg / "sd15" / "unet.onnx").unlink()
+    assert cli.main(["run-workflow", str(pkg)]) == 1
