@@ -81,6 +81,15 @@ class _Scope:
         self.values[name] = value
 
 
+def _invoked_components(steps):
+    """Names of the components that the step tree calls."""
+    for s in steps:
+        if s.kind == "invoke":
+            yield s.component
+        for group in (s.steps, s.setup, list(s.cases.values()), [s.default] if s.default is not None else []):
+            yield from _invoked_components(group)
+
+
 class WorkflowSession:
     def __init__(self, workflow, components: dict, *, validate: bool = True):
         """``workflow``: a parsed :class:`Workflow`, or the mapping under ``pipeline.workflow``.  ``components``: name -> callable(dict) -> dict."""
@@ -116,12 +125,18 @@ class WorkflowSession:
         if wf is None:
             raise WorkflowRuntimeError(f"{package_dir}/{metadata_name} has no pipeline.workflow")
         bound = dict(components or {})
+        invoked = set(_invoked_components(wf.steps))
         for name, comp in wf.components.items():
-            if name in bound:
+            if name in bound or name not in invoked:      # a declared component that no step calls needs no implementation
+                continue
+            if comp.kind == "adapter" and comp.abi == "onnx-genai.image-preprocess" and ((doc.get("preprocessing") or {}).get("image")):
+                from ..preprocess import image_preprocess_adapter
+
+                bound[name] = image_preprocess_adapter(doc["preprocessing"]["image"], next(iter(comp.inputs), "encoded"))
                 continue
             if comp.kind != "onnx" or not comp.artifact:
-                raise WorkflowRuntimeError(f"component '{name}' is a '{comp.kind}' implementation, not an ONNX graph: pass a callable for it "
-                                           "in `components`")
+                raise WorkflowRuntimeError(f"component '{name}' is a '{comp.kind}' implementation{' (' + comp.abi + ')' if comp.abi else ''}, "
+                                           "not an ONNX graph: pass a callable for it in `components`")
             path = os.path.join(package_dir, comp.artifact)
             if not os.path.exists(path):
                 raise WorkflowRuntimeError(f"component '{name}': artifact {path} does not exist")
@@ -129,11 +144,7 @@ class WorkflowSession:
         return cls(wf, bound)
 
     def _invoked(self, steps):
-        for s in steps:
-            if s.kind == "invoke":
-                yield s.component
-            for group in (s.steps, s.setup, list(s.cases.values()), [s.default] if s.default is not None else []):
-                yield from self._invoked(group)
+        return _invoked_components(steps)
 
     # -- checkpoint / restore of session-scoped state ---------------------------------------------------
     def checkpoint(self) -> dict:

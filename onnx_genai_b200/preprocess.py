@@ -242,3 +242,121 @@ def log_mel_spectrogram(samples, sample_rate: int = 16000, n_fft: int = 400, hop
     log = torch.clamp(mel, min=1e-10).log10()
     log = torch.maximum(log, log.max() - 8.0)
     return (log + 4.0) / 4.0
+
+
+# ---------------------------------------------------------------------------------------------
+# declared transform programs (the ``preprocessing.image`` block of the inference metadata)
+# ---------------------------------------------------------------------------------------------
+def _round_half_even_to(value: int, multiple: int) -> int:
+    q, r = divmod(value, multiple)
+    if 2 * r > multiple or (2 * r == multiple and q % 2 == 1):
+        q += 1
+    return q * multiple
+
+
+def pixel_area_size(width: int, height: int, min_pixels: int, max_pixels: int, multiple: int):
+    """Target (width, height) of an area-bounded resize: both sides are multiples of ``multiple`` and the area lies in
+    [min_pixels, max_pixels] as far as rounding allows, keeping the aspect ratio -- the dynamic-resolution rule of
+    patch-based vision encoders (crates/onnx-genai-preprocess/src/image/transform.rs:42-70)."""
+    if not (0 < min_pixels <= max_pixels and multiple > 0):
+        raise PreprocessError("pixel_area resize needs 0 < min_pixels <= max_pixels and size_multiple > 0")
+    if max(width, height) / max(1, min(width, height)) > 200:
+        raise PreprocessError(f"pixel_area resize needs an aspect ratio of at most 200, got {width}x{height}")
+    w, h = _round_half_even_to(width, multiple), _round_half_even_to(height, multiple)
+    if w * h > max_pixels:
+        beta = math.sqrt(width * height / max_pixels)
+        h = max(1, math.floor(height / beta / multiple)) * multiple
+        w = max(1, math.floor(width / beta / multiple)) * multiple
+    elif w * h < min_pixels:
+        beta = math.sqrt(min_pixels / (width * height))
+        h = max(1, math.ceil(height * beta / multiple)) * multiple
+        w = max(1, math.ceil(width * beta / multiple)) * multiple
+    return w, h
+
+
+def decode_rgb(encoded) -> torch.Tensor:
+    """Encoded image bytes (PNG, JPEG, ...) -> uint8-valued float tensor [3, H, W]."""
+    import io
+
+    from PIL import Image
+
+    data = bytes(encoded.cpu().numpy().astype(np.uint8).tobytes()) if isinstance(encoded, torch.Tensor) else bytes(np.asarray(encoded, dtype=np.uint8).tobytes()) \
+        if not isinstance(encoded, (bytes, bytearray)) else bytes(encoded)
+    try:
+        img = Image.open(io.BytesIO(data)).convert("RGB")
+    except Exception as e:
+        raise PreprocessError(f"cannot decode the image ({len(data)} bytes): {e}") from e
+    return torch.from_numpy(np.asarray(img).copy()).permute(2, 0, 1).float()
+
+
+def run_declared_image_program(image, spec: dict) -> dict:
+    """Run the ``transforms`` of a ``preprocessing.image`` block on one image (encoded bytes, or an array [H, W, 3] /
+    [3, H, W]) and return its declared ``outputs`` by name.  Transforms name their inputs and outputs; covered operators:
+    ``decode_rgb``, ``resize`` (modes ``stretch`` and ``pixel_area``), ``rescale``, ``normalize``, ``patchify`` (with temporal
+    replication and merge windows) and ``emit_grid_coordinates``."""
+    values: dict = {}
+    source, last = image, None
+    for i, tr in enumerate(spec.get("transforms") or []):
+        op = tr.get("op")
+        ins = [values[n] for n in tr.get("inputs") or []]
+        x = ins[0] if ins else None
+        if op == "decode_rgb":
+            y = decode_rgb(source) if isinstance(source, (bytes, bytearray)) or (hasattr(source, "ndim") and source.ndim == 1) else _as_chw_float(source)
+        elif op == "resize":
+            _, h, w = x.shape
+            mode = tr.get("mode", "stretch")
+            if mode == "pixel_area":
+                nw, nh = pixel_area_size(w, h, int(tr["min_pixels"]), int(tr["max_pixels"]), int(tr["size_multiple"]))
+            elif mode == "stretch":
+                nh, nw = int(tr["height"]), int(tr["width"])
+            else:
+                raise PreprocessError(f"transform {i}: resize mode {mode!r} is not covered (stretch, pixel_area)")
+            y = _resize(x, nh, nw, tr.get("interpolation", "bilinear"))
+        elif op == "rescale":
+            y = x * float(tr["scale"])
+        elif op == "normalize":
+            mean = torch.tensor(tr["mean"], dtype=x.dtype)[:, None, None]
+            std = torch.tensor(tr["std"], dtype=x.dtype)[:, None, None]
+            y = (x - mean) / std
+        elif op == "patchify":
+            p, t, m = int(tr["patch_size"]), int(tr.get("temporal_patch_size", 1)), int(tr.get("merge_size", 1))
+            c, h, w = x.shape
+            if h % (p * m) or w % (p * m):
+                raise PreprocessError(f"transform {i}: a {h}x{w} image does not split into {p}-pixel patches in {m}x{m} windows; resize first")
+            gh, gw = h // p, w // p
+            frames = x[None].expand(t, c, h, w)                          # a still image fills every temporal slot
+            v = frames.reshape(1, t, c, gh // m, m, p, gw // m, m, p).permute(0, 3, 6, 4, 7, 2, 1, 5, 8)
+            y = v.reshape(gh * gw, c * t * p * p) if tr.get("flatten", True) else v.reshape(gh * gw, c, t, p, p)
+            values["__grid__"] = torch.tensor([[1, gh, gw]], dtype=torch.int64)
+        elif op == "emit_grid_coordinates":
+            if "__grid__" not in values:
+                raise PreprocessError(f"transform {i}: emit_grid_coordinates needs a patchify step before it")
+            y = values["__grid__"]
+        else:
+            raise PreprocessError(f"transform {i}: unknown operator {op!r}; covered: decode_rgb, resize, rescale, normalize, patchify, "
+                                  "emit_grid_coordinates")
+        for name in tr.get("outputs") or []:
+            values[name] = y
+        last = y
+    out = {}
+    for o in spec.get("outputs") or []:
+        if o.get("source") not in values:
+            raise PreprocessError(f"output {o.get('name')!r} reads {o.get('source')!r}, which no transform produced")
+        v = values[o["source"]]
+        want = (o.get("contract") or {}).get("shape")
+        if want and all(isinstance(d, int) for d in want) and list(v.shape) != list(want):
+            raise PreprocessError(f"output {o['name']!r} has shape {list(v.shape)} but its contract says {want}")
+        out[o["name"]] = v
+    if not out and last is not None:
+        out["pixel_values"] = last
+    return out
+
+
+def image_preprocess_adapter(spec: dict, input_port: str = "encoded"):
+    """A workflow component for the ``onnx-genai.image-preprocess`` adapter: encoded bytes in, the program's outputs out
+    (port names are the output names without their ``image.`` prefix)."""
+    def component(ports: dict) -> dict:
+        res = run_declared_image_program(ports[input_port], spec)
+        return {name.split(".", 1)[-1]: v for name, v in res.items()}
+
+    return component

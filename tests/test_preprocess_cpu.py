@@ -81,3 +81,40 @@ def test_wav_resample_and_log_mel():
         b"data" + struct.pack("<I", 8) + struct.pack("<ff", 0.25, -0.5)
     xs, r8 = pp.read_wav(float_wav)
     assert r8 == 8000 and np.allclose(xs, [0.25, -0.5])
+
+
+def test_declared_image_program_pixel_area_and_patch_layout():
+    import io
+
+    import numpy as np
+    import torch
+    from PIL import Image
+
+    from onnx_genai_b200.preprocess import PreprocessError, pixel_area_size, run_declared_image_program
+
+    # both sides multiples of 14, area inside the bounds when rounding allows, aspect kept
+    assert pixel_area_size(8, 8, 224, 224, 14) == (28, 28)              # too small: scaled up, rounded up
+    assert pixel_area_size(640, 480, 56 * 56, 28 * 28 * 16, 28) == (112, 84)
+    assert pixel_area_size(29, 43, 100, 10 ** 6, 14) == (28, 42)        # already inside: just rounded (ties to even multiples)
+    with pytest.raises(PreprocessError, match="aspect ratio"):
+        pixel_area_size(2, 1000, 4, 10 ** 6, 2)
+    spec = {"transforms": [{"op": "decode_rgb", "outputs": ["a"]},
+                           {"op": "resize", "mode": "pixel_area", "interpolation": "bicubic", "min_pixels": 784, "max_pixels": 784, "size_multiple": 14,
+                            "inputs": ["a"], "outputs": ["b"]},
+                           {"op": "rescale", "scale": 1 / 255, "inputs": ["b"], "outputs": ["c"]},
+                           {"op": "normalize", "mean": [0.5] * 3, "std": [0.5] * 3, "inputs": ["c"], "outputs": ["d"]},
+                           {"op": "patchify", "patch_size": 14, "temporal_patch_size": 2, "merge_size": 1, "flatten": True, "inputs": ["d"], "outputs": ["e"]},
+                           {"op": "emit_grid_coordinates", "inputs": ["e"], "outputs": ["g"]}],
+            "outputs": [{"name": "image.pixel_values", "source": "e", "contract": {"shape": [4, 1176]}}, {"name": "image.grid_thw", "source": "g"}]}
+    img = np.zeros((28, 28, 3), np.uint8)
+    img[:14, 14:, 0] = 255                                               # the top-right patch is pure red
+    buf = io.BytesIO()
+    Image.fromarray(img).save(buf, format="PNG")
+    out = run_declared_image_program(buf.getvalue(), spec)
+    assert out["image.grid_thw"].tolist() == [[1, 2, 2]] and out["image.pixel_values"].shape == (4, 1176)
+    p = out["image.pixel_values"].reshape(4, 3, 2, 14, 14)               # patch, channel, temporal slot, y, x
+    assert torch.allclose(p[1, 0], torch.ones(2, 14, 14)) and torch.allclose(p[1, 1], -torch.ones(2, 14, 14))
+    assert torch.allclose(p[0], -torch.ones(3, 2, 14, 14)) and torch.equal(p[:, :, 0], p[:, :, 1])
+    spec["outputs"][0]["contract"]["shape"] = [9, 1176]
+    with pytest.raises(PreprocessError, match="contract says"):
+        run_declared_image_program(buf.getvalue(), spec)

@@ -142,7 +142,9 @@ def _synthetic_inputs(wf, rows=2):
 @pytest.mark.parametrize("name, outputs", [("diffusion", {"latent": (2, 4, 2, 2), "image": (2, 3, 2, 2)}),
                                            ("diffusion_guided", {"latent": (2, 4, 4, 4), "image": (2, 3, 4, 4)}),
                                            ("codec", {"waveform": (2, 1, 2)}), ("masked", {"tokens": (2, 2)}),
-                                           ("static_cache", {"logits": (2, 1, 8), "key_cache": (2, 8, 4)}), ("video", {}), ("decoder", {})])
+                                           ("static_cache", {"logits": (2, 1, 8), "key_cache": (2, 8, 4)}), ("video", {}), ("decoder", {}),
+                                           ("speech_wav", {"audio": (2, 2, 64)}), ("speech_wav_mixed_audio", {"waveform": (2, 1, 64)}),
+                                           ("speech_wav_two_adapters", {"audio": (2, 2, 64)}), ("speech_wav_two_audio", {"audio": (2, 2, 64)})])
 def test_upstream_workflow_packages_execute_end_to_end(name, outputs):
     """Whole packages of the upstream project -- text-format ONNX graphs for every model part and policy, wired by their
     workflow documents -- run unchanged: parsed, validated, every component on the generic graph executor."""
@@ -165,5 +167,26 @@ def test_upstream_workflow_packages_execute_end_to_end(name, outputs):
 
 @pytest.mark.skipif(not os.path.isdir(FIXTURES), reason="the upstream workflow fixtures are not available on this machine")
 def test_packages_with_adapter_components_say_what_to_supply():
-    with pytest.raises(WorkflowRuntimeError, match="is a 'adapter' implementation, not an ONNX graph: pass a callable"):
+    with pytest.raises(WorkflowRuntimeError, match=r"is a 'adapter' implementation \(onnx-genai.parameter-overlay\), not an ONNX graph: pass a callable"):
         WorkflowSession.from_package(os.path.join(FIXTURES, "adapter"))
+
+
+@pytest.mark.skipif(not os.path.isdir(FIXTURES), reason="the upstream workflow fixtures are not available on this machine")
+def test_upstream_vision_language_package_runs_from_image_bytes():
+    """Encoded image -> declared preprocessing program (the image-preprocess adapter) -> vision encoder -> embedding merge ->
+    decoder loop with ONNX sampler and termination policies -> tokens."""
+    import io
+
+    import torch
+    from PIL import Image
+
+    sess = WorkflowSession.from_package(os.path.join(FIXTURES, "vlm"))
+    buf = io.BytesIO()
+    Image.fromarray((np.random.default_rng(0).random((8, 8, 3)) * 255).astype(np.uint8)).save(buf, format="PNG")
+    feeds = _synthetic_inputs(sess.wf)
+    feeds["request.image"] = torch.from_numpy(np.frombuffer(buf.getvalue(), dtype=np.uint8).copy())
+    out = sess.run(feeds)
+    assert len(out["tokens"]) == 3 and sess.stats["invocations"]["image_preprocess"] == 1 and sess.stats["invocations"]["vision_encoder"] == 1
+    feeds["request.image"] = torch.zeros(10, dtype=torch.uint8)
+    with pytest.raises(Exception, match="cannot decode the image"):
+        sess.run(feeds)
