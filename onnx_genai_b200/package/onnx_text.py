@@ -167,10 +167,7 @@ def _dtype(v) -> int:
     return _DTYPES[_str(v)]
 
 
-_BASE_DIR: list = [None]      # directory of the file being read, for tensors stored as external data
-
-
-def _tensor(msg) -> pb.Tensor:
+def _tensor(msg, base_dir=None) -> pb.Tensor:
     t = pb.Tensor(name=_str(_one(msg, "name", b"")), dims=tuple(int(d) for d in msg.get("dims", [])), data_type=_dtype(_one(msg, "data_type")))
     npdt = pb._NP.get(t.data_type)
     if npdt is None:
@@ -181,10 +178,10 @@ def _tensor(msg) -> pb.Tensor:
         import os
 
         ext = {_str(_one(e, "key", b"")): _str(_one(e, "value", b"")) for e in msg["external_data"]}
-        if _BASE_DIR[0] is None:
+        if base_dir is None:
             raise TextFormatError(f"tensor {t.name!r} is stored as external data ({ext.get('location')}), but the text was parsed "
                                   "without a directory to resolve it against; use load_model_text(path)")
-        path = os.path.join(_BASE_DIR[0], ext["location"])
+        path = os.path.join(base_dir, ext["location"])
         if not os.path.exists(path):
             raise TextFormatError(f"tensor {t.name!r}: external data file {path} does not exist")
         t.external = ext
@@ -207,12 +204,12 @@ def _tensor(msg) -> pb.Tensor:
     return t
 
 
-def _attr(msg):
+def _attr(msg, base_dir=None):
     name = _str(_one(msg, "name", b""))
     if "t" in msg:
-        return name, _tensor(msg["t"][0])
+        return name, _tensor(msg["t"][0], base_dir)
     if "g" in msg:
-        return name, _graph(msg["g"][0])
+        return name, _graph(msg["g"][0], base_dir)
     kind = _str(_one(msg, "type", b""))
     if "floats" in msg or kind == "FLOATS":
         return name, [float(v) for v in msg.get("floats", [])]
@@ -237,25 +234,25 @@ def _value_info(msg) -> pb.ValueInfo:
     return pb.ValueInfo(_str(_one(msg, "name", b"")), _dtype(_one(tt, "elem_type")) if tt else pb.FLOAT, tuple(shape))
 
 
-def _graph(msg) -> pb.Graph:
+def _graph(msg, base_dir=None) -> pb.Graph:
     g = pb.Graph(name=_str(_one(msg, "name", b"graph")))
     for n in msg.get("node", []):
         g.nodes.append(pb.Node(op_type=_str(_one(n, "op_type", b"")), inputs=[_str(v) for v in n.get("input", [])],
                                outputs=[_str(v) for v in n.get("output", [])], name=_str(_one(n, "name", b"")),
-                               domain=_str(_one(n, "domain", b"")), attrs=dict(_attr(a) for a in n.get("attribute", []))))
+                               domain=_str(_one(n, "domain", b"")), attrs=dict(_attr(a, base_dir) for a in n.get("attribute", []))))
     for t in msg.get("initializer", []):
-        tensor = _tensor(t)
+        tensor = _tensor(t, base_dir)
         g.initializers[tensor.name] = tensor
     g.inputs = [_value_info(v) for v in msg.get("input", [])]
     g.outputs = [_value_info(v) for v in msg.get("output", [])]
     return g
 
 
-def parse_model_text(text: str) -> pb.Model:
+def parse_model_text(text: str, base_dir: str | None = None) -> pb.Model:
     root = parse_text(text)
     if "graph" not in root:
         raise TextFormatError("the text holds no `graph { ... }`: this is not an ONNX ModelProto in text format")
-    m = pb.Model(graph=_graph(root["graph"][0]), ir_version=int(_one(root, "ir_version", 10)), producer_name=_str(_one(root, "producer_name", b"")))
+    m = pb.Model(graph=_graph(root["graph"][0], base_dir), ir_version=int(_one(root, "ir_version", 10)), producer_name=_str(_one(root, "producer_name", b"")))
     opsets = {_str(_one(o, "domain", b"")): int(_one(o, "version", 1)) for o in root.get("opset_import", [])}
     if opsets:
         m.opsets = opsets
@@ -267,12 +264,7 @@ def load_model_text(path: str) -> pb.Model:
     import os
 
     with open(path, encoding="utf-8") as f:
-        text = f.read()
-    _BASE_DIR[0] = os.path.dirname(os.path.abspath(path))
-    try:
-        return parse_model_text(text)
-    finally:
-        _BASE_DIR[0] = None
+        return parse_model_text(f.read(), os.path.dirname(os.path.abspath(path)))
 
 
 def load_any(path: str) -> pb.Model:
