@@ -487,3 +487,59 @@ class ConstraintProcessor(LogitProcessor):
         if token in self.eos_ids:
             return
         self.constraint.advance(self.token_texts[token])
+
+
+# ---------------------------------------------------------------------------------------------
+# table-driven grammar guidance for workflow documents (the ``onnx-genai.grammar-guidance`` adapter)
+# ---------------------------------------------------------------------------------------------
+def grammar_guidance_adapter(action: str = "lookahead"):
+    """A workflow component that advances per-row grammar states through a transition table.
+
+    Ports: ``state`` [B], ``tokens`` [B, P], ``valid_length`` [B], ``transition_table`` [states, vocab] (next state, or a
+    negative entry where the token is not allowed) -> ``next_state`` [B], ``consumed_length`` [B] (tokens the grammar
+    accepted, in order, before the first one it rejects), ``logits_mask`` [B, vocab] (tokens allowed in ``next_state``),
+    ``forced_tokens`` [B, 1] / ``forced_length`` [B] (the token, when the state allows exactly one).
+    ``clone`` consumes nothing (it only reports the state's mask), ``lookahead`` stops at the first rejected token,
+    ``commit`` treats a rejected token as an error -- the verifier must never commit what the grammar refused.
+    Same behaviour as the reference's adapter (crates/onnx-genai-engine/src/pipeline/workflow.rs:2383-2516)."""
+    if action not in ("clone", "lookahead", "commit"):
+        raise ValueError(f"grammar guidance action {action!r} is not clone, lookahead or commit")
+
+    def component(ports: dict) -> dict:
+        import torch
+
+        table = torch.as_tensor(np.asarray(ports["transition_table"])).long()
+        states = torch.as_tensor(np.asarray(ports["state"])).long().reshape(-1)
+        tokens = torch.as_tensor(np.asarray(ports["tokens"])).long()
+        tokens = tokens.reshape(states.numel(), -1)
+        lengths = torch.as_tensor(np.asarray(ports["valid_length"])).long().reshape(-1)
+        n_states, vocab = table.shape
+        next_state, consumed = [], []
+        for row in range(states.numel()):
+            s = int(states[row])
+            if not 0 <= s < n_states:
+                raise ValueError(f"grammar state {s} of row {row} is outside the table's {n_states} states")
+            want = 0 if action == "clone" else int(lengths[row])
+            if want < 0 or want > tokens.shape[1]:
+                raise ValueError(f"valid_length {want} of row {row} does not fit the {tokens.shape[1]} proposed tokens")
+            taken = 0
+            for col in range(want):
+                tok = int(tokens[row, col])
+                nxt = int(table[s, tok]) if 0 <= tok < vocab else -1
+                if nxt < 0:
+                    if action == "commit":
+                        raise ValueError(f"grammar commit: token {tok} at row {row}, position {col} is not allowed in state {s}")
+                    break
+                if nxt >= n_states:
+                    raise ValueError(f"the transition table sends state {s} on token {tok} to state {nxt}, which does not exist")
+                s, taken = nxt, taken + 1
+            next_state.append(s)
+            consumed.append(taken)
+        ns = torch.tensor(next_state, dtype=torch.int64)
+        mask = table[ns] >= 0
+        single = mask.sum(dim=1) == 1
+        forced = torch.where(single, mask.float().argmax(dim=1), torch.zeros_like(ns))
+        return {"next_state": ns, "consumed_length": torch.tensor(consumed, dtype=torch.int64), "logits_mask": mask,
+                "forced_tokens": forced.reshape(-1, 1), "forced_length": single.long()}
+
+    return component

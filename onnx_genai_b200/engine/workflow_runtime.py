@@ -134,6 +134,11 @@ class WorkflowSession:
 
                 bound[name] = image_preprocess_adapter(doc["preprocessing"]["image"], next(iter(comp.inputs), "encoded"))
                 continue
+            if comp.kind == "adapter" and comp.abi == "onnx-genai.grammar-guidance":
+                from .constraints import grammar_guidance_adapter
+
+                bound[name] = grammar_guidance_adapter(str(comp.params.get("action", "lookahead")))
+                continue
             if comp.kind != "onnx" or not comp.artifact:
                 raise WorkflowRuntimeError(f"component '{name}' is a '{comp.kind}' implementation{' (' + comp.abi + ')' if comp.abi else ''}, "
                                            "not an ONNX graph: pass a callable for it in `components`")

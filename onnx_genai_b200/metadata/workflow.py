@@ -51,6 +51,7 @@ class Component:
     roles: dict             # port -> role name
     declares_ports: bool = True   # False: the ports are those of the ONNX artifact itself and are not checked here
     abi: str | None = None        # adapter components: the named ABI they implement
+    params: dict = field(default_factory=dict)   # adapter components: the contract's parameters (e.g. action)
 
 
 @dataclass
@@ -211,7 +212,8 @@ def parse(doc: dict) -> Workflow:
             inputs={str(p): _contract(c, f"components.{name}.ports.inputs.{p}") for p, c in (ports.get("inputs") or {}).items()},
             outputs={str(p): _contract(c, f"components.{name}.ports.outputs.{p}") for p, c in (ports.get("outputs") or {}).items()},
             roles={str(p): str(r) for p, r in (ports.get("roles") or {}).items()},
-            declares_ports=bool(ports.get("inputs") or ports.get("outputs")), abi=impl.get("abi"))
+            declares_ports=bool(ports.get("inputs") or ports.get("outputs")), abi=impl.get("abi"),
+            params=dict(((d.get("contract") or {}).get("parameters")) or {}))
     state = {}
     for name, d in (doc.get("state") or {}).items():
         rec = d.get("recurrence") or {}

@@ -190,3 +190,49 @@ def test_upstream_vision_language_package_runs_from_image_bytes():
     feeds["request.image"] = torch.zeros(10, dtype=torch.uint8)
     with pytest.raises(Exception, match="cannot decode the image"):
         sess.run(feeds)
+
+
+def test_grammar_guidance_adapter_walks_masks_and_forces():
+    import torch
+
+    from onnx_genai_b200.engine.constraints import grammar_guidance_adapter
+
+    # state 0 accepts tokens 0,1 (-> 1); state 1 accepts only token 2 (-> 0)
+    table = torch.tensor([[1, 1, -1], [-1, -1, 0]])
+    ports = {"state": torch.tensor([0, 1]), "tokens": torch.tensor([[0, 2, 2], [2, 1, 0]]), "valid_length": torch.tensor([3, 3]),
+             "transition_table": table}
+    look = grammar_guidance_adapter("lookahead")(ports)
+    assert look["next_state"].tolist() == [0, 1] and look["consumed_length"].tolist() == [2, 2]
+    assert look["logits_mask"].tolist() == [[True, True, False], [False, False, True]]
+    assert look["forced_tokens"].tolist() == [[0], [2]] and look["forced_length"].tolist() == [0, 1]
+    clone = grammar_guidance_adapter("clone")(ports)
+    assert clone["next_state"].tolist() == [0, 1] and clone["consumed_length"].tolist() == [0, 0]
+    with pytest.raises(ValueError, match="token 2 at row 0, position 2 is not allowed in state 0"):
+        grammar_guidance_adapter("commit")(ports)
+    ok = grammar_guidance_adapter("commit")({**ports, "valid_length": torch.tensor([2, 2])})
+    assert ok["consumed_length"].tolist() == [2, 2]
+    with pytest.raises(ValueError, match="outside the table's 2 states"):
+        grammar_guidance_adapter("clone")({**ports, "state": torch.tensor([0, 5])})
+    with pytest.raises(ValueError, match="not clone, lookahead or commit"):
+        grammar_guidance_adapter("peek")
+
+
+@pytest.mark.skipif(not os.path.isdir(FIXTURES), reason="the upstream workflow fixtures are not available on this machine")
+def test_upstream_grammar_guided_speculative_package_runs():
+    """Proposer and verifier graphs, grammar clone / lookahead / commit adapters over a transition table, ONNX acceptance and
+    adaptive draft-length policies: the whole loop from the package's own document."""
+    import torch
+
+    sess = WorkflowSession.from_package(os.path.join(FIXTURES, "speculative"))
+    rows, vocab = 2, 32
+    table = torch.zeros(2, vocab, dtype=torch.int64)
+    table[0, 5:] = 1
+    table[1, :3] = -1
+    feeds = {"request.tokens": torch.randint(0, vocab, (rows, 4), generator=torch.Generator().manual_seed(0)),
+             "request.max_iterations": torch.tensor([3]), "request.grammar_state": torch.zeros(rows, dtype=torch.int64),
+             "request.grammar_transition_table": table, "request.draft_ms": torch.ones(rows), "request.target_ms": torch.ones(rows) * 4,
+             "request.verifier.past_key_values.0.key": torch.zeros(rows, 2, 0, 8),
+             "request.verifier.past_key_values.0.value": torch.zeros(rows, 4, 0, 4)}
+    out = sess.run(feeds)
+    inv = sess.stats["invocations"]
+    assert len(out["tokens"]) >= 2 and inv["grammar_clone"] == inv["grammar_lookahead"] == inv["grammar_commit"] == inv["verifier"] >= 2
