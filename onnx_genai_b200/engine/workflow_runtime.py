@@ -134,6 +134,26 @@ class WorkflowSession:
 
                 bound[name] = image_preprocess_adapter(doc["preprocessing"]["image"], next(iter(comp.inputs), "encoded"))
                 continue
+            if comp.kind == "adapter" and comp.abi == "onnx-genai.parameter-overlay" and doc.get("adapters"):
+                from ..package.graph_executor import tensor_to_torch
+                from .lora import AdapterStore, parameter_overlay_adapter
+
+                adapters_doc = doc["adapters"]
+                store = AdapterStore(package_dir, adapters_doc)
+                target = store.targets.get(str(comp.params.get("parameter")))
+                if target is None:
+                    raise WorkflowRuntimeError(f"component '{name}' overlays parameter '{comp.params.get('parameter')}', which the adapter "
+                                               f"target manifest does not list (it lists {sorted(store.targets)})")
+                owner = wf.components.get(target["component"])
+                if owner is None or not owner.artifact:
+                    raise WorkflowRuntimeError(f"adapter target '{target['id']}' belongs to component '{target['component']}', which has no graph")
+                graph = load_any(os.path.join(package_dir, owner.artifact)).graph
+                if target["initializer"] not in graph.initializers:
+                    raise WorkflowRuntimeError(f"adapter target '{target['id']}': {owner.artifact} has no initializer '{target['initializer']}'")
+                bound[name] = parameter_overlay_adapter(tensor_to_torch(graph.initializers[target["initializer"]]), store, target["id"],
+                                                        adapters_doc.get("selection") or {}, next(iter(comp.inputs), "input"),
+                                                        next(iter(comp.outputs), "output"))
+                continue
             if comp.kind == "adapter" and comp.abi == "onnx-genai.grammar-guidance":
                 from .constraints import grammar_guidance_adapter
 
@@ -224,6 +244,9 @@ class WorkflowSession:
         kind = step.kind
         if kind == "invoke":
             feed = {port: self._read(scope, val, step) for port, val in step.inputs.items()}
+            for port, val in (getattr(self.components[step.component], "extra_inputs", None) or {}).items():
+                if val and (scope.has(val) or val in self.wf.state):      # values the runtime hands an adapter next to its ports
+                    feed[port] = self._read(scope, val, step)
             result = self.components[step.component](feed)
             if not isinstance(result, dict):
                 raise WorkflowRuntimeError(f"{step.where}: component '{step.component}' returned {type(result).__name__}; a dict of output ports is needed")

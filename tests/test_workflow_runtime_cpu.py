@@ -165,10 +165,18 @@ def test_upstream_workflow_packages_execute_end_to_end(name, outputs):
         assert set(again) == set(out)
 
 
-@pytest.mark.skipif(not os.path.isdir(FIXTURES), reason="the upstream workflow fixtures are not available on this machine")
-def test_packages_with_adapter_components_say_what_to_supply():
-    with pytest.raises(WorkflowRuntimeError, match=r"is a 'adapter' implementation \(onnx-genai.parameter-overlay\), not an ONNX graph: pass a callable"):
-        WorkflowSession.from_package(os.path.join(FIXTURES, "adapter"))
+def test_packages_with_unknown_adapter_components_say_what_to_supply(tmp_path):
+    import yaml
+
+    doc = {"pipeline": {"workflow": {"inputs": {"x": {"source": {"kind": "request"}}}, "outputs": {"y": {}},
+                                     "components": {"telemetry": {"implementation": {"kind": "adapter", "abi": "onnx-genai.telemetry", "version": "1"}}},
+                                     "steps": [{"kind": "invoke", "component": "telemetry", "inputs": {"v": "x"}, "outputs": {"o": "t"}},
+                                               {"kind": "emit", "value": "t", "output": "y", "mode": "replace"}]}}}
+    (tmp_path / "inference_metadata.yaml").write_text(yaml.safe_dump(doc))
+    with pytest.raises(WorkflowRuntimeError, match=r"is a 'adapter' implementation \(onnx-genai.telemetry\), not an ONNX graph: pass a callable"):
+        WorkflowSession.from_package(str(tmp_path))
+    sess = WorkflowSession.from_package(str(tmp_path), components={"telemetry": lambda p: {"o": p["v"] * 2}})
+    assert sess.run({"x": np.asarray([2.0])})["y"].tolist() == [4.0]
 
 
 @pytest.mark.skipif(not os.path.isdir(FIXTURES), reason="the upstream workflow fixtures are not available on this machine")
