@@ -244,3 +244,32 @@ def test_upstream_grammar_guided_speculative_package_runs():
     out = sess.run(feeds)
     inv = sess.stats["invocations"]
     assert len(out["tokens"]) >= 2 and inv["grammar_clone"] == inv["grammar_lookahead"] == inv["grammar_commit"] == inv["verifier"] >= 2
+
+
+COMFY_FIXTURE = os.path.join(os.path.dirname(os.path.dirname(FIXTURES)), "fixtures", "comfyui_workflows", "txt2img_sd15")
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(COMFY_FIXTURE, "reference.json")), reason="the upstream ComfyUI fixture is not available on this machine")
+def test_upstream_text_to_image_package_reproduces_its_golden_latent_and_image():
+    """The upstream converter's own package for a ComfyUI graph, with the pinned outputs it ships: seeded noise generated by
+    an ONNX policy (64-bit integer hashing), four guided Euler steps, VAE decode -- all on the generic graph executor."""
+    import json
+
+    import torch
+
+    with open(os.path.join(COMFY_FIXTURE, "reference.json"), encoding="utf-8") as f:
+        ref = json.load(f)
+    sess = WorkflowSession.from_package(COMFY_FIXTURE)
+    out = sess.run({"request.input_ids": torch.tensor([ref["prompt_tokens"]]), "request.negative_input_ids": torch.tensor([ref["negative_tokens"]])})
+    latent, image = torch.as_tensor(out["latent"]).float(), torch.as_tensor(out["image"]).float()
+    assert list(latent.shape) == ref["latent_shape"] and list(image.shape) == ref["image_shape"]
+    assert float((latent.reshape(-1) - torch.tensor(ref["latent"])).abs().max()) < ref["tolerance"]
+    assert float((image.reshape(-1) - torch.tensor(ref["image"])).abs().max()) < ref["tolerance"]
+    assert sess.stats["iterations"] == ref["steps"] and sess.stats["invocations"]["denoiser"] == 2 * ref["steps"]
+    # the ComfyUI graph next to it goes through this package's own importer too
+    from onnx_genai_b200.package.comfyui import import_comfyui
+
+    with open(os.path.join(COMFY_FIXTURE, "workflow.json"), encoding="utf-8") as f:
+        mine = import_comfyui(json.load(f))
+    d = mine["generation"]["defaults"]
+    assert (d["steps"], d["guidance_scale"], d["seed"], d["sampler"], d["scheduler"]) == (ref["steps"], ref["guidance_scale"], ref["seed"], "euler", "karras")
