@@ -370,8 +370,13 @@ def _group_query_attention(ins, attrs):
     seqlens = ins[5].long().reshape(-1)
     cos = ins[7] if len(ins) > 7 else None
     sin = ins[8] if len(ins) > 8 else None
+    if attrs.get("do_rotary", 0) and (cos is None or sin is None):
+        raise GraphExecutionError("GroupQueryAttention with do_rotary needs the cos and sin caches")
     hq, hkv = int(attrs["num_heads"]), int(attrs["kv_num_heads"])
     b, s = q.shape[0], q.shape[1]
+    if k is None:                                   # packed projections: [q | k | v] along the feature axis
+        d = q.shape[2] // (hq + 2 * hkv)
+        q, k, v = q[..., : hq * d], q[..., hq * d:(hq + hkv) * d], q[..., (hq + hkv) * d:]
     d = q.shape[2] // hq
     q = q.reshape(b, s, hq, d)
     k = k.reshape(b, s, hkv, d)

@@ -51,3 +51,17 @@ def test_upstream_gpt2_style_fixture_decodes_with_consistent_kv():
     full = GraphDecodeSession.from_dir(d)
     logits = full.feed(prompt + toks[:-1])                      # one pass over everything
     assert [int(torch.argmax(logits[len(prompt) - 1 + i])) for i in range(6)] == toks
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "tests", "fixtures", "tiny-native-scalar-gqa")),
+                    reason="the upstream tiny decoder fixtures are not available on this machine")
+def test_upstream_tiny_decoders_reproduce_their_pinned_tokens():
+    """Greedy tokens that the upstream project pins in its own tests (crates/onnx-genai-engine/tests/native_engine.rs:38,341)."""
+    fixtures = os.path.join(REF, "tests", "fixtures")
+    assert GraphDecodeSession.from_dir(os.path.join(fixtures, "tiny-native-scalar-gqa")).generate([0], 4) == [1, 1, 1, 1]
+    assert GraphDecodeSession.from_dir(os.path.join(fixtures, "tiny-native-engine")).generate([0], 3) == [1, 1, 1]
+    # packed q|k|v GroupQueryAttention with in-op rotary embedding: cached steps equal one full pass
+    d = os.path.join(fixtures, "tiny-llm-sharedbuffer")
+    toks = GraphDecodeSession.from_dir(d).generate([3, 9, 27], 5)
+    logits = GraphDecodeSession.from_dir(d).feed([3, 9, 27] + toks[:-1])
+    assert [int(torch.argmax(logits[2 + i])) for i in range(5)] == toks
