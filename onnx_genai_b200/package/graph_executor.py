@@ -409,6 +409,27 @@ def _group_query_attention(ins, attrs):
     return [y.transpose(1, 2).reshape(b, s, hq * d), present_k, present_v]
 
 
+def _tensor_scatter(ins, attrs):
+    """TensorScatter (opset 24): write ``update`` into ``past_cache`` along ``axis`` starting at each batch row's write index
+    (0 when no indices are given); ``mode="circular"`` wraps around the cache length."""
+    cache, update = ins[0], ins[1]
+    idx = ins[2].long().reshape(-1) if len(ins) > 2 and ins[2] is not None else torch.zeros(cache.shape[0], dtype=torch.long, device=cache.device)
+    axis = int(attrs.get("axis", -2)) % cache.dim()
+    if axis == 0:
+        raise GraphExecutionError("TensorScatter writes along a sequence axis; axis 0 is the batch")
+    out = cache.clone()
+    length, n = cache.shape[axis], update.shape[axis]
+    circular = attrs.get("mode", "linear") == "circular"
+    for b in range(cache.shape[0]):
+        pos = int(idx[b]) + torch.arange(n, device=cache.device)
+        if circular:
+            pos = pos % length
+        elif int(pos[-1]) >= length:
+            raise GraphExecutionError(f"TensorScatter: row {b} writes positions up to {int(pos[-1])} into a cache of length {length}")
+        out[b].index_copy_(axis - 1, pos, update[b].to(out.dtype))
+    return out
+
+
 def _bitshift(ins, attrs):
     x, n = ins[0], ins[1]
     if attrs.get("direction", "LEFT") == "LEFT":
@@ -475,7 +496,7 @@ OPS = {
     "BitwiseXor": lambda i, a: i[0] ^ i[1], "BitwiseNot": lambda i, a: ~i[0], "Mod": _mod,
     "IsInf": lambda i, a: torch.isinf(i[0]) & ((i[0] > 0) if not a.get("detect_negative", 1) else True) & ((i[0] < 0) if not a.get("detect_positive", 1) else True),
     "Swish": lambda i, a: i[0] * torch.sigmoid(float(a.get("alpha", 1.0)) * i[0]),
-    "RotaryEmbedding": _rotary, "Attention": _attention, "GroupQueryAttention": _group_query_attention,
+    "TensorScatter": _tensor_scatter, "RotaryEmbedding": _rotary, "Attention": _attention, "GroupQueryAttention": _group_query_attention,
     "MatMul": lambda i, a: i[0] @ i[1],
     "Gemm": lambda i, a: float(a.get("alpha", 1.0)) * ((i[0].T if a.get("transA", 0) else i[0]) @ (i[1].T if a.get("transB", 0) else i[1]))
                          + (float(a.get("beta", 1.0)) * i[2] if len(i) > 2 and i[2] is not None else 0),

@@ -238,3 +238,21 @@ def test_run_workflow_cli_on_a_package_written_to_disk(tmp_path):
     assert cli.main(["run-workflow", str(pkg), "--input", "request.positive_ids=ids:1"]) == 1
     (pkg / "sd15" / "unet.onnx").unlink()
     assert cli.main(["run-workflow", str(pkg)]) == 1
+
+
+def test_tensor_scatter_linear_and_circular():
+    cache = np.zeros((2, 1, 5, 2), np.float32)
+    upd = np.arange(2 * 1 * 2 * 2, dtype=np.float32).reshape(2, 1, 2, 2) + 1
+    for mode, idx, rows in (("linear", [1, 3], ([1, 2], [3, 4])), ("circular", [4, 0], ([4, 0], [0, 1]))):
+        m = model([N("TensorScatter", ["c", "u", "i"], ["o"], axis=-2, mode=mode)], [T("i", np.asarray(idx, np.int64))],
+                  [("c", pb.FLOAT, (2, 1, 5, 2)), ("u", pb.FLOAT, (2, 1, 2, 2))], ["o"])
+        out = GraphExecutor(m).run({"c": cache, "u": upd})["o"]
+        want = torch.zeros(2, 1, 5, 2)
+        for b in range(2):
+            for j, pos in enumerate(rows[b]):
+                want[b, 0, pos] = torch.from_numpy(upd[b, 0, j])
+        assert torch.equal(out, want), mode
+    m = model([N("TensorScatter", ["c", "u", "i"], ["o"])], [T("i", np.asarray([4, 0], np.int64))],
+              [("c", pb.FLOAT, (2, 1, 5, 2)), ("u", pb.FLOAT, (2, 1, 2, 2))], ["o"])
+    with pytest.raises(GraphExecutionError, match="into a cache of length 5"):
+        GraphExecutor(m).run({"c": cache, "u": upd})
