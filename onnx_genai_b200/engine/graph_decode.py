@@ -122,3 +122,58 @@ class GraphDecodeSession:
             with open(meta_path, encoding="utf-8") as f:
                 io = ((yaml.safe_load(f) or {}).get("model") or {}).get("io")
         return cls(load_any(path), device, io)
+
+
+class StaticCacheDecodeSession:
+    """Decode over a graph with fixed-size KV caches updated in place by indexed scatter: inputs ``key_cache.*`` /
+    ``value_cache.*`` of full length, ``write_indices`` (where this call's tokens go) and ``nonpad_kv_seqlen`` (valid length
+    after the write); outputs ``updated_*`` caches that feed the next call.  The reference's static-cache decode session
+    for graphs exported with ``TensorScatter`` (crates/onnx-genai-ort/src/decode, `StaticCacheDecodeSession`; metadata
+    ``kv_update: indexed_scatter``).  Shapes never change between calls, which is what capture-friendly backends want."""
+
+    def __init__(self, model, device="cpu"):
+        self.ex = model if isinstance(model, GraphExecutor) else GraphExecutor(model, device)
+        names = self.ex.input_names
+        self.token_in = next((n for n in names if n in ("input_ids", "tokens")), None)
+        self.cache_in = [n for n in names if n.startswith(("key_cache", "value_cache"))]
+        self.cache_out = [n for n in self.ex.output_names if n.startswith("updated_")]
+        if self.token_in is None or not self.cache_in or len(self.cache_in) != len(self.cache_out):
+            raise ValueError(f"not a static-cache decoder: inputs {names}, outputs {self.ex.output_names}")
+        for need in ("write_indices", "nonpad_kv_seqlen"):
+            if need not in names:
+                raise ValueError(f"a static-cache decoder takes '{need}'; this graph takes {names}")
+        self.logits_out = "logits" if "logits" in self.ex.output_names else self.ex.output_names[0]
+        self.info = {vi.name: vi for vi in self.ex.model.graph.inputs}
+        self.reset()
+
+    def reset(self) -> None:
+        self.tokens: list = []
+        self.cache = {}
+        for name in self.cache_in:
+            vi = self.info[name]
+            shape = [d if isinstance(d, int) else 1 for d in vi.shape]
+            self.cache[name] = torch.zeros(shape, dtype=_TORCH_DTYPE.get(vi.elem_type, torch.float32), device=self.ex.device)
+        first = self.info[self.cache_in[0]].shape
+        self.capacity = int(next(d for d in first[1:] if isinstance(d, int)))
+
+    def feed(self, token_ids) -> torch.Tensor:
+        ids = [int(t) for t in token_ids]
+        past = len(self.tokens)
+        if past + len(ids) > self.capacity:
+            raise ValueError(f"{past} cached + {len(ids)} new tokens exceed the cache length {self.capacity}")
+        feeds = {self.token_in: torch.tensor([ids], dtype=torch.int64), "write_indices": torch.tensor([past], dtype=torch.int64),
+                 "nonpad_kv_seqlen": torch.tensor([past + len(ids)], dtype=torch.int64), **self.cache}
+        out = self.ex.run(feeds, [self.logits_out, *self.cache_out])
+        for src, dst in zip(self.cache_out, self.cache_in):
+            self.cache[dst] = out[src]
+        self.tokens += ids
+        return out[self.logits_out][0].float()
+
+    def generate(self, prompt, max_new_tokens: int) -> list:
+        logits = self.feed(prompt)[-1]
+        out = []
+        for _ in range(max_new_tokens):
+            out.append(int(torch.argmax(logits)))
+            if len(out) < max_new_tokens:
+                logits = self.feed([out[-1]])[-1]
+        return out

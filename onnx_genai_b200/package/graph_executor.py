@@ -347,7 +347,17 @@ def _attention(ins, attrs):
     cap = float(attrs.get("softcap", 0.0))
     if cap > 0:
         scores = cap * torch.tanh(scores / cap)
-    if attrs.get("is_causal", 0):
+    nonpad = ins[6].long().reshape(-1) if len(ins) > 6 and ins[6] is not None else None
+    if nonpad is not None:
+        # fixed-size caches (opset 24): only the first nonpad[b] keys of row b hold tokens, and the queries are its last ones
+        t_all, s_q = scores.shape[-1], scores.shape[-2]
+        key_pos = torch.arange(t_all, device=scores.device)[None, None, :]
+        allowed = key_pos < nonpad[:, None, None]
+        if attrs.get("is_causal", 0):
+            q_pos = (nonpad[:, None] - s_q + torch.arange(s_q, device=scores.device)[None])[:, :, None]
+            allowed = allowed & (key_pos <= q_pos)
+        scores = scores.masked_fill(~allowed[:, None], float("-inf"))
+    elif attrs.get("is_causal", 0):
         # with past keys the triangle is aligned to the last key (query i sees keys up to past + i), which is what makes a
         # cached step equal the same position of a full pass; without past this is the plain lower triangle
         tri = torch.ones(scores.shape[-2], scores.shape[-1], dtype=torch.bool, device=scores.device).tril(scores.shape[-1] - scores.shape[-2])

@@ -65,3 +65,24 @@ def test_upstream_tiny_decoders_reproduce_their_pinned_tokens():
     toks = GraphDecodeSession.from_dir(d).generate([3, 9, 27], 5)
     logits = GraphDecodeSession.from_dir(d).feed([3, 9, 27] + toks[:-1])
     assert [int(torch.argmax(logits[2 + i])) for i in range(5)] == toks
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(REF, "tests", "fixtures", "tiny-llm-scatter", "model.onnx.textproto")),
+                    reason="the upstream static-cache fixture is not available on this machine")
+def test_static_cache_decoder_steps_equal_one_full_pass():
+    """Fixed-size caches written by TensorScatter at ``write_indices``, attention bounded by ``nonpad_kv_seqlen``."""
+    from onnx_genai_b200.engine.graph_decode import StaticCacheDecodeSession
+    from onnx_genai_b200.package.onnx_text import load_any
+
+    path = os.path.join(REF, "tests", "fixtures", "tiny-llm-scatter", "model.onnx.textproto")
+    sess = StaticCacheDecodeSession(load_any(path))
+    toks = sess.generate([3, 9, 27], 5)
+    assert sess.capacity == 16 and len(sess.tokens) == 7
+    full = StaticCacheDecodeSession(load_any(path))
+    logits = full.feed([3, 9, 27] + toks[:-1])
+    assert [int(torch.argmax(logits[2 + i])) for i in range(5)] == toks
+    assert all(tuple(v.shape) == (1, 16, 16) for v in full.cache.values())        # shapes never change
+    with pytest.raises(ValueError, match="exceed the cache length 16"):
+        full.feed(list(range(12)))
+    with pytest.raises(ValueError, match="not a static-cache decoder"):
+        StaticCacheDecodeSession(load_any(os.path.join(REF, "tests", "fixtures", "tiny-llm", "model.onnx.textproto")))
