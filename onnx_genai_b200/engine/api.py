@@ -270,6 +270,23 @@ class Engine:
         if not self.llm.cfg.enable_prefix_cache:
             raise ValueError("a KV connector extends the device prefix cache; build the engine with enable_prefix_cache=True")
         self.kv_offload = KvOffload(self.llm, connector)
+        # the connector's host tier is a reclaimable consumer of host memory: its bytes show in the ledger, and when some
+        # other consumer is short the pressure queue asks it to spill to disk before anyone has to wait
+        if hasattr(connector, "shrink_host"):
+            from .memory import PressureQueue
+
+            ledger = self.llm.memory
+            lease = ledger.lease("kv_offload", "host", 0, "offloaded KV chunks held in host memory")
+
+            def account(nbytes, lease=lease, ledger=ledger):
+                try:
+                    lease.resize(int(nbytes))
+                except Exception:            # over the host limit: give back the excess, keep the rest on disk
+                    connector.max_host_bytes = max(0, (ledger.available("host") or 0) + lease.nbytes)
+                    connector.shrink_host(max(0, int(nbytes) - connector.max_host_bytes))
+
+            connector.on_host_bytes = account
+            self.host_pressure = PressureQueue(ledger, "host", reclaim=connector.shrink_host)
 
     def _finish(self, sid, tokens=None):
         if tokens is not None and getattr(self, "kv_offload", None) is not None:

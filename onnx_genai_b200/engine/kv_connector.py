@@ -64,6 +64,7 @@ class LocalTieredConnector(KvConnector):
         self.disk_bytes = 0
         self.lock = threading.Lock()
         self.stats = {"stores": 0, "host_hits": 0, "disk_hits": 0, "misses": 0, "spilled": 0, "deleted": 0}
+        self.on_host_bytes = None       # callback(bytes now held in host memory), set by whoever accounts for them
         if disk_dir:
             os.makedirs(disk_dir, exist_ok=True)
             for name in sorted(os.listdir(disk_dir)):      # chunks written by an earlier process are usable again
@@ -91,6 +92,9 @@ class LocalTieredConnector(KvConnector):
                 old_key, old = self.host.popitem(last=False)
                 self.host_bytes -= len(old)
                 self._spill(old_key, old)
+            held = self.host_bytes
+        if self.on_host_bytes is not None:
+            self.on_host_bytes(held)
 
     def _spill(self, key, blob):
         if not self.disk_dir or key in self.disk:
@@ -110,6 +114,20 @@ class LocalTieredConnector(KvConnector):
                 os.remove(self._path(old_key))
             except OSError:
                 pass
+
+    def shrink_host(self, nbytes: int) -> int:
+        """Move least recently used chunks from host memory to disk (or drop them without a disk tier) until ``nbytes`` are
+        free again; returns the bytes released.  The memory ledger calls this when another consumer of host memory is short."""
+        freed = 0
+        with self.lock:
+            while freed < nbytes and self.host:
+                key, blob = self.host.popitem(last=False)
+                self.host_bytes -= len(blob)
+                freed += len(blob)
+                self._spill(key, blob)
+        if self.on_host_bytes is not None:
+            self.on_host_bytes(self.host_bytes)
+        return freed
 
     def fetch(self, key):
         with self.lock:

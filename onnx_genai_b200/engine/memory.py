@@ -143,3 +143,148 @@ def tensor_bytes(obj) -> int:
         elif hasattr(o, "__dict__") and not isinstance(o, type):
             stack.extend(vars(o).values())
     return total
+
+
+# ---------------------------------------------------------------------------------------------
+# ticketed, non-blocking pressure protocol for a shared tier (host memory)
+# ---------------------------------------------------------------------------------------------
+class PressureTicket:
+    """A request for bytes that could not be granted at once.  ``poll()`` never blocks and holds no ledger lock;
+    ``wait(timeout)`` sleeps on the ticket's own event.  A grant is published only after the bytes have been charged to
+    the ticket's lease, so nobody can take them in between.  Dropping or cancelling a ticket gives back whatever it held."""
+
+    PENDING, GRANTED, CANCELLED, EXPIRED = "pending", "granted", "cancelled", "expired"
+
+    def __init__(self, queue: "PressureQueue", role: str, nbytes: int, tag: str, deadline: float | None):
+        self.queue, self.role, self.nbytes, self.tag, self.deadline = queue, role, int(nbytes), tag, deadline
+        self.state = self.PENDING
+        self.lease: Lease | None = None
+        self._event = threading.Event()
+        self.id = -1
+
+    def poll(self) -> str:
+        self.queue._expire()
+        return self.state
+
+    def wait(self, timeout: float | None = None) -> str:
+        import time
+
+        end = None if timeout is None else time.monotonic() + timeout
+        while self.poll() == self.PENDING:
+            remaining = None if end is None else end - time.monotonic()
+            if remaining is not None and remaining <= 0:
+                break
+            step = 0.05 if remaining is None else min(0.05, remaining)
+            self._event.wait(step)                 # woken by a grant or a cancellation; the short step notices deadlines
+        return self.state
+
+    def cancel(self) -> None:
+        self.queue.cancel(self)
+
+    def __del__(self):
+        try:
+            if self.state == self.PENDING:
+                self.queue.cancel(self)
+        except Exception:
+            pass
+
+
+class PressureQueue:
+    """First-come, first-served admission to one tier of a :class:`MemoryLedger` under pressure.
+
+    ``request`` charges the bytes at once when they fit and nobody is waiting ahead; otherwise it files a ticket.  Every
+    ``release`` (or cancellation, or expiry) re-examines the queue head: while the head fits it is charged and then
+    woken.  A large request at the head is not overtaken by smaller later ones, so it cannot starve.  No method waits
+    while holding the lock.  Same contract as the reference's host-memory pressure protocol (charge before wake, waits
+    hold no governor lock, cancellation is lossless; crates/onnx-genai-scheduler/src/pressure.rs:1-30)."""
+
+    def __init__(self, ledger: MemoryLedger, tier: str = "host", reclaim=None):
+        """``reclaim(nbytes) -> bytes freed``: optional callback asked to give memory back (evict a cache) before a request
+        has to queue; called without the queue lock held."""
+        if tier not in TIERS:
+            raise ValueError(f"unknown tier {tier!r}")
+        self.ledger, self.tier, self.reclaim = ledger, tier, reclaim
+        self.lock = threading.Lock()
+        self.waiting: list = []
+        self.next_id = 0
+        self.events: list = []          # (sequence, kind, ticket id, bytes): a replayable trace of the linearisation points
+
+    def _log(self, kind, ticket):
+        self.events.append((len(self.events), kind, ticket.id, ticket.nbytes))
+
+    def _try_charge(self, ticket) -> bool:
+        try:
+            ticket.lease = self.ledger.lease(ticket.role, self.tier, ticket.nbytes, ticket.tag)
+        except MemoryLimitError:
+            return False
+        return True
+
+    def request(self, role: str, nbytes: int, tag: str = "", timeout: float | None = None) -> PressureTicket:
+        import time
+
+        ticket = PressureTicket(self, role, nbytes, tag, None if timeout is None else time.monotonic() + timeout)
+        limit = self.ledger.limits.get(self.tier)
+        if limit is not None and nbytes > limit:
+            raise MemoryLimitError(f"{role} ({tag or 'untagged'}) asks for {nbytes / 2**30:.2f} GiB of {self.tier}, more than the whole "
+                                   f"{limit / 2**30:.2f} GiB limit: it could never be granted")
+        if self.reclaim is not None:
+            avail = self.ledger.available(self.tier)
+            if avail is not None and avail < nbytes:
+                self.reclaim(nbytes - avail)
+        with self.lock:
+            ticket.id = self.next_id
+            self.next_id += 1
+            self._log("request", ticket)
+            if not self.waiting and self._try_charge(ticket):
+                ticket.state = PressureTicket.GRANTED
+                self._log("grant", ticket)
+                ticket._event.set()
+            else:
+                self.waiting.append(ticket)
+        return ticket
+
+    def _pump(self) -> None:
+        woken = []
+        with self.lock:
+            while self.waiting and self._try_charge(self.waiting[0]):
+                t = self.waiting.pop(0)
+                t.state = PressureTicket.GRANTED          # charged first, published second, woken last
+                self._log("grant", t)
+                woken.append(t)
+        for t in woken:
+            t._event.set()
+
+    def release(self, ticket_or_lease) -> None:
+        """Give back a granted ticket's (or any lease's) bytes and serve the queue."""
+        lease = ticket_or_lease.lease if isinstance(ticket_or_lease, PressureTicket) else ticket_or_lease
+        if lease is not None:
+            lease.release()
+        self._pump()
+
+    def cancel(self, ticket: PressureTicket) -> None:
+        with self.lock:
+            if ticket.state == PressureTicket.PENDING:
+                ticket.state = PressureTicket.CANCELLED
+                if ticket in self.waiting:
+                    self.waiting.remove(ticket)
+                self._log("cancel", ticket)
+            elif ticket.state == PressureTicket.GRANTED and ticket.lease is not None and not ticket.lease.released:
+                pass                                   # a granted ticket is given back with release(), not cancel()
+        ticket._event.set()
+        self._pump()                                   # the head may have been what blocked the others
+
+    def _expire(self) -> None:
+        import time
+
+        now, expired = time.monotonic(), []
+        with self.lock:
+            for t in list(self.waiting):
+                if t.deadline is not None and now >= t.deadline:
+                    t.state = PressureTicket.EXPIRED
+                    self.waiting.remove(t)
+                    self._log("expire", t)
+                    expired.append(t)
+        for t in expired:
+            t._event.set()
+        if expired:
+            self._pump()

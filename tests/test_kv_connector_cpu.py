@@ -64,3 +64,30 @@ def test_connector_tiers_keys_and_limits(tmp_path):
         llm = LLMEngine(EngineConfig(model=CFG, num_pages=16, max_seqs=2, max_tokens_per_step=64, max_seq_len=128,
                                      enable_prefix_cache=False), weights=random_weights(CFG, "cpu", seed=1, dtype=torch.float32), device="cpu")
         Engine(llm).attach_kv_connector(c)
+
+
+def test_host_tier_is_accounted_and_reclaimed_under_pressure(tmp_path):
+    """Offloaded chunks held in host memory show in the ledger; another consumer of host memory that does not fit makes
+    the connector spill to disk before anyone waits, and the chunks stay restorable."""
+    from onnx_genai_b200.engine.memory import PressureTicket
+
+    weights = random_weights(CFG, "cpu", seed=11, std=0.3, dtype=torch.float32)
+    rng = np.random.default_rng(1)
+    prompt = rng.integers(0, CFG.vocab, size=600).tolist()
+    opt = GenerateOptions(max_new_tokens=4, ignore_eos=True)
+    eng = _engine(weights)
+    conn = LocalTieredConnector(str(tmp_path / "kv"), max_host_bytes=1 << 30)
+    eng.attach_kv_connector(conn)
+    first = eng.generate(prompt, opt)
+    ledger = eng.llm.memory
+    held = conn.host_bytes
+    assert held > 0 and ledger.used("host", "kv_offload") == held
+    ledger.limits["host"] = ledger.used("host") + 1000                         # almost nothing left for anyone else
+    ticket = eng.host_pressure.request("workspace", held // 2 + 1000, "pinned staging")
+    assert ticket.poll() == PressureTicket.GRANTED                              # the connector gave memory back instead of a wait
+    assert conn.host_bytes < held and conn.stats["spilled"] >= 1 and ledger.used("host", "kv_offload") == conn.host_bytes
+    assert ledger.used("host") <= ledger.limits["host"]
+    for _ in range(3):
+        eng.generate(rng.integers(0, CFG.vocab, size=500).tolist(), opt)
+    again = eng.generate(prompt, opt)
+    assert again.token_ids == first.token_ids and eng.kv_offload.tokens_restored >= 256

@@ -49,3 +49,81 @@ def test_engine_registers_what_it_allocated():
     assert snap["by_role"]["weights"] == tensor_bytes(eng.weights) > 0 and snap["by_role"]["activations"] > 0
     shared = torch.zeros(10)
     assert tensor_bytes({"a": shared, "b": [shared, shared[2:]]}) == 40        # one storage counted once
+
+
+def test_pressure_queue_grants_in_order_after_charging():
+    import threading
+    import time
+
+    from onnx_genai_b200.engine.memory import MemoryLedger, MemoryLimitError, PressureQueue, PressureTicket
+
+    ledger = MemoryLedger(limits={"host": 100})
+    q = PressureQueue(ledger, "host")
+    a = q.request("kv_offload", 60, "a")
+    assert a.poll() == PressureTicket.GRANTED and ledger.used("host") == 60
+    b = q.request("kv_offload", 70, "b")                     # does not fit: queued
+    c = q.request("kv_offload", 10, "c")                     # would fit, but must not overtake b
+    assert b.poll() == c.poll() == PressureTicket.PENDING and ledger.used("host") == 60
+    seen = []
+    waiter = threading.Thread(target=lambda: seen.append(b.wait(5.0)))
+    waiter.start()
+    time.sleep(0.05)
+    q.release(a)                                             # frees 60: b (70) is charged and woken, then c (10) fits too
+    waiter.join(5.0)
+    assert seen == [PressureTicket.GRANTED] and c.poll() == PressureTicket.GRANTED and ledger.used("host") == 80
+    # the trace shows charge-before-wake order and first-come-first-served grants
+    grants = [tid for _, kind, tid, _ in q.events if kind == "grant"]
+    assert grants == [a.id, b.id, c.id]
+    # cancellation of the head unblocks what is behind it; expiry does the same
+    d = q.request("kv", 50, "d")
+    e = q.request("kv", 15, "e")
+    assert d.poll() == e.poll() == PressureTicket.PENDING
+    d.cancel()
+    assert d.poll() == PressureTicket.CANCELLED and e.poll() == PressureTicket.GRANTED and ledger.used("host") == 95
+    f = q.request("kv", 30, "f", timeout=0.05)
+    g = q.request("kv", 5, "g")
+    time.sleep(0.08)
+    assert f.poll() == PressureTicket.EXPIRED and g.poll() == PressureTicket.GRANTED and ledger.used("host") == 100
+    with pytest.raises(MemoryLimitError, match="could never be granted"):
+        q.request("kv", 101, "too big")
+    # a reclaim callback is asked before a request has to queue
+    for t in (b, c, e, g):
+        q.release(t)
+    cache = [ledger.lease("kv_offload", "host", 90, "cache")]
+    asked = []
+
+    def reclaim(nbytes):
+        asked.append(nbytes)
+        cache.pop().release()
+        return 90
+
+    q2 = PressureQueue(ledger, "host", reclaim=reclaim)
+    assert q2.request("weights", 40, "h").poll() == PressureTicket.GRANTED and asked == [30]
+
+
+def test_pressure_queue_under_threads_never_exceeds_the_limit():
+    import random
+    import threading
+
+    from onnx_genai_b200.engine.memory import MemoryLedger, PressureQueue, PressureTicket
+
+    ledger = MemoryLedger(limits={"host": 64})
+    q = PressureQueue(ledger, "host")
+    peak, errors = [0], []
+
+    def worker(seed):
+        rng = random.Random(seed)
+        for _ in range(40):
+            t = q.request("workspace", rng.randint(1, 32), f"w{seed}")
+            if t.wait(5.0) != PressureTicket.GRANTED:
+                errors.append("timeout")
+                return
+            peak[0] = max(peak[0], ledger.used("host"))
+            if ledger.used("host") > 64:
+                errors.append("over limit")
+            q.release(t)
+
+    threads = [threading.Thread(target=worker, args=(s,)) for s in range(6)]
+    [t.start() for t in threads]
+    [t.join(30) for t in threads]
+    assert errors == [] and ledger.used("host") == 0 and 0 < peak[0] <= 64 and not q.waiting
