@@ -253,6 +253,17 @@ def ncu_case(name: str, iters: int = 3):
         out = torch.empty(n, hq * d, device="cuda", dtype=torch.bfloat16)
         for _ in range(iters):
             ops.paged_decode(q, out, pool, table, ctx_t, hq, hkv, d)
+    elif name == "decode_fp8":
+        n, ctx = 256, 1200
+        pages_per = (ctx + 15) // 16
+        pool = (torch.randn(n * pages_per, hkv, 2, 16, d, device="cuda") * 0.5).to(torch.float8_e4m3fn).view(torch.uint8)
+        scales = torch.rand(n * pages_per, hkv, 2, device="cuda") * 0.02 + 0.005
+        table = torch.randperm(n * pages_per, device="cuda").to(torch.int32).view(n, pages_per)
+        ctx_t = torch.full((n,), ctx, dtype=torch.int32, device="cuda")
+        q = torch.randn(n, (hq + 2 * hkv) * d, device="cuda").bfloat16()
+        out = torch.empty(n, hq * d, device="cuda", dtype=torch.bfloat16)
+        for _ in range(iters):
+            ops.paged_decode(q, out, pool, table, ctx_t, hq, hkv, d, kv_scales=scales)
     elif name == "prefill":
         nseq, q_len = 4, 1024
         pages_per = q_len // 16
