@@ -430,6 +430,11 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
 
     async def _complete(body: dict, request: Request, chat: bool, session_header):
         opt = _options_from_request(body, 256, max_output_tokens)
+        n_choices = body.get("n", 1)
+        if not isinstance(n_choices, int) or isinstance(n_choices, bool) or not 1 <= n_choices <= 16:
+            raise HTTPException(400, f"n must be an integer between 1 and 16, not {n_choices!r}")
+        if n_choices > 1 and body.get("stream"):
+            raise HTTPException(400, "n > 1 is not supported with stream: true; request the samples without streaming")
         ids = _prompt_ids(body, chat, session_header)
         rid = ("chatcmpl-" if chat else "cmpl-") + uuid.uuid4().hex[:24]
         created = int(time.time())
@@ -495,42 +500,60 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
 
             return StreamingResponse(gen(), media_type="text/event-stream")
 
-        text, out_ids, fin, lps = "", [], None, []
-        while True:
-            ev = await q.get()
-            if ev[0] == "error":
-                raise HTTPException(500, ev[1])
-            if ev[0] == "token":
-                if not out_ids:
-                    metrics.ttft(time.perf_counter() - t0)
-                out_ids.append(ev[1])
-                text += ev[2]
-            elif ev[0] == "done":
-                fin, lps = ev[1], ev[3]
-                break
-        metrics.completion_tokens(len(out_ids))
+        async def collect(queue, pending=None):
+            """Drain one generation: (text, token ids, finish reason, logprobs)."""
+            text, out_ids, fin, lps = "", [], None, []
+            while True:
+                ev = pending if pending is not None else await queue.get()
+                pending = None
+                if ev[0] == "error":
+                    raise HTTPException(500, ev[1])
+                if ev[0] == "token":
+                    if not out_ids:
+                        metrics.ttft(time.perf_counter() - t0)
+                    out_ids.append(ev[1])
+                    text += ev[2]
+                elif ev[0] == "done":
+                    return text, out_ids, ev[1], ev[3]
+
+        def make_choice(index, text, out_ids, fin, lps):
+            if chat:
+                thought, text = reasoning_mod.split(text, think)
+                msg = {"role": "assistant", "content": text}
+                if thought is not None:
+                    msg["reasoning_content"] = thought
+                calls = tool_calls.parse_tool_calls(text) if body.get("tools") else []
+                if calls:
+                    msg = {"role": "assistant", "content": None, "tool_calls": calls}
+                    fin = "tool_calls"
+                choice = {"index": index, "message": msg, "finish_reason": fin}
+                if lps:
+                    choice["logprobs"] = {"content": [
+                        {"token": engine.detokenize([t]), "logprob": lp, "top_logprobs": [{"token": engine.detokenize([i]), "logprob": l} for i, l in top]}
+                        for t, (lp, top) in zip(out_ids, lps)]}
+            else:
+                choice = {"index": index, "text": text, "finish_reason": fin}
+                if lps:
+                    choice["logprobs"] = {"tokens": [engine.detokenize([t]) for t in out_ids], "token_logprobs": [lp for lp, _ in lps]}
+            return choice
+
+        queues, first_event = [q], None
+        if n_choices > 1:
+            # the other samples are submitted once the first has produced a token: by then its prompt pages are in the
+            # prefix cache, so the copies prefill only the last partial page instead of the whole prompt again
+            import dataclasses
+
+            first_event = await q.get()
+            for i in range(1, n_choices):
+                queues.append(await _run_generation(ids, dataclasses.replace(opt, seed=(opt.seed or 0) + i), request))
+        results = [await collect(q, first_event)] + [await collect(other) for other in queues[1:]]
+        total_out = sum(len(r[1]) for r in results)
+        metrics.completion_tokens(total_out)
         metrics.e2e(time.perf_counter() - t0)
-        finish_session(out_ids)
-        usage = {"prompt_tokens": len(ids), "completion_tokens": len(out_ids), "total_tokens": len(ids) + len(out_ids)}
-        if chat:
-            thought, text = reasoning_mod.split(text, think)
-            msg = {"role": "assistant", "content": text}
-            if thought is not None:
-                msg["reasoning_content"] = thought
-            calls = tool_calls.parse_tool_calls(text) if body.get("tools") else []
-            if calls:
-                msg = {"role": "assistant", "content": None, "tool_calls": calls}
-                fin = "tool_calls"
-            choice = {"index": 0, "message": msg, "finish_reason": fin}
-            if lps:
-                choice["logprobs"] = {"content": [
-                    {"token": engine.detokenize([t]), "logprob": lp, "top_logprobs": [{"token": engine.detokenize([i]), "logprob": l} for i, l in top]}
-                    for t, (lp, top) in zip(out_ids, lps)]}
-        else:
-            choice = {"index": 0, "text": text, "finish_reason": fin}
-            if lps:
-                choice["logprobs"] = {"tokens": [engine.detokenize([t]) for t in out_ids], "token_logprobs": [lp for lp, _ in lps]}
-        return JSONResponse({"id": rid, "object": obj, "created": created, "model": model_name, "choices": [choice], "usage": usage})
+        finish_session(results[0][1])
+        usage = {"prompt_tokens": len(ids), "completion_tokens": total_out, "total_tokens": len(ids) + total_out}
+        choices = [make_choice(i, *r) for i, r in enumerate(results)]
+        return JSONResponse({"id": rid, "object": obj, "created": created, "model": model_name, "choices": choices, "usage": usage})
 
     @app.post("/v1/completions")
     async def completions(request: Request, x_session_id: str | None = Header(default=None)):

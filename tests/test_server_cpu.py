@@ -91,3 +91,19 @@ def test_tool_call_parsing():
                              '<tool_call>{broken</tool_call>')
     assert len(calls) == 1 and calls[0]["function"]["name"] == "get_weather"
     assert json.loads(calls[0]["function"]["arguments"]) == {"city": "Oslo"}
+
+
+def test_n_returns_independent_samples_and_shares_the_prompt(client):
+    body = {"model": "tiny", "prompt": "once upon a time there was a", "max_tokens": 6, "temperature": 1.0, "seed": 3, "n": 3}
+    r = client.post("/v1/completions", json=body)
+    assert r.status_code == 200, r.text
+    out = r.json()
+    assert [c["index"] for c in out["choices"]] == [0, 1, 2] and out["usage"]["completion_tokens"] == 18
+    assert len({c["text"] for c in out["choices"]}) >= 2                      # different seeds, different samples
+    again = client.post("/v1/completions", json=body).json()
+    assert [c["text"] for c in again["choices"]] == [c["text"] for c in out["choices"]]      # reproducible from the seed
+    greedy = client.post("/v1/chat/completions", json={"model": "tiny", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 4,
+                                                       "temperature": 0, "n": 2}).json()
+    assert greedy["choices"][0]["message"]["content"] == greedy["choices"][1]["message"]["content"]
+    assert client.post("/v1/completions", json={**body, "n": 0}).status_code == 400
+    assert client.post("/v1/completions", json={**body, "stream": True}).status_code == 400
