@@ -300,10 +300,20 @@ def cmd_serve(args, profiler):
             reg.warmup([os.path.basename(os.path.abspath(args.model))])
         app = RegistryApp(reg, enable_admin_endpoints=args.enable_admin_endpoints)
     else:
+        if not args.model and args.image_package:
+            from .server.images import create_image_app
+
+            app = create_image_app(args.image_package, device="cuda" if args.device.startswith("cuda") else "cpu")
+            uvicorn.run(app, host=host or "127.0.0.1", port=int(port), log_level="info")
+            return 0
         if not args.model:
-            print("serve: give a model directory, --models-dir or --models-config", file=sys.stderr)
+            print("serve: give a model directory, --models-dir, --models-config or --image-package", file=sys.stderr)
             return 2
         eng = _load(args)
+        if args.image_package:
+            from .server.images import ImagePipeline
+
+            app_kw["image_pipeline"] = ImagePipeline(args.image_package, "cuda" if args.device.startswith("cuda") else "cpu")
         app = create_app(eng, model_name=os.path.basename(os.path.abspath(args.model)), **app_kw)
     uvicorn.run(app, host=host or "127.0.0.1", port=int(port), log_level="info")
     return 0
@@ -358,25 +368,10 @@ def cmd_run_workflow(args) -> int:
 
 
 def _save_png(path: str, chw) -> None:
-    """Minimal PNG writer (8-bit RGB or grey), so image workflows need no imaging library."""
-    import struct
-    import zlib
-
-    import numpy as np
-
-    x = np.asarray(chw, dtype=np.float32)
-    lo = -1.0 if x.min() < 0 else 0.0
-    x = np.clip((x - lo) / (1.0 - lo), 0.0, 1.0)
-    img = (x * 255.0 + 0.5).astype(np.uint8).transpose(1, 2, 0)
-    h, w, c = img.shape
-    raw = b"".join(b"\x00" + img[r].tobytes() for r in range(h))
-
-    def chunk(tag, data):
-        return struct.pack(">I", len(data)) + tag + data + struct.pack(">I", zlib.crc32(tag + data) & 0xFFFFFFFF)
+    from .utils.png import encode_png
 
     with open(path, "wb") as f:
-        f.write(b"\x89PNG\r\n\x1a\n" + chunk(b"IHDR", struct.pack(">IIBBBBB", w, h, 8, 2 if c == 3 else 0, 0, 0, 0)) +
-                chunk(b"IDAT", zlib.compress(raw, 6)) + chunk(b"IEND", b""))
+        f.write(encode_png(chw))
 
 
 def cmd_show(args, profiler):
@@ -545,6 +540,7 @@ def main(argv=None):
     s.add_argument("--node-id", default="node-0")
     s.add_argument("--default-reasoning-effort", default="", choices=["", "low", "medium", "high"],
                    help="reasoning effort handed to chat templates that take one, when a request names none")
+    s.add_argument("--image-package", default="", help="text-to-image workflow package to serve at /v1/images/generations and /sdapi/v1/txt2img")
     s.add_argument("--models-config", default="", help="YAML or JSON file: models: {name: {path: DIR, ...engine flags}}")
     s.add_argument("--max-context", type=int, default=0)
     _add_engine(s)

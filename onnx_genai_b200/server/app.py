@@ -207,7 +207,7 @@ def _options_from_request(body: dict, default_max: int, max_cap: int) -> Generat
 
 def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int = 4096, max_queue_depth: int = 256,
                enable_debug_endpoints: bool = False, node_id: str = "node-0", admission_window_ms: float = 2.0,
-               default_reasoning_effort: str | None = None) -> FastAPI:
+               default_reasoning_effort: str | None = None, image_pipeline=None) -> FastAPI:
     app = FastAPI(title="onnx-genai-b200")
     driver = EngineDriver(engine, max_queue_depth, admission_window_ms)
     metrics = Metrics()
@@ -313,8 +313,12 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
         metrics.prompt_tokens(total)
         return {"object": "list", "model": model_name, "data": data, "usage": {"prompt_tokens": total, "total_tokens": total}}
 
-    # Media routes of the reference server (image generation, speech, transcription): this build serves decoder-only
-    # text models, so they answer 501 with the reason instead of 404.
+    # Media routes of the reference server.  Image generation is served when a text-to-image workflow package is mounted
+    # (``image_pipeline``, see server/images.py); speech, transcription and image-to-image answer 501 with the reason.
+    if image_pipeline is not None:
+        from .images import add_image_routes
+
+        add_image_routes(app, image_pipeline, model_name)
     def _not_served(kind: str):
         async def handler():
             raise HTTPException(501, f"{kind} needs a {kind.split()[0]} model pipeline; this server hosts decoder-only text models "
@@ -324,6 +328,8 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
     for _path, _kind in (("/v1/images/generations", "image generation"), ("/sdapi/v1/txt2img", "image generation"),
                          ("/sdapi/v1/img2img", "image generation"), ("/v1/audio/transcriptions", "audio transcription"),
                          ("/v1/audio/speech", "speech synthesis")):
+        if image_pipeline is not None and _path in ("/v1/images/generations", "/sdapi/v1/txt2img"):
+            continue
         app.post(_path)(_not_served(_kind))
 
     if enable_debug_endpoints:
