@@ -300,20 +300,34 @@ def cmd_serve(args, profiler):
             reg.warmup([os.path.basename(os.path.abspath(args.model))])
         app = RegistryApp(reg, enable_admin_endpoints=args.enable_admin_endpoints)
     else:
-        if not args.model and args.image_package:
-            from .server.images import create_image_app
+        media_device = "cuda" if args.device.startswith("cuda") else "cpu"
+        if not args.model and (args.image_package or args.speech_package):
+            from fastapi import FastAPI
 
-            app = create_image_app(args.image_package, device="cuda" if args.device.startswith("cuda") else "cpu")
+            app = FastAPI(title="onnx-genai-b200 media")
+            if args.image_package:
+                from .server.images import ImagePipeline, add_image_routes
+
+                add_image_routes(app, ImagePipeline(args.image_package, media_device), os.path.basename(os.path.abspath(args.image_package)))
+            if args.speech_package:
+                from .server.audio import SpeechPipeline, add_speech_routes
+
+                add_speech_routes(app, SpeechPipeline(args.speech_package, media_device))
+            app.get("/health")(lambda: {"status": "ok"})
             uvicorn.run(app, host=host or "127.0.0.1", port=int(port), log_level="info")
             return 0
         if not args.model:
-            print("serve: give a model directory, --models-dir, --models-config or --image-package", file=sys.stderr)
+            print("serve: give a model directory, --models-dir, --models-config, --image-package or --speech-package", file=sys.stderr)
             return 2
         eng = _load(args)
         if args.image_package:
             from .server.images import ImagePipeline
 
-            app_kw["image_pipeline"] = ImagePipeline(args.image_package, "cuda" if args.device.startswith("cuda") else "cpu")
+            app_kw["image_pipeline"] = ImagePipeline(args.image_package, media_device)
+        if args.speech_package:
+            from .server.audio import SpeechPipeline
+
+            app_kw["speech_pipeline"] = SpeechPipeline(args.speech_package, media_device)
         app = create_app(eng, model_name=os.path.basename(os.path.abspath(args.model)), **app_kw)
     uvicorn.run(app, host=host or "127.0.0.1", port=int(port), log_level="info")
     return 0
@@ -541,6 +555,7 @@ def main(argv=None):
     s.add_argument("--default-reasoning-effort", default="", choices=["", "low", "medium", "high"],
                    help="reasoning effort handed to chat templates that take one, when a request names none")
     s.add_argument("--image-package", default="", help="text-to-image workflow package to serve at /v1/images/generations and /sdapi/v1/txt2img")
+    s.add_argument("--speech-package", default="", help="text-to-speech workflow package to serve at /v1/audio/speech")
     s.add_argument("--models-config", default="", help="YAML or JSON file: models: {name: {path: DIR, ...engine flags}}")
     s.add_argument("--max-context", type=int, default=0)
     _add_engine(s)

@@ -187,6 +187,19 @@ def read_wav(data: bytes):
     return x.astype(np.float32), int(rate)
 
 
+def write_wav(samples, sample_rate: int) -> bytes:
+    """RIFF/WAVE bytes, 16-bit little-endian PCM.  ``samples``: [n] mono or [channels, n], floats in [-1, 1] (clipped)."""
+    x = np.asarray(samples, dtype=np.float32)
+    if x.ndim == 1:
+        x = x[None]
+    if x.ndim != 2 or x.shape[0] > 8:
+        raise PreprocessError(f"write_wav wants [n] or [channels, n] with at most 8 channels, got {list(x.shape)}")
+    channels, n = x.shape
+    pcm = (np.clip(x, -1.0, 1.0) * 32767.0).round().astype("<i2").T.reshape(-1).tobytes()       # interleaved frames
+    fmt = struct.pack("<HHIIHH", 1, channels, int(sample_rate), int(sample_rate) * channels * 2, channels * 2, 16)
+    return b"RIFF" + struct.pack("<I", 36 + len(pcm)) + b"WAVE" + b"fmt " + struct.pack("<I", 16) + fmt + b"data" + struct.pack("<I", len(pcm)) + pcm
+
+
 def resample(samples, src_rate: int, dst_rate: int, taps: int = 32) -> np.ndarray:
     """Band-limited (Hann-windowed sinc) resampling: each output sample is a weighted sum of the 2*taps+1 input
     samples around its position, with the cut-off at the lower of the two Nyquist rates."""

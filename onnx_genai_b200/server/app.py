@@ -207,7 +207,7 @@ def _options_from_request(body: dict, default_max: int, max_cap: int) -> Generat
 
 def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int = 4096, max_queue_depth: int = 256,
                enable_debug_endpoints: bool = False, node_id: str = "node-0", admission_window_ms: float = 2.0,
-               default_reasoning_effort: str | None = None, image_pipeline=None) -> FastAPI:
+               default_reasoning_effort: str | None = None, image_pipeline=None, speech_pipeline=None) -> FastAPI:
     app = FastAPI(title="onnx-genai-b200")
     driver = EngineDriver(engine, max_queue_depth, admission_window_ms)
     metrics = Metrics()
@@ -314,11 +314,16 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
         return {"object": "list", "model": model_name, "data": data, "usage": {"prompt_tokens": total, "total_tokens": total}}
 
     # Media routes of the reference server.  Image generation is served when a text-to-image workflow package is mounted
-    # (``image_pipeline``, see server/images.py); speech, transcription and image-to-image answer 501 with the reason.
+    # (``image_pipeline``, see server/images.py), speech synthesis when a speech package is (``speech_pipeline``, server/audio.py);
+    # transcription and image-to-image answer 501 with the reason.
     if image_pipeline is not None:
         from .images import add_image_routes
 
         add_image_routes(app, image_pipeline, model_name)
+    if speech_pipeline is not None:
+        from .audio import add_speech_routes
+
+        add_speech_routes(app, speech_pipeline)
     def _not_served(kind: str):
         async def handler():
             raise HTTPException(501, f"{kind} needs a {kind.split()[0]} model pipeline; this server hosts decoder-only text models "
@@ -329,6 +334,8 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
                          ("/sdapi/v1/img2img", "image generation"), ("/v1/audio/transcriptions", "audio transcription"),
                          ("/v1/audio/speech", "speech synthesis")):
         if image_pipeline is not None and _path in ("/v1/images/generations", "/sdapi/v1/txt2img"):
+            continue
+        if speech_pipeline is not None and _path == "/v1/audio/speech":
             continue
         app.post(_path)(_not_served(_kind))
 
