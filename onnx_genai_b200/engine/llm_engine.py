@@ -35,6 +35,7 @@ from .core import HDR, Core, CoreConfig
 class EngineConfig:
     model: DecoderConfig
     num_pages: int = 0                 # 0: size from free device memory
+    host_allocator_plugin: str = ""    # shared library implementing the memory plugin ABI: the host swap space comes from it
     kv_max_pages: int = 0              # > num_pages (CUDA, TP=1): reserve address space for this many pages, back num_pages now
                                        # and more on demand when the scheduler runs low (the pool grows in place)
     gpu_memory_utilization: float = 0.85
@@ -146,8 +147,20 @@ class LLMEngine:
         self.host_kv = None
         if cfg.num_host_pages > 0:
             shape = (cfg.num_host_pages,) + tuple(self.kv.pools[0].shape[1:])
-            self.host_kv = [torch.zeros(shape, dtype=self.kv.pools[0].dtype, pin_memory=is_cuda)
-                            for _ in range(m.num_layers)]
+            if cfg.host_allocator_plugin:
+                # swap space from a third-party allocator (memory plugin ABI); copies to it are synchronous, as for any
+                # host memory the CUDA driver has not pinned
+                from ..utils.mem_plugin import PluginAllocator
+
+                self.host_allocator = PluginAllocator(cfg.host_allocator_plugin, purpose="kv-swap")
+                self.host_kv = [self.host_allocator.tensor(shape, self.kv.pools[0].dtype) for _ in range(m.num_layers)]
+            else:
+                self.host_kv = [torch.zeros(shape, dtype=self.kv.pools[0].dtype, pin_memory=is_cuda)
+                                for _ in range(m.num_layers)]
+            try:
+                self.memory.lease("kv", "host", sum(t.numel() * t.element_size() for t in self.host_kv), "swap space")
+            except Exception:
+                pass
             self.swap_stage = torch.zeros((max_pages_per_seq,) + tuple(self.kv.pools[0].shape[1:]),
                                           dtype=self.kv.pools[0].dtype, device=self.device)
         p = self.plan_dev
