@@ -107,7 +107,7 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
 def build_runtime(force: bool = False, verbose: bool = False) -> Path:
     srcs = runtime_sources()
     hdrs: list[Path] = []
-    for sub in ("runtime", "cpu_ref", "capi"):
+    for sub in ("runtime", "cpu_ref", "capi", "abi"):
         hdrs += sorted((ROOT / "csrc" / sub).glob("*.h")) + sorted((ROOT / "csrc" / sub).glob("*.hpp"))
     digest = _digest(srcs + hdrs, " ".join(CXX_FLAGS))
     if not force and _stamp_ok(RUNTIME_LIB, digest):

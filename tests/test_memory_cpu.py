@@ -127,3 +127,32 @@ def test_pressure_queue_under_threads_never_exceeds_the_limit():
     [t.start() for t in threads]
     [t.join(30) for t in threads]
     assert errors == [] and ledger.used("host") == 0 and 0 < peak[0] <= 64 and not q.waiting
+
+
+def test_host_growable_buffer_keeps_its_address_and_returns_pages():
+    import torch
+
+    from onnx_genai_b200.utils.host_vmm import HostGrowableBuffer, HostVmmError
+
+    buf = HostGrowableBuffer(1 << 30)                      # address space only: nothing is committed
+    assert buf.committed == 0 and buf.reserved >= 1 << 30
+    base = buf.ptr
+    buf.grow(100_000)
+    assert buf.committed % buf.page == 0 and buf.committed >= 100_000
+    a = buf.view(torch.int32, (1000,))
+    a.copy_(torch.arange(1000, dtype=torch.int32))
+    first = buf.committed
+    buf.grow(8 << 20)
+    whole = buf.view(torch.uint8)
+    assert buf.ptr == base and whole.data_ptr() == a.data_ptr() and whole.numel() == buf.committed
+    assert torch.equal(buf.view(torch.int32, (1000,)), torch.arange(1000, dtype=torch.int32))      # contents survive growth
+    whole[first:].fill_(7)
+    del whole
+    assert buf.shrink(first) == first
+    buf.grow(8 << 20)
+    assert int(buf.view(torch.uint8)[first:].sum()) == 0   # pages given back come back as fresh zero pages
+    with pytest.raises(HostVmmError, match="exceeds the"):
+        buf.view(torch.uint8, (buf.committed + 1,))
+    with pytest.raises(HostVmmError, match="address space were reserved"):
+        buf.grow(2 << 30)
+    buf.close()
