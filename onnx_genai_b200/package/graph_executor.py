@@ -13,8 +13,8 @@ Coverage: the dense, convolutional, normalisation, activation, shape and indexin
 that such graphs use (see ``OPS``), plus the ``com.microsoft`` contrib forms ``Gelu``, ``FastGelu``, ``BiasGelu``,
 ``SkipLayerNormalization``, ``SimplifiedLayerNormalization``, ``SkipSimplifiedLayerNormalization``, ``GroupQueryAttention``
 (separate past / present buffers) and ``MatMulNBits``.
-Control flow (``If`` / ``Loop`` / ``Scan``) is not interpreted: loops belong to the workflow document.  An operator
-outside the table is an error that names the node and lists what is covered.
+``If`` and ``Loop`` run their subgraphs in a scope chained over the enclosing one (bodies may read outer values by name);
+``Scan`` is not covered.  An operator outside the table is an error that names the node and lists what is covered.
 
 ``as_component(path)`` wraps a graph as a workflow component: a callable from a dict of input ports to a dict of
 output ports (ports are the graph's input and output names).
@@ -567,6 +567,35 @@ OPS = {
 }
 
 
+CONTROL_FLOW = ("If", "Loop")
+_STRUCTURAL = ("Constant", "Split") + CONTROL_FLOW
+
+
+def _subgraphs(node):
+    return [v for v in node.attrs.values() if isinstance(v, onnx_pb.Graph)]
+
+
+def _all_nodes(graph):
+    for n in graph.nodes:
+        yield n
+        for sub in _subgraphs(n):
+            yield from _all_nodes(sub)
+
+
+def _free_values(graph) -> set:
+    """Names a (sub)graph reads from an enclosing scope: used, but neither its inputs, its initializers nor produced in it."""
+    defined = {vi.name for vi in graph.inputs} | set(graph.initializers)
+    free = set()
+    for n in graph.nodes:
+        for x in n.inputs:
+            if x and x not in defined:
+                free.add(x)
+        for sub in _subgraphs(n):
+            free |= {x for x in _free_values(sub) if x not in defined}
+        defined.update(o for o in n.outputs if o)
+    return free
+
+
 class GraphExecutor:
     def __init__(self, model, device="cpu", dtype=None):
         """``model``: a path to an ``.onnx`` file or a parsed :class:`onnx_pb.Model`.  Initializers move to ``device``
@@ -583,11 +612,12 @@ class GraphExecutor:
         self.input_names = [vi.name for vi in g.inputs if vi.name not in self.constants]
         self.output_names = [vi.name for vi in g.outputs]
         self.input_types = {vi.name: vi.elem_type for vi in g.inputs}
-        unknown = sorted({(n.domain + "::" if n.domain else "") + n.op_type for n in g.nodes if n.op_type not in OPS and n.op_type != "Constant"
-                          and n.op_type != "Split"})
+        unknown = sorted({(n.domain + "::" if n.domain else "") + n.op_type for n in _all_nodes(g) if n.op_type not in OPS
+                          and n.op_type not in _STRUCTURAL})
         if unknown:
             raise GraphExecutionError(f"graph '{g.name}' uses operators outside the covered set: {', '.join(unknown)} "
-                                      f"({len(OPS) + 2} operators are covered; control flow belongs to the workflow document)")
+                                      f"({len(OPS) + len(_STRUCTURAL)} operators are covered, If and Loop among them; Scan is not)")
+        self._sub_constants: dict = {}        # id(subgraph) -> its initializers on the device
         self.order = self._toposort(g)
         self.runs = 0
 
@@ -597,7 +627,8 @@ class GraphExecutor:
         while pending:
             rest = []
             for n in pending:
-                if all((not x) or x in produced for x in n.inputs):
+                needs = [x for x in n.inputs if x] + [x for sub in _subgraphs(n) for x in _free_values(sub)]   # bodies capture outer values
+                if all(x in produced for x in needs):
                     order.append(n)
                     produced.update(o for o in n.outputs if o)
                 else:
@@ -622,27 +653,85 @@ class GraphExecutor:
                 t = t.to(want)
             env[name] = t.to(self.device)
         for n in self.order:
-            ins = [env[x] if x else None for x in n.inputs]
-            try:
-                if n.op_type == "Constant":
-                    res = _constant(ins, n.attrs, self.device)
-                elif n.op_type == "Split":
-                    res = _split(ins, n.attrs, len(n.outputs))
-                else:
-                    res = OPS[n.op_type](ins, n.attrs)
-            except GraphExecutionError:
-                raise
-            except Exception as e:
-                shapes = [tuple(t.shape) if isinstance(t, torch.Tensor) else None for t in ins]
-                raise GraphExecutionError(f"node '{n.name or n.outputs[0]}' ({n.op_type}) failed on inputs {shapes}: {e}") from e
-            if isinstance(res, (list, tuple)):
-                for name, r in zip(n.outputs, res):
-                    if name and r is not None:
-                        env[name] = r
-            else:
-                env[n.outputs[0]] = res
+            self._exec_node(n, env)
         self.runs += 1
         return {name: env[name] for name in (outputs or self.output_names)}
+
+
+def _exec_node(self, n, env) -> None:
+    """Run one node against ``env`` (a dict, or a chained scope for control-flow bodies) and bind its outputs there."""
+    ins = [env[x] if x else None for x in n.inputs]
+    try:
+        if n.op_type == "Constant":
+            res = _constant(ins, n.attrs, self.device)
+        elif n.op_type == "Split":
+            res = _split(ins, n.attrs, len(n.outputs))
+        elif n.op_type == "If":
+            branch = n.attrs["then_branch"] if bool(ins[0].reshape(-1)[0]) else n.attrs["else_branch"]
+            res = self._run_body(branch, env, {})
+        elif n.op_type == "Loop":
+            res = self._loop(n, ins, env)
+        else:
+            res = OPS[n.op_type](ins, n.attrs)
+    except GraphExecutionError:
+        raise
+    except Exception as e:
+        shapes = [tuple(t.shape) if isinstance(t, torch.Tensor) else None for t in ins]
+        raise GraphExecutionError(f"node '{n.name or n.outputs[0]}' ({n.op_type}) failed on inputs {shapes}: {e}") from e
+    if isinstance(res, (list, tuple)):
+        for name, r in zip(n.outputs, res):
+            if name and r is not None:
+                env[name] = r
+    else:
+        env[n.outputs[0]] = res
+
+
+def _run_body(self, graph, outer, feeds: dict) -> list:
+    """A control-flow body: its own scope over the enclosing one (bodies read outer values by name); returns its outputs."""
+    import collections
+
+    consts = self._sub_constants.get(id(graph))
+    if consts is None:
+        consts = self._sub_constants[id(graph)] = {k: tensor_to_torch(t, self.device) for k, t in graph.initializers.items()}
+    scope = collections.ChainMap(dict(feeds), consts, outer)
+    for node in graph.nodes:                       # bodies are stored in execution order
+        self._exec_node(node, scope)
+    return [scope[vi.name] for vi in graph.outputs]
+
+
+def _loop(self, n, ins, env) -> list:
+    """Loop: inputs (trip count | "", condition | "", carried...); body (iteration, condition, carried...) ->
+    (condition, carried..., scan outputs...).  Outputs: the final carried values, then each scan output stacked."""
+    body = n.attrs["body"]
+    limit = int(ins[0].reshape(-1)[0]) if ins[0] is not None else None
+    cond = bool(ins[1].reshape(-1)[0]) if len(ins) > 1 and ins[1] is not None else True
+    carried = list(ins[2:])
+    names = [vi.name for vi in body.inputs]
+    n_scan = len(body.outputs) - 1 - len(carried)
+    if len(names) != 2 + len(carried) or n_scan < 0:
+        raise GraphExecutionError(f"Loop body takes {len(names)} inputs and gives {len(body.outputs)} outputs for {len(carried)} carried values")
+    scans = [[] for _ in range(n_scan)]
+    it = 0
+    while cond and (limit is None or it < limit):
+        if it >= 1_000_000:
+            raise GraphExecutionError("Loop ran a million iterations without its condition turning false")
+        feeds = {names[0]: torch.tensor(it, dtype=torch.int64, device=self.device), names[1]: torch.tensor(cond, device=self.device)}
+        feeds.update(zip(names[2:], carried))
+        out = self._run_body(body, env, feeds)
+        cond = bool(out[0].reshape(-1)[0])
+        carried = list(out[1:1 + len(carried)])
+        for acc, v in zip(scans, out[1 + len(carried):]):
+            acc.append(v)
+        it += 1
+    stacked = []
+    for acc, vi in zip(scans, body.outputs[1 + len(carried):]):
+        stacked.append(torch.stack(acc) if acc else torch.zeros((0,), dtype=_TORCH_DTYPE.get(vi.elem_type, torch.float32), device=self.device))
+    return carried + stacked
+
+
+GraphExecutor._exec_node = _exec_node
+GraphExecutor._run_body = _run_body
+GraphExecutor._loop = _loop
 
 
 def as_component(model, device="cpu", dtype=None):

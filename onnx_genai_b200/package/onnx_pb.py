@@ -254,6 +254,8 @@ def _decode_attr(buf, span, base_dir, mapped):
             val = bytes(buf[v[0]:v[1]])
         elif fn == 5:
             val = _decode_tensor(buf, v, base_dir, mapped)
+        elif fn == 6:                      # a subgraph (If / Loop / Scan bodies)
+            val = _decode_graph(buf, v, base_dir, mapped)
         elif fn == 7:
             floats += list(np.frombuffer(buf[v[0]:v[1]], dtype="<f4")) if wt == 2 else [struct.unpack("<f", struct.pack("<I", v))[0]]
         elif fn == 8:
@@ -405,6 +407,8 @@ def _enc_attr(name, val) -> bytes:
         out += _ld(4, val.encode()) + _int(20, 3)
     elif isinstance(val, Tensor):
         out += _ld(5, _enc_tensor(val)) + _int(20, 4)
+    elif isinstance(val, Graph):
+        out += _ld(6, _enc_graph(val)) + _int(20, 5)
     elif isinstance(val, (list, tuple)) and val and isinstance(val[0], float):
         for f in val:
             out += _key(7, 5) + struct.pack("<f", f)
@@ -440,6 +444,21 @@ def _enc_node(n: Node) -> bytes:
     if n.domain:
         out += _str(7, n.domain)
     return bytes(out)
+
+
+def _enc_graph(g: Graph) -> bytes:
+    """A subgraph, tensors inline (bodies of control-flow operators are small)."""
+    gb = bytearray()
+    for n in g.nodes:
+        gb += _ld(1, _enc_node(n))
+    gb += _str(2, g.name)
+    for t in g.initializers.values():
+        gb += _ld(5, _enc_tensor(t))
+    for vi in g.inputs:
+        gb += _ld(11, _enc_value_info(vi))
+    for vi in g.outputs:
+        gb += _ld(12, _enc_value_info(vi))
+    return bytes(gb)
 
 
 def save_model(model: Model, path: str, external_data: bool = True) -> None:

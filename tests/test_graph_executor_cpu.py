@@ -256,3 +256,33 @@ def test_tensor_scatter_linear_and_circular():
               [("c", pb.FLOAT, (2, 1, 5, 2)), ("u", pb.FLOAT, (2, 1, 2, 2))], ["o"])
     with pytest.raises(GraphExecutionError, match="into a cache of length 5"):
         GraphExecutor(m).run({"c": cache, "u": upd})
+
+
+def test_if_and_loop_with_captured_outer_values(tmp_path):
+    """If picks a branch; Loop carries state, emits a scan output and stops on its condition; bodies read outer values."""
+    vi = lambda n, dt=pb.FLOAT, shape=(): pb.ValueInfo(n, dt, shape)
+    then_g = pb.Graph(name="then", nodes=[N("Mul", ["x", "two"], ["t_out"])], outputs=[vi("t_out")])            # captures x and two
+    else_g = pb.Graph(name="else", nodes=[N("Neg", ["x"], ["e_out"])], outputs=[vi("e_out")])
+    # body: acc <- acc + y * step ; keep going while acc < limit ; scan output = acc
+    body = pb.Graph(name="body", inputs=[vi("i", pb.INT64), vi("c", pb.BOOL), vi("acc")],
+                    nodes=[N("Mul", ["y", "step"], ["inc"]), N("Add", ["acc", "inc"], ["acc_next"]), N("Less", ["acc_next", "limit"], ["c_next"]),
+                           N("Identity", ["acc_next"], ["trace"])],
+                    outputs=[vi("c_next", pb.BOOL), vi("acc_next"), vi("trace")])
+    m = model([N("Greater", ["s", "zero"], ["pos"]), N("If", ["pos"], ["y"], then_branch=then_g, else_branch=else_g),
+               N("Loop", ["trips", "go", "zero"], ["final", "history"], body=body)],
+              [T("two", np.asarray(2.0, np.float32)), T("zero", np.asarray(0.0, np.float32)), T("step", np.asarray(0.5, np.float32)),
+               T("limit", np.asarray(7.0, np.float32)), T("trips", np.asarray(10, np.int64)), T("go", np.asarray(True))],
+              [("x", pb.FLOAT, ()), ("s", pb.FLOAT, ())], ["y", "final", "history"], tmp_path)          # through the binary codec
+    ex = GraphExecutor(m)
+    out = ex.run({"x": torch.tensor(3.0), "s": torch.tensor(1.0)})
+    assert float(out["y"]) == 6.0                                     # then-branch: x * 2
+    assert out["history"].tolist() == [3.0, 6.0, 9.0] and float(out["final"]) == 9.0      # stops once acc >= 7
+    out = ex.run({"x": torch.tensor(3.0), "s": torch.tensor(-1.0)})
+    assert float(out["y"]) == -3.0 and out["history"].tolist() == [-1.5 * k for k in range(1, 11)]     # never reaches the limit: trip count ends it
+    bad_body = pb.Graph(name="b", inputs=[vi("i", pb.INT64)], nodes=[N("Identity", ["i"], ["o"])], outputs=[vi("o", pb.INT64)])
+    bad = model([N("Loop", ["trips", "", "x"], ["r"], body=bad_body)], [T("trips", np.asarray(2, np.int64))], [("x", pb.FLOAT, ())], ["r"])
+    with pytest.raises(GraphExecutionError, match="Loop body takes 1 inputs"):
+        GraphExecutor(bad).run({"x": torch.tensor(1.0)})
+    nested_unknown = pb.Graph(name="t", nodes=[N("Sort", ["x"], ["o"])], outputs=[vi("o")])
+    with pytest.raises(GraphExecutionError, match="outside the covered set: Sort"):
+        GraphExecutor(model([N("If", ["c"], ["y"], then_branch=nested_unknown, else_branch=else_g)], [], [("x", pb.FLOAT, ()), ("c", pb.BOOL, ())], ["y"]))
