@@ -188,7 +188,14 @@ def _generate_on_graph_backend(args) -> int:
 def cmd_generate(args, profiler):
     if getattr(args, "backend", "native") == "graph":
         return _generate_on_graph_backend(args)
-    eng = _load(args)
+    from .package.decoder_graph import GraphPatternError
+
+    try:
+        eng = _load(args)
+    except GraphPatternError as e:
+        print(f"generate: {e}\nThe fast path does not recognise this decoder graph; it can still run node by node: add --backend graph",
+              file=sys.stderr)
+        return 2
     prompt = args.prompt if args.prompt is not None else sys.stdin.read()
     t_lat = []
     last = [time.perf_counter()]
@@ -390,12 +397,12 @@ def _save_png(path: str, chw) -> None:
 
 def cmd_show(args, profiler):
     from . import package as pkg
-    from .package import onnx_pb
+    from .package.onnx_text import load_any
     from .package.decoder_graph import lower_decoder
 
     d = pkg.open_model_directory(args.model)
     meta = d.load_metadata()
-    model = onnx_pb.load_model(d.model_path)
+    model = load_any(d.model_path)
     ops_count: dict = {}
     for n in model.graph.nodes:
         key = (n.domain + "::" if n.domain else "") + n.op_type
@@ -416,7 +423,7 @@ def cmd_validate(args, profiler):
     int4 tensors have consistent shapes.  The counterpart of the reference's `validate_metadata` tool and checker."""
     from . import metadata as md
     from . import package as pkg
-    from .package import onnx_pb
+    from .package.onnx_text import load_any
     from .package.decoder_graph import lower_decoder
 
     problems, notes = [], []
@@ -432,7 +439,7 @@ def cmd_validate(args, profiler):
         problems.append(f"metadata: {exc}")
     cfg = None
     try:
-        cfg, weights, _ = lower_decoder(onnx_pb.load_model(d.model_path), keep_int4=True)
+        cfg, weights, _ = lower_decoder(load_any(d.model_path), keep_int4=True)
         notes.append(f"decoder graph recognised: {cfg.num_layers} layers, hidden {cfg.hidden}, {cfg.num_heads}/{cfg.num_kv_heads} heads "
                      f"of {cfg.head_dim}, vocab {cfg.vocab}, weights {cfg.weight_format}")
         for li, lw in enumerate(weights.layers):

@@ -21,6 +21,7 @@ from .. import metadata as md
 from .. import package as pkg
 from ..package import onnx_pb
 from ..package.decoder_graph import lower_decoder
+from ..package.onnx_text import load_any
 from ..speculative import SpeculativeStats
 from . import processors as procs
 from .llm_engine import EngineConfig, LLMEngine
@@ -136,7 +137,7 @@ class Engine:
             from ..ops import cpu as _cpu_ops
 
             keep_int4 = str(device).startswith("cuda") or _cpu_ops.available()
-        cfg, weights, _ = lower_decoder(onnx_pb.load_model(d.model_path), dtype=dtype, device=device, keep_int4=keep_int4)
+        cfg, weights, _ = lower_decoder(load_any(d.model_path), dtype=dtype, device=device, keep_int4=keep_int4)
         if meta.vocab_size and meta.vocab_size != cfg.vocab:
             raise md.MetadataError(f"{d.metadata_path}: model.vocab_size={meta.vocab_size} but the graph's embedding has "
                                    f"{cfg.vocab} rows; fix the metadata or re-export the model")

@@ -85,6 +85,8 @@ def _find_onnx(d: str) -> str:
         if os.path.exists(os.path.join(d, name)):
             return os.path.join(d, name)
     cands = sorted(f for f in os.listdir(d) if f.endswith(".onnx"))
+    if not cands:                      # text-format models (fixtures, hand-written graphs)
+        cands = sorted(f for f in os.listdir(d) if f.endswith(".onnx.textproto"))
     if len(cands) == 1:
         return os.path.join(d, cands[0])
     if not cands:

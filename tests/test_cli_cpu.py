@@ -82,3 +82,17 @@ def test_graph_backend_prints_the_same_greedy_text(pkg_dir):
     graph = subprocess.run(base + ["--backend", "graph"], capture_output=True, text=True)
     assert native.returncode == 0 and graph.returncode == 0, graph.stderr
     assert graph.stdout == native.stdout and "backend graph" in graph.stderr
+
+
+def test_unrecognised_decoder_points_to_the_graph_backend(tmp_path):
+    import os
+
+    ref = os.environ.get("OGB_REFERENCE_DIR", os.path.join(os.path.expanduser("~"), "reference"))
+    src = os.path.join(ref, "tests", "fixtures", "tiny-llm")
+    if not os.path.isdir(src):
+        pytest.skip("the upstream tiny-llm fixture is not available on this machine")
+    base = [sys.executable, "-m", "onnx_genai_b200", "generate", src, "--prompt", "ab", "--max-new-tokens", "3", "--greedy", "--device", "cpu", "--raw"]
+    fast = subprocess.run(base, capture_output=True, text=True)
+    assert fast.returncode == 2 and "--backend graph" in fast.stderr
+    graph = subprocess.run(base + ["--backend", "graph"], capture_output=True, text=True)
+    assert graph.returncode == 0 and "backend graph" in graph.stderr, graph.stderr
