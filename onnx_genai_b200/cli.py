@@ -407,12 +407,20 @@ def cmd_show(args, profiler):
     for n in model.graph.nodes:
         key = (n.domain + "::" if n.domain else "") + n.op_type
         ops_count[key] = ops_count.get(key, 0) + 1
-    cfg, _, _ = lower_decoder(model)
+    from .package.decoder_graph import GraphPatternError
+
+    try:
+        cfg, _, _ = lower_decoder(model)
+        arch = {k: getattr(cfg, k) for k in ("num_layers", "hidden", "num_heads", "num_kv_heads", "head_dim",
+                                             "intermediate", "vocab", "weight_format", "tie_embeddings", "qkv_bias")}
+        weight_bytes = cfg.weight_bytes()
+    except GraphPatternError as e:      # not a decoder the fast path lowers: still describable, and runnable with --backend graph
+        arch = {"recognised_by_fast_path": False, "reason": str(e), "runs_with": "--backend graph"}
+        weight_bytes = sum(int(t.array.nbytes) for t in model.graph.initializers.values() if t.array is not None)
     out = {"model_path": d.model_path, "variant": d.variant, "tokenizer": d.tokenizer_path, "metadata": d.metadata_path,
-           "architecture": {k: getattr(cfg, k) for k in ("num_layers", "hidden", "num_heads", "num_kv_heads", "head_dim",
-                                                         "intermediate", "vocab", "weight_format", "tie_embeddings", "qkv_bias")},
+           "architecture": arch,
            "max_sequence_length": meta.max_sequence_length, "required_capabilities": meta.required_capabilities,
-           "operators": dict(sorted(ops_count.items())), "weight_bytes": cfg.weight_bytes()}
+           "operators": dict(sorted(ops_count.items())), "weight_bytes": weight_bytes}
     print(json.dumps(out, indent=1))
     return 0
 
