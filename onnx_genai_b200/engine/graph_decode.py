@@ -19,7 +19,7 @@ from ..package.graph_executor import _TORCH_DTYPE, GraphExecutor
 
 
 class GraphDecodeSession:
-    def __init__(self, model, device="cpu", io: dict | None = None, dtype=None):
+    def __init__(self, model, device="cpu", io: dict | None = None, dtype=None, extra_outputs=()):
         """``model``: path or parsed model.  ``io`` (optional) names the ports: token_input, attention_mask_input,
         position_ids_input, logits_output, kv_inputs, kv_outputs -- the ``model.io`` block; by default they are found by
         the usual names (``input_ids``, ``attention_mask``, ``position_ids``, ``logits``, ``past*`` / ``present*``)."""
@@ -41,6 +41,8 @@ class GraphDecodeSession:
         if extra:
             raise ValueError(f"the graph has inputs this session does not know how to feed: {extra}")
         self.info = {vi.name: vi for vi in g.inputs}
+        self.extra_outputs = [n for n in extra_outputs]     # e.g. a hidden-state output that a draft head consumes
+        self.last_extra: dict = {}
         self.reset()
 
     def reset(self) -> None:
@@ -76,9 +78,10 @@ class GraphDecodeSession:
         if self.pos_in:
             feeds[self.pos_in] = torch.arange(past_len, past_len + len(ids), dtype=torch.int64)[None]
         feeds.update(self.past)
-        out = self.ex.run(feeds, [self.logits_out, *self.kv_out])
+        out = self.ex.run(feeds, [self.logits_out, *self.kv_out, *self.extra_outputs])
         for src, dst in zip(self.kv_out, self.kv_in):
             self.past[dst] = out[src]
+        self.last_extra = {n: out[n][0] for n in self.extra_outputs}
         self.tokens += ids
         return out[self.logits_out][0].float()
 
@@ -177,3 +180,90 @@ class StaticCacheDecodeSession:
             if len(out) < max_new_tokens:
                 logits = self.feed([out[-1]])[-1]
         return out
+
+
+class GraphMtpSpeculator:
+    """Greedy speculative decoding with an ONNX multi-token-prediction head, both graphs on the generic executor.
+
+    The target graph also outputs its last hidden states; the head graph takes the embedding of the token just chosen and
+    the hidden state behind it (``inputs_embeds``, ``hidden_states``, mask, positions, its own small KV) and returns the
+    hidden state one position ahead, which the target's shared LM head turns into a draft token; the head's output is
+    threaded back in for the following drafts (hidden-threaded: each head call sees one position and an empty cache).
+    The target then scores ``[chosen token, drafts...]`` in one pass, keeps the drafts it agrees with and rewinds its cache
+    past the first disagreement.  Tokens are exactly those of plain greedy decoding.  Same contract as the reference's MTP
+    decode session over a Mobius-exported head (crates/onnx-genai-engine/src/speculative/mod.rs:999-1170; fixture
+    tests/fixtures/tiny-mtp-full: ``embedding.f32`` and ``lm_head.f32`` are the shared tables)."""
+
+    def __init__(self, target: GraphDecodeSession, head, embedding: torch.Tensor, lm_head: torch.Tensor, hidden_output: str, draft_tokens: int = 3):
+        self.target, self.k = target, int(draft_tokens)
+        self.head = head if isinstance(head, GraphExecutor) else GraphExecutor(head, target.ex.device)
+        self.embed, self.lm_head, self.hidden_output = embedding.float(), lm_head.float(), hidden_output
+        if hidden_output not in target.extra_outputs:
+            raise ValueError(f"the target session must be built with extra_outputs=['{hidden_output}']")
+        self.head_kv_in = [n for n in self.head.input_names if n.startswith("past")]
+        self.head_kv_out = [n for n in self.head.output_names if n.startswith("present")]
+        self.head_info = {vi.name: vi for vi in self.head.model.graph.inputs}
+        self.stats = {"target_passes": 0, "proposed": 0, "accepted": 0}
+
+    @classmethod
+    def from_dir(cls, d: str, draft_tokens: int = 3, device="cpu") -> "GraphMtpSpeculator":
+        """A directory laid out like the upstream fixture: target graph + ``mtp/`` head graph + ``embedding.f32`` / ``lm_head.f32``."""
+        import os
+
+        import numpy as np
+        import yaml
+
+        from ..package.onnx_text import load_any
+
+        with open(os.path.join(d, "inference_metadata.yaml"), encoding="utf-8") as f:
+            io = ((yaml.safe_load(f) or {}).get("model") or {}).get("io") or {}
+        hidden_out = io.get("hidden_output", "hidden_states.0")
+        find = lambda base: next(os.path.join(base, n) for n in ("model.onnx", "model.onnx.textproto") if os.path.exists(os.path.join(base, n)))
+        session_io = {k: v for k, v in io.items() if k != "hidden_output"}
+        target = GraphDecodeSession(load_any(find(d)), device, session_io, extra_outputs=[hidden_out])
+        hidden = next(vi.shape[-1] for vi in target.ex.model.graph.outputs if vi.name == hidden_out)
+        table = lambda name: torch.from_numpy(np.fromfile(os.path.join(d, name), dtype="<f4").reshape(-1, int(hidden)).copy())
+        return cls(target, load_any(find(os.path.join(d, "mtp"))), table("embedding.f32"), table("lm_head.f32"), hidden_out, draft_tokens)
+
+    def _draft(self, hidden: torch.Tensor, token: int, position: int) -> list:
+        """Hidden-threaded drafting: every head call sees one position with an empty cache; what links the calls is the hidden
+        state handed from one to the next (the mode the reference uses for heads whose graphs take no history)."""
+        empty = {}
+        for name in self.head_kv_in:
+            shape = [d if isinstance(d, int) else (1 if axis == 0 else 0) for axis, d in enumerate(self.head_info[name].shape)]
+            empty[name] = torch.zeros(shape, device=self.head.device)
+        drafts, h, tok = [], hidden.reshape(1, 1, -1).float(), int(token)
+        for j in range(self.k):
+            feeds = {"inputs_embeds": self.embed[tok].reshape(1, 1, -1), "hidden_states": h, "attention_mask": torch.ones(1, 1, dtype=torch.int64),
+                     "position_ids": torch.tensor([[position + j]], dtype=torch.int64), **empty}
+            out = self.head.run({k: v for k, v in feeds.items() if k in self.head.input_names})
+            h = out["mtp_hidden"] if "mtp_hidden" in out else out[self.head.output_names[0]]
+            tok = int(torch.argmax(h.reshape(-1).float() @ self.lm_head.T))
+            drafts.append(tok)
+        return drafts
+
+    def generate(self, prompt, max_new_tokens: int) -> list:
+        t = self.target
+        logits = t.feed(prompt)
+        self.stats["target_passes"] += 1
+        hidden = t.last_extra[self.hidden_output][-1]
+        out = []
+        while len(out) < max_new_tokens:
+            chosen = int(torch.argmax(logits[-1]))
+            out.append(chosen)
+            if len(out) >= max_new_tokens:
+                break
+            drafts = self._draft(hidden, chosen, t.length)[: max_new_tokens - len(out)]
+            base = t.length
+            rows = t.feed([chosen] + drafts)                       # row i predicts the token after fed position i
+            self.stats["target_passes"] += 1
+            self.stats["proposed"] += len(drafts)
+            accepted = 0
+            while accepted < len(drafts) and int(torch.argmax(rows[accepted])) == drafts[accepted]:
+                accepted += 1
+            self.stats["accepted"] += accepted
+            out += drafts[:accepted]
+            hidden = t.last_extra[self.hidden_output][accepted]
+            logits = rows[accepted:accepted + 1]
+            t.rewind(base + 1 + accepted)                          # drop the cache entries of the rejected drafts
+        return out[:max_new_tokens]

@@ -86,3 +86,19 @@ def test_static_cache_decoder_steps_equal_one_full_pass():
         full.feed(list(range(12)))
     with pytest.raises(ValueError, match="not a static-cache decoder"):
         StaticCacheDecodeSession(load_any(os.path.join(REF, "tests", "fixtures", "tiny-llm", "model.onnx.textproto")))
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "tests", "fixtures", "tiny-mtp-full", "mtp")),
+                    reason="the upstream target + MTP head fixture is not available on this machine")
+@pytest.mark.parametrize("k", [1, 3])
+def test_onnx_mtp_head_speculation_equals_plain_greedy(k):
+    from onnx_genai_b200.engine.graph_decode import GraphMtpSpeculator
+
+    d = os.path.join(REF, "tests", "fixtures", "tiny-mtp-full")
+    for prompt in ([3, 9, 27], [1], [5, 5, 5, 5, 5, 5]):
+        want = GraphDecodeSession.from_dir(d).generate(prompt, 8)
+        spec = GraphMtpSpeculator.from_dir(d, draft_tokens=k)
+        assert spec.generate(prompt, 8) == want
+        st = spec.stats
+        assert st["proposed"] > 0 and 0 <= st["accepted"] <= st["proposed"] and st["target_passes"] <= 9
+        assert spec.target.length == len(prompt) + 8 - 1 or spec.target.length == len(prompt) + 8   # the cache holds no rejected draft
