@@ -122,3 +122,22 @@ def test_model_package_with_shared_assets(tmp_path):
     assert pkg.open_model_directory(root, ep="cpu", device="cpu").variant == "cpu"
     with pytest.raises(pkg.PackageError, match="escapes the package root"):
         pkg.resolve_ref(root, "../../etc/passwd")
+
+
+def test_upstream_metadata_samples_parse_or_fail_with_reasons():
+    import os
+
+    import pytest
+
+    from onnx_genai_b200 import metadata as md
+
+    root = os.path.join(os.environ.get("OGB_REFERENCE_DIR", os.path.join(os.path.expanduser("~"), "reference")), "tests", "fixtures")
+    if not os.path.exists(os.path.join(root, "sample_metadata.yaml")):
+        pytest.skip("the upstream metadata samples are not available on this machine")
+    y, j = md.load(os.path.join(root, "sample_metadata.yaml")), md.load(os.path.join(root, "sample_metadata.json"))
+    assert y.max_sequence_length == j.max_sequence_length == 131072 and y.required_capabilities == j.required_capabilities
+    assert {"grouped_query_attention", "kv_cache"} <= set(y.required_capabilities)
+    with pytest.raises(md.MetadataError, match="required_capabilities: expected a list"):
+        md.load(os.path.join(root, "invalid_metadata.yaml"))
+    with pytest.raises(md.MetadataError, match="cannot parse"):
+        md.load(os.path.join(root, "malformed_metadata.yaml"))
