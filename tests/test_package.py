@@ -141,3 +141,20 @@ def test_upstream_metadata_samples_parse_or_fail_with_reasons():
         md.load(os.path.join(root, "invalid_metadata.yaml"))
     with pytest.raises(md.MetadataError, match="cannot parse"):
         md.load(os.path.join(root, "malformed_metadata.yaml"))
+
+
+def test_every_upstream_fixture_metadata_document_parses():
+    import glob
+    import os
+
+    import pytest
+
+    from onnx_genai_b200 import metadata as md
+
+    root = os.path.join(os.environ.get("OGB_REFERENCE_DIR", os.path.join(os.path.expanduser("~"), "reference")), "tests", "fixtures")
+    docs = sorted(glob.glob(os.path.join(root, "**", "inference_metadata.yaml"), recursive=True))
+    if not docs:
+        pytest.skip("the upstream fixtures are not available on this machine")
+    assert len(docs) >= 20
+    for path in docs:
+        md.load(path)          # unknown fields, capabilities or shapes would raise MetadataError naming the file
