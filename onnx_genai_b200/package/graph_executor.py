@@ -440,6 +440,98 @@ def _tensor_scatter(ins, attrs):
     return out
 
 
+def _dequant_rows(packed, scales, zero_points, bits, block):
+    """[..., out, in / pack] packed integers (least significant bits first along the input axis) with [..., out, in / block]
+    scales (and optional packed zero points) -> float weights [..., out, in]."""
+    pack = 8 // bits
+    mask = (1 << bits) - 1
+    p = packed.to(torch.int32)
+    parts = [(p >> (bits * i)) & mask for i in range(pack)]
+    q = torch.stack(parts, dim=-1).reshape(*packed.shape[:-1], packed.shape[-1] * pack).float()
+    blocks = scales.shape[-1]
+    k = q.shape[-1]
+    if zero_points is not None:
+        z = zero_points.to(torch.int32)
+        z = torch.stack([(z >> (bits * i)) & mask for i in range(pack)], dim=-1).reshape(*zero_points.shape[:-1], -1)[..., :blocks].float()
+    else:
+        z = torch.full(scales.shape, float(1 << (bits - 1)), device=packed.device)
+    per = (k + blocks - 1) // blocks if block <= 0 else block
+    qb = q.reshape(*q.shape[:-1], blocks, per)
+    return ((qb - z[..., None]) * scales.float()[..., None]).reshape(*q.shape[:-1], k)
+
+
+def _moe_route(logits, k, normalize):
+    """Top-k experts by router logit (ties to the lower index); weights are softmax probabilities over all experts, or
+    over the selected ones when ``normalize`` is set."""
+    order = torch.argsort(-logits.float(), dim=-1, stable=True)[:, :k]
+    e = torch.exp(logits.float() - logits.float().amax(dim=-1, keepdim=True))
+    chosen = torch.gather(e, 1, order)
+    denom = chosen.sum(dim=-1, keepdim=True) if normalize else e.sum(dim=-1, keepdim=True)
+    return order, chosen / denom
+
+
+def _moe_core(x, router, w1, b1, w2, b2, w3, b3, attrs):
+    """Mixture of experts on dense expert weights [E, out, in] (``com.microsoft::MoE`` / ``QMoE`` after dequantisation)."""
+    shape = x.shape
+    x2 = x.reshape(-1, shape[-1]).float()
+    order, weights = _moe_route(router.reshape(x2.shape[0], -1), int(attrs.get("k", 1)), bool(attrs.get("normalize_routing_weights", 0)))
+    act = attrs.get("activation_type", "relu")
+    fusion = int(attrs.get("swiglu_fusion", 0))
+    alpha, beta = float(attrs.get("activation_alpha", 1.0)), float(attrs.get("activation_beta", 0.0))
+    limit = float(attrs.get("swiglu_limit", float("inf")))
+
+    def glu(g, l):
+        g, l = torch.clamp(g, max=limit), torch.clamp(l, -limit, limit)
+        return g * torch.sigmoid(alpha * g) * (l + beta)
+
+    out = torch.zeros(x2.shape[0], w2.shape[1])
+    out = out.to(x2.device)
+    for e in torch.unique(order).tolist():
+        rows, slots = (order == e).nonzero(as_tuple=True)
+        h = x2[rows] @ w1[e].float().T
+        if b1 is not None:
+            h = h + b1[e].float()
+        if act == "swiglu" and fusion == 1:
+            h = glu(h[:, 0::2], h[:, 1::2])
+        elif act == "swiglu" and fusion == 2:
+            half = h.shape[1] // 2
+            h = glu(h[:, :half], h[:, half:])
+        elif act == "swiglu":
+            l = x2[rows] @ w3[e].float().T + (b3[e].float() if b3 is not None else 0)
+            h = glu(h, l)
+        elif act == "silu":
+            h = F.silu(h) * (x2[rows] @ w3[e].float().T + (b3[e].float() if b3 is not None else 0)) if w3 is not None else F.silu(h)
+        elif act == "gelu":
+            h = F.gelu(h, approximate="tanh")
+        elif act == "relu":
+            h = F.relu(h)
+        elif act != "identity":
+            raise GraphExecutionError(f"MoE activation_type {act!r} is not covered (relu, gelu, silu, swiglu, identity)")
+        y = h @ w2[e].float().T
+        if b2 is not None:
+            y = y + b2[e].float()
+        out.index_add_(0, rows, y * weights[rows, slots][:, None])
+    return out.to(x.dtype).reshape(*shape[:-1], -1)
+
+
+def _moe(ins, attrs):
+    get = lambda i: ins[i] if len(ins) > i and ins[i] is not None else None
+    return _moe_core(ins[0], ins[1], ins[2], get(3), ins[4], get(5), get(6), get(7), attrs)
+
+
+def _qmoe(ins, attrs):
+    """com.microsoft::QMoE with integer expert weights: inputs (x, router, fc1 w, fc1 scales, fc1 bias, fc2 w, fc2 scales,
+    fc2 bias, fc3 w, fc3 scales, fc3 bias, fc1 zero points, fc2 zero points, fc3 zero points)."""
+    get = lambda i: ins[i] if len(ins) > i and ins[i] is not None else None
+    bits, block = int(attrs.get("expert_weight_bits", 4)), int(attrs.get("block_size", 0))
+    if bits not in (2, 4, 8) or attrs.get("quant_type", "int") != "int":
+        raise GraphExecutionError("QMoE is covered for integer weights of 2, 4 or 8 bits")
+    w1 = _dequant_rows(ins[2], ins[3], get(11), bits, block)
+    w2 = _dequant_rows(ins[5], ins[6], get(12), bits, block)
+    w3 = _dequant_rows(ins[8], ins[9], get(13), bits, block) if get(8) is not None else None
+    return _moe_core(ins[0], ins[1], w1, get(4), w2, get(7), w3, get(10), attrs)
+
+
 def _bitshift(ins, attrs):
     x, n = ins[0], ins[1]
     if attrs.get("direction", "LEFT") == "LEFT":
@@ -506,7 +598,7 @@ OPS = {
     "BitwiseXor": lambda i, a: i[0] ^ i[1], "BitwiseNot": lambda i, a: ~i[0], "Mod": _mod,
     "IsInf": lambda i, a: torch.isinf(i[0]) & ((i[0] > 0) if not a.get("detect_negative", 1) else True) & ((i[0] < 0) if not a.get("detect_positive", 1) else True),
     "Swish": lambda i, a: i[0] * torch.sigmoid(float(a.get("alpha", 1.0)) * i[0]),
-    "TensorScatter": _tensor_scatter, "RotaryEmbedding": _rotary, "Attention": _attention, "GroupQueryAttention": _group_query_attention,
+    "MoE": _moe, "QMoE": _qmoe, "TensorScatter": _tensor_scatter, "RotaryEmbedding": _rotary, "Attention": _attention, "GroupQueryAttention": _group_query_attention,
     "MatMul": lambda i, a: i[0] @ i[1],
     "Gemm": lambda i, a: float(a.get("alpha", 1.0)) * ((i[0].T if a.get("transA", 0) else i[0]) @ (i[1].T if a.get("transB", 0) else i[1]))
                          + (float(a.get("beta", 1.0)) * i[2] if len(i) > 2 and i[2] is not None else 0),

@@ -102,3 +102,12 @@ def test_onnx_mtp_head_speculation_equals_plain_greedy(k):
         st = spec.stats
         assert st["proposed"] > 0 and 0 <= st["accepted"] <= st["proposed"] and st["target_passes"] <= 9
         assert spec.target.length == len(prompt) + 8 - 1 or spec.target.length == len(prompt) + 8   # the cache holds no rejected draft
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "tests", "fixtures", "tiny-deepseek-v2-qmoe-attention")),
+                    reason="the upstream QMoE fixture is not available on this machine")
+def test_upstream_qmoe_decoder_reproduces_its_pinned_tokens():
+    """Integer-quantised mixture of experts (fused interleaved SwiGLU) as a graph operator; tokens pinned upstream in
+    crates/onnx-genai-engine/tests/deepseek_v2_tiny_qmoe_native_e2e.rs:16-17."""
+    d = os.path.join(REF, "tests", "fixtures", "tiny-deepseek-v2-qmoe-attention")
+    assert GraphDecodeSession.from_dir(d).generate([3], 8) == [11] * 8

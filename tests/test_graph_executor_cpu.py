@@ -286,3 +286,42 @@ def test_if_and_loop_with_captured_outer_values(tmp_path):
     nested_unknown = pb.Graph(name="t", nodes=[N("Sort", ["x"], ["o"])], outputs=[vi("o")])
     with pytest.raises(GraphExecutionError, match="outside the covered set: Sort"):
         GraphExecutor(model([N("If", ["c"], ["y"], then_branch=nested_unknown, else_branch=else_g)], [], [("x", pb.FLOAT, ()), ("c", pb.BOOL, ())], ["y"]))
+
+
+def test_moe_and_qmoe_against_a_dense_statement():
+    rng = np.random.default_rng(7)
+    experts, hid, inter, k, t, block = 4, 16, 16, 2, 5, 16          # every input width is one quantisation block
+    x = rng.standard_normal((t, hid)).astype(np.float32)
+    router = rng.standard_normal((t, experts)).astype(np.float32)
+    pack = lambda q: (q[..., 0::2] | (q[..., 1::2] << 4)).astype(np.uint8)      # least significant nibble first along the input axis
+    q1 = rng.integers(0, 16, size=(experts, 2 * inter, hid)).astype(np.uint8)
+    s1 = (rng.random((experts, 2 * inter, 1)).astype(np.float32) + 0.5) * 0.05
+    q2 = rng.integers(0, 16, size=(experts, hid, inter)).astype(np.uint8)
+    s2 = (rng.random((experts, hid, 1)).astype(np.float32) + 0.5) * 0.05
+    w1 = (q1.astype(np.float32) - 8.0) * s1
+    w2 = (q2.astype(np.float32) - 8.0) * s2
+    m = model([N("QMoE", ["x", "r", "w1", "s1", "", "w2", "s2"], ["y"], domain="com.microsoft", k=k, activation_type="swiglu", swiglu_fusion=1,
+                 expert_weight_bits=4, block_size=block, normalize_routing_weights=1, quant_type="int")],
+              [T("w1", pack(q1)), T("s1", s1), T("w2", pack(q2)), T("s2", s2)], [("x", pb.FLOAT, (t, hid)), ("r", pb.FLOAT, (t, experts))], ["y"])
+    got = GraphExecutor(m).run({"x": x, "r": router})["y"]
+    want = np.zeros((t, hid), np.float32)
+    for row in range(t):
+        top = sorted(range(experts), key=lambda e: (-router[row, e], e))[:k]
+        ex = np.exp(router[row] - router[row].max())
+        for e in top:
+            h = w1[e] @ x[row]
+            g, l = h[0::2], h[1::2]
+            act = g * (1 / (1 + np.exp(-g))) * l
+            want[row] += ex[e] / ex[top].sum() * (w2[e] @ act)
+    assert torch.allclose(got, torch.from_numpy(want), atol=1e-4)
+    # float MoE, relu, weights over all experts (no renormalisation)
+    f1, f2 = rng.standard_normal((experts, inter, hid)).astype(np.float32) * 0.2, rng.standard_normal((experts, hid, inter)).astype(np.float32) * 0.2
+    m = model([N("MoE", ["x", "r", "f1", "", "f2"], ["y"], domain="com.microsoft", k=1, activation_type="relu")], [T("f1", f1), T("f2", f2)],
+              [("x", pb.FLOAT, (t, hid)), ("r", pb.FLOAT, (t, experts))], ["y"])
+    got = GraphExecutor(m).run({"x": x, "r": router})["y"]
+    want = np.zeros((t, hid), np.float32)
+    for row in range(t):
+        e = int(np.argmax(router[row]))
+        p = np.exp(router[row] - router[row].max())
+        want[row] = p[e] / p.sum() * (f2[e] @ np.maximum(f1[e] @ x[row], 0))
+    assert torch.allclose(got, torch.from_numpy(want), atol=1e-5)
