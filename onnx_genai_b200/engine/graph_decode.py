@@ -267,3 +267,24 @@ class GraphMtpSpeculator:
             logits = rows[accepted:accepted + 1]
             t.rewind(base + 1 + accepted)                          # drop the cache entries of the rejected drafts
         return out[:max_new_tokens]
+
+
+def open_decode_session(model_dir: str, device="cpu"):
+    """The decode session that fits the directory's graph: fixed-size scatter-updated caches get a
+    :class:`StaticCacheDecodeSession`, past / present graphs a :class:`GraphDecodeSession`."""
+    import os
+
+    from ..package.onnx_text import load_any
+
+    text = os.path.join(model_dir, "model.onnx.textproto")
+    if os.path.exists(text):
+        path = text
+    else:
+        from .. import package as pkg
+
+        path = pkg.open_model_directory(model_dir).model_path
+    model = load_any(path)
+    names = [vi.name for vi in model.graph.inputs]
+    if "write_indices" in names and any(n.startswith(("key_cache", "value_cache")) for n in names):
+        return StaticCacheDecodeSession(model, device)
+    return GraphDecodeSession.from_dir(model_dir, device)

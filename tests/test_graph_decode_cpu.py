@@ -111,3 +111,19 @@ def test_upstream_qmoe_decoder_reproduces_its_pinned_tokens():
     crates/onnx-genai-engine/tests/deepseek_v2_tiny_qmoe_native_e2e.rs:16-17."""
     d = os.path.join(REF, "tests", "fixtures", "tiny-deepseek-v2-qmoe-attention")
     assert GraphDecodeSession.from_dir(d).generate([3], 8) == [11] * 8
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "tests", "fixtures", "tiny-llm-scatter")),
+                    reason="the upstream tiny decoder fixtures are not available on this machine")
+def test_one_model_exported_four_ways_gives_the_same_tokens():
+    """The upstream tiny LLM exists with a fused Attention operator, with explicit IO names, with packed-QKV
+    GroupQueryAttention over shared buffers, and with a reasoning template: every export decodes to the same tokens."""
+    from onnx_genai_b200.engine.graph_decode import StaticCacheDecodeSession, open_decode_session
+
+    fixtures = os.path.join(REF, "tests", "fixtures")
+    runs = {}
+    for name in ("tiny-llm", "tiny-llm-explicit-io", "tiny-llm-sharedbuffer", "tiny-reasoning"):
+        sess = open_decode_session(os.path.join(fixtures, name))
+        runs[name] = sess.generate([3, 9, 27], 6)
+    assert isinstance(open_decode_session(os.path.join(fixtures, "tiny-llm-scatter")), StaticCacheDecodeSession)
+    assert len({tuple(v) for v in runs.values()}) == 1, runs
