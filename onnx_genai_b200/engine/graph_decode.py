@@ -18,6 +18,11 @@ import torch
 from ..package.graph_executor import _TORCH_DTYPE, GraphExecutor
 
 
+def _rows(logits):
+    """[1, n, vocab] or batch-less [n, vocab] logits -> [n, vocab] float32."""
+    return (logits[0] if logits.dim() == 3 else logits.reshape(-1, logits.shape[-1])).float()
+
+
 class GraphDecodeSession:
     def __init__(self, model, device="cpu", io: dict | None = None, dtype=None, extra_outputs=()):
         """``model``: path or parsed model.  ``io`` (optional) names the ports: token_input, attention_mask_input,
@@ -83,7 +88,7 @@ class GraphDecodeSession:
             self.past[dst] = out[src]
         self.last_extra = {n: out[n][0] for n in self.extra_outputs}
         self.tokens += ids
-        return out[self.logits_out][0].float()
+        return _rows(out[self.logits_out])
 
     def rewind(self, new_len: int) -> None:
         if not 0 <= new_len <= self.length:
@@ -170,7 +175,7 @@ class StaticCacheDecodeSession:
         for src, dst in zip(self.cache_out, self.cache_in):
             self.cache[dst] = out[src]
         self.tokens += ids
-        return out[self.logits_out][0].float()
+        return _rows(out[self.logits_out])
 
     def generate(self, prompt, max_new_tokens: int) -> list:
         logits = self.feed(prompt)[-1]

@@ -212,6 +212,78 @@ def _matmul_nbits(ins, attrs):
     return y.to(x.dtype)
 
 
+_E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+_IQ4_NL = (-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113)
+_BLOCK_FORMATS = {"mxfp4": (32, 17), "iq4_nl": (32, 18)}        # values per block, bytes per block
+
+
+def decode_weight_blocks(packed, fmt: str):
+    """[n, blocks, bytes] uint8 -> [n, blocks * 32] float32 for the block formats of ``BlockQuantizedMatMul``.
+
+    ``mxfp4``: one E8M0 scale byte (2^(e-127); 255 is NaN) then 16 bytes of E2M1 codes, where byte ``j`` holds element
+    ``j`` in its low nibble and element ``j + 16`` in its high nibble.  ``iq4_nl``: a little-endian fp16 scale then 16
+    bytes laid out the same way, the codes indexing the 16-entry non-linear table.
+    """
+    if fmt not in _BLOCK_FORMATS:
+        raise GraphExecutionError(f"BlockQuantizedMatMul format {fmt!r} is not covered here (covered: {sorted(_BLOCK_FORMATS)})")
+    qk, nbytes = _BLOCK_FORMATS[fmt]
+    if packed.dim() != 3 or packed.shape[-1] != nbytes:
+        raise GraphExecutionError(f"{fmt} weights must be [N, blocks, {nbytes}] bytes, got {list(packed.shape)}")
+    b = packed.to(torch.int32)
+    head = 1 if fmt == "mxfp4" else 2
+    codes = b[..., head:]
+    idx = torch.cat([codes & 0xF, (codes >> 4) & 0xF], dim=-1).long()
+    if fmt == "mxfp4":
+        e = b[..., 0]
+        scale = torch.where(e == 255, torch.full_like(e, float("nan"), dtype=torch.float64), torch.pow(2.0, (e - 127).double())).float()
+        table = torch.tensor(_E2M1 + tuple(-v for v in _E2M1), device=packed.device)
+        vals = table[idx]
+        vals = torch.where(vals == 0, torch.zeros_like(vals), vals * scale[..., None])      # a zero code stays zero under a NaN scale
+    else:
+        raw = (b[..., 0] | (b[..., 1] << 8)).to(torch.int16).view(torch.float16).float()
+        vals = torch.tensor(_IQ4_NL, device=packed.device, dtype=torch.float32)[idx] * raw[..., None]
+    return vals.reshape(packed.shape[0], -1)
+
+
+def encode_mxfp4(weight):
+    """[n, k] float -> [n, ceil(k/32), 17] uint8 in the ``mxfp4`` block layout (nearest code, power-of-two block scale)."""
+    w = weight.detach().float().cpu()
+    n, k = w.shape
+    blocks = (k + 31) // 32
+    w = F.pad(w, (0, blocks * 32 - k)).reshape(n, blocks, 32)
+    amax = w.abs().amax(-1).clamp_min(2.0 ** -120)
+    e = torch.ceil(torch.log2(amax / 6.0)).clamp(-127, 127)
+    scaled = w / torch.pow(2.0, e)[..., None]
+    table = torch.tensor(_E2M1)
+    mag = (scaled.abs()[..., None] - table).abs().argmin(-1)
+    code = (mag | ((scaled < 0) & (mag > 0)).long() << 3).to(torch.uint8)
+    out = torch.empty(n, blocks, 17, dtype=torch.uint8)
+    out[..., 0] = (e + 127).to(torch.uint8)
+    out[..., 1:] = code[..., :16] | (code[..., 16:] << 4)
+    return out
+
+
+def _block_quantized_matmul(ins, attrs):
+    """pkg.nxrt::BlockQuantizedMatMul: y = A @ dequant(packed_B)^T (+ bias), A [..., K], packed_B [N, blocks, block bytes].
+
+    The reference runs it on its CPU provider (crates/onnx-runtime-ep-cpu/src/kernels/block_quantized_matmul.rs:170-300);
+    a partial last block is stored whole and its tail ignored.
+    """
+    x, packed = ins[0], ins[1]
+    k, n = int(attrs["K"]), int(attrs["N"])
+    if int(attrs.get("block_layout_version", 1)) != 1:
+        raise GraphExecutionError(f"BlockQuantizedMatMul block_layout_version {attrs.get('block_layout_version')} is unknown (known: 1)")
+    fmt = attrs.get("format")
+    fmt = fmt.decode() if isinstance(fmt, bytes) else fmt
+    if x.shape[-1] != k or packed.shape[0] != n:
+        raise GraphExecutionError(f"BlockQuantizedMatMul: A {list(x.shape)} / packed_B {list(packed.shape)} do not match K={k}, N={n}")
+    w = decode_weight_blocks(packed, str(fmt))[:, :k]
+    y = x.float() @ w.T
+    if len(ins) > 2 and ins[2] is not None:
+        y = y + ins[2].float()
+    return y.to(x.dtype)
+
+
 def _gather_nd(data, idx):
     idx = idx.long()
     k = idx.shape[-1]
@@ -602,7 +674,7 @@ OPS = {
     "MatMul": lambda i, a: i[0] @ i[1],
     "Gemm": lambda i, a: float(a.get("alpha", 1.0)) * ((i[0].T if a.get("transA", 0) else i[0]) @ (i[1].T if a.get("transB", 0) else i[1]))
                          + (float(a.get("beta", 1.0)) * i[2] if len(i) > 2 and i[2] is not None else 0),
-    "MatMulNBits": _matmul_nbits,
+    "MatMulNBits": _matmul_nbits, "BlockQuantizedMatMul": _block_quantized_matmul,
     "Conv": lambda i, a: _conv(i, a), "ConvTranspose": lambda i, a: _conv(i, a, transpose=True),
     "MaxPool": lambda i, a: _pool(i, a, "max"), "AveragePool": lambda i, a: _pool(i, a, "avg"),
     "GlobalAveragePool": lambda i, a: i[0].mean(tuple(range(2, i[0].dim())), keepdim=True),

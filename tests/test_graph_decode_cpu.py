@@ -127,3 +127,14 @@ def test_one_model_exported_four_ways_gives_the_same_tokens():
         runs[name] = sess.generate([3, 9, 27], 6)
     assert isinstance(open_decode_session(os.path.join(fixtures, "tiny-llm-scatter")), StaticCacheDecodeSession)
     assert len({tuple(v) for v in runs.values()}) == 1, runs
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "tests", "fixtures", "tiny-native-sub4-engine")),
+                    reason="the upstream sub-4-bit fixture is not available on this machine")
+def test_upstream_block_quantised_decoder_with_batchless_logits():
+    """A decoder whose logits come from ``pkg.nxrt::BlockQuantizedMatMul`` (mxfp4) and have no batch axis: the all-zero
+    weight leaves the bias, so every step picks token 1 (crates/onnx-genai-engine/tests/native_engine.rs uses this fixture)."""
+    from onnx_genai_b200.engine.graph_decode import open_decode_session
+
+    sess = open_decode_session(os.path.join(REF, "tests", "fixtures", "tiny-native-sub4-engine"))
+    assert sess.generate([0], 4) == [1, 1, 1, 1]

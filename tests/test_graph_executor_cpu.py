@@ -325,3 +325,42 @@ def test_moe_and_qmoe_against_a_dense_statement():
         p = np.exp(router[row] - router[row].max())
         want[row] = p[e] / p.sum() * (f2[e] @ np.maximum(f1[e] @ x[row], 0))
     assert torch.allclose(got, torch.from_numpy(want), atol=1e-5)
+
+
+def test_block_quantized_matmul_mxfp4_and_iq4_nl():
+    """Layout facts of the two covered formats, then the operator against a dense product with the decoded weight."""
+    import struct
+
+    from onnx_genai_b200.package.graph_executor import OPS, GraphExecutionError, decode_weight_blocks, encode_mxfp4
+
+    # mxfp4: scale byte first; byte j = element j (low nibble) and element j+16 (high nibble); code 8|m is -m
+    blk = torch.zeros(1, 1, 17, dtype=torch.uint8)
+    blk[0, 0, 0] = 128                               # 2^(128-127) = 2
+    blk[0, 0, 1] = 0x27                              # element 0 = code 7 (6.0), element 16 = code 2 (1.0)
+    blk[0, 0, 2] = 0x0B                              # element 1 = code 11 (-1.5)
+    w = decode_weight_blocks(blk, "mxfp4")[0]
+    assert w[0] == 12.0 and w[16] == 2.0 and w[1] == -3.0 and float(w.abs().sum()) == 17.0
+    blk[0, 0, 0] = 255                               # a NaN scale poisons non-zero codes only
+    w = decode_weight_blocks(blk, "mxfp4")[0]
+    assert torch.isnan(w[0]) and w[2] == 0.0
+    # iq4_nl: fp16 scale, then the same nibble order over the non-linear table
+    raw = bytearray(18)
+    raw[0:2] = struct.pack("<e", 0.5)
+    raw[2] = 0xF0                                    # element 0 = table[0] = -127, element 16 = table[15] = 113
+    w = decode_weight_blocks(torch.tensor(list(raw), dtype=torch.uint8).reshape(1, 1, 18), "iq4_nl")[0]
+    assert w[0] == -63.5 and w[16] == 56.5
+
+    torch.manual_seed(0)
+    dense = torch.randn(5, 70)                       # K = 70: the third block is partial
+    packed = encode_mxfp4(dense)
+    assert tuple(packed.shape) == (5, 3, 17)
+    deq = decode_weight_blocks(packed, "mxfp4")[:, :70]
+    assert float((deq - dense).abs().max()) <= 0.5 * float(dense.abs().max()) / 3      # half the widest code gap (4 -> 6) at scale amax/6
+    assert torch.equal(decode_weight_blocks(encode_mxfp4(deq), "mxfp4")[:, :70], deq)    # representable values survive a second trip
+    x, bias = torch.randn(2, 3, 70), torch.randn(5)
+    y = OPS["BlockQuantizedMatMul"]([x, packed, bias], {"K": 70, "N": 5, "format": "mxfp4", "block_layout_version": 1})
+    assert torch.allclose(y, x @ deq.T + bias, atol=1e-5) and tuple(y.shape) == (2, 3, 5)
+    with pytest.raises(GraphExecutionError, match="iq2_xxs"):
+        OPS["BlockQuantizedMatMul"]([x, packed, None], {"K": 70, "N": 5, "format": "iq2_xxs"})
+    with pytest.raises(GraphExecutionError, match="block_layout_version"):
+        OPS["BlockQuantizedMatMul"]([x, packed, None], {"K": 70, "N": 5, "format": "mxfp4", "block_layout_version": 2})
