@@ -38,17 +38,22 @@ class GraphExecutionError(RuntimeError):
     pass
 
 
+def _signed_home(arr):
+    """Unsigned 16/32/64-bit arrays move to the signed type that holds them (torch computes on signed integers only)."""
+    if arr.dtype == np.uint16:
+        return arr.astype(np.int32)
+    if arr.dtype in (np.uint32, np.uint64):
+        return arr.astype(np.int64)
+    return arr
+
+
 def tensor_to_torch(t: onnx_pb.Tensor, device="cpu") -> torch.Tensor:
     arr = np.ascontiguousarray(t.numpy())
     if t.data_type == onnx_pb.BFLOAT16:
         return torch.from_numpy(arr.view(np.int16).copy()).view(torch.bfloat16).reshape(tuple(t.dims)).to(device)
     if t.data_type == onnx_pb.FLOAT8E4M3FN:
         return torch.from_numpy(arr.copy()).view(torch.float8_e4m3fn).reshape(tuple(t.dims)).to(device)
-    if arr.dtype == np.uint16:
-        arr = arr.astype(np.int32)
-    elif arr.dtype in (np.uint32, np.uint64):
-        arr = arr.astype(np.int64)
-    return torch.from_numpy(arr.copy()).reshape(tuple(t.dims)).to(device)
+    return torch.from_numpy(_signed_home(arr).copy()).reshape(tuple(t.dims)).to(device)
 
 
 def _ints(x):
@@ -126,14 +131,21 @@ def _layer_norm(x, scale, bias, axis, eps):
     xf = x.float()
     mean = xf.mean(dims, keepdim=True)
     var = (xf - mean).pow(2).mean(dims, keepdim=True)
-    y = ((xf - mean) * torch.rsqrt(var + eps)).to(x.dtype) * scale
-    return y + bias if bias is not None else y
+    inv = torch.rsqrt(var + eps)
+    y = ((xf - mean) * inv).to(x.dtype) * scale
+    return [y + bias if bias is not None else y, mean, inv]          # Y, then the optional Mean and InvStdDev outputs
 
 
 def _rms_norm(x, scale, axis, eps):
     dims = tuple(range(axis % x.dim(), x.dim()))
     xf = x.float()
     return (xf * torch.rsqrt(xf.pow(2).mean(dims, keepdim=True) + eps)).to(x.dtype) * scale
+
+
+def _rms_norm_with_stat(x, scale, axis, eps):
+    """The contrib form's optional second output is the inverse root mean square it divided by."""
+    dims = tuple(range(axis % x.dim(), x.dim()))
+    return [_rms_norm(x, scale, axis, eps), torch.rsqrt(x.float().pow(2).mean(dims, keepdim=True) + eps)]
 
 
 def _slice(ins, attrs):
@@ -393,6 +405,96 @@ def _rotary(ins, attrs):
     return out.reshape(x.shape) if three else out.transpose(1, 2)
 
 
+def _contrib_rotary(ins, attrs):
+    """com.microsoft::RotaryEmbedding: the same rotation with inputs ordered (input, position_ids, cos_cache, sin_cache);
+    position ids are [batch, tokens], or one starting offset that the tokens count up from."""
+    x, pos, cos, sin = ins[0], ins[1], ins[2], ins[3]
+    tokens = x.shape[1] if x.dim() == 3 else x.shape[2]
+    if pos.numel() == 1 and (pos.dim() < 2 or tokens > 1):
+        pos = (pos.reshape(1, 1).long() + torch.arange(tokens, device=x.device)[None, :]).expand(x.shape[0], tokens)
+    return _rotary([x, cos, sin, pos], attrs)
+
+
+def _opt(ins, i):
+    return ins[i] if len(ins) > i and ins[i] is not None else None
+
+
+def _multi_head_attention(ins, attrs):
+    """com.microsoft::MultiHeadAttention with separate 3-D query / key / value ([batch, tokens, heads * dim]).
+
+    Optional inputs: a concatenated Q|K|V projection bias, a key padding mask ([batch, kv] of 0/1, or [batch] valid
+    lengths), an additive attention bias broadcast over [batch, heads, q, kv], and past key / value
+    ([batch, heads, past, dim]); outputs are the attention result and the present key / value.
+    """
+    q, k, v = ins[0], _opt(ins, 1), _opt(ins, 2)
+    if k is None or v is None or q.dim() != 3 or k.dim() != 3:
+        raise GraphExecutionError("MultiHeadAttention is covered for separate 3-D query, key and value inputs")
+    h = int(attrs["num_heads"])
+    bias, pad, extra, past_k, past_v = (_opt(ins, i) for i in (3, 4, 5, 6, 7))
+    if bias is not None:
+        bq, bk, bv = torch.split(bias, [q.shape[-1], k.shape[-1], v.shape[-1]])
+        q, k, v = q + bq, k + bk, v + bv
+    b, s = q.shape[0], q.shape[1]
+    q = q.reshape(b, s, h, -1).transpose(1, 2).float()
+    k = k.reshape(b, k.shape[1], h, -1).transpose(1, 2).float()
+    v = v.reshape(b, v.shape[1], h, -1).transpose(1, 2).float()
+    if past_k is not None:
+        k, v = torch.cat([past_k.float(), k], dim=2), torch.cat([past_v.float(), v], dim=2)
+    total = k.shape[2]
+    scale = float(attrs.get("scale", 0.0)) or q.shape[-1] ** -0.5
+    scores = q @ k.transpose(-1, -2) * scale
+    if extra is not None:
+        scores = scores + extra.float()
+    if pad is not None:
+        keep = (torch.arange(total, device=q.device)[None, :] < pad.reshape(b, 1)) if pad.dim() == 1 else pad.reshape(b, -1)[:, -total:].bool()
+        scores = scores.masked_fill(~keep[:, None, None, :], float(attrs.get("mask_filter_value", -10000.0)))
+    if int(attrs.get("unidirectional", 0)):
+        scores = scores.masked_fill(~torch.ones(s, total, dtype=torch.bool, device=q.device).tril(total - s), float("-inf"))
+    out = (torch.softmax(scores, dim=-1) @ v).transpose(1, 2).reshape(b, s, -1)
+    return [out.to(ins[0].dtype), k.to(ins[0].dtype), v.to(ins[0].dtype)]
+
+
+def _contrib_attention(ins, attrs):
+    """com.microsoft::Attention: the input projection fused in -- ``input [batch, tokens, hidden] @ weights [hidden, 3 * hidden]
+    + bias`` split into Q | K | V, then multi-head attention with the same optional mask, past (stacked [2, batch, heads,
+    past, dim]) and additive bias as the unfused operator; returns the result and the stacked present."""
+    x, w = ins[0], ins[1]
+    bias, mask, past, extra = (_opt(ins, i) for i in (2, 3, 4, 5))
+    sizes = attrs.get("qkv_hidden_sizes") or [w.shape[1] // 3] * 3
+    qkv = x.float() @ w.float() + (bias.float() if bias is not None else 0.0)
+    q, k, v = torch.split(qkv, [int(z) for z in sizes], dim=-1)
+    pk, pv = (past[0], past[1]) if past is not None else (None, None)
+    out, nk, nv = _multi_head_attention([q, k, v, None, mask, extra, pk, pv], attrs)
+    return [out.to(x.dtype), torch.stack([nk, nv]).to(x.dtype)]
+
+
+def _packed_multi_head_attention(ins, attrs):
+    """com.microsoft::PackedMultiHeadAttention: padding-free attention over [tokens, heads * dim] rows, where
+    ``cumulative_sequence_length`` ([batch + 1]) cuts the rows into sequences that attend only within themselves."""
+    q, k, v = ins[0], _opt(ins, 1), _opt(ins, 2)
+    if k is None or v is None or q.dim() != 2:
+        raise GraphExecutionError("PackedMultiHeadAttention is covered for separate 2-D query, key and value inputs")
+    h = int(attrs["num_heads"])
+    bias, cu, extra = _opt(ins, 3), _opt(ins, 5), _opt(ins, 6)
+    if cu is None:
+        raise GraphExecutionError("PackedMultiHeadAttention needs cumulative_sequence_length")
+    if bias is not None:
+        bq, bk, bv = torch.split(bias, [q.shape[-1], k.shape[-1], v.shape[-1]])
+        q, k, v = q + bq, k + bk, v + bv
+    t = q.shape[0]
+    qh, kh, vh = (x.reshape(t, h, -1).transpose(0, 1).float() for x in (q, k, v))
+    scale = float(attrs.get("scale", 0.0)) or qh.shape[-1] ** -0.5
+    bounds = [int(c) for c in cu.reshape(-1).tolist()]
+    out = torch.zeros(h, t, vh.shape[-1], device=q.device)
+    for i, (lo, hi) in enumerate(zip(bounds[:-1], bounds[1:])):
+        scores = qh[:, lo:hi] @ kh[:, lo:hi].transpose(-1, -2) * scale
+        if extra is not None:
+            e = extra.float()
+            scores = scores + e[i if e.shape[0] > 1 else 0][..., : hi - lo, : hi - lo]
+        out[:, lo:hi] = torch.softmax(scores, dim=-1) @ vh[:, lo:hi]
+    return out.transpose(0, 1).reshape(t, -1).to(ins[0].dtype)
+
+
 def _attention(ins, attrs):
     """Attention (opset 23): scaled dot-product attention with optional mask, past K/V, grouped query heads, softcap."""
     q, k, v = ins[0], ins[1], ins[2]
@@ -518,6 +620,9 @@ def _dequant_rows(packed, scales, zero_points, bits, block):
     pack = 8 // bits
     mask = (1 << bits) - 1
     p = packed.to(torch.int32)
+    if scales.dim() == packed.dim() - 1:            # one scale per output row
+        scales = scales[..., None]
+        zero_points = zero_points[..., None] if zero_points is not None else None
     parts = [(p >> (bits * i)) & mask for i in range(pack)]
     q = torch.stack(parts, dim=-1).reshape(*packed.shape[:-1], packed.shape[-1] * pack).float()
     blocks = scales.shape[-1]
@@ -674,6 +779,8 @@ OPS = {
     "MatMul": lambda i, a: i[0] @ i[1],
     "Gemm": lambda i, a: float(a.get("alpha", 1.0)) * ((i[0].T if a.get("transA", 0) else i[0]) @ (i[1].T if a.get("transB", 0) else i[1]))
                          + (float(a.get("beta", 1.0)) * i[2] if len(i) > 2 and i[2] is not None else 0),
+    "com.microsoft::Attention": _contrib_attention, "com.microsoft::RotaryEmbedding": _contrib_rotary, "MultiHeadAttention": _multi_head_attention, "PackedMultiHeadAttention": _packed_multi_head_attention,
+    "NonZero": lambda i, a: torch.nonzero(i[0]).T.contiguous(), "PRelu": lambda i, a: torch.where(i[0] >= 0, i[0], i[0] * i[1]),
     "MatMulNBits": _matmul_nbits, "BlockQuantizedMatMul": _block_quantized_matmul,
     "Conv": lambda i, a: _conv(i, a), "ConvTranspose": lambda i, a: _conv(i, a, transpose=True),
     "MaxPool": lambda i, a: _pool(i, a, "max"), "AveragePool": lambda i, a: _pool(i, a, "avg"),
@@ -684,7 +791,7 @@ OPS = {
     "InstanceNormalization": lambda i, a: F.instance_norm(i[0], weight=i[1], bias=i[2], eps=float(a.get("epsilon", 1e-5))),
     "GroupNormalization": lambda i, a: F.group_norm(i[0], int(a["num_groups"]), i[1], i[2], float(a.get("epsilon", 1e-5))),
     "LayerNormalization": lambda i, a: _layer_norm(i[0], i[1], i[2] if len(i) > 2 else None, int(a.get("axis", -1)), float(a.get("epsilon", 1e-5))),
-    "SimplifiedLayerNormalization": lambda i, a: _rms_norm(i[0], i[1], int(a.get("axis", -1)), float(a.get("epsilon", 1e-5))),
+    "SimplifiedLayerNormalization": lambda i, a: _rms_norm_with_stat(i[0], i[1], int(a.get("axis", -1)), float(a.get("epsilon", 1e-5))),
     "RMSNormalization": lambda i, a: _rms_norm(i[0], i[1], int(a.get("axis", -1)), float(a.get("epsilon", 1e-5))),
     "Softmax": lambda i, a: torch.softmax(i[0].float(), int(a.get("axis", -1))).to(i[0].dtype),
     "LogSoftmax": lambda i, a: torch.log_softmax(i[0].float(), int(a.get("axis", -1))).to(i[0].dtype),
@@ -725,7 +832,7 @@ OPS = {
          .reshape(x.shape[0], x.shape[1] // (b * b), x.shape[2] * b, x.shape[3] * b))(i[0], int(a["blocksize"])),
     "SpaceToDepth": lambda i, a: F.pixel_unshuffle(i[0], int(a["blocksize"])),
     "SkipLayerNormalization": lambda i, a: (lambda s: [_layer_norm(s, i[2], i[3] if len(i) > 3 and i[3] is not None else None, -1,
-                                                                   float(a.get("epsilon", 1e-5))), None, None, s])(i[0] + i[1] + (i[4] if len(i) > 4 and i[4] is not None else 0)),
+                                                                   float(a.get("epsilon", 1e-5)))[0], None, None, s])(i[0] + i[1] + (i[4] if len(i) > 4 and i[4] is not None else 0)),
     "SkipSimplifiedLayerNormalization": lambda i, a: (lambda s: [_rms_norm(s, i[2], -1, float(a.get("epsilon", 1e-5))), None, None, s])(
         i[0] + i[1] + (i[3] if len(i) > 3 and i[3] is not None else 0)),
 }
@@ -811,7 +918,7 @@ class GraphExecutor:
             raise GraphExecutionError(f"missing graph input(s) {missing}; the graph takes {self.input_names}")
         env = dict(self.constants)
         for name, v in feeds.items():
-            t = v if isinstance(v, torch.Tensor) else torch.as_tensor(np.asarray(v))
+            t = v if isinstance(v, torch.Tensor) else torch.as_tensor(_signed_home(np.asarray(v)))
             want = _TORCH_DTYPE.get(self.input_types.get(name))
             if want is not None and t.dtype != want and (t.is_floating_point() == want.is_floating_point):
                 t = t.to(want)
@@ -836,7 +943,7 @@ def _exec_node(self, n, env) -> None:
         elif n.op_type == "Loop":
             res = self._loop(n, ins, env)
         else:
-            res = OPS[n.op_type](ins, n.attrs)
+            res = (OPS.get(f"{n.domain}::{n.op_type}") or OPS[n.op_type])(ins, n.attrs)       # a domain-qualified entry wins
     except GraphExecutionError:
         raise
     except Exception as e:

@@ -1,5 +1,6 @@
 """Generic ONNX graph execution over torch: small graphs built with the package's own protobuf writer."""
 import math
+import os
 
 import numpy as np
 import pytest
@@ -8,6 +9,8 @@ import torch.nn.functional as F
 
 from onnx_genai_b200.package import onnx_pb as pb
 from onnx_genai_b200.package.graph_executor import GraphExecutionError, GraphExecutor, as_component
+
+REF = os.environ.get("OGB_REFERENCE_DIR", os.path.join(os.path.expanduser("~"), "reference"))
 
 
 def T(name, arr):
@@ -364,3 +367,81 @@ def test_block_quantized_matmul_mxfp4_and_iq4_nl():
         OPS["BlockQuantizedMatMul"]([x, packed, None], {"K": 70, "N": 5, "format": "iq2_xxs"})
     with pytest.raises(GraphExecutionError, match="block_layout_version"):
         OPS["BlockQuantizedMatMul"]([x, packed, None], {"K": 70, "N": 5, "format": "mxfp4", "block_layout_version": 2})
+
+
+def test_contrib_attention_variants_nonzero_prelu():
+    from onnx_genai_b200.package.graph_executor import OPS
+
+    torch.manual_seed(1)
+    b, s, past, h, d = 2, 3, 4, 4, 8
+    q, k, v = torch.randn(b, s, h * d), torch.randn(b, s, h * d), torch.randn(b, s, h * d)
+    pk, pv = torch.randn(b, h, past, d), torch.randn(b, h, past, d)
+    bias = torch.randn(3 * h * d)
+    pad = torch.ones(b, past + s, dtype=torch.int32)
+    pad[1, :2] = 0
+    out, nk, nv = OPS["MultiHeadAttention"]([q, k, v, bias, pad, None, pk, pv], {"num_heads": h, "unidirectional": 1})
+    bq, bk, bv = bias.split(h * d)
+    heads = lambda x: x.reshape(b, s, h, d).transpose(1, 2)
+    kk, vv = torch.cat([pk, heads(k + bk)], 2), torch.cat([pv, heads(v + bv)], 2)
+    assert torch.equal(nk, kk) and torch.equal(nv, vv)
+    for bi in range(b):
+        for hi in range(h):
+            for si in range(s):
+                sc = (heads(q + bq)[bi, hi, si] @ kk[bi, hi].T) / d ** 0.5
+                sc[past + si + 1:] = float("-inf")
+                if bi == 1:
+                    sc[:2] = -10000.0
+                want = torch.softmax(sc, -1) @ vv[bi, hi]
+                assert torch.allclose(out[bi, si, hi * d:(hi + 1) * d], want, atol=1e-5)
+
+    # packed rows: two sequences of 3 and 5 tokens equal two separate unpadded calls
+    t = 8
+    q, k, v = torch.randn(t, h * d), torch.randn(t, h * d), torch.randn(t, h * d)
+    cu = torch.tensor([0, 3, 8], dtype=torch.int32)
+    packed = OPS["PackedMultiHeadAttention"]([q, k, v, None, torch.zeros(2, 5, dtype=torch.int32), cu], {"num_heads": h})
+    for lo, hi in ((0, 3), (3, 8)):
+        want = OPS["MultiHeadAttention"]([q[None, lo:hi], k[None, lo:hi], v[None, lo:hi]], {"num_heads": h})[0][0]
+        assert torch.allclose(packed[lo:hi], want, atol=1e-5)
+
+    nz = OPS["NonZero"]([torch.tensor([[0.0, 2.0], [3.0, 0.0]])], {})
+    assert nz.dtype == torch.int64 and nz.tolist() == [[0, 1], [1, 0]]
+    assert OPS["PRelu"]([torch.tensor([[-2.0, 4.0], [-1.0, -3.0]]), torch.tensor([0.5, 0.1])], {}).tolist() == [[-1.0, 4.0], [-0.5, pytest.approx(-0.3)]]
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "crates", "onnx-runtime-ep-cpu-plugin", "tests", "fixtures")),
+                    reason="the upstream operator fixtures are not available on this machine")
+def test_every_upstream_operator_fixture_runs():
+    """The reference's provider-plugin fixtures are single-operator or few-operator graphs with declared static shapes;
+    each must execute here on random inputs of those shapes and give outputs of the declared shapes."""
+    import glob
+
+    from onnx_genai_b200.package import onnx_pb as pb
+    from onnx_genai_b200.package.graph_executor import GraphExecutor
+    from onnx_genai_b200.package.onnx_text import load_any
+
+    ran = 0
+    rng = np.random.default_rng(0)
+    for path in sorted(glob.glob(os.path.join(REF, "crates", "onnx-runtime-ep-cpu-plugin", "tests", "fixtures", "*", "model.onnx.textproto"))):
+        model = load_any(path)
+        g = model.graph
+        if any(not all(isinstance(d, int) for d in vi.shape) for vi in g.inputs if vi.name not in g.initializers):
+            continue
+        feeds = {}
+        for vi in g.inputs:
+            if vi.name in g.initializers:
+                continue
+            npdt = np.dtype(pb._NP[vi.elem_type])
+            if vi.name == "cumulative_sequence_length":
+                feeds[vi.name] = np.asarray([0, 8][: vi.shape[0]], dtype=npdt)
+            elif np.issubdtype(npdt, np.floating):
+                feeds[vi.name] = rng.standard_normal(vi.shape).astype(npdt)
+            elif npdt == np.bool_:
+                feeds[vi.name] = rng.integers(0, 2, vi.shape).astype(bool)
+            else:
+                feeds[vi.name] = rng.integers(0, 2, vi.shape).astype(npdt)
+        out = GraphExecutor(model, "cpu").run(feeds)
+        for vo in g.outputs:
+            if vo.shape and all(isinstance(d, int) for d in vo.shape) and "nonzero" not in path:
+                assert tuple(out[vo.name].shape) == tuple(vo.shape), (path, vo.name, tuple(out[vo.name].shape), vo.shape)
+        ran += 1
+    assert ran >= 10, ran
