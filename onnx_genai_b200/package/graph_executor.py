@@ -296,6 +296,13 @@ def _block_quantized_matmul(ins, attrs):
     return y.to(x.dtype)
 
 
+def _topk(x, k, axis, largest):
+    """TopK with the operator's tie rule: among equal values the lower index comes first (``torch.topk`` promises no
+    order among ties, and gated scores -- a ReLU's exact zeros -- tie often)."""
+    order = torch.argsort(x, dim=axis, descending=largest, stable=True).narrow(axis, 0, k)
+    return [torch.gather(x, axis, order), order]
+
+
 def _gather_nd(data, idx):
     idx = idx.long()
     k = idx.shape[-1]
@@ -452,6 +459,56 @@ def _multi_head_attention(ins, attrs):
         scores = scores.masked_fill(~torch.ones(s, total, dtype=torch.bool, device=q.device).tril(total - s), float("-inf"))
     out = (torch.softmax(scores, dim=-1) @ v).transpose(1, 2).reshape(b, s, -1)
     return [out.to(ins[0].dtype), k.to(ins[0].dtype), v.to(ins[0].dtype)]
+
+
+def _index_share(ins, attrs):
+    """pkg.nxrt::IndexShare (version 1): attention over the cache positions an exporter selected.
+
+    query [B, N, Sq, H]; key / value [B, Nkv, Skv, H] appended to the optional past pair; ``selected_indices``
+    [B, N or 1, Sq, K] holds strictly increasing positions of the dense cache with ``-1`` as trailing padding; an
+    optional additive bias broadcasts over [B, N, Sq, total].  Each query attends to its selected positions only; a row
+    whose every selected position is masked to -inf gives zeros.  Returns the result and the dense present pair.
+    (Contract: docs/architecture/INDEXSHARE_DESIGN.md in the reference.)
+    """
+    q, k, v = ins[0], ins[1], ins[2]
+    past_k, past_v, sel, extra = _opt(ins, 3), _opt(ins, 4), _opt(ins, 5), _opt(ins, 6)
+    if sel is None or q.dim() != 4 or k.dim() != 4:
+        raise GraphExecutionError("IndexShare needs 4-D query / key / value and selected_indices")
+    if (past_k is None) != (past_v is None):
+        raise GraphExecutionError("IndexShare: past_key and past_value come as a pair")
+    n = int(attrs["num_heads"])
+    nkv = int(attrs.get("kv_num_heads", n))
+    if n % nkv or q.shape[1] != n or k.shape[1] != nkv:
+        raise GraphExecutionError(f"IndexShare: {q.shape[1]} query heads / {k.shape[1]} KV heads do not match num_heads={n}, kv_num_heads={nkv}")
+    if past_k is not None:
+        k, v = torch.cat([past_k, k], dim=2), torch.cat([past_v, v], dim=2)
+    total, b, sq = k.shape[2], q.shape[0], q.shape[2]
+    sel = sel.long()
+    if sel.dim() != 4 or sel.shape[0] != b or sel.shape[1] not in (1, n) or sel.shape[2] != sq:
+        raise GraphExecutionError(f"IndexShare: selected_indices {list(sel.shape)} must be [{b}, {n} or 1, {sq}, K]")
+    valid = sel >= 0
+    if bool(((sel < -1) | (sel >= total)).any()):
+        raise GraphExecutionError(f"IndexShare: a selected index lies outside [0, {total})")
+    if bool((~valid[..., :1]).any()):
+        raise GraphExecutionError("IndexShare: a row of selected_indices is empty")
+    if sel.shape[-1] > 1:
+        if bool((valid[..., 1:] & ~valid[..., :-1]).any()):
+            raise GraphExecutionError("IndexShare: -1 may only pad the end of a row of selected_indices")
+        if bool((valid[..., 1:] & (sel[..., 1:] <= sel[..., :-1])).any()):
+            raise GraphExecutionError("IndexShare: selected indices must be strictly increasing")
+    chosen = torch.zeros(b, sel.shape[1], sq, total + 1, dtype=torch.bool, device=q.device)
+    chosen.scatter_(3, torch.where(valid, sel, torch.full_like(sel, total)), True)
+    chosen = chosen[..., :total]
+    scale = float(attrs.get("scale", 0.0)) or q.shape[-1] ** -0.5
+    group = n // nkv
+    kf, vf = k.float().repeat_interleave(group, dim=1), v.float().repeat_interleave(group, dim=1)
+    scores = (q.float() * scale ** 0.5) @ (kf * scale ** 0.5).transpose(-1, -2)
+    if extra is not None:
+        scores = scores + extra.float()
+    scores = scores.masked_fill(~chosen, float("-inf"))
+    dead = torch.isneginf(scores).all(dim=-1, keepdim=True)
+    probs = torch.softmax(scores.masked_fill(dead, 0.0), dim=-1).masked_fill(dead, 0.0)
+    return [(probs @ vf).to(q.dtype), k, v]
 
 
 def _contrib_attention(ins, attrs):
@@ -779,7 +836,7 @@ OPS = {
     "MatMul": lambda i, a: i[0] @ i[1],
     "Gemm": lambda i, a: float(a.get("alpha", 1.0)) * ((i[0].T if a.get("transA", 0) else i[0]) @ (i[1].T if a.get("transB", 0) else i[1]))
                          + (float(a.get("beta", 1.0)) * i[2] if len(i) > 2 and i[2] is not None else 0),
-    "com.microsoft::Attention": _contrib_attention, "com.microsoft::RotaryEmbedding": _contrib_rotary, "MultiHeadAttention": _multi_head_attention, "PackedMultiHeadAttention": _packed_multi_head_attention,
+    "IndexShare": _index_share, "com.microsoft::Attention": _contrib_attention, "com.microsoft::RotaryEmbedding": _contrib_rotary, "MultiHeadAttention": _multi_head_attention, "PackedMultiHeadAttention": _packed_multi_head_attention,
     "NonZero": lambda i, a: torch.nonzero(i[0]).T.contiguous(), "PRelu": lambda i, a: torch.where(i[0] >= 0, i[0], i[0] * i[1]),
     "MatMulNBits": _matmul_nbits, "BlockQuantizedMatMul": _block_quantized_matmul,
     "Conv": lambda i, a: _conv(i, a), "ConvTranspose": lambda i, a: _conv(i, a, transpose=True),
@@ -802,7 +859,7 @@ OPS = {
     "ReduceSumSquare": _reduce(lambda x, ax, k: x.pow(2).sum(ax, keepdim=k)),
     "ArgMax": lambda i, a: i[0].argmax(int(a.get("axis", 0)), keepdim=bool(a.get("keepdims", 1))),
     "ArgMin": lambda i, a: i[0].argmin(int(a.get("axis", 0)), keepdim=bool(a.get("keepdims", 1))),
-    "TopK": lambda i, a: list(torch.topk(i[0], int(i[1].reshape(-1)[0]), dim=int(a.get("axis", -1)), largest=bool(a.get("largest", 1)))),
+    "TopK": lambda i, a: _topk(i[0], int(i[1].reshape(-1)[0]), int(a.get("axis", -1)), bool(a.get("largest", 1))),
     "CumSum": lambda i, a: torch.cumsum(i[0], int(i[1].reshape(-1)[0])),
     "Reshape": lambda i, a: _reshape(i[0], i[1], a.get("allowzero", 0)),
     "Flatten": lambda i, a: i[0].reshape(int(np.prod(i[0].shape[: int(a.get("axis", 1))])) if int(a.get("axis", 1)) else 1, -1),

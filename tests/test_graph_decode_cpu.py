@@ -138,3 +138,21 @@ def test_upstream_block_quantised_decoder_with_batchless_logits():
 
     sess = open_decode_session(os.path.join(REF, "tests", "fixtures", "tiny-native-sub4-engine"))
     assert sess.generate([0], 4) == [1, 1, 1, 1]
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "tests", "fixtures", "tiny-glm52-qmoe-indexshare")),
+                    reason="the upstream sparse-attention fixture is not available on this machine")
+def test_upstream_sparse_attention_decoder_reproduces_its_manifest_tokens():
+    """A GLM-style decoder with a learned top-8 indexer feeding ``pkg.nxrt::IndexShare`` and QMoE layers: prompt and
+    expected tokens come from the manifest beside the graph.  Past eight cached tokens the selection decides the result,
+    and the indexer's ReLU-gated scores tie at zero, so TopK's lower-index tie rule is part of what this pins."""
+    import json
+
+    from onnx_genai_b200.engine.graph_decode import open_decode_session
+
+    d = os.path.join(REF, "tests", "fixtures", "tiny-glm52-qmoe-indexshare")
+    with open(os.path.join(d, "manifest.json")) as f:
+        manifest = json.load(f)
+    want = manifest["expected_tokens"]
+    assert len(want) > 8
+    assert open_decode_session(d).generate(manifest["prompt_ids"], len(want)) == want

@@ -445,3 +445,50 @@ def test_every_upstream_operator_fixture_runs():
                 assert tuple(out[vo.name].shape) == tuple(vo.shape), (path, vo.name, tuple(out[vo.name].shape), vo.shape)
         ran += 1
     assert ran >= 10, ran
+
+
+def test_index_share_equals_dense_masked_attention_and_validates_indices():
+    from onnx_genai_b200.package.graph_executor import OPS
+
+    torch.manual_seed(2)
+    b, n, nkv, sq, past, h, kk = 2, 4, 2, 3, 5, 8, 4
+    q, k, v = torch.randn(b, n, sq, h), torch.randn(b, nkv, sq, h), torch.randn(b, nkv, sq, h)
+    pk, pv = torch.randn(b, nkv, past, h), torch.randn(b, nkv, past, h)
+    total = past + sq
+    sel = torch.full((b, 1, sq, kk), -1, dtype=torch.int64)
+    for bi in range(b):
+        for si in range(sq):
+            m = 2 + (bi + si) % 3                                                 # rows of different fill
+            sel[bi, 0, si, :m] = torch.sort(torch.randperm(past + si + 1)[:m]).values
+    bias = torch.zeros(1, 1, sq, total).masked_fill(~torch.ones(sq, total, dtype=torch.bool).tril(past), float("-inf"))
+    out, nk, nv = OPS["IndexShare"]([q, k, v, pk, pv, sel, bias], {"num_heads": n, "kv_num_heads": nkv})
+    assert torch.equal(nk, torch.cat([pk, k], 2)) and torch.equal(nv, torch.cat([pv, v], 2))
+    dense = torch.full((b, 1, sq, total), float("-inf"))
+    for bi in range(b):
+        for si in range(sq):
+            dense[bi, 0, si, sel[bi, 0, si][sel[bi, 0, si] >= 0]] = 0.0
+    kf, vf = nk.repeat_interleave(n // nkv, 1), nv.repeat_interleave(n // nkv, 1)
+    want = torch.softmax(q @ kf.transpose(-1, -2) / h ** 0.5 + dense + bias, -1) @ vf
+    assert torch.allclose(out, want, atol=1e-5)
+    # a row whose selected positions are all masked by the bias gives zeros, not NaN
+    dead = bias.clone()
+    dead[..., 0, :] = float("-inf")
+    out2 = OPS["IndexShare"]([q, k, v, pk, pv, sel, dead], {"num_heads": n, "kv_num_heads": nkv})[0]
+    assert float(out2[:, :, 0].abs().max()) == 0.0 and torch.allclose(out2[:, :, 1:], want[:, :, 1:], atol=1e-5)
+
+    def bad(row, match):
+        s2 = sel.clone()
+        s2[0, 0, 0] = torch.tensor(row)
+        with pytest.raises(GraphExecutionError, match=match):
+            OPS["IndexShare"]([q, k, v, pk, pv, s2, None], {"num_heads": n, "kv_num_heads": nkv})
+
+    bad([1, 1, 2, -1], "strictly increasing")
+    bad([3, 2, -1, -1], "strictly increasing")
+    bad([0, -1, 2, -1], "pad the end")
+    bad([-1, -1, -1, -1], "empty")
+    bad([0, 1, total, -1], "outside")
+
+    # ties go to the lower index, largest or smallest
+    vals, idx = OPS["TopK"]([torch.tensor([[0.0, 2.0, 0.0, 2.0, 1.0]]), torch.tensor([3])], {})
+    assert idx.tolist() == [[1, 3, 4]] and vals.tolist() == [[2.0, 2.0, 1.0]]
+    assert OPS["TopK"]([torch.tensor([[0.0, 2.0, 0.0, 2.0, 1.0]]), torch.tensor([2])], {"largest": 0})[1].tolist() == [[0, 2]]
