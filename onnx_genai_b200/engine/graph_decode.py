@@ -24,10 +24,18 @@ def _rows(logits):
 
 
 class GraphDecodeSession:
-    def __init__(self, model, device="cpu", io: dict | None = None, dtype=None, extra_outputs=()):
+    def __init__(self, model, device="cpu", io: dict | None = None, dtype=None, extra_outputs=(), extra_feeds: dict | None = None):
         """``model``: path or parsed model.  ``io`` (optional) names the ports: token_input, attention_mask_input,
-        position_ids_input, logits_output, kv_inputs, kv_outputs -- the ``model.io`` block; by default they are found by
-        the usual names (``input_ids``, ``attention_mask``, ``position_ids``, ``logits``, ``past*`` / ``present*``)."""
+        position_ids_input, logits_output, kv_inputs, kv_outputs, state_pairs -- the ``model.io`` block; by default they
+        are found by the usual names (``input_ids``, ``attention_mask``, ``position_ids``, ``logits``, ``past*`` /
+        ``present*``, and ``X.in`` / ``X.out`` for loop-carried recurrent state).
+
+        ``state_pairs`` (``[{input, output}, ...]``) are fixed-size tensors a hybrid decoder carries from call to call
+        (convolution or linear-attention state); they start at zero.  Such state cannot be cut back to an earlier length,
+        so :meth:`rewind` on a session that has any re-feeds the kept tokens from the start -- the same full recompute
+        the reference forces for recurrent models (crates/onnx-genai-engine/src/kv_bridge.rs:1189-1212).
+        ``extra_feeds`` maps any other graph input to a tensor, or to ``fn(past_len, n_new) -> tensor``.  Position ids
+        declared with three axes ``[axes, batch, tokens]`` get the same text position on every axis."""
         self.ex = model if isinstance(model, GraphExecutor) else GraphExecutor(model, device, dtype)
         g = self.ex.model.graph
         io = dict(io or {})
@@ -42,7 +50,14 @@ class GraphDecodeSession:
         self.kv_out = list(io.get("kv_outputs") or [n for n in self.ex.output_names if n.startswith("present")])
         if len(self.kv_in) != len(self.kv_out):
             raise ValueError(f"{len(self.kv_in)} KV inputs but {len(self.kv_out)} KV outputs; name them in io")
-        extra = [n for n in names if n not in {self.token_in, self.mask_in, self.pos_in, *self.kv_in}]
+        pairs = io.get("state_pairs")
+        if pairs is None:
+            pairs = [{"input": n, "output": n[:-3] + ".out"} for n in names if n.endswith(".in") and n[:-3] + ".out" in self.ex.output_names]
+        self.state_in = [p["input"] for p in pairs]
+        self.state_out = [p["output"] for p in pairs]
+        self.kv_in = [n for n in self.kv_in if n not in self.state_in]
+        self.extra_feeds = dict(extra_feeds or {})
+        extra = [n for n in names if n not in {self.token_in, self.mask_in, self.pos_in, *self.kv_in, *self.state_in, *self.extra_feeds}]
         if extra:
             raise ValueError(f"the graph has inputs this session does not know how to feed: {extra}")
         self.info = {vi.name: vi for vi in g.inputs}
@@ -66,6 +81,11 @@ class GraphDecodeSession:
                     seq_axis = axis
             self.past[name] = torch.zeros(shape, dtype=_TORCH_DTYPE.get(vi.elem_type, torch.float32), device=self.ex.device)
             self.seq_axis = seq_axis if seq_axis is not None else 2
+        self.state = {}
+        for name in self.state_in:
+            vi = self.info[name]
+            self.state[name] = torch.zeros([d if isinstance(d, int) else 1 for d in vi.shape],
+                                           dtype=_TORCH_DTYPE.get(vi.elem_type, torch.float32), device=self.ex.device)
 
     @property
     def length(self) -> int:
@@ -81,11 +101,18 @@ class GraphDecodeSession:
         if self.mask_in:
             feeds[self.mask_in] = torch.ones(1, past_len + len(ids), dtype=torch.int64)
         if self.pos_in:
-            feeds[self.pos_in] = torch.arange(past_len, past_len + len(ids), dtype=torch.int64)[None]
+            pos = torch.arange(past_len, past_len + len(ids), dtype=torch.int64)[None]
+            declared = self.info[self.pos_in].shape
+            feeds[self.pos_in] = pos[None].expand(int(declared[0]), 1, len(ids)).contiguous() if len(declared) == 3 and isinstance(declared[0], int) else pos
+        for name, value in self.extra_feeds.items():
+            feeds[name] = value(past_len, len(ids)) if callable(value) else value
         feeds.update(self.past)
-        out = self.ex.run(feeds, [self.logits_out, *self.kv_out, *self.extra_outputs])
+        feeds.update(self.state)
+        out = self.ex.run(feeds, [self.logits_out, *self.kv_out, *self.state_out, *self.extra_outputs])
         for src, dst in zip(self.kv_out, self.kv_in):
             self.past[dst] = out[src]
+        for src, dst in zip(self.state_out, self.state_in):
+            self.state[dst] = out[src]
         self.last_extra = {n: out[n][0] for n in self.extra_outputs}
         self.tokens += ids
         return _rows(out[self.logits_out])
@@ -93,6 +120,12 @@ class GraphDecodeSession:
     def rewind(self, new_len: int) -> None:
         if not 0 <= new_len <= self.length:
             raise ValueError(f"cannot rewind to {new_len}: the session holds {self.length} tokens")
+        if self.state_in and new_len < self.length:
+            keep = self.tokens[:new_len]
+            self.reset()
+            if keep:
+                self.feed(keep)
+            return
         self.tokens = self.tokens[:new_len]
         for name, t in self.past.items():
             self.past[name] = t.narrow(self.seq_axis, 0, new_len).contiguous()

@@ -468,7 +468,7 @@ def _index_share(ins, attrs):
     [B, N or 1, Sq, K] holds strictly increasing positions of the dense cache with ``-1`` as trailing padding; an
     optional additive bias broadcasts over [B, N, Sq, total].  Each query attends to its selected positions only; a row
     whose every selected position is masked to -inf gives zeros.  Returns the result and the dense present pair.
-    (Contract: docs/architecture/INDEXSHARE_DESIGN.md in the reference.)
+    (Contract: the reference's frozen v1 operator note for IndexShare under docs/architecture.)
     """
     q, k, v = ins[0], ins[1], ins[2]
     past_k, past_v, sel, extra = _opt(ins, 3), _opt(ins, 4), _opt(ins, 5), _opt(ins, 6)

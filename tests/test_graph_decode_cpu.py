@@ -156,3 +156,62 @@ def test_upstream_sparse_attention_decoder_reproduces_its_manifest_tokens():
     want = manifest["expected_tokens"]
     assert len(want) > 8
     assert open_decode_session(d).generate(manifest["prompt_ids"], len(want)) == want
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "tests", "fixtures", "tiny-multiaxis-state-decoder")),
+                    reason="the upstream stateful decoder fixture is not available on this machine")
+def test_hybrid_decoder_with_recurrent_state_and_three_axis_positions():
+    """The upstream fixture's logits are a one-hot at (sum of the three position axes + sum of both recurrent states), its
+    states grow by 1 and 2 per call, and its KV layers are numbered 3 and 11: the chosen token shows whether positions,
+    state and cache were threaded right, and that a rewind recomputes the state instead of keeping a stale one."""
+    from onnx_genai_b200.package.onnx_text import load_any
+
+    model = load_any(os.path.join(REF, "tests", "fixtures", "tiny-multiaxis-state-decoder", "decoder.onnx.textproto"))
+    with pytest.raises(ValueError, match="routed_sequence"):
+        GraphDecodeSession(model)
+    routed = lambda past, n: torch.zeros(1, n, 1)
+    io = {"kv_inputs": ["past.3.key", "past.3.value", "past.11.key", "past.11.value"],
+          "kv_outputs": ["present.3.key", "present.3.value", "present.11.key", "present.11.value"],
+          "state_pairs": [{"input": "state_a.in", "output": "state_a.out"}, {"input": "state_b.in", "output": "state_b.out"}]}
+    for spec in (io, None):                                       # declared, and found by the .in / .out naming
+        s = GraphDecodeSession(model, io=spec, extra_feeds={"routed_sequence": routed})
+        assert s.state_in == ["state_a.in", "state_b.in"] and len(s.kv_in) == 4
+        assert s.feed([5, 6, 7]).argmax(-1).tolist() == [0, 3, 6]                  # 3 axes x position, zero state
+        assert s.feed([9]).argmax(-1).tolist() == [3 * 3 + 2 + 4]                  # one call later: states (1, 1) and (2, 2)
+        assert s.past["past.11.value"].reshape(-1).tolist() == [16.0, 17.0, 18.0, 20.0]
+        s.rewind(2)                                                                # state cannot be cut: tokens re-fed from zero
+        assert s.length == 2 and s.state["state_a.in"].tolist() == [[1.0, 1.0]]
+        assert s.feed([1]).argmax(-1).tolist() == [3 * 2 + 2 + 4]
+        assert s.past["past.3.key"].reshape(-1).tolist() == [5.0, 6.0, 1.0]
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "tests", "fixtures", "tiny-eagle3")),
+                    reason="the upstream drafter fixtures are not available on this machine")
+@pytest.mark.parametrize("name, hidden_inputs, outputs", [
+    ("tiny-eagle3", {"inputs_embeds": 16, "fused_hidden": 48, "recycled_hidden": 16}, ["draft_logits", "next_hidden"]),
+    ("tiny-qwen35-mtp", {"inputs_embeds": 16, "hidden_states": 16}, ["mtp_hidden"]),
+])
+def test_upstream_drafter_heads_run_and_are_causal(name, hidden_inputs, outputs):
+    """The EAGLE-3 and MTP drafter graphs take hidden-state inputs and a KV cache of their own.  Both were exported with
+    mask-building constants that only hold for an empty cache, so they are exercised from an empty cache: every output
+    has one row per position, and a position's row does not change when later positions are appended."""
+    from onnx_genai_b200.package.graph_executor import GraphExecutor
+    from onnx_genai_b200.package.onnx_text import load_any
+
+    ex = GraphExecutor(load_any(os.path.join(REF, "tests", "fixtures", name, "model.onnx.textproto")), "cpu")
+    g = torch.Generator().manual_seed(3)
+    full = {k: torch.randn(1, 3, w, generator=g) for k, w in hidden_inputs.items()}
+    empty = torch.zeros(1, 1, 0, 8)
+
+    def call(n):
+        feeds = {k: v[:, :n] for k, v in full.items()}
+        feeds.update({"attention_mask": torch.ones(1, n, dtype=torch.int64), "position_ids": torch.arange(n)[None],
+                      "past_key_values.0.key": empty, "past_key_values.0.value": empty})
+        return ex.run(feeds)
+
+    three, two, one = call(3), call(2), call(1)
+    for o in outputs:
+        assert three[o].shape[:2] == (1, 3) and bool(torch.isfinite(three[o]).all())
+        assert torch.allclose(three[o][:, :2], two[o], atol=1e-5) and torch.allclose(two[o][:, :1], one[o], atol=1e-5), o
+        assert not torch.allclose(three[o][:, 2], three[o][:, 1])
+    assert three["present.0.key"].shape == (1, 1, 3, 8) and torch.allclose(three["present.0.key"][:, :, :2], two["present.0.key"], atol=1e-6)

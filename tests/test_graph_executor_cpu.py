@@ -492,3 +492,23 @@ def test_index_share_equals_dense_masked_attention_and_validates_indices():
     vals, idx = OPS["TopK"]([torch.tensor([[0.0, 2.0, 0.0, 2.0, 1.0]]), torch.tensor([3])], {})
     assert idx.tolist() == [[1, 3, 4]] and vals.tolist() == [[2.0, 2.0, 1.0]]
     assert OPS["TopK"]([torch.tensor([[0.0, 2.0, 0.0, 2.0, 1.0]]), torch.tensor([2])], {"largest": 0})[1].tolist() == [[0, 2]]
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "tests", "fixtures", "tiny-fp8-kv")),
+                    reason="the upstream fp8 cache fixtures are not available on this machine")
+def test_fp8_cache_graphs_keep_their_element_type():
+    """The reference probes a runtime for one-byte KV support with two graphs over FLOAT8E4M3FN tensors
+    (crates/onnx-genai-ort/tests/fp8_kv_capability.rs): a scatter of new rows into a cache and an identity."""
+    from onnx_genai_b200.package.onnx_text import load_any
+
+    d = os.path.join(REF, "tests", "fixtures", "tiny-fp8-kv")
+    cache = torch.zeros(2, 4, 8).to(torch.float8_e4m3fn)
+    new = (torch.arange(16).reshape(2, 1, 8).float() / 4).to(torch.float8_e4m3fn)
+    out = GraphExecutor(load_any(os.path.join(d, "scatter.onnx.textproto")), "cpu").run(
+        {"key_cache": cache, "write_indices": torch.tensor([[[0, 2]], [[1, 1]]]), "new_key": new})["updated_key_cache"]
+    assert out.dtype == torch.float8_e4m3fn
+    want = torch.zeros(2, 4, 8)
+    want[0, 2], want[1, 1] = new[0, 0].float(), new[1, 0].float()
+    assert torch.equal(out.float(), want)
+    same = GraphExecutor(load_any(os.path.join(d, "identity.onnx.textproto")), "cpu").run({"key_cache": out})["updated_key_cache"]
+    assert same.dtype == torch.float8_e4m3fn and torch.equal(same.float(), want)
