@@ -12,9 +12,10 @@ right tool; nothing here is used by the decoder.
 Coverage: the dense, convolutional, normalisation, activation, shape and indexing operators of the default domain
 that such graphs use (see ``OPS``), plus the ``com.microsoft`` contrib forms ``Gelu``, ``FastGelu``, ``BiasGelu``,
 ``SkipLayerNormalization``, ``SimplifiedLayerNormalization``, ``SkipSimplifiedLayerNormalization``, ``GroupQueryAttention``
-(separate past / present buffers) and ``MatMulNBits``.
-``If`` and ``Loop`` run their subgraphs in a scope chained over the enclosing one (bodies may read outer values by name);
-``Scan`` is not covered.  An operator outside the table is an error that names the node and lists what is covered.
+(separate past / present buffers), the attention family, ``MatMulNBits`` and the mixture-of-experts operators; the long
+tail lives in ``graph_ops_extra`` and the operators of hybrid and padding-free decoders in ``graph_ops_sequence``.
+``If``, ``Loop`` and ``Scan`` run their subgraphs in a scope chained over the enclosing one (bodies may read outer values
+by name).  An operator outside the table is an error that names the node and lists what is covered.
 
 ``as_component(path)`` wraps a graph as a workflow component: a callable from a dict of input ports to a dict of
 output ports (ports are the graph's input and output names).
@@ -704,11 +705,16 @@ def _moe_route(logits, k, normalize):
     return order, chosen / denom
 
 
-def _moe_core(x, router, w1, b1, w2, b2, w3, b3, attrs):
-    """Mixture of experts on dense expert weights [E, out, in] (``com.microsoft::MoE`` / ``QMoE`` after dequantisation)."""
+def _moe_core(x, router, w1, b1, w2, b2, w3, b3, attrs, agg=None):
+    """Mixture of experts on dense expert weights [E, out, in] (``com.microsoft::MoE`` / ``QMoE`` after dequantisation).
+    ``agg`` ([rows, experts], optional) supplies the mixing weights of the experts the router logits select."""
     shape = x.shape
     x2 = x.reshape(-1, shape[-1]).float()
     order, weights = _moe_route(router.reshape(x2.shape[0], -1), int(attrs.get("k", 1)), bool(attrs.get("normalize_routing_weights", 0)))
+    if agg is not None:
+        weights = torch.gather(agg.reshape(x2.shape[0], -1).float(), 1, order)
+        if attrs.get("normalize_routing_weights", 0):
+            weights = weights / weights.sum(dim=-1, keepdim=True)
     act = attrs.get("activation_type", "relu")
     fusion = int(attrs.get("swiglu_fusion", 0))
     alpha, beta = float(attrs.get("activation_alpha", 1.0)), float(attrs.get("activation_beta", 0.0))
@@ -763,7 +769,7 @@ def _qmoe(ins, attrs):
     w1 = _dequant_rows(ins[2], ins[3], get(11), bits, block)
     w2 = _dequant_rows(ins[5], ins[6], get(12), bits, block)
     w3 = _dequant_rows(ins[8], ins[9], get(13), bits, block) if get(8) is not None else None
-    return _moe_core(ins[0], ins[1], w1, get(4), w2, get(7), w3, get(10), attrs)
+    return _moe_core(ins[0], ins[1], w1, get(4), w2, get(7), w3, get(10), attrs, agg=get(14))
 
 
 def _bitshift(ins, attrs):
@@ -895,7 +901,7 @@ OPS = {
 }
 
 
-CONTROL_FLOW = ("If", "Loop")
+CONTROL_FLOW = ("If", "Loop", "Scan")
 _STRUCTURAL = ("Constant", "Split") + CONTROL_FLOW
 
 
@@ -944,7 +950,7 @@ class GraphExecutor:
                           and n.op_type not in _STRUCTURAL})
         if unknown:
             raise GraphExecutionError(f"graph '{g.name}' uses operators outside the covered set: {', '.join(unknown)} "
-                                      f"({len(OPS) + len(_STRUCTURAL)} operators are covered, If and Loop among them; Scan is not)")
+                                      f"({len(OPS) + len(_STRUCTURAL)} operators are covered, If, Loop and Scan among them)")
         self._sub_constants: dict = {}        # id(subgraph) -> its initializers on the device
         self.order = self._toposort(g)
         self.runs = 0
@@ -999,6 +1005,10 @@ def _exec_node(self, n, env) -> None:
             res = self._run_body(branch, env, {})
         elif n.op_type == "Loop":
             res = self._loop(n, ins, env)
+        elif n.op_type == "Scan":
+            from .graph_ops_sequence import _scan
+
+            res = _scan(self, n, ins, env)
         else:
             res = (OPS.get(f"{n.domain}::{n.op_type}") or OPS[n.op_type])(ins, n.attrs)       # a domain-qualified entry wins
     except GraphExecutionError:
@@ -1071,3 +1081,6 @@ def as_component(model, device="cpu", dtype=None):
 
     component.executor = ex
     return component
+
+
+from . import graph_ops_extra, graph_ops_sequence  # noqa: E402,F401  (they add operators to OPS; they need the names above)
