@@ -231,6 +231,31 @@ def _block_quantized_moe(ins, attrs):
     return _moe_core(x, router, w1, _opt(ins, 3), w2, _opt(ins, 5), w3, _opt(ins, 7), attrs, agg=_opt(ins, 8))
 
 
+def _sparse_kv_gather(ins, attrs):
+    """pkg.nxrt::SparseKvGather: cache [B, G, C, D] and indices [B, G, Q, K] -> the selected rows [B, G, Q, K, D], index
+    order and duplicates kept.  A negative index, one at or past the cache length, or one at or past the row's optional
+    ``valid_lengths`` [B] entry is an error (crates/onnx-runtime-ep-cpu/src/kernels/sparse_kv_gather.rs:72-126)."""
+    cache, idx = ins[0], ins[1].long()
+    lengths = _opt(ins, 2)
+    if int(attrs.get("index_layout_version", 1)) != 1 or (attrs.get("out_of_range", "error") or "error") != "error":
+        raise GraphExecutionError("SparseKvGather knows index_layout_version 1 with out_of_range='error' only")
+    if cache.dim() != 4 or idx.dim() != 4 or cache.shape[:2] != idx.shape[:2]:
+        raise GraphExecutionError(f"SparseKvGather: cache {list(cache.shape)} must be [B, G, C, D] and indices {list(idx.shape)} [B, G, Q, K] with equal B and G")
+    limit = torch.full((cache.shape[0],), cache.shape[2], dtype=torch.int64, device=cache.device)
+    if lengths is not None:
+        lengths = lengths.long().reshape(-1)
+        if lengths.numel() != cache.shape[0] or bool(((lengths < 0) | (lengths > cache.shape[2])).any()):
+            raise GraphExecutionError(f"SparseKvGather: valid_lengths must be [{cache.shape[0]}] values in 0..{cache.shape[2]}")
+        limit = lengths
+    bad = (idx < 0) | (idx >= limit[:, None, None, None])
+    if bool(bad.any()):
+        where = [int(v) for v in bad.nonzero()[0].tolist()]
+        raise GraphExecutionError(f"SparseKvGather: index {int(idx[tuple(where)])} at {where} lies outside the {int(limit[where[0]])} valid cache rows")
+    b, g, q, k = idx.shape
+    picked = torch.gather(cache, 2, idx.reshape(b, g, q * k, 1).expand(b, g, q * k, cache.shape[3]))
+    return picked.reshape(b, g, q, k, cache.shape[3])
+
+
 def _scan(self, n, ins, env):
     """Scan (opset 9+): state variables threaded through the body, scan inputs sliced along their axes (optionally
     reversed), scan outputs stacked along theirs."""
@@ -264,5 +289,5 @@ def _scan(self, n, ins, env):
 OPS.update({
     "LinearAttention": _linear_attention, "CausalConvWithState": _causal_conv_with_state, "VarlenAttention": _varlen_attention,
     "PackedVarlenAttention": _packed_varlen_attention, "FusedAttention": _fused_attention, "GatherBlockQuantized": _gather_block_quantized,
-    "BlockQuantizedMoE": _block_quantized_moe,
+    "BlockQuantizedMoE": _block_quantized_moe, "SparseKvGather": _sparse_kv_gather,
 })

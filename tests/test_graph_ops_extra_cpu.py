@@ -120,3 +120,24 @@ def test_image_operators():
     keep = OPS["NonMaxSuppression"]([boxes, scores, torch.tensor([3]), torch.tensor([0.5]), torch.tensor([0.4])], {})
     assert keep.tolist() == [[0, 0, 3], [0, 0, 0]]
     assert OPS["NonMaxSuppression"]([boxes, scores], {}).shape == (0, 3)
+
+
+def test_operator_table_covers_the_names_the_reference_cpu_provider_registers():
+    """Every quoted operator name in the reference's kernel registry has an entry here, save the listed exceptions."""
+    import os
+    import re
+
+    ref = os.environ.get("OGB_REFERENCE_DIR", os.path.join(os.path.expanduser("~"), "reference"))
+    path = os.path.join(ref, "crates", "onnx-runtime-ep-cpu", "src", "kernels", "mod.rs")
+    if not os.path.exists(path):
+        pytest.skip("the reference kernel registry is not available on this machine")
+    with open(path, encoding="utf-8") as f:
+        src = f.read()
+    body = src[src.index("macro_rules! register_operator_group"):]
+    body = body[: body.index("#[cfg(test)]")] if "#[cfg(test)]" in body else body
+    names = set(re.findall(r'"([A-Z][A-Za-z0-9]+)"', body))
+    assert len(names) > 150
+    have = set(OPS) | {k.split("::")[1] for k in OPS if "::" in k} | {"If", "Loop", "Scan", "Constant", "Split"}
+    not_built = {"CompressedSparseAttention"}           # stateful compressed-cache attention
+    not_operators = {"TotallyFakeOp"}                    # a name the registry's own tests look up and expect to miss
+    assert names - have - not_operators == not_built

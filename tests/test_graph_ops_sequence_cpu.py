@@ -209,3 +209,22 @@ def test_block_quantised_moe_equals_dense_moe_on_the_decoded_weights(activation,
     assert torch.allclose(mixed, by_hand, atol=1e-4)
     with pytest.raises(GraphExecutionError, match="k=9"):
         OPS["BlockQuantizedMoE"]([x, logits, p1, b1, p2, b2, p3], {**attrs, "k": 9})
+
+
+def test_sparse_kv_gather_keeps_order_and_refuses_bad_indices():
+    cache = torch.arange(2 * 2 * 6 * 3, dtype=torch.float32).reshape(2, 2, 6, 3)
+    idx = torch.tensor([[[[5, 0, 0]], [[1, 2, 3]]], [[[4, 4, 1]], [[0, 3, 2]]]])                 # [B=2, G=2, Q=1, K=3]
+    out = OPS["SparseKvGather"]([cache, idx], {})
+    assert tuple(out.shape) == (2, 2, 1, 3, 3)
+    for b in range(2):
+        for g in range(2):
+            assert torch.equal(out[b, g, 0], cache[b, g, idx[b, g, 0]])
+    assert torch.equal(OPS["SparseKvGather"]([cache, idx, torch.tensor([6, 5])], {}), out)
+    with pytest.raises(GraphExecutionError, match=r"index 4 at \[1, 0, 0, 0\] lies outside the 4 valid"):
+        OPS["SparseKvGather"]([cache, idx, torch.tensor([6, 4])], {})
+    with pytest.raises(GraphExecutionError, match="index -1"):
+        OPS["SparseKvGather"]([cache, torch.where(idx == 5, -1, idx)], {})
+    with pytest.raises(GraphExecutionError, match="valid_lengths"):
+        OPS["SparseKvGather"]([cache, idx, torch.tensor([6, 7])], {})
+    with pytest.raises(GraphExecutionError, match="out_of_range"):
+        OPS["SparseKvGather"]([cache, idx], {"out_of_range": "clamp"})
