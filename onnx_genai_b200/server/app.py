@@ -315,7 +315,8 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
 
     # Media routes of the reference server.  Image generation is served when a text-to-image workflow package is mounted
     # (``image_pipeline``, see server/images.py), speech synthesis when a speech package is (``speech_pipeline``, server/audio.py);
-    # transcription and image-to-image answer 501 with the reason.
+    # image-to-image comes with the image routes (and answers 400 when the workflow has no image input); transcription
+    # answers 501 with the reason.
     if image_pipeline is not None:
         from .images import add_image_routes
 
@@ -333,7 +334,7 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
     for _path, _kind in (("/v1/images/generations", "image generation"), ("/sdapi/v1/txt2img", "image generation"),
                          ("/sdapi/v1/img2img", "image generation"), ("/v1/audio/transcriptions", "audio transcription"),
                          ("/v1/audio/speech", "speech synthesis")):
-        if image_pipeline is not None and _path in ("/v1/images/generations", "/sdapi/v1/txt2img"):
+        if image_pipeline is not None and _path in ("/v1/images/generations", "/sdapi/v1/txt2img", "/sdapi/v1/img2img"):
             continue
         if speech_pipeline is not None and _path == "/v1/audio/speech":
             continue

@@ -79,6 +79,61 @@ def test_text_server_mounts_the_image_routes_next_to_chat(tmp_path):
         assert c.post("/v1/completions", json={"model": "tiny", "prompt": "hi", "max_tokens": 2, "temperature": 0}).status_code == 200
         r = c.post("/v1/images/generations", json={"prompt": "fox", "seed": 1})
         assert r.status_code == 200 and _decode_png(r.json()["data"][0]["b64_json"]).shape == (4, 4, 3)
-        assert c.post("/sdapi/v1/img2img").status_code == 501 and c.post("/v1/audio/speech").status_code == 501
+        r = c.post("/sdapi/v1/img2img", json={"prompt": "fox", "init_images": ["AAAA"]})
+        assert r.status_code == 400 and "no image input" in r.text
+        assert c.post("/v1/audio/speech").status_code == 501 and c.post("/v1/audio/transcriptions").status_code == 501
+        assert c.get("/sdapi/v1/sd-models").json()[0]["model_name"] == "tiny"
     with TestClient(create_app(eng, model_name="tiny")) as c:
         assert c.post("/v1/images/generations").status_code == 501
+
+
+def test_a1111_front_end_questions(client):
+    models = client.get("/sdapi/v1/sd-models").json()
+    assert models == [{"title": "sd-tiny", "model_name": "sd-tiny", "hash": None, "sha256": None, "filename": "sd-tiny", "config": None}]
+    samplers = client.get("/sdapi/v1/samplers").json()
+    assert samplers and set(samplers[0]) == {"name", "aliases", "options"}
+    options = client.get("/sdapi/v1/options").json()
+    assert options["sd_model_checkpoint"] == "sd-tiny" and options["samples_format"] == "png" and options["sampler_name"] == samplers[0]["name"]
+    assert client.post("/sdapi/v1/txt2img", json={"prompt": "fox", "sampler_name": "No Such Sampler"}).status_code == 400
+    assert client.post("/sdapi/v1/txt2img", json={"prompt": "fox", "sampler_name": samplers[0]["name"], "seed": 3}).status_code == 200
+
+
+def test_img2img_request_handling_over_a_stand_in_pipeline():
+    """The HTTP layer of image-to-image: one base64 image (data URLs accepted) reaches the pipeline decoded, with the
+    strength checked; what the pipeline returns comes back as PNGs."""
+    from fastapi import FastAPI
+
+    from onnx_genai_b200.server.images import add_image_routes
+    from onnx_genai_b200.utils.png import encode_png
+
+    class StandIn:
+        samplers = ["Euler"]
+        init_in = "init_image"
+
+        def __init__(self):
+            self.calls = []
+
+        def generate(self, **kw):
+            self.calls.append(kw)
+            img = kw["init_image"] / 255.0
+            return [img * (1.0 - kw["strength"])] * kw["n"]
+
+    pipe = StandIn()
+    app = FastAPI()
+    add_image_routes(app, pipe, "stand-in")
+    src = np.zeros((3, 2, 2), dtype=np.float32)
+    src[0] = 1.0                                                                    # a red 2x2 image
+    b64 = base64.b64encode(encode_png(src)).decode()
+    with TestClient(app) as c:
+        r = c.post("/sdapi/v1/img2img", json={"prompt": "fox", "init_images": ["data:image/png;base64," + b64], "denoising_strength": 0.5,
+                                              "batch_size": 2, "seed": 9})
+        assert r.status_code == 200, r.text
+        body = r.json()
+        assert len(body["images"]) == 2 and body["parameters"]["denoising_strength"] == 0.5 and body["parameters"]["seed"] == 9
+        px = _decode_png(body["images"][0])
+        assert px.shape == (2, 2, 3) and abs(int(px[0, 0, 0]) - 128) <= 1 and px[0, 0, 1] == 0
+        call = pipe.calls[0]
+        assert call["init_image"].shape == (3, 2, 2) and call["init_image"][0, 0, 0] == 255.0 and call["n"] == 2 and call["seed"] == 9
+        for bad in ({"init_images": []}, {"init_images": [b64, b64]}, {"init_images": ["@@not base64@@"]},
+                    {"init_images": [base64.b64encode(b"not an image").decode()]}, {"init_images": [b64], "denoising_strength": 1.5}):
+            assert c.post("/sdapi/v1/img2img", json={"prompt": "fox", **bad}).status_code == 400, bad
