@@ -335,6 +335,10 @@ def cmd_serve(args, profiler):
             from .server.audio import SpeechPipeline
 
             app_kw["speech_pipeline"] = SpeechPipeline(args.speech_package, media_device)
+        if getattr(args, "transcribe_package", ""):
+            from .server.transcribe import WorkflowTranscriber
+
+            app_kw["transcriber"] = WorkflowTranscriber(args.transcribe_package, media_device)
         app = create_app(eng, model_name=os.path.basename(os.path.abspath(args.model)), **app_kw)
     uvicorn.run(app, host=host or "127.0.0.1", port=int(port), log_level="info")
     return 0
@@ -571,6 +575,7 @@ def main(argv=None):
                    help="reasoning effort handed to chat templates that take one, when a request names none")
     s.add_argument("--image-package", default="", help="text-to-image workflow package to serve at /v1/images/generations and /sdapi/v1/txt2img")
     s.add_argument("--speech-package", default="", help="text-to-speech workflow package to serve at /v1/audio/speech")
+    s.add_argument("--transcribe-package", default="", help="speech-to-text workflow package to serve at /v1/audio/transcriptions")
     s.add_argument("--models-config", default="", help="YAML or JSON file: models: {name: {path: DIR, ...engine flags}}")
     s.add_argument("--max-context", type=int, default=0)
     _add_engine(s)

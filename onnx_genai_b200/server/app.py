@@ -207,7 +207,7 @@ def _options_from_request(body: dict, default_max: int, max_cap: int) -> Generat
 
 def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int = 4096, max_queue_depth: int = 256,
                enable_debug_endpoints: bool = False, node_id: str = "node-0", admission_window_ms: float = 2.0,
-               default_reasoning_effort: str | None = None, image_pipeline=None, speech_pipeline=None) -> FastAPI:
+               default_reasoning_effort: str | None = None, image_pipeline=None, speech_pipeline=None, transcriber=None) -> FastAPI:
     app = FastAPI(title="onnx-genai-b200")
     driver = EngineDriver(engine, max_queue_depth, admission_window_ms)
     metrics = Metrics()
@@ -315,8 +315,8 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
 
     # Media routes of the reference server.  Image generation is served when a text-to-image workflow package is mounted
     # (``image_pipeline``, see server/images.py), speech synthesis when a speech package is (``speech_pipeline``, server/audio.py);
-    # image-to-image comes with the image routes (and answers 400 when the workflow has no image input); transcription
-    # answers 501 with the reason.
+    # image-to-image comes with the image routes (and answers 400 when the workflow has no image input); transcription is
+    # served when a transcriber is mounted (``transcriber``, server/transcribe.py); a route without its pipeline answers 501 with the reason.
     if image_pipeline is not None:
         from .images import add_image_routes
 
@@ -325,6 +325,10 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
         from .audio import add_speech_routes
 
         add_speech_routes(app, speech_pipeline)
+    if transcriber is not None:
+        from .transcribe import add_transcription_routes
+
+        add_transcription_routes(app, transcriber, model_name)
     def _not_served(kind: str):
         async def handler():
             raise HTTPException(501, f"{kind} needs a {kind.split()[0]} model pipeline; this server hosts decoder-only text models "
@@ -337,6 +341,8 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
         if image_pipeline is not None and _path in ("/v1/images/generations", "/sdapi/v1/txt2img", "/sdapi/v1/img2img"):
             continue
         if speech_pipeline is not None and _path == "/v1/audio/speech":
+            continue
+        if transcriber is not None and _path == "/v1/audio/transcriptions":
             continue
         app.post(_path)(_not_served(_kind))
 
