@@ -215,3 +215,43 @@ def test_upstream_drafter_heads_run_and_are_causal(name, hidden_inputs, outputs)
         assert torch.allclose(three[o][:, :2], two[o], atol=1e-5) and torch.allclose(two[o][:, :1], one[o], atol=1e-5), o
         assert not torch.allclose(three[o][:, 2], three[o][:, 1])
     assert three["present.0.key"].shape == (1, 1, 3, 8) and torch.allclose(three["present.0.key"][:, :, :2], two["present.0.key"], atol=1e-6)
+
+
+def test_recurrent_decoder_steps_like_it_prefills():
+    """A decoder with no attention cache at all -- a causal short convolution and gated-delta linear attention, both
+    carrying state through ``X.in`` / ``X.out`` ports: token-by-token decoding gives the logits of one prefill call."""
+    from onnx_genai_b200.package import onnx_pb as pb
+
+    rng = np.random.default_rng(4)
+    vocab, hidden, heads, dk, dv, taps = 20, 16, 2, 4, 8, 4
+    f = lambda *shape: (rng.standard_normal(shape) * 0.4).astype(np.float32)
+    inits = {"embed": f(vocab, hidden), "conv_w": f(hidden, 1, taps), "conv_b": f(hidden), "wq": f(hidden, heads * dk), "wk": f(hidden, heads * dk),
+             "wv": f(hidden, heads * dv), "wd": f(hidden, heads), "wb": f(hidden, heads), "head": f(heads * dv, vocab)}
+    N = lambda op, ins, outs, domain="", **attrs: pb.Node(op_type=op, inputs=ins, outputs=outs, name=outs[0], domain=domain, attrs=attrs)
+    nodes = [N("Gather", ["embed", "input_ids"], ["x"]), N("Transpose", ["x"], ["x_cf"], perm=[0, 2, 1]),
+             N("CausalConvWithState", ["x_cf", "conv_w", "conv_b", "conv.in"], ["y_cf", "conv.out"], "com.microsoft", activation="silu"),
+             N("Transpose", ["y_cf"], ["y"], perm=[0, 2, 1]), N("MatMul", ["y", "wq"], ["q"]), N("MatMul", ["y", "wk"], ["k_raw"]),
+             N("LpNormalization", ["k_raw"], ["k"], axis=-1, p=2),          # one key head group per row is enough for the test's purpose
+             N("MatMul", ["y", "wv"], ["v"]), N("MatMul", ["y", "wd"], ["d_raw"]), N("Softplus", ["d_raw"], ["d_pos"]), N("Neg", ["d_pos"], ["decay"]),
+             N("MatMul", ["y", "wb"], ["b_raw"]), N("Sigmoid", ["b_raw"], ["beta"]),
+             N("LinearAttention", ["q", "k", "v", "mem.in", "decay", "beta"], ["o", "mem.out"], "com.microsoft", q_num_heads=heads, kv_num_heads=heads,
+               update_rule="gated_delta"),
+             N("MatMul", ["o", "head"], ["logits"])]
+    vi = lambda name, dt, shape: pb.ValueInfo(name, dt, shape)
+    graph = pb.Graph(name="recurrent", nodes=nodes,
+                     initializers={k: pb.Tensor(name=k, dims=tuple(v.shape), data_type=pb.FLOAT, array=v) for k, v in inits.items()},
+                     inputs=[vi("input_ids", pb.INT64, (1, "seq")), vi("conv.in", pb.FLOAT, (1, hidden, taps - 1)), vi("mem.in", pb.FLOAT, (1, heads, dk, dv))],
+                     outputs=[vi("logits", pb.FLOAT, (1, "seq", vocab)), vi("conv.out", pb.FLOAT, (1, hidden, taps - 1)), vi("mem.out", pb.FLOAT, (1, heads, dk, dv))])
+    model = pb.Model(graph=graph)
+    model.opsets = {"": 21, "com.microsoft": 1}
+    tokens = [3, 17, 5, 5, 9, 0, 12, 8]
+    whole = GraphDecodeSession(model)
+    assert whole.state_in == ["conv.in", "mem.in"] and whole.kv_in == []
+    full = whole.feed(tokens)
+    stepped = GraphDecodeSession(model)
+    rows = torch.cat([stepped.feed(tokens[:3])] + [stepped.feed([t]) for t in tokens[3:]])
+    assert torch.allclose(rows, full, atol=1e-5) and float(full.abs().max()) > 1e-3
+    assert torch.allclose(stepped.state["mem.in"], whole.state["mem.in"], atol=1e-5)
+    stepped.rewind(5)                                            # recomputed from the start, then continued
+    assert torch.allclose(stepped.feed(tokens[5:]), full[5:], atol=1e-5)
+    assert GraphDecodeSession(model).generate(tokens[:2], 4) == GraphDecodeSession(model).generate(tokens[:2], 4)
