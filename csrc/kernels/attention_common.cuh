@@ -79,6 +79,8 @@ struct AttnParams {
   int* status;
   const float* kv_scales;   // one-byte pages only: [pages, kv_heads, 2] fp32 (K scale, V scale)
   int kv_fmt;               // one-byte pages only: 0 = e4m3, 1 = int8
+  unsigned long long* dbg;  // optional (tcgen05 prefill): per-role wait / work nanoseconds of the CTA (dbg_tile, head 0)
+  int dbg_tile;
 };
 
 // Producer: stream blocks [b_begin, b_end) of one sequence / kv head into the ring.

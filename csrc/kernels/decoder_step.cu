@@ -24,7 +24,7 @@ struct LayerPtrs {
 
 struct DecoderPlan {
   int num_layers, hidden, hq, hkv, d, rotary_dim, interleaved, inter_local, vocab, swiglu_bn, window, max_pages, max_pos;
-  int tp;
+  int tp, prefill_tc;
   int64_t num_pages;
   float eps, scale;
   const void *embed, *final_norm, *lm_head;
@@ -48,7 +48,7 @@ using namespace ogb;
   } while (0)
 
 // iparams: num_layers, hidden, hq, hkv, d, rotary_dim, interleaved, inter_local, vocab, swiglu_bn, window, max_pages,
-//          max_pos, tp
+//          max_pos, tp, prefill_tc (1: prefill attention on the tcgen05 kernel)
 // fparams: eps, scale
 // gptrs  : embed, final_norm, lm_head, cos_sin, x, h, qkv, attn, act, x_last, h_last, logits, partial, part_o, part_ml, status
 // lptrs  : per layer 8 pointers (ln1, qkv_w, qkv_b, o_w, ln2, gate_up_w, down_w, kv_pool)
@@ -59,6 +59,7 @@ extern "C" void* ogb_decoder_create(const int* iparams, int64_t num_pages, const
   p->rotary_dim = iparams[5]; p->interleaved = iparams[6]; p->inter_local = iparams[7]; p->vocab = iparams[8];
   p->swiglu_bn = iparams[9]; p->window = iparams[10]; p->max_pages = iparams[11]; p->max_pos = iparams[12];
   p->tp = iparams[13];
+  p->prefill_tc = iparams[14];
   p->num_pages = num_pages;
   p->eps = fparams[0]; p->scale = fparams[1];
   auto P = [&](int i) { return reinterpret_cast<void*>(gptrs[i]); };
@@ -79,6 +80,8 @@ extern "C" void* ogb_decoder_create(const int* iparams, int64_t num_pages, const
 
 extern "C" void ogb_decoder_destroy(void* plan) { delete static_cast<DecoderPlan*>(plan); }
 extern "C" long long ogb_decoder_launches(void* plan) { return static_cast<DecoderPlan*>(plan)->launches; }
+// The KV pool is a reserved address range of which `num_pages` pages are backed; the kernels bound page ids by it.
+extern "C" void ogb_decoder_set_num_pages(void* plan, int64_t num_pages) { static_cast<DecoderPlan*>(plan)->num_pages = num_pages; }
 extern "C" void ogb_decoder_set_split_scratch(void* plan, float* part_o, float* part_ml) {
   DecoderPlan* p = static_cast<DecoderPlan*>(plan);
   p->part_o = part_o;
@@ -129,9 +132,15 @@ extern "C" int ogb_decoder_step(void* plan, const int* token_ids, const int* pos
                                        p->status, stream));
     }
     if (Np > 0) {
-      STEP_CHECK(ogb_paged_prefill_bf16(qkv_prefill, attn_prefill, L.kv_pool, page_table + static_cast<size_t>(Nd) * p->max_pages,
-                                        ctx_len + Nd, cu_q, tile_seq, tile_q0, num_tiles, Np, p->max_pages, p->num_pages, hq,
-                                        hkv, d, qkv_n, attn_n, p->scale, p->window, p->status, stream));
+      if (p->prefill_tc && (d == 64 || d == 128) && attn_n % 8 == 0) {
+        STEP_CHECK(ogb_paged_prefill_tc_bf16(qkv_prefill, attn_prefill, L.kv_pool, page_table + static_cast<size_t>(Nd) * p->max_pages,
+                                             ctx_len + Nd, cu_q, tile_seq, tile_q0, num_tiles, Np, T - Nd, p->max_pages,
+                                             p->num_pages, hq, hkv, d, qkv_n, attn_n, p->scale, p->window, p->status, stream));
+      } else {
+        STEP_CHECK(ogb_paged_prefill_bf16(qkv_prefill, attn_prefill, L.kv_pool, page_table + static_cast<size_t>(Nd) * p->max_pages,
+                                          ctx_len + Nd, cu_q, tile_seq, tile_q0, num_tiles, Np, p->max_pages, p->num_pages, hq,
+                                          hkv, d, qkv_n, attn_n, p->scale, p->window, p->status, stream));
+      }
     }
     if (p->tp == 1) {
       STEP_CHECK(ogb_gemm_bf16(p->attn, L.o_w, p->x, nullptr, p->x, nullptr, T, hid, attn_n, attn_n, attn_n, hid, hid, 1, 0,

@@ -328,6 +328,32 @@ __global__ void page_copy_kernel(uint8_t* dst_base, const uint8_t* src_base, con
     dst[v] = src[v];
 }
 
+// Page moves across every layer in one launch: grid = (blocks per page, pages, layers).  `src_bases` / `dst_bases`
+// hold one base address per layer; either side may be pinned host memory (the device reads and writes it over
+// PCIe without a staging copy).  Page ids come from the packed step plan as int32 and are bounds-checked: a bad
+// id raises kStatusIndexOutOfRange and that page is skipped.
+__global__ void page_move_layers_kernel(const uint64_t* __restrict__ dst_bases, const uint64_t* __restrict__ src_bases,
+                                        const int* __restrict__ src_pages, const int* __restrict__ dst_pages,
+                                        int64_t page_bytes, int64_t src_count, int64_t dst_count, int* status) {
+  const int i = blockIdx.y;
+  const int64_t sp = src_pages[i], dp = dst_pages[i];
+  if (sp < 0 || sp >= src_count || dp < 0 || dp >= dst_count) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) atomicOr(status, kStatusIndexOutOfRange);
+    return;
+  }
+  const uint8_t* src = reinterpret_cast<const uint8_t*>(src_bases[blockIdx.z]) + sp * page_bytes;
+  uint8_t* dst = reinterpret_cast<uint8_t*>(dst_bases[blockIdx.z]) + dp * page_bytes;
+  const int64_t first = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  if ((page_bytes & 15) == 0) {
+    for (int64_t v = first; v < page_bytes / 16; v += step)
+      reinterpret_cast<uint4*>(dst)[v] = reinterpret_cast<const uint4*>(src)[v];
+  } else {
+    for (int64_t v = first; v < page_bytes / 4; v += step)
+      reinterpret_cast<uint32_t*>(dst)[v] = reinterpret_cast<const uint32_t*>(src)[v];
+  }
+}
+
 }  // namespace ogb
 
 using namespace ogb;
@@ -432,4 +458,20 @@ extern "C" int ogb_kv_gather_pages(const void* pool, void* staging, const int64_
 extern "C" int ogb_kv_scatter_pages(void* pool, const void* staging, const int64_t* pages, int n, int64_t page_bytes,
                                     void* stream) {
   return launch_page_copy(pool, staging, nullptr, pages, n, page_bytes, 0, 1, stream);
+}
+
+// n pages of every one of `layers` page arrays: dst_bases[l] + dst_pages[i] * page_bytes <- src_bases[l] + src_pages[i] * page_bytes.
+// The base tables and the index lists are device arrays; the arrays they name may be device or pinned host memory.
+extern "C" int ogb_kv_move_pages(const uint64_t* dst_bases, const uint64_t* src_bases, int layers, const int* src_pages,
+                                 const int* dst_pages, int n, int64_t page_bytes, int64_t src_count, int64_t dst_count,
+                                 int* status, void* stream) {
+  if (n <= 0 || layers <= 0) return 0;
+  if (page_bytes % 4 || n > 65535 || layers > 65535) return -3;
+  const int64_t vecs = (page_bytes % 16 == 0) ? page_bytes / 16 : page_bytes / 4;
+  int bx = static_cast<int>((vecs + 255) / 256);
+  if (bx > 16) bx = 16;
+  if (bx < 1) bx = 1;
+  page_move_layers_kernel<<<dim3(bx, n, layers), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      dst_bases, src_bases, src_pages, dst_pages, page_bytes, src_count, dst_count, status);
+  return static_cast<int>(cudaGetLastError());
 }

@@ -39,6 +39,12 @@ int ogb_paged_prefill_bf16(const void* q, void* out, const void* pool, const int
                            const int* cu_q, const int* tile_seq, const int* tile_q0, int num_tiles, int num_seqs,
                            int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride, int o_stride,
                            float scale, int window, int* status, void* stream);
+// Prefill attention on tcgen05 / TMEM: the contract of ogb_paged_prefill_bf16 plus `q_rows`, the number of rows of
+// the packed query buffer the kernel's tensor map may read; each 128-row aligned pair of 64-row tiles is one CTA.
+int ogb_paged_prefill_tc_bf16(const void* q, void* out, const void* pool, const int* page_table, const int* ctx_len,
+                              const int* cu_q, const int* tile_seq, const int* tile_q0, int num_tiles, int num_seqs,
+                              int q_rows, int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride,
+                              int o_stride, float scale, int window, int* status, void* stream);
 int ogb_paged_decode_bf16(const void* q, void* out, const void* pool, const int* page_table, const int* ctx_len,
                           int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride,
                           int o_stride, float scale, int num_splits, float* part_o, float* part_ml, int window,
@@ -82,6 +88,11 @@ int ogb_kv_page_copy(void* pool, const int64_t* src_pages, const int64_t* dst_pa
                      void* stream);
 int ogb_kv_gather_pages(const void* pool, void* staging, const int64_t* pages, int n, int64_t page_bytes, void* stream);
 int ogb_kv_scatter_pages(void* pool, const void* staging, const int64_t* pages, int n, int64_t page_bytes, void* stream);
+// Moves n pages of every one of `layers` page arrays in one launch (swap out / swap in / copy-on-write across the
+// whole model).  Either side may be pinned host memory; int32 page ids are bounds-checked against the two counts.
+int ogb_kv_move_pages(const uint64_t* dst_bases, const uint64_t* src_bases, int layers, const int* src_pages,
+                      const int* dst_pages, int n, int64_t page_bytes, int64_t src_count, int64_t dst_count, int* status,
+                      void* stream);
 
 // MatMulNBits int4 (block 32, optional nibble zero points) weight-only GEMM, in-kernel dequant.
 // qweight [N, K/32, 16] uint8 (low nibble = even k), scales [N, K/32] bf16 or fp32, zp [N, ceil(K/32/2)] or NULL.

@@ -11,12 +11,13 @@
 // the library image instead.
 //
 // Limits and rules:
-//   * at most 4 rows per call and a vocabulary of at most 262144 entries; anything larger is refused with
-//     -3 and nothing is launched.  The array takes 4 MiB on every GPU that loads the library, for the life
-//     of the process.
+//   * at most 4 rows per call and a vocabulary of at most 262144 entries; anything larger, or a row stride
+//     `ld` shorter than the vocabulary, is refused with -3 and nothing is launched.  The array takes 4 MiB on
+//     every GPU that loads the library, for the life of the process.
 //   * the call allocates nothing: no cudaMalloc / cudaFree and no allocating library routine.  The first
 //     call on each device looks up the array's device address (with that device current); make that first
-//     call outside any stream capture.
+//     call outside any stream capture.  The address used is that of the device that is current at the call,
+//     so `stream` must belong to the current device.
 //   * every call uses the same array.  The kernel rewrites each weight it later reads, so nothing needs
 //     clearing between calls, but two calls that run at the same time on one GPU (different streams)
 //     would overwrite each other's weights: issue them one after the other.

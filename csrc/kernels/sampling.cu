@@ -627,7 +627,7 @@ extern "C" int ogb_sample_bf16_no_alloc(const void* logits, int* out_tokens, con
                                         const float* top_p, const float* min_p, const float* uniform, int rows, int vocab,
                                         int ld, void* stream) {
   if (rows <= 0) return 0;
-  if (rows > kNoAllocMaxRows || vocab <= 0 || vocab > kNoAllocMaxVocab) return -3;
+  if (rows > kNoAllocMaxRows || vocab <= 0 || vocab > kNoAllocMaxVocab || ld < vocab) return -3;
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -640,8 +640,17 @@ extern "C" int ogb_sample_bf16_no_alloc(const void* logits, int* out_tokens, con
     if (e != cudaSuccess) return static_cast<int>(e);
     g_no_alloc_work_ptr[dev] = static_cast<uint32_t*>(p);
   }
-  sample_kernel<<<rows, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(logits), out_tokens, temperature, top_k, top_p, min_p, uniform,
-      g_no_alloc_work_ptr[dev], vocab, ld);
+  // same choice as ogb_sample_bf16: the vectorised kernel when rows are 16-byte aligned (the array itself is
+  // 256-byte aligned and a row of it starts at a multiple of vocab * 4 bytes); both kernels pick identical tokens
+  const bool vec_ok = (vocab % 8 == 0) && (ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(logits) & 15) == 0);
+  if (vec_ok) {
+    sample_kernel_vec<<<rows, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(logits), out_tokens, temperature, top_k, top_p, min_p, uniform,
+        g_no_alloc_work_ptr[dev], vocab, ld);
+  } else {
+    sample_kernel<<<rows, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(logits), out_tokens, temperature, top_k, top_p, min_p, uniform,
+        g_no_alloc_work_ptr[dev], vocab, ld);
+  }
   return static_cast<int>(cudaGetLastError());
 }

@@ -39,6 +39,7 @@ int BlockPool::allocate() {
       evictable_.pop_front();
       if (!in_evictable_[cand] || ref_[cand] != 0) continue;  // stale entry
       in_evictable_[cand] = 0;
+      --evictable_live_;
       page = cand;
       break;
     }
@@ -58,6 +59,7 @@ void BlockPool::release(int page) {
   if (--ref_[page] > 0) return;
   if (hash_of_[page] != 0) {
     evictable_.push_back(page);
+    if (!in_evictable_[page]) ++evictable_live_;
     in_evictable_[page] = 1;
   } else {
     free_.push_back(page);
@@ -79,7 +81,10 @@ int BlockPool::lookup(uint64_t hash) {
   auto it = by_hash_.find(hash);
   if (it == by_hash_.end()) return -1;
   const int page = it->second;
-  if (ref_[page] == 0) in_evictable_[page] = 0;  // leaves the LRU lazily (stale deque entry is skipped)
+  if (ref_[page] == 0 && in_evictable_[page]) {  // leaves the LRU lazily (stale deque entry is skipped)
+    in_evictable_[page] = 0;
+    --evictable_live_;
+  }
   ++ref_[page];
   ++hits_;
   return page;
@@ -92,6 +97,20 @@ void BlockPool::publish(int page, uint64_t hash) {
   by_hash_[hash] = page;
 }
 
+bool BlockPool::unpublish(int page) {
+  // only a cached page that nobody references can leave the cache without a holder noticing
+  if (page < 0 || page >= num_pages() || hash_of_[page] == 0 || ref_[page] != 0) return false;
+  auto it = by_hash_.find(hash_of_[page]);
+  if (it != by_hash_.end() && it->second == page) by_hash_.erase(it);
+  hash_of_[page] = 0;
+  if (in_evictable_[page]) {   // its deque entry goes stale and is skipped by allocate()
+    in_evictable_[page] = 0;
+    --evictable_live_;
+  }
+  free_.push_back(page);
+  return true;
+}
+
 void BlockPool::reset_prefix_cache() {
   for (int p : evictable_) {
     if (in_evictable_[p] && ref_[p] == 0) {
@@ -100,6 +119,7 @@ void BlockPool::reset_prefix_cache() {
     }
   }
   evictable_.clear();
+  evictable_live_ = 0;
   by_hash_.clear();
   std::fill(hash_of_.begin(), hash_of_.end(), 0);
 }
@@ -138,6 +158,8 @@ static PlanLayout make_layout(const CoreConfig& c) {
   l.swap_out_host = take(l.max_swap);
   l.swap_in_dev = take(l.max_swap);
   l.swap_in_host = take(l.max_swap);
+  l.max_runs = 2 * c.max_seqs + 4;
+  l.move_runs = take(2 * l.max_runs);
   l.total_words = o;
   return l;
 }
@@ -236,6 +258,7 @@ bool Core::ensure_pages(Sequence& s, int new_len, std::vector<std::pair<int, int
     const int fresh = pool_.allocate();
     if (fresh < 0) return false;
     copies.emplace_back(s.pages[write_page], fresh);
+    move_kinds_.push_back(0);
     pool_.release(s.pages[write_page]);
     s.pages[write_page] = fresh;
   }
@@ -277,6 +300,7 @@ bool Core::preempt_one(Sequence* keep, std::vector<std::pair<int, int>>& swap_ou
       host_free_.pop_back();
       v.host_pages.push_back(hp);
       swap_out.emplace_back(v.pages[i], hp);
+      move_kinds_.push_back(1);
     }
     for (int p : v.pages) pool_.release(p);
     v.pages.clear();
@@ -314,6 +338,7 @@ int Core::build_step(int32_t* plan) {
   const PlanLayout& L = layout_;
   std::memset(plan, 0, sizeof(int32_t) * 32);
   ++step_id_;
+  move_kinds_.clear();
   std::vector<std::pair<int, int>> copies, swap_out, swap_in;
   int budget = cfg_.max_tokens_per_step;
 
@@ -376,6 +401,7 @@ int Core::build_step(int32_t* plan) {
       const int p = pool_.allocate();
       s->pages.push_back(p);
       swap_in.emplace_back(p, s->host_pages[i]);
+      move_kinds_.push_back(2);
       host_free_.push_back(s->host_pages[i]);
     }
     s->host_pages.clear();
@@ -506,6 +532,28 @@ int Core::build_step(int32_t* plan) {
   for (auto& c : swap_out) { if (nso < L.max_swap) { plan[L.swap_out_dev + nso] = c.first; plan[L.swap_out_host + nso] = c.second; ++nso; } }
   for (auto& c : swap_in) { if (nsi < L.max_swap) { plan[L.swap_in_dev + nsi] = c.first; plan[L.swap_in_host + nsi] = c.second; ++nsi; } }
 
+  // The page moves must run in the order they were decided: a page that a victim frees by swapping out can be
+  // handed out again as the target of a later copy, and a page that was the target of a copy can belong to a
+  // sequence preempted later in the same step.  Runs of one kind are kept together; the lists above are in
+  // decision order within each kind.
+  int nruns = 0;
+  {
+    int emitted[3] = {0, 0, 0};
+    const int limit[3] = {ncopy, nso, nsi};
+    for (size_t i = 0; i < move_kinds_.size(); ++i) {
+      const int k = move_kinds_[i];
+      if (emitted[k] >= limit[k]) continue;   // an entry the list had no room for
+      ++emitted[k];
+      if (nruns > 0 && plan[L.move_runs + 2 * (nruns - 1)] == k) {
+        ++plan[L.move_runs + 2 * (nruns - 1) + 1];
+      } else if (nruns < L.max_runs) {
+        plan[L.move_runs + 2 * nruns] = k;
+        plan[L.move_runs + 2 * nruns + 1] = 1;
+        ++nruns;
+      }
+    }
+  }
+  plan[kHdrNumMoveRuns] = nruns;
   plan[kHdrNumTokens] = t;
   plan[kHdrNumDecode] = static_cast<int>(decode_items.size());
   plan[kHdrNumPrefillSeqs] = static_cast<int>(prefill_items.size());
@@ -670,20 +718,34 @@ int Core::prefix_adopt(const int32_t* tokens, int n_tokens, int32_t* out_pages, 
   const int full = std::min(cap, n_tokens / kPageTokens);
   uint64_t h = 0;
   int served = 0;
+  // Adopted pages stay referenced until the loop ends: released at once they would be the first candidates for
+  // eviction by the next allocation of this very call, and a pool smaller than the prefix would hand the same
+  // page out twice.
+  std::vector<int> held;
   for (int i = 0; i < full; ++i) {
     h = BlockPool::chain_hash(h, tokens + i * kPageTokens, kPageTokens);
     if (pool_.contains(h)) {
+      const int page = pool_.peek(h);
+      pool_.retain(page);                 // referenced, so it cannot be evicted below (not a request hit: no statistics)
+      held.push_back(page);
       out_pages[i] = -1;
     } else {
       const int page = pool_.allocate();
       if (page < 0) break;
       pool_.publish(page, h);
-      pool_.release(page);          // cached and unreferenced: the next admission with this prefix retains it
+      held.push_back(page);
       out_pages[i] = page;
     }
     ++served;
   }
+  for (int page : held) pool_.release(page);   // cached and unreferenced: the next admission with this prefix retains them
   return served;
+}
+
+int Core::prefix_unpublish(const int32_t* pages, int n) {
+  int done = 0;
+  for (int i = 0; i < n; ++i) done += pool_.unpublish(pages[i]) ? 1 : 0;
+  return done;
 }
 
 int Core::prefix_peek(const int32_t* tokens, int n_tokens, int32_t* out_pages, int cap) const {
@@ -753,7 +815,7 @@ int ogb_core_layout(void* h, int32_t* out, int cap) {
   const int32_t v[] = {l.header, l.token_ids, l.positions, l.slots, l.seq_slot, l.ctx_len, l.cu_q, l.page_table,
                        l.tile_seq, l.tile_q0, l.logit_rows, l.temperature, l.top_k, l.top_p, l.min_p, l.uniform,
                        l.copy_src, l.copy_dst, l.swap_out_dev, l.swap_out_host, l.swap_in_dev, l.swap_in_host,
-                       l.total_words, l.max_tiles, l.max_swap, l.logit_seq, l.max_rows};
+                       l.total_words, l.max_tiles, l.max_swap, l.logit_seq, l.max_rows, l.move_runs, l.max_runs};
   const int n = static_cast<int>(sizeof(v) / sizeof(v[0]));
   for (int i = 0; i < n && i < cap; ++i) out[i] = v[i];
   return n;
@@ -790,6 +852,7 @@ int ogb_core_seq_pages(void* h, int64_t id, int32_t* out, int cap) { return stat
 int ogb_core_prefix_adopt(void* h, const int32_t* tokens, int n, int32_t* out_pages, int cap) {
   return static_cast<Core*>(h)->prefix_adopt(tokens, n, out_pages, cap);
 }
+int ogb_core_prefix_unpublish(void* h, const int32_t* pages, int n) { return static_cast<Core*>(h)->prefix_unpublish(pages, n); }
 int ogb_core_prefix_peek(void* h, const int32_t* tokens, int n, int32_t* out_pages, int cap) {
   return static_cast<Core*>(h)->prefix_peek(tokens, n, out_pages, cap);
 }

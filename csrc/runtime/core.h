@@ -67,7 +67,7 @@ class BlockPool {
  public:
   explicit BlockPool(int num_pages);
   int num_pages() const { return static_cast<int>(ref_.size()); }
-  int num_free() const { return static_cast<int>(free_.size() + evictable_.size()); }
+  int num_free() const { return static_cast<int>(free_.size()) + evictable_live_; }
   int allocate();                    // -1 when exhausted
   void add_pages(int n);             // the backing buffer grew: ids [old size, old size + n) become free pages
   void retain(int page) { ++ref_[page]; }
@@ -79,6 +79,7 @@ class BlockPool {
   bool contains(uint64_t hash) const { return by_hash_.count(hash) != 0; }
   int peek(uint64_t hash) const { auto it = by_hash_.find(hash); return it == by_hash_.end() ? -1 : it->second; }
   void publish(int page, uint64_t hash);
+  bool unpublish(int page);          // a cached, unreferenced page leaves the prefix cache and becomes free again
   int64_t hits() const { return hits_; }
   int64_t lookups() const { return lookups_; }
   void reset_prefix_cache();
@@ -89,6 +90,7 @@ class BlockPool {
   std::vector<int> free_;
   std::deque<int> evictable_;        // cached, refcount 0, LRU order (front = oldest)
   std::vector<uint8_t> in_evictable_;
+  int evictable_live_ = 0;           // deque entries that are live (the deque also holds stale ones, skipped lazily)
   std::unordered_map<uint64_t, int> by_hash_;
   int64_t hits_ = 0, lookups_ = 0;
 };
@@ -121,14 +123,17 @@ struct PlanLayout {
   int logit_seq;                             // [max_rows] sequence id (low 31 bits) of every logit row
   int copy_src, copy_dst;                    // [max_seqs] CoW page copies to run before the step
   int swap_out_dev, swap_out_host, swap_in_dev, swap_in_host;  // [max_swap]
+  int move_runs;                             // [2 * max_runs] (kind, count) pairs: the order in which the page moves above were
+                                             // decided (kind 0 = CoW copy, 1 = swap out, 2 = swap in); each list is consumed
+                                             // front to back, so running the runs in order reproduces the scheduler's sequence
   int total_words;
-  int max_tiles, max_swap;
+  int max_tiles, max_swap, max_runs;
   int max_rows;                              // max_seqs * (1 + max_draft_tokens)
 };
 
 enum PlanHeader : int {
   kHdrNumTokens = 0, kHdrNumDecode, kHdrNumPrefillSeqs, kHdrNumTiles, kHdrNumLogitRows, kHdrNumCopies,
-  kHdrNumSwapOut, kHdrNumSwapIn, kHdrNumPrefillTokens, kHdrMaxCtx, kHdrNumPreempted, kHdrStepId,
+  kHdrNumSwapOut, kHdrNumSwapIn, kHdrNumPrefillTokens, kHdrMaxCtx, kHdrNumPreempted, kHdrStepId, kHdrNumMoveRuns,
 };
 
 struct StepEvent {
@@ -171,6 +176,9 @@ class Core {
   // existed; returns the number of leading pages that are now served (stops when the pool is exhausted).
   int seq_pages(int64_t seq_id, int32_t* out, int cap) const;
   int prefix_adopt(const int32_t* tokens, int n_tokens, int32_t* out_pages, int cap);
+  // prefix_unpublish: adopted pages that were never filled (the pool ran out in the middle of a chunk) leave the
+  // prefix cache again, so no later request can attach to uninitialised K/V.  Returns how many were removed.
+  int prefix_unpublish(const int32_t* pages, int n);
   // prefix_peek: the pages that currently serve the leading full pages of `tokens` (no reference is taken; valid
   // until the next call that allocates).  Returns how many leading pages are cached.
   int prefix_peek(const int32_t* tokens, int n_tokens, int32_t* out_pages, int cap) const;
@@ -212,6 +220,7 @@ class Core {
   std::deque<int64_t> swapped_;
   std::vector<int64_t> step_rows_;       // sequence of each logit row of the last built step
   std::vector<int64_t> step_seqs_;       // every sequence scheduled in the last built step
+  std::vector<uint8_t> move_kinds_;      // kind of every page move of the step being built, in decision order
   std::unordered_map<int, int64_t> tenant_served_;
   int64_t next_id_ = 1;
   int64_t clock_ = 0;

@@ -84,8 +84,11 @@ def main(argv=None) -> int:
             base.all_reduce(part)
             x_ref.add_(part)
 
+        turn = [0]
+
         def fused_path():
-            fc.row_parallel(a, w, rows, slot=1)
+            turn[0] ^= 1                     # consecutive exchanges alternate between the two slots, as in a decoder layer
+            fc.row_parallel(a, w, rows, slot=turn[0])
 
         def gemm_only():
             ops.gemm(a, w, out=part)

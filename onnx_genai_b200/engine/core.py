@@ -22,12 +22,12 @@ PREEMPT = {"recompute": 0, "swap": 1}
 FINISH = {0: None, 1: "length", 2: "stop", 3: "cancelled", 4: "error"}
 
 HDR = dict(num_tokens=0, num_decode=1, num_prefill_seqs=2, num_tiles=3, num_logit_rows=4, num_copies=5,
-           num_swap_out=6, num_swap_in=7, num_prefill_tokens=8, max_ctx=9, num_preempted=10, step_id=11)
+           num_swap_out=6, num_swap_in=7, num_prefill_tokens=8, max_ctx=9, num_preempted=10, step_id=11, num_move_runs=12)
 
 _LAYOUT_FIELDS = ["header", "token_ids", "positions", "slots", "seq_slot", "ctx_len", "cu_q", "page_table", "tile_seq",
                   "tile_q0", "logit_rows", "temperature", "top_k", "top_p", "min_p", "uniform", "copy_src", "copy_dst",
                   "swap_out_dev", "swap_out_host", "swap_in_dev", "swap_in_host", "total_words", "max_tiles", "max_swap",
-                  "logit_seq", "max_rows"]
+                  "logit_seq", "max_rows", "move_runs", "max_runs"]
 
 
 def load_runtime():
@@ -74,6 +74,8 @@ def load_runtime():
     lib.ogb_core_seq_pages.restype = c_int
     lib.ogb_core_prefix_adopt.argtypes = [P, I32P, c_int, I32P, c_int]
     lib.ogb_core_prefix_adopt.restype = c_int
+    lib.ogb_core_prefix_unpublish.argtypes = [P, I32P, c_int]
+    lib.ogb_core_prefix_unpublish.restype = c_int
     lib.ogb_core_prefix_peek.argtypes = [P, I32P, c_int, I32P, c_int]
     lib.ogb_core_prefix_peek.restype = c_int
     lib.ogb_core_seq_len.argtypes = [P, c_int64]
@@ -194,6 +196,13 @@ class Core:
         n = int(self.lib.ogb_core_prefix_adopt(self.h, arr.ctypes.data_as(POINTER(c_int32)), len(arr),
                                                out.ctypes.data_as(POINTER(c_int32)), len(out)))
         return out[:max(n, 0)].copy()
+
+    def prefix_unpublish(self, pages) -> int:
+        """Take adopted pages that were never filled out of the prefix cache again; returns how many were removed."""
+        arr = np.ascontiguousarray([p for p in pages if p >= 0], dtype=np.int32)
+        if len(arr) == 0:
+            return 0
+        return int(self.lib.ogb_core_prefix_unpublish(self.h, arr.ctypes.data_as(POINTER(c_int32)), len(arr)))
 
     def prefix_peek(self, tokens):
         """Pages that currently serve the leading full pages of ``tokens`` in the prefix cache (no reference taken)."""

@@ -218,20 +218,30 @@ class KvOffload:
             if blob is None:
                 break
             blobs.append(blob)
+        # a blob written by a different model layout ends the run: nothing after it is adopted
+        per_layer = PAGES_PER_CHUNK * (self.page_bytes + self.scale_bytes)
+        want = per_layer * len(self.llm.kv.pools)
+        good = 0
+        while good < len(blobs) and len(blobs[good]) == want:
+            good += 1
+        blobs = blobs[:good]
         if not blobs:
             return 0
+        # Adoption publishes a page under its prefix hash before any byte of it is written, so every adopted page
+        # must be filled below or leave the cache again.  When the pool runs out in the middle of a chunk the pages
+        # of that partial chunk are taken back out (a later request must never attach to uninitialised K/V).
         adopted = self.llm.core.prefix_adopt(toks[: len(blobs) * CHUNK_TOKENS])
         n_chunks = len(adopted) // PAGES_PER_CHUNK
+        tail = adopted[n_chunks * PAGES_PER_CHUNK:]
+        if len(tail):
+            self.llm.core.prefix_unpublish(tail)
         restored_tokens = 0
-        per_layer = PAGES_PER_CHUNK * (self.page_bytes + self.scale_bytes)
         for c in range(n_chunks):
             page_ids = adopted[c * PAGES_PER_CHUNK:(c + 1) * PAGES_PER_CHUNK]
             fill = np.flatnonzero(page_ids >= 0)
             if len(fill) == 0:
                 continue                                  # the device cache already had this chunk
             blob = np.frombuffer(blobs[c], dtype=np.uint8)
-            if len(blob) != per_layer * len(self.llm.kv.pools):
-                break                                     # written by a different model layout: ignore from here on
             dst = torch.from_numpy(page_ids[fill].astype(np.int64)).to(self.llm.device)
             for li, pool in enumerate(self.llm.kv.pools):
                 base = li * per_layer

@@ -138,13 +138,18 @@ class LLMEngine:
         self.L = L
         self.plan_host = torch.zeros(L.total_words, dtype=torch.int32, pin_memory=is_cuda)
         self.plan_np = self.plan_host.numpy()
-        self.dev_words = L.swap_out_dev      # sections after this offset are host-only
-        self.plan_dev = torch.zeros(self.dev_words, dtype=torch.int32, device=self.device) if is_cuda else self.plan_host
+        self.dev_words = L.swap_out_dev      # sections after this offset cross to the device only in steps that swap pages
+        self.plan_dev_full = torch.zeros(L.total_words, dtype=torch.int32, device=self.device) if is_cuda else self.plan_host
+        self.plan_dev = self.plan_dev_full[: self.dev_words] if is_cuda else self.plan_host     # what every step copies
+        self.status_host = torch.zeros(1, dtype=torch.int32, pin_memory=is_cuda)
         self.sampled_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=is_cuda)
         self.sampled_dev = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
         self.sample_work = (torch.empty(max_rows * m.vocab, dtype=torch.int32, device=self.device)
                             if is_cuda else None)
         self.host_kv = None
+        self.host_scales = None
+        self.direct_swap = False
+        self.swap_moves = 0                # page-move launches issued for swap / copy-on-write
         if cfg.num_host_pages > 0:
             shape = (cfg.num_host_pages,) + tuple(self.kv.pools[0].shape[1:])
             if cfg.host_allocator_plugin:
@@ -161,8 +166,22 @@ class LLMEngine:
                 self.memory.lease("kv", "host", sum(t.numel() * t.element_size() for t in self.host_kv), "swap space")
             except Exception:
                 pass
-            self.swap_stage = torch.zeros((max_pages_per_seq,) + tuple(self.kv.pools[0].shape[1:]),
-                                          dtype=self.kv.pools[0].dtype, device=self.device)
+            if self.kv.scales is not None:     # one-byte pages: the per-(page, head, K|V) scales travel with their page
+                sshape = (cfg.num_host_pages,) + tuple(self.kv.scales[0].shape[1:])
+                self.host_scales = [torch.zeros(sshape, dtype=torch.float32, pin_memory=is_cuda and not cfg.host_allocator_plugin)
+                                    for _ in range(m.num_layers)]
+            # Pinned host memory is addressable from the device: swap kernels on a side stream read and write it in
+            # place, so a swap needs no staging buffer and never blocks the host.  Memory from an allocator plugin is
+            # not pinned by the driver and keeps the synchronous copy path.
+            self.direct_swap = is_cuda and not cfg.host_allocator_plugin
+        if is_cuda:
+            addr = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=self.device)
+            self._kv_bases = addr(self.kv.pools)
+            self._scale_bases = addr(self.kv.scales) if self.kv.scales is not None else None
+            if self.direct_swap:
+                self._host_bases = addr(self.host_kv)
+                self._host_scale_bases = addr(self.host_scales) if self.host_scales is not None else None
+                self.swap_stream = torch.cuda.Stream(device=self.device)
         p = self.plan_dev
         S, T, MP = cfg.max_seqs, cfg.max_tokens_per_step, max_pages_per_seq
         self.si = StepInputs(
@@ -190,6 +209,7 @@ class LLMEngine:
         self.graph_replays = 0
         self.verify_on_decode_kernel = 0   # steps whose draft rows ran on the split-KV decode kernel
         self.graph_declines: list = []
+        self.device_faults = 0            # steps that ended with a non-zero device status word
 
     # --------------------------------------------------------------------------------------
     def add_request(self, prompt_ids, max_new_tokens=256, temperature=0.0, top_k=0, top_p=1.0, min_p=0.0, seed=0,
@@ -204,31 +224,80 @@ class LLMEngine:
         return self.core.has_work
 
     def _page_moves(self, hdr):
+        """Copy-on-write copies, swap-outs and swap-ins of the step, in the order the scheduler decided them (a page
+        freed by a swap-out can be the target of a later copy, and the target of a copy can be swapped out later in
+        the same step).  On a GPU with pinned swap space every run is one kernel launch per table (KV pages, scale
+        rows) over all layers on a side stream; the step's own kernels wait for that stream, the host does not."""
         L, pn = self.L, self.plan_np
-        nso, nsi, ncp = int(hdr[HDR["num_swap_out"]]), int(hdr[HDR["num_swap_in"]]), int(hdr[HDR["num_copies"]])
-        if nso:
-            dev_pages = torch.from_numpy(pn[L.swap_out_dev:L.swap_out_dev + nso].astype(np.int64))
-            host_pages = torch.from_numpy(pn[L.swap_out_host:L.swap_out_host + nso].astype(np.int64))
-            dp = dev_pages.to(self.device)
-            for li, pool in enumerate(self.kv.pools):
-                for s in range(0, nso, self.swap_stage.shape[0]):
-                    e = min(nso, s + self.swap_stage.shape[0])
-                    ops.kv_gather_pages(pool, self.swap_stage, dp[s:e])
-                    self.host_kv[li][host_pages[s:e]] = self.swap_stage[: e - s].cpu()
-        if nsi:
-            dev_pages = torch.from_numpy(pn[L.swap_in_dev:L.swap_in_dev + nsi].astype(np.int64))
-            host_pages = torch.from_numpy(pn[L.swap_in_host:L.swap_in_host + nsi].astype(np.int64))
-            dp = dev_pages.to(self.device)
-            for li, pool in enumerate(self.kv.pools):
-                for s in range(0, nsi, self.swap_stage.shape[0]):
-                    e = min(nsi, s + self.swap_stage.shape[0])
-                    self.swap_stage[: e - s].copy_(self.host_kv[li][host_pages[s:e]])
-                    ops.kv_scatter_pages(pool, self.swap_stage, dp[s:e])
-        if ncp:
-            src = torch.from_numpy(pn[L.copy_src:L.copy_src + ncp].astype(np.int64)).to(self.device)
-            dst = torch.from_numpy(pn[L.copy_dst:L.copy_dst + ncp].astype(np.int64)).to(self.device)
-            for pool in self.kv.pools:
-                ops.kv_page_copy(pool, src, dst)
+        nruns = int(hdr[HDR["num_move_runs"]])
+        runs = pn[L.move_runs:L.move_runs + 2 * nruns].reshape(-1, 2)
+        lists = {0: (L.copy_src, L.copy_dst), 1: (L.swap_out_dev, L.swap_out_host), 2: (L.swap_in_host, L.swap_in_dev)}
+        offs = {0: 0, 1: 0, 2: 0}
+        kv = self.kv
+        is_cuda = self.device.type == "cuda"
+        fast = is_cuda and (self.direct_swap or not (hdr[HDR["num_swap_out"]] or hdr[HDR["num_swap_in"]]))
+        if fast:
+            if hdr[HDR["num_swap_out"]] or hdr[HDR["num_swap_in"]]:      # the swap lists sit past the per-step copy
+                tail = slice(self.dev_words, L.total_words)
+                self.plan_dev_full[tail].copy_(self.plan_host[tail], non_blocking=True)
+                self.h2d_bytes += (L.total_words - self.dev_words) * 4
+            main = torch.cuda.current_stream()
+            side = self.swap_stream if self.direct_swap else main
+            if side is not main:
+                side.wait_stream(main)       # earlier steps wrote the pages that leave; the index lists were just copied
+            page_bytes = kv.pools[0].stride(0) * kv.pools[0].element_size()
+            scale_bytes = kv.scales[0].stride(0) * 4 if kv.scales is not None else 0
+            n_host = self.cfg.num_host_pages
+            with torch.cuda.stream(side):
+                for kind, count in runs:
+                    kind, count, o = int(kind), int(count), offs[int(kind)]
+                    src_off, dst_off = lists[kind]
+                    src_idx = self.plan_dev_full[src_off + o:src_off + o + count]
+                    dst_idx = self.plan_dev_full[dst_off + o:dst_off + o + count]
+                    if kind == 0:
+                        tables = [(self._kv_bases, self._kv_bases, page_bytes), (self._scale_bases, self._scale_bases, scale_bytes)]
+                        sc, dc = kv.num_pages, kv.num_pages
+                    elif kind == 1:
+                        tables = [(self._host_bases, self._kv_bases, page_bytes),
+                                  (self._host_scale_bases, self._scale_bases, scale_bytes)]
+                        sc, dc = kv.num_pages, n_host
+                    else:
+                        tables = [(self._kv_bases, self._host_bases, page_bytes),
+                                  (self._scale_bases, self._host_scale_bases, scale_bytes)]
+                        sc, dc = n_host, kv.num_pages
+                    for dst_b, src_b, nbytes in tables:
+                        if dst_b is None or src_b is None or nbytes == 0:
+                            continue
+                        ops.kv_move_pages(dst_b, src_b, len(kv.pools), src_idx, dst_idx, count, nbytes, sc, dc)
+                        self.swap_moves += 1
+                    offs[kind] += count
+            if side is not main:
+                main.wait_stream(side)
+            return
+        # CPU tensors, or swap space the device cannot address (allocator plugin): indexed copies, same order
+        for kind, count in runs:
+            kind, count, o = int(kind), int(count), offs[int(kind)]
+            src_off, dst_off = lists[kind]
+            src = torch.from_numpy(pn[src_off + o:src_off + o + count].astype(np.int64))
+            dst = torch.from_numpy(pn[dst_off + o:dst_off + o + count].astype(np.int64))
+            for li, pool in enumerate(kv.pools):
+                scales = kv.scales[li] if kv.scales is not None else None
+                if kind == 0:
+                    sd, dd = src.to(self.device), dst.to(self.device)
+                    pool[dd] = pool[sd]
+                    if scales is not None:
+                        scales[dd] = scales[sd]
+                elif kind == 1:
+                    sd = src.to(self.device)
+                    self.host_kv[li][dst] = pool[sd].cpu()
+                    if scales is not None:
+                        self.host_scales[li][dst] = scales[sd].cpu()
+                else:
+                    dd = dst.to(self.device)
+                    pool[dd] = self.host_kv[li][src].to(self.device)
+                    if scales is not None:
+                        scales[dd] = self.host_scales[li][src].to(self.device)
+            offs[kind] += count
 
     def _maybe_grow_kv(self) -> None:
         """Back more KV pages when the allocator runs low and the pool has address space left.  Addresses do not move,
@@ -253,6 +322,8 @@ class LLMEngine:
         if kv.num_pages > before:
             self.core.add_pages(kv.num_pages - before)
             self.num_pages = kv.num_pages
+            self.model.set_backed_pages(kv.num_pages)    # kernels bound page ids by the backed count
+            self.graphs.clear()                          # captured launches carry the old bound
             self.kv_lease.resize(kv.mapped_bytes())
             self.kv_grows += 1
 
@@ -260,7 +331,7 @@ class LLMEngine:
         if self.cfg.decode_splits > 0:
             return self.cfg.decode_splits
         ctas = nd * self.model.hkv
-        target = 2 * 148
+        target = 2 * (ops.num_sms() if self.device.type == "cuda" else 148)
         if ctas >= target or max_ctx < 256:
             return 1
         s = 1
@@ -410,6 +481,27 @@ class LLMEngine:
         self.comm.all_gather(self._gather_buf[: tp * chunk], self._shard_buf[:chunk])
         self.sampled_dev[:r].copy_(self._gather_buf[:r])
 
+    def _finish_device_step(self, r: int) -> None:
+        """The step's one synchronisation: the sampled tokens and the device status word cross to pinned host memory
+        behind the step's kernels, the host waits once, and a non-zero word (a bounded wait that ran out, a bad page or
+        token id, a peer that never signalled) becomes an exception *before* any token is committed -- the caller
+        fails the in-flight requests instead of streaming garbage."""
+        if r > 0:
+            self.sampled_host[:r].copy_(self.sampled_dev[:r], non_blocking=True)
+            self.d2h_bytes += r * 4
+        self.status_host.copy_(ops.status_word(self.device), non_blocking=True)
+        self.d2h_bytes += 4
+        torch.cuda.current_stream().synchronize()
+        v = int(self.status_host[0])
+        if v:
+            ops.status_word(self.device).zero_()
+            self.device_faults += 1
+            self.graphs.clear()
+            fc = getattr(self.model, "fused_comm", None)
+            if fc is not None and (v & (ops.STATUS_PEER_TIMEOUT | ops.STATUS_WAIT_TIMEOUT)):
+                fc.poison("device status word %d" % v)      # its counters are part-consumed: the group must be rebuilt
+            raise ops.status_error(v)
+
     def step(self) -> StepOutput:
         """Schedule, run and commit one engine step."""
         out = StepOutput()
@@ -445,7 +537,7 @@ class LLMEngine:
         if self.device.type == "cuda":
             self.plan_dev.copy_(self.plan_host[: self.dev_words], non_blocking=True)
             self.h2d_bytes += self.dev_words * 4
-        if hdr[HDR["num_swap_out"]] or hdr[HDR["num_swap_in"]] or hdr[HDR["num_copies"]]:
+        if hdr[HDR["num_move_runs"]]:
             self._page_moves(hdr)
         self._plan_verify_rows(si)
         if si.num_decode:
@@ -463,15 +555,13 @@ class LLMEngine:
         if r > 0:
             temps = self.plan_np[self.L.temperature:self.L.temperature + r].view(np.float32)
             if graphed:
-                self.sampled_host[:r].copy_(self.sampled_dev[:r], non_blocking=True)
-                torch.cuda.current_stream().synchronize()
-                self.d2h_bytes += r * 4
+                self._finish_device_step(r)
             elif sharded:
                 self.forward_and_sample_sharded(si, r, bool((temps <= 0).all()))
-                self.sampled_host[:r].copy_(self.sampled_dev[:r], non_blocking=True)
                 if self.device.type == "cuda":
-                    torch.cuda.current_stream().synchronize()
-                self.d2h_bytes += r * 4
+                    self._finish_device_step(r)
+                else:
+                    self.sampled_host[:r].copy_(self.sampled_dev[:r])
             elif self.device.type == "cuda":
                 if (temps <= 0).all():
                     ops.argmax(logits, out=self.sampled_dev[:r])
@@ -480,9 +570,7 @@ class LLMEngine:
                                self.uniform[:r], work=self.sample_work, out=self.sampled_dev[:r])
                 if self.tp > 1 and self.cfg.sync_sampled_tokens:
                     self.comm.broadcast(self.sampled_dev[:r], src=0)
-                self.sampled_host[:r].copy_(self.sampled_dev[:r], non_blocking=True)
-                torch.cuda.current_stream().synchronize()
-                self.d2h_bytes += r * 4
+                self._finish_device_step(r)
             else:
                 if (temps <= 0).all():
                     toks = ops.argmax(logits)
@@ -491,7 +579,7 @@ class LLMEngine:
                                       self.uniform[:r])
                 self.sampled_host[:r] = toks
         elif self.device.type == "cuda":
-            torch.cuda.current_stream().synchronize()
+            self._finish_device_step(0)
         if self.hidden_taps and r > 0:
             # embeddings: the final-normed hidden state of a tapped request's last prompt token
             seq_of_row = self.plan_np[self.L.logit_seq:self.L.logit_seq + r]

@@ -200,6 +200,7 @@ class KVCache:
                     self.scale_buffers.append(sb)
                     sb.view(torch.uint8).zero_()
                     self.scales.append(sb.span(torch.float32, (self.max_pages, hkv, 2)))
+            self._mark_backed()
             return
         self.max_pages = num_pages
         self.pools = [torch.zeros(num_pages, hkv, 2, ops.PAGE, cfg.head_dim, dtype=tdtype, device=device)
@@ -208,6 +209,11 @@ class KVCache:
         if quant:
             self.scales = [torch.zeros(num_pages, hkv, 2, dtype=torch.float32, device=device)
                            for _ in range(cfg.num_layers)]
+
+    def _mark_backed(self) -> None:
+        """Record the mapped page count on every pool tensor: kernels bound page ids by it (ops.backed_pages)."""
+        for t in self.pools:
+            t.backed_pages = self.num_pages
 
     @property
     def growable(self) -> bool:
@@ -233,6 +239,7 @@ class KVCache:
             if sb.mapped > old:
                 sb.view(torch.uint8, (sb.mapped - old,), old).zero_()
         self.num_pages = new_pages
+        self._mark_backed()
         return new_pages
 
     def mapped_bytes(self) -> int:
@@ -325,9 +332,10 @@ class DecoderModel:
         lib.ogb_decoder_set_split_scratch.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
         lib.ogb_decoder_set_split_scratch.restype = None
         inter_local = w.layers[0].gate_up_w.shape[0] // 2
-        ip = (ctypes.c_int * 14)(cfg.num_layers, cfg.hidden, self.hq, self.hkv, self.d, self.rotary_dim,
+        ip = (ctypes.c_int * 15)(cfg.num_layers, cfg.hidden, self.hq, self.hkv, self.d, self.rotary_dim,
                                  int(cfg.rotary_interleaved), inter_local, cfg.vocab, 2 * w.swiglu_half,
-                                 cfg.sliding_window, max_pages_per_seq, self.cos_sin.shape[0], self.tp)
+                                 cfg.sliding_window, max_pages_per_seq, self.cos_sin.shape[0], self.tp,
+                                 1 if ops.PREFILL_TC else 0)
         fp = (ctypes.c_float * 2)(cfg.rms_eps, self.scale)
         ptr = lambda t: 0 if t is None else t.data_ptr()
         g = [w.embed, w.final_norm, w.lm_head, self.cos_sin, self.x, self.h, self.qkv, self.attn, self.act, self.x_last,
@@ -338,8 +346,15 @@ class DecoderModel:
             for j, t in enumerate((lw.ln1, lw.qkv_w, lw.qkv_b, lw.o_w, lw.ln2, lw.gate_up_w, lw.down_w, kv.pools[i])):
                 lp[8 * i + j] = ptr(t)
         self._native_lib = lib
-        self.native = lib.ogb_decoder_create(ip, kv.pools[0].shape[0], fp, gp, lp)   # the pool's address range, backed or not yet
+        lib.ogb_decoder_set_num_pages.argtypes = [ctypes.c_void_p, ctypes.c_int64]
+        lib.ogb_decoder_set_num_pages.restype = None
+        self.native = lib.ogb_decoder_create(ip, kv.num_pages, fp, gp, lp)   # backed pages: ids beyond them are refused
         return bool(self.native)
+
+    def set_backed_pages(self, num_pages: int) -> None:
+        """The KV pool grew in place: the step executor bounds page ids by the new backed count from now on."""
+        if self.native:
+            self._native_lib.ogb_decoder_set_num_pages(self.native, int(num_pages))
 
     def _tp_step_args(self, rows: int):
         """(pointer to the 4 device-struct addresses for this step's row chunk, chunk) or (None, 0)."""

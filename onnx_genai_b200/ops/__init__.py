@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import collections
 import math
+import os
 
 import torch
 
@@ -45,6 +46,13 @@ def status_word(device=None) -> torch.Tensor:
     return w
 
 
+def status_error(v: int) -> "_native.KernelError":
+    """The exception for a non-zero status word, with its bits decoded."""
+    names = [n for b, n in ((1, "wait timeout"), (2, "index out of range"), (4, "bad argument"),
+                            (8, "peer wait timeout")) if v & b]
+    return _native.KernelError("device status word = %d (%s)" % (v, ", ".join(names)))
+
+
 def check_status(reset: bool = True) -> None:
     """Synchronising read of the status word; raises with the decoded bits when non-zero."""
     w = status_word()
@@ -52,13 +60,19 @@ def check_status(reset: bool = True) -> None:
     if v:
         if reset:
             w.zero_()
-        names = [n for b, n in ((1, "wait timeout"), (2, "index out of range"), (4, "bad argument"),
-                                (8, "peer wait timeout")) if v & b]
-        raise _native.KernelError("device status word = %d (%s)" % (v, ", ".join(names)))
+        raise status_error(v)
 
 
 def _ptr(t):
     return 0 if t is None else t.data_ptr()
+
+
+def backed_pages(pool) -> int:
+    """Pages of a KV pool that kernels may touch.  A growable pool is a view over a reserved address range whose tail
+    is not mapped yet; its owner records the mapped count on the tensor (``pool.backed_pages``) and every kernel
+    bounds page ids and slots by it, so an id inside the reserve but beyond the backing raises the status bit
+    instead of reaching unmapped memory."""
+    return int(getattr(pool, "backed_pages", pool.shape[0]))
 
 
 # ------------------------------------------------------------------------------------------
@@ -276,7 +290,7 @@ def rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim=
         return reference.rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim, interleaved)
     t = qkv.shape[0]
     assert qkv.is_contiguous() and positions.dtype == torch.int32 and slots.dtype == torch.int32
-    num_slots = pool.shape[0] * PAGE
+    num_slots = backed_pages(pool) * PAGE
     lib = _native.load()
     if kv_scales is None:
         rc = lib.ogb_rope_kv_append_bf16(qkv.data_ptr(), positions.data_ptr(), slots.data_ptr(), cos_sin.data_ptr(),
@@ -295,6 +309,10 @@ def rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim=
 # ------------------------------------------------------------------------------------------
 # attention
 # ------------------------------------------------------------------------------------------
+# OGB_PREFILL_TC=0 keeps prefill attention on the mma.sync kernel (comparison runs); default is the tcgen05 kernel
+PREFILL_TC = os.environ.get("OGB_PREFILL_TC", "1") != "0"
+
+
 def prefill_tiles(q_lens, block_m=64):
     """Host-side tile list for the prefill kernel: (tile_seq, tile_q0) int32 lists."""
     seqs, q0s = [], []
@@ -321,13 +339,24 @@ def paged_prefill(q, out, pool, page_table, ctx_len, cu_q, tile_seq, tile_q0, nu
         rc = _native.load().ogb_paged_prefill_q8(
             q.data_ptr(), out.data_ptr(), pool.data_ptr(), kv_scales.data_ptr(), kv_format(pool), page_table.data_ptr(), ctx_len.data_ptr(),
             cu_q.data_ptr(), tile_seq.data_ptr(), tile_q0.data_ptr(), int(num_tiles), ctx_len.numel(), page_table.shape[1],
-            pool.shape[0], hq, hkv, d, q.stride(0), out.stride(0), float(scale), status_word().data_ptr(), _stream())
+            backed_pages(pool), hq, hkv, d, q.stride(0), out.stride(0), float(scale), status_word().data_ptr(), _stream())
         _native.check(rc, "ogb_paged_prefill_q8")
         launch_counts["paged_prefill_fp8"] += 1
         return out
+    if PREFILL_TC and d in (64, 128) and out.stride(0) % 8 == 0:
+        # tcgen05 / TMEM kernel: S and O accumulators in tensor memory, K/V pages fed by TMA
+        rc = _native.load().ogb_paged_prefill_tc_bf16(
+            q.data_ptr(), out.data_ptr(), pool.data_ptr(), page_table.data_ptr(), ctx_len.data_ptr(), cu_q.data_ptr(),
+            tile_seq.data_ptr(), tile_q0.data_ptr(), int(num_tiles), ctx_len.numel(), q.shape[0], page_table.shape[1],
+            backed_pages(pool), hq, hkv, d, q.stride(0), out.stride(0), float(scale), int(window),
+            status_word().data_ptr(), _stream())
+        _native.check(rc, "ogb_paged_prefill_tc_bf16")
+        launch_counts["paged_prefill_tc"] += 1
+        launch_counts["paged_prefill"] += 1
+        return out
     rc = _native.load().ogb_paged_prefill_bf16(
         q.data_ptr(), out.data_ptr(), pool.data_ptr(), page_table.data_ptr(), ctx_len.data_ptr(), cu_q.data_ptr(),
-        tile_seq.data_ptr(), tile_q0.data_ptr(), int(num_tiles), ctx_len.numel(), page_table.shape[1], pool.shape[0],
+        tile_seq.data_ptr(), tile_q0.data_ptr(), int(num_tiles), ctx_len.numel(), page_table.shape[1], backed_pages(pool),
         hq, hkv, d, q.stride(0), out.stride(0), float(scale), int(window), status_word().data_ptr(), _stream())
     _native.check(rc, "ogb_paged_prefill_bf16")
     launch_counts["paged_prefill"] += 1
@@ -354,14 +383,14 @@ def paged_decode(q, out, pool, page_table, ctx_len, hq, hkv, d, scale=None, num_
     if kv_scales is not None:
         rc = _native.load().ogb_paged_decode_q8(
             q.data_ptr(), out.data_ptr(), pool.data_ptr(), kv_scales.data_ptr(), kv_format(pool), page_table.data_ptr(), ctx_len.data_ptr(), n,
-            page_table.shape[1], pool.shape[0], hq, hkv, d, q.stride(0), out.stride(0), float(scale), int(num_splits),
+            page_table.shape[1], backed_pages(pool), hq, hkv, d, q.stride(0), out.stride(0), float(scale), int(num_splits),
             _ptr(part_o), _ptr(part_ml), status_word().data_ptr(), _stream())
         _native.check(rc, "ogb_paged_decode_q8")
         launch_counts["paged_decode_fp8"] += 1
         return out
     rc = _native.load().ogb_paged_decode_bf16(
         q.data_ptr(), out.data_ptr(), pool.data_ptr(), page_table.data_ptr(), ctx_len.data_ptr(), n,
-        page_table.shape[1], pool.shape[0], hq, hkv, d, q.stride(0), out.stride(0), float(scale), int(num_splits),
+        page_table.shape[1], backed_pages(pool), hq, hkv, d, q.stride(0), out.stride(0), float(scale), int(num_splits),
         _ptr(part_o), _ptr(part_ml), int(window), status_word().data_ptr(), _stream())
     _native.check(rc, "ogb_paged_decode_bf16")
     launch_counts["paged_decode"] += 1
@@ -453,3 +482,20 @@ def kv_scatter_pages(pool, staging, pages):
                                              _page_bytes(pool), _stream())
     _native.check(rc, "ogb_kv_scatter_pages")
     launch_counts["kv_scatter_pages"] += 1
+
+
+def kv_move_pages(dst_bases, src_bases, layers, src_pages, dst_pages, n, page_bytes, src_count, dst_count):
+    """Move ``n`` pages of every layer in one launch: ``dst_bases[l] + dst_pages[i]*page_bytes <- src_bases[l] +
+    src_pages[i]*page_bytes``.  The base tables are int64 device tensors of addresses (device memory or pinned host
+    memory), the index lists int32 device tensors (views of the step plan).  Ids outside ``[0, count)`` raise the
+    status bit and are skipped."""
+    lib = _native.load()
+    done = 0
+    while done < n:
+        m = min(n - done, 65535)
+        rc = lib.ogb_kv_move_pages(dst_bases.data_ptr(), src_bases.data_ptr(), int(layers),
+                                   src_pages.data_ptr() + 4 * done, dst_pages.data_ptr() + 4 * done, m, int(page_bytes),
+                                   int(src_count), int(dst_count), status_word().data_ptr(), _stream())
+        _native.check(rc, "ogb_kv_move_pages")
+        launch_counts["kv_move_pages"] += 1
+        done += m

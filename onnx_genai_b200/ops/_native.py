@@ -29,6 +29,7 @@ _SIGNATURES = {
     "ogb_rope_kv_append_bf16": ([P, P, P, P, P, I, I, I, I, I, I, I, L, I, P, P], I),
     "ogb_rope_kv_append_fp8": ([P, P, P, P, P, P, I, I, I, I, I, I, I, L, I, P, P], I),
     "ogb_paged_prefill_bf16": ([P, P, P, P, P, P, P, P, I, I, I, L, I, I, I, I, I, F, I, P, P], I),
+    "ogb_paged_prefill_tc_bf16": ([P, P, P, P, P, P, P, P, I, I, I, I, L, I, I, I, I, I, F, I, P, P], I),
     "ogb_paged_decode_bf16": ([P, P, P, P, P, I, I, L, I, I, I, I, I, F, I, P, P, I, P, P], I),
     "ogb_paged_decode_fp8": ([P, P, P, P, P, P, I, I, L, I, I, I, I, I, F, I, P, P, P, P], I),
     "ogb_paged_prefill_fp8": ([P, P, P, P, P, P, P, P, P, I, I, I, L, I, I, I, I, I, F, P, P], I),
@@ -41,6 +42,7 @@ _SIGNATURES = {
     "ogb_kv_page_copy": ([P, P, P, I, L, P], I),
     "ogb_kv_gather_pages": ([P, P, P, I, L, P], I),
     "ogb_kv_scatter_pages": ([P, P, P, I, L, P], I),
+    "ogb_kv_move_pages": ([P, P, I, P, P, I, L, L, L, P, P], I),
 }
 
 

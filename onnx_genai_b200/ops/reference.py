@@ -207,8 +207,8 @@ def sample_weights(logits_row, temperature):
     return torch.floor(e.double() * 1073741824.0 + 0.5).clamp_max(1073741823.0).to(torch.int64)
 
 
-def sample_from_weights(w, top_k, top_p, min_p, u):
-    """Exact integer statement of the sampler: thresholds keep ties; draw walks tokens in index order."""
+def sample_threshold(w, top_k, top_p, min_p):
+    """Weight threshold that top-k, then top-p, then min-p leave: a token survives iff its weight is >= the result."""
     vocab = w.numel()
     thr = 1
     total = int(w.sum())
@@ -225,12 +225,23 @@ def sample_from_weights(w, top_k, top_p, min_p, u):
         thr = max(thr, int(vals[pos]))
     if min_p > 0.0:
         thr = max(thr, int(torch.tensor(min(min_p, 1.0), dtype=torch.float32) * 1073741824.0))
-    kept = torch.where(w >= thr, w, torch.zeros_like(w))
+    return thr
+
+
+def sample_draw_target(kept, u):
+    """(target mass, total mass) of the draw ``u`` over the surviving weights ``kept``."""
     final_total = int(kept.sum())
-    if final_total == 0:
-        return int(torch.argmax(w))
     uu = min(max(float(torch.tensor(u, dtype=torch.float32)), 0.0), 0.99999994)
-    target = min(int(uu * float(final_total)), final_total - 1)
+    return min(int(uu * float(final_total)), final_total - 1), final_total
+
+
+def sample_from_weights(w, top_k, top_p, min_p, u):
+    """Exact integer statement of the sampler: thresholds keep ties; draw walks tokens in index order."""
+    thr = sample_threshold(w, top_k, top_p, min_p)
+    kept = torch.where(w >= thr, w, torch.zeros_like(w))
+    if int(kept.sum()) == 0:
+        return int(torch.argmax(w))
+    target, _ = sample_draw_target(kept, u)
     csum = torch.cumsum(kept, 0)
     return int(torch.searchsorted(csum, torch.tensor(target, dtype=csum.dtype), right=True))
 

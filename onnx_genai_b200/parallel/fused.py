@@ -88,6 +88,8 @@ class FusedComm:
         self.device = torch.device(device)
         self.lib = _lib()
         self.ready = False
+        self.failed: str | None = None     # set by poison(): why the region's counters can no longer be trusted
+        self._last_slot = -1
         self.calls = 0
         if hidden and max_tokens:
             self.setup(hidden, max_tokens)
@@ -103,7 +105,10 @@ class FusedComm:
         return self.base.all_gather(out, t)
 
     def barrier(self):
-        return self.base.barrier()
+        """All ranks meet with their streams drained up to here, so the next exchange may use either slot."""
+        out = self.base.barrier()
+        self._last_slot = -1
+        return out
 
     def min_int(self, v):
         return self.base.min_int(v)
@@ -229,6 +234,30 @@ class FusedComm:
         self._structs[key] = hit
         return hit
 
+    def poison(self, why: str) -> None:
+        """Mark the group unusable after a device-side wait ran out.  The arrival counters of the exchange are then
+        part-consumed (the kernel that gives up does not reset them), so a later exchange would count stale arrivals.
+        This rank's counters are cleared so its memory is tidy, but the peers' state is unknown: every further fused
+        call raises until the group is torn down and set up again."""
+        self.failed = why
+        self.ready = False
+        try:
+            cnt = torch.as_tensor(_CudaArray(self.local_ptr + self.off_cnt, (SLOTS * MAX_GROUPS + 64,), "<u4"), device=self.device)
+            cnt.view(torch.int32).zero_()
+        except Exception:
+            pass
+
+    def _guard(self, rows: int, slot: int) -> None:
+        if self.failed is not None:
+            raise RuntimeError(f"fused tensor-parallel group is unusable ({self.failed}); rebuild the process group")
+        if rows > self.max_tokens:
+            raise ValueError(f"{rows} rows exceed the {self.max_tokens}-row symmetric region")
+        # the consumer of a slot resets the slot's counters at its end, which is only safe because no rank can produce
+        # into the same slot again before it has passed the other slot's exchange: uses must alternate
+        if slot == self._last_slot:
+            raise RuntimeError(f"slot {slot} used twice in a row: row-parallel exchanges must alternate between the two slots")
+        self._last_slot = slot
+
     def chunk_for(self, rows: int) -> int:
         tp = self.world
         return max(32, ((rows + tp - 1) // tp + 31) // 32 * 32)
@@ -236,6 +265,7 @@ class FusedComm:
     # -- the fused row-parallel projection -----------------------------------------------------
     def row_parallel(self, a, w, rows: int, slot: int):
         """x[:rows] += sum over ranks of a @ w^T, on every rank (x = the symmetric residual stream)."""
+        self._guard(rows, slot)
         chunk = self.chunk_for(rows)
         sc, rd = self._get_structs(slot, chunk)
         st = ops.status_word(self.device).data_ptr()
@@ -261,6 +291,7 @@ class FusedComm:
 
     def reduce_partial(self, rows: int, slot: int):
         """x[:rows] += sum over ranks of the staged partials (same exchange kernel as :meth:`row_parallel`)."""
+        self._guard(rows, slot)
         chunk = self.chunk_for(rows)
         sc, rd = self._get_structs(slot, chunk)
         st = ops.status_word(self.device).data_ptr()

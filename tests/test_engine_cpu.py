@@ -209,3 +209,39 @@ def test_fp8_codec_chunked_append_equals_token_by_token(dtype):
     got = deq.permute(0, 3, 2, 1, 4).reshape(3 * ref.PAGE, 2, hkv, d)[:t]
     rel = (got - want).abs() / (want.abs() + 0.05 * want.abs().max())
     assert float(rel.mean()) < 0.05
+
+
+def test_page_moves_are_replayed_in_the_order_they_were_decided():
+    """A page that a swapped-out victim frees may be handed out as the target of a later copy-on-write copy in the
+    same step; the plan's run list keeps the two lists in decision order."""
+    core = Core(CoreConfig(num_pages=6, num_host_pages=16, max_seqs=4, max_tokens_per_step=64, max_pages_per_seq=8,
+                           preempt="swap", enable_prefix_cache=False))
+    L = core.layout
+    plan = np.zeros(L.total_words, dtype=np.int32)
+    a = core.add_request(list(range(24)), 40)            # 2 pages, second half full
+    assert core.build_step(plan.ctypes.data) == 24
+    core.commit_step(np.array([5], dtype=np.int32).ctypes.data, 1)
+    b = core.fork(a)                                     # shares both pages
+    c = core.add_request(list(range(50, 98)), 40)        # 3 pages -> with the copy nothing is left
+    n = core.build_step(plan.ctypes.data)
+    hdr = plan[:32]
+    nruns = int(hdr[12])
+    runs = plan[L.move_runs:L.move_runs + 2 * nruns].reshape(-1, 2).tolist()
+    kinds = [k for k, _ in runs]
+    assert n > 0 and nruns >= 1 and kinds[0] == 0        # the copy-on-write copy of the forked page comes first
+    assert sum(cnt for k, cnt in runs if k == 0) == hdr[5]
+    assert sum(cnt for k, cnt in runs if k == 1) == hdr[6]
+    assert sum(cnt for k, cnt in runs if k == 2) == hdr[7]
+    assert all(k1 != k2 for k1, k2 in zip(kinds, kinds[1:]))   # runs are maximal
+
+
+def test_swap_preemption_with_quantised_pages_moves_the_scales_too(weights):
+    """One-byte KV pages keep one scale per (page, head, K|V); a page that comes back from swap space must bring its
+    scales, or attention dequantises with the previous owner's."""
+    rng = np.random.default_rng(14)
+    prompts = [rng.integers(0, CFG.vocab, size=30).tolist() for _ in range(6)]
+    tight = _engine(weights, num_pages=14, num_host_pages=64, preempt="swap", enable_prefix_cache=False, kv_dtype="int8")
+    roomy = _engine(weights, num_pages=128, enable_prefix_cache=False, kv_dtype="int8")
+    got = tight.generate(prompts, 20)
+    assert tight.core.num_preemptions > 0 and tight.host_scales is not None
+    assert got == roomy.generate(prompts, 20)

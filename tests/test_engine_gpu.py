@@ -86,7 +86,7 @@ def test_greedy_gpu_matches_baseline_library_path():
         finally:
             ops.set_baseline(False)
     err = float((outs[False] - outs[True]).norm() / outs[True].norm())
-    assert err < 2e-2, err
+    assert err < 3e-2, err        # two bf16 pipelines that round at different points (the bound of GPU-vs-CPU logits above)
 
 
 def test_int4_package_runs_in_kernel_dequant_on_gpu(tmp_path):
@@ -281,3 +281,38 @@ def test_shared_kv_proposer_reads_target_pages_on_the_device():
     qh = q[0, : m.hq * m.d].float().view(m.hq, m.d)
     want = torch.cat([torch.softmax((qh[h] @ k_all[h // g].T) * m.scale, -1) @ v_all[h // g] for h in range(m.hq)])
     assert float((out[0].float() - want).norm() / want.norm()) < 2e-2
+
+
+@pytest.mark.parametrize("kv", ["bf16", "fp8"])
+def test_swap_preemption_and_cow_fork_on_the_device_keep_tokens(kv):
+    """A pool too small for the batch forces swap preemption; a fork forces a copy-on-write page copy.  Pages (and, for
+    one-byte pages, their scale rows) travel through pinned host memory by the swap kernels on the side stream;
+    tokens must equal those of an unpressured engine."""
+    w = random_weights(CFG128, "cuda", seed=9, std=0.05)
+    rng = np.random.default_rng(7)
+    prompts = [rng.integers(0, CFG128.vocab, size=30).astype(np.int32) for _ in range(6)]
+    mk = lambda **kw: LLMEngine(EngineConfig(model=CFG128, max_seqs=8, max_tokens_per_step=64, max_seq_len=256,
+                                             enable_prefix_cache=False, kv_dtype=kv, **kw), weights=w, device="cuda")
+    roomy = mk(num_pages=128)
+    want = roomy.generate(prompts, 20)
+    tight = mk(num_pages=14, num_host_pages=64, preempt="swap")
+    moves0 = ops.launch_counts["kv_move_pages"]
+    got = tight.generate(prompts, 20)
+    ops.check_status()
+    assert tight.core.num_preemptions > 0 and tight.direct_swap
+    assert ops.launch_counts["kv_move_pages"] > moves0
+    assert got == want
+    # fork: parent and child share pages until the first divergent token, then the written page is copied
+    eng = mk(num_pages=64)
+    sid = eng.add_request(prompts[0], 12)
+    eng.step()                                  # prefill: 30 tokens, the second page is half full
+    child = eng.core.fork(sid)
+    eng.stats[child] = type(eng.stats[sid])()
+    outs = {sid: [], child: []}
+    copies0 = eng.swap_moves
+    while eng.core.has_work:
+        for s, tok, fin in eng.step().events:
+            outs[s].append(tok)
+    ops.check_status()
+    assert eng.swap_moves > copies0             # the copy-on-write copy ran on the device
+    assert outs[sid][1:] == outs[child] == want[0][1:len(outs[child]) + 1]

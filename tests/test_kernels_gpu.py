@@ -125,11 +125,13 @@ def test_paged_decode(hq, hkv, d):
         assert _rel_err(out, want) < 2e-2, splits
 
 
+@pytest.mark.parametrize("tc", [True, False])                                                   # tcgen05 kernel / mma.sync kernel
 @pytest.mark.parametrize("hq,hkv,d", [(28, 4, 128), (14, 2, 64), (4, 2, 128), (4, 1, 64)])   # 64-, 32- and 16-row CTAs
-def test_paged_prefill(hq, hkv, d):
+def test_paged_prefill(hq, hkv, d, tc, monkeypatch):
+    monkeypatch.setattr(ops, "PREFILL_TC", tc)
     torch.manual_seed(5)
-    q_lens = [1, 5, 64, 65, 200, 130]
-    past = [0, 11, 0, 64, 37, 512]
+    q_lens = [1, 5, 64, 65, 200, 130, 257, 128]
+    past = [0, 11, 0, 64, 37, 512, 2200, 128]          # up to 20 key blocks per tile: every ring slot is reused many times
     ctx = [a + b for a, b in zip(q_lens, past)]
     n = len(ctx)
     pool, table = _make_paged(n, ctx, hkv, d, seed=1)
@@ -141,11 +143,15 @@ def test_paged_prefill(hq, hkv, d):
     tile_seq = torch.tensor(ts, dtype=torch.int32, device=DEV)
     tile_q0 = torch.tensor(tq, dtype=torch.int32, device=DEV)
     out = torch.zeros(t, hq * d, device=DEV, dtype=torch.bfloat16)
+    before = ops.launch_counts["paged_prefill_tc"]
     ops.paged_prefill(q, out, pool, table, ctx_t, cu, tile_seq, tile_q0, len(ts), hq, hkv, d)
     torch.cuda.synchronize()
     ops.check_status()
+    assert (ops.launch_counts["paged_prefill_tc"] > before) == tc
     want = ref.paged_attention(q, pool, table, ctx_t, cu, hq, hkv, d)
     assert _rel_err(out, want) < 2e-2
+    for s0, s1 in zip(cu[:-1].tolist(), cu[1:].tolist()):      # every sequence on its own: a short one must not hide in the norm
+        assert _rel_err(out[s0:s1], want[s0:s1]) < 3e-2, (s0, s1)
     # sliding window
     out.zero_()
     ops.paged_prefill(q, out, pool, table, ctx_t, cu, tile_seq, tile_q0, len(ts), hq, hkv, d, window=48)
@@ -203,10 +209,22 @@ def test_sampler_matches_integer_oracle():
             w = ref.sample_weights(logits[r].cpu(), t)
             want = ref.sample_from_weights(w, int(top_k[r]), float(top_p[r]), float(min_p[r]), float(u[r]))
             if int(got[r]) != want:
-                # __expf differs from torch.exp in the last ulp: allow a neighbouring survivor only when
-                # the draw lands within 1e-5 of a CDF boundary
-                kept = w.double() / w.sum()
-                assert abs(int(got[r]) - want) < vocab and kept[int(got[r])] > 0, (r, int(got[r]), want)
+                # The device computes its weights with __expf, torch with exp: single weights differ in the last
+                # place, so the two cumulative sums differ by ~1e-6 of the total.  A different token is accepted
+                # only when (a) it survives the *filtered* distribution (weight at or above the oracle's
+                # threshold, give or take that rounding) and (b) the draw falls within 1e-4 of the total mass of
+                # the token's own interval of the filtered CDF.  A sampler whose top-k / top-p / min-p filter is
+                # wrong fails (a); one that draws from the wrong place fails (b).
+                g = int(got[r])
+                thr = ref.sample_threshold(w, int(top_k[r]), float(top_p[r]), float(min_p[r]))
+                assert int(w[g]) >= thr * (1 - 1e-4), ("filtered-out token sampled", r, g, int(w[g]), thr)
+                kept = torch.where(w >= thr, w, torch.zeros_like(w))
+                target, total = ref.sample_draw_target(kept, float(u[r]))
+                csum = torch.cumsum(kept, 0)
+                lo = int(csum[g - 1]) if g > 0 else 0
+                hi = int(csum[g]) if int(kept[g]) > 0 else lo + int(w[g])
+                tol = max(2, int(1e-4 * total))
+                assert lo - tol <= target <= hi + tol, ("draw far from the sampled token's interval", r, g, want, lo, target, hi)
 
 
 def test_sampler_distribution():

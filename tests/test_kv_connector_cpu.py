@@ -91,3 +91,35 @@ def test_host_tier_is_accounted_and_reclaimed_under_pressure(tmp_path):
         eng.generate(rng.integers(0, CFG.vocab, size=500).tolist(), opt)
     again = eng.generate(prompt, opt)
     assert again.token_ids == first.token_ids and eng.kv_offload.tokens_restored >= 256
+
+
+def test_restore_into_a_pool_that_runs_out_mid_chunk_leaves_no_unfilled_page_in_the_cache(tmp_path):
+    """Adoption publishes pages under their prefix hashes before they are filled.  When the pool cannot hold a whole
+    chunk, the pages adopted for the partial chunk must leave the prefix cache again: a later request with that prefix
+    must not attach to K/V nobody wrote."""
+    weights = random_weights(CFG, "cpu", seed=11, std=0.3, dtype=torch.float32)
+    rng = np.random.default_rng(3)
+    prompt = rng.integers(0, CFG.vocab, size=600).tolist()
+    opt = GenerateOptions(max_new_tokens=4, ignore_eos=True)
+    big = _engine(weights)
+    conn = LocalTieredConnector(str(tmp_path / "kv"))
+    big.attach_kv_connector(conn)
+    first = big.generate(prompt, opt)
+    assert big.kv_offload.chunks_stored == 2
+    conn.flush()
+    small = _engine(weights, num_pages=24)                 # one chunk is 16 pages: the second cannot be adopted whole
+    small.attach_kv_connector(LocalTieredConnector(str(tmp_path / "kv")))
+    restored = small.kv_offload.restore(prompt)
+    assert restored == 256                                 # the whole first chunk, nothing of the second
+    served = small.llm.core.prefix_peek(prompt)
+    assert len(served) == 16                               # no page of the partial chunk stays published
+    assert small.llm.core.num_free_pages == 24             # and they are free again (cached pages count as free)
+    # a wrong-sized blob ends the run before anything is adopted
+    other = _engine(weights)
+    bad = LocalTieredConnector(str(tmp_path / "bad"))
+    for key in chunk_keys(prompt[:512], other.kv_offload.tag if getattr(other, "kv_offload", None) else ""):
+        bad.store(key, b"x" * 10)
+    other.attach_kv_connector(bad)
+    for key in chunk_keys(prompt[:512], other.kv_offload.tag):
+        bad.store(key, b"x" * 10)
+    assert other.kv_offload.restore(prompt) == 0 and len(other.llm.core.prefix_peek(prompt)) == 0

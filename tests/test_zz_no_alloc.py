@@ -58,3 +58,5 @@ def test_no_alloc_sampler_rejects_sizes_beyond_its_array():
     assert rc == -3 and int(out[0]) == -1                       # refused: nothing was launched
     rc, _ = _call(lib, logits, p, 1, 262145)
     assert rc == -3
+    rc, _ = _call(lib, logits, p, 1, 128)                        # a row stride (64) shorter than the vocabulary
+    assert rc == -3
