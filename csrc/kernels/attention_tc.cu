@@ -6,19 +6,23 @@
 //
 //   one CTA   = 128 query rows of one head (two of the scheduler's 64-row tiles) against the
 //               sequence's keys, walked in blocks of BN = 128 tokens (8 pages)
-//   warp 0    : TMA producer.  Q comes from the packed qkv rows through a 2-D tensor map; every K and V
-//               page half (16 tokens x 64 dims = 2 KB, 128-byte swizzled) is one TMA box, landed so
-//               that a block is [dim half][token][64 dims]: K is then a K-major UMMA operand and V an
-//               MN-major one (64-dim blocks BN*128 bytes apart, 8-token groups 1024 bytes apart)
-//   warp 1    : one elected lane issues  S_j = Q K_j^T  (smem x smem -> TMEM, fp32) and
-//               O += P_j V_j (TMEM x smem -> TMEM); S is double-buffered, and S_{j+1} is issued before
-//               P_j V_j so that it runs under the softmax of block j
-//   warps 2-5 : softmax, one thread per query row (a TMEM lane): tcgen05.ld of the row of S, scale to
-//               the log2 domain, mask (causal, context end, sliding window), running max and sum,
-//               P as packed bf16 back into TMEM with tcgen05.st.  The running max is only raised when
-//               it grows by more than 2^8 (the accumulator is then rescaled in TMEM); otherwise the
-//               stale max is kept, which leaves the quotient O / l exact and saves the rescale.
-//   epilogue  : the same warps read O, divide by l and store bf16 rows.
+//   warps 0,1 : TMA producers (warp 0: Q and K, warp 1: V).  Q comes from the packed qkv rows through a 2-D
+//               tensor map; every K and V page half (16 tokens x 64 dims = 2 KB, 128-byte swizzled) is one
+//               TMA box, landed so that a block is [dim half][token][64 dims]: K is then a K-major UMMA
+//               operand and V an MN-major one (64-dim blocks BN*128 bytes apart, 8-token groups 1024 bytes apart)
+//   warp 2    : one elected lane issues  S_j = Q K_j^T  (smem x smem -> TMEM, fp32) and
+//               O_g += P_j V_j (TMEM x smem -> TMEM) in the order S_j, P_{j-1}V_{j-1}, S_{j+1}, ...
+//   warps 3-6 : softmax group A, warps 7-10 : softmax group B.  Even key blocks belong to A, odd ones to B;
+//               each group has its own score buffer, running maximum, running sum and accumulator O_g, so the
+//               two groups never wait for each other: while one waits for its tensor-memory loads, stores and
+//               barriers, the other one computes.  One thread owns one query row (a TMEM lane): tcgen05.ld of
+//               the row of S in two passes (maximum, then exponentials), masking (causal, context end, sliding
+//               window), P as packed bf16 written with tcgen05.st over the columns of S it came from.  The
+//               running maximum is only raised when it grows by more than 2^24 (the accumulator is then
+//               rescaled in TMEM); otherwise the stale maximum is kept, which leaves O / l exact, and blocks
+//               that need no mask take a single pass.
+//   epilogue  : the groups exchange their (m, l) and one half of their accumulators through shared memory;
+//               each merges and stores one half of the output columns (bf16).
 // Every wait is bounded and watches a CTA-wide abort flag; on expiry the status word gets
 // kStatusWaitTimeout, the CTA drains, frees its TMEM and returns.  Page ids are bounds-checked.
 #include <mutex>
@@ -29,8 +33,14 @@
 
 namespace ogb {
 
-constexpr int kFaThreads = 192;
 constexpr int kFaBM = 128;
+constexpr int kFaFirstSoftmaxWarp = 3;                 // warp 0: K (and Q) producer, 1: V producer, 2: MMA issuer
+constexpr int kFaSoftmaxWarps = 8;                     // two groups of four warps (one warp per TMEM lane quarter)
+constexpr int kFaThreads = (kFaFirstSoftmaxWarp + kFaSoftmaxWarps) * 32;
+// The running maximum of a row is re-centred only when a block's maximum exceeds it by more than this many
+// powers of two.  Until then the stale maximum is used: probabilities are then at most 2^24, far inside the
+// range of bf16 and of the fp32 sums, and the quotient O / l does not depend on the centre.
+constexpr float kFaRecentre = 24.f;
 
 template <int D, int BN>
 struct FaCfg {
@@ -40,13 +50,16 @@ struct FaCfg {
   static constexpr int kHalfStrideQ = kFaBM * 128;     // bytes between the 64-dim halves of Q
   static constexpr int kHalfStrideKv = BN * 128;       // bytes between the 64-dim halves of a K / V block
   static constexpr int kStages = 2;
-  static constexpr int kSmemBytes = kQBytes + kStages * 2 * kKvBytes + 1024 /*alignment*/ + 512 /*barriers*/;
-  // TMEM columns: O | S0 | S1 | P0 | P1
+  static constexpr int kSmemBytes = kQBytes + kStages * 2 * kKvBytes + 1024 /*alignment*/ + 512 /*barriers*/ +
+                                    2 * kFaBM * 8 /*(m, l) of both groups*/;
+  // TMEM columns: O_A | O_B | S0 (P0 over its first 64 columns) | S1 (P1)
   static constexpr int kColO = 0;
-  static constexpr int kColS = D;
-  static constexpr int kColP = D + 2 * BN;
+  static constexpr int kColS = 2 * D;
   static constexpr int kTmemCols = 512;
-  static_assert(D + 2 * BN + BN <= 512, "TMEM budget");
+  static constexpr int kXPitch = (D / 2 + 4) * 4;      // bytes per row of the accumulator halves exchanged in the epilogue
+  static_assert(2 * D + 2 * BN <= 512, "TMEM budget");
+  static_assert(BN == 128, "a row of scores is processed as two 64-column chunks");
+  static_assert(2 * kFaBM * kXPitch <= kStages * 2 * kKvBytes, "the exchange slab reuses the K/V rings");
 };
 
 OGB_DEVICE void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -99,8 +112,9 @@ OGB_DEVICE bool fa_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag
 }
 
 // Optional stamps: when p.dbg is set, the CTA (dbg_tile, head 0) accumulates, per role, the nanoseconds spent
-// in each kind of wait.  Slots: 0 start, 1 end, 2 setup done, 3 blocks; producer 4 wait-empty, 5 issue;
-// MMA 6 k_full, 7 s_free, 8 p_full, 9 v_full; softmax (row 0) 10 s_full, 11 pv_done, 12 rescales, 13 math, 14 epilogue.
+// in each kind of wait.  Slots: 0 start, 1 end, 2 setup done, 3 blocks; K producer 4 wait-empty, 5 issue;
+// MMA 6 k_full, 8 p_full, 9 v_full; softmax (row 0 of group A) 10 s_full, 11 pv_done, 12 rescales, 13 math,
+// 14 epilogue.
 struct FaStamp {
   unsigned long long* d;
   uint64_t t;
@@ -111,8 +125,73 @@ struct FaStamp {
 struct FaBars {
   uint64_t q_full;
   uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
-  uint64_t s_full[2], s_free[2], p_full[2], pv_done[2];
+  uint64_t s_full[2], p_full[2], pv_done[2];
 };
+
+// exponentials of one 64-column chunk of a score row: load, mask, exp2((s - m) * scale) as packed bf16 pairs
+// written over the chunk's first 32 columns' worth of the P area; returns the chunk's sum
+template <int BN>
+OGB_DEVICE float fa_exp_chunk(uint32_t s_addr, uint32_t p_addr, int hi, int lo, float scale, float neg_m) {
+  uint32_t s[64];
+  {
+    uint32_t(&c0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[0]);
+    uint32_t(&c1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[32]);
+    tmem_ld_32x32(s_addr, c0);
+    tmem_ld_32x32(s_addr + 32, c1);
+  }
+  tmem_ld_wait();
+  float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int c = 0; c < 32; ++c) {
+    const float v0 = (2 * c <= hi && 2 * c >= lo) ? __uint_as_float(s[2 * c]) : -INFINITY;
+    const float v1 = (2 * c + 1 <= hi && 2 * c + 1 >= lo) ? __uint_as_float(s[2 * c + 1]) : -INFINITY;
+    const float e0 = exp2f(fmaf(v0, scale, neg_m));
+    const float e1 = exp2f(fmaf(v1, scale, neg_m));
+    sum[c & 3] += e0 + e1;
+    s[c] = pack_bf16(e0, e1);          // pair c lands in word c <= 2c: in place
+  }
+  {
+    uint32_t(&c0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[0]);
+    tmem_st_32x32(p_addr, c0);
+  }
+  return (sum[0] + sum[1]) + (sum[2] + sum[3]);
+}
+
+// Fast pass over 32 columns that need no mask: exponentials against the current running maximum, packed into
+// `pk` (16 words), the raw maximum folded into `mx`, the sum returned.  `cur` holds the columns; `nxt` (when
+// non-null address) is loaded for the following call while this one computes.
+OGB_DEVICE float fa_fast32(const uint32_t (&cur)[32], uint32_t (&pk)[16], float scale, float neg_m, float (&mx)[2]) {
+  float sum[2] = {0.f, 0.f};
+#pragma unroll
+  for (int c = 0; c < 16; ++c) {
+    const float v0 = __uint_as_float(cur[2 * c]), v1 = __uint_as_float(cur[2 * c + 1]);
+    mx[0] = fmaxf(mx[0], v0);
+    mx[1] = fmaxf(mx[1], v1);
+    const float e0 = exp2f(fmaf(v0, scale, neg_m));
+    const float e1 = exp2f(fmaf(v1, scale, neg_m));
+    sum[c & 1] += e0 + e1;
+    pk[c] = pack_bf16(e0, e1);
+  }
+  return sum[0] + sum[1];
+}
+
+OGB_DEVICE float fa_max_chunk(uint32_t s_addr, int hi, int lo) {
+  uint32_t s[64];
+  {
+    uint32_t(&c0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[0]);
+    uint32_t(&c1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[32]);
+    tmem_ld_32x32(s_addr, c0);
+    tmem_ld_32x32(s_addr + 32, c1);
+  }
+  tmem_ld_wait();
+  float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int c = 0; c < 64; ++c) {
+    const float v = (c <= hi && c >= lo) ? __uint_as_float(s[c]) : -INFINITY;
+    mx[c & 3] = fmaxf(mx[c & 3], v);
+  }
+  return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+}
 
 template <int D, int BN>
 __global__ void __launch_bounds__(kFaThreads, 1)
@@ -127,12 +206,13 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
   FaBars* bars = reinterpret_cast<FaBars*>(sV + Cfg::kStages * Cfg::kKvBytes);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float2* x_ml = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(bars) + 512);   // [group][row] (m, l)
 
   // ---- which rows ----
   const int tile = blockIdx.x;
   if (tile >= p.num_tiles) return;
   const int q0 = p.tile_q0[tile];
-  if ((q0 & 127) != 0) return;                          // the 64-row tile at q0 - 64 ... covered by its 128-row neighbour
+  if ((q0 & 127) != 0) return;                          // the odd 64-row tiles are served by their 128-row neighbours
   const int head = blockIdx.y;
   const int kvh = head / p.group;
   const int seq = p.tile_seq[tile];
@@ -159,7 +239,6 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
       mbar_init(&bars->v_full[i], 1);
       mbar_init(&bars->v_empty[i], 1);
       mbar_init(&bars->s_full[i], 1);
-      mbar_init(&bars->s_free[i], 4);
       mbar_init(&bars->p_full[i], 4);
       mbar_init(&bars->pv_done[i], 1);
     }
@@ -168,7 +247,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
     tma_prefetch_desc(&q_map);
     tma_prefetch_desc(&kv_map);
   }
-  if (warp == 1) {
+  if (warp == 2) {
     tmem_alloc(tmem_slot, Cfg::kTmemCols);
     tmem_relinquish();
   }
@@ -178,17 +257,24 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
   const uint32_t tmem_base = *tmem_slot;
   if (dbg && threadIdx.x == 0) dbg[2] = global_timer_ns() - dbg[0];
 
-  if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
+  if (warp < 2) {
+    // ------------------------------ TMA producers: warp 0 streams Q and K, warp 1 streams V ------------------------------
     if (lane == 0) {
       bool ok = true;
-      FaStamp st{dbg, 0};
-      mbar_expect_tx(&bars->q_full, Cfg::kQBytes);
+      FaStamp st{warp == 0 ? dbg : nullptr, 0};
+      const bool is_v = (warp == 1);
+      if (!is_v) {
+        mbar_expect_tx(&bars->q_full, Cfg::kQBytes);
 #pragma unroll
-      for (int h = 0; h < Cfg::kHalves; ++h)
-        tma_load_2d(sQ + h * Cfg::kHalfStrideQ, &q_map, &bars->q_full, head * D + h * 64, q_begin + q0);
+        for (int h = 0; h < Cfg::kHalves; ++h)
+          tma_load_2d(sQ + h * Cfg::kHalfStrideQ, &q_map, &bars->q_full, head * D + h * 64, q_begin + q0);
+      }
       const int n_pages = (ctx + kPageTokens - 1) / kPageTokens;
       const int* table = p.page_table + static_cast<size_t>(seq) * p.max_pages;
+      uint64_t* full = is_v ? bars->v_full : bars->k_full;
+      uint64_t* empty = is_v ? bars->v_empty : bars->k_empty;
+      uint8_t* ring = is_v ? sV : sK;
+      const int row_add = is_v ? kPageTokens : 0;
       for (int it = 0; it < nblk && ok; ++it) {
         const int b = b_begin + it;
         const int buf = it & 1;
@@ -204,40 +290,28 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
             atomicOr(p.status, kStatusIndexOutOfRange);
             page = 0;
           }
-          row_of_page[i] = static_cast<int>(((page * p.hkv + kvh) * 2) * kPageTokens);
+          row_of_page[i] = static_cast<int>(((page * p.hkv + kvh) * 2) * kPageTokens) + row_add;
         }
         st.begin();
-        if (!fa_wait(&bars->k_empty[buf], par ^ 1, abort_flag)) { ok = false; break; }
+        if (!fa_wait(&empty[buf], par ^ 1, abort_flag)) { ok = false; break; }
         st.end(4);
         st.begin();
-        mbar_expect_tx(&bars->k_full[buf], Cfg::kKvBytes);
-        uint8_t* dk = sK + buf * Cfg::kKvBytes;
+        mbar_expect_tx(&full[buf], Cfg::kKvBytes);
+        uint8_t* dst = ring + buf * Cfg::kKvBytes;
 #pragma unroll
         for (int i = 0; i < BN / kPageTokens; ++i) {
 #pragma unroll
           for (int h = 0; h < Cfg::kHalves; ++h)
-            tma_load_2d(dk + h * Cfg::kHalfStrideKv + (i << 11), &kv_map, &bars->k_full[buf], h * 64, row_of_page[i]);
-        }
-        st.end(5);
-        st.begin();
-        if (!fa_wait(&bars->v_empty[buf], par ^ 1, abort_flag)) { ok = false; break; }
-        st.end(4);
-        st.begin();
-        mbar_expect_tx(&bars->v_full[buf], Cfg::kKvBytes);
-        uint8_t* dv = sV + buf * Cfg::kKvBytes;
-#pragma unroll
-        for (int i = 0; i < BN / kPageTokens; ++i) {
-#pragma unroll
-          for (int h = 0; h < Cfg::kHalves; ++h)
-            tma_load_2d(dv + h * Cfg::kHalfStrideKv + (i << 11), &kv_map, &bars->v_full[buf], h * 64,
-                        row_of_page[i] + kPageTokens);
+            tma_load_2d(dst + h * Cfg::kHalfStrideKv + (i << 11), &kv_map, &full[buf], h * 64, row_of_page[i]);
         }
         st.end(5);
       }
       if (!ok) { atomicOr(p.status, kStatusWaitTimeout); *abort_flag = 1; }
     }
-  } else if (warp == 1) {
+  } else if (warp == 2) {
     // ------------------------------ MMA issuer ------------------------------
+    // tcgen05.mma instructions of one thread execute in issue order, so S_{j+2}, issued after P_j V_j, cannot
+    // overwrite the columns of P_j (which live inside score buffer j & 1) before that product has read them.
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(kFaBM, BN);
       constexpr uint32_t idesc_o = make_idesc_bf16(kFaBM, D) | (1u << 16);   // B (= V) is MN-major
@@ -254,11 +328,12 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
         st.end(9);
         tc_fence_after();
         const uint32_t sv = smem_u32(sV + buf * Cfg::kKvBytes);
-        const uint32_t p_addr = tmem_base + Cfg::kColP + buf * (BN / 2);
+        const uint32_t p_addr = tmem_base + Cfg::kColS + buf * BN;            // P_t: first BN/2 columns of score buffer t & 1
+        const uint32_t o_addr = tmem_base + Cfg::kColO + buf * D;            // accumulator of the group that owns block t
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k) {
           const uint64_t db = make_mnmajor_sw128_desc(sv + k * 2048, Cfg::kHalfStrideKv);
-          umma_f16_ts(tmem_base + Cfg::kColO, p_addr + k * 8, db, idesc_o, (t | k) != 0 ? 1u : 0u);
+          umma_f16_ts(o_addr, p_addr + k * 8, db, idesc_o, (t >= 2 || k > 0) ? 1u : 0u);
         }
         umma_commit(&bars->v_empty[buf]);
         umma_commit(&bars->pv_done[buf]);
@@ -270,9 +345,6 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
         st.begin();
         if (!fa_wait(&bars->k_full[buf], par, abort_flag)) { ok = false; break; }
         st.end(6);
-        st.begin();
-        if (!fa_wait(&bars->s_free[buf], par ^ 1, abort_flag)) { ok = false; break; }
-        st.end(7);
         tc_fence_after();
         const uint32_t sq = smem_u32(sQ);
         const uint32_t sk = smem_u32(sK + buf * Cfg::kKvBytes);
@@ -292,141 +364,177 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
       if (!ok) { atomicOr(p.status, kStatusWaitTimeout); *abort_flag = 1; }
     }
   } else {
-    // ------------------------------ softmax / correction / epilogue ------------------------------
+    // ------------------------------ softmax groups / correction / epilogue ------------------------------
     const int q = warp & 3;                              // TMEM lane quarter this warp may touch
+    const int g = (warp - kFaFirstSoftmaxWarp) >> 2;     // group: 0 takes the even key blocks, 1 the odd ones
     const int row = q * 32 + lane;                       // query row of this thread
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    const uint32_t s_addr = lane_base + Cfg::kColS + g * BN;
+    const uint32_t o_addr = lane_base + Cfg::kColO + g * D;
     const int qpos = pos0 + row;
-    float m_run = -INFINITY, l_run = 0.f;
+    const int hi_abs = min(qpos, ctx - 1);
+    const int lo_abs = (p.window > 0) ? (qpos - p.window + 1) : 0;
+    float m_run = -INFINITY, l_run = 0.f;                // running maximum in the scaled (log2) domain
     bool ok = true;
-    FaStamp st{(row == 0) ? dbg : nullptr, 0};
-    for (int it = 0; it < nblk; ++it) {
-      const int buf = it & 1;
+    FaStamp st{(row == 0 && g == 0) ? dbg : nullptr, 0};
+    for (int it = g; it < nblk && ok; it += 2) {
       const uint32_t par = static_cast<uint32_t>((it >> 1) & 1);
       st.begin();
-      if (!__all_sync(0xffffffffu, fa_wait(&bars->s_full[buf], par, abort_flag))) { ok = false; break; }
+      ok = __all_sync(0xffffffffu, fa_wait(&bars->s_full[g], par, abort_flag));
       st.end(10);
+      if (!ok) break;
       st.begin();
       tc_fence_after();
-      uint32_t s[BN];
+      const int col0 = (b_begin + it) * BN;
+      bool done = false;
+      // Fast path: every column of the block is visible to every row of the tile and the group already has a
+      // running maximum.  One pass: exponentials against the running maximum, kept in registers until the
+      // block's own maximum is known; they are stored unless some row's maximum grew past the re-centring
+      // threshold, in which case the block takes the two-pass path below (the scores are still intact).
+      const bool plain = (it >= 2) && (col0 + BN - 1 <= pos0) && (col0 + BN <= ctx) &&
+                         (p.window <= 0 || col0 >= pos0 + kFaBM - p.window);
+      if (plain) {
+        const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
+        uint32_t pk[BN / 2];
+        float mx2[2] = {-INFINITY, -INFINITY};
+        float sum = 0.f;
 #pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t(&chunk)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[32 * c]);
-        tmem_ld_32x32(lane_base + Cfg::kColS + buf * BN + 32 * c, chunk);
-      }
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->s_free[buf]);
-      // scale into the log2 domain, mask, row maximum
-      const int kv_base = (b_begin + it) * BN;
-      const bool need_mask = (kv_base + BN - 1 > pos0) || (kv_base + BN > ctx) || (p.window > 0);
-      float mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < BN; ++c) {
-        float v = __uint_as_float(s[c]) * p.scale_log2e;
-        if (need_mask) {
-          const int col = kv_base + c;
-          const bool valid = (col <= qpos) && (col < ctx) && (p.window <= 0 || col > qpos - p.window);
-          if (!valid) v = -INFINITY;
-        }
-        s[c] = __float_as_uint(v);
-        mx = fmaxf(mx, v);
-      }
-      const float m_new = fmaxf(m_run, mx);
-      const bool raise = (m_new > m_run + 8.f) || (m_run == -INFINITY && m_new > -INFINITY);
-      if (it == 0) {
-        m_run = m_new;
-      } else if (__any_sync(0xffffffffu, raise)) {
-        // the accumulator must hold every earlier block before it is rescaled
-        const int t = it - 1;
-        if (!__all_sync(0xffffffffu, fa_wait(&bars->pv_done[t & 1], static_cast<uint32_t>((t >> 1) & 1), abort_flag))) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        if (st.d) st.d[12] += 1;
-        float alpha = 1.f;
-        if (raise) {
-          alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
-          m_run = m_new;
-          l_run *= alpha;
-        }
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld_32x32(lane_base + Cfg::kColO + 32 * c, o);
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t a[32];
+          tmem_ld_32x32(s_addr + 32 * c, a);
           tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-          tmem_st_32x32(lane_base + Cfg::kColO + 32 * c, o);
+          sum += fa_fast32(a, *reinterpret_cast<uint32_t(*)[16]>(&pk[16 * c]), p.scale_log2e, neg_m, mx2);
         }
-        tmem_st_wait();
-      }
-      const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-      float sum = 0.f;
-      // the packed probabilities overwrite the scores in place (pair c lands in word c <= 2c)
-#pragma unroll
-      for (int c = 0; c < BN / 2; ++c) {
-        const float e0 = exp2f(__uint_as_float(s[2 * c]) - m_use);
-        const float e1 = exp2f(__uint_as_float(s[2 * c + 1]) - m_use);
-        sum += e0 + e1;
-        s[c] = pack_bf16(e0, e1);
-      }
-      l_run += sum;
-      st.end(13);
-      // the P buffer was last read by the PV product of block it - 2
-      if (it >= 2) {
-        const int t = it - 2;
-        st.begin();
-        if (!__all_sync(0xffffffffu, fa_wait(&bars->pv_done[t & 1], static_cast<uint32_t>((t >> 1) & 1), abort_flag))) {
-          ok = false;
-          break;
+        const float mx = fmaxf(mx2[0], mx2[1]) * p.scale_log2e;
+        const bool grew = (mx > m_run + kFaRecentre);
+        if (!__any_sync(0xffffffffu, grew)) {
+          l_run += sum;
+          tmem_st_32x32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
+          tmem_st_32x32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[32]));
+          done = true;
         }
-        st.end(11);
-        tc_fence_after();
       }
+      if (!done) {
+        // pass 1: row maximum (columns outside [lo, hi] are masked; both bounds relative to the chunk)
+        const float mx = fmaxf(fa_max_chunk(s_addr, hi_abs - col0, lo_abs - col0),
+                               fa_max_chunk(s_addr + 64, hi_abs - col0 - 64, lo_abs - col0 - 64)) * p.scale_log2e;   // scale > 0
+        const float m_new = fmaxf(m_run, mx);
+        const bool raise = (m_new > m_run + kFaRecentre) || (m_run == -INFINITY && m_new > -INFINITY);
+        if (it < 2) {
+          m_run = m_new;
+        } else if (__any_sync(0xffffffffu, raise)) {
+          // the accumulator must hold every earlier block of this group before it is rescaled
+          const int t = it - 2;
+          st.end(13);
+          st.begin();
+          ok = __all_sync(0xffffffffu, fa_wait(&bars->pv_done[g], static_cast<uint32_t>((t >> 1) & 1), abort_flag));
+          st.end(11);
+          if (!ok) break;
+          st.begin();
+          tc_fence_after();
+          if (st.d) st.d[12] += 1;
+          float alpha = 1.f;
+          if (raise) {
+            alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
+            m_run = m_new;
+            l_run *= alpha;
+          }
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32(o_addr + 32 * c, o);
+            tmem_ld_wait();
 #pragma unroll
-      for (int c = 0; c < BN / 64; ++c) {
-        uint32_t(&chunk)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[32 * c]);
-        tmem_st_32x32(lane_base + Cfg::kColP + buf * (BN / 2) + 32 * c, chunk);
+            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+            tmem_st_32x32(o_addr + 32 * c, o);
+          }
+          tmem_st_wait();
+        }
+        // pass 2: exponentials; P_it overwrites the first 64 columns of the score buffer, 32 at a time, each
+        // chunk only after the scores it covers have been read
+        const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
+        l_run += fa_exp_chunk<BN>(s_addr, s_addr, hi_abs - col0, lo_abs - col0, p.scale_log2e, neg_m);
+        l_run += fa_exp_chunk<BN>(s_addr + 64, s_addr + 32, hi_abs - col0 - 64, lo_abs - col0 - 64, p.scale_log2e, neg_m);
       }
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->p_full[buf]);
+      if (lane == 0) mbar_arrive(&bars->p_full[g]);
+      st.end(13);
     }
-    if (ok) {
-      const int t = nblk - 1;
+    // last block of this group: its product must have landed before the accumulator is read
+    int last = nblk - 1;
+    if ((last & 1) != g) --last;
+    if (ok && last >= 0) {
       st.begin();
-      ok = __all_sync(0xffffffffu, fa_wait(&bars->pv_done[t & 1], static_cast<uint32_t>((t >> 1) & 1), abort_flag));
+      ok = __all_sync(0xffffffffu, fa_wait(&bars->pv_done[g], static_cast<uint32_t>((last >> 1) & 1), abort_flag));
       st.end(11);
     }
+    if (!ok && lane == 0) {
+      atomicOr(p.status, kStatusWaitTimeout);
+      *abort_flag = 1;
+    }
     st.begin();
-    if (ok) {
+    // ---- merge the two groups: each finalises one half of the columns ----
+    constexpr int OC = D / 2;
+    uint8_t* xo = sK;                                    // [group][row][OC floats], pitch kXPitch; the rings are idle by now
+    asm volatile("bar.sync 1, 256;" ::: "memory");       // every tensor-core read of the rings has completed
+    const bool live = ok && last >= 0;                   // this group accumulated something
+    if (live) {
       tc_fence_after();
-      const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
-      __nv_bfloat16* dst = p.out + static_cast<size_t>(q_begin + q0 + row) * p.o_stride + head * D;
+      // the half of O_g that the other group finalises
+      float* dst = reinterpret_cast<float*>(xo + (static_cast<size_t>(g) * kFaBM + row) * Cfg::kXPitch);
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < OC / 32; ++c) {
         uint32_t o[32];
-        tmem_ld_32x32(lane_base + Cfg::kColO + 32 * c, o);
+        tmem_ld_32x32(o_addr + (g ^ 1) * OC + 32 * c, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int v = 0; v < 8; ++v)
+          *reinterpret_cast<uint4*>(dst + 32 * c + 4 * v) = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+      }
+    }
+    x_ml[g * kFaBM + row] = make_float2(live ? m_run : -INFINITY, live ? l_run : 0.f);
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    {
+      const float2 other = x_ml[(g ^ 1) * kFaBM + row];
+      const float m_mine = live ? m_run : -INFINITY;
+      const float m_all = fmaxf(m_mine, other.x);
+      const float w_mine = (m_mine == -INFINITY) ? 0.f : exp2f(m_mine - m_all);
+      const float w_other = (other.x == -INFINITY) ? 0.f : exp2f(other.x - m_all);
+      const float l_tot = (live ? l_run : 0.f) * w_mine + other.y * w_other;
+      const float inv = (l_tot > 0.f) ? 1.f / l_tot : 0.f;
+      const float a = w_mine * inv, b = w_other * inv;
+      const float* src = reinterpret_cast<const float*>(xo + (static_cast<size_t>(g ^ 1) * kFaBM + row) * Cfg::kXPitch);
+      __nv_bfloat16* out = p.out + static_cast<size_t>(q_begin + q0 + row) * p.o_stride + head * D + g * OC;
+#pragma unroll
+      for (int c = 0; c < OC / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32(o_addr + g * OC + 32 * c, o);
         tmem_ld_wait();
         if (row < rows) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
+            float r[8];
+            const uint4 x0 = *reinterpret_cast<const uint4*>(src + 32 * c + 8 * v);
+            const uint4 x1 = *reinterpret_cast<const uint4*>(src + 32 * c + 8 * v + 4);
+            const uint32_t xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              // a group without blocks holds an uninitialised accumulator: select, never multiply by zero
+              const float mine = (a > 0.f) ? __uint_as_float(o[8 * v + j]) * a : 0.f;
+              const float oth = (b > 0.f) ? __uint_as_float(xs[j]) * b : 0.f;
+              r[j] = mine + oth;
+            }
             uint4 w;
-            w.x = pack_bf16(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
-            w.y = pack_bf16(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
-            w.z = pack_bf16(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
-            w.w = pack_bf16(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + 32 * c + 8 * v) = w;
+            w.x = pack_bf16(r[0], r[1]);
+            w.y = pack_bf16(r[2], r[3]);
+            w.z = pack_bf16(r[4], r[5]);
+            w.w = pack_bf16(r[6], r[7]);
+            *reinterpret_cast<uint4*>(out + 32 * c + 8 * v) = w;
           }
         }
       }
-    } else if (lane == 0) {
-      atomicOr(p.status, kStatusWaitTimeout);
-      *abort_flag = 1;
     }
     st.end(14);
   }
@@ -440,7 +548,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
     while (global_timer_ns() - t0 < 200000ull) { __nanosleep(1000); }
   }
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 2) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
