@@ -93,11 +93,19 @@ extern "C" void ogb_decoder_set_split_scratch(void* plan, float* part_o, float* 
 extern "C" int ogb_gemm_bf16_scatter(const void* A, const void* W, int M, int N, int K, int lda, int ldw, const void* sc,
                                      int bn, int* status, void* stream_);
 extern "C" int ogb_tp_reduce_bcast(const void* rp, int rows, int n, int chunk, int tp, int nvls, int* status, void* stream);
+extern "C" int ogb_tp_exchange_norm(const void* rp, const void* norm_w, float eps, int rows, int n, int chunk, int tp, int nvls,
+                                    int* status, void* stream);
+extern "C" int ogb_tp_wait_ready(const void* rp, int rows, int* status, void* stream);
+extern "C" int ogb_gemm_bf16_wait(const void* A, const void* W, void* C, const void* bias, const void* residual, void* C_f32,
+                                  int M, int N, int K, int lda, int ldw, int ldc, int ldr, int epilogue, int bn,
+                                  uint32_t* a_ready, uint32_t* a_done, unsigned long long a_wait_ns, int* status, void* stream_);
 
-// tp > 1: `tp_structs` = {scatter slot 0, reduce slot 0, scatter slot 1, reduce slot 1} device structs, then one
-// word that is non-zero when the reduce structs carry NVSwitch multicast pointers
-// for this step's row chunk; the residual stream p->x then lives in the peer-mapped region and the
-// row-parallel projections run as GEMM-scatter + reduce/broadcast instead of a residual epilogue.
+// tp > 1: `tp_structs` = {scatter slot 0, reduce slot 0, scatter slot 1, reduce slot 1} device structs for this
+// step's row chunk, one word that is non-zero when the reduce structs carry NVSwitch multicast pointers, then the
+// local addresses of the two slots' per-tile ready counters.  The residual stream p->x is then owned by rows
+// (each rank keeps its own chunk), p->h lives in the peer-mapped region, and a row-parallel projection is
+//   GEMM with the scatter epilogue  ->  exchange (reduce-scatter + residual + RMSNorm + all-gather of h)
+// followed by a column-parallel GEMM whose TMA producer waits tile by tile for the rows of h.
 extern "C" int ogb_decoder_step(void* plan, const int* token_ids, const int* positions, const int* slots,
                                 const int* ctx_len, const int* page_table, const int* cu_q, const int* tile_seq,
                                 const int* tile_q0, const int* logit_rows, int T, int Nd, int Np, int num_tiles, int R,
@@ -107,11 +115,15 @@ extern "C" int ogb_decoder_step(void* plan, const int* token_ids, const int* pos
   if (p->tp != 1 && tp_structs == nullptr) return -10;
   const void* sc[2] = {nullptr, nullptr};
   const void* rd[2] = {nullptr, nullptr};
+  uint32_t* ready[2] = {nullptr, nullptr};      // per-tile ready counters of the two slots; [k] + 64 is the slot's GEMM-done word
   int nvls = 0;
-  if (p->tp != 1) {
+  const bool tp = p->tp != 1;
+  if (tp) {
     sc[0] = reinterpret_cast<const void*>(tp_structs[0]); rd[0] = reinterpret_cast<const void*>(tp_structs[1]);
     sc[1] = reinterpret_cast<const void*>(tp_structs[2]); rd[1] = reinterpret_cast<const void*>(tp_structs[3]);
     nvls = tp_structs[4] != 0 ? 1 : 0;
+    ready[0] = reinterpret_cast<uint32_t*>(tp_structs[5]);
+    ready[1] = reinterpret_cast<uint32_t*>(tp_structs[6]);
   }
   const int hid = p->hidden, d = p->d, hq = p->hq, hkv = p->hkv;
   const int qkv_n = (hq + 2 * hkv) * d;
@@ -119,11 +131,15 @@ extern "C" int ogb_decoder_step(void* plan, const int* token_ids, const int* pos
   char* qkv_prefill = static_cast<char*>(p->qkv) + static_cast<size_t>(Nd) * qkv_n * 2;
   char* attn_prefill = static_cast<char*>(p->attn) + static_cast<size_t>(Nd) * attn_n * 2;
   STEP_CHECK(ogb_embedding_bf16(token_ids, p->embed, p->x, T, hid, p->vocab, p->status, stream));
+  if (tp) {
+    // every rank embeds and norms all rows once; from here on a rank only updates the residual rows it owns
+    STEP_CHECK(ogb_rmsnorm_bf16(p->x, nullptr, p->layers[0].ln1, p->h, T, hid, hid, hid, p->eps, stream));
+  }
   for (int l = 0; l < p->num_layers; ++l) {
     const LayerPtrs& L = p->layers[l];
-    STEP_CHECK(ogb_rmsnorm_bf16(p->x, nullptr, L.ln1, p->h, T, hid, hid, hid, p->eps, stream));
-    STEP_CHECK(ogb_gemm_bf16(p->h, L.qkv_w, p->qkv, L.qkv_b, nullptr, nullptr, T, qkv_n, hid, hid, hid, qkv_n, 0, 0, 0,
-                             p->status, stream));
+    if (!tp) STEP_CHECK(ogb_rmsnorm_bf16(p->x, nullptr, L.ln1, p->h, T, hid, hid, hid, p->eps, stream));
+    STEP_CHECK(ogb_gemm_bf16_wait(p->h, L.qkv_w, p->qkv, L.qkv_b, nullptr, nullptr, T, qkv_n, hid, hid, hid, qkv_n, 0, 0, 0,
+                                  (tp && l > 0) ? ready[1] : nullptr, (tp && l > 0) ? ready[1] + 64 : nullptr, 0, p->status, stream));
     STEP_CHECK(ogb_rope_kv_append_bf16(p->qkv, positions, slots, p->cos_sin, L.kv_pool, T, hq, hkv, d, p->rotary_dim,
                                        p->interleaved, 16, p->num_pages * 16, p->max_pos, p->status, stream));
     if (Nd > 0) {
@@ -142,31 +158,42 @@ extern "C" int ogb_decoder_step(void* plan, const int* token_ids, const int* pos
                                           hkv, d, qkv_n, attn_n, p->scale, p->window, p->status, stream));
       }
     }
-    if (p->tp == 1) {
+    if (!tp) {
       STEP_CHECK(ogb_gemm_bf16(p->attn, L.o_w, p->x, nullptr, p->x, nullptr, T, hid, attn_n, attn_n, attn_n, hid, hid, 1, 0,
                                p->status, stream));
+      STEP_CHECK(ogb_rmsnorm_bf16(p->x, nullptr, L.ln2, p->h, T, hid, hid, hid, p->eps, stream));
     } else {
       STEP_CHECK(ogb_gemm_bf16_scatter(p->attn, L.o_w, T, hid, attn_n, attn_n, attn_n, sc[0], 0, p->status, stream));
-      STEP_CHECK(ogb_tp_reduce_bcast(rd[0], T, hid, tp_chunk, p->tp, nvls, p->status, stream));
+      STEP_CHECK(ogb_tp_exchange_norm(rd[0], L.ln2, p->eps, T, hid, tp_chunk, p->tp, nvls, p->status, stream));
     }
-    STEP_CHECK(ogb_rmsnorm_bf16(p->x, nullptr, L.ln2, p->h, T, hid, hid, hid, p->eps, stream));
-    STEP_CHECK(ogb_gemm_bf16(p->h, L.gate_up_w, p->act, nullptr, nullptr, nullptr, T, 2 * p->inter_local, hid, hid, hid,
-                             p->inter_local, 0, 2, p->swiglu_bn, p->status, stream));
-    if (p->tp == 1) {
+    STEP_CHECK(ogb_gemm_bf16_wait(p->h, L.gate_up_w, p->act, nullptr, nullptr, nullptr, T, 2 * p->inter_local, hid, hid, hid,
+                                  p->inter_local, 0, 2, p->swiglu_bn, tp ? ready[0] : nullptr, tp ? ready[0] + 64 : nullptr, 0,
+                                  p->status, stream));
+    if (!tp) {
       STEP_CHECK(ogb_gemm_bf16(p->act, L.down_w, p->x, nullptr, p->x, nullptr, T, hid, p->inter_local, p->inter_local,
                                p->inter_local, hid, hid, 1, 0, p->status, stream));
     } else {
       STEP_CHECK(ogb_gemm_bf16_scatter(p->act, L.down_w, T, hid, p->inter_local, p->inter_local, p->inter_local, sc[1], 0,
                                        p->status, stream));
-      STEP_CHECK(ogb_tp_reduce_bcast(rd[1], T, hid, tp_chunk, p->tp, nvls, p->status, stream));
+      const void* next_norm = (l + 1 < p->num_layers) ? p->layers[l + 1].ln1 : p->final_norm;
+      STEP_CHECK(ogb_tp_exchange_norm(rd[1], next_norm, p->eps, T, hid, tp_chunk, p->tp, nvls, p->status, stream));
     }
   }
   if (R > 0) {
-    // rows that sample: x_last[r] = x[logit_rows[r]] (the embedding gather doubles as a row gather)
-    STEP_CHECK(ogb_embedding_bf16(logit_rows, p->x, p->x_last, R, hid, T, p->status, stream));
-    STEP_CHECK(ogb_rmsnorm_bf16(p->x_last, nullptr, p->final_norm, p->h_last, R, hid, hid, hid, p->eps, stream));
+    if (!tp) {
+      // rows that sample: x_last[r] = x[logit_rows[r]] (the embedding gather doubles as a row gather)
+      STEP_CHECK(ogb_embedding_bf16(logit_rows, p->x, p->x_last, R, hid, T, p->status, stream));
+      STEP_CHECK(ogb_rmsnorm_bf16(p->x_last, nullptr, p->final_norm, p->h_last, R, hid, hid, hid, p->eps, stream));
+    } else {
+      // the last exchange already applied the final norm: wait for every owner's rows, then gather the rows that sample
+      STEP_CHECK(ogb_tp_wait_ready(rd[1], T, p->status, stream));
+      STEP_CHECK(ogb_embedding_bf16(logit_rows, p->h, p->h_last, R, hid, T, p->status, stream));
+    }
     STEP_CHECK(ogb_gemm_bf16(p->h_last, p->lm_head, p->logits, nullptr, nullptr, nullptr, R, p->vocab, hid, hid, hid,
                              p->vocab, 0, 0, 0, p->status, stream));
+  } else if (tp) {
+    // nothing samples in this step, but the slot's counters must still be consumed before the next step reuses them
+    STEP_CHECK(ogb_tp_wait_ready(rd[1], T, p->status, stream));
   }
   return 0;
 }

@@ -61,7 +61,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                          __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias,
                          const __nv_bfloat16* residual, float* __restrict__ C_f32, int M, int N, int K, int ldc, int ldr,
                          int* status, const TpScatter* __restrict__ sc, const int* __restrict__ group_tab,
-                         const int* __restrict__ group_mtiles) {
+                         const int* __restrict__ group_mtiles, uint32_t* a_ready, uint32_t* a_done, unsigned long long a_wait_ns) {
   using Cfg = GemmCfg<BN>;
   // the kernel declares no static shared memory, so the dynamic window starts at the 1024-byte aligned
   // base the 128-byte swizzle needs
@@ -114,11 +114,29 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      unsigned long long seen_ready = 0ull;     // m-tiles (of the first 64) whose rows are known to have arrived
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int mt = tile % m_tiles;
         const int n0 = (tile / m_tiles) * BN;
         const int m0 = group_tab != nullptr ? group_tab[4 * mt + 1] : mt * kBM;
         const int b_row = group_tab != nullptr ? group_tab[4 * mt] * N + n0 : n0;   // expert e's weights start at row e*N
+        if (a_ready != nullptr && !(mt < 64 && ((seen_ready >> mt) & 1ull))) {
+          // The rows of A are delivered by other GPUs (the all-gather half of a tensor-parallel exchange): every 8
+          // rows that land bump the tile's counter.  Wait, bounded, until the whole tile is here; the loads below
+          // go through the async proxy, so a proxy fence follows the acquire.
+          const uint32_t want = static_cast<uint32_t>((min(kBM, M - m0) + 7) / 8);
+          const uint64_t lim = a_wait_ns ? a_wait_ns : kWaitLimitNs;
+          const uint64_t t0 = global_timer_ns();
+          uint32_t spins = 0, got = 0;
+          while (true) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(a_ready + mt) : "memory");
+            if (got >= want) break;
+            if (((++spins) & 0x3f) == 0 && global_timer_ns() - t0 > lim) { ok = false; break; }   // bounded by the timer
+          }
+          if (!ok) { atomicOr(status, kStatusPeerTimeout); break; }
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+          if (mt < 64) seen_ready |= 1ull << mt;
+        }
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::kStage;
@@ -381,6 +399,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
+  if (a_ready != nullptr && threadIdx.x == 0) {
+    // The consumer clears what it consumed: the last CTA to finish zeroes the tiles' ready counters.  The next
+    // arrivals on them belong to an exchange that needs this rank's next row-parallel GEMM, which is launched
+    // after this kernel, so no arrival can be lost.
+    __threadfence();
+    if (atomicAdd(a_done, 1u) == gridDim.x - 1) {
+      for (int i = 0; i < m_tiles; ++i) a_ready[i] = 0;
+      *a_done = 0;
+      __threadfence();
+    }
+  }
 }
 
 // ----------------------------------------------------------------------------------------
@@ -438,7 +467,8 @@ template <int BN, int EPI>
 static int launch_gemm(const void* A, const void* W, void* C, const void* bias, const void* residual, void* C_f32, int M,
                        int N, int K, int lda, int ldw, int ldc, int ldr, int* status, cudaStream_t stream,
                        const TpScatter* sc = nullptr, const int* group_tab = nullptr, const int* group_mtiles = nullptr,
-                       int experts = 1, int max_mtiles = 0) {
+                       int experts = 1, int max_mtiles = 0, uint32_t* a_ready = nullptr, uint32_t* a_done = nullptr,
+                       unsigned long long a_wait_ns = 0) {
   using Cfg = GemmCfg<BN>;
   CUtensorMap ta, tb;
   int rc = make_tmap_bf16_2d(&ta, A, M, K, lda, kBM, kBK);
@@ -456,7 +486,8 @@ static int launch_gemm(const void* A, const void* W, void* C, const void* bias, 
   if (grid > ogb_num_sms()) grid = ogb_num_sms();
   gemm_bf16_tcgen05_kernel<BN, EPI><<<grid, EPI == kEpiScatter ? kGemmThreadsScatter : kGemmThreads, Cfg::kSmemBytes, stream>>>(
       ta, tb, static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(bias),
-      static_cast<const __nv_bfloat16*>(residual), static_cast<float*>(C_f32), M, N, K, ldc, ldr, status, sc, group_tab, group_mtiles);
+      static_cast<const __nv_bfloat16*>(residual), static_cast<float*>(C_f32), M, N, K, ldc, ldr, status, sc, group_tab, group_mtiles,
+      a_ready, a_done, a_wait_ns);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -464,20 +495,36 @@ static int launch_gemm(const void* A, const void* W, void* C, const void* bias, 
 
 using namespace ogb;
 
-#define OGB_GEMM_DISPATCH_BN(EPI)                                                                                       \
-  switch (bn) {                                                                                                         \
-    case 32: return launch_gemm<32, EPI>(A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, status, stream);  \
-    case 64: return launch_gemm<64, EPI>(A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, status, stream);  \
-    case 128: return launch_gemm<128, EPI>(A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, status, stream); \
-    case 192: return launch_gemm<192, EPI>(A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, status, stream); \
-    case 256: return launch_gemm<256, EPI>(A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, status, stream); \
-    default: return -2;                                                                                                 \
+#define OGB_GEMM_ARGS A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, status, stream, nullptr, nullptr, nullptr, 1, 0, a_ready, a_done, a_wait_ns
+#define OGB_GEMM_DISPATCH_BN(EPI)                              \
+  switch (bn) {                                                \
+    case 32: return launch_gemm<32, EPI>(OGB_GEMM_ARGS);       \
+    case 64: return launch_gemm<64, EPI>(OGB_GEMM_ARGS);       \
+    case 128: return launch_gemm<128, EPI>(OGB_GEMM_ARGS);     \
+    case 192: return launch_gemm<192, EPI>(OGB_GEMM_ARGS);     \
+    case 256: return launch_gemm<256, EPI>(OGB_GEMM_ARGS);     \
+    default: return -2;                                        \
   }
+
+// The GEMM whose A rows arrive from other GPUs: `a_ready` holds one counter per 128-row tile of A that grows by one
+// for every 8 rows delivered (tp_exchange_norm_kernel); the TMA producer waits for a tile's counter, at most
+// `a_wait_ns` nanoseconds (0 = the library default), before it loads the tile; the last CTA to finish zeroes the
+// counters again (`a_done` is a zero-initialised word it counts finished CTAs in).  a_ready == nullptr: no wait.
+extern "C" int ogb_gemm_bf16_wait(const void* A, const void* W, void* C, const void* bias, const void* residual, void* C_f32,
+                                  int M, int N, int K, int lda, int ldw, int ldc, int ldr, int epilogue, int bn,
+                                  uint32_t* a_ready, uint32_t* a_done, unsigned long long a_wait_ns, int* status, void* stream_);
 
 extern "C" int ogb_gemm_bf16(const void* A, const void* W, void* C, const void* bias, const void* residual, void* C_f32,
                              int M, int N, int K, int lda, int ldw, int ldc, int ldr, int epilogue, int bn, int* status,
                              void* stream_) {
+  return ogb_gemm_bf16_wait(A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, epilogue, bn, nullptr, nullptr, 0, status, stream_);
+}
+
+extern "C" int ogb_gemm_bf16_wait(const void* A, const void* W, void* C, const void* bias, const void* residual, void* C_f32,
+                                  int M, int N, int K, int lda, int ldw, int ldc, int ldr, int epilogue, int bn,
+                                  uint32_t* a_ready, uint32_t* a_done, unsigned long long a_wait_ns, int* status, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (a_ready != nullptr && a_done == nullptr) return -8;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 8) != 0 || (lda % 8) != 0 || (ldw % 8) != 0 || (ldc % 8) != 0) return -3;  // 16-byte TMA / vector rules
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(C)) & 15) return -4;
@@ -507,9 +554,9 @@ extern "C" int ogb_gemm_bf16(const void* A, const void* W, void* C, const void* 
   if (epilogue == kEpiResidual) { OGB_GEMM_DISPATCH_BN(kEpiResidual) }
   if (epilogue == kEpiSwiGLU) {
     switch (bn) {
-      case 64: return launch_gemm<64, kEpiSwiGLU>(A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, status, stream);
-      case 128: return launch_gemm<128, kEpiSwiGLU>(A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, status, stream);
-      case 256: return launch_gemm<256, kEpiSwiGLU>(A, W, C, bias, residual, C_f32, M, N, K, lda, ldw, ldc, ldr, status, stream);
+      case 64: return launch_gemm<64, kEpiSwiGLU>(OGB_GEMM_ARGS);
+      case 128: return launch_gemm<128, kEpiSwiGLU>(OGB_GEMM_ARGS);
+      case 256: return launch_gemm<256, kEpiSwiGLU>(OGB_GEMM_ARGS);
       default: return -2;
     }
   }

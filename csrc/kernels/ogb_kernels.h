@@ -17,6 +17,13 @@ int ogb_num_sms(void);
 int ogb_gemm_bf16(const void* A, const void* W, void* C, const void* bias, const void* residual, void* C_f32, int M,
                   int N, int K, int lda, int ldw, int ldc, int ldr, int epilogue, int bn, int* status, void* stream);
 
+// ogb_gemm_bf16 whose A rows are delivered by other GPUs: `a_ready` holds one counter per 128-row tile of A, bumped
+// once per 8 rows that land; the TMA producer waits (at most a_wait_ns nanoseconds, 0 = default) for a tile before
+// loading it, and the last CTA to finish clears the counters (a_done: a zeroed word).
+int ogb_gemm_bf16_wait(const void* A, const void* W, void* C, const void* bias, const void* residual, void* C_f32, int M,
+                       int N, int K, int lda, int ldw, int ldc, int ldr, int epilogue, int bn, uint32_t* a_ready,
+                       uint32_t* a_done, unsigned long long a_wait_ns, int* status, void* stream);
+
 // out[r,:] = x[r,:] * rsqrt(mean(x^2) + eps) * w ; if delta != NULL first x += delta (written back to x).
 int ogb_rmsnorm_bf16(void* x, const void* delta, const void* weight, void* out, int rows, int hidden, int ldx, int ldo,
                      float eps, void* stream);

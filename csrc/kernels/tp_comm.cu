@@ -220,6 +220,163 @@ __global__ void __launch_bounds__(kRbThreads) tp_reduce_bcast_nvls_kernel(const 
   if (stamp) r.dbg[3] = global_timer_ns();
 }
 
+// ------------------------------------------------------------------------------------------------------
+// Row-sharded residual: reduce-scatter + residual add + RMSNorm + all-gather of the normed rows, one kernel.
+//
+// One CTA pass = 8 owned rows, one warp per row (the whole row lives in the warp's registers, so the norm needs no
+// shared memory).  Per row: the partial products of all ranks are summed (one multimem.ld_reduce per 16 bytes, or
+// TP peer loads added in rank order), the owner's residual row is added and stored back locally (bf16), the
+// statistics are taken from the rounded values exactly as the stand-alone RMSNorm does, and the normed row goes
+// to every rank's h (multimem.st, or TP peer stores).  After a pass one thread fences and bumps the ready counter
+// of the rows' 128-row tile on every rank; the next GEMM's TMA producer waits on that counter tile by tile, so
+// nothing here waits for other owners and there is no stand-alone norm launch.
+// Counters are cleared by whoever consumed them: tile_cnt[g] (arrivals from the scatter epilogues) by the last of
+// the group's passes to get through its wait, the ready counters by the last CTA of the GEMM that waited on them.
+// ------------------------------------------------------------------------------------------------------
+template <bool NVLS, int TP, int VPL>
+__global__ void __launch_bounds__(kRbThreads) tp_exchange_norm_kernel(const TpReduce* __restrict__ rp,
+                                                                       const __nv_bfloat16* __restrict__ norm_w, float eps,
+                                                                       int rows, int* status) {
+  const TpReduce& r = *rp;
+  const uint64_t limit = r.wait_limit_ns ? r.wait_limit_ns : kWaitLimitNs;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = r.n;
+  const int nvec = n / 8;
+  const int own_rows = max(0, min(r.chunk, rows - r.rank * r.chunk));
+  const int passes = (own_rows + kTpNormRows - 1) / kTpNormRows;
+  __shared__ int ok_sh;
+  const bool stamp = r.dbg != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
+  if (stamp) r.dbg[0] = global_timer_ns();
+  for (int ps = blockIdx.x; ps < passes; ps += gridDim.x) {
+    const int local0 = ps * kTpNormRows;                  // first row of the pass, relative to the owned chunk
+    const int row_base = r.rank * r.chunk + local0;
+    const int g = local0 / 32;                            // 32-row group whose arrival counter covers these rows
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const bool ok = wait_counter(r.tile_cnt + g, static_cast<uint32_t>(n / 32) * r.tp, limit);   // every rank's tiles of the group
+      if (!ok) atomicOr(status, kStatusPeerTimeout);
+      ok_sh = ok ? 1 : 0;
+      if (ok) {
+        // the last pass of the group to get here clears the arrival counter for the slot's next use
+        const int group_rows = min(32, own_rows - g * 32);
+        const uint32_t group_passes = static_cast<uint32_t>((group_rows + kTpNormRows - 1) / kTpNormRows);
+        if (atomicAdd(r.group_done + g, 1u) == group_passes - 1) {
+          r.group_done[g] = 0;
+          r.tile_cnt[g] = 0;
+        }
+      }
+      if (stamp && ps == 0) r.dbg[1] = global_timer_ns();
+    }
+    __syncthreads();
+    const int row = row_base + warp;
+    if (ok_sh && warp < kTpNormRows && local0 + warp < own_rows) {
+      const size_t row_off = static_cast<size_t>(row) * n;
+      uint4 xv[VPL], pv[VPL];
+      if constexpr (NVLS) {
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+          const int v = lane + 32 * j;
+          if (v < nvec) {
+            xv[j] = *reinterpret_cast<const uint4*>(r.x_own + row_off + v * 8);
+            asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(pv[j].x), "=r"(pv[j].y), "=r"(pv[j].z), "=r"(pv[j].w)
+                         : "l"(r.part_mc + row_off + v * 8)
+                         : "memory");
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+          const int v = lane + 32 * j;
+          if (v < nvec) xv[j] = *reinterpret_cast<const uint4*>(r.x_own + row_off + v * 8);
+        }
+      }
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) {
+        const int v = lane + 32 * j;
+        if (v < nvec) {
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          add_bf16x8(acc, xv[j]);
+          if constexpr (NVLS) {
+            add_bf16x8(acc, pv[j]);
+          } else {
+            uint4 src[TP];
+#pragma unroll
+            for (int s = 0; s < TP; ++s) src[s] = *reinterpret_cast<const uint4*>(r.part[s] + row_off + v * 8);
+#pragma unroll
+            for (int s = 0; s < TP; ++s) add_bf16x8(acc, src[s]);      // fixed order: independent of arrival order
+          }
+          // the residual stream is stored in bf16: round first so the statistics see the stored value
+          const uint4 o = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]),
+                                     pack_bf16(acc[6], acc[7]));
+          *reinterpret_cast<uint4*>(r.x_own + row_off + v * 8) = o;
+          xv[j] = o;
+          float2 f;
+          f = unpack_bf16(o.x); ss += f.x * f.x + f.y * f.y;
+          f = unpack_bf16(o.y); ss += f.x * f.x + f.y * f.y;
+          f = unpack_bf16(o.z); ss += f.x * f.x + f.y * f.y;
+          f = unpack_bf16(o.w); ss += f.x * f.x + f.y * f.y;
+        }
+      }
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(ss / static_cast<float>(n) + eps);
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) {
+        const int v = lane + 32 * j;
+        if (v < nvec) {
+          const uint4 wv = __ldg(reinterpret_cast<const uint4*>(norm_w) + v);
+          float2 a, w;
+          uint4 hv;
+          a = unpack_bf16(xv[j].x); w = unpack_bf16(wv.x); hv.x = pack_bf16(a.x * inv * w.x, a.y * inv * w.y);
+          a = unpack_bf16(xv[j].y); w = unpack_bf16(wv.y); hv.y = pack_bf16(a.x * inv * w.x, a.y * inv * w.y);
+          a = unpack_bf16(xv[j].z); w = unpack_bf16(wv.z); hv.z = pack_bf16(a.x * inv * w.x, a.y * inv * w.y);
+          a = unpack_bf16(xv[j].w); w = unpack_bf16(wv.w); hv.w = pack_bf16(a.x * inv * w.x, a.y * inv * w.y);
+          if constexpr (NVLS) {
+            asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(r.h_mc + row_off + v * 8),
+                         "f"(__uint_as_float(hv.x)), "f"(__uint_as_float(hv.y)), "f"(__uint_as_float(hv.z)),
+                         "f"(__uint_as_float(hv.w))
+                         : "memory");
+          } else {
+#pragma unroll
+            for (int p = 0; p < TP; ++p) *reinterpret_cast<uint4*>(r.h[p] + row_off + v * 8) = hv;
+          }
+        }
+      }
+    }
+    if (stamp && ps == 0) r.dbg[4] = global_timer_ns();
+    __syncthreads();
+    if (threadIdx.x == 0 && ok_sh) {
+      __threadfence_system();
+      if (stamp && ps == 0) r.dbg[6] = global_timer_ns();
+      const int tile = row_base / 128;
+      if constexpr (NVLS) {
+        asm volatile("multimem.red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(r.h_ready_mc + tile), "r"(1u) : "memory");
+      } else {
+#pragma unroll
+        for (int p = 0; p < TP; ++p) asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(r.h_ready[p] + tile) : "memory");
+      }
+    }
+  }
+  if (stamp) r.dbg[3] = global_timer_ns();
+}
+
+// Waits (bounded) until every 128-row tile of the slot's normed activation has arrived on this rank: the kernels
+// that follow on the stream and read h without a wait of their own (the gather of the rows that sample) are
+// ordered after it.
+__global__ void tp_wait_ready_kernel(const TpReduce* __restrict__ rp, int rows, int* status) {
+  const TpReduce& r = *rp;
+  const uint64_t limit = r.wait_limit_ns ? r.wait_limit_ns : kWaitLimitNs;
+  const int tiles = (rows + 127) / 128;
+  for (int t = threadIdx.x; t < tiles; t += blockDim.x) {
+    const int valid = min(128, rows - t * 128);
+    const uint32_t want = static_cast<uint32_t>((valid + kTpNormRows - 1) / kTpNormRows);
+    if (!wait_counter(r.h_ready[r.rank] + t, want, limit)) atomicOr(status, kStatusPeerTimeout);
+  }
+  __syncthreads();
+  for (int t = threadIdx.x; t < tiles; t += blockDim.x) r.h_ready[r.rank][t] = 0;     // consumed: clear for the slot's next use
+}
+
 // Marks every 32-row group of this rank's staged partial product as complete on the rank that owns it.  Used
 // when the partial was produced by kernels that do not signal themselves (the MoE combine): the kernel
 // boundary has made the rows visible, one releasing reduction per group publishes them.
@@ -301,6 +458,46 @@ extern "C" int ogb_tp_reduce_bcast(const void* rp, int rows, int n, int chunk, i
     case 8: return launch_exchange(tp_reduce_bcast_kernel<8, 2>, &occ[4], r, rows, n, chunk, 128, status, st);
     default: return -5;
   }
+}
+
+// Row-sharded form of the exchange (see tp_exchange_norm_kernel): x_own[own rows] += sum over ranks of the staged
+// partials, h[own rows] = RMSNorm(x_own) * norm_w on every rank, ready counters of the rows' tiles bumped everywhere.
+// Must follow ogb_gemm_bf16_scatter (or ogb_tp_signal_rows) on the same stream.
+extern "C" int ogb_tp_exchange_norm(const void* rp, const void* norm_w, float eps, int rows, int n, int chunk, int tp, int nvls,
+                                    int* status, void* stream) {
+  if (rows <= 0) return 0;
+  if (n % 8 || n > 16 * 256 || chunk % 32 || chunk / 32 > kTpMaxGroups || rows > kTpMaxTiles * 128) return -3;
+  const TpReduce* r = static_cast<const TpReduce*>(rp);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int passes = (chunk + kTpNormRows - 1) / kTpNormRows;     // upper bound: the kernel clips to the rows it owns
+  int grid = passes < 1 ? 1 : passes;
+  const int cap = 4 * ogb_num_sms();
+  if (grid > cap) grid = cap;
+  const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(norm_w);
+  const int vpl = (n / 8 + 31) / 32;                              // 16-byte vectors per lane
+#define OGB_EXCH(NV, TPN)                                                                                     \
+  do {                                                                                                        \
+    if (vpl <= 8) tp_exchange_norm_kernel<NV, TPN, 8><<<grid, kRbThreads, 0, st>>>(r, w, eps, rows, status);     \
+    else tp_exchange_norm_kernel<NV, TPN, 16><<<grid, kRbThreads, 0, st>>>(r, w, eps, rows, status);             \
+    return static_cast<int>(cudaGetLastError());                                                              \
+  } while (0)
+  if (nvls) {
+    if (tp == 2 || tp == 4 || tp == 8) OGB_EXCH(true, 1);
+    return -5;
+  }
+  switch (tp) {
+    case 2: OGB_EXCH(false, 2);
+    case 4: OGB_EXCH(false, 4);
+    case 8: OGB_EXCH(false, 8);
+    default: return -5;
+  }
+#undef OGB_EXCH
+}
+
+extern "C" int ogb_tp_wait_ready(const void* rp, int rows, int* status, void* stream) {
+  if (rows <= 0) return 0;
+  tp_wait_ready_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const TpReduce*>(rp), rows, status);
+  return static_cast<int>(cudaGetLastError());
 }
 
 // ---- peer mapping helpers (CUDA IPC) ----

@@ -33,6 +33,21 @@ struct TpReduce {
   unsigned long long* dbg;           // optional: 8 globaltimer stamps of CTA (0,0): start, group 0 ready, all rows signalled, end,
                                      // then for group 0: own stores issued, CTA stores issued, fence done
   int rank, tp, chunk, n;
+  // ---- row-sharded residual (tp_exchange_norm_kernel) ----
+  // The residual stream is owned by rows: rank r keeps rows [r*chunk, (r+1)*chunk) in x_own (a local buffer indexed
+  // by global row) and nobody else reads them.  What is replicated is the *normed* activation h, the A operand of
+  // the next column-parallel GEMM: the owner stores its normed rows into every rank's h and bumps, on every rank,
+  // the ready counter of the 128-row tile they belong to (one arrival per 8 rows).
+  __nv_bfloat16* x_own;              // local residual rows [rows, n]
+  __nv_bfloat16* h[kMaxTp];          // every rank's normed-activation buffer [rows, n]
+  __nv_bfloat16* h_mc;               // multicast view of the same (null without a multicast binding)
+  uint32_t* h_ready[kMaxTp];         // every rank's per-128-row-tile ready counters of this slot
+  uint32_t* h_ready_mc;              // multicast view
+  uint32_t* group_done;              // local: per 32-row group, CTAs that have passed the arrival wait (the last one resets tile_cnt)
+  unsigned long long wait_limit_ns;  // bound of every wait on a peer's signal; 0 = the library default
 };
+
+constexpr int kTpMaxTiles = 64;      // 128-row tiles of a step (8192 rows)
+constexpr int kTpNormRows = 8;       // rows per CTA pass of the exchange = rows per arrival on a ready counter
 
 }  // namespace ogb

@@ -269,13 +269,14 @@ class DecoderModel:
                         else ref.rope_table(cfg.max_position, self.rotary_dim, cfg.rope_theta, dev))
         z = lambda *s: torch.zeros(*s, dtype=dt, device=dev)
         self.fused_comm = comm if (comm is not None and hasattr(comm, "row_parallel") and dev.type == "cuda") else None
+        self.x = z(max_tokens, hid)                 # residual stream (under fused TP: only the rows this rank owns stay current)
         if self.fused_comm is not None:
             if not self.fused_comm.ready:
                 self.fused_comm.setup(hid, max_tokens)
-            self.x = self.fused_comm.x              # residual stream lives in the peer-mapped region
+            self.fused_comm.bind_residual(self.x)
+            self.h = self.fused_comm.h              # normed activations live in the peer-mapped region: owners deliver their rows
         else:
-            self.x = z(max_tokens, hid)             # residual stream
-        self.h = z(max_tokens, hid)                 # normed activations
+            self.h = z(max_tokens, hid)             # normed activations
         self.qkv = z(max_tokens, (self.hq + 2 * self.hkv) * self.d)
         self.attn = z(max_tokens, self.hq * self.d)
         inter_local = (weights.layers[0].gate_up_w.shape[0] // 2) if weights.layers[0].gate_up_w is not None else 0
@@ -368,7 +369,8 @@ class DecoderModel:
         if hit is None:
             sc0, rd0 = fc._get_structs(0, chunk)
             sc1, rd1 = fc._get_structs(1, chunk)
-            hit = (ctypes.c_uint64 * 5)(sc0.data_ptr(), rd0.data_ptr(), sc1.data_ptr(), rd1.data_ptr(), 1 if fc.nvls else 0)
+            hit = (ctypes.c_uint64 * 7)(sc0.data_ptr(), rd0.data_ptr(), sc1.data_ptr(), rd1.data_ptr(), 1 if fc.nvls else 0,
+                                        fc.ready_ptrs(0)[0], fc.ready_ptrs(1)[0])
             self._tp_args_cache[chunk] = hit
         return hit, chunk
 
@@ -418,6 +420,8 @@ class DecoderModel:
             n = self._native_lib.ogb_decoder_launches(self.native) - before
             ops.launch_counts["native_step_kernels"] += n
             return self.logits[: si.num_logit_rows]
+        if self.fused_comm is not None and self.tp > 1:
+            return self._forward_tp_fused(si, kv)
         x, h, qkv, attn = self.x[:t], self.h[:t], self.qkv[:t], self.attn[:t]
         ops.embedding(si.token_ids[:t], w.embed, out=x) if x.is_cuda else x.copy_(w.embed[si.token_ids[:t].long()])
         pending = None  # partial sums still to be added to the residual (TP only)
@@ -505,6 +509,66 @@ class DecoderModel:
         torch.index_select(x, 0, si.logit_rows[:r].long(), out=xl)
         hl = self.h_last[:r]
         self._norm(xl, w.final_norm, None, hl)
+        logits = self.logits[:r]
+        self._gemm(hl, w.lm_head, out=logits)
+        return logits
+
+    def _attention(self, si, kv, li, qkv, attn):
+        """Rotary embedding + KV append + paged attention of one layer over the step's rows."""
+        cfg = self.cfg
+        t, nd = si.num_tokens, si.num_decode
+        pool = kv.pools[li]
+        scales = kv.scales[li] if kv.scales is not None else None
+        ops.rope_kv_append(qkv, si.positions[:t], si.slots[:t], self.cos_sin, pool, self.hq, self.hkv, self.d,
+                           self.rotary_dim, cfg.rotary_interleaved, kv_scales=scales)
+        if nd > 0:
+            ops.paged_decode(qkv[:nd], attn[:nd], pool, si.page_table[:nd], si.ctx_len[:nd], self.hq, self.hkv,
+                             self.d, self.scale, self.decode_splits, self.part_o, self.part_ml, cfg.sliding_window,
+                             kv_scales=scales)
+        if si.num_prefill_seqs > 0 and si.verify_table is not None:
+            nv = si.verify_ctx.numel()
+            ops.paged_decode(qkv[nd:nd + nv], attn[nd:nd + nv], pool, si.verify_table, si.verify_ctx, self.hq, self.hkv,
+                             self.d, self.scale, si.verify_splits, self.part_o, self.part_ml, cfg.sliding_window,
+                             kv_scales=scales)
+        elif si.num_prefill_seqs > 0:
+            np_ = si.num_prefill_seqs
+            ops.paged_prefill(qkv[nd:], attn[nd:], pool, si.page_table[nd:nd + np_], si.ctx_len[nd:nd + np_],
+                              si.cu_q, si.tile_seq, si.tile_q0, si.num_tiles, self.hq, self.hkv, self.d, self.scale,
+                              cfg.sliding_window, kv_scales=scales)
+
+    def _forward_tp_fused(self, si: StepInputs, kv: "KVCache") -> torch.Tensor:
+        """The step under fused tensor parallelism, driven op by op (the C++ executor runs the same sequence).
+
+        The residual stream is owned by rows; every row-parallel projection ends in one exchange kernel that
+        reduce-scatters the partial products, adds the owner's residual rows, applies the *next* RMSNorm and
+        all-gathers the normed rows into ``h`` on every rank.  The column-parallel GEMM that follows waits for ``h``
+        tile by tile inside its TMA producer."""
+        cfg, w, fc = self.cfg, self.w, self.fused_comm
+        t = si.num_tokens
+        x, h, qkv, attn = self.x[:t], self.h[:t], self.qkv[:t], self.attn[:t]
+        ops.embedding(si.token_ids[:t], w.embed, out=x)
+        ops.rmsnorm(x, w.layers[0].ln1, cfg.rms_eps, out=h)       # all rows once; owners keep their rows current from here on
+        ready = None
+        n_layers = len(w.layers)
+        for li, lw in enumerate(w.layers):
+            ops.gemm(h, lw.qkv_w, bias=lw.qkv_b, out=qkv, a_ready=ready)
+            self._attention(si, kv, li, qkv, attn)
+            fc.row_parallel_norm(attn, lw.o_w, t, 0, lw.ln2, cfg.rms_eps)
+            ready = fc.ready_ptrs(0)
+            next_norm = w.layers[li + 1].ln1 if li + 1 < n_layers else w.final_norm
+            if lw.gate_up_w is not None:
+                act = self.act[:t]
+                ops.gemm(h, lw.gate_up_w, epilogue="swiglu", swiglu_half=w.swiglu_half, out=act, a_ready=ready)
+                fc.row_parallel_norm(act, lw.down_w, t, 1, next_norm, cfg.rms_eps)
+            else:
+                from . import moe
+
+                moe.moe_forward_fused(self, h, lw, ready, next_norm)
+            ready = fc.ready_ptrs(1)
+        r = si.num_logit_rows
+        fc.wait_ready(1, t)                                      # the last exchange applied the final norm
+        hl = self.h_last[:r]
+        torch.index_select(h, 0, si.logit_rows[:r].long(), out=hl)
         logits = self.logits[:r]
         self._gemm(hl, w.lm_head, out=logits)
         return logits

@@ -44,3 +44,23 @@ def moe_forward(model, h, lw, x):
                         model.w.swiglu_half, e0, accumulate=False)
     model.comm.all_reduce(part)
     return part
+
+
+def moe_forward_fused(model, h, lw, ready, next_norm):
+    """The MoE block under the fused communicator's row-sharded residual: the router GEMM waits for the rows of ``h``
+    (``ready``), this rank's experts write their partial sum into the symmetric staging buffer, and one exchange
+    reduces all ranks' partials into the owners' residual rows, applies the next RMSNorm and all-gathers ``h``."""
+    cfg, fc = model.cfg, model.fused_comm
+    t = h.shape[0]
+    e_local = lw.expert_gate_up.shape[0]
+    e0, _ = shard_range(cfg.moe.num_experts, model.tp, model.rank)
+    ws = getattr(model, "_moe_ws", None)
+    if ws is None:
+        ws = moe_ops.MoEWorkspace(model.max_tokens, cfg.moe.top_k, e_local, cfg.hidden, cfg.moe.expert_intermediate,
+                                  model.device, h.dtype)
+        model._moe_ws = ws
+    router_logits = ops.gemm(h, lw.router_w, a_ready=ready)      # completes only when every tile of h has arrived
+    part = fc.staging_view(1, t)
+    moe_ops.moe_experts(h, router_logits, lw.expert_gate_up, lw.expert_down, ws, part, cfg.moe.top_k, cfg.moe.renormalize,
+                        model.w.swiglu_half, e0, accumulate=False)
+    fc.reduce_partial_norm(t, 1, next_norm, cfg.rms_eps)

@@ -184,11 +184,15 @@ def _baseline_gemm(a, w, bias, residual, epilogue, out, out_f32, swiglu_half):
 
 
 @_timed("gemm")
-def gemm(a, w, bias=None, residual=None, epilogue="none", out=None, out_f32=False, bn=0, swiglu_half=None):
+def gemm(a, w, bias=None, residual=None, epilogue="none", out=None, out_f32=False, bn=0, swiglu_half=None, a_ready=None):
     """out[M,N] = a[M,K] @ w[N,K]^T (+bias)(+residual) or SwiGLU over a :func:`pack_gate_up` weight.
 
     For ``epilogue="swiglu"`` ``w`` must have been packed with half-width ``swiglu_half`` and the
     kernel tile width is ``2*swiglu_half``; the output is [M, N/2].
+
+    ``a_ready`` = (address of per-128-row-tile ready counters, address of a zeroed word, wait limit in ns): the rows of
+    ``a`` are being delivered by other GPUs (a tensor-parallel exchange bumps a tile's counter once per 8 rows); the
+    kernel's TMA producer waits for each tile before loading it and the last CTA clears the counters.
     """
     m, k = a.shape
     n = w.shape[0]
@@ -209,9 +213,14 @@ def gemm(a, w, bias=None, residual=None, epilogue="none", out=None, out_f32=Fals
         out = torch.empty(m, n_out, dtype=torch.float32 if out_f32 else torch.bfloat16, device=a.device)
     c_bf16 = 0 if out_f32 else out.data_ptr()
     c_f32 = out.data_ptr() if out_f32 else 0
-    rc = lib.ogb_gemm_bf16(a.data_ptr(), w.data_ptr(), c_bf16, _ptr(bias), _ptr(residual), c_f32, m, n, k,
-                           a.stride(0), w.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
-                           _EPI[epilogue], bn, status_word().data_ptr(), _stream())
+    if a_ready is not None:
+        rc = lib.ogb_gemm_bf16_wait(a.data_ptr(), w.data_ptr(), c_bf16, _ptr(bias), _ptr(residual), c_f32, m, n, k,
+                                    a.stride(0), w.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
+                                    _EPI[epilogue], bn, a_ready[0], a_ready[1], a_ready[2], status_word().data_ptr(), _stream())
+    else:
+        rc = lib.ogb_gemm_bf16(a.data_ptr(), w.data_ptr(), c_bf16, _ptr(bias), _ptr(residual), c_f32, m, n, k,
+                               a.stride(0), w.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
+                               _EPI[epilogue], bn, status_word().data_ptr(), _stream())
     _native.check(rc, "ogb_gemm_bf16")
     launch_counts["gemm_bf16_tcgen05"] += 1
     return out

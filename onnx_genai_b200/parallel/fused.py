@@ -11,6 +11,13 @@ collective:
                             + residual, stores the new rows into every rank's residual stream, waits
                             for the other owners
 
+The decoder uses the row-sharded form of the exchange (:meth:`FusedComm.row_parallel_norm`): the residual stream is
+owned by rows (rank r keeps rows ``[r*chunk, (r+1)*chunk)`` in a local buffer), and what every rank receives is the
+*normed* activation ``h`` of the next column-parallel GEMM.  One kernel per projection boundary does
+reduce-scatter + residual add + RMSNorm + all-gather, bumping a ready counter per 128-row tile of ``h`` on every
+rank; the next GEMM's TMA producer waits on those counters tile by tile (``ops.gemm(..., a_ready=...)``), so there is
+no stand-alone norm launch and no kernel that waits for the slowest owner.
+
 When the region can be bound to an NVSwitch multicast object (the region is then allocated through
 ``torch.distributed._symmetric_memory``, which does the handle exchange and the binding), the second
 launch uses ``multimem.ld_reduce`` / ``multimem.st`` / ``multimem.red`` instead of per-peer loads and
@@ -49,7 +56,13 @@ class _Reduce(ctypes.Structure):
     _fields_ = [("part", ctypes.c_uint64 * MAX_TP), ("tile_cnt", ctypes.c_uint64), ("x", ctypes.c_uint64 * MAX_TP),
                 ("x_cnt", ctypes.c_uint64 * MAX_TP), ("done_cnt", ctypes.c_uint64),
                 ("part_mc", ctypes.c_uint64), ("x_mc", ctypes.c_uint64), ("x_cnt_mc", ctypes.c_uint64), ("dbg", ctypes.c_uint64),
-                ("rank", ctypes.c_int), ("tp", ctypes.c_int), ("chunk", ctypes.c_int), ("n", ctypes.c_int)]
+                ("rank", ctypes.c_int), ("tp", ctypes.c_int), ("chunk", ctypes.c_int), ("n", ctypes.c_int),
+                ("x_own", ctypes.c_uint64), ("h", ctypes.c_uint64 * MAX_TP), ("h_mc", ctypes.c_uint64),
+                ("h_ready", ctypes.c_uint64 * MAX_TP), ("h_ready_mc", ctypes.c_uint64), ("group_done", ctypes.c_uint64),
+                ("wait_limit_ns", ctypes.c_uint64)]
+
+
+READY_WORDS = 80          # per slot: 64 per-tile ready counters, then the consumer GEMM's finished-CTA word
 
 
 class _CudaArray:
@@ -73,6 +86,10 @@ def _lib():
     lib.ogb_tp_reduce_bcast.argtypes = [P, I, I, I, I, I, P, P]
     lib.ogb_tp_signal_rows.argtypes = [P, I, P]
     lib.ogb_tp_signal_rows.restype = I
+    lib.ogb_tp_exchange_norm.argtypes = [P, P, ctypes.c_float, I, I, I, I, I, P, P]
+    lib.ogb_tp_exchange_norm.restype = I
+    lib.ogb_tp_wait_ready.argtypes = [P, I, P, P]
+    lib.ogb_tp_wait_ready.restype = I
     for f in ("ogb_ipc_alloc", "ogb_ipc_get_handle", "ogb_ipc_open_handle", "ogb_ipc_close_handle", "ogb_ipc_free",
               "ogb_tp_struct_sizes", "ogb_gemm_bf16_scatter", "ogb_tp_reduce_bcast"):
         getattr(lib, f).restype = I
@@ -117,11 +134,8 @@ class FusedComm:
         return self.base.max_float(v)
 
     # -- symmetric region ----------------------------------------------------------------------
-    def setup(self, hidden: int, max_tokens: int):
-        """Allocate, export and map the symmetric region for a residual stream [max_tokens, hidden]."""
-        sb, rb = ctypes.c_int(), ctypes.c_int()
-        self.lib.ogb_tp_struct_sizes(ctypes.byref(sb), ctypes.byref(rb))
-        assert sb.value == ctypes.sizeof(_Scatter) and rb.value == ctypes.sizeof(_Reduce), "struct layout mismatch"
+    def _layout(self, hidden: int, max_tokens: int) -> int:
+        """Offsets of the symmetric region's sections; returns its size in bytes."""
         tp = self.world
         self.hidden, self.max_tokens = hidden, max_tokens
         self.chunk_max = ((max_tokens + tp - 1) // tp + 31) // 32 * 32
@@ -129,10 +143,66 @@ class FusedComm:
         align = lambda v: (v + 255) // 256 * 256
         self.off_stage = [0, align(stage_bytes)]
         self.off_x = self.off_stage[1] + align(stage_bytes)
-        self.off_cnt = self.off_x + align(max_tokens * hidden * 2)
-        # counters: tile_cnt[SLOTS][MAX_GROUPS], x_cnt, done_cnt
-        cnt_words = SLOTS * MAX_GROUPS + 64
-        total = self.off_cnt + align(cnt_words * 4)
+        self.off_h = self.off_x + align(max_tokens * hidden * 2)
+        self.off_cnt = self.off_h + align(max_tokens * hidden * 2)
+        # counters: tile_cnt[SLOTS][MAX_GROUPS], x_cnt / done_cnt (64 words), h_ready[SLOTS][READY_WORDS],
+        # group_done[SLOTS][MAX_GROUPS]
+        self.cnt_words = SLOTS * MAX_GROUPS + 64 + SLOTS * READY_WORDS + SLOTS * MAX_GROUPS
+        self.off_ready = self.off_cnt + (SLOTS * MAX_GROUPS + 64) * 4
+        self.off_gdone = self.off_ready + SLOTS * READY_WORDS * 4
+        self.wait_limit_ns = 0
+        self.x_own_ptr = 0
+        return self.off_cnt + align(self.cnt_words * 4)
+
+    @classmethod
+    def loopback(cls, device, hidden: int, max_tokens: int, world: int = 2):
+        """A group of ``world`` ranks whose regions all live on this one GPU (this process is rank 0; plain memory, no
+        multicast).  Nothing real can be computed with it -- the "peers" never run -- which is its use: a launch on
+        it waits for arrivals that cannot come, so the bounded waits of the exchange kernels can be exercised on one
+        GPU without faulting or hanging anything (see :meth:`set_wait_limit`)."""
+        self = cls.__new__(cls)
+
+        n_ranks = world
+
+        class _Solo:
+            rank = 0
+            world = n_ranks
+            backend_name = "loopback"
+
+            def barrier(self): return None
+            def min_int(self, v): return v
+            def max_float(self, v): return v
+
+        self.base = _Solo()
+        self.rank, self.world = 0, world
+        self.device = torch.device(device)
+        self.lib = _lib()
+        self.failed, self._last_slot, self.calls = None, -1, 0
+        total = self._layout(hidden, max_tokens)
+        self.total_bytes = total
+        self._region = torch.zeros(world * total, dtype=torch.uint8, device=self.device)
+        self.local_ptr = self._region.data_ptr()
+        self.peer_ptrs = [self.local_ptr + p * total for p in range(world)]
+        self.mc_ptr, self.nvls, self._symm, self.dbg = 0, False, None, None
+        self.backend_name = "loopback"
+        self.x = self._region[self.off_x:self.off_x + max_tokens * hidden * 2].view(torch.bfloat16).view(max_tokens, hidden)
+        self.h = self._region[self.off_h:self.off_h + max_tokens * hidden * 2].view(torch.bfloat16).view(max_tokens, hidden)
+        self._structs = {}
+        self.ready = True
+        return self
+
+    def reset_counters(self) -> None:
+        """Zero every counter of this rank's region (after a wait ran out the counters are part-consumed)."""
+        cnt = torch.as_tensor(_CudaArray(self.local_ptr + self.off_cnt, (self.cnt_words,), "<u4"), device=self.device)
+        cnt.view(torch.int32).zero_()
+        self._last_slot = -1
+
+    def setup(self, hidden: int, max_tokens: int):
+        """Allocate, export and map the symmetric region for a residual stream [max_tokens, hidden]."""
+        sb, rb = ctypes.c_int(), ctypes.c_int()
+        self.lib.ogb_tp_struct_sizes(ctypes.byref(sb), ctypes.byref(rb))
+        assert sb.value == ctypes.sizeof(_Scatter) and rb.value == ctypes.sizeof(_Reduce), "struct layout mismatch"
+        total = self._layout(hidden, max_tokens)
         self.total_bytes = total
         self.mc_ptr = 0
         self.nvls = False
@@ -158,6 +228,8 @@ class FusedComm:
             self.backend_name = "fused-nvls"
         self.dbg = torch.zeros(8, dtype=torch.int64, device=self.device) if os.environ.get("OGB_TP_STAMPS") else None
         self.x = torch.as_tensor(_CudaArray(self.local_ptr + self.off_x, (max_tokens, hidden), "<u2"),
+                                 device=self.device).view(torch.bfloat16)
+        self.h = torch.as_tensor(_CudaArray(self.local_ptr + self.off_h, (max_tokens, hidden), "<u2"),
                                  device=self.device).view(torch.bfloat16)
         self._structs: dict = {}
         torch.cuda.synchronize()
@@ -229,6 +301,15 @@ class FusedComm:
             rd.x_cnt_mc = self.mc_ptr + self.off_cnt + SLOTS * MAX_GROUPS * 4
         rd.dbg = self.dbg.data_ptr() if self.dbg is not None else 0
         rd.rank, rd.tp, rd.chunk, rd.n = self.rank, tp, chunk, self.hidden
+        rd.x_own = self.x_own_ptr
+        for p in range(tp):
+            rd.h[p] = self.peer_ptrs[p] + self.off_h
+            rd.h_ready[p] = self.peer_ptrs[p] + self.off_ready + slot * READY_WORDS * 4
+        if self.nvls:
+            rd.h_mc = self.mc_ptr + self.off_h
+            rd.h_ready_mc = self.mc_ptr + self.off_ready + slot * READY_WORDS * 4
+        rd.group_done = self.local_ptr + self.off_gdone + slot * MAX_GROUPS * 4
+        rd.wait_limit_ns = int(self.wait_limit_ns)
         mk = lambda st: torch.frombuffer(bytearray(bytes(st)), dtype=torch.uint8).to(self.device)
         hit = (mk(sc), mk(rd))
         self._structs[key] = hit
@@ -242,7 +323,7 @@ class FusedComm:
         self.failed = why
         self.ready = False
         try:
-            cnt = torch.as_tensor(_CudaArray(self.local_ptr + self.off_cnt, (SLOTS * MAX_GROUPS + 64,), "<u4"), device=self.device)
+            cnt = torch.as_tensor(_CudaArray(self.local_ptr + self.off_cnt, (self.cnt_words,), "<u4"), device=self.device)
             cnt.view(torch.int32).zero_()
         except Exception:
             pass
@@ -280,6 +361,73 @@ class FusedComm:
         ops.launch_counts["gemm_bf16_scatter"] += 1
         ops.launch_counts["tp_reduce_bcast"] += 1
         self.calls += 1
+
+    # -- row-sharded residual: reduce-scatter + residual + RMSNorm + all-gather in one kernel ---------------
+    def bind_residual(self, x) -> None:
+        """``x`` [max_tokens, hidden] is this rank's residual stream (plain local memory, indexed by global row); the
+        exchange updates the rows this rank owns in place.  Structs built earlier are rebuilt with the new address."""
+        assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[1] == self.hidden
+        self._residual = x
+        self.x_own_ptr = x.data_ptr()
+        self._structs.clear()
+
+    def set_wait_limit(self, ns: int) -> None:
+        """Bound, in nanoseconds, of every wait on another rank's signal in the exchange kernels and in the GEMMs that
+        wait for ``h`` (0 = the library's default of two seconds).  A wait that runs out sets the peer-timeout bit of
+        the device status word and the kernel returns."""
+        self.wait_limit_ns = int(ns)
+        self._structs.clear()
+
+    def ready_ptrs(self, slot: int):
+        """(ready counters, finished-CTA word) of ``slot`` on this rank, as ``ops.gemm(..., a_ready=...)`` takes them."""
+        base = self.local_ptr + self.off_ready + slot * READY_WORDS * 4
+        return base, base + 64 * 4, int(self.wait_limit_ns)
+
+    def _exchange_norm(self, rd, norm_w, eps, rows, chunk, st, stream):
+        with ops.timed_region("tp_exchange_norm"):
+            rc = self.lib.ogb_tp_exchange_norm(rd.data_ptr(), norm_w.data_ptr(), float(eps), rows, self.hidden, chunk, self.world,
+                                               1 if self.nvls else 0, st, stream)
+        _native.check(rc, "ogb_tp_exchange_norm")
+        ops.launch_counts["tp_exchange_norm"] += 1
+        self.calls += 1
+
+    def row_parallel_norm(self, a, w, rows: int, slot: int, norm_w, eps: float):
+        """residual[own rows] += sum over ranks of a @ w^T, then h[:rows] = RMSNorm(residual) * norm_w on every rank
+        (delivered tile by tile: consumers wait on :meth:`ready_ptrs`)."""
+        assert self.x_own_ptr, "bind_residual() first"
+        self._guard(rows, slot)
+        chunk = self.chunk_for(rows)
+        sc, rd = self._get_structs(slot, chunk)
+        st = ops.status_word(self.device).data_ptr()
+        stream = torch.cuda.current_stream().cuda_stream
+        with ops.timed_region("gemm_scatter[K=%d]" % a.shape[1]):
+            rc = self.lib.ogb_gemm_bf16_scatter(a.data_ptr(), w.data_ptr(), rows, self.hidden, a.shape[1], a.stride(0),
+                                                w.stride(0), sc.data_ptr(), 0, st, stream)
+        _native.check(rc, "ogb_gemm_bf16_scatter")
+        ops.launch_counts["gemm_bf16_scatter"] += 1
+        self._exchange_norm(rd, norm_w, eps, rows, chunk, st, stream)
+
+    def reduce_partial_norm(self, rows: int, slot: int, norm_w, eps: float):
+        """Same exchange for a partial sum that other kernels left in :meth:`staging_view` (the MoE combine)."""
+        assert self.x_own_ptr, "bind_residual() first"
+        self._guard(rows, slot)
+        chunk = self.chunk_for(rows)
+        sc, rd = self._get_structs(slot, chunk)
+        st = ops.status_word(self.device).data_ptr()
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = self.lib.ogb_tp_signal_rows(sc.data_ptr(), rows, stream)
+        _native.check(rc, "ogb_tp_signal_rows")
+        ops.launch_counts["tp_signal_rows"] += 1
+        self._exchange_norm(rd, norm_w, eps, rows, chunk, st, stream)
+
+    def wait_ready(self, slot: int, rows: int):
+        """Order the stream after the arrival of every tile of ``h[:rows]`` of ``slot`` (and clear its counters)."""
+        chunk = self.chunk_for(rows)
+        _, rd = self._get_structs(slot, chunk)
+        rc = self.lib.ogb_tp_wait_ready(rd.data_ptr(), rows, ops.status_word(self.device).data_ptr(),
+                                        torch.cuda.current_stream().cuda_stream)
+        _native.check(rc, "ogb_tp_wait_ready")
+        ops.launch_counts["tp_wait_ready"] += 1
 
     # -- partial sums produced by other kernels (MoE combine) -------------------------------------
     def staging_view(self, slot: int, rows: int):

@@ -1,4 +1,5 @@
-"""Tensor parallelism on 2 GPUs: the fused peer-memory path and the NCCL baseline against TP=1."""
+"""Tensor parallelism on 2, 4 and 8 GPUs: the fused peer-memory path (NVSwitch multicast kernels and plain peer
+loads) and the NCCL baseline against one GPU."""
 import os
 import subprocess
 import sys
@@ -8,6 +9,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+WORLDS = [2, 4, 8]
 
 
 def _run(nproc, mode, out, port, **extra_env):
@@ -18,43 +20,61 @@ def _run(nproc, mode, out, port, **extra_env):
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
                "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "tp_worker.py"),
                mode, out]
-    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=420)
     assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-4000:]
     return torch.load(out)
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_tp2_fused_and_nccl_match_single_gpu(tmp_path):
-    single = _run(1, "nccl", str(tmp_path / "s.pt"), 0)
-    nccl = _run(2, "nccl", str(tmp_path / "n.pt"), 29631)
-    fused = _run(2, "fused", str(tmp_path / "f.pt"), 29632, OGB_TP_NVLS="1")       # NVSwitch multicast kernels
-    fused_py = _run(2, "fused-py", str(tmp_path / "fp.pt"), 29633, OGB_TP_NVLS="1")
-    assert fused["backend"] == "fused-nvls"
-    p2p = _run(2, "fused", str(tmp_path / "p.pt"), 29634, OGB_TP_NVLS="0", OGB_TP_SYMM="0")   # plain peer loads, CUDA IPC
+def _need(n):
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
+def _err(got, ref):
+    return float((got["logits"] - ref).norm() / ref.norm())
+
+
+@pytest.fixture(scope="module")
+def single(tmp_path_factory):
+    return _run(1, "nccl", str(tmp_path_factory.mktemp("tp") / "s.pt"), 0)
+
+
+@pytest.fixture(scope="module")
+def single_moe(tmp_path_factory):
+    return _run(1, "nccl-moe", str(tmp_path_factory.mktemp("tp") / "sm.pt"), 0)
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_fused_and_nccl_match_single_gpu(world, single, tmp_path):
+    """Every exchange-kernel instantiation a world size selects (multicast: one kernel for all sizes; peer loads:
+    one per size) is compared with the one-GPU logits, through the C++ step executor and op by op from Python."""
+    _need(world)
+    port = 29600 + 10 * world
     ref = single["logits"]
-    err = float((p2p["logits"] - ref).norm() / ref.norm())
-    assert err < 3e-2, ("fused-p2p", err)
-    assert p2p["backend"] == "fused-p2p"
-    assert fused["launches"].get("native_step_kernels", 0) > 0
-    assert fused_py["tokens"] == fused["tokens"]          # C++ executor and Python-driven path run the same kernels
-    fused = fused_py
-    for name, got in (("nccl", nccl), ("fused", fused)):
-        err = float((got["logits"] - ref).norm() / ref.norm())
-        assert err < 3e-2, (name, err)
-    assert fused["launches"].get("gemm_bf16_scatter", 0) > 0 and fused["launches"].get("tp_reduce_bcast", 0) > 0
-    assert len(fused["tokens"]) == len(single["tokens"])
+    nccl = _run(world, "nccl", str(tmp_path / "n.pt"), port)
+    nvls = _run(world, "fused", str(tmp_path / "f.pt"), port + 1, OGB_TP_NVLS="1")          # NVSwitch multicast kernels
+    nvls_py = _run(world, "fused-py", str(tmp_path / "fp.pt"), port + 2, OGB_TP_NVLS="1")
+    p2p = _run(world, "fused", str(tmp_path / "p.pt"), port + 3, OGB_TP_NVLS="0", OGB_TP_SYMM="0")   # peer loads, CUDA IPC
+    assert nvls["backend"] == "fused-nvls" and p2p["backend"] == "fused-p2p"
+    for name, got in (("nccl", nccl), ("fused-nvls", nvls), ("fused-nvls-py", nvls_py), ("fused-p2p", p2p)):
+        assert _err(got, ref) < 3e-2, (world, name, _err(got, ref))
+        assert len(got["tokens"]) == len(single["tokens"])
+    assert nvls["launches"].get("native_step_kernels", 0) > 0
+    assert nvls_py["tokens"] == nvls["tokens"]          # C++ executor and Python-driven path run the same kernels
+    assert nvls_py["launches"].get("gemm_bf16_scatter", 0) > 0 and nvls_py["launches"].get("tp_exchange_norm", 0) > 0
+    assert 0 < nvls_py["launches"].get("rmsnorm", 0) < 20     # one replicated norm per step (13 steps): the other six per step ride in the exchange
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_tp2_moe_combine_over_the_exchange_kernel_matches_single_gpu(tmp_path):
-    """Experts split over 2 ranks: the combine goes through the peer-memory exchange (multicast forced on) and
+@pytest.mark.parametrize("world", WORLDS)
+def test_moe_combine_over_the_exchange_kernel_matches_single_gpu(world, single_moe, tmp_path):
+    """Experts split over the ranks: the combine goes through the peer-memory exchange (multicast forced on) and
     through NCCL; both must agree with one GPU holding every expert."""
-    single = _run(1, "nccl-moe", str(tmp_path / "s.pt"), 0)
-    nccl = _run(2, "nccl-moe", str(tmp_path / "n.pt"), 29641)
-    fused = _run(2, "fused-py-moe", str(tmp_path / "f.pt"), 29642, OGB_TP_NVLS="1")
-    ref = single["logits"]
+    _need(world)
+    port = 29700 + 10 * world
+    ref = single_moe["logits"]
+    nccl = _run(world, "nccl-moe", str(tmp_path / "n.pt"), port)
+    fused = _run(world, "fused-py-moe", str(tmp_path / "f.pt"), port + 1, OGB_TP_NVLS="1")
     for name, got in (("nccl", nccl), ("fused", fused)):
-        err = float((got["logits"] - ref).norm() / ref.norm())
-        assert err < 3e-2, (name, err)
+        assert _err(got, ref) < 3e-2, (world, name, _err(got, ref))
     assert fused["launches"].get("tp_signal_rows", 0) > 0 and fused["launches"].get("moe_grouped_gemm", 0) > 0
-    assert len(fused["tokens"]) == len(single["tokens"])
+    assert len(fused["tokens"]) == len(single_moe["tokens"])
