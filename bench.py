@@ -111,6 +111,10 @@ def main():
     ap.add_argument("--deadline", type=int, default=900, help="seconds after which a stuck run dumps stacks and exits")
     ap.add_argument("--no-native-executor", action="store_true", help="drive the layer stack from Python (for op profiling)")
     ap.add_argument("--profile-ops", action="store_true", help="after the timed regions, replay 4 steps with per-op CUDA-event timing (stderr)")
+    ap.add_argument("--no-anchor", action="store_true",
+                    help="skip the labelled library arm (cuBLAS GEMMs + ncclAllReduce) that is replayed on the same steps for vs_baseline")
+    ap.add_argument("--latency-requests", type=int, default=256,
+                    help="after the timed regions keep the closed loop running until this many requests have finished (TTFT / TPOT sample)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -270,6 +274,8 @@ def main():
         comm.barrier()
     torch.cuda.synchronize()
     launches1 = sum(ops.launch_counts.values())
+    tp_counts0 = (eng.model.native_counter(1), eng.model.native_counter(2), ops.launch_counts["gemm_bf16_scatter"],
+                  ops.launch_counts["tp_exchange_norm"])
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     td0 = time.perf_counter()
     ev0.record()
@@ -282,7 +288,57 @@ def main():
     td1 = time.perf_counter()
     dev_ms = ev0.elapsed_time(ev1)
     launches_dev = sum(ops.launch_counts.values()) - launches1
+    tp_counts1 = (eng.model.native_counter(1), eng.model.native_counter(2), ops.launch_counts["gemm_bf16_scatter"],
+                  ops.launch_counts["tp_exchange_norm"])
     sampler.stop()
+    eng.check_device_status()
+
+    # ---- labelled baseline arm on the same recorded steps: library GEMMs (torch.matmul -> cuBLAS, unfused epilogues),
+    # ncclAllReduce for the row-parallel projections, stand-alone RMSNorm; attention and sampler stay this repo's kernels
+    # (no library kernel reads this page layout).  Driven op by op from Python, timed on the device like region 2. ----
+    base_ms = None
+    if args.impl == "ours" and not args.no_anchor:
+        m = eng.model
+        saved = (m.fused_comm, m.comm, m.native)
+        try:
+            ops.set_baseline(True)
+            m.fused_comm, m.native = None, None
+            if world > 1:
+                m.comm = getattr(comm, "base", comm)
+            for i in range(min(3, args.steps)):
+                replay(i)
+            if comm is not None:
+                comm.barrier()
+            torch.cuda.synchronize()
+            b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            b0.record()
+            for i in range(args.steps):
+                replay(i)
+            b1.record()
+            if comm is not None:
+                comm.barrier()
+            torch.cuda.synchronize()
+            base_ms = b0.elapsed_time(b1)
+        finally:
+            ops.set_baseline(False)
+            m.fused_comm, m.comm, m.native = saved
+        if comm is not None:
+            base_ms = comm.max_float(base_ms)
+        eng.check_device_status()
+
+    # ---- latency sample: requests that arrive after the timed regions (the replays above stretch the wall-clock gaps of
+    # the requests that were in flight), run until enough of them have finished ----
+    extra_steps = 0
+    t_lat0 = time.perf_counter()
+    lat_done = 0
+    seen = len(finished_ids)
+    while lat_done < args.latency_requests and extra_steps < 3 * (args.output_tokens + args.latency_requests):
+        closed_loop_step()
+        extra_steps += 1
+        for sid in finished_ids[seen:]:
+            if eng.stats[sid].arrival >= t_lat0:
+                lat_done += 1
+        seen = len(finished_ids)
     eng.check_device_status()
     if args.profile_ops:
         # every rank replays (the steps contain collectives); rank 0 reports
@@ -308,10 +364,12 @@ def main():
     ttft, tpot = [], []
     for sid in finished_ids:
         st = eng.stats.get(sid)
-        if st and st.finished and st.output_tokens > 1:
+        if st and st.finished and st.output_tokens > 1 and st.arrival >= t_lat0:
             ttft.append((st.first_token - st.arrival) * 1e3)
             tpot.append((st.finished - st.first_token) * 1e3 / (st.output_tokens - 1))
     clocks = sampler.summary(t0, td1)
+    pct = lambda xs, q: round(float(np.percentile(xs, q)), 3) if xs else None
+    base_value = dev_tokens / (base_ms / 1e3) if base_ms else None
     if rank == 0:
         result = {
             "metric": "output tok/s (%s-shape, continuous batching, %d concurrent, %s=%d)" % (
@@ -319,7 +377,7 @@ def main():
                 "TP=EP" if model.moe.num_experts > 0 else "TP", world),
             "value": round(value, 1), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(dev_ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform-random token ids, N(0,0.02) weights)",
+            "vs_baseline": round(value / base_value, 4) if base_value else None, "dtype": "bf16", "data": "synthetic (uniform-random token ids, N(0,0.02) weights)",
             "impl": args.impl,
             "config": {"model": model.name + "-shape", "global_batch": args.concurrency, "seq_len": f"prompt U[{args.min_prompt},{args.max_prompt}] + {args.output_tokens} out",
                        "parallelism": f"tp{world}", "kv": "paged, 16-token bf16 pages", "sampling": "greedy" if args.greedy else "temperature 0.7, top-p 0.9",
@@ -330,11 +388,19 @@ def main():
                        "kv_pages": eng.num_pages, "ramp_steps": ramp_steps, "ramp_s": round(ramp_s, 2)},
             "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                     "ms_per_step": round(e2e_s * 1e3 / args.steps, 4)},
+            "baseline": None if not base_value else {
+                "what": "same %d recorded steps replayed on this repo's labelled library arm: torch.matmul (cuBLAS) GEMMs with unfused "
+                        "epilogues, ncclAllReduce for the row-parallel projections, stand-alone RMSNorm; attention and sampler kernels "
+                        "as in the product arm; device-timed, max over ranks" % args.steps,
+                "value": round(base_value, 1), "unit": "tok/s", "ms_per_step": round(base_ms / args.steps, 4)},
+            "tp_launches_per_step": {
+                "gemm_bf16_scatter": ((tp_counts1[0] - tp_counts0[0]) + (tp_counts1[2] - tp_counts0[2])) / args.steps,
+                "tp_exchange_norm": ((tp_counts1[1] - tp_counts0[1]) + (tp_counts1[3] - tp_counts0[3])) / args.steps},
             "gpu_launches": int(launches_dev),
             "gpu_launches_e2e": int(launches_e2e),
             "clocks": clocks,
-            "latency": {"ttft_ms_p50": round(statistics.median(ttft), 2) if ttft else None,
-                        "tpot_ms_p50": round(statistics.median(tpot), 3) if tpot else None, "finished_requests": len(ttft)},
+            "latency": {"ttft_ms_p50": pct(ttft, 50), "ttft_ms_p99": pct(ttft, 99), "tpot_ms_p50": pct(tpot, 50),
+                        "tpot_ms_p99": pct(tpot, 99), "finished_requests": len(ttft), "extra_steps": extra_steps},
             "baseline_context": BASELINE_CONTEXT,
         }
         if invalid:

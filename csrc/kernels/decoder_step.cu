@@ -34,6 +34,7 @@ struct DecoderPlan {
   int* status;
   std::vector<LayerPtrs> layers;
   long long launches = 0;
+  long long launches_scatter = 0, launches_exchange = 0;   // row-parallel GEMMs with the scatter epilogue / exchange kernels
 };
 
 }  // namespace ogb
@@ -80,6 +81,11 @@ extern "C" void* ogb_decoder_create(const int* iparams, int64_t num_pages, const
 
 extern "C" void ogb_decoder_destroy(void* plan) { delete static_cast<DecoderPlan*>(plan); }
 extern "C" long long ogb_decoder_launches(void* plan) { return static_cast<DecoderPlan*>(plan)->launches; }
+// which: 0 = all kernels, 1 = GEMMs with the tensor-parallel scatter epilogue, 2 = tensor-parallel exchange kernels
+extern "C" long long ogb_decoder_counter(void* plan, int which) {
+  DecoderPlan* p = static_cast<DecoderPlan*>(plan);
+  return which == 1 ? p->launches_scatter : which == 2 ? p->launches_exchange : p->launches;
+}
 // The KV pool is a reserved address range of which `num_pages` pages are backed; the kernels bound page ids by it.
 extern "C" void ogb_decoder_set_num_pages(void* plan, int64_t num_pages) { static_cast<DecoderPlan*>(plan)->num_pages = num_pages; }
 extern "C" void ogb_decoder_set_split_scratch(void* plan, float* part_o, float* part_ml) {
@@ -165,6 +171,8 @@ extern "C" int ogb_decoder_step(void* plan, const int* token_ids, const int* pos
     } else {
       STEP_CHECK(ogb_gemm_bf16_scatter(p->attn, L.o_w, T, hid, attn_n, attn_n, attn_n, sc[0], 0, p->status, stream));
       STEP_CHECK(ogb_tp_exchange_norm(rd[0], L.ln2, p->eps, T, hid, tp_chunk, p->tp, nvls, p->status, stream));
+      p->launches_scatter += 2;     // this layer's two row-parallel projections (the second one follows below)
+      p->launches_exchange += 2;
     }
     STEP_CHECK(ogb_gemm_bf16_wait(p->h, L.gate_up_w, p->act, nullptr, nullptr, nullptr, T, 2 * p->inter_local, hid, hid, hid,
                                   p->inter_local, 0, 2, p->swiglu_bn, tp ? ready[0] : nullptr, tp ? ready[0] + 64 : nullptr, 0,

@@ -335,6 +335,10 @@ def cmd_serve(args, profiler):
             from .server.audio import SpeechPipeline
 
             app_kw["speech_pipeline"] = SpeechPipeline(args.speech_package, media_device)
+        if getattr(args, "multimodal_package", ""):
+            from .server.multimodal import WorkflowMediaChat
+
+            app_kw["media_chat"] = WorkflowMediaChat(args.multimodal_package, media_device)
         if getattr(args, "transcribe_package", ""):
             from .server.transcribe import WorkflowTranscriber
 
@@ -544,6 +548,179 @@ class Profiler:
             write_chrome_trace(self.trace_path, [(n, a, b, "cli") for n, a, b in self.spans])
 
 
+# ------------------------------------------------------------------------------------------
+# transcribe: WAV files or a live PCM stream on standard input -> text / JSON lines / SubRip
+# (the reference's `transcribe` subcommand, crates/onnx-genai-cli/src/transcribe.rs)
+# ------------------------------------------------------------------------------------------
+def srt_timestamp(seconds: float) -> str:
+    ms = int(round(max(0.0, seconds) * 1000.0))
+    return "%02d:%02d:%02d,%03d" % (ms // 3600000, (ms // 60000) % 60, (ms // 1000) % 60, ms % 1000)
+
+
+def format_transcript(fmt: str, index: int, start: float, end: float, text: str) -> str:
+    if fmt == "json":
+        return json.dumps({"index": index, "start": round(start, 3), "end": round(end, 3), "text": text}, ensure_ascii=False)
+    if fmt == "srt":
+        return "%d\n%s --> %s\n%s\n" % (index + 1, srt_timestamp(start), srt_timestamp(end), text)
+    return text
+
+
+class PcmStreamReader:
+    """Mono float samples from a byte stream of 16-bit PCM.  A stream that begins with a RIFF/WAVE header declares its own
+    rate and channel count (its data chunk may claim any length: a pipe has no end until it closes); otherwise the
+    caller's rate and channel count describe the raw samples.  Channels are averaged."""
+
+    def __init__(self, stream, sample_rate: int, channels: int, chunk_seconds: float = 0.25):
+        import struct
+
+        self.stream = stream
+        self.sample_rate, self.channels = int(sample_rate), max(1, int(channels))
+        self.left = b""
+        head = self._read_exact(12)
+        if len(head) == 12 and head[:4] == b"RIFF" and head[8:12] == b"WAVE":
+            while True:
+                hdr = self._read_exact(8)
+                if len(hdr) < 8:
+                    raise ValueError("the WAV stream ended before its data chunk")
+                tag, size = hdr[:4], struct.unpack("<I", hdr[4:])[0]
+                if tag == b"fmt ":
+                    fmt = self._read_exact(size + (size & 1))
+                    code, ch, rate, _, _, bits = struct.unpack("<HHIIHH", fmt[:16])
+                    if code not in (1, 0xFFFE) or bits != 16:
+                        raise ValueError(f"standard input carries WAV format {code} with {bits} bits; 16-bit PCM is read")
+                    self.sample_rate, self.channels = int(rate), max(1, int(ch))
+                elif tag == b"data":
+                    break
+                else:
+                    self._read_exact(size + (size & 1))
+        else:
+            self.left = head
+        if self.sample_rate <= 0:
+            raise ValueError("the sample rate must be positive")
+        self.frame_bytes = 2 * self.channels
+        self.chunk_bytes = max(1, int(self.sample_rate * chunk_seconds)) * self.frame_bytes
+
+    def _read_exact(self, n: int) -> bytes:
+        out = b""
+        while len(out) < n:
+            got = self.stream.read(n - len(out))
+            if not got:
+                break
+            out += got
+        return out
+
+    def read_chunk(self):
+        """The next block of samples (empty at end of stream).  A trailing partial frame is dropped."""
+        import numpy as np
+
+        data = self.left + self._read_exact(max(0, self.chunk_bytes - len(self.left)))
+        usable = len(data) // self.frame_bytes * self.frame_bytes
+        self.left = data[usable:] if usable and len(data) >= self.chunk_bytes else b""
+        if usable == 0:
+            return np.zeros(0, np.float32)
+        x = np.frombuffer(data[:usable], dtype="<i2").astype(np.float32) / 32768.0
+        return x.reshape(-1, self.channels).mean(axis=1).astype(np.float32)
+
+
+def cmd_transcribe(args, profiler, transcriber=None, stdin=None, out=None):
+    import numpy as np
+
+    from .preprocess import StreamSegmenter, resample
+    from .server.transcribe import read_wav
+
+    out = out or sys.stdout
+    t_load = time.perf_counter()
+    if transcriber is None:
+        from .server.transcribe import WorkflowTranscriber
+
+        try:
+            transcriber = WorkflowTranscriber(args.model, getattr(args, "device", "cpu"))
+        except Exception as exc:
+            print(f"What: {args.model} could not be loaded as a speech package.\nWhy: {exc}\n"
+                  "How: point `transcribe` at a speech-to-text workflow package (a waveform input, a token output, tokenizer.json).",
+                  file=sys.stderr)
+            return 2
+    profiler.spans.append(("model load", t_load, time.perf_counter()))
+    window = float(getattr(transcriber, "window_seconds", 30.0) or 30.0)
+    seg_seconds = args.segment_seconds if args.segment_seconds else window
+    if seg_seconds > window + 1e-6:
+        print(f"What: --segment-seconds {seg_seconds:g} was rejected.\nWhy: this model's declared audio input holds at most {window:.2f}s, "
+              f"so a longer segment could not be encoded.\nHow: request at most {window:.2f}s per segment.", file=sys.stderr)
+        return 2
+    want_rate = int(getattr(transcriber, "sample_rate", 16000) or 16000)
+    totals = {"audio_s": 0.0, "compute_s": 0.0, "segments": 0, "slowest_ms": 0.0}
+    index = [0]
+
+    def drain(segments, rate):
+        for samples, start_sample in segments:
+            start, dur = start_sample / rate, len(samples) / rate
+            t0 = time.perf_counter()
+            x = resample(samples, rate, want_rate) if rate != want_rate else samples
+            text = str(transcriber.transcribe(np.asarray(x, dtype=np.float32), args.language or None)).strip()
+            dt = time.perf_counter() - t0
+            totals["audio_s"] += dur
+            totals["compute_s"] += dt
+            totals["segments"] += 1
+            totals["slowest_ms"] = max(totals["slowest_ms"], dt * 1e3)
+            if not text:
+                continue
+            print(format_transcript(args.format, index[0], start, start + dur, text), file=out, flush=True)   # per segment: a live stream is read while it runs
+            index[0] += 1
+
+    def segmenter(rate):
+        return StreamSegmenter(rate, seg_seconds, args.silence_seconds, args.silence_threshold, args.min_segment_seconds)
+
+    t_run = time.perf_counter()
+    for source in (args.audio or ["-"]):
+        if source == "-":
+            try:
+                reader = PcmStreamReader(stdin or sys.stdin.buffer, args.sample_rate, args.channels)
+            except ValueError as exc:
+                print(f"What: standard input could not be read as audio.\nWhy: {exc}\nHow: pipe raw 16-bit PCM (with --sample-rate / "
+                      "--channels) or a 16-bit PCM WAV stream.", file=sys.stderr)
+                return 2
+            print(f"listening on stdin: {reader.sample_rate} Hz, {reader.channels} channel{'s' if reader.channels != 1 else ''}, "
+                  f"up to {seg_seconds:.2f}s per segment (Ctrl-C to stop)", file=sys.stderr)
+            seg = segmenter(reader.sample_rate)
+            try:
+                while True:
+                    chunk = reader.read_chunk()
+                    if len(chunk) == 0:
+                        break
+                    drain(seg.push(chunk), reader.sample_rate)
+            except KeyboardInterrupt:
+                pass
+            last = seg.flush()
+            drain([last] if last is not None else [], reader.sample_rate)
+        else:
+            try:
+                with open(source, "rb") as f:
+                    samples, rate = read_wav(f.read())
+            except OSError as exc:
+                print(f"What: the audio file {source} could not be read.\nWhy: {exc}\nHow: check the path and that the file is readable.",
+                      file=sys.stderr)
+                return 2
+            except ValueError as exc:
+                print(f"What: the audio file {source} could not be decoded.\nWhy: {exc}\nHow: provide a PCM WAV file "
+                      "(convert with `ffmpeg -i in.mp3 -ar 16000 -ac 1 out.wav`).", file=sys.stderr)
+                return 2
+            seg = segmenter(rate)
+            drain(seg.push(samples), rate)
+            last = seg.flush()
+            drain([last] if last is not None else [], rate)
+    profiler.spans.append(("transcription", t_run, time.perf_counter()))
+    if totals["segments"] and totals["audio_s"] > 0:
+        rtf = totals["compute_s"] / totals["audio_s"]
+        print("transcribed %.2fs of audio in %d segment%s, real-time factor %.3fx (below 1.0 keeps up with a live stream), slowest segment %.0f ms"
+              % (totals["audio_s"], totals["segments"], "" if totals["segments"] == 1 else "s", rtf, totals["slowest_ms"]), file=sys.stderr)
+    if profiler.enabled and profiler.json_path:
+        rep = {"stages": [{"name": n, "ms": (b - a) * 1e3} for n, a, b in profiler.spans], "audio_seconds": totals["audio_s"],
+               "segments": totals["segments"], "slowest_segment_ms": totals["slowest_ms"],
+               "real_time_factor": totals["compute_s"] / totals["audio_s"] if totals["audio_s"] else None}
+        json.dump(rep, open(profiler.json_path, "w"), indent=1)
+    return 0
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="onnx-genai-b200")
     ap.add_argument("--profile", action="store_true")
@@ -576,6 +753,8 @@ def main(argv=None):
     s.add_argument("--image-package", default="", help="text-to-image workflow package to serve at /v1/images/generations and /sdapi/v1/txt2img")
     s.add_argument("--speech-package", default="", help="text-to-speech workflow package to serve at /v1/audio/speech")
     s.add_argument("--transcribe-package", default="", help="speech-to-text workflow package to serve at /v1/audio/transcriptions")
+    s.add_argument("--multimodal-package", default="",
+                   help="workflow package with a typed image or audio input: chat requests that carry an image_url / input_audio part run on it")
     s.add_argument("--models-config", default="", help="YAML or JSON file: models: {name: {path: DIR, ...engine flags}}")
     s.add_argument("--max-context", type=int, default=0)
     _add_engine(s)
@@ -594,6 +773,19 @@ def main(argv=None):
     ic = sub.add_parser("import-comfyui", help="convert a ComfyUI API-format graph into a workflow metadata document")
     ic.add_argument("graph")
     ic.add_argument("-o", "--out", default="-")
+    tr = sub.add_parser("transcribe", help="speech to text: WAV files, or a live 16-bit PCM stream on standard input")
+    tr.add_argument("model", help="speech-to-text workflow package directory")
+    tr.add_argument("audio", nargs="*", help="PCM WAV files; `-` (the default) reads a stream from standard input and prints each "
+                                             "segment as soon as it is recognised")
+    tr.add_argument("--language", default="", help="spoken language token, e.g. en or zh (default: the model's own choice)")
+    tr.add_argument("--format", default="text", choices=["text", "json", "srt"])
+    tr.add_argument("--segment-seconds", type=float, default=0.0, help="longest segment transcribed at once (default and maximum: the model's window)")
+    tr.add_argument("--silence-seconds", type=float, default=0.5, help="silence that ends a segment early; 0 cuts on the window alone")
+    tr.add_argument("--silence-threshold", type=float, default=0.01, help="amplitude at or below which audio counts as silence")
+    tr.add_argument("--min-segment-seconds", type=float, default=0.1, help="shortest segment worth transcribing (ignores brief clicks)")
+    tr.add_argument("--sample-rate", type=int, default=16000, help="rate of raw PCM16 on standard input (a WAV header overrides it)")
+    tr.add_argument("--channels", type=int, default=1, help="channels of raw PCM16 on standard input; they are mixed to mono")
+    tr.add_argument("--device", default="cpu")
     rw = sub.add_parser("run-workflow", help="run a workflow package (every ONNX component on the generic graph executor)")
     rw.add_argument("package", help="directory with inference_metadata.yaml and the component graphs")
     rw.add_argument("--input", action="append", default=[], metavar="NAME=VALUE",
@@ -611,7 +803,7 @@ def main(argv=None):
         return 0
     profiler = Profiler(args.profile, args.profile_json, args.profile_trace)
     return {"generate": cmd_generate, "run": cmd_run, "serve": cmd_serve, "show": cmd_show, "validate": cmd_validate, "list": cmd_list,
-            "export": cmd_export}[args.cmd](args, profiler)
+            "export": cmd_export, "transcribe": cmd_transcribe}[args.cmd](args, profiler)
 
 
 if __name__ == "__main__":

@@ -330,6 +330,8 @@ class DecoderModel:
                                                                                          ctypes.c_int])
         lib.ogb_decoder_launches.restype = ctypes.c_longlong
         lib.ogb_decoder_launches.argtypes = [ctypes.c_void_p]
+        lib.ogb_decoder_counter.restype = ctypes.c_longlong
+        lib.ogb_decoder_counter.argtypes = [ctypes.c_void_p, ctypes.c_int]
         lib.ogb_decoder_set_split_scratch.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
         lib.ogb_decoder_set_split_scratch.restype = None
         inter_local = w.layers[0].gate_up_w.shape[0] // 2
@@ -351,6 +353,10 @@ class DecoderModel:
         lib.ogb_decoder_set_num_pages.restype = None
         self.native = lib.ogb_decoder_create(ip, kv.num_pages, fp, gp, lp)   # backed pages: ids beyond them are refused
         return bool(self.native)
+
+    def native_counter(self, which: int) -> int:
+        """Kernels the C++ step executor has launched so far: 0 all, 1 scatter-epilogue GEMMs, 2 exchange kernels."""
+        return int(self._native_lib.ogb_decoder_counter(self.native, which)) if self.native else 0
 
     def set_backed_pages(self, num_pages: int) -> None:
         """The KV pool grew in place: the step executor bounds page ids by the new backed count from now on."""

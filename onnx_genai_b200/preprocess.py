@@ -221,6 +221,105 @@ def resample(samples, src_rate: int, dst_rate: int, taps: int = 32) -> np.ndarra
     return (gathered * w).sum(1).float().numpy()
 
 
+class StreamSegmenter:
+    """Cuts a growing waveform into transcribable segments, incrementally.
+
+    A speech encoder takes a bounded window, so a long recording -- or a live stream -- is split before it is
+    transcribed: at a run of silence when there is one (words stay whole), at the window bound otherwise.  Feed
+    whatever arrives to :meth:`push`; it returns the segments that became final as ``(samples, start_sample)``;
+    :meth:`flush` returns the trailing partial segment once the input ends.  Nothing beyond the current segment is
+    buffered.  Behaviour follows the reference's segmenter (crates/onnx-genai-preprocess/src/audio.rs:225-382):
+    a sample is silent when its square is at most ``silence_rms**2``; ``silence_seconds`` of consecutive silence end
+    a segment and are dropped, as is the rest of the gap; a voiced burst shorter than ``min_seconds`` between two
+    silences is discarded; a cut forced by the window keeps everything, silence included."""
+
+    def __init__(self, sample_rate: int, max_seconds: float, silence_seconds: float = 0.5, silence_rms: float = 0.01,
+                 min_seconds: float = 0.1):
+        if sample_rate <= 0:
+            raise PreprocessError("the sample rate must be positive")
+        n = lambda sec: int(round(max(0.0, float(sec)) * sample_rate))
+        self.max_samples = n(max_seconds)
+        if self.max_samples == 0:
+            raise PreprocessError("the maximum segment length rounds to zero samples")
+        self.silence_samples = n(silence_seconds)
+        self.threshold = max(0.0, float(silence_rms)) ** 2
+        self.min_samples = min(n(min_seconds), self.max_samples)
+        self.pending: list = []          # chunks of the current segment
+        self.pending_len = 0
+        self.pending_start = 0           # stream position of the first pending sample
+        self.trailing_silence = 0
+        self.in_gap = False
+
+    def _take(self, forced: bool):
+        voiced = self.pending_len - self.trailing_silence
+        keep = self.pending_len if forced else voiced
+        total = self.pending_len
+        buf = np.concatenate(self.pending) if self.pending else np.zeros(0, np.float32)
+        self.pending, self.pending_len, self.trailing_silence = [], 0, 0
+        start = self.pending_start
+        self.pending_start += total
+        if keep == 0 or (not forced and keep < self.min_samples):
+            return None
+        return buf[:keep].astype(np.float32), start
+
+    def push(self, samples):
+        x = np.asarray(samples, dtype=np.float32).reshape(-1)
+        silent = x * x <= self.threshold
+        out, i, n = [], 0, len(x)
+        while i < n:
+            if self.in_gap:
+                nz = np.flatnonzero(~silent[i:])
+                if len(nz) == 0:                       # the rest of this chunk is still the gap: drop it
+                    self.pending_start += n - i
+                    break
+                self.pending_start += int(nz[0])
+                i += int(nz[0])
+                self.in_gap = False
+            # how far can the current segment grow before one of the two cuts fires?
+            room = self.max_samples - self.pending_len
+            j_end = min(n, i + room)
+            cut = None
+            if self.silence_samples > 0:
+                # position (exclusive) at which the run of trailing silence reaches silence_samples
+                run = self.trailing_silence
+                seg = silent[i:j_end]
+                if seg.all():
+                    if run + len(seg) >= self.silence_samples:
+                        cut = i + (self.silence_samples - run)
+                else:
+                    # runs inside the chunk: scan for the first run (continuing `run`) that is long enough
+                    idx = np.flatnonzero(~seg)
+                    if run + int(idx[0]) >= self.silence_samples:
+                        cut = i + (self.silence_samples - run)
+                    else:
+                        gaps = np.diff(np.concatenate([idx, [len(seg)]])) - 1      # silent samples after each voiced one
+                        hit = np.flatnonzero(gaps >= self.silence_samples)
+                        if len(hit):
+                            cut = i + int(idx[hit[0]]) + 1 + self.silence_samples
+            stop = cut if cut is not None else j_end
+            piece = x[i:stop]
+            if len(piece):
+                self.pending.append(piece)
+                self.pending_len += len(piece)
+                sil = silent[i:stop]
+                if sil.all():
+                    self.trailing_silence += len(piece)
+                else:
+                    self.trailing_silence = len(piece) - 1 - int(np.flatnonzero(~sil)[-1])
+            i = stop
+            hit_window = self.pending_len >= self.max_samples
+            hit_silence = self.silence_samples > 0 and self.trailing_silence >= self.silence_samples
+            if hit_window or hit_silence:
+                seg_out = self._take(hit_window)
+                if seg_out is not None:
+                    out.append(seg_out)
+                self.in_gap = self.silence_samples > 0 and self.pending_len == 0
+        return out
+
+    def flush(self):
+        return self._take(False)
+
+
 def mel_filterbank(n_mels: int, n_fft: int, sample_rate: int) -> torch.Tensor:
     """Slaney-style triangular mel filters [n_mels, n_fft//2 + 1] (the scale Whisper's features use)."""
     def hz_to_mel(f):

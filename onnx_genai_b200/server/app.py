@@ -207,7 +207,8 @@ def _options_from_request(body: dict, default_max: int, max_cap: int) -> Generat
 
 def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int = 4096, max_queue_depth: int = 256,
                enable_debug_endpoints: bool = False, node_id: str = "node-0", admission_window_ms: float = 2.0,
-               default_reasoning_effort: str | None = None, image_pipeline=None, speech_pipeline=None, transcriber=None) -> FastAPI:
+               default_reasoning_effort: str | None = None, image_pipeline=None, speech_pipeline=None, transcriber=None,
+               media_chat=None) -> FastAPI:
     app = FastAPI(title="onnx-genai-b200")
     driver = EngineDriver(engine, max_queue_depth, admission_window_ms)
     metrics = Metrics()
@@ -403,18 +404,16 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
             msgs = body.get("messages")
             if not isinstance(msgs, list) or not msgs:
                 raise HTTPException(400, "messages must be a non-empty list of {role, content} objects")
-            norm = []
-            for m in msgs:
-                content = m.get("content")
-                if isinstance(content, list):
-                    parts = []
-                    for part in content:
-                        if part.get("type") == "text":
-                            parts.append(part.get("text", ""))
-                        else:
-                            raise HTTPException(400, f"content part of type {part.get('type')!r} is not supported by this text-only model")
-                    content = "".join(parts)
-                norm.append({**m, "content": content or ""})
+            from . import multimodal as mm
+
+            try:
+                norm, images, audio = mm.split_content(msgs)
+                if images or audio:
+                    # media attachments go to the mounted media chat (a workflow package with a typed media input)
+                    mm.admit_attachments(media_chat, model_name, len(images), len(audio))
+                    body["_media"] = {"image": images[0] if images else None, "audio": audio[0] if audio else None}
+            except mm.MediaError as exc:
+                raise HTTPException(exc.status, str(exc)) from exc
             tools = body.get("tools")
             if body.get("tool_choice") == "none":
                 tools = None
@@ -448,6 +447,41 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
             raise HTTPException(400, f"prompt has {len(ids)} tokens but the model's context is {limit}; shorten the prompt")
         return ids
 
+    async def _complete_with_media(body: dict, ids, opt, rid: str, created: int):
+        """A chat request that carries an image or an audio clip: the media chat's workflow runs the whole generation
+        (encoder, merge, decoder loop); the answer is returned whole, or as one content chunk when streaming."""
+        media = body["_media"]
+        loop = asyncio.get_running_loop()
+        t0 = time.perf_counter()
+        try:
+            out_ids = await loop.run_in_executor(None, lambda: media_chat.generate(
+                ids, image=media["image"], audio=media["audio"], max_new_tokens=opt.max_new_tokens))
+        except Exception as exc:
+            raise HTTPException(422, f"the media input could not be processed: {exc}") from exc
+        text = engine.detokenize(list(out_ids))
+        metrics.prompt_tokens(len(ids))
+        metrics.completion_tokens(len(out_ids))
+        metrics.ttft(time.perf_counter() - t0)
+        metrics.e2e(time.perf_counter() - t0)
+        usage = {"prompt_tokens": len(ids), "completion_tokens": len(out_ids), "total_tokens": len(ids) + len(out_ids)}
+        fin = "length" if len(out_ids) >= opt.max_new_tokens else "stop"
+        if body.get("stream"):
+            async def gen():
+                base = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": model_name}
+                yield _sse({**base, "choices": [{"index": 0, "delta": {"role": "assistant"}, "finish_reason": None}]})
+                if text:
+                    yield _sse({**base, "choices": [{"index": 0, "delta": {"content": text}, "finish_reason": None}]})
+                yield _sse({**base, "choices": [{"index": 0, "delta": {}, "finish_reason": fin}], "usage": usage})
+                yield "data: [DONE]\n\n"
+
+            return StreamingResponse(gen(), media_type="text/event-stream")
+        thought, answer = reasoning_mod.split(text, think)
+        msg = {"role": "assistant", "content": answer}
+        if thought is not None:
+            msg["reasoning_content"] = thought
+        return JSONResponse({"id": rid, "object": "chat.completion", "created": created, "model": model_name,
+                             "choices": [{"index": 0, "message": msg, "finish_reason": fin}], "usage": usage})
+
     async def _complete(body: dict, request: Request, chat: bool, session_header):
         opt = _options_from_request(body, 256, max_output_tokens)
         n_choices = body.get("n", 1)
@@ -458,6 +492,8 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
         ids = _prompt_ids(body, chat, session_header)
         rid = ("chatcmpl-" if chat else "cmpl-") + uuid.uuid4().hex[:24]
         created = int(time.time())
+        if body.get("_media"):
+            return await _complete_with_media(body, ids, opt, rid, created)
         q = await _run_generation(ids, opt, request)
         t0 = time.perf_counter()
         metrics.prompt_tokens(len(ids))
