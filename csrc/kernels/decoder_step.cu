@@ -100,14 +100,15 @@ extern "C" int ogb_gemm_bf16_scatter(const void* A, const void* W, int M, int N,
                                      int bn, int* status, void* stream_);
 extern "C" int ogb_tp_reduce_bcast(const void* rp, int rows, int n, int chunk, int tp, int nvls, int* status, void* stream);
 extern "C" int ogb_tp_exchange_norm(const void* rp, const void* norm_w, float eps, int rows, int n, int chunk, int tp, int nvls,
-                                    int* status, void* stream);
+                                    int pushed, int* status, void* stream);
 extern "C" int ogb_tp_wait_ready(const void* rp, int rows, int* status, void* stream);
 extern "C" int ogb_gemm_bf16_wait(const void* A, const void* W, void* C, const void* bias, const void* residual, void* C_f32,
                                   int M, int N, int K, int lda, int ldw, int ldc, int ldr, int epilogue, int bn,
                                   uint32_t* a_ready, uint32_t* a_done, unsigned long long a_wait_ns, int* status, void* stream_);
 
 // tp > 1: `tp_structs` = {scatter slot 0, reduce slot 0, scatter slot 1, reduce slot 1} device structs for this
-// step's row chunk, one word that is non-zero when the reduce structs carry NVSwitch multicast pointers, then the
+// step's row chunk, one flag word (bit 0: the reduce structs carry NVSwitch multicast pointers, bit 1: the scatter
+// epilogue pushes partials into the owners' buffers), then the
 // local addresses of the two slots' per-tile ready counters.  The residual stream p->x is then owned by rows
 // (each rank keeps its own chunk), p->h lives in the peer-mapped region, and a row-parallel projection is
 //   GEMM with the scatter epilogue  ->  exchange (reduce-scatter + residual + RMSNorm + all-gather of h)
@@ -122,12 +123,13 @@ extern "C" int ogb_decoder_step(void* plan, const int* token_ids, const int* pos
   const void* sc[2] = {nullptr, nullptr};
   const void* rd[2] = {nullptr, nullptr};
   uint32_t* ready[2] = {nullptr, nullptr};      // per-tile ready counters of the two slots; [k] + 64 is the slot's GEMM-done word
-  int nvls = 0;
+  int nvls = 0, pushed = 0;
   const bool tp = p->tp != 1;
   if (tp) {
     sc[0] = reinterpret_cast<const void*>(tp_structs[0]); rd[0] = reinterpret_cast<const void*>(tp_structs[1]);
     sc[1] = reinterpret_cast<const void*>(tp_structs[2]); rd[1] = reinterpret_cast<const void*>(tp_structs[3]);
-    nvls = tp_structs[4] != 0 ? 1 : 0;
+    nvls = (tp_structs[4] & 1) != 0 ? 1 : 0;
+    pushed = (tp_structs[4] & 2) != 0 ? 1 : 0;
     ready[0] = reinterpret_cast<uint32_t*>(tp_structs[5]);
     ready[1] = reinterpret_cast<uint32_t*>(tp_structs[6]);
   }
@@ -170,7 +172,7 @@ extern "C" int ogb_decoder_step(void* plan, const int* token_ids, const int* pos
       STEP_CHECK(ogb_rmsnorm_bf16(p->x, nullptr, L.ln2, p->h, T, hid, hid, hid, p->eps, stream));
     } else {
       STEP_CHECK(ogb_gemm_bf16_scatter(p->attn, L.o_w, T, hid, attn_n, attn_n, attn_n, sc[0], 0, p->status, stream));
-      STEP_CHECK(ogb_tp_exchange_norm(rd[0], L.ln2, p->eps, T, hid, tp_chunk, p->tp, nvls, p->status, stream));
+      STEP_CHECK(ogb_tp_exchange_norm(rd[0], L.ln2, p->eps, T, hid, tp_chunk, p->tp, nvls, pushed, p->status, stream));
       p->launches_scatter += 2;     // this layer's two row-parallel projections (the second one follows below)
       p->launches_exchange += 2;
     }
@@ -184,7 +186,7 @@ extern "C" int ogb_decoder_step(void* plan, const int* token_ids, const int* pos
       STEP_CHECK(ogb_gemm_bf16_scatter(p->act, L.down_w, T, hid, p->inter_local, p->inter_local, p->inter_local, sc[1], 0,
                                        p->status, stream));
       const void* next_norm = (l + 1 < p->num_layers) ? p->layers[l + 1].ln1 : p->final_norm;
-      STEP_CHECK(ogb_tp_exchange_norm(rd[1], next_norm, p->eps, T, hid, tp_chunk, p->tp, nvls, p->status, stream));
+      STEP_CHECK(ogb_tp_exchange_norm(rd[1], next_norm, p->eps, T, hid, tp_chunk, p->tp, nvls, pushed, p->status, stream));
     }
   }
   if (R > 0) {

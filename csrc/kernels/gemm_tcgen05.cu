@@ -305,8 +305,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 uint4 v = *reinterpret_cast<const uint4*>(stg + r_loc * kStagingPitch + ch * 16);
                 __nv_bfloat16* dst;
                 if constexpr (EPI == kEpiScatter) {
-                  // the partial product stays in this rank's own buffer; the owner of the row pulls it
-                  dst = sc->staging[sc->rank] + static_cast<size_t>(grow) * N + gcol;
+                  if (sc->push) {
+                    // straight into the buffer of the rank that owns the row (a peer store over NVLink, or a local one):
+                    // slab [this rank][row within the owner's chunk]; the stores drain under the next tile's main loop
+                    const int owner = grow / sc->chunk;
+                    dst = sc->staging[owner] + (static_cast<size_t>(sc->rank) * sc->chunk + (grow - owner * sc->chunk)) * N + gcol;
+                  } else {
+                    // the partial product stays in this rank's own buffer; the owner of the row pulls it
+                    dst = sc->staging[sc->rank] + static_cast<size_t>(grow) * N + gcol;
+                  }
                 } else {
                   dst = C + static_cast<size_t>(grow) * ldc + gcol;
                 }

@@ -233,7 +233,9 @@ __global__ void __launch_bounds__(kRbThreads) tp_reduce_bcast_nvls_kernel(const 
 // Counters are cleared by whoever consumed them: tile_cnt[g] (arrivals from the scatter epilogues) by the last of
 // the group's passes to get through its wait, the ready counters by the last CTA of the GEMM that waited on them.
 // ------------------------------------------------------------------------------------------------------
-template <bool NVLS, int TP, int VPL>
+// PUSHED: the partials were stored into this rank's buffer by their producers ([source][chunk][n], see TpScatter::push),
+// so the reduction reads tp local slabs; otherwise it pulls (multimem.ld_reduce when NVLS, peer loads when not).
+template <bool NVLS, int TP, int VPL, bool PUSHED>
 __global__ void __launch_bounds__(kRbThreads) tp_exchange_norm_kernel(const TpReduce* __restrict__ rp,
                                                                        const __nv_bfloat16* __restrict__ norm_w, float eps,
                                                                        int rows, int* status) {
@@ -272,7 +274,7 @@ __global__ void __launch_bounds__(kRbThreads) tp_exchange_norm_kernel(const TpRe
     if (ok_sh && warp < kTpNormRows && local0 + warp < own_rows) {
       const size_t row_off = static_cast<size_t>(row) * n;
       uint4 xv[VPL], pv[VPL];
-      if constexpr (NVLS) {
+      if constexpr (NVLS && !PUSHED) {
 #pragma unroll
         for (int j = 0; j < VPL; ++j) {
           const int v = lane + 32 * j;
@@ -298,7 +300,15 @@ __global__ void __launch_bounds__(kRbThreads) tp_exchange_norm_kernel(const TpRe
         if (v < nvec) {
           float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
           add_bf16x8(acc, xv[j]);
-          if constexpr (NVLS) {
+          if constexpr (PUSHED) {
+            // slab s = what rank s produced for this rank's rows, already in local memory
+            const __nv_bfloat16* base = r.part[r.rank] + (static_cast<size_t>(local0 + warp)) * n + v * 8;
+            uint4 src[TP];
+#pragma unroll
+            for (int s = 0; s < TP; ++s) src[s] = *reinterpret_cast<const uint4*>(base + static_cast<size_t>(s) * r.chunk * n);
+#pragma unroll
+            for (int s = 0; s < TP; ++s) add_bf16x8(acc, src[s]);      // fixed order: independent of arrival order
+          } else if constexpr (NVLS) {
             add_bf16x8(acc, pv[j]);
           } else {
             uint4 src[TP];
@@ -392,9 +402,41 @@ __global__ void tp_signal_rows_kernel(const TpScatter* __restrict__ scp, int row
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(cnt), "r"(units) : "memory");
 }
 
+// Copies rows [0, rows) of a local partial-sum matrix [rows, n] into the buffers of the ranks that own them (slab of
+// this rank, see TpScatter::push) and bumps the owners' arrival counters.  One CTA per 32-row group, so the CTA's
+// stores and its single releasing signal belong to one owner.
+__global__ void __launch_bounds__(256) tp_push_rows_kernel(const TpScatter* __restrict__ scp, const __nv_bfloat16* __restrict__ src,
+                                                           int rows) {
+  const TpScatter& sc = *scp;
+  const int row0 = blockIdx.x * 32;
+  if (row0 >= rows) return;
+  const int owner = row0 / sc.chunk;
+  const int nvec = sc.n / 8;
+  const int last = min(32, rows - row0);
+  __nv_bfloat16* dst = sc.staging[owner] + (static_cast<size_t>(sc.rank) * sc.chunk + (row0 - owner * sc.chunk)) * sc.n;
+  for (int i = threadIdx.x; i < last * nvec; i += blockDim.x) {
+    const int rr = i / nvec, v = i % nvec;
+    reinterpret_cast<uint4*>(dst + static_cast<size_t>(rr) * sc.n)[v] =
+        reinterpret_cast<const uint4*>(src + static_cast<size_t>(row0 + rr) * sc.n)[v];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t* cnt = sc.tile_cnt[owner] + (row0 - owner * sc.chunk) / 32;
+    __threadfence_system();
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(cnt), "r"(static_cast<uint32_t>(sc.n / 32)) : "memory");
+  }
+}
+
 }  // namespace ogb
 
 using namespace ogb;
+
+extern "C" int ogb_tp_push_rows(const void* sc, const void* src, int rows, void* stream) {
+  if (rows <= 0) return 0;
+  tp_push_rows_kernel<<<(rows + 31) / 32, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const TpScatter*>(sc), static_cast<const __nv_bfloat16*>(src), rows);
+  return static_cast<int>(cudaGetLastError());
+}
 
 // Publishes rows [0, rows) of the local staging buffer described by `sc` (a device TpScatter) to their owners;
 // ogb_tp_reduce_bcast on the same stream then folds all ranks' partials into the residual stream.
@@ -462,9 +504,10 @@ extern "C" int ogb_tp_reduce_bcast(const void* rp, int rows, int n, int chunk, i
 
 // Row-sharded form of the exchange (see tp_exchange_norm_kernel): x_own[own rows] += sum over ranks of the staged
 // partials, h[own rows] = RMSNorm(x_own) * norm_w on every rank, ready counters of the rows' tiles bumped everywhere.
-// Must follow ogb_gemm_bf16_scatter (or ogb_tp_signal_rows) on the same stream.
+// Must follow ogb_gemm_bf16_scatter (or ogb_tp_push_rows / ogb_tp_signal_rows) on the same stream.  pushed != 0: the
+// producers stored their partials into the owners' buffers (TpScatter::push), so the sum reads local memory.
 extern "C" int ogb_tp_exchange_norm(const void* rp, const void* norm_w, float eps, int rows, int n, int chunk, int tp, int nvls,
-                                    int* status, void* stream) {
+                                    int pushed, int* status, void* stream) {
   if (rows <= 0) return 0;
   if (n % 8 || n > 16 * 256 || chunk % 32 || chunk / 32 > kTpMaxGroups || rows > kTpMaxTiles * 128) return -3;
   const TpReduce* r = static_cast<const TpReduce*>(rp);
@@ -475,20 +518,37 @@ extern "C" int ogb_tp_exchange_norm(const void* rp, const void* norm_w, float ep
   if (grid > cap) grid = cap;
   const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(norm_w);
   const int vpl = (n / 8 + 31) / 32;                              // 16-byte vectors per lane
-#define OGB_EXCH(NV, TPN)                                                                                     \
-  do {                                                                                                        \
-    if (vpl <= 8) tp_exchange_norm_kernel<NV, TPN, 8><<<grid, kRbThreads, 0, st>>>(r, w, eps, rows, status);     \
-    else tp_exchange_norm_kernel<NV, TPN, 16><<<grid, kRbThreads, 0, st>>>(r, w, eps, rows, status);             \
-    return static_cast<int>(cudaGetLastError());                                                              \
+#define OGB_EXCH(NV, TPN, PU)                                                                                          \
+  do {                                                                                                             \
+    if (vpl <= 8) tp_exchange_norm_kernel<NV, TPN, 8, PU><<<grid, kRbThreads, 0, st>>>(r, w, eps, rows, status);     \
+    else tp_exchange_norm_kernel<NV, TPN, 16, PU><<<grid, kRbThreads, 0, st>>>(r, w, eps, rows, status);             \
+    return static_cast<int>(cudaGetLastError());                                                                   \
   } while (0)
+  if (pushed) {
+    // partials already local: the template's TP is the number of slabs; NVLS only selects how h and the counters go out
+    if (nvls) {
+      switch (tp) {
+        case 2: OGB_EXCH(true, 2, true);
+        case 4: OGB_EXCH(true, 4, true);
+        case 8: OGB_EXCH(true, 8, true);
+        default: return -5;
+      }
+    }
+    switch (tp) {
+      case 2: OGB_EXCH(false, 2, true);
+      case 4: OGB_EXCH(false, 4, true);
+      case 8: OGB_EXCH(false, 8, true);
+      default: return -5;
+    }
+  }
   if (nvls) {
-    if (tp == 2 || tp == 4 || tp == 8) OGB_EXCH(true, 1);
+    if (tp == 2 || tp == 4 || tp == 8) OGB_EXCH(true, 1, false);
     return -5;
   }
   switch (tp) {
-    case 2: OGB_EXCH(false, 2);
-    case 4: OGB_EXCH(false, 4);
-    case 8: OGB_EXCH(false, 8);
+    case 2: OGB_EXCH(false, 2, false);
+    case 4: OGB_EXCH(false, 4, false);
+    case 8: OGB_EXCH(false, 8, false);
     default: return -5;
   }
 #undef OGB_EXCH

@@ -13,9 +13,13 @@ constexpr int kTpSlots = 2;          // slot 0: o_proj, slot 1: down_proj (separ
 constexpr int kTpMaxGroups = 256;    // 32-row groups one rank can own (8192 rows)
 
 struct TpScatter {
-  __nv_bfloat16* staging[kMaxTp];    // rank p's partial-product buffer for this slot: [rows][N] (only [rank] is written)
+  __nv_bfloat16* staging[kMaxTp];    // rank p's partial-product buffer for this slot
   uint32_t* tile_cnt[kMaxTp];        // rank p's arrival counters for this slot, one per owned 32-row group
   int rank, tp, chunk, n;            // chunk = rows owned per rank (multiple of 32)
+  // push = 0: the partial stays in this rank's own buffer, indexed by global row ([rows][n]); the owner pulls it.
+  // push = 1: the partial is stored straight into the OWNER's buffer over NVLink, laid out [source rank][chunk][n]
+  //           (row = source * chunk + row within the owner's chunk); the owner then sums tp local slabs.
+  int push, pad0, pad1, pad2;
 };
 
 struct TpReduce {

@@ -9,14 +9,13 @@ delegates JSON-Schema/regex/Lark grammars to llguidance; that library is not ava
 
 * ``json``         is a hand-written incremental JSON recogniser (a pushdown automaton over characters);
 * ``regex``        uses the ``regex`` package's partial matching;
-* ``json_schema``  compiles the schema to a regular expression for the subset below and reuses ``regex``;
+* ``json_schema``  compiles the schema to a context-free grammar (engine/grammar.py: nested and recursive schemas,
+                   required / optional properties, additionalProperties, prefixItems, $ref, formats) run by an
+                   incremental Earley recogniser; :func:`schema_to_regex` remains for callers that want a pattern;
 * ``choice``       accepts prefixes of the listed strings;
-* ``lark``         is rejected with an error that says so.
+* ``lark``         parses the grammar text (the commonly used part of Lark's syntax) into the same recogniser.
 
-JSON-Schema subset: ``type`` string / integer / number / boolean / null, ``enum`` and ``const`` of scalars,
-``array`` with ``items`` (and ``minItems``/``maxItems``), ``object`` with ``properties`` emitted in declaration
-order (all properties are produced; ``additionalProperties`` is treated as false), ``anyOf``/``oneOf`` of those,
-string ``pattern``, ``minLength``/``maxLength``.  Anything else raises ``ValueError`` naming the keyword.
+A schema keyword the compiler does not know raises ``ValueError`` naming it.
 """
 from __future__ import annotations
 
@@ -439,17 +438,40 @@ def make_constraint(spec) -> Constraint | None:
     if kind == "json_object":
         return JsonConstraint(require_object=True)
     if kind == "json_schema":
+        from .grammar import GrammarConstraint, schema_to_grammar
+
         schema = json.loads(arg) if isinstance(arg, str) else arg
-        c = RegexConstraint(schema_to_regex(schema))
-        c.name = "json_schema"
-        return c
+        return _GrammarAdapter(GrammarConstraint(schema_to_grammar(schema), "json_schema"))
     if kind == "regex":
         return RegexConstraint(arg)
     if kind == "choice":
         return ChoiceConstraint(arg)
     if kind == "lark":
-        raise ValueError("Lark grammars need llguidance, which is not part of this build; use json, json_schema, regex or choice")
-    raise ValueError(f"unknown constraint kind {kind!r}; use json, json_object, json_schema, regex or choice")
+        from .grammar import GrammarConstraint, parse_lark
+
+        return _GrammarAdapter(GrammarConstraint(parse_lark(arg), "lark"))
+    raise ValueError(f"unknown constraint kind {kind!r}; use json, json_object, json_schema, regex, choice or lark")
+
+
+class _GrammarAdapter(Constraint):
+    """A grammar recogniser (engine/grammar.py) behind the :class:`Constraint` interface."""
+
+    def __init__(self, inner):
+        self.inner = inner
+        self.name = inner.name
+
+    def allowed(self, token_texts):
+        return self.inner.allowed(token_texts)
+
+    def advance(self, text):
+        self.inner.advance(text)
+
+    @property
+    def complete(self):
+        return self.inner.complete
+
+    def terminal(self, token_texts):
+        return self.inner.terminal(token_texts)
 
 
 class ConstraintProcessor(LogitProcessor):

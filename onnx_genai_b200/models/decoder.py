@@ -373,9 +373,10 @@ class DecoderModel:
         chunk = fc.chunk_for(rows)
         hit = self._tp_args_cache.get(chunk)
         if hit is None:
-            sc0, rd0 = fc._get_structs(0, chunk)
-            sc1, rd1 = fc._get_structs(1, chunk)
-            hit = (ctypes.c_uint64 * 7)(sc0.data_ptr(), rd0.data_ptr(), sc1.data_ptr(), rd1.data_ptr(), 1 if fc.nvls else 0,
+            sc0, rd0 = fc._get_structs(0, chunk, fc.push)
+            sc1, rd1 = fc._get_structs(1, chunk, fc.push)
+            hit = (ctypes.c_uint64 * 7)(sc0.data_ptr(), rd0.data_ptr(), sc1.data_ptr(), rd1.data_ptr(),
+                                        (1 if fc.nvls else 0) | (2 if fc.push else 0),
                                         fc.ready_ptrs(0)[0], fc.ready_ptrs(1)[0])
             self._tp_args_cache[chunk] = hit
         return hit, chunk

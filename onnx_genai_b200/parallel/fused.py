@@ -49,7 +49,8 @@ MAX_GROUPS = 256
 
 class _Scatter(ctypes.Structure):
     _fields_ = [("staging", ctypes.c_uint64 * MAX_TP), ("tile_cnt", ctypes.c_uint64 * MAX_TP),
-                ("rank", ctypes.c_int), ("tp", ctypes.c_int), ("chunk", ctypes.c_int), ("n", ctypes.c_int)]
+                ("rank", ctypes.c_int), ("tp", ctypes.c_int), ("chunk", ctypes.c_int), ("n", ctypes.c_int),
+                ("push", ctypes.c_int), ("pad0", ctypes.c_int), ("pad1", ctypes.c_int), ("pad2", ctypes.c_int)]
 
 
 class _Reduce(ctypes.Structure):
@@ -86,7 +87,9 @@ def _lib():
     lib.ogb_tp_reduce_bcast.argtypes = [P, I, I, I, I, I, P, P]
     lib.ogb_tp_signal_rows.argtypes = [P, I, P]
     lib.ogb_tp_signal_rows.restype = I
-    lib.ogb_tp_exchange_norm.argtypes = [P, P, ctypes.c_float, I, I, I, I, I, P, P]
+    lib.ogb_tp_exchange_norm.argtypes = [P, P, ctypes.c_float, I, I, I, I, I, I, P, P]
+    lib.ogb_tp_push_rows.argtypes = [P, P, I, P]
+    lib.ogb_tp_push_rows.restype = I
     lib.ogb_tp_exchange_norm.restype = I
     lib.ogb_tp_wait_ready.argtypes = [P, I, P, P]
     lib.ogb_tp_wait_ready.restype = I
@@ -139,7 +142,9 @@ class FusedComm:
         tp = self.world
         self.hidden, self.max_tokens = hidden, max_tokens
         self.chunk_max = ((max_tokens + tp - 1) // tp + 31) // 32 * 32
-        stage_bytes = max_tokens * hidden * 2          # one partial-product buffer [max_tokens, hidden] per slot
+        # one partial-product buffer per slot: [max_tokens, hidden] when owners pull, [tp][chunk][hidden] when producers
+        # push (chunk is rounded up to 32 rows, so the pushed layout can need a little more)
+        stage_bytes = max(max_tokens, tp * self.chunk_max) * hidden * 2
         align = lambda v: (v + 255) // 256 * 256
         self.off_stage = [0, align(stage_bytes)]
         self.off_x = self.off_stage[1] + align(stage_bytes)
@@ -152,6 +157,9 @@ class FusedComm:
         self.off_gdone = self.off_ready + SLOTS * READY_WORDS * 4
         self.wait_limit_ns = 0
         self.x_own_ptr = 0
+        # OGB_TP_PUSH=0: the scatter epilogue keeps partials local and the owners pull them (multimem.ld_reduce / peer loads)
+        self.push = os.environ.get("OGB_TP_PUSH", "1") != "0"
+        self._partial_scratch = None
         return self.off_cnt + align(self.cnt_words * 4)
 
     @classmethod
@@ -279,8 +287,8 @@ class FusedComm:
     def _x_cnt(self, p):
         return self.peer_ptrs[p] + self.off_cnt + SLOTS * MAX_GROUPS * 4
 
-    def _get_structs(self, slot: int, chunk: int):
-        key = (slot, chunk)
+    def _get_structs(self, slot: int, chunk: int, push: bool = False):
+        key = (slot, chunk, bool(push))
         hit = self._structs.get(key)
         if hit is not None:
             return hit
@@ -293,6 +301,7 @@ class FusedComm:
             rd.x[p] = self.peer_ptrs[p] + self.off_x
             rd.x_cnt[p] = self._x_cnt(p)
         sc.rank, sc.tp, sc.chunk, sc.n = self.rank, tp, chunk, self.hidden
+        sc.push = 1 if push else 0
         rd.tile_cnt = self._tile_cnt(self.rank, slot)
         rd.done_cnt = self.local_ptr + self.off_cnt + (SLOTS * MAX_GROUPS + 8) * 4
         if self.nvls:
@@ -386,7 +395,7 @@ class FusedComm:
     def _exchange_norm(self, rd, norm_w, eps, rows, chunk, st, stream):
         with ops.timed_region("tp_exchange_norm"):
             rc = self.lib.ogb_tp_exchange_norm(rd.data_ptr(), norm_w.data_ptr(), float(eps), rows, self.hidden, chunk, self.world,
-                                               1 if self.nvls else 0, st, stream)
+                                               1 if self.nvls else 0, 1 if self.push else 0, st, stream)
         _native.check(rc, "ogb_tp_exchange_norm")
         ops.launch_counts["tp_exchange_norm"] += 1
         self.calls += 1
@@ -397,7 +406,7 @@ class FusedComm:
         assert self.x_own_ptr, "bind_residual() first"
         self._guard(rows, slot)
         chunk = self.chunk_for(rows)
-        sc, rd = self._get_structs(slot, chunk)
+        sc, rd = self._get_structs(slot, chunk, self.push)
         st = ops.status_word(self.device).data_ptr()
         stream = torch.cuda.current_stream().cuda_stream
         with ops.timed_region("gemm_scatter[K=%d]" % a.shape[1]):
@@ -412,11 +421,15 @@ class FusedComm:
         assert self.x_own_ptr, "bind_residual() first"
         self._guard(rows, slot)
         chunk = self.chunk_for(rows)
-        sc, rd = self._get_structs(slot, chunk)
+        sc, rd = self._get_structs(slot, chunk, self.push)
         st = ops.status_word(self.device).data_ptr()
         stream = torch.cuda.current_stream().cuda_stream
-        rc = self.lib.ogb_tp_signal_rows(sc.data_ptr(), rows, stream)
-        _native.check(rc, "ogb_tp_signal_rows")
+        if self.push:      # the partial sits in local scratch: copy each 32-row group to its owner and signal it
+            rc = self.lib.ogb_tp_push_rows(sc.data_ptr(), self._partial_scratch.data_ptr(), rows, stream)
+            _native.check(rc, "ogb_tp_push_rows")
+        else:
+            rc = self.lib.ogb_tp_signal_rows(sc.data_ptr(), rows, stream)
+            _native.check(rc, "ogb_tp_signal_rows")
         ops.launch_counts["tp_signal_rows"] += 1
         self._exchange_norm(rd, norm_w, eps, rows, chunk, st, stream)
 
@@ -433,6 +446,11 @@ class FusedComm:
     def staging_view(self, slot: int, rows: int):
         """This rank's staging buffer of ``slot`` as a [rows, hidden] bf16 tensor: kernels that produce a partial
         sum of the residual stream write it here, then call :meth:`reduce_partial`."""
+        if self.push and self.x_own_ptr:
+            # producers push: kernels write their partial into local scratch, reduce_partial_norm() forwards the rows
+            if self._partial_scratch is None:
+                self._partial_scratch = torch.zeros(self.max_tokens, self.hidden, dtype=torch.bfloat16, device=self.device)
+            return self._partial_scratch[:rows]
         t = torch.as_tensor(_CudaArray(self.local_ptr + self.off_stage[slot], (self.max_tokens, self.hidden), "<u2"),
                             device=self.device).view(torch.bfloat16)
         return t[:rows]

@@ -42,8 +42,8 @@ def test_schema_compiles_to_a_regex_for_the_documented_subset():
         assert not rx.fullmatch(json.dumps(bad)), bad
     with pytest.raises(ValueError, match="patternProperties"):
         cons.schema_to_regex({"type": "object", "patternProperties": {}})
-    with pytest.raises(ValueError, match="llguidance"):
-        cons.make_constraint(("lark", "start: 'a'"))
+    with pytest.raises(ValueError, match="Lark grammar, line 1"):
+        cons.make_constraint(("lark", "start: 'a'"))          # Lark strings use double quotes
 
 
 @pytest.fixture(scope="module")
@@ -72,7 +72,7 @@ def test_regex_choice_and_schema_constraints_through_the_engine(engine):
     res = engine.generate("obj", GenerateOptions(max_new_tokens=120, greedy=False, seed=2, constraint=("json_schema", schema)))
     if res.finish_reason == "stop":
         doc = json.loads(res.text)
-        assert set(doc) == {"n", "ok"} and isinstance(doc["n"], int) and isinstance(doc["ok"], bool)
+        assert isinstance(doc, dict) and isinstance(doc.get("n", 0), int) and isinstance(doc.get("ok", True), bool)    # neither is required
     batch = engine.generate_batch(["a", "b"], GenerateOptions(max_new_tokens=30, greedy=False, seed=9, constraint=("regex", r"(yes|no)!")))
     assert all(r.text in ("yes!", "no!") for r in batch)
 
@@ -85,7 +85,8 @@ def test_server_response_format_uses_the_constraint(engine):
     with TestClient(create_app(engine, model_name="tiny")) as client:
         body = {"model": "tiny", "messages": [{"role": "user", "content": "give json"}], "max_tokens": 160, "temperature": 0.8, "seed": 4,
                 "response_format": {"type": "json_schema", "json_schema": {"name": "t", "schema": {
-                    "type": "object", "properties": {"city": {"type": "string", "maxLength": 6}, "pop": {"type": "integer"}}}}}}
+                    "type": "object", "properties": {"city": {"type": "string", "maxLength": 6}, "pop": {"type": "integer"}},
+                    "required": ["city", "pop"], "additionalProperties": False}}}}
         r = client.post("/v1/chat/completions", json=body)
         assert r.status_code == 200, r.text
         choice = r.json()["choices"][0]
