@@ -18,6 +18,11 @@
 //   TMEM holds two accumulators so the epilogue of tile i overlaps the main loop of tile i+1.
 // Every wait is bounded; a wait that runs out sets kStatusWaitTimeout in *status, the CTA
 // drains and frees its TMEM, and the kernel returns.
+#include <stdlib.h>
+
+#include <mutex>
+#include <unordered_map>
+
 #include "common.cuh"
 #include "ogb_kernels.h"
 #include "tp_comm.cuh"
@@ -55,14 +60,91 @@ struct GemmCfg {
   static constexpr int kSmemBytes = kStages * kStage + 256 /*barriers*/ + 4 * kStagingWarpBytes /*epilogue staging*/;
 };
 
+// ----------------------------------------------------------------------------------------
+// Work decomposition.  Data-parallel: output tiles are dealt round-robin to the persistent CTAs and a CTA runs the
+// whole K loop of each of its tiles.  Stream-K: the (tile, k-block) iterations of all tiles are laid end to end and cut
+// into one contiguous, equally long range per CTA, so every SM does the same amount of tensor-core work even when
+// the tile count is not a multiple of the SM count.  A range may begin or end in the middle of a tile: the CTA whose
+// range holds a tile's last k-block finishes the tile; CTAs that hold an earlier part of it leave their fp32
+// accumulator in a workspace slot (one slot per CTA: a range ends inside at most one tile) and raise a flag; the
+// finisher, which always has the higher block index, waits for those flags (bounded) and adds the partials before
+// its epilogue.  Waiting only on lower-numbered CTAs keeps the scheme free of deadlock whatever the residency, and
+// walking every range backwards (GemmWork::next) makes partials the first thing a CTA produces and fix-ups the last.
+// ----------------------------------------------------------------------------------------
+struct GemmSeg {
+  int tile, kb0, kb1;
+};
+
+struct GemmWork {
+  int k_blocks, num_tiles, stride, tile;   // data-parallel cursor
+  long long it, it_end;                    // stream-K cursor over iterations
+  bool sk;
+  OGB_DEVICE static long long range_begin(long long total, int ctas, int b) {
+    const long long base = total / ctas, rem = total % ctas;
+    return b * base + (b < rem ? b : rem);
+  }
+  // the CTA whose range holds iteration i
+  OGB_DEVICE static int owner(long long total, int ctas, long long i) {
+    const long long base = total / ctas, rem = total % ctas;
+    const long long cut = (base + 1) * rem;
+    return i < cut ? static_cast<int>(i / (base + 1)) : static_cast<int>(rem + (i - cut) / base);
+  }
+  OGB_DEVICE GemmWork(bool stream_k, int tiles, int kblocks) : k_blocks(kblocks), num_tiles(tiles), sk(stream_k) {
+    stride = gridDim.x;
+    tile = blockIdx.x;
+    const long long total = static_cast<long long>(tiles) * kblocks;
+    it = stream_k ? range_begin(total, gridDim.x, blockIdx.x) : 0;
+    it_end = stream_k ? range_begin(total, gridDim.x, blockIdx.x + 1) : 0;
+  }
+  OGB_DEVICE bool next(GemmSeg& s) {
+    if (!sk) {
+      if (tile >= num_tiles) return false;
+      s.tile = tile; s.kb0 = 0; s.kb1 = k_blocks;
+      tile += stride;
+      return true;
+    }
+    // The range is walked from its end to its beginning.  The segment at the end of the range is the head of a tile
+    // that a higher-numbered CTA finishes: it is produced first, so the finisher -- for which that tile's tail is the
+    // *last* segment -- finds the partial waiting instead of stalling on a neighbour that has its whole range to go.
+    if (it_end <= it) return false;
+    s.tile = static_cast<int>((it_end - 1) / k_blocks);
+    const long long tile_start = static_cast<long long>(s.tile) * k_blocks;
+    const long long seg_begin = tile_start > it ? tile_start : it;
+    s.kb0 = static_cast<int>(seg_begin - tile_start);
+    s.kb1 = static_cast<int>(it_end - tile_start);
+    it_end = seg_begin;
+    return true;
+  }
+};
+
+// fp32 partial accumulators of stream-K: slot = CTA, layout [BN / 32 column chunks][128 rows][32 floats], so a warp's
+// 32 rows of one chunk are 4 KB contiguous.  flags[cta * 4 + quarter] holds the sequence number of the launch whose
+// partial of that row quarter is complete.
+template <int BN>
+OGB_DEVICE float* sk_slot(float* ws, int cta, int chunk, int row) {
+  return ws + ((static_cast<size_t>(cta) * (BN / 32) + chunk) * kBM + row) * 32;
+}
+OGB_DEVICE void sk_add32(uint32_t (&r)[32], const float* src) {
+#pragma unroll
+  for (int v = 0; v < 8; ++v) {
+    const float4 f = *reinterpret_cast<const float4*>(src + 4 * v);
+    r[4 * v + 0] = __float_as_uint(__uint_as_float(r[4 * v + 0]) + f.x);
+    r[4 * v + 1] = __float_as_uint(__uint_as_float(r[4 * v + 1]) + f.y);
+    r[4 * v + 2] = __float_as_uint(__uint_as_float(r[4 * v + 2]) + f.z);
+    r[4 * v + 3] = __float_as_uint(__uint_as_float(r[4 * v + 3]) + f.w);
+  }
+}
+
 template <int BN, int EPI>
 __global__ void __launch_bounds__(kGemmThreadsScatter, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias,
                          const __nv_bfloat16* residual, float* __restrict__ C_f32, int M, int N, int K, int ldc, int ldr,
                          int* status, const TpScatter* __restrict__ sc, const int* __restrict__ group_tab,
-                         const int* __restrict__ group_mtiles, uint32_t* a_ready, uint32_t* a_done, unsigned long long a_wait_ns) {
+                         const int* __restrict__ group_mtiles, uint32_t* a_ready, uint32_t* a_done, unsigned long long a_wait_ns,
+                         float* sk_ws, uint32_t* sk_flags, uint32_t sk_seq) {
   using Cfg = GemmCfg<BN>;
+  const bool stream_k = sk_ws != nullptr;
   // the kernel declares no static shared memory, so the dynamic window starts at the 1024-byte aligned
   // base the 128-byte swizzle needs
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -115,7 +197,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       uint32_t phase = 0;
       bool ok = true;
       unsigned long long seen_ready = 0ull;     // m-tiles (of the first 64) whose rows are known to have arrived
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      GemmWork work(stream_k, num_tiles, k_blocks);
+      GemmSeg seg;
+      while (ok && work.next(seg)) {
+        const int tile = seg.tile;
         const int mt = tile % m_tiles;
         const int n0 = (tile / m_tiles) * BN;
         const int m0 = group_tab != nullptr ? group_tab[4 * mt + 1] : mt * kBM;
@@ -137,7 +222,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           asm volatile("fence.proxy.async.global;" ::: "memory");
           if (mt < 64) seen_ready |= 1ull << mt;
         }
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::kStage;
           uint8_t* sb = sa + Cfg::kStageA;
@@ -157,13 +242,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       uint32_t phase = 0;
       bool ok = true;
       int it = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      GemmWork work(stream_k, num_tiles, k_blocks);
+      GemmSeg seg;
+      for (; ok && work.next(seg); ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_addr = tmem_base + acc * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * Cfg::kStage);
@@ -173,7 +260,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
             // advance 16 bf16 = 32 bytes inside the swizzle row: +2 in the (>>4) address field
-            umma_f16(d_addr, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16(d_addr, da + 2 * k, db + 2 * k, idesc, (kb > seg.kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
@@ -187,7 +274,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     bool ok = true;
     int it = 0;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+    GemmWork work(stream_k, num_tiles, k_blocks);
+    GemmSeg seg;
+    const long long sk_total = static_cast<long long>(num_tiles) * k_blocks;
+    for (; ok && work.next(seg); ++it) {
+      const int tile = seg.tile;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       const int mt = tile % m_tiles;
@@ -200,6 +291,47 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      // ---- stream-K: a partial segment leaves its accumulator in this CTA's workspace slot; the segment that
+      // finishes a tile begun by other CTAs waits for their slots and adds them below ----
+      int fix_lo = 0, fix_hi = 0;                      // CTAs [fix_lo, fix_hi) hold earlier parts of this tile
+      if (stream_k) {
+        if (seg.kb1 < k_blocks) {
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_row + c * 32, r);
+            tmem_ld_wait();
+            float* dst = sk_slot<BN>(sk_ws, blockIdx.x, c, q * 32 + lane);
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              *reinterpret_cast<float4*>(dst + 4 * v) = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                                                  __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+          }
+          __syncwarp();
+          if (lane == 0) {
+            __threadfence();
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(sk_flags + blockIdx.x * 4 + q), "r"(sk_seq) : "memory");
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+          continue;
+        }
+        if (seg.kb0 > 0) {
+          fix_lo = GemmWork::owner(sk_total, gridDim.x, static_cast<long long>(tile) * k_blocks);
+          fix_hi = blockIdx.x;
+          for (int x = fix_lo; x < fix_hi && ok; ++x) {
+            const uint64_t t0 = global_timer_ns();
+            uint32_t spins = 0, got = 0;
+            while (true) {
+              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(got) : "l"(sk_flags + x * 4 + q) : "memory");
+              if (got == sk_seq) break;
+              if (((++spins) & 0x3f) == 0 && global_timer_ns() - t0 > kWaitLimitNs) { ok = false; break; }   // bounded by the timer
+            }
+          }
+          if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+        }
+      }
       if (C_f32 != nullptr) {
         // fp32 output (diagnostics / fp32 logits): direct row-per-thread stores
 #pragma unroll 1
@@ -207,6 +339,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           uint32_t r[32];
           tmem_ld_32x32(t_row + c * 32, r);
           tmem_ld_wait();
+          for (int x = fix_lo; x < fix_hi; ++x) sk_add32(r, sk_slot<BN>(sk_ws, x, c, q * 32 + lane));
           const int col = n0 + c * 32;
           if (row < m_end && col < N) {
             float* dst = C_f32 + static_cast<size_t>(row) * ldc + col;
@@ -241,6 +374,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
               tmem_ld_32x32(t_row + cb + c * 32, g);
               tmem_ld_32x32(t_row + BN / 2 + cb + c * 32, u);
               tmem_ld_wait();
+              for (int x = fix_lo; x < fix_hi; ++x) {
+                sk_add32(g, sk_slot<BN>(sk_ws, x, (cb + c * 32) / 32, q * 32 + lane));
+                sk_add32(u, sk_slot<BN>(sk_ws, x, (BN / 2 + cb + c * 32) / 32, q * 32 + lane));
+              }
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
@@ -251,6 +388,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
               uint32_t r[32];
               tmem_ld_32x32(t_row + cb + c * 32, r);
               tmem_ld_wait();
+              for (int x = fix_lo; x < fix_hi; ++x) sk_add32(r, sk_slot<BN>(sk_ws, x, (cb + c * 32) / 32, q * 32 + lane));
               const int col = n0 + cb + c * 32;
               if (bias != nullptr && col < N) {
                 if (col + 32 <= N) {
@@ -368,7 +506,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         const int q = lane;  // row quarter of the tile = TMEM quarter of the epilogue warp that stores it
         uint32_t done = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++done) {
+        GemmWork work(stream_k, num_tiles, k_blocks);
+        GemmSeg seg;
+        while (ok && work.next(seg)) {
+          if (seg.kb1 < k_blocks) continue;            // a partial segment stores nothing: its finisher signals the tile
+          const int tile = seg.tile;
           const uint64_t t0 = global_timer_ns();
           uint32_t spins = 0;
           while (true) {
@@ -389,6 +531,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             const uint32_t units = static_cast<uint32_t>(min(BN, N - n0) / 32);
             asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(cnt), "r"(units) : "memory");
           }
+          ++done;
         }
       }
     }
@@ -470,6 +613,70 @@ int make_tmap_u8_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t 
   return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 1000;
 }
 
+// Stream-K workspace: one fp32 slot of 128 x 256 per CTA plus four flag words per CTA, allocated once per
+// (device, stream) at the first launch that wants it (outside any stream capture: a step is run eagerly before it
+// is captured).  Launches on one stream are ordered, so they can share a workspace; the sequence number written
+// into the flags distinguishes their partials without any reset.
+struct SkWorkspace {
+  float* ws = nullptr;
+  uint32_t* flags = nullptr;
+  uint32_t seq = 0;
+  int ctas = 0;
+};
+
+static SkWorkspace* sk_workspace(cudaStream_t stream, int ctas) {
+  static std::mutex mu;
+  static std::unordered_map<uint64_t, SkWorkspace> table;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  const uint64_t key = (static_cast<uint64_t>(dev) << 56) ^ reinterpret_cast<uint64_t>(stream);
+  std::lock_guard<std::mutex> lock(mu);
+  SkWorkspace& w = table[key];
+  if (w.ws == nullptr || w.ctas < ctas) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return nullptr;
+    if (w.ws != nullptr) { cudaFree(w.ws); cudaFree(w.flags); w.ws = nullptr; w.flags = nullptr; }
+    const size_t bytes = static_cast<size_t>(ctas) * kBM * 256 * sizeof(float);
+    if (cudaMalloc(&w.ws, bytes) != cudaSuccess) { w.ws = nullptr; return nullptr; }
+    if (cudaMalloc(&w.flags, static_cast<size_t>(ctas) * 4 * sizeof(uint32_t)) != cudaSuccess ||
+        cudaMemset(w.flags, 0, static_cast<size_t>(ctas) * 4 * sizeof(uint32_t)) != cudaSuccess) {
+      cudaFree(w.ws);
+      w.ws = nullptr;
+      return nullptr;
+    }
+    w.ctas = ctas;
+    w.seq = 0;
+  }
+  return &w;
+}
+
+static int g_stream_k = -1;     // -1: read OGB_STREAM_K once (default on); 0 / 1 set by ogb_gemm_set_stream_k
+
+static bool stream_k_enabled() {
+  if (g_stream_k < 0) {
+    const char* e = getenv("OGB_STREAM_K");
+    g_stream_k = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return g_stream_k == 1;
+}
+// Stream-K pays when round-robin tiles would leave a large part of the last wave idle and the fix-up is cheap next
+// to a tile: every CTA boundary that falls inside a tile costs one fp32 partial written and read back (about 5 us,
+// i.e. about 13 k-blocks of tensor-core time), so the estimate adds 13 / k_blocks waves to the exact share.
+static bool stream_k_applies(int tiles, int k_blocks, int sms) {
+  if (!stream_k_enabled() || tiles % sms == 0 || static_cast<long long>(tiles) * k_blocks < 2LL * sms) return false;
+  const float w = static_cast<float>(tiles) / static_cast<float>(sms);
+  const float dp = static_cast<float>((tiles + sms - 1) / sms);
+  const float sk = w + 13.0f / static_cast<float>(k_blocks);
+  return sk < 0.93f * dp;
+}
+// Relative duration of a launch with `tiles` tiles of relative cost `cost`: whole waves when tiles are dealt
+// round-robin, the exact share plus the fix-up when stream-K spreads the k-blocks evenly.
+static float launch_cost(int tiles, int k_blocks, int sms, float cost) {
+  if (stream_k_applies(tiles, k_blocks, sms))
+    return (static_cast<float>(tiles) / static_cast<float>(sms) + 13.0f / static_cast<float>(k_blocks)) * cost;
+  return static_cast<float>((tiles + sms - 1) / sms) * cost;
+}
+
 template <int BN, int EPI>
 static int launch_gemm(const void* A, const void* W, void* C, const void* bias, const void* residual, void* C_f32, int M,
                        int N, int K, int lda, int ldw, int ldc, int ldr, int* status, cudaStream_t stream,
@@ -489,12 +696,30 @@ static int launch_gemm(const void* A, const void* W, void* C, const void* bias, 
     attr_set = true;
   }
   const int m_tiles = group_tab != nullptr ? max_mtiles : (M + kBM - 1) / kBM, n_tiles = (N + BN - 1) / BN;
-  int grid = m_tiles * n_tiles;
-  if (grid > ogb_num_sms()) grid = ogb_num_sms();
+  const int tiles = m_tiles * n_tiles;
+  const int sms = ogb_num_sms();
+  int grid = tiles;
+  if (grid > sms) grid = sms;
+  // Stream-K when the tiles do not fill whole waves and there are few waves (with many, the idle tail is a small
+  // share and the workspace traffic is not worth it); not for grouped (MoE) launches, whose tile table lives on the device.
+  float* sk_ws = nullptr;
+  uint32_t* sk_flags = nullptr;
+  uint32_t sk_seq = 0;
+  const int k_blocks = (K + kBK - 1) / kBK;
+  if (group_tab == nullptr && stream_k_applies(tiles, k_blocks, sms)) {
+    SkWorkspace* w = sk_workspace(stream, sms);
+    if (w != nullptr) {
+      grid = sms;
+      sk_ws = w->ws;
+      sk_flags = w->flags;
+      sk_seq = ++w->seq;
+      if (sk_seq == 0) sk_seq = ++w->seq;     // the flags start at zero
+    }
+  }
   gemm_bf16_tcgen05_kernel<BN, EPI><<<grid, EPI == kEpiScatter ? kGemmThreadsScatter : kGemmThreads, Cfg::kSmemBytes, stream>>>(
       ta, tb, static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(bias),
       static_cast<const __nv_bfloat16*>(residual), static_cast<float*>(C_f32), M, N, K, ldc, ldr, status, sc, group_tab, group_mtiles,
-      a_ready, a_done, a_wait_ns);
+      a_ready, a_done, a_wait_ns, sk_ws, sk_flags, sk_seq);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -520,6 +745,13 @@ using namespace ogb;
 extern "C" int ogb_gemm_bf16_wait(const void* A, const void* W, void* C, const void* bias, const void* residual, void* C_f32,
                                   int M, int N, int K, int lda, int ldw, int ldc, int ldr, int epilogue, int bn,
                                   uint32_t* a_ready, uint32_t* a_done, unsigned long long a_wait_ns, int* status, void* stream_);
+
+// Switches the stream-K decomposition on (1) or off (0) for the GEMMs launched from now on; returns the old setting.
+extern "C" int ogb_gemm_set_stream_k(int on) {
+  const int old = g_stream_k < 0 ? 1 : g_stream_k;
+  g_stream_k = on ? 1 : 0;
+  return old;
+}
 
 extern "C" int ogb_gemm_bf16(const void* A, const void* W, void* C, const void* bias, const void* residual, void* C_f32,
                              int M, int N, int K, int lda, int ldw, int ldc, int ldr, int epilogue, int bn, int* status,
@@ -553,7 +785,7 @@ extern "C" int ogb_gemm_bf16_wait(const void* A, const void* W, void* C, const v
     for (int i = 0; i < 5; ++i) {
       if (cand[i] < 128 && m_tiles > 3) break;  // narrow tiles only pay off for decode-sized M
       const int tiles = m_tiles * ((N + cand[i] - 1) / cand[i]);
-      const float t = static_cast<float>((tiles + sms - 1) / sms) * cost[i];
+      const float t = launch_cost(tiles, (K + kBK - 1) / kBK, sms, cost[i]);
       if (t < best - 1e-6f) { best = t; bn = cand[i]; }
     }
   }
@@ -587,7 +819,7 @@ extern "C" int ogb_gemm_bf16_scatter(const void* A, const void* W, int M, int N,
     bn = 256;
     for (int i = 0; i < 3; ++i) {
       const int tiles = m_tiles * ((N + cand[i] - 1) / cand[i]);
-      const float t = static_cast<float>((tiles + sms - 1) / sms) * cost[i];
+      const float t = launch_cost(tiles, (K + kBK - 1) / kBK, sms, cost[i]);
       if (t < best - 1e-6f) { best = t; bn = cand[i]; }
     }
   }

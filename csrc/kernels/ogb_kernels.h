@@ -24,6 +24,9 @@ int ogb_gemm_bf16_wait(const void* A, const void* W, void* C, const void* bias, 
                        int N, int K, int lda, int ldw, int ldc, int ldr, int epilogue, int bn, uint32_t* a_ready,
                        uint32_t* a_done, unsigned long long a_wait_ns, int* status, void* stream);
 
+// Stream-K decomposition of the GEMMs (on by default; OGB_STREAM_K=0 disables it): 1 / 0 sets it, the old value is returned.
+int ogb_gemm_set_stream_k(int on);
+
 // out[r,:] = x[r,:] * rsqrt(mean(x^2) + eps) * w ; if delta != NULL first x += delta (written back to x).
 int ogb_rmsnorm_bf16(void* x, const void* delta, const void* weight, void* out, int rows, int hidden, int ldx, int ldo,
                      float eps, void* stream);

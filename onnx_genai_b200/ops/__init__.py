@@ -163,6 +163,13 @@ def set_baseline(on: bool) -> None:
     _BASELINE = bool(on)
 
 
+def set_stream_k(on: bool) -> bool:
+    """Switch the stream-K work decomposition of the GEMM kernel on or off (it is on by default); returns the old
+    setting.  With it, the k-block iterations of all output tiles are cut into one equal range per SM, so a tile count
+    that is not a multiple of the SM count no longer leaves SMs idle in the last wave."""
+    return bool(_native.load().ogb_gemm_set_stream_k(1 if on else 0))
+
+
 def _baseline_gemm(a, w, bias, residual, epilogue, out, out_f32, swiglu_half):
     y = torch.matmul(a, w.t())
     launch_counts["baseline_cublas_gemm"] += 1

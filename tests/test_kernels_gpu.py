@@ -34,6 +34,44 @@ def test_gemm_tcgen05(m, n, k, bn):
     assert _rel_err(out32, ref.gemm(a, w, out_dtype=torch.float32)) < 1e-5 + 1e-3
 
 
+@pytest.mark.parametrize("m,n,k,epi", [(1280, 3584, 18944, "residual"), (1280, 4608, 3584, "bias"), (256, 4608, 3584, "none"),
+                                       (1500, 3584, 2368, "none"), (1280, 9472, 3584, "swiglu"), (200, 768, 3584, "bias"),
+                                       (128, 256, 8192, "none")])
+def test_gemm_stream_k_matches_data_parallel_and_fp32(m, n, k, epi):
+    """Tile counts that are not a multiple of the SM count run stream-K: k-block ranges cross tile boundaries, partial
+    accumulators meet in the fp32 workspace.  Results must match the fp32 statement like the data-parallel kernel's."""
+    torch.manual_seed(m + n + k)
+    a = (torch.randn(m, k, device=DEV) * 0.1).bfloat16()
+    w = (torch.randn(n, k, device=DEV) * 0.05).bfloat16()
+    bias = (torch.randn(n, device=DEV) * 0.1).bfloat16() if epi == "bias" else None
+    res = torch.randn(m, n, device=DEV).bfloat16() if epi == "residual" else None
+    if epi == "swiglu":
+        gate, up = w[: n // 2].contiguous(), w[n // 2:].contiguous()
+        wp = ops.pack_gate_up(gate, up, 128)
+        run = lambda: ops.gemm(a, wp, epilogue="swiglu", swiglu_half=128)
+        want = torch.nn.functional.silu(a.float() @ gate.float().t()) * (a.float() @ up.float().t())
+    else:
+        run = lambda: ops.gemm(a, w, bias=bias, residual=res, epilogue="residual" if res is not None else "none")
+        want = a.float() @ w.float().t()
+        if bias is not None:
+            want = want + bias.float()
+        if res is not None:
+            want = want + res.float()
+    old = ops.set_stream_k(True)
+    try:
+        got_sk = run().float()
+        got_sk2 = run().float()                    # the workspace and its flags are reused by the next launch
+        ops.set_stream_k(False)
+        got_dp = run().float()
+    finally:
+        ops.set_stream_k(old)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert _rel_err(got_sk, want) < 1e-2 and _rel_err(got_dp, want) < 1e-2
+    assert torch.equal(got_sk, got_sk2)
+    assert _rel_err(got_sk, got_dp) < 4e-3         # the same products, summed in a different order
+
+
 def test_gemm_residual_in_place():
     torch.manual_seed(1)
     m, n, k = 390, 3584, 512
