@@ -48,7 +48,8 @@ def _add_engine(p):
     p.add_argument("--host-ram-limit", default="auto", help="cap on pinned host memory for KV swap and the KV offload host tier: auto, a size such as 32GiB, or a fraction of RAM")
     p.add_argument("--cpu-cores", type=int, default=0, help="threads for CPU kernels and host-side work (0: leave as is)")
     p.add_argument("--draft-model", default="", help="directory of a smaller model that drafts for speculative requests")
-    p.add_argument("--draft-tokens", type=int, default=4, help="draft tokens per verification step when speculation is on")
+    p.add_argument("--draft-tokens", type=int, default=0,
+                   help="draft tokens per verification step when speculation is on (default: ONNX_GENAI_SPEC_TOKENS, else 4)")
     p.add_argument("--proposer", default="auto", choices=["auto", "ngram", "draft", "mtp", "eagle3", "shared-kv"],
                    help="who drafts for speculative requests (auto: the draft model if given, a packaged MTP head, else prompt lookup)")
     p.add_argument("--kv-offload-dir", default="", help="keep the K/V of finished prompts in host memory and this directory; restored on prefix hits")
@@ -81,9 +82,14 @@ def _load(args):
 
     from .engine.api import Engine
 
+    from .utils.runtime_config import runtime_config
+
+    rt = runtime_config()
     dev = args.device
-    if dev == "auto":
-        dev = "cuda" if torch.cuda.is_available() else "cpu"
+    if dev == "auto":       # no --device: ONNX_GENAI_CUDA_DEVICE / ONNX_GENAI_REQUIRE_CUDA decide
+        dev = rt.default_device(torch.cuda.is_available())
+    for name, why in rt.ignored.items():
+        print(f"note: {name} is set but has no effect here: {why}", file=sys.stderr)
     # --vram-limit: a fraction keeps its old meaning (share of the device the engine may fill); a size such as 8GiB
     # caps weights + activations + KV pool through the memory ledger
     try:
@@ -101,7 +107,7 @@ def _load(args):
     extra = {"kv_max_pages": args.kv_max_pages} if getattr(args, "kv_max_pages", 0) > 0 else {}
     eng = Engine.from_dir(args.model, device=dev, max_seqs=args.max_batch, kv_dtype={"fp8_e4m3fn": "fp8", "int8": "int8"}.get(args.kv_cache_dtype, "bf16"),
                           gpu_memory_utilization=util if 0 < util <= 1 else 0.85, vram_limit=limit,
-                          max_draft_tokens=getattr(args, "draft_tokens", 4) if speculative else 0,
+                          max_draft_tokens=(getattr(args, "draft_tokens", 0) or rt.spec_tokens) if speculative else 0,
                           draft_model_dir=(getattr(args, "draft_model", "") or None) if proposer in ("auto", "draft") else None,
                           max_seq_len=args.max_context or None, **extra)
     if proposer == "ngram":

@@ -128,7 +128,17 @@ class Engine:
         compatibility; pages hold 16 tokens (the attention kernels' tile)."""
         if page_size not in (None, 16):
             raise ValueError(f"page_size={page_size} is not supported: KV pages hold 16 tokens")
-        device = device or ("cuda" if torch.cuda.is_available() else "cpu")
+        # precedence: the caller's arguments > ONNX_GENAI_* environment (utils/runtime_config.py) > metadata > built-in
+        from ..utils.runtime_config import runtime_config
+
+        rt = runtime_config()
+        device = device or rt.default_device(torch.cuda.is_available())
+        if rt.require_cuda and not str(device).startswith("cuda"):
+            raise RuntimeError(f"ONNX_GENAI_REQUIRE_CUDA is set but the engine was asked to load on {device!r}")
+        if rt.baseline_gemm and str(device).startswith("cuda"):
+            from .. import ops as _ops
+
+            _ops.set_baseline(True)          # ONNX_GENAI_BASELINE_GEMM: library GEMMs, for comparisons
         d = pkg.open_model_directory(model_dir, ep="cuda" if str(device).startswith("cuda") else "cpu",
                                      device="gpu" if str(device).startswith("cuda") else "cpu")
         meta = d.load_metadata()
@@ -158,7 +168,7 @@ class Engine:
 
             eos = eos_token_ids(d.genai_config) or eos
         cfg = cfg.replace(eos_token=eos[0] if eos else -1)
-        engine_kw.setdefault("cuda_graphs", str(device).startswith("cuda"))
+        rt.apply_engine_defaults(engine_kw, str(device).startswith("cuda"))
         ecfg = EngineConfig(model=cfg, num_pages=num_pages, max_seqs=max_seqs, max_seq_len=max_seq_len,
                             max_tokens_per_step=max_tokens_per_step, prefill_chunk=meta.chunked_prefill_size or 2048,
                             kv_dtype=kv_dtype, max_draft_tokens=max_draft_tokens, **engine_kw)

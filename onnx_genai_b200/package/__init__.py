@@ -41,9 +41,17 @@ class ModelDirectory:
         if self.metadata_path:
             return md.load(self.metadata_path)
         if self.genai_config is not None:
-            from .genai_config import import_genai_config
+            from .genai_config import graph_ports, import_genai_config
 
-            return md.parse(import_genai_config(self.genai_config))
+            graph = None
+            if self.model_path and os.path.exists(self.model_path):
+                try:                                  # ports only: the weights stay on disk (external data is mapped lazily)
+                    from .onnx_pb import load_model
+
+                    graph = graph_ports(load_model(self.model_path))
+                except Exception:                     # an unreadable graph leaves the declared name patterns in charge
+                    graph = None
+            return md.parse(import_genai_config(self.genai_config, graph=graph))
         return md.InferenceMetadata()
 
 

@@ -364,7 +364,13 @@ def create_app(engine: Engine, model_name: str = "model", max_output_tokens: int
 
         @app.get("/v1/debug/config")
         async def debug_config():
-            return {k: (v if isinstance(v, (int, float, str, bool, type(None))) else str(v)) for k, v in engine.llm.cfg.__dict__.items()}
+            from ..utils.runtime_config import runtime_config
+
+            out = {k: (v if isinstance(v, (int, float, str, bool, type(None))) else str(v)) for k, v in engine.llm.cfg.__dict__.items()}
+            out["environment"] = runtime_config().describe()       # what the ONNX_GENAI_* variables resolved to
+            out["cuda_graph_declines"] = [{"bucket": list(k), "reason": why} for k, why in engine.llm.graph_declines]
+            out["device_faults"] = engine.llm.device_faults
+            return out
 
         @app.get("/v1/debug/kv")
         async def debug_kv():

@@ -51,11 +51,35 @@ class RuntimeConfig:
         return cfg
 
 
+    def describe(self) -> dict:
+        """What the engine loader will do with the environment (served by ``/v1/debug/config`` and ``show``)."""
+        return {"cuda_device": self.cuda_device, "cuda_graph": self.cuda_graph, "require_cuda": self.require_cuda,
+                "profile": self.profile, "trace_path": self.trace_path, "trace_verbosity": self.trace_verbosity,
+                "backend": self.backend, "spec_tokens": self.spec_tokens, "decode_splits": self.decode_splits,
+                "baseline_gemm": self.baseline_gemm, "ignored": dict(self.ignored)}
+
+    def default_device(self, cuda_available: bool) -> str:
+        """The device an engine loads on when the caller names none: ``cuda:<ONNX_GENAI_CUDA_DEVICE>`` when CUDA is there,
+        else the CPU -- unless ``ONNX_GENAI_REQUIRE_CUDA`` forbids that fallback."""
+        if cuda_available:
+            return f"cuda:{self.cuda_device}"
+        if self.require_cuda:
+            raise RuntimeError("ONNX_GENAI_REQUIRE_CUDA is set but no CUDA device is available; unset it to run on the CPU")
+        return "cpu"
+
+    def apply_engine_defaults(self, engine_kw: dict, on_cuda: bool) -> dict:
+        """Fill engine options the caller left open from the environment (a caller's explicit value always wins)."""
+        engine_kw.setdefault("cuda_graphs", bool(on_cuda and self.cuda_graph))
+        if self.decode_splits > 0:
+            engine_kw.setdefault("decode_splits", self.decode_splits)
+        return engine_kw
+
+
 _CACHED = None
 
 
-def runtime_config() -> RuntimeConfig:
+def runtime_config(refresh: bool = False) -> RuntimeConfig:
     global _CACHED
-    if _CACHED is None:
+    if _CACHED is None or refresh:
         _CACHED = RuntimeConfig.from_env()
     return _CACHED

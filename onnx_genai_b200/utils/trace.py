@@ -46,7 +46,9 @@ class Tracer:
     def __init__(self):
         self.lock = threading.Lock()
         self.spans = []
-        self.path = os.environ.get("ONNX_GENAI_TRACE") or None
+        from .runtime_config import runtime_config
+
+        self.path = runtime_config().trace_path or None      # ONNX_GENAI_TRACE
         self.enabled = self.path is not None
 
     def start(self, path):
