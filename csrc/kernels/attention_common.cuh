@@ -118,4 +118,7 @@ OGB_DEVICE bool attn_produce(const CUtensorMap* kv_map, const AttnParams& p, uin
   return true;
 }
 
+// tcgen05 decode over e4m3 pages (attention_fp8_tc.cu): `p` fully filled, at most 8 query heads per KV head, head_dim 128.
+int launch_decode_e4m3_tc(const AttnParams& p, const void* pool, void* stream);
+
 }  // namespace ogb

@@ -74,6 +74,10 @@ int ogb_paged_prefill_fp8(const void* q, void* out, const void* pool, const floa
 int ogb_rope_kv_append_q8(void* qkv, const int* positions, const int* slots, const float* cos_sin, void* pool, float* scales,
                           int kv_format, int tokens, int hq, int hkv, int d, int rotary_dim, int interleaved, int page_size,
                           int64_t num_slots, int max_pos, int* status, void* stream);
+// How decode reads e4m3 pages when a KV head serves at most 8 query heads: 2 = tcgen05 kernel with the raw bytes as
+// kind::f8f6f4 operands (default), 1 = mma.sync e4m3 kernel, 0 = expand pages to bf16 first.  OGB_E4M3_MMA=0|1|2 picks
+// it at start-up; this call sets it and returns the old value.
+int ogb_attn_set_e4m3_mma(int mode);
 int ogb_paged_decode_q8(const void* q, void* out, const void* pool, const float* scales, int kv_format, const int* page_table,
                         const int* ctx_len, int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d,
                         int q_stride, int o_stride, float scale, int num_splits, float* part_o, float* part_ml, int* status,

@@ -170,6 +170,13 @@ def set_stream_k(on: bool) -> bool:
     return bool(_native.load().ogb_gemm_set_stream_k(1 if on else 0))
 
 
+def set_e4m3_mma(mode: int) -> int:
+    """Pick the decode kernel for e4m3 KV pages (query groups of at most 8 heads): 2 = tcgen05 kernel that feeds the raw
+    bytes to the tensor cores (default), 1 = the ``mma.sync`` e4m3 kernel, 0 = the kernel that expands pages to bf16 in
+    shared memory first.  Returns the old setting."""
+    return int(_native.load().ogb_attn_set_e4m3_mma(int(mode)))
+
+
 def _baseline_gemm(a, w, bias, residual, epilogue, out, out_f32, swiglu_half):
     y = torch.matmul(a, w.t())
     launch_counts["baseline_cublas_gemm"] += 1

@@ -462,6 +462,42 @@ def test_paged_attention_fp8_pages(fmt):
     assert _rel_err(outp, wantp) < 2e-2
 
 
+@pytest.mark.parametrize("hq,hkv", [(28, 4), (32, 4), (8, 2), (4, 4)])
+def test_decode_over_e4m3_pages_as_mma_operands_is_as_accurate_as_expanding_them(hq, hkv):
+    """The kernel that feeds raw e4m3 bytes to e4m3 MMAs (queries and probabilities carried as a hi + lo pair of rows)
+    against fp32, and against the kernel that expands pages to bf16: block edges of its 128-key stages, split counts
+    that leave splits empty, large query magnitudes, and pages whose V scale is tiny next to the others'."""
+    torch.manual_seed(17)
+    d = 128
+    ctx = [1, 31, 32, 33, 127, 128, 129, 255, 257, 700, 2000]
+    n = len(ctx)
+    pool, scales, table = _make_paged_fp8(ctx, hkv, d, seed=3)
+    scales[::3, :, 1] *= 1e-4                                     # some V pages count for almost nothing
+    ctx_t = torch.tensor(ctx, dtype=torch.int32, device=DEV)
+    q = (torch.randn(n, (hq + 2 * hkv) * d, device=DEV) * torch.tensor([0.05, 1.0, 30.0] * 4, device=DEV)[:n, None]).bfloat16()
+    cu = torch.arange(n + 1, dtype=torch.int32, device=DEV)
+    want = ref.paged_attention(q, pool, table, ctx_t, cu, hq, hkv, d, kv_scales=scales)
+    errs = {}
+    old = ops.set_e4m3_mma(2)
+    try:
+        for mma in (2, 1, 0):
+            ops.set_e4m3_mma(mma)
+            for splits in (1, 3, 8):
+                out = torch.full((n, hq * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+                ops.paged_decode(q, out, pool, table, ctx_t, hq, hkv, d, num_splits=splits, kv_scales=scales)
+                torch.cuda.synchronize()
+                ops.check_status()
+                assert torch.isfinite(out.float()).all(), (mma, splits)
+                errs[mma, splits] = _rel_err(out, want)
+                worst = ((out.float() - want.float()).norm(dim=1) / want.float().norm(dim=1).clamp_min(1e-6)).max().item()
+                assert worst < 2e-2, (mma, splits, worst)
+    finally:
+        ops.set_e4m3_mma(old)
+    for splits in (1, 3, 8):
+        for mma in (2, 1):
+            assert errs[mma, splits] < 1e-2 and errs[mma, splits] < 1.5 * errs[0, splits] + 1e-3, errs
+
+
 @pytest.mark.parametrize("fmt", ["fp8", "int8"])
 def test_rope_kv_append_fp8_roundtrip(fmt):
     torch.manual_seed(14)
