@@ -215,10 +215,11 @@ int ogb_cpu_rope_kv_append(float* qkv, const int32_t* positions, const int32_t* 
 
 // Varlen causal GQA over the paged pool.  Sequence s owns query rows cu_q[s]..cu_q[s+1]; its last row sits
 // at position ctx_len[s] - 1.  q rows are the first hq*d columns of a [T, ldq] matrix; out [T, hq*d].
-// window > 0 keeps only the last `window` keys of each query.
+// window > 0 keeps only the last `window` keys of each query, plus the first `sink` keys of the sequence (attention
+// sinks); pages between the two are never read, so their table entries may be -1.
 int ogb_cpu_paged_attention(const float* q, int64_t ldq, float* out, const float* pool, const int32_t* page_table,
                             int table_stride, const int32_t* ctx_len, const int32_t* cu_q, int num_seqs, int hq, int hkv, int d,
-                            float scale, int window) {
+                            float scale, int window, int sink) {
   const int g = hq / hkv;
   std::vector<int64_t> work;   // (seq, row) pairs flattened so OpenMP balances long and short sequences
   for (int s = 0; s < num_seqs; ++s)
@@ -243,21 +244,26 @@ int ogb_cpu_paged_attention(const float* q, int64_t ldq, float* out, const float
       const int kvh = h / g;
       const float* qv = q + row * ldq + static_cast<int64_t>(h) * d;
       const int32_t* table = page_table + static_cast<int64_t>(s) * table_stride;
-      scores.resize(k1 - k0);
+      const int ns = (window > 0) ? std::min(std::max(sink, 0), k0) : 0;   // sink keys below the window
+      auto key_at = [&](int j) { return j < ns ? j : k0 + (j - ns); };
+      const int nk = ns + (k1 - k0);
+      scores.resize(nk);
       float mx = -std::numeric_limits<float>::infinity();
-      for (int k = k0; k < k1; ++k) {
+      for (int j = 0; j < nk; ++j) {
+        const int k = key_at(j);
         const int64_t page = table[k / kPage];
         const float* kv = pool + (((page * hkv + kvh) * 2 + 0) * kPage + (k % kPage)) * d;
         float lanes[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         for (int i = 0; i < d; ++i) lanes[i & 7] = std::fmaf(qv[i], kv[i], lanes[i & 7]);
         const float sc = hsum8(lanes) * scale;
-        scores[k - k0] = sc;
+        scores[j] = sc;
         mx = std::max(mx, sc);
       }
       float denom = 0.f;
       std::fill(o, o + d, 0.f);
-      for (int k = k0; k < k1; ++k) {
-        const float p = std::exp(scores[k - k0] - mx);
+      for (int j = 0; j < nk; ++j) {
+        const int k = key_at(j);
+        const float p = std::exp(scores[j] - mx);
         denom += p;
         const int64_t page = table[k / kPage];
         const float* vv = pool + (((page * hkv + kvh) * 2 + 1) * kPage + (k % kPage)) * d;

@@ -58,9 +58,7 @@ __global__ void __launch_bounds__((ROWS / 16 + 1) * 32, 2) paged_prefill_kernel(
   const int pos0 = ctx - q_len + q0;
   if (rows <= 0 || ctx <= 0) return;
   const int kv_end = min(ctx, pos0 + rows);
-  const int kv_lo = (p.window > 0) ? max(0, pos0 - p.window + 1) : 0;
-  const int b_begin = kv_lo / kKvBlock;
-  const int b_end = (kv_end + kKvBlock - 1) / kKvBlock;
+  const KvBlocks blocks = make_kv_blocks(p.window, p.sink, max(0, pos0 - p.window + 1), kv_end, kKvBlock);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -72,7 +70,7 @@ __global__ void __launch_bounds__((ROWS / 16 + 1) * 32, 2) paged_prefill_kernel(
 
   if (warp == kWarps) {
     if (lane == 0) {
-      if (!attn_produce<Cfg>(&kv_map, p, stages, full_bar, empty_bar, seq, kvh, ctx, b_begin, b_end))
+      if (!attn_produce<Cfg>(&kv_map, p, stages, full_bar, empty_bar, seq, kvh, ctx, blocks, 0, blocks.count))
         atomicOr(p.status, kStatusWaitTimeout);
     }
     return;
@@ -110,7 +108,8 @@ __global__ void __launch_bounds__((ROWS / 16 + 1) * 32, 2) paged_prefill_kernel(
   int stage = 0;
   uint32_t phase = 0;
   bool ok = true;
-  for (int b = b_begin; b < b_end; ++b) {
+  for (int jb = 0; jb < blocks.count; ++jb) {
+    const int b = blocks.phys(jb);
     if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], phase))) { ok = false; break; }
     const uint32_t sk = smem_u32(stages + stage * Cfg::kStageBytes);
     const uint32_t sv = sk + Cfg::kTileBytes;
@@ -141,8 +140,7 @@ __global__ void __launch_bounds__((ROWS / 16 + 1) * 32, 2) paged_prefill_kernel(
         if (need_mask) {
           const int col = kv_base + 8 * j + 2 * (lane & 3) + (e & 1);
           const int qpos = (e < 2) ? qpos_a : qpos_b;
-          const bool valid = (col <= qpos) && (col < ctx) && (p.window <= 0 || col > qpos - p.window);
-          if (!valid) v = -INFINITY;
+          if (!key_visible(col, qpos, ctx, p.window, p.sink)) v = -INFINITY;
         }
         s[j][e] = v;
       }
@@ -233,15 +231,15 @@ __global__ void __launch_bounds__(kAttnThreads, 2) paged_decode_kernel(const __g
   const int ctx = p.ctx_len[seq];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  int b_begin = 0, b_end = 0, kv_lo = 0;
+  int b_begin = 0, b_end = 0;            // logical blocks of this split (sink blocks first, then the window's)
+  KvBlocks blocks{0, 0, 0, 0};
   if (ctx > 0) {
-    kv_lo = (p.window > 0) ? max(0, ctx - p.window) : 0;
-    const int first = kv_lo / kKvBlock;
-    const int last = (ctx + kKvBlock - 1) / kKvBlock;
-    const int per = (last - first + p.num_splits - 1) / p.num_splits;
-    b_begin = first + split * per;
-    b_end = min(b_begin + per, last);
+    blocks = make_kv_blocks(p.window, p.sink, max(0, ctx - p.window), ctx, kKvBlock);
+    const int per = (blocks.count + p.num_splits - 1) / p.num_splits;
+    b_begin = split * per;
+    b_end = min(b_begin + per, blocks.count);
   }
+  const int kv_lo = blocks.kv_lo;
   if (b_begin >= b_end) {
     // nothing to do for this split (or an inactive row): publish an empty partial
     if (p.num_splits > 1 && ctx > 0) {
@@ -264,7 +262,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) paged_decode_kernel(const __g
 
   if (warp == 4) {
     if (lane == 0) {
-      if (!attn_produce<Cfg>(&kv_map, p, stages, full_bar, empty_bar, seq, kvh, ctx, b_begin, b_end))
+      if (!attn_produce<Cfg>(&kv_map, p, stages, full_bar, empty_bar, seq, kvh, ctx, blocks, b_begin, b_end))
         atomicOr(p.status, kStatusWaitTimeout);
     }
     return;
@@ -298,10 +296,12 @@ __global__ void __launch_bounds__(kAttnThreads, 2) paged_decode_kernel(const __g
   int stage = 0;
   uint32_t phase = 0;
   bool ok = true;
-  for (int b = b_begin; b < b_end; ++b) {
+  const int sink = (p.window > 0) ? p.sink : 0;
+  for (int jb = b_begin; jb < b_end; ++jb) {
+    const int b = blocks.phys(jb);
     if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], phase))) { ok = false; break; }
     const int tok0 = b * kKvBlock + 16 * warp;  // first token of this warp's page in the block
-    if (tok0 < ctx && tok0 + 16 > kv_lo) {
+    if (tok0 < ctx && (tok0 + 16 > kv_lo || tok0 < sink)) {
       const uint32_t sk = smem_u32(stages + stage * Cfg::kStageBytes);
       const uint32_t sv = sk + Cfg::kTileBytes;
       float s[2][4];
@@ -321,7 +321,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) paged_decode_kernel(const __g
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int col = tok0 + 8 * j + 2 * (lane & 3) + (e & 1);
-          const bool valid = (col < ctx) && (col >= kv_lo);
+          const bool valid = (col < ctx) && (col >= kv_lo || col < sink);
           s[j][e] = valid ? s[j][e] * p.scale_log2e : -INFINITY;
         }
       }
@@ -514,7 +514,7 @@ using namespace ogb;
 extern "C" int ogb_paged_prefill_bf16(const void* q, void* out, const void* pool, const int* page_table, const int* ctx_len,
                                       const int* cu_q, const int* tile_seq, const int* tile_q0, int num_tiles, int num_seqs,
                                       int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride, int o_stride,
-                                      float scale, int window, int* status, void* stream) {
+                                      float scale, int window, int sink, int* status, void* stream) {
   if (num_tiles <= 0) return 0;
   if ((d != 64 && d != 128) || hkv <= 0 || hq % hkv != 0 || (q_stride % 8) != 0 || (o_stride % 2) != 0) return -3;
   CUtensorMap map;
@@ -526,7 +526,7 @@ extern "C" int ogb_paged_prefill_bf16(const void* q, void* out, const void* pool
   p.page_table = page_table; p.ctx_len = ctx_len; p.cu_q = cu_q; p.tile_seq = tile_seq; p.tile_q0 = tile_q0;
   p.num_tiles = num_tiles; p.num_seqs = num_seqs; p.max_pages = max_pages; p.num_pages = num_pages;
   p.hq = hq; p.hkv = hkv; p.group = hq / hkv; p.q_stride = q_stride; p.o_stride = o_stride;
-  p.scale_log2e = scale * 1.4426950408889634f; p.window = window; p.num_splits = 1; p.status = status;
+  p.scale_log2e = scale * 1.4426950408889634f; p.window = window; p.sink = window > 0 ? sink : 0; p.num_splits = 1; p.status = status;
   return d == 128 ? launch_prefill<128>(map, p, static_cast<cudaStream_t>(stream))
                   : launch_prefill<64>(map, p, static_cast<cudaStream_t>(stream));
 }
@@ -534,7 +534,7 @@ extern "C" int ogb_paged_prefill_bf16(const void* q, void* out, const void* pool
 extern "C" int ogb_paged_decode_bf16(const void* q, void* out, const void* pool, const int* page_table, const int* ctx_len,
                                      int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride,
                                      int o_stride, float scale, int num_splits, float* part_o, float* part_ml, int window,
-                                     int* status, void* stream) {
+                                     int sink, int* status, void* stream) {
   if (num_seqs <= 0) return 0;
   if ((d != 64 && d != 128) || hkv <= 0 || hq % hkv != 0 || hq / hkv > 16 || (q_stride % 8) != 0) return -3;
   if (num_splits < 1) num_splits = 1;
@@ -548,7 +548,7 @@ extern "C" int ogb_paged_decode_bf16(const void* q, void* out, const void* pool,
   p.page_table = page_table; p.ctx_len = ctx_len;
   p.num_seqs = num_seqs; p.max_pages = max_pages; p.num_pages = num_pages;
   p.hq = hq; p.hkv = hkv; p.group = hq / hkv; p.q_stride = q_stride; p.o_stride = o_stride;
-  p.scale_log2e = scale * 1.4426950408889634f; p.window = window; p.num_splits = num_splits;
+  p.scale_log2e = scale * 1.4426950408889634f; p.window = window; p.sink = window > 0 ? sink : 0; p.num_splits = num_splits;
   p.part_o = part_o; p.part_ml = part_ml; p.status = status;
   return d == 128 ? launch_decode<128>(map, p, static_cast<cudaStream_t>(stream))
                   : launch_decode<64>(map, p, static_cast<cudaStream_t>(stream));

@@ -72,7 +72,8 @@ struct AttnParams {
   int hq, hkv, group;
   int q_stride, o_stride;
   float scale_log2e;
-  int window;
+  int window;               // > 0: a query sees only the last `window` keys ...
+  int sink;                 // ... and, with window > 0, the first `sink` keys as well (attention sinks)
   int num_splits;
   float* part_o;
   float* part_ml;
@@ -83,15 +84,48 @@ struct AttnParams {
   int dbg_tile;
 };
 
-// Producer: stream blocks [b_begin, b_end) of one sequence / kv head into the ring.
+// Sliding window with attention sinks (the retention policy of crates/onnx-genai-kv/src/paged_cache.rs:483-585, done
+// here as a mask plus a block walk instead of a compacted buffer): a query at position qpos sees keys
+// [0, sink) and (qpos - window, qpos].
+OGB_DEVICE bool key_visible(int col, int qpos, int ctx, int window, int sink) {
+  return col <= qpos && col < ctx && (window <= 0 || col > qpos - window || col < sink);
+}
+// The scheduler may release the pages that lie wholly between the sinks and the window (their page-table entries
+// become -1).  `kv_lo` is the first key any query of the CTA sees inside its window; a page index in the gap is replaced
+// by the window's first page, whose keys are masked where they stand in for gap keys.
+OGB_DEVICE int skip_gap_page(int pi, int window, int sink, int kv_lo) {
+  if (window > 0) {
+    const int gap_lo = (sink + kPageTokens - 1) / kPageTokens, gap_hi = kv_lo / kPageTokens;
+    if (pi >= gap_lo && pi < gap_hi) pi = gap_hi;
+  }
+  return pi;
+}
+// The key blocks a CTA walks: the sink blocks, then the blocks from the window's first key to the last key.
+struct KvBlocks {
+  int nsink, first, count, kv_lo;
+  OGB_DEVICE int phys(int j) const { return j < nsink ? j : first + (j - nsink); }
+};
+OGB_DEVICE KvBlocks make_kv_blocks(int window, int sink, int kv_lo, int kv_end, int block) {
+  KvBlocks r;
+  const int last = (kv_end + block - 1) / block;
+  r.kv_lo = (window > 0) ? kv_lo : 0;
+  r.first = r.kv_lo / block;
+  r.nsink = (window > 0 && sink > 0) ? (min(sink, kv_end) + block - 1) / block : 0;
+  if (r.first <= r.nsink) { r.first = 0; r.nsink = 0; }      // the window reaches the sinks: one contiguous walk
+  r.count = r.nsink + last - r.first;
+  return r;
+}
+
+// Producer: stream logical blocks [j_begin, j_end) of one sequence / kv head into the ring.
 template <class Cfg>
 OGB_DEVICE bool attn_produce(const CUtensorMap* kv_map, const AttnParams& p, uint8_t* stages, uint64_t* full_bar,
-                             uint64_t* empty_bar, int seq, int kvh, int ctx, int b_begin, int b_end) {
+                             uint64_t* empty_bar, int seq, int kvh, int ctx, const KvBlocks& blocks, int j_begin, int j_end) {
   const int n_pages = (ctx + kPageTokens - 1) / kPageTokens;
   const int* table = p.page_table + static_cast<size_t>(seq) * p.max_pages;
   int stage = 0;
   uint32_t phase = 0;
-  for (int b = b_begin; b < b_end; ++b) {
+  for (int j = j_begin; j < j_end; ++j) {
+    const int b = blocks.phys(j);
     if (!mbar_wait(&empty_bar[stage], phase ^ 1)) return false;
     uint8_t* sk = stages + stage * Cfg::kStageBytes;
     uint8_t* sv = sk + Cfg::kTileBytes;
@@ -101,6 +135,7 @@ OGB_DEVICE bool attn_produce(const CUtensorMap* kv_map, const AttnParams& p, uin
       int pi = b * 4 + i;
       if (pi > n_pages - 1) pi = n_pages - 1;  // tail: re-read the last page, masked later
       if (pi > p.max_pages - 1) pi = p.max_pages - 1;
+      pi = skip_gap_page(pi, p.window, p.sink, blocks.kv_lo);
       int64_t page = table[pi];
       if (page < 0 || page >= p.num_pages) {
         atomicOr(p.status, kStatusIndexOutOfRange);

@@ -92,7 +92,7 @@ OGB_DEVICE void expand_page(const uint8_t* raw, uint8_t* work, int tid, int nthr
 }
 
 OGB_DEVICE bool fp8_produce(const CUtensorMap* kv_map, const AttnParams& p, uint8_t* stages, uint64_t* full_bar,
-                            uint64_t* empty_bar, int nstages, int seq, int kvh, int ctx, int b_begin, int b_end) {
+                            uint64_t* empty_bar, int nstages, int seq, int kvh, int ctx, int b_begin, int b_end, int kv_lo) {
   const int n_pages = (ctx + kPageTokens - 1) / kPageTokens;
   const int* table = p.page_table + static_cast<size_t>(seq) * p.max_pages;
   int stage = 0;
@@ -104,6 +104,7 @@ OGB_DEVICE bool fp8_produce(const CUtensorMap* kv_map, const AttnParams& p, uint
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       int pi = min(min(b * 4 + i, n_pages - 1), p.max_pages - 1);
+      pi = skip_gap_page(pi, p.window, p.sink, kv_lo);
       int64_t page = table[pi];
       if (page < 0 || page >= p.num_pages) { atomicOr(p.status, kStatusIndexOutOfRange); page = 0; }
       const int row_k = static_cast<int>(((page * p.hkv + kvh) * 2) * kPageTokens);
@@ -115,9 +116,9 @@ OGB_DEVICE bool fp8_produce(const CUtensorMap* kv_map, const AttnParams& p, uint
   return true;
 }
 
-OGB_DEVICE int64_t page_of(const AttnParams& p, int seq, int ctx, int pi) {
+OGB_DEVICE int64_t page_of(const AttnParams& p, int seq, int ctx, int pi, int kv_lo) {
   const int n_pages = (ctx + kPageTokens - 1) / kPageTokens;
-  pi = min(min(pi, n_pages - 1), p.max_pages - 1);
+  pi = skip_gap_page(min(min(pi, n_pages - 1), p.max_pages - 1), p.window, p.sink, kv_lo);
   int64_t page = p.page_table[static_cast<size_t>(seq) * p.max_pages + pi];
   return (page < 0 || page >= p.num_pages) ? 0 : page;
 }
@@ -144,10 +145,13 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_fp8_kernel(const __
   const int ctx = p.ctx_len[seq];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int b_begin = 0, b_end = 0;
+  const int kv_lo = (p.window > 0) ? max(0, ctx - p.window) : 0;     // first key inside the window
+  const int sink = (p.window > 0) ? p.sink : 0;
   if (ctx > 0) {
+    const int first = (sink > 0) ? 0 : kv_lo / kKvBlock;            // with sinks the walk starts at key 0 (gap blocks are masked)
     const int last = (ctx + kKvBlock - 1) / kKvBlock;
-    const int per = (last + p.num_splits - 1) / p.num_splits;
-    b_begin = split * per;
+    const int per = (last - first + p.num_splits - 1) / p.num_splits;
+    b_begin = first + split * per;
     b_end = min(b_begin + per, last);
   }
   if (b_begin >= b_end) {
@@ -168,7 +172,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_fp8_kernel(const __
   }
   __syncthreads();
   if (warp == 4) {
-    if (lane == 0 && !fp8_produce(&kv_map, p, stages, full_bar, empty_bar, kDecStages, seq, kvh, ctx, b_begin, b_end))
+    if (lane == 0 && !fp8_produce(&kv_map, p, stages, full_bar, empty_bar, kDecStages, seq, kvh, ctx, b_begin, b_end, kv_lo))
       atomicOr(p.status, kStatusWaitTimeout);
     return;
   }
@@ -204,14 +208,14 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_fp8_kernel(const __
   // block ahead so that their latency overlaps the expansion and the MMAs of the current block instead of stalling it.
   float ks_next, vs_next;
   {
-    const int64_t page = page_of(p, seq, ctx, b_begin * 4 + warp);
+    const int64_t page = page_of(p, seq, ctx, b_begin * 4 + warp, kv_lo);
     ks_next = p.kv_scales[(page * p.hkv + kvh) * 2];
     vs_next = p.kv_scales[(page * p.hkv + kvh) * 2 + 1];
   }
   for (int b = b_begin; b < b_end; ++b) {
     const float ks = ks_next * p.scale_log2e, vs = vs_next;
     if (b + 1 < b_end) {
-      const int64_t page = page_of(p, seq, ctx, (b + 1) * 4 + warp);
+      const int64_t page = page_of(p, seq, ctx, (b + 1) * 4 + warp, kv_lo);
       ks_next = p.kv_scales[(page * p.hkv + kvh) * 2];
       vs_next = p.kv_scales[(page * p.hkv + kvh) * 2 + 1];
     }
@@ -237,7 +241,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_fp8_kernel(const __
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int col = tok0 + 8 * j + 2 * (lane & 3) + (e & 1);
-          s[j][e] = (col < ctx) ? s[j][e] * ks : -INFINITY;
+          s[j][e] = (col < ctx && (col >= kv_lo || col < sink)) ? s[j][e] * ks : -INFINITY;
         }
       float pv[2][4];
 #pragma unroll
@@ -415,7 +419,7 @@ OGB_DEVICE void mbar_expect_tx_only(uint64_t* bar, uint32_t bytes) {
 // (a consumer warp reads both pages of its pair; masked probabilities must meet finite bytes).
 OGB_DEVICE bool fp8_produce_wide(const CUtensorMap* kv_map, const AttnParams& p, uint8_t* stages, float* stage_scales,
                                  uint64_t* full_bar, uint64_t* empty_bar, int seq, int kvh, int ctx, int b_begin, int b_end,
-                                 int lane) {
+                                 int kv_lo, int lane) {
   const int n_pages = (ctx + kPageTokens - 1) / kPageTokens;
   const int* table = p.page_table + static_cast<size_t>(seq) * p.max_pages;
   int stage = 0;
@@ -424,7 +428,7 @@ OGB_DEVICE bool fp8_produce_wide(const CUtensorMap* kv_map, const AttnParams& p,
     const int n_load = min(kMmaPages, ((n_pages - b * kMmaPages + 1) >> 1) << 1);
     int64_t page = 0;
     if (lane < n_load) {
-      const int pi = min(min(b * kMmaPages + lane, n_pages - 1), p.max_pages - 1);
+      const int pi = skip_gap_page(min(min(b * kMmaPages + lane, n_pages - 1), p.max_pages - 1), p.window, p.sink, kv_lo);
       page = table[pi];
       if (page < 0 || page >= p.num_pages) { atomicOr(p.status, kStatusIndexOutOfRange); page = 0; }
     }
@@ -462,10 +466,13 @@ __global__ void __maxnreg__(168) paged_decode_e4m3_mma_kernel(const __grid_const
   const int ctx = p.ctx_len[seq];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int b_begin = 0, b_end = 0;
+  const int kv_lo = (p.window > 0) ? max(0, ctx - p.window) : 0;
+  const int sink = (p.window > 0) ? p.sink : 0;
   if (ctx > 0) {
+    const int first = (sink > 0) ? 0 : kv_lo / kMmaKeys;
     const int last = (ctx + kMmaKeys - 1) / kMmaKeys;
-    const int per = (last + p.num_splits - 1) / p.num_splits;
-    b_begin = split * per;
+    const int per = (last - first + p.num_splits - 1) / p.num_splits;
+    b_begin = first + split * per;
     b_end = min(b_begin + per, last);
   }
   if (b_begin >= b_end) {
@@ -486,7 +493,7 @@ __global__ void __maxnreg__(168) paged_decode_e4m3_mma_kernel(const __grid_const
   }
   __syncthreads();
   if (warp == 4) {
-    if (!fp8_produce_wide(&kv_map, p, stages, stage_scales, full_bar, empty_bar, seq, kvh, ctx, b_begin, b_end, lane) && lane == 0)
+    if (!fp8_produce_wide(&kv_map, p, stages, stage_scales, full_bar, empty_bar, seq, kvh, ctx, b_begin, b_end, kv_lo, lane) && lane == 0)
       atomicOr(p.status, kStatusWaitTimeout);
     return;
   }
@@ -571,7 +578,7 @@ __global__ void __maxnreg__(168) paged_decode_e4m3_mma_kernel(const __grid_const
         for (int e = 0; e < 2; ++e) {
           const int col = tok0 + 8 * ng + 2 * q + e;
           const float s = (c[e] + c[2 + e] * 0.0625f) * kf[pg] + lv[pg];
-          sc[ng][e] = (col < ctx) ? s : -INFINITY;
+          sc[ng][e] = (col < ctx && (col >= kv_lo || col < sink)) ? s : -INFINITY;
         }
       }
       float mx = fmaxf(fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1])),
@@ -702,6 +709,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_prefill_fp8_kernel(const _
   const int pos0 = ctx - q_len + q0;
   if (rows <= 0 || ctx <= 0) return;
   const int kv_end = min(ctx, pos0 + rows);
+  const int kv_lo = (p.window > 0) ? max(0, pos0 - p.window + 1) : 0;   // first key any row of the tile sees in its window
   const int b_end = (kv_end + kKvBlock - 1) / kKvBlock;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -711,7 +719,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_prefill_fp8_kernel(const _
   }
   __syncthreads();
   if (warp == 4) {
-    if (lane == 0 && !fp8_produce(&kv_map, p, stages, full_bar, empty_bar, kPreStages, seq, kvh, ctx, 0, b_end))
+    if (lane == 0 && !fp8_produce(&kv_map, p, stages, full_bar, empty_bar, kPreStages, seq, kvh, ctx, 0, b_end, kv_lo))
       atomicOr(p.status, kStatusWaitTimeout);
     return;
   }
@@ -750,7 +758,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_prefill_fp8_kernel(const _
     expand_page(raw + warp * kRawPage, tile_k + warp * kWorkPage, lane, 32, p.kv_fmt);
     expand_page(raw + (4 + warp) * kRawPage, tile_v + warp * kWorkPage, lane, 32, p.kv_fmt);
     if (lane < 2) {
-      const int64_t page = page_of(p, seq, ctx, b * 4 + warp);
+      const int64_t page = page_of(p, seq, ctx, b * 4 + warp, kv_lo);
       sc_sh[warp * 2 + lane] = p.kv_scales[(page * p.hkv + kvh) * 2 + lane];
     }
     __syncwarp();
@@ -778,7 +786,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_prefill_fp8_kernel(const _
       for (int e = 0; e < 4; ++e) {
         const int col = kv_base + 8 * j + 2 * (lane & 3) + (e & 1);
         const int qpos = (e < 2) ? qpos_a : qpos_b;
-        s[j][e] = (col <= qpos && col < ctx) ? s[j][e] * ks : -INFINITY;
+        s[j][e] = key_visible(col, qpos, ctx, p.window, p.sink) ? s[j][e] * ks : -INFINITY;
       }
     }
 #pragma unroll
@@ -892,7 +900,7 @@ extern "C" int ogb_attn_set_e4m3_mma(int mode) {
 static int launch_decode_q(const void* q, void* out, const void* pool, const float* scales, int kv_fmt, const int* page_table,
                            const int* ctx_len, int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d,
                            int q_stride, int o_stride, float scale, int num_splits, float* part_o, float* part_ml,
-                           int* status, void* stream) {
+                           int window, int sink, int* status, void* stream) {
   if (num_seqs <= 0) return 0;
   if (kv_fmt != 0 && kv_fmt != 1) return -3;
   if (d != kD || hkv <= 0 || hq % hkv != 0 || hq / hkv > 16 || (q_stride % 8) != 0 || scales == nullptr) return -3;
@@ -904,6 +912,7 @@ static int launch_decode_q(const void* q, void* out, const void* pool, const flo
   AttnParams p{};
   fill_params(p, q, out, scales, page_table, ctx_len, num_seqs, max_pages, num_pages, hq, hkv, q_stride, o_stride, scale, status);
   p.num_splits = num_splits; p.part_o = part_o; p.part_ml = part_ml; p.kv_fmt = kv_fmt;
+  p.window = window; p.sink = window > 0 ? sink : 0;
   static bool attr_set = false;
   if (!attr_set) {
     OGB_CUDA_CHECK(cudaFuncSetAttribute(paged_decode_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem));
@@ -937,7 +946,7 @@ static int launch_decode_q(const void* q, void* out, const void* pool, const flo
 static int launch_prefill_q(const void* q, void* out, const void* pool, const float* scales, int kv_fmt, const int* page_table,
                             const int* ctx_len, const int* cu_q, const int* tile_seq, const int* tile_q0, int num_tiles,
                             int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride,
-                            int o_stride, float scale, int* status, void* stream) {
+                            int o_stride, float scale, int window, int sink, int* status, void* stream) {
   if (num_tiles <= 0) return 0;
   if (kv_fmt != 0 && kv_fmt != 1) return -3;
   if (d != kD || hkv <= 0 || hq % hkv != 0 || (q_stride % 8) != 0 || (o_stride % 2) != 0 || scales == nullptr) return -3;
@@ -947,6 +956,7 @@ static int launch_prefill_q(const void* q, void* out, const void* pool, const fl
   AttnParams p{};
   fill_params(p, q, out, scales, page_table, ctx_len, num_seqs, max_pages, num_pages, hq, hkv, q_stride, o_stride, scale, status);
   p.cu_q = cu_q; p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.num_tiles = num_tiles; p.kv_fmt = kv_fmt;
+  p.window = window; p.sink = window > 0 ? sink : 0;
   static bool attr_set = false;
   if (!attr_set) {
     OGB_CUDA_CHECK(cudaFuncSetAttribute(paged_prefill_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPreSmem));
@@ -962,27 +972,28 @@ extern "C" int ogb_paged_decode_fp8(const void* q, void* out, const void* pool, 
                                     int q_stride, int o_stride, float scale, int num_splits, float* part_o, float* part_ml,
                                     int* status, void* stream) {
   return launch_decode_q(q, out, pool, scales, 0, page_table, ctx_len, num_seqs, max_pages, num_pages, hq, hkv, d, q_stride, o_stride,
-                         scale, num_splits, part_o, part_ml, status, stream);
+                         scale, num_splits, part_o, part_ml, 0, 0, status, stream);
 }
 extern "C" int ogb_paged_prefill_fp8(const void* q, void* out, const void* pool, const float* scales, const int* page_table,
                                      const int* ctx_len, const int* cu_q, const int* tile_seq, const int* tile_q0, int num_tiles,
                                      int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride,
                                      int o_stride, float scale, int* status, void* stream) {
   return launch_prefill_q(q, out, pool, scales, 0, page_table, ctx_len, cu_q, tile_seq, tile_q0, num_tiles, num_seqs, max_pages,
-                          num_pages, hq, hkv, d, q_stride, o_stride, scale, status, stream);
+                          num_pages, hq, hkv, d, q_stride, o_stride, scale, 0, 0, status, stream);
 }
 // One-byte pages in either format: kv_format 0 = e4m3, 1 = int8 (symmetric, same per-(page, head, K|V) scale layout).
 extern "C" int ogb_paged_decode_q8(const void* q, void* out, const void* pool, const float* scales, int kv_format,
                                    const int* page_table, const int* ctx_len, int num_seqs, int max_pages, int64_t num_pages,
                                    int hq, int hkv, int d, int q_stride, int o_stride, float scale, int num_splits,
-                                   float* part_o, float* part_ml, int* status, void* stream) {
+                                   float* part_o, float* part_ml, int window, int sink, int* status, void* stream) {
   return launch_decode_q(q, out, pool, scales, kv_format, page_table, ctx_len, num_seqs, max_pages, num_pages, hq, hkv, d, q_stride,
-                         o_stride, scale, num_splits, part_o, part_ml, status, stream);
+                         o_stride, scale, num_splits, part_o, part_ml, window, sink, status, stream);
 }
 extern "C" int ogb_paged_prefill_q8(const void* q, void* out, const void* pool, const float* scales, int kv_format,
                                     const int* page_table, const int* ctx_len, const int* cu_q, const int* tile_seq,
                                     const int* tile_q0, int num_tiles, int num_seqs, int max_pages, int64_t num_pages, int hq,
-                                    int hkv, int d, int q_stride, int o_stride, float scale, int* status, void* stream) {
+                                    int hkv, int d, int q_stride, int o_stride, float scale, int window, int sink, int* status,
+                                    void* stream) {
   return launch_prefill_q(q, out, pool, scales, kv_format, page_table, ctx_len, cu_q, tile_seq, tile_q0, num_tiles, num_seqs,
-                          max_pages, num_pages, hq, hkv, d, q_stride, o_stride, scale, status, stream);
+                          max_pages, num_pages, hq, hkv, d, q_stride, o_stride, scale, window, sink, status, stream);
 }

@@ -160,10 +160,13 @@ __global__ void __launch_bounds__(kTcThreads) paged_decode_e4m3_tc_kernel(const 
   const int ctx = p.ctx_len[seq];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int b_begin = 0, b_end = 0;
+  const int kv_lo = (p.window > 0) ? max(0, ctx - p.window) : 0;     // first key inside the window
+  const int sink = (p.window > 0) ? p.sink : 0;
   if (ctx > 0) {
+    const int first = (sink > 0) ? 0 : kv_lo / kTcKeys;             // with sinks the walk starts at key 0 (gap blocks are masked)
     const int last = (ctx + kTcKeys - 1) / kTcKeys;
-    const int per = (last + p.num_splits - 1) / p.num_splits;
-    b_begin = split * per;
+    const int per = (last - first + p.num_splits - 1) / p.num_splits;
+    b_begin = first + split * per;
     b_end = min(b_begin + per, last);
   }
   if (b_begin >= b_end) {
@@ -217,7 +220,7 @@ __global__ void __launch_bounds__(kTcThreads) paged_decode_e4m3_tc_kernel(const 
       const int n_load = side ? kTcPages : min(kTcPages, n_pages - b * kTcPages);
       int64_t page = 0;
       if (lane < kTcPages) {
-        const int pi = min(min(b * kTcPages + lane, n_pages - 1), p.max_pages - 1);
+        const int pi = skip_gap_page(min(min(b * kTcPages + lane, n_pages - 1), p.max_pages - 1), p.window, p.sink, kv_lo);
         page = table[pi];
         if (page < 0 || page >= p.num_pages) { atomicOr(p.status, kStatusIndexOutOfRange); page = 0; }
       }
@@ -363,7 +366,8 @@ __global__ void __launch_bounds__(kTcThreads) paged_decode_e4m3_tc_kernel(const 
       const float ks = sh.scales[s][t >> 4][0];
       const float vs = fmaxf(sh.scales[s][t >> 4][1], 1e-30f);
       const float lv = __log2f(vs), inv_v = __fdividef(1.f, vs);
-      const bool valid = (b_begin + i) * kTcKeys + t < ctx;
+      const int key = (b_begin + i) * kTcKeys + t;
+      const bool valid = key < ctx && (key >= kv_lo || key < sink);
       float sc[8], blk[8];
 #pragma unroll
       for (int g = 0; g < 8; ++g) {

@@ -285,6 +285,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_
           int pi = b * (BN / kPageTokens) + i;
           if (pi > n_pages - 1) pi = n_pages - 1;      // tail: re-read the last page, masked later
           if (pi > p.max_pages - 1) pi = p.max_pages - 1;
+          pi = skip_gap_page(pi, p.window, 0, kv_lo);    // pages before the window may have been released
           int64_t page = table[pi];
           if (page < 0 || page >= p.num_pages) {
             atomicOr(p.status, kStatusIndexOutOfRange);
@@ -626,8 +627,11 @@ extern "C" void ogb_prefill_tc_debug(void* buf16, int tile) {
 extern "C" int ogb_paged_prefill_tc_bf16(const void* q, void* out, const void* pool, const int* page_table, const int* ctx_len,
                                          const int* cu_q, const int* tile_seq, const int* tile_q0, int num_tiles, int num_seqs,
                                          int q_rows, int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride,
-                                         int o_stride, float scale, int window, int* status, void* stream) {
+                                         int o_stride, float scale, int window, int sink, int* status, void* stream) {
   if (num_tiles <= 0) return 0;
+  if (window > 0 && sink > 0)   // attention sinks: the block walk with a gap lives in the mma.sync kernel
+    return ogb_paged_prefill_bf16(q, out, pool, page_table, ctx_len, cu_q, tile_seq, tile_q0, num_tiles, num_seqs, max_pages,
+                                  num_pages, hq, hkv, d, q_stride, o_stride, scale, window, sink, status, stream);
   if ((d != 64 && d != 128) || hkv <= 0 || hq % hkv != 0 || (q_stride % 8) != 0 || (o_stride % 8) != 0 || q_rows <= 0) return -3;
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(pool)) & 15) return -4;
   AttnParams p{};

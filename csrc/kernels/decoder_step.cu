@@ -23,7 +23,7 @@ struct LayerPtrs {
 };
 
 struct DecoderPlan {
-  int num_layers, hidden, hq, hkv, d, rotary_dim, interleaved, inter_local, vocab, swiglu_bn, window, max_pages, max_pos;
+  int num_layers, hidden, hq, hkv, d, rotary_dim, interleaved, inter_local, vocab, swiglu_bn, window, sink, max_pages, max_pos;
   int tp, prefill_tc;
   int64_t num_pages;
   float eps, scale;
@@ -49,7 +49,7 @@ using namespace ogb;
   } while (0)
 
 // iparams: num_layers, hidden, hq, hkv, d, rotary_dim, interleaved, inter_local, vocab, swiglu_bn, window, max_pages,
-//          max_pos, tp, prefill_tc (1: prefill attention on the tcgen05 kernel)
+//          max_pos, tp, prefill_tc (1: prefill attention on the tcgen05 kernel), sink (attention-sink keys kept by a window)
 // fparams: eps, scale
 // gptrs  : embed, final_norm, lm_head, cos_sin, x, h, qkv, attn, act, x_last, h_last, logits, partial, part_o, part_ml, status
 // lptrs  : per layer 8 pointers (ln1, qkv_w, qkv_b, o_w, ln2, gate_up_w, down_w, kv_pool)
@@ -61,6 +61,7 @@ extern "C" void* ogb_decoder_create(const int* iparams, int64_t num_pages, const
   p->swiglu_bn = iparams[9]; p->window = iparams[10]; p->max_pages = iparams[11]; p->max_pos = iparams[12];
   p->tp = iparams[13];
   p->prefill_tc = iparams[14];
+  p->sink = iparams[15];
   p->num_pages = num_pages;
   p->eps = fparams[0]; p->scale = fparams[1];
   auto P = [&](int i) { return reinterpret_cast<void*>(gptrs[i]); };
@@ -153,17 +154,17 @@ extern "C" int ogb_decoder_step(void* plan, const int* token_ids, const int* pos
     if (Nd > 0) {
       STEP_CHECK(ogb_paged_decode_bf16(p->qkv, p->attn, L.kv_pool, page_table, ctx_len, Nd, p->max_pages, p->num_pages, hq,
                                        hkv, d, qkv_n, attn_n, p->scale, decode_splits, p->part_o, p->part_ml, p->window,
-                                       p->status, stream));
+                                       p->sink, p->status, stream));
     }
     if (Np > 0) {
       if (p->prefill_tc && (d == 64 || d == 128) && attn_n % 8 == 0) {
         STEP_CHECK(ogb_paged_prefill_tc_bf16(qkv_prefill, attn_prefill, L.kv_pool, page_table + static_cast<size_t>(Nd) * p->max_pages,
                                              ctx_len + Nd, cu_q, tile_seq, tile_q0, num_tiles, Np, T - Nd, p->max_pages,
-                                             p->num_pages, hq, hkv, d, qkv_n, attn_n, p->scale, p->window, p->status, stream));
+                                             p->num_pages, hq, hkv, d, qkv_n, attn_n, p->scale, p->window, p->sink, p->status, stream));
       } else {
         STEP_CHECK(ogb_paged_prefill_bf16(qkv_prefill, attn_prefill, L.kv_pool, page_table + static_cast<size_t>(Nd) * p->max_pages,
                                           ctx_len + Nd, cu_q, tile_seq, tile_q0, num_tiles, Np, p->max_pages, p->num_pages, hq,
-                                          hkv, d, qkv_n, attn_n, p->scale, p->window, p->status, stream));
+                                          hkv, d, qkv_n, attn_n, p->scale, p->window, p->sink, p->status, stream));
       }
     }
     if (!tp) {

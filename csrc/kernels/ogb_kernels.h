@@ -44,21 +44,23 @@ int ogb_rope_kv_append_fp8(void* qkv, const int* positions, const int* slots, co
                            float* scales, int tokens, int hq, int hkv, int d, int rotary_dim, int interleaved,
                            int page_size, int64_t num_slots, int max_pos, int* status, void* stream);
 
-// Paged GQA attention.  q rows live inside the packed qkv buffer (row stride q_stride elements).
+// Paged GQA attention.  q rows live inside the packed qkv buffer (row stride q_stride elements).  window > 0: a query
+// sees only its last `window` keys, plus -- attention sinks -- the first `sink` keys of the sequence; the page-table
+// entries of pages that lie wholly between the two are never read (the scheduler may have released them).
 int ogb_paged_prefill_bf16(const void* q, void* out, const void* pool, const int* page_table, const int* ctx_len,
                            const int* cu_q, const int* tile_seq, const int* tile_q0, int num_tiles, int num_seqs,
                            int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride, int o_stride,
-                           float scale, int window, int* status, void* stream);
+                           float scale, int window, int sink, int* status, void* stream);
 // Prefill attention on tcgen05 / TMEM: the contract of ogb_paged_prefill_bf16 plus `q_rows`, the number of rows of
 // the packed query buffer the kernel's tensor map may read; each 128-row aligned pair of 64-row tiles is one CTA.
 int ogb_paged_prefill_tc_bf16(const void* q, void* out, const void* pool, const int* page_table, const int* ctx_len,
                               const int* cu_q, const int* tile_seq, const int* tile_q0, int num_tiles, int num_seqs,
                               int q_rows, int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride,
-                              int o_stride, float scale, int window, int* status, void* stream);
+                              int o_stride, float scale, int window, int sink, int* status, void* stream);
 int ogb_paged_decode_bf16(const void* q, void* out, const void* pool, const int* page_table, const int* ctx_len,
                           int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride,
                           int o_stride, float scale, int num_splits, float* part_o, float* part_ml, int window,
-                          int* status, void* stream);
+                          int sink, int* status, void* stream);
 
 // Same over e4m3 pages [pages, hkv, 2, 16, 128] uint8 with scales [pages, hkv, 2] fp32 (head_dim 128 only).
 int ogb_paged_decode_fp8(const void* q, void* out, const void* pool, const float* scales, const int* page_table,
@@ -80,12 +82,12 @@ int ogb_rope_kv_append_q8(void* qkv, const int* positions, const int* slots, con
 int ogb_attn_set_e4m3_mma(int mode);
 int ogb_paged_decode_q8(const void* q, void* out, const void* pool, const float* scales, int kv_format, const int* page_table,
                         const int* ctx_len, int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d,
-                        int q_stride, int o_stride, float scale, int num_splits, float* part_o, float* part_ml, int* status,
-                        void* stream);
+                        int q_stride, int o_stride, float scale, int num_splits, float* part_o, float* part_ml, int window,
+                        int sink, int* status, void* stream);
 int ogb_paged_prefill_q8(const void* q, void* out, const void* pool, const float* scales, int kv_format, const int* page_table,
                          const int* ctx_len, const int* cu_q, const int* tile_seq, const int* tile_q0, int num_tiles,
                          int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride, int o_stride,
-                         float scale, int* status, void* stream);
+                         float scale, int window, int sink, int* status, void* stream);
 
 // Sampling.  logits [rows, vocab] bf16 (ld = row stride).  out_tokens int32 [rows].
 int ogb_argmax_bf16(const void* logits, int* out_tokens, int rows, int vocab, int ld, void* stream);

@@ -10,6 +10,8 @@
 //     streams whole 32-weight blocks with 128-bit loads (one scale per load), nibbles are turned into
 //     floats with the 0x4300 bf16 magic-number trick (no int->float conversions), fp32 accumulate;
 //   * w4a16_dequant_kernel -- expands W to bf16 [N, K] so larger M runs on the tcgen05 GEMM.
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 #include "ogb_kernels.h"
 
@@ -27,6 +29,12 @@ OGB_DEVICE void nibbles_to_float(uint32_t w, float (&f)[8]) {
     const uint32_t bits = (0x4300u | ((w >> (4 * i)) & 0xFu)) << 16;
     f[i] = __uint_as_float(bits) - 128.0f;
   }
+}
+
+OGB_DEVICE __half2 as_half2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+OGB_DEVICE uint32_t pack_f16(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
 }
 
 template <bool SCALES_F32>
@@ -177,6 +185,15 @@ __global__ void w4a16_dequant_kernel(const uint8_t* __restrict__ qw, const void*
 // matrices that stream in 1-2 us).  Activations are staged once per CTA in shared memory as bf16 -- after
 // the prologue, rounded exactly as the unfused path rounds them -- in chunks of kGemvChunk values of K.
 // Each warp owns kFusedCols output columns; lanes stride over the 32-weight blocks of a chunk.
+//
+// Arithmetic: two weights per instruction.  A 32-bit word holds nibbles n0..n7; `(w & 0x000F000F) | 0x64006400` read as
+// two fp16 is (1024 + n0, 1024 + n4) and `(w & 0x00F000F0) | 0x54005400` is (64 + n1, 64 + n5) -- no shift needed for
+// the odd nibbles -- and the same on w >> 8 gives (n2, n6) and (n3, n7).  One HSUB2 removes the offset and the zero
+// point exactly, one HFMA2 multiplies by the matching pair of activations, which are staged as fp16 in the order
+// (x0, x4, x1, x5, x2, x6, x3, x7) of every eight.  A block's 32 products are summed in two fp16x2 accumulators (8
+// terms each), then go to fp32 for the scale and the sum over blocks, as the reference's fp16 GEMV variants do
+// (crates/onnx-runtime-ep-cuda/src/kernels/marlin_gemm.rs:585).  The activations are rounded to bf16 first, exactly as
+// the unfused path rounds them; a bf16 value is an fp16 value unless it lies outside +-65504 (clamped) or below 6e-8.
 // ------------------------------------------------------------------------------------------
 constexpr int kFusedCols = 2;
 constexpr int kFusedWarps = 8;
@@ -317,7 +334,20 @@ __global__ void __launch_bounds__(kFusedWarps * 32) w4a16_gemv_fused_kernel(cons
             o = make_uint4(oa[0], oa[1], oa[2], oa[3]);
           }
         }
-        *reinterpret_cast<uint4*>(xs + m * kGemvChunk + i) = o;
+        {
+          // bf16 x8 -> fp16 x8 in the pair order of the nibble words
+          const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+          float v[8];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 t = unpack_bf16(ow[e]);
+            v[2 * e] = fminf(fmaxf(t.x, -65504.f), 65504.f);
+            v[2 * e + 1] = fminf(fmaxf(t.y, -65504.f), 65504.f);
+          }
+          uint4 h;
+          h.x = pack_f16(v[0], v[4]); h.y = pack_f16(v[1], v[5]); h.z = pack_f16(v[2], v[6]); h.w = pack_f16(v[3], v[7]);
+          *reinterpret_cast<uint4*>(xs + m * kGemvChunk + i) = h;
+        }
       }
     }
     __syncthreads();
@@ -327,43 +357,47 @@ __global__ void __launch_bounds__(kFusedWarps * 32) w4a16_gemv_fused_kernel(cons
         BlockW<C, SCALES_F32> w;
         if (k0 == 0 && j == j0 && have_w0) w = w0;
         else w.load(p, n0, b0 + j, kb, zp_stride);
-        float dot[C][MT], xsum[MT];
+        __half2 dot[C][MT][2];
 #pragma unroll
-        for (int m = 0; m < MT; ++m) {
-          xsum[m] = 0.f;
+        for (int c = 0; c < C; ++c)
 #pragma unroll
-          for (int c = 0; c < C; ++c) dot[c][m] = 0.f;
+          for (int m = 0; m < MT; ++m) dot[c][m][0] = dot[c][m][1] = __float2half2_rn(0.f);
+        __half2 off_lo[C], off_hi[C];     // what the two magic numbers add, plus the zero point
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+          off_lo[c] = __float2half2_rn(1024.f + w.zz[c]);
+          off_hi[c] = __float2half2_rn(64.f + w.zz[c]);
         }
         const __nv_bfloat16* xb = xs + j * 32;
 #pragma unroll
         for (int wi = 0; wi < 4; ++wi) {
-          float f[C][8];
+          __half2 wv[C][4];
 #pragma unroll
           for (int c = 0; c < C; ++c) {
             const uint32_t word = (wi == 0) ? w.wq[c].x : (wi == 1) ? w.wq[c].y : (wi == 2) ? w.wq[c].z : w.wq[c].w;
-            nibbles_to_float(word, f[c]);
+            const uint32_t w8 = word >> 8;
+            wv[c][0] = __hsub2(as_half2((word & 0x000F000Fu) | 0x64006400u), off_lo[c]);
+            wv[c][1] = __hsub2(as_half2((word & 0x00F000F0u) | 0x54005400u), off_hi[c]);
+            wv[c][2] = __hsub2(as_half2((w8 & 0x000F000Fu) | 0x64006400u), off_lo[c]);
+            wv[c][3] = __hsub2(as_half2((w8 & 0x00F000F0u) | 0x54005400u), off_hi[c]);
           }
 #pragma unroll
           for (int m = 0; m < MT; ++m) {
             const uint4 q = *reinterpret_cast<const uint4*>(xb + m * kGemvChunk + 8 * wi);
-            float xv[8];
-            float2 t;
-            t = unpack_bf16(q.x); xv[0] = t.x; xv[1] = t.y;
-            t = unpack_bf16(q.y); xv[2] = t.x; xv[3] = t.y;
-            t = unpack_bf16(q.z); xv[4] = t.x; xv[5] = t.y;
-            t = unpack_bf16(q.w); xv[6] = t.x; xv[7] = t.y;
+            const __half2 xv[4] = {as_half2(q.x), as_half2(q.y), as_half2(q.z), as_half2(q.w)};
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              xsum[m] += xv[i];
+            for (int c = 0; c < C; ++c)
 #pragma unroll
-              for (int c = 0; c < C; ++c) dot[c][m] += f[c][i] * xv[i];
-            }
+              for (int i = 0; i < 4; ++i) dot[c][m][wi & 1] = __hfma2(wv[c][i], xv[i], dot[c][m][wi & 1]);
           }
         }
 #pragma unroll
         for (int c = 0; c < C; ++c)
 #pragma unroll
-          for (int m = 0; m < MT; ++m) acc[c][m] += w.sc[c] * (dot[c][m] - w.zz[c] * xsum[m]);
+          for (int m = 0; m < MT; ++m) {
+            const float2 d0 = __half22float2(dot[c][m][0]), d1 = __half22float2(dot[c][m][1]);
+            acc[c][m] += w.sc[c] * ((d0.x + d0.y) + (d1.x + d1.y));
+          }
       }
     }
   }

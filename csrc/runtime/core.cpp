@@ -217,8 +217,36 @@ int64_t Core::add_request(const int32_t* prompt, int n, int max_new_tokens, cons
 
 void Core::free_pages(Sequence& s, bool publish_prefix) {
   if (publish_prefix) publish_full_pages(s);
-  for (int p : s.pages) pool_.release(p);
+  for (int p : s.pages) if (p >= 0) pool_.release(p);
   s.pages.clear();
+  s.trim_end = 0;
+}
+
+void Core::set_window(int window, int sink_tokens) {
+  window_ = std::max(window, 0);
+  sink_pages_ = window_ > 0 ? (std::max(sink_tokens, 0) + kPageTokens - 1) / kPageTokens : 0;
+}
+
+int Core::released_pages(int64_t seq_id) const {
+  const Sequence* s = find(seq_id);
+  if (!s) return -1;
+  int n = 0;
+  for (int p : s->pages) n += p < 0 ? 1 : 0;
+  return n;
+}
+
+// The next query of `s` sits at position num_computed and sees keys above num_computed - window; a rejected draft can
+// pull num_computed back by at most max_draft_tokens, and one more page of slack keeps ordinary session rewinds cheap.
+void Core::trim_window(Sequence& s) {
+  if (window_ <= 0) return;
+  const int first_needed = s.num_computed - window_ - cfg_.max_draft_tokens - kPageTokens;
+  const int hi = std::min(first_needed / kPageTokens, static_cast<int>(s.pages.size()));
+  const int lo = std::max(sink_pages_, s.trim_end);
+  if (first_needed <= 0 || hi <= lo) return;
+  for (int i = lo; i < hi; ++i) {
+    if (s.pages[i] >= 0) { pool_.release(s.pages[i]); s.pages[i] = -1; }
+  }
+  s.trim_end = hi;
 }
 
 void Core::publish_full_pages(Sequence& s) {
@@ -227,7 +255,7 @@ void Core::publish_full_pages(Sequence& s) {
   uint64_t h = 0;
   for (int i = 0; i < full && i < static_cast<int>(s.pages.size()); ++i) {
     h = BlockPool::chain_hash(h, s.tokens.data() + i * kPageTokens, kPageTokens);
-    pool_.publish(s.pages[i], h);
+    if (s.pages[i] >= 0) pool_.publish(s.pages[i], h);
   }
 }
 
@@ -296,13 +324,14 @@ bool Core::preempt_one(Sequence* keep, std::vector<std::pair<int, int>>& swap_ou
   if (cfg_.preempt == PreemptMode::Swap && static_cast<int>(host_free_.size()) >= used_pages && used_pages > 0) {
     v.host_pages.clear();
     for (int i = 0; i < used_pages; ++i) {
+      if (v.pages[i] < 0) { v.host_pages.push_back(-1); continue; }   // released under the sliding window: nothing to save
       const int hp = host_free_.back();
       host_free_.pop_back();
       v.host_pages.push_back(hp);
       swap_out.emplace_back(v.pages[i], hp);
       move_kinds_.push_back(1);
     }
-    for (int p : v.pages) pool_.release(p);
+    for (int p : v.pages) if (p >= 0) pool_.release(p);
     v.pages.clear();
     v.status = SeqStatus::Swapped;
     swapped_.push_back(v.id);
@@ -398,6 +427,7 @@ int Core::build_step(int32_t* plan) {
     const int used_pages = static_cast<int>(s->host_pages.size());
     if (used_pages + 1 > pool_.num_free()) break;
     for (int i = 0; i < used_pages; ++i) {
+      if (s->host_pages[i] < 0) { s->pages.push_back(-1); continue; }
       const int p = pool_.allocate();
       s->pages.push_back(p);
       swap_in.emplace_back(p, s->host_pages[i]);
@@ -574,7 +604,7 @@ void Core::finish(Sequence& s, FinishReason why) {
   s.status = SeqStatus::Finished;
   s.scheduled = 0;
   free_pages(s, why != FinishReason::Error);
-  for (int hp : s.host_pages) host_free_.push_back(hp);
+  for (int hp : s.host_pages) if (hp >= 0) host_free_.push_back(hp);
   s.host_pages.clear();
   running_.erase(std::remove(running_.begin(), running_.end(), s.id), running_.end());
   waiting_.erase(std::remove(waiting_.begin(), waiting_.end(), s.id), waiting_.end());
@@ -623,7 +653,10 @@ int Core::commit_step(const int32_t* sampled, int n, StepEvent* events, int max_
       // K/V of the last token and of the accepted drafts are valid; everything after is rewound
       s->num_computed = base + a;
       const int keep_pages = (s->num_computed + kPageTokens - 1) / kPageTokens;
-      while (static_cast<int>(s->pages.size()) > keep_pages) { pool_.release(s->pages.back()); s->pages.pop_back(); }
+      while (static_cast<int>(s->pages.size()) > keep_pages) {
+        if (s->pages.back() >= 0) pool_.release(s->pages.back());
+        s->pages.pop_back();
+      }
       bool done = false;
       for (int j = 0; j < a && !done; ++j) done = push_token(s, accepted[j]);
       if (done) {
@@ -635,6 +668,12 @@ int Core::commit_step(const int32_t* sampled, int n, StepEvent* events, int max_
       push_token(s, sampled[r + group - 1]);
     }
     r += group;
+  }
+  if (window_ > 0) {
+    for (int64_t id : step_seqs_) {
+      Sequence* s = find(id);
+      if (s && s->status == SeqStatus::Running) trim_window(*s);
+    }
   }
   step_rows_.clear();
   step_seqs_.clear();
@@ -658,9 +697,10 @@ int64_t Core::fork(int64_t seq_id) {
   c.scheduled = 0;
   c.samples_this_step = false;
   c.rng_state ^= 0xD1B54A32D192ED03ull * static_cast<uint64_t>(c.id);
-  for (int p : c.pages) pool_.retain(p);
+  for (int p : c.pages) if (p >= 0) pool_.retain(p);
   if (s->status == SeqStatus::Swapped) {  // a swapped parent has no device pages to share
     c.pages.clear();
+    c.trim_end = 0;
     c.num_computed = 0;
     c.status = SeqStatus::Waiting;
   }
@@ -675,13 +715,15 @@ int64_t Core::fork(int64_t seq_id) {
 bool Core::rewind(int64_t seq_id, int new_len) {
   Sequence* s = find(seq_id);
   if (!s || new_len < 1 || new_len > static_cast<int>(s->tokens.size())) return false;
+  // keys released under the sliding window cannot come back into view
+  if (s->trim_end > sink_pages_ && std::min(new_len, s->num_computed) - window_ < s->trim_end * kPageTokens) return false;
   s->tokens.resize(new_len);
   if (s->prompt_len > new_len) s->prompt_len = new_len;
   // the last kept token must be re-run to produce logits unless its successor is about to be fed
   if (s->num_computed > new_len) s->num_computed = new_len;
   const int keep_pages = (s->num_computed + kPageTokens - 1) / kPageTokens;
   while (static_cast<int>(s->pages.size()) > keep_pages) {
-    pool_.release(s->pages.back());
+    if (s->pages.back() >= 0) pool_.release(s->pages.back());
     s->pages.pop_back();
   }
   return true;
@@ -810,6 +852,8 @@ void* ogb_core_create(int num_pages, int num_host_pages, int max_seqs, int max_t
   return new Core(c);
 }
 void ogb_core_destroy(void* h) { delete static_cast<Core*>(h); }
+void ogb_core_set_window(void* h, int window, int sink_tokens) { static_cast<Core*>(h)->set_window(window, sink_tokens); }
+int ogb_core_released_pages(void* h, int64_t seq_id) { return static_cast<Core*>(h)->released_pages(seq_id); }
 int ogb_core_layout(void* h, int32_t* out, int cap) {
   const PlanLayout& l = static_cast<Core*>(h)->layout();
   const int32_t v[] = {l.header, l.token_ids, l.positions, l.slots, l.seq_slot, l.ctx_len, l.cu_q, l.page_table,

@@ -53,7 +53,8 @@ struct Sequence {
   uint64_t rng_state = 0;
   SeqStatus status = SeqStatus::Waiting;
   FinishReason finish = FinishReason::None;
-  std::vector<int32_t> pages;        // device page ids, one per 16 tokens
+  std::vector<int32_t> pages;        // device page ids, one per 16 tokens; -1 = released (see Core::set_window)
+  int trim_end = 0;                  // pages [sink pages, trim_end) have been released under the sliding window
   std::vector<int32_t> host_pages;   // swap space page ids while Swapped
   int num_cached_prefix = 0;         // tokens served from the prefix cache at admission
   int scheduled = 0;                 // tokens scheduled in the step being built
@@ -158,7 +159,14 @@ class Core {
 
   // session-style operations on a live sequence
   int64_t fork(int64_t seq_id);                    // copy-on-write clone (shares pages)
-  bool rewind(int64_t seq_id, int new_len);        // drop trailing tokens and their pages
+  bool rewind(int64_t seq_id, int new_len);
+  // Sliding-window retention with attention sinks (the policy of crates/onnx-genai-kv/src/paged_cache.rs:483-585, kept
+  // position-indexed instead of compacted): once a sequence has run `window` + slack tokens past a page, no later query
+  // can see it, so every page that lies wholly between the first ceil(sink_tokens / 16) pages and the window is released
+  // and its page-table entry becomes -1 (the attention kernels never read those entries).  window <= 0 turns it off.
+  // A rewind that would bring released keys back into view is refused.
+  void set_window(int window, int sink_tokens);
+  int released_pages(int64_t seq_id) const;        // drop trailing tokens and their pages
   int seq_len(int64_t seq_id) const;
   int seq_tokens(int64_t seq_id, int32_t* out, int cap) const;
   // Speculative decoding: propose `k` tokens to follow the sequence's last token.  The next step feeds the
@@ -203,6 +211,7 @@ class Core {
   const Sequence* find(int64_t id) const;
   bool ensure_pages(Sequence& s, int new_len, std::vector<std::pair<int, int>>& copies);
   void free_pages(Sequence& s, bool publish_prefix);
+  void trim_window(Sequence& s);
   void try_prefix_attach(Sequence& s);
   void publish_full_pages(Sequence& s);
   bool preempt_one(Sequence* keep, std::vector<std::pair<int, int>>& swap_out);
@@ -226,6 +235,7 @@ class Core {
   int64_t clock_ = 0;
   int64_t step_id_ = 0;
   int64_t preemptions_ = 0;
+  int window_ = 0, sink_pages_ = 0;   // sliding-window retention (set_window)
   int64_t spec_proposed_ = 0, spec_accepted_ = 0, spec_steps_ = 0;
 };
 

@@ -196,6 +196,35 @@ def bench_misc(timer, pk):
     return rows
 
 
+def bench_w4a16(timer, pk):
+    """Decode-size int4 projections (block 32, bf16 scales) of the 7B and 0.5B shapes: bytes streamed per launch
+    (nibbles + scales) over the measured copy bandwidth."""
+    from onnx_genai_b200.ops.quant import QuantLinear
+
+    rows = []
+    cases = [("7b_gate_up", 37888, 3584, "rmsnorm"), ("7b_down", 3584, 18944, "silu_mul"), ("7b_qkv", 4608, 3584, "rmsnorm"),
+             ("0.5b_gate_up", 9728, 896, "rmsnorm"), ("0.5b_down", 896, 4864, "silu_mul")]
+    for name, n_, k_, pro in cases:
+        q = torch.randint(0, 256, (n_, k_ // 32, 16), dtype=torch.uint8)
+        sc = (torch.rand(n_, k_ // 32) * 0.02 + 0.005).bfloat16()
+        lin = QuantLinear(q, sc, None, None, k=k_, device="cuda")
+        for m in (1, 4):
+            out = torch.empty(m, n_, device="cuda", dtype=torch.bfloat16)
+            if pro == "rmsnorm":
+                x = torch.randn(m, k_, device="cuda").bfloat16()
+                g = torch.ones(k_, device="cuda", dtype=torch.bfloat16)
+                fn = lambda: lin.fused(x, out, norm_weight=g, eps=1e-6)
+            else:
+                x = torch.randn(m, 2 * k_, device="cuda").bfloat16()
+                fn = lambda: lin.fused(x, out, silu_mul=True)
+            med, _ = timer.time(fn)
+            nbytes = n_ * k_ // 2 + n_ * (k_ // 32) * 2
+            rows.append({"kernel": "w4a16_gemv_fused", "case": name, "m": m, "n": n_, "k": k_, "ms": round(med, 4),
+                         "gbs": round(nbytes / med / 1e6, 1), "frac_of_measured_hbm": round(nbytes / med / 1e6 / pk["hbm_gbs"], 3)})
+            print(json.dumps(rows[-1]), flush=True)
+    return rows
+
+
 def ncu_case(name: str, iters: int = 3):
     """Small single-kernel workloads for `ncu` captures: inputs larger than L2 where DRAM figures matter,
     a few hundred MB on the device at most, `iters` launches of the one kernel of interest."""
@@ -293,7 +322,7 @@ def ncu_case(name: str, iters: int = 3):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ncu-case", default="", help="run one small single-kernel workload (for ncu) and exit")
-    ap.add_argument("--what", default="gemm,attn,misc", help="comma list of gemm, attn, attn8 (one-byte KV pages), misc")
+    ap.add_argument("--what", default="gemm,attn,misc", help="comma list of gemm, attn, attn8 (one-byte KV pages), misc, w4 (int4 decode projections)")
     ap.add_argument("--json", default="")
     args = ap.parse_args()
     if args.ncu_case:
@@ -310,6 +339,8 @@ def main():
         res["attn8"] = bench_attention_one_byte(timer, pk)
     if "misc" in what:
         res["misc"] = bench_misc(timer, pk)
+    if "w4" in what:
+        res["w4a16"] = bench_w4a16(timer, pk)
     if args.json:
         Path(args.json).write_text(json.dumps(res, indent=1))
 

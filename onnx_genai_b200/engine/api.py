@@ -151,6 +151,10 @@ class Engine:
         if meta.vocab_size and meta.vocab_size != cfg.vocab:
             raise md.MetadataError(f"{d.metadata_path}: model.vocab_size={meta.vocab_size} but the graph's embedding has "
                                    f"{cfg.vocab} rows; fix the metadata or re-export the model")
+        if meta.sliding_window and cfg.sliding_window <= 0:
+            cfg.sliding_window = int(meta.sliding_window)         # graphs exported without local_window_size
+        if cfg.sliding_window > 0 and meta.sink_tokens:
+            cfg.attention_sinks = int(meta.sink_tokens)
         limit = meta.max_sequence_length or cfg.max_position
         max_seq_len = min(max_seq_len or limit, limit, cfg.max_position)
         tok = None

@@ -66,6 +66,10 @@ def load_runtime():
     lib.ogb_core_fork.restype = c_int64
     lib.ogb_core_rewind.argtypes = [P, c_int64, c_int]
     lib.ogb_core_rewind.restype = c_int
+    lib.ogb_core_set_window.argtypes = [P, c_int, c_int]
+    lib.ogb_core_set_window.restype = None
+    lib.ogb_core_released_pages.argtypes = [P, c_int64]
+    lib.ogb_core_released_pages.restype = c_int
     lib.ogb_core_set_draft.argtypes = [P, c_int64, I32P, c_int]
     lib.ogb_core_set_draft.restype = c_int
     lib.ogb_core_append_tokens.argtypes = [P, c_int64, I32P, c_int]
@@ -171,6 +175,15 @@ class Core:
 
     def rewind(self, sid, new_len):
         return bool(self.lib.ogb_core_rewind(self.h, sid, new_len))
+
+    def set_window(self, window: int, sink_tokens: int = 0):
+        """Sliding-window retention: pages that no later query can see -- all of them lie between the first
+        ceil(sink_tokens / 16) pages and the window -- are released as sequences advance (their page-table entries
+        become -1); a rewind that would need them again is refused.  ``window`` <= 0 turns it off."""
+        self.lib.ogb_core_set_window(self.h, int(window), int(sink_tokens))
+
+    def released_pages(self, sid) -> int:
+        return int(self.lib.ogb_core_released_pages(self.h, sid))
 
     def set_draft(self, sid, tokens):
         """Propose tokens to follow the sequence's last token; verified (and rewound) by the next step."""

@@ -48,6 +48,7 @@ class EngineConfig:
     policy: str = "fcfs"
     preempt: str = "recompute"
     enable_prefix_cache: bool = True
+    release_window_pages: bool = True  # sliding-window models: give back the KV pages no later query can see (sinks are kept)
     kv_dtype: str = "bf16"
     decode_splits: int = 0             # 0: pick from batch shape
     sync_sampled_tokens: bool = True   # TP: broadcast rank 0's tokens so replicas cannot diverge
@@ -134,6 +135,8 @@ class LLMEngine:
                                     policy=cfg.policy, preempt=cfg.preempt,
                                     enable_prefix_cache=cfg.enable_prefix_cache, eos_token=m.eos_token,
                                     max_draft_tokens=cfg.max_draft_tokens))
+        if m.sliding_window > 0 and cfg.release_window_pages:
+            self.core.set_window(m.sliding_window, m.attention_sinks)
         L = self.core.layout
         self.L = L
         self.plan_host = torch.zeros(L.total_words, dtype=torch.int32, pin_memory=is_cuda)

@@ -109,6 +109,8 @@ class InferenceMetadata:
     vocab_size: int | None = None
     io: ModelIo | None = None
     chunked_prefill_size: int | None = None
+    sliding_window: int | None = None      # model.attention.sliding_window: keys a query keeps seeing behind it
+    sink_tokens: int = 0                   # model.attention.sink_tokens: leading keys kept under the window (attention sinks)
     mixture_of_experts: MixtureOfExperts | None = None
     supports_tensor_parallel: bool | None = None
     min_tp_degree: int | None = None
@@ -150,6 +152,17 @@ def parse(doc: dict) -> InferenceMetadata:
     model = doc.get("model") or {}
     _closed(model, MODEL_KEYS, "model")
     md.max_sequence_length = model.get("max_sequence_length")
+    att = model.get("attention")
+    if isinstance(att, dict):
+        win, sink = att.get("sliding_window"), att.get("sink_tokens")
+        if win is not None:
+            if not isinstance(win, int) or isinstance(win, bool) or win <= 0:
+                raise MetadataError("model.attention.sliding_window must be an integer greater than zero")
+            md.sliding_window = win
+        if sink is not None:
+            if not isinstance(sink, int) or isinstance(sink, bool) or sink < 0:
+                raise MetadataError("model.attention.sink_tokens must be a non-negative integer")
+            md.sink_tokens = sink if win is not None else 0     # only meaningful under a sliding window
     md.vocab_size = model.get("vocab_size")
     rc = model.get("runtime_configurable") or {}
     if isinstance(rc, dict) and isinstance(rc.get("chunked_prefill"), dict):
@@ -269,6 +282,11 @@ def emit(cfg, required_capabilities=("kv_cache", "grouped_query_attention"), gen
         },
         "hardware_requirements": {"supports_tensor_parallel": bool(supports_tensor_parallel), "min_tp_degree": 1},
     }
+    if cfg.sliding_window > 0:
+        att = {"type": "group_query_attention", "sliding_window": int(cfg.sliding_window)}
+        if cfg.attention_sinks > 0:
+            att["sink_tokens"] = int(cfg.attention_sinks)
+        doc["model"]["attention"] = att
     if cfg.moe.num_experts:
         doc["model"]["mixture_of_experts"] = {
             "representation": "expert_major", "routed_expert_count": cfg.moe.num_experts, "shared_expert_count": 0,

@@ -39,11 +39,17 @@ class DecoderConfig:
     rotary_interleaved: bool = False
     rotary_dim: int = 0           # 0 = head_dim
     sliding_window: int = 0
+    attention_sinks: int = 0      # with a sliding window: leading tokens every query keeps seeing (rounded up to whole KV pages)
     weight_format: str = "bf16"   # "bf16" | "int4" (MatMulNBits block 32)
     int4_block: int = 32
     int4_scale_dtype: str = "bf16"
     moe: MoEConfig = field(default_factory=MoEConfig)
     eos_token: int = -1
+
+    @property
+    def sink_len(self) -> int:
+        """Attention-sink keys as the kernels see them: whole 16-token pages, and only under a sliding window."""
+        return ((self.attention_sinks + 15) // 16) * 16 if self.sliding_window > 0 and self.attention_sinks > 0 else 0
 
     @property
     def q_size(self) -> int:

@@ -335,10 +335,10 @@ class DecoderModel:
         lib.ogb_decoder_set_split_scratch.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
         lib.ogb_decoder_set_split_scratch.restype = None
         inter_local = w.layers[0].gate_up_w.shape[0] // 2
-        ip = (ctypes.c_int * 15)(cfg.num_layers, cfg.hidden, self.hq, self.hkv, self.d, self.rotary_dim,
+        ip = (ctypes.c_int * 16)(cfg.num_layers, cfg.hidden, self.hq, self.hkv, self.d, self.rotary_dim,
                                  int(cfg.rotary_interleaved), inter_local, cfg.vocab, 2 * w.swiglu_half,
                                  cfg.sliding_window, max_pages_per_seq, self.cos_sin.shape[0], self.tp,
-                                 1 if ops.PREFILL_TC else 0)
+                                 1 if ops.PREFILL_TC else 0, cfg.sink_len)
         fp = (ctypes.c_float * 2)(cfg.rms_eps, self.scale)
         ptr = lambda t: 0 if t is None else t.data_ptr()
         g = [w.embed, w.final_norm, w.lm_head, self.cos_sin, self.x, self.h, self.qkv, self.attn, self.act, self.x_last,
@@ -447,12 +447,12 @@ class DecoderModel:
                 if nd > 0:
                     ops.paged_decode(qkv[:nd], attn[:nd], pool, si.page_table[:nd], si.ctx_len[:nd], self.hq, self.hkv,
                                      self.d, self.scale, self.decode_splits, self.part_o, self.part_ml, cfg.sliding_window,
-                                     kv_scales=kv.scales[li] if kv.scales is not None else None)
+                                     kv_scales=kv.scales[li] if kv.scales is not None else None, sink=cfg.sink_len)
                 if si.num_prefill_seqs > 0:
                     np_ = si.num_prefill_seqs
                     ops.paged_prefill(qkv[nd:], attn[nd:], pool, si.page_table[nd:nd + np_], si.ctx_len[nd:nd + np_],
                                       si.cu_q, si.tile_seq, si.tile_q0, si.num_tiles, self.hq, self.hkv, self.d, self.scale,
-                                      cfg.sliding_window, kv_scales=kv.scales[li] if kv.scales is not None else None)
+                                      cfg.sliding_window, kv_scales=kv.scales[li] if kv.scales is not None else None, sink=cfg.sink_len)
                 lw.quant["o"].fused(attn, x, residual=x)
                 gu = self.gate_up[:t, : 2 * lw.quant["gate"].n]
                 lw.quant["gate_up"].fused(x, gu, norm_weight=lw.ln2, eps=cfg.rms_eps)
@@ -474,17 +474,17 @@ class DecoderModel:
             if nd > 0:
                 ops.paged_decode(qkv[:nd], attn[:nd], pool, si.page_table[:nd], si.ctx_len[:nd], self.hq, self.hkv,
                                  self.d, self.scale, self.decode_splits, self.part_o, self.part_ml, cfg.sliding_window,
-                                 kv_scales=kv.scales[li] if kv.scales is not None else None)
+                                 kv_scales=kv.scales[li] if kv.scales is not None else None, sink=cfg.sink_len)
             if si.num_prefill_seqs > 0 and si.verify_table is not None:
                 nv = si.verify_ctx.numel()
                 ops.paged_decode(qkv[nd:nd + nv], attn[nd:nd + nv], pool, si.verify_table, si.verify_ctx, self.hq, self.hkv,
                                  self.d, self.scale, si.verify_splits, self.part_o, self.part_ml, cfg.sliding_window,
-                                 kv_scales=kv.scales[li] if kv.scales is not None else None)
+                                 kv_scales=kv.scales[li] if kv.scales is not None else None, sink=cfg.sink_len)
             elif si.num_prefill_seqs > 0:
                 np_ = si.num_prefill_seqs
                 ops.paged_prefill(qkv[nd:], attn[nd:], pool, si.page_table[nd:nd + np_], si.ctx_len[nd:nd + np_],
                                   si.cu_q, si.tile_seq, si.tile_q0, si.num_tiles, self.hq, self.hkv, self.d, self.scale,
-                                  cfg.sliding_window, kv_scales=kv.scales[li] if kv.scales is not None else None)
+                                  cfg.sliding_window, kv_scales=kv.scales[li] if kv.scales is not None else None, sink=cfg.sink_len)
             if lw.quant:
                 pending = lw.quant["o"](attn, out=self.partial[:t])
                 self._norm(x, lw.ln2, pending, h)
@@ -531,17 +531,17 @@ class DecoderModel:
         if nd > 0:
             ops.paged_decode(qkv[:nd], attn[:nd], pool, si.page_table[:nd], si.ctx_len[:nd], self.hq, self.hkv,
                              self.d, self.scale, self.decode_splits, self.part_o, self.part_ml, cfg.sliding_window,
-                             kv_scales=scales)
+                             kv_scales=scales, sink=cfg.sink_len)
         if si.num_prefill_seqs > 0 and si.verify_table is not None:
             nv = si.verify_ctx.numel()
             ops.paged_decode(qkv[nd:nd + nv], attn[nd:nd + nv], pool, si.verify_table, si.verify_ctx, self.hq, self.hkv,
                              self.d, self.scale, si.verify_splits, self.part_o, self.part_ml, cfg.sliding_window,
-                             kv_scales=scales)
+                             kv_scales=scales, sink=cfg.sink_len)
         elif si.num_prefill_seqs > 0:
             np_ = si.num_prefill_seqs
             ops.paged_prefill(qkv[nd:], attn[nd:], pool, si.page_table[nd:nd + np_], si.ctx_len[nd:nd + np_],
                               si.cu_q, si.tile_seq, si.tile_q0, si.num_tiles, self.hq, self.hkv, self.d, self.scale,
-                              cfg.sliding_window, kv_scales=scales)
+                              cfg.sliding_window, kv_scales=scales, sink=cfg.sink_len)
 
     def _forward_tp_fused(self, si: StepInputs, kv: "KVCache") -> torch.Tensor:
         """The step under fused tensor parallelism, driven op by op (the C++ executor runs the same sequence).

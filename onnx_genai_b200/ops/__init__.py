@@ -348,21 +348,22 @@ def prefill_tiles(q_lens, block_m=64):
 
 @_timed("paged_prefill")
 def paged_prefill(q, out, pool, page_table, ctx_len, cu_q, tile_seq, tile_q0, num_tiles, hq, hkv, d, scale=None,
-                  window=0, kv_scales=None):
+                  window=0, kv_scales=None, sink=0):
     """Causal varlen GQA over paged KV for chunks of new tokens.  q: packed qkv rows (first hq*d cols).
     ``kv_scales`` selects the e4m3 page kernels."""
     scale = scale or 1.0 / math.sqrt(d)
     if not q.is_cuda:
         if kv_scales is None and _cpu_native(q) and pool.dtype == torch.float32 and pool.is_contiguous():
-            out.copy_(cpu.paged_attention(q, pool, page_table, ctx_len, cu_q, hq, hkv, d, scale, window))
+            out.copy_(cpu.paged_attention(q, pool, page_table, ctx_len, cu_q, hq, hkv, d, scale, window, sink))
             return out
-        out.copy_(reference.paged_attention(q, pool, page_table, ctx_len, cu_q, hq, hkv, d, scale, window, kv_scales))
+        out.copy_(reference.paged_attention(q, pool, page_table, ctx_len, cu_q, hq, hkv, d, scale, window, kv_scales, sink))
         return out
     if kv_scales is not None:
         rc = _native.load().ogb_paged_prefill_q8(
             q.data_ptr(), out.data_ptr(), pool.data_ptr(), kv_scales.data_ptr(), kv_format(pool), page_table.data_ptr(), ctx_len.data_ptr(),
             cu_q.data_ptr(), tile_seq.data_ptr(), tile_q0.data_ptr(), int(num_tiles), ctx_len.numel(), page_table.shape[1],
-            backed_pages(pool), hq, hkv, d, q.stride(0), out.stride(0), float(scale), status_word().data_ptr(), _stream())
+            backed_pages(pool), hq, hkv, d, q.stride(0), out.stride(0), float(scale), int(window), int(sink), status_word().data_ptr(),
+            _stream())
         _native.check(rc, "ogb_paged_prefill_q8")
         launch_counts["paged_prefill_fp8"] += 1
         return out
@@ -371,7 +372,7 @@ def paged_prefill(q, out, pool, page_table, ctx_len, cu_q, tile_seq, tile_q0, nu
         rc = _native.load().ogb_paged_prefill_tc_bf16(
             q.data_ptr(), out.data_ptr(), pool.data_ptr(), page_table.data_ptr(), ctx_len.data_ptr(), cu_q.data_ptr(),
             tile_seq.data_ptr(), tile_q0.data_ptr(), int(num_tiles), ctx_len.numel(), q.shape[0], page_table.shape[1],
-            backed_pages(pool), hq, hkv, d, q.stride(0), out.stride(0), float(scale), int(window),
+            backed_pages(pool), hq, hkv, d, q.stride(0), out.stride(0), float(scale), int(window), int(sink),
             status_word().data_ptr(), _stream())
         _native.check(rc, "ogb_paged_prefill_tc_bf16")
         launch_counts["paged_prefill_tc"] += 1
@@ -380,7 +381,7 @@ def paged_prefill(q, out, pool, page_table, ctx_len, cu_q, tile_seq, tile_q0, nu
     rc = _native.load().ogb_paged_prefill_bf16(
         q.data_ptr(), out.data_ptr(), pool.data_ptr(), page_table.data_ptr(), ctx_len.data_ptr(), cu_q.data_ptr(),
         tile_seq.data_ptr(), tile_q0.data_ptr(), int(num_tiles), ctx_len.numel(), page_table.shape[1], backed_pages(pool),
-        hq, hkv, d, q.stride(0), out.stride(0), float(scale), int(window), status_word().data_ptr(), _stream())
+        hq, hkv, d, q.stride(0), out.stride(0), float(scale), int(window), int(sink), status_word().data_ptr(), _stream())
     _native.check(rc, "ogb_paged_prefill_bf16")
     launch_counts["paged_prefill"] += 1
     return out
@@ -388,7 +389,7 @@ def paged_prefill(q, out, pool, page_table, ctx_len, cu_q, tile_seq, tile_q0, nu
 
 @_timed("paged_decode")
 def paged_decode(q, out, pool, page_table, ctx_len, hq, hkv, d, scale=None, num_splits=1, part_o=None, part_ml=None,
-                 window=0, kv_scales=None):
+                 window=0, kv_scales=None, sink=0):
     """One query token per sequence (row s of q) over paged KV; ctx_len[s] <= 0 marks an idle row.
     ``kv_scales`` selects the e4m3 page kernels."""
     scale = scale or 1.0 / math.sqrt(d)
@@ -396,9 +397,9 @@ def paged_decode(q, out, pool, page_table, ctx_len, hq, hkv, d, scale=None, num_
     if not q.is_cuda:
         cu = torch.arange(n + 1, dtype=torch.int32)
         if kv_scales is None and _cpu_native(q) and pool.dtype == torch.float32 and pool.is_contiguous():
-            out[:n].copy_(cpu.paged_attention(q[:n], pool, page_table, ctx_len, cu, hq, hkv, d, scale, window))
+            out[:n].copy_(cpu.paged_attention(q[:n], pool, page_table, ctx_len, cu, hq, hkv, d, scale, window, sink))
             return out
-        out[:n].copy_(reference.paged_attention(q[:n], pool, page_table, ctx_len, cu, hq, hkv, d, scale, window, kv_scales))
+        out[:n].copy_(reference.paged_attention(q[:n], pool, page_table, ctx_len, cu, hq, hkv, d, scale, window, kv_scales, sink))
         return out
     if num_splits > 1 and part_o is None:
         part_o = torch.empty(n * hq * num_splits * d, dtype=torch.float32, device=q.device)
@@ -407,14 +408,14 @@ def paged_decode(q, out, pool, page_table, ctx_len, hq, hkv, d, scale=None, num_
         rc = _native.load().ogb_paged_decode_q8(
             q.data_ptr(), out.data_ptr(), pool.data_ptr(), kv_scales.data_ptr(), kv_format(pool), page_table.data_ptr(), ctx_len.data_ptr(), n,
             page_table.shape[1], backed_pages(pool), hq, hkv, d, q.stride(0), out.stride(0), float(scale), int(num_splits),
-            _ptr(part_o), _ptr(part_ml), status_word().data_ptr(), _stream())
+            _ptr(part_o), _ptr(part_ml), int(window), int(sink), status_word().data_ptr(), _stream())
         _native.check(rc, "ogb_paged_decode_q8")
         launch_counts["paged_decode_fp8"] += 1
         return out
     rc = _native.load().ogb_paged_decode_bf16(
         q.data_ptr(), out.data_ptr(), pool.data_ptr(), page_table.data_ptr(), ctx_len.data_ptr(), n,
         page_table.shape[1], backed_pages(pool), hq, hkv, d, q.stride(0), out.stride(0), float(scale), int(num_splits),
-        _ptr(part_o), _ptr(part_ml), int(window), status_word().data_ptr(), _stream())
+        _ptr(part_o), _ptr(part_ml), int(window), int(sink), status_word().data_ptr(), _stream())
     _native.check(rc, "ogb_paged_decode_bf16")
     launch_counts["paged_decode"] += 1
     return out

@@ -31,14 +31,14 @@ _SIGNATURES = {
     "ogb_silu_mul_bf16": ([P, P, I, I, P], I),
     "ogb_rope_kv_append_bf16": ([P, P, P, P, P, I, I, I, I, I, I, I, L, I, P, P], I),
     "ogb_rope_kv_append_fp8": ([P, P, P, P, P, P, I, I, I, I, I, I, I, L, I, P, P], I),
-    "ogb_paged_prefill_bf16": ([P, P, P, P, P, P, P, P, I, I, I, L, I, I, I, I, I, F, I, P, P], I),
-    "ogb_paged_prefill_tc_bf16": ([P, P, P, P, P, P, P, P, I, I, I, I, L, I, I, I, I, I, F, I, P, P], I),
-    "ogb_paged_decode_bf16": ([P, P, P, P, P, I, I, L, I, I, I, I, I, F, I, P, P, I, P, P], I),
+    "ogb_paged_prefill_bf16": ([P, P, P, P, P, P, P, P, I, I, I, L, I, I, I, I, I, F, I, I, P, P], I),
+    "ogb_paged_prefill_tc_bf16": ([P, P, P, P, P, P, P, P, I, I, I, I, L, I, I, I, I, I, F, I, I, P, P], I),
+    "ogb_paged_decode_bf16": ([P, P, P, P, P, I, I, L, I, I, I, I, I, F, I, P, P, I, I, P, P], I),
     "ogb_paged_decode_fp8": ([P, P, P, P, P, P, I, I, L, I, I, I, I, I, F, I, P, P, P, P], I),
     "ogb_paged_prefill_fp8": ([P, P, P, P, P, P, P, P, P, I, I, I, L, I, I, I, I, I, F, P, P], I),
     "ogb_rope_kv_append_q8": ([P, P, P, P, P, P, I, I, I, I, I, I, I, I, L, I, P, P], I),
-    "ogb_paged_decode_q8": ([P, P, P, P, I, P, P, I, I, L, I, I, I, I, I, F, I, P, P, P, P], I),
-    "ogb_paged_prefill_q8": ([P, P, P, P, I, P, P, P, P, P, I, I, I, L, I, I, I, I, I, F, P, P], I),
+    "ogb_paged_decode_q8": ([P, P, P, P, I, P, P, I, I, L, I, I, I, I, I, F, I, P, P, I, I, P, P], I),
+    "ogb_paged_prefill_q8": ([P, P, P, P, I, P, P, P, P, P, I, I, I, L, I, I, I, I, I, F, I, I, P, P], I),
     "ogb_argmax_bf16": ([P, P, I, I, I, P], I),
     "ogb_sample_bf16": ([P, P, P, P, P, P, P, P, I, I, I, P], I),
     "ogb_spec_verify_greedy": ([P, P, P, P, I, I, I, I, P], I),

@@ -36,7 +36,7 @@ def _lib():
             "ogb_cpu_rmsnorm": [P, P, P, P, I, I, F],
             "ogb_cpu_silu_mul": [P, L, P, I, I],
             "ogb_cpu_rope_kv_append": [P, P, P, P, I, P, L, I, I, I, I, I, I],
-            "ogb_cpu_paged_attention": [P, L, P, P, P, I, P, P, I, I, I, I, F, I],
+            "ogb_cpu_paged_attention": [P, L, P, P, P, I, P, P, I, I, I, I, F, I, I],
             "ogb_cpu_argmax": [P, L, P, I, I],
             "ogb_cpu_sample": [P, L, P, P, P, P, P, P, I, I],
             "ogb_cpu_dequant_nbits": [P, P, P, P, I, I],
@@ -149,7 +149,7 @@ def rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim=
     return qkv
 
 
-def paged_attention(q, pool, page_table, ctx_len, cu_q, hq, hkv, d, scale=None, window=0):
+def paged_attention(q, pool, page_table, ctx_len, cu_q, hq, hkv, d, scale=None, window=0, sink=0):
     lib = _lib()
     q = _rows(q)
     assert pool.dtype == torch.float32 and pool.is_contiguous()
@@ -162,7 +162,7 @@ def paged_attention(q, pool, page_table, ctx_len, cu_q, hq, hkv, d, scale=None, 
     cu = cu_q.to(torch.int32).contiguous()
     n = ctx.numel()
     lib.ogb_cpu_paged_attention(q.data_ptr(), q.stride(0), out.data_ptr(), pool.data_ptr(), table.data_ptr(), table.stride(0),
-                                ctx.data_ptr(), cu.data_ptr(), n, hq, hkv, d, float(scale or d ** -0.5), int(window))
+                                ctx.data_ptr(), cu.data_ptr(), n, hq, hkv, d, float(scale or d ** -0.5), int(window), int(sink))
     _count("paged_attention")
     return out
 

@@ -141,19 +141,29 @@ def rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim=
     return qkv
 
 
+def _live_pages(table, n_pages):
+    """Page ids of a sequence; entries of released pages (-1: between the attention sinks and the sliding window, never
+    visible to a query) are replaced by a live page so that the gather stays in range -- their keys are masked."""
+    idx = table[:n_pages].long()
+    if bool((idx < 0).any()):
+        idx = torch.where(idx < 0, idx[idx >= 0][-1], idx)
+    return idx
+
+
 def _gather_kv(pool, table, ctx):
     n_pages = (ctx + PAGE - 1) // PAGE
-    pages = pool[table[:n_pages].long()]  # [n, hkv, 2, PAGE, d]
+    pages = pool[_live_pages(table, n_pages)]  # [n, hkv, 2, PAGE, d]
     k = pages[:, :, 0].permute(1, 0, 2, 3).reshape(pool.shape[1], -1, pool.shape[-1])[:, :ctx]
     v = pages[:, :, 1].permute(1, 0, 2, 3).reshape(pool.shape[1], -1, pool.shape[-1])[:, :ctx]
     return k.float(), v.float()
 
 
-def paged_attention(q, pool, page_table, ctx_len, cu_q, hq, hkv, d, scale=None, window=0, kv_scales=None):
+def paged_attention(q, pool, page_table, ctx_len, cu_q, hq, hkv, d, scale=None, window=0, kv_scales=None, sink=0):
     """Varlen causal GQA over paged KV.  q [T, >=hq*d] (first hq*d columns used); returns [T, hq*d].
 
     Sequence s owns query rows cu_q[s]:cu_q[s+1]; its last row sits at position ctx_len[s]-1.
-    ``kv_scales`` [P,hkv,2] dequantises fp8 pages.
+    ``kv_scales`` [P,hkv,2] dequantises fp8 pages.  ``window`` > 0 keeps the last ``window`` keys of each query and,
+    with ``sink`` > 0, the first ``sink`` keys of the sequence as well (attention sinks).
     """
     scale = scale or 1.0 / math.sqrt(d)
     t = q.shape[0]
@@ -166,7 +176,7 @@ def paged_attention(q, pool, page_table, ctx_len, cu_q, hq, hkv, d, scale=None, 
             continue
         if kv_scales is not None:
             n_pages = (ctx + PAGE - 1) // PAGE
-            idx = page_table[s][:n_pages].long()
+            idx = _live_pages(page_table[s], n_pages)
             raw = pool[idx]
             if raw.dtype == torch.uint8:   # e4m3 bytes
                 raw = raw.view(torch.float8_e4m3fn)
@@ -181,7 +191,7 @@ def paged_attention(q, pool, page_table, ctx_len, cu_q, hq, hkv, d, scale=None, 
         kpos = torch.arange(ctx, device=q.device)[None, :]
         mask = kpos <= qpos
         if window > 0:
-            mask &= kpos > qpos - window
+            mask &= (kpos > qpos - window) | (kpos < sink)
         scores = scores.masked_fill(~mask[:, None, None, :], float("-inf"))
         p = torch.softmax(scores, dim=-1)
         o = torch.einsum("thgk,hkd->thgd", p, v)

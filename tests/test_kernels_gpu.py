@@ -625,3 +625,65 @@ def test_vmm_growable_buffer_keeps_its_address_and_contents():
     del a
     buf.close()
     assert torch.cuda.mem_get_info()[0] >= free_before - (1 << 20)
+
+
+def _punch_holes(table, ctx, q_lens, window, sink):
+    """What the scheduler does under a sliding window: entries of pages wholly between the sinks and the window of the
+    sequence's first query row become -1."""
+    table = table.clone()
+    for s, (c, ql) in enumerate(zip(ctx, q_lens)):
+        lo, hi = (sink + 15) // 16, max(0, c - ql - window + 1) // 16
+        if hi > lo:
+            table[s, lo:hi] = -1
+    return table
+
+
+@pytest.mark.parametrize("window,sink", [(100, 0), (100, 16), (300, 32), (64, 48)])
+@pytest.mark.parametrize("pages", ["bf16", "fp8", "int8"])
+def test_sliding_window_with_attention_sinks(pages, window, sink):
+    """Decode (with and without KV splits) and chunked prefill under window + sinks, with the invisible pages taken out of
+    the page table, against the fp32 reference on the same pages."""
+    torch.manual_seed(21)
+    hq, hkv, d = 28, 4, 128
+    ctx = [1, 17, 90, 129, 257, 700, 1500]
+    n = len(ctx)
+    if pages == "bf16":
+        pool, table = _make_paged(n, ctx, hkv, d)
+        scales = None
+    else:
+        pool, scales, table = _make_paged_fp8(ctx, hkv, d, seed=5, fmt=pages)
+    ctx_t = torch.tensor(ctx, dtype=torch.int32, device=DEV)
+    q = torch.randn(n, (hq + 2 * hkv) * d, device=DEV).bfloat16()
+    cu = torch.arange(n + 1, dtype=torch.int32, device=DEV)
+    holes = _punch_holes(table, ctx, [1] * n, window, sink)
+    assert bool((holes < 0).any())
+    want = ref.paged_attention(q, pool, table, ctx_t, cu, hq, hkv, d, window=window, kv_scales=scales, sink=sink)
+    full = ref.paged_attention(q, pool, table, ctx_t, cu, hq, hkv, d, kv_scales=scales)
+    assert _rel_err(want, full) > 0.05                      # the mask matters on this data
+    modes = (2, 1, 0) if pages == "fp8" else (None,)
+    old = ops.set_e4m3_mma(2)
+    try:
+        for mode in modes:
+            if mode is not None:
+                ops.set_e4m3_mma(mode)
+            for splits in (1, 4):
+                out = torch.full((n, hq * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+                ops.paged_decode(q, out, pool, holes, ctx_t, hq, hkv, d, num_splits=splits, window=window, kv_scales=scales, sink=sink)
+                torch.cuda.synchronize()
+                ops.check_status()
+                assert torch.isfinite(out.float()).all() and _rel_err(out, want) < 2e-2, (mode, splits, _rel_err(out, want))
+    finally:
+        ops.set_e4m3_mma(old)
+    q_lens = [1, 7, 40, 64, 65, 130, 200]
+    t = sum(q_lens)
+    qp = torch.randn(t, (hq + 2 * hkv) * d, device=DEV).bfloat16()
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    ts, tq = ops.prefill_tiles(q_lens)
+    holes = _punch_holes(table, ctx, q_lens, window, sink)
+    wantp = ref.paged_attention(qp, pool, table, ctx_t, cu, hq, hkv, d, window=window, kv_scales=scales, sink=sink)
+    outp = torch.full((t, hq * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops.paged_prefill(qp, outp, pool, holes, ctx_t, cu, torch.tensor(ts, dtype=torch.int32, device=DEV),
+                      torch.tensor(tq, dtype=torch.int32, device=DEV), len(ts), hq, hkv, d, window=window, kv_scales=scales, sink=sink)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.isfinite(outp.float()).all() and _rel_err(outp, wantp) < 2e-2, _rel_err(outp, wantp)

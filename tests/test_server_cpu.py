@@ -75,6 +75,8 @@ def test_sessions_and_errors(client):
     assert client.post("/v1/completions", content=b"not json").status_code == 400
     assert client.post("/v1/embeddings", json={"input": "x"}).status_code == 200
     bad = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": [{"type": "image_url"}]}]})
+    assert bad.status_code == 400 and "image_url needs a url" in bad.json()["detail"]
+    bad = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": [{"type": "video", "video": "x"}]}]})
     assert bad.status_code == 400 and "not supported" in bad.json()["detail"]
 
 
