@@ -12,6 +12,8 @@
 //   * w4a16_dequant_kernel -- expands W to bf16 [N, K] so larger M runs on the tcgen05 GEMM.
 #include <cuda_fp16.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "ogb_kernels.h"
 
@@ -183,7 +185,7 @@ __global__ void w4a16_dequant_kernel(const uint8_t* __restrict__ qw, const void*
 // The kernel is specialised on the row count MT in {1,2,4,8} so the M=1 code stays small: with one
 // generic 8-row body the unrolled kernel was dominated by instruction fetch (22-35 us per launch for
 // matrices that stream in 1-2 us).  Activations are staged once per CTA in shared memory as bf16 -- after
-// the prologue, rounded exactly as the unfused path rounds them -- in chunks of kGemvChunk values of K.
+// the prologue, rounded exactly as the unfused path rounds them -- in chunks of as many values of K as 64 KB hold for the row count (all of K for decode shapes).
 // Each warp owns kFusedCols output columns; lanes stride over the 32-weight blocks of a chunk.
 //
 // Arithmetic: two weights per instruction.  A 32-bit word holds nibbles n0..n7; `(w & 0x000F000F) | 0x64006400` read as
@@ -197,7 +199,6 @@ __global__ void w4a16_dequant_kernel(const uint8_t* __restrict__ qw, const void*
 // ------------------------------------------------------------------------------------------
 constexpr int kFusedCols = 2;
 constexpr int kFusedWarps = 8;
-constexpr int kGemvChunk = 4096;   // K values staged per pass (8 rows x 4096 x 2 B = 64 KB of shared memory)
 
 enum : int { kProNone = 0, kProRmsNorm = 1, kProSiluMul = 2 };
 
@@ -241,10 +242,14 @@ struct BlockW {
 constexpr int kSplitCols = 4;
 
 template <int MT, int PRO, bool SCALES_F32, bool SPLITK>
-__global__ void __launch_bounds__(kFusedWarps * 32) w4a16_gemv_fused_kernel(const GemvFusedParams p) {
+__global__ void __launch_bounds__(kFusedWarps * 32) w4a16_gemv_fused_kernel(const GemvFusedParams p, const int chunk,
+                                                                            const int num_tiles) {
+  // Persistent over column tiles: a CTA stages the activations once (when all of K fits its shared memory, which is the
+  // decode case) and then walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...; the norm statistics, the prologue and the
+  // fp16 staging are paid once per CTA instead of once per 16 columns.
   constexpr int C = SPLITK ? kSplitCols : kFusedCols;
   extern __shared__ __align__(16) uint8_t gemv_smem[];
-  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(gemv_smem);   // [MT][kGemvChunk]
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(gemv_smem);   // [MT][chunk] fp16 bits in pair order
   __shared__ float rstd_sh[MT];
   __shared__ float red_sh[kFusedWarps][MT];
   __shared__ float part_sh[SPLITK ? kFusedWarps : 1][C][MT];
@@ -252,16 +257,18 @@ __global__ void __launch_bounds__(kFusedWarps * 32) w4a16_gemv_fused_kernel(cons
   const int K = p.K, N = p.N, M = p.M;
   const int kb = (K + 31) / 32;
   const int zp_stride = (kb + 1) / 2;
-  const int n0 = SPLITK ? blockIdx.x * C : (blockIdx.x * kFusedWarps + warp) * C;
-  // block index of this lane inside a chunk of kGemvChunk/32 = 128 blocks, and the stride to its next one
+  const bool one_chunk = K <= chunk;
+  // block index of this lane inside a chunk, and the stride to its next one
   const int j0 = SPLITK ? warp * 32 + lane : lane;
   constexpr int jstep = SPLITK ? kFusedWarps * 32 : 32;
+  auto tile_n0 = [&](int tile) { return SPLITK ? tile * C : (tile * kFusedWarps + warp) * C; };
 
   // The first block's weights do not depend on the activations: request them before the prologue so the
   // DRAM round trip overlaps the norm / staging chain.
   BlockW<C, SCALES_F32> w0;
-  const bool have_w0 = (n0 < N) && (j0 < min(kb, kGemvChunk / 32));
-  if (have_w0) w0.load(p, n0, j0, kb, zp_stride);
+  const int first_tile = blockIdx.x;
+  const bool have_w0 = first_tile < num_tiles && (tile_n0(first_tile) < N) && (j0 < min(kb, chunk / 32));
+  if (have_w0) w0.load(p, tile_n0(first_tile), j0, kb, zp_stride);
 
   if constexpr (PRO == kProRmsNorm) {
     float ss[MT];
@@ -294,16 +301,20 @@ __global__ void __launch_bounds__(kFusedWarps * 32) w4a16_gemv_fused_kernel(cons
     __syncthreads();
   }
 
+  for (int tile = first_tile; tile < num_tiles; tile += gridDim.x) {
+  const int n0 = tile_n0(tile);
   float acc[C][MT];
 #pragma unroll
   for (int c = 0; c < C; ++c)
 #pragma unroll
     for (int m = 0; m < MT; ++m) acc[c][m] = 0.f;
 
-  for (int k0 = 0; k0 < K; k0 += kGemvChunk) {
-    const int klen = min(kGemvChunk, K - k0);
+  for (int k0 = 0; k0 < K; k0 += chunk) {
+    const int klen = min(chunk, K - k0);
     const int klen_pad = (klen + 31) / 32 * 32;
-    if (k0 > 0) __syncthreads();                 // every warp is done with the previous chunk
+    const bool stage = !one_chunk || tile == first_tile;   // with one chunk the activations stay staged across tiles
+    if (stage) {
+    if (k0 > 0 || tile != first_tile) __syncthreads();     // every warp is done with what the buffer held
     // stage prologue(x) for this chunk, 8 values per thread per step (K, ldx multiples of 8)
     for (int i = threadIdx.x * 8; i < klen_pad; i += blockDim.x * 8) {
 #pragma unroll
@@ -346,17 +357,21 @@ __global__ void __launch_bounds__(kFusedWarps * 32) w4a16_gemv_fused_kernel(cons
           }
           uint4 h;
           h.x = pack_f16(v[0], v[4]); h.y = pack_f16(v[1], v[5]); h.z = pack_f16(v[2], v[6]); h.w = pack_f16(v[3], v[7]);
-          *reinterpret_cast<uint4*>(xs + m * kGemvChunk + i) = h;
+          *reinterpret_cast<uint4*>(xs + m * chunk + i) = h;
         }
       }
     }
     __syncthreads();
+    }
     if (n0 < N) {
       const int b0 = k0 / 32, nb = klen_pad / 32;
+      BlockW<C, SCALES_F32> w, wn;
+      if (j0 < nb) {
+        if (k0 == 0 && tile == first_tile && have_w0) w = w0;
+        else w.load(p, n0, b0 + j0, kb, zp_stride);
+      }
       for (int j = j0; j < nb; j += jstep) {
-        BlockW<C, SCALES_F32> w;
-        if (k0 == 0 && j == j0 && have_w0) w = w0;
-        else w.load(p, n0, b0 + j, kb, zp_stride);
+        if (j + jstep < nb) wn.load(p, n0, b0 + j + jstep, kb, zp_stride);   // the next block is in flight while this one is used
         __half2 dot[C][MT][2];
 #pragma unroll
         for (int c = 0; c < C; ++c)
@@ -383,7 +398,7 @@ __global__ void __launch_bounds__(kFusedWarps * 32) w4a16_gemv_fused_kernel(cons
           }
 #pragma unroll
           for (int m = 0; m < MT; ++m) {
-            const uint4 q = *reinterpret_cast<const uint4*>(xb + m * kGemvChunk + 8 * wi);
+            const uint4 q = *reinterpret_cast<const uint4*>(xb + m * chunk + 8 * wi);
             const __half2 xv[4] = {as_half2(q.x), as_half2(q.y), as_half2(q.z), as_half2(q.w)};
 #pragma unroll
             for (int c = 0; c < C; ++c)
@@ -398,6 +413,7 @@ __global__ void __launch_bounds__(kFusedWarps * 32) w4a16_gemv_fused_kernel(cons
             const float2 d0 = __half22float2(dot[c][m][0]), d1 = __half22float2(dot[c][m][1]);
             acc[c][m] += w.sc[c] * ((d0.x + d0.y) + (d1.x + d1.y));
           }
+        w = wn;
       }
     }
   }
@@ -421,8 +437,9 @@ __global__ void __launch_bounds__(kFusedWarps * 32) w4a16_gemv_fused_kernel(cons
         p.y[static_cast<size_t>(m) * p.ldy + n] = __float2bfloat16(v);
       }
     }
+    __syncthreads();                                       // part_sh is rewritten by the next tile
   } else {
-    if (n0 >= N) return;
+    if (n0 < N) {
 #pragma unroll
     for (int c = 0; c < C; ++c) {
 #pragma unroll
@@ -436,17 +453,31 @@ __global__ void __launch_bounds__(kFusedWarps * 32) w4a16_gemv_fused_kernel(cons
         }
       }
     }
+    }
+  }
   }
 }
 
 template <int MT, int PRO, bool SF32, bool SPLITK>
 static int launch_gemv_fused_one(const GemvFusedParams& p, cudaStream_t st) {
   const int per_cta = SPLITK ? kSplitCols : kFusedWarps * kFusedCols;
-  const int blocks = (p.N + per_cta - 1) / per_cta;
-  const size_t smem = static_cast<size_t>(MT) * kGemvChunk * sizeof(__nv_bfloat16);
+  const int tiles = (p.N + per_cta - 1) / per_cta;
+  // as much of K as 64 KB of shared memory hold for MT rows (a multiple of 32 values): all of it for decode shapes
+  const int k_pad = (p.K + 31) / 32 * 32;
+  const int chunk = std::min(k_pad, (64 * 1024 / (MT * 2)) / 32 * 32);
+  const size_t smem = static_cast<size_t>(MT) * chunk * sizeof(__nv_bfloat16);
   auto kern = w4a16_gemv_fused_kernel<MT, PRO, SF32, SPLITK>;
-  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-  kern<<<blocks, kFusedWarps * 32, smem, st>>>(p);
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    attr_set = true;
+  }
+  int ctas_per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, kern, kFusedWarps * 32, smem) != cudaSuccess || ctas_per_sm < 1)
+    ctas_per_sm = 1;
+  // persistent only when the activations stay staged (one chunk); otherwise one tile per CTA as before
+  const int blocks = (p.K <= chunk) ? std::min(tiles, ogb_num_sms() * ctas_per_sm) : tiles;
+  kern<<<blocks, kFusedWarps * 32, smem, st>>>(p, chunk, tiles);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -474,6 +474,17 @@ def cmd_validate(args, profiler):
                         problems.append(f"layer {li} {name}: scales have {one.scales.numel()} entries, expected {one.q.shape[0] * kb}")
     except Exception as exc:
         problems.append(f"graph: {exc}")
+    try:   # static shapes: what resolves without running the graph, and what the graph's declared outputs disagree with
+        from .package import shape_inference as si
+
+        rep = si.infer(load_any(d.model_path), policy="strict")
+        notes.append(f"shape inference: {len(rep.types) - len(rep.unresolved)} of {len(rep.types)} values resolved"
+                     + (f", {rep.fresh_symbols} data-dependent extents" if rep.fresh_symbols else "")
+                     + (f"; no rule for {sorted(rep.unregistered)}" if rep.unregistered else ""))
+    except si.ShapeInferenceError as exc:
+        problems.append(f"shape inference: {exc}")
+    except Exception as exc:
+        notes.append(f"shape inference skipped: {exc}")
     if meta is not None and cfg is not None:
         if meta.vocab_size and meta.vocab_size != cfg.vocab:
             problems.append(f"metadata model.vocab_size={meta.vocab_size} but the embedding has {cfg.vocab} rows")

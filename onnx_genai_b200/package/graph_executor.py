@@ -947,7 +947,7 @@ class GraphExecutor:
         self.output_names = [vi.name for vi in g.outputs]
         self.input_types = {vi.name: vi.elem_type for vi in g.inputs}
         unknown = sorted({(n.domain + "::" if n.domain else "") + n.op_type for n in _all_nodes(g) if n.op_type not in OPS
-                          and n.op_type not in _STRUCTURAL})
+                          and f"{n.domain}::{n.op_type}" not in OPS and n.op_type not in _STRUCTURAL})
         if unknown:
             raise GraphExecutionError(f"graph '{g.name}' uses operators outside the covered set: {', '.join(unknown)} "
                                       f"({len(OPS) + len(_STRUCTURAL)} operators are covered, If, Loop and Scan among them)")
