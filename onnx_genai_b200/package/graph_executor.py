@@ -931,11 +931,18 @@ def _free_values(graph) -> set:
 
 
 class GraphExecutor:
-    def __init__(self, model, device="cpu", dtype=None):
+    def __init__(self, model, device="cpu", dtype=None, optimize=False):
         """``model``: a path to an ``.onnx`` file or a parsed :class:`onnx_pb.Model`.  Initializers move to ``device``
-        (floating-point ones are cast to ``dtype`` when given)."""
+        (floating-point ones are cast to ``dtype`` when given).  ``optimize``: run the rewrite passes of
+        :mod:`graph_optimizer` on the graph first (constant folding, no-op removal, GELU / LayerNorm / Gemm fusion, dead
+        nodes); the model object is rewritten in place and ``self.optimization`` holds the report."""
         self.model = onnx_pb.load_model(model) if isinstance(model, str) else model
         self.device = torch.device(device)
+        self.optimization = None
+        if optimize:
+            from .graph_optimizer import optimize as _optimize
+
+            self.optimization = _optimize(self.model)
         g = self.model.graph
         self.constants = {}
         for name, t in g.initializers.items():
