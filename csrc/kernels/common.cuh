@@ -185,6 +185,36 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n) {
 }
 
 // ----------------------------------------------------------------------------------------
+// programmatic dependent launch
+// ----------------------------------------------------------------------------------------
+// A kernel that calls this lets the next kernel of its stream -- when that one is launched with the programmatic
+// stream serialization attribute -- start as soon as every CTA of this grid has called it or exited, instead of after
+// the grid has drained.  The follower must then find its inputs through its own flags (acquire loads); used between
+// the scatter GEMM, the exchange kernel and the GEMM that consumes the exchanged rows, which are chained by per-tile
+// counters anyway.  Every CTA of the leader is resident (or done) when the follower starts, so a follower that waits
+// on the leader's flags cannot starve it.
+OGB_DEVICE void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Process-wide switch for those launches (OGB_TP_PDL=1 or ogb_tp_set_pdl(1); off by default).
+int tp_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl,
+                                     Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = pdl ? attr : nullptr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// ----------------------------------------------------------------------------------------
 // small numeric helpers
 // ----------------------------------------------------------------------------------------
 OGB_DEVICE float warp_sum(float v) {

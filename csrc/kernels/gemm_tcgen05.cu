@@ -145,6 +145,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                          float* sk_ws, uint32_t* sk_flags, uint32_t sk_seq) {
   using Cfg = GemmCfg<BN>;
   const bool stream_k = sk_ws != nullptr;
+  if constexpr (EPI == kEpiScatter) pdl_trigger();   // the exchange kernel may start: it waits on the tile counters this kernel bumps
   // the kernel declares no static shared memory, so the dynamic window starts at the 1024-byte aligned
   // base the 128-byte swizzle needs
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -716,11 +717,14 @@ static int launch_gemm(const void* A, const void* W, void* C, const void* bias, 
       if (sk_seq == 0) sk_seq = ++w->seq;     // the flags start at zero
     }
   }
-  gemm_bf16_tcgen05_kernel<BN, EPI><<<grid, EPI == kEpiScatter ? kGemmThreadsScatter : kGemmThreads, Cfg::kSmemBytes, stream>>>(
-      ta, tb, static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(bias),
-      static_cast<const __nv_bfloat16*>(residual), static_cast<float*>(C_f32), M, N, K, ldc, ldr, status, sc, group_tab, group_mtiles,
-      a_ready, a_done, a_wait_ns, sk_ws, sk_flags, sk_seq);
-  return static_cast<int>(cudaGetLastError());
+  // A GEMM whose A rows arrive behind per-tile counters follows the exchange kernel that fills them: with PDL it starts
+  // while that kernel is still running.
+  const bool pdl = a_ready != nullptr && tp_pdl_enabled() != 0;
+  return static_cast<int>(launch_kernel_pdl(
+      gemm_bf16_tcgen05_kernel<BN, EPI>, dim3(grid), dim3(EPI == kEpiScatter ? kGemmThreadsScatter : kGemmThreads), Cfg::kSmemBytes, stream,
+      pdl, ta, tb, static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(bias), static_cast<const __nv_bfloat16*>(residual),
+      static_cast<float*>(C_f32), M, N, K, ldc, ldr, status, sc, group_tab, group_mtiles, a_ready, a_done,
+      static_cast<unsigned long long>(a_wait_ns), sk_ws, sk_flags, sk_seq));
 }
 
 }  // namespace ogb

@@ -26,6 +26,10 @@ int ogb_gemm_bf16_wait(const void* A, const void* W, void* C, const void* bias, 
 
 // Stream-K decomposition of the GEMMs (on by default; OGB_STREAM_K=0 disables it): 1 / 0 sets it, the old value is returned.
 int ogb_gemm_set_stream_k(int on);
+// Programmatic dependent launch along scatter GEMM -> exchange kernel -> consuming GEMM (off by default; OGB_TP_PDL=1
+// enables it at start-up): the follower starts while the leader is still running and finds its rows through the per-tile
+// counters.  1 / 0 sets it, the old value is returned.
+int ogb_tp_set_pdl(int on);
 
 // out[r,:] = x[r,:] * rsqrt(mean(x^2) + eps) * w ; if delta != NULL first x += delta (written back to x).
 int ogb_rmsnorm_bf16(void* x, const void* delta, const void* weight, void* out, int rows, int hidden, int ldx, int ldo,

@@ -249,6 +249,7 @@ __global__ void __launch_bounds__(kRbThreads) tp_exchange_norm_kernel(const TpRe
   __shared__ int ok_sh;
   const bool stamp = r.dbg != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
   if (stamp) r.dbg[0] = global_timer_ns();
+  pdl_trigger();      // the GEMM that consumes h may start now: it waits per M-tile on the ready counters
   for (int ps = blockIdx.x; ps < passes; ps += gridDim.x) {
     const int local0 = ps * kTpNormRows;                  // first row of the pass, relative to the owned chunk
     const int row_base = r.rank * r.chunk + local0;
@@ -520,9 +521,10 @@ extern "C" int ogb_tp_exchange_norm(const void* rp, const void* norm_w, float ep
   const int vpl = (n / 8 + 31) / 32;                              // 16-byte vectors per lane
 #define OGB_EXCH(NV, TPN, PU)                                                                                          \
   do {                                                                                                             \
-    if (vpl <= 8) tp_exchange_norm_kernel<NV, TPN, 8, PU><<<grid, kRbThreads, 0, st>>>(r, w, eps, rows, status);     \
-    else tp_exchange_norm_kernel<NV, TPN, 16, PU><<<grid, kRbThreads, 0, st>>>(r, w, eps, rows, status);             \
-    return static_cast<int>(cudaGetLastError());                                                                   \
+    /* with PDL the kernel starts while the scatter GEMM is still running and takes row groups as their tiles land */ \
+    const bool pdl = tp_pdl_enabled() != 0;                                                                        \
+    if (vpl <= 8) return static_cast<int>(launch_kernel_pdl(tp_exchange_norm_kernel<NV, TPN, 8, PU>, dim3(grid), dim3(kRbThreads), 0, st, pdl, r, w, eps, rows, status)); \
+    return static_cast<int>(launch_kernel_pdl(tp_exchange_norm_kernel<NV, TPN, 16, PU>, dim3(grid), dim3(kRbThreads), 0, st, pdl, r, w, eps, rows, status)); \
   } while (0)
   if (pushed) {
     // partials already local: the template's TP is the number of slabs; NVLS only selects how h and the counters go out
@@ -552,6 +554,22 @@ extern "C" int ogb_tp_exchange_norm(const void* rp, const void* norm_w, float ep
     default: return -5;
   }
 #undef OGB_EXCH
+}
+
+static int g_tp_pdl = -1;
+int ogb::tp_pdl_enabled() {
+  if (g_tp_pdl < 0) {
+    const char* e = getenv("OGB_TP_PDL");
+    g_tp_pdl = (e != nullptr && e[0] == '1') ? 1 : 0;
+  }
+  return g_tp_pdl;
+}
+// Programmatic dependent launch between the scatter GEMM, the exchange kernel and the consuming GEMM: 1 / 0 sets it, the
+// old value is returned.
+extern "C" int ogb_tp_set_pdl(int on) {
+  const int old = ogb::tp_pdl_enabled();
+  g_tp_pdl = on ? 1 : 0;
+  return old;
 }
 
 extern "C" int ogb_tp_wait_ready(const void* rp, int rows, int* status, void* stream) {

@@ -170,6 +170,12 @@ def set_stream_k(on: bool) -> bool:
     return bool(_native.load().ogb_gemm_set_stream_k(1 if on else 0))
 
 
+def set_tp_pdl(on: bool) -> bool:
+    """Programmatic dependent launch along scatter GEMM -> exchange kernel -> consuming GEMM of the tensor-parallel path (off by
+    default; ``OGB_TP_PDL=1`` enables it at start-up).  Returns the old setting."""
+    return bool(_native.load().ogb_tp_set_pdl(1 if on else 0))
+
+
 def set_e4m3_mma(mode: int) -> int:
     """Pick the decode kernel for e4m3 KV pages (query groups of at most 8 heads): 2 = tcgen05 kernel that feeds the raw
     bytes to the tensor cores (default), 1 = the ``mma.sync`` e4m3 kernel, 0 = the kernel that expands pages to bf16 in

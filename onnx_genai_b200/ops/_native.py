@@ -25,6 +25,7 @@ _SIGNATURES = {
     "ogb_gemm_bf16": ([P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P], I),
     "ogb_gemm_bf16_wait": ([P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P, ctypes.c_uint64, P, P], I),
     "ogb_gemm_set_stream_k": ([I], I),
+    "ogb_tp_set_pdl": ([I], I),
     "ogb_attn_set_e4m3_mma": ([I], I),
     "ogb_rmsnorm_bf16": ([P, P, P, P, I, I, I, I, F, P], I),
     "ogb_embedding_bf16": ([P, P, P, I, I, I, P, P], I),
