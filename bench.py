@@ -353,6 +353,16 @@ def main():
         for name, (t, c) in sorted(agg.items(), key=lambda kv: -kv[1][0]):
             print("  %-44s %8.3f ms %6.1f calls %5.1f%%" % (name, t / n_prof, c / n_prof, 100 * t / tot), file=sys.stderr)
         print("  %-44s %8.3f ms" % ("sum", tot / n_prof), file=sys.stderr)
+        try:      # findings (what / why / how) over the same table, with the cost model's FLOPs and bytes per part
+            from onnx_genai_b200.utils import diagnose as _dg
+            from onnx_genai_b200.utils.cost_model import StepShape
+
+            sh = shapes[0]
+            shape_ = StepShape(decode_rows=int(sh[1]), prefill_tokens=int(sh[0]) - int(sh[1]), mean_context=(args.min_prompt + args.max_prompt) // 2 + args.output_tokens // 2,
+                               prefill_context=(args.min_prompt + args.max_prompt) // 4)
+            print(_dg.diagnose_samples(_dg.samples_from_profile(agg, model, shape_, tp=world, steps=n_prof), steps=n_prof).report(), file=sys.stderr)
+        except Exception as exc:   # the diagnosis is a convenience: never let it break the bench line
+            print(f"diagnosis skipped: {exc}", file=sys.stderr)
 
     if comm is not None:
         dev_ms = comm.max_float(dev_ms)

@@ -809,7 +809,14 @@ def main(argv=None):
                     help="a workflow input: a .npy file, a JSON literal (3, [1,2], 0.5) or ids:1,2,3 for a row of token ids")
     rw.add_argument("--out", default="", help="directory for the outputs (one .npy per output, .png for image outputs)")
     rw.add_argument("--device", default="cpu")
+    dgp = sub.add_parser("diagnose", help="findings (what / why / how) and rooflines from a Chrome-trace JSON")
+    dgp.add_argument("trace", help="trace written by ONNX_GENAI_TRACE, --profile-trace or /v1/debug/trace/perfetto")
+    dgp.add_argument("--category", default=None, help="only events of this category")
+    dgp.add_argument("--peaks", default=None, help="measured-peaks JSON (hbm_gbs, bf16_tflops_sustained)")
     args = ap.parse_args(argv)
+    if args.cmd == "diagnose":
+        from .utils.diagnose import main as diagnose_main
+        return diagnose_main([args.trace] + (["--category", args.category] if args.category else []) + (["--peaks", args.peaks] if args.peaks else []))
     if args.cmd == "run-workflow":
         return cmd_run_workflow(args)
     if args.cmd == "import-comfyui":
