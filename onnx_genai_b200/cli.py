@@ -9,6 +9,7 @@ compact per-turn stats line (TTFT, decode tok/s, finish reason).
 from __future__ import annotations
 
 import argparse
+import copy
 import json
 import os
 import sys
@@ -221,12 +222,135 @@ def cmd_generate(args, profiler):
     return 0
 
 
+class Repl:
+    """State and command handling of the interactive session (``run``).  Slash commands, as in the reference's REPL
+    (crates/onnx-genai-cli/src/lib.rs:1254-1383): /system /raw /stats /profile /reset /model, plus /image and /audio
+    (attachments for the next prompt, answered by the media chat of ``--multimodal-package``), /ep (show or switch the
+    device the engine runs on) and /backend (show or switch between the fused executor and the node-by-node graph
+    backend)."""
+
+    HELP = ("/system TEXT  /raw  /stats  /profile  /reset  /model  /image PATH|clear  /audio PATH|clear  /ep [cpu|cuda]  "
+            "/backend [native|graph]  /quit")
+
+    def __init__(self, args, profiler, loader=None, media_chat=None, out=None):
+        self.args, self.profiler = args, profiler
+        self.loader = loader or _load
+        self.out = out or (lambda text: print(text))
+        self.eng = self.loader(args)
+        self.session = self.eng.create_session()
+        self.system, self.raw, self.stats = None, getattr(args, "raw", False), True
+        self.media_chat = media_chat
+        self.images, self.audio = [], None
+        self.done = False
+
+    def _reload(self):
+        self.eng = self.loader(self.args)
+        self.session = self.eng.create_session()
+
+    def command(self, line: str) -> None:
+        cmd, _, rest = line.partition(" ")
+        rest = rest.strip()
+        if cmd in ("/quit", "/exit"):
+            self.done = True
+        elif cmd == "/help":
+            self.out(self.HELP)
+        elif cmd == "/system":
+            self.system = rest or None
+        elif cmd == "/raw":
+            self.raw = not self.raw
+            self.out(f"raw = {self.raw}")
+        elif cmd == "/stats":
+            self.stats = not self.stats
+        elif cmd == "/reset":
+            self.eng.reset_session(self.session)
+            self.images, self.audio = [], None
+        elif cmd == "/model":
+            self.out(json.dumps(self.eng.resource_snapshot(), indent=1))
+        elif cmd == "/profile":
+            self.profiler.enabled = not self.profiler.enabled
+            self.out(f"profile = {self.profiler.enabled}")
+        elif cmd in ("/image", "/audio"):
+            kind = cmd[1:]
+            if not rest:
+                held = [f"{len(b)} bytes" for b in self.images] if kind == "image" else ([f"{len(self.audio)} bytes"] if self.audio else [])
+                self.out(f"{kind}: " + (", ".join(held) if held else "nothing attached") + f"; {cmd} PATH attaches a file to the next prompt")
+            elif rest == "clear":
+                if kind == "image":
+                    self.images = []
+                else:
+                    self.audio = None
+            elif self.media_chat is None or not self.media_chat.accepts.get(kind):
+                self.out(f"{cmd}: this session has no {kind} pipeline; start it with --multimodal-package DIR (a workflow package with "
+                         f"a typed {kind} input)")
+            else:
+                try:
+                    with open(os.path.expanduser(rest), "rb") as f:
+                        data = f.read()
+                except OSError as exc:
+                    self.out(f"{cmd}: {exc}")
+                    return
+                if kind == "image":
+                    self.images.append(data)
+                else:
+                    self.audio = data
+                self.out(f"{kind} attached ({len(data)} bytes); it goes with the next prompt")
+        elif cmd == "/ep":
+            cur = str(getattr(self.eng.llm, "device", getattr(self.args, "device", "cpu")))
+            if not rest:
+                self.out(f"execution device: {cur} (/ep cpu or /ep cuda reloads the model there)")
+            elif rest not in ("cpu", "cuda"):
+                self.out("/ep: expected cpu or cuda")
+            else:
+                if rest == "cuda":
+                    import torch
+
+                    if not torch.cuda.is_available():
+                        self.out("/ep: no CUDA device is visible to this process")
+                        return
+                self.args.device = rest
+                self._reload()
+                self.out(f"model reloaded on {rest}; the session starts over")
+        elif cmd == "/backend":
+            cur = getattr(self.args, "backend", "native")
+            if not rest:
+                self.out(f"decode backend: {cur} (native = fused executor over paged KV, graph = the ONNX graph node by node)")
+            elif rest not in ("native", "graph"):
+                self.out("/backend: expected native or graph")
+            else:
+                self.args.backend = rest
+                self.out(f"decode backend = {rest}" + ("; prompts now run one at a time through the graph executor, without the session's history"
+                                                       if rest == "graph" else ""))
+        else:
+            self.out(f"unknown command {cmd}; /help lists commands")
+
+    def prompt(self, line: str, on_text=None) -> object:
+        on_text = on_text or (lambda d: (sys.stdout.write(d), sys.stdout.flush()))
+        if self.images or self.audio is not None:
+            ids = self.eng.tokenizer.encode(_prompt_text(self.eng, line, self.raw, self.system))
+            image, audio = (self.images[0] if self.images else None), self.audio
+            self.images, self.audio = [], None
+            out_ids = self.media_chat.generate(ids, image=image, audio=audio, max_new_tokens=getattr(self.args, "max_tokens", 64) or 64)
+            text = self.eng.tokenizer.decode(list(out_ids))
+            on_text(text)
+            return None
+        if getattr(self.args, "backend", "native") == "graph":
+            a = copy.copy(self.args)
+            a.prompt = line
+            _generate_on_graph_backend(a)
+            return None
+        text = _prompt_text(self.eng, line, self.raw, self.system if self.eng.session_len(self.session) == 0 else None)
+        return self.eng.generate_in_session(self.session, text, _options(self.args), on_token=lambda t, d: on_text(d))
+
+
 def cmd_run(args, profiler):
-    eng = _load(args)
-    session = eng.create_session()
-    system, raw, stats = None, args.raw, True
+    media = None
+    if getattr(args, "multimodal_package", ""):
+        from .server.multimodal import WorkflowMediaChat
+
+        media = WorkflowMediaChat(args.multimodal_package, "cuda" if str(args.device).startswith("cuda") else "cpu")
+    repl = Repl(args, profiler, media_chat=media)
     print("interactive session; /help lists commands", file=sys.stderr)
-    while True:
+    while not repl.done:
         try:
             line = input(">>> ")
         except (EOFError, KeyboardInterrupt):
@@ -235,33 +359,13 @@ def cmd_run(args, profiler):
         if not line.strip():
             continue
         if line.startswith("/"):
-            cmd, _, rest = line.partition(" ")
-            if cmd in ("/quit", "/exit"):
-                return 0
-            if cmd == "/help":
-                print("/system TEXT  /raw  /stats  /profile  /reset  /model  /quit")
-            elif cmd == "/system":
-                system = rest.strip() or None
-            elif cmd == "/raw":
-                raw = not raw
-                print(f"raw = {raw}")
-            elif cmd == "/stats":
-                stats = not stats
-            elif cmd == "/reset":
-                eng.reset_session(session)
-            elif cmd == "/model":
-                print(json.dumps(eng.resource_snapshot(), indent=1))
-            elif cmd == "/profile":
-                profiler.enabled = not profiler.enabled
-                print(f"profile = {profiler.enabled}")
-            else:
-                print(f"unknown command {cmd}; /help lists commands")
+            repl.command(line)
             continue
-        text = _prompt_text(eng, line, raw, system if eng.session_len(session) == 0 else None)
-        res = eng.generate_in_session(session, text, _options(args), on_token=lambda t, d: (sys.stdout.write(d), sys.stdout.flush()))
+        res = repl.prompt(line)
         print()
-        if stats:
+        if repl.stats and res is not None:
             print(_stats_line(res), file=sys.stderr)
+    return 0
 
 
 def cmd_serve(args, profiler):
@@ -753,6 +857,8 @@ def main(argv=None):
     r.add_argument("model")
     _add_sampling(r)
     _add_engine(r)
+    r.add_argument("--multimodal-package", default="",
+                   help="workflow package with a typed image or audio input: /image and /audio attachments are answered by it")
     s = sub.add_parser("serve")
     s.add_argument("model", nargs="?", default="", help="model directory (or use --models-dir)")
     s.add_argument("--models-dir", default="", help="serve every model directory below this one; requests pick one by name")

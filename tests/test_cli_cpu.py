@@ -96,3 +96,91 @@ def test_unrecognised_decoder_points_to_the_graph_backend(tmp_path):
     assert fast.returncode == 2 and "--backend graph" in fast.stderr
     graph = subprocess.run(base + ["--backend", "graph"], capture_output=True, text=True)
     assert graph.returncode == 0 and "backend graph" in graph.stderr, graph.stderr
+
+
+def test_repl_commands_media_device_and_backend(tmp_path):
+    """The REPL's slash commands, driven without a terminal: attachments go to the media chat with the next prompt, /ep
+    reloads the engine on the other device, /backend switches the decode path, unknown input is explained."""
+    import argparse
+
+    from onnx_genai_b200 import cli
+
+    class FakeTok:
+        def encode(self, text):
+            return [ord(c) % 50 for c in text][:8]
+
+        def decode(self, ids):
+            return "ids:" + ",".join(str(i) for i in ids)
+
+    class FakeEngine:
+        loads = []
+
+        def __init__(self, device):
+            self.llm = argparse.Namespace(device=device)
+            self.tokenizer = FakeTok()
+            self.sessions = 0
+            FakeEngine.loads.append(device)
+
+        def create_session(self):
+            self.sessions += 1
+            return self.sessions
+
+        def reset_session(self, s):
+            self.was_reset = s
+
+        def session_len(self, s):
+            return 0
+
+        def resource_snapshot(self):
+            return {"kv": 1}
+
+    class FakeMedia:
+        accepts = {"image": True, "audio": False}
+
+        def __init__(self):
+            self.calls = []
+
+        def generate(self, ids, image=None, audio=None, max_new_tokens=64):
+            self.calls.append((list(ids), image, audio, max_new_tokens))
+            return [7, 8, 9]
+
+    args = argparse.Namespace(device="cpu", backend="native", raw=True, max_tokens=5)
+    said = []
+    media = FakeMedia()
+    prof = argparse.Namespace(enabled=False)
+    repl = cli.Repl(args, prof, loader=lambda a: FakeEngine(a.device), media_chat=media, out=said.append)
+    repl.command("/help")
+    assert "/image PATH|clear" in said[-1] and "/backend [native|graph]" in said[-1] and "/ep [cpu|cuda]" in said[-1]
+    img = tmp_path / "cat.png"
+    img.write_bytes(b"\x89PNG1234")
+    repl.command(f"/image {img}")
+    assert "image attached (8 bytes)" in said[-1]
+    repl.command("/image")
+    assert "8 bytes" in said[-1]
+    repl.command(f"/audio {img}")
+    assert "no audio pipeline" in said[-1] and "--multimodal-package" in said[-1]
+    repl.command("/image /nonexistent/file.png")
+    assert "No such file" in said[-1]
+    got = []
+    assert repl.prompt("what is this", on_text=got.append) is None
+    assert got == ["ids:7,8,9"] and media.calls[0][1] == b"\x89PNG1234" and media.calls[0][3] == 5 and repl.images == []
+    repl.command("/ep")
+    assert "execution device: cpu" in said[-1]
+    repl.command("/ep tpu")
+    assert "expected cpu or cuda" in said[-1]
+    repl.command("/ep cuda")
+    assert ("no CUDA device" in said[-1]) or FakeEngine.loads[-1] == "cuda"
+    repl.command("/ep cpu")
+    assert FakeEngine.loads[-1] == "cpu" and "reloaded on cpu" in said[-1]
+    repl.command("/backend")
+    assert "decode backend: native" in said[-1]
+    repl.command("/backend graph")
+    assert args.backend == "graph" and "graph executor" in said[-1]
+    repl.command("/backend warp")
+    assert "expected native or graph" in said[-1]
+    repl.command("/profile")
+    assert prof.enabled is True
+    repl.command("/bogus")
+    assert "unknown command /bogus" in said[-1]
+    repl.command("/quit")
+    assert repl.done
