@@ -50,6 +50,26 @@ OGB_DEVICE uint32_t i8x2_to_bf16x2(uint32_t t) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// e5m2 (s eeeee mm, bias 15): the seven magnitude bits dropped at bit 5 of a bf16 read as the same number times 2^-112
+// (subnormals land on bf16 subnormals), so one exact multiply by 2^112 finishes the conversion.  Input word as for e4m3.
+OGB_DEVICE uint32_t e5m2x2_to_bf16x2(uint32_t t) {
+  uint32_t bits = (t & 0x80008000u) | ((t >> 3) & 0x0fe00fe0u);
+  const uint32_t two112 = 0x77807780u;
+  __nv_bfloat162 v = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&bits), *reinterpret_cast<const __nv_bfloat162*>(&two112));
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+OGB_DEVICE void cvt16_e5m2_bf16(const uint4& raw, uint4& lo, uint4& hi) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  uint32_t o[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    o[2 * i] = e5m2x2_to_bf16x2(__byte_perm(w[i], 0, 0x1404));
+    o[2 * i + 1] = e5m2x2_to_bf16x2(__byte_perm(w[i], 0, 0x3424));
+  }
+  lo = make_uint4(o[0], o[1], o[2], o[3]);
+  hi = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
 // 16 e4m3 bytes -> 16 bf16, as two 16-byte vectors
 OGB_DEVICE void cvt16_e4m3_bf16(const uint4& raw, uint4& lo, uint4& hi) {
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -77,14 +97,15 @@ OGB_DEVICE void cvt16_i8_bf16(const uint4& raw, uint4& lo, uint4& hi) {
 }
 
 // Expand one raw page side (16 tokens x 128 one-byte values, 128-byte swizzled rows) into a bf16 page tile
-// ([2 halves][16 rows][128 B], same swizzle), using `nthreads` threads starting at `tid`.  fmt 0: e4m3, 1: int8.
+// ([2 halves][16 rows][128 B], same swizzle), using `nthreads` threads starting at `tid`.  fmt 0: e4m3, 1: int8, 2: e5m2.
 OGB_DEVICE void expand_page(const uint8_t* raw, uint8_t* work, int tid, int nthreads, int fmt) {
   for (int i = tid; i < kPageTokens * 8; i += nthreads) {   // 16 rows x 8 chunks of 16 bytes
     const int r = i >> 3, c = i & 7;
     const uint4 v = *reinterpret_cast<const uint4*>(raw + r * 128 + ((c ^ (r & 7)) << 4));
     uint4 lo, hi;
     if (fmt == 0) cvt16_e4m3_bf16(v, lo, hi);
-    else cvt16_i8_bf16(v, lo, hi);
+    else if (fmt == 1) cvt16_i8_bf16(v, lo, hi);
+    else cvt16_e5m2_bf16(v, lo, hi);
     const int d0 = c * 16;
     *reinterpret_cast<uint4*>(work + kv_tile_off<kD>(r, d0)) = lo;
     *reinterpret_cast<uint4*>(work + kv_tile_off<kD>(r, d0 + 8)) = hi;
@@ -902,7 +923,7 @@ static int launch_decode_q(const void* q, void* out, const void* pool, const flo
                            int q_stride, int o_stride, float scale, int num_splits, float* part_o, float* part_ml,
                            int window, int sink, int* status, void* stream) {
   if (num_seqs <= 0) return 0;
-  if (kv_fmt != 0 && kv_fmt != 1) return -3;
+  if (kv_fmt < 0 || kv_fmt > 2) return -3;
   if (d != kD || hkv <= 0 || hq % hkv != 0 || hq / hkv > 16 || (q_stride % 8) != 0 || scales == nullptr) return -3;
   if (num_splits < 1) num_splits = 1;
   if (num_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return -4;
@@ -948,7 +969,7 @@ static int launch_prefill_q(const void* q, void* out, const void* pool, const fl
                             int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride,
                             int o_stride, float scale, int window, int sink, int* status, void* stream) {
   if (num_tiles <= 0) return 0;
-  if (kv_fmt != 0 && kv_fmt != 1) return -3;
+  if (kv_fmt < 0 || kv_fmt > 2) return -3;
   if (d != kD || hkv <= 0 || hq % hkv != 0 || (q_stride % 8) != 0 || (o_stride % 2) != 0 || scales == nullptr) return -3;
   CUtensorMap map;
   int rc = get_fp8_tmap(pool, num_pages, hkv, &map);
@@ -981,7 +1002,7 @@ extern "C" int ogb_paged_prefill_fp8(const void* q, void* out, const void* pool,
   return launch_prefill_q(q, out, pool, scales, 0, page_table, ctx_len, cu_q, tile_seq, tile_q0, num_tiles, num_seqs, max_pages,
                           num_pages, hq, hkv, d, q_stride, o_stride, scale, 0, 0, status, stream);
 }
-// One-byte pages in either format: kv_format 0 = e4m3, 1 = int8 (symmetric, same per-(page, head, K|V) scale layout).
+// One-byte pages in any format: kv_format 0 = e4m3, 1 = int8 (symmetric), 2 = e5m2; same per-(page, head, K|V) scale layout.
 extern "C" int ogb_paged_decode_q8(const void* q, void* out, const void* pool, const float* scales, int kv_format,
                                    const int* page_table, const int* ctx_len, int num_seqs, int max_pages, int64_t num_pages,
                                    int hq, int hkv, int d, int q_stride, int o_stride, float scale, int num_splits,

@@ -259,7 +259,7 @@ __global__ void rope_kv_append_kernel(__nv_bfloat16* __restrict__ qkv, const int
 __global__ void kv_append_fp8_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ slots,
                                      uint8_t* __restrict__ pool, float* __restrict__ scales, int hq, int hkv, int d,
                                      int page_size, int64_t num_slots, int fmt, int* status) {
-  const float qmax = fmt == 0 ? 448.f : 127.f;     // fmt 0: e4m3, 1: int8 (symmetric)
+  const float qmax = fmt == 0 ? 448.f : (fmt == 1 ? 127.f : 57344.f);     // fmt 0: e4m3, 1: int8 (symmetric), 2: e5m2
   const int t = blockIdx.x;
   const int64_t slot = slots[t];
   if (slot < 0) return;
@@ -306,7 +306,8 @@ __global__ void kv_append_fp8_kernel(const __nv_bfloat16* __restrict__ qkv, cons
       float v = __bfloat162float(row[col + j]) * inv;
       v = fminf(fmaxf(v, -qmax), qmax);
       dst[j] = fmt == 0 ? static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3))
-                        : static_cast<uint8_t>(static_cast<int8_t>(__float2int_rn(v)));
+               : fmt == 1 ? static_cast<uint8_t>(static_cast<int8_t>(__float2int_rn(v)))
+                          : static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E5M2));
     }
   }
 }

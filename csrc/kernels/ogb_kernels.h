@@ -76,7 +76,7 @@ int ogb_paged_prefill_fp8(const void* q, void* out, const void* pool, const floa
                           int num_seqs, int max_pages, int64_t num_pages, int hq, int hkv, int d, int q_stride, int o_stride,
                           float scale, int* status, void* stream);
 
-// One-byte pages in either format (kv_format 0 = e4m3, 1 = symmetric int8), same pool and scale layout.
+// One-byte pages (kv_format 0 = e4m3, 1 = symmetric int8, 2 = e5m2), same pool and scale layout.
 int ogb_rope_kv_append_q8(void* qkv, const int* positions, const int* slots, const float* cos_sin, void* pool, float* scales,
                           int kv_format, int tokens, int hq, int hkv, int d, int rotary_dim, int interleaved, int page_size,
                           int64_t num_slots, int max_pos, int* status, void* stream);

@@ -42,7 +42,7 @@ def _add_engine(p):
     p.add_argument("--backend", default="native", choices=["native", "graph"],
                    help="native: this package's kernels and scheduler; graph: interpret the ONNX graph node by node "
                         "(any decoder architecture, `generate` only, one sequence)")
-    p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3fn", "int8"])
+    p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3fn", "fp8_e5m2", "int8"])
     p.add_argument("--max-batch", type=int, default=32)
     p.add_argument("--vram-limit", default="0.85", help="0.85 (fraction of the device the engine may fill), auto, or a size such as 8GiB for weights + activations + KV")
     p.add_argument("--kv-max-pages", type=int, default=0, help="reserve address space for this many KV pages and back them on demand (CUDA, one GPU)")
@@ -106,7 +106,7 @@ def _load(args):
     if proposer == "draft" and not getattr(args, "draft_model", ""):
         raise SystemExit("--proposer draft needs --draft-model DIR")
     extra = {"kv_max_pages": args.kv_max_pages} if getattr(args, "kv_max_pages", 0) > 0 else {}
-    eng = Engine.from_dir(args.model, device=dev, max_seqs=args.max_batch, kv_dtype={"fp8_e4m3fn": "fp8", "int8": "int8"}.get(args.kv_cache_dtype, "bf16"),
+    eng = Engine.from_dir(args.model, device=dev, max_seqs=args.max_batch, kv_dtype={"fp8_e4m3fn": "fp8", "int8": "int8", "fp8_e5m2": "fp8_e5m2"}.get(args.kv_cache_dtype, "bf16"),
                           gpu_memory_utilization=util if 0 < util <= 1 else 0.85, vram_limit=limit,
                           max_draft_tokens=(getattr(args, "draft_tokens", 0) or rt.spec_tokens) if speculative else 0,
                           draft_model_dir=(getattr(args, "draft_model", "") or None) if proposer in ("auto", "draft") else None,

@@ -197,7 +197,8 @@ class KvOffload:
             idx = torch.from_numpy(pages[c * PAGES_PER_CHUNK:(c + 1) * PAGES_PER_CHUNK].astype(np.int64)).to(self.llm.device)
             parts = []
             for li, pool in enumerate(self.llm.kv.pools):
-                parts.append(pool.index_select(0, idx).contiguous().view(torch.uint8).cpu().numpy().tobytes())
+                raw_pool = pool.view(torch.uint8) if pool.element_size() == 1 else pool
+                parts.append(raw_pool.index_select(0, idx).contiguous().view(torch.uint8).cpu().numpy().tobytes())
                 if self.llm.kv.scales is not None:
                     parts.append(self.llm.kv.scales[li].index_select(0, idx).contiguous().cpu().numpy().tobytes())
             self.connector.store(key, b"".join(parts))
@@ -245,9 +246,11 @@ class KvOffload:
             dst = torch.from_numpy(page_ids[fill].astype(np.int64)).to(self.llm.device)
             for li, pool in enumerate(self.llm.kv.pools):
                 base = li * per_layer
-                pg = torch.from_numpy(blob[base:base + PAGES_PER_CHUNK * self.page_bytes].copy()).view(pool.dtype).view(
+                # one-byte pools are moved as plain bytes (index kernels do not take every 8-bit float type)
+                raw_pool = pool.view(torch.uint8) if pool.element_size() == 1 else pool
+                pg = torch.from_numpy(blob[base:base + PAGES_PER_CHUNK * self.page_bytes].copy()).view(raw_pool.dtype).view(
                     (PAGES_PER_CHUNK,) + tuple(pool.shape[1:]))
-                pool.index_copy_(0, dst, pg[torch.from_numpy(fill)].to(self.llm.device))
+                raw_pool.index_copy_(0, dst, pg[torch.from_numpy(fill)].to(self.llm.device))
                 if self.llm.kv.scales is not None:
                     sc = torch.from_numpy(blob[base + PAGES_PER_CHUNK * self.page_bytes:base + per_layer].copy()).view(torch.float32).view(
                         (PAGES_PER_CHUNK,) + tuple(self.llm.kv.scales[li].shape[1:]))

@@ -109,7 +109,7 @@ class LLMEngine:
         self.memory.lease("activations", tier, act_bytes, "step buffers")
         num_pages = cfg.num_pages
         if num_pages <= 0:
-            kv_bytes = 1 if cfg.kv_dtype in ("fp8", "int8") else 2
+            kv_bytes = 1 if cfg.kv_dtype in ("fp8", "int8", "fp8_e5m2") else 2
             page_bytes = m.num_layers * len(hs.kv_heads) * 2 * ops.PAGE * m.head_dim * kv_bytes
             if is_cuda:
                 free, total = torch.cuda.mem_get_info(self.device)

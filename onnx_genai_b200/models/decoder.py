@@ -175,12 +175,13 @@ class KVCache:
         hkv = kv_heads_local or cfg.num_kv_heads
         self.num_pages = num_pages
         self.dtype = dtype
-        if dtype not in ("bf16", "fp8", "int8"):
-            raise ValueError(f"kv dtype {dtype!r} is not supported; use bf16, fp8 (e4m3 pages) or int8")
-        tdtype = {"bf16": torch.bfloat16, "fp8": torch.uint8, "int8": torch.int8}[dtype]   # one-byte pools say their format by dtype
+        if dtype not in ("bf16", "fp8", "int8", "fp8_e5m2"):
+            raise ValueError(f"kv dtype {dtype!r} is not supported; use bf16, fp8 (e4m3 pages), fp8_e5m2 or int8")
+        # one-byte pools say their format by dtype
+        tdtype = {"bf16": torch.bfloat16, "fp8": torch.uint8, "int8": torch.int8, "fp8_e5m2": torch.float8_e5m2}[dtype]
         if torch.device(device).type == "cpu" and dtype == "bf16":
             tdtype = torch.float32
-        quant = dtype in ("fp8", "int8")
+        quant = dtype in ("fp8", "int8", "fp8_e5m2")
         self.max_pages = max(int(max_pages), num_pages)
         self.buffers = None
         if self.max_pages > num_pages and torch.device(device).type == "cuda":

@@ -303,8 +303,9 @@ def silu_mul(gate_up, out=None):
 
 @_timed("rope_kv_append")
 def kv_format(pool) -> int:
-    """One-byte page pools say their format by dtype: uint8 holds e4m3 bit patterns (0), int8 holds symmetric int8 (1)."""
-    return 1 if pool.dtype == torch.int8 else 0
+    """One-byte page pools say their format by dtype: uint8 holds e4m3 bit patterns (0), int8 holds symmetric int8 (1),
+    float8_e5m2 holds e5m2 (2)."""
+    return 1 if pool.dtype == torch.int8 else (2 if pool.dtype == torch.float8_e5m2 else 0)
 
 
 def rope_kv_append(qkv, positions, slots, cos_sin, pool, hq, hkv, d, rotary_dim=None, interleaved=False,

@@ -95,6 +95,11 @@ def e4m3_bytes(x):
     return x.float().clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
 
 
+def e5m2_bytes(x):
+    """fp32 -> e5m2 with saturation at +-57344 (round to nearest even)."""
+    return x.float().clamp(-57344.0, 57344.0).to(torch.float8_e5m2)
+
+
 def int8_bytes(x):
     """fp32 -> symmetric int8 with saturation at +-127 (round to nearest even)."""
     return torch.round(x.float().clamp(-127.0, 127.0)).to(torch.int8)
@@ -108,7 +113,7 @@ def kv_append_fp8(qkv, slots, pool, scales, hq, hkv, d):
     scales [P,hkv,2] fp32; qkv already rotated."""
     t = qkv.shape[0]
     v = qkv.view(t, hq + 2 * hkv, d).float()
-    qmax, encode = (127.0, int8_bytes) if pool.dtype == torch.int8 else (448.0, e4m3_bytes)
+    qmax, encode = (127.0, int8_bytes) if pool.dtype == torch.int8 else ((57344.0, e5m2_bytes) if pool.dtype == torch.float8_e5m2 else (448.0, e4m3_bytes))
     for i in range(t):
         slot = int(slots[i])
         if slot < 0:

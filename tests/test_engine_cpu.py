@@ -174,17 +174,18 @@ def test_fp8_kv_pages_on_cpu_stay_close_to_full_precision(weights):
     rng = np.random.default_rng(9)
     prompt = rng.integers(0, CFG.vocab, size=70).tolist()
     logits = {}
-    for kv in ("bf16", "fp8", "int8"):
+    for kv in ("bf16", "fp8", "int8", "fp8_e5m2"):
         eng = _engine(weights, kv_dtype=kv)
         eng.add_request(np.asarray(prompt, dtype=np.int32), 3)
         eng.step()
         eng.step()
         logits[kv] = eng.model.logits[:1].float().clone()
         if kv != "bf16":
-            assert eng.kv.pools[0].dtype == (torch.uint8 if kv == "fp8" else torch.int8) and float(eng.kv.scales[0].max()) > 0
-    for kv in ("fp8", "int8"):
+            want = {"fp8": torch.uint8, "int8": torch.int8, "fp8_e5m2": torch.float8_e5m2}[kv]
+            assert eng.kv.pools[0].dtype == want and float(eng.kv.scales[0].max()) > 0
+    for kv in ("fp8", "int8", "fp8_e5m2"):
         err = float((logits[kv] - logits["bf16"]).norm() / logits["bf16"].norm())
-        assert err < 0.25, (kv, err)          # 3 mantissa bits and sharp attention (weights of std 0.3): noise, not garbage
+        assert err < (0.45 if kv == "fp8_e5m2" else 0.25), (kv, err)   # 3 (e5m2: 2) mantissa bits and sharp attention (weights of std 0.3): noise, not garbage
     with pytest.raises(ValueError, match="kv dtype 'int4' is not supported"):
         _engine(weights, kv_dtype="int4")
 

@@ -400,8 +400,8 @@ def test_moe_experts_grouped_gemm(t, e, k, hidden, inter):
     assert _rel_err(lo.float() + hi.float() + x0.float(), want) < 3e-2
 
 
-QMAX = {"fp8": 448.0, "int8": 127.0}
-POOL_DTYPE = {"fp8": torch.uint8, "int8": torch.int8}
+QMAX = {"fp8": 448.0, "int8": 127.0, "e5m2": 57344.0}
+POOL_DTYPE = {"fp8": torch.uint8, "int8": torch.int8, "e5m2": torch.float8_e5m2}
 
 
 def _dequant(pool, scales):
@@ -424,12 +424,14 @@ def _make_paged_fp8(ctx_lens, hkv, d, seed=0, fmt="fp8"):
     scales = vals.abs().amax(dim=(-1, -2)).clamp_min(1e-6) / QMAX[fmt]
     if fmt == "int8":
         q8 = torch.round(vals / scales[..., None, None]).clamp(-127, 127).to(torch.int8)
+    elif fmt == "e5m2":
+        q8 = (vals / scales[..., None, None]).to(torch.float8_e5m2)
     else:
         q8 = (vals / scales[..., None, None]).to(torch.float8_e4m3fn).view(torch.uint8)
     return q8.to(DEV), scales.float().to(DEV), table.to(DEV)
 
 
-@pytest.mark.parametrize("fmt", ["fp8", "int8"])
+@pytest.mark.parametrize("fmt", ["fp8", "int8", "e5m2"])
 def test_paged_attention_fp8_pages(fmt):
     torch.manual_seed(13)
     hq, hkv, d = 28, 4, 128
@@ -498,7 +500,7 @@ def test_decode_over_e4m3_pages_as_mma_operands_is_as_accurate_as_expanding_them
             assert errs[mma, splits] < 1e-2 and errs[mma, splits] < 1.5 * errs[0, splits] + 1e-3, errs
 
 
-@pytest.mark.parametrize("fmt", ["fp8", "int8"])
+@pytest.mark.parametrize("fmt", ["fp8", "int8", "e5m2"])
 def test_rope_kv_append_fp8_roundtrip(fmt):
     torch.manual_seed(14)
     qmax = QMAX[fmt]
@@ -526,7 +528,7 @@ def test_rope_kv_append_fp8_roundtrip(fmt):
     assert float(err[(bf_pool.float().abs() <= qmax * scales[..., None, None])].mean()) < 0.05
 
 
-@pytest.mark.parametrize("fmt", ["fp8", "int8"])
+@pytest.mark.parametrize("fmt", ["fp8", "int8", "e5m2"])
 def test_rope_kv_append_fp8_one_launch_equals_token_by_token(fmt):
     """A prefill chunk appends many tokens of a page in one launch; the stored bytes and scales must be exactly those
     of appending the tokens one launch at a time (every token of a page uses the scale of the page's first token),
@@ -560,7 +562,7 @@ def test_rope_kv_append_fp8_one_launch_equals_token_by_token(fmt):
         assert torch.equal(pool, pool_a)
 
 
-@pytest.mark.parametrize("fmt", ["fp8", "int8"])
+@pytest.mark.parametrize("fmt", ["fp8", "int8", "e5m2"])
 def test_fp8_append_kernel_matches_the_cpu_codec_byte_for_byte(fmt):
     """The device one-byte append (rotation launch + codec launch) against the CPU statement of the same codec."""
     torch.manual_seed(16)
@@ -584,7 +586,8 @@ def test_fp8_append_kernel_matches_the_cpu_codec_byte_for_byte(fmt):
     same_rot = (q_g.cpu() == q_c).float().mean()
     assert float(same_rot) > 0.999
     assert torch.allclose(sc_g.cpu(), sc_c, rtol=1e-2)
-    mismatch = (pool_g.cpu() != pool_c).float()
+    as_bytes = lambda x: x.view(torch.uint8) if x.dtype == torch.float8_e5m2 else x
+    mismatch = (as_bytes(pool_g.cpu()) != as_bytes(pool_c)).float()
     assert float(mismatch.mean()) < 0.01                            # bytes differ only where the rotated input differed by an ulp
 
 
