@@ -22,6 +22,21 @@ struct LayerPtrs {
   void* kv_pool;
 };
 
+// Weight paging: the matrices of the layers from `first` on live in pinned host memory, one contiguous pack per layer
+// (qkv_w | o_w | gate_up_w | down_w), and pass through two device slots.  While layer l runs out of one slot the copy
+// stream fills the other with layer l + 1; `copied` orders a layer's first GEMM after its copy, `consumed` orders the
+// next copy into a slot after the layer that used it.  Role of the reference's weight paging for models larger than
+// device memory (crates/onnx-runtime-ep-cuda/src/weight_paging.rs), done with two streams and four events.
+struct WeightPaging {
+  int first = -1;
+  std::vector<const void*> host;
+  void* slot[2] = {nullptr, nullptr};
+  size_t bytes = 0, off[4] = {0, 0, 0, 0};
+  cudaStream_t copy = nullptr;
+  cudaEvent_t copied[2] = {nullptr, nullptr}, consumed[2] = {nullptr, nullptr};
+  long long copies = 0;
+};
+
 struct DecoderPlan {
   int num_layers, hidden, hq, hkv, d, rotary_dim, interleaved, inter_local, vocab, swiglu_bn, window, sink, max_pages, max_pos;
   int tp, prefill_tc;
@@ -35,6 +50,7 @@ struct DecoderPlan {
   std::vector<LayerPtrs> layers;
   long long launches = 0;
   long long launches_scatter = 0, launches_exchange = 0;   // row-parallel GEMMs with the scatter epilogue / exchange kernels
+  WeightPaging wp;
 };
 
 }  // namespace ogb
@@ -80,7 +96,37 @@ extern "C" void* ogb_decoder_create(const int* iparams, int64_t num_pages, const
   return p;
 }
 
-extern "C" void ogb_decoder_destroy(void* plan) { delete static_cast<DecoderPlan*>(plan); }
+extern "C" void ogb_decoder_destroy(void* plan) {
+  DecoderPlan* p = static_cast<DecoderPlan*>(plan);
+  if (p != nullptr && p->wp.copy != nullptr) {
+    cudaStreamSynchronize(p->wp.copy);
+    for (int i = 0; i < 2; ++i) { cudaEventDestroy(p->wp.copied[i]); cudaEventDestroy(p->wp.consumed[i]); }
+    cudaStreamDestroy(p->wp.copy);
+  }
+  delete p;
+}
+
+// Page the matrices of layers [first_layer, num_layers) through two device slots (see WeightPaging).  host_packs: one
+// pinned pointer per paged layer; slots: two device buffers of `bytes`; offsets: qkv_w, o_w, gate_up_w, down_w inside a pack.
+extern "C" int ogb_decoder_set_weight_paging(void* plan, int first_layer, const uint64_t* host_packs, const uint64_t* slots,
+                                             int64_t bytes, const int64_t* offsets) {
+  DecoderPlan* p = static_cast<DecoderPlan*>(plan);
+  if (p == nullptr || first_layer < 0 || first_layer >= p->num_layers || bytes <= 0 || p->wp.copy != nullptr) return -3;
+  WeightPaging& w = p->wp;
+  for (int l = first_layer; l < p->num_layers; ++l) w.host.push_back(reinterpret_cast<const void*>(host_packs[l - first_layer]));
+  w.slot[0] = reinterpret_cast<void*>(slots[0]);
+  w.slot[1] = reinterpret_cast<void*>(slots[1]);
+  w.bytes = static_cast<size_t>(bytes);
+  for (int i = 0; i < 4; ++i) w.off[i] = static_cast<size_t>(offsets[i]);
+  OGB_CUDA_CHECK(cudaStreamCreateWithFlags(&w.copy, cudaStreamNonBlocking));
+  for (int i = 0; i < 2; ++i) {
+    OGB_CUDA_CHECK(cudaEventCreateWithFlags(&w.copied[i], cudaEventDisableTiming));
+    OGB_CUDA_CHECK(cudaEventCreateWithFlags(&w.consumed[i], cudaEventDisableTiming));
+  }
+  w.first = first_layer;
+  return 0;
+}
+extern "C" long long ogb_decoder_weight_copies(void* plan) { return static_cast<DecoderPlan*>(plan)->wp.copies; }
 extern "C" long long ogb_decoder_launches(void* plan) { return static_cast<DecoderPlan*>(plan)->launches; }
 // which: 0 = all kernels, 1 = GEMMs with the tensor-parallel scatter epilogue, 2 = tensor-parallel exchange kernels
 extern "C" long long ogb_decoder_counter(void* plan, int which) {
@@ -144,8 +190,27 @@ extern "C" int ogb_decoder_step(void* plan, const int* token_ids, const int* pos
     // every rank embeds and norms all rows once; from here on a rank only updates the residual rows it owns
     STEP_CHECK(ogb_rmsnorm_bf16(p->x, nullptr, p->layers[0].ln1, p->h, T, hid, hid, hid, p->eps, stream));
   }
+  WeightPaging& wp = p->wp;
+  cudaStream_t cstream = static_cast<cudaStream_t>(stream);
+  auto page_in = [&](int l) -> int {          // start the copy of layer l into its slot, behind the slot's last reader
+    const int i = l - wp.first, s = i & 1;
+    OGB_CUDA_CHECK(cudaStreamWaitEvent(wp.copy, wp.consumed[s], 0));
+    OGB_CUDA_CHECK(cudaMemcpyAsync(wp.slot[s], wp.host[i], wp.bytes, cudaMemcpyHostToDevice, wp.copy));
+    OGB_CUDA_CHECK(cudaEventRecord(wp.copied[s], wp.copy));
+    ++wp.copies;
+    return 0;
+  };
+  if (wp.first >= 0) STEP_CHECK(page_in(wp.first));
   for (int l = 0; l < p->num_layers; ++l) {
-    const LayerPtrs& L = p->layers[l];
+    LayerPtrs L = p->layers[l];
+    const bool paged = wp.first >= 0 && l >= wp.first;
+    if (paged) {
+      const int s = (l - wp.first) & 1;
+      if (l + 1 < p->num_layers) STEP_CHECK(page_in(l + 1));      // one layer ahead: it lands while this layer computes
+      OGB_CUDA_CHECK(cudaStreamWaitEvent(cstream, wp.copied[s], 0));
+      const char* base = static_cast<const char*>(wp.slot[s]);
+      L.qkv_w = base + wp.off[0]; L.o_w = base + wp.off[1]; L.gate_up_w = base + wp.off[2]; L.down_w = base + wp.off[3];
+    }
     if (!tp) STEP_CHECK(ogb_rmsnorm_bf16(p->x, nullptr, L.ln1, p->h, T, hid, hid, hid, p->eps, stream));
     STEP_CHECK(ogb_gemm_bf16_wait(p->h, L.qkv_w, p->qkv, L.qkv_b, nullptr, nullptr, T, qkv_n, hid, hid, hid, qkv_n, 0, 0, 0,
                                   (tp && l > 0) ? ready[1] : nullptr, (tp && l > 0) ? ready[1] + 64 : nullptr, 0, p->status, stream));
@@ -189,6 +254,7 @@ extern "C" int ogb_decoder_step(void* plan, const int* token_ids, const int* pos
       const void* next_norm = (l + 1 < p->num_layers) ? p->layers[l + 1].ln1 : p->final_norm;
       STEP_CHECK(ogb_tp_exchange_norm(rd[1], next_norm, p->eps, T, hid, tp_chunk, p->tp, nvls, pushed, p->status, stream));
     }
+    if (paged) OGB_CUDA_CHECK(cudaEventRecord(wp.consumed[(l - wp.first) & 1], cstream));
   }
   if (R > 0) {
     if (!tp) {

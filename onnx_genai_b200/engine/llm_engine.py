@@ -55,6 +55,7 @@ class EngineConfig:
     max_draft_tokens: int = 0          # speculative decoding: drafts verified per sequence per step
     native_executor: bool = True       # launch the layer stack from the C++ step executor when possible
     cuda_graphs: bool = False          # replay decode-only steps (forward + sampler) from captured CUDA graphs
+    weight_offload_layers: int = 0     # keep the matrices of the last N layers in pinned host memory and stream them per step
     shard_sampling: bool = True        # TP: each rank runs lm_head + sampler for 1/tp of the rows, tokens are all-gathered
     vram_limit: str | None = None      # "8GiB" | "0.9" | "auto": cap on device bytes (weights + activations + KV pool)
     seed: int = 0
@@ -101,7 +102,7 @@ class LLMEngine:
         if is_cuda and cfg.vram_limit:
             self.memory.limits["vram"] = parse_limit(cfg.vram_limit, torch.cuda.mem_get_info(self.device)[1])
         w_bytes = tensor_bytes(weights)
-        self.memory.lease("weights", tier, w_bytes, m.name)
+        self.weights_lease = self.memory.lease("weights", tier, w_bytes, m.name)
         try:
             act_bytes = max(0, tensor_bytes(self.model) - w_bytes)
         except Exception:            # accounting must never stop an engine from starting
@@ -198,7 +199,14 @@ class LLMEngine:
         self.temperature, self.top_p, self.min_p, self.uniform = (f32(L.temperature), f32(L.top_p), f32(L.min_p),
                                                                   f32(L.uniform))
         self.top_k = p[L.top_k:L.top_k + max_rows]
+        self.model.weight_offload_layers = cfg.weight_offload_layers if is_cuda else 0
         self.native_executor = cfg.native_executor and self.model.bind_native(self.kv, max_pages_per_seq)
+        if cfg.weight_offload_layers > 0:
+            if not (self.native_executor and getattr(self.model, "weight_packs", None)):
+                raise ValueError("weight_offload_layers needs the C++ step executor (CUDA, dense bf16 layers, bf16 KV pages)")
+            self.memory.lease("weights", "host", self.model.paged_weight_bytes, f"{cfg.weight_offload_layers} paged layer(s)")
+            slots = sum(s.numel() for s in self.model.weight_slots)
+            self.weights_lease.resize(max(0, self.weights_lease.nbytes - self.model.paged_weight_bytes + slots))   # two slots stay on the device
         self.host_samplers: dict = {}     # seq id -> fn(logits_row fp32 numpy, uniform) -> token id
         self.proposers: dict = {}         # seq id -> SpeculativeProposer
         self.stats: dict[int, RequestStats] = {}
@@ -347,6 +355,7 @@ class LLMEngine:
 
     def _graph_eligible(self, si, r, hdr) -> bool:
         return (self.cfg.cuda_graphs and self.device.type == "cuda" and self.tp == 1 and not getattr(self.model, "tap_layers", None)
+                and not self.cfg.weight_offload_layers
                 and si.num_prefill_seqs == 0 and si.num_tiles == 0 and si.num_decode == si.num_tokens == r and r > 0
                 and r <= min(self.cfg.max_seqs, self.GRAPH_BUCKETS[-1]))
 

@@ -353,7 +353,51 @@ class DecoderModel:
         lib.ogb_decoder_set_num_pages.argtypes = [ctypes.c_void_p, ctypes.c_int64]
         lib.ogb_decoder_set_num_pages.restype = None
         self.native = lib.ogb_decoder_create(ip, kv.num_pages, fp, gp, lp)   # backed pages: ids beyond them are refused
+        if self.native and getattr(self, "weight_offload_layers", 0) > 0:
+            self._page_weights(lib, int(self.weight_offload_layers))
         return bool(self.native)
+
+    def _page_weights(self, lib, n_layers: int) -> None:
+        """Move the matrices of the last ``n_layers`` layers to pinned host memory, one contiguous pack per layer, and let
+        the step executor stream them through two device slots (the copy of layer l + 1 runs under the compute of layer
+        l).  Device memory then holds the first layers, two slots and the activations; the cost is one PCIe pass over the
+        paged weights per step.  The device copies are released here."""
+        import ctypes
+
+        w = self.w
+        n_layers = min(n_layers, len(w.layers))
+        first = len(w.layers) - n_layers
+        names = ("qkv_w", "o_w", "gate_up_w", "down_w")
+        align = lambda b: (b + 255) // 256 * 256
+        sizes = [align(getattr(w.layers[first], n).numel() * 2) for n in names]
+        offsets = [sum(sizes[:i]) for i in range(4)]
+        total = sum(sizes)
+        self.weight_packs, self.weight_slots = [], [torch.empty(total, dtype=torch.uint8, device=self.device) for _ in range(2)]
+        for lw in w.layers[first:]:
+            pack = torch.empty(total, dtype=torch.uint8, pin_memory=True)
+            for n, off in zip(names, offsets):
+                t = getattr(lw, n)
+                if t.numel() * 2 > sizes[names.index(n)] or t.dtype != torch.bfloat16:
+                    raise ValueError("weight paging needs layers of one shape in bf16")
+                pack[off:off + t.numel() * 2].copy_(t.contiguous().view(torch.uint8).reshape(-1))
+                setattr(lw, n, None)                      # the device copy goes away; the Python-driven path cannot run paged layers
+            self.weight_packs.append(pack)
+        lib.ogb_decoder_set_weight_paging.restype = ctypes.c_int
+        lib.ogb_decoder_set_weight_paging.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
+        lib.ogb_decoder_weight_copies.restype = ctypes.c_longlong
+        lib.ogb_decoder_weight_copies.argtypes = [ctypes.c_void_p]
+        hp = (ctypes.c_uint64 * n_layers)(*[p.data_ptr() for p in self.weight_packs])
+        sp = (ctypes.c_uint64 * 2)(*[s.data_ptr() for s in self.weight_slots])
+        op = (ctypes.c_int64 * 4)(*offsets)
+        rc = lib.ogb_decoder_set_weight_paging(self.native, first, hp, sp, total, op)
+        if rc != 0:
+            raise RuntimeError(f"ogb_decoder_set_weight_paging failed with code {rc}")
+        self.paged_weight_bytes = total * n_layers
+        torch.cuda.empty_cache()
+
+    def weight_copies(self) -> int:
+        """Layer packs copied host -> device by the step executor so far (weight paging)."""
+        return int(self._native_lib.ogb_decoder_weight_copies(self.native)) if self.native and getattr(self, "weight_packs", None) else 0
 
     def native_counter(self, which: int) -> int:
         """Kernels the C++ step executor has launched so far: 0 all, 1 scatter-epilogue GEMMs, 2 exchange kernels."""

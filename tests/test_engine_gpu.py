@@ -317,3 +317,33 @@ def test_swap_preemption_and_cow_fork_on_the_device_keep_tokens(kv):
     assert eng.swap_moves > copies0             # the copy-on-write copy ran on the device
     n = min(len(outs[sid]), len(outs[child]))
     assert n >= 8 and outs[sid][:n] == outs[child][:n] == want[0][1:n + 1]      # both continue the unforked run
+
+
+def test_weight_paging_streams_layers_from_pinned_memory_and_changes_no_token():
+    """The last layers' matrices live in pinned host memory and pass through two device slots per step; greedy tokens
+    equal the resident run, the ledger shows the bytes on the host tier, and every step copies each paged layer once."""
+    cfg = CFG128.replace(num_layers=5) if hasattr(CFG128, "replace") else CFG128
+    w = random_weights(cfg, "cuda", seed=9, std=0.05)
+    prompts = [np.random.default_rng(4).integers(0, cfg.vocab, size=n).astype(np.int32) for n in (40, 300)]
+    outs = {}
+    import copy
+
+    for paged in (0, 3):
+        eng = LLMEngine(EngineConfig(model=cfg, num_pages=128, max_seqs=4, max_tokens_per_step=512, max_seq_len=512,
+                                     weight_offload_layers=paged), weights=copy.deepcopy(w), device="cuda")
+        sids = [eng.add_request(p, 12, ignore_eos=True) for p in prompts]
+        steps = 0
+        while eng.core.has_work:
+            eng.step()
+            steps += 1
+        outs[paged] = [list(eng.core.seq_tokens(s)) for s in sids]
+        if paged:
+            assert eng.model.weight_copies() == steps * paged
+            snap = eng.memory.snapshot()
+            assert snap["host"]["by_role"]["weights"] == eng.model.paged_weight_bytes > 0
+            assert all(getattr(lw, "qkv_w") is None for lw in eng.model.w.layers[-paged:])
+    ops.check_status()
+    assert outs[0] == outs[3]
+    with pytest.raises(ValueError, match="weight_offload_layers needs the C\\+\\+ step executor"):
+        LLMEngine(EngineConfig(model=cfg, num_pages=64, max_seqs=2, max_tokens_per_step=256, max_seq_len=256, kv_dtype="fp8",
+                               weight_offload_layers=2), weights=copy.deepcopy(w), device="cuda")
