@@ -45,6 +45,8 @@ def _add_engine(p):
     p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3fn", "fp8_e5m2", "int8"])
     p.add_argument("--max-batch", type=int, default=32)
     p.add_argument("--vram-limit", default="0.85", help="0.85 (fraction of the device the engine may fill), auto, or a size such as 8GiB for weights + activations + KV")
+    p.add_argument("--context-cache", action="store_true", help="keep the lowered weight layout beside the model (ogb_context/) and reuse it on the next load")
+    p.add_argument("--weight-offload-layers", type=int, default=0, help="keep the matrices of the last N layers in pinned host memory and stream them every step (CUDA)")
     p.add_argument("--kv-max-pages", type=int, default=0, help="reserve address space for this many KV pages and back them on demand (CUDA, one GPU)")
     p.add_argument("--host-ram-limit", default="auto", help="cap on pinned host memory for KV swap and the KV offload host tier: auto, a size such as 32GiB, or a fraction of RAM")
     p.add_argument("--cpu-cores", type=int, default=0, help="threads for CPU kernels and host-side work (0: leave as is)")
@@ -106,6 +108,10 @@ def _load(args):
     if proposer == "draft" and not getattr(args, "draft_model", ""):
         raise SystemExit("--proposer draft needs --draft-model DIR")
     extra = {"kv_max_pages": args.kv_max_pages} if getattr(args, "kv_max_pages", 0) > 0 else {}
+    if getattr(args, "context_cache", False):
+        extra["context_cache"] = True
+    if getattr(args, "weight_offload_layers", 0) > 0:
+        extra["weight_offload_layers"] = args.weight_offload_layers
     eng = Engine.from_dir(args.model, device=dev, max_seqs=args.max_batch, kv_dtype={"fp8_e4m3fn": "fp8", "int8": "int8", "fp8_e5m2": "fp8_e5m2"}.get(args.kv_cache_dtype, "bf16"),
                           gpu_memory_utilization=util if 0 < util <= 1 else 0.85, vram_limit=limit,
                           max_draft_tokens=(getattr(args, "draft_tokens", 0) or rt.spec_tokens) if speculative else 0,

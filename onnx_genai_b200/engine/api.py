@@ -123,9 +123,11 @@ class Engine:
     def from_dir(cls, model_dir: str, device=None, page_size: int | None = None, max_seqs: int = 32,
                  max_seq_len: int | None = None, num_pages: int = 0, max_tokens_per_step: int = 2048,
                  kv_dtype: str = "bf16", max_draft_tokens: int = 0, draft_model_dir: str | None = None,
-                 keep_int4: bool | None = None, **engine_kw):
+                 keep_int4: bool | None = None, context_cache=None, **engine_kw):
         """Load a flat model directory or a model package.  ``page_size`` is accepted for API
-        compatibility; pages hold 16 tokens (the attention kernels' tile)."""
+        compatibility; pages hold 16 tokens (the attention kernels' tile).  ``context_cache``: True (or a directory) keeps the
+        lowered weight layout beside the model (``ogb_context/``) and reads it back on the next load instead of parsing and
+        packing the graph again; ``ONNX_GENAI_CONTEXT_CACHE=1`` turns it on for every load."""
         if page_size not in (None, 16):
             raise ValueError(f"page_size={page_size} is not supported: KV pages hold 16 tokens")
         # precedence: the caller's arguments > ONNX_GENAI_* environment (utils/runtime_config.py) > metadata > built-in
@@ -147,7 +149,16 @@ class Engine:
             from ..ops import cpu as _cpu_ops
 
             keep_int4 = str(device).startswith("cuda") or _cpu_ops.available()
-        cfg, weights, _ = lower_decoder(load_any(d.model_path), dtype=dtype, device=device, keep_int4=keep_int4)
+        if context_cache is None:
+            context_cache = os.environ.get("ONNX_GENAI_CONTEXT_CACHE", "0") not in ("", "0")
+        cache_hit = None
+        if context_cache:
+            from ..package.context_cache import lower_with_cache
+
+            cfg, weights, cache_hit = lower_with_cache(d.model_path, lambda: load_any(d.model_path), dtype, device, keep_int4,
+                                                       cache_dir=context_cache if isinstance(context_cache, str) else None)
+        else:
+            cfg, weights, _ = lower_decoder(load_any(d.model_path), dtype=dtype, device=device, keep_int4=keep_int4)
         if meta.vocab_size and meta.vocab_size != cfg.vocab:
             raise md.MetadataError(f"{d.metadata_path}: model.vocab_size={meta.vocab_size} but the graph's embedding has "
                                    f"{cfg.vocab} rows; fix the metadata or re-export the model")
@@ -179,6 +190,7 @@ class Engine:
         llm = LLMEngine(ecfg, weights=weights, device=device)
         draft = cls.from_dir(draft_model_dir, device=device, max_seqs=max_seqs, max_seq_len=max_seq_len) if draft_model_dir else None
         eng = cls(llm, tok, d.chat_template, meta, eos, draft)
+        eng.context_cache_hit = cache_hit            # None: cache off, False: written by this load, True: read back
         mtp_path = os.path.join(os.path.dirname(d.model_path), "mtp_head.safetensors")
         if max_draft_tokens > 0 and draft is None and os.path.exists(mtp_path):
             # a package that ships an MTP head drafts with it (speculative requests only)

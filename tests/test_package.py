@@ -158,3 +158,39 @@ def test_every_upstream_fixture_metadata_document_parses():
     assert len(docs) >= 20
     for path in docs:
         md.load(path)          # unknown fields, capabilities or shapes would raise MetadataError naming the file
+
+
+def test_context_cache_round_trips_dense_and_int4_lowerings(tmp_path):
+    """The cached lowering gives the same configuration, the same tensors and the same tokens; touching the model file
+    or changing the options makes it stale."""
+    import dataclasses
+
+    from onnx_genai_b200.bench.config_bench import _export
+    from onnx_genai_b200.engine.api import Engine, GenerateOptions
+    from onnx_genai_b200.package import context_cache as cc
+
+    for fmt in ("fp32", "int4"):
+        d = str(tmp_path / fmt)
+        _export("tiny-llama", d, fmt, layers=2)
+        first = Engine.from_dir(d, device="cpu", max_seqs=2, max_seq_len=64, context_cache=True)
+        assert first.context_cache_hit is False and os.path.exists(os.path.join(d, "ogb_context", "weights.bin"))
+        second = Engine.from_dir(d, device="cpu", max_seqs=2, max_seq_len=64, context_cache=True)
+        assert second.context_cache_hit is True
+        assert dataclasses.asdict(first.llm.cfg.model) == dataclasses.asdict(second.llm.cfg.model)
+        opt = GenerateOptions(max_new_tokens=6, greedy=True)
+        assert first.generate("hello", opt).token_ids == second.generate("hello", opt).token_ids
+        plain = Engine.from_dir(d, device="cpu", max_seqs=2, max_seq_len=64)
+        assert plain.context_cache_hit is None and plain.generate("hello", opt).token_ids == second.generate("hello", opt).token_ids
+        # stale: another option, then a touched source file
+        model_path = os.path.join(d, "decoder.onnx")
+        key = cc.fingerprint(model_path, torch.float32, True)
+        assert cc.load(os.path.join(d, "ogb_context"), key + "x", "cpu") is None
+        os.utime(model_path, ns=(1, 1))
+        assert cc.fingerprint(model_path, torch.float32, True) != key
+        third = Engine.from_dir(d, device="cpu", max_seqs=2, max_seq_len=64, context_cache=True)
+        assert third.context_cache_hit is False
+    # a truncated blob is a miss, not a crash
+    blob = os.path.join(d, "ogb_context", "weights.bin")
+    with open(blob, "r+b") as f:
+        f.truncate(100)
+    assert Engine.from_dir(d, device="cpu", max_seqs=2, max_seq_len=64, context_cache=True).context_cache_hit is False
