@@ -142,6 +142,48 @@ def bench_attention(timer, pk):
     return rows
 
 
+def bench_attention_tp_shapes(timer, pk):
+    """Decode attention as one rank of a tensor-parallel group sees it: one KV head and 7 (TP=4) or 4 (TP=8) query heads, 255
+    sequences with contexts drawn from U[128, 2304] as in the serving bench.  Launch trains over distinct pools (together
+    larger than L2) so that a launch's host path does not count."""
+    rows = []
+    d, n = 128, 255
+    g = torch.Generator(device="cpu").manual_seed(5)
+    ctx = torch.randint(128, 2305, (n,), generator=g)
+    pages_per = int((int(ctx.max()) + 15) // 16)
+    total = int(((ctx + 15) // 16).sum()) + 1
+    copies = 3
+    for hq, hkv in ((7, 1), (4, 1)):
+        pools = [(torch.randn(total, hkv, 2, 16, d, device="cuda") * 0.5).bfloat16() for _ in range(copies)]
+        perm = torch.randperm(total)
+        table = torch.zeros(n, pages_per, dtype=torch.int32)
+        o = 0
+        for s in range(n):
+            k = int((ctx[s] + 15) // 16)
+            table[s, :k] = perm[o:o + k].to(torch.int32)
+            o += k
+        table, ctx_t = table.cuda(), ctx.to(torch.int32).cuda()
+        q = torch.randn(n, (hq + 2 * hkv) * d, device="cuda").bfloat16()
+        out = torch.empty(n, hq * d, device="cuda", dtype=torch.bfloat16)
+        byts = float(ctx.sum()) * hkv * 2 * d * 2
+        for splits in (1, 2, 4):
+            po = torch.empty(n * hq * splits * d, dtype=torch.float32, device="cuda")
+            pm = torch.empty(n * hq * splits * 2, dtype=torch.float32, device="cuda")
+
+            def fn():
+                for i in range(2 * copies):
+                    ops.paged_decode(q, out, pools[i % copies], table, ctx_t, hq, hkv, d, num_splits=splits, part_o=po, part_ml=pm)
+
+            med, _ = timer.time(fn)
+            per = med / (2 * copies)
+            rows.append({"kernel": "paged_decode_tp_rank", "hq": hq, "hkv": hkv, "seqs": n, "ctx": "U[128,2304]", "splits": splits, "ms": round(per, 4),
+                         "gbs": round(byts / per / 1e6, 1), "frac_of_%s_hbm" % pk["source"]: round(byts / per / 1e6 / pk["hbm_gbs"], 3)})
+            print(json.dumps(rows[-1]), flush=True)
+        del pools
+    ops.check_status()
+    return rows
+
+
 def bench_attention_one_byte(timer, pk):
     """Decode attention over one-byte KV pages (e4m3 and int8): same contexts as the bf16 rows, half the bytes."""
     rows = []
@@ -332,7 +374,7 @@ def ncu_case(name: str, iters: int = 3):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ncu-case", default="", help="run one small single-kernel workload (for ncu) and exit")
-    ap.add_argument("--what", default="gemm,attn,misc", help="comma list of gemm, attn, attn8 (one-byte KV pages), misc, w4 (int4 decode projections)")
+    ap.add_argument("--what", default="gemm,attn,misc", help="comma list of gemm, attn, attn_tp (one rank's decode share at TP=4 / 8), attn8 (one-byte KV pages), misc, w4 (int4 decode projections)")
     ap.add_argument("--json", default="")
     args = ap.parse_args()
     if args.ncu_case:
@@ -345,6 +387,8 @@ def main():
         res["gemm"] = bench_gemm(timer, pk)
     if "attn" in what:
         res["attn"] = bench_attention(timer, pk)
+    if "attn_tp" in what:
+        res["attn_tp"] = bench_attention_tp_shapes(timer, pk)
     if "attn8" in what:
         res["attn8"] = bench_attention_one_byte(timer, pk)
     if "misc" in what:
