@@ -411,7 +411,7 @@ static int launch_rope_kv_append_q8(void* qkv, const int* positions, const int* 
                                     float* scales, int kv_format, int tokens, int hq, int hkv, int d, int rotary_dim,
                                     int interleaved, int page_size, int64_t num_slots, int max_pos, int* status, void* stream) {
   if (tokens <= 0) return 0;
-  if (d % 8 || rotary_dim % 2 || rotary_dim > d || (kv_format != 0 && kv_format != 1)) return -3;
+  if (d % 8 || rotary_dim % 2 || rotary_dim > d || kv_format < 0 || kv_format > 2) return -3;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   rope_kv_append_kernel<false><<<tokens, 256, 0, st>>>(static_cast<__nv_bfloat16*>(qkv), positions, slots, cos_sin, nullptr,
                                                       nullptr, hq, hkv, d, rotary_dim, interleaved, page_size, num_slots,
@@ -427,7 +427,7 @@ extern "C" int ogb_rope_kv_append_fp8(void* qkv, const int* positions, const int
   return launch_rope_kv_append_q8(qkv, positions, slots, cos_sin, pool, scales, 0, tokens, hq, hkv, d, rotary_dim, interleaved,
                                   page_size, num_slots, max_pos, status, stream);
 }
-// kv_format 0 = e4m3, 1 = int8; same pool and scale layout
+// kv_format 0 = e4m3, 1 = int8, 2 = e5m2; same pool and scale layout
 extern "C" int ogb_rope_kv_append_q8(void* qkv, const int* positions, const int* slots, const float* cos_sin, void* pool,
                                      float* scales, int kv_format, int tokens, int hq, int hkv, int d, int rotary_dim,
                                      int interleaved, int page_size, int64_t num_slots, int max_pos, int* status,
