@@ -584,6 +584,15 @@ def cmd_validate(args, profiler):
                         problems.append(f"layer {li} {name}: scales have {one.scales.numel()} entries, expected {one.q.shape[0] * kb}")
     except Exception as exc:
         problems.append(f"graph: {exc}")
+    try:   # well-formedness: single assignment, defined inputs, no cycle, operator arity and attribute kinds
+        from .package import onnx_checker as ck
+
+        found = ck.check_model(load_any(d.model_path))
+        problems.extend(f"checker: {p}" for p in ck.errors(found))
+        warn = [p for p in found if p.severity == "warning"]
+        notes.append(f"checker: {len(found) - len(warn)} errors, {len(warn)} warnings" + (f" (first: {warn[0]})" if warn else ""))
+    except Exception as exc:
+        notes.append(f"checker skipped: {exc}")
     try:   # static shapes: what resolves without running the graph, and what the graph's declared outputs disagree with
         from .package import shape_inference as si
 
