@@ -1,0 +1,342 @@
+// Weight-only int4 GEMM on the 5th-generation tensor cores: C[M, N] = A[M, K] (bf16) x dequant(W)[N, K]^T (+ bias), W in
+// the MatMulNBits layout (block 32: 16 bytes of nibbles per block, one scale per block, optional packed 4-bit zero
+// points).  The weights cross HBM as int4 and never exist in bf16 outside shared memory:
+//
+//   warp 0        TMA producer: the A tile(s) of each k-block (128-byte swizzle) into the stage ring
+//   warp 1        MMA issuer and TMEM owner: tcgen05.mma kind::f16, fp32 accumulators in TMEM, double-buffered
+//   warps 2..5    epilogue: tcgen05.ld -> (+ bias) -> bf16 -> staged in shared memory -> coalesced 16-byte stores
+//   warps 6..13   dequantisers: each thread owns one 32-weight block of the stage's B tile (128 rows x 64 k): a 16-byte
+//                 load two iterations ahead, nibble -> bf16 through the 0x4300 mantissa trick (128 + n, exact), minus
+//                 (128 + zero point), times the scale as bf16x2, stored in the same swizzled K-major layout a TMA load
+//                 of a bf16 tile would have produced, then a proxy fence and one arrival per warp on the stage's barrier
+//
+// A work item is MT 128-row tiles of A against one 128-column tile of W, so with MT = 2 one dequantised B tile feeds
+// two accumulators and the ALU work per MMA halves; MT = 1 serves M <= 128, where the kernel is bound by the int4
+// stream.  It is the counterpart of the reference's Marlin-style kernel
+// (crates/onnx-runtime-ep-cuda/src/kernels/marlin_gemm.rs: int4 tiles dequantised in registers in front of mma.sync).
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "attention_common.cuh"
+#include "common.cuh"
+#include "ogb_kernels.h"
+
+namespace ogb {
+
+constexpr int kWTile = 128;                 // rows of an A tile, columns of a W tile
+constexpr int kWBK = 64;                    // k per stage: one 128-byte swizzle row of bf16
+constexpr int kWDequantWarps = 8;
+constexpr int kWThreads = (2 + 4 + kWDequantWarps) * 32;
+constexpr int kWStagePitch = 272;           // epilogue staging: 128 bf16 + 16 bytes, conflict-free for 16-byte accesses
+constexpr int kWStageWarpBytes = 32 * kWStagePitch;
+
+template <int MT>
+struct W4Cfg {
+  static constexpr int kStageA = MT * kWTile * kWBK * 2;
+  static constexpr int kStageB = kWTile * kWBK * 2;
+  static constexpr int kStage = kStageA + kStageB;
+  static constexpr int kStages = MT == 2 ? 4 : 6;
+  static constexpr int kAccCols = MT * kWTile;          // TMEM columns of one accumulator set
+  static constexpr int kTmemCols = 2 * kAccCols;        // 256 or 512: a power of two
+  static constexpr int kSmemBytes = kStages * kStage + 256 + 4 * kWStageWarpBytes;
+};
+
+// 8 nibbles of `w` (k order: low nibble of byte 0 first) -> 4 bf16x2 words in k order, each (nibble - zero) * scale.
+// prmt lines the nibbles up so that one mask yields the two neighbours of a pair in the two 16-bit halves.
+OGB_DEVICE void dequant_word(uint32_t w, __nv_bfloat162 zz, __nv_bfloat162 ss, uint32_t (&out)[4]) {
+  const uint32_t w4 = w >> 4;
+  uint32_t x, y;
+  asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(x) : "r"(w), "r"(w4));   // bytes (n0 n1) (n2 n3) | (n1 n2) (n3 n4)
+  asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(y) : "r"(w), "r"(w4));   // bytes (n4 n5) (n6 n7) | (n5 n6) (n7 0)
+  const uint32_t p[4] = {(x & 0x000F000Fu) | 0x43004300u, ((x >> 8) & 0x000F000Fu) | 0x43004300u,
+                         (y & 0x000F000Fu) | 0x43004300u, ((y >> 8) & 0x000F000Fu) | 0x43004300u};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 v = __hmul2(__hsub2(*reinterpret_cast<const __nv_bfloat162*>(&p[i]), zz), ss);   // the subtraction is exact
+    out[i] = *reinterpret_cast<const uint32_t*>(&v);
+  }
+}
+
+struct W4Unit {
+  uint4 q;
+  __nv_bfloat162 ss, zz;
+};
+
+template <int MT, bool SF32>
+__global__ void __launch_bounds__(kWThreads, 1)
+gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t* __restrict__ qw, const void* __restrict__ scales,
+                          const uint8_t* __restrict__ zp, const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ C,
+                          int M, int N, int K, int ldc, int* status) {
+  using Cfg = W4Cfg<MT>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStage);
+  uint8_t* staging = smem + Cfg::kStages * Cfg::kStage + 256;
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + Cfg::kStages;
+  uint64_t* tmem_full = bars + 2 * Cfg::kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_tiles = (M + MT * kWTile - 1) / (MT * kWTile);
+  const int n_tiles = (N + kWTile - 1) / kWTile;
+  const int num_tiles = m_tiles * n_tiles;
+  const int k_blocks = (K + kWBK - 1) / kWBK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < Cfg::kStages; ++i) {
+      mbar_init(&full_bar[i], 1 + kWDequantWarps);   // the producer's arrive.expect_tx + one arrival per dequantiser warp
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (A) ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * (MT * kWTile);
+        const int mt_here = (MT == 2 && m0 + kWTile < M) ? 2 : 1;     // a second tile wholly past M is neither loaded nor multiplied
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; break; }
+          uint8_t* sa = smem + stage * Cfg::kStage;
+          mbar_expect_tx(&full_bar[stage], static_cast<uint32_t>(mt_here * kWTile * kWBK * 2));
+          for (int mi = 0; mi < mt_here; ++mi)
+            tma_load_2d(sa + mi * (kWTile * kWBK * 2), &tmap_a, &full_bar[stage], kb * kWBK, m0 + mi * kWTile);
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) { atomicOr(status, kStatusWaitTimeout); *abort_flag = 1; }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(kWTile, kWTile);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
+        const int m0 = (tile % m_tiles) * (MT * kWTile);
+        const int mt_here = (MT == 2 && m0 + kWTile < M) ? 2 : 1;
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_addr = tmem_base + acc * Cfg::kAccCols;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::kStage);
+          const uint64_t db = make_kmajor_sw128_desc(sa + Cfg::kStageA);
+          for (int mi = 0; mi < mt_here; ++mi) {
+            const uint64_t da = make_kmajor_sw128_desc(sa + mi * (kWTile * kWBK * 2));
+#pragma unroll
+            for (int k = 0; k < kWBK / 16; ++k)
+              umma_f16(d_addr + mi * kWTile, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&tmem_full[acc]);
+      }
+      if (!ok) { atomicOr(status, kStatusWaitTimeout); *abort_flag = 1; }
+    }
+  } else if (warp < 6) {
+    // ------------------------------ epilogue ------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    bool ok = true;
+    int it = 0;
+    uint8_t* stg = staging + (warp - 2) * kWStageWarpBytes;
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const int m0 = (tile % m_tiles) * (MT * kWTile);
+      const int mt_here = (MT == 2 && m0 + kWTile < M) ? 2 : 1;
+      const int n0 = (tile / m_tiles) * kWTile;
+      if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full[acc], acc_phase))) { ok = false; break; }
+      tc_fence_after();
+      for (int mi = 0; mi < mt_here; ++mi) {
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * Cfg::kAccCols + mi * kWTile;
+        const int row0 = m0 + mi * kWTile + q * 32;
+        // phase 1 (thread = row): TMEM -> registers -> + bias -> bf16 into this warp's staging slab
+#pragma unroll 1
+        for (int c = 0; c < kWTile / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c * 32, r);
+          tmem_ld_wait();
+          const int col = n0 + c * 32;
+          if (bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col + j < N) r[j] = __float_as_uint(__uint_as_float(r[j]) + __bfloat162float(__ldg(bias + col + j)));
+          }
+          uint4* srow = reinterpret_cast<uint4*>(stg + lane * kWStagePitch + c * 64);
+#pragma unroll
+          for (int v = 0; v < 4; ++v)
+            srow[v] = make_uint4(pack_bf16(__uint_as_float(r[8 * v]), __uint_as_float(r[8 * v + 1])),
+                                 pack_bf16(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3])),
+                                 pack_bf16(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5])),
+                                 pack_bf16(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7])));
+        }
+        __syncwarp();
+        // phase 2 (16 lanes along a row): two rows per pass, 256-byte row segments per warp instruction
+        const int ch = lane & 15;
+        const int gcol = n0 + ch * 8;
+#pragma unroll 4
+        for (int rb = 0; rb < 32; rb += 2) {
+          const int r_loc = rb + (lane >> 4);
+          const int grow = row0 + r_loc;
+          if (grow < M && gcol < N) {
+            const uint4 v = *reinterpret_cast<const uint4*>(stg + r_loc * kWStagePitch + ch * 16);
+            __nv_bfloat16* dst = C + static_cast<size_t>(grow) * ldc + gcol;
+            if (gcol + 8 <= N) {
+              *reinterpret_cast<uint4*>(dst) = v;
+            } else {
+              const __nv_bfloat16* pv = reinterpret_cast<const __nv_bfloat16*>(&v);
+              for (int j = 0; j < 8 && gcol + j < N; ++j) dst[j] = pv[j];
+            }
+          }
+        }
+        __syncwarp();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+    }
+    if (!ok && lane == 0) { atomicOr(status, kStatusWaitTimeout); *abort_flag = 1; }
+  } else {
+    // ------------------------------ dequantisers (B) ------------------------------
+    const int u = (warp - 6) * 32 + lane;          // 0..255: one 32-weight block of the stage's B tile each
+    const int r_tile = u >> 1;                     // row of the tile; the two lanes of a pair share a 32-byte sector
+    const int half = u & 1;                        // which 32-k block of the stage's 64 k
+    const int kb32 = (K + 31) / 32;
+    const int zp_stride = (kb32 + 1) / 2;
+    const int my_tiles = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const long long iters = static_cast<long long>(my_tiles) * k_blocks;
+    auto fetch = [&](long long j, W4Unit& un) {
+      un.q = make_uint4(0, 0, 0, 0);
+      float s = 0.f;
+      int z = 8;
+      if (j < iters) {
+        const int tile = blockIdx.x + static_cast<int>(j / k_blocks) * gridDim.x;
+        const int n = (tile / m_tiles) * kWTile + r_tile;
+        const int b = static_cast<int>(j % k_blocks) * 2 + half;
+        if (n < N && b < kb32) {
+          const size_t blk = static_cast<size_t>(n) * kb32 + b;
+          un.q = __ldg(reinterpret_cast<const uint4*>(qw) + blk);
+          if constexpr (SF32) s = __ldg(static_cast<const float*>(scales) + blk);
+          else s = __bfloat162float(__ldg(static_cast<const __nv_bfloat16*>(scales) + blk));
+          if (zp != nullptr) {
+            const uint8_t zb = __ldg(zp + static_cast<size_t>(n) * zp_stride + (b >> 1));
+            z = (b & 1) ? (zb >> 4) : (zb & 0xF);
+          }
+        }
+      }
+      un.ss = __float2bfloat162_rn(s);
+      un.zz = __float2bfloat162_rn(static_cast<float>(128 + z));
+    };
+    W4Unit u0, u1;
+    fetch(0, u0);
+    fetch(1, u1);
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    const uint32_t row_off = static_cast<uint32_t>(r_tile) * 128u;
+    const uint32_t sw = static_cast<uint32_t>(r_tile & 7);
+    for (long long j = 0; j < iters; ++j) {
+      W4Unit u2;
+      fetch(j + 2, u2);
+      if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[stage], phase ^ 1))) { ok = false; break; }
+      uint8_t* sb = smem + stage * Cfg::kStage + Cfg::kStageA + row_off;
+      const uint32_t words[4] = {u0.q.x, u0.q.y, u0.q.z, u0.q.w};
+#pragma unroll
+      for (int wi = 0; wi < 4; ++wi) {
+        uint32_t o[4];
+        dequant_word(words[wi], u0.zz, u0.ss, o);
+        const uint32_t chunk = static_cast<uint32_t>(half * 4 + wi) ^ sw;       // 128-byte swizzle: 16-byte chunk index XOR row mod 8
+        *reinterpret_cast<uint4*>(sb + chunk * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+      fence_proxy_async_smem();      // the tensor core reads these bytes through the async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full_bar[stage]);
+      u0 = u1;
+      u1 = u2;
+      if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+    }
+    if (!ok && lane == 0) { atomicOr(status, kStatusWaitTimeout); *abort_flag = 1; }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0 && threadIdx.x == 0) {
+    // A wait ran out: give copies that may still be in flight a bounded time to land.
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) { __nanosleep(1000); }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+template <int MT, bool SF32>
+static int launch_w4a16_gemm(const void* x, const void* qweight, const void* scales, const void* zp, const void* bias, void* out,
+                             int M, int N, int K, int ldx, int ldc, int* status, cudaStream_t stream) {
+  using Cfg = W4Cfg<MT>;
+  CUtensorMap ta;
+  const int rc = make_tmap_bf16_2d(&ta, x, M, K, ldx, kWTile, kWBK);
+  if (rc != 0) return rc;
+  static bool attr_set = false;
+  if (!attr_set) {
+    OGB_CUDA_CHECK(cudaFuncSetAttribute(gemm_w4a16_tcgen05_kernel<MT, SF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    attr_set = true;
+  }
+  const int tiles = ((M + MT * kWTile - 1) / (MT * kWTile)) * ((N + kWTile - 1) / kWTile);
+  const int grid = tiles < ogb_num_sms() ? tiles : ogb_num_sms();
+  gemm_w4a16_tcgen05_kernel<MT, SF32><<<grid, kWThreads, Cfg::kSmemBytes, stream>>>(
+      ta, static_cast<const uint8_t*>(qweight), scales, static_cast<const uint8_t*>(zp), static_cast<const __nv_bfloat16*>(bias),
+      static_cast<__nv_bfloat16*>(out), M, N, K, ldc, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace ogb
+
+using namespace ogb;
+
+// out[M, N] (bf16, row stride ldc) = x[M, K] (bf16, row stride ldx) * dequant(qweight)[N, K]^T (+ bias).  qweight is
+// [N, K/32, 16] bytes, scales [N, K/32] fp32 (scales_f32 = 1) or bf16, zp packed nibbles [N, ceil(K/32 / 2)] or null
+// (zero point 8).  K must be a multiple of 32; x and out 16-byte aligned with ldx, ldc multiples of 8.
+extern "C" int ogb_w4a16_gemm(const void* x, const void* qweight, const void* scales, const void* zp, const void* bias, void* out,
+                              int M, int N, int K, int ldx, int ldc, int scales_f32, int* status, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K % 32) != 0 || (ldx % 8) != 0 || (ldc % 8) != 0) return -3;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(qweight)) & 15) return -4;
+  if (M > kWTile) {
+    return scales_f32 ? launch_w4a16_gemm<2, true>(x, qweight, scales, zp, bias, out, M, N, K, ldx, ldc, status, stream)
+                      : launch_w4a16_gemm<2, false>(x, qweight, scales, zp, bias, out, M, N, K, ldx, ldc, status, stream);
+  }
+  return scales_f32 ? launch_w4a16_gemm<1, true>(x, qweight, scales, zp, bias, out, M, N, K, ldx, ldc, status, stream)
+                    : launch_w4a16_gemm<1, false>(x, qweight, scales, zp, bias, out, M, N, K, ldx, ldc, status, stream);
+}

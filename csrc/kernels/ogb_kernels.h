@@ -123,6 +123,28 @@ int ogb_w4a16_gemv_fused(const void* x, const void* qweight, const void* scales,
                          float eps, int prologue, int scales_fp32, void* stream);
 int ogb_w4a16_dequant(const void* qweight, const void* scales, const void* zp, void* w_bf16, int N, int K,
                       int scales_fp32, void* stream);
+// The same product for any M on the tensor cores: int4 tiles are dequantised to bf16 in shared memory in front of
+// tcgen05.mma, so no bf16 copy of the weights exists.  K a multiple of 32; ldx, ldc multiples of 8.
+int ogb_w4a16_gemm(const void* x, const void* qweight, const void* scales, const void* zp, const void* bias, void* out,
+                   int M, int N, int K, int ldx, int ldc, int scales_fp32, int* status, void* stream);
+
+// Operators of hybrid and sparse decoders (fp32 math; dtype 0 = fp32, 1 = bf16, 2 = fp16; all tensors contiguous).
+// Linear attention: q [B,T,Hq*dk], k [B,T,Nk*dk], v [B,T,Hkv*dv], past / state_out [B,Hkv,dk,dv], decay [B,T,Hkv] or
+// [B,T,Hkv*dk] (log decay), beta [B,T,Hkv] or [B,T,1]; out [B,T,max(Hq,Hkv)*dv].  Returns -2 for key widths other than 32, 64, 128.
+int ogb_linear_attention(const void* q, const void* k, const void* v, const void* past, const void* decay, const void* beta,
+                         void* out, void* state_out, int B, int T, int Hq, int Nk, int Hkv, int dk, int dv, int decay_per_dim,
+                         int beta_heads, int use_decay, int use_delta, float scale, int dtype, void* stream);
+// Depthwise causal convolution over concat(past, x): x / y [B,C,L], w [C,K], past / state_out [B,C,K-1].
+int ogb_causal_conv_state(const void* x, const void* w, const void* bias, const void* past, void* y, void* state_out, int B,
+                          int C, int L, int K, int silu, int dtype, void* stream);
+// Attention of each query row over the positions listed for it: q / out [B,N,Sq,D], k / v [B,Nkv,total,D], sel int64
+// [B, sel_heads (1 or N), Sq, Ksel] increasing with -1 as trailing padding, bias with four element strides or NULL.
+int ogb_index_share_attention(const void* q, const void* k, const void* v, const void* sel, const void* bias, void* out, int B,
+                              int N, int Nkv, int Sq, int total, int D, int Ksel, int sel_heads, const long long* bias_strides,
+                              float scale, int dtype, int* status, void* stream);
+// cache [B,G,C,row] and int64 idx [B,G,Q,K] -> out [B,G,Q,K,row]; an index outside the row's valid length sets the status word.
+int ogb_sparse_kv_gather(const void* cache, const void* idx, const void* lengths, void* out, int B, int G, int C, int Q, int K,
+                         int row_bytes, int* status, void* stream);
 
 // MoE: softmax router with top-k (renormalised), device-side permutation by expert, grouped GEMM, combine.
 int ogb_moe_route_topk(const void* router_logits, int* topk_ids, float* topk_w, int tokens, int experts, int k,

@@ -277,6 +277,36 @@ def bench_w4a16(timer, pk):
     return rows
 
 
+def bench_w4a16_gemm(timer, pk):
+    """The int4 tensor-core GEMM (B tiles dequantised in shared memory) at batch sizes above the GEMV range, beside the bf16
+    GEMM over a dequantised copy of the same weights: time, FLOP rate against the measured cuBLAS bf16 rate, int4 bytes
+    streamed against the measured copy bandwidth, and the device bytes each arm keeps per projection."""
+    from onnx_genai_b200.ops.quant import QuantLinear
+
+    rows = []
+    for name, n_, k_ in (("7b_gate_up", 37888, 3584), ("7b_down", 3584, 18944), ("7b_qkv", 4608, 3584)):
+        q = torch.randint(0, 256, (n_, k_ // 32, 16), dtype=torch.uint8)
+        sc = (torch.rand(n_, k_ // 32) * 0.02 + 0.005).bfloat16()
+        lin = QuantLinear(q, sc, None, None, k=k_, device="cuda")
+        dense = QuantLinear(q, sc, None, None, k=k_, device="cuda")
+        dense.large_m = "dense"
+        nbytes = n_ * k_ // 2 + n_ * (k_ // 32) * 2
+        for m in (16, 64, 128, 256, 1024, 2048):
+            x = (torch.randn(m, k_, device="cuda") * 0.3).bfloat16()
+            out = torch.empty(m, n_, device="cuda", dtype=torch.bfloat16)
+            dense(x, out=out)                               # builds the copy outside the timed region
+            t_int4, _ = timer.time(lambda: lin(x, out=out))
+            t_dense, _ = timer.time(lambda: dense(x, out=out))
+            fl = 2.0 * m * n_ * k_
+            rows.append({"kernel": "gemm_w4a16_tcgen05", "case": name, "m": m, "n": n_, "k": k_, "ms": round(t_int4, 4),
+                         "tflops": round(fl / t_int4 / 1e9, 1), "frac_of_measured_bf16": round(fl / t_int4 / 1e9 / pk["bf16_tflops"], 3),
+                         "int4_gbs": round(nbytes / t_int4 / 1e6, 1), "frac_of_measured_hbm": round(nbytes / t_int4 / 1e6 / pk["hbm_gbs"], 3),
+                         "bf16_copy_gemm_ms": round(t_dense, 4), "int4_over_bf16_time": round(t_int4 / t_dense, 2),
+                         "device_bytes_int4": lin.device_weight_bytes(), "device_bytes_bf16_copy": dense.device_weight_bytes()})
+            print(json.dumps(rows[-1]), flush=True)
+    return rows
+
+
 def ncu_case(name: str, iters: int = 3):
     """Small single-kernel workloads for `ncu` captures: inputs larger than L2 where DRAM figures matter,
     a few hundred MB on the device at most, `iters` launches of the one kernel of interest."""
@@ -295,6 +325,16 @@ def ncu_case(name: str, iters: int = 3):
                 ops.gemm(a, w, residual=res, epilogue="residual", out=out)
             else:
                 ops.gemm(a, w, out=out)
+    elif name in ("w4a16_gemm_m1024", "w4a16_gemm_m64"):
+        from onnx_genai_b200.ops.quant import QuantLinear
+
+        m, n, k = (1024 if name.endswith("1024") else 64), 37888, 3584
+        lin = QuantLinear(torch.randint(0, 256, (n, k // 32, 16), dtype=torch.uint8), (torch.rand(n, k // 32) * 0.02 + 0.005).bfloat16(),
+                          None, None, k=k, device="cuda")
+        x = (torch.randn(m, k, device="cuda") * 0.3).bfloat16()
+        out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        for _ in range(iters):
+            lin(x, out=out)
     elif name == "decode_step_0p5b_int4":
         # whole decode steps of the Qwen2.5-0.5B-shape int4 model at batch 1 (512-token prompt), launched one kernel
         # at a time so a launch list shows the device time of every kernel of a step
@@ -374,7 +414,7 @@ def ncu_case(name: str, iters: int = 3):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ncu-case", default="", help="run one small single-kernel workload (for ncu) and exit")
-    ap.add_argument("--what", default="gemm,attn,misc", help="comma list of gemm, attn, attn_tp (one rank's decode share at TP=4 / 8), attn8 (one-byte KV pages), misc, w4 (int4 decode projections)")
+    ap.add_argument("--what", default="gemm,attn,misc", help="comma list of gemm, attn, attn_tp (one rank's decode share at TP=4 / 8), attn8 (one-byte KV pages), misc, w4 (int4 decode projections), w4gemm (int4 tensor-core GEMM against the bf16 GEMM over a dequantised copy)")
     ap.add_argument("--json", default="")
     args = ap.parse_args()
     if args.ncu_case:
@@ -395,6 +435,8 @@ def main():
         res["misc"] = bench_misc(timer, pk)
     if "w4" in what:
         res["w4a16"] = bench_w4a16(timer, pk)
+    if "w4gemm" in what:
+        res["w4a16_gemm"] = bench_w4a16_gemm(timer, pk)
     if args.json:
         Path(args.json).write_text(json.dumps(res, indent=1))
 

@@ -1,5 +1,5 @@
-"""MatMulNBits int4 projections on the GPU: GEMV with in-kernel dequant for decode-sized M, dequant +
-tcgen05 GEMM above that.  CPU tensors use the C++ block-wise kernel (ops.cpu), or the fp32 statement in
+"""MatMulNBits int4 projections on the GPU: GEMV with in-kernel dequant for decode-sized M, above that a tcgen05
+GEMM whose B tiles are dequantised in shared memory (the weights stay int4 in device memory).  CPU tensors use the C++ block-wise kernel (ops.cpu), or the fp32 statement in
 ops.reference when the runtime library is not built."""
 from __future__ import annotations
 
@@ -9,9 +9,10 @@ from . import _native, launch_counts, reference, status_word, timed_region
 from . import gemm as _gemm
 
 GEMV_MAX_M = 8          # rows the GEMV kernels accept
-FUSED_MAX_M = 4         # above this the cached-bf16 tcgen05 GEMM is faster than the row-specialised GEMV (measured: 8 rows 2.2 ms/step vs 16 rows 2.1 ms/step on the 0.5B shape)
+FUSED_MAX_M = 4         # above this the tensor-core GEMM is faster than the row-specialised GEMV (measured: 8 rows 2.2 ms/step vs 16 rows 2.1 ms/step on the 0.5B shape)
 _native.register("ogb_w4a16_gemv", [_native.P] * 6 + [_native.I] * 6 + [_native.P])
 _native.register("ogb_w4a16_dequant", [_native.P] * 4 + [_native.I] * 3 + [_native.P])
+_native.register("ogb_w4a16_gemm", [_native.P] * 6 + [_native.I] * 6 + [_native.P] * 2)
 _native.register("ogb_w4a16_gemv_fused", [_native.P] * 8 + [_native.I] * 6 + [_native.F] + [_native.I] * 2 + [_native.P])
 PRO_NONE, PRO_RMSNORM, PRO_SILU_MUL = 0, 1, 2
 _LEGACY_GEMV = __import__("os").environ.get("OGB_W4A16_LEGACY", "0") == "1"   # A/B switch: the unspecialised 8-row GEMV
@@ -32,11 +33,10 @@ class QuantLinear:
         self.bias = bias.to(torch.bfloat16).contiguous().to(dev) if bias is not None else None
         self._scratch = None
 
-    # Above the GEMV range the tcgen05 GEMM needs bf16 weights.  With cache_dense the dequantised copy is
-    # built once per projection and kept (a one-time repack, as the reference keeps its interleaved-weight
-    # cache, crates/onnx-runtime-ep-cuda/src/interleave_cache.rs); without it the copy is rebuilt into a
-    # scratch buffer on every call, which costs a full weight write + read per step.
-    cache_dense = True
+    # "int4": the tensor-core GEMM with in-kernel dequant (device memory holds the int4 weights only).  "dense": the
+    # earlier path, a bf16 copy of the weights built once per projection and multiplied by the bf16 GEMM; kept as the
+    # A/B arm of the kernel benchmark (4x the weight bytes).
+    large_m = __import__("os").environ.get("OGB_W4A16_LARGE_M", "int4")
 
     @classmethod
     def merge(cls, parts):
@@ -110,13 +110,28 @@ class QuantLinear:
             _native.check(rc, "ogb_w4a16_gemv")
             launch_counts["w4a16_gemv"] += 1
             return out
-        if self._scratch is not None and self.cache_dense:
-            return _gemm(x, self._scratch, bias=self.bias, out=out)
+        if self.large_m == "int4" and self.k % 32 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and out.stride(0) % 8 == 0:
+            with timed_region("w4a16_gemm"):
+                rc = lib.ogb_w4a16_gemm(x.data_ptr(), self.qweight.data_ptr(), self.scales.data_ptr(),
+                                        self.zp.data_ptr() if self.zp is not None else 0,
+                                        self.bias.data_ptr() if self.bias is not None else 0, out.data_ptr(), m, self.n, self.k,
+                                        x.stride(0), out.stride(0), int(self.scales_fp32), status_word(x.device).data_ptr(), stream)
+            _native.check(rc, "ogb_w4a16_gemm")
+            launch_counts["w4a16_gemm"] += 1
+            return out
         if self._scratch is None:
             self._scratch = torch.empty(self.n, self.k, dtype=torch.bfloat16, device=x.device)
-        with timed_region("w4a16_dequant"):
-            rc = lib.ogb_w4a16_dequant(self.qweight.data_ptr(), self.scales.data_ptr(), self.zp.data_ptr() if self.zp is not None else 0,
-                                       self._scratch.data_ptr(), self.n, self.k, int(self.scales_fp32), stream)
-        _native.check(rc, "ogb_w4a16_dequant")
-        launch_counts["w4a16_dequant"] += 1
+            with timed_region("w4a16_dequant"):
+                rc = lib.ogb_w4a16_dequant(self.qweight.data_ptr(), self.scales.data_ptr(), self.zp.data_ptr() if self.zp is not None else 0,
+                                           self._scratch.data_ptr(), self.n, self.k, int(self.scales_fp32), stream)
+            _native.check(rc, "ogb_w4a16_dequant")
+            launch_counts["w4a16_dequant"] += 1
         return _gemm(x, self._scratch, bias=self.bias, out=out)
+
+    def device_weight_bytes(self) -> int:
+        """Bytes this projection holds in device memory (int4 weights, scales, zero points, bias and, on the dense path, the bf16 copy)."""
+        n = self.qweight.numel() + self.scales.numel() * self.scales.element_size()
+        n += self.zp.numel() if self.zp is not None else 0
+        n += self.bias.numel() * 2 if self.bias is not None else 0
+        n += self._scratch.numel() * 2 if self._scratch is not None else 0
+        return n

@@ -497,6 +497,13 @@ def _index_share(ins, attrs):
             raise GraphExecutionError("IndexShare: -1 may only pad the end of a row of selected_indices")
         if bool((valid[..., 1:] & (sel[..., 1:] <= sel[..., :-1])).any()):
             raise GraphExecutionError("IndexShare: selected indices must be strictly increasing")
+    scale = float(attrs.get("scale", 0.0)) or q.shape[-1] ** -0.5
+    if q.is_cuda:                                       # one warp per query row walks its selected positions (online softmax)
+        from ..ops import sequence as _seq
+
+        got = _seq.index_share_attention(q, k.to(q.dtype), v.to(q.dtype), sel, extra.to(q.dtype) if extra is not None else None, scale)
+        if got is not None:
+            return [got, k, v]
     chosen = torch.zeros(b, sel.shape[1], sq, total + 1, dtype=torch.bool, device=q.device)
     chosen.scatter_(3, torch.where(valid, sel, torch.full_like(sel, total)), True)
     chosen = chosen[..., :total]

@@ -42,6 +42,13 @@ def _linear_attention(ins, attrs):
     if (use_decay and decay is None) or (use_delta and beta is None):
         raise GraphExecutionError(f"LinearAttention: update_rule {rule!r} needs its gate input")
     scale = float(attrs.get("scale", 0.0)) or dk ** -0.5
+    if ins[0].is_cuda:                                  # the recurrent kernel: one state column per thread, fp32 state in registers
+        from ..ops import sequence as _seq
+
+        same = lambda x: x.to(ins[0].dtype) if x is not None else None
+        got = _seq.linear_attention(ins[0], same(ins[1]), same(ins[2]), same(past), same(decay), same(beta), hq, hkv, rule, scale)
+        if got is not None:
+            return [got[0], got[1]]
     qh = q.reshape(b, t, hq, dk)
     kh = k.reshape(b, t, nk, dk).repeat_interleave(hkv // nk, dim=2)                      # [B, T, Hkv, dk]
     vh = v.reshape(b, t, hkv, dv)
@@ -77,6 +84,14 @@ def _causal_conv_with_state(ins, attrs):
     if int(attrs.get("ndim", 1)) != 1 or x.dim() != 3 or w.dim() != 3 or w.shape[1] != 1:
         raise GraphExecutionError("CausalConvWithState is covered for ndim=1: x [B, C, L] with a depthwise weight [C, 1, K]")
     k = w.shape[2]
+    act = attrs.get("activation", "none") or "none"
+    if x.is_cuda and act in ("none", "silu", "swish"):
+        from ..ops import sequence as _seq
+
+        same = lambda t: t.to(x.dtype) if t is not None else None
+        got = _seq.causal_conv_state(x, same(w), same(bias), same(past), act != "none")
+        if got is not None:
+            return [got[0], got[1]]
     if past is None:
         past = torch.zeros(x.shape[0], x.shape[1], k - 1, dtype=x.dtype, device=x.device)
     seq = torch.cat([past.float(), x.float()], dim=2)
@@ -252,6 +267,12 @@ def _sparse_kv_gather(ins, attrs):
         where = [int(v) for v in bad.nonzero()[0].tolist()]
         raise GraphExecutionError(f"SparseKvGather: index {int(idx[tuple(where)])} at {where} lies outside the {int(limit[where[0]])} valid cache rows")
     b, g, q, k = idx.shape
+    if cache.is_cuda:
+        from ..ops import sequence as _seq
+
+        got = _seq.sparse_kv_gather(cache, idx, lengths)       # the indices were checked above; the kernel checks them again
+        if got is not None:
+            return got
     picked = torch.gather(cache, 2, idx.reshape(b, g, q * k, 1).expand(b, g, q * k, cache.shape[3]))
     return picked.reshape(b, g, q, k, cache.shape[3])
 

@@ -311,7 +311,9 @@ def test_kv_page_utils():
 
 
 @pytest.mark.parametrize("m,n,k,sym,fp32_scales", [(1, 896, 896, True, False), (3, 1152, 896, False, True), (8, 896, 4864, True, False),
-                                                   (5, 100, 688, False, False), (40, 1152, 896, True, False)])
+                                                   (5, 100, 688, False, False), (40, 1152, 896, True, False),
+                                                   (16, 1152, 896, False, True), (128, 896, 4864, True, False),
+                                                   (1024, 1000, 1760, False, False), (300, 3584, 3584, True, True)])
 def test_w4a16_linear(m, n, k, sym, fp32_scales):
     from onnx_genai_b200.ops.quant import QuantLinear
 
@@ -328,7 +330,30 @@ def test_w4a16_linear(m, n, k, sym, fp32_scales):
     ops.check_status()
     want = x.float().cpu() @ ref.dequant_w4(q, s.float(), zp, 32, k).t() + bias.bfloat16().float()
     assert _rel_err(got.cpu(), want) < 1.2e-2
-    assert ops.launch_counts["w4a16_gemv_fused" if m <= 4 else ("w4a16_gemv" if (m <= 8 and n % 32) else "w4a16_dequant")] > 0
+    assert ops.launch_counts["w4a16_gemv_fused" if m <= 4 else ("w4a16_gemv" if (m <= 8 and n % 32) else "w4a16_gemm")] > 0
+    assert lin._scratch is None                        # no bf16 copy of the weights exists
+
+
+def test_w4a16_gemm_strided_output_matches_the_dense_arm():
+    """The int4 tensor-core GEMM writes a column slice of a wider buffer and nothing else, and agrees with the bf16 GEMM
+    over a dequantised copy of the same weights (the A/B arm) to bf16 rounding of the weights."""
+    from onnx_genai_b200.ops.quant import QuantLinear
+
+    torch.manual_seed(17)
+    m, n, k = 200, 640, 1024
+    q, s, zp = ref.quantize_w4(torch.randn(n, k) * 0.05, 32, symmetric=False)
+    lin = QuantLinear(q, s.bfloat16(), zp, None, k=k, device=DEV)
+    x = (torch.randn(m, k, device=DEV) * 0.5).bfloat16()
+    wide = torch.zeros(m, n + 128, device=DEV, dtype=torch.bfloat16)
+    lin(x, out=wide[:, 64:64 + n])
+    assert float(wide[:, :64].abs().max()) == 0 and float(wide[:, 64 + n:].abs().max()) == 0
+    dense = QuantLinear(q, s.bfloat16(), zp, None, k=k, device=DEV)
+    dense.large_m = "dense"
+    want = dense(x)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert dense._scratch is not None and dense.device_weight_bytes() > 4 * lin.device_weight_bytes() * 0.9
+    assert _rel_err(wide[:, 64:64 + n].float().cpu(), want.float().cpu()) < 4e-3
 
 
 @pytest.mark.parametrize("m,n,k,sym", [(1, 896, 896, True), (2, 1152, 896, False), (4, 128, 4864, True), (7, 100, 688, False), (8, 64, 9000, True)])

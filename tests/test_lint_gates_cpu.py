@@ -32,6 +32,8 @@ def _sources(exts, roots=("onnx_genai_b200", "csrc", "tests", "examples")):
 def test_every_kernel_entry_point_in_the_header_is_bound_with_the_same_arity():
     from onnx_genai_b200.ops import _native
     import onnx_genai_b200.ops.moe  # noqa: F401  (registers its entry points)
+    import onnx_genai_b200.ops.quant  # noqa: F401
+    import onnx_genai_b200.ops.sequence  # noqa: F401
     import onnx_genai_b200.utils.vmm  # noqa: F401
 
     header = _read(os.path.join(ROOT, "csrc", "kernels", "ogb_kernels.h"))
@@ -48,7 +50,7 @@ def test_every_kernel_entry_point_in_the_header_is_bound_with_the_same_arity():
     assert not arity, f"ctypes argument count differs from the header: {arity}"
     # entry points that only the C++ step executor calls, or that parallel/fused.py binds when a group forms, are not in
     # the table; everything else must be
-    internal = {m for m in missing if m.startswith(("ogb_decoder_", "ogb_ipc_", "ogb_tp_", "ogb_moe_", "ogb_w4a16_", "ogb_cpu_"))
+    internal = {m for m in missing if m.startswith(("ogb_decoder_", "ogb_ipc_", "ogb_tp_", "ogb_moe_", "ogb_cpu_"))
                 or m == "ogb_gemm_bf16_scatter"}
     assert set(missing) - internal == set(), sorted(set(missing) - internal)
 
