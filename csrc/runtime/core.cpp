@@ -712,6 +712,24 @@ int64_t Core::fork(int64_t seq_id) {
   return id;
 }
 
+bool Core::swap_state(int64_t a, int64_t b) {
+  Sequence* sa = find(a);
+  Sequence* sb = find(b);
+  if (!sa || !sb || a == b) return false;
+  std::swap(*sa, *sb);
+  std::swap(sa->id, sb->id);
+  std::swap(sa->arrival, sb->arrival);
+  for (Sequence* s : {sa, sb}) {          // queue membership follows the status each id now has
+    running_.erase(std::remove(running_.begin(), running_.end(), s->id), running_.end());
+    waiting_.erase(std::remove(waiting_.begin(), waiting_.end(), s->id), waiting_.end());
+    swapped_.erase(std::remove(swapped_.begin(), swapped_.end(), s->id), swapped_.end());
+    if (s->status == SeqStatus::Running) running_.push_back(s->id);
+    else if (s->status == SeqStatus::Waiting) waiting_.push_back(s->id);
+    else if (s->status == SeqStatus::Swapped) swapped_.push_back(s->id);
+  }
+  return true;
+}
+
 bool Core::rewind(int64_t seq_id, int new_len) {
   Sequence* s = find(seq_id);
   if (!s || new_len < 1 || new_len > static_cast<int>(s->tokens.size())) return false;
@@ -809,6 +827,11 @@ int Core::seq_len(int64_t seq_id) const {
   return s ? static_cast<int>(s->tokens.size()) : -1;
 }
 
+int Core::seq_computed(int64_t seq_id) const {
+  const Sequence* s = find(seq_id);
+  return s ? s->num_computed : -1;
+}
+
 int Core::seq_tokens(int64_t seq_id, int32_t* out, int cap) const {
   const Sequence* s = find(seq_id);
   if (!s) return -1;
@@ -885,6 +908,7 @@ int ogb_core_commit_step(void* h, const int32_t* sampled, int n, int64_t* ev_seq
 }
 int ogb_core_cancel(void* h, int64_t id) { return static_cast<Core*>(h)->cancel(id) ? 1 : 0; }
 int64_t ogb_core_fork(void* h, int64_t id) { return static_cast<Core*>(h)->fork(id); }
+int ogb_core_swap_state(void* h, int64_t a, int64_t b) { return static_cast<Core*>(h)->swap_state(a, b) ? 1 : 0; }
 int ogb_core_rewind(void* h, int64_t id, int new_len) { return static_cast<Core*>(h)->rewind(id, new_len) ? 1 : 0; }
 int ogb_core_set_draft(void* h, int64_t id, const int32_t* tokens, int k) {
   return static_cast<Core*>(h)->set_draft(id, tokens, k) ? 1 : 0;
@@ -901,6 +925,7 @@ int ogb_core_prefix_peek(void* h, const int32_t* tokens, int n, int32_t* out_pag
   return static_cast<Core*>(h)->prefix_peek(tokens, n, out_pages, cap);
 }
 int ogb_core_seq_len(void* h, int64_t id) { return static_cast<Core*>(h)->seq_len(id); }
+int ogb_core_seq_computed(void* h, int64_t id) { return static_cast<Core*>(h)->seq_computed(id); }
 int ogb_core_seq_tokens(void* h, int64_t id, int32_t* out, int cap) { return static_cast<Core*>(h)->seq_tokens(id, out, cap); }
 void ogb_core_release(void* h, int64_t id) { static_cast<Core*>(h)->release(id); }
 void ogb_core_add_pages(void* h, int n) { static_cast<Core*>(h)->add_pages(n); }

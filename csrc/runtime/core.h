@@ -159,6 +159,9 @@ class Core {
 
   // session-style operations on a live sequence
   int64_t fork(int64_t seq_id);                    // copy-on-write clone (shares pages)
+  // The two sequences exchange everything but their ids and arrival order (tokens, pages, progress, status); used between
+  // steps when a forked branch of a speculation tree won and the caller's id has to continue as that branch.
+  bool swap_state(int64_t a, int64_t b);
   bool rewind(int64_t seq_id, int new_len);
   // Sliding-window retention with attention sinks (the policy of crates/onnx-genai-kv/src/paged_cache.rs:483-585, kept
   // position-indexed instead of compacted): once a sequence has run `window` + slack tokens past a page, no later query
@@ -168,6 +171,7 @@ class Core {
   void set_window(int window, int sink_tokens);
   int released_pages(int64_t seq_id) const;        // drop trailing tokens and their pages
   int seq_len(int64_t seq_id) const;
+  int seq_computed(int64_t seq_id) const;          // tokens whose K/V are in the cache, -1 for an unknown id
   int seq_tokens(int64_t seq_id, int32_t* out, int cap) const;
   // Speculative decoding: propose `k` tokens to follow the sequence's last token.  The next step feeds the
   // last token plus the drafts, samples every position, and commit_step keeps the longest prefix of the

@@ -64,6 +64,10 @@ def load_runtime():
     lib.ogb_core_add_pages.restype = None
     lib.ogb_core_fork.argtypes = [P, c_int64]
     lib.ogb_core_fork.restype = c_int64
+    lib.ogb_core_seq_computed.argtypes = [P, c_int64]
+    lib.ogb_core_seq_computed.restype = c_int
+    lib.ogb_core_swap_state.argtypes = [P, c_int64, c_int64]
+    lib.ogb_core_swap_state.restype = c_int
     lib.ogb_core_rewind.argtypes = [P, c_int64, c_int]
     lib.ogb_core_rewind.restype = c_int
     lib.ogb_core_set_window.argtypes = [P, c_int, c_int]
@@ -173,6 +177,10 @@ class Core:
     def fork(self, sid):
         return int(self.lib.ogb_core_fork(self.h, sid))
 
+    def swap_state(self, a, b) -> bool:
+        """The two sequences exchange everything but their ids (between steps only)."""
+        return bool(self.lib.ogb_core_swap_state(self.h, a, b))
+
     def rewind(self, sid, new_len):
         return bool(self.lib.ogb_core_rewind(self.h, sid, new_len))
 
@@ -227,6 +235,10 @@ class Core:
 
     def seq_len(self, sid):
         return int(self.lib.ogb_core_seq_len(self.h, sid))
+
+    def seq_computed(self, sid):
+        """Tokens of the sequence whose K/V are in the cache."""
+        return int(self.lib.ogb_core_seq_computed(self.h, sid))
 
     def seq_tokens(self, sid):
         n = self.seq_len(sid)

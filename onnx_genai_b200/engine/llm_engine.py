@@ -55,6 +55,7 @@ class EngineConfig:
     max_draft_tokens: int = 0          # speculative decoding: drafts verified per sequence per step
     native_executor: bool = True       # launch the layer stack from the C++ step executor when possible
     cuda_graphs: bool = False          # replay decode-only steps (forward + sampler) from captured CUDA graphs
+    max_tree_branches: int = 4         # root-to-leaf paths of a speculation tree verified per step (one forked sequence each)
     weight_offload_layers: int = 0     # keep the matrices of the last N layers in pinned host memory and stream them per step
     shard_sampling: bool = True        # TP: each rank runs lm_head + sampler for 1/tp of the rows, tokens are all-gathered
     vram_limit: str | None = None      # "8GiB" | "0.9" | "auto": cap on device bytes (weights + activations + KV pool)
@@ -218,6 +219,8 @@ class LLMEngine:
         self.hidden_taps: dict = {}       # seq id -> None until the request's first logits row exists, then its final hidden state
         self.graphs: dict = {}
         self.graph_replays = 0
+        self.tree_groups: dict = {}         # sequence id -> ids of the forks verifying the other paths of its speculation tree
+        self.tree_branches = self.tree_branch_wins = 0
         self.verify_on_decode_kernel = 0   # steps whose draft rows ran on the split-KV decode kernel
         self.graph_declines: list = []
         self.device_faults = 0            # steps that ended with a non-zero device status word
@@ -451,6 +454,69 @@ class LLMEngine:
         si.verify_splits = splits
         self.verify_on_decode_kernel += 1
 
+    # ---- speculation trees verified as forked branches --------------------------------------------
+    def _fork_tree_branches(self, sid, tree) -> None:
+        """Verify a speculation tree with the linear machinery: the sequence drafts the tree's first root-to-leaf path
+        and every other path is drafted by a copy-on-write fork of the sequence (the context's pages are shared; a
+        branch writes only its own tail).  All branches run in the same step; `_settle_tree_branches` keeps the one that
+        got furthest.  Shared prefixes of paths are recomputed per branch -- what a tree-masked attention pass would
+        save -- but rows of a step are cheap next to the weights they share.  Greedy requests only: branches of a
+        sampled request would draw different tokens for the same position."""
+        if tree is None or len(tree) == 0 or sid in self.tree_groups:
+            return
+        if self.core.seq_computed(sid) < self.core.seq_len(sid) - 1:
+            return                                            # still prefilling: a fork would repeat the prefill
+        k = self.cfg.max_draft_tokens
+        paths = []
+        for leaf in tree.leaves():
+            toks = [tree.nodes[i].token for i in tree.path_to(leaf)][:k]
+            if toks and toks not in paths:
+                paths.append(toks)
+        paths.sort(key=len, reverse=True)
+        room = max(0, self.cfg.max_seqs - (self.core.num_running + self.core.num_waiting + self.core.num_swapped))
+        paths = paths[: max(1, min(self.cfg.max_tree_branches, 1 + room))]
+        self.core.set_draft(sid, np.asarray(paths[0], dtype=np.int32))
+        forks = []
+        for path in paths[1:]:
+            fid = self.core.fork(sid)
+            if fid < 0:
+                break
+            self.core.set_draft(fid, np.asarray(path, dtype=np.int32))
+            forks.append(fid)
+        if forks:
+            self.tree_groups[sid] = forks
+            self.tree_branches += len(forks)
+
+    def _settle_tree_branches(self, events):
+        """After the commit: per tree, the branch that committed the most tokens becomes the sequence (its state moves
+        under the caller's id), the other branches are released, and only the winner's events are reported."""
+        committed: dict = {}
+        for ev_sid, _tok, _fin in events:
+            committed[ev_sid] = committed.get(ev_sid, 0) + 1
+        relabel, dropped = {}, set()
+        for sid, forks in self.tree_groups.items():
+            members = [sid] + forks
+            if not any(m in committed for m in members):
+                continue                                      # the tree's rows were not scheduled this step: settle at the next
+            winner = max(members, key=lambda m: (committed.get(m, 0), m == sid))
+            if winner != sid:
+                self.core.swap_state(sid, winner)
+                self.tree_branch_wins += 1
+            relabel[winner] = sid
+            dropped.update(m for m in members if m != winner)
+            for f in forks:                                   # after the swap the fork ids hold the losing states
+                self.core.cancel(f)
+                self.core.release(f)
+            self.tree_groups[sid] = None
+        self.tree_groups = {k: v for k, v in self.tree_groups.items() if v is not None}
+        out = []
+        for ev_sid, tok, fin in events:
+            if ev_sid in relabel:
+                out.append((relabel[ev_sid], tok, fin))
+            elif ev_sid not in dropped:
+                out.append((ev_sid, tok, fin))
+        return out
+
     # ---- TP: rows of the logits/sampling stage split over the ranks -------------------------------
     def _shard_rows(self, r: int) -> bool:
         """With a replicated lm_head every rank would compute and sample all r rows.  Instead rank k takes rows
@@ -524,6 +590,9 @@ class LLMEngine:
                 continue
             if getattr(proposer, "wants_sequence", False):   # proposers that read this sequence's KV pages
                 proposer.bind(self, sid)
+            if hasattr(proposer, "propose_tree"):            # a tree of candidates: one forked sequence per root-to-leaf path
+                self._fork_tree_branches(sid, proposer.propose_tree(toks, self.cfg.max_draft_tokens))
+                continue
             key = getattr(proposer, "batch_key", None)
             if key is not None:                              # proposers that can answer together (one draft engine)
                 batches.setdefault(key, []).append((sid, proposer, toks))
@@ -611,6 +680,8 @@ class LLMEngine:
                     self.d2h_bytes += row_logits.nbytes
                     self.sampled_host[row] = int(fn(row_logits, float(unis[row])))
         events = self.core.commit_step(self.sampled_host.data_ptr(), r)
+        if self.tree_groups:
+            events = self._settle_tree_branches(events)
         if r > 0 and any(getattr(p, "wants_hidden", False) for p in self.proposers.values()):
             # proposers that draft from the target's hidden state get the row that produced the last committed token:
             # a sequence's rows are consecutive, and it committed (accepted drafts + 1) tokens

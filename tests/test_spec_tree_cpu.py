@@ -81,3 +81,56 @@ def test_verify_tree_scores_every_node_with_its_own_path():
     scorer = PathScorer(toy_logits)
     acc, plan = verify_tree(ctx, t, scorer)
     assert acc.tokens.tolist() == truth and acc.path == [0, 1] and plan.new_length == 5 and scorer.calls == 1 + len(t)
+
+
+def test_engine_verifies_a_tree_as_forked_branches_and_keeps_the_winner():
+    """A proposer whose first path goes wrong after one token and whose second path is right: the forked branch wins,
+    its state continues under the request's id, the output equals plain greedy decoding, fewer steps are taken, and
+    every page returns to the pool."""
+    import torch
+
+    from onnx_genai_b200.engine.llm_engine import EngineConfig, LLMEngine
+    from onnx_genai_b200.models.config import DecoderConfig
+    from onnx_genai_b200.models.decoder import random_weights
+
+    cfg = DecoderConfig(name="t", num_layers=2, hidden=64, num_heads=4, num_kv_heads=2, head_dim=16, intermediate=96, vocab=97,
+                        rope_theta=1e4, tie_embeddings=True, qkv_bias=True, weight_format="bf16", max_position=512)
+    w = random_weights(cfg, "cpu", seed=5, std=0.3, dtype=torch.float32)
+    mk = lambda **kw: LLMEngine(EngineConfig(model=cfg, num_pages=48, max_seqs=8, max_tokens_per_step=128, max_seq_len=256,
+                                             enable_prefix_cache=False, **kw), weights=w, device="cpu")
+    prompts = [np.random.default_rng(i).integers(0, cfg.vocab, size=n).astype(np.int32) for i, n in enumerate((37, 21))]
+    plain = mk()
+    want = plain.generate([p for p in prompts], 24)
+    plain_steps = plain.steps
+
+    class OracleTree:
+        """Knows the continuation; hides it on the second path of the tree."""
+        def __init__(self, full):
+            self.full = list(full)
+
+        def propose_tree(self, toks, k):
+            done = len(toks)
+            nxt = self.full[done:done + k]
+            if len(nxt) < 2:
+                return SpecTree()
+            wrong = lambda t: (int(t) + 1) % cfg.vocab
+            return SpecTree.from_paths([[nxt[0], wrong(nxt[1])] + [wrong(t) for t in nxt[2:]], list(nxt), [wrong(nxt[0])]])
+
+    eng = mk(max_draft_tokens=4)
+    free0 = eng.core.num_free_pages
+    ids = []
+    for p, out in zip(prompts, want):
+        sid = eng.add_request(p, 24)
+        eng.proposers[sid] = OracleTree(list(p) + list(out))
+        ids.append(sid)
+    got = {i: [] for i in ids}
+    while eng.has_work:
+        for sid, tok, fin in eng.step().events:
+            assert sid in got                                  # fork ids never surface
+            got[sid].append(tok)
+    for sid in ids:
+        eng.core.release(sid)
+    assert [got[i] for i in ids] == want
+    assert eng.tree_branch_wins > 0 and eng.tree_branches >= 2 * eng.tree_branch_wins
+    assert eng.steps < plain_steps
+    assert eng.core.num_free_pages == free0 and not eng.tree_groups
