@@ -82,19 +82,36 @@ class StepOutput:
 
 class LLMEngine:
     def __init__(self, cfg: EngineConfig, weights: DecoderWeights | None = None, device="cuda", tp: int = 1,
-                 rank: int = 0, comm=None):
+                 rank: int = 0, comm=None, pp: int = 1):
+        """``tp`` > 1: this process is rank ``rank`` of a tensor-parallel group.  ``pp`` > 1 (with tp = 1): this process is
+        stage ``rank`` of a pipeline over the layers -- every stage runs the same scheduler, the residual stream moves
+        stage to stage by send / recv, the last stage samples and broadcasts the tokens."""
         self.cfg, self.device = cfg, torch.device(device)
         self.tp, self.rank, self.comm = tp, rank, comm
+        self.pp = int(pp)
+        if self.pp > 1 and (tp != 1 or comm is None or cfg.weight_offload_layers):
+            raise ValueError("pipeline parallelism needs tp = 1, a communicator, and no weight paging")
         m = cfg.model
         is_cuda = self.device.type == "cuda"
+        shard_rank = 0 if self.pp > 1 else rank       # a pipeline stage holds whole layers: nothing is sharded within one
         if weights is None:
             dtype = torch.bfloat16 if is_cuda else torch.float32
-            weights = random_weights(m, self.device, tp, rank, seed=cfg.seed, dtype=dtype)
+            weights = random_weights(m, self.device, tp, shard_rank, seed=cfg.seed, dtype=dtype)
         self.weights = weights
         max_pages_per_seq = (cfg.max_seq_len + ops.PAGE - 1) // ops.PAGE
-        hs = shard_heads(m.num_heads, m.num_kv_heads, tp, rank)
+        hs = shard_heads(m.num_heads, m.num_kv_heads, tp, shard_rank)
         max_rows = cfg.max_seqs * (1 + max(0, cfg.max_draft_tokens))
-        self.model = DecoderModel(m, weights, self.device, cfg.max_tokens_per_step, max_rows, tp, rank, comm)
+        self.model = DecoderModel(m, weights, self.device, cfg.max_tokens_per_step, max_rows, tp, shard_rank, comm)
+        own_layers = None
+        if self.pp > 1:
+            from ..parallel.pipeline import plan_stages
+
+            # the first stage also embeds and the last one runs the LM head: weigh them like the layers they displace
+            head = 2.0 * m.vocab * m.hidden / max(1.0, 2.0 * m.hidden * (m.num_heads + 2 * m.num_kv_heads) * m.head_dim + 2.0 * m.hidden * m.hidden
+                                                  + 6.0 * m.hidden * max(m.intermediate, 1))
+            self.stage_plan = plan_stages(m.num_layers, self.pp, head_cost=head)
+            self.model.set_pipeline(rank, self.pp, self.stage_plan.ranges)
+            own_layers = range(*self.stage_plan.ranges[rank])
         # memory ledger: bytes come from the tensors that exist, the KV pool gets what the limit leaves
         from .memory import MemoryLedger, parse_limit, tensor_bytes
 
@@ -127,8 +144,8 @@ class LLMEngine:
             else:
                 num_pages = min(4096, cfg.max_seqs * max_pages_per_seq + 16)
         self.num_pages = int(num_pages)
-        kv_max = cfg.kv_max_pages if (is_cuda and self.tp == 1 and cfg.kv_max_pages > self.num_pages) else 0
-        self.kv = KVCache(m, self.num_pages, self.device, len(hs.kv_heads), cfg.kv_dtype, max_pages=kv_max)
+        kv_max = cfg.kv_max_pages if (is_cuda and self.tp == 1 and self.pp == 1 and cfg.kv_max_pages > self.num_pages) else 0
+        self.kv = KVCache(m, self.num_pages, self.device, len(hs.kv_heads), cfg.kv_dtype, max_pages=kv_max, layers=own_layers)
         self.kv_lease = self.memory.lease("kv", tier, self.kv.mapped_bytes(), f"pages of 16 tokens, {cfg.kv_dtype}")
         self.kv_grows, self.kv_grow_error = 0, None
         self.core = Core(CoreConfig(num_pages=self.num_pages, num_host_pages=cfg.num_host_pages, max_seqs=cfg.max_seqs,
@@ -156,33 +173,33 @@ class LLMEngine:
         self.direct_swap = False
         self.swap_moves = 0                # page-move launches issued for swap / copy-on-write
         if cfg.num_host_pages > 0:
-            shape = (cfg.num_host_pages,) + tuple(self.kv.pools[0].shape[1:])
+            own_pools, own_scales = self.kv.own_pools, self.kv.own_scales
+            shape = (cfg.num_host_pages,) + tuple(own_pools[0].shape[1:])
             if cfg.host_allocator_plugin:
                 # swap space from a third-party allocator (memory plugin ABI); copies to it are synchronous, as for any
                 # host memory the CUDA driver has not pinned
                 from ..utils.mem_plugin import PluginAllocator
 
                 self.host_allocator = PluginAllocator(cfg.host_allocator_plugin, purpose="kv-swap")
-                self.host_kv = [self.host_allocator.tensor(shape, self.kv.pools[0].dtype) for _ in range(m.num_layers)]
+                self.host_kv = [self.host_allocator.tensor(shape, own_pools[0].dtype) for _ in own_pools]
             else:
-                self.host_kv = [torch.zeros(shape, dtype=self.kv.pools[0].dtype, pin_memory=is_cuda)
-                                for _ in range(m.num_layers)]
+                self.host_kv = [torch.zeros(shape, dtype=own_pools[0].dtype, pin_memory=is_cuda) for _ in own_pools]
             try:
                 self.memory.lease("kv", "host", sum(t.numel() * t.element_size() for t in self.host_kv), "swap space")
             except Exception:
                 pass
             if self.kv.scales is not None:     # one-byte pages: the per-(page, head, K|V) scales travel with their page
-                sshape = (cfg.num_host_pages,) + tuple(self.kv.scales[0].shape[1:])
+                sshape = (cfg.num_host_pages,) + tuple(own_scales[0].shape[1:])
                 self.host_scales = [torch.zeros(sshape, dtype=torch.float32, pin_memory=is_cuda and not cfg.host_allocator_plugin)
-                                    for _ in range(m.num_layers)]
+                                    for _ in own_pools]
             # Pinned host memory is addressable from the device: swap kernels on a side stream read and write it in
             # place, so a swap needs no staging buffer and never blocks the host.  Memory from an allocator plugin is
             # not pinned by the driver and keeps the synchronous copy path.
             self.direct_swap = is_cuda and not cfg.host_allocator_plugin
         if is_cuda:
             addr = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=self.device)
-            self._kv_bases = addr(self.kv.pools)
-            self._scale_bases = addr(self.kv.scales) if self.kv.scales is not None else None
+            self._kv_bases = addr(self.kv.own_pools)
+            self._scale_bases = addr(self.kv.own_scales) if self.kv.scales is not None else None
             if self.direct_swap:
                 self._host_bases = addr(self.host_kv)
                 self._host_scale_bases = addr(self.host_scales) if self.host_scales is not None else None
@@ -201,7 +218,7 @@ class LLMEngine:
                                                                   f32(L.uniform))
         self.top_k = p[L.top_k:L.top_k + max_rows]
         self.model.weight_offload_layers = cfg.weight_offload_layers if is_cuda else 0
-        self.native_executor = cfg.native_executor and self.model.bind_native(self.kv, max_pages_per_seq)
+        self.native_executor = cfg.native_executor and self.pp == 1 and self.model.bind_native(self.kv, max_pages_per_seq)
         if cfg.weight_offload_layers > 0:
             if not (self.native_executor and getattr(self.model, "weight_packs", None)):
                 raise ValueError("weight_offload_layers needs the C++ step executor (CUDA, dense bf16 layers, bf16 KV pages)")
@@ -259,8 +276,8 @@ class LLMEngine:
             side = self.swap_stream if self.direct_swap else main
             if side is not main:
                 side.wait_stream(main)       # earlier steps wrote the pages that leave; the index lists were just copied
-            page_bytes = kv.pools[0].stride(0) * kv.pools[0].element_size()
-            scale_bytes = kv.scales[0].stride(0) * 4 if kv.scales is not None else 0
+            page_bytes = kv.own_pools[0].stride(0) * kv.own_pools[0].element_size()
+            scale_bytes = kv.own_scales[0].stride(0) * 4 if kv.scales is not None else 0
             n_host = self.cfg.num_host_pages
             with torch.cuda.stream(side):
                 for kind, count in runs:
@@ -282,7 +299,7 @@ class LLMEngine:
                     for dst_b, src_b, nbytes in tables:
                         if dst_b is None or src_b is None or nbytes == 0:
                             continue
-                        ops.kv_move_pages(dst_b, src_b, len(kv.pools), src_idx, dst_idx, count, nbytes, sc, dc)
+                        ops.kv_move_pages(dst_b, src_b, len(kv.own_layers), src_idx, dst_idx, count, nbytes, sc, dc)
                         self.swap_moves += 1
                     offs[kind] += count
             if side is not main:
@@ -294,8 +311,8 @@ class LLMEngine:
             src_off, dst_off = lists[kind]
             src = torch.from_numpy(pn[src_off + o:src_off + o + count].astype(np.int64))
             dst = torch.from_numpy(pn[dst_off + o:dst_off + o + count].astype(np.int64))
-            for li, pool in enumerate(kv.pools):
-                scales = kv.scales[li] if kv.scales is not None else None
+            for li, pool in enumerate(kv.own_pools):             # li also indexes the swap space, which holds the own layers only
+                scales = kv.own_scales[li] if kv.scales is not None else None
                 if kind == 0:
                     sd, dd = src.to(self.device), dst.to(self.device)
                     pool[dd] = pool[sd]
@@ -357,7 +374,7 @@ class LLMEngine:
     GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512)
 
     def _graph_eligible(self, si, r, hdr) -> bool:
-        return (self.cfg.cuda_graphs and self.device.type == "cuda" and self.tp == 1 and not getattr(self.model, "tap_layers", None)
+        return (self.cfg.cuda_graphs and self.device.type == "cuda" and self.tp == 1 and self.pp == 1 and not getattr(self.model, "tap_layers", None)
                 and not self.cfg.weight_offload_layers
                 and si.num_prefill_seqs == 0 and si.num_tiles == 0 and si.num_decode == si.num_tokens == r and r > 0
                 and r <= min(self.cfg.max_seqs, self.GRAPH_BUCKETS[-1]))
@@ -644,21 +661,28 @@ class LLMEngine:
                 else:
                     self.sampled_host[:r].copy_(self.sampled_dev[:r])
             elif self.device.type == "cuda":
-                if (temps <= 0).all():
+                if logits is None:
+                    pass                                      # an earlier pipeline stage: the last stage samples
+                elif (temps <= 0).all():
                     ops.argmax(logits, out=self.sampled_dev[:r])
                 else:
                     ops.sample(logits, self.temperature[:r], self.top_k[:r], self.top_p[:r], self.min_p[:r],
                                self.uniform[:r], work=self.sample_work, out=self.sampled_dev[:r])
                 if self.tp > 1 and self.cfg.sync_sampled_tokens:
                     self.comm.broadcast(self.sampled_dev[:r], src=0)
+                if self.pp > 1:
+                    self.comm.broadcast(self.sampled_dev[:r], src=self.pp - 1)
                 self._finish_device_step(r)
             else:
-                if (temps <= 0).all():
-                    toks = ops.argmax(logits)
+                if logits is None:
+                    pass
+                elif (temps <= 0).all():
+                    self.sampled_host[:r] = ops.argmax(logits)
                 else:
-                    toks = ops.sample(logits, self.temperature[:r], self.top_k[:r], self.top_p[:r], self.min_p[:r],
-                                      self.uniform[:r])
-                self.sampled_host[:r] = toks
+                    self.sampled_host[:r] = ops.sample(logits, self.temperature[:r], self.top_k[:r], self.top_p[:r], self.min_p[:r],
+                                                       self.uniform[:r])
+                if self.pp > 1:
+                    self.comm.broadcast(self.sampled_host[:r], src=self.pp - 1)
         elif self.device.type == "cuda":
             self._finish_device_step(0)
         if self.hidden_taps and r > 0:

@@ -171,8 +171,11 @@ class KVCache:
     beyond ``num_pages``; the page allocator never hands them out before :meth:`grow` has returned."""
 
     def __init__(self, cfg: DecoderConfig, num_pages: int, device, kv_heads_local: int | None = None, dtype="bf16",
-                 max_pages: int = 0):
+                 max_pages: int = 0, layers=None):
+        """``layers``: the layer indices this process runs (a pipeline stage); the others get no pool."""
         hkv = kv_heads_local or cfg.num_kv_heads
+        own = set(range(cfg.num_layers)) if layers is None else set(layers)
+        self.own_layers = sorted(own)
         self.num_pages = num_pages
         self.dtype = dtype
         if dtype not in ("bf16", "fp8", "int8", "fp8_e5m2"):
@@ -204,12 +207,12 @@ class KVCache:
             self._mark_backed()
             return
         self.max_pages = num_pages
-        self.pools = [torch.zeros(num_pages, hkv, 2, ops.PAGE, cfg.head_dim, dtype=tdtype, device=device)
-                      for _ in range(cfg.num_layers)]
+        self.pools = [torch.zeros(num_pages, hkv, 2, ops.PAGE, cfg.head_dim, dtype=tdtype, device=device) if li in own else None
+                      for li in range(cfg.num_layers)]
         self.scales = None
         if quant:
-            self.scales = [torch.zeros(num_pages, hkv, 2, dtype=torch.float32, device=device)
-                           for _ in range(cfg.num_layers)]
+            self.scales = [torch.zeros(num_pages, hkv, 2, dtype=torch.float32, device=device) if li in own else None
+                           for li in range(cfg.num_layers)]
 
     def _mark_backed(self) -> None:
         """Record the mapped page count on every pool tensor: kernels bound page ids by it (ops.backed_pages)."""
@@ -243,14 +246,23 @@ class KVCache:
         self._mark_backed()
         return new_pages
 
+    @property
+    def own_pools(self) -> list:
+        """The pools this process holds (all of them unless it is a pipeline stage), in layer order."""
+        return [self.pools[li] for li in self.own_layers]
+
+    @property
+    def own_scales(self):
+        return [self.scales[li] for li in self.own_layers] if self.scales is not None else None
+
     def mapped_bytes(self) -> int:
         if self.buffers is None:
-            return sum(p.numel() * p.element_size() for p in self.pools) + sum(s.numel() * 4 for s in (self.scales or []))
+            return sum(p.numel() * p.element_size() for p in self.own_pools) + sum(s.numel() * 4 for s in (self.own_scales or []))
         return sum(b.mapped for b in self.buffers) + sum(b.mapped for b in self.scale_buffers)
 
     def page_bytes(self) -> int:
-        p = self.pools[0]
-        return p.stride(0) * p.element_size() * len(self.pools)
+        p = self.own_pools[0]
+        return p.stride(0) * p.element_size() * len(self.own_layers)
 
 
 class DecoderModel:
@@ -308,6 +320,7 @@ class DecoderModel:
         self.decode_splits = 1
         self.part_o = self.part_ml = None
         self._tp_args_cache: dict = {}
+        self.pipeline = (0, 1)      # (stage, stages): see set_pipeline
         self.native = None          # C++ step executor (dense bf16 layers, bf16 pages; TP needs the fused communicator)
         self.native_launches = 0
 
@@ -443,6 +456,22 @@ class DecoderModel:
         return self.ensure_split_scratch(splits)
 
     # --------------------------------------------------------------------------------------
+    def set_pipeline(self, stage: int, stages: int, ranges) -> None:
+        """Make this model one stage of a pipeline: it keeps the layers ``ranges[stage]`` (the others' weights are
+        dropped), the first stage embeds, every other stage receives the residual stream from its predecessor, the last
+        stage applies the final norm and the LM head.  Stages run the step op by op from Python."""
+        if self.tp != 1:
+            raise ValueError("pipeline stages are built for tp = 1 (one GPU per stage)")
+        lo, hi = ranges[stage]
+        self.pipeline = (stage, stages)
+        self.layer_range = (lo, hi)
+        if self.native:
+            self._native_lib.ogb_decoder_destroy(self.native)
+            self.native = None
+        for li in range(len(self.w.layers)):
+            if not lo <= li < hi:
+                self.w.layers[li] = None
+
     def set_hidden_taps(self, layers) -> None:
         """Keep, for every logit row of a step, the residual stream entering each of ``layers`` (0 = the embeddings,
         ``num_layers`` is not allowed: that state is ``h_last`` before its norm).  Draft heads that read intermediate
@@ -475,12 +504,18 @@ class DecoderModel:
         if self.fused_comm is not None and self.tp > 1:
             return self._forward_tp_fused(si, kv)
         x, h, qkv, attn = self.x[:t], self.h[:t], self.qkv[:t], self.attn[:t]
-        ops.embedding(si.token_ids[:t], w.embed, out=x) if x.is_cuda else x.copy_(w.embed[si.token_ids[:t].long()])
+        stage, stages = self.pipeline
+        if stage == 0:
+            ops.embedding(si.token_ids[:t], w.embed, out=x) if x.is_cuda else x.copy_(w.embed[si.token_ids[:t].long()])
+        else:
+            self.comm.recv(x, stage - 1)                 # the residual stream after the previous stage's last layer
         pending = None  # partial sums still to be added to the residual (TP only)
         # int4 layers at decode size: norm, SwiGLU glue and residual adds live inside the GEMV launches
-        fused_q = (x.is_cuda and t <= 4 and self.tp == 1 and all(l.quant and len(l.quant["qkv"]) == 1 and
+        fused_q = (x.is_cuda and t <= 4 and self.tp == 1 and all(l is not None and l.quant and len(l.quant["qkv"]) == 1 and
                                                                  l.quant.get("gate_up") is not None for l in w.layers))
         for li, lw in enumerate(w.layers):
+            if lw is None:                               # a layer of another pipeline stage
+                continue
             pool = kv.pools[li]
             if fused_q:
                 if tapping and li in self.taps:
@@ -557,6 +592,9 @@ class DecoderModel:
         r = si.num_logit_rows
         if pending is not None:   # fold the last partial sum into the residual before selecting rows
             x.add_(pending)
+        if stage < stages - 1:
+            self.comm.send(x, stage + 1)
+            return None                                  # the last stage computes the logits and samples
         xl = self.x_last[:r]
         torch.index_select(x, 0, si.logit_rows[:r].long(), out=xl)
         hl = self.h_last[:r]

@@ -41,6 +41,17 @@ def test_four_cpu_ranks_replicate_kv_heads(tmp_path):
     assert four["tokens"] == single["tokens"]
 
 
+def test_pipeline_stages_on_cpu_ranks_match_one_rank(tmp_path):
+    """Two and three pipeline stages (the three layers split 2 + 1 and 1 + 1 + 1): the residual stream crosses stages by
+    send / recv, the last stage samples, every stage commits the same tokens as a single process."""
+    single = _run(1, "nccl", str(tmp_path / "s.pt"), 0)
+    for stages, port in ((2, 29655), (3, 29656)):
+        piped = _run(stages, "pp", str(tmp_path / f"pp{stages}.pt"), port)
+        err = float((piped["logits"] - single["logits"]).norm() / single["logits"].norm())
+        assert err < 1e-5, (stages, err)
+        assert piped["tokens"] == single["tokens"], stages
+
+
 def test_communicator_exchanges_and_expert_dispatch_over_gloo(tmp_path):
     res = _run(3, "comm-api", str(tmp_path / "c.pt"), 29654)
     assert res["backend"] == "gloo" and res["world"] == 3

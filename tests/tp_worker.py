@@ -70,16 +70,27 @@ def main():
         from onnx_genai_b200.parallel.fused import FusedComm
 
         comm = FusedComm(comm, dev)
+    pipeline = mode == "pp" and world > 1
     eng = LLMEngine(EngineConfig(model=cfg, num_pages=256, max_seqs=16, max_tokens_per_step=512, max_seq_len=512,
-                                 seed=21, native_executor=(mode != "fused-py")), device=dev, tp=world, rank=rank,
-                    comm=comm)
+                                 seed=21, native_executor=(mode != "fused-py")), device=dev, tp=1 if pipeline else world, rank=rank,
+                    comm=comm, pp=world if pipeline else 1)
     rng = np.random.default_rng(0)
     prompts = [rng.integers(0, cfg.vocab, size=n).astype(np.int32) for n in (3, 64, 97, 200)]
     for p in prompts:
         eng.add_request(p, 12)
     eng.step()
     n = len(prompts)
-    if world > 1 and eng._shard_rows(n):
+    if pipeline:
+        # only the last stage has logits; every stage must hold its own layers' weights and KV pools and nothing else
+        import torch.distributed as dist
+
+        lo, hi = eng.stage_plan.ranges[rank]
+        assert [i for i, l in enumerate(eng.weights.layers) if l is not None] == list(range(lo, hi))
+        assert [i for i, p in enumerate(eng.kv.pools) if p is not None] == list(range(lo, hi))
+        shares = [None] * world
+        dist.all_gather_object(shares, eng.model.logits[:n].float().cpu().clone() if rank == world - 1 else None)
+        logits = shares[world - 1]
+    elif world > 1 and eng._shard_rows(n):
         # each rank ran lm_head for its share of the rows only: collect the shares in rank order
         import torch.distributed as dist
 
