@@ -533,4 +533,6 @@ class Engine:
                 "waiting": core.num_waiting, "running": core.num_running, "swapped": core.num_swapped,
                 "prefix_cache_hits": core.prefix_hits, "prefix_cache_lookups": core.prefix_lookups,
                 "preemptions": core.num_preemptions, "steps": self.llm.steps, "sessions": len(self.sessions),
-                "memory": self.llm.memory.snapshot()}
+                "memory": self.llm.memory.snapshot(),
+                "allocator": self.llm.allocator.stats() if self.llm.allocator is not None else {"kind": "torch"},
+                "deferred_releases": self.llm.release_queue.stats()}

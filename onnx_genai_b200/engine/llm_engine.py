@@ -55,6 +55,7 @@ class EngineConfig:
     max_draft_tokens: int = 0          # speculative decoding: drafts verified per sequence per step
     native_executor: bool = True       # launch the layer stack from the C++ step executor when possible
     cuda_graphs: bool = False          # replay decode-only steps (forward + sampler) from captured CUDA graphs
+    allocator: object | None = None    # engine/allocator.py Allocator for KV pools and swap space (torch's allocator when None)
     max_tree_branches: int = 4         # root-to-leaf paths of a speculation tree verified per step (one forked sequence each)
     weight_offload_layers: int = 0     # keep the matrices of the last N layers in pinned host memory and stream them per step
     shard_sampling: bool = True        # TP: each rank runs lm_head + sampler for 1/tp of the rows, tokens are all-gathered
@@ -145,7 +146,12 @@ class LLMEngine:
                 num_pages = min(4096, cfg.max_seqs * max_pages_per_seq + 16)
         self.num_pages = int(num_pages)
         kv_max = cfg.kv_max_pages if (is_cuda and self.tp == 1 and self.pp == 1 and cfg.kv_max_pages > self.num_pages) else 0
-        self.kv = KVCache(m, self.num_pages, self.device, len(hs.kv_heads), cfg.kv_dtype, max_pages=kv_max, layers=own_layers)
+        from .allocator import DeferredReleaseQueue
+
+        self.allocator = cfg.allocator
+        self.release_queue = DeferredReleaseQueue()
+        self.kv = KVCache(m, self.num_pages, self.device, len(hs.kv_heads), cfg.kv_dtype, max_pages=kv_max, layers=own_layers,
+                          allocator=self.allocator)
         self.kv_lease = self.memory.lease("kv", tier, self.kv.mapped_bytes(), f"pages of 16 tokens, {cfg.kv_dtype}")
         self.kv_grows, self.kv_grow_error = 0, None
         self.core = Core(CoreConfig(num_pages=self.num_pages, num_host_pages=cfg.num_host_pages, max_seqs=cfg.max_seqs,
@@ -737,6 +743,21 @@ class LLMEngine:
         out.events, out.num_tokens, out.num_decode = events, t, si.num_decode
         out.num_prefill_tokens = int(hdr[HDR["num_prefill_tokens"]])
         return out
+
+    def close(self) -> dict:
+        """Give the KV pools back to the engine's allocator.  The releases are parked behind an event on the current
+        stream (steps still in flight may touch the pages) and completed once it has passed; returns the queue's
+        figures.  The engine must not step afterwards."""
+        allocs = self.kv.allocations()
+        stream = torch.cuda.current_stream() if self.device.type == "cuda" else None
+        self.kv.pools = [None] * len(self.kv.pools)
+        if self.kv.scales is not None:
+            self.kv.scales = [None] * len(self.kv.scales)
+        for a in allocs:
+            self.release_queue.enqueue(a, stream, "engine closed")
+        self.release_queue.flush()
+        self.kv_lease.release()
+        return self.release_queue.stats()
 
     # --------------------------------------------------------------------------------------
     def generate(self, prompts, max_new_tokens=64, **sampling):

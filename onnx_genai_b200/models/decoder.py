@@ -171,8 +171,9 @@ class KVCache:
     beyond ``num_pages``; the page allocator never hands them out before :meth:`grow` has returned."""
 
     def __init__(self, cfg: DecoderConfig, num_pages: int, device, kv_heads_local: int | None = None, dtype="bf16",
-                 max_pages: int = 0, layers=None):
-        """``layers``: the layer indices this process runs (a pipeline stage); the others get no pool."""
+                 max_pages: int = 0, layers=None, allocator=None):
+        """``layers``: the layer indices this process runs (a pipeline stage); the others get no pool.  ``allocator``: an
+        engine allocator (engine/allocator.py) the fixed-size pools come from; torch's allocator when absent."""
         hkv = kv_heads_local or cfg.num_kv_heads
         own = set(range(cfg.num_layers)) if layers is None else set(layers)
         self.own_layers = sorted(own)
@@ -207,11 +208,15 @@ class KVCache:
             self._mark_backed()
             return
         self.max_pages = num_pages
-        self.pools = [torch.zeros(num_pages, hkv, 2, ops.PAGE, cfg.head_dim, dtype=tdtype, device=device) if li in own else None
+        if allocator is not None:
+            make = lambda shape, dt, tag: allocator.tensor(shape, dt, "kv", tag)
+        else:
+            make = lambda shape, dt, tag: torch.zeros(*shape, dtype=dt, device=device)
+        self.pools = [make((num_pages, hkv, 2, ops.PAGE, cfg.head_dim), tdtype, f"pages of layer {li}") if li in own else None
                       for li in range(cfg.num_layers)]
         self.scales = None
         if quant:
-            self.scales = [torch.zeros(num_pages, hkv, 2, dtype=torch.float32, device=device) if li in own else None
+            self.scales = [make((num_pages, hkv, 2), torch.float32, f"page scales of layer {li}") if li in own else None
                            for li in range(cfg.num_layers)]
 
     def _mark_backed(self) -> None:
@@ -245,6 +250,11 @@ class KVCache:
         self.num_pages = new_pages
         self._mark_backed()
         return new_pages
+
+    def allocations(self) -> list:
+        """The allocator's records behind the pools and scale tables (empty when torch's allocator made them)."""
+        ts = [t for t in (self.pools + (self.scales or [])) if t is not None]
+        return [t.ogb_allocation for t in ts if hasattr(t, "ogb_allocation")]
 
     @property
     def own_pools(self) -> list:
