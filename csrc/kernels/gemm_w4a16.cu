@@ -6,7 +6,7 @@
 //   warp 1        MMA issuer and TMEM owner: tcgen05.mma kind::f16, fp32 accumulators in TMEM, double-buffered
 //   warps 2..5    epilogue: tcgen05.ld -> (+ bias) -> bf16 -> staged in shared memory -> coalesced 16-byte stores
 //   warps 6..13   dequantisers: each thread owns one 32-weight block of the stage's B tile (128 rows x 64 k): a 16-byte
-//                 load two iterations ahead, nibble -> bf16 through the 0x4300 mantissa trick (128 + n, exact), minus
+//                 load eight iterations ahead (a register ring), nibble -> bf16 through the 0x4300 mantissa trick (128 + n, exact), minus
 //                 (128 + zero point), times the scale as bf16x2, stored in the same swizzled K-major layout a TMA load
 //                 of a bf16 tile would have produced, then a proxy fence and one arrival per warp on the stage's barrier
 //
@@ -57,9 +57,12 @@ OGB_DEVICE void dequant_word(uint32_t w, __nv_bfloat162 zz, __nv_bfloat162 ss, u
   }
 }
 
+// What a dequantiser keeps per block between the load and its use.  The scale and the zero point stay as loaded (raw
+// bits): converting them at load time would make the thread wait for the load right there and serialise the ring.
 struct W4Unit {
   uint4 q;
-  __nv_bfloat162 ss, zz;
+  uint32_t s_raw;      // fp32 bits, or bf16 bits in the low half
+  uint32_t z_raw;      // the byte that holds the zero-point nibble, or 0x88 (zero point 8)
 };
 
 template <int MT, bool SF32>
@@ -233,55 +236,87 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint
     const int zp_stride = (kb32 + 1) / 2;
     const int my_tiles = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     const long long iters = static_cast<long long>(my_tiles) * k_blocks;
-    auto fetch = [&](long long j, W4Unit& un) {
-      un.q = make_uint4(0, 0, 0, 0);
-      float s = 0.f;
-      int z = 8;
-      if (j < iters) {
-        const int tile = blockIdx.x + static_cast<int>(j / k_blocks) * gridDim.x;
-        const int n = (tile / m_tiles) * kWTile + r_tile;
-        const int b = static_cast<int>(j % k_blocks) * 2 + half;
-        if (n < N && b < kb32) {
-          const size_t blk = static_cast<size_t>(n) * kb32 + b;
-          un.q = __ldg(reinterpret_cast<const uint4*>(qw) + blk);
-          if constexpr (SF32) s = __ldg(static_cast<const float*>(scales) + blk);
-          else s = __bfloat162float(__ldg(static_cast<const __nv_bfloat16*>(scales) + blk));
-          if (zp != nullptr) {
-            const uint8_t zb = __ldg(zp + static_cast<size_t>(n) * zp_stride + (b >> 1));
-            z = (b & 1) ? (zb >> 4) : (zb & 0xF);
-          }
-        }
-      }
-      un.ss = __float2bfloat162_rn(s);
-      un.zz = __float2bfloat162_rn(static_cast<float>(128 + z));
+    // The loads run kDepth iterations ahead of their use, in a register ring: a block's 16 bytes, its scale and its zero
+    // point each take a DRAM round trip, and only many of them in flight per thread keep the int4 stream near the
+    // memory rate (256 threads x kDepth x 16 bytes per SM in flight).
+    constexpr int kDepth = 8;
+    struct Cursor {
+      int tile, kb;
+      size_t row_blk;      // index of the row's first block
+      size_t row_zp;
+      bool row_ok;
     };
-    W4Unit u0, u1;
-    fetch(0, u0);
-    fetch(1, u1);
+    auto seat = [&](Cursor& c) {               // derive the row data of c.tile
+      const int n = c.tile < num_tiles ? (c.tile / m_tiles) * kWTile + r_tile : N;
+      c.row_ok = n < N;
+      c.row_blk = static_cast<size_t>(c.row_ok ? n : 0) * kb32;
+      c.row_zp = static_cast<size_t>(c.row_ok ? n : 0) * zp_stride;
+    };
+    auto fetch = [&](Cursor& c, W4Unit& un) {
+      un.q = make_uint4(0, 0, 0, 0);
+      un.s_raw = 0u;
+      un.z_raw = 0x88u;
+      const int b = c.kb * 2 + half;
+      if (c.row_ok && b < kb32) {
+        const size_t blk = c.row_blk + b;
+        un.q = __ldg(reinterpret_cast<const uint4*>(qw) + blk);
+        if constexpr (SF32) un.s_raw = __float_as_uint(__ldg(static_cast<const float*>(scales) + blk));
+        else un.s_raw = __ldg(static_cast<const unsigned short*>(scales) + blk);
+        if (zp != nullptr) un.z_raw = __ldg(zp + c.row_zp + (b >> 1));
+      }
+      if (++c.kb == k_blocks) {
+        c.kb = 0;
+        c.tile += gridDim.x;
+        seat(c);
+      }
+    };
+    Cursor cur{static_cast<int>(blockIdx.x), 0, 0, 0, false};
+    seat(cur);
+    W4Unit ring[kDepth];
+#pragma unroll
+    for (int d = 0; d < kDepth; ++d) fetch(cur, ring[d]);
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
     const uint32_t row_off = static_cast<uint32_t>(r_tile) * 128u;
     const uint32_t sw = static_cast<uint32_t>(r_tile & 7);
-    for (long long j = 0; j < iters; ++j) {
-      W4Unit u2;
-      fetch(j + 2, u2);
-      if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[stage], phase ^ 1))) { ok = false; break; }
-      uint8_t* sb = smem + stage * Cfg::kStage + Cfg::kStageA + row_off;
-      const uint32_t words[4] = {u0.q.x, u0.q.y, u0.q.z, u0.q.w};
+    for (long long j0 = 0; ok && j0 < iters; j0 += kDepth) {
 #pragma unroll
-      for (int wi = 0; wi < 4; ++wi) {
-        uint32_t o[4];
-        dequant_word(words[wi], u0.zz, u0.ss, o);
-        const uint32_t chunk = static_cast<uint32_t>(half * 4 + wi) ^ sw;       // 128-byte swizzle: 16-byte chunk index XOR row mod 8
-        *reinterpret_cast<uint4*>(sb + chunk * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+      for (int d = 0; d < kDepth; ++d) {
+        if (ok && j0 + d < iters) {
+          if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[stage], phase ^ 1))) {
+            ok = false;
+          } else {
+            uint8_t* sb = smem + stage * Cfg::kStage + Cfg::kStageA + row_off;
+            const uint32_t words[4] = {ring[d].q.x, ring[d].q.y, ring[d].q.z, ring[d].q.w};
+            // this block is half `half` of its k-block: an odd block's zero point is the high nibble of its byte
+            const uint32_t z = half ? (ring[d].z_raw >> 4) & 0xFu : ring[d].z_raw & 0xFu;
+            const uint32_t zbits = 0x4300u | z;                       // bf16 128 + z, exact
+            const uint32_t zz_u = zbits | (zbits << 16);
+            uint32_t ss_u;
+            if constexpr (SF32) {
+              const __nv_bfloat162 t = __float2bfloat162_rn(__uint_as_float(ring[d].s_raw));
+              ss_u = *reinterpret_cast<const uint32_t*>(&t);
+            } else {
+              ss_u = ring[d].s_raw | (ring[d].s_raw << 16);
+            }
+            const __nv_bfloat162 zz = *reinterpret_cast<const __nv_bfloat162*>(&zz_u);
+            const __nv_bfloat162 ss = *reinterpret_cast<const __nv_bfloat162*>(&ss_u);
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) {
+              uint32_t o[4];
+              dequant_word(words[wi], zz, ss, o);
+              const uint32_t chunk = static_cast<uint32_t>(half * 4 + wi) ^ sw;       // 128-byte swizzle: 16-byte chunk index XOR row mod 8
+              *reinterpret_cast<uint4*>(sb + chunk * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+            fence_proxy_async_smem();      // the tensor core reads these bytes through the async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full_bar[stage]);
+            fetch(cur, ring[d]);
+            if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+          }
+        }
       }
-      fence_proxy_async_smem();      // the tensor core reads these bytes through the async proxy
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&full_bar[stage]);
-      u0 = u1;
-      u1 = u2;
-      if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
     }
     if (!ok && lane == 0) { atomicOr(status, kStatusWaitTimeout); *abort_flag = 1; }
   }
