@@ -5,14 +5,20 @@
 //   warp 0        TMA producer: the A tile(s) of each k-block (128-byte swizzle) into the stage ring
 //   warp 1        MMA issuer and TMEM owner: tcgen05.mma kind::f16, fp32 accumulators in TMEM, double-buffered
 //   warps 2..5    epilogue: tcgen05.ld -> (+ bias) -> bf16 -> staged in shared memory -> coalesced 16-byte stores
-//   warps 6..13   dequantisers: each thread owns one 32-weight block of the stage's B tile (128 rows x 64 k): a 16-byte
-//                 load eight iterations ahead (a register ring), nibble -> bf16 through the 0x4300 mantissa trick (128 + n, exact), minus
-//                 (128 + zero point), times the scale as bf16x2, stored in the same swizzled K-major layout a TMA load
-//                 of a bf16 tile would have produced, then a proxy fence and one arrival per warp on the stage's barrier
+//   warps 6..13   dequantisers, two groups of four warps that take alternate k-blocks (a k-block's chain of loads ready ->
+//                 nibbles to bf16 -> stores -> proxy fence -> arrival is latency-bound for one warp, so two run side by
+//                 side on different ring slots).  A thread owns two 32-weight blocks of its group's k-block (128 rows x
+//                 64 k): their 16 bytes of nibbles, scale and zero point sit in a register ring loaded four of the group's
+//                 k-blocks ahead; nibble -> bf16 through the 0x4300 mantissa trick (128 + n, exact), minus (128 + zero
+//                 point), times the scale as bf16x2, stored in the same swizzled K-major layout a TMA load of a bf16 tile
+//                 would have produced, then a proxy fence and one arrival per warp on the slot's barrier
 //
-// A work item is MT 128-row tiles of A against one 128-column tile of W, so with MT = 2 one dequantised B tile feeds
-// two accumulators and the ALU work per MMA halves; MT = 1 serves M <= 128, where the kernel is bound by the int4
-// stream.  It is the counterpart of the reference's Marlin-style kernel
+// (A variant that brought the packed nibbles in by TMA -- 128 rows x 32 bytes per k-block, unswizzled, into a ring of
+// its own -- was 10 % faster and produced, in repeated runs, rare stale rows of B; the cause was not found, so the
+// nibbles stay on plain loads.)
+//
+// A work item is MT 128-row tiles of A against one 128-column tile of W, so with MT = 2 (M > 128) one dequantised B
+// tile feeds two accumulators and the ALU work per MMA halves.  It is the counterpart of the reference's Marlin-style kernel
 // (crates/onnx-runtime-ep-cuda/src/kernels/marlin_gemm.rs: int4 tiles dequantised in registers in front of mma.sync).
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -27,6 +33,9 @@ constexpr int kWTile = 128;                 // rows of an A tile, columns of a W
 constexpr int kWBK = 64;                    // k per stage: one 128-byte swizzle row of bf16
 constexpr int kWDequantWarps = 8;
 constexpr int kWThreads = (2 + 4 + kWDequantWarps) * 32;
+constexpr int kWGroups = 2;                 // dequantiser groups working on alternate k-blocks
+constexpr int kWGroupWarps = kWDequantWarps / kWGroups;
+constexpr int kWUnits = 256 / (kWGroupWarps * 32);   // 32-weight blocks per thread per k-block
 constexpr int kWStagePitch = 272;           // epilogue staging: 128 bf16 + 16 bytes, conflict-free for 16-byte accesses
 constexpr int kWStageWarpBytes = 32 * kWStagePitch;
 
@@ -38,7 +47,9 @@ struct W4Cfg {
   static constexpr int kStages = MT == 2 ? 4 : 6;
   static constexpr int kAccCols = MT * kWTile;          // TMEM columns of one accumulator set
   static constexpr int kTmemCols = 2 * kAccCols;        // 256 or 512: a power of two
-  static constexpr int kSmemBytes = kStages * kStage + 256 + 4 * kWStageWarpBytes;
+  static constexpr int kBarOff = kStages * kStage;                      // barriers (512 bytes)
+  static constexpr int kStagingOff = kBarOff + 512;
+  static constexpr int kSmemBytes = kStagingOff + 4 * kWStageWarpBytes;
 };
 
 // 8 nibbles of `w` (k order: low nibble of byte 0 first) -> 4 bf16x2 words in k order, each (nibble - zero) * scale.
@@ -60,9 +71,10 @@ OGB_DEVICE void dequant_word(uint32_t w, __nv_bfloat162 zz, __nv_bfloat162 ss, u
 // What a dequantiser keeps per block between the load and its use.  The scale and the zero point stay as loaded (raw
 // bits): converting them at load time would make the thread wait for the load right there and serialise the ring.
 struct W4Unit {
-  uint4 q;
+  uint4 q;             // the block's 32 nibbles
   uint32_t s_raw;      // fp32 bits, or bf16 bits in the low half
   uint32_t z_raw;      // the byte that holds the zero-point nibble, or 0x88 (zero point 8)
+  bool valid;          // false: a row past N or a block past K -- the loads went to a clamped address, the result is zero
 };
 
 template <int MT, bool SF32>
@@ -72,8 +84,8 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint
                           int M, int N, int K, int ldc, int* status) {
   using Cfg = W4Cfg<MT>;
   extern __shared__ __align__(1024) uint8_t smem[];
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStage);
-  uint8_t* staging = smem + Cfg::kStages * Cfg::kStage + 256;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kBarOff);
+  uint8_t* staging = smem + Cfg::kStagingOff;
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + Cfg::kStages;
   uint64_t* tmem_full = bars + 2 * Cfg::kStages;
@@ -90,7 +102,7 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < Cfg::kStages; ++i) {
-      mbar_init(&full_bar[i], 1 + kWDequantWarps);   // the producer's arrive.expect_tx + one arrival per dequantiser warp
+      mbar_init(&full_bar[i], 1 + kWGroupWarps);     // the producer's arrive.expect_tx + one arrival per warp of the group that fills it
       mbar_init(&empty_bar[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -229,91 +241,108 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint
     if (!ok && lane == 0) { atomicOr(status, kStatusWaitTimeout); *abort_flag = 1; }
   } else {
     // ------------------------------ dequantisers (B) ------------------------------
-    const int u = (warp - 6) * 32 + lane;          // 0..255: one 32-weight block of the stage's B tile each
-    const int r_tile = u >> 1;                     // row of the tile; the two lanes of a pair share a 32-byte sector
-    const int half = u & 1;                        // which 32-k block of the stage's 64 k
+    // Group g takes k-blocks g, g + 2, ...; a thread owns two 32-weight blocks of such a k-block: rows r and r + 64, the
+    // same half.
+    const int group = (warp - 6) / kWGroupWarps;
+    const int t = ((warp - 6) % kWGroupWarps) * 32 + lane;   // 0..127 within the group
+    const int half = t & 1;                                   // which 32-k block of the 64 k
     const int kb32 = (K + 31) / 32;
     const int zp_stride = (kb32 + 1) / 2;
     const int my_tiles = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     const long long iters = static_cast<long long>(my_tiles) * k_blocks;
-    // The loads run kDepth iterations ahead of their use, in a register ring: a block's 16 bytes, its scale and its zero
-    // point each take a DRAM round trip, and only many of them in flight per thread keep the int4 stream near the
-    // memory rate (256 threads x kDepth x 16 bytes per SM in flight).
-    constexpr int kDepth = 8;
+    // The loads run kDepth of the group's k-blocks ahead of their use, in a register ring (each takes a trip to L2 or
+    // DRAM): 128 threads x kDepth x 2 blocks x 16 bytes per group in flight.
+    constexpr int kDepth = 4;
     struct Cursor {
       int tile, kb;
-      size_t row_blk;      // index of the row's first block
-      size_t row_zp;
-      bool row_ok;
+      size_t row_blk[kWUnits];   // index of each row's first block
+      size_t row_zp[kWUnits];
+      bool row_ok[kWUnits];
     };
     auto seat = [&](Cursor& c) {               // derive the row data of c.tile
-      const int n = c.tile < num_tiles ? (c.tile / m_tiles) * kWTile + r_tile : N;
-      c.row_ok = n < N;
-      c.row_blk = static_cast<size_t>(c.row_ok ? n : 0) * kb32;
-      c.row_zp = static_cast<size_t>(c.row_ok ? n : 0) * zp_stride;
-    };
-    auto fetch = [&](Cursor& c, W4Unit& un) {
-      un.q = make_uint4(0, 0, 0, 0);
-      un.s_raw = 0u;
-      un.z_raw = 0x88u;
-      const int b = c.kb * 2 + half;
-      if (c.row_ok && b < kb32) {
-        const size_t blk = c.row_blk + b;
-        un.q = __ldg(reinterpret_cast<const uint4*>(qw) + blk);
-        if constexpr (SF32) un.s_raw = __float_as_uint(__ldg(static_cast<const float*>(scales) + blk));
-        else un.s_raw = __ldg(static_cast<const unsigned short*>(scales) + blk);
-        if (zp != nullptr) un.z_raw = __ldg(zp + c.row_zp + (b >> 1));
+#pragma unroll
+      for (int i = 0; i < kWUnits; ++i) {
+        const int n = c.tile < num_tiles ? (c.tile / m_tiles) * kWTile + (t >> 1) + i * (kWTile / kWUnits) : N;
+        c.row_ok[i] = n < N;
+        c.row_blk[i] = static_cast<size_t>(c.row_ok[i] ? n : 0) * kb32;
+        c.row_zp[i] = static_cast<size_t>(c.row_ok[i] ? n : 0) * zp_stride;
       }
-      if (++c.kb == k_blocks) {
-        c.kb = 0;
+    };
+    auto fetch = [&](Cursor& c, W4Unit (&un)[kWUnits]) {
+      // The loads are unconditional (an out-of-range unit reads block 0, which always exists, and is zeroed through
+      // its scale at use): a load under a data-dependent condition tends to become load + select, and the select
+      // would wait for the load here instead of several iterations later.
+      const int b = c.kb * 2 + half;
+#pragma unroll
+      for (int i = 0; i < kWUnits; ++i) {
+        un[i].valid = c.row_ok[i] && b < kb32;
+        const size_t blk = un[i].valid ? c.row_blk[i] + b : 0;
+        un[i].q = __ldg(reinterpret_cast<const uint4*>(qw) + blk);
+        if constexpr (SF32) un[i].s_raw = __float_as_uint(__ldg(static_cast<const float*>(scales) + blk));
+        else un[i].s_raw = __ldg(static_cast<const unsigned short*>(scales) + blk);
+        un[i].z_raw = 0x88u;
+        if (zp != nullptr) un[i].z_raw = __ldg(zp + (un[i].valid ? c.row_zp[i] + (b >> 1) : 0));
+      }
+      c.kb += kWGroups;                          // the group's next k-block
+      while (c.kb >= k_blocks) {
+        c.kb -= k_blocks;
         c.tile += gridDim.x;
         seat(c);
       }
     };
-    Cursor cur{static_cast<int>(blockIdx.x), 0, 0, 0, false};
+    Cursor cur{static_cast<int>(blockIdx.x), group, {}, {}, {}};
+    while (cur.kb >= k_blocks) { cur.kb -= k_blocks; cur.tile += gridDim.x; }
     seat(cur);
-    W4Unit ring[kDepth];
+    W4Unit ring[kDepth][kWUnits];
 #pragma unroll
     for (int d = 0; d < kDepth; ++d) fetch(cur, ring[d]);
-    int stage = 0;
-    uint32_t phase = 0;
+    // ring positions of k-iteration j = group: the slots advance by kWGroups per step of this group
+    int stage = group % Cfg::kStages;
+    uint32_t phase = (group / Cfg::kStages) & 1;
     bool ok = true;
-    const uint32_t row_off = static_cast<uint32_t>(r_tile) * 128u;
-    const uint32_t sw = static_cast<uint32_t>(r_tile & 7);
-    for (long long j0 = 0; ok && j0 < iters; j0 += kDepth) {
+    for (long long j0 = group; ok && j0 < iters; j0 += kDepth * kWGroups) {
 #pragma unroll
       for (int d = 0; d < kDepth; ++d) {
-        if (ok && j0 + d < iters) {
+        if (ok && j0 + d * kWGroups < iters) {
           if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[stage], phase ^ 1))) {
             ok = false;
           } else {
-            uint8_t* sb = smem + stage * Cfg::kStage + Cfg::kStageA + row_off;
-            const uint32_t words[4] = {ring[d].q.x, ring[d].q.y, ring[d].q.z, ring[d].q.w};
-            // this block is half `half` of its k-block: an odd block's zero point is the high nibble of its byte
-            const uint32_t z = half ? (ring[d].z_raw >> 4) & 0xFu : ring[d].z_raw & 0xFu;
-            const uint32_t zbits = 0x4300u | z;                       // bf16 128 + z, exact
-            const uint32_t zz_u = zbits | (zbits << 16);
-            uint32_t ss_u;
-            if constexpr (SF32) {
-              const __nv_bfloat162 t = __float2bfloat162_rn(__uint_as_float(ring[d].s_raw));
-              ss_u = *reinterpret_cast<const uint32_t*>(&t);
-            } else {
-              ss_u = ring[d].s_raw | (ring[d].s_raw << 16);
-            }
-            const __nv_bfloat162 zz = *reinterpret_cast<const __nv_bfloat162*>(&zz_u);
-            const __nv_bfloat162 ss = *reinterpret_cast<const __nv_bfloat162*>(&ss_u);
+            tc_fence_after();              // the tensor core's reads of this slot are ordered before the stores below
 #pragma unroll
-            for (int wi = 0; wi < 4; ++wi) {
-              uint32_t o[4];
-              dequant_word(words[wi], zz, ss, o);
-              const uint32_t chunk = static_cast<uint32_t>(half * 4 + wi) ^ sw;       // 128-byte swizzle: 16-byte chunk index XOR row mod 8
-              *reinterpret_cast<uint4*>(sb + chunk * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+            for (int i = 0; i < kWUnits; ++i) {
+              const int r_tile = (t >> 1) + i * (kWTile / kWUnits);
+              uint8_t* sb = smem + stage * Cfg::kStage + Cfg::kStageA + static_cast<uint32_t>(r_tile) * 128u;
+              const uint32_t sw = static_cast<uint32_t>(r_tile & 7);
+              const W4Unit& un = ring[d][i];
+              const uint32_t words[4] = {un.q.x, un.q.y, un.q.z, un.q.w};
+              // this block is half `half` of its k-block: an odd block's zero point is the high nibble of its byte
+              const uint32_t z = half ? (un.z_raw >> 4) & 0xFu : un.z_raw & 0xFu;
+              const uint32_t zbits = 0x4300u | z;                       // bf16 128 + z, exact
+              const uint32_t zz_u = zbits | (zbits << 16);
+              uint32_t ss_u;
+              if constexpr (SF32) {
+                const __nv_bfloat162 tt = __float2bfloat162_rn(__uint_as_float(un.s_raw));
+                ss_u = *reinterpret_cast<const uint32_t*>(&tt);
+              } else {
+                ss_u = un.s_raw | (un.s_raw << 16);
+              }
+              if (!un.valid) ss_u = 0u;
+              const __nv_bfloat162 zz = *reinterpret_cast<const __nv_bfloat162*>(&zz_u);
+              const __nv_bfloat162 ss = *reinterpret_cast<const __nv_bfloat162*>(&ss_u);
+#pragma unroll
+              for (int wi = 0; wi < 4; ++wi) {
+                uint32_t o[4];
+                dequant_word(words[wi], zz, ss, o);
+                const uint32_t chunk = static_cast<uint32_t>(half * 4 + wi) ^ sw;       // 128-byte swizzle: 16-byte chunk index XOR row mod 8
+                *reinterpret_cast<uint4*>(sb + chunk * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+              }
             }
             fence_proxy_async_smem();      // the tensor core reads these bytes through the async proxy
             __syncwarp();
             if (lane == 0) mbar_arrive(&full_bar[stage]);
             fetch(cur, ring[d]);
-            if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+            stage += kWGroups;
+            if (stage >= Cfg::kStages) { stage -= Cfg::kStages; phase ^= 1; }
           }
         }
       }
@@ -340,7 +369,7 @@ static int launch_w4a16_gemm(const void* x, const void* qweight, const void* sca
                              int M, int N, int K, int ldx, int ldc, int* status, cudaStream_t stream) {
   using Cfg = W4Cfg<MT>;
   CUtensorMap ta;
-  const int rc = make_tmap_bf16_2d(&ta, x, M, K, ldx, kWTile, kWBK);
+  int rc = make_tmap_bf16_2d(&ta, x, M, K, ldx, kWTile, kWBK);
   if (rc != 0) return rc;
   static bool attr_set = false;
   if (!attr_set) {

@@ -334,6 +334,28 @@ def test_w4a16_linear(m, n, k, sym, fp32_scales):
     assert lin._scratch is None                        # no bf16 copy of the weights exists
 
 
+@pytest.mark.parametrize("m,n,k,sym,fp32_scales", [(300, 3584, 3584, True, True), (64, 896, 4864, False, True), (700, 19072, 3584, True, False)])
+def test_w4a16_gemm_repeated_runs_agree_bit_for_bit(m, n, k, sym, fp32_scales):
+    """Eight launches over the same inputs (one tile per CTA; many k-blocks on few CTAs; several tiles per CTA): every
+    result equals the first bit for bit and the fp32 statement to bf16 accuracy -- a slot of the operand ring that is
+    read before it is written, or overwritten while it is read, shows up as a run that differs."""
+    from onnx_genai_b200.ops.quant import QuantLinear
+
+    torch.manual_seed(11)
+    q, s, zp = ref.quantize_w4(torch.randn(n, k) * 0.05, 32, symmetric=sym)
+    if not fp32_scales:
+        s = s.bfloat16()
+    lin = QuantLinear(q, s, zp, None, k=k, device=DEV)
+    x = (torch.randn(m, k, device=DEV) * 0.5).bfloat16()
+    want = x.float() @ ref.dequant_w4(q, s.float(), zp, 32, k).to(DEV).t()
+    first = lin(x).clone()
+    assert float((first.float() - want).abs().max()) < 0.08 + 0.03 * float(want.abs().max())
+    for _ in range(7):
+        assert torch.equal(lin(x), first)
+    torch.cuda.synchronize()
+    ops.check_status()
+
+
 def test_w4a16_gemm_strided_output_matches_the_dense_arm():
     """The int4 tensor-core GEMM writes a column slice of a wider buffer and nothing else, and agrees with the bf16 GEMM
     over a dequantised copy of the same weights (the A/B arm) to bf16 rounding of the weights."""
