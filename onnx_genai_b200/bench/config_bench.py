@@ -88,8 +88,15 @@ def config2(args) -> dict:
             dt = time.perf_counter() - t0
             ttft = float(np.median([r.ttft_s for r in res]))
             decode = sum(r.completion_tokens - 1 for r in res) / max(dt - ttft, 1e-9)
+            wbytes = 0                                   # device bytes of the int4 projections (a bf16 copy would show here)
+            for lw in eng.llm.weights.layers:
+                for lin in (lw.quant or {}).values():
+                    for one in (lin if isinstance(lin, (list, tuple)) else [lin]):
+                        if hasattr(one, "device_weight_bytes"):
+                            wbytes += one.device_weight_bytes()
             rows.append({"batch": batch, "output_tok_s": round(sum(r.completion_tokens for r in res) / dt, 1),
-                         "decode_tok_s": round(decode, 1), "ttft_ms_p50": round(ttft * 1e3, 2)})
+                         "decode_tok_s": round(decode, 1), "ttft_ms_p50": round(ttft * 1e3, 2),
+                         "int4_projection_device_bytes": int(wbytes)})
             del eng
             torch.cuda.empty_cache()
         ops.check_status()
