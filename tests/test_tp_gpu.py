@@ -78,3 +78,12 @@ def test_moe_combine_over_the_exchange_kernel_matches_single_gpu(world, single_m
         assert _err(got, ref) < 3e-2, (world, name, _err(got, ref))
     assert fused["launches"].get("tp_signal_rows", 0) > 0 and fused["launches"].get("moe_grouped_gemm", 0) > 0
     assert len(fused["tokens"]) == len(single_moe["tokens"])
+
+
+def test_pipeline_stages_on_two_gpus_match_one(single, tmp_path):
+    """Two pipeline stages (layers 2 + 1): the residual stream crosses GPUs by NCCL send / recv, the last stage samples
+    and broadcasts; logits and tokens against one GPU holding every layer."""
+    _need(2)
+    piped = _run(2, "pp", str(tmp_path / "pp.pt"), 29790)
+    assert _err(piped, single["logits"]) < 3e-2
+    assert len(piped["tokens"]) == len(single["tokens"])
