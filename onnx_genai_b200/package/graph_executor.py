@@ -227,15 +227,18 @@ def _matmul_nbits(ins, attrs):
 
 _E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
 _IQ4_NL = (-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113)
-_BLOCK_FORMATS = {"mxfp4": (32, 17), "iq4_nl": (32, 18)}        # values per block, bytes per block
+_BLOCK_FORMATS = {"mxfp4": (32, 17), "iq4_nl": (32, 18), "iq4_xs": (256, 136)}        # values per block, bytes per block
 
 
 def decode_weight_blocks(packed, fmt: str):
-    """[n, blocks, bytes] uint8 -> [n, blocks * 32] float32 for the block formats of ``BlockQuantizedMatMul``.
+    """[n, blocks, bytes] uint8 -> [n, blocks * values per block] float32 for the block formats of ``BlockQuantizedMatMul``.
 
     ``mxfp4``: one E8M0 scale byte (2^(e-127); 255 is NaN) then 16 bytes of E2M1 codes, where byte ``j`` holds element
     ``j`` in its low nibble and element ``j + 16`` in its high nibble.  ``iq4_nl``: a little-endian fp16 scale then 16
-    bytes laid out the same way, the codes indexing the 16-entry non-linear table.
+    bytes laid out the same way, the codes indexing the 16-entry non-linear table.  ``iq4_xs``: super-blocks of 256
+    values in 136 bytes -- fp16 scale d, 16 bits holding the two high bits of eight 6-bit sub-block scales, 4 bytes holding
+    their low nibbles, then 128 bytes of codes for eight sub-blocks of 32 (16 bytes each, low nibble = element j, high
+    nibble = element j + 16); a sub-block's values are d * (scale - 32) * table[code].
     """
     if fmt not in _BLOCK_FORMATS:
         raise GraphExecutionError(f"BlockQuantizedMatMul format {fmt!r} is not covered here (covered: {sorted(_BLOCK_FORMATS)})")
@@ -243,6 +246,17 @@ def decode_weight_blocks(packed, fmt: str):
     if packed.dim() != 3 or packed.shape[-1] != nbytes:
         raise GraphExecutionError(f"{fmt} weights must be [N, blocks, {nbytes}] bytes, got {list(packed.shape)}")
     b = packed.to(torch.int32)
+    if fmt == "iq4_xs":
+        d = (b[..., 0] | (b[..., 1] << 8)).to(torch.int16).view(torch.float16).float()                       # [n, blocks]
+        high = b[..., 2] | (b[..., 3] << 8)
+        sub = torch.arange(8, device=packed.device)
+        low = (b[..., 4:8][..., sub // 2] >> (4 * (sub % 2))) & 0xF                                           # [n, blocks, 8]
+        ls = low | (((high[..., None] >> (2 * sub)) & 3) << 4)
+        dl = d[..., None] * (ls - 32).float()
+        q = b[..., 8:].reshape(*b.shape[:2], 8, 16)
+        idx = torch.cat([q & 0xF, (q >> 4) & 0xF], dim=-1).long()                                             # [n, blocks, 8, 32]
+        vals = torch.tensor(_IQ4_NL, device=packed.device, dtype=torch.float32)[idx] * dl[..., None]
+        return vals.reshape(packed.shape[0], -1)
     head = 1 if fmt == "mxfp4" else 2
     codes = b[..., head:]
     idx = torch.cat([codes & 0xF, (codes >> 4) & 0xF], dim=-1).long()

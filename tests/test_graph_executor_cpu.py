@@ -369,6 +369,40 @@ def test_block_quantized_matmul_mxfp4_and_iq4_nl():
         OPS["BlockQuantizedMatMul"]([x, packed, None], {"K": 70, "N": 5, "format": "mxfp4", "block_layout_version": 2})
 
 
+def test_block_quantized_matmul_iq4_xs_superblocks():
+    """iq4_xs: the pinned vector of the reference's unit test (d = 0.5, every 6-bit sub-scale 37, every code byte 0x98 ->
+    sixteen 2.5 then sixteen 32.5 per sub-block), then random super-blocks against a scalar statement of the layout."""
+    import struct
+
+    from onnx_genai_b200.package.graph_executor import _IQ4_NL, OPS, decode_weight_blocks
+
+    raw = bytearray(struct.pack("<e", 0.5)) + bytearray(struct.pack("<H", 0xAAAA)) + bytearray([0x55] * 4) + bytearray([0x98] * 128)
+    w = decode_weight_blocks(torch.tensor(list(raw), dtype=torch.uint8).reshape(1, 1, 136), "iq4_xs")[0]
+    assert w.tolist() == ([2.5] * 16 + [32.5] * 16) * 8
+
+    g = torch.Generator().manual_seed(3)
+    packed = torch.randint(0, 256, (3, 2, 136), dtype=torch.uint8, generator=g)
+    packed[..., 0:2] = torch.tensor(list(struct.pack("<e", 0.03125)), dtype=torch.uint8)      # a finite fp16 scale
+    got = decode_weight_blocks(packed, "iq4_xs")
+    want = torch.zeros(3, 512)
+    for n in range(3):
+        for blk in range(2):
+            b = packed[n, blk].tolist()
+            d = struct.unpack("<e", bytes(b[0:2]))[0]
+            high = b[2] | (b[3] << 8)
+            for ib in range(8):
+                ls = ((b[4 + ib // 2] >> (4 * (ib % 2))) & 0xF) | (((high >> (2 * ib)) & 3) << 4)
+                dl = d * (ls - 32)
+                qs = b[8 + 16 * ib: 8 + 16 * ib + 16]
+                for j in range(16):
+                    want[n, blk * 256 + ib * 32 + j] = dl * _IQ4_NL[qs[j] & 0xF]
+                    want[n, blk * 256 + ib * 32 + j + 16] = dl * _IQ4_NL[qs[j] >> 4]
+    assert torch.allclose(got, want, rtol=0, atol=1e-6)
+    x = torch.randn(4, 300)                            # K = 300: the second super-block is partial
+    y = OPS["BlockQuantizedMatMul"]([x, packed, None], {"K": 300, "N": 3, "format": "iq4_xs", "block_layout_version": 1})
+    assert torch.allclose(y, x @ want[:, :300].T, atol=1e-4)
+
+
 def test_contrib_attention_variants_nonzero_prelu():
     from onnx_genai_b200.package.graph_executor import OPS
 
