@@ -50,6 +50,28 @@ class Tracer:
 
         self.path = runtime_config().trace_path or None      # ONNX_GENAI_TRACE
         self.enabled = self.path is not None
+        # ONNX_GENAI_TRACE_NVTX=1: every span also opens an NVTX range, so an external profiler that records NVTX
+        # (Nsight Systems, a CUPTI-based collector) sees the engine's stages on the same timeline as the kernels.  This
+        # is the hand-off to vendor collectors that the reference does through its ITT / CUPTI tracer back ends
+        # (crates/onnx-runtime-tracer/src/itt.rs, cupti.rs); no collector is embedded here.
+        import os
+
+        self.nvtx = None
+        if os.environ.get("ONNX_GENAI_TRACE_NVTX", "0") not in ("", "0"):
+            self.enable_nvtx()
+
+    def enable_nvtx(self, push=None, pop=None):
+        """Mirror spans as NVTX ranges (``push(name)`` / ``pop()`` default to torch.cuda.nvtx; tests pass fakes)."""
+        if push is None or pop is None:
+            try:
+                import torch
+
+                push, pop = torch.cuda.nvtx.range_push, torch.cuda.nvtx.range_pop
+            except Exception:        # no CUDA build: ranges have nowhere to go
+                self.nvtx = None
+                return False
+        self.nvtx = (push, pop)
+        return True
 
     def start(self, path):
         self.path, self.enabled = path, True
@@ -60,9 +82,18 @@ class Tracer:
         class _Span:
             def __enter__(self):
                 self.t0 = time.perf_counter()
+                self.ranged = False
+                if tracer.nvtx is not None:
+                    try:
+                        tracer.nvtx[0](f"{cat}:{name}")
+                        self.ranged = True
+                    except Exception:
+                        tracer.nvtx = None           # NVTX is not usable in this process: stop trying
                 return self
 
             def __exit__(self, *exc):
+                if self.ranged and tracer.nvtx is not None:
+                    tracer.nvtx[1]()
                 if tracer.enabled:
                     with tracer.lock:
                         tracer.spans.append((name, self.t0, time.perf_counter(), cat))
