@@ -106,6 +106,9 @@ def main():
     ap.add_argument("--greedy", action="store_true", help="greedy decoding instead of temperature 0.7 / top-p 0.9 (the MoE config)")
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
     ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "fused"])
+    ap.add_argument("--tp", type=int, default=0,
+                    help="tensor-parallel degree (0 = all GPUs, the headline layout); with a smaller value the GPUs form --gpus / --tp "
+                         "replicas that share the concurrent requests, each with its own engine (a deployment layout, labelled in the output)")
     ap.add_argument("--token-multiple", type=int, default=128,
                     help="the scheduler trims the last prefill chunk so a step's token count is a multiple of this (GEMM M tile)")
     ap.add_argument("--deadline", type=int, default=900, help="seconds after which a stuck run dumps stacks and exits")
@@ -148,9 +151,26 @@ def main():
     if args.impl == "baseline":
         os.environ["OGB_BASELINE"] = "1"
         ops.set_baseline(True)
+    model = preset(args.model)
+    # Replicas x tensor parallelism: rank r is rank r % tp of replica r // tp.  Every replica runs its own engine over its
+    # own share of the concurrent requests; the timed regions are bracketed by barriers over all ranks.
+    tp = args.tp if args.tp > 0 else world      # the headline metric is tensor parallelism over all GPUs; --tp asks for replicas
+    if world % tp or args.concurrency % (world // tp):
+        if rank == 0:
+            print(f"bench.py: --tp {tp} does not divide {world} GPUs, or {world // tp} replicas do not divide {args.concurrency} requests", file=sys.stderr)
+        return 2
+    dp, replica, tp_rank = world // tp, rank // tp, rank % tp
+    wcomm = comm_mod.NcclComm() if world > 1 else None          # all ranks: barriers and the reductions of the report
+    args.concurrency //= dp
+    args.latency_requests = (args.latency_requests + dp - 1) // dp
     comm = None
-    if world > 1:
-        comm = comm_mod.NcclComm()
+    if tp > 1:
+        comm = wcomm
+        if dp > 1:
+            import torch.distributed as dist
+
+            groups = [dist.new_group(ranks=list(range(g * tp, (g + 1) * tp))) for g in range(dp)]   # every rank creates every group
+            comm = comm_mod.NcclComm(groups[replica])
         if args.comm in ("auto", "fused") and args.impl == "ours":
             try:
                 from onnx_genai_b200.parallel.fused import FusedComm
@@ -160,7 +180,6 @@ def main():
                 if rank == 0:
                     print(f"bench.py: fused communicator unavailable ({exc}); using NCCL", file=sys.stderr)
 
-    model = preset(args.model)
     invalid = None
     if args.layers:
         model = model.replace(num_layers=args.layers)
@@ -171,8 +190,8 @@ def main():
                        token_multiple=args.token_multiple,
                        native_executor=not (args.no_native_executor or args.profile_ops),
                        sync_sampled_tokens=True)
-    eng = LLMEngine(cfg, device=dev, tp=world, rank=rank, comm=comm)
-    rng = np.random.default_rng(1234)  # same stream on every rank: replicas schedule identically
+    eng = LLMEngine(cfg, device=dev, tp=tp, rank=tp_rank, comm=comm)
+    rng = np.random.default_rng(1234 + replica)  # same stream on every rank of a replica: they schedule identically
 
     def new_request():
         n = int(rng.integers(args.min_prompt, args.max_prompt + 1))
@@ -226,8 +245,8 @@ def main():
     shapes = []
     launches0 = sum(ops.launch_counts.values())
     h2d0, d2h0 = eng.h2d_bytes, eng.d2h_bytes
-    if comm is not None:
-        comm.barrier()
+    if wcomm is not None:
+        wcomm.barrier()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     e2e_tokens = 0
@@ -238,8 +257,8 @@ def main():
         si = eng.si
         shapes.append((si.num_tokens, si.num_decode, si.num_prefill_seqs, si.num_tiles, si.num_logit_rows, si.max_ctx,
                        eng.model.decode_splits))
-    if comm is not None:
-        comm.barrier()
+    if wcomm is not None:
+        wcomm.barrier()
     torch.cuda.synchronize()
     t1 = time.perf_counter()
     e2e_s = t1 - t0
@@ -270,8 +289,8 @@ def main():
 
     for i in range(min(3, args.steps)):
         replay(i)
-    if comm is not None:
-        comm.barrier()
+    if wcomm is not None:
+        wcomm.barrier()
     torch.cuda.synchronize()
     launches1 = sum(ops.launch_counts.values())
     tp_counts0 = (eng.model.native_counter(1), eng.model.native_counter(2), ops.launch_counts["gemm_bf16_scatter"],
@@ -282,8 +301,8 @@ def main():
     for i in range(args.steps):
         replay(i)
     ev1.record()
-    if comm is not None:
-        comm.barrier()
+    if wcomm is not None:
+        wcomm.barrier()
     torch.cuda.synchronize()
     td1 = time.perf_counter()
     dev_ms = ev0.elapsed_time(ev1)
@@ -303,27 +322,27 @@ def main():
         try:
             ops.set_baseline(True)
             m.fused_comm, m.native = None, None
-            if world > 1:
+            if tp > 1:
                 m.comm = getattr(comm, "base", comm)
             for i in range(min(3, args.steps)):
                 replay(i)
-            if comm is not None:
-                comm.barrier()
+            if wcomm is not None:
+                wcomm.barrier()
             torch.cuda.synchronize()
             b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             b0.record()
             for i in range(args.steps):
                 replay(i)
             b1.record()
-            if comm is not None:
-                comm.barrier()
+            if wcomm is not None:
+                wcomm.barrier()
             torch.cuda.synchronize()
             base_ms = b0.elapsed_time(b1)
         finally:
             ops.set_baseline(False)
             m.fused_comm, m.comm, m.native = saved
-        if comm is not None:
-            base_ms = comm.max_float(base_ms)
+        if wcomm is not None:
+            base_ms = wcomm.max_float(base_ms)
         eng.check_device_status()
 
     # ---- latency sample: requests that arrive after the timed regions (the replays above stretch the wall-clock gaps of
@@ -360,14 +379,18 @@ def main():
             sh = shapes[0]
             shape_ = StepShape(decode_rows=int(sh[1]), prefill_tokens=int(sh[0]) - int(sh[1]), mean_context=(args.min_prompt + args.max_prompt) // 2 + args.output_tokens // 2,
                                prefill_context=(args.min_prompt + args.max_prompt) // 4)
-            print(_dg.diagnose_samples(_dg.samples_from_profile(agg, model, shape_, tp=world, steps=n_prof), steps=n_prof).report(), file=sys.stderr)
+            print(_dg.diagnose_samples(_dg.samples_from_profile(agg, model, shape_, tp=tp, steps=n_prof), steps=n_prof).report(), file=sys.stderr)
         except Exception as exc:   # the diagnosis is a convenience: never let it break the bench line
             print(f"diagnosis skipped: {exc}", file=sys.stderr)
 
-    if comm is not None:
-        dev_ms = comm.max_float(dev_ms)
-        e2e_s = comm.max_float(e2e_s)
     dev_tokens = sum(s[4] for s in shapes)
+    if wcomm is not None:
+        dev_ms = wcomm.max_float(dev_ms)
+        e2e_s = wcomm.max_float(e2e_s)
+        if dp > 1:      # tokens of all replicas: every rank of a replica holds the same count, so the sum over ranks counts it tp times
+            tot = torch.tensor([float(dev_tokens), float(e2e_tokens)], dtype=torch.float64, device=dev)
+            wcomm.all_reduce(tot)
+            dev_tokens, e2e_tokens = float(tot[0]) / tp, float(tot[1]) / tp
     value = dev_tokens / (dev_ms / 1e3)
     e2e_value = e2e_tokens / e2e_s
 
@@ -383,14 +406,14 @@ def main():
     if rank == 0:
         result = {
             "metric": "output tok/s (%s-shape, continuous batching, %d concurrent, %s=%d)" % (
-                {"qwen2.5-7b": "Qwen2.5-7B", "qwen3-30b-a3b": "Qwen3-30B-A3B"}.get(model.name, model.name), args.concurrency,
-                "TP=EP" if model.moe.num_experts > 0 else "TP", world),
+                {"qwen2.5-7b": "Qwen2.5-7B", "qwen3-30b-a3b": "Qwen3-30B-A3B"}.get(model.name, model.name), args.concurrency * dp,
+                "TP=EP" if model.moe.num_experts > 0 else "TP", tp) + (" x %d replicas" % dp if dp > 1 else ""),
             "value": round(value, 1), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(dev_ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": round(value / base_value, 4) if base_value else None, "dtype": "bf16", "data": "synthetic (uniform-random token ids, N(0,0.02) weights)",
             "impl": args.impl,
-            "config": {"model": model.name + "-shape", "global_batch": args.concurrency, "seq_len": f"prompt U[{args.min_prompt},{args.max_prompt}] + {args.output_tokens} out",
-                       "parallelism": f"tp{world}", "kv": "paged, 16-token bf16 pages", "sampling": "greedy" if args.greedy else "temperature 0.7, top-p 0.9",
+            "config": {"model": model.name + "-shape", "global_batch": args.concurrency * dp, "seq_len": f"prompt U[{args.min_prompt},{args.max_prompt}] + {args.output_tokens} out",
+                       "parallelism": f"tp{tp}" + (f" x dp{dp} (each replica serves {args.concurrency} of the requests)" if dp > 1 else ""), "kv": "paged, 16-token bf16 pages", "sampling": "greedy" if args.greedy else "temperature 0.7, top-p 0.9",
                        "l2": "per-step inputs (weights + KV) exceed L2; no explicit flush",
                        "comm": getattr(comm, "backend_name", "none"),
                        "tokens_per_step_mean": round(sum(s[0] for s in shapes) / len(shapes), 1),
@@ -403,6 +426,7 @@ def main():
                         "epilogues, ncclAllReduce for the row-parallel projections, stand-alone RMSNorm; attention and sampler kernels "
                         "as in the product arm; device-timed, max over ranks" % args.steps,
                 "value": round(base_value, 1), "unit": "tok/s", "ms_per_step": round(base_ms / args.steps, 4)},
+            "latency_scope": "replica 0" if dp > 1 else "all requests",
             "tp_launches_per_step": {
                 "gemm_bf16_scatter": ((tp_counts1[0] - tp_counts0[0]) + (tp_counts1[2] - tp_counts0[2])) / args.steps,
                 "tp_exchange_norm": ((tp_counts1[1] - tp_counts0[1]) + (tp_counts1[3] - tp_counts0[3])) / args.steps},

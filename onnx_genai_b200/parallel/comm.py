@@ -89,7 +89,8 @@ class NcclComm:
         return t
 
     def broadcast(self, t, src=0):
-        dist.broadcast(t, src=src, group=self.group)
+        """``src`` is a rank of this communicator's group (not a global rank)."""
+        dist.broadcast(t, src=dist.get_global_rank(self.group, src) if self.group is not None else src, group=self.group)
         return t
 
     def all_gather(self, out, t):

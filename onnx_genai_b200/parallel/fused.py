@@ -248,7 +248,7 @@ class FusedComm:
         import torch.distributed._symmetric_memory as symm_mem
 
         buf = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
-        hdl = symm_mem.rendezvous(buf, dist.group.WORLD)
+        hdl = symm_mem.rendezvous(buf, getattr(self.base, "group", None) or dist.group.WORLD)   # the ranks of this communicator only
         buf.zero_()
         self._symm = (buf, hdl)
         self.peer_ptrs = [int(p) for p in hdl.buffer_ptrs]
@@ -268,7 +268,7 @@ class FusedComm:
         if rc != 0:
             raise RuntimeError(f"cudaIpcGetMemHandle failed ({rc})")
         handles = [None] * tp
-        dist.all_gather_object(handles, bytes(handle.raw))
+        dist.all_gather_object(handles, bytes(handle.raw), group=getattr(self.base, "group", None))
         self.peer_ptrs = []
         for p in range(tp):
             if p == self.rank:
