@@ -1,5 +1,4 @@
-
-
+"""Trace spans: the optional NVTX hand-off to external profilers."""
 def test_spans_mirror_into_nvtx_ranges_when_asked():
     """With the NVTX hand-off on, every span pushes and pops one range named category:name, nested in order; a push
     that raises turns the hand-off off instead of breaking the span."""
