@@ -583,9 +583,50 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+int encode_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                        uint32_t box_cols);
+
+// Descriptors that were encoded before, per thread: a tensor map is a pure function of (address, extents, stride, box),
+// the weights and the static activation buffers come back with the same values at every step, and a lookup costs a tenth
+// of an encode.  The table is dropped when it grows past a bound (a process that keeps making new shapes).
+struct TmapKey {
+  const void* base;
+  uint64_t rows, cols, ld;
+  uint32_t box_rows, box_cols;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows && box_cols == o.box_cols;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    uint64_t h = reinterpret_cast<uint64_t>(k.base) * 0x9E3779B97F4A7C15ull;
+    h ^= (k.rows + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+    h ^= (k.cols * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2));
+    h ^= (k.ld + (static_cast<uint64_t>(k.box_rows) << 32) + k.box_cols + (h << 6) + (h >> 2));
+    return static_cast<size_t>(h);
+  }
+};
+
 // 2-D row-major bf16 matrix [rows, cols] with row stride `ld` elements; box = {64 cols, box_rows}.
 int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
                       uint32_t box_cols) {
+  static thread_local std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  const TmapKey key{base, rows, cols, ld, box_rows, box_cols};
+  auto hit = cache.find(key);
+  if (hit != cache.end()) {
+    *out = hit->second;
+    return 0;
+  }
+  const int rc = encode_tmap_bf16_2d(out, base, rows, cols, ld, box_rows, box_cols);
+  if (rc == 0) {
+    if (cache.size() > 16384) cache.clear();
+    cache.emplace(key, *out);
+  }
+  return rc;
+}
+
+int encode_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                        uint32_t box_cols) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return -1;
   cuuint64_t dims[2] = {cols, rows};
