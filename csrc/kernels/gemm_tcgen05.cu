@@ -702,20 +702,25 @@ static bool stream_k_enabled() {
   return g_stream_k == 1;
 }
 // Stream-K pays when round-robin tiles would leave a large part of the last wave idle and the fix-up is cheap next
-// to a tile: every CTA boundary that falls inside a tile costs one fp32 partial written and read back (about 5 us,
-// i.e. about 13 k-blocks of tensor-core time), so the estimate adds 13 / k_blocks waves to the exact share.
-static bool stream_k_applies(int tiles, int k_blocks, int sms) {
+// to a tile: every CTA boundary that falls inside a tile costs one fp32 partial written and read back and a flag wait
+// in the finisher.  `fix` is that cost in k-blocks of tensor-core time.  Measured on the 7B shapes (tile widths 32 - 256
+// with and without stream-K, M = 32 - 1472): about 40 for a plain epilogue -- with 13 the estimate chose wide stream-K
+// tiles for K = 3584 projections that ran 1.3 - 1.5x slower than plain 128-wide tiles -- while the scatter epilogue of
+// the tensor-parallel path, whose tiles end in stores to other GPUs, keeps the 13 it was tuned with.
+constexpr float kSkFixPlain = 40.0f;
+constexpr float kSkFixScatter = 13.0f;
+static bool stream_k_applies(int tiles, int k_blocks, int sms, float fix) {
   if (!stream_k_enabled() || tiles % sms == 0 || static_cast<long long>(tiles) * k_blocks < 2LL * sms) return false;
   const float w = static_cast<float>(tiles) / static_cast<float>(sms);
   const float dp = static_cast<float>((tiles + sms - 1) / sms);
-  const float sk = w + 13.0f / static_cast<float>(k_blocks);
+  const float sk = w + fix / static_cast<float>(k_blocks);
   return sk < 0.93f * dp;
 }
 // Relative duration of a launch with `tiles` tiles of relative cost `cost`: whole waves when tiles are dealt
 // round-robin, the exact share plus the fix-up when stream-K spreads the k-blocks evenly.
-static float launch_cost(int tiles, int k_blocks, int sms, float cost) {
-  if (stream_k_applies(tiles, k_blocks, sms))
-    return (static_cast<float>(tiles) / static_cast<float>(sms) + 13.0f / static_cast<float>(k_blocks)) * cost;
+static float launch_cost(int tiles, int k_blocks, int sms, float cost, float fix) {
+  if (stream_k_applies(tiles, k_blocks, sms, fix))
+    return (static_cast<float>(tiles) / static_cast<float>(sms) + fix / static_cast<float>(k_blocks)) * cost;
   return static_cast<float>((tiles + sms - 1) / sms) * cost;
 }
 
@@ -748,7 +753,7 @@ static int launch_gemm(const void* A, const void* W, void* C, const void* bias, 
   uint32_t* sk_flags = nullptr;
   uint32_t sk_seq = 0;
   const int k_blocks = (K + kBK - 1) / kBK;
-  if (group_tab == nullptr && stream_k_applies(tiles, k_blocks, sms)) {
+  if (group_tab == nullptr && stream_k_applies(tiles, k_blocks, sms, EPI == kEpiScatter ? kSkFixScatter : kSkFixPlain)) {
     SkWorkspace* w = sk_workspace(stream, sms);
     if (w != nullptr) {
       grid = sms;
@@ -830,7 +835,7 @@ extern "C" int ogb_gemm_bf16_wait(const void* A, const void* W, void* C, const v
     for (int i = 0; i < 5; ++i) {
       if (cand[i] < 128 && m_tiles > 3) break;  // narrow tiles only pay off for decode-sized M
       const int tiles = m_tiles * ((N + cand[i] - 1) / cand[i]);
-      const float t = launch_cost(tiles, (K + kBK - 1) / kBK, sms, cost[i]);
+      const float t = launch_cost(tiles, (K + kBK - 1) / kBK, sms, cost[i], kSkFixPlain);
       if (t < best - 1e-6f) { best = t; bn = cand[i]; }
     }
   }
@@ -864,7 +869,7 @@ extern "C" int ogb_gemm_bf16_scatter(const void* A, const void* W, int M, int N,
     bn = 256;
     for (int i = 0; i < 3; ++i) {
       const int tiles = m_tiles * ((N + cand[i] - 1) / cand[i]);
-      const float t = launch_cost(tiles, (K + kBK - 1) / kBK, sms, cost[i]);
+      const float t = launch_cost(tiles, (K + kBK - 1) / kBK, sms, cost[i], kSkFixScatter);
       if (t < best - 1e-6f) { best = t; bn = cand[i]; }
     }
   }
