@@ -108,6 +108,17 @@ def _load(args):
     if proposer == "draft" and not getattr(args, "draft_model", ""):
         raise SystemExit("--proposer draft needs --draft-model DIR")
     extra = {"kv_max_pages": args.kv_max_pages} if getattr(args, "kv_max_pages", 0) > 0 else {}
+    # Launched by torchrun (WORLD_SIZE > 1): the processes form one tensor-parallel group; this function returns on rank 0
+    # only -- the other ranks follow the leader's requests inside it and exit when the leader does.
+    tp_world = int(os.environ.get("WORLD_SIZE", "1"))
+    if tp_world > 1:
+        from .engine.tp_driver import bootstrap
+
+        tp_rank, tp_world, tp_dev, tp_comm = bootstrap(None if dev == "auto" else dev)
+        dev = str(tp_dev)
+        if speculative:
+            raise SystemExit("speculative decoding is not available under tensor parallelism (launch one process for it)")
+        extra.update(tp=tp_world, tp_rank=tp_rank, comm=tp_comm)
     if getattr(args, "context_cache", False):
         extra["context_cache"] = True
     if getattr(args, "weight_offload_layers", 0) > 0:
@@ -117,6 +128,23 @@ def _load(args):
                           max_draft_tokens=(getattr(args, "draft_tokens", 0) or rt.spec_tokens) if speculative else 0,
                           draft_model_dir=(getattr(args, "draft_model", "") or None) if proposer in ("auto", "draft") else None,
                           max_seq_len=args.max_context or None, **extra)
+    if tp_world > 1:
+        if tp_rank != 0:
+            steps = eng.follow()
+            print(f"rank {tp_rank}: followed {steps} steps", file=sys.stderr)
+            import torch.distributed as dist
+
+            dist.barrier()
+            raise SystemExit(0)
+        import atexit
+
+        def _release_followers():
+            import torch.distributed as dist
+
+            eng.shutdown()
+            dist.barrier()
+
+        atexit.register(_release_followers)
     if proposer == "ngram":
         from .speculative import NgramProposer
 

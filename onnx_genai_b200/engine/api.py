@@ -123,11 +123,14 @@ class Engine:
     def from_dir(cls, model_dir: str, device=None, page_size: int | None = None, max_seqs: int = 32,
                  max_seq_len: int | None = None, num_pages: int = 0, max_tokens_per_step: int = 2048,
                  kv_dtype: str = "bf16", max_draft_tokens: int = 0, draft_model_dir: str | None = None,
-                 keep_int4: bool | None = None, context_cache=None, **engine_kw):
+                 keep_int4: bool | None = None, context_cache=None, tp: int = 1, tp_rank: int = 0, comm=None, **engine_kw):
         """Load a flat model directory or a model package.  ``page_size`` is accepted for API
         compatibility; pages hold 16 tokens (the attention kernels' tile).  ``context_cache``: True (or a directory) keeps the
         lowered weight layout beside the model (``ogb_context/``) and reads it back on the next load instead of parsing and
-        packing the graph again; ``ONNX_GENAI_CONTEXT_CACHE=1`` turns it on for every load."""
+        packing the graph again; ``ONNX_GENAI_CONTEXT_CACHE=1`` turns it on for every load.  ``tp`` > 1: this process is
+        rank ``tp_rank`` of a tensor-parallel group that talks over ``comm`` (engine/tp_driver.py ``bootstrap`` gives all
+        three from the launcher's environment); it loads its shard of the weights, rank 0 serves and the others call
+        :meth:`follow`."""
         if page_size not in (None, 16):
             raise ValueError(f"page_size={page_size} is not supported: KV pages hold 16 tokens")
         # precedence: the caller's arguments > ONNX_GENAI_* environment (utils/runtime_config.py) > metadata > built-in
@@ -145,6 +148,10 @@ class Engine:
                                      device="gpu" if str(device).startswith("cuda") else "cpu")
         meta = d.load_metadata()
         dtype = torch.bfloat16 if str(device).startswith("cuda") else torch.float32
+        if tp > 1:
+            if comm is None:
+                raise ValueError("tensor parallelism needs a communicator: use engine.tp_driver.bootstrap() under a launcher")
+            keep_int4, context_cache = False, False       # shards are cut from dense weights; the cache holds whole models
         if keep_int4 is None:   # MatMulNBits weights stay packed wherever a kernel reads them directly
             from ..ops import cpu as _cpu_ops
 
@@ -158,7 +165,7 @@ class Engine:
             cfg, weights, cache_hit = lower_with_cache(d.model_path, lambda: load_any(d.model_path), dtype, device, keep_int4,
                                                        cache_dir=context_cache if isinstance(context_cache, str) else None)
         else:
-            cfg, weights, _ = lower_decoder(load_any(d.model_path), dtype=dtype, device=device, keep_int4=keep_int4)
+            cfg, weights, _ = lower_decoder(load_any(d.model_path), dtype=dtype, device=device, keep_int4=keep_int4, tp=tp, rank=tp_rank)
         if meta.vocab_size and meta.vocab_size != cfg.vocab:
             raise md.MetadataError(f"{d.metadata_path}: model.vocab_size={meta.vocab_size} but the graph's embedding has "
                                    f"{cfg.vocab} rows; fix the metadata or re-export the model")
@@ -187,9 +194,15 @@ class Engine:
         ecfg = EngineConfig(model=cfg, num_pages=num_pages, max_seqs=max_seqs, max_seq_len=max_seq_len,
                             max_tokens_per_step=max_tokens_per_step, prefill_chunk=meta.chunked_prefill_size or 2048,
                             kv_dtype=kv_dtype, max_draft_tokens=max_draft_tokens, **engine_kw)
-        llm = LLMEngine(ecfg, weights=weights, device=device)
-        draft = cls.from_dir(draft_model_dir, device=device, max_seqs=max_seqs, max_seq_len=max_seq_len) if draft_model_dir else None
+        llm = LLMEngine(ecfg, weights=weights, device=device, tp=tp, rank=tp_rank, comm=comm)
+        draft = cls.from_dir(draft_model_dir, device=device, max_seqs=max_seqs, max_seq_len=max_seq_len) if (draft_model_dir and tp == 1) else None
         eng = cls(llm, tok, d.chat_template, meta, eos, draft)
+        if tp > 1:
+            from .tp_driver import TpControl
+
+            eng.tp_control = TpControl(llm, tp_rank, tp, getattr(getattr(comm, "base", comm), "group", None))
+            if tp_rank == 0:
+                eng.tp_control.install()
         eng.context_cache_hit = cache_hit            # None: cache off, False: written by this load, True: read back
         mtp_path = os.path.join(os.path.dirname(d.model_path), "mtp_head.safetensors")
         if max_draft_tokens > 0 and draft is None and os.path.exists(mtp_path):
@@ -227,6 +240,16 @@ class Engine:
         greedy = opt.greedy or opt.temperature == 0
         temperature = 0.0 if greedy else (opt.temperature if opt.temperature is not None else defaults.get("temperature", 1.0))
         stop_ids = tuple(opt.stop_token_ids) + (() if opt.ignore_eos else self.eos_token_ids)
+        tpc = getattr(self, "tp_control", None)
+        if tpc is not None:
+            # what the followers cannot mirror is refused before the request reaches any scheduler
+            if opt.constraint is not None or sampler is not None or processors or opt.logprobs:
+                tpc.refuse("constrained decoding / a custom sampler or processor / log-probabilities")
+            eff0 = GenerateOptions(**{**opt.__dict__, "greedy": greedy})
+            if procs.device_sampling_plan(procs.build_processor_chain(eff0, len(ids), np.random.default_rng(0)), eff0, False) == "host":
+                tpc.refuse("this combination of sampling options (it runs on the host)")
+            if opt.speculative:
+                tpc.refuse("speculative decoding")
         if getattr(self, "kv_offload", None) is not None:
             self.kv_offload.restore(ids)
         sid = self.llm.add_request(np.asarray(ids, dtype=np.int32), opt.max_new_tokens, temperature=temperature,
@@ -449,6 +472,8 @@ class Engine:
         """[n, hidden] fp32: the final-normed hidden state of each input's last token (last-token pooling, the
         usual choice for decoder-only models), L2-normalised unless ``normalize`` is False.  Inputs are strings
         or token-id lists; they run as one continuous batch of prefill-only requests."""
+        if getattr(self, "tp_control", None) is not None:
+            self.tp_control.refuse("embeddings (hidden-state taps)")
         if isinstance(inputs, str) or (inputs and isinstance(inputs[0], int)):
             inputs = [inputs]
         sids = []
@@ -482,6 +507,17 @@ class Engine:
         self._next_session += 1
         self.sessions[sid] = _Session(sid)
         return sid
+
+    def follow(self) -> int:
+        """Ranks other than 0 of a tensor-parallel group: mirror the leader's requests and steps until it shuts down."""
+        if getattr(self, "tp_control", None) is None or self.tp_control.rank == 0:
+            raise RuntimeError("follow() is for ranks 1..n-1 of an engine loaded with tp > 1")
+        return self.tp_control.follow()
+
+    def shutdown(self) -> None:
+        """Rank 0 of a tensor-parallel group: release the followers.  A no-op for a single-GPU engine."""
+        if getattr(self, "tp_control", None) is not None:
+            self.tp_control.shutdown()
 
     def close_session(self, session_id: int) -> None:
         self.sessions.pop(session_id, None)

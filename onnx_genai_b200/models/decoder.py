@@ -91,7 +91,7 @@ def random_weights(cfg: DecoderConfig, device, tp: int = 1, rank: int = 0, seed:
     kv_rows = torch.tensor([h * d + i for h in hs.kv_heads for i in range(d)], device=dev)
     moe = cfg.moe.num_experts > 0
     if not moe:
-        i0, i1 = shard_range(cfg.intermediate, tp, rank, 32 if tp > 1 else 1)
+        i0, i1 = shard_range(cfg.intermediate, tp, rank, math.gcd(cfg.intermediate, 32) if tp > 1 else 1)
         half = pick_swiglu_half((i1 - i0) + (-(i1 - i0)) % 64 if (i1 - i0) % 32 else (i1 - i0))
     else:
         half = pick_swiglu_half(cfg.moe.expert_intermediate)

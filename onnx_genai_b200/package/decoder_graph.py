@@ -12,6 +12,8 @@ executor runs.  A graph that does not match the pattern is rejected with the nod
 """
 from __future__ import annotations
 
+import math
+
 import numpy as np
 import torch
 
@@ -170,7 +172,7 @@ class _Lin:
         return ref.dequant_w4(self.q, self.scales.float(), self.zp, self.block, self.k).to(dtype)
 
 
-def lower_decoder(model: pb.Model, dtype=torch.float32, device="cpu", keep_int4: bool = False):
+def lower_decoder(model: pb.Model, dtype=torch.float32, device="cpu", keep_int4: bool = False, tp: int = 1, rank: int = 0):
     """Returns (DecoderConfig, DecoderWeights, gate_up_unpacked) recognised from the graph."""
     g = model.graph
     inits = g.initializers
@@ -297,7 +299,22 @@ def lower_decoder(model: pb.Model, dtype=torch.float32, device="cpu", keep_int4:
                         rotary_dim=int(cos.shape[1] * 2) if cos is not None else 0,
                         sliding_window=max(0, int(gqa_attrs.get("local_window_size", -1))),
                         weight_format="int4" if int4 else "bf16", int4_block=first["o"].block if int4 else 32)
-    half = pick_swiglu_half(inter + (-inter) % 64 if inter % 32 else inter)
+    # Tensor parallelism: this rank keeps its query / KV heads (rows of q, k, v; columns of o) and its slice of the MLP's
+    # intermediate width (rows of gate / up, columns of down), cut exactly as the seeded weights of the benchmarks are
+    # (models/decoder.py random_weights); embeddings, norms and the LM head stay whole.
+    q_rows = kv_rows = None
+    i0, i1 = 0, inter
+    if tp > 1:
+        if keep_int4 and int4:
+            raise GraphPatternError("tensor parallelism over packed int4 weights is not built: load with keep_int4=False (bf16 shards)")
+        from ..parallel.sharding import shard_heads, shard_range
+
+        hs = shard_heads(hq, hkv, tp, rank)
+        q_rows = torch.tensor([h * d + i for h in hs.q_heads for i in range(d)])
+        kv_rows = torch.tensor([h * d + i for h in hs.kv_heads for i in range(d)])
+        i0, i1 = shard_range(inter, tp, rank, math.gcd(inter, 32))        # 32 where the width allows (int4 blocks, MMA tiles)
+    inter_local = i1 - i0
+    half = pick_swiglu_half(inter_local + (-inter_local) % 64 if inter_local % 32 else inter_local)
     dev = torch.device(device)
     layers, unpacked = [], []
     for lr in layers_raw:
@@ -309,12 +326,20 @@ def lower_decoder(model: pb.Model, dtype=torch.float32, device="cpu", keep_int4:
         if projs[0].bias is not None:
             qkv_b = torch.cat([p.bias if p.bias is not None else torch.zeros(p.dense(torch.float32).shape[0]) for p in projs], 0)
         gate, up, down = (lr["mlp"][i].dense(torch.float32) for i in range(3))
+        o_w = lr["o"].dense(dtype)
+        if tp > 1:
+            q_size, kv_size = hq * d, hkv * d
+            rows = torch.cat([q_rows, q_size + kv_rows, q_size + kv_size + kv_rows])
+            qkv_w = qkv_w[rows]
+            qkv_b = qkv_b[rows] if qkv_b is not None else None
+            o_w = o_w[:, q_rows].contiguous()
+            gate, up, down = gate[i0:i1], up[i0:i1], down[:, i0:i1]
         unpacked.append((gate, up))
-        if inter % 32:
+        if inter_local % 32:
             gate, up, down = pad_mlp(gate, up, down)
         lw = LayerWeights(ln1=lr["ln1"].to(dtype).to(dev), qkv_w=qkv_w.to(dtype).to(dev),
                           qkv_b=qkv_b.to(dtype).to(dev) if qkv_b is not None else None,
-                          o_w=lr["o"].dense(dtype).to(dev), ln2=lr["ln2"].to(dtype).to(dev),
+                          o_w=o_w.to(dev), ln2=lr["ln2"].to(dtype).to(dev),
                           gate_up_w=ref.pack_gate_up(gate, up, half).to(dtype).to(dev), down_w=down.to(dtype).to(dev))
         if keep_int4 and int4:
             lw.quant = {"o": lr["o"], "down": lr["mlp"][2], "gate": lr["mlp"][0], "up": lr["mlp"][1], "qkv": projs}

@@ -18,6 +18,13 @@ def _run(nproc, mode, out, port):
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
                "--master-port", str(port), worker, mode, out]
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    if proc.returncode != 0 and nproc > 1 and "--master-port" in cmd:      # the fixed port may be taken: once more on a free one
+        import socket
+
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            cmd[cmd.index("--master-port") + 1] = str(s.getsockname()[1])
+        proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-4000:]
     return torch.load(out)
 
