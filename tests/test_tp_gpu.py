@@ -87,3 +87,30 @@ def test_pipeline_stages_on_two_gpus_match_one(single, tmp_path):
     piped = _run(2, "pp", str(tmp_path / "pp.pt"), 29790)
     assert _err(piped, single["logits"]) < 3e-2
     assert len(piped["tokens"]) == len(single["tokens"])
+
+
+def test_public_api_serves_over_two_gpus(tmp_path):
+    """`Engine.from_dir(tp=2)`: the package's graph is lowered into per-rank shards, rank 0 answers `generate*` while rank 1
+    follows the broadcast scheduler commands, over the peer-memory communicator; against the same package on one GPU."""
+    _need(2)
+    worker = os.path.join(ROOT, "tests", "tp_engine_worker.py")
+    env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
+    for k in ("WORLD_SIZE", "RANK", "LOCAL_RANK"):
+        env.pop(k, None)
+    outs = {}
+    for nproc in (1, 2):
+        out = str(tmp_path / f"e{nproc}.pt")
+        cmd = [sys.executable, worker, out] if nproc == 1 else [
+            sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+            "--master-port", "29795", worker, out]
+        proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=420)
+        assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-4000:]
+        outs[nproc] = torch.load(out)
+    one, two = outs[1], outs[2]
+    assert two["world"] == 2 and two["device"].startswith("cuda") and two["comm"] == "FusedComm"
+    assert [len(t) for t in two["greedy"]] == [len(t) for t in one["greedy"]] == [10, 10, 10]
+    assert len(two["sampled"]) == 8 and len(two["streamed"]) == 6
+    # bf16 shards sum in another order than one GPU's GEMM, so later tokens may part ways; the first token of most prompts holds
+    assert sum(a[0] == b[0] for a, b in zip(two["greedy"], one["greedy"])) >= 2
+    assert two["launches"].get("native_step_kernels", 0) > 0 or two["launches"].get("tp_exchange_norm", 0) > 0
+    assert "not available under tensor parallelism" in two["refused"]

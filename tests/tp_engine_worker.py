@@ -14,14 +14,26 @@ from onnx_genai_b200.models.decoder import random_weights
 from onnx_genai_b200.package.export import export_package
 
 
+def _launches():
+    from onnx_genai_b200 import ops
+
+    return {k: v for k, v in ops.launch_counts.items() if v}
+
+
 def main():
     out_path = sys.argv[1]
     dev_kind = "cpu" if os.environ.get("OGB_TEST_DEVICE") == "cpu" or not torch.cuda.is_available() else "cuda"
     rank, world, dev, comm = bootstrap(dev_kind)
-    cfg = DecoderConfig(name="tpe", num_layers=2, hidden=256, num_heads=8, num_kv_heads=2, head_dim=32, intermediate=512, vocab=512,
-                        rope_theta=1e4, tie_embeddings=False, qkv_bias=True, max_position=256)
+    if dev.type == "cuda":          # shapes the CUDA kernels take (head dim 64, tile-sized widths); bf16 shards
+        cfg = DecoderConfig(name="tpe", num_layers=3, hidden=512, num_heads=8, num_kv_heads=2, head_dim=64, intermediate=1024, vocab=2048,
+                            rope_theta=1e6, tie_embeddings=False, qkv_bias=True, max_position=1024)
+        std = 0.05
+    else:
+        cfg = DecoderConfig(name="tpe", num_layers=2, hidden=256, num_heads=8, num_kv_heads=2, head_dim=32, intermediate=512, vocab=512,
+                            rope_theta=1e4, tie_embeddings=False, qkv_bias=True, max_position=256)
+        std = 0.3
     with tempfile.TemporaryDirectory() as tmp:                  # every rank writes the same seeded package for itself
-        export_package(cfg, random_weights(cfg, "cpu", seed=3, std=0.3, dtype=torch.float32), tmp, dtype="fp32", int4=False)
+        export_package(cfg, random_weights(cfg, "cpu", seed=3, std=std, dtype=torch.float32), tmp, dtype="fp32", int4=False)
         eng = Engine.from_dir(tmp, device=str(dev), max_seqs=4, max_seq_len=128, num_pages=64, tp=world, tp_rank=rank, comm=comm)
     if rank != 0:
         steps = eng.follow()
@@ -40,7 +52,8 @@ def main():
                 refused = str(exc)
         eng.shutdown()
         torch.save({"greedy": [r.token_ids for r in greedy], "sampled": sampled.token_ids, "streamed": streamed, "refused": refused,
-                    "world": world, "steps": eng.llm.steps}, out_path)
+                    "world": world, "steps": eng.llm.steps, "device": str(dev),
+                    "comm": type(comm).__name__ if comm is not None else "", "launches": dict(_launches())}, out_path)
     if world > 1:
         import torch.distributed as dist
 
