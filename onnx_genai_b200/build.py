@@ -104,6 +104,19 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
     return CUDA_LIB
 
 
+def cuda_include_dir() -> str:
+    """The CUDA toolkit's include directory (CUDA_HOME, else beside nvcc, else the usual place), or '' when there is none."""
+    cands = [os.environ.get("CUDA_HOME", ""), os.environ.get("CUDA_PATH", "")]
+    nvcc = shutil.which("nvcc")
+    if nvcc:
+        cands.append(str(Path(nvcc).resolve().parent.parent))
+    cands.append("/usr/local/cuda")
+    for c in cands:
+        if c and (Path(c) / "include" / "cupti.h").exists():
+            return str(Path(c) / "include")
+    return ""
+
+
 def build_runtime(force: bool = False, verbose: bool = False) -> Path:
     srcs = runtime_sources()
     hdrs: list[Path] = []
@@ -118,6 +131,9 @@ def build_runtime(force: bool = False, verbose: bool = False) -> Path:
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
     cxx = os.environ.get("OGB_CXX") or shutil.which("g++") or "g++"
     inc = ["-I", str(ROOT / "csrc"), "-I", str(ROOT / "csrc" / "capi")]
+    cuda_inc = cuda_include_dir()            # the GPU activity collector reads record layouts from cupti.h when it is there
+    if cuda_inc:
+        inc += ["-I", cuda_inc]
 
     def one(src: Path) -> Path:
         obj = OBJ_DIR / (src.parent.name + "_" + src.stem + ".o")

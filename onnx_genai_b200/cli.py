@@ -675,9 +675,19 @@ def cmd_export(args, profiler):
 class Profiler:
     """--profile: per-stage wall clock table + latency percentiles; --profile-json / --profile-trace write files."""
 
-    def __init__(self, enabled, json_path=None, trace_path=None):
-        self.enabled, self.json_path, self.trace_path = enabled or bool(json_path) or bool(trace_path), json_path, trace_path
+    def __init__(self, enabled, json_path=None, trace_path=None, gpu=False):
+        self.enabled, self.json_path, self.trace_path = enabled or bool(json_path) or bool(trace_path) or gpu, json_path, trace_path
         self.spans = []
+        # --profile-gpu: device activity (kernels, copies) through CUPTI for the whole command; its per-kernel table goes
+        # to stderr and, with --profile-trace, one track per GPU stream joins the timeline
+        self.gpu = None
+        if gpu:
+            from .utils.gpu_activity import GpuActivityCollector
+
+            try:
+                self.gpu = GpuActivityCollector().start()
+            except Exception as exc:
+                print(f"--profile-gpu: device activity is not collected: {exc}", file=sys.stderr)
 
     def span(self, name):
         prof = self
@@ -704,12 +714,18 @@ class Profiler:
                "kv": eng.resource_snapshot(), "stages": [{"name": n, "ms": (b - a) * 1e3} for n, a, b in self.spans]}
         print("profile: TTFT %.1f ms | decode %.2f tok/s | ITL p50 %.1f / p99 %.1f ms | %s" %
               (rep["ttft_ms"], rep["decode_tok_per_s"], rep["itl_ms"]["p50"], rep["itl_ms"]["p99"], rep["finish_reason"]), file=sys.stderr)
+        gpu_spans = []
+        if self.gpu is not None:
+            self.gpu.stop()
+            rep["gpu_activity"] = {"busy_fraction": self.gpu.busy_fraction(), "dropped": self.gpu.dropped, "top": self.gpu.summary()[:40]}
+            gpu_spans = self.gpu.spans()
+            print(self.gpu.table(), file=sys.stderr)
         if self.json_path:
             json.dump(rep, open(self.json_path, "w"), indent=1)
         if self.trace_path:
             from .utils.trace import write_chrome_trace
 
-            write_chrome_trace(self.trace_path, [(n, a, b, "cli") for n, a, b in self.spans])
+            write_chrome_trace(self.trace_path, [(n, a, b, "cli") for n, a, b in self.spans] + gpu_spans)
 
 
 # ------------------------------------------------------------------------------------------
@@ -890,6 +906,8 @@ def main(argv=None):
     ap.add_argument("--profile", action="store_true")
     ap.add_argument("--profile-json", default=None)
     ap.add_argument("--profile-trace", default=None)
+    ap.add_argument("--profile-gpu", action="store_true",
+                    help="collect kernels and copies with their device timestamps (CUPTI): table on stderr, tracks in --profile-trace")
     sub = ap.add_subparsers(dest="cmd", required=True)
     g = sub.add_parser("generate")
     g.add_argument("model")
@@ -974,7 +992,7 @@ def main(argv=None):
     if args.cmd == "version":
         print(f"onnx-genai-b200 {__version__}")
         return 0
-    profiler = Profiler(args.profile, args.profile_json, args.profile_trace)
+    profiler = Profiler(args.profile, args.profile_json, args.profile_trace, gpu=getattr(args, "profile_gpu", False))
     return {"generate": cmd_generate, "run": cmd_run, "serve": cmd_serve, "show": cmd_show, "validate": cmd_validate, "list": cmd_list,
             "export": cmd_export, "transcribe": cmd_transcribe}[args.cmd](args, profiler)
 

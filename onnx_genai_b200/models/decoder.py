@@ -284,6 +284,9 @@ class DecoderModel:
         self.hq, self.hkv, self.d = len(hs.q_heads), len(hs.kv_heads), cfg.head_dim
         self.rotary_dim = cfg.rotary_dim or cfg.head_dim
         self.max_tokens, self.max_seqs = max_tokens, max_seqs
+        if self.device.type == "cuda" and cfg.head_dim not in (64, 128):
+            raise ValueError(f"head dimension {cfg.head_dim} is not supported on CUDA: the paged attention kernels are built for 64 and 128 "
+                             "(the CPU path and the node-by-node graph backend take any head dimension)")
         dt = weights.embed.dtype
         dev = self.device
         hid = cfg.hidden

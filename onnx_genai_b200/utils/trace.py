@@ -52,13 +52,27 @@ class Tracer:
         self.enabled = self.path is not None
         # ONNX_GENAI_TRACE_NVTX=1: every span also opens an NVTX range, so an external profiler that records NVTX
         # (Nsight Systems, a CUPTI-based collector) sees the engine's stages on the same timeline as the kernels.  This
-        # is the hand-off to vendor collectors that the reference does through its ITT / CUPTI tracer back ends
-        # (crates/onnx-runtime-tracer/src/itt.rs, cupti.rs); no collector is embedded here.
+        # is the hand-off to vendor collectors that the reference does through its ITT tracer back end
+        # (crates/onnx-runtime-tracer/src/itt.rs).
         import os
 
         self.nvtx = None
         if os.environ.get("ONNX_GENAI_TRACE_NVTX", "0") not in ("", "0"):
             self.enable_nvtx()
+        # ONNX_GENAI_TRACE_CUPTI=1 (with ONNX_GENAI_TRACE): device activity (kernels, copies) is collected through CUPTI
+        # from the first span on and written as one track per GPU stream beside the host spans (utils/gpu_activity.py).
+        self.gpu = None
+        self.gpu_error = ""
+        self.want_gpu = os.environ.get("ONNX_GENAI_TRACE_CUPTI", "0") not in ("", "0")
+
+    def _start_gpu(self):
+        self.want_gpu = False
+        try:
+            from .gpu_activity import GpuActivityCollector
+
+            self.gpu = GpuActivityCollector().start()
+        except Exception as exc:            # no CUPTI here: the host spans are still worth having
+            self.gpu, self.gpu_error = None, str(exc)
 
     def enable_nvtx(self, push=None, pop=None):
         """Mirror spans as NVTX ranges (``push(name)`` / ``pop()`` default to torch.cuda.nvtx; tests pass fakes)."""
@@ -81,6 +95,8 @@ class Tracer:
 
         class _Span:
             def __enter__(self):
+                if tracer.want_gpu and tracer.enabled:
+                    tracer._start_gpu()
                 self.t0 = time.perf_counter()
                 self.ranged = False
                 if tracer.nvtx is not None:
@@ -103,7 +119,14 @@ class Tracer:
 
     def flush(self):
         if self.enabled and self.path:
-            write_chrome_trace(self.path, self.spans)
+            spans = list(self.spans)
+            if self.gpu is not None:
+                try:
+                    self.gpu.poll()
+                    spans += self.gpu.spans()
+                except Exception as exc:
+                    self.gpu_error = str(exc)
+            write_chrome_trace(self.path, spans)
 
 
 TRACER = Tracer()
