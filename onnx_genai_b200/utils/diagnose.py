@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import json
 import os
+import re
 import sys
 from dataclasses import dataclass, field
 
@@ -114,9 +115,10 @@ _COMM = ("tp_", "exchange", "all_reduce", "nccl", "scatter")
 
 
 def diagnose_samples(samples, analyzer: RooflineAnalyzer | None = None, wall_s: float | None = None, steps: int = 1,
-                     preemptions: int = 0, graph_replays: int = 0) -> Diagnosis:
+                     preemptions: int = 0, graph_replays: int = 0, device_busy_s: float | None = None) -> Diagnosis:
     """``samples``: KernelSample list covering ``steps`` engine steps; ``wall_s``: host wall-clock time of the same steps
-    (to find host-side gaps)."""
+    (to find host-side gaps); ``device_busy_s``: time with at least one device event running, when the samples come from
+    several streams whose events overlap (default: the sum of the samples)."""
     analyzer = analyzer or RooflineAnalyzer.measured()
     d = Diagnosis()
     d.total_s = sum(s.duration_s for s in samples)
@@ -150,10 +152,11 @@ def diagnose_samples(samples, analyzer: RooflineAnalyzer | None = None, wall_s: 
                               f"{comm * 1e3 / max(1, steps):.3f} ms per step in reduce / broadcast kernels.",
                               "fixed fence-and-signal latency per exchange (two per layer), not bytes",
                               "use push mode (OGB_TP_PUSH=1) so the reduce reads local memory, enable OGB_TP_PDL=1 so the consumer GEMM starts under the exchange, or lower the TP degree (cost_model.pick_tp)"))
-    if wall_s is not None and wall_s > 0 and d.total_s / wall_s < 0.85:
-        sev = "high" if d.total_s / wall_s < 0.6 else "medium"
-        d.issues.append(Issue(sev, "the GPU waits for the host", f"Device kernels cover {100 * d.total_s / wall_s:.0f}% of the wall-clock time of the profiled steps.",
-                              f"{wall_s * 1e3 / max(1, steps):.3f} ms per step on the wall clock against {d.total_s * 1e3 / max(1, steps):.3f} ms of kernels"
+    busy_s = d.total_s if device_busy_s is None else device_busy_s
+    if wall_s is not None and wall_s > 0 and busy_s / wall_s < 0.85:
+        sev = "high" if busy_s / wall_s < 0.6 else "medium"
+        d.issues.append(Issue(sev, "the GPU waits for the host", f"Device kernels cover {100 * busy_s / wall_s:.0f}% of the wall-clock time of the profiled steps.",
+                              f"{wall_s * 1e3 / max(1, steps):.3f} ms per step on the wall clock against {busy_s * 1e3 / max(1, steps):.3f} ms of kernels"
                               + (f"; {graph_replays} graph replays" if graph_replays else "; no graph replays"),
                               "scheduling, plan packing or Python between steps is not overlapped with device work",
                               "enable CUDA-graph replay for decode steps, raise max_tokens_per_step so each step carries more work, or move per-step host work off the critical path"))
@@ -224,6 +227,51 @@ def samples_from_trace(doc: dict, category: str | None = None) -> tuple:
     return samples, (0.0 if t0 is None else t1 - t0)
 
 
+_DEVICE_TRACK = re.compile(r"gpu\d+ stream \d+$")
+
+
+def device_view(doc: dict):
+    """A trace that carries device tracks (one category per GPU stream, written by the CUPTI activity collector of
+    utils/gpu_activity.py): the device events inside the longest host span, aggregated by kernel (copies by direction),
+    with that span's wall-clock length and the time during which at least one device event ran.  None when the trace has
+    no device track.  Returns ``(samples, wall_s, busy_s, window_name)``."""
+    from .gpu_activity import short_name
+
+    host, device = [], []
+    for ev in doc.get("traceEvents", []):
+        if ev.get("ph") != "X":
+            continue
+        ts, dur = float(ev.get("ts", 0.0)) / 1e6, float(ev.get("dur", 0.0)) / 1e6
+        (device if _DEVICE_TRACK.match(str(ev.get("cat", ""))) else host).append((ts, ts + dur, ev["name"]))
+    if not device:
+        return None
+    if host:
+        w0, w1, window = max(host, key=lambda e: e[1] - e[0])
+    else:
+        w0, w1, window = min(e[0] for e in device), max(e[1] for e in device), "device events"
+    inside = sorted(e for e in device if w0 <= e[0] <= w1)
+    agg: dict = {}
+    busy, cur = 0.0, None
+    for a, b, name in inside:
+        if name.startswith("memcpy") or name.startswith("memset"):
+            key, cat = " ".join(name.split()[:-2]) if name.endswith(" B") else name, "copy"     # drop the byte count: one row per direction
+        else:
+            key, cat = short_name(name), "compute"
+        rec = agg.setdefault(key, [0.0, 0, cat])
+        rec[0] += b - a
+        rec[1] += 1
+        if cur is None or a > cur[1]:
+            if cur is not None:
+                busy += cur[1] - cur[0]
+            cur = [a, b]
+        else:
+            cur[1] = max(cur[1], b)
+    if cur is not None:
+        busy += cur[1] - cur[0]
+    samples = [KernelSample(n, r[0], r[1], None, None, r[2]) for n, r in agg.items()]
+    return samples, w1 - w0, busy, window
+
+
 def main(argv=None) -> int:
     import argparse
 
@@ -234,6 +282,13 @@ def main(argv=None) -> int:
     args = ap.parse_args(argv)
     with open(args.trace, encoding="utf-8") as f:
         doc = json.load(f)
+    view = device_view(doc) if args.category is None else None
+    if view is not None:                 # device tracks present: judge device time against the host span that encloses it
+        samples, wall, busy, window = view
+        d = diagnose_samples(samples, RooflineAnalyzer.measured(args.peaks), wall_s=wall, device_busy_s=busy)
+        d.notes.append(f"device events inside the host span '{window}' ({wall * 1e3:.3f} ms); the device was busy {busy * 1e3:.3f} ms of it")
+        print(d.report())
+        return 0
     samples, wall = samples_from_trace(doc, args.category)
     nested = args.category is None and len({s.category for s in samples}) > 1
     d = diagnose_samples(samples, RooflineAnalyzer.measured(args.peaks), wall_s=None if nested else wall)

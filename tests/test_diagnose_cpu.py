@@ -68,3 +68,29 @@ def test_trace_documents_are_read_and_reported(tmp_path, capsys):
     assert dg.main([str(p)]) == 0
     out = capsys.readouterr().out
     assert "MatMul runs at" in out and "Softmax" in out and "indeterminate" in out
+
+
+def test_device_tracks_are_judged_against_the_host_span_that_encloses_them():
+    """A trace with one category per GPU stream (what the CUPTI activity collector writes): kernels are aggregated under
+    short names, copies by direction, load-time events outside the longest host span are left out, overlapping streams
+    count once, and a mostly idle device is reported as waiting for the host."""
+    from onnx_genai_b200.utils.diagnose import device_view, diagnose_samples
+
+    ev = lambda name, cat, ts_us, dur_us: {"name": name, "cat": cat, "ph": "X", "ts": ts_us, "dur": dur_us, "pid": 1, "tid": 1}
+    events = [ev("load", "cli", 0, 500), ev("generate", "cli", 1000, 10000),
+              ev("memcpy host to device 1048576 B", "gpu0 stream 13", 100, 300)]                      # load time: outside the window
+    for i in range(20):
+        events.append(ev("void ogb::gemm_bf16_tcgen05_kernel<32, 1>(CUtensorMap_st, int)", "gpu0 stream 7", 1100 + 400 * i, 30))
+        events.append(ev("void ogb::rmsnorm_warp_kernel(__nv_bfloat16*, int)", "gpu0 stream 7", 1140 + 400 * i, 3))
+        events.append(ev("memcpy device to host 4 B", "gpu0 stream 13", 1110 + 400 * i, 10))           # under the GEMM: no extra busy time
+    view = device_view({"traceEvents": events})
+    samples, wall, busy, window = view
+    assert window == "generate" and abs(wall - 0.010) < 1e-9
+    by = {s.name: s for s in samples}
+    assert set(by) == {"gemm_bf16_tcgen05_kernel<32, 1>", "rmsnorm_warp_kernel", "memcpy device to host"}
+    assert by["gemm_bf16_tcgen05_kernel<32, 1>"].calls == 20 and by["memcpy device to host"].category == "copy"
+    assert abs(busy - 20 * 33e-6) < 1e-9                                                              # 30 + 3 us per step, the copy hidden
+    d = diagnose_samples(samples, wall_s=wall, device_busy_s=busy)
+    titles = [i.title for i in d.issues]
+    assert "the GPU waits for the host" in titles and any("rmsnorm_warp_kernel is launch-bound" in t for t in titles)
+    assert device_view({"traceEvents": [ev("step", "engine", 0, 10)]}) is None
