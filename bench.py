@@ -113,6 +113,8 @@ def main():
                     help="the scheduler trims the last prefill chunk so a step's token count is a multiple of this (GEMM M tile)")
     ap.add_argument("--deadline", type=int, default=900, help="seconds after which a stuck run dumps stacks and exits")
     ap.add_argument("--no-native-executor", action="store_true", help="drive the layer stack from Python (for op profiling)")
+    ap.add_argument("--profile-gpu", default="", help="after the timed regions and the latency sample, replay the recorded steps once more under "
+                    "the CUPTI activity collector and write the per-kernel device-time table (JSON) here; the bench line is not affected")
     ap.add_argument("--profile-ops", action="store_true", help="after the timed regions, replay 4 steps with per-op CUDA-event timing (stderr)")
     ap.add_argument("--no-anchor", action="store_true",
                     help="skip the labelled library arm (cuBLAS GEMMs + ncclAllReduce) that is replayed on the same steps for vs_baseline")
@@ -382,6 +384,31 @@ def main():
             print(_dg.diagnose_samples(_dg.samples_from_profile(agg, model, shape_, tp=tp, steps=n_prof), steps=n_prof).report(), file=sys.stderr)
         except Exception as exc:   # the diagnosis is a convenience: never let it break the bench line
             print(f"diagnosis skipped: {exc}", file=sys.stderr)
+
+    if args.profile_gpu:
+        # every rank replays (the steps contain collectives); rank 0 collects.  Through the same executor as the timed
+        # region, so the table is the kernel-level breakdown of `ms_per_step` (plus CUPTI's own cost per launch).
+        from onnx_genai_b200.utils.gpu_activity import GpuActivityCollector, short_name
+
+        gpu = None
+        if rank == 0:
+            try:
+                gpu = GpuActivityCollector(copies=True).start()
+            except Exception as exc:
+                print(f"--profile-gpu: device activity is not collected: {exc}", file=sys.stderr)
+        torch.cuda.synchronize()
+        for i in range(args.steps):
+            replay(i)
+        torch.cuda.synchronize()
+        if gpu is not None:
+            gpu.stop()
+            rows = [{**r, "name": short_name(r["name"]), "ms_per_step": r["total_us"] / 1e3 / args.steps, "calls_per_step": r["count"] / args.steps}
+                    for r in gpu.summary()]
+            busy_ms = gpu.busy_fraction() * (gpu.records[-1].end_s - gpu.records[0].start_s) * 1e3 / args.steps if gpu.records else 0.0
+            with open(args.profile_gpu, "w", encoding="utf-8") as f:
+                json.dump({"steps": args.steps, "device_busy_ms_per_step": busy_ms, "sum_ms_per_step": sum(r["ms_per_step"] for r in rows),
+                           "dropped": gpu.dropped, "kernels": rows}, f, indent=1)
+            print(gpu.table(30), file=sys.stderr)
 
     dev_tokens = sum(s[4] for s in shapes)
     if wcomm is not None:

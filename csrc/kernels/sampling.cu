@@ -346,7 +346,7 @@ OGB_DEVICE uint32_t radix_threshold_vec(const uint32_t* __restrict__ w, int voca
   return prefix < floor_w ? floor_w : prefix;
 }
 
-__global__ void __launch_bounds__(kSampleThreads)
+__global__ void __launch_bounds__(kSampleThreads, 2)
 sample_kernel_vec(const __nv_bfloat16* __restrict__ logits, int* __restrict__ out, const float* __restrict__ temperature,
                   const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
                   const float* __restrict__ uniform, uint32_t* __restrict__ work, int vocab, int ld) {
