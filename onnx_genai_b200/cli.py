@@ -946,6 +946,10 @@ def main(argv=None):
     sh.add_argument("model")
     va = sub.add_parser("validate", help="check a model directory and report every problem")
     va.add_argument("model")
+    pm = sub.add_parser("plan-memory", help="lifetimes, arena size and lower bound of a graph's intermediates (JSON)")
+    pm.add_argument("graph", help=".onnx or .onnx.textproto file")
+    pm.add_argument("--bind", action="append", default=[], metavar="SYMBOL=N", help="value of a symbolic dimension (repeatable)")
+    pm.add_argument("--values", action="store_true", help="also list every value with its lifetime and offset")
     ls = sub.add_parser("list")
     ls.add_argument("--models-dir", default=".")
     sub.add_parser("version")
@@ -986,6 +990,25 @@ def main(argv=None):
         return diagnose_main([args.trace] + (["--category", args.category] if args.category else []) + (["--peaks", args.peaks] if args.peaks else []))
     if args.cmd == "run-workflow":
         return cmd_run_workflow(args)
+    if args.cmd == "plan-memory":
+        from .package.memory_plan import plan_memory
+        from .package.onnx_text import load_any
+
+        try:
+            symbols = {k: int(v) for k, v in (b.split("=", 1) for b in args.bind)}
+        except ValueError:
+            print("plan-memory: --bind takes SYMBOL=N with N an integer", file=sys.stderr)
+            return 2
+        plan = plan_memory(load_any(args.graph), symbols=symbols)
+        plan.check()
+        doc = plan.summary()
+        if plan.unsized:
+            doc["unsized_values"] = plan.unsized[:20]
+        if args.values:
+            doc["lifetimes"] = [{"name": v.name, "born": v.born, "dies": v.dies, "bytes": v.bytes, "offset": v.offset, "alias_of": v.alias_of}
+                                for v in sorted(plan.values.values(), key=lambda v: v.born)]
+        print(json.dumps(doc, indent=1))
+        return 0
     if args.cmd == "import-comfyui":
         from .package.comfyui import main as comfy_main
         return comfy_main([args.graph, "-o", args.out])

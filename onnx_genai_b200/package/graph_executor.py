@@ -952,11 +952,14 @@ def _free_values(graph) -> set:
 
 
 class GraphExecutor:
-    def __init__(self, model, device="cpu", dtype=None, optimize=False):
+    def __init__(self, model, device="cpu", dtype=None, optimize=False, release=False):
         """``model``: a path to an ``.onnx`` file or a parsed :class:`onnx_pb.Model`.  Initializers move to ``device``
         (floating-point ones are cast to ``dtype`` when given).  ``optimize``: run the rewrite passes of
         :mod:`graph_optimizer` on the graph first (constant folding, no-op removal, GELU / LayerNorm / Gemm fusion, dead
-        nodes); the model object is rewritten in place and ``self.optimization`` holds the report."""
+        nodes); the model object is rewritten in place and ``self.optimization`` holds the report.  ``release``: drop every
+        intermediate from the interpreter's scope right after its last reader (lifetimes of :mod:`memory_plan`), so a
+        run holds its live set rather than every value it ever produced; ``self.peak_live_bytes`` then reports the
+        largest live set of the last run."""
         self.model = onnx_pb.load_model(model) if isinstance(model, str) else model
         self.device = torch.device(device)
         self.optimization = None
@@ -982,6 +985,18 @@ class GraphExecutor:
         self._sub_constants: dict = {}        # id(subgraph) -> its initializers on the device
         self.order = self._toposort(g)
         self.runs = 0
+        self.release = bool(release)
+        self.peak_live_bytes = 0
+        self._drop_after: list = []
+        if self.release:
+            from .memory_plan import lifetimes
+
+            _, born, last = lifetimes(self.model, self.order)
+            keep = set(self.output_names)
+            self._drop_after = [[] for _ in self.order]
+            for name, i in last.items():
+                if name in born and name not in keep and i < len(self.order):
+                    self._drop_after[i].append(name)
 
     def _toposort(self, g):
         produced = set(self.constants) | set(self.input_names)
@@ -1014,8 +1029,39 @@ class GraphExecutor:
             if want is not None and t.dtype != want and (t.is_floating_point() == want.is_floating_point):
                 t = t.to(want)
             env[name] = t.to(self.device)
-        for n in self.order:
-            self._exec_node(n, env)
+        if self.release and not outputs:
+            # live bytes are counted per storage: an operator may hand back a view of its input (a transpose, a slice), and
+            # the bytes stay live until the last name over that storage is dropped.  Inputs and initializers are the caller's.
+            def key(t):
+                return t.untyped_storage().data_ptr() if isinstance(t, torch.Tensor) and t.numel() else None
+
+            external = {key(t) for t in env.values()}
+            holders: dict = {}                       # storage -> [bytes, names bound over it]
+            live = peak = 0
+            for i, n in enumerate(self.order):
+                self._exec_node(n, env)
+                for o in n.outputs:
+                    k = key(env.get(o)) if o else None
+                    if k is None or k in external:
+                        continue
+                    slot = holders.get(k)
+                    if slot is None:
+                        slot = holders[k] = [env[o].untyped_storage().nbytes(), set()]
+                        live += slot[0]
+                    slot[1].add(o)
+                peak = max(peak, live)
+                for name in self._drop_after[i]:
+                    t = env.pop(name, None)
+                    slot = holders.get(key(t))
+                    if slot is not None:
+                        slot[1].discard(name)
+                        if not slot[1]:
+                            live -= slot[0]
+                            del holders[key(t)]
+            self.peak_live_bytes = peak
+        else:
+            for n in self.order:
+                self._exec_node(n, env)
         self.runs += 1
         return {name: env[name] for name in (outputs or self.output_names)}
 
