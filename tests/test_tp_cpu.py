@@ -9,8 +9,8 @@ import torch
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(nproc, mode, out, port):
-    env = dict(os.environ, PYTHONPATH=ROOT, OGB_TEST_DEVICE="cpu", CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2")
+def _run(nproc, mode, out, port, **extra_env):
+    env = dict(os.environ, PYTHONPATH=ROOT, OGB_TEST_DEVICE="cpu", CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2", **extra_env)
     worker = os.path.join(ROOT, "tests", "tp_worker.py")
     if nproc == 1:
         cmd = [sys.executable, worker, mode, out]
@@ -65,3 +65,16 @@ def test_communicator_exchanges_and_expert_dispatch_over_gloo(tmp_path):
     assert res["recv"] == [s + 0 + 1 for s in range(3)]                    # what each source sends to rank 0
     assert res["rows"] == [[s, 0] for s in range(3) for _ in range(s + 1)]
     assert res["ring"] == 2.0 and res["ep_ok"] == 3
+
+
+def test_token_sharded_expert_dispatch_in_the_engine_matches_one_rank(tmp_path):
+    """`OGB_EP_DISPATCH=a2a`: each rank routes its slice of the rows, rows travel to the experts' owners and back
+    (exchange_counts + all_to_all_v), an all-gather restores the replicated rows; against one rank holding every expert,
+    over 2 and 4 ranks (4: some rows' slices are empty in decode steps with fewer rows than ranks)."""
+    one = _run(1, "nccl-moe", str(tmp_path / "o.pt"), 0)
+    for world, port in ((2, 29657), (4, 29658)):
+        got = _run(world, "nccl-moe", str(tmp_path / f"a{world}.pt"), port, OGB_EP_DISPATCH="a2a")
+        err = float((got["logits"] - one["logits"]).norm() / one["logits"].norm())
+        assert err < 1e-4, (world, err)
+        assert got["tokens"] == one["tokens"]
+        assert got["launches"].get("ep_dispatch_a2a", 0) > 0 and one["launches"].get("ep_dispatch_a2a", 0) == 0

@@ -114,3 +114,13 @@ def test_public_api_serves_over_two_gpus(tmp_path):
     assert sum(a[0] == b[0] for a, b in zip(two["greedy"], one["greedy"])) >= 2
     assert two["launches"].get("native_step_kernels", 0) > 0 or two["launches"].get("tp_exchange_norm", 0) > 0
     assert "not available under tensor parallelism" in two["refused"]
+
+
+def test_token_sharded_expert_dispatch_on_two_gpus(single_moe, tmp_path):
+    """`OGB_EP_DISPATCH=a2a` over NCCL: rows travel to the experts' owners and back (all-to-all with exchanged counts)
+    instead of every rank routing every row; the grouped expert GEMM runs on the received rows; against one GPU."""
+    _need(2)
+    got = _run(2, "nccl-moe", str(tmp_path / "a2a.pt"), 29796, OGB_EP_DISPATCH="a2a")
+    assert _err(got, single_moe["logits"]) < 3e-2
+    assert got["launches"].get("ep_dispatch_a2a", 0) > 0 and got["launches"].get("moe_grouped_gemm", 0) > 0
+    assert len(got["tokens"]) == len(single_moe["tokens"])
