@@ -35,18 +35,19 @@ constexpr int kWDequantWarps = 8;
 constexpr int kWThreads = (2 + 4 + kWDequantWarps) * 32;
 constexpr int kWGroups = 2;                 // dequantiser groups working on alternate k-blocks
 constexpr int kWGroupWarps = kWDequantWarps / kWGroups;
-constexpr int kWUnits = 256 / (kWGroupWarps * 32);   // 32-weight blocks per thread per k-block
+constexpr int kWUnitRows = 64;              // rows of a W tile covered by one unit per thread of a group (128 threads x 2 halves of k)
 constexpr int kWStagePitch = 272;           // epilogue staging: 128 bf16 + 16 bytes, conflict-free for 16-byte accesses
 constexpr int kWStageWarpBytes = 32 * kWStagePitch;
 
-template <int MT>
+// MT: A tiles (128 rows each) per W tile; TN: columns of a W tile (128, or 64 when 128-wide tiles would leave most SMs idle).
+template <int MT, int TN>
 struct W4Cfg {
   static constexpr int kStageA = MT * kWTile * kWBK * 2;
-  static constexpr int kStageB = kWTile * kWBK * 2;
+  static constexpr int kStageB = TN * kWBK * 2;
   static constexpr int kStage = kStageA + kStageB;
   static constexpr int kStages = MT == 2 ? 4 : 6;
-  static constexpr int kAccCols = MT * kWTile;          // TMEM columns of one accumulator set
-  static constexpr int kTmemCols = 2 * kAccCols;        // 256 or 512: a power of two
+  static constexpr int kAccCols = MT * TN;              // TMEM columns of one accumulator set
+  static constexpr int kTmemCols = 2 * kAccCols;        // 128, 256 or 512: a power of two
   static constexpr int kBarOff = kStages * kStage;                      // barriers (512 bytes)
   static constexpr int kStagingOff = kBarOff + 512;
   static constexpr int kSmemBytes = kStagingOff + 4 * kWStageWarpBytes;
@@ -77,12 +78,13 @@ struct W4Unit {
   bool valid;          // false: a row past N or a block past K -- the loads went to a clamped address, the result is zero
 };
 
-template <int MT, bool SF32>
+template <int MT, bool SF32, int TN>
 __global__ void __launch_bounds__(kWThreads, 1)
 gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t* __restrict__ qw, const void* __restrict__ scales,
                           const uint8_t* __restrict__ zp, const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ C,
                           int M, int N, int K, int ldc, int* status) {
-  using Cfg = W4Cfg<MT>;
+  using Cfg = W4Cfg<MT, TN>;
+  constexpr int kUnits = TN / kWUnitRows;     // 32-weight blocks per dequantiser thread per k-block
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kBarOff);
   uint8_t* staging = smem + Cfg::kStagingOff;
@@ -96,7 +98,7 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int m_tiles = (M + MT * kWTile - 1) / (MT * kWTile);
-  const int n_tiles = (N + kWTile - 1) / kWTile;
+  const int n_tiles = (N + TN - 1) / TN;
   const int num_tiles = m_tiles * n_tiles;
   const int k_blocks = (K + kWBK - 1) / kWBK;
 
@@ -145,7 +147,7 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(kWTile, kWTile);
+      constexpr uint32_t idesc = make_idesc_bf16(kWTile, TN);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -167,7 +169,7 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint
             const uint64_t da = make_kmajor_sw128_desc(sa + mi * (kWTile * kWBK * 2));
 #pragma unroll
             for (int k = 0; k < kWBK / 16; ++k)
-              umma_f16(d_addr + mi * kWTile, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+              umma_f16(d_addr + mi * TN, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
@@ -187,15 +189,15 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint
       const uint32_t acc_phase = (it >> 1) & 1;
       const int m0 = (tile % m_tiles) * (MT * kWTile);
       const int mt_here = (MT == 2 && m0 + kWTile < M) ? 2 : 1;
-      const int n0 = (tile / m_tiles) * kWTile;
+      const int n0 = (tile / m_tiles) * TN;
       if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full[acc], acc_phase))) { ok = false; break; }
       tc_fence_after();
       for (int mi = 0; mi < mt_here; ++mi) {
-        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * Cfg::kAccCols + mi * kWTile;
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * Cfg::kAccCols + mi * TN;
         const int row0 = m0 + mi * kWTile + q * 32;
         // phase 1 (thread = row): TMEM -> registers -> + bias -> bf16 into this warp's staging slab
 #pragma unroll 1
-        for (int c = 0; c < kWTile / 32; ++c) {
+        for (int c = 0; c < TN / 32; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(t_row + c * 32, r);
           tmem_ld_wait();
@@ -221,7 +223,7 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint
         for (int rb = 0; rb < 32; rb += 2) {
           const int r_loc = rb + (lane >> 4);
           const int grow = row0 + r_loc;
-          if (grow < M && gcol < N) {
+          if (grow < M && gcol < N && ch * 8 < TN) {
             const uint4 v = *reinterpret_cast<const uint4*>(stg + r_loc * kWStagePitch + ch * 16);
             __nv_bfloat16* dst = C + static_cast<size_t>(grow) * ldc + gcol;
             if (gcol + 8 <= N) {
@@ -252,29 +254,29 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint
     const long long iters = static_cast<long long>(my_tiles) * k_blocks;
     // The loads run kDepth of the group's k-blocks ahead of their use, in a register ring (each takes a trip to L2 or
     // DRAM): 128 threads x kDepth x 2 blocks x 16 bytes per group in flight.
-    constexpr int kDepth = 4;
+    constexpr int kDepth = 4;                // a deeper ring (8) for the one-unit form measured no different
     struct Cursor {
       int tile, kb;
-      size_t row_blk[kWUnits];   // index of each row's first block
-      size_t row_zp[kWUnits];
-      bool row_ok[kWUnits];
+      size_t row_blk[kUnits];   // index of each row's first block
+      size_t row_zp[kUnits];
+      bool row_ok[kUnits];
     };
     auto seat = [&](Cursor& c) {               // derive the row data of c.tile
 #pragma unroll
-      for (int i = 0; i < kWUnits; ++i) {
-        const int n = c.tile < num_tiles ? (c.tile / m_tiles) * kWTile + (t >> 1) + i * (kWTile / kWUnits) : N;
+      for (int i = 0; i < kUnits; ++i) {
+        const int n = c.tile < num_tiles ? (c.tile / m_tiles) * TN + (t >> 1) + i * kWUnitRows : N;
         c.row_ok[i] = n < N;
         c.row_blk[i] = static_cast<size_t>(c.row_ok[i] ? n : 0) * kb32;
         c.row_zp[i] = static_cast<size_t>(c.row_ok[i] ? n : 0) * zp_stride;
       }
     };
-    auto fetch = [&](Cursor& c, W4Unit (&un)[kWUnits]) {
+    auto fetch = [&](Cursor& c, W4Unit (&un)[kUnits]) {
       // The loads are unconditional (an out-of-range unit reads block 0, which always exists, and is zeroed through
       // its scale at use): a load under a data-dependent condition tends to become load + select, and the select
       // would wait for the load here instead of several iterations later.
       const int b = c.kb * 2 + half;
 #pragma unroll
-      for (int i = 0; i < kWUnits; ++i) {
+      for (int i = 0; i < kUnits; ++i) {
         un[i].valid = c.row_ok[i] && b < kb32;
         const size_t blk = un[i].valid ? c.row_blk[i] + b : 0;
         un[i].q = __ldg(reinterpret_cast<const uint4*>(qw) + blk);
@@ -293,7 +295,7 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint
     Cursor cur{static_cast<int>(blockIdx.x), group, {}, {}, {}};
     while (cur.kb >= k_blocks) { cur.kb -= k_blocks; cur.tile += gridDim.x; }
     seat(cur);
-    W4Unit ring[kDepth][kWUnits];
+    W4Unit ring[kDepth][kUnits];
 #pragma unroll
     for (int d = 0; d < kDepth; ++d) fetch(cur, ring[d]);
     // ring positions of k-iteration j = group: the slots advance by kWGroups per step of this group
@@ -309,8 +311,8 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint
           } else {
             tc_fence_after();              // the tensor core's reads of this slot are ordered before the stores below
 #pragma unroll
-            for (int i = 0; i < kWUnits; ++i) {
-              const int r_tile = (t >> 1) + i * (kWTile / kWUnits);
+            for (int i = 0; i < kUnits; ++i) {
+              const int r_tile = (t >> 1) + i * kWUnitRows;
               uint8_t* sb = smem + stage * Cfg::kStage + Cfg::kStageA + static_cast<uint32_t>(r_tile) * 128u;
               const uint32_t sw = static_cast<uint32_t>(r_tile & 7);
               const W4Unit& un = ring[d][i];
@@ -364,21 +366,21 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint
   }
 }
 
-template <int MT, bool SF32>
+template <int MT, bool SF32, int TN>
 static int launch_w4a16_gemm(const void* x, const void* qweight, const void* scales, const void* zp, const void* bias, void* out,
                              int M, int N, int K, int ldx, int ldc, int* status, cudaStream_t stream) {
-  using Cfg = W4Cfg<MT>;
+  using Cfg = W4Cfg<MT, TN>;
   CUtensorMap ta;
   int rc = make_tmap_bf16_2d(&ta, x, M, K, ldx, kWTile, kWBK);
   if (rc != 0) return rc;
   static bool attr_set = false;
   if (!attr_set) {
-    OGB_CUDA_CHECK(cudaFuncSetAttribute(gemm_w4a16_tcgen05_kernel<MT, SF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    OGB_CUDA_CHECK(cudaFuncSetAttribute(gemm_w4a16_tcgen05_kernel<MT, SF32, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     attr_set = true;
   }
-  const int tiles = ((M + MT * kWTile - 1) / (MT * kWTile)) * ((N + kWTile - 1) / kWTile);
+  const int tiles = ((M + MT * kWTile - 1) / (MT * kWTile)) * ((N + TN - 1) / TN);
   const int grid = tiles < ogb_num_sms() ? tiles : ogb_num_sms();
-  gemm_w4a16_tcgen05_kernel<MT, SF32><<<grid, kWThreads, Cfg::kSmemBytes, stream>>>(
+  gemm_w4a16_tcgen05_kernel<MT, SF32, TN><<<grid, kWThreads, Cfg::kSmemBytes, stream>>>(
       ta, static_cast<const uint8_t*>(qweight), scales, static_cast<const uint8_t*>(zp), static_cast<const __nv_bfloat16*>(bias),
       static_cast<__nv_bfloat16*>(out), M, N, K, ldc, status);
   return static_cast<int>(cudaGetLastError());
@@ -397,10 +399,18 @@ extern "C" int ogb_w4a16_gemm(const void* x, const void* qweight, const void* sc
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 32) != 0 || (ldx % 8) != 0 || (ldc % 8) != 0) return -3;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(qweight)) & 15) return -4;
-  if (M > kWTile) {
-    return scales_f32 ? launch_w4a16_gemm<2, true>(x, qweight, scales, zp, bias, out, M, N, K, ldx, ldc, status, stream)
-                      : launch_w4a16_gemm<2, false>(x, qweight, scales, zp, bias, out, M, N, K, ldx, ldc, status, stream);
+  // 64-column W tiles when 128-column ones would occupy at most half of the SMs: the dequantisers of a CTA, not its
+  // tensor core, set the pace, so twice the CTAs over half the rows each is close to twice as fast (down and o
+  // projections at decode-sized M).
+  const int mt = M > kWTile ? 2 : 1;
+  const int tiles128 = ((M + mt * kWTile - 1) / (mt * kWTile)) * ((N + kWTile - 1) / kWTile);
+  const bool narrow = 2 * tiles128 <= ogb_num_sms();
+#define OGB_W4_LAUNCH(MT_, SF_, TN_) launch_w4a16_gemm<MT_, SF_, TN_>(x, qweight, scales, zp, bias, out, M, N, K, ldx, ldc, status, stream)
+  if (mt == 2) {
+    if (narrow) return scales_f32 ? OGB_W4_LAUNCH(2, true, 64) : OGB_W4_LAUNCH(2, false, 64);
+    return scales_f32 ? OGB_W4_LAUNCH(2, true, 128) : OGB_W4_LAUNCH(2, false, 128);
   }
-  return scales_f32 ? launch_w4a16_gemm<1, true>(x, qweight, scales, zp, bias, out, M, N, K, ldx, ldc, status, stream)
-                    : launch_w4a16_gemm<1, false>(x, qweight, scales, zp, bias, out, M, N, K, ldx, ldc, status, stream);
+  if (narrow) return scales_f32 ? OGB_W4_LAUNCH(1, true, 64) : OGB_W4_LAUNCH(1, false, 64);
+  return scales_f32 ? OGB_W4_LAUNCH(1, true, 128) : OGB_W4_LAUNCH(1, false, 128);
+#undef OGB_W4_LAUNCH
 }
