@@ -860,6 +860,15 @@ extern "C" int ogb_gemm_bf16_scatter(const void* A, const void* W, int M, int N,
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (M <= 0) return 0;
   if ((K % 8) != 0 || (lda % 8) != 0 || (ldw % 8) != 0 || (N % 32) != 0 || sc == nullptr) return -3;
+  if (bn == 0) {      // OGB_TP_SCATTER_BN=128|192|256 fixes the tile width (an A/B switch for measurements)
+    static int forced = -1;
+    if (forced < 0) {
+      const char* e = getenv("OGB_TP_SCATTER_BN");
+      forced = e != nullptr ? atoi(e) : 0;
+      if (forced != 128 && forced != 192 && forced != 256) forced = 0;
+    }
+    bn = forced;
+  }
   if (bn == 0) {
     const int m_tiles = (M + kBM - 1) / kBM;
     const int sms = ogb_num_sms();
