@@ -28,6 +28,7 @@ from .. import ops
 from ..models.config import DecoderConfig
 from ..models.decoder import DecoderModel, DecoderWeights, KVCache, StepInputs, random_weights
 from ..parallel.sharding import shard_heads
+from ..utils.trace import TRACER
 from .core import HDR, Core, CoreConfig
 
 
@@ -605,7 +606,15 @@ class LLMEngine:
 
     def step(self) -> StepOutput:
         """Schedule, run and commit one engine step."""
+        tracing = TRACER.enabled or TRACER.want_gpu or TRACER.nvtx is not None
+        if not tracing:
+            return self._step()
+        with TRACER.span("loop.step"):        # with its parts (loop.schedule / loop.forward / loop.commit) recorded inside
+            return self._step(True)
+
+    def _step(self, tracing: bool = False) -> StepOutput:
         out = StepOutput()
+        t_begin = time.perf_counter() if tracing else 0.0
         batches: dict = {}
         for sid, proposer in list(self.proposers.items()):   # speculative drafts for the coming step
             toks = self.core.seq_tokens(sid) if self.core.seq_len(sid) > 0 else None
@@ -630,6 +639,9 @@ class LLMEngine:
                     self.core.set_draft(sid, draft)
         self._maybe_grow_kv()
         t = self.core.build_step(self.plan_host.data_ptr())
+        if tracing:
+            t_sched = time.perf_counter()
+            TRACER.add("loop.schedule", t_begin, t_sched)
         if t <= 0:
             return out
         hdr = self.plan_np[:32]
@@ -691,6 +703,9 @@ class LLMEngine:
                     self.comm.broadcast(self.sampled_host[:r], src=self.pp - 1)
         elif self.device.type == "cuda":
             self._finish_device_step(0)
+        if tracing:                       # launches of the forward pass and the sampler, and the read-back of the sampled tokens
+            t_fwd = time.perf_counter()
+            TRACER.add("loop.forward", t_sched, t_fwd)
         if self.hidden_taps and r > 0:
             # embeddings: the final-normed hidden state of a tapped request's last prompt token
             seq_of_row = self.plan_np[self.L.logit_seq:self.L.logit_seq + r]
@@ -740,6 +755,8 @@ class LLMEngine:
             if fin is not None:
                 st.finished, st.finish_reason = now, fin
         self.steps += 1
+        if tracing:
+            TRACER.add("loop.commit", t_fwd, time.perf_counter())
         out.events, out.num_tokens, out.num_decode = events, t, si.num_decode
         out.num_prefill_tokens = int(hdr[HDR["num_prefill_tokens"]])
         return out

@@ -64,6 +64,8 @@ class Tracer:
         self.gpu = None
         self.gpu_error = ""
         self.want_gpu = os.environ.get("ONNX_GENAI_TRACE_CUPTI", "0") not in ("", "0")
+        if self.enabled:                     # ONNX_GENAI_TRACE=<path>: the file is written when the process exits
+            self._flush_at_exit()
 
     def _start_gpu(self):
         self.want_gpu = False
@@ -89,6 +91,20 @@ class Tracer:
 
     def start(self, path):
         self.path, self.enabled = path, True
+        self._flush_at_exit()
+
+    def add(self, name, t0, t1, cat="engine"):
+        """Record a span whose ends the caller timed itself (``time.perf_counter()`` seconds)."""
+        if self.enabled:
+            with self.lock:
+                self.spans.append((name, t0, t1, cat))
+
+    def _flush_at_exit(self):
+        if not getattr(self, "_exit_hook", False):
+            import atexit
+
+            atexit.register(self.flush)
+            self._exit_hook = True
 
     def span(self, name, cat="engine"):
         tracer = self
